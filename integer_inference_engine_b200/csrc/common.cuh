@@ -1,0 +1,136 @@
+// Shared device helpers for the integer MoE kernels (sm_100a).
+//
+// Numerics contract (north-mini-code/src/nmc/cohere2.py:97-111, qk_codec.py:54-90):
+//   activations are int64 at scale 2^fa, weights are int64 at scale 2^fw derived from raw Q4_K/Q6_K
+//   blocks, a linear is one floor shift after an exact full-K sum.  Everything here is exact integer
+//   arithmetic; no fast-math, no floating point.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace iie {
+
+typedef __int128 i128;
+typedef unsigned __int128 u128;
+
+constexpr int QT_Q4K = 0;
+constexpr int QT_Q6K = 1;
+constexpr int QT_I64 = 2;          // dense int64 rows (norm gains, dense routers)
+
+// Bytes of one repacked 8-row x 256-column tile ("half-tile block"); equal to 8 raw blocks.
+constexpr int HTB_Q4K = 8 * 144;   // 1152
+constexpr int HTB_Q6K = 8 * 210;   // 1680
+
+__host__ __device__ inline int htb_bytes(int qtype) { return qtype == QT_Q4K ? HTB_Q4K : HTB_Q6K; }
+
+// round_half_even(half * 2^frac) with integers only.  Every finite half is m * 2^e with an 11-bit
+// m, so the product is a shift; a right shift rounds half to even.  Replaces the double + llrint
+// conversion of north-mini-code/tools/nmc_qk_kernel.c:16-39 (same values for all finite halves).
+__host__ __device__ inline int64_t half_to_fixed(uint32_t h, int frac) {
+    int64_t m = h & 0x3FF;
+    int e = (h >> 10) & 0x1F;
+    if (e == 0) e = -24; else { m |= 0x400; e -= 25; }
+    e += frac;
+    int64_t v;
+    if (e >= 0) v = (int64_t)((uint64_t)m << (e > 52 ? 52 : e));
+    else {
+        int s = -e; if (s > 40) s = 40;
+        int64_t q = m >> s, rem = m & (((int64_t)1 << s) - 1), half = (int64_t)1 << (s - 1);
+        v = q + ((rem > half) || (rem == half && (q & 1)));
+    }
+    return (h & 0x8000) ? -v : v;
+}
+
+// ---- integer sigmoid / SiLU (north-mini-code/src/nmc/_bonsai/fixedpoint.py:74-96,136-163) ----------
+__device__ __forceinline__ int64_t exp2_neg_fixed(int64_t u, int fa) {
+    const int s = 16 - fa;
+    int64_t c0 = 65536, c1 = 45426, c2 = 15743, c3 = 3638;
+    if (s >= 0) { c0 >>= s; c1 >>= s; c2 >>= s; c3 >>= s; } else { c0 <<= -s; c1 <<= -s; c2 <<= -s; c3 <<= -s; }
+    const int64_t k = u >> fa, f = u & (((int64_t)1 << fa) - 1);
+    const int64_t f2 = (f * f) >> fa, f3 = (f2 * f) >> fa;
+    int64_t p = c0 - ((c1 * f) >> fa) + ((c2 * f2) >> fa) - ((c3 * f3) >> fa);
+    if (p < 0) p = 0;
+    return p >> (k < 63 ? k : 63);
+}
+
+__device__ __forceinline__ int64_t sigmoid_fixed(int64_t x, int fa) {
+    const int s = 16 - fa;
+    const int64_t log2e = s >= 0 ? ((int64_t)94548 >> s) : ((int64_t)94548 << -s);
+    const int64_t clip = (((int64_t)(fa + 2)) << (2 * fa)) / log2e;
+    const int64_t m = x > 0 ? x : 0;
+    const int64_t d0 = m < clip ? m : clip;
+    // the NumPy oracle evaluates m - x and d * log2e in wrapping int64 (only x = INT64_MIN wraps)
+    int64_t d1 = (int64_t)((uint64_t)m - (uint64_t)x);
+    if (d1 > clip) d1 = clip;
+    const int64_t e0 = exp2_neg_fixed((d0 * log2e) >> fa, fa);
+    const int64_t e1 = exp2_neg_fixed((int64_t)((uint64_t)d1 * (uint64_t)log2e) >> fa, fa);
+    const int64_t z = e0 + e1;          // e0, e1 <= 2^fa, fa <= 29: the quotient below fits 64 bits
+    return z == 0 ? 0 : (int64_t)(((uint64_t)e1 << fa) / (uint64_t)z);
+}
+
+__device__ __forceinline__ int64_t mul_shift(int64_t a, int64_t b, int sh) {
+    return (int64_t)(((i128)a * (i128)b) >> sh);
+}
+
+__device__ __forceinline__ int64_t silu_fixed(int64_t x, int fa) { return mul_shift(x, sigmoid_fixed(x, fa), fa); }
+
+// ---- balanced base-256 digits: x = sum_l d_l * 256^l, d_l in [-128,127] --------------------------------
+// Eight digits cover |x| <= 127*(2^64-1)/255; `ok` is cleared when a ninth digit would be needed
+// (capacity rule of north-mini-code/src/nmc/qk_cuda.py:973-992).
+__device__ __forceinline__ uint64_t balanced_digits8(int64_t x, bool &ok) {
+    uint64_t packed = 0;
+#pragma unroll
+    for (int l = 0; l < 8; l++) {
+        const int64_t d = (int64_t)(int8_t)(x & 0xFF);
+        packed |= (uint64_t)(uint8_t)d << (8 * l);
+        x = (x - d) >> 8;
+    }
+    ok = (x == 0);
+    return packed;
+}
+
+// ---- warp-level integer MMA (legacy tensor path; the decode kernels are HBM-bound) ---------------------
+// D(16x8,s32) += A(16x32,u8,row) * B(32x8,s8,col)
+__device__ __forceinline__ void mma_u8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// D(16x8,s32) += A(16x16,s8,row) * B(16x8,s8,col)
+__device__ __forceinline__ void mma_s8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+}
+// D(16x8,s32) += A(16x32,s8,row) * B(32x8,s8,col)
+__device__ __forceinline__ void mma_s8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg128(const void *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
+__device__ __forceinline__ uint2 ldg64(const void *p) { return __ldg(reinterpret_cast<const uint2 *>(p)); }
+__device__ __forceinline__ uint32_t ldg32(const void *p) { return __ldg(reinterpret_cast<const uint32_t *>(p)); }
+
+// Streaming (read-once) 128-bit load that does not pollute L1.
+__device__ __forceinline__ uint4 ldg128_stream(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// Unpack the 12 packed scale bytes of a Q4_K block (three words) into byte-packed 6-bit values:
+// sc_lo/mn_lo hold sub-blocks 0..3, sc_hi/mn_hi hold 4..7 (qk_codec.py:28-35).
+__device__ __forceinline__ void q4k_scales(uint32_t u0, uint32_t u1, uint32_t u2, uint32_t &sc_lo, uint32_t &sc_hi,
+                                           uint32_t &mn_lo, uint32_t &mn_hi) {
+    sc_lo = u0 & 0x3f3f3f3fu;
+    mn_lo = u1 & 0x3f3f3f3fu;
+    sc_hi = (u2 & 0x0f0f0f0fu) | ((u0 >> 2) & 0x30303030u);
+    mn_hi = ((u2 >> 4) & 0x0f0f0f0fu) | ((u1 >> 2) & 0x30303030u);
+}
+
+}  // namespace iie

@@ -1,0 +1,71 @@
+// Host-callable launchers of the CUDA kernels (internal interface between the .cu files).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace iie {
+
+enum SkinnyMode { MODE_LINEAR = 0, MODE_GATEUP = 1, MODE_DOWN = 2 };
+
+// Arguments of the streamed ("skinny") fused-dequant product.  Work is organised in groups: group g
+// uses weight matrix `expert = grp_expert ? grp_expert[g] : g` and owns the activation rows
+// ("pairs") [grp_off[g], grp_off[g+1]) (grp_off == nullptr: every group owns exactly pair g... see
+// `pairs_per_group`).
+struct SkinnyArgs {
+    const uint8_t *const *wa;      // per expert: repacked weight (stream A: linear/down weight, or gate)
+    const uint8_t *const *wb;      // per expert: stream B (up weight) for MODE_GATEUP, else unused
+    const int *grp_expert;         // [n_groups] or nullptr (identity)
+    const int *grp_off;            // [n_groups+1] or nullptr (group g owns pairs [g*ppg, (g+1)*ppg))
+    int pairs_per_group;           // used when grp_off == nullptr
+    long long out_f;               // output rows of the weight matrix
+    long long n_blocks;            // 256-column super-blocks per row
+    int fw, fa;
+    const int8_t *xl;              // activation limb planes [x_row][8][K]
+    const int *xidx;               // pair -> x_row, or nullptr (identity)
+    int64_t *out;                  // LINEAR: [pair][out_f]; GATEUP: gu [pair][out_f]; DOWN: [token][out_f] accumulated
+    int8_t *out_limbs;             // GATEUP: limb planes of gu [pair][8][out_f] (nullable)
+    const int64_t *gates;          // DOWN: per-pair gate weight
+    const int *pair_tok;           // DOWN: pair -> token row of `out`, or nullptr (token 0)
+    int *flags;                    // bit 0: a value left the 8-limb envelope
+};
+
+cudaError_t launch_skinny(int qtype, int mode, const SkinnyArgs &a, int n_groups, int max_pairs_per_group,
+                          cudaStream_t s);
+
+// Re-order raw GGUF blocks into the half-tile layout; also reduces max |d| and max |dmin| half bit
+// patterns (sign stripped) into maxbits[0..1] (device memory, caller zeroes).
+cudaError_t launch_repack(const uint8_t *raw, uint8_t *dst, long long out_f, long long n_blocks, int qtype,
+                          unsigned *maxbits, cudaStream_t s);
+// Inverse of launch_repack (used by tests and by weight export).
+cudaError_t launch_unpack(const uint8_t *src, uint8_t *raw, long long out_f, long long n_blocks, int qtype,
+                          cudaStream_t s);
+
+// int64 rows -> balanced base-256 limb planes [row][8][K]; sets flags bit 0 on overflow.
+cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, cudaStream_t s);
+
+// Exact 128-bit reference-order product for inputs outside the fast envelope: out[pair][o].
+cudaError_t launch_exact_linear(const uint8_t *w, int qtype, long long out_f, long long n_blocks, const int64_t *x,
+                                long long T, int fw, int64_t *out, cudaStream_t s);
+cudaError_t launch_exact_dense(const int64_t *w, long long out_f, long long in_f, const int64_t *x, long long T,
+                               int fw, int64_t *out, int *flags, cudaStream_t s);
+
+// a[i] = (silu(a[i]) * b[i]) >> fa
+cudaError_t launch_silu_mul(int64_t *a, const int64_t *b, long long n, int fa, cudaStream_t s);
+// out[t][o] (+)= sum_j (dn[(t*k+j)][o] * gates[t*k+j]) >> fa
+cudaError_t launch_combine(const int64_t *dn, const int64_t *gates, long long T, int k, long long d_model, int fa,
+                           int64_t *out, cudaStream_t s);
+
+// Top-k (descending, lowest index on ties) + sigmoid gates; one warp per row.  n_experts <= 1024.
+cudaError_t launch_topk(const int64_t *logits, long long rows, int n_experts, int k, int fa, int *ids,
+                        int64_t *gates, cudaStream_t s);
+
+// Integer RMSNorm with optional gain; flags bit 1 set when a row leaves the exact envelope.
+cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
+                           unsigned long long eps, int64_t *out, int *flags, cudaStream_t s);
+
+// Counting-sort dispatch of (token, slot) pairs by expert.
+//   ids [T*k] -> grp_off [E+1], pair_tok [T*k], pair_src [T*k] (index t*k+j of each sorted pair)
+cudaError_t launch_dispatch(const int *ids, long long T, int k, int n_experts, int *grp_off, int *pair_tok,
+                            int *pair_src, int *cursor_scratch, cudaStream_t s);
+
+}  // namespace iie

@@ -1,0 +1,154 @@
+"""Regenerate the golden vectors in this directory from the reference project's own Python code.
+
+Run where the reference tree is mounted (default /root/reference, override with
+IIE_REFERENCE_ROOT):
+
+    python tests/golden/make_golden.py
+
+Inputs come from the seeded generators in ``oracle/qk_oracle.py`` (so the fixtures only need to
+store seeds and outputs); outputs come from the reference's modules ``nmc.qk_codec``,
+``nmc.cohere2``, ``nmc._bonsai.fixedpoint`` and ``trinote.infer_int.reference_bonsai``.  The test
+``tests/test_oracle_golden.py`` replays the same seeds through this repository's oracle and
+compares bytes, which pins the oracle to the reference without the reference being present.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parents[1]
+REF = Path(os.environ.get("IIE_REFERENCE_ROOT", "/root/reference"))
+sys.path.insert(0, str(REF / "north-mini-code" / "src"))
+sys.path.insert(0, str(REF / "bonsai" / "src"))
+sys.path.insert(0, str(ROOT))
+
+from nmc import cohere2 as c2                        # noqa: E402
+from nmc import qk_codec as rq                       # noqa: E402
+from nmc._bonsai import fixedpoint as rfp            # noqa: E402
+from trinote.infer_int.reference_bonsai import q1_linear_ref   # noqa: E402
+
+from oracle import qk_oracle as o                    # noqa: E402
+
+FA, FW = 16, 24
+
+
+def sha(a: np.ndarray) -> str:
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def ref_dequant(raw, out_f, nb, qtype, frac):
+    fn = rq.dequant_q4k_tensor if qtype == 0 else rq.dequant_q6k_tensor
+    return fn(raw, out_f * nb * 256, frac).reshape(out_f, nb * 256)
+
+
+def half_fixture():
+    bits = np.arange(65536, dtype=np.uint16)
+    bits = bits[((bits >> 10) & 31) != 31]
+    out = {}
+    for frac in (24, 16, 11):
+        v = np.array([int(round(float(h) * (1 << frac))) for h in bits.view(np.float16)], dtype=np.int64)
+        out[f"sha_{frac}"] = sha(v)
+        out[f"sample_{frac}"] = v[::251]
+    return out
+
+
+def codec_fixture():
+    out = {}
+    for seed in (0, 1):
+        rng = np.random.default_rng(100 + seed)
+        r4, r6 = o.synth_q4k(rng, 3, 2), o.synth_q6k(rng, 3, 2)
+        out[f"q4k_{seed}"] = ref_dequant(r4, 3, 2, 0, FW)
+        out[f"q6k_{seed}"] = ref_dequant(r6, 3, 2, 1, FW)
+        out[f"q4k_f16_{seed}"] = ref_dequant(r4, 3, 2, 0, 16)
+    # the reference's own block generators, scalar decoder
+    b4, b6 = rq.random_q4k(7), rq.random_q6k(7)
+    out["ref_q4k_raw"] = np.frombuffer(np.float16(b4["d"]).tobytes() + np.float16(b4["dmin"]).tobytes()
+                                       + b4["scales"].tobytes() + b4["qs"].tobytes(), np.uint8)
+    out["ref_q4k_int"] = rq.dequant_q4k_int(**b4, frac=FW)
+    out["ref_q6k_raw"] = np.frombuffer(b6["ql"].tobytes() + b6["qh"].tobytes() + b6["scales"].tobytes()
+                                       + np.float16(b6["d"]).tobytes(), np.uint8)
+    out["ref_q6k_int"] = rq.dequant_q6k_int(**b6, frac=FW)
+    return out
+
+
+def linear_fixture():
+    out = {}
+    for i, (qt, out_f, nb, T, magbits) in enumerate(LINEAR_CASES):
+        rng = np.random.default_rng(200 + i)
+        raw = (o.synth_q4k if qt == 0 else o.synth_q6k)(rng, out_f, nb)
+        x = rng.integers(-(1 << magbits), 1 << magbits, size=(T, nb * 256), dtype=np.int64)
+        out[f"y_{i}"] = c2.linear(x, ref_dequant(raw, out_f, nb, qt, FW), FW)
+    return out
+
+
+def scalar_fixture():
+    rng = np.random.default_rng(300)
+    x = np.concatenate([rng.integers(-(1 << 22), 1 << 22, size=4000), rng.integers(-(1 << 40), 1 << 40, size=500),
+                        np.array([0, 1, -1, 65536, -65536, (1 << 62), -(1 << 62), np.iinfo(np.int64).max,
+                                  np.iinfo(np.int64).min, 851968, -851968, 851967])]).astype(np.int64)
+    safe = x[np.abs(x.astype(object)) < (1 << 46)].astype(np.int64)
+    xx = rng.integers(-(1 << 18), 1 << 18, size=(3, 256), dtype=np.int64)
+    g = rng.integers(1 << 15, 1 << 17, size=256, dtype=np.int64)
+    lg = rng.integers(-4, 4, size=(12, 16), dtype=np.int64)
+    return {"x": x, "sigmoid": rfp.fixed_point_sigmoid(x, FA), "sigmoid_f20": rfp.fixed_point_sigmoid(x, 20),
+            "silu_x": safe, "silu": c2.silu_int(safe, FA),
+            "rms_x": xx, "rms_g": g, "rms": rfp.fixed_point_rmsnorm(xx, FA, 1, gain_q=g),
+            "topk_logits": lg, "topk": np.stack([c2._topk_lowidx(r, 5) for r in lg])}
+
+
+class _LazyExperts:
+    """Dequantise an expert's matrix with the reference codec only when the router selects it."""
+    def __init__(self, raws, out_f, nb, qt): self.raws, self.out_f, self.nb, self.qt = raws, out_f, nb, qt
+    def __getitem__(self, e): return ref_dequant(self.raws[e], self.out_f, self.nb, self.qt, FW)
+
+
+synth_moe = o.synth_moe
+LINEAR_CASES = o.GOLDEN_LINEAR_CASES
+
+
+MOE_CASES = o.GOLDEN_MOE_CASES
+
+
+def moe_fixture():
+    out = {}
+    for name, (seed, d, eff, E, k, T) in MOE_CASES.items():
+        router, gate, up, down, h = synth_moe(seed, d, eff, E, T)
+        cfg = c2.Cfg(d_model=d, n_heads=1, n_kv=1, head_dim=d, ffn=eff, vocab=1, n_experts=E, n_used=k,
+                     expert_ffn=eff, fa=FA, fw=FW)
+        We = {"router": ref_dequant(router, E, d // 256, 0, FW), "gate": _LazyExperts(gate, eff, d // 256, 0),
+              "up": _LazyExperts(up, eff, d // 256, 0), "down": _LazyExperts(down, d, eff // 256, 1)}
+        logits = c2.linear(h, We["router"], FW)
+        out[f"{name}_ids"] = np.stack([c2._topk_lowidx(r, k) for r in logits]).astype(np.int32)
+        out[f"{name}_out"] = c2.moe_layer_int(h, We, cfg)
+        print(name, "done", flush=True)
+    return out
+
+
+def q1_fixture():
+    out = {}
+    for i, (out_f, nb, T, magbits) in enumerate([(7, 3, 1, 20), (7, 3, 3, 20), (16, 2, 2, 62)]):
+        rng = np.random.default_rng(500 + i)
+        bits, scale = o.synth_q1(rng, out_f, nb)
+        if magbits > 40:
+            scale = rng.integers(-(1 << 40), 1 << 40, size=scale.shape, dtype=np.int64)
+        x = rng.integers(-(1 << magbits), 1 << magbits, size=(T, nb * 128), dtype=np.int64)
+        out[f"y_{i}"] = q1_linear_ref(x, bits, scale, 16)
+    return out
+
+
+def main():
+    np.savez_compressed(HERE / "half_fixed.npz", **half_fixture())
+    np.savez_compressed(HERE / "codec.npz", **codec_fixture())
+    np.savez_compressed(HERE / "linear.npz", **linear_fixture())
+    np.savez_compressed(HERE / "scalar.npz", **scalar_fixture())
+    np.savez_compressed(HERE / "q1.npz", **q1_fixture())
+    np.savez_compressed(HERE / "moe.npz", **moe_fixture())
+
+
+if __name__ == "__main__":
+    main()
