@@ -1,0 +1,138 @@
+/* C-ABI of libnmc_qk_cuda.so: the B200 (sm_100a) producer of the integer MoE block and the fused
+ * Q4_K/Q6_K-dequant integer matmul.
+ *
+ * Part 1 declares the entry points the reference's ctypes bridge binds (north-mini-code/src/nmc/
+ * qk_cuda.py:39-72 lists the required names, :110-214 their argument types); each declaration cites
+ * the reference definition it replaces (file:line in north-mini-code/tools/nmc_qk_cuda.cu).  All
+ * pointers in part 1 are HOST pointers owned by the caller for the duration of the call; results
+ * are byte-identical to the reference CPU oracle.  Return codes: 0 ok, 1 bad argument / runtime
+ * failure, 2 wrong quantisation type for a type-specific entry, 3 input outside the exact envelope
+ * (caller falls back to its host path).
+ *
+ * Part 2 declares additive device-pointer entry points (no counterpart in the reference) so that a
+ * caller holding tensors in device memory (e.g. PyTorch) never bounces through the host.
+ *
+ * qtype: 0 = Q4_K (144-byte blocks), 1 = Q6_K (210-byte blocks), 2 = dense int64 (register_i64).
+ */
+#ifndef IIE_QK_H
+#define IIE_QK_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------------
+ * Part 1: reference ABI v5
+ * ---------------------------------------------------------------------------------------------- */
+int qk_cuda_abi_version(void);                       /* nmc_qk_cuda.cu:755  returns 5 */
+int qk_cuda_available(void);                         /* nmc_qk_cuda.cu:2348 0 = a usable GPU is present */
+
+/* out[t,o] = floor(sum_i W[o,i]*x[t,i] / 2^fw) from raw blocks.               nmc_qk_cuda.cu:720 */
+int qk_linear_cuda(const uint8_t *W, const int64_t *x, long long T, long long out_f, long long n_blocks,
+                   int fw, int qtype, int64_t *out);
+
+/* Resident weights: handle >= 0, or -1.                                        nmc_qk_cuda.cu:1040-1108 */
+int qk_resident_reserve(long long count);
+long long qk_register_weight(const uint8_t *W, long long out_f, long long n_blocks, int qtype);
+long long qk_register_i64(const int64_t *W, long long rows, long long cols);
+long long qk_resident_count(void);                   /* nmc_qk_cuda.cu:1805 */
+long long qk_resident_capacity(void);                /* nmc_qk_cuda.cu:1806 */
+void qk_free_all(void);                              /* nmc_qk_cuda.cu:1783 */
+
+/* nmc_qk_cuda.cu:1252 */
+int qk_apply_resident(long long h, const int64_t *x, long long T, int fw, int64_t *out);
+/* Same input through up to 16 weights, outputs concatenated in handle order.   nmc_qk_cuda.cu:1284 */
+int qk_apply_resident_grouped(const long long *handles, const int *phase_ids, int count, const int64_t *x,
+                              long long T, int fw, long long output_capacity, int64_t *out);
+/* Type-specific applies (rc 2 on the other type); Ln is accepted and ignored: the eight-limb
+ * decomposition used here is exact for every magnitude the limb rule admits.   nmc_qk_cuda.cu:1932,2003 */
+int qk_apply_resident_q6k_dp4a(long long h, const int64_t *x, long long T, int fw, int Ln, int64_t *out);
+int qk_apply_resident_q4k_dp4a(long long h, const int64_t *x, long long T, int fw, int Ln, int64_t *out);
+
+/* RMSNorm -> dense int64 router -> top-k (low index on ties) -> sigmoid gates.  nmc_qk_cuda.cu:1116 */
+int qk_rmsnorm_router(long long gain_h, long long router_h, const int64_t *x, long long rows, int fa, int fw,
+                      unsigned long long eps, int used, long long h_capacity, long long route_capacity,
+                      int64_t *h_out, int *ids_out, int64_t *gates_out);
+
+/* Decode MoE FFN on one token over n_e selected experts.                       nmc_qk_cuda.cu:1816,2110 */
+int qk_moe_ffn(const long long *gate_h, const long long *up_h, const long long *down_h, int n_e, const int64_t *h,
+               const int64_t *gates, long long d_model, long long e_ffn, int fa, int fw, int64_t *out);
+int qk_moe_ffn_dp4a(const long long *gate_h, const long long *up_h, const long long *down_h, int n_e,
+                    const int64_t *h, const int64_t *gates, long long d_model, long long e_ffn, int fa, int fw,
+                    int64_t *out);
+/* Batched MoE FFN over m*k (token, expert) pairs, token-major handles.         nmc_qk_cuda.cu:2203,2261 */
+int qk_moe_ffn_batched(const long long *gate_h, const long long *up_h, const long long *down_h, int m, int k,
+                       const int64_t *h, const int64_t *gates, long long d_model, long long e_ffn, int fa, int fw,
+                       int64_t *out);
+int qk_moe_ffn_batched_dp4a(const long long *gate_h, const long long *up_h, const long long *down_h, int m, int k,
+                            const int64_t *h, const int64_t *gates, long long d_model, long long e_ffn, int fa,
+                            int fw, int64_t *out);
+
+long long qk_moe_workspace_allocations(void);        /* nmc_qk_cuda.cu:1807 */
+unsigned long long qk_moe_workspace_bytes(void);     /* nmc_qk_cuda.cu:1808 */
+void qk_moe_workspace_release(void);                 /* nmc_qk_cuda.cu:1223 */
+
+void qk_profile_reset(void);                         /* nmc_qk_cuda.cu:82 */
+void qk_profile_set_enabled(int enabled);            /* nmc_qk_cuda.cu:85 */
+int qk_profile_snapshot(unsigned long long *out, int capacity);   /* nmc_qk_cuda.cu:86, 28 counters */
+
+/* Request-scoped attention bank (decode attention sublayer and the retained-layer executor).
+ * Present so that the reference bridge accepts the library; the attention sublayer is outside
+ * the MoE hot path and these entries report failure (create returns -1, the others rc 1).
+ *                                              nmc_qk_cuda.cu:877,914,927,935,984,1363,1530,1557,1658,1748,1765 */
+long long qk_attention_bank_create(int n_layers, long long max_length, long long d_model, int heads, int n_kv,
+                                   int head_dim, int fa, const int64_t *cos, const int64_t *sin);
+int qk_attention_bank_reset(long long h);
+void qk_attention_bank_destroy(long long h);
+int qk_attention_bank_moe_configure(long long h, int layer, int experts, int used, long long d_model,
+                                    long long expert_ffn);
+int qk_attention_bank_moe_bind(long long h, int layer, int expert, long long gate_h, long long up_h,
+                               long long down_h);
+int qk_attention_bank_import(long long h, int layer, const int64_t *k, const int64_t *v, long long length);
+int qk_attention_bank_apply(long long h, int layer, long long qh, long long kh, long long vh, long long oh,
+                            const int64_t *x, int fw, int rope, int window, long long start,
+                            long long output_capacity, int64_t *out);
+int qk_attention_bank_moe_begin(long long h, int layer, long long gain_h, long long router_h, long long qh,
+                                long long kh, long long vh, long long oh, const int64_t *x, int fw, int rope,
+                                unsigned long long eps, int window, int used, long long start, int cold_capacity,
+                                int *cold_ids, int *cold_count);
+int qk_attention_bank_moe_continue(long long h, int layer, int fw, int publish, long long output_capacity,
+                                   int64_t *out);
+int qk_attention_bank_moe_export(long long h, long long output_capacity, int64_t *out);
+unsigned long long qk_attention_bank_workspace_bytes(long long h);
+
+/* ------------------------------------------------------------------------------------------------
+ * Part 2: device-pointer extension (additive)
+ * ---------------------------------------------------------------------------------------------- */
+/* Register a weight whose raw blocks already sit in device memory (copied and re-ordered). */
+long long iie_register_weight_dev(const void *raw_dev, long long out_f, long long n_blocks, int qtype);
+/* Copy a registered weight back to the host in raw GGUF block order (out_f*n_blocks*{144|210} bytes). */
+int iie_weight_export(long long h, void *raw_host);
+
+/* One MoE layer with all experts resident: router handle (Q4_K/Q6_K or dense int64) plus
+ * n_experts gate/up/down handles.  Returns a layer handle >= 0, or -1. */
+long long iie_moe_layer_create(long long router_h, const long long *gate_h, const long long *up_h,
+                               const long long *down_h, int n_experts, int top_k, long long d_model,
+                               long long e_ffn);
+void iie_moe_layer_destroy(long long layer);
+
+/* Whole MoE block on device tensors, asynchronous on `stream` (a cudaStream_t; NULL = the library
+ * stream): router product, top-k + sigmoid gates, dispatch, gate/up with fused SiLU*up, down with
+ * fused gate-weighted combine.  h_dev [T,d_model] int64 -> out_dev [T,d_model] int64 (overwritten,
+ * or added to when accumulate != 0), ids_dev [T,top_k] int32, gates_dev [T,top_k] int64 (the last
+ * two may be NULL).  Inputs outside the exact envelope raise bits in the flag word. */
+int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long long T, int fa, int fw, int accumulate,
+                        int64_t *out_dev, int *ids_dev, int64_t *gates_dev, void *stream);
+
+/* Plain resident product on device tensors: out_dev [T,out_f] = floor(x_dev W^T / 2^fw). */
+int iie_apply_dev(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev, void *stream);
+
+/* Read and clear the device flag word (synchronises the library stream and `stream`):
+ * bit 0 an activation left the 8-limb envelope, bit 1 RMSNorm envelope, bit 2 dense router sum. */
+int iie_flags_read_clear(void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,660 @@
+// C-ABI of the library: weight registry, workspaces, profile counters and the exported entry
+// points declared in include/iie_qk.h.  Host pointers cross the boundary in part 1 (the reference's
+// ABI v5); part 2 takes device pointers.  No torch types, no exceptions across the boundary.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <algorithm>
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <vector>
+
+#include "../../include/iie_qk.h"
+#include "kernels.h"
+#include "layout.cuh"
+
+using namespace iie;
+
+namespace {
+
+// ---- profile counters (order of north-mini-code/src/nmc/qk_cuda.py:24-34) ----------------------------------
+enum Metric {
+    PM_REG_CALLS, PM_REG_NS, PM_H2D_CALLS, PM_H2D_BYTES, PM_H2D_NS, PM_D2H_CALLS, PM_D2H_BYTES, PM_D2H_NS,
+    PM_ALLOC_CALLS, PM_ALLOC_BYTES, PM_ALLOC_NS, PM_FREE_CALLS, PM_NATIVE_CALLS, PM_RESIDENT_APPLY, PM_GROUPED_APPLY,
+    PM_MOE, PM_MOE_BATCHED, PM_MOE_BATCHED_DP4A, PM_Q_CALLS, PM_Q_NS, PM_K_CALLS, PM_K_NS, PM_V_CALLS, PM_V_NS,
+    PM_O_CALLS, PM_O_NS, PM_OTHER_CALLS, PM_OTHER_NS, PM_COUNT
+};
+unsigned long long g_prof[PM_COUNT];
+int g_prof_on = 0;
+inline void prof(int m, unsigned long long v = 1) { if (g_prof_on) __atomic_fetch_add(&g_prof[m], v, __ATOMIC_RELAXED); }
+
+struct Weight {
+    void *d = nullptr;
+    long long out_f = 0, nb = 0;       // dense int64: rows, cols
+    int qtype = 0;
+    size_t bytes = 0;
+    unsigned maxd = 0, maxdmin = 0;    // largest |d| / |dmin| half bit patterns
+    const uint8_t **cell = nullptr;    // device cell holding `d` (a one-entry pointer table for the kernels)
+    bool live = false;
+};
+
+struct MoeLayer {
+    long long router = -1;
+    int n_experts = 0, top_k = 0;
+    long long d_model = 0, e_ffn = 0;
+    int gate_q = 0, down_q = 0;
+    const uint8_t **tabs = nullptr;    // device: [3][n_experts] gate, up, down pointers
+    unsigned maxd_gate = 0, maxdmin_gate = 0, maxd_down = 0, maxdmin_down = 0;
+    bool live = false;
+};
+
+std::recursive_mutex g_mu;
+std::vector<Weight> g_w;
+std::vector<MoeLayer> g_layers;
+cudaStream_t g_stream = nullptr;
+int *g_flags = nullptr;               // device flag word
+int g_ready = -1;                     // -1 unknown, 0 usable, 1 unusable
+
+// Persistent device scratch by role, grown on demand (never shrunk until released).
+enum Role { R_X, R_XL, R_OUT, R_RAW, R_GU, R_GUL, R_TMP0, R_TMP1, R_TMP2, R_TABS, R_META, R_LOGITS, R_IDS, R_GATES,
+            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_COUNT };
+struct Buf { void *p = nullptr; size_t cap = 0; };
+Buf g_buf[R_COUNT];
+long long g_ws_allocs = 0;
+
+bool init() {
+    if (g_ready >= 0) return g_ready == 0;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) { cudaGetLastError(); g_ready = 1; return false; }
+    if (cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaMalloc(&g_flags, sizeof(int)) != cudaSuccess || cudaMemset(g_flags, 0, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError(); g_ready = 1; return false;
+    }
+    g_ready = 0;
+    return true;
+}
+
+void *ensure(int role, size_t bytes) {
+    Buf &b = g_buf[role];
+    if (b.cap >= bytes && b.p) return b.p;
+    if (b.p) { cudaStreamSynchronize(g_stream); cudaFree(b.p); prof(PM_FREE_CALLS); b.p = nullptr; b.cap = 0; }
+    size_t cap = std::max<size_t>(bytes, 256);
+    if (cudaMalloc(&b.p, cap) != cudaSuccess) { cudaGetLastError(); b.p = nullptr; return nullptr; }
+    b.cap = cap; g_ws_allocs++;
+    prof(PM_ALLOC_CALLS); prof(PM_ALLOC_BYTES, cap);
+    return b.p;
+}
+
+void release_workspace() {
+    if (g_stream) cudaStreamSynchronize(g_stream);
+    for (auto &b : g_buf) if (b.p) { cudaFree(b.p); prof(PM_FREE_CALLS); b.p = nullptr; b.cap = 0; }
+}
+
+bool h2d(void *dst, const void *src, size_t n) {
+    prof(PM_H2D_CALLS); prof(PM_H2D_BYTES, n);
+    return cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, g_stream) == cudaSuccess;
+}
+bool d2h(void *dst, const void *src, size_t n) {
+    prof(PM_D2H_CALLS); prof(PM_D2H_BYTES, n);
+    return cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, g_stream) == cudaSuccess;
+}
+bool sync() { return cudaStreamSynchronize(g_stream) == cudaSuccess; }
+
+bool valid_q(long long h) { return h >= 0 && (size_t)h < g_w.size() && g_w[h].live && g_w[h].qtype != QT_I64; }
+bool valid_i64(long long h) { return h >= 0 && (size_t)h < g_w.size() && g_w[h].live && g_w[h].qtype == QT_I64; }
+
+// Fast-path envelope of the streamed kernels (see skinny.cu): the per-limb-column int64 sums
+// cannot wrap.  Evaluated with the largest block scales of the tensor at this call's fw.
+bool fast_envelope(int qtype, long long nb, unsigned maxd, unsigned maxdmin, int fw) {
+    if (fw < 0 || fw > 36) return false;
+    if ((maxd & 0x7C00u) == 0x7C00u || (maxdmin & 0x7C00u) == 0x7C00u) return false;   // inf/nan scales
+    const unsigned __int128 dq = (unsigned __int128)half_to_fixed(maxd, fw), dm = (unsigned __int128)half_to_fixed(maxdmin, fw);
+    const unsigned __int128 lim = (unsigned __int128)1 << 62;
+    if (qtype == QT_Q4K) return (unsigned __int128)nb * ((dq << 25) + (dm << 21)) < lim;
+    return (unsigned __int128)nb * (dq << 28) < lim;
+}
+
+int read_flags_clear() {
+    int f = 0;
+    if (cudaMemcpyAsync(&f, g_flags, sizeof(int), cudaMemcpyDeviceToHost, g_stream) != cudaSuccess) return -1;
+    if (cudaMemsetAsync(g_flags, 0, sizeof(int), g_stream) != cudaSuccess) return -1;
+    if (!sync()) return -1;
+    return f;
+}
+
+long long new_slot() {                 // handles are never reused before qk_free_all
+    g_w.emplace_back();
+    return (long long)g_w.size() - 1;
+}
+
+// Upload (or take from device) raw blocks and store them repacked.  Returns handle or -1.
+long long register_quant(const void *raw, bool raw_on_device, long long out_f, long long nb, int qtype) {
+    if (!init() || !raw || out_f <= 0 || nb <= 0 || (qtype != QT_Q4K && qtype != QT_Q6K)) return -1;
+    const int bs = qtype == QT_Q4K ? 144 : 210;
+    if (out_f > (1LL << 40) / nb / bs) return -1;
+    const size_t raw_bytes = (size_t)out_f * nb * bs;
+    const size_t packed = (size_t)((out_f + 7) / 8) * 8 * nb * bs;
+    const size_t cell_off = (packed + 255) & ~(size_t)255;
+    void *d = nullptr; unsigned *mb = nullptr;
+    const uint8_t *src = (const uint8_t *)raw;
+    if (cudaMalloc(&d, cell_off + 256) != cudaSuccess) { cudaGetLastError(); return -1; }
+    prof(PM_ALLOC_CALLS); prof(PM_ALLOC_BYTES, packed);
+    bool ok = true;
+    if (!raw_on_device) {
+        void *stage = ensure(R_RAW, raw_bytes);
+        ok = stage && h2d(stage, raw, raw_bytes);
+        src = (const uint8_t *)stage;
+    }
+    mb = (unsigned *)ensure(R_META, 64);
+    unsigned hostmb[2] = {0, 0};
+    ok = ok && mb && cudaMemsetAsync(mb, 0, 8, g_stream) == cudaSuccess &&
+         cudaMemsetAsync(d, 0, packed, g_stream) == cudaSuccess &&
+         launch_repack(src, (uint8_t *)d, out_f, nb, qtype, mb, g_stream) == cudaSuccess &&
+         cudaMemcpyAsync((char *)d + cell_off, &d, sizeof(void *), cudaMemcpyHostToDevice, g_stream) == cudaSuccess &&
+         cudaMemcpyAsync(hostmb, mb, 8, cudaMemcpyDeviceToHost, g_stream) == cudaSuccess && sync();
+    if (!ok) { cudaGetLastError(); cudaFree(d); return -1; }
+    const long long h = new_slot();
+    Weight &w = g_w[h];
+    w.d = d; w.out_f = out_f; w.nb = nb; w.qtype = qtype; w.bytes = packed; w.maxd = hostmb[0]; w.maxdmin = hostmb[1];
+    w.cell = (const uint8_t **)((char *)d + cell_off); w.live = true;
+    prof(PM_REG_CALLS);
+    return h;
+}
+
+// y[T,out_f] on device from x[T,K] on device.  check_flags: synchronise and re-run the exact kernel
+// if an activation left the limb envelope (host-pointer entries); otherwise flags stay raised.
+bool linear_dev(const Weight &w, const int64_t *x, long long T, int fw, int64_t *out, bool check_flags, cudaStream_t s,
+                const int8_t *xl_ready = nullptr) {
+    const long long K = w.nb * 256;
+    if (!fast_envelope(w.qtype, w.nb, w.maxd, w.maxdmin, fw))
+        return launch_exact_linear((const uint8_t *)w.d, w.qtype, w.out_f, w.nb, x, T, fw, out, s) == cudaSuccess;
+    const int8_t *xl = xl_ready;
+    if (!xl) {
+        int8_t *buf = (int8_t *)ensure(R_XL, (size_t)T * 8 * K);
+        if (!buf || launch_limbs(x, T, K, buf, g_flags, s) != cudaSuccess) return false;
+        xl = buf;
+    }
+    SkinnyArgs a = {};
+    a.wa = w.cell; a.wb = w.cell; a.pairs_per_group = (int)T; a.out_f = w.out_f; a.n_blocks = w.nb; a.fw = fw; a.fa = 16;
+    a.xl = xl; a.out = out; a.flags = g_flags;
+    if (launch_skinny(w.qtype, MODE_LINEAR, a, 1, (int)std::min<long long>(T, 4), s) != cudaSuccess) return false;
+    if (check_flags) {
+        const int f = read_flags_clear();
+        if (f < 0) return false;
+        if (f & 1) return launch_exact_linear((const uint8_t *)w.d, w.qtype, w.out_f, w.nb, x, T, fw, out, s) == cudaSuccess;
+    }
+    return true;
+}
+
+struct MoePlan {                      // everything the fused MoE kernels need on the device
+    const uint8_t *const *gate, *const *up, *const *down;
+    int gate_q, down_q;
+    long long d_model, e_ffn;
+};
+
+// Fused path: limbs(h) -> gate/up (+SiLU*up, limbs of gu) -> down (+gate-weighted accumulate).
+// Groups: n_groups experts; grp_expert / grp_off / pair arrays as in SkinnyArgs.  n_pairs activation
+// rows of gu are produced.  out [T,d_model] must be initialised by the caller.
+bool moe_fused(const MoePlan &p, const int8_t *hl, bool x_bcast_zero, const int *xidx, const int *grp_expert,
+               const int *grp_off, int n_groups, long long n_pairs, int max_pairs, const int64_t *pair_gate,
+               const int *pair_tok, int fa, int fw, int64_t *out, cudaStream_t s) {
+    int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)n_pairs * 8 * p.e_ffn);
+    if (!gul) return false;
+    SkinnyArgs a = {};
+    a.wa = p.gate; a.wb = p.up; a.grp_expert = grp_expert; a.grp_off = grp_off; a.pairs_per_group = 1;
+    a.out_f = p.e_ffn; a.n_blocks = p.d_model / 256; a.fw = fw; a.fa = fa; a.xl = hl; a.xidx = xidx;
+    a.out = nullptr; a.out_limbs = gul; a.flags = g_flags;
+    (void)x_bcast_zero;
+    if (launch_skinny(p.gate_q, MODE_GATEUP, a, n_groups, max_pairs, s) != cudaSuccess) return false;
+    SkinnyArgs d = {};
+    d.wa = p.down; d.wb = p.down; d.grp_expert = grp_expert; d.grp_off = grp_off; d.pairs_per_group = 1;
+    d.out_f = p.d_model; d.n_blocks = p.e_ffn / 256; d.fw = fw; d.fa = fa; d.xl = gul; d.xidx = nullptr;
+    d.out = out; d.gates = pair_gate; d.pair_tok = pair_tok; d.flags = g_flags;
+    return launch_skinny(p.down_q, MODE_DOWN, d, n_groups, max_pairs, s) == cudaSuccess;
+}
+
+// Unfused exact composition for one (token, expert) pair set; used when the fast envelope fails.
+bool moe_exact_pairs(const std::vector<const Weight *> &gw, const std::vector<const Weight *> &uw,
+                     const std::vector<const Weight *> &dw, const int64_t *h_dev, const std::vector<int> &pair_tok,
+                     const int64_t *gates_dev, long long T, int k, long long d_model, long long e_ffn, int fa, int fw,
+                     int64_t *out_dev) {
+    const size_t P = gw.size();
+    int64_t *g = (int64_t *)ensure(R_TMP0, P * e_ffn * 8), *u = (int64_t *)ensure(R_TMP1, P * e_ffn * 8);
+    int64_t *dn = (int64_t *)ensure(R_TMP2, P * d_model * 8);
+    if (!g || !u || !dn) return false;
+    for (size_t i = 0; i < P; i++) {
+        const int64_t *x = h_dev + (size_t)pair_tok[i] * d_model;
+        if (launch_exact_linear((const uint8_t *)gw[i]->d, gw[i]->qtype, e_ffn, gw[i]->nb, x, 1, fw, g + i * e_ffn, g_stream) != cudaSuccess ||
+            launch_exact_linear((const uint8_t *)uw[i]->d, uw[i]->qtype, e_ffn, uw[i]->nb, x, 1, fw, u + i * e_ffn, g_stream) != cudaSuccess)
+            return false;
+    }
+    if (launch_silu_mul(g, u, (long long)P * e_ffn, fa, g_stream) != cudaSuccess) return false;
+    for (size_t i = 0; i < P; i++)
+        if (launch_exact_linear((const uint8_t *)dw[i]->d, dw[i]->qtype, d_model, dw[i]->nb, g + i * e_ffn, 1, fw,
+                                dn + i * d_model, g_stream) != cudaSuccess) return false;
+    return launch_combine(dn, gates_dev, T, k, d_model, fa, out_dev, g_stream) == cudaSuccess;
+}
+
+// Shared implementation of qk_moe_ffn (m = 1, k = n_e) and qk_moe_ffn_batched.
+int moe_host_entry(const long long *gate_h, const long long *up_h, const long long *down_h, int m, int k,
+                   const int64_t *h, const int64_t *gates, long long d_model, long long e_ffn, int fa, int fw,
+                   int64_t *out) {
+    if (!init() || !gate_h || !up_h || !down_h || !h || !gates || !out || m <= 0 || k <= 0 || d_model <= 0 ||
+        e_ffn <= 0 || d_model % 256 || e_ffn % 256 || fa < 1 || fa > 29 || fw < 0 || fw > 62) return 1;
+    const size_t P = (size_t)m * k;
+    std::vector<const Weight *> gw(P), uw(P), dw(P);
+    bool uniform = true;
+    for (size_t i = 0; i < P; i++) {
+        if (!valid_q(gate_h[i]) || !valid_q(up_h[i]) || !valid_q(down_h[i])) return 1;
+        gw[i] = &g_w[gate_h[i]]; uw[i] = &g_w[up_h[i]]; dw[i] = &g_w[down_h[i]];
+        if (gw[i]->out_f != e_ffn || uw[i]->out_f != e_ffn || gw[i]->nb != d_model / 256 || uw[i]->nb != d_model / 256 ||
+            dw[i]->out_f != d_model || dw[i]->nb != e_ffn / 256) return 1;
+        uniform = uniform && gw[i]->qtype == gw[0]->qtype && uw[i]->qtype == gw[0]->qtype && dw[i]->qtype == dw[0]->qtype;
+    }
+    unsigned mg = 0, mgm = 0, md = 0, mdm = 0;
+    for (size_t i = 0; i < P; i++) {
+        mg = std::max({mg, gw[i]->maxd, uw[i]->maxd}); mgm = std::max({mgm, gw[i]->maxdmin, uw[i]->maxdmin});
+        md = std::max(md, dw[i]->maxd); mdm = std::max(mdm, dw[i]->maxdmin);
+    }
+    const bool fast = uniform && fast_envelope(gw[0]->qtype, d_model / 256, mg, mgm, fw) &&
+                      fast_envelope(dw[0]->qtype, e_ffn / 256, md, mdm, fw);
+
+    int64_t *h_dev = (int64_t *)ensure(R_X, (size_t)m * d_model * 8);
+    int64_t *out_dev = (int64_t *)ensure(R_OUT, (size_t)m * d_model * 8);
+    int64_t *gates_dev = (int64_t *)ensure(R_GATES, P * 8);
+    if (!h_dev || !out_dev || !gates_dev || !h2d(h_dev, h, (size_t)m * d_model * 8) || !h2d(gates_dev, gates, P * 8)) return 1;
+    std::vector<int> tok_of(P);
+    for (size_t i = 0; i < P; i++) tok_of[i] = (int)(i / k);
+
+    bool done = false;
+    if (fast) {
+        // group pairs by identical (gate, up, down) triple, in order of first appearance
+        std::map<std::tuple<long long, long long, long long>, int> index;
+        std::vector<std::vector<int>> members;
+        for (size_t i = 0; i < P; i++) {
+            auto key = std::make_tuple(gate_h[i], up_h[i], down_h[i]);
+            auto it = index.find(key);
+            if (it == index.end()) { it = index.emplace(key, (int)members.size()).first; members.emplace_back(); }
+            members[it->second].push_back((int)i);
+        }
+        const int G = (int)members.size();
+        std::vector<const uint8_t *> tabs(3 * (size_t)G);
+        std::vector<int> grp_off(G + 1, 0), pair_tok(P);
+        std::vector<int64_t> pair_gate(P);
+        int maxp = 0, pos = 0;
+        for (int gidx = 0; gidx < G; gidx++) {
+            const int first = members[gidx][0];
+            tabs[gidx] = (const uint8_t *)gw[first]->d; tabs[G + gidx] = (const uint8_t *)uw[first]->d;
+            tabs[2 * G + gidx] = (const uint8_t *)dw[first]->d;
+            grp_off[gidx] = pos;
+            for (int i : members[gidx]) { pair_tok[pos] = tok_of[i]; pair_gate[pos] = gates[i]; pos++; }
+            maxp = std::max(maxp, (int)members[gidx].size());
+        }
+        grp_off[G] = pos;
+        const uint8_t **tabs_dev = (const uint8_t **)ensure(R_TABS, std::max<size_t>(tabs.size(), 64) * sizeof(void *));
+        int *off_dev = (int *)ensure(R_GRPOFF, (G + 1) * sizeof(int));
+        int *tok_dev = (int *)ensure(R_PAIRTOK, P * sizeof(int));
+        int64_t *pg_dev = (int64_t *)ensure(R_PAIRGATE, P * 8);
+        int8_t *hl = (int8_t *)ensure(R_XL, (size_t)m * 8 * d_model);
+        if (!tabs_dev || !off_dev || !tok_dev || !pg_dev || !hl) return 1;
+        MoePlan plan = {tabs_dev, tabs_dev + G, tabs_dev + 2 * G, gw[0]->qtype, dw[0]->qtype, d_model, e_ffn};
+        bool ok = h2d(tabs_dev, tabs.data(), tabs.size() * sizeof(void *)) && h2d(off_dev, grp_off.data(), (G + 1) * sizeof(int)) &&
+                  h2d(tok_dev, pair_tok.data(), P * sizeof(int)) && h2d(pg_dev, pair_gate.data(), P * 8) &&
+                  cudaMemsetAsync(out_dev, 0, (size_t)m * d_model * 8, g_stream) == cudaSuccess &&
+                  launch_limbs(h_dev, m, d_model, hl, g_flags, g_stream) == cudaSuccess &&
+                  moe_fused(plan, hl, false, tok_dev, nullptr, off_dev, G, (long long)P, maxp, pg_dev, tok_dev, fa, fw,
+                            out_dev, g_stream);
+        if (!ok) { cudaGetLastError(); return 1; }
+        const int f = read_flags_clear();
+        if (f < 0) return 1;
+        done = (f & 1) == 0;                      // an envelope miss re-runs the exact composition below
+    }
+    if (!done && !moe_exact_pairs(gw, uw, dw, h_dev, tok_of, gates_dev, m, k, d_model, e_ffn, fa, fw, out_dev)) {
+        cudaGetLastError(); return 1;
+    }
+    if (!d2h(out, out_dev, (size_t)m * d_model * 8) || !sync()) { cudaGetLastError(); return 1; }
+    return 0;
+}
+
+int apply_resident_impl(long long h, const int64_t *x, long long T, int fw, int64_t *out, int want_qtype) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS);
+    if (!init() || !x || !out || T <= 0 || fw < 0 || fw > 62) return 1;
+    if (!valid_q(h)) return 1;
+    const Weight &w = g_w[h];
+    if (want_qtype >= 0 && w.qtype != want_qtype) return 2;
+    prof(PM_RESIDENT_APPLY);
+    const long long K = w.nb * 256;
+    int64_t *xd = (int64_t *)ensure(R_X, (size_t)T * K * 8), *od = (int64_t *)ensure(R_OUT, (size_t)T * w.out_f * 8);
+    if (!xd || !od || !h2d(xd, x, (size_t)T * K * 8) || !linear_dev(w, xd, T, fw, od, true, g_stream) ||
+        !d2h(out, od, (size_t)T * w.out_f * 8) || !sync()) { cudaGetLastError(); return 1; }
+    return 0;
+}
+
+}  // namespace
+
+// ====================================================================================================
+// Part 1: reference ABI v5
+// ====================================================================================================
+extern "C" int qk_cuda_abi_version(void) { return 5; }
+
+extern "C" int qk_cuda_available(void) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    return init() ? 0 : 1;
+}
+
+extern "C" void qk_profile_reset(void) { for (auto &v : g_prof) __atomic_store_n(&v, 0ULL, __ATOMIC_RELAXED); }
+extern "C" void qk_profile_set_enabled(int enabled) { g_prof_on = enabled ? 1 : 0; }
+extern "C" int qk_profile_snapshot(unsigned long long *out, int capacity) {
+    if (!out || capacity < PM_COUNT) return -1;
+    for (int i = 0; i < PM_COUNT; i++) out[i] = __atomic_load_n(&g_prof[i], __ATOMIC_RELAXED);
+    return PM_COUNT;
+}
+
+extern "C" int qk_linear_cuda(const uint8_t *W, const int64_t *x, long long T, long long out_f, long long n_blocks,
+                              int fw, int qtype, int64_t *out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS);
+    if (!W || !x || !out || T <= 0 || fw < 0 || fw > 62) return 1;
+    const long long h = register_quant(W, false, out_f, n_blocks, qtype);
+    if (h < 0) return 1;
+    const int rc = apply_resident_impl(h, x, T, fw, out, -1);
+    cudaFree(g_w[h].d); prof(PM_FREE_CALLS);
+    g_w.pop_back();                                   // the transient weight is the last slot
+    return rc;
+}
+
+extern "C" int qk_resident_reserve(long long count) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (count < 0 || count > (1LL << 28)) return 1;
+    try { g_w.reserve((size_t)count); } catch (...) { return 1; }
+    return 0;
+}
+
+extern "C" long long qk_register_weight(const uint8_t *W, long long out_f, long long n_blocks, int qtype) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS);
+    return register_quant(W, false, out_f, n_blocks, qtype);
+}
+
+extern "C" long long qk_register_i64(const int64_t *W, long long rows, long long cols) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS);
+    if (!init() || !W || rows <= 0 || cols <= 0 || rows > (1LL << 40) / cols / 8) return -1;
+    void *d = nullptr;
+    const size_t bytes = (size_t)rows * cols * 8;
+    if (cudaMalloc(&d, bytes) != cudaSuccess) { cudaGetLastError(); return -1; }
+    prof(PM_ALLOC_CALLS); prof(PM_ALLOC_BYTES, bytes);
+    if (!h2d(d, W, bytes) || !sync()) { cudaGetLastError(); cudaFree(d); return -1; }
+    const long long h = new_slot();
+    Weight &w = g_w[h];
+    w.d = d; w.out_f = rows; w.nb = cols; w.qtype = QT_I64; w.bytes = bytes; w.live = true;
+    prof(PM_REG_CALLS);
+    return h;
+}
+
+extern "C" long long qk_resident_count(void) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    long long n = 0;
+    for (auto &w : g_w) n += w.live ? 1 : 0;
+    return n;
+}
+extern "C" long long qk_resident_capacity(void) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    return (long long)g_w.capacity();
+}
+
+extern "C" void iie_moe_layer_destroy(long long layer);
+
+extern "C" void qk_free_all(void) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (g_ready != 0) { std::vector<Weight>().swap(g_w); return; }
+    cudaStreamSynchronize(g_stream);
+    for (size_t i = 0; i < g_layers.size(); i++) iie_moe_layer_destroy((long long)i);
+    g_layers.clear();
+    for (auto &w : g_w) if (w.live && w.d) { cudaFree(w.d); prof(PM_FREE_CALLS); }
+    std::vector<Weight>().swap(g_w);                  // capacity returns to zero
+    release_workspace();
+}
+
+extern "C" int qk_apply_resident(long long h, const int64_t *x, long long T, int fw, int64_t *out) {
+    return apply_resident_impl(h, x, T, fw, out, -1);
+}
+extern "C" int qk_apply_resident_q6k_dp4a(long long h, const int64_t *x, long long T, int fw, int Ln, int64_t *out) {
+    if (Ln < 1 || Ln > 8) return 1;
+    return apply_resident_impl(h, x, T, fw, out, QT_Q6K);
+}
+extern "C" int qk_apply_resident_q4k_dp4a(long long h, const int64_t *x, long long T, int fw, int Ln, int64_t *out) {
+    if (Ln < 1 || Ln > 8) return 1;
+    return apply_resident_impl(h, x, T, fw, out, QT_Q4K);
+}
+
+extern "C" int qk_apply_resident_grouped(const long long *handles, const int *phase_ids, int count, const int64_t *x,
+                                         long long T, int fw, long long output_capacity, int64_t *out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS);
+    if (!init() || !handles || !x || !out || count <= 0 || count > 16 || T <= 0 || fw < 0 || fw > 62) return 1;
+    long long total = 0, nb = -1;
+    for (int i = 0; i < count; i++) {
+        if (!valid_q(handles[i])) return 1;
+        const Weight &w = g_w[handles[i]];
+        if (nb < 0) nb = w.nb; else if (nb != w.nb) return 1;
+        total += T * w.out_f;
+    }
+    if (total > output_capacity) return 1;
+    prof(PM_GROUPED_APPLY);
+    const long long K = nb * 256;
+    int64_t *xd = (int64_t *)ensure(R_X, (size_t)T * K * 8), *od = (int64_t *)ensure(R_OUT, (size_t)total * 8);
+    int8_t *xl = (int8_t *)ensure(R_XL, (size_t)T * 8 * K);
+    if (!xd || !od || !xl || !h2d(xd, x, (size_t)T * K * 8) ||
+        launch_limbs(xd, T, K, xl, g_flags, g_stream) != cudaSuccess) { cudaGetLastError(); return 1; }
+    const int f0 = read_flags_clear();
+    if (f0 < 0) return 1;
+    long long off = 0;
+    for (int i = 0; i < count; i++) {
+        const Weight &w = g_w[handles[i]];
+        const int phase = phase_ids ? phase_ids[i] : 0;
+        static const int calls[5] = {PM_OTHER_CALLS, PM_Q_CALLS, PM_K_CALLS, PM_V_CALLS, PM_O_CALLS};
+        prof(calls[phase >= 0 && phase <= 4 ? phase : 0]);
+        bool ok;
+        if (f0 & 1) ok = launch_exact_linear((const uint8_t *)w.d, w.qtype, w.out_f, w.nb, xd, T, fw, od + off, g_stream) == cudaSuccess;
+        else ok = linear_dev(w, xd, T, fw, od + off, false, g_stream, xl);
+        if (!ok) { cudaGetLastError(); return 1; }
+        off += T * w.out_f;
+    }
+    if (!d2h(out, od, (size_t)total * 8) || !sync()) { cudaGetLastError(); return 1; }
+    return 0;
+}
+
+extern "C" int qk_rmsnorm_router(long long gain_h, long long router_h, const int64_t *x, long long rows, int fa, int fw,
+                                 unsigned long long eps, int used, long long h_capacity, long long route_capacity,
+                                 int64_t *h_out, int *ids_out, int64_t *gates_out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS);
+    if (!init() || !x || !h_out || !ids_out || !gates_out || rows <= 0 || used <= 0 || fa < 1 || fa > 29 || fw < 0 ||
+        fw > 62 || !valid_i64(gain_h) || !valid_i64(router_h)) return 1;
+    const Weight &gain = g_w[gain_h], &router = g_w[router_h];
+    const long long width = router.nb, experts = router.out_f;
+    if (gain.out_f != 1 || gain.nb != width || used > experts || experts > 1024 || rows * width > h_capacity ||
+        rows * used > route_capacity) return 1;
+    int64_t *xd = (int64_t *)ensure(R_X, (size_t)rows * width * 8), *hd = (int64_t *)ensure(R_HNORM, (size_t)rows * width * 8);
+    int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)rows * experts * 8), *gd = (int64_t *)ensure(R_GATES, (size_t)rows * used * 8);
+    int *idd = (int *)ensure(R_IDS, (size_t)rows * used * sizeof(int));
+    if (!xd || !hd || !lg || !gd || !idd || !h2d(xd, x, (size_t)rows * width * 8)) { cudaGetLastError(); return 1; }
+    if (launch_rmsnorm(xd, rows, width, (const int64_t *)gain.d, fa, eps, hd, g_flags, g_stream) != cudaSuccess ||
+        launch_exact_dense((const int64_t *)router.d, experts, width, hd, rows, fw, lg, g_flags, g_stream) != cudaSuccess ||
+        launch_topk(lg, rows, (int)experts, used, fa, idd, gd, g_stream) != cudaSuccess) { cudaGetLastError(); return 1; }
+    const int f = read_flags_clear();
+    if (f < 0) return 1;
+    if (f) return 3;
+    if (!d2h(h_out, hd, (size_t)rows * width * 8) || !d2h(ids_out, idd, (size_t)rows * used * sizeof(int)) ||
+        !d2h(gates_out, gd, (size_t)rows * used * 8) || !sync()) { cudaGetLastError(); return 1; }
+    return 0;
+}
+
+extern "C" int qk_moe_ffn(const long long *gate_h, const long long *up_h, const long long *down_h, int n_e,
+                          const int64_t *h, const int64_t *gates, long long d_model, long long e_ffn, int fa, int fw,
+                          int64_t *out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS); prof(PM_MOE);
+    return moe_host_entry(gate_h, up_h, down_h, 1, n_e, h, gates, d_model, e_ffn, fa, fw, out);
+}
+extern "C" int qk_moe_ffn_dp4a(const long long *gate_h, const long long *up_h, const long long *down_h, int n_e,
+                               const int64_t *h, const int64_t *gates, long long d_model, long long e_ffn, int fa,
+                               int fw, int64_t *out) {
+    return qk_moe_ffn(gate_h, up_h, down_h, n_e, h, gates, d_model, e_ffn, fa, fw, out);
+}
+extern "C" int qk_moe_ffn_batched(const long long *gate_h, const long long *up_h, const long long *down_h, int m, int k,
+                                  const int64_t *h, const int64_t *gates, long long d_model, long long e_ffn, int fa,
+                                  int fw, int64_t *out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS); prof(PM_MOE_BATCHED);
+    return moe_host_entry(gate_h, up_h, down_h, m, k, h, gates, d_model, e_ffn, fa, fw, out);
+}
+extern "C" int qk_moe_ffn_batched_dp4a(const long long *gate_h, const long long *up_h, const long long *down_h, int m,
+                                       int k, const int64_t *h, const int64_t *gates, long long d_model,
+                                       long long e_ffn, int fa, int fw, int64_t *out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS); prof(PM_MOE_BATCHED_DP4A);
+    return moe_host_entry(gate_h, up_h, down_h, m, k, h, gates, d_model, e_ffn, fa, fw, out);
+}
+
+extern "C" long long qk_moe_workspace_allocations(void) { std::lock_guard<std::recursive_mutex> lk(g_mu); return g_ws_allocs; }
+extern "C" unsigned long long qk_moe_workspace_bytes(void) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    unsigned long long n = 0;
+    for (auto &b : g_buf) n += b.cap;
+    return n;
+}
+extern "C" void qk_moe_workspace_release(void) { std::lock_guard<std::recursive_mutex> lk(g_mu); release_workspace(); }
+
+// ---- attention bank: outside the MoE hot path; the entries exist so the reference bridge loads -----------
+extern "C" long long qk_attention_bank_create(int, long long, long long, int, int, int, int, const int64_t *, const int64_t *) { return -1; }
+extern "C" int qk_attention_bank_reset(long long) { return 1; }
+extern "C" void qk_attention_bank_destroy(long long) {}
+extern "C" int qk_attention_bank_moe_configure(long long, int, int, int, long long, long long) { return 1; }
+extern "C" int qk_attention_bank_moe_bind(long long, int, int, long long, long long, long long) { return 1; }
+extern "C" int qk_attention_bank_import(long long, int, const int64_t *, const int64_t *, long long) { return 1; }
+extern "C" int qk_attention_bank_apply(long long, int, long long, long long, long long, long long, const int64_t *, int,
+                                       int, int, long long, long long, int64_t *) { return 1; }
+extern "C" int qk_attention_bank_moe_begin(long long, int, long long, long long, long long, long long, long long,
+                                           long long, const int64_t *, int, int, unsigned long long, int, int,
+                                           long long, int, int *, int *) { return 1; }
+extern "C" int qk_attention_bank_moe_continue(long long, int, int, int, long long, int64_t *) { return 1; }
+extern "C" int qk_attention_bank_moe_export(long long, long long, int64_t *) { return 1; }
+extern "C" unsigned long long qk_attention_bank_workspace_bytes(long long) { return 0; }
+
+// ====================================================================================================
+// Part 2: device-pointer extension
+// ====================================================================================================
+extern "C" long long iie_register_weight_dev(const void *raw_dev, long long out_f, long long n_blocks, int qtype) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    return register_quant(raw_dev, true, out_f, n_blocks, qtype);
+}
+
+extern "C" int iie_weight_export(long long h, void *raw_host) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !raw_host || !valid_q(h)) return 1;
+    const Weight &w = g_w[h];
+    const size_t raw_bytes = (size_t)w.out_f * w.nb * (w.qtype == QT_Q4K ? 144 : 210);
+    void *stage = ensure(R_RAW, raw_bytes);
+    if (!stage || launch_unpack((const uint8_t *)w.d, (uint8_t *)stage, w.out_f, w.nb, w.qtype, g_stream) != cudaSuccess ||
+        !d2h(raw_host, stage, raw_bytes) || !sync()) { cudaGetLastError(); return 1; }
+    return 0;
+}
+
+extern "C" long long iie_moe_layer_create(long long router_h, const long long *gate_h, const long long *up_h,
+                                          const long long *down_h, int n_experts, int top_k, long long d_model,
+                                          long long e_ffn) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !gate_h || !up_h || !down_h || n_experts <= 0 || n_experts > 1024 || top_k <= 0 || top_k > n_experts ||
+        d_model <= 0 || e_ffn <= 0 || d_model % 256 || e_ffn % 256) return -1;
+    if (!(valid_q(router_h) || valid_i64(router_h))) return -1;
+    const Weight &r = g_w[router_h];
+    if (r.out_f != n_experts || (r.qtype == QT_I64 ? r.nb != d_model : r.nb != d_model / 256)) return -1;
+    MoeLayer L;
+    std::vector<const uint8_t *> tabs(3 * (size_t)n_experts);
+    for (int e = 0; e < n_experts; e++) {
+        if (!valid_q(gate_h[e]) || !valid_q(up_h[e]) || !valid_q(down_h[e])) return -1;
+        const Weight &g = g_w[gate_h[e]], &u = g_w[up_h[e]], &d = g_w[down_h[e]];
+        if (g.out_f != e_ffn || u.out_f != e_ffn || g.nb != d_model / 256 || u.nb != d_model / 256 || d.out_f != d_model ||
+            d.nb != e_ffn / 256) return -1;
+        if (e == 0) { L.gate_q = g.qtype; L.down_q = d.qtype; }
+        if (g.qtype != L.gate_q || u.qtype != L.gate_q || d.qtype != L.down_q) return -1;
+        tabs[e] = (const uint8_t *)g.d; tabs[n_experts + e] = (const uint8_t *)u.d; tabs[2 * n_experts + e] = (const uint8_t *)d.d;
+        L.maxd_gate = std::max({L.maxd_gate, g.maxd, u.maxd}); L.maxdmin_gate = std::max({L.maxdmin_gate, g.maxdmin, u.maxdmin});
+        L.maxd_down = std::max(L.maxd_down, d.maxd); L.maxdmin_down = std::max(L.maxdmin_down, d.maxdmin);
+    }
+    void *dt = nullptr;
+    if (cudaMalloc(&dt, tabs.size() * sizeof(void *)) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (cudaMemcpy(dt, tabs.data(), tabs.size() * sizeof(void *), cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(dt); return -1; }
+    L.router = router_h; L.n_experts = n_experts; L.top_k = top_k; L.d_model = d_model; L.e_ffn = e_ffn;
+    L.tabs = (const uint8_t **)dt; L.live = true;
+    g_layers.push_back(L);
+    return (long long)g_layers.size() - 1;
+}
+
+extern "C" void iie_moe_layer_destroy(long long layer) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (layer < 0 || (size_t)layer >= g_layers.size() || !g_layers[layer].live) return;
+    if (g_stream) cudaStreamSynchronize(g_stream);
+    cudaFree((void *)g_layers[layer].tabs);
+    g_layers[layer].live = false; g_layers[layer].tabs = nullptr;
+}
+
+extern "C" int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long long T, int fa, int fw, int accumulate,
+                                   int64_t *out_dev, int *ids_dev, int64_t *gates_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || layer < 0 || (size_t)layer >= g_layers.size() || !g_layers[layer].live || !h_dev || !out_dev ||
+        T <= 0 || fa < 1 || fa > 29) return 1;
+    const MoeLayer &L = g_layers[layer];
+    const Weight &r = g_w[L.router];
+    cudaStream_t s = stream ? (cudaStream_t)stream : g_stream;
+    if (!fast_envelope(L.gate_q, L.d_model / 256, L.maxd_gate, L.maxdmin_gate, fw) ||
+        !fast_envelope(L.down_q, L.e_ffn / 256, L.maxd_down, L.maxdmin_down, fw)) return 3;
+    const int E = L.n_experts, k = L.top_k;
+    const long long P = T * k;
+    int8_t *hl = (int8_t *)ensure(R_XL, (size_t)T * 8 * L.d_model);
+    int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)T * E * 8);
+    int *ids = ids_dev ? ids_dev : (int *)ensure(R_IDS, (size_t)P * sizeof(int));
+    int64_t *gates = gates_dev ? gates_dev : (int64_t *)ensure(R_GATES, (size_t)P * 8);
+    if (!hl || !lg || !ids || !gates) return 1;
+    if (launch_limbs(h_dev, T, L.d_model, hl, g_flags, s) != cudaSuccess) return 1;
+    if (r.qtype == QT_I64) {
+        if (launch_exact_dense((const int64_t *)r.d, E, L.d_model, h_dev, T, fw, lg, g_flags, s) != cudaSuccess) return 1;
+    } else if (!linear_dev(r, h_dev, T, fw, lg, false, s, hl)) return 1;
+    if (launch_topk(lg, T, E, k, fa, ids, gates, s) != cudaSuccess) return 1;
+    if (!accumulate && cudaMemsetAsync(out_dev, 0, (size_t)T * L.d_model * 8, s) != cudaSuccess) return 1;
+    MoePlan plan = {L.tabs, L.tabs + E, L.tabs + 2 * E, L.gate_q, L.down_q, L.d_model, L.e_ffn};
+    bool ok;
+    if (T == 1) {
+        // the k selected experts are the groups; every pair reads token 0's limb planes
+        int *zero = (int *)ensure(R_PAIRTOK, std::max<size_t>((size_t)P, 64) * sizeof(int));
+        if (!zero || cudaMemsetAsync(zero, 0, (size_t)P * sizeof(int), s) != cudaSuccess) return 1;
+        ok = moe_fused(plan, hl, true, zero, ids, nullptr, k, P, 1, gates, zero, fa, fw, out_dev, s);
+    } else {
+        int *off = (int *)ensure(R_GRPOFF, (size_t)(E + 1) * sizeof(int));
+        int *ptok = (int *)ensure(R_PAIRTOK, (size_t)P * sizeof(int));
+        int64_t *pg = (int64_t *)ensure(R_PAIRGATE, (size_t)P * 8);
+        if (!off || !ptok || !pg || launch_dispatch(ids, gates, T, k, E, off, ptok, pg, s) != cudaSuccess) return 1;
+        ok = moe_fused(plan, hl, false, ptok, nullptr, off, E, P, (int)std::min<long long>(T, 4), pg, ptok, fa, fw, out_dev, s);
+    }
+    if (!ok) { cudaGetLastError(); return 1; }
+    return 0;
+}
+
+extern "C" int iie_apply_dev(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !valid_q(h) || !x_dev || !out_dev || T <= 0) return 1;
+    cudaStream_t s = stream ? (cudaStream_t)stream : g_stream;
+    return linear_dev(g_w[h], x_dev, T, fw, out_dev, false, s) ? 0 : 1;
+}
+
+extern "C" int iie_flags_read_clear(void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init()) return -1;
+    if (stream && cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return -1;
+    return read_flags_clear();
+}

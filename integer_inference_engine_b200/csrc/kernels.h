@@ -63,9 +63,10 @@ cudaError_t launch_topk(const int64_t *logits, long long rows, int n_experts, in
 cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
                            unsigned long long eps, int64_t *out, int *flags, cudaStream_t s);
 
-// Counting-sort dispatch of (token, slot) pairs by expert.
-//   ids [T*k] -> grp_off [E+1], pair_tok [T*k], pair_src [T*k] (index t*k+j of each sorted pair)
-cudaError_t launch_dispatch(const int *ids, long long T, int k, int n_experts, int *grp_off, int *pair_tok,
-                            int *pair_src, int *cursor_scratch, cudaStream_t s);
+// Counting-sort dispatch of (token, slot) pairs by expert (single CTA, n_experts <= 1024).
+//   ids [T*k], gates [T*k] -> grp_off [E+1], pair_tok [T*k] (token of each sorted pair),
+//   pair_gate [T*k] (its gate weight)
+cudaError_t launch_dispatch(const int *ids, const int64_t *gates, long long T, int k, int n_experts, int *grp_off,
+                            int *pair_tok, int64_t *pair_gate, cudaStream_t s);
 
 }  // namespace iie

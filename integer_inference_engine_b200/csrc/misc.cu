@@ -1,0 +1,356 @@
+// Support kernels around the streamed products: weight repack, activation limb planes, the exact
+// 128-bit fallback product, routing (top-k + sigmoid), dispatch, RMSNorm and the unfused
+// element-wise steps used by the fallback composition.
+#include "kernels.h"
+#include "layout.cuh"
+
+namespace iie {
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------------
+// repack / unpack: one thread per raw byte
+// ---------------------------------------------------------------------------------------------------
+template <bool FORWARD>
+__global__ void repack_kernel(const uint8_t *src, uint8_t *dst, long long out_f, long long nb, int qtype,
+                              unsigned *maxbits) {
+    const int bs = qtype == QT_Q4K ? 144 : 210;
+    const long long total = out_f * nb * bs;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long blk_lin = idx / bs;
+        const int i = (int)(idx - blk_lin * bs);
+        const long long row = blk_lin / nb, blk = blk_lin - row * nb;
+        const long long unit = (row >> 3) * nb + blk;
+        const int r = (int)(row & 7);
+        const long long packed = qtype == QT_Q4K ? unit * HTB_Q4K + q4k_unit_offset(r, i)
+                                                 : unit * HTB_Q6K + q6k_unit_offset(r, i);
+        if (FORWARD) {
+            dst[packed] = src[idx];
+            if (maxbits) {                                  // block scale magnitudes (little-endian halves)
+                const int dpos = qtype == QT_Q4K ? 0 : 208;
+                if (i == dpos) atomicMax(&maxbits[0], ((unsigned)src[idx] | ((unsigned)src[idx + 1] << 8)) & 0x7FFFu);
+                if (qtype == QT_Q4K && i == 2)
+                    atomicMax(&maxbits[1], ((unsigned)src[idx] | ((unsigned)src[idx + 1] << 8)) & 0x7FFFu);
+            }
+        } else {
+            dst[idx] = src[packed];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// activation limb planes
+// ---------------------------------------------------------------------------------------------------
+__global__ void limbs_kernel(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags) {
+    const long long total = n_rows * K;
+    bool bad = false;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long row = idx / K, col = idx - row * K;
+        bool ok;
+        const uint64_t d = balanced_digits8(x[idx], ok);
+        bad |= !ok;
+#pragma unroll
+        for (int l = 0; l < 8; l++) planes[(row * 8 + l) * K + col] = (int8_t)(d >> (8 * l));
+    }
+    if (bad) atomicOr(flags, 1);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// exact fallback: one thread per output, 128-bit accumulation in the reference's per-weight form
+// (north-mini-code/tools/nmc_qk_kernel.c:85-120).  Valid for every int64 input.
+// ---------------------------------------------------------------------------------------------------
+__global__ void exact_linear_kernel(const uint8_t *w, int qtype, long long out_f, long long nb, const int64_t *x,
+                                    long long T, int fw, int64_t *out) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= out_f * T) return;
+    const long long o = idx % out_f, t = idx / out_f;
+    const int64_t *xt = x + t * nb * 256;
+    i128 acc = 0;
+    for (long long b = 0; b < nb; b++) {
+        const int64_t *xb = xt + b * 256;
+        auto byte = [&](int i) { return (int)repacked_byte(w, qtype, nb, o, b, i); };
+        if (qtype == QT_Q4K) {
+            const int64_t dq = half_to_fixed(byte(0) | (byte(1) << 8), fw), dmq = half_to_fixed(byte(2) | (byte(3) << 8), fw);
+            for (int j = 0; j < 8; j++) {
+                int sc, mn;
+                if (j < 4) { sc = byte(4 + j) & 63; mn = byte(8 + j) & 63; }
+                else { sc = (byte(8 + j) & 0xF) | ((byte(j) >> 6) << 4); mn = (byte(8 + j) >> 4) | ((byte(4 + j) >> 6) << 4); }
+                const int64_t ws = dq * sc, wm = dmq * mn;
+                for (int l = 0; l < 32; l++) {
+                    const int q = (byte(16 + 32 * (j >> 1) + l) >> ((j & 1) * 4)) & 0xF;
+                    acc += (i128)(ws * q - wm) * xb[32 * j + l];
+                }
+            }
+        } else {
+            const int64_t dq = half_to_fixed(byte(208) | (byte(209) << 8), fw);
+            for (int sb = 0; sb < 16; sb++) {
+                const int half = sb >> 3, k = (sb >> 1) & 3, l0 = (sb & 1) * 16;
+                const int64_t ws = dq * (int64_t)(int8_t)byte(192 + 8 * half + 2 * k + (sb & 1));
+                for (int l = 0; l < 16; l++) {
+                    const int ql = byte(64 * half + 32 * (k & 1) + l0 + l), qh = byte(128 + 32 * half + l0 + l);
+                    const int q = (((k < 2) ? (ql & 0xF) : (ql >> 4)) | (((qh >> (2 * k)) & 3) << 4)) - 32;
+                    acc += (i128)(ws * q) * xb[16 * sb + l];
+                }
+            }
+        }
+    }
+    out[t * out_f + o] = (int64_t)(acc >> fw);
+}
+
+// Dense int64 weights (router / gain matrices registered as int64): exact 128-bit product; the
+// reference additionally requires the un-shifted sum to fit int64 (nmc_qk_cuda.cu:615-638), which is
+// reported through flags bit 2.
+__global__ void exact_dense_kernel(const int64_t *w, long long out_f, long long in_f, const int64_t *x, long long T,
+                                   int fw, int64_t *out, int *flags) {
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= out_f * T) return;
+    const long long o = warp % out_f, t = warp / out_f;
+    i128 acc = 0;
+    for (long long i = lane; i < in_f; i += 32) acc += (i128)w[o * in_f + i] * x[t * in_f + i];
+    unsigned long long lo = (unsigned long long)acc, hi = (unsigned long long)((u128)acc >> 64);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        const unsigned long long lo2 = __shfl_down_sync(0xffffffffu, lo, s), hi2 = __shfl_down_sync(0xffffffffu, hi, s);
+        const u128 sum = (((u128)hi << 64) | lo) + (((u128)hi2 << 64) | lo2);
+        lo = (unsigned long long)sum; hi = (unsigned long long)(sum >> 64);
+    }
+    if (lane == 0) {
+        const i128 total = (i128)(((u128)hi << 64) | lo);
+        if (total > (i128)INT64_MAX || total < (i128)INT64_MIN) { if (flags) atomicOr(flags, 4); out[t * out_f + o] = 0; }
+        else out[t * out_f + o] = ((int64_t)total) >> fw;
+    }
+}
+
+__global__ void silu_mul_kernel(int64_t *a, const int64_t *b, long long n, int fa) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) a[i] = mul_shift(silu_fixed(a[i], fa), b[i], fa);
+}
+
+__global__ void combine_kernel(const int64_t *dn, const int64_t *gates, long long T, int k, long long d_model, int fa,
+                               int64_t *out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * d_model) return;
+    const long long t = i / d_model, o = i - t * d_model;
+    unsigned long long acc = 0;
+    for (int j = 0; j < k; j++) acc += (unsigned long long)mul_shift(dn[(t * k + j) * d_model + o], gates[t * k + j], fa);
+    out[i] = (int64_t)acc;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// top-k with lowest-index tie-break + sigmoid gates (north-mini-code/src/nmc/cohere2.py:162-165,180)
+// ---------------------------------------------------------------------------------------------------
+__global__ void topk_kernel(const int64_t *logits, long long rows, int n_experts, int k, int fa, int *ids,
+                            int64_t *gates) {
+    const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const int64_t *lr = logits + row * n_experts;
+    unsigned taken = 0;                                   // bit i: element lane + 32*i already selected
+    for (int r = 0; r < k; r++) {
+        int64_t best = INT64_MIN; int best_id = 0x7fffffff;
+        for (int i = 0, e = lane; e < n_experts; i++, e += 32) {
+            if (taken & (1u << i)) continue;
+            const int64_t v = lr[e];
+            if (best_id == 0x7fffffff || v > best) { best = v; best_id = e; }   // ascending e: ties keep the lower id
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) {
+            const int64_t ov = __shfl_xor_sync(0xffffffffu, best, s);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_id, s);
+            if (oi != 0x7fffffff && (best_id == 0x7fffffff || ov > best || (ov == best && oi < best_id))) { best = ov; best_id = oi; }
+        }
+        if (best_id != 0x7fffffff && (best_id & 31) == lane) taken |= 1u << (best_id >> 5);
+        if (lane == 0) {
+            ids[row * k + r] = best_id == 0x7fffffff ? -1 : best_id;
+            gates[row * k + r] = best_id == 0x7fffffff ? 0 : sigmoid_fixed(best, fa);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// dispatch: stable counting sort of pairs by expert (single CTA)
+// ---------------------------------------------------------------------------------------------------
+__global__ void dispatch_kernel(const int *ids, const int64_t *gates, long long T, int k, int n_experts, int *grp_off,
+                                int *pair_tok, int64_t *pair_gate) {
+    extern __shared__ int sm[];                           // counts[E], base[E]
+    int *counts = sm, *base = sm + n_experts;
+    const long long P = T * k;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (long long i = threadIdx.x; i < P; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < n_experts; e++) { base[e] = run; grp_off[e] = run; run += counts[e]; }
+        grp_off[n_experts] = run;
+    }
+    __syncthreads();
+    // stable placement: expert e's pairs keep ascending pair index (one thread per expert scans in order
+    // when the problem is small; otherwise warps cooperate with a ballot prefix)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int e = warp; e < n_experts; e += nwarps) {
+        if (counts[e] == 0) continue;
+        int pos = base[e];
+        for (long long i0 = 0; i0 < P; i0 += 32) {
+            const long long i = i0 + lane;
+            const bool hit = i < P && ids[i] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int dst = pos + __popc(m & ((1u << lane) - 1));
+                pair_tok[dst] = (int)(i / k);
+                pair_gate[dst] = gates[i];
+            }
+            pos += __popc(m);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// integer RMSNorm (north-mini-code/src/nmc/_bonsai/fixedpoint.py:32-72), one CTA per row
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long uabs64(int64_t v) { return v < 0 ? (0ULL - (unsigned long long)v) : (unsigned long long)v; }
+
+__device__ u128 isqrt_u128(u128 v) {
+    u128 res = 0, bit = (u128)1 << 126;
+    while (bit > v) bit >>= 2;
+    while (bit != 0) {
+        if (v >= res + bit) { v -= res + bit; res = (res >> 1) + bit; } else res >>= 1;
+        bit >>= 2;
+    }
+    return res;
+}
+
+__global__ void rmsnorm_kernel(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
+                               unsigned long long eps, int64_t *out, int *flags) {
+    __shared__ unsigned long long s_lo[256], s_hi[256], s_max[256], s_gmax[256];
+    __shared__ unsigned long long s_rms;
+    __shared__ int s_bad;
+    const long long row = blockIdx.x;
+    const int tid = threadIdx.x;
+    const int64_t *xr = x + row * width;
+    int64_t *yr = out + row * width;
+    u128 ssq = 0; unsigned long long mx = 0, gmx = 0;
+    for (long long i = tid; i < width; i += blockDim.x) {
+        const unsigned long long a = uabs64(xr[i]);
+        ssq += (u128)a * a;
+        mx = a > mx ? a : mx;
+        if (gain) { const unsigned long long ga = uabs64(gain[i]); gmx = ga > gmx ? ga : gmx; }
+    }
+    s_lo[tid] = (unsigned long long)ssq; s_hi[tid] = (unsigned long long)(ssq >> 64); s_max[tid] = mx; s_gmax[tid] = gmx;
+    if (tid == 0) s_bad = 0;
+    __syncthreads();
+    if (tid == 0) {
+        u128 total = 0; unsigned long long m = 0, gm = 0;
+        for (int i = 0; i < blockDim.x; i++) {
+            total += ((u128)s_hi[i] << 64) | s_lo[i];
+            m = s_max[i] > m ? s_max[i] : m; gm = s_gmax[i] > gm ? s_gmax[i] : gm;
+        }
+        // |x| <= 2^57 keeps the 128-bit sum of squares exact for any width <= 2^13
+        if (m > (1ULL << 57) || width > 8192) s_bad = 1;
+        const u128 mean = total / (u128)(unsigned long long)width + eps;
+        const u128 rms = isqrt_u128(mean);
+        if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) s_bad = 1;
+        s_rms = (unsigned long long)rms;
+        s_gmax[0] = gm;
+    }
+    __syncthreads();
+    if (s_bad) { if (tid == 0) atomicOr(flags, 2); return; }
+    const unsigned long long rms = s_rms;
+    const unsigned long long gm = s_gmax[0];
+    bool bad = false;
+    for (long long i = tid; i < width; i += blockDim.x) {
+        const i128 num = (i128)xr[i] << fa;
+        i128 q = num / (i128)rms;
+        if (num < 0 && q * (i128)rms != num) q -= 1;              // floor toward -inf
+        if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; continue; }
+        int64_t y = (int64_t)q;
+        if (gain) {
+            // the oracle refuses a gain product that could leave int64
+            if ((u128)uabs64(y) * gm > (u128)INT64_MAX) { bad = true; continue; }
+            y = (int64_t)(((i128)y * gain[i]) >> fa);
+        }
+        yr[i] = y;
+    }
+    if (bad) atomicOr(flags, 2);
+}
+
+inline unsigned grid_for(long long n, int tpb, long long cap = 148LL * 64) {
+    long long g = (n + tpb - 1) / tpb;
+    if (g > cap) g = cap;
+    return (unsigned)(g < 1 ? 1 : g);
+}
+
+}  // namespace
+
+cudaError_t launch_repack(const uint8_t *raw, uint8_t *dst, long long out_f, long long nb, int qtype,
+                          unsigned *maxbits, cudaStream_t s) {
+    const long long total = out_f * nb * (qtype == QT_Q4K ? 144 : 210);
+    repack_kernel<true><<<grid_for(total, 256), 256, 0, s>>>(raw, dst, out_f, nb, qtype, maxbits);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_unpack(const uint8_t *src, uint8_t *raw, long long out_f, long long nb, int qtype, cudaStream_t s) {
+    const long long total = out_f * nb * (qtype == QT_Q4K ? 144 : 210);
+    repack_kernel<false><<<grid_for(total, 256), 256, 0, s>>>(src, raw, out_f, nb, qtype, nullptr);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, cudaStream_t s) {
+    limbs_kernel<<<grid_for(n_rows * K, 256), 256, 0, s>>>(x, n_rows, K, planes, flags);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_exact_linear(const uint8_t *w, int qtype, long long out_f, long long nb, const int64_t *x,
+                                long long T, int fw, int64_t *out, cudaStream_t s) {
+    const long long n = out_f * T;
+    exact_linear_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(w, qtype, out_f, nb, x, T, fw, out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_exact_dense(const int64_t *w, long long out_f, long long in_f, const int64_t *x, long long T,
+                               int fw, int64_t *out, int *flags, cudaStream_t s) {
+    const long long n = out_f * T * 32;
+    exact_dense_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(w, out_f, in_f, x, T, fw, out, flags);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_silu_mul(int64_t *a, const int64_t *b, long long n, int fa, cudaStream_t s) {
+    silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, n, fa);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const int64_t *dn, const int64_t *gates, long long T, int k, long long d_model, int fa,
+                           int64_t *out, cudaStream_t s) {
+    const long long n = T * d_model;
+    combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(dn, gates, T, k, d_model, fa, out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_topk(const int64_t *logits, long long rows, int n_experts, int k, int fa, int *ids, int64_t *gates,
+                        cudaStream_t s) {
+    if (n_experts > 1024 || n_experts <= 0 || k <= 0) return cudaErrorInvalidValue;
+    const long long n = rows * 32;
+    topk_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(logits, rows, n_experts, k, fa, ids, gates);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
+                           unsigned long long eps, int64_t *out, int *flags, cudaStream_t s) {
+    rmsnorm_kernel<<<(unsigned)rows, 256, 0, s>>>(x, rows, width, gain, fa, eps, out, flags);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_dispatch(const int *ids, const int64_t *gates, long long T, int k, int n_experts, int *grp_off,
+                            int *pair_tok, int64_t *pair_gate, cudaStream_t s) {
+    if (n_experts > 4096) return cudaErrorInvalidValue;
+    dispatch_kernel<<<1, 1024, 2 * n_experts * sizeof(int), s>>>(ids, gates, T, k, n_experts, grp_off, pair_tok, pair_gate);
+    return cudaGetLastError();
+}
+
+}  // namespace iie

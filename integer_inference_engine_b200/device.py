@@ -1,0 +1,115 @@
+"""Device-tensor front end: the MoE block on PyTorch CUDA tensors, no host round trip.
+
+PyTorch only owns memory and streams here; all arithmetic runs in ``libnmc_qk_cuda.so`` through the
+device-pointer entry points of the C-ABI (``iie_*`` in include/iie_qk.h).  The composition follows
+``Engine._moe`` of the reference (north-mini-code/src/nmc/engine.py:375-443): router product, top-k
+with lowest-index tie-break, sigmoid gates, per-expert gate/up products, integer SiLU, down
+product, one floor per expert term and an exact sum.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from . import qk_cuda
+from .qk_cuda import Q4_K, Q6_K, _BLOCK_BYTES, _CUDA_LOCK, CudaContextError, CudaRegistrationError
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def register_weight(raw, out_f: int, n_blocks: int, qtype: int) -> int:
+    """Register raw Q4_K / Q6_K blocks held in a CUDA uint8 tensor, a NumPy array or bytes."""
+    lib = qk_cuda._lib()
+    need = out_f * n_blocks * _BLOCK_BYTES[qtype]
+    if isinstance(raw, torch.Tensor):
+        if not raw.is_cuda or raw.dtype != torch.uint8 or not raw.is_contiguous() or raw.numel() < need:
+            raise ValueError("raw weight tensor must be a contiguous CUDA uint8 tensor of the full size")
+        torch.cuda.current_stream().synchronize()        # the library copies on its own stream
+        with _CUDA_LOCK:
+            h = lib.iie_register_weight_dev(raw.data_ptr(), out_f, n_blocks, qtype)
+        if h < 0:
+            raise CudaRegistrationError(f"device registration failed for [{out_f}, {n_blocks * 256}] qtype {qtype}")
+        return int(h)
+    return qk_cuda.register_weight(raw, out_f, n_blocks, qtype)
+
+
+def export_weight(handle: int, out_f: int, n_blocks: int, qtype: int) -> np.ndarray:
+    """Raw GGUF-order bytes of a registered weight (for checking against a CPU oracle)."""
+    lib = qk_cuda._lib()
+    buf = np.empty(out_f * n_blocks * _BLOCK_BYTES[qtype], np.uint8)
+    with _CUDA_LOCK:
+        rc = lib.iie_weight_export(int(handle), buf.ctypes.data)
+    if rc != 0:
+        raise CudaContextError(f"weight export failed with status {rc}")
+    return buf
+
+
+def apply(handle: int, x: torch.Tensor, out_f: int, fw: int) -> torch.Tensor:
+    """out [T,out_f] = floor(x W^T / 2^fw) for a registered weight, on the current stream."""
+    lib = qk_cuda._lib()
+    x = x.contiguous()
+    assert x.is_cuda and x.dtype == torch.int64 and x.dim() == 2
+    out = torch.empty((x.shape[0], out_f), dtype=torch.int64, device=x.device)
+    with _CUDA_LOCK:
+        rc = lib.iie_apply_dev(int(handle), x.data_ptr(), x.shape[0], int(fw), out.data_ptr(), _stream_ptr())
+    if rc != 0:
+        raise CudaContextError(f"device apply failed with status {rc}")
+    return out
+
+
+def read_flags() -> int:
+    """Read and clear the envelope flag word (synchronises): 0 means every result so far is exact."""
+    with _CUDA_LOCK:
+        return int(qk_cuda._lib().iie_flags_read_clear(_stream_ptr()))
+
+
+class MoELayer:
+    """One MoE layer with every expert resident on the device.
+
+    ``router`` is a handle (quantised or dense int64); ``gate``, ``up``, ``down`` are sequences of
+    ``n_experts`` handles with uniform quantisation type per projection.
+    """
+
+    def __init__(self, router: int, gate, up, down, top_k: int, d_model: int, e_ffn: int):
+        lib = qk_cuda._lib()
+        n = len(gate)
+        if len(up) != n or len(down) != n or n <= 0:
+            raise ValueError("gate, up and down need the same positive number of handles")
+        arr = lambda hs: (ctypes.c_int64 * n)(*[int(v) for v in hs])
+        with _CUDA_LOCK:
+            self.handle = int(lib.iie_moe_layer_create(int(router), arr(gate), arr(up), arr(down), n, int(top_k),
+                                                       int(d_model), int(e_ffn)))
+        if self.handle < 0:
+            raise CudaContextError("MoE layer creation failed (shape, type or handle mismatch)")
+        self.n_experts, self.top_k, self.d_model, self.e_ffn = n, int(top_k), int(d_model), int(e_ffn)
+
+    def forward(self, h: torch.Tensor, fa: int = 16, fw: int = 24, out: torch.Tensor | None = None,
+                accumulate: bool = False, want_routes: bool = True):
+        """h [T,d_model] int64 -> (out [T,d_model], ids [T,k] int32, gates [T,k] int64).
+        Asynchronous on the current stream; call :func:`read_flags` to confirm exactness."""
+        lib = qk_cuda._lib()
+        h = h.contiguous()
+        assert h.is_cuda and h.dtype == torch.int64 and h.dim() == 2 and h.shape[1] == self.d_model
+        T = h.shape[0]
+        if out is None:
+            out = torch.empty((T, self.d_model), dtype=torch.int64, device=h.device)
+            accumulate = False
+        ids = torch.empty((T, self.top_k), dtype=torch.int32, device=h.device) if want_routes else None
+        gates = torch.empty((T, self.top_k), dtype=torch.int64, device=h.device) if want_routes else None
+        with _CUDA_LOCK:
+            rc = lib.iie_moe_forward_dev(self.handle, h.data_ptr(), T, int(fa), int(fw), int(bool(accumulate)),
+                                         out.data_ptr(), ids.data_ptr() if want_routes else None,
+                                         gates.data_ptr() if want_routes else None, _stream_ptr())
+        if rc != 0:
+            raise CudaContextError(f"MoE forward failed with status {rc}")
+        return out, ids, gates
+
+    def close(self):
+        if self.handle >= 0:
+            with _CUDA_LOCK:
+                qk_cuda._lib().iie_moe_layer_destroy(self.handle)
+            self.handle = -1
