@@ -1,0 +1,389 @@
+"""Benchmark of the integer MoE decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one decoded token pushed through every MoE block of the synthetic 30B-A3B-shaped model
+(48 blocks; d=2048, 128 experts, top-8, expert width 768; Q4_K router/gate/up, Q6_K down):
+RMSNorm -> router product -> top-8 + sigmoid gates -> gate/up products with fused integer SiLU ->
+down product with fused gate-weighted combine -> residual add.  Weights are seeded synthetic blocks
+generated on the device; a step streams 1.18 GB of distinct weights, far above the 126 MB L2.
+
+Printed JSON line (rank 0): `value` = tokens/s with the token's hidden state already on the device
+(the whole 48-block step is one CUDA graph); `e2e` = the same through the host-buffer C-ABI call
+(one call per block, upload and download inside the timed region); `roofline` = the gate/up kernel
+timed alone with CUDA events against the measured HBM copy bandwidth; `cpu_baseline` = the CPU
+oracle on this box's host cores for a bounded sample.  Before timing, every block's router ids and
+output are compared byte for byte with the CPU oracle.
+
+`--impl reference` times the reference project's compiled CPU kernel (oracle/_ref) composed the way
+its engine composes the MoE block on the CPU, on a bounded sample per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FA, FW = 16, 24
+D_MODEL, E_FFN, N_EXPERTS, TOP_K = 2048, 768, 128, 8
+WORKLOAD = "config2_moe_decode: batch-1 decode, 48 MoE blocks (d=2048, 128 experts, top-8, eff=768, Q4_K/Q6_K)"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--verify-layers", type=int, default=48, help="blocks checked against the CPU oracle before timing")
+    ap.add_argument("--cpu-sample-layers", type=int, default=4)
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------------ clocks ---
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while a timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx = max(mx, float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def measured_peak_gbs():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# -------------------------------------------------------------------------------------- reference arm -----
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_moe_block_time(kind: str, n_layers: int, repeats: int, seed: int = 1):
+    """Time the CPU MoE block (one token) on `n_layers` synthetic layers with all host threads.
+    kind "reference": linears by the reference project's compiled kernel (oracle/_ref), element-wise
+    steps in NumPy, composed as north-mini-code/src/nmc/engine.py:429-443; kind "port": this
+    repository's C oracle.  Returns seconds per layer-token (median over repeats)."""
+    from oracle import native as onat
+    from oracle import qk_oracle as o
+    layers = []
+    for li in range(n_layers):
+        router, gate, up, down, h = o.synth_moe(seed * 1000 + li, D_MODEL, E_FFN, N_EXPERTS, 1, FA)
+        layers.append((router, gate, up, down, h))
+    nb_in, nb_dn = D_MODEL // 256, E_FFN // 256
+
+    def ref_block(router, gate, up, down, h):
+        lin = onat.ref_qk_linear
+        logits = lin(router, h, N_EXPERTS, nb_in, FW, o.Q4_K)[0]
+        sel = o.topk_lowidx(logits, TOP_K)
+        gates = o.sigmoid_fixed(logits[sel], FA)
+        out = np.zeros(D_MODEL, dtype=object)
+        for j, e in enumerate(sel):
+            g = o.silu_int(lin(gate[e], h, E_FFN, nb_in, FW, o.Q4_K), FA)
+            u = lin(up[e], h, E_FFN, nb_in, FW, o.Q4_K)
+            gu = o.mul_shift(g, u, FA)
+            dn = lin(down[e], gu, D_MODEL, nb_dn, FW, o.Q6_K)[0].astype(object)
+            out += (dn * int(gates[j])) >> FA
+        return out.astype(np.int64)
+
+    def port_block(router, gate, up, down, h):
+        return onat.moe_block(router, o.Q4_K, gate, up, down, o.Q4_K, o.Q6_K, TOP_K, h, D_MODEL, E_FFN, FA, FW)[2][0]
+
+    fn = ref_block if kind == "reference" else port_block
+    a = ref_block(*layers[0]) if onat.ref_available() else None
+    b = port_block(*layers[0])
+    if a is not None:
+        assert np.array_equal(a, b), "reference-built kernel and the C oracle disagree"
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for lay in layers:
+            fn(*lay)
+        times.append((time.perf_counter() - t0) / n_layers)
+    return float(np.median(times))
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import native as onat
+    kind = "reference" if onat.ref_available() else "port"
+    n_layers = 2
+    for _ in range(max(args.warmup, 1) - 1):
+        cpu_moe_block_time(kind, n_layers, 1)
+    t0 = time.perf_counter()
+    per_layer = cpu_moe_block_time(kind, n_layers, max(args.steps, 1))
+    wall = time.perf_counter() - t0
+    value = 1.0 / (per_layer * args.layers)
+    sample = f"{n_layers} blocks x 1 token per step, scaled to {args.layers} blocks"
+    print(json.dumps({
+        "impl": "reference", "metric": "decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_layer * args.layers * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": "n/a (CPU)"},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": host_cores(), "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": wall,
+    }))
+
+
+# ---------------------------------------------------------------------------------------------- our arm ---
+def verify_against_oracle(stack, x0, n_check: int):
+    """Eager pass over the blocks; each checked block's ids, gates and output against the C oracle,
+    using the weights exported back from the device."""
+    import torch
+
+    from integer_inference_engine_b200 import device
+    from oracle import native as onat
+    from oracle import qk_oracle as o
+    nb_in, nb_dn = D_MODEL // 256, E_FFN // 256
+    x = x0.clone()
+    checked = 0
+    for li, layer in enumerate(stack.layers):
+        hs = stack.handles[li]
+        h = device.rmsnorm(x, hs["gain_h"], FA, 1)
+        out, ids, gates = layer.forward(h, FA, FW)
+        torch.cuda.synchronize()
+        assert device.read_flags() == 0, f"block {li}: envelope flag raised"
+        if li < n_check:
+            xn, hn = x.cpu().numpy(), h.cpu().numpy()
+            assert np.array_equal(hn, o.rmsnorm_fixed(xn, FA, 1, hs["gain"].cpu().numpy())), f"block {li}: RMSNorm"
+            router = device.export_weight(hs["router"], N_EXPERTS, nb_in, o.Q4_K)
+            logits = onat.qk_linear(router, hn, N_EXPERTS, nb_in, FW, o.Q4_K)
+            sel = np.stack([onat.topk_lowidx(r, TOP_K) for r in logits])
+            assert np.array_equal(ids.cpu().numpy(), sel), f"block {li}: router ids"
+            gref = np.stack([onat.sigmoid(logits[t][sel[t]], FA) for t in range(sel.shape[0])])
+            assert np.array_equal(gates.cpu().numpy(), gref), f"block {li}: gates"
+            ref = np.zeros((xn.shape[0], D_MODEL), dtype=object)
+            for t in range(xn.shape[0]):
+                for j, e in enumerate(sel[t]):
+                    gw = device.export_weight(hs["gate"][e], E_FFN, nb_in, o.Q4_K)
+                    uw = device.export_weight(hs["up"][e], E_FFN, nb_in, o.Q4_K)
+                    dw = device.export_weight(hs["down"][e], D_MODEL, nb_dn, o.Q6_K)
+                    g = onat.silu(onat.qk_linear(gw, hn[t:t + 1], E_FFN, nb_in, FW, o.Q4_K), FA)
+                    u = onat.qk_linear(uw, hn[t:t + 1], E_FFN, nb_in, FW, o.Q4_K)
+                    dn = onat.qk_linear(dw, o.mul_shift(g, u, FA), D_MODEL, nb_dn, FW, o.Q6_K)[0].astype(object)
+                    ref[t] += (dn * int(gref[t, j])) >> FA
+            assert np.array_equal(out.cpu().numpy(), ref.astype(np.int64)), f"block {li}: block output"
+            checked += 1
+        x = x + out
+    return checked, x
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from integer_inference_engine_b200 import device, qk_cuda
+    from integer_inference_engine_b200.synth import SyntheticMoEStack
+    from oracle import qk_oracle as o
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if not qk_cuda.available():
+        raise SystemExit("CUDA library or GPU missing: there is no fallback path")
+
+    stack = SyntheticMoEStack(args.layers, D_MODEL, E_FFN, N_EXPERTS, TOP_K, seed=1 + rank, fa=FA)
+    # per-step inputs: a small table of hidden states standing in for embedding rows of sampled tokens
+    rng = np.random.default_rng(1000 + rank)
+    table_host = o.to_fixed(rng.standard_normal((16, D_MODEL)), FA)
+    table = torch.from_numpy(table_host).cuda()
+    pinned_in = torch.from_numpy(table_host).pin_memory()
+
+    checked, _ = verify_against_oracle(stack, table[:1], args.verify_layers if rank == 0 else 0)
+
+    # ---- device-resident timing: one CUDA graph per token -------------------------------------------------
+    x_static = table[:1].clone()
+    stack.decode_step(x_static.clone(), FW)                     # sizes every workspace before capture
+    torch.cuda.synchronize()
+    l0 = device.launch_count()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        x_work = x_static.clone()
+        with torch.cuda.graph(graph, stream=side):
+            x_work.copy_(x_static)
+            stack.decode_step(x_work, FW)
+    launches_per_step = device.launch_count() - l0
+    torch.cuda.synchronize()
+
+    def step(i):
+        x_static.copy_(table[i % 16:i % 16 + 1])
+        graph.replay()
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        ev0.record()
+        for i in range(args.steps):
+            step(args.warmup + i)
+        ev1.record()
+        torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    assert device.read_flags() == 0, "an activation left the exact envelope during the timed region"
+    # the graph result equals the eager, oracle-checked chain for the same input
+    step(0); torch.cuda.synchronize()
+    _, x_ref = verify_against_oracle(stack, table[:1], 0)
+    assert torch.equal(x_work, x_ref), "graph replay differs from the oracle-checked eager chain"
+
+    # ---- roofline of the dominant kernel (gate/up), timed alone over all blocks' weights -----------------
+    peak, peak_kind = measured_peak_gbs()
+    h_probe = device.rmsnorm(table[:1], stack.gains[0], FA, 1)
+    outs = torch.zeros_like(h_probe)
+    for layer in stack.layers:                                   # leaves ids/gates/limbs of the last block in place
+        layer.forward(h_probe, FA, FW, out=outs, accumulate=True, want_routes=False)
+    torch.cuda.synchronize()
+    device.set_stage_mask(8)
+    reps = 3
+    g2 = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g2, stream=side):
+            for layer in stack.layers:
+                layer.forward(h_probe, FA, FW, out=outs, accumulate=True, want_routes=False)
+    device.set_stage_mask(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g2.replay()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        g2.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    device.read_flags()
+    gateup_ms = e0.elapsed_time(e1) / (reps * len(stack.layers))
+    gateup_bytes = TOP_K * 2 * E_FFN * (D_MODEL // 256) * 144
+    achieved = gateup_bytes / (gateup_ms * 1e-3) / 1e9
+
+    # ---- end to end through the host-buffer C-ABI call ----------------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        def host_step(i):
+            x = pinned_in[i % 16:i % 16 + 1].numpy()
+            for li, layer in enumerate(stack.layers):
+                res = qk_cuda.moe_block(layer.handle, x, TOP_K, FA, FW, gain_handle=stack.gains[li])
+                assert res is not None
+                x = res[0]
+            return x
+        got = host_step(0)
+        assert np.array_equal(got, x_ref.cpu().numpy()), "host-buffer path differs from the device path"
+        n_e2e = max(2, min(args.steps, 8))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(n_e2e):
+            host_step(i)
+        e2e_s = (time.perf_counter() - t0) / n_e2e
+        if world > 1:
+            t = torch.tensor([e2e_s], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t.item())
+        e2e = {"value": world / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": args.layers * D_MODEL * 8,
+               "d2h_bytes_per_step": args.layers * (D_MODEL * 8 + TOP_K * 12), "steps": n_e2e}
+
+    if rank != 0:
+        return
+    cpu = None
+    if world == 1 or rank == 0:
+        n_cpu = min(args.cpu_sample_layers, args.layers)
+        per_layer = cpu_moe_block_time("port", n_cpu, 3)
+        cpu = {"value": 1.0 / (per_layer * args.layers), "unit": "tok/s", "cores": host_cores(), "kind": "port",
+               "sample": f"{n_cpu} blocks x 1 token, median of 3, scaled to {args.layers} blocks"}
+    ms_step = ms / args.steps
+    bytes_tok = stack.weight_bytes_per_token()
+    print(json.dumps({
+        "metric": "decode_tok_per_s", "value": world * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers": args.layers, "parallelism": f"replicas x{world}",
+                   "l2": "inputs larger than L2: each step streams %d MB of distinct weights" % (bytes_tok // 2**20),
+                   "weight_bytes_per_token": bytes_tok, "step_hbm_frac_of_%s_peak" % peak_kind:
+                       bytes_tok / (ms_step * 1e-3) / 1e9 / peak,
+                   "oracle_checked_blocks": checked},
+        "clocks": clk.summary(),
+        "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps),
+        "roofline": {"bound": "hbm", "kernel": "skinny_kernel<Q4_K, GATEUP>", "achieved": achieved, "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "bytes_per_launch": gateup_bytes, "ms_per_launch": gateup_ms},
+        "cpu_baseline": cpu,
+    }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -125,8 +125,27 @@ void iie_moe_layer_destroy(long long layer);
 int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long long T, int fa, int fw, int accumulate,
                         int64_t *out_dev, int *ids_dev, int64_t *gates_dev, void *stream);
 
+/* The same block on HOST buffers in one call (one upload, one download): out = moe(x) when
+ * gain_h < 0, else out = x + moe(rmsnorm(x, gain)) -- the parallel-residual form of the reference's
+ * MoE block without its attention term.  ids_out / gates_out may be NULL.  rc 3: an input left the
+ * exact envelope and nothing was written. */
+int iie_moe_block_host(long long layer, long long gain_h, const int64_t *x, long long T, int fa, int fw,
+                       unsigned long long eps, int64_t *out, int *ids_out, int64_t *gates_out);
+
 /* Plain resident product on device tensors: out_dev [T,out_f] = floor(x_dev W^T / 2^fw). */
 int iie_apply_dev(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev, void *stream);
+
+/* Integer RMSNorm on device tensors: out = ((x << fa) // isqrt(sum(x^2)//width + eps)) * gain >> fa.
+ * gain_h is a dense int64 handle of one row, or -1 for no gain.  Rows outside the exact envelope
+ * raise flag bit 1.  (Arithmetic of north-mini-code/src/nmc/_bonsai/fixedpoint.py:32-72.) */
+int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long rows, long long width, int fa,
+                    unsigned long long eps, int64_t *out_dev, void *stream);
+
+/* Profiling hooks: restrict iie_moe_forward_dev to a subset of its stages (bit 0 limb planes,
+ * 1 router product, 2 top-k, 3 gate/up, 4 down; 0 = all) so that one kernel can be timed alone on
+ * data left by a previous full call; and the number of kernels launched since load. */
+void iie_profile_stage_mask(int mask);
+unsigned long long iie_launch_count(void);
 
 /* Read and clear the device flag word (synchronises the library stream and `stream`):
  * bit 0 an activation left the 8-limb envelope, bit 1 RMSNorm envelope, bit 2 dense router sum. */

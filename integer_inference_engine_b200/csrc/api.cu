@@ -56,10 +56,13 @@ std::vector<MoeLayer> g_layers;
 cudaStream_t g_stream = nullptr;
 int *g_flags = nullptr;               // device flag word
 int g_ready = -1;                     // -1 unknown, 0 usable, 1 unusable
+int g_stage_mask = 0;                 // profiling: when non-zero, iie_moe_forward_dev runs only these stages
+enum Stage { ST_LIMBS = 1, ST_ROUTER = 2, ST_TOPK = 4, ST_GATEUP = 8, ST_DOWN = 16 };
+inline bool stage_on(int st) { return g_stage_mask == 0 || (g_stage_mask & st); }
 
 // Persistent device scratch by role, grown on demand (never shrunk until released).
 enum Role { R_X, R_XL, R_OUT, R_RAW, R_GU, R_GUL, R_TMP0, R_TMP1, R_TMP2, R_TABS, R_META, R_LOGITS, R_IDS, R_GATES,
-            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_COUNT };
+            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_COUNT };
 struct Buf { void *p = nullptr; size_t cap = 0; };
 Buf g_buf[R_COUNT];
 long long g_ws_allocs = 0;
@@ -207,11 +210,12 @@ bool moe_fused(const MoePlan &p, const int8_t *hl, bool x_bcast_zero, const int 
     a.out_f = p.e_ffn; a.n_blocks = p.d_model / 256; a.fw = fw; a.fa = fa; a.xl = hl; a.xidx = xidx;
     a.out = nullptr; a.out_limbs = gul; a.flags = g_flags;
     (void)x_bcast_zero;
-    if (launch_skinny(p.gate_q, MODE_GATEUP, a, n_groups, max_pairs, s) != cudaSuccess) return false;
+    if (stage_on(ST_GATEUP) && launch_skinny(p.gate_q, MODE_GATEUP, a, n_groups, max_pairs, s) != cudaSuccess) return false;
     SkinnyArgs d = {};
     d.wa = p.down; d.wb = p.down; d.grp_expert = grp_expert; d.grp_off = grp_off; d.pairs_per_group = 1;
     d.out_f = p.d_model; d.n_blocks = p.e_ffn / 256; d.fw = fw; d.fa = fa; d.xl = gul; d.xidx = nullptr;
     d.out = out; d.gates = pair_gate; d.pair_tok = pair_tok; d.flags = g_flags;
+    if (!stage_on(ST_DOWN)) return true;
     return launch_skinny(p.down_q, MODE_DOWN, d, n_groups, max_pairs, s) == cudaSuccess;
 }
 
@@ -621,18 +625,22 @@ extern "C" int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long l
     int *ids = ids_dev ? ids_dev : (int *)ensure(R_IDS, (size_t)P * sizeof(int));
     int64_t *gates = gates_dev ? gates_dev : (int64_t *)ensure(R_GATES, (size_t)P * 8);
     if (!hl || !lg || !ids || !gates) return 1;
-    if (launch_limbs(h_dev, T, L.d_model, hl, g_flags, s) != cudaSuccess) return 1;
-    if (r.qtype == QT_I64) {
-        if (launch_exact_dense((const int64_t *)r.d, E, L.d_model, h_dev, T, fw, lg, g_flags, s) != cudaSuccess) return 1;
-    } else if (!linear_dev(r, h_dev, T, fw, lg, false, s, hl)) return 1;
-    if (launch_topk(lg, T, E, k, fa, ids, gates, s) != cudaSuccess) return 1;
+    if (stage_on(ST_LIMBS) && launch_limbs(h_dev, T, L.d_model, hl, g_flags, s) != cudaSuccess) return 1;
+    if (stage_on(ST_ROUTER)) {
+        if (r.qtype == QT_I64) {
+            if (launch_exact_dense((const int64_t *)r.d, E, L.d_model, h_dev, T, fw, lg, g_flags, s) != cudaSuccess) return 1;
+        } else if (!linear_dev(r, h_dev, T, fw, lg, false, s, hl)) return 1;
+    }
+    if (stage_on(ST_TOPK) && launch_topk(lg, T, E, k, fa, ids, gates, s) != cudaSuccess) return 1;
     if (!accumulate && cudaMemsetAsync(out_dev, 0, (size_t)T * L.d_model * 8, s) != cudaSuccess) return 1;
     MoePlan plan = {L.tabs, L.tabs + E, L.tabs + 2 * E, L.gate_q, L.down_q, L.d_model, L.e_ffn};
     bool ok;
     if (T == 1) {
         // the k selected experts are the groups; every pair reads token 0's limb planes
-        int *zero = (int *)ensure(R_PAIRTOK, std::max<size_t>((size_t)P, 64) * sizeof(int));
-        if (!zero || cudaMemsetAsync(zero, 0, (size_t)P * sizeof(int), s) != cudaSuccess) return 1;
+        const bool fresh = g_buf[R_ZERO].p == nullptr;
+        int *zero = (int *)ensure(R_ZERO, 4096 * sizeof(int));          // all-zero index table, written once
+        if (!zero || P > 4096) return 1;
+        if (fresh && (cudaMemsetAsync(zero, 0, 4096 * sizeof(int), g_stream) != cudaSuccess || !sync())) return 1;
         ok = moe_fused(plan, hl, true, zero, ids, nullptr, k, P, 1, gates, zero, fa, fw, out_dev, s);
     } else {
         int *off = (int *)ensure(R_GRPOFF, (size_t)(E + 1) * sizeof(int));
@@ -657,4 +665,54 @@ extern "C" int iie_flags_read_clear(void *stream) {
     if (!init()) return -1;
     if (stream && cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return -1;
     return read_flags_clear();
+}
+
+extern "C" int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long rows, long long width, int fa,
+                               unsigned long long eps, int64_t *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !x_dev || !out_dev || rows <= 0 || width <= 0 || fa < 1 || fa > 29) return 1;
+    const int64_t *gain = nullptr;
+    if (gain_h >= 0) {
+        if (!valid_i64(gain_h) || g_w[gain_h].out_f != 1 || g_w[gain_h].nb != width) return 1;
+        gain = (const int64_t *)g_w[gain_h].d;
+    }
+    cudaStream_t s = stream ? (cudaStream_t)stream : g_stream;
+    return launch_rmsnorm(x_dev, rows, width, gain, fa, eps, out_dev, g_flags, s) == cudaSuccess ? 0 : 1;
+}
+
+extern "C" void iie_profile_stage_mask(int mask) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    g_stage_mask = mask;
+}
+
+extern "C" unsigned long long iie_launch_count(void) { return __atomic_load_n(&iie::g_launches, __ATOMIC_RELAXED); }
+
+extern "C" int iie_moe_block_host(long long layer, long long gain_h, const int64_t *x, long long T, int fa, int fw,
+                                  unsigned long long eps, int64_t *out, int *ids_out, int64_t *gates_out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS);
+    if (!init() || layer < 0 || (size_t)layer >= g_layers.size() || !g_layers[layer].live || !x || !out || T <= 0) return 1;
+    const MoeLayer &L = g_layers[layer];
+    const size_t n = (size_t)T * L.d_model;
+    const size_t P = (size_t)T * L.top_k;
+    int64_t *xd = (int64_t *)ensure(R_X, n * 8), *od = (int64_t *)ensure(R_OUT, n * 8);
+    int64_t *hd = (int64_t *)ensure(R_HNORM, n * 8), *gd = (int64_t *)ensure(R_GATES, P * 8);
+    int *idd = (int *)ensure(R_IDS, P * sizeof(int));
+    if (!xd || !od || !hd || !gd || !idd || !h2d(xd, x, n * 8)) { cudaGetLastError(); return 1; }
+    const int64_t *h = xd;
+    int rc = 0;
+    if (gain_h >= 0) {
+        rc = iie_rmsnorm_dev(gain_h, xd, T, L.d_model, fa, eps, hd, g_stream);
+        h = hd;
+        // residual: out starts as x and the block output is added to it
+        if (rc == 0 && cudaMemcpyAsync(od, xd, n * 8, cudaMemcpyDeviceToDevice, g_stream) != cudaSuccess) rc = 1;
+    }
+    if (rc == 0) rc = iie_moe_forward_dev(layer, h, T, fa, fw, gain_h >= 0 ? 1 : 0, od, idd, gd, g_stream);
+    if (rc != 0) { cudaGetLastError(); return rc; }
+    const int f = read_flags_clear();
+    if (f < 0) return 1;
+    if (f) return 3;
+    if (!d2h(out, od, n * 8) || (ids_out && !d2h(ids_out, idd, P * sizeof(int))) ||
+        (gates_out && !d2h(gates_out, gd, P * 8)) || !sync()) { cudaGetLastError(); return 1; }
+    return 0;
 }

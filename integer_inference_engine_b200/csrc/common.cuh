@@ -81,9 +81,8 @@ __device__ __forceinline__ uint64_t balanced_digits8(int64_t x, bool &ok) {
     uint64_t packed = 0;
 #pragma unroll
     for (int l = 0; l < 8; l++) {
-        const int64_t d = (int64_t)(int8_t)(x & 0xFF);
-        packed |= (uint64_t)(uint8_t)d << (8 * l);
-        x = (x - d) >> 8;
+        packed |= (uint64_t)(x & 0xFF) << (8 * l);
+        x = (x >> 8) + ((x >> 7) & 1);          // (x - digit) / 256 without leaving int64
     }
     ok = (x == 0);
     return packed;

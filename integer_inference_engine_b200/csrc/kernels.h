@@ -5,6 +5,10 @@
 
 namespace iie {
 
+// Number of kernels this library has launched since it was loaded (benchmarks report it).
+extern unsigned long long g_launches;
+inline void note_launch(unsigned long long n = 1) { __atomic_fetch_add(&g_launches, n, __ATOMIC_RELAXED); }
+
 enum SkinnyMode { MODE_LINEAR = 0, MODE_GATEUP = 1, MODE_DOWN = 2 };
 
 // Arguments of the streamed ("skinny") fused-dequant product.  Work is organised in groups: group g

@@ -6,6 +6,8 @@
 
 namespace iie {
 
+unsigned long long g_launches = 0;
+
 namespace {
 
 // ---------------------------------------------------------------------------------------------------
@@ -292,17 +294,20 @@ cudaError_t launch_repack(const uint8_t *raw, uint8_t *dst, long long out_f, lon
                           unsigned *maxbits, cudaStream_t s) {
     const long long total = out_f * nb * (qtype == QT_Q4K ? 144 : 210);
     repack_kernel<true><<<grid_for(total, 256), 256, 0, s>>>(raw, dst, out_f, nb, qtype, maxbits);
+    note_launch();
     return cudaGetLastError();
 }
 
 cudaError_t launch_unpack(const uint8_t *src, uint8_t *raw, long long out_f, long long nb, int qtype, cudaStream_t s) {
     const long long total = out_f * nb * (qtype == QT_Q4K ? 144 : 210);
     repack_kernel<false><<<grid_for(total, 256), 256, 0, s>>>(src, raw, out_f, nb, qtype, nullptr);
+    note_launch();
     return cudaGetLastError();
 }
 
 cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, cudaStream_t s) {
     limbs_kernel<<<grid_for(n_rows * K, 256), 256, 0, s>>>(x, n_rows, K, planes, flags);
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -310,6 +315,7 @@ cudaError_t launch_exact_linear(const uint8_t *w, int qtype, long long out_f, lo
                                 long long T, int fw, int64_t *out, cudaStream_t s) {
     const long long n = out_f * T;
     exact_linear_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(w, qtype, out_f, nb, x, T, fw, out);
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -317,11 +323,13 @@ cudaError_t launch_exact_dense(const int64_t *w, long long out_f, long long in_f
                                int fw, int64_t *out, int *flags, cudaStream_t s) {
     const long long n = out_f * T * 32;
     exact_dense_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(w, out_f, in_f, x, T, fw, out, flags);
+    note_launch();
     return cudaGetLastError();
 }
 
 cudaError_t launch_silu_mul(int64_t *a, const int64_t *b, long long n, int fa, cudaStream_t s) {
     silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, n, fa);
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -329,6 +337,7 @@ cudaError_t launch_combine(const int64_t *dn, const int64_t *gates, long long T,
                            int64_t *out, cudaStream_t s) {
     const long long n = T * d_model;
     combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(dn, gates, T, k, d_model, fa, out);
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -337,12 +346,14 @@ cudaError_t launch_topk(const int64_t *logits, long long rows, int n_experts, in
     if (n_experts > 1024 || n_experts <= 0 || k <= 0) return cudaErrorInvalidValue;
     const long long n = rows * 32;
     topk_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(logits, rows, n_experts, k, fa, ids, gates);
+    note_launch();
     return cudaGetLastError();
 }
 
 cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
                            unsigned long long eps, int64_t *out, int *flags, cudaStream_t s) {
     rmsnorm_kernel<<<(unsigned)rows, 256, 0, s>>>(x, rows, width, gain, fa, eps, out, flags);
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -350,6 +361,7 @@ cudaError_t launch_dispatch(const int *ids, const int64_t *gates, long long T, i
                             int *pair_tok, int64_t *pair_gate, cudaStream_t s) {
     if (n_experts > 4096) return cudaErrorInvalidValue;
     dispatch_kernel<<<1, 1024, 2 * n_experts * sizeof(int), s>>>(ids, gates, T, k, n_experts, grp_off, pair_tok, pair_gate);
+    note_launch();
     return cudaGetLastError();
 }
 

@@ -262,6 +262,7 @@ cudaError_t launch_t(const SkinnyArgs &a, int n_groups, int max_pairs, cudaStrea
     if (max_pairs <= 1) skinny_kernel<QT, MODE, 1><<<grid, block, 0, s>>>(a);
     else if (max_pairs <= 2) skinny_kernel<QT, MODE, 2><<<grid, block, 0, s>>>(a);
     else skinny_kernel<QT, MODE, 4><<<grid, block, 0, s>>>(a);
+    note_launch();
     return cudaGetLastError();
 }
 

@@ -61,6 +61,32 @@ def apply(handle: int, x: torch.Tensor, out_f: int, fw: int) -> torch.Tensor:
     return out
 
 
+def rmsnorm(x: torch.Tensor, gain_handle: int = -1, fa: int = 16, eps: int = 1, out: torch.Tensor | None = None):
+    """Integer RMSNorm of x [rows,width] with an optional registered int64 gain row."""
+    lib = qk_cuda._lib()
+    x = x.contiguous()
+    assert x.is_cuda and x.dtype == torch.int64 and x.dim() == 2
+    if out is None:
+        out = torch.empty_like(x)
+    with _CUDA_LOCK:
+        rc = lib.iie_rmsnorm_dev(int(gain_handle), x.data_ptr(), x.shape[0], x.shape[1], int(fa), int(eps),
+                                 out.data_ptr(), _stream_ptr())
+    if rc != 0:
+        raise CudaContextError(f"device RMSNorm failed with status {rc}")
+    return out
+
+
+def launch_count() -> int:
+    """Kernels launched by the library since it was loaded."""
+    return int(qk_cuda.load_library().iie_launch_count())
+
+
+def set_stage_mask(mask: int) -> None:
+    """Profiling: restrict MoELayer.forward to a subset of its stages (0 = all)."""
+    with _CUDA_LOCK:
+        qk_cuda._lib().iie_profile_stage_mask(int(mask))
+
+
 def read_flags() -> int:
     """Read and clear the envelope flag word (synchronises): 0 means every result so far is exact."""
     with _CUDA_LOCK:

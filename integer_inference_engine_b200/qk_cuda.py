@@ -42,7 +42,8 @@ EXPORTED_SYMBOLS = (
     "qk_attention_bank_apply", "qk_attention_bank_moe_begin", "qk_attention_bank_moe_continue",
     "qk_attention_bank_moe_export", "qk_attention_bank_workspace_bytes",
     "iie_register_weight_dev", "iie_weight_export", "iie_moe_layer_create", "iie_moe_layer_destroy",
-    "iie_moe_forward_dev", "iie_apply_dev", "iie_flags_read_clear",
+    "iie_moe_forward_dev", "iie_apply_dev", "iie_flags_read_clear", "iie_rmsnorm_dev", "iie_profile_stage_mask",
+    "iie_launch_count", "iie_moe_block_host",
 )
 # The library keeps one registry and one set of workspaces per process and ctypes releases the GIL:
 # serialise callers here as the reference bridge does (qk_cuda.py:35-38).
@@ -101,6 +102,9 @@ def load_library():
         "iie_moe_layer_destroy": ([i64], None),
         "iie_moe_forward_dev": ([i64, vp, i64, c_int, c_int, c_int, vp, vp, vp, vp], c_int),
         "iie_apply_dev": ([i64, vp, i64, c_int, vp, vp], c_int), "iie_flags_read_clear": ([vp], c_int),
+        "iie_rmsnorm_dev": ([i64, vp, i64, i64, c_int, u64, vp, vp], c_int),
+        "iie_profile_stage_mask": ([c_int], None), "iie_launch_count": ([], u64),
+        "iie_moe_block_host": ([i64, i64, vp, i64, c_int, c_int, u64, vp, vp, vp], c_int),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)
@@ -484,3 +488,23 @@ def profile_snapshot() -> dict:
     if n != len(_PROFILE_METRICS):
         raise CudaContextError("profile snapshot size mismatch")
     return {name: int(buf[i]) for i, name in enumerate(_PROFILE_METRICS)}
+
+
+def moe_block(layer_handle: int, x_int, n_used: int, fa: int, fw: int, gain_handle: int = -1, eps: int = 1):
+    """Whole MoE block on host arrays in one native call: ``moe(x)`` or, with a gain handle,
+    ``x + moe(rmsnorm(x, gain))``.  Returns (out [T,d], ids [T,k] int32, gates [T,k]) or ``None`` when an
+    input leaves the exact envelope.  Additive entry (no counterpart in the reference bridge): it
+    replaces the per-layer sequence rmsnorm_router + moe_ffn with one upload and one download."""
+    lib = _lib()
+    x = _x2d(x_int)
+    out = np.empty_like(x)
+    ids = np.empty((x.shape[0], int(n_used)), np.int32)
+    gates = np.empty((x.shape[0], int(n_used)), np.int64)
+    with _CUDA_LOCK:
+        rc = lib.iie_moe_block_host(int(layer_handle), int(gain_handle), x.ctypes.data, x.shape[0], int(fa), int(fw),
+                                    int(eps), out.ctypes.data, ids.ctypes.data, gates.ctypes.data)
+    if rc == 3:
+        return None
+    if rc != 0:
+        raise CudaContextError(f"MoE block failed with native status {rc}")
+    return out, ids, gates

@@ -274,9 +274,8 @@ def balanced_limbs(x, n_limbs: int) -> np.ndarray:
     v = np.asarray(x, np.int64).copy()
     out = np.empty((n_limbs,) + v.shape, np.int8)
     for l in range(n_limbs):
-        d = v.astype(np.int8)
-        out[l] = d
-        v = (v - d.astype(np.int64)) >> 8
+        out[l] = v.astype(np.int8)
+        v = (v >> 8) + ((v >> 7) & 1)               # (v - digit) / 256 without leaving int64
     return out
 
 
