@@ -354,7 +354,7 @@ def run_ours(args):
     if rank != 0:
         return
     cpu = None
-    if world == 1 or rank == 0:
+    if args.cpu_sample_layers > 0:
         n_cpu = min(args.cpu_sample_layers, args.layers)
         per_layer = cpu_moe_block_time("port", n_cpu, 3)
         cpu = {"value": 1.0 / (per_layer * args.layers), "unit": "tok/s", "cores": host_cores(), "kind": "port",

@@ -125,6 +125,12 @@ void iie_moe_layer_destroy(long long layer);
 int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long long T, int fa, int fw, int accumulate,
                         int64_t *out_dev, int *ids_dev, int64_t *gates_dev, void *stream);
 
+/* The block with its normalisation and residual on device tensors: out = moe(x) when gain_h < 0, else
+ * out = x + moe(rmsnorm(x, gain)).  A single token with a quantised router takes three launches
+ * (fused routing, gate/up, down); out_dev may alias x_dev. */
+int iie_moe_block_dev(long long layer, long long gain_h, const int64_t *x_dev, long long T, int fa, int fw,
+                      unsigned long long eps, int64_t *out_dev, int *ids_dev, int64_t *gates_dev, void *stream);
+
 /* The same block on HOST buffers in one call (one upload, one download): out = moe(x) when
  * gain_h < 0, else out = x + moe(rmsnorm(x, gain)) -- the parallel-residual form of the reference's
  * MoE block without its attention term.  ids_out / gates_out may be NULL.  rc 3: an input left the

@@ -55,6 +55,7 @@ std::vector<Weight> g_w;
 std::vector<MoeLayer> g_layers;
 cudaStream_t g_stream = nullptr;
 int *g_flags = nullptr;               // device flag word
+int *g_cells = nullptr;               // device ints: [0] limbs of h, [1] limbs of gate*up, [2] routing ticket
 int g_ready = -1;                     // -1 unknown, 0 usable, 1 unusable
 int g_stage_mask = 0;                 // profiling: when non-zero, iie_moe_forward_dev runs only these stages
 enum Stage { ST_LIMBS = 1, ST_ROUTER = 2, ST_TOPK = 4, ST_GATEUP = 8, ST_DOWN = 16 };
@@ -72,7 +73,8 @@ bool init() {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) { cudaGetLastError(); g_ready = 1; return false; }
     if (cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaMalloc(&g_flags, sizeof(int)) != cudaSuccess || cudaMemset(g_flags, 0, sizeof(int)) != cudaSuccess) {
+        cudaMalloc(&g_flags, sizeof(int)) != cudaSuccess || cudaMemset(g_flags, 0, sizeof(int)) != cudaSuccess ||
+        cudaMalloc(&g_cells, 64) != cudaSuccess || cudaMemset(g_cells, 0, 64) != cudaSuccess) {
         cudaGetLastError(); g_ready = 1; return false;
     }
     g_ready = 0;
@@ -239,6 +241,36 @@ bool moe_exact_pairs(const std::vector<const Weight *> &gw, const std::vector<co
         if (launch_exact_linear((const uint8_t *)dw[i]->d, dw[i]->qtype, d_model, dw[i]->nb, g + i * e_ffn, 1, fw,
                                 dn + i * d_model, g_stream) != cudaSuccess) return false;
     return launch_combine(dn, gates_dev, T, k, d_model, fa, out_dev, g_stream) == cudaSuccess;
+}
+
+// Single-token fused path: route (optional RMSNorm, limbs, router, top-k) -> gate/up -> down.
+// init_mode: 0 leave `out`, 1 zero it, 2 start from x (residual).  Requires a quantised router.
+bool moe_decode_token(const MoeLayer &L, const int64_t *x, const int64_t *gain, int fa, int fw, unsigned long long eps,
+                      int init_mode, int64_t *out, int *ids, int64_t *gates, cudaStream_t s) {
+    const Weight &r = g_w[L.router];
+    const int E = L.n_experts, k = L.top_k;
+    int8_t *hl = (int8_t *)ensure(R_XL, (size_t)8 * L.d_model);
+    int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)E * 8);
+    int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)k * 8 * L.e_ffn);
+    if (!hl || !lg || !gul) return false;
+    RouteArgs ra = {};
+    ra.x = x; ra.gain = gain; ra.d = (int)L.d_model; ra.fa = fa; ra.fw = fw; ra.eps = eps;
+    ra.router = (const uint8_t *)r.d; ra.router_q = r.qtype; ra.n_experts = E; ra.k = k;
+    ra.hl = hl; ra.h_nl = g_cells; ra.h_out = nullptr; ra.logits = lg; ra.ids = ids; ra.gates = gates;
+    ra.init_out = out; ra.init_mode = init_mode; ra.gu_nl = g_cells + 1; ra.counter = (unsigned *)(g_cells + 2);
+    ra.flags = g_flags;
+    if (stage_on(ST_ROUTER) && launch_route(ra, s) != cudaSuccess) return false;
+    StreamArgs ga = {};
+    ga.wa = L.tabs; ga.wb = L.tabs + E; ga.sel = ids; ga.n_sel = k; ga.out_f = L.e_ffn; ga.n_blocks = L.d_model / 256;
+    ga.fw = fw; ga.fa = fa; ga.xl = hl; ga.x_per_sel = 0; ga.x_nl = g_cells; ga.out = nullptr; ga.out_limbs = gul;
+    ga.out_nl = g_cells + 1; ga.flags = g_flags;
+    if (stage_on(ST_GATEUP) && launch_stream(L.gate_q, MODE_GATEUP, ga, s) != cudaSuccess) return false;
+    StreamArgs da = {};
+    da.wa = L.tabs + 2 * E; da.wb = da.wa; da.sel = ids; da.n_sel = k; da.out_f = L.d_model; da.n_blocks = L.e_ffn / 256;
+    da.fw = fw; da.fa = fa; da.xl = gul; da.x_per_sel = 1; da.x_nl = g_cells + 1; da.out = out; da.gates = gates;
+    da.flags = g_flags;
+    if (stage_on(ST_DOWN) && launch_stream(L.down_q, MODE_DOWN, da, s) != cudaSuccess) return false;
+    return true;
 }
 
 // Shared implementation of qk_moe_ffn (m = 1, k = n_e) and qk_moe_ffn_batched.
@@ -620,6 +652,13 @@ extern "C" int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long l
         !fast_envelope(L.down_q, L.e_ffn / 256, L.maxd_down, L.maxdmin_down, fw)) return 3;
     const int E = L.n_experts, k = L.top_k;
     const long long P = T * k;
+    if (T == 1 && r.qtype != QT_I64 && L.d_model <= 8192 && k <= 32) {
+        int *ids1 = ids_dev ? ids_dev : (int *)ensure(R_IDS, (size_t)P * sizeof(int));
+        int64_t *gates1 = gates_dev ? gates_dev : (int64_t *)ensure(R_GATES, (size_t)P * 8);
+        if (!ids1 || !gates1) return 1;
+        if (!moe_decode_token(L, h_dev, nullptr, fa, fw, 0, accumulate ? 0 : 1, out_dev, ids1, gates1, s)) { cudaGetLastError(); return 1; }
+        return 0;
+    }
     int8_t *hl = (int8_t *)ensure(R_XL, (size_t)T * 8 * L.d_model);
     int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)T * E * 8);
     int *ids = ids_dev ? ids_dev : (int *)ensure(R_IDS, (size_t)P * sizeof(int));
@@ -687,6 +726,39 @@ extern "C" void iie_profile_stage_mask(int mask) {
 
 extern "C" unsigned long long iie_launch_count(void) { return __atomic_load_n(&iie::g_launches, __ATOMIC_RELAXED); }
 
+extern "C" int iie_moe_block_dev(long long layer, long long gain_h, const int64_t *x_dev, long long T, int fa, int fw,
+                                 unsigned long long eps, int64_t *out_dev, int *ids_dev, int64_t *gates_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || layer < 0 || (size_t)layer >= g_layers.size() || !g_layers[layer].live || !x_dev || !out_dev ||
+        T <= 0 || fa < 1 || fa > 29) return 1;
+    const MoeLayer &L = g_layers[layer];
+    cudaStream_t s = stream ? (cudaStream_t)stream : g_stream;
+    if (!fast_envelope(L.gate_q, L.d_model / 256, L.maxd_gate, L.maxdmin_gate, fw) ||
+        !fast_envelope(L.down_q, L.e_ffn / 256, L.maxd_down, L.maxdmin_down, fw)) return 3;
+    const int64_t *gain = nullptr;
+    if (gain_h >= 0) {
+        if (!valid_i64(gain_h) || g_w[gain_h].out_f != 1 || g_w[gain_h].nb != L.d_model) return 1;
+        gain = (const int64_t *)g_w[gain_h].d;
+    }
+    const size_t n = (size_t)T * L.d_model, P = (size_t)T * L.top_k;
+    if (T == 1 && g_w[L.router].qtype != QT_I64 && L.d_model <= 8192 && L.top_k <= 32) {
+        int *ids = ids_dev ? ids_dev : (int *)ensure(R_IDS, P * sizeof(int));
+        int64_t *gates = gates_dev ? gates_dev : (int64_t *)ensure(R_GATES, P * 8);
+        if (!ids || !gates) return 1;
+        const int init_mode = gain ? (out_dev == x_dev ? 0 : 2) : 1;
+        if (!moe_decode_token(L, x_dev, gain, fa, fw, eps, init_mode, out_dev, ids, gates, s)) { cudaGetLastError(); return 1; }
+        return 0;
+    }
+    const int64_t *h = x_dev;
+    if (gain) {
+        int64_t *hd = (int64_t *)ensure(R_HNORM, n * 8);
+        if (!hd || launch_rmsnorm(x_dev, T, L.d_model, gain, fa, eps, hd, g_flags, s) != cudaSuccess) return 1;
+        h = hd;
+        if (out_dev != x_dev && cudaMemcpyAsync(out_dev, x_dev, n * 8, cudaMemcpyDeviceToDevice, s) != cudaSuccess) return 1;
+    }
+    return iie_moe_forward_dev(layer, h, T, fa, fw, gain ? 1 : 0, out_dev, ids_dev, gates_dev, s);
+}
+
 extern "C" int iie_moe_block_host(long long layer, long long gain_h, const int64_t *x, long long T, int fa, int fw,
                                   unsigned long long eps, int64_t *out, int *ids_out, int64_t *gates_out) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
@@ -696,18 +768,10 @@ extern "C" int iie_moe_block_host(long long layer, long long gain_h, const int64
     const size_t n = (size_t)T * L.d_model;
     const size_t P = (size_t)T * L.top_k;
     int64_t *xd = (int64_t *)ensure(R_X, n * 8), *od = (int64_t *)ensure(R_OUT, n * 8);
-    int64_t *hd = (int64_t *)ensure(R_HNORM, n * 8), *gd = (int64_t *)ensure(R_GATES, P * 8);
+    int64_t *gd = (int64_t *)ensure(R_GATES, P * 8);
     int *idd = (int *)ensure(R_IDS, P * sizeof(int));
-    if (!xd || !od || !hd || !gd || !idd || !h2d(xd, x, n * 8)) { cudaGetLastError(); return 1; }
-    const int64_t *h = xd;
-    int rc = 0;
-    if (gain_h >= 0) {
-        rc = iie_rmsnorm_dev(gain_h, xd, T, L.d_model, fa, eps, hd, g_stream);
-        h = hd;
-        // residual: out starts as x and the block output is added to it
-        if (rc == 0 && cudaMemcpyAsync(od, xd, n * 8, cudaMemcpyDeviceToDevice, g_stream) != cudaSuccess) rc = 1;
-    }
-    if (rc == 0) rc = iie_moe_forward_dev(layer, h, T, fa, fw, gain_h >= 0 ? 1 : 0, od, idd, gd, g_stream);
+    if (!xd || !od || !gd || !idd || !h2d(xd, x, n * 8)) { cudaGetLastError(); return 1; }
+    const int rc = iie_moe_block_dev(layer, gain_h, xd, T, fa, fw, eps, od, idd, gd, g_stream);
     if (rc != 0) { cudaGetLastError(); return rc; }
     const int f = read_flags_clear();
     if (f < 0) return 1;

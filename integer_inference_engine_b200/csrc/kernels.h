@@ -36,6 +36,49 @@ struct SkinnyArgs {
 cudaError_t launch_skinny(int qtype, int mode, const SkinnyArgs &a, int n_groups, int max_pairs_per_group,
                           cudaStream_t s);
 
+// Single-token streaming product (stream.cu).  Work = n_sel selected matrices x their 16-row tiles.
+struct StreamArgs {
+    const uint8_t *const *wa;      // per matrix: repacked weight (linear/down weight, or gate)
+    const uint8_t *const *wb;      // per matrix: up weight (MODE_GATEUP)
+    const int *sel;                // [n_sel] matrix indices on the device, or nullptr (identity)
+    int n_sel;
+    int tiles_per_expert, tiles_per_cta;   // filled in by the launcher
+    long long out_f, n_blocks;
+    int fw, fa;
+    const int8_t *xl;              // limb planes [8][K] (shared) or [n_sel][8][K]
+    int x_per_sel;
+    const int *x_nl;               // device: limbs in use by x (<= 4 enables the half-column path), or nullptr
+    int64_t *out;                  // LINEAR [n_sel][out_f]; GATEUP gu [n_sel][out_f] (nullable); DOWN [out_f] accumulated
+    int8_t *out_limbs;             // GATEUP: limb planes of gu [n_sel][8][out_f]
+    int *out_nl;                   // GATEUP: atomicMax of the limbs gu needs
+    const int64_t *gates;          // DOWN: [n_sel]
+    int *flags;                    // bit 0 limb envelope, bit 3 a copy never arrived
+};
+cudaError_t launch_stream(int qtype, int mode, const StreamArgs &a, cudaStream_t s);
+
+// Fused single-token routing (route.cu): optional RMSNorm, limb planes, quantised router product,
+// top-k + sigmoid gates, and initialisation of the block's output row.
+struct RouteArgs {
+    const int64_t *x;              // [d] input row
+    const int64_t *gain;           // [d] RMSNorm gain, or nullptr (no normalisation: h = x)
+    int d, fa, fw;
+    unsigned long long eps;
+    const uint8_t *router;         // repacked quantised router [n_experts, d]
+    int router_q, n_experts, k;
+    int8_t *hl;                    // out: limb planes of h [8][d]
+    int *h_nl;                     // out: limbs in use by h
+    int64_t *h_out;                // out (nullable): h as int64
+    int64_t *logits;               // scratch [n_experts]
+    int *ids;                      // out [k]
+    int64_t *gates;                // out [k]
+    int64_t *init_out;             // nullable: row to initialise for the down stage
+    int init_mode;                 // 0 leave, 1 zero, 2 copy x (residual)
+    int *gu_nl;                    // zeroed here for the following gate/up kernel
+    unsigned *counter;             // zero-initialised ticket for last-CTA detection (self-resetting)
+    int *flags;                    // bit 0 limb envelope, bit 1 RMSNorm envelope
+};
+cudaError_t launch_route(const RouteArgs &a, cudaStream_t s);
+
 // Re-order raw GGUF blocks into the half-tile layout; also reduces max |d| and max |dmin| half bit
 // patterns (sign stripped) into maxbits[0..1] (device memory, caller zeroes).
 cudaError_t launch_repack(const uint8_t *raw, uint8_t *dst, long long out_f, long long n_blocks, int qtype,

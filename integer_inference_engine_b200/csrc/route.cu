@@ -1,0 +1,224 @@
+// Fused single-token routing: RMSNorm -> limb planes -> quantised router product -> top-k with
+// lowest-index tie-break -> sigmoid gates, in one launch.
+//
+// Replaces the reference's five-launch sequence rmsnorm_fast_u64_k / rmsnorm_exact_k /
+// router_fast_i64_k / router_i64_k / topk_lowidx_k (north-mini-code/tools/nmc_qk_cuda.cu:434-657,
+// host entry :1116-1173) for the configuration in which the router itself is a Q4_K / Q6_K tensor.
+// Arithmetic: north-mini-code/src/nmc/_bonsai/fixedpoint.py:32-72 (RMSNorm), cohere2.py:162-180
+// (routing).  Every CTA recomputes the (tiny) normalisation so that no grid-wide barrier is needed
+// before the router rows; the CTA that finishes last performs the top-k.
+#include "kernels.h"
+#include "layout.cuh"
+#include "mma_items.cuh"
+
+namespace iie {
+
+namespace {
+
+constexpr int RT_THREADS = 256;
+constexpr int RT_MAX_D = 8192;            // elements of one row staged per CTA
+constexpr int RT_PAD = 32;                // plane padding (bytes): keeps the 8 limb planes on different banks
+
+__device__ __forceinline__ unsigned long long uabs64(int64_t v) { return v < 0 ? (0ULL - (unsigned long long)v) : (unsigned long long)v; }
+
+__device__ u128 isqrt128(u128 v) {
+    if (v < ((u128)1 << 62)) {             // common case: exact from a double estimate plus a fix-up
+        const unsigned long long x = (unsigned long long)v;
+        unsigned long long r = (unsigned long long)sqrt((double)x);
+        while (r * r > x) r--;
+        while ((r + 1) * (r + 1) <= x) r++;
+        return r;
+    }
+    u128 res = 0, bit = (u128)1 << 126;
+    while (bit > v) bit >>= 2;
+    while (bit != 0) {
+        if (v >= res + bit) { v -= res + bit; res = (res >> 1) + bit; } else res >>= 1;
+        bit >>= 2;
+    }
+    return res;
+}
+
+template <int QT>
+__global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int d = a.d, stride = d + RT_PAD;
+    int8_t *planes = reinterpret_cast<int8_t *>(smem);                       // [8][stride]
+    __shared__ unsigned long long s_lo[RT_THREADS / 32], s_hi[RT_THREADS / 32], s_max[RT_THREADS / 32], s_gmax[RT_THREADS / 32];
+    __shared__ unsigned long long s_rms, s_gm;
+    __shared__ int s_bad, s_nl, s_last;
+    __shared__ unsigned long long red[16][8];
+    __shared__ int64_t s_logits[1024];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
+    const int nb = d / 256;
+
+    if (tid == 0) { s_bad = 0; s_nl = 1; s_last = 0; }
+    for (int i = tid; i < 128; i += RT_THREADS) (&red[0][0])[i] = 0ULL;
+
+    // ---- sum of squares and magnitudes --------------------------------------------------------------------
+    u128 ssq = 0; unsigned long long mx = 0, gmx = 0;
+    if (a.gain) {
+        for (int i = tid; i < d; i += RT_THREADS) {
+            const unsigned long long v = uabs64(a.x[i]);
+            ssq += (u128)v * v;
+            mx = v > mx ? v : mx;
+            const unsigned long long gv = uabs64(a.gain[i]);
+            gmx = gv > gmx ? gv : gmx;
+        }
+        unsigned long long lo = (unsigned long long)ssq, hi = (unsigned long long)(ssq >> 64);
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) {
+            const unsigned long long lo2 = __shfl_xor_sync(0xffffffffu, lo, s), hi2 = __shfl_xor_sync(0xffffffffu, hi, s);
+            const u128 sum = (((u128)hi << 64) | lo) + (((u128)hi2 << 64) | lo2);
+            lo = (unsigned long long)sum; hi = (unsigned long long)(sum >> 64);
+            const unsigned long long m2 = __shfl_xor_sync(0xffffffffu, mx, s), g2 = __shfl_xor_sync(0xffffffffu, gmx, s);
+            mx = m2 > mx ? m2 : mx; gmx = g2 > gmx ? g2 : gmx;
+        }
+        if (lane == 0) { s_lo[warp] = lo; s_hi[warp] = hi; s_max[warp] = mx; s_gmax[warp] = gmx; }
+        __syncthreads();
+        if (tid == 0) {
+            u128 total = 0; unsigned long long m = 0, gm = 0;
+            for (int i = 0; i < RT_THREADS / 32; i++) {
+                total += ((u128)s_hi[i] << 64) | s_lo[i];
+                m = s_max[i] > m ? s_max[i] : m; gm = s_gmax[i] > gm ? s_gmax[i] : gm;
+            }
+            if (m > (1ULL << 57)) s_bad = 1;                 // keeps the 128-bit sum of squares exact
+            u128 mean;
+            if ((total >> 64) == 0) mean = (u128)((unsigned long long)total / (unsigned long long)d);
+            else mean = total / (u128)(unsigned long long)d;
+            const u128 rms = isqrt128(mean + a.eps);
+            if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) s_bad = 1;
+            s_rms = (unsigned long long)rms; s_gm = gm;
+        }
+    }
+    __syncthreads();
+    if (s_bad) { if (tid == 0 && blockIdx.x == 0) atomicOr(a.flags, 2); return; }
+
+    // ---- normalise, apply the gain, split into limb planes ---------------------------------------------
+    const unsigned long long rms = s_rms, gm = s_gm;
+    bool bad = false, over = false;
+    int nl = 1;
+    for (int i = tid; i < d; i += RT_THREADS) {
+        const int64_t xv = a.x[i];
+        int64_t y = xv;
+        if (a.gain) {
+            const unsigned long long ax = uabs64(xv);
+            if (ax < (1ULL << (62 - a.fa))) {               // 64-bit floor division
+                const long long num = xv * ((long long)1 << a.fa);
+                long long q = num / (long long)rms;
+                if (num < 0 && q * (long long)rms != num) q -= 1;
+                y = q;
+            } else {
+                const i128 num = (i128)xv * ((i128)1 << a.fa);
+                i128 q = num / (i128)rms;
+                if (num < 0 && q * (i128)rms != num) q -= 1;
+                if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; q = 0; }
+                y = (int64_t)q;
+            }
+            if ((u128)uabs64(y) * gm > (u128)INT64_MAX) bad = true;      // the oracle refuses such a gain product
+            y = mul_shift(y, a.gain[i], a.fa);
+        }
+        bool ok;
+        const uint64_t dg = balanced_digits8(y, ok);
+        over |= !ok;
+        nl = max(nl, digits_used(dg));
+#pragma unroll
+        for (int l = 0; l < 8; l++) planes[l * stride + i] = (int8_t)(dg >> (8 * l));
+        if (blockIdx.x == 0) {
+#pragma unroll
+            for (int l = 0; l < 8; l++) a.hl[(long long)l * d + i] = (int8_t)(dg >> (8 * l));
+            if (a.h_out) a.h_out[i] = y;
+            if (a.init_out && a.init_mode) a.init_out[i] = a.init_mode == 2 ? xv : 0;
+        }
+    }
+    if (bad) atomicOr(a.flags, 2);
+    if (over) atomicOr(a.flags, 1);
+    atomicMax(&s_nl, nl);
+    __syncthreads();
+    if (blockIdx.x == 0 && tid == 0) { *a.h_nl = s_nl; if (a.gu_nl) *a.gu_nl = 0; }
+    const bool half = s_nl <= 4;
+
+    // ---- router rows of this CTA: one 16-row tile, K split over the warps ------------------------------
+    const long long n_ht = ((long long)a.n_experts + 7) >> 3;
+    const long long htA = 2LL * blockIdx.x, htB = htA + 1 < n_ht ? htA + 1 : htA;
+    const int g = lane >> 2, t = lane & 3;
+    int64_t acc[4] = {0, 0, 0, 0};
+    for (int b = warp; b < nb; b += RT_THREADS / 32) {
+        uint32_t bf[16];
+        load_bfrag<QT, false>(planes + col_limb(g) * stride + b * 256, t, bf);
+        const uint8_t *ua = a.router + (htA * nb + b) * HTB, *ub = a.router + (htB * nb + b) * HTB;
+        if (QT == QT_Q4K) item_q4k(ua, ub, lane, a.fw, bf, half, acc);
+        else              item_q6k(ua, ub, lane, a.fw, bf, half, acc);
+    }
+    atomicAdd(&red[g][2 * t], (unsigned long long)acc[0]);
+    atomicAdd(&red[g + 8][2 * t], (unsigned long long)acc[2]);
+    if (!half) {
+        atomicAdd(&red[g][2 * t + 1], (unsigned long long)acc[1]);
+        atomicAdd(&red[g + 8][2 * t + 1], (unsigned long long)acc[3]);
+    }
+    __syncthreads();
+    if (tid < 16) {
+        const long long row = (tid < 8 ? htA : htB) * 8 + (tid & 7);
+        if (row < a.n_experts && (tid < 8 || htB != htA)) a.logits[row] = recombine_cols(red[tid], a.fw);
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned ticket = atomicAdd(a.counter, 1u);
+        if (ticket == gridDim.x - 1) { s_last = 1; *a.counter = 0; }
+    }
+    __syncthreads();
+    if (!s_last) return;
+
+    // ---- last CTA: top-k (descending, lowest index on ties) and sigmoid gates --------------------------
+    __threadfence();
+    for (int i = tid; i < a.n_experts; i += RT_THREADS) s_logits[i] = *((volatile int64_t *)&a.logits[i]);
+    __syncthreads();
+    if (warp == 0) {
+        unsigned taken = 0;
+        int64_t my_val = 0; int my_id = -1;                  // lane r keeps the r-th pick
+        for (int r = 0; r < a.k; r++) {
+            int64_t best = INT64_MIN; int best_id = 0x7fffffff;
+            for (int i = 0, e = lane; e < a.n_experts; i++, e += 32) {
+                if (taken & (1u << i)) continue;
+                const int64_t v = s_logits[e];
+                if (best_id == 0x7fffffff || v > best) { best = v; best_id = e; }
+            }
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) {
+                const int64_t ov = __shfl_xor_sync(0xffffffffu, best, s);
+                const int oi = __shfl_xor_sync(0xffffffffu, best_id, s);
+                if (oi != 0x7fffffff && (best_id == 0x7fffffff || ov > best || (ov == best && oi < best_id))) { best = ov; best_id = oi; }
+            }
+            if (best_id != 0x7fffffff && (best_id & 31) == lane) taken |= 1u << (best_id >> 5);
+            if ((r & 31) == lane) { my_val = best; my_id = best_id == 0x7fffffff ? -1 : best_id; }
+            if (r >= 32 && (r & 31) == 31) { /* k > 32 is handled by the generic top-k kernel */ }
+        }
+        if (lane < a.k) {
+            a.ids[lane] = my_id;
+            a.gates[lane] = my_id < 0 ? 0 : sigmoid_fixed(my_val, a.fa);
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_route(const RouteArgs &a, cudaStream_t s) {
+    if (a.d <= 0 || a.d % 256 || a.d > RT_MAX_D || a.n_experts <= 0 || a.n_experts > 1024 || a.k <= 0 || a.k > 32 ||
+        a.k > a.n_experts) return cudaErrorInvalidValue;
+    const unsigned grid = (unsigned)((((a.n_experts + 7) >> 3) + 1) / 2);
+    const size_t smem = (size_t)8 * (a.d + RT_PAD);
+    if (a.router_q == QT_Q4K) {
+        static bool cfg = false;
+        if (!cfg) { cudaFuncSetAttribute(route_kernel<QT_Q4K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (RT_MAX_D + RT_PAD)); cfg = true; }
+        route_kernel<QT_Q4K><<<grid, RT_THREADS, smem, s>>>(a);
+    } else if (a.router_q == QT_Q6K) {
+        static bool cfg = false;
+        if (!cfg) { cudaFuncSetAttribute(route_kernel<QT_Q6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (RT_MAX_D + RT_PAD)); cfg = true; }
+        route_kernel<QT_Q6K><<<grid, RT_THREADS, smem, s>>>(a);
+    } else return cudaErrorInvalidValue;
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace iie

@@ -1,0 +1,206 @@
+// Single-token ("decode") fused-dequant products: bulk-copy weight streaming into shared memory.
+//
+// Batch-1 decode touches each weight byte once, so the kernels are bound by HBM bandwidth and, at
+// these sizes (10-14 MB per launch), by latency.  Every CTA therefore owns a contiguous run of
+// 16-row tiles, asks the copy engine for ALL of its bytes up front (cp.async.bulk, one mbarrier per
+// tile, nothing is recycled so no barrier is ever re-armed), and its warps unpack and multiply the
+// tiles as they land.  The arithmetic is the limb-MMA scheme of skinny.cu: the activation's eight
+// balanced base-256 digits are the N=8 columns of a warp MMA; sub-block scales and minimums are
+// applied in int32, the block scale in int64, the columns are recombined in 128 bits and shifted
+// once.  Epilogues fuse the integer SiLU * up product (gate/up pair) and the gate-weighted combine
+// (down), replacing north-mini-code/tools/nmc_qk_cuda.cu:208-237 (silu_k, mul_shift_k,
+// matmul_multi_k, combine_k).
+//
+// Column order: MMA column c carries limb (c >> 1) + 4 * (c & 1), so that when the activation needs
+// at most four limbs (the usual case for normalised hidden states) every odd column is zero and
+// each thread skips half of its scale multiplies.
+#include <algorithm>
+
+#include "kernels.h"
+#include "layout.cuh"
+#include "mma_items.cuh"
+
+namespace iie {
+
+namespace {
+
+constexpr int NWARPS = 16;
+constexpr unsigned WAIT_LIMIT = 1u << 22;   // mbarrier polls before a wait gives up and raises flag bit 3
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the bytes never arrived (the caller raises an error flag and skips the work).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    for (unsigned it = 0; it < WAIT_LIMIT; it++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+template <int QT, int MODE>
+__global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
+    const int nb = (int)a.n_blocks;
+    const long long K = a.n_blocks * 256;
+    const int tile_bytes = 2 * nb * HTB;
+    const int tpc = a.tiles_per_cta;
+    uint8_t *wbuf = smem;
+    unsigned long long *red = reinterpret_cast<unsigned long long *>(smem + (size_t)tpc * tile_bytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(red + (size_t)tpc * 128);
+    __shared__ int s_timeout;
+
+    const long long n_tiles = (long long)a.n_sel * a.tiles_per_expert;
+    const long long tile0 = (long long)blockIdx.x * tpc;
+    const int my_tiles = (int)min((long long)tpc, n_tiles - tile0);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long n_ht = (a.out_f + 7) >> 3;
+
+    for (int i = threadIdx.x; i < my_tiles * 128; i += blockDim.x) red[i] = 0ULL;
+    if (threadIdx.x == 0) {
+        s_timeout = 0;
+        for (int i = 0; i < my_tiles; i++) mbar_init(&bars[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < my_tiles; i++) {
+            const long long tau = tile0 + i;
+            const int s = (int)(tau / a.tiles_per_expert), p = (int)(tau % a.tiles_per_expert);
+            const int e = a.sel ? a.sel[s] : s;
+            uint8_t *dst = wbuf + (size_t)i * tile_bytes;
+            if (MODE == MODE_GATEUP) {
+                mbar_expect_tx(&bars[i], (uint32_t)tile_bytes);
+                bulk_g2s(dst, a.wa[e] + (size_t)p * nb * HTB, (uint32_t)(nb * HTB), &bars[i]);
+                bulk_g2s(dst + nb * HTB, a.wb[e] + (size_t)p * nb * HTB, (uint32_t)(nb * HTB), &bars[i]);
+            } else {
+                const int units = (2LL * p + 1 < n_ht) ? 2 : 1;          // an odd last half-tile stands alone
+                mbar_expect_tx(&bars[i], (uint32_t)(units * nb * HTB));
+                bulk_g2s(dst, a.wa[e] + (size_t)(2 * p) * nb * HTB, (uint32_t)(units * nb * HTB), &bars[i]);
+            }
+        }
+    }
+    const bool half = a.x_nl ? (*a.x_nl <= 4) : false;
+
+    const int n_items = my_tiles * nb;
+    for (int it = warp; it < n_items; it += NWARPS) {
+        const int ti = it / nb, b = it - ti * nb;
+        const long long tau = tile0 + ti;
+        const int s = (int)(tau / a.tiles_per_expert), p = (int)(tau % a.tiles_per_expert);
+        const int8_t *xp = a.xl + (a.x_per_sel ? (long long)s * 8 * K : 0);
+        const uint8_t *ua = wbuf + (size_t)ti * tile_bytes + (size_t)b * HTB;
+        const uint8_t *ub;
+        if (MODE == MODE_GATEUP) ub = ua + (size_t)nb * HTB;
+        else ub = (2LL * p + 1 < n_ht) ? ua + (size_t)nb * HTB : ua;
+        const int g = lane >> 2, t = lane & 3;
+        uint32_t bf[16];                                      // activation fragments first: they overlap the wait
+        load_bfrag<QT, true>(xp + (long long)col_limb(g) * K + (long long)b * 256, t, bf);
+        if (!mbar_wait(&bars[ti], 0)) { s_timeout = 1; continue; }
+        int64_t acc[4] = {0, 0, 0, 0};
+        if (QT == QT_Q4K) item_q4k(ua, ub, lane, a.fw, bf, half, acc);
+        else              item_q6k(ua, ub, lane, a.fw, bf, half, acc);
+        unsigned long long *r = red + (size_t)ti * 128;
+        atomicAdd(&r[g * 8 + 2 * t], (unsigned long long)acc[0]);
+        atomicAdd(&r[(g + 8) * 8 + 2 * t], (unsigned long long)acc[2]);
+        if (!half) {
+            atomicAdd(&r[g * 8 + 2 * t + 1], (unsigned long long)acc[1]);
+            atomicAdd(&r[(g + 8) * 8 + 2 * t + 1], (unsigned long long)acc[3]);
+        }
+    }
+    __syncthreads();
+    if (s_timeout) { if (threadIdx.x == 0) atomicOr(a.flags, 8); return; }
+
+    if (MODE == MODE_GATEUP) {
+        int nl_max = 0;
+        for (int idx = threadIdx.x; idx < my_tiles * 8; idx += blockDim.x) {
+            const int ti = idx >> 3, r = idx & 7;
+            const long long tau = tile0 + ti;
+            const int s = (int)(tau / a.tiles_per_expert), p = (int)(tau % a.tiles_per_expert);
+            const long long row = (long long)p * 8 + r;
+            if (row >= a.out_f) continue;
+            const unsigned long long *rr = red + (size_t)ti * 128;
+            const int64_t yg = recombine_cols(rr + r * 8, a.fw), yu = recombine_cols(rr + (r + 8) * 8, a.fw);
+            const int64_t gu = mul_shift(silu_fixed(yg, a.fa), yu, a.fa);
+            if (a.out) a.out[(long long)s * a.out_f + row] = gu;
+            bool ok;
+            const uint64_t d = balanced_digits8(gu, ok);
+            if (!ok) atomicOr(a.flags, 1);
+            nl_max = max(nl_max, digits_used(d));
+#pragma unroll
+            for (int l = 0; l < 8; l++) a.out_limbs[((long long)s * 8 + l) * a.out_f + row] = (int8_t)(d >> (8 * l));
+        }
+        if (a.out_nl && nl_max > 0) atomicMax(a.out_nl, nl_max);
+    } else {
+        for (int idx = threadIdx.x; idx < my_tiles * 16; idx += blockDim.x) {
+            const int ti = idx >> 4, r = idx & 15;
+            const long long tau = tile0 + ti;
+            const int s = (int)(tau / a.tiles_per_expert), p = (int)(tau % a.tiles_per_expert);
+            const long long row = (long long)p * 16 + r;
+            if (row >= a.out_f) continue;
+            const int64_t y = recombine_cols(red + (size_t)ti * 128 + r * 8, a.fw);
+            if (MODE == MODE_LINEAR) a.out[(long long)s * a.out_f + row] = y;
+            else atomicAdd(reinterpret_cast<unsigned long long *>(a.out + row),
+                           (unsigned long long)mul_shift(y, a.gates[s], a.fa));
+        }
+    }
+}
+
+template <int QT, int MODE>
+cudaError_t launch_stream_t(const StreamArgs &a_in, cudaStream_t s) {
+    StreamArgs a = a_in;
+    constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
+    const long long n_ht = (a.out_f + 7) >> 3;
+    a.tiles_per_expert = (int)(MODE == MODE_GATEUP ? n_ht : (n_ht + 1) / 2);
+    const long long n_tiles = (long long)a.n_sel * a.tiles_per_expert;
+    const size_t tile_bytes = (size_t)2 * a.n_blocks * HTB, per_tile = tile_bytes + 128 * 8 + 8;
+    const int max_tpc = (int)((200 * 1024) / per_tile);
+    if (max_tpc < 1) return cudaErrorInvalidConfiguration;
+    int tpc = (int)((n_tiles + 147) / 148);                      // one wave when everything fits
+    if (tpc > max_tpc) tpc = (int)std::max<long long>(1, std::min<long long>(max_tpc, (100 * 1024) / (long long)per_tile));
+    a.tiles_per_cta = tpc;
+    const unsigned grid = (unsigned)((n_tiles + tpc - 1) / tpc);
+    const size_t smem = (size_t)tpc * per_tile + 64;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(stream_kernel<QT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    stream_kernel<QT, MODE><<<grid, NWARPS * 32, smem, s>>>(a);
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_stream(int qtype, int mode, const StreamArgs &a, cudaStream_t s) {
+    if (a.n_sel <= 0 || a.out_f <= 0 || a.n_blocks <= 0) return cudaErrorInvalidValue;
+    if (qtype == QT_Q4K) {
+        if (mode == MODE_LINEAR) return launch_stream_t<QT_Q4K, MODE_LINEAR>(a, s);
+        if (mode == MODE_GATEUP) return launch_stream_t<QT_Q4K, MODE_GATEUP>(a, s);
+        return launch_stream_t<QT_Q4K, MODE_DOWN>(a, s);
+    }
+    if (qtype == QT_Q6K) {
+        if (mode == MODE_LINEAR) return launch_stream_t<QT_Q6K, MODE_LINEAR>(a, s);
+        if (mode == MODE_GATEUP) return launch_stream_t<QT_Q6K, MODE_GATEUP>(a, s);
+        return launch_stream_t<QT_Q6K, MODE_DOWN>(a, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace iie

@@ -134,6 +134,25 @@ class MoELayer:
             raise CudaContextError(f"MoE forward failed with status {rc}")
         return out, ids, gates
 
+    def block(self, x: torch.Tensor, gain_handle: int = -1, fa: int = 16, fw: int = 24, eps: int = 1,
+              out: torch.Tensor | None = None, want_routes: bool = True):
+        """The block with normalisation and residual: ``moe(x)`` without a gain handle, otherwise
+        ``x + moe(rmsnorm(x, gain))``.  ``out`` may be ``x`` itself.  Returns (out, ids, gates)."""
+        lib = qk_cuda._lib()
+        assert x.is_cuda and x.dtype == torch.int64 and x.dim() == 2 and x.shape[1] == self.d_model and x.is_contiguous()
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty_like(x)
+        ids = torch.empty((T, self.top_k), dtype=torch.int32, device=x.device) if want_routes else None
+        gates = torch.empty((T, self.top_k), dtype=torch.int64, device=x.device) if want_routes else None
+        with _CUDA_LOCK:
+            rc = lib.iie_moe_block_dev(self.handle, int(gain_handle), x.data_ptr(), T, int(fa), int(fw), int(eps),
+                                       out.data_ptr(), ids.data_ptr() if want_routes else None,
+                                       gates.data_ptr() if want_routes else None, _stream_ptr())
+        if rc != 0:
+            raise CudaContextError(f"MoE block failed with status {rc}")
+        return out, ids, gates
+
     def close(self):
         if self.handle >= 0:
             with _CUDA_LOCK:

@@ -69,8 +69,6 @@ class SyntheticMoEStack:
 
     def decode_step(self, x: torch.Tensor, fw: int = 24) -> torch.Tensor:
         """x [T,d] int64, updated in place through every block: x += moe(rmsnorm(x, gain))."""
-        h = torch.empty_like(x)
         for layer, gain_h in zip(self.layers, self.gains):
-            device.rmsnorm(x, gain_h, self.fa, 1, out=h)
-            layer.forward(h, self.fa, fw, out=x, accumulate=True, want_routes=False)
+            layer.block(x, gain_h, self.fa, fw, 1, out=x, want_routes=False)
         return x

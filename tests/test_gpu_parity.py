@@ -291,3 +291,78 @@ def test_registry_lifecycle_and_profile_counters(qk):
     assert stats["h2d_bytes"] >= len(raw) + x.nbytes and stats["d2h_bytes"] >= r2.nbytes
     qk.profile_set_enabled(False)
     qk.free_all()
+
+
+# ------------------------------------------------------------------------------------------------
+# device-tensor front end: the fused single-token path (routing kernel + streamed gate/up + down)
+# and the batched dispatch path, against the C oracle
+# ------------------------------------------------------------------------------------------------
+def _device_layer(qk, seed, d, eff, E, k, T, xbits=None):
+    import torch
+
+    from integer_inference_engine_b200 import device
+    router, gate, up, down, h = o.synth_moe(seed, d, eff, E, T)
+    if xbits is not None:
+        h = np.random.default_rng(seed).integers(-(1 << xbits), 1 << xbits, size=(T, d), dtype=np.int64)
+    rh = qk.register_weight(router, E, d // 256, o.Q4_K)
+    gh = [qk.register_weight(w, eff, d // 256, o.Q4_K) for w in gate]
+    uh = [qk.register_weight(w, eff, d // 256, o.Q4_K) for w in up]
+    dh = [qk.register_weight(w, d, eff // 256, o.Q6_K) for w in down]
+    layer = device.MoELayer(rh, gh, uh, dh, k, d, eff)
+    ref = onat.moe_block(router, o.Q4_K, gate, up, down, o.Q4_K, o.Q6_K, k, h, d, eff, FA, FW)
+    return layer, torch.from_numpy(h).cuda(), ref
+
+
+@pytest.mark.parametrize("d,eff,E,k,T,xbits", [(512, 256, 8, 2, 1, None), (2048, 768, 20, 8, 1, None),
+                                              (256, 512, 5, 3, 1, None), (512, 256, 8, 2, 1, 22),
+                                              (512, 256, 8, 2, 6, None), (2048, 768, 128, 8, 1, None)])
+def test_device_moe_forward(qk, d, eff, E, k, T, xbits):
+    import torch
+
+    from integer_inference_engine_b200 import device
+    qk.free_all()
+    layer, h, (ids_ref, gates_ref, out_ref) = _device_layer(qk, 40 + d + E, d, eff, E, k, T, xbits)
+    out, ids, gates = layer.forward(h, FA, FW)
+    torch.cuda.synchronize()
+    assert device.read_flags() == 0
+    assert np.array_equal(ids.cpu().numpy(), ids_ref)
+    assert np.array_equal(gates.cpu().numpy(), gates_ref)
+    assert np.array_equal(out.cpu().numpy(), out_ref)
+    acc = torch.ones_like(out)                                   # accumulate adds to what is there
+    layer.forward(h, FA, FW, out=acc, accumulate=True)
+    assert np.array_equal(acc.cpu().numpy(), out_ref + 1)
+    qk.free_all()
+
+
+@pytest.mark.parametrize("T", [1, 3])
+def test_device_moe_block_with_norm_and_residual(qk, T):
+    import torch
+
+    from integer_inference_engine_b200 import device
+    qk.free_all()
+    d, eff, E, k = 2048, 768, 16, 4
+    router, gate, up, down, h0 = o.synth_moe(91, d, eff, E, T)
+    rh = qk.register_weight(router, E, d // 256, o.Q4_K)
+    gh = [qk.register_weight(w, eff, d // 256, o.Q4_K) for w in gate]
+    uh = [qk.register_weight(w, eff, d // 256, o.Q4_K) for w in up]
+    dh = [qk.register_weight(w, d, eff // 256, o.Q6_K) for w in down]
+    layer = device.MoELayer(rh, gh, uh, dh, k, d, eff)
+    gain = o.to_fixed(np.abs(np.random.default_rng(3).standard_normal(d)) + 0.5, FA)
+    gain_h = qk.register_i64(gain)
+    xn = (h0 * 37).astype(np.int64)                               # an un-normalised residual stream
+    hn = o.rmsnorm_fixed(xn, FA, 1, gain)
+    ids_ref, gates_ref, moe_ref = onat.moe_block(router, o.Q4_K, gate, up, down, o.Q4_K, o.Q6_K, k, hn, d, eff, FA, FW)
+    x = torch.from_numpy(xn).cuda()
+    out, ids, gates = layer.block(x, gain_h, FA, FW, 1)
+    torch.cuda.synchronize()
+    assert device.read_flags() == 0
+    assert np.array_equal(ids.cpu().numpy(), ids_ref) and np.array_equal(gates.cpu().numpy(), gates_ref)
+    assert np.array_equal(out.cpu().numpy(), xn + moe_ref)
+    inplace = x.clone()
+    layer.block(inplace, gain_h, FA, FW, 1, out=inplace)            # out may alias x
+    assert np.array_equal(inplace.cpu().numpy(), xn + moe_ref)
+    got = qk.moe_block(layer.handle, xn, k, FA, FW, gain_handle=gain_h)   # host-buffer entry of the same block
+    assert got is not None and np.array_equal(got[0], xn + moe_ref) and np.array_equal(got[1], ids_ref)
+    plain = qk.moe_block(layer.handle, hn, k, FA, FW)                    # no gain: moe(x) only
+    assert plain is not None and np.array_equal(plain[0], moe_ref)
+    qk.free_all()
