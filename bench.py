@@ -372,7 +372,7 @@ def run_ours(args):
                    "oracle_checked_blocks": checked},
         "clocks": clk.summary(),
         "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps),
-        "roofline": {"bound": "hbm", "kernel": "skinny_kernel<Q4_K, GATEUP>", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "stream_kernel<Q4_K, GATEUP>", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                      "bytes_per_launch": gateup_bytes, "ms_per_launch": gateup_ms},
         "cpu_baseline": cpu,

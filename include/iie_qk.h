@@ -117,7 +117,7 @@ long long iie_moe_layer_create(long long router_h, const long long *gate_h, cons
                                long long e_ffn);
 void iie_moe_layer_destroy(long long layer);
 
-/* Whole MoE block on device tensors, asynchronous on `stream` (a cudaStream_t; NULL = the library
+/* Whole MoE block on device tensors, asynchronous on `stream` (a cudaStream_t; NULL = the CUDA default
  * stream): router product, top-k + sigmoid gates, dispatch, gate/up with fused SiLU*up, down with
  * fused gate-weighted combine.  h_dev [T,d_model] int64 -> out_dev [T,d_model] int64 (overwritten,
  * or added to when accumulate != 0), ids_dev [T,top_k] int32, gates_dev [T,top_k] int64 (the last

@@ -647,7 +647,7 @@ extern "C" int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long l
         T <= 0 || fa < 1 || fa > 29) return 1;
     const MoeLayer &L = g_layers[layer];
     const Weight &r = g_w[L.router];
-    cudaStream_t s = stream ? (cudaStream_t)stream : g_stream;
+    cudaStream_t s = (cudaStream_t)stream;              // NULL is the CUDA default stream
     if (!fast_envelope(L.gate_q, L.d_model / 256, L.maxd_gate, L.maxdmin_gate, fw) ||
         !fast_envelope(L.down_q, L.e_ffn / 256, L.maxd_down, L.maxdmin_down, fw)) return 3;
     const int E = L.n_experts, k = L.top_k;
@@ -695,7 +695,7 @@ extern "C" int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long l
 extern "C" int iie_apply_dev(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev, void *stream) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (!init() || !valid_q(h) || !x_dev || !out_dev || T <= 0) return 1;
-    cudaStream_t s = stream ? (cudaStream_t)stream : g_stream;
+    cudaStream_t s = (cudaStream_t)stream;              // NULL is the CUDA default stream
     return linear_dev(g_w[h], x_dev, T, fw, out_dev, false, s) ? 0 : 1;
 }
 
@@ -715,7 +715,7 @@ extern "C" int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long
         if (!valid_i64(gain_h) || g_w[gain_h].out_f != 1 || g_w[gain_h].nb != width) return 1;
         gain = (const int64_t *)g_w[gain_h].d;
     }
-    cudaStream_t s = stream ? (cudaStream_t)stream : g_stream;
+    cudaStream_t s = (cudaStream_t)stream;              // NULL is the CUDA default stream
     return launch_rmsnorm(x_dev, rows, width, gain, fa, eps, out_dev, g_flags, s) == cudaSuccess ? 0 : 1;
 }
 
@@ -732,7 +732,7 @@ extern "C" int iie_moe_block_dev(long long layer, long long gain_h, const int64_
     if (!init() || layer < 0 || (size_t)layer >= g_layers.size() || !g_layers[layer].live || !x_dev || !out_dev ||
         T <= 0 || fa < 1 || fa > 29) return 1;
     const MoeLayer &L = g_layers[layer];
-    cudaStream_t s = stream ? (cudaStream_t)stream : g_stream;
+    cudaStream_t s = (cudaStream_t)stream;              // NULL is the CUDA default stream
     if (!fast_envelope(L.gate_q, L.d_model / 256, L.maxd_gate, L.maxdmin_gate, fw) ||
         !fast_envelope(L.down_q, L.e_ffn / 256, L.maxd_down, L.maxdmin_down, fw)) return 3;
     const int64_t *gain = nullptr;
