@@ -305,24 +305,30 @@ def run_ours(args):
     for layer in stack.layers:                                   # leaves ids/gates/limbs of the last block in place
         layer.forward(h_probe, FA, FW, out=outs, accumulate=True, want_routes=False)
     torch.cuda.synchronize()
-    device.set_stage_mask(8)
     reps = 3
-    g2 = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(g2, stream=side):
-            for layer in stack.layers:
-                layer.forward(h_probe, FA, FW, out=outs, accumulate=True, want_routes=False)
-    device.set_stage_mask(0)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    g2.replay()
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(reps):
+
+    def time_stage(mask):
+        """Average device time of one stage over all blocks, captured as one graph and replayed."""
+        x_probe = table[:1].clone()
+        device.set_stage_mask(mask)
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g2, stream=side):
+                for layer, gain_h in zip(stack.layers, stack.gains):
+                    layer.block(x_probe, gain_h, FA, FW, 1, out=outs, want_routes=False)
+        device.set_stage_mask(0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         g2.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    device.read_flags()
-    gateup_ms = e0.elapsed_time(e1) / (reps * len(stack.layers))
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            g2.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        device.read_flags()
+        return e0.elapsed_time(e1) / (reps * len(stack.layers))
+
+    route_ms, gateup_ms, down_ms = time_stage(2), time_stage(8), time_stage(16)
     gateup_bytes = TOP_K * 2 * E_FFN * (D_MODEL // 256) * 144
     achieved = gateup_bytes / (gateup_ms * 1e-3) / 1e9
 
@@ -374,7 +380,9 @@ def run_ours(args):
         "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps),
         "roofline": {"bound": "hbm", "kernel": "stream_kernel<Q4_K, GATEUP>", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                     "bytes_per_launch": gateup_bytes, "ms_per_launch": gateup_ms},
+                     "bytes_per_launch": gateup_bytes, "ms_per_launch": gateup_ms,
+                     "other_kernels_us": {"route": route_ms * 1e3, "down": down_ms * 1e3,
+                                          "down_frac": TOP_K * D_MODEL * (E_FFN // 256) * 210 / (down_ms * 1e-3) / 1e9 / peak}},
         "cpu_baseline": cpu,
     }))
     if world > 1:

@@ -27,15 +27,14 @@ __host__ __device__ inline int htb_bytes(int qtype) { return qtype == QT_Q4K ? H
 // m, so the product is a shift; a right shift rounds half to even.  Replaces the double + llrint
 // conversion of north-mini-code/tools/nmc_qk_kernel.c:16-39 (same values for all finite halves).
 __host__ __device__ inline int64_t half_to_fixed(uint32_t h, int frac) {
-    int64_t m = h & 0x3FF;
-    int e = (h >> 10) & 0x1F;
-    if (e == 0) e = -24; else { m |= 0x400; e -= 25; }
-    e += frac;
+    const int ex = (h >> 10) & 0x1F;
+    const int64_t m = ex ? ((h & 0x3FF) | 0x400) : (h & 0x3FF);
+    const int e = (ex ? ex - 25 : -24) + frac;
     int64_t v;
-    if (e >= 0) v = (int64_t)((uint64_t)m << (e > 52 ? 52 : e));
+    if (e >= 0) v = (int64_t)((uint64_t)m << (e > 52 ? 52 : e));      // the only path at frac >= 24
     else {
         int s = -e; if (s > 40) s = 40;
-        int64_t q = m >> s, rem = m & (((int64_t)1 << s) - 1), half = (int64_t)1 << (s - 1);
+        const int64_t q = m >> s, rem = m & (((int64_t)1 << s) - 1), half = (int64_t)1 << (s - 1);
         v = q + ((rem > half) || (rem == half && (q & 1)));
     }
     return (h & 0x8000) ? -v : v;
@@ -53,10 +52,11 @@ __device__ __forceinline__ int64_t exp2_neg_fixed(int64_t u, int fa) {
     return p >> (k < 63 ? k : 63);
 }
 
-__device__ __forceinline__ int64_t sigmoid_fixed(int64_t x, int fa) {
-    const int s = 16 - fa;
-    const int64_t log2e = s >= 0 ? ((int64_t)94548 >> s) : ((int64_t)94548 << -s);
-    const int64_t clip = (((int64_t)(fa + 2)) << (2 * fa)) / log2e;
+// log2(e) at scale 2^fa and the distance beyond which exp2 underflows to zero (fixedpoint.py:136-146).
+__host__ __device__ inline int64_t sigmoid_log2e(int fa) { const int s = 16 - fa; return s >= 0 ? ((int64_t)94548 >> s) : ((int64_t)94548 << -s); }
+__host__ __device__ inline int64_t sigmoid_clip(int fa) { return (((int64_t)(fa + 2)) << (2 * fa)) / sigmoid_log2e(fa); }
+
+__device__ __forceinline__ int64_t sigmoid_fixed_c(int64_t x, int fa, int64_t log2e, int64_t clip) {
     const int64_t m = x > 0 ? x : 0;
     const int64_t d0 = m < clip ? m : clip;
     // the NumPy oracle evaluates m - x and d * log2e in wrapping int64 (only x = INT64_MIN wraps)
@@ -66,6 +66,10 @@ __device__ __forceinline__ int64_t sigmoid_fixed(int64_t x, int fa) {
     const int64_t e1 = exp2_neg_fixed((int64_t)((uint64_t)d1 * (uint64_t)log2e) >> fa, fa);
     const int64_t z = e0 + e1;          // e0, e1 <= 2^fa, fa <= 29: the quotient below fits 64 bits
     return z == 0 ? 0 : (int64_t)(((uint64_t)e1 << fa) / (uint64_t)z);
+}
+
+__device__ __forceinline__ int64_t sigmoid_fixed(int64_t x, int fa) {
+    return sigmoid_fixed_c(x, fa, sigmoid_log2e(fa), sigmoid_clip(fa));
 }
 
 __device__ __forceinline__ int64_t mul_shift(int64_t a, int64_t b, int sh) {
@@ -108,6 +112,21 @@ __device__ __forceinline__ void mma_s8s8_k32(int (&c)[4], uint32_t a0, uint32_t 
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Variants with a zero accumulator input (one shared zero register instead of four moves per call).
+__device__ __forceinline__ void mma_u8s8_k32_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    const int z = 0;
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
+}
+__device__ __forceinline__ void mma_s8s8_k16_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    const int z = 0;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(z));
 }
 
 __device__ __forceinline__ uint4 ldg128(const void *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }

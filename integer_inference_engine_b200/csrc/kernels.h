@@ -45,6 +45,7 @@ struct StreamArgs {
     int tiles_per_expert, tiles_per_cta;   // filled in by the launcher
     long long out_f, n_blocks;
     int fw, fa;
+    long long sig_log2e, sig_clip; // sigmoid constants for fa (filled in by the launcher)
     const int8_t *xl;              // limb planes [8][K] (shared) or [n_sel][8][K]
     int x_per_sel;
     const int *x_nl;               // device: limbs in use by x (<= 4 enables the half-column path), or nullptr

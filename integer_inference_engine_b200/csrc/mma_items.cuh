@@ -56,10 +56,10 @@ __device__ __forceinline__ void item_q4k(const uint8_t *ua, const uint8_t *ub, i
         const uint32_t a0 = (wa[2 * G] >> sh) & 0x0f0f0f0fu, a2 = (wa[2 * G + 1] >> sh) & 0x0f0f0f0fu;
         const uint32_t a1 = (wb[2 * G] >> sh) & 0x0f0f0f0fu, a3 = (wb[2 * G + 1] >> sh) & 0x0f0f0f0fu;
         const int sA = ubyte_at(scA[j >> 2], j & 3), sB = ubyte_at(scB[j >> 2], j & 3);
-        const uint32_t mA = (uint32_t)ubyte_at(mnA[j >> 2], j & 3) * 0x01010101u;
-        const uint32_t mB = (uint32_t)ubyte_at(mnB[j >> 2], j & 3) * 0x01010101u;
-        int c[4] = {0, 0, 0, 0};
-        mma_u8s8_k32(c, a0, a1, a2, a3, bf[2 * j], bf[2 * j + 1]);
+        const uint32_t mA = __byte_perm(mnA[j >> 2], 0, 0x1111 * (j & 3));   // byte j replicated four times
+        const uint32_t mB = __byte_perm(mnB[j >> 2], 0, 0x1111 * (j & 3));
+        int c[4];
+        mma_u8s8_k32_z(c, a0, a1, a2, a3, bf[2 * j], bf[2 * j + 1]);
         mma_u8s8_k32(M4, mA, mB, mA, mB, bf[2 * j], bf[2 * j + 1]);
         T4[0] += sA * c[0]; T4[2] += sB * c[2];
         if (!half) { T4[1] += sA * c[1]; T4[3] += sB * c[3]; }
@@ -102,8 +102,8 @@ __device__ __forceinline__ void item_q6k(const uint8_t *ua, const uint8_t *ub, i
                 const uint32_t qA = __vsub4(loA | hiA, 0x20202020u), qB = __vsub4(loB | hiB, 0x20202020u);
                 const int si = 8 * h + 2 * kq + u;
                 const int scA = sbyte_at(sA[si >> 2], si & 3), scB = sbyte_at(sB[si >> 2], si & 3);
-                int c[4] = {0, 0, 0, 0};
-                mma_s8s8_k16(c, qA, qB, bf[h * 8 + kq * 2 + u]);
+                int c[4];
+                mma_s8s8_k16_z(c, qA, qB, bf[h * 8 + kq * 2 + u]);
                 T4[0] += scA * c[0]; T4[2] += scB * c[2];
                 if (!half) { T4[1] += scA * c[1]; T4[3] += scB * c[3]; }
             }

@@ -7,9 +7,13 @@
 // Arithmetic: north-mini-code/src/nmc/_bonsai/fixedpoint.py:32-72 (RMSNorm), cohere2.py:162-180
 // (routing).  Every CTA recomputes the (tiny) normalisation so that no grid-wide barrier is needed
 // before the router rows; the CTA that finishes last performs the top-k.
+#include <cooperative_groups.h>
+
 #include "kernels.h"
 #include "layout.cuh"
 #include "mma_items.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace iie {
 
@@ -38,26 +42,49 @@ __device__ u128 isqrt128(u128 v) {
     return res;
 }
 
-template <int QT>
+__device__ __forceinline__ uint32_t rt_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// floor(num / den) for |num| < 2^62 and 0 < den < 2^62 through a precomputed reciprocal
+// inv = floor((2^64 - 1) / den): the estimate is at most 2 below the quotient.
+__device__ __forceinline__ int64_t floor_div_recip(int64_t num, unsigned long long den, unsigned long long inv) {
+    const unsigned long long n = uabs64(num);
+    unsigned long long q = __umul64hi(n, inv), r = n - q * den;
+    while (r >= den) { q++; r -= den; }
+    return num >= 0 ? (int64_t)q : -(int64_t)q - (r != 0);
+}
+
+template <int QT, bool CLUSTER>
 __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    const int d = a.d, stride = d + RT_PAD;
-    int8_t *planes = reinterpret_cast<int8_t *>(smem);                       // [8][stride]
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
+    const int d = a.d, stride = d + RT_PAD, nb = d / 256;
+    uint8_t *wtile = smem;                                                  // this CTA's router tile: 2 units x nb blocks
+    int8_t *planes = reinterpret_cast<int8_t *>(smem + (size_t)2 * nb * HTB);  // [8][stride]
     __shared__ unsigned long long s_lo[RT_THREADS / 32], s_hi[RT_THREADS / 32], s_max[RT_THREADS / 32], s_gmax[RT_THREADS / 32];
-    __shared__ unsigned long long s_rms, s_gm;
-    __shared__ int s_bad, s_nl, s_last;
+    __shared__ unsigned long long s_rms, s_inv, s_gm;
+    __shared__ int s_bad, s_nl, s_last, s_timeout;
     __shared__ unsigned long long red[16][8];
     __shared__ int64_t s_logits[1024];
+    __shared__ __align__(8) uint64_t s_bar;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
-    const int nb = d / 256;
 
-    if (tid == 0) { s_bad = 0; s_nl = 1; s_last = 0; }
+    // ---- ask for the router tile first: it does not depend on x ----------------------------------------
+    const long long n_ht = ((long long)a.n_experts + 7) >> 3;
+    const long long htA = 2LL * blockIdx.x, htB = htA + 1 < n_ht ? htA + 1 : htA;
+    if (tid == 0) {
+        s_bad = 0; s_nl = 1; s_last = 0; s_timeout = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(rt_smem_u32(&s_bar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const uint32_t bytes = (uint32_t)((htB != htA ? 2 : 1) * nb * HTB);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(rt_smem_u32(&s_bar)), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(rt_smem_u32(wtile)), "l"(a.router + (size_t)htA * nb * HTB), "r"(bytes), "r"(rt_smem_u32(&s_bar)) : "memory");
+    }
     for (int i = tid; i < 128; i += RT_THREADS) (&red[0][0])[i] = 0ULL;
 
     // ---- sum of squares and magnitudes --------------------------------------------------------------------
-    u128 ssq = 0; unsigned long long mx = 0, gmx = 0;
     if (a.gain) {
+        u128 ssq = 0; unsigned long long mx = 0, gmx = 0;
         for (int i = tid; i < d; i += RT_THREADS) {
             const unsigned long long v = uabs64(a.x[i]);
             ssq += (u128)v * v;
@@ -89,26 +116,22 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
             const u128 rms = isqrt128(mean + a.eps);
             if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) s_bad = 1;
             s_rms = (unsigned long long)rms; s_gm = gm;
+            s_inv = rms != 0 ? 0xFFFFFFFFFFFFFFFFULL / (unsigned long long)rms : 0;
         }
     }
     __syncthreads();
-    if (s_bad) { if (tid == 0 && blockIdx.x == 0) atomicOr(a.flags, 2); return; }
+    if (s_bad) { if (tid == 0 && blockIdx.x == 0) atomicOr(a.flags, 2); return; }   // uniform over the grid
 
     // ---- normalise, apply the gain, split into limb planes ---------------------------------------------
-    const unsigned long long rms = s_rms, gm = s_gm;
+    const unsigned long long rms = s_rms, inv = s_inv, gm = s_gm;
     bool bad = false, over = false;
     int nl = 1;
     for (int i = tid; i < d; i += RT_THREADS) {
         const int64_t xv = a.x[i];
         int64_t y = xv;
         if (a.gain) {
-            const unsigned long long ax = uabs64(xv);
-            if (ax < (1ULL << (62 - a.fa))) {               // 64-bit floor division
-                const long long num = xv * ((long long)1 << a.fa);
-                long long q = num / (long long)rms;
-                if (num < 0 && q * (long long)rms != num) q -= 1;
-                y = q;
-            } else {
+            if (uabs64(xv) < (1ULL << (62 - a.fa)) && rms < (1ULL << 62)) y = floor_div_recip(xv * ((long long)1 << a.fa), rms, inv);
+            else {
                 const i128 num = (i128)xv * ((i128)1 << a.fa);
                 i128 q = num / (i128)rms;
                 if (num < 0 && q * (i128)rms != num) q -= 1;
@@ -133,23 +156,33 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
     }
     if (bad) atomicOr(a.flags, 2);
     if (over) atomicOr(a.flags, 1);
-    atomicMax(&s_nl, nl);
+    nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 16)); nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 8));
+    nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 4));  nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 2));
+    nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 1));
+    if (lane == 0) atomicMax(&s_nl, nl);
     __syncthreads();
     if (blockIdx.x == 0 && tid == 0) { *a.h_nl = s_nl; if (a.gu_nl) *a.gu_nl = 0; }
     const bool half = s_nl <= 4;
 
     // ---- router rows of this CTA: one 16-row tile, K split over the warps ------------------------------
-    const long long n_ht = ((long long)a.n_experts + 7) >> 3;
-    const long long htA = 2LL * blockIdx.x, htB = htA + 1 < n_ht ? htA + 1 : htA;
     const int g = lane >> 2, t = lane & 3;
     int64_t acc[4] = {0, 0, 0, 0};
-    for (int b = warp; b < nb; b += RT_THREADS / 32) {
-        uint32_t bf[16];
-        load_bfrag<QT, false>(planes + col_limb(g) * stride + b * 256, t, bf);
-        const uint8_t *ua = a.router + (htA * nb + b) * HTB, *ub = a.router + (htB * nb + b) * HTB;
-        if (QT == QT_Q4K) item_q4k(ua, ub, lane, a.fw, bf, half, acc);
-        else              item_q6k(ua, ub, lane, a.fw, bf, half, acc);
+    bool arrived = false;
+    for (unsigned it = 0; it < (1u << 22) && !arrived; it++) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(rt_smem_u32(&s_bar)) : "memory");
+        arrived = ok != 0;
     }
+    if (!arrived) s_timeout = 1;
+    else
+        for (int b = warp; b < nb; b += RT_THREADS / 32) {
+            uint32_t bf[16];
+            load_bfrag<QT, false>(planes + col_limb(g) * stride + b * 256, t, bf);
+            const uint8_t *ua = wtile + (size_t)b * HTB, *ub = htB != htA ? ua + (size_t)nb * HTB : ua;
+            if (QT == QT_Q4K) item_q4k(ua, ub, lane, a.fw, bf, half, acc);
+            else              item_q6k(ua, ub, lane, a.fw, bf, half, acc);
+        }
     atomicAdd(&red[g][2 * t], (unsigned long long)acc[0]);
     atomicAdd(&red[g + 8][2 * t], (unsigned long long)acc[2]);
     if (!half) {
@@ -157,68 +190,84 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
         atomicAdd(&red[g + 8][2 * t + 1], (unsigned long long)acc[3]);
     }
     __syncthreads();
-    if (tid < 16) {
-        const long long row = (tid < 8 ? htA : htB) * 8 + (tid & 7);
-        if (row < a.n_experts && (tid < 8 || htB != htA)) a.logits[row] = recombine_cols(red[tid], a.fw);
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned ticket = atomicAdd(a.counter, 1u);
-        if (ticket == gridDim.x - 1) { s_last = 1; *a.counter = 0; }
-    }
-    __syncthreads();
-    if (!s_last) return;
+    if (s_timeout && tid == 0) atomicOr(a.flags, 8);
 
-    // ---- last CTA: top-k (descending, lowest index on ties) and sigmoid gates --------------------------
-    __threadfence();
-    for (int i = tid; i < a.n_experts; i += RT_THREADS) s_logits[i] = *((volatile int64_t *)&a.logits[i]);
-    __syncthreads();
-    if (warp == 0) {
-        unsigned taken = 0;
-        int64_t my_val = 0; int my_id = -1;                  // lane r keeps the r-th pick
-        for (int r = 0; r < a.k; r++) {
-            int64_t best = INT64_MIN; int best_id = 0x7fffffff;
-            for (int i = 0, e = lane; e < a.n_experts; i++, e += 32) {
-                if (taken & (1u << i)) continue;
-                const int64_t v = s_logits[e];
-                if (best_id == 0x7fffffff || v > best) { best = v; best_id = e; }
+    // ---- gather the logits: distributed shared memory inside a cluster, or a last-CTA ticket --------------
+    if (CLUSTER) {
+        cg::cluster_group cluster = cg::this_cluster();
+        if (tid < 16) {
+            const long long row = (tid < 8 ? htA : htB) * 8 + (tid & 7);
+            if (row < a.n_experts && (tid < 8 || htB != htA)) {
+                int64_t *remote = cluster.map_shared_rank(s_logits, 0);
+                remote[row] = recombine_cols(red[tid], a.fw);
             }
-#pragma unroll
-            for (int s = 16; s > 0; s >>= 1) {
-                const int64_t ov = __shfl_xor_sync(0xffffffffu, best, s);
-                const int oi = __shfl_xor_sync(0xffffffffu, best_id, s);
-                if (oi != 0x7fffffff && (best_id == 0x7fffffff || ov > best || (ov == best && oi < best_id))) { best = ov; best_id = oi; }
-            }
-            if (best_id != 0x7fffffff && (best_id & 31) == lane) taken |= 1u << (best_id >> 5);
-            if ((r & 31) == lane) { my_val = best; my_id = best_id == 0x7fffffff ? -1 : best_id; }
-            if (r >= 32 && (r & 31) == 31) { /* k > 32 is handled by the generic top-k kernel */ }
         }
-        if (lane < a.k) {
-            a.ids[lane] = my_id;
-            a.gates[lane] = my_id < 0 ? 0 : sigmoid_fixed(my_val, a.fa);
+        cluster.sync();
+        if (cluster.block_rank() != 0) return;
+    } else {
+        if (tid < 16) {
+            const long long row = (tid < 8 ? htA : htB) * 8 + (tid & 7);
+            if (row < a.n_experts && (tid < 8 || htB != htA)) a.logits[row] = recombine_cols(red[tid], a.fw);
         }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned ticket = atomicAdd(a.counter, 1u);
+            if (ticket == gridDim.x - 1) { s_last = 1; *a.counter = 0; }
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        for (int i = tid; i < a.n_experts; i += RT_THREADS) s_logits[i] = *((volatile int64_t *)&a.logits[i]);
+        __syncthreads();
+    }
+
+    // ---- top-k by rank: element e is pick number #{j : v_j > v_e, or v_j == v_e and j < e} -----------------
+    const int64_t log2e = sigmoid_log2e(a.fa), clip = sigmoid_clip(a.fa);
+    for (int e = tid; e < a.n_experts; e += RT_THREADS) {
+        const int64_t v = s_logits[e];
+        int rank = 0;
+        for (int j = 0; j < a.n_experts; j++) {
+            const int64_t w = s_logits[j];
+            rank += (w > v) || (w == v && j < e);
+        }
+        if (rank < a.k) { a.ids[rank] = e; a.gates[rank] = sigmoid_fixed_c(v, a.fa, log2e, clip); }
     }
 }
 
 }  // namespace
 
 cudaError_t launch_route(const RouteArgs &a, cudaStream_t s) {
-    if (a.d <= 0 || a.d % 256 || a.d > RT_MAX_D || a.n_experts <= 0 || a.n_experts > 1024 || a.k <= 0 || a.k > 32 ||
+    if (a.d <= 0 || a.d % 256 || a.d > RT_MAX_D || a.n_experts <= 0 || a.n_experts > 1024 || a.k <= 0 ||
         a.k > a.n_experts) return cudaErrorInvalidValue;
     const unsigned grid = (unsigned)((((a.n_experts + 7) >> 3) + 1) / 2);
-    const size_t smem = (size_t)8 * (a.d + RT_PAD);
-    if (a.router_q == QT_Q4K) {
-        static bool cfg = false;
-        if (!cfg) { cudaFuncSetAttribute(route_kernel<QT_Q4K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (RT_MAX_D + RT_PAD)); cfg = true; }
-        route_kernel<QT_Q4K><<<grid, RT_THREADS, smem, s>>>(a);
-    } else if (a.router_q == QT_Q6K) {
-        static bool cfg = false;
-        if (!cfg) { cudaFuncSetAttribute(route_kernel<QT_Q6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (RT_MAX_D + RT_PAD)); cfg = true; }
-        route_kernel<QT_Q6K><<<grid, RT_THREADS, smem, s>>>(a);
-    } else return cudaErrorInvalidValue;
+    const int HTB = a.router_q == QT_Q4K ? HTB_Q4K : HTB_Q6K;
+    const size_t smem = (size_t)2 * (a.d / 256) * HTB + (size_t)8 * (a.d + RT_PAD);
+    const bool use_cluster = grid <= 8;
+    void (*kern)(RouteArgs) = nullptr;
+    if (a.router_q == QT_Q4K) kern = use_cluster ? route_kernel<QT_Q4K, true> : route_kernel<QT_Q4K, false>;
+    else if (a.router_q == QT_Q6K) kern = use_cluster ? route_kernel<QT_Q6K, true> : route_kernel<QT_Q6K, false>;
+    else return cudaErrorInvalidValue;
+    static bool configured[2][2] = {{false, false}, {false, false}};
+    bool &cfg = configured[a.router_q == QT_Q6K][use_cluster];
+    if (!cfg) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        cfg = true;
+    }
+    cudaLaunchConfig_t cfgl = {};
+    cfgl.gridDim = dim3(grid); cfgl.blockDim = dim3(RT_THREADS); cfgl.dynamicSmemBytes = smem; cfgl.stream = s;
+    cudaLaunchAttribute attr[1];
+    int n_attr = 0;
+    if (use_cluster) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = grid; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        n_attr = 1;
+    }
+    cfgl.attrs = attr; cfgl.numAttrs = n_attr;
+    const cudaError_t e = cudaLaunchKernelEx(&cfgl, kern, a);
     note_launch();
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace iie

@@ -63,15 +63,22 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
     uint8_t *wbuf = smem;
     unsigned long long *red = reinterpret_cast<unsigned long long *>(smem + (size_t)tpc * tile_bytes);
     uint64_t *bars = reinterpret_cast<uint64_t *>(red + (size_t)tpc * 128);
+    int *done = reinterpret_cast<int *>(bars + tpc);             // blocks of each tile already accumulated
+    int *t_sel = done + tpc, *t_pos = t_sel + tpc;               // tile -> (selected matrix slot, tile inside it)
     __shared__ int s_timeout;
 
-    const long long n_tiles = (long long)a.n_sel * a.tiles_per_expert;
-    const long long tile0 = (long long)blockIdx.x * tpc;
-    const int my_tiles = (int)min((long long)tpc, n_tiles - tile0);
+    const int n_tiles = a.n_sel * a.tiles_per_expert;
+    const int tile0 = (int)blockIdx.x * tpc;
+    const int my_tiles = min(tpc, n_tiles - tile0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long n_ht = (a.out_f + 7) >> 3;
 
     for (int i = threadIdx.x; i < my_tiles * 128; i += blockDim.x) red[i] = 0ULL;
+    for (int i = threadIdx.x; i < my_tiles; i += blockDim.x) {
+        done[i] = 0;
+        const int tau = tile0 + i, sl = tau / a.tiles_per_expert;
+        t_sel[i] = sl; t_pos[i] = tau - sl * a.tiles_per_expert;
+    }
     if (threadIdx.x == 0) {
         s_timeout = 0;
         for (int i = 0; i < my_tiles; i++) mbar_init(&bars[i], 1);
@@ -80,8 +87,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int i = 0; i < my_tiles; i++) {
-            const long long tau = tile0 + i;
-            const int s = (int)(tau / a.tiles_per_expert), p = (int)(tau % a.tiles_per_expert);
+            const int s = t_sel[i], p = t_pos[i];
             const int e = a.sel ? a.sel[s] : s;
             uint8_t *dst = wbuf + (size_t)i * tile_bytes;
             if (MODE == MODE_GATEUP) {
@@ -100,8 +106,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
     const int n_items = my_tiles * nb;
     for (int it = warp; it < n_items; it += NWARPS) {
         const int ti = it / nb, b = it - ti * nb;
-        const long long tau = tile0 + ti;
-        const int s = (int)(tau / a.tiles_per_expert), p = (int)(tau % a.tiles_per_expert);
+        const int s = t_sel[ti], p = t_pos[ti];
         const int8_t *xp = a.xl + (a.x_per_sel ? (long long)s * 8 * K : 0);
         const uint8_t *ua = wbuf + (size_t)ti * tile_bytes + (size_t)b * HTB;
         const uint8_t *ub;
@@ -121,43 +126,53 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
             atomicAdd(&r[g * 8 + 2 * t + 1], (unsigned long long)acc[1]);
             atomicAdd(&r[(g + 8) * 8 + 2 * t + 1], (unsigned long long)acc[3]);
         }
+        // the warp that completes a tile (all nb blocks added) runs its epilogue; nobody waits
+        __threadfence_block();
+        int prior = 0;
+        if (lane == 0) prior = atomicAdd(&done[ti], 1);
+        prior = __shfl_sync(0xffffffffu, prior, 0);
+        if (prior != nb - 1) continue;
+        __threadfence_block();
+        const volatile unsigned long long *rv = r;
+        if (MODE == MODE_GATEUP) {
+            int nl = 0;
+            if (lane < 8) {
+                const long long row = (long long)p * 8 + lane;
+                if (row < a.out_f) {
+                    unsigned long long cg[8], cu[8];
+#pragma unroll
+                    for (int c = 0; c < 8; c++) { cg[c] = rv[lane * 8 + c]; cu[c] = rv[(lane + 8) * 8 + c]; }
+                    const int64_t yg = recombine_cols(cg, a.fw), yu = recombine_cols(cu, a.fw);
+                    const int64_t sg = mul_shift(yg, sigmoid_fixed_c(yg, a.fa, a.sig_log2e, a.sig_clip), a.fa);
+                    const int64_t gu = mul_shift(sg, yu, a.fa);
+                    if (a.out) a.out[(long long)s * a.out_f + row] = gu;
+                    bool ok;
+                    const uint64_t d = balanced_digits8(gu, ok);
+                    if (!ok) atomicOr(a.flags, 1);
+                    nl = digits_used(d);
+#pragma unroll
+                    for (int l = 0; l < 8; l++) a.out_limbs[((long long)s * 8 + l) * a.out_f + row] = (int8_t)(d >> (8 * l));
+                }
+            }
+            nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 1));
+            nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 2));
+            nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 4));
+            if (lane == 0 && a.out_nl) atomicMax(a.out_nl, nl);
+        } else if (lane < 16) {
+            const long long row = (long long)p * 16 + lane;
+            if (row < a.out_f) {
+                unsigned long long cc[8];
+#pragma unroll
+                for (int c = 0; c < 8; c++) cc[c] = rv[lane * 8 + c];
+                const int64_t y = recombine_cols(cc, a.fw);
+                if (MODE == MODE_LINEAR) a.out[(long long)s * a.out_f + row] = y;
+                else atomicAdd(reinterpret_cast<unsigned long long *>(a.out + row),
+                               (unsigned long long)mul_shift(y, a.gates[s], a.fa));
+            }
+        }
     }
     __syncthreads();
-    if (s_timeout) { if (threadIdx.x == 0) atomicOr(a.flags, 8); return; }
-
-    if (MODE == MODE_GATEUP) {
-        int nl_max = 0;
-        for (int idx = threadIdx.x; idx < my_tiles * 8; idx += blockDim.x) {
-            const int ti = idx >> 3, r = idx & 7;
-            const long long tau = tile0 + ti;
-            const int s = (int)(tau / a.tiles_per_expert), p = (int)(tau % a.tiles_per_expert);
-            const long long row = (long long)p * 8 + r;
-            if (row >= a.out_f) continue;
-            const unsigned long long *rr = red + (size_t)ti * 128;
-            const int64_t yg = recombine_cols(rr + r * 8, a.fw), yu = recombine_cols(rr + (r + 8) * 8, a.fw);
-            const int64_t gu = mul_shift(silu_fixed(yg, a.fa), yu, a.fa);
-            if (a.out) a.out[(long long)s * a.out_f + row] = gu;
-            bool ok;
-            const uint64_t d = balanced_digits8(gu, ok);
-            if (!ok) atomicOr(a.flags, 1);
-            nl_max = max(nl_max, digits_used(d));
-#pragma unroll
-            for (int l = 0; l < 8; l++) a.out_limbs[((long long)s * 8 + l) * a.out_f + row] = (int8_t)(d >> (8 * l));
-        }
-        if (a.out_nl && nl_max > 0) atomicMax(a.out_nl, nl_max);
-    } else {
-        for (int idx = threadIdx.x; idx < my_tiles * 16; idx += blockDim.x) {
-            const int ti = idx >> 4, r = idx & 15;
-            const long long tau = tile0 + ti;
-            const int s = (int)(tau / a.tiles_per_expert), p = (int)(tau % a.tiles_per_expert);
-            const long long row = (long long)p * 16 + r;
-            if (row >= a.out_f) continue;
-            const int64_t y = recombine_cols(red + (size_t)ti * 128 + r * 8, a.fw);
-            if (MODE == MODE_LINEAR) a.out[(long long)s * a.out_f + row] = y;
-            else atomicAdd(reinterpret_cast<unsigned long long *>(a.out + row),
-                           (unsigned long long)mul_shift(y, a.gates[s], a.fa));
-        }
-    }
+    if (s_timeout && threadIdx.x == 0) atomicOr(a.flags, 8);
 }
 
 template <int QT, int MODE>
@@ -167,12 +182,13 @@ cudaError_t launch_stream_t(const StreamArgs &a_in, cudaStream_t s) {
     const long long n_ht = (a.out_f + 7) >> 3;
     a.tiles_per_expert = (int)(MODE == MODE_GATEUP ? n_ht : (n_ht + 1) / 2);
     const long long n_tiles = (long long)a.n_sel * a.tiles_per_expert;
-    const size_t tile_bytes = (size_t)2 * a.n_blocks * HTB, per_tile = tile_bytes + 128 * 8 + 8;
+    const size_t tile_bytes = (size_t)2 * a.n_blocks * HTB, per_tile = tile_bytes + 128 * 8 + 8 + 12;
     const int max_tpc = (int)((200 * 1024) / per_tile);
     if (max_tpc < 1) return cudaErrorInvalidConfiguration;
     int tpc = (int)((n_tiles + 147) / 148);                      // one wave when everything fits
     if (tpc > max_tpc) tpc = (int)std::max<long long>(1, std::min<long long>(max_tpc, (100 * 1024) / (long long)per_tile));
     a.tiles_per_cta = tpc;
+    a.sig_log2e = sigmoid_log2e(a.fa); a.sig_clip = sigmoid_clip(a.fa);
     const unsigned grid = (unsigned)((n_tiles + tpc - 1) / tpc);
     const size_t smem = (size_t)tpc * per_tile + 64;
     static bool configured = false;
