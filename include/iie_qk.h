@@ -151,6 +151,8 @@ int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long rows, long
  * 1 router product, 2 top-k, 3 gate/up, 4 down; 0 = all) so that one kernel can be timed alone on
  * data left by a previous full call; and the number of kernels launched since load. */
 void iie_profile_stage_mask(int mask);
+/* Switch programmatic dependent launch between the three single-token kernels on (default) or off. */
+void iie_set_pdl(int enabled);
 unsigned long long iie_launch_count(void);
 
 /* Read and clear the device flag word (synchronises the library stream and `stream`):

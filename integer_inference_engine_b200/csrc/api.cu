@@ -56,6 +56,8 @@ std::vector<MoeLayer> g_layers;
 cudaStream_t g_stream = nullptr;
 int *g_flags = nullptr;               // device flag word
 int *g_cells = nullptr;               // device ints: [0] limbs of h, [1] limbs of gate*up, [2] routing ticket
+const uint8_t **g_selptr = nullptr;   // device: [3][64] pointers of the experts the last routing selected
+int g_pdl = 1;                        // programmatic dependent launch between the three decode kernels
 int g_ready = -1;                     // -1 unknown, 0 usable, 1 unusable
 int g_stage_mask = 0;                 // profiling: when non-zero, iie_moe_forward_dev runs only these stages
 enum Stage { ST_LIMBS = 1, ST_ROUTER = 2, ST_TOPK = 4, ST_GATEUP = 8, ST_DOWN = 16 };
@@ -74,7 +76,8 @@ bool init() {
     if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) { cudaGetLastError(); g_ready = 1; return false; }
     if (cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaMalloc(&g_flags, sizeof(int)) != cudaSuccess || cudaMemset(g_flags, 0, sizeof(int)) != cudaSuccess ||
-        cudaMalloc(&g_cells, 64) != cudaSuccess || cudaMemset(g_cells, 0, 64) != cudaSuccess) {
+        cudaMalloc(&g_cells, 64) != cudaSuccess || cudaMemset(g_cells, 0, 64) != cudaSuccess ||
+        cudaMalloc(&g_selptr, 3 * 64 * sizeof(void *)) != cudaSuccess) {
         cudaGetLastError(); g_ready = 1; return false;
     }
     g_ready = 0;
@@ -112,6 +115,12 @@ bool valid_i64(long long h) { return h >= 0 && (size_t)h < g_w.size() && g_w[h].
 
 // Fast-path envelope of the streamed kernels (see skinny.cu): the per-limb-column int64 sums
 // cannot wrap.  Evaluated with the largest block scales of the tensor at this call's fw.
+// Scales small enough for the 32-bit fast conversions of the streaming kernels.
+bool small_scales(unsigned maxd, unsigned maxdmin, int fw) {
+    if (fw < 24 || fw > 36) return false;
+    return half_to_fixed(maxd, fw) < ((int64_t)1 << 31) && half_to_fixed(maxdmin, fw) < ((int64_t)1 << 31);
+}
+
 bool fast_envelope(int qtype, long long nb, unsigned maxd, unsigned maxdmin, int fw) {
     if (fw < 0 || fw > 36) return false;
     if ((maxd & 0x7C00u) == 0x7C00u || (maxdmin & 0x7C00u) == 0x7C00u) return false;   // inf/nan scales
@@ -259,16 +268,24 @@ bool moe_decode_token(const MoeLayer &L, const int64_t *x, const int64_t *gain, 
     ra.hl = hl; ra.h_nl = g_cells; ra.h_out = nullptr; ra.logits = lg; ra.ids = ids; ra.gates = gates;
     ra.init_out = out; ra.init_mode = init_mode; ra.gu_nl = g_cells + 1; ra.counter = (unsigned *)(g_cells + 2);
     ra.flags = g_flags;
+    const bool ptrs = k <= 64;
+    ra.tabs = ptrs ? L.tabs : nullptr; ra.sel_ptrs = ptrs ? g_selptr : nullptr; ra.pdl = g_pdl;
     if (stage_on(ST_ROUTER) && launch_route(ra, s) != cudaSuccess) return false;
     StreamArgs ga = {};
     ga.wa = L.tabs; ga.wb = L.tabs + E; ga.sel = ids; ga.n_sel = k; ga.out_f = L.e_ffn; ga.n_blocks = L.d_model / 256;
     ga.fw = fw; ga.fa = fa; ga.xl = hl; ga.x_per_sel = 0; ga.x_nl = g_cells; ga.out = nullptr; ga.out_limbs = gul;
-    ga.out_nl = g_cells + 1; ga.flags = g_flags;
+    ga.out_nl = g_cells + 1; ga.flags = g_flags; ga.fast = small_scales(L.maxd_gate, L.maxdmin_gate, fw);
+    if (ptrs) { ga.sel_wa = g_selptr; ga.sel_wb = g_selptr + k; }
+    ga.pdl = g_pdl; ga.early_weights = 0;
     if (stage_on(ST_GATEUP) && launch_stream(L.gate_q, MODE_GATEUP, ga, s) != cudaSuccess) return false;
     StreamArgs da = {};
     da.wa = L.tabs + 2 * E; da.wb = da.wa; da.sel = ids; da.n_sel = k; da.out_f = L.d_model; da.n_blocks = L.e_ffn / 256;
     da.fw = fw; da.fa = fa; da.xl = gul; da.x_per_sel = 1; da.x_nl = g_cells + 1; da.out = out; da.gates = gates;
-    da.flags = g_flags;
+    da.flags = g_flags; da.fast = small_scales(L.maxd_down, L.maxdmin_down, fw);
+    if (ptrs) da.sel_wa = g_selptr + 2 * k;
+    // the gate/up kernel releases its dependents only after the routing kernel has completed, so the
+    // selected pointers are final when this kernel's CTAs start: its weights may be requested early
+    da.pdl = g_pdl; da.early_weights = (g_pdl && ptrs && stage_on(ST_GATEUP)) ? 1 : 0;
     if (stage_on(ST_DOWN) && launch_stream(L.down_q, MODE_DOWN, da, s) != cudaSuccess) return false;
     return true;
 }
@@ -717,6 +734,11 @@ extern "C" int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long
     }
     cudaStream_t s = (cudaStream_t)stream;              // NULL is the CUDA default stream
     return launch_rmsnorm(x_dev, rows, width, gain, fa, eps, out_dev, g_flags, s) == cudaSuccess ? 0 : 1;
+}
+
+extern "C" void iie_set_pdl(int enabled) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    g_pdl = enabled ? 1 : 0;
 }
 
 extern "C" void iie_profile_stage_mask(int mask) {

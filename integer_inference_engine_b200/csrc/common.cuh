@@ -40,16 +40,35 @@ __host__ __device__ inline int64_t half_to_fixed(uint32_t h, int frac) {
     return (h & 0x8000) ? -v : v;
 }
 
+// half * 2^frac when the caller guarantees frac >= 24 (a pure shift) and the result fits int32.
+__device__ __forceinline__ int half_to_fixed_small(uint32_t h, int frac) {
+    const int ex = (h >> 10) & 0x1F;
+    const int m = ex ? ((h & 0x3FF) | 0x400) : (h & 0x3FF);
+    const int v = m << ((ex ? ex - 25 : -24) + frac);
+    return (h & 0x8000) ? -v : v;
+}
+
 // ---- integer sigmoid / SiLU (north-mini-code/src/nmc/_bonsai/fixedpoint.py:74-96,136-163) ----------
 __device__ __forceinline__ int64_t exp2_neg_fixed(int64_t u, int fa) {
     const int s = 16 - fa;
-    int64_t c0 = 65536, c1 = 45426, c2 = 15743, c3 = 3638;
+    uint32_t c0 = 65536, c1 = 45426, c2 = 15743, c3 = 3638;          // all operands below stay under 2^32 for fa <= 29
     if (s >= 0) { c0 >>= s; c1 >>= s; c2 >>= s; c3 >>= s; } else { c0 <<= -s; c1 <<= -s; c2 <<= -s; c3 <<= -s; }
-    const int64_t k = u >> fa, f = u & (((int64_t)1 << fa) - 1);
-    const int64_t f2 = (f * f) >> fa, f3 = (f2 * f) >> fa;
-    int64_t p = c0 - ((c1 * f) >> fa) + ((c2 * f2) >> fa) - ((c3 * f3) >> fa);
+    const int64_t k = u >> fa;
+    const uint32_t f = (uint32_t)(u & (((int64_t)1 << fa) - 1));
+    const uint32_t f2 = (uint32_t)(((uint64_t)f * f) >> fa), f3 = (uint32_t)(((uint64_t)f2 * f) >> fa);
+    int64_t p = (int64_t)c0 - (int64_t)(((uint64_t)c1 * f) >> fa) + (int64_t)(((uint64_t)c2 * f2) >> fa) -
+                (int64_t)(((uint64_t)c3 * f3) >> fa);
     if (p < 0) p = 0;
     return p >> (k < 63 ? k : 63);
+}
+
+// floor(num / z) for 0 <= num < 2^60, 0 < z < 2^31 from a double estimate with an exact fix-up.
+__device__ __forceinline__ uint64_t udiv_small(uint64_t num, uint64_t z) {
+    uint64_t q = (uint64_t)((double)num / (double)z);
+    int64_t r = (int64_t)(num - q * z);
+    while (r < 0) { q--; r += (int64_t)z; }
+    while (r >= (int64_t)z) { q++; r -= (int64_t)z; }
+    return q;
 }
 
 // log2(e) at scale 2^fa and the distance beyond which exp2 underflows to zero (fixedpoint.py:136-146).
@@ -65,7 +84,7 @@ __device__ __forceinline__ int64_t sigmoid_fixed_c(int64_t x, int fa, int64_t lo
     const int64_t e0 = exp2_neg_fixed((d0 * log2e) >> fa, fa);
     const int64_t e1 = exp2_neg_fixed((int64_t)((uint64_t)d1 * (uint64_t)log2e) >> fa, fa);
     const int64_t z = e0 + e1;          // e0, e1 <= 2^fa, fa <= 29: the quotient below fits 64 bits
-    return z == 0 ? 0 : (int64_t)(((uint64_t)e1 << fa) / (uint64_t)z);
+    return z == 0 ? 0 : (int64_t)udiv_small((uint64_t)e1 << fa, (uint64_t)z);
 }
 
 __device__ __forceinline__ int64_t sigmoid_fixed(int64_t x, int fa) {

@@ -41,10 +41,15 @@ struct StreamArgs {
     const uint8_t *const *wa;      // per matrix: repacked weight (linear/down weight, or gate)
     const uint8_t *const *wb;      // per matrix: up weight (MODE_GATEUP)
     const int *sel;                // [n_sel] matrix indices on the device, or nullptr (identity)
+    const uint8_t *const *sel_wa;  // optional: [n_sel] already-resolved pointers (then wa/wb/sel are not read)
+    const uint8_t *const *sel_wb;
     int n_sel;
+    int pdl;                       // 1: launched with programmatic stream serialization (see stream.cu)
+    int early_weights;             // 1: the selected-pointer arrays are final before the previous kernel ends
     int tiles_per_expert, tiles_per_cta;   // filled in by the launcher
     long long out_f, n_blocks;
     int fw, fa;
+    int fast;                      // fw >= 24 and every block scale below 2^31: 32-bit scale arithmetic
     long long sig_log2e, sig_clip; // sigmoid constants for fa (filled in by the launcher)
     const int8_t *xl;              // limb planes [8][K] (shared) or [n_sel][8][K]
     int x_per_sel;
@@ -74,6 +79,9 @@ struct RouteArgs {
     int64_t *gates;                // out [k]
     int64_t *init_out;             // nullable: row to initialise for the down stage
     int init_mode;                 // 0 leave, 1 zero, 2 copy x (residual)
+    const uint8_t *const *tabs;    // optional: [3][n_experts] gate/up/down pointer tables of the layer
+    const uint8_t **sel_ptrs;      // optional out: [3][k] pointers of the selected experts
+    int pdl;                       // 1: launched with programmatic stream serialization
     int *gu_nl;                    // zeroed here for the following gate/up kernel
     unsigned *counter;             // zero-initialised ticket for last-CTA detection (self-resetting)
     int *flags;                    // bit 0 limb envelope, bit 1 RMSNorm envelope

@@ -81,6 +81,11 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
                      ::"r"(rt_smem_u32(wtile)), "l"(a.router + (size_t)htA * nb * HTB), "r"(bytes), "r"(rt_smem_u32(&s_bar)) : "memory");
     }
     for (int i = tid; i < 128; i += RT_THREADS) (&red[0][0])[i] = 0ULL;
+    if (a.tabs && blockIdx.x == 0)                       // warm the layer's pointer tables in L2 for the tail of this kernel
+        for (int i = tid * 16; i < 3 * a.n_experts; i += RT_THREADS * 16)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(a.tabs + i));
+    // Programmatic dependent launch: nothing above read data written by earlier kernels.
+    if (a.pdl) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
 
     // ---- sum of squares and magnitudes --------------------------------------------------------------------
     if (a.gain) {
@@ -180,8 +185,7 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
             uint32_t bf[16];
             load_bfrag<QT, false>(planes + col_limb(g) * stride + b * 256, t, bf);
             const uint8_t *ua = wtile + (size_t)b * HTB, *ub = htB != htA ? ua + (size_t)nb * HTB : ua;
-            if (QT == QT_Q4K) item_q4k(ua, ub, lane, a.fw, bf, half, acc);
-            else              item_q6k(ua, ub, lane, a.fw, bf, half, acc);
+            run_item<QT, false>(ua, ub, lane, a.fw, bf, half, acc);
         }
     atomicAdd(&red[g][2 * t], (unsigned long long)acc[0]);
     atomicAdd(&red[g + 8][2 * t], (unsigned long long)acc[2]);
@@ -231,7 +235,11 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
             const int64_t w = s_logits[j];
             rank += (w > v) || (w == v && j < e);
         }
-        if (rank < a.k) { a.ids[rank] = e; a.gates[rank] = sigmoid_fixed_c(v, a.fa, log2e, clip); }
+        if (rank < a.k) {
+            a.ids[rank] = e; a.gates[rank] = sigmoid_fixed_c(v, a.fa, log2e, clip);
+            if (a.sel_ptrs)
+                for (int m = 0; m < 3; m++) a.sel_ptrs[m * a.k + rank] = a.tabs[(size_t)m * a.n_experts + e];
+        }
     }
 }
 
@@ -257,12 +265,17 @@ cudaError_t launch_route(const RouteArgs &a, cudaStream_t s) {
     }
     cudaLaunchConfig_t cfgl = {};
     cfgl.gridDim = dim3(grid); cfgl.blockDim = dim3(RT_THREADS); cfgl.dynamicSmemBytes = smem; cfgl.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     int n_attr = 0;
     if (use_cluster) {
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = grid; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         n_attr = 1;
+    }
+    if (a.pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        n_attr++;
     }
     cfgl.attrs = attr; cfgl.numAttrs = n_attr;
     const cudaError_t e = cudaLaunchKernelEx(&cfgl, kern, a);

@@ -25,6 +25,23 @@ namespace iie {
 namespace {
 
 constexpr int NWARPS = 16;
+
+// Optional phase timestamps (compile with -DIIE_TRACE): per CTA, %globaltimer at kernel entry, after the
+// copies were issued, when the first / last tile had arrived, after the last item and at exit.
+#ifdef IIE_TRACE
+__device__ unsigned long long g_trace[256 * 8];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ unsigned long long g_trace2[16 * 8 * 8];
+#define TRACE_ITEM(k, pt) do { if (lane == 0 && blockIdx.x == 3 && (k) < 8) g_trace2[(warp * 8 + (k)) * 8 + (pt)] = gtime(); } while (0)
+#define TRACE(slot) do { if (threadIdx.x == 0 && blockIdx.x < 256) g_trace[blockIdx.x * 8 + (slot)] = gtime(); } while (0)
+#define TRACE_ANY(slot) do { if (lane == 0 && blockIdx.x < 256) atomicMax(&g_trace[blockIdx.x * 8 + (slot)], gtime()); } while (0)
+#define TRACE_MIN(slot) do { if (lane == 0 && blockIdx.x < 256) atomicMin(&g_trace[blockIdx.x * 8 + (slot)], gtime()); } while (0)
+#else
+#define TRACE_ITEM(k, pt) do {} while (0)
+#define TRACE(slot) do {} while (0)
+#define TRACE_ANY(slot) do {} while (0)
+#define TRACE_MIN(slot) do {} while (0)
+#endif
 constexpr unsigned WAIT_LIMIT = 1u << 22;   // mbarrier polls before a wait gives up and raises flag bit 3
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -52,7 +69,7 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-template <int QT, int MODE>
+template <int QT, int MODE, bool FAST>
 __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
@@ -67,69 +84,96 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
     int *t_sel = done + tpc, *t_pos = t_sel + tpc;               // tile -> (selected matrix slot, tile inside it)
     __shared__ int s_timeout;
 
+    TRACE(0);
+#ifdef IIE_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 256) { g_trace[blockIdx.x * 8 + 2] = ~0ULL; g_trace[blockIdx.x * 8 + 3] = 0; g_trace[blockIdx.x * 8 + 4] = 0; g_trace[blockIdx.x * 8 + 6] = 0; }
+#endif
     const int n_tiles = a.n_sel * a.tiles_per_expert;
     const int tile0 = (int)blockIdx.x * tpc;
     const int my_tiles = min(tpc, n_tiles - tile0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long n_ht = (a.out_f + 7) >> 3;
+    const int n_ht = (int)((a.out_f + 7) >> 3);
 
     for (int i = threadIdx.x; i < my_tiles * 128; i += blockDim.x) red[i] = 0ULL;
     for (int i = threadIdx.x; i < my_tiles; i += blockDim.x) {
         done[i] = 0;
         const int tau = tile0 + i, sl = tau / a.tiles_per_expert;
         t_sel[i] = sl; t_pos[i] = tau - sl * a.tiles_per_expert;
+        mbar_init(&bars[i], 1);
     }
-    if (threadIdx.x == 0) {
-        s_timeout = 0;
-        for (int i = 0; i < my_tiles; i++) mbar_init(&bars[i], 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
+    if (threadIdx.x == 0) s_timeout = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < my_tiles; i++) {
-            const int s = t_sel[i], p = t_pos[i];
-            const int e = a.sel ? a.sel[s] : s;
-            uint8_t *dst = wbuf + (size_t)i * tile_bytes;
-            if (MODE == MODE_GATEUP) {
-                mbar_expect_tx(&bars[i], (uint32_t)tile_bytes);
-                bulk_g2s(dst, a.wa[e] + (size_t)p * nb * HTB, (uint32_t)(nb * HTB), &bars[i]);
-                bulk_g2s(dst + nb * HTB, a.wb[e] + (size_t)p * nb * HTB, (uint32_t)(nb * HTB), &bars[i]);
-            } else {
-                const int units = (2LL * p + 1 < n_ht) ? 2 : 1;          // an odd last half-tile stands alone
-                mbar_expect_tx(&bars[i], (uint32_t)(units * nb * HTB));
-                bulk_g2s(dst, a.wa[e] + (size_t)(2 * p) * nb * HTB, (uint32_t)(units * nb * HTB), &bars[i]);
-            }
+    // Programmatic dependent launch: everything above touched only this CTA's shared memory.  When the
+    // selected-expert pointers were final before the previous kernel started (early_weights), the weight
+    // copies are requested before waiting for that kernel, so they overlap its execution.
+    if (a.pdl && !a.early_weights) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
+    // one lane per tile resolves its matrix pointer and asks the copy engine for the whole tile
+    for (int i = threadIdx.x; i < my_tiles; i += blockDim.x) {
+        const int s = t_sel[i], p = t_pos[i];
+        const uint8_t *pa, *pb = nullptr;
+        if (a.sel_wa) { pa = a.sel_wa[s]; if (MODE == MODE_GATEUP) pb = a.sel_wb[s]; }
+        else { const int e = a.sel ? a.sel[s] : s; pa = a.wa[e]; if (MODE == MODE_GATEUP) pb = a.wb[e]; }
+        uint8_t *dst = wbuf + (size_t)i * tile_bytes;
+        if (MODE == MODE_GATEUP) {
+            mbar_expect_tx(&bars[i], (uint32_t)tile_bytes);
+            bulk_g2s(dst, pa + (size_t)p * nb * HTB, (uint32_t)(nb * HTB), &bars[i]);
+            bulk_g2s(dst + nb * HTB, pb + (size_t)p * nb * HTB, (uint32_t)(nb * HTB), &bars[i]);
+        } else {
+            const int units = (2 * p + 1 < n_ht) ? 2 : 1;                // an odd last half-tile stands alone
+            mbar_expect_tx(&bars[i], (uint32_t)(units * nb * HTB));
+            bulk_g2s(dst, pa + (size_t)(2 * p) * nb * HTB, (uint32_t)(units * nb * HTB), &bars[i]);
         }
     }
+    if (a.pdl && a.early_weights) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
+    TRACE(1);
     const bool half = a.x_nl ? (*a.x_nl <= 4) : false;
 
+    // items (tile, block) are dealt round-robin to the warps; indices advance without divisions
     const int n_items = my_tiles * nb;
-    for (int it = warp; it < n_items; it += NWARPS) {
-        const int ti = it / nb, b = it - ti * nb;
+    const int step_t = NWARPS / nb, step_b = NWARPS - step_t * nb;
+    int ti = warp / nb, b = warp - ti * nb;
+    const int g = lane >> 2, t = lane & 3;
+    const long long xoff = (long long)col_limb(g) * K;
+    uint32_t bf[16];
+    const int8_t *xcur = nullptr;
+    int bcur = -1;
+    int item_no = 0;
+    for (int it = warp; it < n_items; it += NWARPS, item_no++) {
+        TRACE_ITEM(item_no, 0);
         const int s = t_sel[ti], p = t_pos[ti];
         const int8_t *xp = a.xl + (a.x_per_sel ? (long long)s * 8 * K : 0);
+        if (xp != xcur || b != bcur) {                        // activation fragments: reused while (vector, block) repeat
+            load_bfrag<QT, true>(xp + xoff + (long long)b * 256, t, bf);
+            xcur = xp; bcur = b;
+        }
         const uint8_t *ua = wbuf + (size_t)ti * tile_bytes + (size_t)b * HTB;
         const uint8_t *ub;
         if (MODE == MODE_GATEUP) ub = ua + (size_t)nb * HTB;
-        else ub = (2LL * p + 1 < n_ht) ? ua + (size_t)nb * HTB : ua;
-        const int g = lane >> 2, t = lane & 3;
-        uint32_t bf[16];                                      // activation fragments first: they overlap the wait
-        load_bfrag<QT, true>(xp + (long long)col_limb(g) * K + (long long)b * 256, t, bf);
-        if (!mbar_wait(&bars[ti], 0)) { s_timeout = 1; continue; }
+        else ub = (2 * p + 1 < n_ht) ? ua + (size_t)nb * HTB : ua;
+        const int ti_now = ti;
+        b += step_b; ti += step_t;
+        if (b >= nb) { b -= nb; ti++; }
+        TRACE_ITEM(item_no, 1);
+        if (!mbar_wait(&bars[ti_now], 0)) { s_timeout = 1; continue; }
+        TRACE_ITEM(item_no, 2);
+        TRACE_MIN(2); TRACE_ANY(3);
         int64_t acc[4] = {0, 0, 0, 0};
-        if (QT == QT_Q4K) item_q4k(ua, ub, lane, a.fw, bf, half, acc);
-        else              item_q6k(ua, ub, lane, a.fw, bf, half, acc);
-        unsigned long long *r = red + (size_t)ti * 128;
+        run_item<QT, FAST>(ua, ub, lane, a.fw, bf, half, acc);
+        TRACE_ITEM(item_no, 3);
+        unsigned long long *r = red + (size_t)ti_now * 128;
         atomicAdd(&r[g * 8 + 2 * t], (unsigned long long)acc[0]);
         atomicAdd(&r[(g + 8) * 8 + 2 * t], (unsigned long long)acc[2]);
         if (!half) {
             atomicAdd(&r[g * 8 + 2 * t + 1], (unsigned long long)acc[1]);
             atomicAdd(&r[(g + 8) * 8 + 2 * t + 1], (unsigned long long)acc[3]);
         }
+        TRACE_ANY(4);
+        TRACE_ITEM(item_no, 4);
         // the warp that completes a tile (all nb blocks added) runs its epilogue; nobody waits
         __threadfence_block();
         int prior = 0;
-        if (lane == 0) prior = atomicAdd(&done[ti], 1);
+        if (lane == 0) prior = atomicAdd(&done[ti_now], 1);
         prior = __shfl_sync(0xffffffffu, prior, 0);
         if (prior != nb - 1) continue;
         __threadfence_block();
@@ -171,11 +215,26 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
             }
         }
     }
+    TRACE_ANY(6);
     __syncthreads();
+    TRACE(5);
     if (s_timeout && threadIdx.x == 0) atomicOr(a.flags, 8);
 }
 
-template <int QT, int MODE>
+#ifdef IIE_TRACE
+}  // namespace
+}  // namespace iie
+extern "C" int iie_trace2_read(unsigned long long *out) {
+    return cudaMemcpyFromSymbol(out, iie::g_trace2, sizeof(unsigned long long) * 16 * 8 * 8) == cudaSuccess ? 0 : 1;
+}
+extern "C" int iie_trace_read(unsigned long long *out, int n) {
+    return cudaMemcpyFromSymbol(out, iie::g_trace, sizeof(unsigned long long) * (n < 2048 ? n : 2048)) == cudaSuccess ? 0 : 1;
+}
+namespace iie {
+namespace {
+#endif
+
+template <int QT, int MODE, bool FAST>
 cudaError_t launch_stream_t(const StreamArgs &a_in, cudaStream_t s) {
     StreamArgs a = a_in;
     constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
@@ -193,13 +252,24 @@ cudaError_t launch_stream_t(const StreamArgs &a_in, cudaStream_t s) {
     const size_t smem = (size_t)tpc * per_tile + 64;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(stream_kernel<QT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(stream_kernel<QT, MODE, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    stream_kernel<QT, MODE><<<grid, NWARPS * 32, smem, s>>>(a);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(NWARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = a.pdl ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, stream_kernel<QT, MODE, FAST>, a);
     note_launch();
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+template <int QT, int MODE>
+cudaError_t launch_stream_f(const StreamArgs &a, cudaStream_t s) {
+    return a.fast ? launch_stream_t<QT, MODE, true>(a, s) : launch_stream_t<QT, MODE, false>(a, s);
 }
 
 }  // namespace
@@ -207,14 +277,14 @@ cudaError_t launch_stream_t(const StreamArgs &a_in, cudaStream_t s) {
 cudaError_t launch_stream(int qtype, int mode, const StreamArgs &a, cudaStream_t s) {
     if (a.n_sel <= 0 || a.out_f <= 0 || a.n_blocks <= 0) return cudaErrorInvalidValue;
     if (qtype == QT_Q4K) {
-        if (mode == MODE_LINEAR) return launch_stream_t<QT_Q4K, MODE_LINEAR>(a, s);
-        if (mode == MODE_GATEUP) return launch_stream_t<QT_Q4K, MODE_GATEUP>(a, s);
-        return launch_stream_t<QT_Q4K, MODE_DOWN>(a, s);
+        if (mode == MODE_LINEAR) return launch_stream_f<QT_Q4K, MODE_LINEAR>(a, s);
+        if (mode == MODE_GATEUP) return launch_stream_f<QT_Q4K, MODE_GATEUP>(a, s);
+        return launch_stream_f<QT_Q4K, MODE_DOWN>(a, s);
     }
     if (qtype == QT_Q6K) {
-        if (mode == MODE_LINEAR) return launch_stream_t<QT_Q6K, MODE_LINEAR>(a, s);
-        if (mode == MODE_GATEUP) return launch_stream_t<QT_Q6K, MODE_GATEUP>(a, s);
-        return launch_stream_t<QT_Q6K, MODE_DOWN>(a, s);
+        if (mode == MODE_LINEAR) return launch_stream_f<QT_Q6K, MODE_LINEAR>(a, s);
+        if (mode == MODE_GATEUP) return launch_stream_f<QT_Q6K, MODE_GATEUP>(a, s);
+        return launch_stream_f<QT_Q6K, MODE_DOWN>(a, s);
     }
     return cudaErrorInvalidValue;
 }
