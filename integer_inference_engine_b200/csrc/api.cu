@@ -669,7 +669,7 @@ extern "C" int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long l
         !fast_envelope(L.down_q, L.e_ffn / 256, L.maxd_down, L.maxdmin_down, fw)) return 3;
     const int E = L.n_experts, k = L.top_k;
     const long long P = T * k;
-    if (T == 1 && r.qtype != QT_I64 && L.d_model <= 8192 && k <= 32) {
+    if (T == 1 && r.qtype != QT_I64 && L.d_model <= 4096 && k <= 32) {
         int *ids1 = ids_dev ? ids_dev : (int *)ensure(R_IDS, (size_t)P * sizeof(int));
         int64_t *gates1 = gates_dev ? gates_dev : (int64_t *)ensure(R_GATES, (size_t)P * 8);
         if (!ids1 || !gates1) return 1;
@@ -763,7 +763,7 @@ extern "C" int iie_moe_block_dev(long long layer, long long gain_h, const int64_
         gain = (const int64_t *)g_w[gain_h].d;
     }
     const size_t n = (size_t)T * L.d_model, P = (size_t)T * L.top_k;
-    if (T == 1 && g_w[L.router].qtype != QT_I64 && L.d_model <= 8192 && L.top_k <= 32) {
+    if (T == 1 && g_w[L.router].qtype != QT_I64 && L.d_model <= 4096 && L.top_k <= 32) {
         int *ids = ids_dev ? ids_dev : (int *)ensure(R_IDS, P * sizeof(int));
         int64_t *gates = gates_dev ? gates_dev : (int64_t *)ensure(R_GATES, P * 8);
         if (!ids || !gates) return 1;

@@ -17,10 +17,18 @@ namespace cg = cooperative_groups;
 
 namespace iie {
 
+#ifdef IIE_TRACE
+__device__ unsigned long long g_rtrace[16 * 16];
+__device__ __forceinline__ unsigned long long rt_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define RTRACE(slot) do { if (threadIdx.x == 0 && blockIdx.x < 16) g_rtrace[blockIdx.x * 16 + (slot)] = rt_gtime(); } while (0)
+#else
+#define RTRACE(slot) do {} while (0)
+#endif
+
 namespace {
 
 constexpr int RT_THREADS = 256;
-constexpr int RT_MAX_D = 8192;            // elements of one row staged per CTA
+constexpr int RT_MAX_D = 4096;            // elements of one row staged per CTA (tile + planes + x + gain fit shared memory)
 constexpr int RT_PAD = 32;                // plane padding (bytes): keeps the 8 limb planes on different banks
 
 __device__ __forceinline__ unsigned long long uabs64(int64_t v) { return v < 0 ? (0ULL - (unsigned long long)v) : (unsigned long long)v; }
@@ -53,13 +61,25 @@ __device__ __forceinline__ int64_t floor_div_recip(int64_t num, unsigned long lo
     return num >= 0 ? (int64_t)q : -(int64_t)q - (r != 0);
 }
 
+// rank of element e among n logits: how many beat it (greater, or equal with a lower index)
+__device__ __forceinline__ int rank_part(const int64_t *lg, int e, int64_t v, int j0, int j1) {
+    int rank = 0;
+    for (int j = j0; j < j1; j++) {
+        const int64_t w = lg[j];
+        rank += (w > v) || (w == v && j < e);
+    }
+    return rank;
+}
+
 template <int QT, bool CLUSTER>
 __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
     const int d = a.d, stride = d + RT_PAD, nb = d / 256;
-    uint8_t *wtile = smem;                                                  // this CTA's router tile: 2 units x nb blocks
+    uint8_t *wtile = smem;                                                     // this CTA's router tile: 2 units x nb blocks
     int8_t *planes = reinterpret_cast<int8_t *>(smem + (size_t)2 * nb * HTB);  // [8][stride]
+    int64_t *xs = reinterpret_cast<int64_t *>(planes + (size_t)8 * stride);    // [d] staged input row
+    int64_t *gs = xs + d;                                                      // [d] staged gain
     __shared__ unsigned long long s_lo[RT_THREADS / 32], s_hi[RT_THREADS / 32], s_max[RT_THREADS / 32], s_gmax[RT_THREADS / 32];
     __shared__ unsigned long long s_rms, s_inv, s_gm;
     __shared__ int s_bad, s_nl, s_last, s_timeout;
@@ -67,8 +87,9 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
     __shared__ int64_t s_logits[1024];
     __shared__ __align__(8) uint64_t s_bar;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    RTRACE(0);
 
-    // ---- ask for the router tile first: it does not depend on x ----------------------------------------
+    // ---- before the dependency wait: everything that reads only immutable data ---------------------------
     const long long n_ht = ((long long)a.n_experts + 7) >> 3;
     const long long htA = 2LL * blockIdx.x, htB = htA + 1 < n_ht ? htA + 1 : htA;
     if (tid == 0) {
@@ -84,79 +105,99 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
     if (a.tabs && blockIdx.x == 0)                       // warm the layer's pointer tables in L2 for the tail of this kernel
         for (int i = tid * 16; i < 3 * a.n_experts; i += RT_THREADS * 16)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(a.tabs + i));
-    // Programmatic dependent launch: nothing above read data written by earlier kernels.
+    unsigned long long gmx = 0;
+    if (a.gain)
+        for (int i = tid * 2; i < d; i += RT_THREADS * 2) {
+            const longlong2 gv = *reinterpret_cast<const longlong2 *>(a.gain + i);
+            *reinterpret_cast<longlong2 *>(gs + i) = gv;
+            const unsigned long long g0 = uabs64(gv.x), g1 = uabs64(gv.y);
+            gmx = g0 > gmx ? g0 : gmx; gmx = g1 > gmx ? g1 : gmx;
+        }
     if (a.pdl) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
 
-    // ---- sum of squares and magnitudes --------------------------------------------------------------------
-    if (a.gain) {
-        u128 ssq = 0; unsigned long long mx = 0, gmx = 0;
-        for (int i = tid; i < d; i += RT_THREADS) {
-            const unsigned long long v = uabs64(a.x[i]);
-            ssq += (u128)v * v;
-            mx = v > mx ? v : mx;
-            const unsigned long long gv = uabs64(a.gain[i]);
-            gmx = gv > gmx ? gv : gmx;
+    RTRACE(1);
+    // ---- stage x, sum of squares and magnitudes -------------------------------------------------------
+    {
+        u128 ssq = 0; unsigned long long mx = 0;
+        for (int i = tid * 2; i < d; i += RT_THREADS * 2) {
+            const longlong2 xv = *reinterpret_cast<const longlong2 *>(a.x + i);
+            *reinterpret_cast<longlong2 *>(xs + i) = xv;
+            const unsigned long long v0 = uabs64(xv.x), v1 = uabs64(xv.y);
+            ssq += (u128)v0 * v0; ssq += (u128)v1 * v1;
+            mx = v0 > mx ? v0 : mx; mx = v1 > mx ? v1 : mx;
         }
-        unsigned long long lo = (unsigned long long)ssq, hi = (unsigned long long)(ssq >> 64);
+        if (a.gain) {
+            unsigned long long lo = (unsigned long long)ssq, hi = (unsigned long long)(ssq >> 64);
 #pragma unroll
-        for (int s = 16; s > 0; s >>= 1) {
-            const unsigned long long lo2 = __shfl_xor_sync(0xffffffffu, lo, s), hi2 = __shfl_xor_sync(0xffffffffu, hi, s);
-            const u128 sum = (((u128)hi << 64) | lo) + (((u128)hi2 << 64) | lo2);
-            lo = (unsigned long long)sum; hi = (unsigned long long)(sum >> 64);
-            const unsigned long long m2 = __shfl_xor_sync(0xffffffffu, mx, s), g2 = __shfl_xor_sync(0xffffffffu, gmx, s);
-            mx = m2 > mx ? m2 : mx; gmx = g2 > gmx ? g2 : gmx;
-        }
-        if (lane == 0) { s_lo[warp] = lo; s_hi[warp] = hi; s_max[warp] = mx; s_gmax[warp] = gmx; }
-        __syncthreads();
-        if (tid == 0) {
-            u128 total = 0; unsigned long long m = 0, gm = 0;
-            for (int i = 0; i < RT_THREADS / 32; i++) {
-                total += ((u128)s_hi[i] << 64) | s_lo[i];
-                m = s_max[i] > m ? s_max[i] : m; gm = s_gmax[i] > gm ? s_gmax[i] : gm;
+            for (int s = 16; s > 0; s >>= 1) {
+                const unsigned long long lo2 = __shfl_xor_sync(0xffffffffu, lo, s), hi2 = __shfl_xor_sync(0xffffffffu, hi, s);
+                const u128 sum = (((u128)hi << 64) | lo) + (((u128)hi2 << 64) | lo2);
+                lo = (unsigned long long)sum; hi = (unsigned long long)(sum >> 64);
+                const unsigned long long m2 = __shfl_xor_sync(0xffffffffu, mx, s), g2 = __shfl_xor_sync(0xffffffffu, gmx, s);
+                mx = m2 > mx ? m2 : mx; gmx = g2 > gmx ? g2 : gmx;
             }
-            if (m > (1ULL << 57)) s_bad = 1;                 // keeps the 128-bit sum of squares exact
-            u128 mean;
-            if ((total >> 64) == 0) mean = (u128)((unsigned long long)total / (unsigned long long)d);
-            else mean = total / (u128)(unsigned long long)d;
-            const u128 rms = isqrt128(mean + a.eps);
-            if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) s_bad = 1;
-            s_rms = (unsigned long long)rms; s_gm = gm;
-            s_inv = rms != 0 ? 0xFFFFFFFFFFFFFFFFULL / (unsigned long long)rms : 0;
+            if (lane == 0) { s_lo[warp] = lo; s_hi[warp] = hi; s_max[warp] = mx; s_gmax[warp] = gmx; }
+            __syncthreads();
+            if (tid == 0) {
+                u128 total = 0; unsigned long long m = 0, gm = 0;
+                for (int i = 0; i < RT_THREADS / 32; i++) {
+                    total += ((u128)s_hi[i] << 64) | s_lo[i];
+                    m = s_max[i] > m ? s_max[i] : m; gm = s_gmax[i] > gm ? s_gmax[i] : gm;
+                }
+                if (m > (1ULL << 57)) s_bad = 1;                 // keeps the 128-bit sum of squares exact
+                u128 mean;
+                if ((total >> 64) == 0) mean = (u128)((unsigned long long)total / (unsigned long long)d);
+                else mean = total / (u128)(unsigned long long)d;
+                const u128 rms = isqrt128(mean + a.eps);
+                if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) s_bad = 1;
+                s_rms = (unsigned long long)rms; s_gm = gm;
+                s_inv = rms != 0 ? 0xFFFFFFFFFFFFFFFFULL / (unsigned long long)rms : 0;
+            }
         }
     }
     __syncthreads();
     if (s_bad) { if (tid == 0 && blockIdx.x == 0) atomicOr(a.flags, 2); return; }   // uniform over the grid
 
-    // ---- normalise, apply the gain, split into limb planes ---------------------------------------------
+    RTRACE(2);
+    // ---- normalise, apply the gain, split into limb planes (four consecutive elements per step) ------------
     const unsigned long long rms = s_rms, inv = s_inv, gm = s_gm;
     bool bad = false, over = false;
     int nl = 1;
-    for (int i = tid; i < d; i += RT_THREADS) {
-        const int64_t xv = a.x[i];
-        int64_t y = xv;
-        if (a.gain) {
-            if (uabs64(xv) < (1ULL << (62 - a.fa)) && rms < (1ULL << 62)) y = floor_div_recip(xv * ((long long)1 << a.fa), rms, inv);
-            else {
-                const i128 num = (i128)xv * ((i128)1 << a.fa);
-                i128 q = num / (i128)rms;
-                if (num < 0 && q * (i128)rms != num) q -= 1;
-                if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; q = 0; }
-                y = (int64_t)q;
-            }
-            if ((u128)uabs64(y) * gm > (u128)INT64_MAX) bad = true;      // the oracle refuses such a gain product
-            y = mul_shift(y, a.gain[i], a.fa);
-        }
-        bool ok;
-        const uint64_t dg = balanced_digits8(y, ok);
-        over |= !ok;
-        nl = max(nl, digits_used(dg));
+    for (int i = tid * 4; i < d; i += RT_THREADS * 4) {
+        uint32_t pw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int64_t yv[4];
 #pragma unroll
-        for (int l = 0; l < 8; l++) planes[l * stride + i] = (int8_t)(dg >> (8 * l));
+        for (int e = 0; e < 4; e++) {
+            const int64_t xv = xs[i + e];
+            int64_t y = xv;
+            if (a.gain) {
+                if (uabs64(xv) < (1ULL << (62 - a.fa)) && rms < (1ULL << 62)) y = floor_div_recip(xv * ((long long)1 << a.fa), rms, inv);
+                else {
+                    const i128 num = (i128)xv * ((i128)1 << a.fa);
+                    i128 q = num / (i128)rms;
+                    if (num < 0 && q * (i128)rms != num) q -= 1;
+                    if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; q = 0; }
+                    y = (int64_t)q;
+                }
+                if ((u128)uabs64(y) * gm > (u128)INT64_MAX) bad = true;      // the oracle refuses such a gain product
+                y = mul_shift(y, gs[i + e], a.fa);
+            }
+            yv[e] = y;
+            bool ok;
+            const uint64_t dg = balanced_digits8(y, ok);
+            over |= !ok;
+            nl = max(nl, digits_used(dg));
+#pragma unroll
+            for (int l = 0; l < 8; l++) pw[l] |= (uint32_t)((dg >> (8 * l)) & 0xFF) << (8 * e);
+        }
+#pragma unroll
+        for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(planes + l * stride + i) = pw[l];
         if (blockIdx.x == 0) {
 #pragma unroll
-            for (int l = 0; l < 8; l++) a.hl[(long long)l * d + i] = (int8_t)(dg >> (8 * l));
-            if (a.h_out) a.h_out[i] = y;
-            if (a.init_out && a.init_mode) a.init_out[i] = a.init_mode == 2 ? xv : 0;
+            for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(a.hl + (long long)l * d + i) = pw[l];
+            if (a.h_out) { for (int e = 0; e < 4; e++) a.h_out[i + e] = yv[e]; }
+            if (a.init_out && a.init_mode)
+                for (int e = 0; e < 4; e++) a.init_out[i + e] = a.init_mode == 2 ? xs[i + e] : 0;
         }
     }
     if (bad) atomicOr(a.flags, 2);
@@ -169,6 +210,7 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
     if (blockIdx.x == 0 && tid == 0) { *a.h_nl = s_nl; if (a.gu_nl) *a.gu_nl = 0; }
     const bool half = s_nl <= 4;
 
+    RTRACE(3);
     // ---- router rows of this CTA: one 16-row tile, K split over the warps ------------------------------
     const int g = lane >> 2, t = lane & 3;
     int64_t acc[4] = {0, 0, 0, 0};
@@ -196,22 +238,41 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
     __syncthreads();
     if (s_timeout && tid == 0) atomicOr(a.flags, 8);
 
-    // ---- gather the logits: distributed shared memory inside a cluster, or a last-CTA ticket --------------
+    RTRACE(4);
+    const int64_t log2e = sigmoid_log2e(a.fa), clip = sigmoid_clip(a.fa);
+    const int n = a.n_experts;
     if (CLUSTER) {
+        // ---- every CTA of the cluster receives all logits through distributed shared memory, then ranks
+        //      its own 16 rows: sixteen threads per row each compare against a slice of the logits
         cg::cluster_group cluster = cg::this_cluster();
+        const unsigned nranks = cluster.num_blocks();
         if (tid < 16) {
             const long long row = (tid < 8 ? htA : htB) * 8 + (tid & 7);
-            if (row < a.n_experts && (tid < 8 || htB != htA)) {
-                int64_t *remote = cluster.map_shared_rank(s_logits, 0);
-                remote[row] = recombine_cols(red[tid], a.fw);
+            if (row < n && (tid < 8 || htB != htA)) {
+                const int64_t v = recombine_cols(red[tid], a.fw);
+                for (unsigned r = 0; r < nranks; r++) cluster.map_shared_rank(s_logits, r)[row] = v;
             }
         }
         cluster.sync();
-        if (cluster.block_rank() != 0) return;
+        RTRACE(5);
+        const int el = tid >> 4, part = tid & 15;
+        const long long row = (el < 8 ? htA : htB) * 8 + (el & 7);
+        const bool live = row < n && (el < 8 || htB != htA);
+        const int64_t v = live ? s_logits[row] : 0;
+        const int per = (n + 15) >> 4, j0 = min(n, part * per), j1 = min(n, j0 + per);
+        int rank = live ? rank_part(s_logits, (int)row, v, j0, j1) : 0;
+        rank += __shfl_xor_sync(0xffffffffu, rank, 8); rank += __shfl_xor_sync(0xffffffffu, rank, 4);
+        rank += __shfl_xor_sync(0xffffffffu, rank, 2); rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+        if (live && part == 0 && rank < a.k) {
+            a.ids[rank] = (int)row; a.gates[rank] = sigmoid_fixed_c(v, a.fa, log2e, clip);
+            if (a.sel_ptrs)
+                for (int m = 0; m < 3; m++) a.sel_ptrs[m * a.k + rank] = a.tabs[(size_t)m * n + row];
+        }
     } else {
+        // ---- no cluster: the CTA that finishes last ranks everything ---------------------------------
         if (tid < 16) {
             const long long row = (tid < 8 ? htA : htB) * 8 + (tid & 7);
-            if (row < a.n_experts && (tid < 8 || htB != htA)) a.logits[row] = recombine_cols(red[tid], a.fw);
+            if (row < n && (tid < 8 || htB != htA)) a.logits[row] = recombine_cols(red[tid], a.fw);
         }
         __threadfence();
         __syncthreads();
@@ -222,25 +283,20 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
         __syncthreads();
         if (!s_last) return;
         __threadfence();
-        for (int i = tid; i < a.n_experts; i += RT_THREADS) s_logits[i] = *((volatile int64_t *)&a.logits[i]);
+        for (int i = tid; i < n; i += RT_THREADS) s_logits[i] = *((volatile int64_t *)&a.logits[i]);
         __syncthreads();
-    }
-
-    // ---- top-k by rank: element e is pick number #{j : v_j > v_e, or v_j == v_e and j < e} -----------------
-    const int64_t log2e = sigmoid_log2e(a.fa), clip = sigmoid_clip(a.fa);
-    for (int e = tid; e < a.n_experts; e += RT_THREADS) {
-        const int64_t v = s_logits[e];
-        int rank = 0;
-        for (int j = 0; j < a.n_experts; j++) {
-            const int64_t w = s_logits[j];
-            rank += (w > v) || (w == v && j < e);
-        }
-        if (rank < a.k) {
-            a.ids[rank] = e; a.gates[rank] = sigmoid_fixed_c(v, a.fa, log2e, clip);
-            if (a.sel_ptrs)
-                for (int m = 0; m < 3; m++) a.sel_ptrs[m * a.k + rank] = a.tabs[(size_t)m * a.n_experts + e];
+        RTRACE(5);
+        for (int e = tid; e < n; e += RT_THREADS) {
+            const int64_t v = s_logits[e];
+            const int rank = rank_part(s_logits, e, v, 0, n);
+            if (rank < a.k) {
+                a.ids[rank] = e; a.gates[rank] = sigmoid_fixed_c(v, a.fa, log2e, clip);
+                if (a.sel_ptrs)
+                    for (int m = 0; m < 3; m++) a.sel_ptrs[m * a.k + rank] = a.tabs[(size_t)m * n + e];
+            }
         }
     }
+    RTRACE(6);
 }
 
 }  // namespace
@@ -250,7 +306,7 @@ cudaError_t launch_route(const RouteArgs &a, cudaStream_t s) {
         a.k > a.n_experts) return cudaErrorInvalidValue;
     const unsigned grid = (unsigned)((((a.n_experts + 7) >> 3) + 1) / 2);
     const int HTB = a.router_q == QT_Q4K ? HTB_Q4K : HTB_Q6K;
-    const size_t smem = (size_t)2 * (a.d / 256) * HTB + (size_t)8 * (a.d + RT_PAD);
+    const size_t smem = (size_t)2 * (a.d / 256) * HTB + (size_t)8 * (a.d + RT_PAD) + (size_t)16 * a.d;
     const bool use_cluster = grid <= 8;
     void (*kern)(RouteArgs) = nullptr;
     if (a.router_q == QT_Q4K) kern = use_cluster ? route_kernel<QT_Q4K, true> : route_kernel<QT_Q4K, false>;
@@ -259,7 +315,7 @@ cudaError_t launch_route(const RouteArgs &a, cudaStream_t s) {
     static bool configured[2][2] = {{false, false}, {false, false}};
     bool &cfg = configured[a.router_q == QT_Q6K][use_cluster];
     if (!cfg) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
         if (e != cudaSuccess) return e;
         cfg = true;
     }
@@ -283,4 +339,11 @@ cudaError_t launch_route(const RouteArgs &a, cudaStream_t s) {
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
+#ifdef IIE_TRACE
+}  // namespace iie
+extern "C" int iie_rtrace_read(unsigned long long *out) {
+    return cudaMemcpyFromSymbol(out, iie::g_rtrace, sizeof(unsigned long long) * 256) == cudaSuccess ? 0 : 1;
+}
+namespace iie {
+#endif
 }  // namespace iie

@@ -170,6 +170,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
         }
         TRACE_ANY(4);
         TRACE_ITEM(item_no, 4);
+        if (MODE == MODE_GATEUP) continue;                    // its epilogue is long: all rows run it in parallel below
         // the warp that completes a tile (all nb blocks added) runs its epilogue; nobody waits
         __threadfence_block();
         int prior = 0;
@@ -178,31 +179,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
         if (prior != nb - 1) continue;
         __threadfence_block();
         const volatile unsigned long long *rv = r;
-        if (MODE == MODE_GATEUP) {
-            int nl = 0;
-            if (lane < 8) {
-                const long long row = (long long)p * 8 + lane;
-                if (row < a.out_f) {
-                    unsigned long long cg[8], cu[8];
-#pragma unroll
-                    for (int c = 0; c < 8; c++) { cg[c] = rv[lane * 8 + c]; cu[c] = rv[(lane + 8) * 8 + c]; }
-                    const int64_t yg = recombine_cols(cg, a.fw), yu = recombine_cols(cu, a.fw);
-                    const int64_t sg = mul_shift(yg, sigmoid_fixed_c(yg, a.fa, a.sig_log2e, a.sig_clip), a.fa);
-                    const int64_t gu = mul_shift(sg, yu, a.fa);
-                    if (a.out) a.out[(long long)s * a.out_f + row] = gu;
-                    bool ok;
-                    const uint64_t d = balanced_digits8(gu, ok);
-                    if (!ok) atomicOr(a.flags, 1);
-                    nl = digits_used(d);
-#pragma unroll
-                    for (int l = 0; l < 8; l++) a.out_limbs[((long long)s * 8 + l) * a.out_f + row] = (int8_t)(d >> (8 * l));
-                }
-            }
-            nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 1));
-            nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 2));
-            nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 4));
-            if (lane == 0 && a.out_nl) atomicMax(a.out_nl, nl);
-        } else if (lane < 16) {
+        if (lane < 16) {
             const long long row = (long long)p * 16 + lane;
             if (row < a.out_f) {
                 unsigned long long cc[8];
@@ -214,6 +191,32 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
                                (unsigned long long)mul_shift(y, a.gates[s], a.fa));
             }
         }
+    }
+    if (MODE == MODE_GATEUP) {
+        // rows 0..7 of a tile are the gate projection, rows 8..15 the up projection of the same output index
+        __syncthreads();
+        int nl = 0;
+        for (int idx = threadIdx.x; idx < my_tiles * 8; idx += blockDim.x) {
+            const int tq = idx >> 3, r8 = idx & 7;
+            const int s = t_sel[tq], p = t_pos[tq];
+            const long long row = (long long)p * 8 + r8;
+            if (row >= a.out_f) continue;
+            const unsigned long long *rr = red + (size_t)tq * 128;
+            const int64_t yg = recombine_cols(rr + r8 * 8, a.fw), yu = recombine_cols(rr + (r8 + 8) * 8, a.fw);
+            const int64_t sg = mul_shift(yg, sigmoid_fixed_c(yg, a.fa, a.sig_log2e, a.sig_clip), a.fa);
+            const int64_t gu = mul_shift(sg, yu, a.fa);
+            if (a.out) a.out[(long long)s * a.out_f + row] = gu;
+            bool ok;
+            const uint64_t d = balanced_digits8(gu, ok);
+            if (!ok) atomicOr(a.flags, 1);
+            nl = max(nl, digits_used(d));
+#pragma unroll
+            for (int l = 0; l < 8; l++) a.out_limbs[((long long)s * 8 + l) * a.out_f + row] = (int8_t)(d >> (8 * l));
+        }
+        nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 16)); nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 8));
+        nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 4));  nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 2));
+        nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 1));
+        if (lane == 0 && nl > 0 && a.out_nl) atomicMax(a.out_nl, nl);
     }
     TRACE_ANY(6);
     __syncthreads();
