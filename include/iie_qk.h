@@ -155,6 +155,17 @@ void iie_profile_stage_mask(int mask);
 void iie_set_pdl(int enabled);
 unsigned long long iie_launch_count(void);
 
+/* iie_apply_dev without any allocation (no counterpart in the reference).  For callers that cannot let
+ * a library allocate device memory at call time: a process whose own pool already holds the whole
+ * device, or a latency-critical loop that cannot take the implicit synchronisation of cudaMalloc.
+ * The limb planes of the activation live in a 4 MiB array inside the library image (held by every GPU
+ * that loads the library until exit), so T * 8 * in_features must not exceed 4 194 304 bytes
+ * (e.g. T <= 256 at 2048 input features); larger requests return 4 and do nothing.  The first call
+ * on a device looks up the array's device address; make that call before starting any stream
+ * capture.  All calls share the array: two calls that overlap on the GPU race.  Same results and
+ * flag bits as iie_apply_dev. */
+int iie_apply_dev_static(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev, void *stream);
+
 /* Read and clear the device flag word (synchronises the library stream and `stream`):
  * bit 0 an activation left the 8-limb envelope, bit 1 RMSNorm envelope, bit 2 dense router sum. */
 int iie_flags_read_clear(void *stream);

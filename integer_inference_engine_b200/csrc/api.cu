@@ -802,3 +802,46 @@ extern "C" int iie_moe_block_host(long long layer, long long gain_h, const int64
         (gates_out && !d2h(gates_out, gd, P * 8)) || !sync()) { cudaGetLastError(); return 1; }
     return 0;
 }
+
+// ====================================================================================================
+// Static-scratch variant of the device-pointer product
+// ====================================================================================================
+// Some callers must not trigger a device allocation when they ask for a product: a serving process
+// whose memory pool already owns the whole device (a cudaMalloc from a library would fail or fragment
+// the pool), or a latency-critical loop that cannot afford the implicit synchronisation of
+// cudaMalloc / cudaFree.  iie_apply_dev_static is iie_apply_dev with its one piece of scratch, the
+// activation limb planes [T][8][K] int8, placed in the fixed array below instead of a grown workspace.
+// The array is part of the library image: every GPU that loads the library holds these 4 MiB until
+// the process exits.
+constexpr size_t STATIC_SCRATCH_BYTES = (size_t)4 << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+static void *g_static_scratch_addr[64];        // device address of the array, per device ordinal
+
+extern "C" int iie_apply_dev_static(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev,
+                                    void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    // The handle was registered earlier, so the library is already initialised; nothing here allocates.
+    if (g_ready != 0 || !valid_q(h) || !x_dev || !out_dev || T <= 0 || fw < 0 || fw > 62) return 1;
+    const Weight &w = g_w[h];
+    const long long K = w.nb * 256;
+    if ((unsigned long long)T > STATIC_SCRATCH_BYTES / 8 / (unsigned long long)K) return 4;   // T*8*K bytes of limb planes
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!fast_envelope(w.qtype, w.nb, w.maxd, w.maxdmin, fw))       // the exact 128-bit kernel needs no scratch
+        return launch_exact_linear((const uint8_t *)w.d, w.qtype, w.out_f, w.nb, x_dev, T, fw, out_dev, s) == cudaSuccess ? 0 : 1;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+    if (!g_static_scratch_addr[dev]) {
+        // In host code the array's name is only a handle; the kernels need its device address.
+        void *addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_static_scratch) != cudaSuccess || !addr) { cudaGetLastError(); return 1; }
+        g_static_scratch_addr[dev] = addr;
+    }
+    int8_t *planes = (int8_t *)g_static_scratch_addr[dev];
+    // Nothing in the scratch has to start at zero: the limb kernel overwrites every byte the product reads.
+    if (launch_limbs(x_dev, T, K, planes, g_flags, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    SkinnyArgs a = {};
+    a.wa = w.cell; a.wb = w.cell; a.pairs_per_group = (int)T; a.out_f = w.out_f; a.n_blocks = w.nb; a.fw = fw; a.fa = 16;
+    a.xl = planes; a.out = out_dev; a.flags = g_flags;
+    if (launch_skinny(w.qtype, MODE_LINEAR, a, 1, (int)std::min<long long>(T, 4), s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    return 0;
+}
