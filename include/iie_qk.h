@@ -153,6 +153,9 @@ int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long rows, long
 void iie_profile_stage_mask(int mask);
 /* Switch programmatic dependent launch between the three single-token kernels on (default) or off. */
 void iie_set_pdl(int enabled);
+/* Token count from which iie_moe_forward_dev uses the tcgen05 grouped GEMMs instead of the streamed
+ * kernels (default 32; a very large value disables the tensor-core path). */
+void iie_set_tc_min_tokens(long long tokens);
 unsigned long long iie_launch_count(void);
 
 /* iie_apply_dev without any allocation (no counterpart in the reference).  For callers that cannot let

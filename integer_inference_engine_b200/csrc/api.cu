@@ -58,6 +58,7 @@ int *g_flags = nullptr;               // device flag word
 int *g_cells = nullptr;               // device ints: [0] limbs of h, [1] limbs of gate*up, [2] routing ticket
 const uint8_t **g_selptr = nullptr;   // device: [3][64] pointers of the experts the last routing selected
 int g_pdl = 1;                        // programmatic dependent launch between the three decode kernels
+long long g_tc_min_tokens = 32;       // from this many tokens on, the MoE block runs on the tcgen05 grouped GEMMs
 int g_ready = -1;                     // -1 unknown, 0 usable, 1 unusable
 int g_stage_mask = 0;                 // profiling: when non-zero, iie_moe_forward_dev runs only these stages
 enum Stage { ST_LIMBS = 1, ST_ROUTER = 2, ST_TOPK = 4, ST_GATEUP = 8, ST_DOWN = 16 };
@@ -250,6 +251,76 @@ bool moe_exact_pairs(const std::vector<const Weight *> &gw, const std::vector<co
         if (launch_exact_linear((const uint8_t *)dw[i]->d, dw[i]->qtype, d_model, dw[i]->nb, g + i * e_ffn, 1, fw,
                                 dn + i * d_model, g_stream) != cudaSuccess) return false;
     return launch_combine(dn, gates_dev, T, k, d_model, fa, out_dev, g_stream) == cudaSuccess;
+}
+
+// Largest dequantised |weight| of a tensor family at this fw (from the largest block scales).
+unsigned __int128 max_weight(int qtype, unsigned maxd, unsigned maxdmin, int fw) {
+    const unsigned __int128 dq = (unsigned __int128)half_to_fixed(maxd, fw), dm = (unsigned __int128)half_to_fixed(maxdmin, fw);
+    return qtype == QT_Q4K ? dq * 945 + dm * 63 : dq * 128 * 32;
+}
+const unsigned __int128 CAP4 = 2139062143ULL, CAP5 = 547599908735ULL;      // 127 * (256^n - 1) / 255
+
+int read_cell(int idx, cudaStream_t s) {
+    int v = -1;
+    if (cudaMemcpyAsync(&v, g_cells + idx, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
+    return v;
+}
+
+// Tensor-core (tcgen05) path for many tokens: router GEMM, top-k, dispatch, grouped gate/up and down GEMMs.
+// Returns 0 done, 1 error, -1 not applicable (caller uses the streamed kernels).
+int moe_prefill_tc(const MoeLayer &L, const int64_t *h_dev, long long T, int fa, int fw, int accumulate, int64_t *out_dev,
+                   int *ids, int64_t *gates, cudaStream_t s) {
+    const Weight &r = g_w[L.router];
+    const int E = L.n_experts, k = L.top_k;
+    const long long P = T * k;
+    if (r.qtype != QT_Q4K || L.gate_q != QT_Q4K || L.d_model > 8192 || L.e_ffn > 8192) return -1;
+    if (!small_scales(L.maxd_gate, L.maxdmin_gate, fw) || !small_scales(L.maxd_down, L.maxdmin_down, fw) ||
+        !small_scales(r.maxd, r.maxdmin, fw)) return -1;
+    if (max_weight(QT_Q4K, L.maxd_gate, L.maxdmin_gate, fw) > CAP4 || max_weight(QT_Q4K, r.maxd, r.maxdmin, fw) > CAP4) return -1;
+    if (max_weight(L.down_q, L.maxd_down, L.maxdmin_down, fw) > (L.down_q == QT_Q4K ? CAP4 : CAP5)) return -1;
+    int8_t *hl = (int8_t *)ensure(R_XL, (size_t)T * 8 * L.d_model);
+    int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)T * E * 8);
+    int *off = (int *)ensure(R_GRPOFF, (size_t)(E + 2) * sizeof(int));
+    int *ptok = (int *)ensure(R_PAIRTOK, (size_t)P * sizeof(int));
+    int64_t *pg = (int64_t *)ensure(R_PAIRGATE, (size_t)P * 8);
+    int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)P * 8 * L.e_ffn);
+    int *one_off = (int *)ensure(R_META, 64);
+    if (!hl || !lg || !off || !ptok || !pg || !gul || !one_off) return 1;
+    if (cudaMemsetAsync(g_cells, 0, 2 * sizeof(int), s) != cudaSuccess) return 1;
+    if (launch_limbs(h_dev, T, L.d_model, hl, g_flags, s, g_cells) != cudaSuccess) return 1;
+    const int nl_h = read_cell(0, s);
+    if (nl_h < 1 || nl_h > 4) return nl_h < 1 ? 1 : -1;
+    // router: one "expert" that owns all T rows
+    const int host_off[2] = {0, (int)T};
+    if (cudaMemcpyAsync(one_off, host_off, sizeof(host_off), cudaMemcpyHostToDevice, s) != cudaSuccess) return 1;
+    PrefillArgs ra = {};
+    ra.wa = r.cell; ra.wb = r.cell; ra.grp_off = one_off; ra.n_experts = 1; ra.n_pairs = T; ra.out_f = E;
+    ra.n_blocks = L.d_model / 256; ra.fw = fw; ra.fa = fa; ra.xl = hl; ra.out = lg; ra.flags = g_flags;
+    if (launch_prefill(QT_Q4K, MODE_LINEAR, nl_h, ra, s) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (launch_topk(lg, T, E, k, fa, ids, gates, s) != cudaSuccess) return 1;
+    if (launch_dispatch(ids, gates, T, k, E, off, ptok, pg, s) != cudaSuccess) return 1;
+    PrefillArgs ga = {};
+    ga.wa = L.tabs; ga.wb = L.tabs + E; ga.grp_off = off; ga.n_experts = E; ga.n_pairs = P; ga.out_f = L.e_ffn;
+    ga.n_blocks = L.d_model / 256; ga.fw = fw; ga.fa = fa; ga.xl = hl; ga.xidx = ptok; ga.out = nullptr; ga.out_limbs = gul;
+    ga.out_nl = g_cells + 1; ga.flags = g_flags;
+    if (launch_prefill(QT_Q4K, MODE_GATEUP, nl_h, ga, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    const int nl_gu = read_cell(1, s);
+    if (nl_gu < 0) return 1;
+    if (!accumulate && cudaMemsetAsync(out_dev, 0, (size_t)T * L.d_model * 8, s) != cudaSuccess) return 1;
+    PrefillArgs da = {};
+    da.wa = L.tabs + 2 * E; da.wb = da.wa; da.grp_off = off; da.n_experts = E; da.n_pairs = P; da.out_f = L.d_model;
+    da.n_blocks = L.e_ffn / 256; da.fw = fw; da.fa = fa; da.xl = gul; da.xidx = nullptr; da.out = out_dev; da.gates = pg;
+    da.pair_tok = ptok; da.flags = g_flags;
+    const cudaError_t de = launch_prefill(L.down_q, MODE_DOWN, nl_gu < 1 ? 1 : nl_gu, da, s);
+    if (de == cudaSuccess) return 0;
+    cudaGetLastError();
+    // the activation needs more digits than the tensor-core tiles carry: streamed kernels for the down stage
+    MoePlan plan = {L.tabs, L.tabs + E, L.tabs + 2 * E, L.gate_q, L.down_q, L.d_model, L.e_ffn};
+    SkinnyArgs d = {};
+    d.wa = plan.down; d.wb = plan.down; d.grp_off = off; d.pairs_per_group = 1; d.out_f = L.d_model; d.n_blocks = L.e_ffn / 256;
+    d.fw = fw; d.fa = fa; d.xl = gul; d.out = out_dev; d.gates = pg; d.pair_tok = ptok; d.flags = g_flags;
+    return launch_skinny(L.down_q, MODE_DOWN, d, E, 4, s) == cudaSuccess ? 0 : 1;
 }
 
 // Single-token fused path: route (optional RMSNorm, limbs, router, top-k) -> gate/up -> down.
@@ -676,11 +747,16 @@ extern "C" int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long l
         if (!moe_decode_token(L, h_dev, nullptr, fa, fw, 0, accumulate ? 0 : 1, out_dev, ids1, gates1, s)) { cudaGetLastError(); return 1; }
         return 0;
     }
-    int8_t *hl = (int8_t *)ensure(R_XL, (size_t)T * 8 * L.d_model);
-    int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)T * E * 8);
     int *ids = ids_dev ? ids_dev : (int *)ensure(R_IDS, (size_t)P * sizeof(int));
     int64_t *gates = gates_dev ? gates_dev : (int64_t *)ensure(R_GATES, (size_t)P * 8);
-    if (!hl || !lg || !ids || !gates) return 1;
+    if (!ids || !gates) return 1;
+    if (T >= g_tc_min_tokens && g_stage_mask == 0) {
+        const int rc = moe_prefill_tc(L, h_dev, T, fa, fw, accumulate, out_dev, ids, gates, s);
+        if (rc >= 0) { if (rc) cudaGetLastError(); return rc; }
+    }
+    int8_t *hl = (int8_t *)ensure(R_XL, (size_t)T * 8 * L.d_model);
+    int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)T * E * 8);
+    if (!hl || !lg) return 1;
     if (stage_on(ST_LIMBS) && launch_limbs(h_dev, T, L.d_model, hl, g_flags, s) != cudaSuccess) return 1;
     if (stage_on(ST_ROUTER)) {
         if (r.qtype == QT_I64) {
@@ -734,6 +810,11 @@ extern "C" int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long
     }
     cudaStream_t s = (cudaStream_t)stream;              // NULL is the CUDA default stream
     return launch_rmsnorm(x_dev, rows, width, gain, fa, eps, out_dev, g_flags, s) == cudaSuccess ? 0 : 1;
+}
+
+extern "C" void iie_set_tc_min_tokens(long long tokens) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    g_tc_min_tokens = tokens < 2 ? 2 : tokens;
 }
 
 extern "C" void iie_set_pdl(int enabled) {

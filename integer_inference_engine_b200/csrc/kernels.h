@@ -88,6 +88,29 @@ struct RouteArgs {
 };
 cudaError_t launch_route(const RouteArgs &a, cudaStream_t s);
 
+// Prefill-regime grouped products on tcgen05 (prefill.cu).  Pairs are sorted by expert: expert x owns
+// pairs [grp_off[x], grp_off[x+1]).
+struct PrefillArgs {
+    const uint8_t *const *wa;      // per expert: repacked weight (down / linear weight, or gate)
+    const uint8_t *const *wb;      // per expert: up weight (MODE_GATEUP)
+    const int *grp_off;            // [n_experts + 1]
+    int n_experts;
+    long long n_pairs;             // total pairs (bounds the grid)
+    long long out_f, n_blocks;
+    int fw, fa;
+    int n_ntiles;                  // filled in by the launcher
+    long long sig_log2e, sig_clip;
+    const int8_t *xl;              // activation limb planes [x_row][8][K]
+    const int *xidx;               // pair -> x_row, or nullptr (identity)
+    int64_t *out;                  // GATEUP: gu [pair][out_f] (nullable); DOWN: [token][out_f] accumulated; LINEAR [pair][out_f]
+    int8_t *out_limbs;             // GATEUP: limb planes of gu [pair][8][out_f]
+    int *out_nl;                   // GATEUP: atomicMax of the limbs gu needs
+    const int64_t *gates;          // DOWN: per pair
+    const int *pair_tok;           // DOWN: pair -> token row
+    int *flags;
+};
+cudaError_t launch_prefill(int qtype, int mode, int nl, const PrefillArgs &a, cudaStream_t s);
+
 // Re-order raw GGUF blocks into the half-tile layout; also reduces max |d| and max |dmin| half bit
 // patterns (sign stripped) into maxbits[0..1] (device memory, caller zeroes).
 cudaError_t launch_repack(const uint8_t *raw, uint8_t *dst, long long out_f, long long n_blocks, int qtype,
@@ -97,7 +120,8 @@ cudaError_t launch_unpack(const uint8_t *src, uint8_t *raw, long long out_f, lon
                           cudaStream_t s);
 
 // int64 rows -> balanced base-256 limb planes [row][8][K]; sets flags bit 0 on overflow.
-cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, cudaStream_t s);
+cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, cudaStream_t s,
+                         int *nl_out = nullptr);   // nl_out: atomicMax of the limbs in use (caller zeroes)
 
 // Exact 128-bit reference-order product for inputs outside the fast envelope: out[pair][o].
 cudaError_t launch_exact_linear(const uint8_t *w, int qtype, long long out_f, long long n_blocks, const int64_t *x,

@@ -44,19 +44,23 @@ __global__ void repack_kernel(const uint8_t *src, uint8_t *dst, long long out_f,
 // ---------------------------------------------------------------------------------------------------
 // activation limb planes
 // ---------------------------------------------------------------------------------------------------
-__global__ void limbs_kernel(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags) {
+__global__ void limbs_kernel(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, int *nl_out) {
     const long long total = n_rows * K;
     bool bad = false;
+    int nl = 0;
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long row = idx / K, col = idx - row * K;
         bool ok;
         const uint64_t d = balanced_digits8(x[idx], ok);
         bad |= !ok;
+        const int used = d == 0 ? 1 : 8 - (__clzll((long long)d) >> 3);
+        nl = used > nl ? used : nl;
 #pragma unroll
         for (int l = 0; l < 8; l++) planes[(row * 8 + l) * K + col] = (int8_t)(d >> (8 * l));
     }
     if (bad) atomicOr(flags, 1);
+    if (nl_out && nl > 0) atomicMax(nl_out, nl);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -305,8 +309,9 @@ cudaError_t launch_unpack(const uint8_t *src, uint8_t *raw, long long out_f, lon
     return cudaGetLastError();
 }
 
-cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, cudaStream_t s) {
-    limbs_kernel<<<grid_for(n_rows * K, 256), 256, 0, s>>>(x, n_rows, K, planes, flags);
+cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, cudaStream_t s,
+                         int *nl_out) {
+    limbs_kernel<<<grid_for(n_rows * K, 256), 256, 0, s>>>(x, n_rows, K, planes, flags, nl_out);
     note_launch();
     return cudaGetLastError();
 }

@@ -1,0 +1,399 @@
+// Prefill-regime grouped expert products on the 5th-generation tensor cores (tcgen05, kind::i8).
+//
+// Replaces the reference's pair-parallel prefill kernels (north-mini-code/tools/nmc_qk_cuda.cu:2184-2201
+// matmul_multi_tok / combine_tok and the host loop :2203-2346), which stream one expert's weights once
+// per (token, expert) pair, with expert-grouped GEMMs whose weights are dequantised once per tile.
+//
+// Exactness on an int8 x int8 -> int32 tensor core.  Inside the fast envelope a dequantised weight
+// W = d_q*sc*q - dmin_q*m (Q4_K) or d_q*sc*(q-32) (Q6_K) fits NWL balanced base-256 digits and an
+// activation fits NL digits, so  sum_k W[n,k] x[m,k] = sum_{a<NWL, b<NL} 256^(a+b) sum_k Wa[n,k] xb[m,k].
+// Every digit pair (a,b) is one int8 MMA; pairs with equal a+b share a TMEM accumulator (at most
+// min(NWL,NL) pairs x K x 128 x 128 < 2^31 for K <= 8192), the accumulation runs over the FULL K, and the
+// epilogue forms sum_s 256^s acc_s in 128 bits and performs the reference's single floor shift.
+//
+// Tile: 128 (token, expert) pairs (MMA M, TMEM lanes) x BN weight rows (MMA N) x K in chunks of 64.
+// Warps 0-3 produce: they copy the activation digit planes of their pair into the canonical K-major
+// shared-memory layout (A operand) and dequantise + digit-split the weight chunk (B operand); then they
+// run the epilogue, one TMEM lane = one pair each.  Warp 4 allocates TMEM and one elected thread issues
+// the MMAs; tcgen05.commit hands a stage back to the producers.  Gate and up rows share a tile
+// (columns 0..BN/2-1 gate, BN/2..BN-1 up) so the integer SiLU * up product is formed in the epilogue.
+// Every wait is bounded; on a time-out the CTA raises flag bit 3, leaves its loops, frees TMEM and exits.
+#include <algorithm>
+
+#include "kernels.h"
+#include "layout.cuh"
+#include "mma_items.cuh"
+
+namespace iie {
+
+namespace {
+
+constexpr int PF_BM = 128, PF_KC = 64, PF_STAGES = 3, PF_THREADS = 160;
+constexpr unsigned PF_WAIT_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t pf_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void pf_bar_init(uint64_t *b, int n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pf_u32(b)), "r"(n)); }
+__device__ __forceinline__ void pf_bar_arrive(uint64_t *b) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pf_u32(b)) : "memory"); }
+__device__ __forceinline__ bool pf_bar_wait(uint64_t *b, uint32_t parity, volatile int *abort_flag) {
+    for (unsigned it = 0; it < PF_WAIT_LIMIT; it++) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(pf_u32(b)), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 1023) == 1023 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; LBO = distance of
+// the two 16-byte K halves of one MMA, SBO = distance of consecutive 8-row groups (bytes, 16-byte units).
+__device__ __forceinline__ uint64_t pf_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ULL << 46);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, int8 x int8 -> int32, M = 128, K = 32
+__device__ __forceinline__ void pf_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void pf_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pf_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void pf_tmem_ld8(uint32_t taddr, int (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+
+// four int32 weights -> one word per digit plane (byte i of plane l = digit l of weight i)
+__device__ __forceinline__ void digits4(const int (&w)[4], uint32_t (&plane)[4]) {
+    uint32_t v[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) v[i] = ((uint32_t)w[i] + 0x80808080u) ^ 0x80808080u;   // byte l = balanced digit l
+    const uint32_t t0 = __byte_perm(v[0], v[1], 0x5140), t1 = __byte_perm(v[2], v[3], 0x5140);
+    const uint32_t t2 = __byte_perm(v[0], v[1], 0x7362), t3 = __byte_perm(v[2], v[3], 0x7362);
+    plane[0] = __byte_perm(t0, t1, 0x5410); plane[1] = __byte_perm(t0, t1, 0x7632);
+    plane[2] = __byte_perm(t2, t3, 0x5410); plane[3] = __byte_perm(t2, t3, 0x7632);
+}
+
+// Dequantise 32 consecutive-k weights of one row into NWL digit planes (eight words each).
+// Q4_K: chunk = group G of a block; hsel 0 = low nibbles (first 32 columns), 1 = high nibbles.
+template <int NWL>
+__device__ __forceinline__ void dequant32_q4k(const uint8_t *unit, int rr, int G, int hsel, int fw, uint32_t (&pl)[NWL][8]) {
+    const uint4 meta = ldg128(unit + 1024 + rr * 16);
+    uint32_t sc[2], mn[2];
+    q4k_scales(meta.y, meta.z, meta.w, sc[0], sc[1], mn[0], mn[1]);
+    const int j = 2 * G + hsel;
+    const int ws = scale_small(meta.x & 0xFFFF, fw) * ubyte_at(sc[j >> 2], j & 3);
+    const int wm = scale_small(meta.x >> 16, fw) * ubyte_at(mn[j >> 2], j & 3);
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        const uint2 q = ldg64(unit + (G >> 1) * 512 + (rr * 4 + t) * 16 + (G & 1) * 8);   // qs[32G + 8t .. +7]
+        const uint32_t words[2] = {(q.x >> (4 * hsel)) & 0x0f0f0f0fu, (q.y >> (4 * hsel)) & 0x0f0f0f0fu};
+#pragma unroll
+        for (int h2 = 0; h2 < 2; h2++) {
+            int w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) w[i] = ws * (int)((words[h2] >> (8 * i)) & 0xFF) - wm;
+            uint32_t p4[4];
+            digits4(w, p4);
+#pragma unroll
+            for (int l = 0; l < 4; l++) pl[l][t * 2 + h2] = p4[l];
+            if (NWL > 4) pl[NWL - 1][t * 2 + h2] = 0;
+        }
+    }
+}
+
+// Q6_K: chunk cc (0..3) of a block covers half h = cc >> 1 and kq = 2*(cc & 1) + hsel.  |W| can need a
+// fifth digit (d_q * 128 * 32), so the split works on int64.
+template <int NWL>
+__device__ __forceinline__ void dequant32_q6k(const uint8_t *unit, int rr, int cc, int hsel, int fw, uint32_t (&pl)[NWL][8]) {
+    const int h = cc >> 1, kq = 2 * (cc & 1) + hsel;
+    const uint4 sw = ldg128(unit + 1536 + rr * 16);
+    const uint32_t scw[4] = {sw.x, sw.y, sw.z, sw.w};
+    const int64_t dq = scale_small(__ldg(reinterpret_cast<const unsigned short *>(unit + 1664 + rr * 2)), fw);
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+        const int si = 8 * h + 2 * kq + u;
+        const int64_t ws = dq * sbyte_at(scw[si >> 2], si & 3);
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            const uint4 lw = ldg128(unit + h * 512 + (rr * 4 + t) * 16);            // u0:{A,B} u1:{A,B}
+            const uint4 hw = ldg128(unit + 1024 + (rr * 4 + t) * 16);               // [h*2+u]
+            const uint32_t lsel[4] = {lw.x, lw.y, lw.z, lw.w}, hsel4[4] = {hw.x, hw.y, hw.z, hw.w};
+            const uint32_t n = lsel[u * 2 + (kq & 1)], hb = hsel4[h * 2 + u];
+            const uint32_t lo = (kq < 2 ? n : (n >> 4)) & 0x0f0f0f0fu, hi = ((hb >> (2 * kq)) << 4) & 0x30303030u;
+            const uint32_t q = lo | hi;
+            // 4 weights; digits of an int64 value, five of them kept
+            uint32_t pw[NWL];
+#pragma unroll
+            for (int l = 0; l < NWL; l++) pw[l] = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                int64_t w = ws * ((int)((q >> (8 * i)) & 0xFF) - 32);
+#pragma unroll
+                for (int l = 0; l < NWL; l++) {
+                    pw[l] |= (uint32_t)(w & 0xFF) << (8 * i);
+                    w = (w >> 8) + ((w >> 7) & 1);
+                }
+            }
+#pragma unroll
+            for (int l = 0; l < NWL; l++) pl[l][u * 4 + t] = pw[l];
+        }
+    }
+}
+
+template <int QT, int MODE, int NL, int NWL, int BN>
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArgs a) {
+    constexpr int NACC = NL + NWL - 1;
+    static_assert(NACC * BN <= 512, "accumulators exceed TMEM");
+    constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
+    constexpr int A_PLANE = 2 * 2 * (PF_BM / 8) * 128;        // [kstep][khalf][row group][128 B] = 8192
+    constexpr int B_PLANE = 2 * 2 * (BN / 8) * 128;
+    constexpr int STAGE_BYTES = NL * A_PLANE + NWL * B_PLANE;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_bar[PF_STAGES], empty_bar[PF_STAGES], accum_bar;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nb = (int)a.n_blocks, K = nb * 256, n_chunks = K / PF_KC;
+
+    // ---- which tile: (expert, 128-pair slab, BN-row slab) ---------------------------------------------
+    const int n_ntiles = a.n_ntiles;
+    const int mt = blockIdx.x / n_ntiles, ni = blockIdx.x - mt * n_ntiles;
+    int e = -1, m0 = 0, m_end = 0;
+    {
+        int acc_tiles = 0;
+        for (int x = 0; x < a.n_experts; x++) {
+            const int lo = a.grp_off[x], hi = a.grp_off[x + 1];
+            const int nt = (hi - lo + PF_BM - 1) / PF_BM;
+            if (mt < acc_tiles + nt) { e = x; m0 = lo + (mt - acc_tiles) * PF_BM; m_end = hi; break; }
+            acc_tiles += nt;
+        }
+    }
+    if (e < 0) return;                                        // grid is an upper bound on the tile count
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < PF_STAGES; s++) { pf_bar_init(&full_bar[s], 128); pf_bar_init(&empty_bar[s], 1); }
+        pf_bar_init(&accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pf_u32(&s_tmem)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp < 4) {
+        // ================= producers ====================================================================
+        const int prow = tid;                                  // pair row of this thread (A) ...
+        const int pair = m0 + prow;
+        const bool live = pair < m_end;
+        const long long xrow = live ? (a.xidx ? a.xidx[pair] : pair) : 0;
+        const int8_t *xsrc = a.xl + xrow * 8 * (long long)K;
+        const int brow = tid >> 1, hsel = tid & 1;             // ... and weight row / 32-column half (B)
+        for (int c = 0; c < n_chunks; c++) {
+            const int s = c % PF_STAGES;
+            if (c >= PF_STAGES && !pf_bar_wait(&empty_bar[s], ((c / PF_STAGES) - 1) & 1, &s_abort)) break;
+            uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
+            // A: NL digit planes x 64 columns of this thread's pair
+#pragma unroll
+            for (int b = 0; b < NL; b++) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (live) v = ldg128(xsrc + (long long)b * K + c * PF_KC + j * 16);
+                    *reinterpret_cast<uint4 *>(stage + b * A_PLANE + (j >> 1) * (A_PLANE / 2) + (j & 1) * (A_PLANE / 4) +
+                                               (prow >> 3) * 128 + (prow & 7) * 16) = v;
+                }
+            }
+            // B: BN weight rows x 64 columns, each thread one (row, 32-column half) per pass
+            for (int r0 = 0; r0 < BN; r0 += 64) {
+                const int r = r0 + brow;
+                if (r < BN) {
+                    long long wrow; const uint8_t *wbase;
+                    if (MODE == MODE_GATEUP) { wrow = (long long)ni * (BN / 2) + (r % (BN / 2)); wbase = r < BN / 2 ? a.wa[e] : a.wb[e]; }
+                    else { wrow = (long long)ni * BN + r; wbase = a.wa[e]; }
+                    uint32_t pl[NWL][8];
+                    if (wrow < a.out_f) {
+                        const uint8_t *unit = wbase + ((wrow >> 3) * nb + (c >> 2)) * HTB;
+                        if (QT == QT_Q4K) dequant32_q4k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
+                        else              dequant32_q6k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
+                    } else {
+#pragma unroll
+                        for (int l = 0; l < NWL; l++)
+#pragma unroll
+                            for (int w = 0; w < 8; w++) pl[l][w] = 0;
+                    }
+                    uint8_t *bdst = stage + NL * A_PLANE + hsel * (B_PLANE / 2) + (r >> 3) * 128 + (r & 7) * 16;
+#pragma unroll
+                    for (int l = 0; l < NWL; l++) {
+                        *reinterpret_cast<uint4 *>(bdst + l * B_PLANE) = make_uint4(pl[l][0], pl[l][1], pl[l][2], pl[l][3]);
+                        *reinterpret_cast<uint4 *>(bdst + l * B_PLANE + B_PLANE / 4) = make_uint4(pl[l][4], pl[l][5], pl[l][6], pl[l][7]);
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> visible to the MMA
+            pf_bar_arrive(&full_bar[s]);
+        }
+
+        // ================= epilogue: TMEM lane = pair ========================================================
+        if (pf_bar_wait(&accum_bar, 0, &s_abort)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
+            constexpr int NOUT = MODE == MODE_GATEUP ? BN / 2 : BN;
+            int nl_max = 0;
+            for (int c0 = 0; c0 < NOUT; c0 += 8) {
+                int64_t y0[8], y1[8];
+#pragma unroll
+                for (int part = 0; part < (MODE == MODE_GATEUP ? 2 : 1); part++) {
+                    int r[NACC][8];
+#pragma unroll
+                    for (int s = 0; s < NACC; s++) pf_tmem_ld8(tlane + s * BN + part * (BN / 2) + c0, r[s]);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        i128 v = 0;
+#pragma unroll
+                        for (int s = NACC - 1; s >= 0; s--) v = (v << 8) + (i128)r[s][j];
+                        const int64_t y = (int64_t)(v >> a.fw);
+                        if (part == 0) y0[j] = y; else y1[j] = y;
+                    }
+                }
+                if (!live) continue;
+                const long long row0 = (long long)ni * NOUT + c0;
+                if (MODE == MODE_GATEUP) {
+                    uint64_t packed[8];
+#pragma unroll
+                    for (int l = 0; l < 8; l++) packed[l] = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const int64_t sg = mul_shift(y0[j], sigmoid_fixed_c(y0[j], a.fa, a.sig_log2e, a.sig_clip), a.fa);
+                        const int64_t gu = mul_shift(sg, y1[j], a.fa);
+                        if (a.out && row0 + j < a.out_f) a.out[(long long)pair * a.out_f + row0 + j] = gu;
+                        bool ok;
+                        const uint64_t d = balanced_digits8(gu, ok);
+                        if (!ok) atomicOr(a.flags, 1);
+                        nl_max = max(nl_max, digits_used(d));
+#pragma unroll
+                        for (int l = 0; l < 8; l++) packed[l] |= ((d >> (8 * l)) & 0xFF) << (8 * j);
+                    }
+                    if (row0 + 8 <= a.out_f) {
+#pragma unroll
+                        for (int l = 0; l < 8; l++)
+                            *reinterpret_cast<uint64_t *>(a.out_limbs + ((long long)pair * 8 + l) * a.out_f + row0) = packed[l];
+                    } else {
+                        for (int j = 0; j < 8 && row0 + j < a.out_f; j++)
+                            for (int l = 0; l < 8; l++)
+                                a.out_limbs[((long long)pair * 8 + l) * a.out_f + row0 + j] = (int8_t)(packed[l] >> (8 * j));
+                    }
+                } else {
+                    const long long tok = a.pair_tok ? a.pair_tok[pair] : pair;
+                    const int64_t gate = a.gates ? a.gates[pair] : 0;
+                    for (int j = 0; j < 8; j++) {
+                        if (row0 + j >= a.out_f) break;
+                        if (MODE == MODE_LINEAR) a.out[(long long)pair * a.out_f + row0 + j] = y0[j];
+                        else atomicAdd(reinterpret_cast<unsigned long long *>(a.out + tok * a.out_f + row0 + j),
+                                       (unsigned long long)mul_shift(y0[j], gate, a.fa));
+                    }
+                }
+            }
+            if (MODE == MODE_GATEUP && a.out_nl) {
+                nl_max = max(nl_max, __shfl_xor_sync(0xffffffffu, nl_max, 16)); nl_max = max(nl_max, __shfl_xor_sync(0xffffffffu, nl_max, 8));
+                nl_max = max(nl_max, __shfl_xor_sync(0xffffffffu, nl_max, 4));  nl_max = max(nl_max, __shfl_xor_sync(0xffffffffu, nl_max, 2));
+                nl_max = max(nl_max, __shfl_xor_sync(0xffffffffu, nl_max, 1));
+                if (lane == 0 && nl_max > 0) atomicMax(a.out_nl, nl_max);
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    } else {
+        // ================= MMA issuer ====================================================================
+        if (lane == 0) {
+            constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(PF_BM >> 4) << 24);
+            uint32_t started = 0;                              // bit s: accumulator s already holds a partial sum
+            bool ok = true;
+            for (int c = 0; c < n_chunks && ok; c++) {
+                const int s = c % PF_STAGES;
+                ok = pf_bar_wait(&full_bar[s], (c / PF_STAGES) & 1, &s_abort);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t stage = pf_u32(smem + (size_t)s * STAGE_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+                    for (int b = 0; b < NL; b++)
+#pragma unroll
+                        for (int w = 0; w < NWL; w++) {
+                            const uint64_t da = pf_desc(stage + b * A_PLANE + ks * (A_PLANE / 2), A_PLANE / 4, 128);
+                            const uint64_t db = pf_desc(stage + NL * A_PLANE + w * B_PLANE + ks * (B_PLANE / 2), B_PLANE / 4, 128);
+                            const int acc = b + w;
+                            pf_mma(tmem + acc * BN, da, db, IDESC, (started >> acc) & 1u);
+                            started |= 1u << acc;
+                        }
+                pf_commit(&empty_bar[s]);                      // stage free once these MMAs have read it
+            }
+            if (ok) pf_commit(&accum_bar);                     // all MMAs done -> epilogue may read TMEM
+        }
+        __syncwarp();
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 4) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+    if (tid == 0 && s_abort) atomicOr(a.flags, 8);
+}
+
+template <int QT, int MODE, int NL, int NWL, int BN>
+cudaError_t launch_pf(const PrefillArgs &a_in, cudaStream_t s) {
+    PrefillArgs a = a_in;
+    constexpr int A_PLANE = 2 * 2 * (PF_BM / 8) * 128, B_PLANE = 2 * 2 * (BN / 8) * 128;
+    constexpr size_t smem = (size_t)PF_STAGES * (NL * A_PLANE + NWL * B_PLANE) + 1024;
+    constexpr int NOUT = MODE == MODE_GATEUP ? BN / 2 : BN;
+    a.n_ntiles = (int)((a.out_f + NOUT - 1) / NOUT);
+    a.sig_log2e = sigmoid_log2e(a.fa); a.sig_clip = sigmoid_clip(a.fa);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_kernel<QT, MODE, NL, NWL, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const long long max_mtiles = (a.n_pairs + PF_BM - 1) / PF_BM + a.n_experts;
+    prefill_kernel<QT, MODE, NL, NWL, BN><<<(unsigned)(max_mtiles * a.n_ntiles), PF_THREADS, smem, s>>>(a);
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// nl: digits the activation needs (host-known upper bound).  Returns cudaErrorNotSupported when the
+// combination has no tensor-core instantiation (the caller then uses the streamed kernels).
+cudaError_t launch_prefill(int qtype, int mode, int nl, const PrefillArgs &a, cudaStream_t s) {
+    if (a.n_blocks <= 0 || a.n_blocks * 256 > 8192 || a.out_f <= 0 || a.n_pairs <= 0) return cudaErrorInvalidValue;
+    if (qtype == QT_Q4K && mode == MODE_GATEUP) {
+        if (nl <= 3) return launch_pf<QT_Q4K, MODE_GATEUP, 3, 4, 64>(a, s);
+        if (nl == 4) return launch_pf<QT_Q4K, MODE_GATEUP, 4, 4, 64>(a, s);
+    }
+    if (qtype == QT_Q6K && mode == MODE_DOWN) {
+        if (nl <= 5) return launch_pf<QT_Q6K, MODE_DOWN, 5, 5, 32>(a, s);
+        if (nl == 6) return launch_pf<QT_Q6K, MODE_DOWN, 6, 5, 32>(a, s);
+    }
+    if (qtype == QT_Q4K && mode == MODE_DOWN) {
+        if (nl <= 5) return launch_pf<QT_Q4K, MODE_DOWN, 5, 4, 64>(a, s);
+    }
+    if (qtype == QT_Q4K && mode == MODE_LINEAR) {
+        if (nl <= 3) return launch_pf<QT_Q4K, MODE_LINEAR, 3, 4, 64>(a, s);
+        if (nl <= 5) return launch_pf<QT_Q4K, MODE_LINEAR, 5, 4, 64>(a, s);
+    }
+    return cudaErrorNotSupported;
+}
+
+}  // namespace iie
