@@ -58,7 +58,7 @@ int *g_flags = nullptr;               // device flag word
 int *g_cells = nullptr;               // device ints: [0] limbs of h, [1] limbs of gate*up, [2] routing ticket
 const uint8_t **g_selptr = nullptr;   // device: [3][64] pointers of the experts the last routing selected
 int g_pdl = 1;                        // programmatic dependent launch between the three decode kernels
-long long g_tc_min_tokens = 32;       // from this many tokens on, the MoE block runs on the tcgen05 grouped GEMMs
+long long g_tc_min_tokens = 192;      // from this many tokens on, the MoE block runs on the tcgen05 grouped GEMMs
 int g_ready = -1;                     // -1 unknown, 0 usable, 1 unusable
 int g_stage_mask = 0;                 // profiling: when non-zero, iie_moe_forward_dev runs only these stages
 enum Stage { ST_LIMBS = 1, ST_ROUTER = 2, ST_TOPK = 4, ST_GATEUP = 8, ST_DOWN = 16 };
@@ -258,7 +258,7 @@ unsigned __int128 max_weight(int qtype, unsigned maxd, unsigned maxdmin, int fw)
     const unsigned __int128 dq = (unsigned __int128)half_to_fixed(maxd, fw), dm = (unsigned __int128)half_to_fixed(maxdmin, fw);
     return qtype == QT_Q4K ? dq * 945 + dm * 63 : dq * 128 * 32;
 }
-const unsigned __int128 CAP4 = 2139062143ULL, CAP5 = 547599908735ULL;      // 127 * (256^n - 1) / 255
+const unsigned __int128 CAP4 = 2139062143ULL;                              // 127 * (256^4 - 1) / 255
 
 int read_cell(int idx, cudaStream_t s) {
     int v = -1;
@@ -278,7 +278,7 @@ int moe_prefill_tc(const MoeLayer &L, const int64_t *h_dev, long long T, int fa,
     if (!small_scales(L.maxd_gate, L.maxdmin_gate, fw) || !small_scales(L.maxd_down, L.maxdmin_down, fw) ||
         !small_scales(r.maxd, r.maxdmin, fw)) return -1;
     if (max_weight(QT_Q4K, L.maxd_gate, L.maxdmin_gate, fw) > CAP4 || max_weight(QT_Q4K, r.maxd, r.maxdmin, fw) > CAP4) return -1;
-    if (max_weight(L.down_q, L.maxd_down, L.maxdmin_down, fw) > (L.down_q == QT_Q4K ? CAP4 : CAP5)) return -1;
+    if (max_weight(L.down_q, L.maxd_down, L.maxdmin_down, fw) > (L.down_q == QT_Q4K ? CAP4 : (unsigned __int128)0x7FFFFFFFULL * 32)) return -1;   // Q6_K: d_q * 128 stays in int32
     int8_t *hl = (int8_t *)ensure(R_XL, (size_t)T * 8 * L.d_model);
     int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)T * E * 8);
     int *off = (int *)ensure(R_GRPOFF, (size_t)(E + 2) * sizeof(int));

@@ -28,7 +28,9 @@ namespace iie {
 
 namespace {
 
-constexpr int PF_BM = 128, PF_KC = 64, PF_STAGES = 3, PF_THREADS = 160;
+constexpr int PF_BM = 128, PF_KC = 64, PF_STAGES = 3;
+constexpr int PF_GROUPS = PF_STAGES;                     // producer groups of 128 threads; group g owns stage g
+constexpr int PF_THREADS = PF_GROUPS * 128 + 32;          // + the MMA / TMEM warp
 constexpr unsigned PF_WAIT_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t pf_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -84,14 +86,15 @@ __device__ __forceinline__ void digits4(const int (&w)[4], uint32_t (&plane)[4])
 template <int NWL>
 __device__ __forceinline__ void dequant32_q4k(const uint8_t *unit, int rr, int G, int hsel, int fw, uint32_t (&pl)[NWL][8]) {
     const uint4 meta = ldg128(unit + 1024 + rr * 16);
-    uint32_t sc[2], mn[2];
-    q4k_scales(meta.y, meta.z, meta.w, sc[0], sc[1], mn[0], mn[1]);
+    uint32_t sc0, sc1, mn0, mn1;
+    q4k_scales(meta.y, meta.z, meta.w, sc0, sc1, mn0, mn1);
     const int j = 2 * G + hsel;
-    const int ws = scale_small(meta.x & 0xFFFF, fw) * ubyte_at(sc[j >> 2], j & 3);
-    const int wm = scale_small(meta.x >> 16, fw) * ubyte_at(mn[j >> 2], j & 3);
+    const int ws = scale_small(meta.x & 0xFFFF, fw) * (int)(((j < 4 ? sc0 : sc1) >> (8 * (j & 3))) & 0xFF);
+    const int wm = scale_small(meta.x >> 16, fw) * (int)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xFF);
+    const uint8_t *qp = unit + (G >> 1) * 512 + rr * 64 + (G & 1) * 8;
 #pragma unroll
     for (int t = 0; t < 4; t++) {
-        const uint2 q = ldg64(unit + (G >> 1) * 512 + (rr * 4 + t) * 16 + (G & 1) * 8);   // qs[32G + 8t .. +7]
+        const uint2 q = ldg64(qp + t * 16);                                              // qs[32G + 8t .. +7]
         const uint32_t words[2] = {(q.x >> (4 * hsel)) & 0x0f0f0f0fu, (q.y >> (4 * hsel)) & 0x0f0f0f0fu};
 #pragma unroll
         for (int h2 = 0; h2 < 2; h2++) {
@@ -107,41 +110,39 @@ __device__ __forceinline__ void dequant32_q4k(const uint8_t *unit, int rr, int G
     }
 }
 
-// Q6_K: chunk cc (0..3) of a block covers half h = cc >> 1 and kq = 2*(cc & 1) + hsel.  |W| can need a
-// fifth digit (d_q * 128 * 32), so the split works on int64.
+// Q6_K: chunk cc (0..3) of a block covers half h = cc >> 1 and kq = 2*(cc & 1) + hsel.  |W| = |d_q sc (q-32)|
+// can need a fifth digit, so the split adds 0x80...80 over 40 bits: byte l of (w + 0x8080808080) ^ 0x80..80
+// is the balanced digit l for |w| <= 127*(256^5-1)/255.
 template <int NWL>
 __device__ __forceinline__ void dequant32_q6k(const uint8_t *unit, int rr, int cc, int hsel, int fw, uint32_t (&pl)[NWL][8]) {
+    static_assert(NWL == 5, "Q6_K tiles carry five weight digits");
     const int h = cc >> 1, kq = 2 * (cc & 1) + hsel;
-    const uint4 sw = ldg128(unit + 1536 + rr * 16);
-    const uint32_t scw[4] = {sw.x, sw.y, sw.z, sw.w};
-    const int64_t dq = scale_small(__ldg(reinterpret_cast<const unsigned short *>(unit + 1664 + rr * 2)), fw);
+    const int dq = scale_small(__ldg(reinterpret_cast<const unsigned short *>(unit + 1664 + rr * 2)), fw);
+    const int8_t *scp = reinterpret_cast<const int8_t *>(unit + 1536 + rr * 16 + 8 * h + 2 * kq);
 #pragma unroll
     for (int u = 0; u < 2; u++) {
-        const int si = 8 * h + 2 * kq + u;
-        const int64_t ws = dq * sbyte_at(scw[si >> 2], si & 3);
+        const int ws = dq * (int)__ldg(scp + u);                                          // |ws| < 2^31 inside the envelope
 #pragma unroll
         for (int t = 0; t < 4; t++) {
-            const uint4 lw = ldg128(unit + h * 512 + (rr * 4 + t) * 16);            // u0:{A,B} u1:{A,B}
-            const uint4 hw = ldg128(unit + 1024 + (rr * 4 + t) * 16);               // [h*2+u]
-            const uint32_t lsel[4] = {lw.x, lw.y, lw.z, lw.w}, hsel4[4] = {hw.x, hw.y, hw.z, hw.w};
-            const uint32_t n = lsel[u * 2 + (kq & 1)], hb = hsel4[h * 2 + u];
+            const uint4 lw = ldg128(unit + h * 512 + (rr * 4 + t) * 16);                // u0:{first 32, second 32} u1:{..}
+            const uint4 hw = ldg128(unit + 1024 + (rr * 4 + t) * 16);                   // [h*2+u]
+            const uint32_t n = (kq & 1) ? (u ? lw.w : lw.y) : (u ? lw.z : lw.x);
+            const uint32_t hb = h ? (u ? hw.w : hw.z) : (u ? hw.y : hw.x);
             const uint32_t lo = (kq < 2 ? n : (n >> 4)) & 0x0f0f0f0fu, hi = ((hb >> (2 * kq)) << 4) & 0x30303030u;
             const uint32_t q = lo | hi;
-            // 4 weights; digits of an int64 value, five of them kept
-            uint32_t pw[NWL];
-#pragma unroll
-            for (int l = 0; l < NWL; l++) pw[l] = 0;
+            uint32_t vlo[4], d4 = 0;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                int64_t w = ws * ((int)((q >> (8 * i)) & 0xFF) - 32);
-#pragma unroll
-                for (int l = 0; l < NWL; l++) {
-                    pw[l] |= (uint32_t)(w & 0xFF) << (8 * i);
-                    w = (w >> 8) + ((w >> 7) & 1);
-                }
+                const int64_t w = (int64_t)ws * ((int)((q >> (8 * i)) & 0xFF) - 32);
+                const uint64_t uu = (uint64_t)w + 0x8080808080ULL;
+                vlo[i] = (uint32_t)uu ^ 0x80808080u;
+                d4 |= ((((uint32_t)(uu >> 32)) & 0xFF) ^ 0x80u) << (8 * i);
             }
-#pragma unroll
-            for (int l = 0; l < NWL; l++) pl[l][u * 4 + t] = pw[l];
+            const uint32_t t0 = __byte_perm(vlo[0], vlo[1], 0x5140), t1 = __byte_perm(vlo[2], vlo[3], 0x5140);
+            const uint32_t t2 = __byte_perm(vlo[0], vlo[1], 0x7362), t3 = __byte_perm(vlo[2], vlo[3], 0x7362);
+            pl[0][u * 4 + t] = __byte_perm(t0, t1, 0x5410); pl[1][u * 4 + t] = __byte_perm(t0, t1, 0x7632);
+            pl[2][u * 4 + t] = __byte_perm(t2, t3, 0x5410); pl[3][u * 4 + t] = __byte_perm(t2, t3, 0x7632);
+            pl[4][u * 4 + t] = d4;
         }
     }
 }
@@ -182,7 +183,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
         pf_bar_init(&accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == PF_GROUPS * 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pf_u32(&s_tmem)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
@@ -191,16 +192,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
 
-    if (warp < 4) {
-        // ================= producers ====================================================================
-        const int prow = tid;                                  // pair row of this thread (A) ...
+    if (warp < PF_GROUPS * 4) {
+        // ================= producers: group g fills stage g for chunks g, g + 3, ... ======================
+        const int group = warp >> 2, gtid = tid & 127;
+        const int prow = gtid;                                 // pair row of this thread (A) ...
         const int pair = m0 + prow;
         const bool live = pair < m_end;
         const long long xrow = live ? (a.xidx ? a.xidx[pair] : pair) : 0;
         const int8_t *xsrc = a.xl + xrow * 8 * (long long)K;
-        const int brow = tid >> 1, hsel = tid & 1;             // ... and weight row / 32-column half (B)
-        for (int c = 0; c < n_chunks; c++) {
-            const int s = c % PF_STAGES;
+        const int brow = gtid >> 1, hsel = gtid & 1;           // ... and weight row / 32-column half (B)
+        for (int c = group; c < n_chunks; c += PF_GROUPS) {
+            const int s = group;
             if (c >= PF_STAGES && !pf_bar_wait(&empty_bar[s], ((c / PF_STAGES) - 1) & 1, &s_abort)) break;
             uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
             // A: NL digit planes x 64 columns of this thread's pair
@@ -224,8 +226,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                     uint32_t pl[NWL][8];
                     if (wrow < a.out_f) {
                         const uint8_t *unit = wbase + ((wrow >> 3) * nb + (c >> 2)) * HTB;
-                        if (QT == QT_Q4K) dequant32_q4k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
-                        else              dequant32_q6k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
+                        if constexpr (QT == QT_Q4K) dequant32_q4k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
+                        else                        dequant32_q6k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
                     } else {
 #pragma unroll
                         for (int l = 0; l < NWL; l++)
@@ -247,10 +249,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
         // ================= epilogue: TMEM lane = pair ========================================================
         if (pf_bar_wait(&accum_bar, 0, &s_abort)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
+            const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
             constexpr int NOUT = MODE == MODE_GATEUP ? BN / 2 : BN;
             int nl_max = 0;
-            for (int c0 = 0; c0 < NOUT; c0 += 8) {
+            for (int c0 = group * 8; c0 < NOUT; c0 += 8 * PF_GROUPS) {     // the groups share the columns
                 int64_t y0[8], y1[8];
 #pragma unroll
                 for (int part = 0; part < (MODE == MODE_GATEUP ? 2 : 1); part++) {
@@ -345,7 +347,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 4) {
+    if (warp == PF_GROUPS * 4) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
     }
