@@ -1,0 +1,81 @@
+/* C-ABI of the Q1_0 (1-bit weights) dense path.
+ *
+ * Part 1 re-exports, with identical names, argument order and return codes, the entry points that the
+ * reference bridge bonsai/src/trinote/infer_int/gpu_native.py:44-185 binds from libbonsai_q1_gpu.so
+ * (implemented there in bonsai/tools/bonsai_q1_gpu.cu).  All pointers in part 1 are HOST pointers and
+ * every call synchronises before it returns.  Arrays are C-contiguous:
+ *     x      [tokens][n_blocks*128]  int64     activations at scale 2^frac
+ *     bits   [out_f][n_blocks][16]   uint8     sign bits, little-endian inside a byte, 1 -> +1, 0 -> -1
+ *     scale  [out_f][n_blocks]       int64 (or int32 for the *_i32 registrations)
+ *     out    [tokens][out_f]         int64
+ *     out[t,o] = sum_b floor( ((sum_i +-x[t,128b+i]) * scale[o,b] mod 2^64) / 2^frac )   (mod 2^64)
+ * Return codes: 0 ok, 1 bad arguments, 2 CUDA failure, 4 outside the caller-chosen digit envelope.
+ *
+ * Part 2 is additive (device pointers, no reference counterpart).
+ */
+#ifndef IIE_Q1_H
+#define IIE_Q1_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- part 1: the reference's names ---------------------------------------------------------------- */
+
+/* bonsai_q1_gpu.cu:1970 - ABI generation the bridge may probe (3). */
+int bonsai_gpu_abi_version(void);
+/* bonsai_q1_gpu.cu:1974,1978 - code and text of the calling thread's last failure ("ok" when none). */
+int bonsai_gpu_last_error_code(void);
+const char *bonsai_gpu_last_error(void);
+/* bonsai_q1_gpu.cu:2032 - 0 iff a usable CUDA device exists. */
+int bonsai_gpu_available(void);
+/* bonsai_q1_gpu.cu:2041 - free / total device memory as the allocator sees it; 0 ok, 1 null, 2 CUDA. */
+int bonsai_gpu_mem_info(unsigned long long *free_bytes, unsigned long long *total_bytes);
+/* bonsai_q1_gpu.cu:2073 - bytes of bits + scales registered so far (as handed in, before re-ordering). */
+unsigned long long bonsai_q1_resident_weight_bytes(void);
+
+/* bonsai_q1_gpu.cu:2200 - one-shot product: uploads the weight, multiplies, downloads. */
+int bonsai_q1_linear_gpu(const long long *x, const unsigned char *bits, const long long *scale, long long tokens,
+                         long long out_f, long long n_blocks, long long frac, long long *out);
+/* bonsai_q1_gpu.cu:2245 - same product through the digit path; |L| in 1..8 is the number of base-256
+ * digits the caller vouches for (a negative L only selected another kernel shape in the reference).
+ * Every L computes with all eight digits here; rc 4 when an activation needs more than |L| < 8 digits,
+ * as the reference's L = 4 range guard reports. */
+int bonsai_q1_linear_dp4a_gpu(const long long *x, const unsigned char *bits, const long long *scale, long long tokens,
+                              long long out_f, long long n_blocks, long long frac, int L, long long *out);
+
+/* bonsai_q1_gpu.cu:2308,2329,2350,2368 - upload once, returns a handle >= 0 or -1.  The three int32
+ * variants differ only in the device layout the reference chose; here every registration is stored
+ * in the same tensor-core order. */
+long long bonsai_q1_register_weight(const unsigned char *bits, const long long *scale, long long out_f, long long n_blocks);
+long long bonsai_q1_register_weight_i32(const unsigned char *bits, const int *scale, long long out_f, long long n_blocks);
+long long bonsai_q1_register_weight_i32_gpu_layout(const unsigned char *bits, const int *scale, long long out_f,
+                                                   long long n_blocks);
+long long bonsai_q1_register_weight_i32_bmma(const unsigned char *bits, const int *scale, long long out_f,
+                                             long long n_blocks);
+/* bonsai_q1_gpu.cu:2388 - product with a registered weight. */
+int bonsai_q1_apply_resident(long long handle, const long long *x, long long tokens, long long frac, long long *out);
+/* bonsai_q1_gpu.cu:3659 - drop every registered weight; handles start again at 0. */
+void bonsai_q1_free_weights(void);
+
+/* bonsai_q1_gpu.cu:2428 - RMSNorm of fixed-point rows, gain nullable.  0 ok, 1 bad arguments or CUDA
+ * failure, 4 a row left the exact envelope (the caller recomputes on its big-integer path). */
+int bonsai_rmsnorm_gpu(const long long *x, long long rows, long long cols, long long frac, long long eps,
+                       const long long *gain, long long *out);
+
+/* ---- part 2: additive, device pointers (no counterpart in the reference) --------------------------- */
+
+/* Product with a registered weight on device buffers, asynchronous on `stream` (NULL = the CUDA default
+ * stream).  Scratch for the digit planes is process-global and grows on demand: one caller at a time. */
+int iie_q1_apply_dev(long long handle, const int64_t *x_dev, long long tokens, long long frac, int64_t *out_dev,
+                     void *stream);
+/* Shape of a registered weight; 0 ok, 1 unknown handle. */
+int iie_q1_weight_shape(long long handle, long long *out_f, long long *n_blocks, int *scale_bits);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

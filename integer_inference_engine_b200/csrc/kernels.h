@@ -149,4 +149,13 @@ cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, co
 cudaError_t launch_dispatch(const int *ids, const int64_t *gates, long long T, int k, int n_experts, int *grp_off,
                             int *pair_tok, int64_t *pair_gate, cudaStream_t s);
 
+// Q1_0 linear (q1.cu).  Units: 16-row tiles x 128-weight blocks, 256 B of sign bits in MMA order + 16 scales.
+size_t q1_unit_bytes(bool sc32);
+cudaError_t launch_q1_repack(const uint8_t *bits, const void *scale, int src_bits, bool sc32, long long out_f, long long nb,
+                             uint8_t *units, cudaStream_t s);
+cudaError_t launch_q1_prep(const int64_t *x, long long T, long long nb, int8_t *planes, int64_t *totals, int *nl_out,
+                           cudaStream_t s);
+cudaError_t launch_q1_apply(const uint8_t *units, bool sc32, long long out_f, long long nb, const int8_t *planes,
+                            const int64_t *totals, long long T, long long frac, int64_t *out, cudaStream_t s);
+
 }  // namespace iie

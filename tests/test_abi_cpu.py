@@ -6,7 +6,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from integer_inference_engine_b200 import build, qk_cuda
+from integer_inference_engine_b200 import build, q1_gpu, qk_cuda
 
 ROOT = Path(__file__).resolve().parents[1]
 
@@ -45,6 +45,22 @@ def test_reference_required_symbols_are_present(lib):
         qk_profile_set_enabled qk_profile_snapshot""".split()
     for name in required:
         assert hasattr(lib, name), name
+
+
+def test_q1_header_bridge_and_library_agree():
+    """include/iie_q1.h, the Q1_0 bridge and the library (under the file name the reference's Q1 bridge
+    loads) name the same entry points, including the one that bridge treats as mandatory."""
+    build.build()
+    text = re.sub(r"/\*.*?\*/", "", (ROOT / "include" / "iie_q1.h").read_text(), flags=re.S)
+    declared = sorted(set(re.findall(r"\b((?:bonsai|iie)_[a-z0-9_]+)\s*\(", text)))
+    assert declared == sorted(q1_gpu.EXPORTED_SYMBOLS)
+    lib = q1_gpu.load_library()
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert "bonsai_q1_linear_gpu" in declared and lib.bonsai_gpu_abi_version() == 3
+    if not q1_gpu.gpu_available():
+        with pytest.raises(q1_gpu.CudaUnavailableError):
+            q1_gpu.q1_apply_gpu(np.zeros((1, 128), np.int64), np.zeros((1, 1, 16), np.uint8), np.ones((1, 1), np.int64), 16)
 
 
 def test_limb_policy_matches_the_capacity_rule():
