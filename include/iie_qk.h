@@ -138,6 +138,19 @@ int iie_moe_block_dev(long long layer, long long gain_h, const int64_t *x_dev, l
 int iie_moe_block_host(long long layer, long long gain_h, const int64_t *x, long long T, int fa, int fw,
                        unsigned long long eps, int64_t *out, int *ids_out, int64_t *gates_out);
 
+/* The two halves of the block for expert-parallel callers (the reference has no multi-GPU path; these
+ * split what Engine._moe does at north-mini-code/src/nmc/engine.py:375-443 at the point where rows change
+ * owner).  iie_route_dev: logits of the replicated router (any registered matrix with one row per expert of
+ * the WHOLE model), top-k ids (lowest index wins ties) and sigmoid gates for every row.
+ * iie_moe_experts_dev: expert stage of `layer`, whose experts are the ids expert_base .. expert_base +
+ * n_experts - 1; every row carries `slots` (id, gate) pairs and pairs with other ids are skipped, so the
+ * routing arrays can travel unmodified.  out_dev [T,d_model] receives, per row, the sum over this shard's
+ * pairs of floor(down * gate / 2^fa) (overwritten, or added to when accumulate != 0). */
+int iie_route_dev(long long router_h, int top_k, const int64_t *h_dev, long long T, int fa, int fw, int *ids_dev,
+                  int64_t *gates_dev, void *stream);
+int iie_moe_experts_dev(long long layer, const int64_t *h_dev, long long T, const int *ids_dev, const int64_t *gates_dev,
+                        int slots, int expert_base, int fa, int fw, int accumulate, int64_t *out_dev, void *stream);
+
 /* Plain resident product on device tensors: out_dev [T,out_f] = floor(x_dev W^T / 2^fw). */
 int iie_apply_dev(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev, void *stream);
 

@@ -269,37 +269,25 @@ int read_cell(int idx, cudaStream_t s) {
 
 // Tensor-core (tcgen05) path for many tokens: router GEMM, top-k, dispatch, grouped gate/up and down GEMMs.
 // Returns 0 done, 1 error, -1 not applicable (caller uses the streamed kernels).
-int moe_prefill_tc(const MoeLayer &L, const int64_t *h_dev, long long T, int fa, int fw, int accumulate, int64_t *out_dev,
-                   int *ids, int64_t *gates, cudaStream_t s) {
-    const Weight &r = g_w[L.router];
+// Expert stage of the MoE block on the tensor-core tiles: dispatch -> gate/up (+SiLU*up) -> down (+combine).
+// hl = digit planes of the T hidden rows (nl_h digits in use), ids/gates = routing of every row; experts
+// of this layer are ids expert_base .. expert_base + n_experts - 1, other slots are skipped.
+// Returns -1 when the layer is outside what the tiles carry (the caller then streams), 0 ok, 1 failure.
+int moe_experts_tc(const MoeLayer &L, const int8_t *hl, int nl_h, long long T, const int *ids, const int64_t *gates,
+                   int expert_base, int fa, int fw, int accumulate, int64_t *out_dev, cudaStream_t s) {
     const int E = L.n_experts, k = L.top_k;
     const long long P = T * k;
-    if (r.qtype != QT_Q4K || L.gate_q != QT_Q4K || L.d_model > 8192 || L.e_ffn > 8192) return -1;
-    if (!small_scales(L.maxd_gate, L.maxdmin_gate, fw) || !small_scales(L.maxd_down, L.maxdmin_down, fw) ||
-        !small_scales(r.maxd, r.maxdmin, fw)) return -1;
-    if (max_weight(QT_Q4K, L.maxd_gate, L.maxdmin_gate, fw) > CAP4 || max_weight(QT_Q4K, r.maxd, r.maxdmin, fw) > CAP4) return -1;
+    if (L.gate_q != QT_Q4K || L.d_model > 8192 || L.e_ffn > 8192 || nl_h < 1 || nl_h > 4) return -1;
+    if (!small_scales(L.maxd_gate, L.maxdmin_gate, fw) || !small_scales(L.maxd_down, L.maxdmin_down, fw)) return -1;
+    if (max_weight(QT_Q4K, L.maxd_gate, L.maxdmin_gate, fw) > CAP4) return -1;
     if (max_weight(L.down_q, L.maxd_down, L.maxdmin_down, fw) > (L.down_q == QT_Q4K ? CAP4 : (unsigned __int128)0x7FFFFFFFULL * 32)) return -1;   // Q6_K: d_q * 128 stays in int32
-    int8_t *hl = (int8_t *)ensure(R_XL, (size_t)T * 8 * L.d_model);
-    int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)T * E * 8);
     int *off = (int *)ensure(R_GRPOFF, (size_t)(E + 2) * sizeof(int));
     int *ptok = (int *)ensure(R_PAIRTOK, (size_t)P * sizeof(int));
     int64_t *pg = (int64_t *)ensure(R_PAIRGATE, (size_t)P * 8);
     int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)P * 8 * L.e_ffn);
-    int *one_off = (int *)ensure(R_META, 64);
-    if (!hl || !lg || !off || !ptok || !pg || !gul || !one_off) return 1;
-    if (cudaMemsetAsync(g_cells, 0, 2 * sizeof(int), s) != cudaSuccess) return 1;
-    if (launch_limbs(h_dev, T, L.d_model, hl, g_flags, s, g_cells) != cudaSuccess) return 1;
-    const int nl_h = read_cell(0, s);
-    if (nl_h < 1 || nl_h > 4) return nl_h < 1 ? 1 : -1;
-    // router: one "expert" that owns all T rows
-    const int host_off[2] = {0, (int)T};
-    if (cudaMemcpyAsync(one_off, host_off, sizeof(host_off), cudaMemcpyHostToDevice, s) != cudaSuccess) return 1;
-    PrefillArgs ra = {};
-    ra.wa = r.cell; ra.wb = r.cell; ra.grp_off = one_off; ra.n_experts = 1; ra.n_pairs = T; ra.out_f = E;
-    ra.n_blocks = L.d_model / 256; ra.fw = fw; ra.fa = fa; ra.xl = hl; ra.out = lg; ra.flags = g_flags;
-    if (launch_prefill(QT_Q4K, MODE_LINEAR, nl_h, ra, s) != cudaSuccess) { cudaGetLastError(); return -1; }
-    if (launch_topk(lg, T, E, k, fa, ids, gates, s) != cudaSuccess) return 1;
-    if (launch_dispatch(ids, gates, T, k, E, off, ptok, pg, s) != cudaSuccess) return 1;
+    if (!off || !ptok || !pg || !gul) return 1;
+    if (cudaMemsetAsync(g_cells + 1, 0, sizeof(int), s) != cudaSuccess) return 1;
+    if (launch_dispatch(ids, gates, T, k, E, off, ptok, pg, s, expert_base) != cudaSuccess) return 1;
     PrefillArgs ga = {};
     ga.wa = L.tabs; ga.wb = L.tabs + E; ga.grp_off = off; ga.n_experts = E; ga.n_pairs = P; ga.out_f = L.e_ffn;
     ga.n_blocks = L.d_model / 256; ga.fw = fw; ga.fa = fa; ga.xl = hl; ga.xidx = ptok; ga.out = nullptr; ga.out_limbs = gul;
@@ -316,11 +304,45 @@ int moe_prefill_tc(const MoeLayer &L, const int64_t *h_dev, long long T, int fa,
     if (de == cudaSuccess) return 0;
     cudaGetLastError();
     // the activation needs more digits than the tensor-core tiles carry: streamed kernels for the down stage
-    MoePlan plan = {L.tabs, L.tabs + E, L.tabs + 2 * E, L.gate_q, L.down_q, L.d_model, L.e_ffn};
     SkinnyArgs d = {};
-    d.wa = plan.down; d.wb = plan.down; d.grp_off = off; d.pairs_per_group = 1; d.out_f = L.d_model; d.n_blocks = L.e_ffn / 256;
+    d.wa = L.tabs + 2 * E; d.wb = d.wa; d.grp_off = off; d.pairs_per_group = 1; d.out_f = L.d_model; d.n_blocks = L.e_ffn / 256;
     d.fw = fw; d.fa = fa; d.xl = gul; d.out = out_dev; d.gates = pg; d.pair_tok = ptok; d.flags = g_flags;
     return launch_skinny(L.down_q, MODE_DOWN, d, E, 4, s) == cudaSuccess ? 0 : 1;
+}
+
+// Whole block (router GEMM, top-k, expert stage) on the tensor-core tiles.  Same return codes.
+int moe_prefill_tc(const MoeLayer &L, const int64_t *h_dev, long long T, int fa, int fw, int accumulate, int64_t *out_dev,
+                   int *ids, int64_t *gates, cudaStream_t s) {
+    const Weight &r = g_w[L.router];
+    const int E = L.n_experts, k = L.top_k;
+    if (r.qtype != QT_Q4K || L.gate_q != QT_Q4K || L.d_model > 8192 || L.e_ffn > 8192) return -1;
+    if (!small_scales(r.maxd, r.maxdmin, fw) || max_weight(QT_Q4K, r.maxd, r.maxdmin, fw) > CAP4) return -1;
+    int8_t *hl = (int8_t *)ensure(R_XL, (size_t)T * 8 * L.d_model);
+    int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)T * E * 8);
+    int *one_off = (int *)ensure(R_META, 64);
+    if (!hl || !lg || !one_off) return 1;
+    if (cudaMemsetAsync(g_cells, 0, 2 * sizeof(int), s) != cudaSuccess) return 1;
+    if (launch_limbs(h_dev, T, L.d_model, hl, g_flags, s, g_cells) != cudaSuccess) return 1;
+    const int nl_h = read_cell(0, s);
+    if (nl_h < 1 || nl_h > 4) return nl_h < 1 ? 1 : -1;
+    // router: one "expert" that owns all T rows
+    const int host_off[2] = {0, (int)T};
+    if (cudaMemcpyAsync(one_off, host_off, sizeof(host_off), cudaMemcpyHostToDevice, s) != cudaSuccess) return 1;
+    PrefillArgs ra = {};
+    ra.wa = r.cell; ra.wb = r.cell; ra.grp_off = one_off; ra.n_experts = 1; ra.n_pairs = T; ra.out_f = E;
+    ra.n_blocks = L.d_model / 256; ra.fw = fw; ra.fa = fa; ra.xl = hl; ra.out = lg; ra.flags = g_flags;
+    if (launch_prefill(QT_Q4K, MODE_LINEAR, nl_h, ra, s) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (launch_topk(lg, T, E, k, fa, ids, gates, s) != cudaSuccess) return 1;
+    const int rc = moe_experts_tc(L, hl, nl_h, T, ids, gates, 0, fa, fw, accumulate, out_dev, s);
+    if (rc != -1) return rc;
+    // routing is done; stream the expert stage
+    int *off = (int *)ensure(R_GRPOFF, (size_t)(E + 2) * sizeof(int));
+    int *ptok = (int *)ensure(R_PAIRTOK, (size_t)T * k * sizeof(int));
+    int64_t *pg = (int64_t *)ensure(R_PAIRGATE, (size_t)T * k * 8);
+    if (!off || !ptok || !pg || launch_dispatch(ids, gates, T, k, E, off, ptok, pg, s) != cudaSuccess) return 1;
+    if (!accumulate && cudaMemsetAsync(out_dev, 0, (size_t)T * L.d_model * 8, s) != cudaSuccess) return 1;
+    MoePlan plan = {L.tabs, L.tabs + E, L.tabs + 2 * E, L.gate_q, L.down_q, L.d_model, L.e_ffn};
+    return moe_fused(plan, hl, false, ptok, nullptr, off, E, T * k, (int)std::min<long long>(T, 4), pg, ptok, fa, fw, out_dev, s) ? 0 : 1;
 }
 
 // Single-token fused path: route (optional RMSNorm, limbs, router, top-k) -> gate/up -> down.
@@ -693,11 +715,14 @@ extern "C" long long iie_moe_layer_create(long long router_h, const long long *g
                                           const long long *down_h, int n_experts, int top_k, long long d_model,
                                           long long e_ffn) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
-    if (!init() || !gate_h || !up_h || !down_h || n_experts <= 0 || n_experts > 1024 || top_k <= 0 || top_k > n_experts ||
+    if (!init() || !gate_h || !up_h || !down_h || n_experts <= 0 || n_experts > 1024 || top_k <= 0 ||
+        (router_h >= 0 && top_k > n_experts) ||
         d_model <= 0 || e_ffn <= 0 || d_model % 256 || e_ffn % 256) return -1;
-    if (!(valid_q(router_h) || valid_i64(router_h))) return -1;
-    const Weight &r = g_w[router_h];
-    if (r.out_f != n_experts || (r.qtype == QT_I64 ? r.nb != d_model : r.nb != d_model / 256)) return -1;
+    if (router_h >= 0) {                                // router_h < 0: an expert shard without a router of its own
+        if (!(valid_q(router_h) || valid_i64(router_h))) return -1;
+        const Weight &r = g_w[router_h];
+        if (r.out_f != n_experts || (r.qtype == QT_I64 ? r.nb != d_model : r.nb != d_model / 256)) return -1;
+    }
     MoeLayer L;
     std::vector<const uint8_t *> tabs(3 * (size_t)n_experts);
     for (int e = 0; e < n_experts; e++) {
@@ -714,7 +739,7 @@ extern "C" long long iie_moe_layer_create(long long router_h, const long long *g
     void *dt = nullptr;
     if (cudaMalloc(&dt, tabs.size() * sizeof(void *)) != cudaSuccess) { cudaGetLastError(); return -1; }
     if (cudaMemcpy(dt, tabs.data(), tabs.size() * sizeof(void *), cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(dt); return -1; }
-    L.router = router_h; L.n_experts = n_experts; L.top_k = top_k; L.d_model = d_model; L.e_ffn = e_ffn;
+    L.router = router_h < 0 ? -1 : router_h; L.n_experts = n_experts; L.top_k = top_k; L.d_model = d_model; L.e_ffn = e_ffn;
     L.tabs = (const uint8_t **)dt; L.live = true;
     g_layers.push_back(L);
     return (long long)g_layers.size() - 1;
@@ -732,7 +757,7 @@ extern "C" int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long l
                                    int64_t *out_dev, int *ids_dev, int64_t *gates_dev, void *stream) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (!init() || layer < 0 || (size_t)layer >= g_layers.size() || !g_layers[layer].live || !h_dev || !out_dev ||
-        T <= 0 || fa < 1 || fa > 29) return 1;
+        T <= 0 || fa < 1 || fa > 29 || g_layers[layer].router < 0) return 1;
     const MoeLayer &L = g_layers[layer];
     const Weight &r = g_w[L.router];
     cudaStream_t s = (cudaStream_t)stream;              // NULL is the CUDA default stream
@@ -785,6 +810,59 @@ extern "C" int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long l
     return 0;
 }
 
+extern "C" int iie_route_dev(long long router_h, int top_k, const int64_t *h_dev, long long T, int fa, int fw,
+                             int *ids_dev, int64_t *gates_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !(valid_q(router_h) || valid_i64(router_h)) || !h_dev || !ids_dev || !gates_dev || T <= 0 || fa < 1 ||
+        fa > 29) return 1;
+    const Weight &r = g_w[router_h];
+    const int E = (int)r.out_f;
+    const long long d = r.qtype == QT_I64 ? r.nb : r.nb * 256;
+    if (top_k <= 0 || top_k > E || E > 1024) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)T * E * 8);
+    if (!lg) return 1;
+    if (r.qtype == QT_I64) {
+        if (launch_exact_dense((const int64_t *)r.d, E, d, h_dev, T, fw, lg, g_flags, s) != cudaSuccess) return 1;
+    } else if (!linear_dev(r, h_dev, T, fw, lg, false, s)) { cudaGetLastError(); return 1; }
+    return launch_topk(lg, T, E, top_k, fa, ids_dev, gates_dev, s) == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int iie_moe_experts_dev(long long layer, const int64_t *h_dev, long long T, const int *ids_dev,
+                                   const int64_t *gates_dev, int slots, int expert_base, int fa, int fw, int accumulate,
+                                   int64_t *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || layer < 0 || (size_t)layer >= g_layers.size() || !g_layers[layer].live || !h_dev || !out_dev ||
+        !ids_dev || !gates_dev || T <= 0 || slots <= 0 || fa < 1 || fa > 29) return 1;
+    MoeLayer L = g_layers[layer];
+    L.top_k = slots;                                     // routing slots per row as the caller laid them out
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!fast_envelope(L.gate_q, L.d_model / 256, L.maxd_gate, L.maxdmin_gate, fw) ||
+        !fast_envelope(L.down_q, L.e_ffn / 256, L.maxd_down, L.maxdmin_down, fw)) return 3;
+    const int E = L.n_experts;
+    const long long P = T * slots;
+    int8_t *hl = (int8_t *)ensure(R_XL, (size_t)T * 8 * L.d_model);
+    if (!hl) return 1;
+    if (cudaMemsetAsync(g_cells, 0, sizeof(int), s) != cudaSuccess) return 1;
+    if (launch_limbs(h_dev, T, L.d_model, hl, g_flags, s, g_cells) != cudaSuccess) return 1;
+    if (T >= g_tc_min_tokens) {
+        const int nl_h = read_cell(0, s);
+        if (nl_h < 1) return 1;
+        const int rc = moe_experts_tc(L, hl, nl_h, T, ids_dev, gates_dev, expert_base, fa, fw, accumulate, out_dev, s);
+        if (rc >= 0) { if (rc) cudaGetLastError(); return rc; }
+    }
+    int *off = (int *)ensure(R_GRPOFF, (size_t)(E + 2) * sizeof(int));
+    int *ptok = (int *)ensure(R_PAIRTOK, (size_t)P * sizeof(int));
+    int64_t *pg = (int64_t *)ensure(R_PAIRGATE, (size_t)P * 8);
+    if (!off || !ptok || !pg || launch_dispatch(ids_dev, gates_dev, T, slots, E, off, ptok, pg, s, expert_base) != cudaSuccess) return 1;
+    if (!accumulate && cudaMemsetAsync(out_dev, 0, (size_t)T * L.d_model * 8, s) != cudaSuccess) return 1;
+    MoePlan plan = {L.tabs, L.tabs + E, L.tabs + 2 * E, L.gate_q, L.down_q, L.d_model, L.e_ffn};
+    if (!moe_fused(plan, hl, false, ptok, nullptr, off, E, P, (int)std::min<long long>(T, 4), pg, ptok, fa, fw, out_dev, s)) {
+        cudaGetLastError(); return 1;
+    }
+    return 0;
+}
+
 extern "C" int iie_apply_dev(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev, void *stream) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (!init() || !valid_q(h) || !x_dev || !out_dev || T <= 0) return 1;
@@ -833,7 +911,7 @@ extern "C" int iie_moe_block_dev(long long layer, long long gain_h, const int64_
                                  unsigned long long eps, int64_t *out_dev, int *ids_dev, int64_t *gates_dev, void *stream) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (!init() || layer < 0 || (size_t)layer >= g_layers.size() || !g_layers[layer].live || !x_dev || !out_dev ||
-        T <= 0 || fa < 1 || fa > 29) return 1;
+        T <= 0 || fa < 1 || fa > 29 || g_layers[layer].router < 0) return 1;
     const MoeLayer &L = g_layers[layer];
     cudaStream_t s = (cudaStream_t)stream;              // NULL is the CUDA default stream
     if (!fast_envelope(L.gate_q, L.d_model / 256, L.maxd_gate, L.maxdmin_gate, fw) ||

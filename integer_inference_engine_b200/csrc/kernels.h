@@ -145,9 +145,9 @@ cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, co
 
 // Counting-sort dispatch of (token, slot) pairs by expert (single CTA, n_experts <= 1024).
 //   ids [T*k], gates [T*k] -> grp_off [E+1], pair_tok [T*k] (token of each sorted pair),
-//   pair_gate [T*k] (its gate weight)
+//   pair_gate [T*k] (its gate weight).  Expert e of this shard is id expert_base + e; other ids are dropped.
 cudaError_t launch_dispatch(const int *ids, const int64_t *gates, long long T, int k, int n_experts, int *grp_off,
-                            int *pair_tok, int64_t *pair_gate, cudaStream_t s);
+                            int *pair_tok, int64_t *pair_gate, cudaStream_t s, int expert_base = 0);
 
 // Q1_0 linear (q1.cu).  Units: 16-row tiles x 128-weight blocks, 256 B of sign bits in MMA order + 16 scales.
 size_t q1_unit_bytes(bool sc32);

@@ -177,43 +177,57 @@ __global__ void topk_kernel(const int64_t *logits, long long rows, int n_experts
 }
 
 // ---------------------------------------------------------------------------------------------------
-// dispatch: stable counting sort of pairs by expert (single CTA)
+// dispatch: stable counting sort of (token, slot) pairs by expert, single CTA.  Warp w owns the w-th
+// contiguous slice of the pair list; inside a slice, 32 pairs at a time are ranked with a warp match,
+// so expert e's pairs keep ascending pair index.  Slots whose expert id falls outside
+// [expert_base, expert_base + n_experts) are dropped (they belong to another expert shard).
 // ---------------------------------------------------------------------------------------------------
-__global__ void dispatch_kernel(const int *ids, const int64_t *gates, long long T, int k, int n_experts, int *grp_off,
-                                int *pair_tok, int64_t *pair_gate) {
-    extern __shared__ int sm[];                           // counts[E], base[E]
-    int *counts = sm, *base = sm + n_experts;
+__global__ void dispatch_kernel(const int *ids, const int64_t *gates, long long T, int k, int n_experts, int expert_base,
+                                int *grp_off, int *pair_tok, int64_t *pair_gate) {
+    extern __shared__ int sm[];                           // cnt[nwarps][E], then start[E + 1]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    int *cnt = sm, *start = sm + nwarps * n_experts;
     const long long P = T * k;
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+    const long long per = ((P + nwarps - 1) / nwarps + 31) / 32 * 32;      // slice length, a multiple of 32
+    const long long lo = (long long)warp * per, hi = lo + per < P ? lo + per : P;
+    for (int i = threadIdx.x; i < nwarps * n_experts; i += blockDim.x) cnt[i] = 0;
     __syncthreads();
-    for (long long i = threadIdx.x; i < P; i += blockDim.x) {
-        const int e = ids[i];
-        if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);
+    int *mine = cnt + warp * n_experts;
+    for (long long i0 = lo; i0 < hi; i0 += 32) {
+        const long long i = i0 + lane;
+        int e = i < hi ? ids[i] - expert_base : -1;
+        if (e < 0 || e >= n_experts) e = -1;
+        const unsigned m = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && lane == __ffs(m) - 1) mine[e] += __popc(m);
+        __syncwarp();
+    }
+    __syncthreads();
+    // per expert: slice counts -> slice offsets inside the expert's range; then the ranges themselves
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        int run = 0;
+        for (int w = 0; w < nwarps; w++) { const int c = cnt[w * n_experts + e]; cnt[w * n_experts + e] = run; run += c; }
+        start[e] = run;                                  // total of expert e for now
     }
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
-        for (int e = 0; e < n_experts; e++) { base[e] = run; grp_off[e] = run; run += counts[e]; }
-        grp_off[n_experts] = run;
+        for (int e = 0; e < n_experts; e++) { const int c = start[e]; start[e] = run; grp_off[e] = run; run += c; }
+        start[n_experts] = run; grp_off[n_experts] = run;
     }
     __syncthreads();
-    // stable placement: expert e's pairs keep ascending pair index (one thread per expert scans in order
-    // when the problem is small; otherwise warps cooperate with a ballot prefix)
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    for (int e = warp; e < n_experts; e += nwarps) {
-        if (counts[e] == 0) continue;
-        int pos = base[e];
-        for (long long i0 = 0; i0 < P; i0 += 32) {
-            const long long i = i0 + lane;
-            const bool hit = i < P && ids[i] == e;
-            const unsigned m = __ballot_sync(0xffffffffu, hit);
-            if (hit) {
-                const int dst = pos + __popc(m & ((1u << lane) - 1));
-                pair_tok[dst] = (int)(i / k);
-                pair_gate[dst] = gates[i];
-            }
-            pos += __popc(m);
+    for (long long i0 = lo; i0 < hi; i0 += 32) {
+        const long long i = i0 + lane;
+        int e = i < hi ? ids[i] - expert_base : -1;
+        if (e < 0 || e >= n_experts) e = -1;
+        const unsigned m = __match_any_sync(0xffffffffu, e);
+        if (e >= 0) {
+            const int dst = start[e] + mine[e] + __popc(m & ((1u << lane) - 1));
+            pair_tok[dst] = (int)(i / k);
+            pair_gate[dst] = gates[i];
         }
+        __syncwarp();
+        if (e >= 0 && lane == __ffs(m) - 1) mine[e] += __popc(m);
+        __syncwarp();
     }
 }
 
@@ -363,9 +377,11 @@ cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, co
 }
 
 cudaError_t launch_dispatch(const int *ids, const int64_t *gates, long long T, int k, int n_experts, int *grp_off,
-                            int *pair_tok, int64_t *pair_gate, cudaStream_t s) {
-    if (n_experts > 4096) return cudaErrorInvalidValue;
-    dispatch_kernel<<<1, 1024, 2 * n_experts * sizeof(int), s>>>(ids, gates, T, k, n_experts, grp_off, pair_tok, pair_gate);
+                            int *pair_tok, int64_t *pair_gate, cudaStream_t s, int expert_base) {
+    if (n_experts > 1024 || n_experts <= 0) return cudaErrorInvalidValue;
+    const int warps = n_experts <= 320 ? 32 : 8;                        // cnt[warps][E] + start[E + 1] stays below 48 KB
+    const size_t smem = ((size_t)warps * n_experts + n_experts + 1) * sizeof(int);
+    dispatch_kernel<<<1, 32 * warps, smem, s>>>(ids, gates, T, k, n_experts, expert_base, grp_off, pair_tok, pair_gate);
     note_launch();
     return cudaGetLastError();
 }

@@ -93,11 +93,30 @@ def read_flags() -> int:
         return int(qk_cuda._lib().iie_flags_read_clear(_stream_ptr()))
 
 
+def route(router: int, top_k: int, h: torch.Tensor, fa: int = 16, fw: int = 24):
+    """Router logits, top-k expert ids (lowest index wins ties) and sigmoid gates of every row of ``h``.
+    ``router`` is a registered matrix with one row per expert.  Returns (ids [T,k] int32, gates [T,k] int64)."""
+    lib = qk_cuda._lib()
+    assert h.is_cuda and h.dtype == torch.int64 and h.dim() == 2 and h.is_contiguous()
+    T = h.shape[0]
+    ids = torch.empty((T, top_k), dtype=torch.int32, device=h.device)
+    gates = torch.empty((T, top_k), dtype=torch.int64, device=h.device)
+    if T == 0:
+        return ids, gates
+    with _CUDA_LOCK:
+        rc = lib.iie_route_dev(int(router), int(top_k), h.data_ptr(), T, int(fa), int(fw), ids.data_ptr(), gates.data_ptr(),
+                               _stream_ptr())
+    if rc != 0:
+        raise CudaContextError(f"routing failed with status {rc}")
+    return ids, gates
+
+
 class MoELayer:
     """One MoE layer with every expert resident on the device.
 
-    ``router`` is a handle (quantised or dense int64); ``gate``, ``up``, ``down`` are sequences of
-    ``n_experts`` handles with uniform quantisation type per projection.
+    ``router`` is a handle (quantised or dense int64), or -1 for an expert shard that is only driven through
+    :meth:`experts`; ``gate``, ``up``, ``down`` are sequences of ``n_experts`` handles with uniform quantisation
+    type per projection.
     """
 
     def __init__(self, router: int, gate, up, down, top_k: int, d_model: int, e_ffn: int):
@@ -152,6 +171,29 @@ class MoELayer:
         if rc != 0:
             raise CudaContextError(f"MoE block failed with status {rc}")
         return out, ids, gates
+
+    def experts(self, h: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, expert_base: int = 0, fa: int = 16,
+                fw: int = 24, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+        """Expert stage only, with routing supplied by the caller: ``ids`` [T,slots] int32 are expert ids of the
+        whole model, this layer owning ``expert_base .. expert_base + n_experts - 1``; other slots are skipped.
+        Returns, per row, the sum over this shard's slots of ``floor(down * gate / 2**fa)``."""
+        lib = qk_cuda._lib()
+        assert h.is_cuda and h.dtype == torch.int64 and h.dim() == 2 and h.shape[1] == self.d_model and h.is_contiguous()
+        T = h.shape[0]
+        assert ids.dtype == torch.int32 and gates.dtype == torch.int64 and ids.shape == gates.shape and ids.shape[0] == T
+        ids, gates = ids.contiguous(), gates.contiguous()
+        if out is None:
+            out = torch.empty((T, self.d_model), dtype=torch.int64, device=h.device)
+            accumulate = False
+        if T == 0:
+            return out
+        with _CUDA_LOCK:
+            rc = lib.iie_moe_experts_dev(self.handle, h.data_ptr(), T, ids.data_ptr(), gates.data_ptr(), int(ids.shape[1]),
+                                         int(expert_base), int(fa), int(fw), int(bool(accumulate)), out.data_ptr(),
+                                         _stream_ptr())
+        if rc != 0:
+            raise CudaContextError(f"MoE expert stage failed with status {rc}")
+        return out
 
     def close(self):
         if self.handle >= 0:
