@@ -49,6 +49,10 @@ def parse():
     ap.add_argument("--verify-layers", type=int, default=48, help="blocks checked against the CPU oracle before timing")
     ap.add_argument("--cpu-sample-layers", type=int, default=4)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep_decode", "q1"],
+                    help="decode = the headline line (batch-1 MoE decode); the others print a line of the same "
+                         "shape for the prefill, expert-parallel and Q1_0 configurations")
+    ap.add_argument("--tokens", type=int, default=0, help="prefill: tokens per step (2048); ep_decode: sequences (64)")
     return ap.parse_args()
 
 
@@ -389,9 +393,266 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------- secondary workloads ------
+def _dist_setup():
+    import torch
+    import torch.distributed as dist
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def _timed(fn, steps, warmup, world, local):
+    """W warm-up calls, then K calls between CUDA events on the current stream; max over ranks (ms total)."""
+    import torch
+    import torch.distributed as dist
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, clk.summary()
+
+
+def _oracle_rows(stack, li, h_rows):
+    """CPU checker for a few rows of block `li` (rows are independent in the MoE block)."""
+    from integer_inference_engine_b200 import device
+    from oracle import native as onat
+    from oracle import qk_oracle as o
+    hs = stack.handles[li]
+    nb_in, nb_dn = D_MODEL // 256, E_FFN // 256
+    router = device.export_weight(hs["router"], N_EXPERTS, nb_in, o.Q4_K)
+    logits = onat.qk_linear(router, h_rows, N_EXPERTS, nb_in, FW, o.Q4_K)
+    sel = np.stack([onat.topk_lowidx(r, TOP_K) for r in logits])
+    lo, hi = stack.expert_range
+    ref = np.zeros(h_rows.shape, dtype=object)
+    for t in range(h_rows.shape[0]):
+        gts = onat.sigmoid(logits[t][sel[t]], FA)
+        for j, e in enumerate(sel[t]):
+            if not lo <= e < hi:
+                continue
+            gw = device.export_weight(hs["gate"][e - lo], E_FFN, nb_in, o.Q4_K)
+            uw = device.export_weight(hs["up"][e - lo], E_FFN, nb_in, o.Q4_K)
+            dw = device.export_weight(hs["down"][e - lo], D_MODEL, nb_dn, o.Q6_K)
+            g = onat.silu(onat.qk_linear(gw, h_rows[t:t + 1], E_FFN, nb_in, FW, o.Q4_K), FA)
+            u = onat.qk_linear(uw, h_rows[t:t + 1], E_FFN, nb_in, FW, o.Q4_K)
+            dn = onat.qk_linear(dw, o.mul_shift(g, u, FA), D_MODEL, nb_dn, FW, o.Q6_K)[0].astype(object)
+            ref[t] += (dn * int(gts[j])) >> FA
+    return sel, ref.astype(np.int64)
+
+
+def run_prefill(args):
+    """Prefill configuration: `tokens` (2048) rows through every MoE block per step, each rank a replica."""
+    import torch
+    import torch.distributed as dist
+
+    from integer_inference_engine_b200 import device
+    from integer_inference_engine_b200.synth import SyntheticMoEStack
+    from oracle import qk_oracle as o
+    rank, world, local = _dist_setup()
+    T = args.tokens or 2048
+    stack = SyntheticMoEStack(args.layers, D_MODEL, E_FFN, N_EXPERTS, TOP_K, seed=1 + rank, fa=FA)
+    x0 = torch.from_numpy(o.to_fixed(np.random.default_rng(7 + rank).standard_normal((T, D_MODEL)), FA)).cuda()
+    h = device.rmsnorm(x0, stack.gains[0], FA, 1)
+    out, ids, _ = stack.layers[0].forward(h, FA, FW)
+    torch.cuda.synchronize()
+    assert device.read_flags() == 0
+    rows = [0, T // 3, T - 1]
+    sel, ref = _oracle_rows(stack, 0, h[rows].cpu().numpy())
+    assert np.array_equal(ids[rows].cpu().numpy(), sel) and np.array_equal(out[rows].cpu().numpy(), ref), "block 0 differs from the oracle"
+    x = x0.clone()
+    l0 = device.launch_count()
+    stack.decode_step(x, FW)
+    launches = device.launch_count() - l0
+
+    def step(i):
+        x.copy_(x0)
+        stack.decode_step(x, FW)
+    ms, clocks = _timed(step, args.steps, args.warmup, world, local)
+    assert device.read_flags() == 0
+    if rank == 0:
+        ms_step = ms / args.steps
+        print(json.dumps({
+            "metric": "prefill_tok_per_s", "value": world * T * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int64 via int8 digit planes (tcgen05 kind::i8)", "data": "synthetic",
+            "config": {"workload": f"config3_moe_prefill: {T} tokens x {args.layers} MoE blocks, grouped expert GEMMs",
+                       "ms_per_block": ms_step / args.layers, "parallelism": f"replicas x{world}",
+                       "l2": "inputs larger than L2 (1.2 GB of expert weights per block)", "oracle_checked_rows": len(rows)},
+            "clocks": clocks, "gpu_launches": int(launches * args.steps)}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_ep_decode(args):
+    """Expert-parallel batched decode: `tokens` (64) sequences split over the ranks, experts sharded 128/P per
+    rank, one all-to-all dispatch and one combine per block.  One rank runs the same code with both elided."""
+    import torch
+    import torch.distributed as dist
+
+    from integer_inference_engine_b200 import device, ep
+    from integer_inference_engine_b200.synth import SyntheticMoEStack
+    from oracle import qk_oracle as o
+    rank, world, local = _dist_setup()
+    S = args.tokens or 64
+    assert S % world == 0 and N_EXPERTS % world == 0
+    per = S // world
+    epr = N_EXPERTS // world
+    stack = SyntheticMoEStack(args.layers, D_MODEL, E_FFN, N_EXPERTS, TOP_K, seed=1, fa=FA,
+                              expert_range=(rank * epr, (rank + 1) * epr))
+    blocks = [ep.from_device_layer(stack.handles[li]["router"], stack.layers[li], N_EXPERTS, FA, FW) for li in range(args.layers)]
+    xs = o.to_fixed(np.random.default_rng(11).standard_normal((S, D_MODEL)), FA)          # same on every rank
+    x0 = torch.from_numpy(xs[rank * per:(rank + 1) * per].copy()).cuda()
+
+    def forward(x):
+        for li, blk in enumerate(blocks):
+            h = device.rmsnorm(x, stack.gains[li], FA, 1)
+            out, _, _ = blk.forward(h)
+            x += out
+        return x
+    # parity of block 0: this rank's rows against the checker run over ALL experts (needs the other shards'
+    # weights, so the check uses a full-model stack of one block on rank 0 only)
+    h0 = device.rmsnorm(x0, stack.gains[0], FA, 1)
+    out0, ids0, _ = blocks[0].forward(h0)
+    torch.cuda.synchronize()
+    assert device.read_flags() == 0
+    if rank == 0:
+        full = SyntheticMoEStack(1, D_MODEL, E_FFN, N_EXPERTS, TOP_K, seed=1, fa=FA)
+        rows = [0, per - 1]
+        sel, ref = _oracle_rows(full, 0, h0[rows].cpu().numpy())
+        assert np.array_equal(ids0[rows].cpu().numpy(), sel) and np.array_equal(out0[rows].cpu().numpy(), ref), \
+            "expert-parallel block 0 differs from the oracle"
+        for lay in full.layers:
+            lay.close()
+    x = x0.clone()
+    l0 = device.launch_count()
+    forward(x)
+    launches = device.launch_count() - l0
+
+    def step(i):
+        x.copy_(x0)
+        forward(x)
+    ms, clocks = _timed(step, args.steps, args.warmup, world, local)
+    assert device.read_flags() == 0
+    if rank == 0:
+        ms_step = ms / args.steps
+        print(json.dumps({
+            "metric": "decode_tok_per_s", "value": S * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int64", "data": "synthetic",
+            "config": {"workload": f"config4_ep_decode: {S} sequences, {args.layers} MoE blocks, experts {epr}/rank, "
+                                   f"all-to-all dispatch + combine per block", "parallelism": f"ep{world}",
+                       "a2a_bytes_per_rank_per_block": blocks[0].bytes_sent_last,
+                       "l2": "inputs larger than L2 (expert weights streamed per block)", "oracle_checked_rows": 2},
+            "clocks": clocks, "gpu_launches": int(launches * args.steps)}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_q1(args):
+    """Q1_0 dense configuration (8B shape: 36 layers, d=4096, ffn 12288, vocab 151936): the seven linear
+    products of every layer plus the output head, as a 512-token prefill pass and as batch-1 decode steps."""
+    import torch
+
+    from integer_inference_engine_b200 import device, q1_gpu
+    from oracle import native as onat
+    from oracle import qk_oracle as o
+    rank, world, local = _dist_setup()
+    assert world == 1, "the Q1_0 line is a single-GPU measurement"
+    L = 36 if args.layers == 48 else args.layers
+    d, ffn, vocab, frac = 4096, 12288, 151936, 16
+    shapes = [("qkv", d + 2 * 1024, d), ("o", d, d), ("gate", ffn, d), ("up", ffn, d), ("down", d, ffn)]
+    rng = np.random.default_rng(2)
+
+    def make(out_f, in_f):
+        bits = rng.integers(0, 256, size=(out_f, in_f // 128, 16), dtype=np.uint8)
+        sc = np.rint(np.abs(rng.standard_normal((out_f, in_f // 128)) * 0.02).astype(np.float16).astype(np.float64) * (1 << frac))
+        return bits, sc.astype(np.int32)
+    layers, wbytes = [], 0
+    first = None
+    for li in range(L):
+        hs = {}
+        for name, of, inf in shapes:
+            bits, sc = make(of, inf)
+            hs[name] = q1_gpu.q1_register_weight(bits, sc)
+            wbytes += of * (inf // 128) * 20
+            if li == 0 and name == "gate":
+                first = (bits, sc)
+        layers.append(hs)
+    hb, hsc = make(vocab, d)
+    head = q1_gpu.q1_register_weight(hb, hsc)
+    wbytes += vocab * (d // 128) * 20
+    # parity: layer 0's gate projection on 3 rows against the checker
+    xt = o.to_fixed(rng.standard_normal((3, d)), frac)
+    got = q1_gpu.apply_dev(layers[0]["gate"], torch.from_numpy(xt).cuda(), frac).cpu().numpy()
+    assert np.array_equal(got, onat.q1_linear(xt, first[0], first[1].astype(np.int64), frac)), "Q1_0 product differs from the oracle"
+
+    def pass_(x_d, x_f, with_head):
+        for hs in layers:
+            q1_gpu.apply_dev(hs["qkv"], x_d, frac)
+            q1_gpu.apply_dev(hs["o"], x_d, frac)
+            q1_gpu.apply_dev(hs["gate"], x_d, frac)
+            q1_gpu.apply_dev(hs["up"], x_d, frac)
+            q1_gpu.apply_dev(hs["down"], x_f, frac)
+        if with_head:
+            q1_gpu.apply_dev(head, x_d[:1], frac)
+    T = args.tokens or 512
+    xd = torch.from_numpy(o.to_fixed(rng.standard_normal((T, d)), frac)).cuda()
+    xf = torch.from_numpy(o.to_fixed(rng.standard_normal((T, ffn)), frac)).cuda()
+    pf_ms, _ = _timed(lambda i: pass_(xd, xf, False), max(1, args.steps // 8), 1, 1, local)
+    pf_ms /= max(1, args.steps // 8)
+    x1, f1 = xd[:1].clone(), xf[:1].clone()
+    pass_(x1, f1, True)                                           # sizes the scratch before capture
+    torch.cuda.synchronize()
+    l0 = device.launch_count()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            pass_(x1, f1, True)
+    launches = device.launch_count() - l0
+    ms, clocks = _timed(lambda i: graph.replay(), args.steps, args.warmup, 1, local)
+    ms_step = ms / args.steps
+    peak, kind = measured_peak_gbs()
+    print(json.dumps({
+        "metric": "decode_tok_per_s", "value": 1e3 / ms_step, "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int64 modulo 2^64 via int8 digit planes", "data": "synthetic",
+        "config": {"workload": f"config5_q1_linears: {L} layers x (qkv, o, gate, up, down) + head, batch-1 decode; "
+                               f"attention, norms and the residual are not part of this line",
+                   "prefill_tokens": T, "prefill_ms": pf_ms, "prefill_tok_per_s": T * 1e3 / pf_ms,
+                   "l2": "inputs larger than L2: %d MB of weights per step" % (wbytes // 2**20)},
+        "clocks": clocks, "gpu_launches": int(launches * args.steps),
+        "roofline": {"bound": "hbm", "kernel": "q1 linears of one decode step (aggregate)", "achieved": wbytes / (ms_step * 1e-3) / 1e9,
+                     "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": wbytes / (ms_step * 1e-3) / 1e9 / peak,
+                     "traffic": None, "bytes_per_launch": wbytes}}))
+
+
 if __name__ == "__main__":
     a = parse()
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload == "prefill":
+        run_prefill(a)
+    elif a.workload == "ep_decode":
+        run_ep_decode(a)
+    elif a.workload == "q1":
+        run_q1(a)
     else:
         run_ours(a)

@@ -30,6 +30,13 @@ _L4_LO, _L4_HI = -2155905152, 2139062143      # balanced base-256 range of four 
 
 
 def lib_path() -> Path:
+    """The build writes one binary under two names: ``libbonsai_q1_gpu.so`` is what the reference's Q1 bridge
+    looks for; this module opens ``libnmc_qk_cuda.so`` so that it shares one library instance (launch counter,
+    mutex) with :mod:`integer_inference_engine_b200.qk_cuda`."""
+    return Path(__file__).resolve().parent / "lib" / "libnmc_qk_cuda.so"
+
+
+def reference_lib_path() -> Path:
     return Path(__file__).resolve().parent / "lib" / "libbonsai_q1_gpu.so"
 
 

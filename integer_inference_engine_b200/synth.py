@@ -34,11 +34,17 @@ def synth_q6k(n_blocks_total: int, gen: torch.Generator, dmag: float = 0.01) -> 
 class SyntheticMoEStack:
     """``n_layers`` MoE blocks of the 30B-A3B shape: per layer an int64 RMSNorm gain
     (to_fixed(|N(0,1)| + 0.5)), a Q4_K router [E,d], and E experts with Q4_K gate/up [eff,d] and
-    Q6_K down [d,eff].  All experts stay resident."""
+    Q6_K down [d,eff].  All experts stay resident.
+
+    ``expert_range=(lo, hi)`` keeps only experts lo..hi-1 (an expert-parallel shard): the tensors are drawn
+    exactly as for the full stack, so every shard of the same seed is a slice of the same model; the layers
+    are then router-less shards and the replicated router handles are in ``handles[i]["router"]``."""
 
     def __init__(self, n_layers: int, d_model: int = 2048, e_ffn: int = 768, n_experts: int = 128, top_k: int = 8,
-                 seed: int = 1, fa: int = 16):
+                 seed: int = 1, fa: int = 16, expert_range: "tuple[int, int] | None" = None):
         from . import qk_cuda
+        lo, hi = expert_range if expert_range is not None else (0, n_experts)
+        self.expert_range = (lo, hi)
         self.n_layers, self.d_model, self.e_ffn, self.n_experts, self.top_k, self.fa = \
             n_layers, d_model, e_ffn, n_experts, top_k, fa
         nb_in, nb_dn = d_model // 256, e_ffn // 256
@@ -53,11 +59,11 @@ class SyntheticMoEStack:
             gate = synth_q4k(n_experts * e_ffn * nb_in, gen).view(n_experts, -1)
             up = synth_q4k(n_experts * e_ffn * nb_in, gen).view(n_experts, -1)
             down = synth_q6k(n_experts * d_model * nb_dn, gen).view(n_experts, -1)
-            gh = [device.register_weight(gate[e], e_ffn, nb_in, Q4_K) for e in range(n_experts)]
-            uh = [device.register_weight(up[e], e_ffn, nb_in, Q4_K) for e in range(n_experts)]
-            dh = [device.register_weight(down[e], d_model, nb_dn, Q6_K) for e in range(n_experts)]
+            gh = [device.register_weight(gate[e], e_ffn, nb_in, Q4_K) for e in range(lo, hi)]
+            uh = [device.register_weight(up[e], e_ffn, nb_in, Q4_K) for e in range(lo, hi)]
+            dh = [device.register_weight(down[e], d_model, nb_dn, Q6_K) for e in range(lo, hi)]
             del router, gate, up, down
-            self.layers.append(device.MoELayer(router_h, gh, uh, dh, top_k, d_model, e_ffn))
+            self.layers.append(device.MoELayer(router_h if expert_range is None else -1, gh, uh, dh, top_k, d_model, e_ffn))
             self.gains.append(gain_h)
             self.handles.append({"router": router_h, "gate": gh, "up": uh, "down": dh, "gain": gain, "gain_h": gain_h})
 

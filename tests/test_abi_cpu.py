@@ -54,9 +54,11 @@ def test_q1_header_bridge_and_library_agree():
     text = re.sub(r"/\*.*?\*/", "", (ROOT / "include" / "iie_q1.h").read_text(), flags=re.S)
     declared = sorted(set(re.findall(r"\b((?:bonsai|iie)_[a-z0-9_]+)\s*\(", text)))
     assert declared == sorted(q1_gpu.EXPORTED_SYMBOLS)
+    import ctypes
     lib = q1_gpu.load_library()
+    ref_named = ctypes.CDLL(str(q1_gpu.reference_lib_path()))
     for name in declared:
-        assert hasattr(lib, name), name
+        assert hasattr(lib, name) and hasattr(ref_named, name), name
     assert "bonsai_q1_linear_gpu" in declared and lib.bonsai_gpu_abi_version() == 3
     if not q1_gpu.gpu_available():
         with pytest.raises(q1_gpu.CudaUnavailableError):
