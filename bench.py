@@ -332,9 +332,15 @@ def run_ours(args):
         device.read_flags()
         return e0.elapsed_time(e1) / (reps * len(stack.layers))
 
-    route_ms, gateup_ms, down_ms = time_stage(2), time_stage(8), time_stage(16)
+    route_ms, gateup_ms, down_ms, expert_ms = time_stage(2), time_stage(8), time_stage(16), time_stage(24)
     gateup_bytes = TOP_K * 2 * E_FFN * (D_MODEL // 256) * 144
-    achieved = gateup_bytes / (gateup_ms * 1e-3) / 1e9
+    down_bytes = TOP_K * D_MODEL * (E_FFN // 256) * 210
+    fused = launches_per_step == 2 * args.layers          # routing + one cluster launch per block
+    if fused:
+        dom_name, dom_bytes, dom_ms = "expert_kernel<Q4_K, Q6_K> (gate/up + SiLU*up + down + combine)", gateup_bytes + down_bytes, expert_ms
+    else:
+        dom_name, dom_bytes, dom_ms = "stream_kernel<Q4_K, GATEUP>", gateup_bytes, gateup_ms
+    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
 
     # ---- end to end through the host-buffer C-ABI call ----------------------------------------------------
     e2e = None
@@ -382,11 +388,13 @@ def run_ours(args):
                    "oracle_checked_blocks": checked},
         "clocks": clk.summary(),
         "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps),
-        "roofline": {"bound": "hbm", "kernel": "stream_kernel<Q4_K, GATEUP>", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                     "bytes_per_launch": gateup_bytes, "ms_per_launch": gateup_ms,
-                     "other_kernels_us": {"route": route_ms * 1e3, "down": down_ms * 1e3,
-                                          "down_frac": TOP_K * D_MODEL * (E_FFN // 256) * 210 / (down_ms * 1e-3) / 1e9 / peak}},
+                     "bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
+                     "other_kernels_us": {"route": route_ms * 1e3, "gateup_alone": gateup_ms * 1e3, "down_alone": down_ms * 1e3,
+                                          "expert_stage": expert_ms * 1e3,
+                                          "gateup_alone_frac": gateup_bytes / (gateup_ms * 1e-3) / 1e9 / peak,
+                                          "down_alone_frac": down_bytes / (down_ms * 1e-3) / 1e9 / peak}},
         "cpu_baseline": cpu,
     }))
     if world > 1:

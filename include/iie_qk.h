@@ -164,6 +164,17 @@ int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long rows, long
  * 1 router product, 2 top-k, 3 gate/up, 4 down; 0 = all) so that one kernel can be timed alone on
  * data left by a previous full call; and the number of kernels launched since load. */
 void iie_profile_stage_mask(int mask);
+/* Two alternative launch structures of the single-token block, both off by default because they measured
+ * slower on B200 than the three-launch form (routing, gate/up, down); results are identical either way.
+ * 1: a single token's routing is recomputed inside the gate/up launch (two launches per block). */
+void iie_set_fused_route(int enabled);
+/* 1: a single token's expert stage runs as one launch, one thread-block cluster per selected expert;
+ * 0 (default): as two streamed launches (gate/up, down).  Results are identical; for measurements. */
+void iie_set_fused_expert(int enabled);
+/* Cluster shape that launch settled on: 1000 * CTAs per cluster + clusters the device holds at once
+ * (-1 before its first use). */
+int iie_expert_clusters(void);
+
 /* Switch programmatic dependent launch between the three single-token kernels on (default) or off. */
 void iie_set_pdl(int enabled);
 /* Token count from which iie_moe_forward_dev uses the tcgen05 grouped GEMMs instead of the streamed

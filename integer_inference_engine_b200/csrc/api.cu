@@ -57,7 +57,10 @@ cudaStream_t g_stream = nullptr;
 int *g_flags = nullptr;               // device flag word
 int *g_cells = nullptr;               // device ints: [0] limbs of h, [1] limbs of gate*up, [2] routing ticket
 const uint8_t **g_selptr = nullptr;   // device: [3][64] pointers of the experts the last routing selected
-int g_pdl = 1;                        // programmatic dependent launch between the three decode kernels
+int g_pdl = 1;                        // programmatic dependent launch between the decode kernels
+int g_fused_expert = 0;               // single-token expert stage as one cluster launch (expert.cu): slower on this part
+int g_fused_route = 0;                // routing recomputed inside the gate/up launch (rgu.cu): slower than its own launch
+int g_gu_parity = 0;                  // which of the two gu digit-count cells the next fused launch uses
 long long g_tc_min_tokens = 192;      // from this many tokens on, the MoE block runs on the tcgen05 grouped GEMMs
 int g_ready = -1;                     // -1 unknown, 0 usable, 1 unusable
 int g_stage_mask = 0;                 // profiling: when non-zero, iie_moe_forward_dev runs only these stages
@@ -355,6 +358,28 @@ bool moe_decode_token(const MoeLayer &L, const int64_t *x, const int64_t *gain, 
     int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)E * 8);
     int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)k * 8 * L.e_ffn);
     if (!hl || !lg || !gul) return false;
+    if (g_fused_route && g_stage_mask == 0 && r.qtype == QT_Q4K && L.gate_q == QT_Q4K && k <= 64 &&
+        !(init_mode == 1 && out == x)) {
+        int *cell = g_cells + 4 + g_gu_parity, *cell_next = g_cells + 4 + (g_gu_parity ^ 1);
+        RoutedGateUpArgs fa_ = {};
+        fa_.x = x; fa_.gain = gain; fa_.d = (int)L.d_model; fa_.fa = fa; fa_.fw = fw; fa_.eps = eps;
+        fa_.router = (const uint8_t *)r.d; fa_.n_experts = E; fa_.k = k; fa_.e_ffn = L.e_ffn; fa_.tabs = L.tabs;
+        fa_.ids = ids; fa_.gates = gates; fa_.sel_down = g_selptr + 2 * k; fa_.init_out = out; fa_.init_mode = init_mode;
+        fa_.out_limbs = gul; fa_.gu_nl = cell; fa_.gu_nl_next = cell_next; fa_.flags = g_flags; fa_.pdl = g_pdl;
+        fa_.fast = small_scales(L.maxd_gate, L.maxdmin_gate, fw);
+        const cudaError_t fe = launch_routed_gateup(L.gate_q, fa_, s);
+        if (fe == cudaSuccess) {
+            g_gu_parity ^= 1;
+            StreamArgs da = {};
+            da.wa = L.tabs + 2 * E; da.wb = da.wa; da.sel = ids; da.n_sel = k; da.out_f = L.d_model; da.n_blocks = L.e_ffn / 256;
+            da.fw = fw; da.fa = fa; da.xl = gul; da.x_per_sel = 1; da.x_nl = cell; da.out = out; da.gates = gates;
+            da.flags = g_flags; da.fast = small_scales(L.maxd_down, L.maxdmin_down, fw);
+            da.sel_wa = g_selptr + 2 * k; da.pdl = g_pdl; da.early_weights = 0;
+            return launch_stream(L.down_q, MODE_DOWN, da, s) == cudaSuccess;
+        }
+        cudaGetLastError();
+        if (fe != cudaErrorNotSupported) return false;
+    }
     RouteArgs ra = {};
     ra.x = x; ra.gain = gain; ra.d = (int)L.d_model; ra.fa = fa; ra.fw = fw; ra.eps = eps;
     ra.router = (const uint8_t *)r.d; ra.router_q = r.qtype; ra.n_experts = E; ra.k = k;
@@ -364,6 +389,16 @@ bool moe_decode_token(const MoeLayer &L, const int64_t *x, const int64_t *gain, 
     const bool ptrs = k <= 64;
     ra.tabs = ptrs ? L.tabs : nullptr; ra.sel_ptrs = ptrs ? g_selptr : nullptr; ra.pdl = g_pdl;
     if (stage_on(ST_ROUTER) && launch_route(ra, s) != cudaSuccess) return false;
+    if (g_fused_expert && ptrs && (g_stage_mask == 0 || (g_stage_mask & 24) == 24) && small_scales(L.maxd_gate, L.maxdmin_gate, fw) &&
+        small_scales(L.maxd_down, L.maxdmin_down, fw)) {
+        ExpertArgs ea = {};
+        ea.sel_ptrs = g_selptr; ea.k = k; ea.d_model = L.d_model; ea.e_ffn = L.e_ffn; ea.fw = fw; ea.fa = fa;
+        ea.hl = hl; ea.h_nl = g_cells; ea.gates = gates; ea.out = out; ea.flags = g_flags; ea.pdl = g_pdl;
+        const cudaError_t ee = launch_expert(L.gate_q, L.down_q, ea, s);
+        if (ee == cudaSuccess) return true;
+        cudaGetLastError();
+        if (ee != cudaErrorNotSupported) return false;
+    }
     StreamArgs ga = {};
     ga.wa = L.tabs; ga.wb = L.tabs + E; ga.sel = ids; ga.n_sel = k; ga.out_f = L.e_ffn; ga.n_blocks = L.d_model / 256;
     ga.fw = fw; ga.fa = fa; ga.xl = hl; ga.x_per_sel = 0; ga.x_nl = g_cells; ga.out = nullptr; ga.out_limbs = gul;
@@ -893,6 +928,18 @@ extern "C" int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long
 extern "C" void iie_set_tc_min_tokens(long long tokens) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     g_tc_min_tokens = tokens < 2 ? 2 : tokens;
+}
+
+extern "C" void iie_set_fused_route(int enabled) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    g_fused_route = enabled ? 1 : 0;
+}
+
+extern "C" int iie_expert_clusters(void) { return iie::g_expert_clusters < 0 ? -1 : iie::g_expert_cluster_size * 1000 + iie::g_expert_clusters; }
+
+extern "C" void iie_set_fused_expert(int enabled) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    g_fused_expert = enabled ? 1 : 0;
 }
 
 extern "C" void iie_set_pdl(int enabled) {

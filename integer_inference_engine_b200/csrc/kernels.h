@@ -88,6 +88,52 @@ struct RouteArgs {
 };
 cudaError_t launch_route(const RouteArgs &a, cudaStream_t s);
 
+// Single-token routing + gate/up in one launch (rgu.cu): every CTA recomputes the routing, then multiplies its
+// run of gate/up tiles of the selected experts.
+struct RoutedGateUpArgs {
+    const int64_t *x;              // [d] input row
+    const int64_t *gain;           // [d] RMSNorm gain, or nullptr (h = x)
+    int d, fa, fw;
+    unsigned long long eps;
+    const uint8_t *router;         // repacked Q4_K router [n_experts, d]
+    int n_experts, k;
+    long long e_ffn;
+    const uint8_t *const *tabs;    // device [3][n_experts]: gate, up, down pointers of the layer
+    int *ids;                      // out [k]
+    int64_t *gates;                // out [k]
+    const uint8_t **sel_down;      // out [k]: down-projection pointers of the selected experts
+    int64_t *init_out;             // nullable: the block's output row, initialised here
+    int init_mode;                 // 0 leave, 1 zero, 2 copy x (residual)
+    int8_t *out_limbs;             // out: digit planes of gu [k][8][e_ffn]
+    int *gu_nl;                    // atomicMax of the digits gu needs (zero on entry)
+    int *gu_nl_next;               // zeroed here: the cell the next block's launch uses
+    int *flags;                    // bit 0 digit envelope, bit 1 RMSNorm envelope, bit 3 a copy never arrived
+    int pdl, fast;
+    int tiles_per_expert, tiles_per_cta;   // filled in by the launcher
+    long long sig_log2e, sig_clip;
+};
+cudaError_t launch_routed_gateup(int qtype, const RoutedGateUpArgs &a, cudaStream_t s);
+
+// Single-token expert stage in one launch (expert.cu): one 16-CTA cluster per selected expert runs gate/up,
+// SiLU * up, down and the gate-weighted combine.
+struct ExpertArgs {
+    const uint8_t *const *sel_ptrs;   // device [3][k]: gate, up, down pointers of the selected experts
+    int k;
+    long long d_model, e_ffn;
+    int fw, fa;
+    long long sig_log2e, sig_clip;    // filled in by the launcher
+    const int8_t *hl;                 // digit planes of the hidden row [8][d_model]
+    const int *h_nl;                  // digits in use by it
+    const int64_t *gates;             // [k]
+    int64_t *out;                     // [d_model], accumulated into
+    int *flags;                       // bit 0 digit envelope, bit 3 a copy never arrived
+    int pdl;                          // 1: launched with programmatic stream serialization
+    int gt, dt, down_early;           // tiles per CTA; down tiles requested up front (filled in by the launcher)
+};
+cudaError_t launch_expert(int gate_q, int down_q, const ExpertArgs &a, cudaStream_t s);
+extern int g_expert_clusters;      // co-resident clusters reported for the expert kernel, -1 before its first launch
+extern int g_expert_cluster_size;  // CTAs per cluster the launcher chose
+
 // Prefill-regime grouped products on tcgen05 (prefill.cu).  Pairs are sorted by expert: expert x owns
 // pairs [grp_off[x], grp_off[x+1]).
 struct PrefillArgs {
