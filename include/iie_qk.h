@@ -151,6 +151,26 @@ int iie_route_dev(long long router_h, int top_k, const int64_t *h_dev, long long
 int iie_moe_experts_dev(long long layer, const int64_t *h_dev, long long T, const int *ids_dev, const int64_t *gates_dev,
                         int slots, int expert_base, int fa, int fw, int accumulate, int64_t *out_dev, void *stream);
 
+/* Attention of ONE new token over an int32 KV cache, on device tensors (the arithmetic of
+ * north-mini-code/src/nmc/cohere2.py:324-354 attention_cached with m = 1; in the reference's CUDA library this
+ * lives behind qk_attention_bank_apply, north-mini-code/tools/nmc_qk_cuda.cu:1436-1551):
+ *   q_dev [n_heads*head_dim], k_dev / v_dev [n_kv*head_dim]  projected rows of the token (q is rotated IN PLACE),
+ *   kcache_dev / vcache_dev [n_kv][cache_rows][head_dim] int32, row `pos` is written by this call,
+ *   window > 0: only keys pos-window+1 .. pos are visible; otherwise all keys 0 .. pos,
+ *   rope 0 none, 1 interleaved pairs, 2 rotate-half pairs; cos_dev / sin_dev [>= pos+1][head_dim/2] int64 at 2^fa,
+ *   inv_sqrt = round(2^fa / sqrt(head_dim)) as the caller's model defines it,
+ *   out_dev [n_heads*head_dim] = (softmax(scores) v) >> fa.
+ * Flag bit 2 is raised when a key or value does not fit the int32 cache. */
+int iie_attn_decode_dev(int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
+                        int32_t *vcache_dev, long long pos, long long window, const int64_t *cos_dev,
+                        const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim, long long cache_rows,
+                        int fa, long long inv_sqrt, int64_t *out_dev, void *stream);
+/* Row `token` (or *token_dev when token_dev != NULL) of a registered Q4_K / Q6_K matrix as int64 at 2^frac:
+ * the embedding look-up (north-mini-code/src/nmc/engine.py:239-243). */
+int iie_embed_dev(long long h, const int *token_dev, long long token, int frac, int64_t *out_dev, void *stream);
+/* Index of the largest of n int64 values, lowest index on ties (greedy pick of engine.py:585). */
+int iie_argmax_dev(const int64_t *x_dev, long long n, int *out_dev, void *stream);
+
 /* Plain resident product on device tensors: out_dev [T,out_f] = floor(x_dev W^T / 2^fw). */
 int iie_apply_dev(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev, void *stream);
 

@@ -69,7 +69,7 @@ inline bool stage_on(int st) { return g_stage_mask == 0 || (g_stage_mask & st); 
 
 // Persistent device scratch by role, grown on demand (never shrunk until released).
 enum Role { R_X, R_XL, R_OUT, R_RAW, R_GU, R_GUL, R_TMP0, R_TMP1, R_TMP2, R_TABS, R_META, R_LOGITS, R_IDS, R_GATES,
-            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_COUNT };
+            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_ASCORES, R_AEXP, R_ASTAT, R_COUNT };
 struct Buf { void *p = nullptr; size_t cap = 0; };
 Buf g_buf[R_COUNT];
 long long g_ws_allocs = 0;
@@ -194,10 +194,19 @@ bool linear_dev(const Weight &w, const int64_t *x, long long T, int fw, int64_t 
         if (!buf || launch_limbs(x, T, K, buf, g_flags, s) != cudaSuccess) return false;
         xl = buf;
     }
-    SkinnyArgs a = {};
-    a.wa = w.cell; a.wb = w.cell; a.pairs_per_group = (int)T; a.out_f = w.out_f; a.n_blocks = w.nb; a.fw = fw; a.fa = 16;
-    a.xl = xl; a.out = out; a.flags = g_flags;
-    if (launch_skinny(w.qtype, MODE_LINEAR, a, 1, (int)std::min<long long>(T, 4), s) != cudaSuccess) return false;
+    if (T == 1 && w.out_f >= 256 && g_stage_mask == 0) {
+        // one row: the bulk-copy streaming kernel (every CTA requests its run of 16-row tiles up front)
+        StreamArgs sa = {};
+        sa.wa = w.cell; sa.wb = w.cell; sa.n_sel = 1; sa.out_f = w.out_f; sa.n_blocks = w.nb; sa.fw = fw; sa.fa = 16;
+        sa.xl = xl; sa.x_per_sel = 0; sa.x_nl = nullptr; sa.out = out; sa.flags = g_flags;
+        sa.fast = small_scales(w.maxd, w.maxdmin, fw); sa.pdl = 0;
+        if (launch_stream(w.qtype, MODE_LINEAR, sa, s) != cudaSuccess) return false;
+    } else {
+        SkinnyArgs a = {};
+        a.wa = w.cell; a.wb = w.cell; a.pairs_per_group = (int)T; a.out_f = w.out_f; a.n_blocks = w.nb; a.fw = fw; a.fa = 16;
+        a.xl = xl; a.out = out; a.flags = g_flags;
+        if (launch_skinny(w.qtype, MODE_LINEAR, a, 1, (int)std::min<long long>(T, 4), s) != cudaSuccess) return false;
+    }
     if (check_flags) {
         const int f = read_flags_clear();
         if (f < 0) return false;
@@ -896,6 +905,46 @@ extern "C" int iie_moe_experts_dev(long long layer, const int64_t *h_dev, long l
         cudaGetLastError(); return 1;
     }
     return 0;
+}
+
+extern "C" int iie_attn_decode_dev(int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
+                                   int32_t *vcache_dev, long long pos, long long window, const int64_t *cos_dev,
+                                   const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim,
+                                   long long cache_rows, int fa, long long inv_sqrt, int64_t *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !q_dev || !k_dev || !v_dev || !kcache_dev || !vcache_dev || !out_dev || n_heads <= 0 || head_dim <= 0 ||
+        cache_rows <= 0 || fa < 1 || fa > 29) return 1;
+    AttnArgs a = {};
+    a.q = q_dev; a.k = k_dev; a.v = v_dev; a.kcache = kcache_dev; a.vcache = vcache_dev; a.pos = pos;
+    a.lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0; a.Lmax = cache_rows;
+    a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim; a.fa = fa;
+    a.inv_sqrt = inv_sqrt; a.log2e = sigmoid_log2e(fa);
+    const long long ca = (((long long)(fa + 2)) << (2 * fa)) / a.log2e, cb = ((long long)1 << 62) / a.log2e;
+    a.clip = ca < cb ? ca : cb;
+    a.scores = (int64_t *)ensure(R_ASCORES, (size_t)n_heads * cache_rows * 8);
+    a.e = (int32_t *)ensure(R_AEXP, (size_t)n_heads * cache_rows * 4);
+    uint8_t *st = (uint8_t *)ensure(R_ASTAT, (size_t)n_heads * 16 + (size_t)n_heads * head_dim * 8 + 64);
+    if (!a.scores || !a.e || !st) return 1;
+    a.hmax = (long long *)st; a.Z = (unsigned long long *)(st + (size_t)n_heads * 8);
+    a.acc = (long long *)(st + (size_t)n_heads * 16); a.ticket = (unsigned *)(st + (size_t)n_heads * 16 + (size_t)n_heads * head_dim * 8);
+    a.out = out_dev; a.flags = g_flags;
+    const cudaError_t e = launch_attn_decode(a, (cudaStream_t)stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return 1; }
+    return 0;
+}
+
+extern "C" int iie_embed_dev(long long h, const int *token_dev, long long token, int frac, int64_t *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !valid_q(h) || !out_dev || frac < 0 || frac > 40) return 1;
+    const Weight &w = g_w[h];
+    if (!token_dev && (token < 0 || token >= w.out_f)) return 1;
+    return launch_embed_row((const uint8_t *)w.d, w.qtype, w.nb, token_dev, token, frac, out_dev, (cudaStream_t)stream) == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int iie_argmax_dev(const int64_t *x_dev, long long n, int *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !x_dev || !out_dev || n <= 0) return 1;
+    return launch_argmax(x_dev, n, out_dev, (cudaStream_t)stream) == cudaSuccess ? 0 : 1;
 }
 
 extern "C" int iie_apply_dev(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev, void *stream) {

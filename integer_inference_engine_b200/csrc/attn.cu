@@ -1,0 +1,262 @@
+// Integer attention for one new token over a KV cache, plus the two small ends of a decode step
+// (embedding row, arg-max of the logits).
+//
+// Arithmetic of north-mini-code/src/nmc/cohere2.py:324-354 (attention_cached) with
+// _bonsai/fixedpoint.py:99-133 (fixed_point_softmax) and _bonsai/rope.py:79-100 / rope_v2.py:92-117:
+//     score_l = (((q . k_l) >> fa) * inv_sqrt) >> fa          over the visible keys lo..pos
+//     e_l     = 2^-(((min(max - score_l, clip)) * log2e) >> fa)          (cubic fixed-point 2^-f)
+//     p_l     = (e_l << fa) // sum(e)
+//     out_d   = (sum_l p_l v_{l,d}) >> fa
+// Masked keys carry the sentinel -(2^(fa+30)) in the reference; their e is exactly 0 and the row maximum is
+// always a visible key, so skipping them gives the same bytes.
+//
+// The floors make the softmax non-linear, so the three passes need the row maximum and the normaliser of ALL
+// visible keys: scores + max, exponentials + sum, probabilities x values are three launches over
+// (KV head, key chunk) CTAs; a CTA serves every query head of its KV head so K and V are read once.
+// The cache holds K (after rotation) and V as int32: values outside int32 raise flag bit 2 (the reference bank
+// stores them the same way and refuses such values).
+#include "kernels.h"
+#include "layout.cuh"
+
+namespace iie {
+
+namespace {
+
+constexpr int AT_CH = 64;                   // keys per CTA
+constexpr int AT_MAXREP = 16;               // query heads per KV head
+
+__global__ void attn_prep_kernel(const AttnArgs a) {
+    const int tid = threadIdx.x, nth = blockDim.x;
+    const int half = a.hd / 2;
+    const int64_t *cs = a.cos ? a.cos + a.pos * half : nullptr, *sn = a.sin ? a.sin + a.pos * half : nullptr;
+    bool bad = false;
+    // q rotated in place; k rotated into the cache; v copied into the cache
+    for (int idx = tid; idx < (a.H + a.Hkv) * half; idx += nth) {
+        const bool is_q = idx < a.H * half;
+        const int j = is_q ? idx : idx - a.H * half, head = j / half, i = j - head * half;
+        const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
+        const int64_t *src = is_q ? a.q + head * a.hd : a.k + head * a.hd;
+        int64_t x0 = src[i0], x1 = src[i1];
+        if (a.rope) {
+            const int64_t c = cs[i], s = sn[i];
+            const int64_t y0 = (x0 * c - x1 * s) >> a.fa, y1 = (x0 * s + x1 * c) >> a.fa;
+            x0 = y0; x1 = y1;
+        }
+        if (is_q) { a.q[head * a.hd + i0] = x0; a.q[head * a.hd + i1] = x1; }
+        else {
+            int32_t *dst = a.kcache + ((long long)head * a.Lmax + a.pos) * a.hd;
+            bad |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+            dst[i0] = (int32_t)x0; dst[i1] = (int32_t)x1;
+        }
+    }
+    for (int idx = tid; idx < a.Hkv * a.hd; idx += nth) {
+        const int head = idx / a.hd, i = idx - head * a.hd;
+        const int64_t v = a.v[idx];
+        bad |= v != (int32_t)v;
+        a.vcache[((long long)head * a.Lmax + a.pos) * a.hd + i] = (int32_t)v;
+    }
+    for (int idx = tid; idx < a.H; idx += nth) { a.hmax[idx] = INT64_MIN; a.Z[idx] = 0ULL; }
+    for (int idx = tid; idx < a.H * a.hd; idx += nth) a.acc[idx] = 0;
+    if (tid == 0) *a.ticket = 0u;
+    if (bad) atomicOr(a.flags, 4);
+}
+
+// pass 1: scores of AT_CH keys for the `rep` query heads of one KV head; one warp per key
+__global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a) {
+    extern __shared__ long long at_q[];                   // [rep][hd]
+    __shared__ long long s_max[AT_MAXREP];
+    const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
+    for (int i = tid; i < rep * a.hd; i += blockDim.x) at_q[i] = a.q[(long long)kv * rep * a.hd + i];
+    if (tid < AT_MAXREP) s_max[tid] = INT64_MIN;
+    __syncthreads();
+    long long wmax[AT_MAXREP];
+#pragma unroll
+    for (int r = 0; r < AT_MAXREP; r++) wmax[r] = INT64_MIN;
+    const int per_lane = a.hd / 32;                        // 4 for head_dim 128
+    for (long long l = l0 + warp; l < l1; l += 8) {
+        const int32_t *krow = a.kcache + ((long long)kv * a.Lmax + l) * a.hd + lane * per_lane;
+        int32_t kk[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) kk[j] = j < per_lane ? __ldg(krow + j) : 0;
+#pragma unroll
+        for (int r = 0; r < AT_MAXREP; r++) {
+            if (r < rep) {
+                const long long *qq = at_q + r * a.hd + lane * per_lane;
+                long long part = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) if (j < per_lane) part += qq[j] * (long long)kk[j];
+#pragma unroll
+                for (int s = 16; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
+                const long long sc = ((part >> a.fa) * a.inv_sqrt) >> a.fa;
+                if (lane == 0) a.scores[(long long)(kv * rep + r) * a.Lmax + l] = sc;
+                wmax[r] = max(wmax[r], sc);
+            }
+        }
+    }
+    if (lane == 0)
+        for (int r = 0; r < rep; r++) if (wmax[r] != INT64_MIN) atomicMax(&s_max[r], wmax[r]);
+    __syncthreads();
+    if (tid < rep && s_max[tid] != INT64_MIN) atomicMax(a.hmax + kv * rep + tid, s_max[tid]);
+}
+
+// pass 2: exponentials and their sum
+__global__ void __launch_bounds__(256) attn_exp_kernel(const AttnArgs a) {
+    __shared__ unsigned long long s_sum[8];
+    const int h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long l = a.lo + (long long)blockIdx.x * 256 + tid;
+    unsigned long long e = 0;
+    if (l <= a.pos) {
+        const long long m = a.hmax[h], s = a.scores[(long long)h * a.Lmax + l];
+        long long dlt = m - s;
+        dlt = dlt < a.clip ? dlt : a.clip;
+        e = (unsigned long long)exp2_neg_fixed((dlt * a.log2e) >> a.fa, a.fa);
+        a.e[(long long)h * a.Lmax + l] = (int32_t)e;
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) e += __shfl_xor_sync(0xffffffffu, e, s);
+    if (lane == 0) s_sum[warp] = e;
+    __syncthreads();
+    if (tid == 0) {
+        unsigned long long t = 0;
+        for (int i = 0; i < 8; i++) t += s_sum[i];
+        if (t) atomicAdd(a.Z + h, t);
+    }
+}
+
+// pass 3: probabilities x values, partial sums added into acc; the CTA that finishes last shifts and writes out
+__global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a) {
+    __shared__ long long s_p[AT_MAXREP][AT_CH];
+    __shared__ int s_last;
+    const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x;
+    const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
+    const int nk = (int)(l1 - l0);
+    for (int i = tid; i < rep * AT_CH; i += blockDim.x) {
+        const int r = i / AT_CH, j = i - r * AT_CH;
+        long long p = 0;
+        if (j < nk) {
+            const int h = kv * rep + r;
+            const unsigned long long z = a.Z[h];
+            const unsigned long long e = (unsigned long long)(unsigned)a.e[(long long)h * a.Lmax + l0 + j];
+            p = z ? (long long)((e << a.fa) / z) : 0;
+        }
+        s_p[r][j] = p;
+    }
+    __syncthreads();
+    const int G = blockDim.x / a.hd, grp = tid / a.hd, d = tid - grp * a.hd;      // head groups sharing the CTA
+    if (grp < G) {
+        long long accv[AT_MAXREP / 2];
+#pragma unroll
+        for (int i = 0; i < AT_MAXREP / 2; i++) accv[i] = 0;
+        const int32_t *vbase = a.vcache + ((long long)kv * a.Lmax + l0) * a.hd + d;
+        for (int j = 0; j < nk; j++) {
+            const long long v = (long long)__ldg(vbase + (long long)j * a.hd);
+#pragma unroll
+            for (int i = 0; i < AT_MAXREP / 2; i++) {
+                const int r = grp + i * G;
+                if (r < rep) accv[i] += s_p[r][j] * v;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < AT_MAXREP / 2; i++) {
+            const int r = grp + i * G;
+            if (r < rep && accv[i] != 0)
+                atomicAdd(reinterpret_cast<unsigned long long *>(a.acc + (long long)(kv * rep + r) * a.hd + d), (unsigned long long)accv[i]);
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(a.ticket, 1u) == gridDim.x * gridDim.y - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int i = tid; i < a.H * a.hd; i += blockDim.x) a.out[i] = *((volatile long long *)(a.acc + i)) >> a.fa;
+}
+
+// one row of a registered Q4_K / Q6_K matrix as int64 at 2^frac (the embedding look-up)
+__global__ void embed_row_kernel(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,
+                                 int64_t *out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nb * 256) return;
+    const long long o = row_dev ? (long long)*row_dev : row_host, b = i >> 8;
+    const int e = (int)(i & 255);
+    auto byte = [&](int k) { return (int)repacked_byte(w, qtype, nb, o, b, k); };
+    int64_t val;
+    if (qtype == QT_Q4K) {
+        const int64_t dq = half_to_fixed(byte(0) | (byte(1) << 8), frac), dmq = half_to_fixed(byte(2) | (byte(3) << 8), frac);
+        const int j = e >> 5, l = e & 31;
+        int sc, mn;
+        if (j < 4) { sc = byte(4 + j) & 63; mn = byte(8 + j) & 63; }
+        else { sc = (byte(8 + j) & 0xF) | ((byte(j) >> 6) << 4); mn = (byte(8 + j) >> 4) | ((byte(4 + j) >> 6) << 4); }
+        const int q = (byte(16 + 32 * (j >> 1) + l) >> ((j & 1) * 4)) & 0xF;
+        val = dq * sc * q - dmq * mn;
+    } else {
+        const int64_t dq = half_to_fixed(byte(208) | (byte(209) << 8), frac);
+        const int sb = e >> 4, l = e & 15, half = sb >> 3, k = (sb >> 1) & 3, l0 = (sb & 1) * 16;
+        const int ql = byte(64 * half + 32 * (k & 1) + l0 + l), qh = byte(128 + 32 * half + l0 + l);
+        const int q = (((k < 2) ? (ql & 0xF) : (ql >> 4)) | (((qh >> (2 * k)) & 3) << 4)) - 32;
+        val = dq * (int64_t)(int8_t)byte(192 + 8 * half + 2 * k + (sb & 1)) * q;
+    }
+    out[i] = val;
+}
+
+// arg-max with the lowest index on ties, one CTA
+__global__ void __launch_bounds__(1024) argmax_kernel(const int64_t *x, long long n, int *out) {
+    __shared__ long long s_v[32];
+    __shared__ long long s_i[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    long long bv = INT64_MIN, bi = n;
+    for (long long i = tid; i < n; i += blockDim.x) {
+        const long long v = x[i];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        const long long ov = __shfl_xor_sync(0xffffffffu, bv, s), oi = __shfl_xor_sync(0xffffffffu, bi, s);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { s_v[warp] = bv; s_i[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        bv = lane < (blockDim.x >> 5) ? s_v[lane] : INT64_MIN; bi = lane < (blockDim.x >> 5) ? s_i[lane] : n;
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) {
+            const long long ov = __shfl_xor_sync(0xffffffffu, bv, s), oi = __shfl_xor_sync(0xffffffffu, bi, s);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) *out = (int)bi;
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
+    const int rep = a.Hkv > 0 ? a.H / a.Hkv : 0;
+    if (a.H <= 0 || a.Hkv <= 0 || a.H % a.Hkv || rep > AT_MAXREP || (a.hd > 0 && a.hd <= 256 && rep > (256 / a.hd) * (AT_MAXREP / 2)) || a.hd < 32 || a.hd > 256 || a.hd % 32 || 256 % a.hd ||
+        a.pos < 0 || a.pos >= a.Lmax || a.lo < 0 || a.lo > a.pos || a.fa < 1 || a.fa > 29 || (a.rope && (!a.cos || !a.sin)))
+        return cudaErrorInvalidValue;
+    const long long n_keys = a.pos - a.lo + 1;
+    const unsigned chunks = (unsigned)((n_keys + AT_CH - 1) / AT_CH);
+    attn_prep_kernel<<<1, 512, 0, s>>>(a);
+    attn_scores_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)rep * a.hd * 8, s>>>(a);
+    attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H), 256, 0, s>>>(a);
+    attn_pv_kernel<<<dim3(chunks, a.Hkv), 256, 0, s>>>(a);
+    note_launch(4);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_embed_row(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,
+                             int64_t *out, cudaStream_t s) {
+    embed_row_kernel<<<(unsigned)((nb * 256 + 255) / 256), 256, 0, s>>>(w, qtype, nb, row_dev, row_host, frac, out);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax(const int64_t *x, long long n, int *out, cudaStream_t s) {
+    if (n <= 0) return cudaErrorInvalidValue;
+    argmax_kernel<<<1, 1024, 0, s>>>(x, n, out);
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace iie

@@ -195,6 +195,30 @@ cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, co
 cudaError_t launch_dispatch(const int *ids, const int64_t *gates, long long T, int k, int n_experts, int *grp_off,
                             int *pair_tok, int64_t *pair_gate, cudaStream_t s, int expert_base = 0);
 
+// One new token's attention over an int32 KV cache (attn.cu): rotation, cache append, three softmax passes.
+struct AttnArgs {
+    int64_t *q;                    // [H*hd] projected query, rotated in place
+    const int64_t *k, *v;          // [Hkv*hd] projected key / value of the new token
+    int32_t *kcache, *vcache;      // [Hkv][Lmax][hd]
+    long long pos, lo, Lmax;       // position of the new token, first visible key, cache rows
+    const int64_t *cos, *sin;      // [>= pos+1][hd/2] at 2^fa, or nullptr when rope == 0
+    int rope;                      // 0 none, 1 interleaved pairs (2i, 2i+1), 2 rotate-half pairs (i, i + hd/2)
+    int H, Hkv, hd, fa;
+    long long inv_sqrt, log2e, clip;
+    int64_t *scores;               // scratch [H][Lmax]
+    int32_t *e;                    // scratch [H][Lmax]
+    long long *hmax;               // scratch [H]
+    unsigned long long *Z;         // scratch [H]
+    long long *acc;                // scratch [H][hd]
+    unsigned *ticket;              // scratch
+    int64_t *out;                  // [H*hd]
+    int *flags;                    // bit 2: a key / value does not fit the int32 cache
+};
+cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s);
+cudaError_t launch_embed_row(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,
+                             int64_t *out, cudaStream_t s);
+cudaError_t launch_argmax(const int64_t *x, long long n, int *out, cudaStream_t s);
+
 // Q1_0 linear (q1.cu).  Units: 16-row tiles x 128-weight blocks, 256 B of sign bits in MMA order + 16 scales.
 size_t q1_unit_bytes(bool sc32);
 cudaError_t launch_q1_repack(const uint8_t *bits, const void *scale, int src_bits, bool sc32, long long out_f, long long nb,

@@ -76,6 +76,58 @@ def rmsnorm(x: torch.Tensor, gain_handle: int = -1, fa: int = 16, eps: int = 1, 
     return out
 
 
+def attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                     pos: int, n_heads: int, n_kv: int, head_dim: int, fa: int = 16, window: int = 0,
+                     cos: torch.Tensor | None = None, sin: torch.Tensor | None = None, rope: int = 0,
+                     inv_sqrt: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One new token's GQA attention over the int32 caches ``[n_kv, rows, head_dim]``; writes cache row ``pos``
+    and rotates ``q`` in place.  Returns ``[n_heads * head_dim]`` int64."""
+    lib = qk_cuda._lib()
+    assert q.is_cuda and q.dtype == torch.int64 and q.is_contiguous() and q.numel() == n_heads * head_dim
+    assert k.dtype == torch.int64 and v.dtype == torch.int64 and k.numel() == n_kv * head_dim == v.numel()
+    assert kcache.dtype == torch.int32 and vcache.dtype == torch.int32 and kcache.is_contiguous() and vcache.is_contiguous()
+    assert kcache.shape == vcache.shape and kcache.shape[0] == n_kv and kcache.shape[2] == head_dim
+    if inv_sqrt is None:
+        inv_sqrt = int(round((1.0 / head_dim ** 0.5) * (1 << fa)))
+    if out is None:
+        out = torch.empty(n_heads * head_dim, dtype=torch.int64, device=q.device)
+    with _CUDA_LOCK:
+        rc = lib.iie_attn_decode_dev(q.data_ptr(), k.contiguous().data_ptr(), v.contiguous().data_ptr(), kcache.data_ptr(),
+                                     vcache.data_ptr(), int(pos), int(window or 0), cos.data_ptr() if rope else None,
+                                     sin.data_ptr() if rope else None, int(rope), n_heads, n_kv, head_dim,
+                                     int(kcache.shape[1]), int(fa), int(inv_sqrt), out.data_ptr(), _stream_ptr())
+    if rc != 0:
+        raise CudaContextError(f"attention failed with status {rc}")
+    return out
+
+
+def embed(handle: int, token, d_model: int, fa: int = 16, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Row ``token`` (an int, or a CUDA int32 tensor holding it) of a registered matrix at 2**fa -> [1, d_model]."""
+    lib = qk_cuda._lib()
+    if out is None:
+        out = torch.empty((1, d_model), dtype=torch.int64, device="cuda")
+    on_dev = isinstance(token, torch.Tensor)
+    with _CUDA_LOCK:
+        rc = lib.iie_embed_dev(int(handle), token.data_ptr() if on_dev else None, 0 if on_dev else int(token), int(fa),
+                               out.data_ptr(), _stream_ptr())
+    if rc != 0:
+        raise CudaContextError(f"embedding look-up failed with status {rc}")
+    return out
+
+
+def argmax(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Index of the largest value, lowest index on ties -> CUDA int32 tensor [1]."""
+    lib = qk_cuda._lib()
+    assert x.is_cuda and x.dtype == torch.int64 and x.is_contiguous()
+    if out is None:
+        out = torch.empty(1, dtype=torch.int32, device=x.device)
+    with _CUDA_LOCK:
+        rc = lib.iie_argmax_dev(x.data_ptr(), x.numel(), out.data_ptr(), _stream_ptr())
+    if rc != 0:
+        raise CudaContextError(f"argmax failed with status {rc}")
+    return out
+
+
 def launch_count() -> int:
     """Kernels launched by the library since it was loaded."""
     return int(qk_cuda.load_library().iie_launch_count())

@@ -252,6 +252,84 @@ def moe_layer(h_int, router_fixed, experts, k: int, fa: int, fw: int):
 
 
 # ------------------------------------------------------------------------------------------------
+# attention sublayer: RoPE tables, rotation, softmax, KV-cached GQA attention
+# ------------------------------------------------------------------------------------------------
+def build_rope_tables(seq_len: int, head_dim: int, base: float = 10000.0, frac: int = 16):
+    """cos/sin at scale 2**frac, shape [seq_len, head_dim // 2]: round(cos(p * base**(-2i/d)) * 2**frac)
+    (_bonsai/rope.py:42-66)."""
+    import math
+    half = head_dim // 2
+    inv = [base ** (-(2 * i) / head_dim) for i in range(half)]
+    cos = np.empty((seq_len, half), np.int64)
+    sin = np.empty((seq_len, half), np.int64)
+    for p in range(seq_len):
+        for i in range(half):
+            cos[p, i] = round(math.cos(p * inv[i]) * (1 << frac))
+            sin[p, i] = round(math.sin(p * inv[i]) * (1 << frac))
+    return cos, sin
+
+
+def rope_fixed(x, cos, sin, frac: int = 16, neox: bool = False) -> np.ndarray:
+    """x [..., seq, hd] rotated with table rows 0..seq-1.  Interleaved pairs (2i, 2i+1)
+    (_bonsai/rope.py:79-100) or rotate-half pairs (i, i + hd/2) (_bonsai/rope_v2.py:92-117):
+    out0 = (x0 c - x1 s) >> frac, out1 = (x0 s + x1 c) >> frac."""
+    x = np.asarray(x, np.int64)
+    seq, hd = x.shape[-2], x.shape[-1]
+    c, s = cos[:seq], sin[:seq]
+    out = np.empty_like(x)
+    if neox:
+        x0, x1 = x[..., :hd // 2], x[..., hd // 2:]
+        out[..., :hd // 2] = (x0 * c - x1 * s) >> frac
+        out[..., hd // 2:] = (x0 * s + x1 * c) >> frac
+    else:
+        x0, x1 = x[..., 0::2], x[..., 1::2]
+        out[..., 0::2] = (x0 * c - x1 * s) >> frac
+        out[..., 1::2] = (x0 * s + x1 * c) >> frac
+    return out
+
+
+def softmax_fixed(z, frac: int = 16) -> np.ndarray:
+    """Row softmax in integers: d = min(max - z, clip); e = 2**-(d log2e); p = (e << frac) // sum(e)
+    (_bonsai/fixedpoint.py:99-133)."""
+    z = np.atleast_2d(np.asarray(z, np.int64))
+    log2e = _scaled_log2e(frac)
+    clip = min(((frac + 2) << (2 * frac)) // log2e, (1 << 62) // log2e)
+    out = np.empty_like(z)
+    for r in range(z.shape[0]):
+        d = np.minimum(int(z[r].max()) - z[r], clip)
+        e = exp2_neg_fixed((d * log2e) >> frac, frac)
+        tot = int(e.sum())
+        out[r] = 0 if tot == 0 else (e << frac) // tot
+    return out
+
+
+def attention_cached(q, ck, cv, start: int, n_heads: int, n_kv: int, fa: int = 16, window=None, inv_sqrt=None):
+    """m queries q [m, H, hd] at absolute positions start.. over the cache ck/cv [Hkv, Lc, hd] (Lc = start + m):
+    scores = ((q k^T) >> fa) * inv_sqrt >> fa, causal + sliding-window mask with -(2**(fa+30)), integer softmax,
+    out = (p v) >> fa  ->  [m, H*hd]  (cohere2.py:324-354)."""
+    import math
+    q = np.asarray(q, np.int64)
+    m, H, hd = q.shape
+    Lc = ck.shape[1]
+    rep = n_heads // n_kv
+    if inv_sqrt is None:
+        inv_sqrt = int(round((1.0 / math.sqrt(hd)) * (1 << fa)))
+    neg = -(1 << (fa + 30))
+    out = np.empty((m, H, hd), np.int64)
+    for h in range(H):
+        kh, vh = np.asarray(ck[h // rep], np.int64), np.asarray(cv[h // rep], np.int64)
+        scores = ((q[:, h, :] @ kh.T) >> fa)
+        scores = (scores * inv_sqrt) >> fa
+        for i in range(m):
+            p = start + i
+            scores[i, p + 1:] = neg
+            if window is not None and p - window >= 0:
+                scores[i, :p - window + 1] = neg
+        out[:, h, :] = (softmax_fixed(scores, fa) @ vh) >> fa
+    return out.reshape(m, H * hd)
+
+
+# ------------------------------------------------------------------------------------------------
 # balanced base-256 limbs (the decomposition the tensor/dp4a style kernels rely on)
 # ------------------------------------------------------------------------------------------------
 def balanced_capacity(n_limbs: int) -> int:

@@ -141,6 +141,33 @@ def q1_fixture():
     return out
 
 
+def attention_fixture():
+    """RoPE (both pairings), softmax rows incl. masked sentinels, and KV-cached attention (decode and a short
+    prefill, full and sliding-window) from the reference's own functions."""
+    from nmc._bonsai import rope as rrope
+    from nmc._bonsai import rope_v2 as rrope2
+    out = {}
+    rng = np.random.default_rng(700)
+    cos, sin = rrope.build_rope_tables(40, 16, 50000.0, FA)
+    out["rope_cos"], out["rope_sin"] = cos, sin
+    x = rng.integers(-(1 << 22), 1 << 22, size=(3, 40, 16), dtype=np.int64)
+    out["rope_inter"] = rrope.apply_rope_fixed(x, cos, sin, FA)
+    out["rope_neox"] = rrope2.apply_rope_fixed_neox(x, cos, sin, FA)
+    z = rng.integers(-(1 << 20), 1 << 20, size=(6, 50), dtype=np.int64)
+    z[1, 10:] = -(1 << (FA + 30)); z[2, :] = 7; z[3, 0] = 1 << 40
+    out["softmax"] = rfp.fixed_point_softmax(z, FA)
+    H, Hkv, hd = 4, 2, 16
+    cfg = c2.Cfg(d_model=H * hd, n_heads=H, n_kv=Hkv, head_dim=hd, ffn=0, vocab=0)
+    for name, (Lc, m, window) in {"dec_full": (37, 1, None), "dec_win": (37, 1, 9), "pre_full": (12, 12, None),
+                                  "pre_win": (20, 5, 7)}.items():
+        r2 = np.random.default_rng(710 + len(name) + Lc)
+        q = r2.integers(-(1 << 19), 1 << 19, size=(m, H, hd), dtype=np.int64)
+        ck = r2.integers(-(1 << 19), 1 << 19, size=(Hkv, Lc, hd), dtype=np.int64)
+        cv = r2.integers(-(1 << 19), 1 << 19, size=(Hkv, Lc, hd), dtype=np.int64)
+        out[f"att_{name}"] = c2.attention_cached(q, ck, cv, Lc - m, cfg, window)
+    return out
+
+
 def main():
     np.savez_compressed(HERE / "half_fixed.npz", **half_fixture())
     np.savez_compressed(HERE / "codec.npz", **codec_fixture())
@@ -148,6 +175,7 @@ def main():
     np.savez_compressed(HERE / "scalar.npz", **scalar_fixture())
     np.savez_compressed(HERE / "q1.npz", **q1_fixture())
     np.savez_compressed(HERE / "moe.npz", **moe_fixture())
+    np.savez_compressed(HERE / "attention.npz", **attention_fixture())
 
 
 if __name__ == "__main__":

@@ -1,0 +1,118 @@
+"""GPU parity of the single-token attention, the embedding look-up and the arg-max against the golden vectors
+generated from the reference and against the NumPy oracle."""
+import numpy as np
+import pytest
+
+from oracle import qk_oracle as o
+
+pytestmark = pytest.mark.gpu
+FA, FW = 16, 24
+
+
+def _run(q, ck, cv, pos, H, Hkv, hd, window, rope=0, cos=None, sin=None, rows=None):
+    """Feeds the cache rows 0..pos-1, then calls the entry for the token at `pos` with un-rotated q/k."""
+    import torch
+
+    from integer_inference_engine_b200 import device
+    rows = rows or pos + 3
+    kc = torch.zeros((Hkv, rows, hd), dtype=torch.int32, device="cuda")
+    vc = torch.zeros_like(kc)
+    kc[:, :pos] = torch.from_numpy(ck[:, :pos].astype(np.int32)).cuda()
+    vc[:, :pos] = torch.from_numpy(cv[:, :pos].astype(np.int32)).cuda()
+    qd = torch.from_numpy(q.reshape(-1).copy()).cuda()
+    kd = torch.from_numpy(ck[:, pos].reshape(-1).copy()).cuda()
+    vd = torch.from_numpy(cv[:, pos].reshape(-1).copy()).cuda()
+    out = device.attention_decode(qd, kd, vd, kc, vc, pos, H, Hkv, hd, FA, window or 0,
+                                  None if cos is None else torch.from_numpy(cos).cuda(),
+                                  None if sin is None else torch.from_numpy(sin).cuda(), rope)
+    torch.cuda.synchronize()
+    assert device.read_flags() == 0
+    return out.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy(), qd.cpu().numpy()
+
+
+@pytest.mark.parametrize("name,Lc,window", [("dec_full", 37, None), ("dec_win", 37, 9)])
+def test_golden_decode_cases(golden_dir, name, Lc, window):
+    """Same seeds as tests/golden/make_golden.py::attention_fixture (reference: cohere2.attention_cached)."""
+    g = np.load(golden_dir / "attention.npz")
+    H, Hkv, hd = 4, 2, 16
+    r2 = np.random.default_rng(710 + len(name) + Lc)
+    q = r2.integers(-(1 << 19), 1 << 19, size=(1, H, hd), dtype=np.int64)
+    ck = r2.integers(-(1 << 19), 1 << 19, size=(Hkv, Lc, hd), dtype=np.int64)
+    cv = r2.integers(-(1 << 19), 1 << 19, size=(Hkv, Lc, hd), dtype=np.int64)
+    # head_dim 16 is below the kernel's 32-lane split: embed each head in 32 columns of zeros (dot products,
+    # and therefore every byte of the result, are unchanged; inv_sqrt stays that of head_dim 16)
+    import torch
+
+    from integer_inference_engine_b200 import device
+    pad = lambda a: np.concatenate([a, np.zeros(a.shape[:-1] + (16,), np.int64)], axis=-1)
+    qp, ckp, cvp = pad(q), pad(ck), pad(cv)
+    pos = Lc - 1
+    kc = torch.zeros((Hkv, Lc + 2, 32), dtype=torch.int32, device="cuda")
+    vc = torch.zeros_like(kc)
+    kc[:, :pos] = torch.from_numpy(ckp[:, :pos].astype(np.int32)).cuda()
+    vc[:, :pos] = torch.from_numpy(cvp[:, :pos].astype(np.int32)).cuda()
+    out = device.attention_decode(torch.from_numpy(qp.reshape(-1).copy()).cuda(), torch.from_numpy(ckp[:, pos].reshape(-1).copy()).cuda(),
+                                  torch.from_numpy(cvp[:, pos].reshape(-1).copy()).cuda(), kc, vc, pos, H, Hkv, 32, FA, window or 0,
+                                  inv_sqrt=int(round((1.0 / 16 ** 0.5) * (1 << FA))))
+    torch.cuda.synchronize()
+    assert device.read_flags() == 0
+    assert np.array_equal(out.cpu().numpy().reshape(H, 32)[:, :16].reshape(1, -1), g[f"att_{name}"])
+
+
+@pytest.mark.parametrize("H,Hkv,hd,pos,window,rope", [(32, 4, 128, 200, None, 0), (32, 4, 128, 333, 100, 1), (8, 8, 64, 70, None, 2),
+                                                     (32, 8, 128, 0, None, 2), (16, 2, 128, 1100, 1024, 1)])
+def test_decode_attention_matches_the_oracle(H, Hkv, hd, pos, window, rope):
+    rng = np.random.default_rng(H * 7 + pos)
+    Lc = pos + 1
+    q = rng.integers(-(1 << 20), 1 << 20, size=(1, H, hd), dtype=np.int64)
+    k_new = rng.integers(-(1 << 20), 1 << 20, size=(Hkv, 1, hd), dtype=np.int64)
+    ck = rng.integers(-(1 << 20), 1 << 20, size=(Hkv, Lc, hd), dtype=np.int64)       # rows < pos: already rotated keys
+    cv = rng.integers(-(1 << 20), 1 << 20, size=(Hkv, Lc, hd), dtype=np.int64)
+    cos = sin = None
+    q_rot, k_rot = q, k_new
+    if rope:
+        cos, sin = o.build_rope_tables(Lc, hd, 50000.0, FA)
+        at = lambda x: o.rope_fixed(x, cos[pos:pos + 1], sin[pos:pos + 1], FA, neox=rope == 2)
+        q_rot = at(np.transpose(q, (1, 0, 2))).transpose(1, 0, 2)                     # [H,1,hd] rotated at `pos`
+        k_rot = at(k_new)
+    ck_full = ck.copy(); ck_full[:, pos:pos + 1] = k_rot
+    want = o.attention_cached(q_rot, ck_full, cv, pos, H, Hkv, FA, window)
+    ck_in = ck.copy(); ck_in[:, pos:pos + 1] = k_new                                   # the entry rotates the new key itself
+    got, kc, vc, q_after = _run(q, ck_in, cv, pos, H, Hkv, hd, window, rope, cos, sin)
+    assert np.array_equal(q_after.reshape(1, H, hd), q_rot)
+    assert np.array_equal(kc[:, pos], k_rot[:, 0].astype(np.int32)) and np.array_equal(vc[:, pos], cv[:, pos].astype(np.int32))
+    assert np.array_equal(got.reshape(1, -1), want)
+
+
+def test_cache_overflow_is_flagged():
+    import torch
+
+    from integer_inference_engine_b200 import device
+    H, Hkv, hd = 4, 2, 32
+    q = torch.ones(H * hd, dtype=torch.int64, device="cuda")
+    k = torch.ones(Hkv * hd, dtype=torch.int64, device="cuda"); k[3] = 1 << 33
+    v = torch.ones(Hkv * hd, dtype=torch.int64, device="cuda")
+    kc = torch.zeros((Hkv, 4, hd), dtype=torch.int32, device="cuda"); vc = torch.zeros_like(kc)
+    device.attention_decode(q, k, v, kc, vc, 0, H, Hkv, hd, FA)
+    torch.cuda.synchronize()
+    assert device.read_flags() & 4
+
+
+def test_embedding_row_and_argmax():
+    import torch
+
+    from integer_inference_engine_b200 import device, qk_cuda as qk
+    rng = np.random.default_rng(5)
+    for qt, synth in ((o.Q6_K, o.synth_q6k), (o.Q4_K, o.synth_q4k)):
+        raw = synth(rng, 50, 3)
+        h = qk.register_weight(raw, 50, 3, qt)
+        table = o.dequant(raw, 50, 3, qt, FA)
+        for tok in (0, 17, 49):
+            assert np.array_equal(device.embed(h, tok, 768, FA).cpu().numpy()[0], table[tok])
+        tok_dev = torch.tensor([33], dtype=torch.int32, device="cuda")
+        assert np.array_equal(device.embed(h, tok_dev, 768, FA).cpu().numpy()[0], table[33])
+    x = rng.integers(-1000, 1000, size=151936, dtype=np.int64)
+    x[[7, 90000, 151935]] = 5000
+    assert int(device.argmax(torch.from_numpy(x).cuda()).item()) == 7
+    x[:] = -5
+    assert int(device.argmax(torch.from_numpy(x).cuda()).item()) == 0

@@ -128,3 +128,25 @@ def test_balanced_limbs_capacity_and_roundtrip():
     assert np.array_equal(np.asarray(back, dtype=object), x.astype(object))
     with pytest.raises(OverflowError):
         o.limbs_needed(o.balanced_capacity(8) + 1)
+
+
+def test_attention_rope_softmax(golden_dir):
+    """Same seeds as tests/golden/make_golden.py::attention_fixture; outputs are the reference's."""
+    g = np.load(golden_dir / "attention.npz")
+    rng = np.random.default_rng(700)
+    cos, sin = o.build_rope_tables(40, 16, 50000.0, FA)
+    assert np.array_equal(cos, g["rope_cos"]) and np.array_equal(sin, g["rope_sin"])
+    x = rng.integers(-(1 << 22), 1 << 22, size=(3, 40, 16), dtype=np.int64)
+    assert np.array_equal(o.rope_fixed(x, cos, sin, FA), g["rope_inter"])
+    assert np.array_equal(o.rope_fixed(x, cos, sin, FA, neox=True), g["rope_neox"])
+    z = rng.integers(-(1 << 20), 1 << 20, size=(6, 50), dtype=np.int64)
+    z[1, 10:] = -(1 << (FA + 30)); z[2, :] = 7; z[3, 0] = 1 << 40
+    assert np.array_equal(o.softmax_fixed(z, FA), g["softmax"])
+    H, Hkv, hd = 4, 2, 16
+    for name, (Lc, m, window) in {"dec_full": (37, 1, None), "dec_win": (37, 1, 9), "pre_full": (12, 12, None),
+                                  "pre_win": (20, 5, 7)}.items():
+        r2 = np.random.default_rng(710 + len(name) + Lc)
+        q = r2.integers(-(1 << 19), 1 << 19, size=(m, H, hd), dtype=np.int64)
+        ck = r2.integers(-(1 << 19), 1 << 19, size=(Hkv, Lc, hd), dtype=np.int64)
+        cv = r2.integers(-(1 << 19), 1 << 19, size=(Hkv, Lc, hd), dtype=np.int64)
+        assert np.array_equal(o.attention_cached(q, ck, cv, Lc - m, H, Hkv, FA, window), g[f"att_{name}"]), name
