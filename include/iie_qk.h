@@ -156,13 +156,15 @@ int iie_moe_experts_dev(long long layer, const int64_t *h_dev, long long T, cons
  * lives behind qk_attention_bank_apply, north-mini-code/tools/nmc_qk_cuda.cu:1436-1551):
  *   q_dev [n_heads*head_dim], k_dev / v_dev [n_kv*head_dim]  projected rows of the token (q is rotated IN PLACE),
  *   kcache_dev / vcache_dev [n_kv][cache_rows][head_dim] int32, row `pos` is written by this call,
+ *   pos_dev != NULL: the position is read from that device cell when the kernels run and `pos` is only an upper
+ *   bound of it (sizes the grids), so a captured launch sequence can be replayed for successive tokens,
  *   window > 0: only keys pos-window+1 .. pos are visible; otherwise all keys 0 .. pos,
  *   rope 0 none, 1 interleaved pairs, 2 rotate-half pairs; cos_dev / sin_dev [>= pos+1][head_dim/2] int64 at 2^fa,
  *   inv_sqrt = round(2^fa / sqrt(head_dim)) as the caller's model defines it,
  *   out_dev [n_heads*head_dim] = (softmax(scores) v) >> fa.
  * Flag bit 2 is raised when a key or value does not fit the int32 cache. */
 int iie_attn_decode_dev(int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
-                        int32_t *vcache_dev, long long pos, long long window, const int64_t *cos_dev,
+                        int32_t *vcache_dev, long long pos, const int *pos_dev, long long window, const int64_t *cos_dev,
                         const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim, long long cache_rows,
                         int fa, long long inv_sqrt, int64_t *out_dev, void *stream);
 /* Row `token` (or *token_dev when token_dev != NULL) of a registered Q4_K / Q6_K matrix as int64 at 2^frac:

@@ -908,7 +908,7 @@ extern "C" int iie_moe_experts_dev(long long layer, const int64_t *h_dev, long l
 }
 
 extern "C" int iie_attn_decode_dev(int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
-                                   int32_t *vcache_dev, long long pos, long long window, const int64_t *cos_dev,
+                                   int32_t *vcache_dev, long long pos, const int *pos_dev, long long window, const int64_t *cos_dev,
                                    const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim,
                                    long long cache_rows, int fa, long long inv_sqrt, int64_t *out_dev, void *stream) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
@@ -916,7 +916,7 @@ extern "C" int iie_attn_decode_dev(int64_t *q_dev, const int64_t *k_dev, const i
         cache_rows <= 0 || fa < 1 || fa > 29) return 1;
     AttnArgs a = {};
     a.q = q_dev; a.k = k_dev; a.v = v_dev; a.kcache = kcache_dev; a.vcache = vcache_dev; a.pos = pos;
-    a.lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0; a.Lmax = cache_rows;
+    a.pos_dev = pos_dev; a.window = window; a.lo = 0; a.Lmax = cache_rows;
     a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim; a.fa = fa;
     a.inv_sqrt = inv_sqrt; a.log2e = sigmoid_log2e(fa);
     const long long ca = (((long long)(fa + 2)) << (2 * fa)) / a.log2e, cb = ((long long)1 << 62) / a.log2e;

@@ -25,7 +25,16 @@ namespace {
 constexpr int AT_CH = 64;                   // keys per CTA
 constexpr int AT_MAXREP = 16;               // query heads per KV head
 
-__global__ void attn_prep_kernel(const AttnArgs a) {
+// position of the new token and first visible key: from the device cell when the caller replays a captured graph
+__device__ __forceinline__ void at_span(const AttnArgs &a, long long &pos, long long &lo) {
+    pos = a.pos_dev ? (long long)*a.pos_dev : a.pos;
+    lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+}
+
+__global__ void attn_prep_kernel(const AttnArgs a_in) {
+    AttnArgs a = a_in;
+    long long lo_unused;
+    at_span(a_in, a.pos, lo_unused);
     const int tid = threadIdx.x, nth = blockDim.x;
     const int half = a.hd / 2;
     const int64_t *cs = a.cos ? a.cos + a.pos * half : nullptr, *sn = a.sin ? a.sin + a.pos * half : nullptr;
@@ -62,7 +71,9 @@ __global__ void attn_prep_kernel(const AttnArgs a) {
 }
 
 // pass 1: scores of AT_CH keys for the `rep` query heads of one KV head; one warp per key
-__global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
+    AttnArgs a = a_in;
+    at_span(a_in, a.pos, a.lo);
     extern __shared__ long long at_q[];                   // [rep][hd]
     __shared__ long long s_max[AT_MAXREP];
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -101,7 +112,9 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a) {
 }
 
 // pass 2: exponentials and their sum
-__global__ void __launch_bounds__(256) attn_exp_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(256) attn_exp_kernel(const AttnArgs a_in) {
+    AttnArgs a = a_in;
+    at_span(a_in, a.pos, a.lo);
     __shared__ unsigned long long s_sum[8];
     const int h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long l = a.lo + (long long)blockIdx.x * 256 + tid;
@@ -125,12 +138,14 @@ __global__ void __launch_bounds__(256) attn_exp_kernel(const AttnArgs a) {
 }
 
 // pass 3: probabilities x values, partial sums added into acc; the CTA that finishes last shifts and writes out
-__global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
+    AttnArgs a = a_in;
+    at_span(a_in, a.pos, a.lo);
     __shared__ long long s_p[AT_MAXREP][AT_CH];
     __shared__ int s_last;
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x;
     const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
-    const int nk = (int)(l1 - l0);
+    const int nk = (int)max(0LL, l1 - l0);
     for (int i = tid; i < rep * AT_CH; i += blockDim.x) {
         const int r = i / AT_CH, j = i - r * AT_CH;
         long long p = 0;
@@ -233,9 +248,12 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const int64_t *x, long lon
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
     const int rep = a.Hkv > 0 ? a.H / a.Hkv : 0;
     if (a.H <= 0 || a.Hkv <= 0 || a.H % a.Hkv || rep > AT_MAXREP || (a.hd > 0 && a.hd <= 256 && rep > (256 / a.hd) * (AT_MAXREP / 2)) || a.hd < 32 || a.hd > 256 || a.hd % 32 || 256 % a.hd ||
-        a.pos < 0 || a.pos >= a.Lmax || a.lo < 0 || a.lo > a.pos || a.fa < 1 || a.fa > 29 || (a.rope && (!a.cos || !a.sin)))
+        a.pos < 0 || a.pos >= a.Lmax || a.fa < 1 || a.fa > 29 || (a.rope && (!a.cos || !a.sin)))
         return cudaErrorInvalidValue;
-    const long long n_keys = a.pos - a.lo + 1;
+    // a.pos is the position itself, or with pos_dev an upper bound of it: the grids cover the largest key span
+    const long long lo_min = (a.window > 0 && !a.pos_dev && a.pos - a.window + 1 > 0) ? a.pos - a.window + 1 : 0;
+    long long n_keys = a.pos - lo_min + 1;
+    if (a.window > 0 && n_keys > a.window) n_keys = a.window;
     const unsigned chunks = (unsigned)((n_keys + AT_CH - 1) / AT_CH);
     attn_prep_kernel<<<1, 512, 0, s>>>(a);
     attn_scores_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)rep * a.hd * 8, s>>>(a);

@@ -200,7 +200,10 @@ struct AttnArgs {
     int64_t *q;                    // [H*hd] projected query, rotated in place
     const int64_t *k, *v;          // [Hkv*hd] projected key / value of the new token
     int32_t *kcache, *vcache;      // [Hkv][Lmax][hd]
-    long long pos, lo, Lmax;       // position of the new token, first visible key, cache rows
+    long long pos, lo, Lmax;       // position of the new token (an upper bound when pos_dev is set), first visible key
+                                   // (computed on the device), cache rows
+    const int *pos_dev;            // optional: the position in device memory (for replayed graphs)
+    long long window;              // > 0: only the last `window` keys are visible
     const int64_t *cos, *sin;      // [>= pos+1][hd/2] at 2^fa, or nullptr when rope == 0
     int rope;                      // 0 none, 1 interleaved pairs (2i, 2i+1), 2 rotate-half pairs (i, i + hd/2)
     int H, Hkv, hd, fa;

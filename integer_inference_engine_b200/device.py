@@ -48,12 +48,14 @@ def export_weight(handle: int, out_f: int, n_blocks: int, qtype: int) -> np.ndar
     return buf
 
 
-def apply(handle: int, x: torch.Tensor, out_f: int, fw: int) -> torch.Tensor:
+def apply(handle: int, x: torch.Tensor, out_f: int, fw: int, out: torch.Tensor | None = None) -> torch.Tensor:
     """out [T,out_f] = floor(x W^T / 2^fw) for a registered weight, on the current stream."""
     lib = qk_cuda._lib()
     x = x.contiguous()
     assert x.is_cuda and x.dtype == torch.int64 and x.dim() == 2
-    out = torch.empty((x.shape[0], out_f), dtype=torch.int64, device=x.device)
+    if out is None:
+        out = torch.empty((x.shape[0], out_f), dtype=torch.int64, device=x.device)
+    assert out.is_contiguous() and out.numel() == x.shape[0] * out_f
     with _CUDA_LOCK:
         rc = lib.iie_apply_dev(int(handle), x.data_ptr(), x.shape[0], int(fw), out.data_ptr(), _stream_ptr())
     if rc != 0:
@@ -79,9 +81,11 @@ def rmsnorm(x: torch.Tensor, gain_handle: int = -1, fa: int = 16, eps: int = 1, 
 def attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                      pos: int, n_heads: int, n_kv: int, head_dim: int, fa: int = 16, window: int = 0,
                      cos: torch.Tensor | None = None, sin: torch.Tensor | None = None, rope: int = 0,
-                     inv_sqrt: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+                     inv_sqrt: int | None = None, out: torch.Tensor | None = None,
+                     pos_dev: torch.Tensor | None = None) -> torch.Tensor:
     """One new token's GQA attention over the int32 caches ``[n_kv, rows, head_dim]``; writes cache row ``pos``
-    and rotates ``q`` in place.  Returns ``[n_heads * head_dim]`` int64."""
+    and rotates ``q`` in place.  With ``pos_dev`` (CUDA int32 [1]) the position is read on the device and ``pos``
+    is an upper bound (for replayed graphs).  Returns ``[n_heads * head_dim]`` int64."""
     lib = qk_cuda._lib()
     assert q.is_cuda and q.dtype == torch.int64 and q.is_contiguous() and q.numel() == n_heads * head_dim
     assert k.dtype == torch.int64 and v.dtype == torch.int64 and k.numel() == n_kv * head_dim == v.numel()
@@ -93,7 +97,8 @@ def attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kcache: 
         out = torch.empty(n_heads * head_dim, dtype=torch.int64, device=q.device)
     with _CUDA_LOCK:
         rc = lib.iie_attn_decode_dev(q.data_ptr(), k.contiguous().data_ptr(), v.contiguous().data_ptr(), kcache.data_ptr(),
-                                     vcache.data_ptr(), int(pos), int(window or 0), cos.data_ptr() if rope else None,
+                                     vcache.data_ptr(), int(pos), pos_dev.data_ptr() if pos_dev is not None else None,
+                                     int(window or 0), cos.data_ptr() if rope else None,
                                      sin.data_ptr() if rope else None, int(rope), n_heads, n_kv, head_dim,
                                      int(kcache.shape[1]), int(fa), int(inv_sqrt), out.data_ptr(), _stream_ptr())
     if rc != 0:

@@ -108,7 +108,7 @@ def load_library():
         "iie_rmsnorm_dev": ([i64, vp, i64, i64, c_int, u64, vp, vp], c_int),
         "iie_profile_stage_mask": ([c_int], None), "iie_launch_count": ([], u64), "iie_set_pdl": ([c_int], None),
         "iie_set_tc_min_tokens": ([i64], None), "iie_set_fused_expert": ([c_int], None), "iie_expert_clusters": ([], c_int), "iie_set_fused_route": ([c_int], None),
-        "iie_attn_decode_dev": ([vp, vp, vp, vp, vp, i64, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, i64, vp, vp], c_int),
+        "iie_attn_decode_dev": ([vp, vp, vp, vp, vp, i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, i64, vp, vp], c_int),
         "iie_embed_dev": ([i64, vp, i64, c_int, vp, vp], c_int), "iie_argmax_dev": ([vp, i64, vp, vp], c_int),
         "iie_route_dev": ([i64, c_int, vp, i64, c_int, c_int, vp, vp, vp], c_int),
         "iie_moe_experts_dev": ([i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, c_int, vp, vp], c_int),
