@@ -1,22 +1,26 @@
-"""Benchmark of the integer MoE decode path on B200.
+"""Benchmark of the integer decode path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|prefill|ep_decode|q1]
 
-One step = one decoded token pushed through every MoE block of the synthetic 30B-A3B-shaped model
-(48 blocks; d=2048, 128 experts, top-8, expert width 768; Q4_K router/gate/up, Q6_K down):
-RMSNorm -> router product -> top-8 + sigmoid gates -> gate/up products with fused integer SiLU ->
-down product with fused gate-weighted combine -> residual add.  Weights are seeded synthetic blocks
-generated on the device; a step streams 1.18 GB of distinct weights, far above the 126 MB L2.
+Default workload, one step = one greedily decoded token of the synthetic 30B-A3B-shaped model at context 4096:
+embedding row -> 48 blocks (RMSNorm, Q/K/V products, RoPE on sliding-window blocks, KV-cache append, exact
+integer softmax attention, O product, MoE block: router, top-8 + sigmoid gates, gate/up with fused integer SiLU,
+down with fused gate-weighted combine; x += attention + moe) -> output norm -> tied head over 151936 tokens ->
+arg-max.  Weights are seeded synthetic blocks generated on the device; the KV cache is filled with seeded int32
+values in place of a prefill.  A step streams 1.9 GB of distinct weights and 0.8 GB of cache, far above the
+126 MB L2.
 
-Printed JSON line (rank 0): `value` = tokens/s with the token's hidden state already on the device
-(the whole 48-block step is one CUDA graph); `e2e` = the same through the host-buffer C-ABI call
-(one call per block, upload and download inside the timed region); `roofline` = the gate/up kernel
-timed alone with CUDA events against the measured HBM copy bandwidth; `cpu_baseline` = the CPU
-oracle on this box's host cores for a bounded sample.  Before timing, every block's router ids and
-output are compared byte for byte with the CPU oracle.
+Printed JSON line (rank 0): `value` = tokens/s of the device-resident greedy chain (token id and position stay in
+device cells; one CUDA-graph replay per token); `e2e` = the same through the public per-token call with the
+token id going in and coming out through pinned host buffers; `roofline` = the MoE gate/up kernel (largest single
+consumer of the step) timed alone with CUDA events against the measured HBM copy bandwidth; `cpu_baseline` = the
+CPU oracle on this box's host cores for a bounded sample; `config.moe_blocks_only` = the 48 MoE blocks alone.
+Before timing, every stage of one token (embedding, norms, projections, cache row, attention, MoE routing and
+output of every block, head logits, pick) is compared byte for byte with the CPU oracle, and the graph replay is
+compared with the eager chain.
 
-`--impl reference` times the reference project's compiled CPU kernel (oracle/_ref) composed the way
-its engine composes the MoE block on the CPU, on a bounded sample per step.
+`--impl reference` times the reference project's compiled CPU kernel (oracle/_ref) composed the way its engine
+composes a decode step on the CPU, on a bounded sample per step.
 """
 from __future__ import annotations
 
@@ -36,7 +40,11 @@ sys.path.insert(0, str(ROOT))
 
 FA, FW = 16, 24
 D_MODEL, E_FFN, N_EXPERTS, TOP_K = 2048, 768, 128, 8
-WORKLOAD = "config2_moe_decode: batch-1 decode, 48 MoE blocks (d=2048, 128 experts, top-8, eff=768, Q4_K/Q6_K)"
+N_HEADS, N_KV, HEAD_DIM, VOCAB, WINDOW = 32, 4, 128, 151936, 4096
+GATEUP_DRAM_BYTES_NCU = 14200000          # dram read+write of one gate/up launch (ncu capture of this workload's kernel)
+WORKLOAD = ("config2_decode: batch-1 KV-cached greedy decode of the 30B-A3B-shaped model, 48 blocks (RMSNorm, Q/K/V, RoPE on "
+            "sliding-window blocks, int32 KV cache at context 4096, exact integer softmax attention, O, MoE with 128 experts "
+            "top-8 eff 768), tied Q6_K head over 151936 tokens, arg-max; Q4_K weights, Q6_K down and head")
 
 
 def parse():
@@ -47,7 +55,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--verify-layers", type=int, default=48, help="blocks checked against the CPU oracle before timing")
-    ap.add_argument("--cpu-sample-layers", type=int, default=4)
+    ap.add_argument("--cpu-sample-layers", type=int, default=2)
+    ap.add_argument("--context", type=int, default=4096, help="KV-cache rows already filled when decoding starts")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep_decode", "q1"],
                     help="decode = the headline line (batch-1 MoE decode); the others print a line of the same "
@@ -166,6 +175,39 @@ def cpu_moe_block_time(kind: str, n_layers: int, repeats: int, seed: int = 1):
     return float(np.median(times))
 
 
+def cpu_token_time(kind: str, n_layers: int, repeats: int, context: int, seed: int = 1):
+    """CPU time of a decode step, split as (seconds per block, seconds for the head): per sampled block the four
+    attention projections and the MoE block (reference-built kernel or the C oracle), NumPy integer attention over
+    `context` cached keys as north-mini-code/src/nmc/cohere2.py:324-354, and once the tied head product."""
+    from oracle import native as onat
+    from oracle import qk_oracle as o
+    rng = np.random.default_rng(seed)
+    nb = D_MODEL // 256
+    lin = onat.ref_qk_linear if kind == "reference" else onat.qk_linear
+    wq = o.synth_q4k(rng, N_HEADS * HEAD_DIM, nb); wk = o.synth_q4k(rng, N_KV * HEAD_DIM, nb); wv = o.synth_q4k(rng, N_KV * HEAD_DIM, nb)
+    wo = o.synth_q4k(rng, D_MODEL, N_HEADS * HEAD_DIM // 256)
+    ck = rng.integers(-(1 << 18), 1 << 18, size=(N_KV, context + 1, HEAD_DIM), dtype=np.int64)
+    cv = rng.integers(-(1 << 18), 1 << 18, size=(N_KV, context + 1, HEAD_DIM), dtype=np.int64)
+    h = o.to_fixed(rng.standard_normal((1, D_MODEL)), FA)
+    cos, sin = o.build_rope_tables(1, HEAD_DIM, 50000.0, FA)
+
+    def attn_part():
+        q = lin(wq, h, N_HEADS * HEAD_DIM, nb, FW, o.Q4_K).reshape(1, N_HEADS, HEAD_DIM)
+        k = lin(wk, h, N_KV * HEAD_DIM, nb, FW, o.Q4_K).reshape(1, N_KV, HEAD_DIM)
+        v = lin(wv, h, N_KV * HEAD_DIM, nb, FW, o.Q4_K).reshape(1, N_KV, HEAD_DIM)
+        q = o.rope_fixed(np.transpose(q, (1, 0, 2)), cos, sin, FA).transpose(1, 0, 2)
+        ck[:, context] = o.rope_fixed(np.transpose(k, (1, 0, 2)), cos, sin, FA)[:, 0]; cv[:, context] = v[0]
+        att = o.attention_cached(q, ck, cv, context, N_HEADS, N_KV, FA, WINDOW)
+        return lin(wo, att, D_MODEL, N_HEADS * HEAD_DIM // 256, FW, o.Q4_K)
+    moe_s = cpu_moe_block_time(kind, n_layers, repeats, seed)
+    ts = []
+    for _ in range(repeats):
+        t0 = time.perf_counter(); attn_part(); ts.append(time.perf_counter() - t0)
+    embd = o.synth_q6k(rng, VOCAB, nb)
+    t0 = time.perf_counter(); lin(embd, h, VOCAB, nb, FW, o.Q6_K); head_s = time.perf_counter() - t0
+    return moe_s + float(np.median(ts)), head_s
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -176,13 +218,15 @@ def run_reference(args):
     for _ in range(max(args.warmup, 1) - 1):
         cpu_moe_block_time(kind, n_layers, 1)
     t0 = time.perf_counter()
-    per_layer = cpu_moe_block_time(kind, n_layers, max(args.steps, 1))
+    per_layer, head_s = cpu_token_time(kind, n_layers, max(args.steps, 1), args.context)
     wall = time.perf_counter() - t0
-    value = 1.0 / (per_layer * args.layers)
-    sample = f"{n_layers} blocks x 1 token per step, scaled to {args.layers} blocks"
+    step_s = per_layer * args.layers + head_s
+    value = 1.0 / step_s
+    sample = (f"{n_layers} blocks (4 projections, attention over {args.context} keys, MoE block) and the head per step, "
+              f"scaled to {args.layers} blocks")
     print(json.dumps({
         "impl": "reference", "metric": "decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_layer * args.layers * 1e3,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
         "config": {"workload": WORKLOAD, "l2": "n/a (CPU)"},
         "cpu_baseline": {"value": value, "unit": "tok/s", "cores": host_cores(), "kind": kind, "sample": sample},
@@ -192,46 +236,96 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------------------------- our arm ---
-def verify_against_oracle(stack, x0, n_check: int):
-    """Eager pass over the blocks; each checked block's ids, gates and output against the C oracle,
-    using the weights exported back from the device."""
+def check_moe_block(stack, li, hn, ids, gates, out):
+    """One block's routing and output against the C oracle, using the weights exported back from the device."""
+    from integer_inference_engine_b200 import device
+    from oracle import native as onat
+    from oracle import qk_oracle as o
+    nb_in, nb_dn = D_MODEL // 256, E_FFN // 256
+    hs = stack.handles[li]
+    router = device.export_weight(hs["router"], N_EXPERTS, nb_in, o.Q4_K)
+    logits = onat.qk_linear(router, hn, N_EXPERTS, nb_in, FW, o.Q4_K)
+    sel = np.stack([onat.topk_lowidx(r, TOP_K) for r in logits])
+    assert np.array_equal(ids, sel), f"block {li}: router ids"
+    gref = np.stack([onat.sigmoid(logits[t][sel[t]], FA) for t in range(sel.shape[0])])
+    assert np.array_equal(gates, gref), f"block {li}: gates"
+    ref = np.zeros((hn.shape[0], D_MODEL), dtype=object)
+    for t in range(hn.shape[0]):
+        for j, e in enumerate(sel[t]):
+            gw = device.export_weight(hs["gate"][e], E_FFN, nb_in, o.Q4_K)
+            uw = device.export_weight(hs["up"][e], E_FFN, nb_in, o.Q4_K)
+            dw = device.export_weight(hs["down"][e], D_MODEL, nb_dn, o.Q6_K)
+            g = onat.silu(onat.qk_linear(gw, hn[t:t + 1], E_FFN, nb_in, FW, o.Q4_K), FA)
+            u = onat.qk_linear(uw, hn[t:t + 1], E_FFN, nb_in, FW, o.Q4_K)
+            dn = onat.qk_linear(dw, o.mul_shift(g, u, FA), D_MODEL, nb_dn, FW, o.Q6_K)[0].astype(object)
+            ref[t] += (dn * int(gref[t, j])) >> FA
+    assert np.array_equal(out, ref.astype(np.int64)), f"block {li}: block output"
+
+
+def verify_token(model, token: int, n_check: int):
+    """Eager walk of one decode step; every stage of the first `n_check` blocks, the head and the pick are compared
+    with the CPU oracle fed with the SAME stage inputs (exported weights, host copies of the caches)."""
     import torch
 
     from integer_inference_engine_b200 import device
     from oracle import native as onat
     from oracle import qk_oracle as o
-    nb_in, nb_dn = D_MODEL // 256, E_FFN // 256
-    x = x0.clone()
+    d, H, Hkv, hd, nb = model.d, model.H, model.Hkv, model.hd, model.d // 256
+    pos = int(model.pos.item())
+    cos, sin = model.cos[pos:pos + 1].cpu().numpy(), model.sin[pos:pos + 1].cpu().numpy()
+    embd_raw = device.export_weight(model.embd, model.vocab, nb, o.Q6_K) if n_check > 0 else None
+    x = device.embed(model.embd, token, d, FA)
+    if n_check > 0:
+        row = embd_raw[token * nb * 210:(token + 1) * nb * 210]
+        assert np.array_equal(x.cpu().numpy()[0], o.dequant(row, 1, nb, o.Q6_K, FA)[0]), "embedding row"
     checked = 0
-    for li, layer in enumerate(stack.layers):
-        hs = stack.handles[li]
-        h = device.rmsnorm(x, hs["gain_h"], FA, 1)
-        out, ids, gates = layer.forward(h, FA, FW)
+    for li in range(model.n_layers):
+        a, gain_h = model.attn[li], model.moe.gains[li]
+        full = model.layer_is_full(li)
+        h = device.rmsnorm(x, gain_h, FA, 1)
+        qr, kr = H * hd, Hkv * hd
+        qkv = device.apply(a["wqkv"], h, qr + 2 * kr, FW)
+        q_in, k, v = qkv[:, :qr].contiguous(), qkv[:, qr:qr + kr].contiguous(), qkv[:, qr + kr:].contiguous()
+        att = device.attention_decode(q_in.view(-1), k.view(-1), v.view(-1), a["k"], a["v"], pos, H, Hkv, hd, FA,
+                                      0 if full else model.window, model.cos, model.sin, 0 if full else 1).view(1, -1)
+        ao = device.apply(a["wo"], att, d, FW)
+        out, ids, gates = model.moe.layers[li].forward(h, FA, FW)
+        # the two block entries the timed step uses (MoE half, then attention half) on a copy of the row
+        xb = x.clone()
+        model.moe.layers[li].block(xb, gain_h, FA, FW, 1, out=xb, want_routes=False)
+        device.attention_block(a["wqkv"], a["wo"], xb, a["k"], a["v"], pos, H, Hkv, hd, FA, FW, 0 if full else model.window,
+                               model.cos, model.sin, 0 if full else 1)
         torch.cuda.synchronize()
         assert device.read_flags() == 0, f"block {li}: envelope flag raised"
+        assert torch.equal(xb, x + ao + out), f"block {li}: block entries differ from the stage-by-stage composition"
         if li < n_check:
             xn, hn = x.cpu().numpy(), h.cpu().numpy()
-            assert np.array_equal(hn, o.rmsnorm_fixed(xn, FA, 1, hs["gain"].cpu().numpy())), f"block {li}: RMSNorm"
-            router = device.export_weight(hs["router"], N_EXPERTS, nb_in, o.Q4_K)
-            logits = onat.qk_linear(router, hn, N_EXPERTS, nb_in, FW, o.Q4_K)
-            sel = np.stack([onat.topk_lowidx(r, TOP_K) for r in logits])
-            assert np.array_equal(ids.cpu().numpy(), sel), f"block {li}: router ids"
-            gref = np.stack([onat.sigmoid(logits[t][sel[t]], FA) for t in range(sel.shape[0])])
-            assert np.array_equal(gates.cpu().numpy(), gref), f"block {li}: gates"
-            ref = np.zeros((xn.shape[0], D_MODEL), dtype=object)
-            for t in range(xn.shape[0]):
-                for j, e in enumerate(sel[t]):
-                    gw = device.export_weight(hs["gate"][e], E_FFN, nb_in, o.Q4_K)
-                    uw = device.export_weight(hs["up"][e], E_FFN, nb_in, o.Q4_K)
-                    dw = device.export_weight(hs["down"][e], D_MODEL, nb_dn, o.Q6_K)
-                    g = onat.silu(onat.qk_linear(gw, hn[t:t + 1], E_FFN, nb_in, FW, o.Q4_K), FA)
-                    u = onat.qk_linear(uw, hn[t:t + 1], E_FFN, nb_in, FW, o.Q4_K)
-                    dn = onat.qk_linear(dw, o.mul_shift(g, u, FA), D_MODEL, nb_dn, FW, o.Q6_K)[0].astype(object)
-                    ref[t] += (dn * int(gref[t, j])) >> FA
-            assert np.array_equal(out.cpu().numpy(), ref.astype(np.int64)), f"block {li}: block output"
+            assert np.array_equal(hn, o.rmsnorm_fixed(xn, FA, 1, model.moe.handles[li]["gain"].cpu().numpy())), f"block {li}: RMSNorm"
+            w = device.export_weight(a["wqkv"], qr + 2 * kr, nb, o.Q4_K)
+            assert np.array_equal(qkv.cpu().numpy(), onat.qk_linear(w, hn, qr + 2 * kr, nb, FW, o.Q4_K)), f"block {li}: fused QKV"
+            qn, kn = q_in.cpu().numpy().reshape(1, H, hd), k.cpu().numpy().reshape(1, Hkv, hd)
+            if not full:
+                rot = lambda t: o.rope_fixed(np.transpose(t, (1, 0, 2)), cos, sin, FA).transpose(1, 0, 2)
+                qn, kn = rot(qn), rot(kn)
+            lo = 0 if full else max(0, pos - model.window + 1)
+            ck = a["k"][:, :pos + 1].cpu().numpy().astype(np.int64); cv = a["v"][:, :pos + 1].cpu().numpy().astype(np.int64)
+            assert np.array_equal(ck[:, pos], kn[0]) and np.array_equal(cv[:, pos], v.cpu().numpy().reshape(Hkv, hd)), f"block {li}: cache row"
+            want = o.attention_cached(qn, ck, cv, pos, H, Hkv, FA, None if full else model.window)
+            assert np.array_equal(att.cpu().numpy(), want), f"block {li}: attention (keys {lo}..{pos})"
+            wo = device.export_weight(a["wo"], d, H * hd // 256, o.Q4_K)
+            assert np.array_equal(ao.cpu().numpy(), onat.qk_linear(wo, att.cpu().numpy(), d, H * hd // 256, FW, o.Q4_K)), f"block {li}: wo"
+            check_moe_block(model.moe, li, hn, ids.cpu().numpy(), gates.cpu().numpy(), out.cpu().numpy())
             checked += 1
-        x = x + out
-    return checked, x
+        x = x + ao + out
+    hn = device.rmsnorm(x, model.out_gain_h, FA, 1)
+    logits = device.apply(model.embd, hn, model.vocab, FW)
+    tok = int(device.argmax(logits.view(-1)).item())
+    if n_check > 0:
+        assert np.array_equal(hn.cpu().numpy(), o.rmsnorm_fixed(x.cpu().numpy(), FA, 1, model.out_gain.cpu().numpy())), "output norm"
+        want = onat.qk_linear(embd_raw, hn.cpu().numpy(), model.vocab, nb, FW, o.Q6_K)[0]
+        assert np.array_equal(logits.cpu().numpy()[0], want), "head logits"
+        assert tok == int(np.flatnonzero(want == want.max())[0]), "greedy pick"
+    return checked, tok
 
 
 def run_ours(args):
@@ -239,8 +333,7 @@ def run_ours(args):
     import torch.distributed as dist
 
     from integer_inference_engine_b200 import device, qk_cuda
-    from integer_inference_engine_b200.synth import SyntheticMoEStack
-    from oracle import qk_oracle as o
+    from integer_inference_engine_b200.model import SyntheticDecoder
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -250,36 +343,36 @@ def run_ours(args):
     if not qk_cuda.available():
         raise SystemExit("CUDA library or GPU missing: there is no fallback path")
 
-    stack = SyntheticMoEStack(args.layers, D_MODEL, E_FFN, N_EXPERTS, TOP_K, seed=1 + rank, fa=FA)
-    # per-step inputs: a small table of hidden states standing in for embedding rows of sampled tokens
-    rng = np.random.default_rng(1000 + rank)
-    table_host = o.to_fixed(rng.standard_normal((16, D_MODEL)), FA)
-    table = torch.from_numpy(table_host).cuda()
-    pinned_in = torch.from_numpy(table_host).pin_memory()
+    n_e2e = 0 if args.no_e2e else max(2, min(args.steps, 16))
+    total_steps = args.warmup + args.steps + n_e2e + 24
+    model = SyntheticDecoder(n_layers=args.layers, d_model=D_MODEL, n_heads=N_HEADS, n_kv=N_KV, head_dim=HEAD_DIM, e_ffn=E_FFN,
+                             n_experts=N_EXPERTS, top_k=TOP_K, vocab=VOCAB, context=args.context, max_new=total_steps + 8,
+                             window=WINDOW, seed=1 + rank, fa=FA, fw=FW)
+    stack = model.moe
+    first_token = 1234 + rank
+    pos0 = model.context
+    pos_bound = pos0 + total_steps
 
-    checked, _ = verify_against_oracle(stack, table[:1], args.verify_layers if rank == 0 else 0)
-
-    # ---- device-resident timing: one CUDA graph per token -------------------------------------------------
-    x_static = table[:1].clone()
-    stack.decode_step(x_static.clone(), FW)                     # sizes every workspace before capture
-    torch.cuda.synchronize()
+    # ---- parity before timing: every stage of one token, then graph replay == eager chain --------------------------
+    checked, _ = verify_token(model, first_token, args.verify_layers if rank == 0 else 0)
+    model.token.fill_(first_token)
+    eager_ids = []
+    for i in range(3):
+        model.step(pos0 + i)
+        eager_ids.append(int(model.token.item()))
+    model.token.fill_(first_token); model.pos.fill_(pos0)
     l0 = device.launch_count()
-    side = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(side):
-        x_work = x_static.clone()
-        with torch.cuda.graph(graph, stream=side):
-            x_work.copy_(x_static)
-            stack.decode_step(x_work, FW)
-    launches_per_step = device.launch_count() - l0
-    torch.cuda.synchronize()
+    model.capture(pos_bound)
+    launches_per_step = (device.launch_count() - l0) // 2         # capture() runs the step twice
+    replay_ids = []
+    for i in range(3):
+        model.replay()
+        replay_ids.append(int(model.token.item()))
+    assert replay_ids == eager_ids, f"graph replay {replay_ids} differs from the eager chain {eager_ids}"
 
-    def step(i):
-        x_static.copy_(table[i % 16:i % 16 + 1])
-        graph.replay()
-
+    # ---- device-resident timing: the greedy chain continues, one graph replay per token ----------------------------
     for i in range(args.warmup):
-        step(i)
+        model.replay()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -288,7 +381,7 @@ def run_ours(args):
     with ClockSampler(local) as clk:
         ev0.record()
         for i in range(args.steps):
-            step(args.warmup + i)
+            model.replay()
         ev1.record()
         torch.cuda.synchronize()
     ms = ev0.elapsed_time(ev1)
@@ -297,13 +390,29 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     assert device.read_flags() == 0, "an activation left the exact envelope during the timed region"
-    # the graph result equals the eager, oracle-checked chain for the same input
-    step(0); torch.cuda.synchronize()
-    _, x_ref = verify_against_oracle(stack, table[:1], 0)
-    assert torch.equal(x_work, x_ref), "graph replay differs from the oracle-checked eager chain"
+    pos_timed = int(model.pos.item())
 
-    # ---- roofline of the dominant kernel (gate/up), timed alone over all blocks' weights -----------------
+    # ---- the MoE blocks alone (the hot path of this build) and the roofline of its dominant kernel --------------------
     peak, peak_kind = measured_peak_gbs()
+    rng = np.random.default_rng(1000 + rank)
+    from oracle import qk_oracle as o
+    table = torch.from_numpy(o.to_fixed(rng.standard_normal((4, D_MODEL)), FA)).cuda()
+    side = torch.cuda.Stream()
+    x_moe = table[:1].clone()
+    stack.decode_step(x_moe.clone(), FW)
+    torch.cuda.synchronize()
+    g_moe = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g_moe, stream=side):
+            stack.decode_step(x_moe, FW)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g_moe.replay(); torch.cuda.synchronize()
+    e0.record()
+    for _ in range(8):
+        g_moe.replay()
+    e1.record(); torch.cuda.synchronize()
+    moe_only_ms = e0.elapsed_time(e1) / 8
     h_probe = device.rmsnorm(table[:1], stack.gains[0], FA, 1)
     outs = torch.zeros_like(h_probe)
     for layer in stack.layers:                                   # leaves ids/gates/limbs of the last block in place
@@ -332,69 +441,64 @@ def run_ours(args):
         device.read_flags()
         return e0.elapsed_time(e1) / (reps * len(stack.layers))
 
-    route_ms, gateup_ms, down_ms, expert_ms = time_stage(2), time_stage(8), time_stage(16), time_stage(24)
+    route_ms, gateup_ms, down_ms = time_stage(2), time_stage(8), time_stage(16)
     gateup_bytes = TOP_K * 2 * E_FFN * (D_MODEL // 256) * 144
     down_bytes = TOP_K * D_MODEL * (E_FFN // 256) * 210
-    fused = launches_per_step == 2 * args.layers          # routing + one cluster launch per block
-    if fused:
-        dom_name, dom_bytes, dom_ms = "expert_kernel<Q4_K, Q6_K> (gate/up + SiLU*up + down + combine)", gateup_bytes + down_bytes, expert_ms
-    else:
-        dom_name, dom_bytes, dom_ms = "stream_kernel<Q4_K, GATEUP>", gateup_bytes, gateup_ms
-    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+    achieved = gateup_bytes / (gateup_ms * 1e-3) / 1e9
 
-    # ---- end to end through the host-buffer C-ABI call ----------------------------------------------------
+    # ---- end to end: the public per-token call, token id in and out through pinned host buffers -----------------------
     e2e = None
-    if not args.no_e2e:
-        def host_step(i):
-            x = pinned_in[i % 16:i % 16 + 1].numpy()
-            for li, layer in enumerate(stack.layers):
-                res = qk_cuda.moe_block(layer.handle, x, TOP_K, FA, FW, gain_handle=stack.gains[li])
-                assert res is not None
-                x = res[0]
-            return x
-        got = host_step(0)
-        assert np.array_equal(got, x_ref.cpu().numpy()), "host-buffer path differs from the device path"
-        n_e2e = max(2, min(args.steps, 8))
+    if n_e2e:
+        tok_in = torch.zeros(1, dtype=torch.int32).pin_memory()
+        tok_out = torch.zeros(1, dtype=torch.int32).pin_memory()
+        tok_in[0] = int(model.token.item())
+        model.decode_token(tok_in, tok_out)                       # untimed first call
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for i in range(n_e2e):
-            host_step(i)
+            tok_in[0] = tok_out[0]
+            model.decode_token(tok_in, tok_out)
         e2e_s = (time.perf_counter() - t0) / n_e2e
         if world > 1:
             t = torch.tensor([e2e_s], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e2e_s = float(t.item())
-        e2e = {"value": world / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": args.layers * D_MODEL * 8,
-               "d2h_bytes_per_step": args.layers * (D_MODEL * 8 + TOP_K * 12), "steps": n_e2e}
+        e2e = {"value": world / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4, "steps": n_e2e}
+    assert device.read_flags() == 0
 
     if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
         return
     cpu = None
     if args.cpu_sample_layers > 0:
         n_cpu = min(args.cpu_sample_layers, args.layers)
-        per_layer = cpu_moe_block_time("port", n_cpu, 3)
-        cpu = {"value": 1.0 / (per_layer * args.layers), "unit": "tok/s", "cores": host_cores(), "kind": "port",
-               "sample": f"{n_cpu} blocks x 1 token, median of 3, scaled to {args.layers} blocks"}
+        per_layer, head_s = cpu_token_time("port", n_cpu, 3, args.context)
+        cpu = {"value": 1.0 / (per_layer * args.layers + head_s), "unit": "tok/s", "cores": host_cores(), "kind": "port",
+               "sample": f"{n_cpu} blocks (attention over {args.context} keys + MoE) and the head, 1 token, median of 3, "
+                         f"scaled to {args.layers} blocks"}
     ms_step = ms / args.steps
-    bytes_tok = stack.weight_bytes_per_token()
+    w_bytes, kv_bytes = model.weight_bytes_per_token(), model.kv_bytes_per_token(pos_timed)
     print(json.dumps({
         "metric": "decode_tok_per_s", "value": world * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers": args.layers, "parallelism": f"replicas x{world}",
-                   "l2": "inputs larger than L2: each step streams %d MB of distinct weights" % (bytes_tok // 2**20),
-                   "weight_bytes_per_token": bytes_tok, "step_hbm_frac_of_%s_peak" % peak_kind:
-                       bytes_tok / (ms_step * 1e-3) / 1e9 / peak,
-                   "oracle_checked_blocks": checked},
+        "config": {"workload": WORKLOAD, "layers": args.layers, "context": args.context, "parallelism": f"replicas x{world}",
+                   "l2": "inputs larger than L2: each step streams %d MB of distinct weights and %d MB of KV cache"
+                         % (w_bytes // 2**20, kv_bytes // 2**20),
+                   "weight_bytes_per_token": w_bytes, "kv_bytes_per_token": kv_bytes,
+                   "step_hbm_frac_of_%s_peak" % peak_kind: (w_bytes + kv_bytes) / (ms_step * 1e-3) / 1e9 / peak,
+                   "moe_blocks_only": {"ms_per_token": moe_only_ms, "tok_per_s": 1e3 / moe_only_ms,
+                                       "weight_bytes": stack.weight_bytes_per_token()},
+                   "oracle_checked_blocks": checked, "kv_cache": "seeded int32 values stand in for the prefill"},
         "clocks": clk.summary(),
         "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps),
-        "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak,
-                     "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                     "bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
-                     "other_kernels_us": {"route": route_ms * 1e3, "gateup_alone": gateup_ms * 1e3, "down_alone": down_ms * 1e3,
-                                          "expert_stage": expert_ms * 1e3,
-                                          "gateup_alone_frac": gateup_bytes / (gateup_ms * 1e-3) / 1e9 / peak,
-                                          "down_alone_frac": down_bytes / (down_ms * 1e-3) / 1e9 / peak}},
+        "roofline": {"bound": "hbm", "kernel": "stream_kernel<Q4_K, GATEUP>", "achieved": achieved, "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": GATEUP_DRAM_BYTES_NCU,
+                     "traffic_source": "ncu dram__bytes_read+write of one launch, profiles/stream_kernel_gateup_decode.md",
+                     "bytes_per_launch": gateup_bytes, "ms_per_launch": gateup_ms,
+                     "other_kernels_us": {"route": route_ms * 1e3, "down": down_ms * 1e3,
+                                          "down_frac": down_bytes / (down_ms * 1e-3) / 1e9 / peak}},
         "cpu_baseline": cpu,
     }))
     if world > 1:

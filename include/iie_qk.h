@@ -154,7 +154,7 @@ int iie_moe_experts_dev(long long layer, const int64_t *h_dev, long long T, cons
 /* Attention of ONE new token over an int32 KV cache, on device tensors (the arithmetic of
  * north-mini-code/src/nmc/cohere2.py:324-354 attention_cached with m = 1; in the reference's CUDA library this
  * lives behind qk_attention_bank_apply, north-mini-code/tools/nmc_qk_cuda.cu:1436-1551):
- *   q_dev [n_heads*head_dim], k_dev / v_dev [n_kv*head_dim]  projected rows of the token (q is rotated IN PLACE),
+ *   q_dev [n_heads*head_dim], k_dev / v_dev [n_kv*head_dim]  projected rows of the token, before rotation (not modified),
  *   kcache_dev / vcache_dev [n_kv][cache_rows][head_dim] int32, row `pos` is written by this call,
  *   pos_dev != NULL: the position is read from that device cell when the kernels run and `pos` is only an upper
  *   bound of it (sizes the grids), so a captured launch sequence can be replayed for successive tokens,
@@ -163,10 +163,21 @@ int iie_moe_experts_dev(long long layer, const int64_t *h_dev, long long T, cons
  *   inv_sqrt = round(2^fa / sqrt(head_dim)) as the caller's model defines it,
  *   out_dev [n_heads*head_dim] = (softmax(scores) v) >> fa.
  * Flag bit 2 is raised when a key or value does not fit the int32 cache. */
-int iie_attn_decode_dev(int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
+int iie_attn_decode_dev(const int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
                         int32_t *vcache_dev, long long pos, const int *pos_dev, long long window, const int64_t *cos_dev,
                         const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim, long long cache_rows,
                         int fa, long long inv_sqrt, int64_t *out_dev, void *stream);
+/* The attention half of a decoder block for ONE token, accumulated into the residual row:
+ *   x_dev [d_model] += (attention(q, cache) Wo^T), with [q | k | v] = h Wqkv^T,
+ * where h is the normalised row whose digit planes the LAST single-token iie_moe_block_dev / iie_moe_forward_dev
+ * call left in the library (the reference's block uses the same h for attention and experts, cohere2.py:357-376), so
+ * the MoE half of the block must run first.  wqkv_h: one registered matrix with the rows of Wq, Wk, Wv stacked
+ * (n_heads*head_dim + 2*n_kv*head_dim rows); wo_h: [d_model, n_heads*head_dim].  Five launches: fused QKV product,
+ * the three attention passes, O product.  rc 3: a weight outside the exact envelope.  Other arguments as above. */
+int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t *kcache_dev, int32_t *vcache_dev, long long pos,
+                       const int *pos_dev, long long window, const int64_t *cos_dev, const int64_t *sin_dev, int rope,
+                       int n_heads, int n_kv, int head_dim, long long cache_rows, int fa, int fw, long long inv_sqrt,
+                       void *stream);
 /* Row `token` (or *token_dev when token_dev != NULL) of a registered Q4_K / Q6_K matrix as int64 at 2^frac:
  * the embedding look-up (north-mini-code/src/nmc/engine.py:239-243). */
 int iie_embed_dev(long long h, const int *token_dev, long long token, int frac, int64_t *out_dev, void *stream);

@@ -60,6 +60,8 @@ const uint8_t **g_selptr = nullptr;   // device: [3][64] pointers of the experts
 int g_pdl = 1;                        // programmatic dependent launch between the decode kernels
 int g_fused_expert = 0;               // single-token expert stage as one cluster launch (expert.cu): slower on this part
 int g_fused_route = 0;                // routing recomputed inside the gate/up launch (rgu.cu): slower than its own launch
+long long g_hl_d = 0;                 // width of the digit planes the last single-token routing left in the R_XL scratch
+int64_t *g_pow2 = nullptr;            // device: 2^i for i = 0..31 (unit gates at any activation scale)
 int g_gu_parity = 0;                  // which of the two gu digit-count cells the next fused launch uses
 long long g_tc_min_tokens = 192;      // from this many tokens on, the MoE block runs on the tcgen05 grouped GEMMs
 int g_ready = -1;                     // -1 unknown, 0 usable, 1 unusable
@@ -81,9 +83,12 @@ bool init() {
     if (cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaMalloc(&g_flags, sizeof(int)) != cudaSuccess || cudaMemset(g_flags, 0, sizeof(int)) != cudaSuccess ||
         cudaMalloc(&g_cells, 64) != cudaSuccess || cudaMemset(g_cells, 0, 64) != cudaSuccess ||
-        cudaMalloc(&g_selptr, 3 * 64 * sizeof(void *)) != cudaSuccess) {
+        cudaMalloc(&g_selptr, 3 * 64 * sizeof(void *)) != cudaSuccess || cudaMalloc(&g_pow2, 32 * sizeof(int64_t)) != cudaSuccess) {
         cudaGetLastError(); g_ready = 1; return false;
     }
+    int64_t pw[32];
+    for (int i = 0; i < 32; i++) pw[i] = (int64_t)1 << i;
+    if (cudaMemcpy(g_pow2, pw, sizeof(pw), cudaMemcpyHostToDevice) != cudaSuccess) { cudaGetLastError(); g_ready = 1; return false; }
     g_ready = 0;
     return true;
 }
@@ -367,6 +372,7 @@ bool moe_decode_token(const MoeLayer &L, const int64_t *x, const int64_t *gain, 
     int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)E * 8);
     int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)k * 8 * L.e_ffn);
     if (!hl || !lg || !gul) return false;
+    g_hl_d = L.d_model;
     if (g_fused_route && g_stage_mask == 0 && r.qtype == QT_Q4K && L.gate_q == QT_Q4K && k <= 64 &&
         !(init_mode == 1 && out == x)) {
         int *cell = g_cells + 4 + g_gu_parity, *cell_next = g_cells + 4 + (g_gu_parity ^ 1);
@@ -378,7 +384,7 @@ bool moe_decode_token(const MoeLayer &L, const int64_t *x, const int64_t *gain, 
         fa_.fast = small_scales(L.maxd_gate, L.maxdmin_gate, fw);
         const cudaError_t fe = launch_routed_gateup(L.gate_q, fa_, s);
         if (fe == cudaSuccess) {
-            g_gu_parity ^= 1;
+            g_gu_parity ^= 1; g_hl_d = 0;                   // this path keeps the digit planes in shared memory only
             StreamArgs da = {};
             da.wa = L.tabs + 2 * E; da.wb = da.wa; da.sel = ids; da.n_sel = k; da.out_f = L.d_model; da.n_blocks = L.e_ffn / 256;
             da.fw = fw; da.fa = fa; da.xl = gul; da.x_per_sel = 1; da.x_nl = cell; da.out = out; da.gates = gates;
@@ -907,7 +913,35 @@ extern "C" int iie_moe_experts_dev(long long layer, const int64_t *h_dev, long l
     return 0;
 }
 
-extern "C" int iie_attn_decode_dev(int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
+namespace {
+
+// scratch of the attention passes; returns false on allocation failure.  The statistics are reset once per
+// (re)allocation or shape change; every call leaves them reset.
+bool attn_scratch(AttnArgs &a, cudaStream_t s) {
+    static void *last_ptr = nullptr;
+    static int last_h = 0, last_hd = 0;
+    a.scores = (int64_t *)ensure(R_ASCORES, (size_t)a.H * a.Lmax * 8);
+    a.e = (int32_t *)ensure(R_AEXP, (size_t)a.H * a.Lmax * 4);
+    uint8_t *st = (uint8_t *)ensure(R_ASTAT, (size_t)a.H * 16 + (size_t)a.H * a.hd * 8 + 64);
+    if (!a.scores || !a.e || !st) return false;
+    a.hmax = (long long *)st; a.Z = (unsigned long long *)(st + (size_t)a.H * 8);
+    a.acc = (long long *)(st + (size_t)a.H * 16); a.ticket = (unsigned *)(st + (size_t)a.H * 16 + (size_t)a.H * a.hd * 8);
+    if (st != last_ptr || a.H != last_h || a.hd != last_hd) {
+        if (launch_attn_reset(a.hmax, a.Z, a.acc, a.ticket, a.H, a.hd, s) != cudaSuccess) return false;
+        last_ptr = st; last_h = a.H; last_hd = a.hd;
+    }
+    return true;
+}
+
+void attn_consts(AttnArgs &a, int fa, long long inv_sqrt) {
+    a.fa = fa; a.inv_sqrt = inv_sqrt; a.log2e = sigmoid_log2e(fa);
+    const long long ca = (((long long)(fa + 2)) << (2 * fa)) / a.log2e, cb = ((long long)1 << 62) / a.log2e;
+    a.clip = ca < cb ? ca : cb;
+}
+
+}  // namespace
+
+extern "C" int iie_attn_decode_dev(const int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
                                    int32_t *vcache_dev, long long pos, const int *pos_dev, long long window, const int64_t *cos_dev,
                                    const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim,
                                    long long cache_rows, int fa, long long inv_sqrt, int64_t *out_dev, void *stream) {
@@ -917,19 +951,50 @@ extern "C" int iie_attn_decode_dev(int64_t *q_dev, const int64_t *k_dev, const i
     AttnArgs a = {};
     a.q = q_dev; a.k = k_dev; a.v = v_dev; a.kcache = kcache_dev; a.vcache = vcache_dev; a.pos = pos;
     a.pos_dev = pos_dev; a.window = window; a.lo = 0; a.Lmax = cache_rows;
-    a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim; a.fa = fa;
-    a.inv_sqrt = inv_sqrt; a.log2e = sigmoid_log2e(fa);
-    const long long ca = (((long long)(fa + 2)) << (2 * fa)) / a.log2e, cb = ((long long)1 << 62) / a.log2e;
-    a.clip = ca < cb ? ca : cb;
-    a.scores = (int64_t *)ensure(R_ASCORES, (size_t)n_heads * cache_rows * 8);
-    a.e = (int32_t *)ensure(R_AEXP, (size_t)n_heads * cache_rows * 4);
-    uint8_t *st = (uint8_t *)ensure(R_ASTAT, (size_t)n_heads * 16 + (size_t)n_heads * head_dim * 8 + 64);
-    if (!a.scores || !a.e || !st) return 1;
-    a.hmax = (long long *)st; a.Z = (unsigned long long *)(st + (size_t)n_heads * 8);
-    a.acc = (long long *)(st + (size_t)n_heads * 16); a.ticket = (unsigned *)(st + (size_t)n_heads * 16 + (size_t)n_heads * head_dim * 8);
+    a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim;
+    attn_consts(a, fa, inv_sqrt);
+    if (!attn_scratch(a, (cudaStream_t)stream)) return 1;
     a.out = out_dev; a.flags = g_flags;
     const cudaError_t e = launch_attn_decode(a, (cudaStream_t)stream);
     if (e != cudaSuccess) { cudaGetLastError(); return 1; }
+    return 0;
+}
+
+extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t *kcache_dev, int32_t *vcache_dev,
+                                  long long pos, const int *pos_dev, long long window, const int64_t *cos_dev,
+                                  const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim, long long cache_rows,
+                                  int fa, int fw, long long inv_sqrt, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !valid_q(wqkv_h) || !valid_q(wo_h) || !x_dev || !kcache_dev || !vcache_dev || n_heads <= 0 || n_kv <= 0 ||
+        head_dim <= 0 || cache_rows <= 0 || fa < 1 || fa > 29) return 1;
+    const Weight &wqkv = g_w[wqkv_h], &wo = g_w[wo_h];
+    const long long d = wqkv.nb * 256, qd = (long long)n_heads * head_dim, kd = (long long)n_kv * head_dim;
+    if (wqkv.out_f != qd + 2 * kd || wo.nb * 256 != qd || wo.out_f != d || g_hl_d != d) return 1;   // g_hl_d: the digit planes on hand
+    if (!fast_envelope(wqkv.qtype, wqkv.nb, wqkv.maxd, wqkv.maxdmin, fw) || !fast_envelope(wo.qtype, wo.nb, wo.maxd, wo.maxdmin, fw)) return 3;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int8_t *hl = (const int8_t *)g_buf[R_XL].p;
+    int64_t *qkv = (int64_t *)ensure(R_TMP0, (size_t)(qd + 2 * kd) * 8);
+    int8_t *al = (int8_t *)ensure(R_TMP1, (size_t)8 * qd);
+    if (!hl || !qkv || !al) return 1;
+    StreamArgs sa = {};
+    sa.wa = wqkv.cell; sa.wb = wqkv.cell; sa.n_sel = 1; sa.out_f = wqkv.out_f; sa.n_blocks = wqkv.nb; sa.fw = fw; sa.fa = fa;
+    sa.xl = hl; sa.x_per_sel = 0; sa.x_nl = g_cells; sa.out = qkv; sa.flags = g_flags;
+    sa.fast = small_scales(wqkv.maxd, wqkv.maxdmin, fw); sa.pdl = 0;
+    if (launch_stream(wqkv.qtype, MODE_LINEAR, sa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    AttnArgs a = {};
+    a.q = qkv; a.k = qkv + qd; a.v = qkv + qd + kd; a.kcache = kcache_dev; a.vcache = vcache_dev; a.pos = pos;
+    a.pos_dev = pos_dev; a.window = window; a.lo = 0; a.Lmax = cache_rows;
+    a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim;
+    attn_consts(a, fa, inv_sqrt);
+    if (!attn_scratch(a, s)) return 1;
+    a.out = nullptr; a.out_limbs = al; a.out_nl = g_cells + 7; a.flags = g_flags;
+    if (launch_attn_decode(a, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    // O product accumulated into the residual row: the "down" form of the streaming kernel with a unit gate
+    StreamArgs oa = {};
+    oa.wa = wo.cell; oa.wb = wo.cell; oa.n_sel = 1; oa.out_f = wo.out_f; oa.n_blocks = wo.nb; oa.fw = fw; oa.fa = fa;
+    oa.xl = al; oa.x_per_sel = 1; oa.x_nl = g_cells + 7; oa.out = x_dev; oa.gates = g_pow2 + fa; oa.flags = g_flags;
+    oa.fast = small_scales(wo.maxd, wo.maxdmin, fw); oa.pdl = 0;
+    if (launch_stream(wo.qtype, MODE_DOWN, oa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     return 0;
 }
 

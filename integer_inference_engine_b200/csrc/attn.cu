@@ -13,10 +13,15 @@
 // The floors make the softmax non-linear, so the three passes need the row maximum and the normaliser of ALL
 // visible keys: scores + max, exponentials + sum, probabilities x values are three launches over
 // (KV head, key chunk) CTAs; a CTA serves every query head of its KV head so K and V are read once.
+// The first pass also rotates the query heads (into shared memory, the caller's q is not modified) and, in the
+// CTA that owns the new position, rotates the new key and appends key and value to the cache; the last CTA of
+// the third pass writes the result (optionally as digit planes for the following product) and resets the
+// shared statistics, so a call is exactly three launches.
 // The cache holds K (after rotation) and V as int32: values outside int32 raise flag bit 2 (the reference bank
 // stores them the same way and refuses such values).
 #include "kernels.h"
 #include "layout.cuh"
+#include "mma_items.cuh"
 
 namespace iie {
 
@@ -31,54 +36,57 @@ __device__ __forceinline__ void at_span(const AttnArgs &a, long long &pos, long 
     lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
 }
 
-__global__ void attn_prep_kernel(const AttnArgs a_in) {
-    AttnArgs a = a_in;
-    long long lo_unused;
-    at_span(a_in, a.pos, lo_unused);
-    const int tid = threadIdx.x, nth = blockDim.x;
+// rotation of one (x0, x1) pair with the table row of `pos`
+__device__ __forceinline__ void at_rotate(const AttnArgs &a, long long pos, int i, int64_t &x0, int64_t &x1) {
+    if (!a.rope) return;
     const int half = a.hd / 2;
-    const int64_t *cs = a.cos ? a.cos + a.pos * half : nullptr, *sn = a.sin ? a.sin + a.pos * half : nullptr;
-    bool bad = false;
-    // q rotated in place; k rotated into the cache; v copied into the cache
-    for (int idx = tid; idx < (a.H + a.Hkv) * half; idx += nth) {
-        const bool is_q = idx < a.H * half;
-        const int j = is_q ? idx : idx - a.H * half, head = j / half, i = j - head * half;
-        const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
-        const int64_t *src = is_q ? a.q + head * a.hd : a.k + head * a.hd;
-        int64_t x0 = src[i0], x1 = src[i1];
-        if (a.rope) {
-            const int64_t c = cs[i], s = sn[i];
-            const int64_t y0 = (x0 * c - x1 * s) >> a.fa, y1 = (x0 * s + x1 * c) >> a.fa;
-            x0 = y0; x1 = y1;
-        }
-        if (is_q) { a.q[head * a.hd + i0] = x0; a.q[head * a.hd + i1] = x1; }
-        else {
-            int32_t *dst = a.kcache + ((long long)head * a.Lmax + a.pos) * a.hd;
-            bad |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
-            dst[i0] = (int32_t)x0; dst[i1] = (int32_t)x1;
-        }
-    }
-    for (int idx = tid; idx < a.Hkv * a.hd; idx += nth) {
-        const int head = idx / a.hd, i = idx - head * a.hd;
-        const int64_t v = a.v[idx];
-        bad |= v != (int32_t)v;
-        a.vcache[((long long)head * a.Lmax + a.pos) * a.hd + i] = (int32_t)v;
-    }
-    for (int idx = tid; idx < a.H; idx += nth) { a.hmax[idx] = INT64_MIN; a.Z[idx] = 0ULL; }
-    for (int idx = tid; idx < a.H * a.hd; idx += nth) a.acc[idx] = 0;
-    if (tid == 0) *a.ticket = 0u;
-    if (bad) atomicOr(a.flags, 4);
+    const int64_t c = a.cos[pos * half + i], s = a.sin[pos * half + i];
+    const int64_t y0 = (x0 * c - x1 * s) >> a.fa, y1 = (x0 * s + x1 * c) >> a.fa;
+    x0 = y0; x1 = y1;
 }
 
-// pass 1: scores of AT_CH keys for the `rep` query heads of one KV head; one warp per key
+__global__ void attn_reset_kernel(long long *hmax, unsigned long long *Z, long long *acc, unsigned *ticket, int H, int hd) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { hmax[i] = INT64_MIN; Z[i] = 0ULL; }
+    for (int i = threadIdx.x; i < H * hd; i += blockDim.x) acc[i] = 0;
+    if (threadIdx.x == 0) *ticket = 0u;
+}
+
+// pass 1: scores of AT_CH keys for the `rep` query heads of one KV head; one warp per key.  Every CTA rotates
+// its query heads into shared memory; the CTA whose chunk holds `pos` rotates the new key and appends key and
+// value to the cache first.
 __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
     at_span(a_in, a.pos, a.lo);
     extern __shared__ long long at_q[];                   // [rep][hd]
     __shared__ long long s_max[AT_MAXREP];
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int half = a.hd / 2;
     const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
-    for (int i = tid; i < rep * a.hd; i += blockDim.x) at_q[i] = a.q[(long long)kv * rep * a.hd + i];
+    for (int idx = tid; idx < rep * half; idx += blockDim.x) {
+        const int r = idx / half, i = idx - r * half;
+        const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
+        const int64_t *src = a.q + (long long)(kv * rep + r) * a.hd;
+        int64_t x0 = src[i0], x1 = src[i1];
+        at_rotate(a, a.pos, i, x0, x1);
+        at_q[r * a.hd + i0] = x0; at_q[r * a.hd + i1] = x1;
+    }
+    if (l0 <= a.pos && a.pos < l0 + AT_CH) {              // this CTA owns the new token's cache row
+        bool bad = false;
+        for (int i = tid; i < half; i += blockDim.x) {
+            const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
+            int64_t x0 = a.k[kv * a.hd + i0], x1 = a.k[kv * a.hd + i1];
+            at_rotate(a, a.pos, i, x0, x1);
+            bad |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+            int32_t *dst = a.kcache + ((long long)kv * a.Lmax + a.pos) * a.hd;
+            dst[i0] = (int32_t)x0; dst[i1] = (int32_t)x1;
+        }
+        for (int i = tid; i < a.hd; i += blockDim.x) {
+            const int64_t v = a.v[kv * a.hd + i];
+            bad |= v != (int32_t)v;
+            a.vcache[((long long)kv * a.Lmax + a.pos) * a.hd + i] = (int32_t)v;
+        }
+        if (bad) atomicOr(a.flags, 4);
+    }
     if (tid < AT_MAXREP) s_max[tid] = INT64_MIN;
     __syncthreads();
     long long wmax[AT_MAXREP];
@@ -86,10 +94,10 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
     for (int r = 0; r < AT_MAXREP; r++) wmax[r] = INT64_MIN;
     const int per_lane = a.hd / 32;                        // 4 for head_dim 128
     for (long long l = l0 + warp; l < l1; l += 8) {
-        const int32_t *krow = a.kcache + ((long long)kv * a.Lmax + l) * a.hd + lane * per_lane;
+        const volatile int32_t *krow = a.kcache + ((long long)kv * a.Lmax + l) * a.hd + lane * per_lane;
         int32_t kk[8];
 #pragma unroll
-        for (int j = 0; j < 8; j++) kk[j] = j < per_lane ? __ldg(krow + j) : 0;
+        for (int j = 0; j < 8; j++) kk[j] = j < per_lane ? krow[j] : 0;
 #pragma unroll
         for (int r = 0; r < AT_MAXREP; r++) {
             if (r < rep) {
@@ -137,12 +145,13 @@ __global__ void __launch_bounds__(256) attn_exp_kernel(const AttnArgs a_in) {
     }
 }
 
-// pass 3: probabilities x values, partial sums added into acc; the CTA that finishes last shifts and writes out
+// pass 3: probabilities x values, partial sums added into acc.  The CTA that finishes last shifts, writes the
+// result (and, on request, its digit planes) and returns the shared statistics to their initial state.
 __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
     at_span(a_in, a.pos, a.lo);
     __shared__ long long s_p[AT_MAXREP][AT_CH];
-    __shared__ int s_last;
+    __shared__ int s_last, s_nl;
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x;
     const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
     const int nk = (int)max(0LL, l1 - l0);
@@ -157,15 +166,16 @@ __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
         }
         s_p[r][j] = p;
     }
+    if (tid == 0) s_nl = 1;
     __syncthreads();
     const int G = blockDim.x / a.hd, grp = tid / a.hd, d = tid - grp * a.hd;      // head groups sharing the CTA
-    if (grp < G) {
+    if (grp < G && nk > 0) {
         long long accv[AT_MAXREP / 2];
 #pragma unroll
         for (int i = 0; i < AT_MAXREP / 2; i++) accv[i] = 0;
         const int32_t *vbase = a.vcache + ((long long)kv * a.Lmax + l0) * a.hd + d;
         for (int j = 0; j < nk; j++) {
-            const long long v = (long long)__ldg(vbase + (long long)j * a.hd);
+            const long long v = (long long)vbase[(long long)j * a.hd];
 #pragma unroll
             for (int i = 0; i < AT_MAXREP / 2; i++) {
                 const int r = grp + i * G;
@@ -185,7 +195,27 @@ __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    for (int i = tid; i < a.H * a.hd; i += blockDim.x) a.out[i] = *((volatile long long *)(a.acc + i)) >> a.fa;
+    const long long n = (long long)a.H * a.hd;
+    int nl = 1;
+    bool over = false;
+    for (long long i = tid; i < n; i += blockDim.x) {
+        const long long y = *((volatile long long *)(a.acc + i)) >> a.fa;
+        if (a.out) a.out[i] = y;
+        if (a.out_limbs) {
+            bool ok;
+            const uint64_t dg = balanced_digits8(y, ok);
+            over |= !ok;
+            nl = max(nl, digits_used(dg));
+#pragma unroll
+            for (int l = 0; l < 8; l++) a.out_limbs[l * n + i] = (int8_t)(dg >> (8 * l));
+        }
+        a.acc[i] = 0;
+    }
+    if (over) atomicOr(a.flags, 1);
+    if (a.out_limbs) atomicMax(&s_nl, nl);
+    for (int i = tid; i < a.H; i += blockDim.x) { a.hmax[i] = INT64_MIN; a.Z[i] = 0ULL; }
+    __syncthreads();
+    if (tid == 0) { *a.ticket = 0u; if (a.out_nl) *a.out_nl = s_nl; }
 }
 
 // one row of a registered Q4_K / Q6_K matrix as int64 at 2^frac (the embedding look-up)
@@ -255,11 +285,16 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
     long long n_keys = a.pos - lo_min + 1;
     if (a.window > 0 && n_keys > a.window) n_keys = a.window;
     const unsigned chunks = (unsigned)((n_keys + AT_CH - 1) / AT_CH);
-    attn_prep_kernel<<<1, 512, 0, s>>>(a);
     attn_scores_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)rep * a.hd * 8, s>>>(a);
     attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H), 256, 0, s>>>(a);
     attn_pv_kernel<<<dim3(chunks, a.Hkv), 256, 0, s>>>(a);
-    note_launch(4);
+    note_launch(3);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_attn_reset(long long *hmax, unsigned long long *Z, long long *acc, unsigned *ticket, int H, int hd, cudaStream_t s) {
+    attn_reset_kernel<<<1, 256, 0, s>>>(hmax, Z, acc, ticket, H, hd);
+    note_launch();
     return cudaGetLastError();
 }
 

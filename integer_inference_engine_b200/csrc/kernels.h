@@ -197,7 +197,7 @@ cudaError_t launch_dispatch(const int *ids, const int64_t *gates, long long T, i
 
 // One new token's attention over an int32 KV cache (attn.cu): rotation, cache append, three softmax passes.
 struct AttnArgs {
-    int64_t *q;                    // [H*hd] projected query, rotated in place
+    const int64_t *q;              // [H*hd] projected query (rotated on the fly, not modified)
     const int64_t *k, *v;          // [Hkv*hd] projected key / value of the new token
     int32_t *kcache, *vcache;      // [Hkv][Lmax][hd]
     long long pos, lo, Lmax;       // position of the new token (an upper bound when pos_dev is set), first visible key
@@ -214,10 +214,14 @@ struct AttnArgs {
     unsigned long long *Z;         // scratch [H]
     long long *acc;                // scratch [H][hd]
     unsigned *ticket;              // scratch
-    int64_t *out;                  // [H*hd]
-    int *flags;                    // bit 2: a key / value does not fit the int32 cache
+    int64_t *out;                  // [H*hd], nullable
+    int8_t *out_limbs;             // nullable: digit planes [8][H*hd] of the result
+    int *out_nl;                   // nullable: digits in use by the result
+    int *flags;                    // bit 0 digit envelope, bit 2 a key / value does not fit the int32 cache
 };
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s);
+// hmax = INT64_MIN, Z = acc = ticket = 0: once after the statistics buffer is (re)allocated; every call leaves them so
+cudaError_t launch_attn_reset(long long *hmax, unsigned long long *Z, long long *acc, unsigned *ticket, int H, int hd, cudaStream_t s);
 cudaError_t launch_embed_row(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,
                              int64_t *out, cudaStream_t s);
 cudaError_t launch_argmax(const int64_t *x, long long n, int *out, cudaStream_t s);

@@ -84,7 +84,7 @@ def attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kcache: 
                      inv_sqrt: int | None = None, out: torch.Tensor | None = None,
                      pos_dev: torch.Tensor | None = None) -> torch.Tensor:
     """One new token's GQA attention over the int32 caches ``[n_kv, rows, head_dim]``; writes cache row ``pos``
-    and rotates ``q`` in place.  With ``pos_dev`` (CUDA int32 [1]) the position is read on the device and ``pos``
+    (``q`` and ``k`` are given before rotation and are not modified).  With ``pos_dev`` (CUDA int32 [1]) the position is read on the device and ``pos``
     is an upper bound (for replayed graphs).  Returns ``[n_heads * head_dim]`` int64."""
     lib = qk_cuda._lib()
     assert q.is_cuda and q.dtype == torch.int64 and q.is_contiguous() and q.numel() == n_heads * head_dim
@@ -104,6 +104,26 @@ def attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kcache: 
     if rc != 0:
         raise CudaContextError(f"attention failed with status {rc}")
     return out
+
+
+def attention_block(wqkv: int, wo: int, x: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: int, n_heads: int,
+                    n_kv: int, head_dim: int, fa: int = 16, fw: int = 24, window: int = 0, cos: torch.Tensor | None = None,
+                    sin: torch.Tensor | None = None, rope: int = 0, inv_sqrt: int | None = None,
+                    pos_dev: torch.Tensor | None = None) -> None:
+    """``x += attention(...) Wo^T`` for the row the last single-token MoE block call normalised (see
+    ``iie_attn_block_dev``): fused QKV product, cache append, exact attention, O product."""
+    lib = qk_cuda._lib()
+    assert x.is_cuda and x.dtype == torch.int64 and x.is_contiguous()
+    assert kcache.dtype == torch.int32 and vcache.dtype == torch.int32 and kcache.is_contiguous() and vcache.is_contiguous()
+    if inv_sqrt is None:
+        inv_sqrt = int(round((1.0 / head_dim ** 0.5) * (1 << fa)))
+    with _CUDA_LOCK:
+        rc = lib.iie_attn_block_dev(int(wqkv), int(wo), x.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), int(pos),
+                                    pos_dev.data_ptr() if pos_dev is not None else None, int(window or 0),
+                                    cos.data_ptr() if rope else None, sin.data_ptr() if rope else None, int(rope), n_heads, n_kv,
+                                    head_dim, int(kcache.shape[1]), int(fa), int(fw), int(inv_sqrt), _stream_ptr())
+    if rc != 0:
+        raise CudaContextError(f"attention block failed with status {rc}")
 
 
 def embed(handle: int, token, d_model: int, fa: int = 16, out: torch.Tensor | None = None) -> torch.Tensor:

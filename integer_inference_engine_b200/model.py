@@ -46,14 +46,14 @@ class SyntheticDecoder:
         self.attn = []
         for li in range(n_layers):
             gen = torch.Generator(device="cuda").manual_seed(seed * 7919 + 1000 + li)
-            wq = device.register_weight(synth_q4k(n_heads * head_dim * nb, gen).view(-1), n_heads * head_dim, nb, Q4_K)
-            wk = device.register_weight(synth_q4k(n_kv * head_dim * nb, gen).view(-1), n_kv * head_dim, nb, Q4_K)
-            wv = device.register_weight(synth_q4k(n_kv * head_dim * nb, gen).view(-1), n_kv * head_dim, nb, Q4_K)
+            # Wq, Wk, Wv stacked row-wise into one matrix (rows are independent in the block layout)
+            qkv_rows = (n_heads + 2 * n_kv) * head_dim
+            wqkv = device.register_weight(synth_q4k(qkv_rows * nb, gen).view(-1), qkv_rows, nb, Q4_K)
             wo = device.register_weight(synth_q4k(d_model * (n_heads * head_dim // 256), gen).view(-1), d_model,
                                         n_heads * head_dim // 256, Q4_K)
             kc = torch.randint(-(1 << 18), 1 << 18, (n_kv, self.rows, head_dim), generator=gen, device="cuda", dtype=torch.int32)
             vc = torch.randint(-(1 << 18), 1 << 18, (n_kv, self.rows, head_dim), generator=gen, device="cuda", dtype=torch.int32)
-            self.attn.append({"wq": wq, "wk": wk, "wv": wv, "wo": wo, "k": kc, "v": vc})
+            self.attn.append({"wqkv": wqkv, "wo": wo, "k": kc, "v": vc})
         gen = torch.Generator(device="cuda").manual_seed(seed * 7919 + 999)
         self.embd = device.register_weight(synth_q6k(vocab * nb, gen).view(-1), vocab, nb, Q6_K)
         gain = torch.round((torch.randn(d_model, generator=gen, device="cuda", dtype=torch.float64).abs() + 0.5)
@@ -67,8 +67,7 @@ class SyntheticDecoder:
         self.context = context
         # scratch rows of a step
         z = lambda n: torch.empty((1, n), dtype=torch.int64, device="cuda")
-        self.x, self.h, self.q, self.k, self.v = z(d_model), z(d_model), z(n_heads * head_dim), z(n_kv * head_dim), z(n_kv * head_dim)
-        self.att, self.ao, self.hn, self.logits = z(n_heads * head_dim), z(d_model), z(d_model), z(vocab)
+        self.x, self.hn, self.logits = z(d_model), z(d_model), z(vocab)
 
     def layer_is_full(self, li: int) -> bool:
         return li % SWA_PERIOD == 0
@@ -92,26 +91,39 @@ class SyntheticDecoder:
         device.embed(self.embd, self.token, self.d, fa, out=self.x)
         for li in range(self.n_layers):
             a = self.attn[li]
-            gain_h = self.moe.gains[li]
-            device.rmsnorm(self.x, gain_h, fa, 1, out=self.h)
-            device.apply(a["wq"], self.h, self.H * self.hd, fw, out=self.q)
-            device.apply(a["wk"], self.h, self.Hkv * self.hd, fw, out=self.k)
-            device.apply(a["wv"], self.h, self.Hkv * self.hd, fw, out=self.v)
             full = self.layer_is_full(li)
-            device.attention_decode(self.q.view(-1), self.k.view(-1), self.v.view(-1), a["k"], a["v"], pos_bound, self.H,
-                                    self.Hkv, self.hd, fa, 0 if full else self.window, self.cos, self.sin, 0 if full else 1,
-                                    out=self.att.view(-1), pos_dev=self.pos)
-            device.apply(a["wo"], self.att, self.d, fw, out=self.ao)
-            self.moe.layers[li].block(self.x, gain_h, fa, fw, 1, out=self.x, want_routes=False)     # x += moe(h)
-            self.x += self.ao
+            # MoE half first: it normalises x, leaves the digit planes of h in the library and adds moe(h) to x;
+            # the attention half then reads those planes and adds its own term
+            self.moe.layers[li].block(self.x, self.moe.gains[li], fa, fw, 1, out=self.x, want_routes=False)
+            device.attention_block(a["wqkv"], a["wo"], self.x, a["k"], a["v"], pos_bound, self.H, self.Hkv, self.hd, fa, fw,
+                                   0 if full else self.window, self.cos, self.sin, 0 if full else 1, pos_dev=self.pos)
         device.rmsnorm(self.x, self.out_gain_h, fa, 1, out=self.hn)
         device.apply(self.embd, self.hn, self.vocab, fw, out=self.logits)
         device.argmax(self.logits.view(-1), out=self.token)
         self.pos += 1
 
-    def decode_token(self, token_host: torch.Tensor, out_host: torch.Tensor, pos_bound: int) -> None:
-        """Public per-token call with host buffers: pinned int32 ``token_host`` [1] in, ``out_host`` [1] out."""
+    def capture(self, pos_bound: int) -> None:
+        """Record one step as a CUDA graph valid for every position up to ``pos_bound``; token and position are
+        restored afterwards, the KV row written during the warm-up / capture pass is overwritten by the next real step."""
+        keep = (self.token.clone(), self.pos.clone())
+        self.step(pos_bound)                                   # sizes every workspace
+        torch.cuda.synchronize()
+        self._stream = torch.cuda.Stream()
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(self._stream):
+            with torch.cuda.graph(self._graph, stream=self._stream):
+                self.step(pos_bound)
+        torch.cuda.synchronize()
+        self.token.copy_(keep[0]); self.pos.copy_(keep[1])
+        self._bound = pos_bound
+
+    def replay(self) -> None:
+        self._graph.replay()
+
+    def decode_token(self, token_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """Public per-token call with host buffers: pinned int32 ``token_host`` [1] in, next id in pinned ``out_host``
+        [1]; returns when the id has arrived.  Needs :meth:`capture` first."""
         self.token.copy_(token_host, non_blocking=True)
-        self.step(pos_bound)
+        self._graph.replay()
         out_host.copy_(self.token, non_blocking=True)
         torch.cuda.current_stream().synchronize()

@@ -79,7 +79,7 @@ def test_decode_attention_matches_the_oracle(H, Hkv, hd, pos, window, rope):
     want = o.attention_cached(q_rot, ck_full, cv, pos, H, Hkv, FA, window)
     ck_in = ck.copy(); ck_in[:, pos:pos + 1] = k_new                                   # the entry rotates the new key itself
     got, kc, vc, q_after = _run(q, ck_in, cv, pos, H, Hkv, hd, window, rope, cos, sin)
-    assert np.array_equal(q_after.reshape(1, H, hd), q_rot)
+    assert np.array_equal(q_after.reshape(1, H, hd), q)                               # the caller's q is left as it was
     assert np.array_equal(kc[:, pos], k_rot[:, 0].astype(np.int32)) and np.array_equal(vc[:, pos], cv[:, pos].astype(np.int32))
     assert np.array_equal(got.reshape(1, -1), want)
 

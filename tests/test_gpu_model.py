@@ -16,10 +16,11 @@ def _host_view(model):
     for li in range(model.n_layers):
         a, hs = model.attn[li], model.moe.handles[li]
         E = model.moe.n_experts
+        qr, kr = model.H * model.hd, model.Hkv * model.hd
+        fused = device.export_weight(a["wqkv"], qr + 2 * kr, nb, o.Q4_K)          # rows of Wq, Wk, Wv stacked
+        cut = lambda r0, r1: bytes(fused[r0 * nb * 144:r1 * nb * 144])
         layers.append({
-            "gain": hs["gain"].cpu().numpy(),
-            "wq": device.export_weight(a["wq"], model.H * model.hd, nb, o.Q4_K), "wk": device.export_weight(a["wk"], model.Hkv * model.hd, nb, o.Q4_K),
-            "wv": device.export_weight(a["wv"], model.Hkv * model.hd, nb, o.Q4_K),
+            "gain": hs["gain"].cpu().numpy(), "wq": cut(0, qr), "wk": cut(qr, qr + kr), "wv": cut(qr + kr, qr + 2 * kr),
             "wo": device.export_weight(a["wo"], model.d, model.H * model.hd // 256, o.Q4_K),
             "k": a["k"].cpu().numpy().astype(np.int64), "v": a["v"].cpu().numpy().astype(np.int64), "full": model.layer_is_full(li),
             "moe": (device.export_weight(hs["router"], E, nb, o.Q4_K),
