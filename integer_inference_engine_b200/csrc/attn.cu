@@ -51,7 +51,8 @@ __global__ void attn_reset_kernel(long long *hmax, unsigned long long *Z, long l
     if (threadIdx.x == 0) *ticket = 0u;
 }
 
-// pass 1: scores of AT_CH keys for the `rep` query heads of one KV head; one warp per key.  Every CTA rotates
+// pass 1: scores of AT_CH keys for the `rep` query heads of one KV head; the keys are staged in shared memory and
+// each thread owns one key for a quarter of the query heads.  Every CTA rotates
 // its query heads into shared memory; the CTA whose chunk holds `pos` rotates the new key and appends key and
 // value to the cache first.
 __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
@@ -59,7 +60,7 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
     at_span(a_in, a.pos, a.lo);
     extern __shared__ long long at_q[];                   // [rep][hd]
     __shared__ long long s_max[AT_MAXREP];
-    const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31;
     const int half = a.hd / 2;
     const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
     for (int idx = tid; idx < rep * half; idx += blockDim.x) {
@@ -88,33 +89,37 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
         if (bad) atomicOr(a.flags, 4);
     }
     if (tid < AT_MAXREP) s_max[tid] = INT64_MIN;
-    __syncthreads();
-    long long wmax[AT_MAXREP];
-#pragma unroll
-    for (int r = 0; r < AT_MAXREP; r++) wmax[r] = INT64_MIN;
-    const int per_lane = a.hd / 32;                        // 4 for head_dim 128
-    for (long long l = l0 + warp; l < l1; l += 8) {
-        const volatile int32_t *krow = a.kcache + ((long long)kv * a.Lmax + l) * a.hd + lane * per_lane;
-        int32_t kk[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) kk[j] = j < per_lane ? krow[j] : 0;
-#pragma unroll
-        for (int r = 0; r < AT_MAXREP; r++) {
-            if (r < rep) {
-                const long long *qq = at_q + r * a.hd + lane * per_lane;
-                long long part = 0;
-#pragma unroll
-                for (int j = 0; j < 8; j++) if (j < per_lane) part += qq[j] * (long long)kk[j];
-#pragma unroll
-                for (int s = 16; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
-                const long long sc = ((part >> a.fa) * a.inv_sqrt) >> a.fa;
-                if (lane == 0) a.scores[(long long)(kv * rep + r) * a.Lmax + l] = sc;
-                wmax[r] = max(wmax[r], sc);
-            }
-        }
+    __syncthreads();                                       // q in shared memory; the new row is in the cache
+    // stage the chunk's keys: coalesced 16-byte loads, rows padded by one word so that a warp reading one
+    // column of 32 consecutive keys touches 32 different banks
+    int32_t *sk = reinterpret_cast<int32_t *>(at_q + rep * a.hd);
+    const int nk = (int)max(0LL, l1 - l0), ld = a.hd + 1, vec_per_row = a.hd / 4;
+    const int4 *src = reinterpret_cast<const int4 *>(a.kcache + ((long long)kv * a.Lmax + l0) * a.hd);
+    for (int i = tid; i < nk * vec_per_row; i += blockDim.x) {
+        const int4 v = src[i];
+        const int row = i / vec_per_row, col = (i - row * vec_per_row) * 4;
+        int32_t *dst = sk + row * ld + col;
+        dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
     }
-    if (lane == 0)
-        for (int r = 0; r < rep; r++) if (wmax[r] != INT64_MIN) atomicMax(&s_max[r], wmax[r]);
+    __syncthreads();
+    // thread -> (key, head group): 64 keys x 4 groups, each group takes every fourth query head
+    const int key = tid & (AT_CH - 1), hg = tid / AT_CH, n_hg = blockDim.x / AT_CH;
+    for (int r = hg; r < rep; r += n_hg) {
+        long long sc = INT64_MIN;
+        if (key < nk) {
+            const long long *qq = at_q + r * a.hd;
+            const int32_t *kk = sk + key * ld;
+            long long dot = 0;
+#pragma unroll 8
+            for (int j = 0; j < a.hd; j++) dot += qq[j] * (long long)kk[j];
+            sc = ((dot >> a.fa) * a.inv_sqrt) >> a.fa;
+            a.scores[(long long)(kv * rep + r) * a.Lmax + l0 + key] = sc;
+        }
+        long long m = sc;
+#pragma unroll
+        for (int s2 = 16; s2 > 0; s2 >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s2));
+        if (lane == 0 && m != INT64_MIN) atomicMax(&s_max[r], m);
+    }
     __syncthreads();
     if (tid < rep && s_max[tid] != INT64_MIN) atomicMax(a.hmax + kv * rep + tid, s_max[tid]);
 }
@@ -168,14 +173,21 @@ __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
     }
     if (tid == 0) s_nl = 1;
     __syncthreads();
+    // stage the chunk's values with coalesced 16-byte loads, then every thread walks its column in shared memory
+    extern __shared__ int32_t at_v[];                      // [AT_CH][hd]
+    {
+        const int4 *src = reinterpret_cast<const int4 *>(a.vcache + ((long long)kv * a.Lmax + l0) * a.hd);
+        int4 *dst = reinterpret_cast<int4 *>(at_v);
+        for (int i = tid; i < nk * (a.hd / 4); i += blockDim.x) dst[i] = src[i];
+    }
+    __syncthreads();
     const int G = blockDim.x / a.hd, grp = tid / a.hd, d = tid - grp * a.hd;      // head groups sharing the CTA
     if (grp < G && nk > 0) {
         long long accv[AT_MAXREP / 2];
 #pragma unroll
         for (int i = 0; i < AT_MAXREP / 2; i++) accv[i] = 0;
-        const int32_t *vbase = a.vcache + ((long long)kv * a.Lmax + l0) * a.hd + d;
         for (int j = 0; j < nk; j++) {
-            const long long v = (long long)vbase[(long long)j * a.hd];
+            const long long v = (long long)at_v[j * a.hd + d];
 #pragma unroll
             for (int i = 0; i < AT_MAXREP / 2; i++) {
                 const int r = grp + i * G;
@@ -285,9 +297,15 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
     long long n_keys = a.pos - lo_min + 1;
     if (a.window > 0 && n_keys > a.window) n_keys = a.window;
     const unsigned chunks = (unsigned)((n_keys + AT_CH - 1) / AT_CH);
-    attn_scores_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)rep * a.hd * 8, s>>>(a);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_pv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess) return cudaGetLastError();
+        configured = true;
+    }
+    attn_scores_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)rep * a.hd * 8 + (size_t)AT_CH * (a.hd + 1) * 4, s>>>(a);
     attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H), 256, 0, s>>>(a);
-    attn_pv_kernel<<<dim3(chunks, a.Hkv), 256, 0, s>>>(a);
+    attn_pv_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)AT_CH * a.hd * 4, s>>>(a);
     note_launch(3);
     return cudaGetLastError();
 }
