@@ -58,11 +58,18 @@ __global__ void attn_reset_kernel(long long *hmax, unsigned long long *Z, long l
 __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
     at_span(a_in, a.pos, a.lo);
-    extern __shared__ long long at_q[];                   // [rep][hd]
+    extern __shared__ __align__(16) long long at_q[];     // [rep][hd] int64, then [rep][hd] int32, then the key chunk
     __shared__ long long s_max[AT_MAXREP];
+    __shared__ int s_wide;
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31;
     const int half = a.hd / 2;
     const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
+    int32_t *q32 = reinterpret_cast<int32_t *>(at_q + rep * a.hd);
+    int32_t *sk = q32 + rep * a.hd;
+    if (tid == 0) s_wide = 0;
+    if (tid < AT_MAXREP) s_max[tid] = INT64_MIN;
+    __syncthreads();
+    bool wide = false;
     for (int idx = tid; idx < rep * half; idx += blockDim.x) {
         const int r = idx / half, i = idx - r * half;
         const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
@@ -70,7 +77,10 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
         int64_t x0 = src[i0], x1 = src[i1];
         at_rotate(a, a.pos, i, x0, x1);
         at_q[r * a.hd + i0] = x0; at_q[r * a.hd + i1] = x1;
+        q32[r * a.hd + i0] = (int32_t)x0; q32[r * a.hd + i1] = (int32_t)x1;
+        wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
     }
+    if (wide) s_wide = 1;
     if (l0 <= a.pos && a.pos < l0 + AT_CH) {              // this CTA owns the new token's cache row
         bool bad = false;
         for (int i = tid; i < half; i += blockDim.x) {
@@ -88,37 +98,51 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
         }
         if (bad) atomicOr(a.flags, 4);
     }
-    if (tid < AT_MAXREP) s_max[tid] = INT64_MIN;
     __syncthreads();                                       // q in shared memory; the new row is in the cache
-    // stage the chunk's keys: coalesced 16-byte loads, rows padded by one word so that a warp reading one
-    // column of 32 consecutive keys touches 32 different banks
-    int32_t *sk = reinterpret_cast<int32_t *>(at_q + rep * a.hd);
-    const int nk = (int)max(0LL, l1 - l0), ld = a.hd + 1, vec_per_row = a.hd / 4;
+    // stage the chunk's keys: coalesced 16-byte loads; rows padded by four words keep them 16-byte aligned and put
+    // the eight rows of a quarter-warp's vector load on different banks
+    const int nk = (int)max(0LL, l1 - l0), ld = a.hd + 4, vec_per_row = a.hd / 4;
     const int4 *src = reinterpret_cast<const int4 *>(a.kcache + ((long long)kv * a.Lmax + l0) * a.hd);
     for (int i = tid; i < nk * vec_per_row; i += blockDim.x) {
-        const int4 v = src[i];
         const int row = i / vec_per_row, col = (i - row * vec_per_row) * 4;
-        int32_t *dst = sk + row * ld + col;
-        dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+        *reinterpret_cast<int4 *>(sk + row * ld + col) = src[i];
     }
     __syncthreads();
-    // thread -> (key, head group): 64 keys x 4 groups, each group takes every fourth query head
-    const int key = tid & (AT_CH - 1), hg = tid / AT_CH, n_hg = blockDim.x / AT_CH;
-    for (int r = hg; r < rep; r += n_hg) {
-        long long sc = INT64_MIN;
+    // thread -> (key, head group): 64 keys x 4 groups; a group takes `hpt` consecutive query heads
+    const int key = tid & (AT_CH - 1), hg = tid / AT_CH, n_hg = blockDim.x / AT_CH, hpt = (rep + n_hg - 1) / n_hg;
+    const bool use_wide = s_wide != 0;
+    for (int r0 = hg * hpt; r0 < min(rep, (hg + 1) * hpt); r0 += 2) {
+        const bool two = r0 + 1 < min(rep, (hg + 1) * hpt);
+        long long d0 = 0, d1 = 0;
         if (key < nk) {
-            const long long *qq = at_q + r * a.hd;
             const int32_t *kk = sk + key * ld;
-            long long dot = 0;
-#pragma unroll 8
-            for (int j = 0; j < a.hd; j++) dot += qq[j] * (long long)kk[j];
-            sc = ((dot >> a.fa) * a.inv_sqrt) >> a.fa;
-            a.scores[(long long)(kv * rep + r) * a.Lmax + l0 + key] = sc;
+            if (!use_wide) {                               // every query value fits 32 bits: one wide multiply-add per term
+                const int32_t *qa = q32 + r0 * a.hd, *qb = q32 + (two ? r0 + 1 : r0) * a.hd;
+                for (int j = 0; j < a.hd; j += 4) {
+                    const int4 k4 = *reinterpret_cast<const int4 *>(kk + j);
+                    const int4 a4 = *reinterpret_cast<const int4 *>(qa + j), b4 = *reinterpret_cast<const int4 *>(qb + j);
+                    d0 += (long long)a4.x * k4.x; d0 += (long long)a4.y * k4.y; d0 += (long long)a4.z * k4.z; d0 += (long long)a4.w * k4.w;
+                    d1 += (long long)b4.x * k4.x; d1 += (long long)b4.y * k4.y; d1 += (long long)b4.z * k4.z; d1 += (long long)b4.w * k4.w;
+                }
+            } else {
+                const long long *qa = at_q + r0 * a.hd, *qb = at_q + (two ? r0 + 1 : r0) * a.hd;
+                for (int j = 0; j < a.hd; j++) { const long long kj = kk[j]; d0 += qa[j] * kj; d1 += qb[j] * kj; }
+            }
         }
-        long long m = sc;
 #pragma unroll
-        for (int s2 = 16; s2 > 0; s2 >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s2));
-        if (lane == 0 && m != INT64_MIN) atomicMax(&s_max[r], m);
+        for (int u = 0; u < 2; u++) {
+            if (u == 1 && !two) break;
+            const int r = r0 + u;
+            long long sc = INT64_MIN;
+            if (key < nk) {
+                sc = (((u ? d1 : d0) >> a.fa) * a.inv_sqrt) >> a.fa;
+                a.scores[(long long)(kv * rep + r) * a.Lmax + l0 + key] = sc;
+            }
+            long long m = sc;
+#pragma unroll
+            for (int s2 = 16; s2 > 0; s2 >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s2));
+            if (lane == 0 && m != INT64_MIN) atomicMax(&s_max[r], m);
+        }
     }
     __syncthreads();
     if (tid < rep && s_max[tid] != INT64_MIN) atomicMax(a.hmax + kv * rep + tid, s_max[tid]);
@@ -155,50 +179,45 @@ __global__ void __launch_bounds__(256) attn_exp_kernel(const AttnArgs a_in) {
 __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
     at_span(a_in, a.pos, a.lo);
-    __shared__ long long s_p[AT_MAXREP][AT_CH];
+    extern __shared__ __align__(16) int32_t at_v[];        // [AT_CH][hd] values, then [AT_CH][AT_MAXREP] probabilities
     __shared__ int s_last, s_nl;
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x;
     const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
     const int nk = (int)max(0LL, l1 - l0);
-    for (int i = tid; i < rep * AT_CH; i += blockDim.x) {
-        const int r = i / AT_CH, j = i - r * AT_CH;
-        long long p = 0;
-        if (j < nk) {
+    int32_t *s_p = at_v + AT_CH * a.hd;                    // p <= 2^fa fits 32 bits
+    for (int i = tid; i < AT_MAXREP * AT_CH; i += blockDim.x) {
+        const int j = i / AT_MAXREP, r = i - j * AT_MAXREP;
+        int32_t p = 0;
+        if (j < nk && r < rep) {
             const int h = kv * rep + r;
             const unsigned long long z = a.Z[h];
             const unsigned long long e = (unsigned long long)(unsigned)a.e[(long long)h * a.Lmax + l0 + j];
-            p = z ? (long long)((e << a.fa) / z) : 0;
+            p = z ? (int32_t)((e << a.fa) / z) : 0;
         }
-        s_p[r][j] = p;
+        s_p[i] = p;
     }
-    if (tid == 0) s_nl = 1;
-    __syncthreads();
-    // stage the chunk's values with coalesced 16-byte loads, then every thread walks its column in shared memory
-    extern __shared__ int32_t at_v[];                      // [AT_CH][hd]
     {
         const int4 *src = reinterpret_cast<const int4 *>(a.vcache + ((long long)kv * a.Lmax + l0) * a.hd);
         int4 *dst = reinterpret_cast<int4 *>(at_v);
         for (int i = tid; i < nk * (a.hd / 4); i += blockDim.x) dst[i] = src[i];
     }
+    if (tid == 0) s_nl = 1;
     __syncthreads();
-    const int G = blockDim.x / a.hd, grp = tid / a.hd, d = tid - grp * a.hd;      // head groups sharing the CTA
+    // thread -> (column d, head group): a group owns four consecutive query heads per pass
+    const int G = blockDim.x / a.hd, grp = tid / a.hd, d = tid - grp * a.hd;
     if (grp < G && nk > 0) {
-        long long accv[AT_MAXREP / 2];
-#pragma unroll
-        for (int i = 0; i < AT_MAXREP / 2; i++) accv[i] = 0;
-        for (int j = 0; j < nk; j++) {
-            const long long v = (long long)at_v[j * a.hd + d];
-#pragma unroll
-            for (int i = 0; i < AT_MAXREP / 2; i++) {
-                const int r = grp + i * G;
-                if (r < rep) accv[i] += s_p[r][j] * v;
+        for (int r0 = grp * 4; r0 < rep; r0 += G * 4) {
+            long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+            for (int j = 0; j < nk; j++) {
+                const int32_t v = at_v[j * a.hd + d];
+                const int4 p4 = *reinterpret_cast<const int4 *>(s_p + j * AT_MAXREP + r0);
+                c0 += (long long)p4.x * v; c1 += (long long)p4.y * v; c2 += (long long)p4.z * v; c3 += (long long)p4.w * v;
             }
-        }
+            const long long cs[4] = {c0, c1, c2, c3};
 #pragma unroll
-        for (int i = 0; i < AT_MAXREP / 2; i++) {
-            const int r = grp + i * G;
-            if (r < rep && accv[i] != 0)
-                atomicAdd(reinterpret_cast<unsigned long long *>(a.acc + (long long)(kv * rep + r) * a.hd + d), (unsigned long long)accv[i]);
+            for (int u = 0; u < 4; u++)
+                if (r0 + u < rep && cs[u] != 0)
+                    atomicAdd(reinterpret_cast<unsigned long long *>(a.acc + (long long)(kv * rep + r0 + u) * a.hd + d), (unsigned long long)cs[u]);
         }
     }
     __threadfence();
@@ -210,18 +229,29 @@ __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
     const long long n = (long long)a.H * a.hd;
     int nl = 1;
     bool over = false;
-    for (long long i = tid; i < n; i += blockDim.x) {
-        const long long y = *((volatile long long *)(a.acc + i)) >> a.fa;
-        if (a.out) a.out[i] = y;
-        if (a.out_limbs) {
-            bool ok;
-            const uint64_t dg = balanced_digits8(y, ok);
-            over |= !ok;
-            nl = max(nl, digits_used(dg));
+    for (long long i0 = 0; i0 < n; i0 += (long long)blockDim.x * 8) {
+        long long yv[8];
 #pragma unroll
-            for (int l = 0; l < 8; l++) a.out_limbs[l * n + i] = (int8_t)(dg >> (8 * l));
+        for (int u = 0; u < 8; u++) {                     // all eight loads in flight before any is used
+            const long long i = i0 + (long long)u * blockDim.x + tid;
+            yv[u] = i < n ? __ldcg(a.acc + i) : 0;
         }
-        a.acc[i] = 0;
+#pragma unroll 1
+        for (int u = 0; u < 8; u++) {
+            const long long i = i0 + (long long)u * blockDim.x + tid;
+            if (i >= n) continue;
+            const long long y = yv[u] >> a.fa;
+            if (a.out) a.out[i] = y;
+            if (a.out_limbs) {
+                bool ok;
+                const uint64_t dg = balanced_digits8(y, ok);
+                over |= !ok;
+                nl = max(nl, digits_used(dg));
+#pragma unroll
+                for (int l = 0; l < 8; l++) a.out_limbs[l * n + i] = (int8_t)(dg >> (8 * l));
+            }
+            a.acc[i] = 0;
+        }
     }
     if (over) atomicOr(a.flags, 1);
     if (a.out_limbs) atomicMax(&s_nl, nl);
@@ -303,9 +333,9 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
             cudaFuncSetAttribute(attn_pv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess) return cudaGetLastError();
         configured = true;
     }
-    attn_scores_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)rep * a.hd * 8 + (size_t)AT_CH * (a.hd + 1) * 4, s>>>(a);
+    attn_scores_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)rep * a.hd * 12 + (size_t)AT_CH * (a.hd + 4) * 4, s>>>(a);
     attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H), 256, 0, s>>>(a);
-    attn_pv_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)AT_CH * a.hd * 4, s>>>(a);
+    attn_pv_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)AT_CH * a.hd * 4 + (size_t)AT_CH * AT_MAXREP * 4, s>>>(a);
     note_launch(3);
     return cudaGetLastError();
 }
