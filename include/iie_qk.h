@@ -178,6 +178,9 @@ int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t
                        const int *pos_dev, long long window, const int64_t *cos_dev, const int64_t *sin_dev, int rope,
                        int n_heads, int n_kv, int head_dim, long long cache_rows, int fa, int fw, long long inv_sqrt,
                        void *stream);
+/* 1 (default): the three attention passes run as one cooperative launch whenever all of its CTAs fit on the device
+ * at once (contexts up to roughly 4700 visible keys per KV head on B200); 0: always three launches. */
+void iie_set_attn_fused(int enabled);
 /* Row `token` (or *token_dev when token_dev != NULL) of a registered Q4_K / Q6_K matrix as int64 at 2^frac:
  * the embedding look-up (north-mini-code/src/nmc/engine.py:239-243). */
 int iie_embed_dev(long long h, const int *token_dev, long long token, int frac, int64_t *out_dev, void *stream);

@@ -71,7 +71,7 @@ inline bool stage_on(int st) { return g_stage_mask == 0 || (g_stage_mask & st); 
 
 // Persistent device scratch by role, grown on demand (never shrunk until released).
 enum Role { R_X, R_XL, R_OUT, R_RAW, R_GU, R_GUL, R_TMP0, R_TMP1, R_TMP2, R_TABS, R_META, R_LOGITS, R_IDS, R_GATES,
-            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_ASCORES, R_AEXP, R_ASTAT, R_COUNT };
+            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_ASCORES, R_AEXP, R_ASTAT, R_APART, R_COUNT };
 struct Buf { void *p = nullptr; size_t cap = 0; };
 Buf g_buf[R_COUNT];
 long long g_ws_allocs = 0;
@@ -923,7 +923,8 @@ bool attn_scratch(AttnArgs &a, cudaStream_t s) {
     a.scores = (int64_t *)ensure(R_ASCORES, (size_t)a.H * a.Lmax * 8);
     a.e = (int32_t *)ensure(R_AEXP, (size_t)a.H * a.Lmax * 4);
     uint8_t *st = (uint8_t *)ensure(R_ASTAT, (size_t)a.H * 16 + (size_t)a.H * a.hd * 8 + 64);
-    if (!a.scores || !a.e || !st) return false;
+    a.partial = (long long *)ensure(R_APART, (size_t)((a.Lmax + 63) / 64) * a.H * a.hd * 8);
+    if (!a.scores || !a.e || !st || !a.partial) return false;
     a.hmax = (long long *)st; a.Z = (unsigned long long *)(st + (size_t)a.H * 8);
     a.acc = (long long *)(st + (size_t)a.H * 16); a.ticket = (unsigned *)(st + (size_t)a.H * 16 + (size_t)a.H * a.hd * 8);
     if (st != last_ptr || a.H != last_h || a.hd != last_hd) {
@@ -1042,6 +1043,11 @@ extern "C" int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long
 extern "C" void iie_set_tc_min_tokens(long long tokens) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     g_tc_min_tokens = tokens < 2 ? 2 : tokens;
+}
+
+extern "C" void iie_set_attn_fused(int enabled) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    iie::g_attn_fused = enabled ? 1 : 0;
 }
 
 extern "C" void iie_set_fused_route(int enabled) {

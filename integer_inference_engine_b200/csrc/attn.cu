@@ -19,11 +19,17 @@
 // shared statistics, so a call is exactly three launches.
 // The cache holds K (after rotation) and V as int32: values outside int32 raise flag bit 2 (the reference bank
 // stores them the same way and refuses such values).
+#include <cooperative_groups.h>
+
 #include "kernels.h"
 #include "layout.cuh"
 #include "mma_items.cuh"
 
+namespace cg = cooperative_groups;
+
 namespace iie {
+
+int g_attn_fused = 1;                      // 1: the three passes as one cooperative launch when every CTA fits on the device
 
 namespace {
 
@@ -43,6 +49,19 @@ __device__ __forceinline__ void at_rotate(const AttnArgs &a, long long pos, int 
     const int64_t c = a.cos[pos * half + i], s = a.sin[pos * half + i];
     const int64_t y0 = (x0 * c - x1 * s) >> a.fa, y1 = (x0 * s + x1 * c) >> a.fa;
     x0 = y0; x1 = y1;
+}
+
+// Copy n 16-byte vectors from global to shared memory with eight loads of a thread in flight before the first
+// store (a plain loop would wait for every load in turn).  dst_of(i) gives the destination vector index.
+template <typename F>
+__device__ __forceinline__ void at_stage(const int4 *src, int n, int tid, int nth, int32_t *dst_base, F dst_of) {
+    for (int i0 = 0; i0 < n; i0 += nth * 8) {
+        int4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) { const int i = i0 + u * nth + tid; if (i < n) v[u] = src[i]; }
+#pragma unroll
+        for (int u = 0; u < 8; u++) { const int i = i0 + u * nth + tid; if (i < n) *reinterpret_cast<int4 *>(dst_base + dst_of(i)) = v[u]; }
+    }
 }
 
 __global__ void attn_reset_kernel(long long *hmax, unsigned long long *Z, long long *acc, unsigned *ticket, int H, int hd) {
@@ -102,11 +121,8 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
     // stage the chunk's keys: coalesced 16-byte loads; rows padded by four words keep them 16-byte aligned and put
     // the eight rows of a quarter-warp's vector load on different banks
     const int nk = (int)max(0LL, l1 - l0), ld = a.hd + 4, vec_per_row = a.hd / 4;
-    const int4 *src = reinterpret_cast<const int4 *>(a.kcache + ((long long)kv * a.Lmax + l0) * a.hd);
-    for (int i = tid; i < nk * vec_per_row; i += blockDim.x) {
-        const int row = i / vec_per_row, col = (i - row * vec_per_row) * 4;
-        *reinterpret_cast<int4 *>(sk + row * ld + col) = src[i];
-    }
+    at_stage(reinterpret_cast<const int4 *>(a.kcache + ((long long)kv * a.Lmax + l0) * a.hd), nk * vec_per_row, tid, blockDim.x, sk,
+             [&](int i) { const int row = i / vec_per_row; return row * ld + (i - row * vec_per_row) * 4; });
     __syncthreads();
     // thread -> (key, head group): 64 keys x 4 groups; a group takes `hpt` consecutive query heads
     const int key = tid & (AT_CH - 1), hg = tid / AT_CH, n_hg = blockDim.x / AT_CH, hpt = (rep + n_hg - 1) / n_hg;
@@ -196,11 +212,8 @@ __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
         }
         s_p[i] = p;
     }
-    {
-        const int4 *src = reinterpret_cast<const int4 *>(a.vcache + ((long long)kv * a.Lmax + l0) * a.hd);
-        int4 *dst = reinterpret_cast<int4 *>(at_v);
-        for (int i = tid; i < nk * (a.hd / 4); i += blockDim.x) dst[i] = src[i];
-    }
+    at_stage(reinterpret_cast<const int4 *>(a.vcache + ((long long)kv * a.Lmax + l0) * a.hd), nk * (a.hd / 4), tid, blockDim.x, at_v,
+             [](int i) { return i * 4; });
     if (tid == 0) s_nl = 1;
     __syncthreads();
     // thread -> (column d, head group): a group owns four consecutive query heads per pass
@@ -258,6 +271,188 @@ __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
     for (int i = tid; i < a.H; i += blockDim.x) { a.hmax[i] = INT64_MIN; a.Z[i] = 0ULL; }
     __syncthreads();
     if (tid == 0) { *a.ticket = 0u; if (a.out_nl) *a.out_nl = s_nl; }
+}
+
+// The three passes in ONE cooperative launch (all CTAs co-resident, two grid-wide barriers): scores and
+// exponentials stay in registers, the value chunk is requested into shared memory together with the key chunk so
+// its latency is hidden behind the first two passes, and nothing but the statistics goes through global memory.
+__global__ void __launch_bounds__(256) attn_fused_kernel(const AttnArgs a_in) {
+    AttnArgs a = a_in;
+    at_span(a_in, a.pos, a.lo);
+    cg::grid_group grid = cg::this_grid();
+    extern __shared__ __align__(16) long long at_q[];     // q int64 [rep][hd], q int32 [rep][hd], keys [CH][hd+4], values [CH][hd], p [CH][MAXREP]
+    __shared__ long long s_max[AT_MAXREP];
+    __shared__ unsigned long long s_z[AT_MAXREP];
+    __shared__ int s_wide;
+    const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31;
+    const int half = a.hd / 2;
+    const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
+    const int nk = (int)max(0LL, l1 - l0), ld = a.hd + 4, vec_per_row = a.hd / 4;
+    int32_t *q32 = reinterpret_cast<int32_t *>(at_q + rep * a.hd);
+    int32_t *sk = q32 + rep * a.hd;
+    int32_t *sv = sk + AT_CH * ld;
+    int32_t *s_p = sv + AT_CH * a.hd;
+    if (tid == 0) s_wide = 0;
+    if (tid < AT_MAXREP) { s_max[tid] = INT64_MIN; s_z[tid] = 0ULL; }
+    __syncthreads();
+    bool wide = false;
+    for (int idx = tid; idx < rep * half; idx += blockDim.x) {
+        const int r = idx / half, i = idx - r * half;
+        const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
+        const int64_t *src = a.q + (long long)(kv * rep + r) * a.hd;
+        int64_t x0 = src[i0], x1 = src[i1];
+        at_rotate(a, a.pos, i, x0, x1);
+        at_q[r * a.hd + i0] = x0; at_q[r * a.hd + i1] = x1;
+        q32[r * a.hd + i0] = (int32_t)x0; q32[r * a.hd + i1] = (int32_t)x1;
+        wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+    }
+    if (wide) s_wide = 1;
+    if (l0 <= a.pos && a.pos < l0 + AT_CH) {              // this CTA owns the new token's cache row
+        bool bad = false;
+        for (int i = tid; i < half; i += blockDim.x) {
+            const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
+            int64_t x0 = a.k[kv * a.hd + i0], x1 = a.k[kv * a.hd + i1];
+            at_rotate(a, a.pos, i, x0, x1);
+            bad |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+            int32_t *dst = a.kcache + ((long long)kv * a.Lmax + a.pos) * a.hd;
+            dst[i0] = (int32_t)x0; dst[i1] = (int32_t)x1;
+        }
+        for (int i = tid; i < a.hd; i += blockDim.x) {
+            const int64_t v = a.v[kv * a.hd + i];
+            bad |= v != (int32_t)v;
+            a.vcache[((long long)kv * a.Lmax + a.pos) * a.hd + i] = (int32_t)v;
+        }
+        if (bad) atomicOr(a.flags, 4);
+    }
+    __syncthreads();
+    at_stage(reinterpret_cast<const int4 *>(a.kcache + ((long long)kv * a.Lmax + l0) * a.hd), nk * vec_per_row, tid, blockDim.x, sk,
+             [&](int i) { const int row = i / vec_per_row; return row * ld + (i - row * vec_per_row) * 4; });
+    at_stage(reinterpret_cast<const int4 *>(a.vcache + ((long long)kv * a.Lmax + l0) * a.hd), nk * vec_per_row, tid, blockDim.x, sv,
+             [](int i) { return i * 4; });
+    __syncthreads();
+    // ---- pass 1: thread -> (key, head group); a group takes `hpt` (<= 4) consecutive query heads -------------------
+    const int key = tid & (AT_CH - 1), hg = tid / AT_CH, n_hg = blockDim.x / AT_CH, hpt = (rep + n_hg - 1) / n_hg;
+    const int r_lo = hg * hpt, r_hi = min(rep, (hg + 1) * hpt);
+    const bool use_wide = s_wide != 0;
+    long long sc[4] = {INT64_MIN, INT64_MIN, INT64_MIN, INT64_MIN};
+#pragma unroll
+    for (int pr = 0; pr < 2; pr++) {
+        const int r0 = r_lo + 2 * pr;
+        if (r0 >= r_hi) break;
+        const bool two = r0 + 1 < r_hi;
+        long long d0 = 0, d1 = 0;
+        if (key < nk) {
+            const int32_t *kk = sk + key * ld;
+            if (!use_wide) {
+                const int32_t *qa = q32 + r0 * a.hd, *qb = q32 + (two ? r0 + 1 : r0) * a.hd;
+                for (int j = 0; j < a.hd; j += 4) {
+                    const int4 k4 = *reinterpret_cast<const int4 *>(kk + j);
+                    const int4 a4 = *reinterpret_cast<const int4 *>(qa + j), b4 = *reinterpret_cast<const int4 *>(qb + j);
+                    d0 += (long long)a4.x * k4.x; d0 += (long long)a4.y * k4.y; d0 += (long long)a4.z * k4.z; d0 += (long long)a4.w * k4.w;
+                    d1 += (long long)b4.x * k4.x; d1 += (long long)b4.y * k4.y; d1 += (long long)b4.z * k4.z; d1 += (long long)b4.w * k4.w;
+                }
+            } else {
+                const long long *qa = at_q + r0 * a.hd, *qb = at_q + (two ? r0 + 1 : r0) * a.hd;
+                for (int j = 0; j < a.hd; j++) { const long long kj = kk[j]; d0 += qa[j] * kj; d1 += qb[j] * kj; }
+            }
+            sc[2 * pr] = ((d0 >> a.fa) * a.inv_sqrt) >> a.fa;
+            if (two) sc[2 * pr + 1] = ((d1 >> a.fa) * a.inv_sqrt) >> a.fa;
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        if (r_lo + u >= r_hi) break;
+        long long m = sc[u];
+#pragma unroll
+        for (int s2 = 16; s2 > 0; s2 >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s2));
+        if (lane == 0 && m != INT64_MIN) atomicMax(&s_max[r_lo + u], m);
+    }
+    __syncthreads();
+    if (tid < rep && s_max[tid] != INT64_MIN) atomicMax(a.hmax + kv * rep + tid, s_max[tid]);
+    grid.sync();
+    // ---- pass 2: exponentials (kept in registers) and their sum ---------------------------------------------------------
+    unsigned ev[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        if (r_lo + u >= r_hi) break;
+        unsigned long long e = 0;
+        if (key < nk) {
+            long long dlt = __ldcg(a.hmax + kv * rep + r_lo + u) - sc[u];
+            dlt = dlt < a.clip ? dlt : a.clip;
+            e = (unsigned long long)exp2_neg_fixed((dlt * a.log2e) >> a.fa, a.fa);
+            ev[u] = (unsigned)e;
+        }
+#pragma unroll
+        for (int s2 = 16; s2 > 0; s2 >>= 1) e += __shfl_xor_sync(0xffffffffu, e, s2);
+        if (lane == 0 && e) atomicAdd(&s_z[r_lo + u], e);
+    }
+    __syncthreads();
+    if (tid < rep && s_z[tid]) atomicAdd(a.Z + kv * rep + tid, s_z[tid]);
+    grid.sync();
+    // ---- pass 3: probabilities into shared memory, then probabilities x values ------------------------------------------
+    for (int i = tid; i < AT_MAXREP * AT_CH; i += blockDim.x) s_p[i] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        if (r_lo + u >= r_hi) break;
+        if (key < nk) {
+            const unsigned long long z = __ldcg(a.Z + kv * rep + r_lo + u);
+            s_p[key * AT_MAXREP + r_lo + u] = z ? (int32_t)(((unsigned long long)ev[u] << a.fa) / z) : 0;
+        }
+    }
+    __syncthreads();
+    const int G = blockDim.x / a.hd, grp = tid / a.hd, d = tid - grp * a.hd;
+    long long *part = a.partial + ((long long)blockIdx.x * a.Hkv + kv) * rep * a.hd;      // this CTA's [rep][hd] partial sums
+    if (grp < G) {
+        for (int r0 = grp * 4; r0 < rep; r0 += G * 4) {
+            long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+            for (int j = 0; j < nk; j++) {
+                const int32_t v = sv[j * a.hd + d];
+                const int4 p4 = *reinterpret_cast<const int4 *>(s_p + j * AT_MAXREP + r0);
+                c0 += (long long)p4.x * v; c1 += (long long)p4.y * v; c2 += (long long)p4.z * v; c3 += (long long)p4.w * v;
+            }
+            const long long cs[4] = {c0, c1, c2, c3};
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (r0 + u < rep) part[(r0 + u) * a.hd + d] = cs[u];
+        }
+    }
+    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && a.out_nl) *a.out_nl = 1;
+    grid.sync();
+    // ---- pass 4: every output is the sum of the chunk partials; sixteen lanes share one output ---------------------------
+    if (blockIdx.x == 0 && blockIdx.y == 0)
+        for (int i = tid; i < a.H; i += blockDim.x) { a.hmax[i] = INT64_MIN; a.Z[i] = 0ULL; }     // nobody reads them any more
+    const long long n = (long long)a.H * a.hd;
+    const int used = (int)((a.pos - a.lo) / AT_CH) + 1;                      // chunks that held keys
+    const long long gid = ((long long)(blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + tid);
+    const long long n_groups = (long long)gridDim.x * gridDim.y * blockDim.x / 16;
+    const int sub = (int)(gid & 15);
+    int nl = 1;
+    bool over = false;
+    for (long long o = gid >> 4; o < n + 15; o += n_groups) {                // +15: whole 16-lane groups stay together for the shuffles
+        long long sum = 0;
+        if (o < n) {
+            const int h = (int)(o / a.hd), dd = (int)(o - (long long)h * a.hd), kvh = h / rep, r = h - kvh * rep;
+            for (int c = sub; c < used; c += 16)
+                sum += __ldcg(a.partial + (((long long)c * a.Hkv + kvh) * rep + r) * a.hd + dd);
+        }
+#pragma unroll
+        for (int s2 = 8; s2 > 0; s2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s2);
+        if (o < n && sub == 0) {
+            const long long y = sum >> a.fa;
+            if (a.out) a.out[o] = y;
+            if (a.out_limbs) {
+                bool ok;
+                const uint64_t dg = balanced_digits8(y, ok);
+                over |= !ok;
+                nl = max(nl, digits_used(dg));
+#pragma unroll
+                for (int l = 0; l < 8; l++) a.out_limbs[l * n + o] = (int8_t)(dg >> (8 * l));
+            }
+        }
+    }
+    if (over) atomicOr(a.flags, 1);
+    if (a.out_limbs && a.out_nl && nl > 1) atomicMax(a.out_nl, nl);
 }
 
 // one row of a registered Q4_K / Q6_K matrix as int64 at 2^frac (the embedding look-up)
@@ -328,10 +523,32 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
     if (a.window > 0 && n_keys > a.window) n_keys = a.window;
     const unsigned chunks = (unsigned)((n_keys + AT_CH - 1) / AT_CH);
     static bool configured = false;
+    static int n_sms = 0;
+    const int rep4 = (rep + 3) / 4;                       // the fused kernel keeps at most four heads per thread
+    const size_t fused_smem = (size_t)rep * a.hd * 12 + (size_t)AT_CH * (a.hd + 4) * 4 + (size_t)AT_CH * a.hd * 4 + (size_t)AT_CH * AT_MAXREP * 4;
     if (!configured) {
         if (cudaFuncSetAttribute(attn_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
-            cudaFuncSetAttribute(attn_pv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess) return cudaGetLastError();
+            cudaFuncSetAttribute(attn_pv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return cudaGetLastError();
+        int dev = 0, coop = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+        if (!coop) n_sms = 0;
         configured = true;
+    }
+    bool fused = g_attn_fused && a.partial && n_sms > 0 && rep4 <= 256 / AT_CH && fused_smem <= 200 * 1024;
+    if (fused) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_fused_kernel, 256, fused_smem) != cudaSuccess) { cudaGetLastError(); per_sm = 0; }
+        fused = (long long)chunks * a.Hkv <= (long long)per_sm * n_sms;      // a cooperative launch needs every CTA resident
+    }
+    if (fused) {
+        AttnArgs copy = a;
+        void *params[] = {&copy};
+        const cudaError_t e = cudaLaunchCooperativeKernel((const void *)attn_fused_kernel, dim3(chunks, a.Hkv), dim3(256), params, fused_smem, s);
+        note_launch(1);
+        return e != cudaSuccess ? e : cudaGetLastError();
     }
     attn_scores_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)rep * a.hd * 12 + (size_t)AT_CH * (a.hd + 4) * 4, s>>>(a);
     attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H), 256, 0, s>>>(a);

@@ -214,12 +214,14 @@ struct AttnArgs {
     unsigned long long *Z;         // scratch [H]
     long long *acc;                // scratch [H][hd]
     unsigned *ticket;              // scratch
+    long long *partial;            // scratch [ceil(Lmax/64)][Hkv][H/Hkv][hd]: per-chunk partial sums of the one-launch form
     int64_t *out;                  // [H*hd], nullable
     int8_t *out_limbs;             // nullable: digit planes [8][H*hd] of the result
     int *out_nl;                   // nullable: digits in use by the result
     int *flags;                    // bit 0 digit envelope, bit 2 a key / value does not fit the int32 cache
 };
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s);
+extern int g_attn_fused;           // 1: one cooperative launch when all CTAs are co-resident, else three launches
 // hmax = INT64_MIN, Z = acc = ticket = 0: once after the statistics buffer is (re)allocated; every call leaves them so
 cudaError_t launch_attn_reset(long long *hmax, unsigned long long *Z, long long *acc, unsigned *ticket, int H, int hd, cudaStream_t s);
 cudaError_t launch_embed_row(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,
