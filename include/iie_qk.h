@@ -178,6 +178,9 @@ int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t
                        const int *pos_dev, long long window, const int64_t *cos_dev, const int64_t *sin_dev, int rope,
                        int n_heads, int n_kv, int head_dim, long long cache_rows, int fa, int fw, long long inv_sqrt,
                        void *stream);
+/* 1 (default): batches of 2 .. tc_min_tokens-1 rows stream every touched expert tile once for all of its rows;
+ * 0: the older kernel that re-reads a tile for every four rows.  Results are identical; for measurements. */
+void iie_set_batch_stream(int enabled);
 /* 1 (default): the three attention passes run as one cooperative launch whenever all of its CTAs fit on the device
  * at once (contexts up to roughly 4700 visible keys per KV head on B200); 0: always three launches. */
 void iie_set_attn_fused(int enabled);

@@ -58,6 +58,7 @@ int *g_flags = nullptr;               // device flag word
 int *g_cells = nullptr;               // device ints: [0] limbs of h, [1] limbs of gate*up, [2] routing ticket
 const uint8_t **g_selptr = nullptr;   // device: [3][64] pointers of the experts the last routing selected
 int g_pdl = 1;                        // programmatic dependent launch between the decode kernels
+int g_batch_stream = 1;               // small batches: stream each touched expert tile once (batch.cu) instead of per 4 rows
 int g_fused_expert = 0;               // single-token expert stage as one cluster launch (expert.cu): slower on this part
 int g_fused_route = 0;                // routing recomputed inside the gate/up launch (rgu.cu): slower than its own launch
 long long g_hl_d = 0;                 // width of the digit planes the last single-token routing left in the R_XL scratch
@@ -231,14 +232,31 @@ struct MoePlan {                      // everything the fused MoE kernels need o
 // rows of gu are produced.  out [T,d_model] must be initialised by the caller.
 bool moe_fused(const MoePlan &p, const int8_t *hl, bool x_bcast_zero, const int *xidx, const int *grp_expert,
                const int *grp_off, int n_groups, long long n_pairs, int max_pairs, const int64_t *pair_gate,
-               const int *pair_tok, int fa, int fw, int64_t *out, cudaStream_t s) {
+               const int *pair_tok, int fa, int fw, int64_t *out, cudaStream_t s, const int *h_nl = nullptr,
+               unsigned maxd_gate = 0x7C00, unsigned maxdmin_gate = 0x7C00, unsigned maxd_down = 0x7C00, unsigned maxdmin_down = 0x7C00) {
     int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)n_pairs * 8 * p.e_ffn);
     if (!gul) return false;
+    (void)x_bcast_zero;
+    if (!grp_expert && grp_off && g_batch_stream && g_stage_mask == 0) {
+        // groups are the experts themselves: stream every touched expert tile once for all of its rows
+        if (cudaMemsetAsync(g_cells + 1, 0, sizeof(int), s) != cudaSuccess) return false;
+        BatchArgs ga = {};
+        ga.wa = p.gate; ga.wb = p.up; ga.grp_off = grp_off; ga.n_groups = n_groups; ga.out_f = p.e_ffn; ga.n_blocks = p.d_model / 256;
+        ga.fw = fw; ga.fa = fa; ga.fast = small_scales(maxd_gate, maxdmin_gate, fw); ga.xl = hl; ga.xidx = xidx; ga.x_nl = h_nl;
+        ga.out = nullptr; ga.out_limbs = gul; ga.out_nl = g_cells + 1; ga.flags = g_flags;
+        BatchArgs da = {};
+        da.wa = p.down; da.wb = p.down; da.grp_off = grp_off; da.n_groups = n_groups; da.out_f = p.d_model; da.n_blocks = p.e_ffn / 256;
+        da.fw = fw; da.fa = fa; da.fast = small_scales(maxd_down, maxdmin_down, fw); da.xl = gul; da.xidx = nullptr; da.x_nl = g_cells + 1;
+        da.out = out; da.gates = pair_gate; da.pair_tok = pair_tok; da.flags = g_flags;
+        const cudaError_t e1 = launch_batch(p.gate_q, MODE_GATEUP, ga, s);
+        if (e1 == cudaSuccess) return launch_batch(p.down_q, MODE_DOWN, da, s) == cudaSuccess;
+        cudaGetLastError();
+        if (e1 != cudaErrorNotSupported) return false;
+    }
     SkinnyArgs a = {};
     a.wa = p.gate; a.wb = p.up; a.grp_expert = grp_expert; a.grp_off = grp_off; a.pairs_per_group = 1;
     a.out_f = p.e_ffn; a.n_blocks = p.d_model / 256; a.fw = fw; a.fa = fa; a.xl = hl; a.xidx = xidx;
     a.out = nullptr; a.out_limbs = gul; a.flags = g_flags;
-    (void)x_bcast_zero;
     if (stage_on(ST_GATEUP) && launch_skinny(p.gate_q, MODE_GATEUP, a, n_groups, max_pairs, s) != cudaSuccess) return false;
     SkinnyArgs d = {};
     d.wa = p.down; d.wb = p.down; d.grp_expert = grp_expert; d.grp_off = grp_off; d.pairs_per_group = 1;
@@ -359,7 +377,8 @@ int moe_prefill_tc(const MoeLayer &L, const int64_t *h_dev, long long T, int fa,
     if (!off || !ptok || !pg || launch_dispatch(ids, gates, T, k, E, off, ptok, pg, s) != cudaSuccess) return 1;
     if (!accumulate && cudaMemsetAsync(out_dev, 0, (size_t)T * L.d_model * 8, s) != cudaSuccess) return 1;
     MoePlan plan = {L.tabs, L.tabs + E, L.tabs + 2 * E, L.gate_q, L.down_q, L.d_model, L.e_ffn};
-    return moe_fused(plan, hl, false, ptok, nullptr, off, E, T * k, (int)std::min<long long>(T, 4), pg, ptok, fa, fw, out_dev, s) ? 0 : 1;
+    return moe_fused(plan, hl, false, ptok, nullptr, off, E, T * k, (int)std::min<long long>(T, 4), pg, ptok, fa, fw, out_dev, s, g_cells,
+                     L.maxd_gate, L.maxdmin_gate, L.maxd_down, L.maxdmin_down) ? 0 : 1;
 }
 
 // Single-token fused path: route (optional RMSNorm, limbs, router, top-k) -> gate/up -> down.
@@ -832,7 +851,8 @@ extern "C" int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long l
     int8_t *hl = (int8_t *)ensure(R_XL, (size_t)T * 8 * L.d_model);
     int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)T * E * 8);
     if (!hl || !lg) return 1;
-    if (stage_on(ST_LIMBS) && launch_limbs(h_dev, T, L.d_model, hl, g_flags, s) != cudaSuccess) return 1;
+    if (stage_on(ST_LIMBS) && (cudaMemsetAsync(g_cells, 0, sizeof(int), s) != cudaSuccess ||
+                               launch_limbs(h_dev, T, L.d_model, hl, g_flags, s, g_cells) != cudaSuccess)) return 1;
     if (stage_on(ST_ROUTER)) {
         if (r.qtype == QT_I64) {
             if (launch_exact_dense((const int64_t *)r.d, E, L.d_model, h_dev, T, fw, lg, g_flags, s) != cudaSuccess) return 1;
@@ -854,7 +874,8 @@ extern "C" int iie_moe_forward_dev(long long layer, const int64_t *h_dev, long l
         int *ptok = (int *)ensure(R_PAIRTOK, (size_t)P * sizeof(int));
         int64_t *pg = (int64_t *)ensure(R_PAIRGATE, (size_t)P * 8);
         if (!off || !ptok || !pg || launch_dispatch(ids, gates, T, k, E, off, ptok, pg, s) != cudaSuccess) return 1;
-        ok = moe_fused(plan, hl, false, ptok, nullptr, off, E, P, (int)std::min<long long>(T, 4), pg, ptok, fa, fw, out_dev, s);
+        ok = moe_fused(plan, hl, false, ptok, nullptr, off, E, P, (int)std::min<long long>(T, 4), pg, ptok, fa, fw, out_dev, s, g_cells,
+                       L.maxd_gate, L.maxdmin_gate, L.maxd_down, L.maxdmin_down);
     }
     if (!ok) { cudaGetLastError(); return 1; }
     return 0;
@@ -907,7 +928,8 @@ extern "C" int iie_moe_experts_dev(long long layer, const int64_t *h_dev, long l
     if (!off || !ptok || !pg || launch_dispatch(ids_dev, gates_dev, T, slots, E, off, ptok, pg, s, expert_base) != cudaSuccess) return 1;
     if (!accumulate && cudaMemsetAsync(out_dev, 0, (size_t)T * L.d_model * 8, s) != cudaSuccess) return 1;
     MoePlan plan = {L.tabs, L.tabs + E, L.tabs + 2 * E, L.gate_q, L.down_q, L.d_model, L.e_ffn};
-    if (!moe_fused(plan, hl, false, ptok, nullptr, off, E, P, (int)std::min<long long>(T, 4), pg, ptok, fa, fw, out_dev, s)) {
+    if (!moe_fused(plan, hl, false, ptok, nullptr, off, E, P, (int)std::min<long long>(T, 4), pg, ptok, fa, fw, out_dev, s, g_cells,
+                   L.maxd_gate, L.maxdmin_gate, L.maxd_down, L.maxdmin_down)) {
         cudaGetLastError(); return 1;
     }
     return 0;
@@ -1043,6 +1065,11 @@ extern "C" int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long
 extern "C" void iie_set_tc_min_tokens(long long tokens) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     g_tc_min_tokens = tokens < 2 ? 2 : tokens;
+}
+
+extern "C" void iie_set_batch_stream(int enabled) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    g_batch_stream = enabled ? 1 : 0;
 }
 
 extern "C" void iie_set_attn_fused(int enabled) {

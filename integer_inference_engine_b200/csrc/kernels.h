@@ -88,6 +88,28 @@ struct RouteArgs {
 };
 cudaError_t launch_route(const RouteArgs &a, cudaStream_t s);
 
+// Grouped products for small batches (batch.cu): group e = expert e with the rows [grp_off[e], grp_off[e+1]).
+struct BatchArgs {
+    const uint8_t *const *wa;      // per expert: linear / down weight, or gate
+    const uint8_t *const *wb;      // per expert: up weight (MODE_GATEUP)
+    const int *grp_off;            // device [n_groups + 1]
+    int n_groups;
+    long long out_f, n_blocks;
+    int fw, fa, fast;
+    const int8_t *xl;              // digit planes [x_row][8][K]
+    const int *xidx;               // pair -> x_row, or nullptr (identity)
+    const int *x_nl;               // device: digits in use by x (<= 4 enables the half-column path), or nullptr
+    int64_t *out;                  // LINEAR [pair][out_f]; GATEUP gu [pair][out_f] (nullable); DOWN [token][out_f] accumulated
+    int8_t *out_limbs;             // GATEUP: digit planes of gu [pair][8][out_f]
+    int *out_nl;                   // GATEUP: atomicMax of the digits gu needs
+    const int64_t *gates;          // DOWN: per pair
+    const int *pair_tok;           // DOWN: pair -> token row
+    int *flags;
+    int tiles_per_expert, tiles_per_cta;   // filled in by the launcher
+    long long sig_log2e, sig_clip;
+};
+cudaError_t launch_batch(int qtype, int mode, const BatchArgs &a, cudaStream_t s);
+
 // Single-token routing + gate/up in one launch (rgu.cu): every CTA recomputes the routing, then multiplies its
 // run of gate/up tiles of the selected experts.
 struct RoutedGateUpArgs {

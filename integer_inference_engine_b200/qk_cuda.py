@@ -45,7 +45,7 @@ EXPORTED_SYMBOLS = (
     "iie_moe_forward_dev", "iie_apply_dev", "iie_flags_read_clear", "iie_rmsnorm_dev", "iie_profile_stage_mask",
     "iie_launch_count", "iie_moe_block_host", "iie_moe_block_dev", "iie_set_pdl",
     "iie_apply_dev_static", "iie_set_tc_min_tokens", "iie_route_dev", "iie_moe_experts_dev",
-    "iie_set_fused_expert", "iie_expert_clusters", "iie_set_fused_route", "iie_attn_decode_dev", "iie_embed_dev", "iie_argmax_dev", "iie_attn_block_dev", "iie_set_attn_fused",
+    "iie_set_fused_expert", "iie_expert_clusters", "iie_set_fused_route", "iie_attn_decode_dev", "iie_embed_dev", "iie_argmax_dev", "iie_attn_block_dev", "iie_set_attn_fused", "iie_set_batch_stream",
 )
 # The library keeps one registry and one set of workspaces per process and ctypes releases the GIL:
 # serialise callers here as the reference bridge does (qk_cuda.py:35-38).
@@ -110,7 +110,7 @@ def load_library():
         "iie_set_tc_min_tokens": ([i64], None), "iie_set_fused_expert": ([c_int], None), "iie_expert_clusters": ([], c_int), "iie_set_fused_route": ([c_int], None),
         "iie_attn_decode_dev": ([vp, vp, vp, vp, vp, i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, i64, vp, vp], c_int),
         "iie_attn_block_dev": ([i64, i64, vp, vp, vp, i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, c_int, i64, vp], c_int),
-        "iie_embed_dev": ([i64, vp, i64, c_int, vp, vp], c_int), "iie_set_attn_fused": ([c_int], None), "iie_argmax_dev": ([vp, i64, vp, vp], c_int),
+        "iie_embed_dev": ([i64, vp, i64, c_int, vp, vp], c_int), "iie_set_attn_fused": ([c_int], None), "iie_set_batch_stream": ([c_int], None), "iie_argmax_dev": ([vp, i64, vp, vp], c_int),
         "iie_route_dev": ([i64, c_int, vp, i64, c_int, c_int, vp, vp, vp], c_int),
         "iie_moe_experts_dev": ([i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, c_int, vp, vp], c_int),
         "iie_moe_block_host": ([i64, i64, vp, i64, c_int, c_int, u64, vp, vp, vp], c_int),
