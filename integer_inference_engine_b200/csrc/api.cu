@@ -207,6 +207,15 @@ bool linear_dev(const Weight &w, const int64_t *x, long long T, int fw, int64_t 
         sa.xl = xl; sa.x_per_sel = 0; sa.x_nl = nullptr; sa.out = out; sa.flags = g_flags;
         sa.fast = small_scales(w.maxd, w.maxdmin, fw); sa.pdl = 0;
         if (launch_stream(w.qtype, MODE_LINEAR, sa, s) != cudaSuccess) return false;
+    } else if (T >= 2 && T < (1 << 20) && g_batch_stream && g_stage_mask == 0) {
+        // a few rows: one group that owns all of them, every tile streamed once
+        int *off = (int *)ensure(R_META, 64);
+        const int host_off[2] = {0, (int)T};
+        if (!off || cudaMemcpyAsync(off, host_off, sizeof(host_off), cudaMemcpyHostToDevice, s) != cudaSuccess) return false;
+        BatchArgs ba = {};
+        ba.wa = w.cell; ba.wb = w.cell; ba.grp_off = off; ba.n_groups = 1; ba.out_f = w.out_f; ba.n_blocks = w.nb; ba.fw = fw; ba.fa = 16;
+        ba.fast = small_scales(w.maxd, w.maxdmin, fw); ba.xl = xl; ba.out = out; ba.flags = g_flags;
+        if (launch_batch(w.qtype, MODE_LINEAR, ba, s) != cudaSuccess) return false;
     } else {
         SkinnyArgs a = {};
         a.wa = w.cell; a.wb = w.cell; a.pairs_per_group = (int)T; a.out_f = w.out_f; a.n_blocks = w.nb; a.fw = fw; a.fa = 16;
@@ -1002,7 +1011,7 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     StreamArgs sa = {};
     sa.wa = wqkv.cell; sa.wb = wqkv.cell; sa.n_sel = 1; sa.out_f = wqkv.out_f; sa.n_blocks = wqkv.nb; sa.fw = fw; sa.fa = fa;
     sa.xl = hl; sa.x_per_sel = 0; sa.x_nl = g_cells; sa.out = qkv; sa.flags = g_flags;
-    sa.fast = small_scales(wqkv.maxd, wqkv.maxdmin, fw); sa.pdl = 0;
+    sa.fast = small_scales(wqkv.maxd, wqkv.maxdmin, fw); sa.pdl = g_pdl; sa.early_weights = g_pdl;   // fixed weight pointer: request before the wait
     if (launch_stream(wqkv.qtype, MODE_LINEAR, sa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     AttnArgs a = {};
     a.q = qkv; a.k = qkv + qd; a.v = qkv + qd + kd; a.kcache = kcache_dev; a.vcache = vcache_dev; a.pos = pos;
@@ -1010,13 +1019,13 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim;
     attn_consts(a, fa, inv_sqrt);
     if (!attn_scratch(a, s)) return 1;
-    a.out = nullptr; a.out_limbs = al; a.out_nl = g_cells + 7; a.flags = g_flags;
+    a.out = nullptr; a.out_limbs = al; a.out_nl = g_cells + 7; a.flags = g_flags; a.pdl = g_pdl;
     if (launch_attn_decode(a, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     // O product accumulated into the residual row: the "down" form of the streaming kernel with a unit gate
     StreamArgs oa = {};
     oa.wa = wo.cell; oa.wb = wo.cell; oa.n_sel = 1; oa.out_f = wo.out_f; oa.n_blocks = wo.nb; oa.fw = fw; oa.fa = fa;
     oa.xl = al; oa.x_per_sel = 1; oa.x_nl = g_cells + 7; oa.out = x_dev; oa.gates = g_pow2 + fa; oa.flags = g_flags;
-    oa.fast = small_scales(wo.maxd, wo.maxdmin, fw); oa.pdl = 0;
+    oa.fast = small_scales(wo.maxd, wo.maxdmin, fw); oa.pdl = g_pdl; oa.early_weights = g_pdl;
     if (launch_stream(wo.qtype, MODE_DOWN, oa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     return 0;
 }

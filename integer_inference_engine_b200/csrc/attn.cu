@@ -295,6 +295,9 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const AttnArgs a_in) {
     if (tid == 0) s_wide = 0;
     if (tid < AT_MAXREP) { s_max[tid] = INT64_MIN; s_z[tid] = 0ULL; }
     __syncthreads();
+    // programmatic dependent launch: everything above touched only shared memory and the position cell (written a
+    // whole step earlier); q, k, v come from the product launched just before
+    if (a.pdl) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
     bool wide = false;
     for (int idx = tid; idx < rep * half; idx += blockDim.x) {
         const int r = idx / half, i = idx - r * half;
@@ -544,9 +547,13 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
         fused = (long long)chunks * a.Hkv <= (long long)per_sm * n_sms;      // a cooperative launch needs every CTA resident
     }
     if (fused) {
-        AttnArgs copy = a;
-        void *params[] = {&copy};
-        const cudaError_t e = cudaLaunchCooperativeKernel((const void *)attn_fused_kernel, dim3(chunks, a.Hkv), dim3(256), params, fused_smem, s);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(chunks, a.Hkv); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = fused_smem; cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = a.pdl ? 2 : 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fused_kernel, a);
         note_launch(1);
         return e != cudaSuccess ? e : cudaGetLastError();
     }

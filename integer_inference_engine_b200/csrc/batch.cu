@@ -19,7 +19,8 @@ namespace iie {
 
 namespace {
 
-constexpr int BT_WARPS = 16;
+constexpr int BT_WARPS = 8;                 // two CTAs per SM: one multiplies while the other's tiles stream in
+constexpr int BT_SMEM = 108 * 1024;
 constexpr unsigned BT_WAIT_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t bt_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -34,7 +35,7 @@ __device__ __forceinline__ bool bt_wait(uint64_t *bar) {
 }
 
 template <int QT, int MODE, bool FAST>
-__global__ void __launch_bounds__(BT_WARPS * 32, 1) batch_kernel(const BatchArgs a) {
+__global__ void __launch_bounds__(BT_WARPS * 32, 2) batch_kernel(const BatchArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
     const int nb = (int)a.n_blocks, tile_bytes = 2 * nb * HTB, tpc = a.tiles_per_cta;
@@ -154,17 +155,17 @@ cudaError_t launch_t(const BatchArgs &a_in, cudaStream_t s) {
     a.tiles_per_expert = (int)(MODE == MODE_GATEUP ? n_ht : (n_ht + 1) / 2);
     const size_t tile_bytes = (size_t)2 * a.n_blocks * HTB;
     const size_t fixed = (size_t)BT_WARPS * 1024 + 64;
-    int tpc = (int)((200 * 1024 - fixed) / (tile_bytes + 16));
+    int tpc = (int)((BT_SMEM - fixed) / (tile_bytes + 16));
     if (tpc < 1) return cudaErrorNotSupported;
     const long long n_tiles = (long long)a.n_groups * a.tiles_per_expert;
-    tpc = (int)std::min<long long>(tpc, std::max<long long>(1, (n_tiles + 147) / 148));
+    tpc = (int)std::min<long long>(tpc, std::max<long long>(1, (n_tiles + 295) / 296));
     tpc = std::min(tpc, BT_WARPS * 32);
     a.tiles_per_cta = tpc;
     a.sig_log2e = sigmoid_log2e(a.fa); a.sig_clip = sigmoid_clip(a.fa);
     const size_t smem = (size_t)tpc * tile_bytes + (size_t)BT_WARPS * 1024 + (size_t)tpc * 8 + (size_t)(tpc + 1) * 4 + 16;
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(batch_kernel<QT, MODE, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        const cudaError_t e = cudaFuncSetAttribute(batch_kernel<QT, MODE, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, BT_SMEM);
         if (e != cudaSuccess) return e;
         configured = true;
     }

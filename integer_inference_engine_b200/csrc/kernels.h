@@ -240,6 +240,7 @@ struct AttnArgs {
     int64_t *out;                  // [H*hd], nullable
     int8_t *out_limbs;             // nullable: digit planes [8][H*hd] of the result
     int *out_nl;                   // nullable: digits in use by the result
+    int pdl;                       // 1: the one-launch form is launched with programmatic stream serialization
     int *flags;                    // bit 0 digit envelope, bit 2 a key / value does not fit the int32 cache
 };
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s);
