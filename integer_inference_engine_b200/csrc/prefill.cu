@@ -12,10 +12,10 @@
 // epilogue forms sum_s 256^s acc_s in 128 bits and performs the reference's single floor shift.
 //
 // Tile: 128 (token, expert) pairs (MMA M, TMEM lanes) x BN weight rows (MMA N) x K in chunks of 64.
-// Warps 0-3 produce: they copy the activation digit planes of their pair into the canonical K-major
-// shared-memory layout (A operand) and dequantise + digit-split the weight chunk (B operand); then they
-// run the epilogue, one TMEM lane = one pair each.  Warp 4 allocates TMEM and one elected thread issues
-// the MMAs; tcgen05.commit hands a stage back to the producers.  Gate and up rows share a tile
+// Three groups of four warps produce, one shared-memory stage each: they copy the activation digit planes of
+// their pair into the canonical K-major layout with cp.async (A operand, no register staging) and dequantise +
+// digit-split the weight chunk (B operand); then they run the epilogue, one TMEM lane = one pair each.  The last
+// warp allocates TMEM and one elected thread issues the MMAs; tcgen05.commit hands a stage back to its group.  Gate and up rows share a tile
 // (columns 0..BN/2-1 gate, BN/2..BN-1 up) so the integer SiLU * up product is formed in the epilogue.
 // Every wait is bounded; on a time-out the CTA raises flag bit 3, leaves its loops, frees TMEM and exits.
 #include <algorithm>
@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < PF_STAGES; s++) { pf_bar_init(&full_bar[s], 128); pf_bar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < PF_STAGES; s++) { pf_bar_init(&full_bar[s], 256); pf_bar_init(&empty_bar[s], 1); }   // 128 async-copy + 128 store arrivals
         pf_bar_init(&accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -200,22 +200,24 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
         const bool live = pair < m_end;
         const long long xrow = live ? (a.xidx ? a.xidx[pair] : pair) : 0;
         const int8_t *xsrc = a.xl + xrow * 8 * (long long)K;
-        const int brow = gtid >> 1, hsel = gtid & 1;           // ... and weight row / 32-column half (B)
+        const int brow = gtid & 63, hsel = gtid >> 6;          // ... and weight row / 32-column half (B): consecutive lanes, consecutive rows
         for (int c = group; c < n_chunks; c += PF_GROUPS) {
             const int s = group;
             if (c >= PF_STAGES && !pf_bar_wait(&empty_bar[s], ((c / PF_STAGES) - 1) & 1, &s_abort)) break;
             uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
-            // A: NL digit planes x 64 columns of this thread's pair
+            // A: NL digit planes x 64 columns of this thread's pair, copied global -> shared without passing through
+            // registers (cp.async, zero-filled for rows past the slab); the copies complete on the stage's barrier
 #pragma unroll
             for (int b = 0; b < NL; b++) {
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    uint4 v = make_uint4(0, 0, 0, 0);
-                    if (live) v = ldg128(xsrc + (long long)b * K + c * PF_KC + j * 16);
-                    *reinterpret_cast<uint4 *>(stage + b * A_PLANE + (j >> 1) * (A_PLANE / 2) + (j & 1) * (A_PLANE / 4) +
-                                               (prow >> 3) * 128 + (prow & 7) * 16) = v;
+                    const uint32_t dst = pf_u32(stage + b * A_PLANE + (j >> 1) * (A_PLANE / 2) + (j & 1) * (A_PLANE / 4) +
+                                                (prow >> 3) * 128 + (prow & 7) * 16);
+                    const int8_t *src = xsrc + (long long)b * K + c * PF_KC + j * 16;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(live ? 16 : 0) : "memory");
                 }
             }
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(pf_u32(&full_bar[s])) : "memory");
             // B: BN weight rows x 64 columns, each thread one (row, 32-column half) per pass
             for (int r0 = 0; r0 < BN; r0 += 64) {
                 const int r = r0 + brow;
@@ -325,6 +327,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                 const int s = c % PF_STAGES;
                 ok = pf_bar_wait(&full_bar[s], (c / PF_STAGES) & 1, &s_abort);
                 if (!ok) break;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the cp.async writes, observed through the barrier
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t stage = pf_u32(smem + (size_t)s * STAGE_BYTES);
 #pragma unroll

@@ -248,7 +248,7 @@ cudaError_t launch_stream_t(const StreamArgs &a_in, cudaStream_t s) {
     const int max_tpc = (int)((200 * 1024) / per_tile);
     if (max_tpc < 1) return cudaErrorInvalidConfiguration;
     int tpc = (int)((n_tiles + 147) / 148);                      // one wave when everything fits
-    if (tpc > max_tpc) tpc = (int)std::max<long long>(1, std::min<long long>(max_tpc, (100 * 1024) / (long long)per_tile));
+    if (tpc > max_tpc) tpc = max_tpc;                            // several waves: one CTA per SM (registers), so the longest run that fits
     a.tiles_per_cta = tpc;
     a.sig_log2e = sigmoid_log2e(a.fa); a.sig_clip = sigmoid_clip(a.fa);
     const unsigned grid = (unsigned)((n_tiles + tpc - 1) / tpc);
