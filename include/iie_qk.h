@@ -181,8 +181,10 @@ int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t
 /* 1 (default): batches of 2 .. tc_min_tokens-1 rows stream every touched expert tile once for all of its rows;
  * 0: the older kernel that re-reads a tile for every four rows.  Results are identical; for measurements. */
 void iie_set_batch_stream(int enabled);
-/* 1 (default): the three attention passes run as one cooperative launch whenever all of its CTAs fit on the device
- * at once (contexts up to roughly 4700 visible keys per KV head on B200); 0: always three launches. */
+/* Form of the single-token attention: 1 (default) one cooperative launch when all of its CTAs fit on the device at
+ * once (about 4700 visible keys per KV head on B200), else three launches; 0: always three launches; 2: one
+ * thread-block cluster per KV head (up to 5120 visible keys, at most eight query heads per KV head, head_dim <= 128;
+ * measured slower: 64 CTAs cannot pull the cache fast enough).  Same bytes in every form. */
 void iie_set_attn_fused(int enabled);
 /* Row `token` (or *token_dev when token_dev != NULL) of a registered Q4_K / Q6_K matrix as int64 at 2^frac:
  * the embedding look-up (north-mini-code/src/nmc/engine.py:239-243). */

@@ -63,6 +63,7 @@ int g_fused_expert = 0;               // single-token expert stage as one cluste
 int g_fused_route = 0;                // routing recomputed inside the gate/up launch (rgu.cu): slower than its own launch
 long long g_hl_d = 0;                 // width of the digit planes the last single-token routing left in the R_XL scratch
 int64_t *g_pow2 = nullptr;            // device: 2^i for i = 0..31 (unit gates at any activation scale)
+int g_attn_parity = 0;                // which of the two attention digit-count cells the next block call uses
 int g_gu_parity = 0;                  // which of the two gu digit-count cells the next fused launch uses
 long long g_tc_min_tokens = 192;      // from this many tokens on, the MoE block runs on the tcgen05 grouped GEMMs
 int g_ready = -1;                     // -1 unknown, 0 usable, 1 unusable
@@ -1019,12 +1020,14 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim;
     attn_consts(a, fa, inv_sqrt);
     if (!attn_scratch(a, s)) return 1;
-    a.out = nullptr; a.out_limbs = al; a.out_nl = g_cells + 7; a.flags = g_flags; a.pdl = g_pdl;
+    int *nl_cell = g_cells + 8 + g_attn_parity, *nl_next = g_cells + 8 + (g_attn_parity ^ 1);   // alternate between calls
+    g_attn_parity ^= 1;
+    a.out = nullptr; a.out_limbs = al; a.out_nl = nl_cell; a.out_nl_next = nl_next; a.flags = g_flags; a.pdl = g_pdl;
     if (launch_attn_decode(a, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     // O product accumulated into the residual row: the "down" form of the streaming kernel with a unit gate
     StreamArgs oa = {};
     oa.wa = wo.cell; oa.wb = wo.cell; oa.n_sel = 1; oa.out_f = wo.out_f; oa.n_blocks = wo.nb; oa.fw = fw; oa.fa = fa;
-    oa.xl = al; oa.x_per_sel = 1; oa.x_nl = g_cells + 7; oa.out = x_dev; oa.gates = g_pow2 + fa; oa.flags = g_flags;
+    oa.xl = al; oa.x_per_sel = 1; oa.x_nl = nl_cell; oa.out = x_dev; oa.gates = g_pow2 + fa; oa.flags = g_flags;
     oa.fast = small_scales(wo.maxd, wo.maxdmin, fw); oa.pdl = g_pdl; oa.early_weights = g_pdl;
     if (launch_stream(wo.qtype, MODE_DOWN, oa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     return 0;
@@ -1083,7 +1086,7 @@ extern "C" void iie_set_batch_stream(int enabled) {
 
 extern "C" void iie_set_attn_fused(int enabled) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
-    iie::g_attn_fused = enabled ? 1 : 0;
+    iie::g_attn_fused = enabled < 0 ? 0 : (enabled > 2 ? 2 : enabled);
 }
 
 extern "C" void iie_set_fused_route(int enabled) {

@@ -240,11 +240,12 @@ struct AttnArgs {
     int64_t *out;                  // [H*hd], nullable
     int8_t *out_limbs;             // nullable: digit planes [8][H*hd] of the result
     int *out_nl;                   // nullable: digits in use by the result
+    int *out_nl_next;              // nullable: zeroed by the cluster form (the cell the next call accumulates into)
     int pdl;                       // 1: the one-launch form is launched with programmatic stream serialization
     int *flags;                    // bit 0 digit envelope, bit 2 a key / value does not fit the int32 cache
 };
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s);
-extern int g_attn_fused;           // 1: one cooperative launch when all CTAs are co-resident, else three launches
+extern int g_attn_fused;           // 2: cluster per KV head, 1: one cooperative launch, 0: three launches (each falls back to the next)
 // hmax = INT64_MIN, Z = acc = ticket = 0: once after the statistics buffer is (re)allocated; every call leaves them so
 cudaError_t launch_attn_reset(long long *hmax, unsigned long long *Z, long long *acc, unsigned *ticket, int H, int hd, cudaStream_t s);
 cudaError_t launch_embed_row(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,

@@ -116,3 +116,27 @@ def test_embedding_row_and_argmax():
     assert int(device.argmax(torch.from_numpy(x).cuda()).item()) == 7
     x[:] = -5
     assert int(device.argmax(torch.from_numpy(x).cuda()).item()) == 0
+
+
+@pytest.mark.parametrize("form", [0, 1, 2])
+def test_every_launch_form_gives_the_same_bytes(form):
+    """Three launches, one cooperative launch, one cluster per KV head."""
+    from integer_inference_engine_b200 import qk_cuda as qk
+    lib = qk.load_library()
+    H, Hkv, hd, pos, window = 32, 4, 128, 700, 512
+    rng = np.random.default_rng(99)
+    Lc = pos + 1
+    q = rng.integers(-(1 << 20), 1 << 20, size=(1, H, hd), dtype=np.int64)
+    ck = rng.integers(-(1 << 20), 1 << 20, size=(Hkv, Lc, hd), dtype=np.int64)
+    cv = rng.integers(-(1 << 20), 1 << 20, size=(Hkv, Lc, hd), dtype=np.int64)
+    cos, sin = o.build_rope_tables(Lc, hd, 50000.0, FA)
+    at = lambda x: o.rope_fixed(x, cos[pos:pos + 1], sin[pos:pos + 1], FA)
+    ck_full = ck.copy(); ck_full[:, pos:pos + 1] = at(ck[:, pos:pos + 1])
+    want = o.attention_cached(at(np.transpose(q, (1, 0, 2))).transpose(1, 0, 2), ck_full, cv, pos, H, Hkv, FA, window)
+    try:
+        lib.iie_set_attn_fused(form)
+        for _ in range(2):
+            got, _, _, _ = _run(q, ck, cv, pos, H, Hkv, hd, window, 1, cos, sin)
+            assert np.array_equal(got.reshape(1, -1), want)
+    finally:
+        lib.iie_set_attn_fused(1)
