@@ -19,6 +19,7 @@
 // (columns 0..BN/2-1 gate, BN/2..BN-1 up) so the integer SiLU * up product is formed in the epilogue.
 // Every wait is bounded; on a time-out the CTA raises flag bit 3, leaves its loops, frees TMEM and exits.
 #include <algorithm>
+#include <type_traits>
 
 #include "kernels.h"
 #include "layout.cuh"
@@ -30,7 +31,8 @@ namespace {
 
 constexpr int PF_BM = 128, PF_KC = 64, PF_STAGES = 3;
 constexpr int PF_GROUPS = PF_STAGES;                     // producer groups of 128 threads; group g owns stage g
-constexpr int PF_THREADS = PF_GROUPS * 128 + 32;          // + the MMA / TMEM warp
+constexpr int PF_ISSUERS = 3;                              // MMA-issuing warps: accumulator s belongs to issuer s % 3
+constexpr int PF_THREADS = PF_GROUPS * 128 + PF_ISSUERS * 32;
 constexpr unsigned PF_WAIT_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t pf_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -179,8 +181,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < PF_STAGES; s++) { pf_bar_init(&full_bar[s], 256); pf_bar_init(&empty_bar[s], 1); }   // 128 async-copy + 128 store arrivals
-        pf_bar_init(&accum_bar, 1);
+        for (int s = 0; s < PF_STAGES; s++) { pf_bar_init(&full_bar[s], 256); pf_bar_init(&empty_bar[s], PF_ISSUERS); }   // 128 async-copy + 128 store arrivals; one commit per issuer
+        pf_bar_init(&accum_bar, PF_ISSUERS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == PF_GROUPS * 4) {
@@ -318,10 +320,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     } else {
-        // ================= MMA issuer ====================================================================
+        // ================= MMA issuers ===================================================================
+        // One thread can only issue an MMA every few cycles and a chunk needs 2*NL*NWL of them, so the digit pairs
+        // are split over three issuing warps by accumulator (s = a + b belongs to issuer s % 3: MMAs into
+        // different accumulators are independent).  Descriptors are a per-stage base plus compile-time offsets.
         if (lane == 0) {
             constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(PF_BM >> 4) << 24);
-            uint32_t started = 0;                              // bit s: accumulator s already holds a partial sum
+            const int issuer = warp - PF_GROUPS * 4;
             bool ok = true;
             for (int c = 0; c < n_chunks && ok; c++) {
                 const int s = c % PF_STAGES;
@@ -330,21 +335,32 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the cp.async writes, observed through the barrier
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t stage = pf_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint64_t da0 = pf_desc(stage, A_PLANE / 4, 128), db0 = pf_desc(stage + NL * A_PLANE, B_PLANE / 4, 128);
+                const uint32_t later = c > 0 ? 1u : 0u;
+                auto issue = [&](auto iss_c) {                 // ISS is a compile-time constant: the skipped pairs fold away
+                    constexpr int ISS = decltype(iss_c)::value;
+                    uint32_t seen = 0;
 #pragma unroll
-                for (int ks = 0; ks < 2; ks++)
+                    for (int ks = 0; ks < 2; ks++)
 #pragma unroll
-                    for (int b = 0; b < NL; b++)
+                        for (int b = 0; b < NL; b++)
 #pragma unroll
-                        for (int w = 0; w < NWL; w++) {
-                            const uint64_t da = pf_desc(stage + b * A_PLANE + ks * (A_PLANE / 2), A_PLANE / 4, 128);
-                            const uint64_t db = pf_desc(stage + NL * A_PLANE + w * B_PLANE + ks * (B_PLANE / 2), B_PLANE / 4, 128);
-                            const int acc = b + w;
-                            pf_mma(tmem + acc * BN, da, db, IDESC, (started >> acc) & 1u);
-                            started |= 1u << acc;
-                        }
-                pf_commit(&empty_bar[s]);                      // stage free once these MMAs have read it
+                            for (int w = 0; w < NWL; w++) {
+                                const int acc = b + w;
+                                const bool first = !((seen >> acc) & 1u);
+                                seen |= 1u << acc;
+                                if (acc % PF_ISSUERS != ISS) continue;
+                                const uint64_t da = da0 + (uint64_t)((b * A_PLANE + ks * (A_PLANE / 2)) >> 4);
+                                const uint64_t db = db0 + (uint64_t)((w * B_PLANE + ks * (B_PLANE / 2)) >> 4);
+                                pf_mma(tmem + acc * BN, da, db, IDESC, first ? later : 1u);
+                            }
+                };
+                if (issuer == 0) issue(std::integral_constant<int, 0>{});
+                else if (issuer == 1) issue(std::integral_constant<int, 1>{});
+                else issue(std::integral_constant<int, 2>{});
+                pf_commit(&empty_bar[s]);                      // stage free once every issuer's MMAs have read it
             }
-            if (ok) pf_commit(&accum_bar);                     // all MMAs done -> epilogue may read TMEM
+            if (ok) pf_commit(&accum_bar);                     // this issuer's MMAs done -> epilogue may read TMEM after all three
         }
         __syncwarp();
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
