@@ -85,19 +85,25 @@ __device__ __forceinline__ void digits4(const int (&w)[4], uint32_t (&plane)[4])
 
 // Dequantise 32 consecutive-k weights of one row into NWL digit planes (eight words each).
 // Q4_K: chunk = group G of a block; hsel 0 = low nibbles (first 32 columns), 1 = high nibbles.
-template <int NWL>
-__device__ __forceinline__ void dequant32_q4k(const uint8_t *unit, int rr, int G, int hsel, int fw, uint32_t (&pl)[NWL][8]) {
-    const uint4 meta = ldg128(unit + 1024 + rr * 16);
-    uint32_t sc0, sc1, mn0, mn1;
-    q4k_scales(meta.y, meta.z, meta.w, sc0, sc1, mn0, mn1);
-    const int j = 2 * G + hsel;
-    const int ws = scale_small(meta.x & 0xFFFF, fw) * (int)(((j < 4 ? sc0 : sc1) >> (8 * (j & 3))) & 0xFF);
-    const int wm = scale_small(meta.x >> 16, fw) * (int)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xFF);
+struct Q4Raw { uint4 meta; uint2 q[4]; };                 // the 48 bytes of one (row, group) of a repacked Q4_K unit
+
+__device__ __forceinline__ void load_q4k(const uint8_t *unit, int rr, int G, Q4Raw &raw) {
+    raw.meta = ldg128(unit + 1024 + rr * 16);
     const uint8_t *qp = unit + (G >> 1) * 512 + rr * 64 + (G & 1) * 8;
 #pragma unroll
+    for (int t = 0; t < 4; t++) raw.q[t] = ldg64(qp + t * 16);                       // qs[32G + 8t .. +7]
+}
+
+template <int NWL>
+__device__ __forceinline__ void expand_q4k(const Q4Raw &raw, int G, int hsel, int fw, uint32_t (&pl)[NWL][8]) {
+    uint32_t sc0, sc1, mn0, mn1;
+    q4k_scales(raw.meta.y, raw.meta.z, raw.meta.w, sc0, sc1, mn0, mn1);
+    const int j = 2 * G + hsel;
+    const int ws = scale_small(raw.meta.x & 0xFFFF, fw) * (int)(((j < 4 ? sc0 : sc1) >> (8 * (j & 3))) & 0xFF);
+    const int wm = scale_small(raw.meta.x >> 16, fw) * (int)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xFF);
+#pragma unroll
     for (int t = 0; t < 4; t++) {
-        const uint2 q = ldg64(qp + t * 16);                                              // qs[32G + 8t .. +7]
-        const uint32_t words[2] = {(q.x >> (4 * hsel)) & 0x0f0f0f0fu, (q.y >> (4 * hsel)) & 0x0f0f0f0fu};
+        const uint32_t words[2] = {(raw.q[t].x >> (4 * hsel)) & 0x0f0f0f0fu, (raw.q[t].y >> (4 * hsel)) & 0x0f0f0f0fu};
 #pragma unroll
         for (int h2 = 0; h2 < 2; h2++) {
             int w[4];
@@ -110,6 +116,15 @@ __device__ __forceinline__ void dequant32_q4k(const uint8_t *unit, int rr, int G
             if (NWL > 4) pl[NWL - 1][t * 2 + h2] = 0;
         }
     }
+}
+
+// Dequantise 32 consecutive-k weights of one row into NWL digit planes (eight words each).
+// Q4_K: chunk = group G of a block; hsel 0 = low nibbles (first 32 columns), 1 = high nibbles.
+template <int NWL>
+__device__ __forceinline__ void dequant32_q4k(const uint8_t *unit, int rr, int G, int hsel, int fw, uint32_t (&pl)[NWL][8]) {
+    Q4Raw raw;
+    load_q4k(unit, rr, G, raw);
+    expand_q4k<NWL>(raw, G, hsel, fw, pl);
 }
 
 // Q6_K: chunk cc (0..3) of a block covers half h = cc >> 1 and kq = 2*(cc & 1) + hsel.  |W| = |d_q sc (q-32)|
@@ -203,8 +218,24 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
         const long long xrow = live ? (a.xidx ? a.xidx[pair] : pair) : 0;
         const int8_t *xsrc = a.xl + xrow * 8 * (long long)K;
         const int brow = gtid & 63, hsel = gtid >> 6;          // ... and weight row / 32-column half (B): consecutive lanes, consecutive rows
+        // Q4_K tiles of 64 rows (one row and column half per thread): the 48 weight-block bytes of the NEXT chunk of this
+        // group are requested before waiting for the stage, so their latency hides behind the wait and the A copies
+        constexpr bool PREFETCH = QT == QT_Q4K && BN == 64;
+        long long pf_wrow = 0; const uint8_t *pf_wbase = nullptr;
+        if (PREFETCH) {
+            if (MODE == MODE_GATEUP) { pf_wrow = (long long)ni * (BN / 2) + (brow % (BN / 2)); pf_wbase = brow < BN / 2 ? a.wa[e] : a.wb[e]; }
+            else { pf_wrow = (long long)ni * BN + brow; pf_wbase = a.wa[e]; }
+        }
+        const bool pf_row_ok = PREFETCH && pf_wrow < a.out_f;
+        Q4Raw raw_next = {};
+        if (pf_row_ok && group < n_chunks) load_q4k(pf_wbase + ((pf_wrow >> 3) * nb + (group >> 2)) * HTB, (int)(pf_wrow & 7), group & 3, raw_next);
         for (int c = group; c < n_chunks; c += PF_GROUPS) {
             const int s = group;
+            const Q4Raw raw = raw_next;
+            if (pf_row_ok && c + PF_GROUPS < n_chunks) {
+                const int cn = c + PF_GROUPS;
+                load_q4k(pf_wbase + ((pf_wrow >> 3) * nb + (cn >> 2)) * HTB, (int)(pf_wrow & 7), cn & 3, raw_next);
+            }
             if (c >= PF_STAGES && !pf_bar_wait(&empty_bar[s], ((c / PF_STAGES) - 1) & 1, &s_abort)) break;
             uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
             // A: NL digit planes x 64 columns of this thread's pair, copied global -> shared without passing through
@@ -230,8 +261,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                     uint32_t pl[NWL][8];
                     if (wrow < a.out_f) {
                         const uint8_t *unit = wbase + ((wrow >> 3) * nb + (c >> 2)) * HTB;
-                        if constexpr (QT == QT_Q4K) dequant32_q4k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
-                        else                        dequant32_q6k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
+                        if constexpr (PREFETCH) expand_q4k<NWL>(raw, c & 3, hsel, a.fw, pl);
+                        else if constexpr (QT == QT_Q4K) dequant32_q4k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
+                        else dequant32_q6k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
                     } else {
 #pragma unroll
                         for (int l = 0; l < NWL; l++)
