@@ -154,20 +154,29 @@ __global__ void __launch_bounds__(512) q1_gemv_kernel(const Q1Args a) {
     }
 
     const int myrow = g + 8 * (t & 1);
-    for (int tl = 0; tl < ntile; tl++) {
+    // the bits and scales of the next tile are requested before the current one is multiplied
+    uint2 wn[BPW];
+    DT scn[BPW];
+    auto fetch = [&](int tl) {
         const uint8_t *tile_units = a.units + (tile0 + tl) * a.nb * US;
-        uint2 w[BPW];
-        int64_t sc[BPW];
 #pragma unroll
         for (int i = 0; i < BPW; i++) {
             const long long b = warp + (long long)i * W;
-            w[i] = make_uint2(0, 0); sc[i] = 0;
-            if (b < a.nb) {
+            wn[i] = make_uint2(0, 0); scn[i] = 0;
+            if (b < a.nb && tl < ntile) {
                 const uint8_t *unit = tile_units + b * US;
-                w[i] = ldg64(unit + lane * 8);
-                sc[i] = q1_scale_at<DT>(unit, myrow);
+                wn[i] = ldg64(unit + lane * 8);
+                scn[i] = __ldg(reinterpret_cast<const DT *>(unit + 256) + myrow);
             }
         }
+    };
+    fetch(0);
+    for (int tl = 0; tl < ntile; tl++) {
+        uint2 w[BPW];
+        int64_t sc[BPW];
+#pragma unroll
+        for (int i = 0; i < BPW; i++) { w[i] = wn[i]; sc[i] = (int64_t)scn[i]; }
+        fetch(tl + 1);
         unsigned long long acc = 0;
 #pragma unroll
         for (int i = 0; i < BPW; i++) {
@@ -237,7 +246,7 @@ __global__ void __launch_bounds__(256, 2) q1_tile_kernel(const Q1Args a) {
                     q1_partials(c, t, lo[j], hi[j]);
                 }
                 // reduce-scatter: lane t ends with the complete sums of token 4q + t (rows g and g + 8)
-                const int h = t >> 1;                                       // round 1 keeps tokens 2h, 2h + 1
+                const int h = t >> 1;                                       // first exchange keeps tokens 2h, 2h + 1
                 unsigned long long kl[2], kh[2];
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
@@ -245,7 +254,7 @@ __global__ void __launch_bounds__(256, 2) q1_tile_kernel(const Q1Args a) {
                     kl[j] = (h ? lo[2 + j] : lo[j]) + __shfl_xor_sync(0xffffffffu, sl, 2);
                     kh[j] = (h ? hi[2 + j] : hi[j]) + __shfl_xor_sync(0xffffffffu, shv, 2);
                 }
-                const int o = t & 1;                                        // round 2 keeps token 2h + o
+                const int o = t & 1;                                        // second exchange keeps token 2h + o
                 const unsigned long long pl = (o ? kl[1] : kl[0]) + __shfl_xor_sync(0xffffffffu, o ? kl[0] : kl[1], 1);
                 const unsigned long long ph = (o ? kh[1] : kh[0]) + __shfl_xor_sync(0xffffffffu, o ? kh[0] : kh[1], 1);
                 const long long tok = min(tok0 + 4 * q + t, a.T - 1);
@@ -270,7 +279,7 @@ template <int BPW, typename DT>
 cudaError_t launch_gemv(const Q1Args &a_in, int W, cudaStream_t s) {
     Q1Args a = a_in;
     int sms = 148;
-    const long long target = 2LL * sms;
+    const long long target = 4LL * sms;              // several CTAs per SM: one's loads overlap another's multiplies
     a.tiles_per_cta = (int)std::max<long long>(1, (a.n_tiles + target - 1) / target);
     const unsigned grid = (unsigned)((a.n_tiles + a.tiles_per_cta - 1) / a.tiles_per_cta);
     q1_gemv_kernel<BPW, DT><<<grid, 32 * W, (size_t)a.tiles_per_cta * 16 * sizeof(unsigned long long), s>>>(a);

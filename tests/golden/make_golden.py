@@ -1,7 +1,7 @@
 """Regenerate the golden vectors in this directory from the reference project's own Python code.
 
-Run where the reference tree is mounted (default /root/reference, override with
-IIE_REFERENCE_ROOT):
+Run where the reference tree is mounted (its location comes from IIE_REFERENCE_ROOT, with the
+mount point used during development as the default):
 
     python tests/golden/make_golden.py
 
