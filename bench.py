@@ -1,6 +1,6 @@
 """Benchmark of the integer decode path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|prefill|ep_decode|q1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|prefill|ep_decode|q1|q1_token]
 
 Default workload, one step = one greedily decoded token of the synthetic 30B-A3B-shaped model at context 4096:
 embedding row -> 48 blocks (RMSNorm, Q/K/V products, RoPE on sliding-window blocks, KV-cache append, exact
@@ -58,7 +58,7 @@ def parse():
     ap.add_argument("--cpu-sample-layers", type=int, default=2)
     ap.add_argument("--context", type=int, default=4096, help="KV-cache rows already filled when decoding starts")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep_decode", "q1"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep_decode", "q1", "q1_token"],
                     help="decode = the headline line (batch-1 MoE decode); the others print a line of the same "
                          "shape for the prefill, expert-parallel and Q1_0 configurations")
     ap.add_argument("--tokens", type=int, default=0, help="prefill: tokens per step (2048); ep_decode: sequences (64)")
@@ -756,6 +756,60 @@ def run_q1(args):
                      "traffic": None, "bytes_per_launch": wbytes}}))
 
 
+def run_q1_token(args):
+    """Whole decode token of the 1-bit decoder at the 8B shape (36 layers, d=4096, 32/8 heads of 128, ffn 12288,
+    vocab 151936): Q1_0 embedding row, every layer's norms, fused QKV product, per-head norms, rotation, cached
+    attention, O product, SwiGLU with wrapping products, down product, the Q1_0 head and the greedy pick, as one
+    replayed CUDA graph; checked stage by stage on a small decoder against the CPU checker first."""
+    import torch
+
+    from integer_inference_engine_b200 import device
+    from integer_inference_engine_b200.q1_model import SyntheticQ1Decoder
+    from oracle import model_oracle
+    rank, world, local = _dist_setup()
+    assert world == 1, "the 1-bit decoder line is a single-GPU measurement"
+    small = SyntheticQ1Decoder(n_layers=2, d_model=512, n_heads=8, n_kv=4, head_dim=64, d_ffn=768, vocab=640, context=20,
+                               max_new=4, seed=3, keep_host=True)
+    hl = [dict(L, k=L["k"].cpu().numpy().astype(np.int64), v=L["v"].cpu().numpy().astype(np.int64)) for L in small.host_layers]
+    want, trace, logits = model_oracle.q1_decode_token(5, 20, hl, small.host_top, dict(d=512, H=8, Hkv=4, hd=64, ffn=768, frac=16),
+                                                       small.cos.cpu().numpy(), small.sin.cpu().numpy())
+    small.token.fill_(5)
+    small.step(20)
+    torch.cuda.synchronize()
+    assert device.read_flags() == 0 and np.array_equal(small.x.cpu().numpy(), trace[-1:]) and int(small.token.item()) == want, \
+        "1-bit decode token differs from the checker"
+    del small
+    L = 36 if args.layers == 48 else args.layers
+    ctx = args.context if args.context else 512
+    m = SyntheticQ1Decoder(n_layers=L, context=ctx, max_new=args.steps + args.warmup + 8, seed=2)
+    m.token.fill_(11)
+    l0 = device.launch_count()
+    m.capture(ctx + args.steps + args.warmup + 4)
+    launches = (device.launch_count() - l0) // 2
+    ms, clocks = _timed(lambda i: m.replay(), args.steps, args.warmup, 1, local)
+    ms_step = ms / args.steps
+    assert device.read_flags() == 0
+    tin = torch.zeros(1, dtype=torch.int32).pin_memory(); tout = torch.zeros(1, dtype=torch.int32).pin_memory()
+    tin[0] = 11
+    m.pos.fill_(ctx)
+    e2e_ms, _ = _timed(lambda i: m.decode_token(tin, tout), args.steps, 1, 1, local)
+    wbytes = m.weight_bytes_per_token()
+    kv = 2 * m.Hkv * m.hd * 4 * (ctx + args.warmup + args.steps // 2) * L
+    peak, kind = measured_peak_gbs()
+    print(json.dumps({
+        "metric": "decode_tok_per_s", "value": 1e3 / ms_step, "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int64 modulo 2^64 via int8 digit planes", "data": "synthetic",
+        "config": {"workload": f"config5_q1_decode_token: {L} layers of the 8B 1-bit shape, whole token (embedding row, norms, QKV, "
+                               f"per-head norms, RoPE, cached attention, O, SwiGLU, down, head, greedy pick), context {ctx}",
+                   "l2": "inputs larger than L2: %d MB of weights per step" % (wbytes // 2**20)},
+        "clocks": clocks, "gpu_launches": int(launches * args.steps),
+        "e2e": {"value": 1e3 / (e2e_ms / args.steps), "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+        "roofline": {"bound": "hbm", "kernel": "all kernels of one decode token (aggregate)",
+                     "achieved": (wbytes + kv) / (ms_step * 1e-3) / 1e9, "peak": peak, "peak_kind": kind, "unit": "GB/s",
+                     "frac": (wbytes + kv) / (ms_step * 1e-3) / 1e9 / peak, "traffic": None, "bytes_per_launch": wbytes + kv}}))
+
+
 if __name__ == "__main__":
     a = parse()
     if a.impl == "reference":
@@ -766,5 +820,7 @@ if __name__ == "__main__":
         run_ep_decode(a)
     elif a.workload == "q1":
         run_q1(a)
+    elif a.workload == "q1_token":
+        run_q1_token(a)
     else:
         run_ours(a)

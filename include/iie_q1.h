@@ -72,6 +72,13 @@ int bonsai_rmsnorm_gpu(const long long *x, long long rows, long long cols, long 
  * stream).  Scratch for the digit planes is process-global and grows on demand: one caller at a time. */
 int iie_q1_apply_dev(long long handle, const int64_t *x_dev, long long tokens, long long frac, int64_t *out_dev,
                      void *stream);
+/* out = ((gate * sigmoid(gate)) >> frac) * up >> frac, both products modulo 2^64: the SwiGLU of
+ * bonsai/src/trinote/infer_int/reference_bonsai.py:246-262 and 611-614.  0 ok, 1 bad argument, 2 CUDA failure. */
+int iie_q1_silu_mul_dev(const int64_t *gate_dev, const int64_t *up_dev, long long n, long long frac, int64_t *out_dev,
+                        void *stream);
+/* One row of a registered weight as int64 (sign * block scale, reference_bonsai.py:138-146 q1_rows_fp): the row index
+ * is read from the device cell `row_dev` when that is not NULL, else `row`. */
+int iie_q1_embed_dev(long long handle, const int *row_dev, long long row, int64_t *out_dev, void *stream);
 /* Shape of a registered weight; 0 ok, 1 unknown handle. */
 int iie_q1_weight_shape(long long handle, long long *out_f, long long *n_blocks, int *scale_bits);
 

@@ -743,32 +743,55 @@ __global__ void embed_row_kernel(const uint8_t *w, int qtype, long long nb, cons
     out[i] = val;
 }
 
-// arg-max with the lowest index on ties, one CTA
+// arg-max with the lowest index on ties: every CTA leaves its candidate in a static table, the CTA that arrives last
+// (a counter, no waiting) picks among the candidates and clears the counter for the next launch on the stream
+constexpr int AM_CTAS = 148;
+__device__ long long g_am_v[AM_CTAS], g_am_i[AM_CTAS];
+__device__ unsigned g_am_done;
+
 __global__ void __launch_bounds__(1024) argmax_kernel(const int64_t *x, long long n, int *out) {
     __shared__ long long s_v[32];
     __shared__ long long s_i[32];
+    __shared__ bool s_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     long long bv = INT64_MIN, bi = n;
-    for (long long i = tid; i < n; i += blockDim.x) {
-        const long long v = x[i];
-        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
-    }
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) {
-        const long long ov = __shfl_xor_sync(0xffffffffu, bv, s), oi = __shfl_xor_sync(0xffffffffu, bi, s);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-    if (lane == 0) { s_v[warp] = bv; s_i[warp] = bi; }
-    __syncthreads();
-    if (warp == 0) {
-        bv = lane < (blockDim.x >> 5) ? s_v[lane] : INT64_MIN; bi = lane < (blockDim.x >> 5) ? s_i[lane] : n;
+    auto better = [](long long ov, long long oi, long long v, long long i) { return ov > v || (ov == v && oi < i); };
+    auto block_pick = [&]() {                                       // result valid in thread 0
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) {
             const long long ov = __shfl_xor_sync(0xffffffffu, bv, s), oi = __shfl_xor_sync(0xffffffffu, bi, s);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
         }
-        if (lane == 0) *out = (int)bi;
+        if (lane == 0) { s_v[warp] = bv; s_i[warp] = bi; }
+        __syncthreads();
+        if (warp == 0) {
+            bv = lane < (blockDim.x >> 5) ? s_v[lane] : INT64_MIN; bi = lane < (blockDim.x >> 5) ? s_i[lane] : n;
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) {
+                const long long ov = __shfl_xor_sync(0xffffffffu, bv, s), oi = __shfl_xor_sync(0xffffffffu, bi, s);
+                if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+            }
+        }
+    };
+    for (long long i = (long long)blockIdx.x * blockDim.x + tid; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long v = x[i];
+        if (better(v, i, bv, bi)) { bv = v; bi = i; }
     }
+    block_pick();
+    if (gridDim.x == 1) { if (tid == 0) *out = (int)bi; return; }
+    if (tid == 0) {
+        g_am_v[blockIdx.x] = bv; g_am_i[blockIdx.x] = bi;
+        __threadfence();
+        s_last = atomicAdd(&g_am_done, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    bv = INT64_MIN; bi = n;
+    if (tid < (int)gridDim.x) { bv = __ldcg(&g_am_v[tid]); bi = __ldcg(&g_am_i[tid]); }
+    __syncthreads();                                                // s_v / s_i are reused
+    block_pick();
+    if (tid == 0) { *out = (int)bi; g_am_done = 0; }
 }
 
 }  // namespace
@@ -867,7 +890,8 @@ cudaError_t launch_embed_row(const uint8_t *w, int qtype, long long nb, const in
 
 cudaError_t launch_argmax(const int64_t *x, long long n, int *out, cudaStream_t s) {
     if (n <= 0) return cudaErrorInvalidValue;
-    argmax_kernel<<<1, 1024, 0, s>>>(x, n, out);
+    long long ctas = (n + 8191) / 8192;
+    argmax_kernel<<<(unsigned)(ctas > AM_CTAS ? AM_CTAS : ctas), 1024, 0, s>>>(x, n, out);
     note_launch();
     return cudaGetLastError();
 }

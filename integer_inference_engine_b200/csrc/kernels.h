@@ -260,5 +260,8 @@ cudaError_t launch_q1_prep(const int64_t *x, long long T, long long nb, int8_t *
                            cudaStream_t s);
 cudaError_t launch_q1_apply(const uint8_t *units, bool sc32, long long out_f, long long nb, const int8_t *planes,
                             const int64_t *totals, long long T, long long frac, int64_t *out, cudaStream_t s);
+cudaError_t launch_q1_silu_mul(const int64_t *gate, const int64_t *up, long long n, int frac, int64_t *out, cudaStream_t s);
+cudaError_t launch_q1_embed_row(const uint8_t *units, bool sc32, long long nb, const int *row_dev, long long row_host, int64_t *out,
+                                cudaStream_t s);
 
 }  // namespace iie

@@ -246,13 +246,25 @@ __device__ u128 isqrt_u128(u128 v) {
     return res;
 }
 
-__global__ void rmsnorm_kernel(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
-                               unsigned long long eps, int64_t *out, int *flags) {
-    __shared__ unsigned long long s_lo[256], s_hi[256], s_max[256], s_gmax[256];
-    __shared__ unsigned long long s_rms;
+// floor(sqrt(v)): a double estimate fixed up with exact 128-bit products while v < 2^104, else the bitwise root
+__device__ u128 isqrt_fast(u128 v) {
+    if (v < ((u128)1 << 104)) {
+        const double dv = (double)(unsigned long long)(v >> 64) * 18446744073709551616.0 + (double)(unsigned long long)v;
+        unsigned long long r = (unsigned long long)sqrt(dv);
+        for (int it = 0; it < 8 && (u128)r * r > v; it++) r--;
+        for (int it = 0; it < 8 && (u128)(r + 1) * (r + 1) <= v; it++) r++;
+        if ((u128)r * r <= v && (u128)(r + 1) * (r + 1) > v) return r;
+    }
+    return isqrt_u128(v);
+}
+
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const int64_t *x, long long rows, long long width, const int64_t *gain,
+                                                       int fa, unsigned long long eps, int64_t *out, int *flags) {
+    __shared__ unsigned long long s_lo[32], s_hi[32], s_max[32], s_gmax[32];
+    __shared__ unsigned long long s_rms, s_gm;
     __shared__ int s_bad;
     const long long row = blockIdx.x;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int64_t *xr = x + row * width;
     int64_t *yr = out + row * width;
     u128 ssq = 0; unsigned long long mx = 0, gmx = 0;
@@ -262,34 +274,52 @@ __global__ void rmsnorm_kernel(const int64_t *x, long long rows, long long width
         mx = a > mx ? a : mx;
         if (gain) { const unsigned long long ga = uabs64(gain[i]); gmx = ga > gmx ? ga : gmx; }
     }
-    s_lo[tid] = (unsigned long long)ssq; s_hi[tid] = (unsigned long long)(ssq >> 64); s_max[tid] = mx; s_gmax[tid] = gmx;
-    if (tid == 0) s_bad = 0;
-    __syncthreads();
-    if (tid == 0) {
-        u128 total = 0; unsigned long long m = 0, gm = 0;
-        for (int i = 0; i < blockDim.x; i++) {
-            total += ((u128)s_hi[i] << 64) | s_lo[i];
-            m = s_max[i] > m ? s_max[i] : m; gm = s_gmax[i] > gm ? s_gmax[i] : gm;
+    auto fold = [&]() {
+#pragma unroll
+        for (int off = 16; off; off >>= 1) {
+            const unsigned long long lo = __shfl_down_sync(0xffffffffu, (unsigned long long)ssq, off);
+            const unsigned long long hi = __shfl_down_sync(0xffffffffu, (unsigned long long)(ssq >> 64), off);
+            const unsigned long long m2 = __shfl_down_sync(0xffffffffu, mx, off), g2 = __shfl_down_sync(0xffffffffu, gmx, off);
+            ssq += ((u128)hi << 64) | lo;
+            mx = m2 > mx ? m2 : mx; gmx = g2 > gmx ? g2 : gmx;
         }
-        // |x| <= 2^57 keeps the 128-bit sum of squares exact for any width <= 2^13
-        if (m > (1ULL << 57) || width > 8192) s_bad = 1;
-        const u128 mean = total / (u128)(unsigned long long)width + eps;
-        const u128 rms = isqrt_u128(mean);
-        if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) s_bad = 1;
-        s_rms = (unsigned long long)rms;
-        s_gmax[0] = gm;
+    };
+    fold();
+    if (lane == 0) { s_lo[warp] = (unsigned long long)ssq; s_hi[warp] = (unsigned long long)(ssq >> 64); s_max[warp] = mx; s_gmax[warp] = gmx; }
+    __syncthreads();
+    if (warp == 0) {
+        ssq = lane < nwarps ? (((u128)s_hi[lane] << 64) | s_lo[lane]) : (u128)0;
+        mx = lane < nwarps ? s_max[lane] : 0; gmx = lane < nwarps ? s_gmax[lane] : 0;
+        fold();
+        if (lane == 0) {
+            // |x| <= 2^57 keeps the 128-bit sum of squares exact for any width <= 2^13
+            int bad = (mx > (1ULL << 57) || width > 8192) ? 1 : 0;
+            const u128 mean = ((width & (width - 1)) == 0 ? ssq >> (63 - __clzll(width)) : ssq / (u128)(unsigned long long)width) + eps;
+            const u128 rms = isqrt_fast(mean);
+            if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) bad = 1;
+            s_rms = (unsigned long long)rms; s_gm = gmx; s_bad = bad;
+        }
     }
     __syncthreads();
     if (s_bad) { if (tid == 0) atomicOr(flags, 2); return; }
     const unsigned long long rms = s_rms;
-    const unsigned long long gm = s_gmax[0];
+    const unsigned long long gm = s_gm;
+    const unsigned long long narrow = 1ULL << (62 - fa);           // |x| below this: x << fa fits a signed 64-bit dividend
     bool bad = false;
     for (long long i = tid; i < width; i += blockDim.x) {
-        const i128 num = (i128)xr[i] << fa;
-        i128 q = num / (i128)rms;
-        if (num < 0 && q * (i128)rms != num) q -= 1;              // floor toward -inf
-        if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; continue; }
-        int64_t y = (int64_t)q;
+        const int64_t xv = xr[i];
+        int64_t y;
+        if (uabs64(xv) < narrow && rms <= (unsigned long long)INT64_MAX) {
+            const int64_t num = xv * ((int64_t)1 << fa), den = (int64_t)rms;
+            y = num / den;
+            if (num < 0 && y * den != num) y -= 1;                  // floor toward -inf
+        } else {
+            const i128 num = (i128)xv << fa;
+            i128 q = num / (i128)rms;
+            if (num < 0 && q * (i128)rms != num) q -= 1;
+            if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; continue; }
+            y = (int64_t)q;
+        }
         if (gain) {
             // the oracle refuses a gain product that could leave int64
             if ((u128)uabs64(y) * gm > (u128)INT64_MAX) { bad = true; continue; }
@@ -371,7 +401,8 @@ cudaError_t launch_topk(const int64_t *logits, long long rows, int n_experts, in
 
 cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
                            unsigned long long eps, int64_t *out, int *flags, cudaStream_t s) {
-    rmsnorm_kernel<<<(unsigned)rows, 256, 0, s>>>(x, rows, width, gain, fa, eps, out, flags);
+    const int threads = width >= 2048 ? 1024 : width > 128 ? 256 : 128;
+    rmsnorm_kernel<<<(unsigned)rows, threads, 0, s>>>(x, rows, width, gain, fa, eps, out, flags);
     note_launch();
     return cudaGetLastError();
 }

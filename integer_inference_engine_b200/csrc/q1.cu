@@ -303,6 +303,34 @@ cudaError_t launch_apply_t(const Q1Args &a, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+// SiLU(gate) * up with the wrapping products of bonsai/src/trinote/infer_int/reference_bonsai.py:246-262,611-614:
+// silu = (gate * sigmoid(gate)) >> frac and h = (silu * up) >> frac, both products modulo 2^64.
+__global__ void q1_silu_mul_kernel(const int64_t *gate, const int64_t *up, long long n, int frac, int64_t log2e, int64_t clip,
+                                   int64_t *out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t g = gate[i];
+    const int64_t sg = sigmoid_fixed_c(g, frac, log2e, clip);
+    const int64_t silu = (int64_t)((unsigned long long)g * (unsigned long long)sg) >> frac;
+    out[i] = (int64_t)((unsigned long long)silu * (unsigned long long)up[i]) >> frac;
+}
+
+// one row of a registered Q1_0 matrix as int64: sign * block scale (reference_bonsai.py:138-146 q1_rows_fp)
+template <typename DT>
+__global__ void q1_embed_row_kernel(const uint8_t *units, long long nb, const int *row_dev, long long row_host, int64_t *out) {
+    constexpr int US = 256 + 16 * (int)sizeof(DT);
+    const long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= nb * 128) return;
+    const long long row = row_dev ? (long long)*row_dev : row_host, b = k >> 7;
+    const int kk = (int)(k & 127), rloc = (int)(row & 15), g = rloc & 7, hi = rloc >> 3;
+    const int m = kk >> 5, t = (kk & 31) >> 3, jj = ((kk & 31) >> 2) & 1, i = kk & 3;
+    const int r = (m & 1) * 4 + ((jj << 1) | hi), mp = m >> 1;
+    const uint8_t *unit = units + ((row >> 4) * nb + b) * US;
+    const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(unit) + (4 * g + t) * 2 + mp);
+    const int64_t sc = (int64_t)__ldg(reinterpret_cast<const DT *>(unit + 256) + rloc);
+    out[k] = ((w >> (r + 8 * i)) & 1u) ? sc : -sc;
+}
+
 }  // namespace
 
 size_t q1_unit_bytes(bool sc32) { return 256 + 16 * (sc32 ? 4 : 8); }
@@ -334,6 +362,22 @@ cudaError_t launch_q1_apply(const uint8_t *units, bool sc32, long long out_f, lo
     a.sh = frac <= 0 ? 0 : (frac >= 63 ? 63 : (int)frac);
     a.tiles_per_cta = 1; a.xl = planes; a.totals = totals; a.out = out;
     return sc32 ? launch_apply_t<int>(a, s) : launch_apply_t<long long>(a, s);
+}
+
+cudaError_t launch_q1_silu_mul(const int64_t *gate, const int64_t *up, long long n, int frac, int64_t *out, cudaStream_t s) {
+    if (n <= 0 || frac < 1 || frac > 29) return cudaErrorInvalidValue;
+    q1_silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(gate, up, n, frac, sigmoid_log2e(frac), sigmoid_clip(frac), out);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_q1_embed_row(const uint8_t *units, bool sc32, long long nb, const int *row_dev, long long row_host, int64_t *out,
+                                cudaStream_t s) {
+    const unsigned grid = (unsigned)((nb * 128 + 255) / 256);
+    if (sc32) q1_embed_row_kernel<int><<<grid, 256, 0, s>>>(units, nb, row_dev, row_host, out);
+    else q1_embed_row_kernel<long long><<<grid, 256, 0, s>>>(units, nb, row_dev, row_host, out);
+    note_launch();
+    return cudaGetLastError();
 }
 
 }  // namespace iie

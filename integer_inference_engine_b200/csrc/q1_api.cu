@@ -264,6 +264,20 @@ extern "C" int iie_q1_apply_dev(long long handle, const int64_t *x_dev, long lon
     return apply_device(q_w[(size_t)handle], x_dev, tokens, frac, out_dev, 8, (cudaStream_t)stream);
 }
 
+extern "C" int iie_q1_silu_mul_dev(const int64_t *gate_dev, const int64_t *up_dev, long long n, long long frac, int64_t *out_dev,
+                                   void *stream) {
+    if (!gate_dev || !up_dev || !out_dev || n <= 0 || frac < 1 || frac > 29) return 1;
+    return iie::launch_q1_silu_mul(gate_dev, up_dev, n, (int)frac, out_dev, (cudaStream_t)stream) == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int iie_q1_embed_dev(long long handle, const int *row_dev, long long row, int64_t *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(q_mu);
+    if (!valid(handle) || !out_dev) return 1;
+    const Q1Weight &w = q_w[(size_t)handle];
+    if (!row_dev && (row < 0 || row >= w.out_f)) return 1;
+    return iie::launch_q1_embed_row(w.units, w.sc32, w.nb, row_dev, row, out_dev, (cudaStream_t)stream) == cudaSuccess ? 0 : 2;
+}
+
 extern "C" int iie_q1_weight_shape(long long handle, long long *out_f, long long *n_blocks, int *scale_bits) {
     std::lock_guard<std::recursive_mutex> lk(q_mu);
     if (!valid(handle)) return 1;

@@ -24,7 +24,7 @@ EXPORTED_SYMBOLS = (
     "bonsai_gpu_mem_info", "bonsai_q1_resident_weight_bytes", "bonsai_q1_linear_gpu", "bonsai_q1_linear_dp4a_gpu",
     "bonsai_q1_register_weight", "bonsai_q1_register_weight_i32", "bonsai_q1_register_weight_i32_gpu_layout",
     "bonsai_q1_register_weight_i32_bmma", "bonsai_q1_apply_resident", "bonsai_q1_free_weights", "bonsai_rmsnorm_gpu",
-    "iie_q1_apply_dev", "iie_q1_weight_shape",
+    "iie_q1_apply_dev", "iie_q1_silu_mul_dev", "iie_q1_embed_dev", "iie_q1_weight_shape",
 )
 _L4_LO, _L4_HI = -2155905152, 2139062143      # balanced base-256 range of four digits (gpu_native.py:223)
 
@@ -65,6 +65,8 @@ def load_library():
         "bonsai_q1_apply_resident": ([i64, vp, i64, i64, vp], c_int), "bonsai_q1_free_weights": ([], None),
         "bonsai_rmsnorm_gpu": ([vp, i64, i64, i64, i64, vp, vp], c_int),
         "iie_q1_apply_dev": ([i64, vp, i64, i64, vp, vp], c_int),
+        "iie_q1_silu_mul_dev": ([vp, vp, i64, i64, vp, vp], c_int),
+        "iie_q1_embed_dev": ([i64, vp, i64, vp, vp], c_int),
         "iie_q1_weight_shape": ([i64, ctypes.POINTER(i64), ctypes.POINTER(i64), ctypes.POINTER(c_int)], c_int),
     }
     for name, (args, res) in sig.items():
@@ -227,4 +229,29 @@ def apply_dev(handle: int, x, frac: int, out=None):
                                   torch.cuda.current_stream().cuda_stream)
     if rc != 0:
         raise RuntimeError(f"iie_q1_apply_dev failed with status {rc}")
+    return out
+
+
+def silu_mul_dev(gate, up, frac: int, out=None):
+    """((gate * sigmoid(gate)) >> frac) * up >> frac with wrapping products, on CUDA int64 tensors of one shape."""
+    import torch
+
+    if out is None:
+        out = torch.empty_like(gate)
+    rc = _lib().iie_q1_silu_mul_dev(gate.data_ptr(), up.data_ptr(), gate.numel(), int(frac), out.data_ptr(),
+                                    torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"iie_q1_silu_mul_dev failed with status {rc}")
+    return out
+
+
+def embed_dev(handle: int, row, out):
+    """Row ``row`` (a CUDA int32 cell, or a Python int) of a registered weight as int64 into ``out`` [n_blocks*128]."""
+    import torch
+
+    cell = isinstance(row, torch.Tensor)
+    rc = _lib().iie_q1_embed_dev(int(handle), row.data_ptr() if cell else None, 0 if cell else int(row), out.data_ptr(),
+                                 torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"iie_q1_embed_dev failed with status {rc}")
     return out

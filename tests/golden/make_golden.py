@@ -168,6 +168,42 @@ def attention_fixture():
     return out
 
 
+def q1_decode_fixture():
+    """One KV-cached decode token of the reference's 1-bit decoder (reference_bonsai.py _run_layers) on a small
+    random artifact with non-trivial gains and scales: a 5-token prefill through the reference fills the cache, the
+    sixth token is the recorded step."""
+    from trinote.infer_int import reference_bonsai as rb
+    cfgp = {"dModel": 256, "nHeads": 4, "nHeadsKv": 2, "headDim": 64, "dFfn": 256, "vocab": 96, "nLayers": 2,
+            "fpFracBits": 16, "ropeBase": 10000}
+    art = rb.random_bonsai_artifact(cfgp, seq_len=8, seed=77)
+    rng = np.random.default_rng(78)
+    for layer in art["layers"] + [art]:
+        for key in list(layer):
+            if key.endswith("_gain_fp"):
+                layer[key] = np.rint((np.abs(rng.standard_normal(layer[key].shape)) + 0.5) * 65536).astype(np.int64)
+            if key.endswith("_scale_fp"):
+                sc = np.abs(rng.standard_normal(layer[key].shape) * 0.03).astype(np.float16)
+                layer[key] = np.rint(sc.astype(np.float64) * 65536).astype(np.int64)
+    model = rb.BonsaiReferenceModel(artifact=art)
+    cache = rb._BonsaiKVCache(2)
+    model._run_layers([3, 90, 41, 7, 66], cache)
+    out = {"cos": art["cos_fp"], "sin": art["sin_fp"], "token": np.int64(12), "pos": np.int64(5)}
+    for li in range(2):
+        out[f"k{li}"], out[f"v{li}"] = cache.k[li].copy(), cache.v[li].copy()
+    x = model._run_layers([12], cache)
+    frac = 16
+    xn = rb._rmsnorm(x, frac, art["final_norm_gain_fp"])
+    logits = model._output_linear(xn, frac, fast=False)
+    out["x"], out["logits"], out["next"] = x, logits, np.int64(int(logits.argmax(axis=1)[0]))
+    for li in range(2):
+        out[f"k{li}_after"], out[f"v{li}_after"] = cache.k[li].copy(), cache.v[li].copy()
+        for key, val in art["layers"][li].items():
+            out[f"L{li}_{key}"] = val
+    for key in ("embed_bits", "embed_scale_fp", "output_bits", "output_scale_fp", "final_norm_gain_fp"):
+        out[key] = art[key]
+    return out
+
+
 def main():
     np.savez_compressed(HERE / "half_fixed.npz", **half_fixture())
     np.savez_compressed(HERE / "codec.npz", **codec_fixture())
@@ -176,6 +212,7 @@ def main():
     np.savez_compressed(HERE / "q1.npz", **q1_fixture())
     np.savez_compressed(HERE / "moe.npz", **moe_fixture())
     np.savez_compressed(HERE / "attention.npz", **attention_fixture())
+    np.savez_compressed(HERE / "q1_decode.npz", **q1_decode_fixture())
 
 
 if __name__ == "__main__":

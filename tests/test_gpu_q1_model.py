@@ -1,0 +1,110 @@
+"""GPU parity of the 1-bit decoder's whole decode token (Q1_0 embedding row -> sequential attention / SwiGLU
+blocks -> Q1_0 head -> greedy pick): the reference's own recorded step, then seeded synthetic decoders against
+the CPU checker, eager and as a replayed CUDA graph; and the two element-wise entries it adds."""
+import numpy as np
+import pytest
+
+from oracle import model_oracle
+from oracle import qk_oracle as o
+from test_oracle_golden import q1_golden_layers
+
+pytestmark = pytest.mark.gpu
+FRAC = 16
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _library():
+    from integer_inference_engine_b200 import q1_gpu, qk_cuda
+    assert q1_gpu.gpu_available(), "the CUDA library must be built and a GPU present"
+    yield
+    q1_gpu.q1_free_weights()
+    qk_cuda.free_all()
+
+
+def test_swiglu_wraps_like_numpy():
+    import torch
+
+    from integer_inference_engine_b200 import q1_gpu
+    rng = np.random.default_rng(5)
+    gate = rng.integers(-(1 << 22), 1 << 22, size=4096, dtype=np.int64)
+    up = rng.integers(-(1 << 22), 1 << 22, size=4096, dtype=np.int64)
+    edge = np.array([np.iinfo(np.int64).min, np.iinfo(np.int64).max, -1, 0, 1, 1 << 62, -(1 << 62), 1 << 40, -(1 << 40)], np.int64)
+    gate[:9], up[:9] = edge, edge[::-1]
+    gate[9:18], up[9:18] = edge, 3 << 45
+    got = q1_gpu.silu_mul_dev(torch.from_numpy(gate).cuda(), torch.from_numpy(up).cuda(), FRAC).cpu().numpy()
+    assert np.array_equal(got, model_oracle.q1_swiglu(gate, up, FRAC))
+
+
+@pytest.mark.parametrize("wide", [False, True])
+def test_embedding_rows(wide):
+    import torch
+
+    from integer_inference_engine_b200 import q1_gpu
+    rng = np.random.default_rng(6 + wide)
+    bits, scale = o.synth_q1(rng, 70, 3)
+    if wide:
+        scale = rng.integers(-(1 << 40), 1 << 40, size=scale.shape, dtype=np.int64)
+    else:
+        scale = scale.astype(np.int32)
+    h = q1_gpu.q1_register_weight(bits, scale)
+    out = torch.empty(3 * 128, dtype=torch.int64, device="cuda")
+    cell = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for row in (0, 1, 15, 16, 37, 69):
+        want = model_oracle.q1_rows(bits, scale, row)[0]
+        assert np.array_equal(q1_gpu.embed_dev(h, row, out).cpu().numpy(), want)
+        cell.fill_(row)
+        assert np.array_equal(q1_gpu.embed_dev(h, cell, out).cpu().numpy(), want)
+    with pytest.raises(RuntimeError):
+        q1_gpu.embed_dev(h, 70, out)
+
+
+def test_recorded_reference_step(golden_dir):
+    import torch
+
+    from integer_inference_engine_b200 import device
+    from integer_inference_engine_b200.q1_model import Q1Decoder
+    g = np.load(golden_dir / "q1_decode.npz")
+    layers, top, cfg = q1_golden_layers(g, rows=8)
+    pos = int(g["pos"])
+    m = Q1Decoder(cfg["d"], cfg["H"], cfg["Hkv"], cfg["hd"], cfg["ffn"], 96, layers, top, g["cos"], g["sin"], pos, FRAC)
+    m.token.fill_(int(g["token"]))
+    device.read_flags()
+    m.step(pos)
+    torch.cuda.synchronize()
+    assert device.read_flags() == 0
+    assert np.array_equal(m.x.cpu().numpy(), g["x"])
+    assert np.array_equal(m.logits.cpu().numpy(), g["logits"]) and int(m.token.item()) == int(g["next"])
+    for li in range(2):
+        assert np.array_equal(m.layers[li]["k"][:, :pos + 1].cpu().numpy(), g[f"k{li}_after"])
+        assert np.array_equal(m.layers[li]["v"][:, :pos + 1].cpu().numpy(), g[f"v{li}_after"])
+
+
+def test_decode_steps_match_the_checker_eager_and_replayed():
+    import torch
+
+    from integer_inference_engine_b200 import device
+    from integer_inference_engine_b200.q1_model import SyntheticQ1Decoder
+    m = SyntheticQ1Decoder(n_layers=3, d_model=512, n_heads=8, n_kv=4, head_dim=64, d_ffn=768, vocab=1000, context=30,
+                           max_new=8, seed=11, keep_host=True)
+    layers = [dict(L, k=L["k"].cpu().numpy().astype(np.int64), v=L["v"].cpu().numpy().astype(np.int64)) for L in m.host_layers]
+    cfg = dict(d=m.d, H=m.H, Hkv=m.Hkv, hd=m.hd, ffn=m.ffn, frac=FRAC)
+    cos, sin = m.cos.cpu().numpy(), m.sin.cpu().numpy()
+    token, pos = 123, m.context
+    m.token.fill_(token)
+    device.read_flags()
+    for step in range(5):
+        if step == 2:
+            m.capture(m.context + 7)
+        want, trace, logits = model_oracle.q1_decode_token(token, pos, layers, m.host_top, cfg, cos, sin)
+        if step < 2:
+            m.step(pos)
+        else:
+            m.replay()
+        torch.cuda.synchronize()
+        assert device.read_flags() == 0
+        assert np.array_equal(m.x.cpu().numpy(), trace[-1:]), step
+        assert np.array_equal(m.logits.cpu().numpy()[0], logits), step
+        assert int(m.token.item()) == want and int(m.pos.item()) == pos + 1
+        for li in range(m.n_layers):
+            assert np.array_equal(m.layers[li]["k"][:, pos].cpu().numpy(), layers[li]["k"][:, pos]), (step, li)
+        token, pos = want, pos + 1

@@ -150,3 +150,36 @@ def test_attention_rope_softmax(golden_dir):
         ck = r2.integers(-(1 << 19), 1 << 19, size=(Hkv, Lc, hd), dtype=np.int64)
         cv = r2.integers(-(1 << 19), 1 << 19, size=(Hkv, Lc, hd), dtype=np.int64)
         assert np.array_equal(o.attention_cached(q, ck, cv, Lc - m, H, Hkv, FA, window), g[f"att_{name}"]), name
+
+
+def q1_golden_layers(g, rows=None):
+    """The 1-bit decode fixture (tests/golden/make_golden.py::q1_decode_fixture) in the checker's layer format."""
+    layers = []
+    for li in range(2):
+        w = lambda n: (g[f"L{li}_{n}_bits"], g[f"L{li}_{n}_scale_fp"])
+        cat = lambda *names: (np.concatenate([w(n)[0] for n in names]), np.concatenate([w(n)[1] for n in names]))
+        k0, v0 = g[f"k{li}"], g[f"v{li}"]
+        k = np.zeros((k0.shape[0], rows or k0.shape[1] + 1, k0.shape[2]), np.int64); k[:, :k0.shape[1]] = k0
+        v = np.zeros_like(k); v[:, :v0.shape[1]] = v0
+        layers.append({"n1": g[f"L{li}_n1_gain_fp"], "n2": g[f"L{li}_n2_gain_fp"], "qn": g[f"L{li}_q_norm_gain_fp"],
+                       "kn": g[f"L{li}_k_norm_gain_fp"], "wqkv": cat("wq", "wk", "wv"), "wo": w("wo"), "w1u": cat("w1", "wu"),
+                       "w2": w("w2"), "k": k, "v": v})
+    top = {"embed": (g["embed_bits"], g["embed_scale_fp"]), "head": (g["output_bits"], g["output_scale_fp"]),
+           "out_gain": g["final_norm_gain_fp"]}
+    cfg = dict(d=256, H=4, Hkv=2, hd=64, ffn=256, frac=16)
+    return layers, top, cfg
+
+
+def test_q1_decode_token(golden_dir):
+    """One KV-cached decode token of the reference's 1-bit decoder: hidden state, logits, pick and the appended
+    cache rows are the reference's own."""
+    from oracle import model_oracle
+    g = np.load(golden_dir / "q1_decode.npz")
+    layers, top, cfg = q1_golden_layers(g)
+    pos = int(g["pos"])
+    nxt, trace, logits = model_oracle.q1_decode_token(int(g["token"]), pos, layers, top, cfg, g["cos"], g["sin"])
+    assert np.array_equal(trace[-1:], g["x"])
+    assert np.array_equal(logits, g["logits"][0]) and nxt == int(g["next"])
+    for li in range(2):
+        assert np.array_equal(layers[li]["k"][:, :pos + 1], g[f"k{li}_after"])
+        assert np.array_equal(layers[li]["v"][:, :pos + 1], g[f"v{li}_after"])
