@@ -72,6 +72,20 @@ int bonsai_rmsnorm_gpu(const long long *x, long long rows, long long cols, long 
  * stream).  Scratch for the digit planes is process-global and grows on demand: one caller at a time. */
 int iie_q1_apply_dev(long long handle, const int64_t *x_dev, long long tokens, long long frac, int64_t *out_dev,
                      void *stream);
+/* Product with the activation step before it and the residual after it in the same two launches:
+ *   mode 0: a = x;   mode 1: a = rmsnorm(x, gain_dev, eps 1) (gain_dev NULL = no gain; an envelope violation sets
+ *   bit 1 of the flag word iie_flags_read_clear reports);   mode 2: a = ((x * sigmoid(x)) >> frac) * x2 >> frac with
+ *   wrapping products, x and x2 rows `ld` apart (reference_bonsai.py:603-615 _ffn_ref).
+ *   out = a W^T (+ add_dev when not NULL; add_dev may be out_dev).  x is [tokens][n_blocks*128] (mode 2: row stride ld).
+ * 0 ok, 1 bad argument, 2 CUDA failure. */
+int iie_q1_apply_fused_dev(long long handle, int mode, const int64_t *x_dev, const int64_t *x2_dev, long long ld,
+                           const int64_t *gain_dev, long long tokens, long long frac, const int64_t *add_dev,
+                           int64_t *out_dev, void *stream);
+/* RMSNorm (eps 1) of rows_a + rows_b consecutive rows of `width` values in one launch: the first rows_a rows with
+ * gain_a_dev, the rest with gain_b_dev (the per-head query and key norms of reference_bonsai.py:286-297,672-673).
+ * Envelope violations set bit 1 of the flag word.  0 ok, 1 bad argument, 2 CUDA failure. */
+int iie_q1_head_norm_dev(const int64_t *x_dev, long long rows_a, long long rows_b, long long width, const int64_t *gain_a_dev,
+                         const int64_t *gain_b_dev, long long frac, int64_t *out_dev, void *stream);
 /* out = ((gate * sigmoid(gate)) >> frac) * up >> frac, both products modulo 2^64: the SwiGLU of
  * bonsai/src/trinote/infer_int/reference_bonsai.py:246-262 and 611-614.  0 ok, 1 bad argument, 2 CUDA failure. */
 int iie_q1_silu_mul_dev(const int64_t *gate_dev, const int64_t *up_dev, long long n, long long frac, int64_t *out_dev,

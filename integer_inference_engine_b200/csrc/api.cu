@@ -563,6 +563,13 @@ int apply_resident_impl(long long h, const int64_t *x, long long T, int fw, int6
 // ====================================================================================================
 // Part 1: reference ABI v5
 // ====================================================================================================
+namespace iie {
+int *shared_flag_word() {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    return init() ? g_flags : nullptr;
+}
+}  // namespace iie
+
 extern "C" int qk_cuda_abi_version(void) { return 5; }
 
 extern "C" int qk_cuda_available(void) {

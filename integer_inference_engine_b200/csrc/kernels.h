@@ -210,6 +210,10 @@ cudaError_t launch_topk(const int64_t *logits, long long rows, int n_experts, in
 // Integer RMSNorm with optional gain; flags bit 1 set when a row leaves the exact envelope.
 cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
                            unsigned long long eps, int64_t *out, int *flags, cudaStream_t s);
+// the same with the normalised rows also (out may be NULL: only) written as Q1_0 activation operands: digit planes
+// [row][8][width] and 128-element block sums [row][width/128]; width must be a multiple of 128
+cudaError_t launch_rmsnorm_planes(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
+                                  unsigned long long eps, int64_t *out, int8_t *planes, int64_t *totals, int *flags, cudaStream_t s);
 
 // Counting-sort dispatch of (token, slot) pairs by expert (single CTA, n_experts <= 1024).
 //   ids [T*k], gates [T*k] -> grp_off [E+1], pair_tok [T*k] (token of each sorted pair),
@@ -259,7 +263,13 @@ cudaError_t launch_q1_repack(const uint8_t *bits, const void *scale, int src_bit
 cudaError_t launch_q1_prep(const int64_t *x, long long T, long long nb, int8_t *planes, int64_t *totals, int *nl_out,
                            cudaStream_t s);
 cudaError_t launch_q1_apply(const uint8_t *units, bool sc32, long long out_f, long long nb, const int8_t *planes,
-                            const int64_t *totals, long long T, long long frac, int64_t *out, cudaStream_t s);
+                            const int64_t *totals, long long T, long long frac, int64_t *out, cudaStream_t s,
+                            const int64_t *add = nullptr);
+cudaError_t launch_q1_prep_swiglu(const int64_t *gate, const int64_t *up, long long ld, int frac, long long T, long long nb,
+                                  int8_t *planes, int64_t *totals, cudaStream_t s);
+cudaError_t launch_rmsnorm_pair(const int64_t *x, long long rows_a, long long rows_b, long long width, const int64_t *gain_a,
+                                const int64_t *gain_b, int fa, unsigned long long eps, int64_t *out, int *flags, cudaStream_t s);
+int *shared_flag_word();           // the library's device flag word (bit 1: RMSNorm envelope), NULL without a device
 cudaError_t launch_q1_silu_mul(const int64_t *gate, const int64_t *up, long long n, int frac, int64_t *out, cudaStream_t s);
 cudaError_t launch_q1_embed_row(const uint8_t *units, bool sc32, long long nb, const int *row_dev, long long row_host, int64_t *out,
                                 cudaStream_t s);

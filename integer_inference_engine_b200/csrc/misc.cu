@@ -258,12 +258,39 @@ __device__ u128 isqrt_fast(u128 v) {
     return isqrt_u128(v);
 }
 
-__global__ void __launch_bounds__(1024) rmsnorm_kernel(const int64_t *x, long long rows, long long width, const int64_t *gain,
-                                                       int fa, unsigned long long eps, int64_t *out, int *flags) {
+// one element of the normalised row: floor((x << fa) / rms), then (y * gain) >> fa; `bad` is set (and 0 returned)
+// where the oracle's envelope checks would refuse the value
+__device__ __forceinline__ int64_t norm_value(int64_t xv, unsigned long long rms, unsigned long long gm, int64_t g, bool has_gain,
+                                              int fa, bool &bad) {
+    int64_t y;
+    if (uabs64(xv) < (1ULL << (62 - fa)) && rms <= (unsigned long long)INT64_MAX) {     // x << fa fits a signed 64-bit dividend
+        const int64_t num = xv * ((int64_t)1 << fa), den = (int64_t)rms;
+        y = num / den;
+        if (num < 0 && y * den != num) y -= 1;                  // floor toward -inf
+    } else {
+        const i128 num = (i128)xv << fa;
+        i128 q = num / (i128)rms;
+        if (num < 0 && q * (i128)rms != num) q -= 1;
+        if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; return 0; }
+        y = (int64_t)q;
+    }
+    if (has_gain) {
+        // the oracle refuses a gain product that could leave int64
+        if ((u128)uabs64(y) * gm > (u128)INT64_MAX) { bad = true; return 0; }
+        y = (int64_t)(((i128)y * g) >> fa);
+    }
+    return y;
+}
+
+// rows from `rows_a` on use gain_b (per-head norms of queries and keys in one launch)
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const int64_t *x, long long rows, long long width, const int64_t *gain_a,
+                                                       int fa, unsigned long long eps, int64_t *out, int *flags,
+                                                       int8_t *planes, int64_t *totals, const int64_t *gain_b, long long rows_a) {
     __shared__ unsigned long long s_lo[32], s_hi[32], s_max[32], s_gmax[32];
     __shared__ unsigned long long s_rms, s_gm;
     __shared__ int s_bad;
     const long long row = blockIdx.x;
+    const int64_t *gain = row < rows_a ? gain_a : gain_b;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int64_t *xr = x + row * width;
     int64_t *yr = out + row * width;
@@ -304,28 +331,33 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const int64_t *x, long lo
     if (s_bad) { if (tid == 0) atomicOr(flags, 2); return; }
     const unsigned long long rms = s_rms;
     const unsigned long long gm = s_gm;
-    const unsigned long long narrow = 1ULL << (62 - fa);           // |x| below this: x << fa fits a signed 64-bit dividend
     bool bad = false;
-    for (long long i = tid; i < width; i += blockDim.x) {
-        const int64_t xv = xr[i];
-        int64_t y;
-        if (uabs64(xv) < narrow && rms <= (unsigned long long)INT64_MAX) {
-            const int64_t num = xv * ((int64_t)1 << fa), den = (int64_t)rms;
-            y = num / den;
-            if (num < 0 && y * den != num) y -= 1;                  // floor toward -inf
-        } else {
-            const i128 num = (i128)xv << fa;
-            i128 q = num / (i128)rms;
-            if (num < 0 && q * (i128)rms != num) q -= 1;
-            if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; continue; }
-            y = (int64_t)q;
+    if (planes) {
+        // digit planes [row][8][width] and 128-element block sums of the normalised row, for the Q1_0 product
+        const long long nb = width >> 7;
+        for (long long b = warp; b < nb; b += nwarps) {
+            const long long i0 = b * 128 + lane * 4;
+            uint32_t pl[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            unsigned long long sum = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int64_t y = norm_value(xr[i0 + j], rms, gm, gain ? gain[i0 + j] : 0, gain != nullptr, fa, bad);
+                if (out) yr[i0 + j] = y;
+                bool ok;
+                const uint64_t d = balanced_digits8(y, ok);
+                sum += (unsigned long long)y;
+#pragma unroll
+                for (int l = 0; l < 8; l++) pl[l] |= (uint32_t)((d >> (8 * l)) & 0xFF) << (8 * j);
+            }
+#pragma unroll
+            for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(planes + (row * 8 + l) * width + i0) = pl[l];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            if (lane == 0) totals[row * nb + b] = (int64_t)sum;
         }
-        if (gain) {
-            // the oracle refuses a gain product that could leave int64
-            if ((u128)uabs64(y) * gm > (u128)INT64_MAX) { bad = true; continue; }
-            y = (int64_t)(((i128)y * gain[i]) >> fa);
-        }
-        yr[i] = y;
+    } else {
+        for (long long i = tid; i < width; i += blockDim.x)
+            yr[i] = norm_value(xr[i], rms, gm, gain ? gain[i] : 0, gain != nullptr, fa, bad);
     }
     if (bad) atomicOr(flags, 2);
 }
@@ -402,7 +434,25 @@ cudaError_t launch_topk(const int64_t *logits, long long rows, int n_experts, in
 cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
                            unsigned long long eps, int64_t *out, int *flags, cudaStream_t s) {
     const int threads = width >= 2048 ? 1024 : width > 128 ? 256 : 128;
-    rmsnorm_kernel<<<(unsigned)rows, threads, 0, s>>>(x, rows, width, gain, fa, eps, out, flags);
+    rmsnorm_kernel<<<(unsigned)rows, threads, 0, s>>>(x, rows, width, gain, fa, eps, out, flags, nullptr, nullptr, nullptr, rows);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rmsnorm_pair(const int64_t *x, long long rows_a, long long rows_b, long long width, const int64_t *gain_a,
+                                const int64_t *gain_b, int fa, unsigned long long eps, int64_t *out, int *flags, cudaStream_t s) {
+    const int threads = width >= 2048 ? 1024 : width > 128 ? 256 : 128;
+    rmsnorm_kernel<<<(unsigned)(rows_a + rows_b), threads, 0, s>>>(x, rows_a + rows_b, width, gain_a, fa, eps, out, flags, nullptr, nullptr,
+                                                                  gain_b, rows_a);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rmsnorm_planes(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
+                                  unsigned long long eps, int64_t *out, int8_t *planes, int64_t *totals, int *flags, cudaStream_t s) {
+    if (width <= 0 || (width & 127) || !planes || !totals) return cudaErrorInvalidValue;
+    const int threads = width >= 4096 ? 1024 : width >= 1024 ? (int)(width >> 2) : 256;      // one warp per 128-element block
+    rmsnorm_kernel<<<(unsigned)rows, threads, 0, s>>>(x, rows, width, gain, fa, eps, out, flags, planes, totals, nullptr, rows);
     note_launch();
     return cudaGetLastError();
 }

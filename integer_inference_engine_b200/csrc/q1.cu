@@ -59,14 +59,28 @@ __global__ void q1_repack_kernel(const uint8_t *bits, const ST *scale, long long
 }
 
 // ---- activations: digit planes [tok][8][K], block sums [tok][nb], digits in use ---------------------------
-__global__ void q1_prep_kernel(const int64_t *x, long long T, long long nb, int8_t *planes, int64_t *totals, int *nl_out) {
+// With `up` the activation is the SwiGLU of two rows of width K: ((x * sigmoid(x)) >> frac) * up >> frac, wrapping products;
+// x and up then advance by `ld` per token.
+__global__ void q1_prep_kernel(const int64_t *x, const int64_t *up, long long ld, int frac, int64_t log2e, int64_t clip, long long T,
+                               long long nb, int8_t *planes, int64_t *totals, int *nl_out) {
     const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (wid >= T * nb) return;
     const long long tok = wid / nb, b = wid - tok * nb, K = nb * 128;
-    const int64_t *src = x + tok * K + b * 128 + lane * 4;
+    const int64_t *src = x + tok * (up ? ld : K) + b * 128 + lane * 4;
     const longlong2 v0 = *reinterpret_cast<const longlong2 *>(src), v1 = *reinterpret_cast<const longlong2 *>(src + 2);
-    const int64_t v[4] = {v0.x, v0.y, v1.x, v1.y};
+    int64_t v[4] = {v0.x, v0.y, v1.x, v1.y};
+    if (up) {
+        const int64_t *us = up + tok * ld + b * 128 + lane * 4;
+        const longlong2 u0 = *reinterpret_cast<const longlong2 *>(us), u1 = *reinterpret_cast<const longlong2 *>(us + 2);
+        const int64_t u[4] = {u0.x, u0.y, u1.x, u1.y};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int64_t sg = sigmoid_fixed_c(v[i], frac, log2e, clip);
+            const int64_t silu = (int64_t)((unsigned long long)v[i] * (unsigned long long)sg) >> frac;
+            v[i] = (int64_t)((unsigned long long)silu * (unsigned long long)u[i]) >> frac;
+        }
+    }
     uint32_t pl[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     unsigned long long sum = 0;
     int nl = 0;
@@ -100,6 +114,7 @@ struct Q1Args {
     const int8_t *xl;               // [T][8][K]
     const int64_t *totals;          // [T][nb]
     int64_t *out;                   // [T][out_f]
+    const int64_t *add;             // optional [T][out_f] added to the product (may be `out` itself)
 };
 
 // A fragments of MMA m from the two bit words of a lane
@@ -201,7 +216,7 @@ __global__ void __launch_bounds__(512) q1_gemv_kernel(const Q1Args a) {
     __syncthreads();
     for (int i = threadIdx.x; i < ntile * 16; i += blockDim.x) {
         const long long row = tile0 * 16 + i;
-        if (row < a.out_f) a.out[row] = (int64_t)q1_red[i];
+        if (row < a.out_f) a.out[row] = (int64_t)(q1_red[i] + (a.add ? (unsigned long long)a.add[row] : 0ULL));
     }
 }
 
@@ -269,8 +284,10 @@ __global__ void __launch_bounds__(256, 2) q1_tile_kernel(const Q1Args a) {
         const long long tok = tok0 + 4 * q + t;
         if (q < ngrp && tok < a.T) {
             const long long row = tile * 16 + g;
-            if (row < a.out_f) a.out[tok * a.out_f + row] = (int64_t)acc[q][0];
-            if (row + 8 < a.out_f) a.out[tok * a.out_f + row + 8] = (int64_t)acc[q][1];
+            if (row < a.out_f)
+                a.out[tok * a.out_f + row] = (int64_t)(acc[q][0] + (a.add ? (unsigned long long)a.add[tok * a.out_f + row] : 0ULL));
+            if (row + 8 < a.out_f)
+                a.out[tok * a.out_f + row + 8] = (int64_t)(acc[q][1] + (a.add ? (unsigned long long)a.add[tok * a.out_f + row + 8] : 0ULL));
         }
     }
 }
@@ -349,18 +366,28 @@ cudaError_t launch_q1_repack(const uint8_t *bits, const void *scale, int src_bit
 
 cudaError_t launch_q1_prep(const int64_t *x, long long T, long long nb, int8_t *planes, int64_t *totals, int *nl_out, cudaStream_t s) {
     const long long warps = T * nb;
-    q1_prep_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(x, T, nb, planes, totals, nl_out);
+    q1_prep_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(x, nullptr, 0, 0, 0, 0, T, nb, planes, totals, nl_out);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_q1_prep_swiglu(const int64_t *gate, const int64_t *up, long long ld, int frac, long long T, long long nb,
+                                  int8_t *planes, int64_t *totals, cudaStream_t s) {
+    if (!gate || !up || frac < 1 || frac > 29) return cudaErrorInvalidValue;
+    const long long warps = T * nb;
+    q1_prep_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(gate, up, ld, frac, sigmoid_log2e(frac), sigmoid_clip(frac), T, nb,
+                                                                        planes, totals, nullptr);
     note_launch();
     return cudaGetLastError();
 }
 
 cudaError_t launch_q1_apply(const uint8_t *units, bool sc32, long long out_f, long long nb, const int8_t *planes,
-                            const int64_t *totals, long long T, long long frac, int64_t *out, cudaStream_t s) {
+                            const int64_t *totals, long long T, long long frac, int64_t *out, cudaStream_t s, const int64_t *add) {
     if (out_f <= 0 || nb <= 0 || T <= 0) return cudaErrorInvalidValue;
     Q1Args a;
     a.units = units; a.out_f = out_f; a.nb = nb; a.n_tiles = (out_f + 15) / 16; a.T = T;
     a.sh = frac <= 0 ? 0 : (frac >= 63 ? 63 : (int)frac);
-    a.tiles_per_cta = 1; a.xl = planes; a.totals = totals; a.out = out;
+    a.tiles_per_cta = 1; a.xl = planes; a.totals = totals; a.out = out; a.add = add;
     return sc32 ? launch_apply_t<int>(a, s) : launch_apply_t<long long>(a, s);
 }
 

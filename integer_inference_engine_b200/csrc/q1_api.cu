@@ -264,6 +264,41 @@ extern "C" int iie_q1_apply_dev(long long handle, const int64_t *x_dev, long lon
     return apply_device(q_w[(size_t)handle], x_dev, tokens, frac, out_dev, 8, (cudaStream_t)stream);
 }
 
+extern "C" int iie_q1_apply_fused_dev(long long handle, int mode, const int64_t *x_dev, const int64_t *x2_dev, long long ld,
+                                      const int64_t *gain_dev, long long tokens, long long frac, const int64_t *add_dev,
+                                      int64_t *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(q_mu);
+    if (!valid(handle) || !x_dev || !out_dev || tokens <= 0 || mode < 0 || mode > 2 || frac < 1 || frac > 29) return 1;
+    const Q1Weight &w = q_w[(size_t)handle];
+    const long long K = w.nb * 128, T = tokens;
+    cudaStream_t s = (cudaStream_t)stream;
+    int8_t *planes = (int8_t *)q_ensure(QR_PLANES, (size_t)T * 8 * K);
+    int64_t *totals = (int64_t *)q_ensure(QR_TOTALS, (size_t)T * w.nb * 8);
+    if (!planes || !totals) return 2;
+    cudaError_t e;
+    if (mode == 1) {
+        int *flags = iie::shared_flag_word();
+        if (!flags) return 2;
+        e = iie::launch_rmsnorm_planes(x_dev, T, K, gain_dev, (int)frac, 1ULL, nullptr, planes, totals, flags, s);
+    } else if (mode == 2) {
+        if (!x2_dev || ld < K) return 1;
+        e = iie::launch_q1_prep_swiglu(x_dev, x2_dev, ld, (int)frac, T, w.nb, planes, totals, s);
+    } else {
+        e = iie::launch_q1_prep(x_dev, T, w.nb, planes, totals, nullptr, s);
+    }
+    if (e != cudaSuccess) return 2;
+    return iie::launch_q1_apply(w.units, w.sc32, w.out_f, w.nb, planes, totals, T, frac, out_dev, s, add_dev) == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int iie_q1_head_norm_dev(const int64_t *x_dev, long long rows_a, long long rows_b, long long width, const int64_t *gain_a_dev,
+                                    const int64_t *gain_b_dev, long long frac, int64_t *out_dev, void *stream) {
+    if (!x_dev || !out_dev || rows_a < 0 || rows_b < 0 || rows_a + rows_b <= 0 || width <= 0 || frac < 1 || frac > 29) return 1;
+    int *flags = iie::shared_flag_word();
+    if (!flags) return 2;
+    return iie::launch_rmsnorm_pair(x_dev, rows_a, rows_b, width, gain_a_dev, gain_b_dev, (int)frac, 1ULL, out_dev, flags,
+                                    (cudaStream_t)stream) == cudaSuccess ? 0 : 2;
+}
+
 extern "C" int iie_q1_silu_mul_dev(const int64_t *gate_dev, const int64_t *up_dev, long long n, long long frac, int64_t *out_dev,
                                    void *stream) {
     if (!gate_dev || !up_dev || !out_dev || n <= 0 || frac < 1 || frac > 29) return 1;

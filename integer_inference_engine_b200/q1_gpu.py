@@ -24,7 +24,7 @@ EXPORTED_SYMBOLS = (
     "bonsai_gpu_mem_info", "bonsai_q1_resident_weight_bytes", "bonsai_q1_linear_gpu", "bonsai_q1_linear_dp4a_gpu",
     "bonsai_q1_register_weight", "bonsai_q1_register_weight_i32", "bonsai_q1_register_weight_i32_gpu_layout",
     "bonsai_q1_register_weight_i32_bmma", "bonsai_q1_apply_resident", "bonsai_q1_free_weights", "bonsai_rmsnorm_gpu",
-    "iie_q1_apply_dev", "iie_q1_silu_mul_dev", "iie_q1_embed_dev", "iie_q1_weight_shape",
+    "iie_q1_apply_dev", "iie_q1_apply_fused_dev", "iie_q1_head_norm_dev", "iie_q1_silu_mul_dev", "iie_q1_embed_dev", "iie_q1_weight_shape",
 )
 _L4_LO, _L4_HI = -2155905152, 2139062143      # balanced base-256 range of four digits (gpu_native.py:223)
 
@@ -65,6 +65,8 @@ def load_library():
         "bonsai_q1_apply_resident": ([i64, vp, i64, i64, vp], c_int), "bonsai_q1_free_weights": ([], None),
         "bonsai_rmsnorm_gpu": ([vp, i64, i64, i64, i64, vp, vp], c_int),
         "iie_q1_apply_dev": ([i64, vp, i64, i64, vp, vp], c_int),
+        "iie_q1_apply_fused_dev": ([i64, c_int, vp, vp, i64, vp, i64, i64, vp, vp, vp], c_int),
+        "iie_q1_head_norm_dev": ([vp, i64, i64, i64, vp, vp, i64, vp, vp], c_int),
         "iie_q1_silu_mul_dev": ([vp, vp, i64, i64, vp, vp], c_int),
         "iie_q1_embed_dev": ([i64, vp, i64, vp, vp], c_int),
         "iie_q1_weight_shape": ([i64, ctypes.POINTER(i64), ctypes.POINTER(i64), ctypes.POINTER(c_int)], c_int),
@@ -254,4 +256,38 @@ def embed_dev(handle: int, row, out):
                                  torch.cuda.current_stream().cuda_stream)
     if rc != 0:
         raise RuntimeError(f"iie_q1_embed_dev failed with status {rc}")
+    return out
+
+
+def apply_fused_dev(handle: int, x, frac: int, out, *, gain=None, norm: bool = False, up=None, add=None):
+    """``out = a W^T (+ add)`` with ``a = x`` (default), ``rmsnorm(x, gain)`` (``norm=True``; ``gain`` a CUDA int64 row or
+    None) or the wrapping SwiGLU of ``x`` (gate) and ``up``.  All tensors CUDA int64; ``x`` [T, n_blocks*128] (gate / up may
+    be column slices of one [T, ld] tensor); ``add`` may be ``out``."""
+    import torch
+
+    mode = 1 if norm else (2 if up is not None else 0)
+    T = x.shape[0]
+    ld = x.stride(0) if mode == 2 else x.shape[1]
+    if mode == 2 and (up.stride(0) != ld or x.stride(1) != 1 or up.stride(1) != 1):
+        raise ValueError("gate and up must share one row stride")
+    if mode != 2 and not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    with _CUDA_LOCK:
+        rc = _lib().iie_q1_apply_fused_dev(int(handle), mode, x.data_ptr(), ptr(up), int(ld), ptr(gain), int(T), int(frac),
+                                           ptr(add), out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"iie_q1_apply_fused_dev failed with status {rc}")
+    return out
+
+
+def head_norm_dev(x, rows_a: int, rows_b: int, width: int, gain_a, gain_b, frac: int, out):
+    """RMSNorm of ``rows_a + rows_b`` consecutive rows of ``width`` values: the first ``rows_a`` with ``gain_a``, the rest with
+    ``gain_b`` (CUDA int64 rows), one launch."""
+    import torch
+
+    rc = _lib().iie_q1_head_norm_dev(x.data_ptr(), int(rows_a), int(rows_b), int(width), gain_a.data_ptr(), gain_b.data_ptr(),
+                                     int(frac), out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"iie_q1_head_norm_dev failed with status {rc}")
     return out

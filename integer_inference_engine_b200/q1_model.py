@@ -19,7 +19,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from . import device, q1_gpu, qk_cuda
+from . import device, q1_gpu
 from .model import rope_tables
 
 
@@ -41,7 +41,7 @@ class Q1Decoder:
         self.vocab, self.frac, self.context = vocab, frac, context
         qd, kd = n_heads * head_dim, n_kv * head_dim
         reg = lambda w: q1_gpu.q1_register_weight(np.ascontiguousarray(w[0]), np.ascontiguousarray(w[1]))
-        gain = lambda g: qk_cuda.register_i64(np.ascontiguousarray(g, dtype=np.int64))
+        gain = lambda g: torch.from_numpy(np.ascontiguousarray(g, dtype=np.int64)).cuda()
         dev = lambda c: c if isinstance(c, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(c, dtype=np.int32)).cuda()
         self.layers = []
         for L in layers:
@@ -54,8 +54,8 @@ class Q1Decoder:
         self.pos = torch.tensor([context], dtype=torch.int32, device="cuda")        # position of the next token
         self.token = torch.zeros(1, dtype=torch.int32, device="cuda")               # its id
         z = lambda n: torch.empty((1, n), dtype=torch.int64, device="cuda")
-        self.x, self.hn, self.qkv, self.qkvn, self.att, self.proj = z(d_model), z(d_model), z(qd + 2 * kd), z(qd + kd), z(qd), z(d_model)
-        self.gu, self.act, self.logits = z(2 * d_ffn), z(d_ffn), z(vocab)
+        self.x, self.qkv, self.qkvn, self.att = z(d_model), z(qd + 2 * kd), z(qd + kd), z(qd)
+        self.gu, self.logits = z(2 * d_ffn), z(vocab)
 
     def weight_bytes_per_token(self) -> int:
         """Sign bits + int32 scales every matrix streams for one token (one embedding row excluded)."""
@@ -65,25 +65,20 @@ class Q1Decoder:
         return (self.n_layers * rows_in + self.vocab * self.d) // 128 * per_block
 
     def step(self, pos_bound: int) -> None:
+        """One token: reads ``self.token`` / ``self.pos`` on the device, leaves the next id in ``self.token`` and advances
+        ``self.pos``.  Per layer ten launches: norm + digit planes, QKV product, both head norms, attention, planes,
+        O product with the residual, norm + planes, gate/up product, SwiGLU + planes, down product with the residual."""
         f, qd, kd = self.frac, self.H * self.hd, self.Hkv * self.hd
         q1_gpu.embed_dev(self.embed, self.token, self.x)
         for L in self.layers:
-            device.rmsnorm(self.x, L["n1"], f, 1, out=self.hn)
-            q1_gpu.apply_dev(L["wqkv"], self.hn, f, out=self.qkv)
-            device.rmsnorm(self.qkv[:, :qd].view(self.H, self.hd), L["qn"], f, 1, out=self.qkvn[:, :qd].view(self.H, self.hd))
-            device.rmsnorm(self.qkv[:, qd:qd + kd].view(self.Hkv, self.hd), L["kn"], f, 1,
-                           out=self.qkvn[:, qd:].view(self.Hkv, self.hd))
+            q1_gpu.apply_fused_dev(L["wqkv"], self.x, f, self.qkv, norm=True, gain=L["n1"])
+            q1_gpu.head_norm_dev(self.qkv, self.H, self.Hkv, self.hd, L["qn"], L["kn"], f, self.qkvn)
             device.attention_decode(self.qkvn[0, :qd], self.qkvn[0, qd:], self.qkv[0, qd + kd:], L["k"], L["v"], pos_bound,
                                     self.H, self.Hkv, self.hd, f, 0, self.cos, self.sin, 2, out=self.att.view(-1), pos_dev=self.pos)
-            q1_gpu.apply_dev(L["wo"], self.att, f, out=self.proj)
-            self.x += self.proj
-            device.rmsnorm(self.x, L["n2"], f, 1, out=self.hn)
-            q1_gpu.apply_dev(L["w1u"], self.hn, f, out=self.gu)
-            q1_gpu.silu_mul_dev(self.gu[:, :self.ffn], self.gu[:, self.ffn:], f, out=self.act)
-            q1_gpu.apply_dev(L["w2"], self.act, f, out=self.proj)
-            self.x += self.proj
-        device.rmsnorm(self.x, self.out_gain, f, 1, out=self.hn)
-        q1_gpu.apply_dev(self.head, self.hn, f, out=self.logits)
+            q1_gpu.apply_fused_dev(L["wo"], self.att, f, self.x, add=self.x)
+            q1_gpu.apply_fused_dev(L["w1u"], self.x, f, self.gu, norm=True, gain=L["n2"])
+            q1_gpu.apply_fused_dev(L["w2"], self.gu[:, :self.ffn], f, self.x, up=self.gu[:, self.ffn:], add=self.x)
+        q1_gpu.apply_fused_dev(self.head, self.x, f, self.logits, norm=True, gain=self.out_gain)
         device.argmax(self.logits.view(-1), out=self.token)
         self.pos += 1
 

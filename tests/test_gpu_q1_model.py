@@ -108,3 +108,61 @@ def test_decode_steps_match_the_checker_eager_and_replayed():
         for li in range(m.n_layers):
             assert np.array_equal(m.layers[li]["k"][:, pos].cpu().numpy(), layers[li]["k"][:, pos]), (step, li)
         token, pos = want, pos + 1
+
+
+@pytest.mark.parametrize("T", [1, 3])
+def test_fused_product_forms(T):
+    """Norm, SwiGLU and residual steps folded into the product's launches against their separate restatements."""
+    import torch
+
+    from integer_inference_engine_b200 import device, q1_gpu
+    from oracle import native as onat
+    rng = np.random.default_rng(40 + T)
+    nb, out_f = 4, 200
+    K = nb * 128
+    bits, scale = o.synth_q1(rng, out_f, nb)
+    h = q1_gpu.q1_register_weight(bits, scale.astype(np.int32))
+    x = o.to_fixed(rng.standard_normal((T, K)) * 3, FRAC)
+    gain = np.rint((np.abs(rng.standard_normal(K)) + 0.5) * (1 << FRAC)).astype(np.int64)
+    res = rng.integers(-(1 << 40), 1 << 40, size=(T, out_f), dtype=np.int64)
+    cuda = lambda a: torch.from_numpy(a).cuda()
+    device.read_flags()
+    out = torch.empty((T, out_f), dtype=torch.int64, device="cuda")
+    # plain, with a residual that is the output buffer itself
+    out.copy_(cuda(res))
+    q1_gpu.apply_fused_dev(h, cuda(x), FRAC, out, add=out)
+    assert np.array_equal(out.cpu().numpy(), onat.q1_linear(x, bits, scale, FRAC) + res)
+    # RMSNorm with and without a gain
+    for g in (gain, None):
+        q1_gpu.apply_fused_dev(h, cuda(x), FRAC, out, norm=True, gain=None if g is None else cuda(g))
+        assert np.array_equal(out.cpu().numpy(), onat.q1_linear(o.rmsnorm_fixed(x, FRAC, 1, g), bits, scale, FRAC))
+    # SwiGLU of two column slices of one buffer, plus a residual
+    gu = rng.integers(-(1 << 21), 1 << 21, size=(T, 2 * K), dtype=np.int64)
+    gu[0, :4] = [np.iinfo(np.int64).min, np.iinfo(np.int64).max, 1 << 50, -(1 << 50)]
+    gud = cuda(gu)
+    q1_gpu.apply_fused_dev(h, gud[:, :K], FRAC, out, up=gud[:, K:], add=cuda(res))
+    with np.errstate(over="ignore"):
+        want = onat.q1_linear(model_oracle.q1_swiglu(gu[:, :K], gu[:, K:], FRAC), bits, scale, FRAC) + res
+    assert np.array_equal(out.cpu().numpy(), want)
+    assert device.read_flags() == 0
+    # a row outside the RMSNorm envelope raises the flag instead of a wrong value
+    big = x.copy(); big[0, 0] = 1 << 60
+    q1_gpu.apply_fused_dev(h, cuda(big), FRAC, out, norm=True, gain=cuda(gain))
+    torch.cuda.synchronize()
+    assert device.read_flags() & 2
+
+
+def test_head_norms_in_one_launch():
+    import torch
+
+    from integer_inference_engine_b200 import device, q1_gpu
+    rng = np.random.default_rng(50)
+    H, Hkv, hd = 8, 2, 64
+    x = o.to_fixed(rng.standard_normal((H + Hkv, hd)) * 5, FRAC)
+    ga = np.rint((np.abs(rng.standard_normal(hd)) + 0.5) * (1 << FRAC)).astype(np.int64)
+    gb = np.rint((np.abs(rng.standard_normal(hd)) + 0.5) * (1 << FRAC)).astype(np.int64)
+    out = torch.empty((H + Hkv, hd), dtype=torch.int64, device="cuda")
+    device.read_flags()
+    q1_gpu.head_norm_dev(torch.from_numpy(x).cuda(), H, Hkv, hd, torch.from_numpy(ga).cuda(), torch.from_numpy(gb).cuda(), FRAC, out)
+    want = np.concatenate([o.rmsnorm_fixed(x[:H], FRAC, 1, ga), o.rmsnorm_fixed(x[H:], FRAC, 1, gb)])
+    assert np.array_equal(out.cpu().numpy(), want) and device.read_flags() == 0
