@@ -77,10 +77,20 @@ void qk_profile_reset(void);                         /* nmc_qk_cuda.cu:82 */
 void qk_profile_set_enabled(int enabled);            /* nmc_qk_cuda.cu:85 */
 int qk_profile_snapshot(unsigned long long *out, int capacity);   /* nmc_qk_cuda.cu:86, 28 counters */
 
-/* Request-scoped attention bank (decode attention sublayer and the retained-layer executor).
- * Present so that the reference bridge accepts the library; the attention sublayer is outside
- * the MoE hot path and these entries report failure (create returns -1, the others rc 1).
- *                                              nmc_qk_cuda.cu:877,914,927,935,984,1363,1530,1557,1658,1748,1765 */
+/* Request-scoped attention bank: per-layer K/V rows on the device and the single-token attention sublayer
+ * (Q/K/V products of a normalised hidden row, optional interleaved RoPE at position = rows held, K/V append, exact
+ * integer softmax attention over the rows held, O product).      nmc_qk_cuda.cu:877,914,927,1363,1530,1765
+ *   create  -> handle >= 0, or -1 (bad dimensions, an attention shape the kernels do not cover, out of memory)
+ *   import  -> host K/V [n_kv][length][head_dim] int64 of a prefill; rows are held as int32: after a value outside
+ *              int32 the next apply on that layer reports the guard (rc 3), where the reference holds int64 and
+ *              guards the products
+ *   apply   -> x [d_model] and out [>= d_model] are host rows; window -1 = attend to everything, > 0 = that many most
+ *              recent rows; rc 0 ok (the layer then holds one more row), 1 bad argument or CUDA failure, 3 an exact
+ *              envelope guard fired (K/V beyond int32 or an activation beyond eight base-256 digits); after 1 or 3 from
+ *              queued work the layer is poisoned until qk_attention_bank_reset
+ * The retained-layer executor entries (moe_configure, moe_bind, moe_begin, moe_continue, moe_export;
+ * nmc_qk_cuda.cu:935,984,1557,1658,1748) serve the case where the experts do not all fit on the device; they exist so
+ * that the reference bridge accepts the library and report failure (rc 1). */
 long long qk_attention_bank_create(int n_layers, long long max_length, long long d_model, int heads, int n_kv,
                                    int head_dim, int fa, const int64_t *cos, const int64_t *sin);
 int qk_attention_bank_reset(long long h);
@@ -91,12 +101,12 @@ int qk_attention_bank_moe_bind(long long h, int layer, int expert, long long gat
                                long long down_h);
 int qk_attention_bank_import(long long h, int layer, const int64_t *k, const int64_t *v, long long length);
 int qk_attention_bank_apply(long long h, int layer, long long qh, long long kh, long long vh, long long oh,
-                            const int64_t *x, int fw, int rope, int window, long long start,
+                            const int64_t *x, int fw, int window, int rope, long long inv_sqrt,
                             long long output_capacity, int64_t *out);
 int qk_attention_bank_moe_begin(long long h, int layer, long long gain_h, long long router_h, long long qh,
-                                long long kh, long long vh, long long oh, const int64_t *x, int fw, int rope,
-                                unsigned long long eps, int window, int used, long long start, int cold_capacity,
-                                int *cold_ids, int *cold_count);
+                                long long kh, long long vh, long long oh, const int64_t *x, int use_retained, int fw,
+                                unsigned long long eps, int window, int rope, long long inv_sqrt, int cold_capacity,
+                                int *cold_count_out, int *cold_ids_out);
 int qk_attention_bank_moe_continue(long long h, int layer, int fw, int publish, long long output_capacity,
                                    int64_t *out);
 int qk_attention_bank_moe_export(long long h, long long output_capacity, int64_t *out);

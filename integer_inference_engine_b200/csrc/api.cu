@@ -762,21 +762,16 @@ extern "C" unsigned long long qk_moe_workspace_bytes(void) {
 }
 extern "C" void qk_moe_workspace_release(void) { std::lock_guard<std::recursive_mutex> lk(g_mu); release_workspace(); }
 
-// ---- attention bank: outside the MoE hot path; the entries exist so the reference bridge loads -----------
-extern "C" long long qk_attention_bank_create(int, long long, long long, int, int, int, int, const int64_t *, const int64_t *) { return -1; }
-extern "C" int qk_attention_bank_reset(long long) { return 1; }
-extern "C" void qk_attention_bank_destroy(long long) {}
+// ---- attention bank, retained-layer executor part: only meaningful when the experts do not all fit on the device;
+// these entries report failure so the reference bridge keeps its host path for that protocol.  The bank itself
+// (create / import / apply) follows the attention entries further down.
 extern "C" int qk_attention_bank_moe_configure(long long, int, int, int, long long, long long) { return 1; }
 extern "C" int qk_attention_bank_moe_bind(long long, int, int, long long, long long, long long) { return 1; }
-extern "C" int qk_attention_bank_import(long long, int, const int64_t *, const int64_t *, long long) { return 1; }
-extern "C" int qk_attention_bank_apply(long long, int, long long, long long, long long, long long, const int64_t *, int,
-                                       int, int, long long, long long, int64_t *) { return 1; }
 extern "C" int qk_attention_bank_moe_begin(long long, int, long long, long long, long long, long long, long long,
                                            long long, const int64_t *, int, int, unsigned long long, int, int,
                                            long long, int, int *, int *) { return 1; }
 extern "C" int qk_attention_bank_moe_continue(long long, int, int, int, long long, int64_t *) { return 1; }
 extern "C" int qk_attention_bank_moe_export(long long, long long, int64_t *) { return 1; }
-extern "C" unsigned long long qk_attention_bank_workspace_bytes(long long) { return 0; }
 
 // ====================================================================================================
 // Part 2: device-pointer extension
@@ -998,6 +993,161 @@ extern "C" int iie_attn_decode_dev(const int64_t *q_dev, const int64_t *k_dev, c
     const cudaError_t e = launch_attn_decode(a, (cudaStream_t)stream);
     if (e != cudaSuccess) { cudaGetLastError(); return 1; }
     return 0;
+}
+
+// ---- attention bank (north-mini-code/tools/nmc_qk_cuda.cu:877-1551): request-scoped K/V rows on the device and the
+// single-token attention sublayer on a normalised hidden row: Q/K/V products, optional interleaved RoPE, K/V append,
+// exact softmax attention, O product.  K/V rows are kept as int32; a value that does not fit raises the guard
+// (status 3, layer poisoned) where the reference's own guards are wider.
+namespace {
+struct BankLayer { int32_t *k = nullptr, *v = nullptr; long long length = 0; bool poisoned = false, wide = false; };
+struct Bank {
+    bool live = false;
+    int n_layers = 0, heads = 0, n_kv = 0, head_dim = 0, fa = 0;
+    long long max_length = 0, d_model = 0;
+    int64_t *cos = nullptr, *sin = nullptr;
+    std::vector<BankLayer> layers;
+};
+std::vector<Bank> g_banks;
+
+bool valid_bank(long long h) { return h >= 0 && (size_t)h < g_banks.size() && g_banks[(size_t)h].live; }
+
+void destroy_bank(Bank &b) {
+    cudaDeviceSynchronize();
+    for (auto &l : b.layers) { if (l.k) cudaFree(l.k); if (l.v) cudaFree(l.v); }
+    if (b.cos) cudaFree(b.cos);
+    if (b.sin) cudaFree(b.sin);
+    b = Bank();
+}
+
+bool ensure_bank_layer(Bank &b, BankLayer &l) {
+    if (l.k && l.v) return true;
+    const size_t bytes = (size_t)b.n_kv * (size_t)b.max_length * (size_t)b.head_dim * sizeof(int32_t);
+    if (cudaMalloc(&l.k, bytes) != cudaSuccess || cudaMalloc(&l.v, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        if (l.k) cudaFree(l.k);
+        l.k = l.v = nullptr;
+        return false;
+    }
+    return true;
+}
+}  // namespace
+
+extern "C" long long qk_attention_bank_create(int n_layers, long long max_length, long long d_model, int heads, int n_kv,
+                                              int head_dim, int fa, const int64_t *cos, const int64_t *sin) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!cos || !sin || n_layers <= 0 || max_length <= 0 || d_model <= 0 || d_model % 256 != 0 || heads <= 0 || n_kv <= 0 ||
+        heads % n_kv != 0 || head_dim <= 0 || head_dim % 2 != 0 || fa < 1 || fa > 29 || ((long long)heads * head_dim) % 256 != 0 ||
+        max_length > (1LL << 30) || !attn_shape_ok(heads, n_kv, head_dim) || !init()) return -1;
+    Bank b;
+    const size_t table = (size_t)max_length * (size_t)(head_dim / 2) * 8;
+    if (cudaMalloc(&b.cos, table) != cudaSuccess || cudaMalloc(&b.sin, table) != cudaSuccess ||
+        cudaMemcpy(b.cos, cos, table, cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemcpy(b.sin, sin, table, cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        if (b.cos) cudaFree(b.cos);
+        if (b.sin) cudaFree(b.sin);
+        return -1;
+    }
+    b.live = true; b.n_layers = n_layers; b.max_length = max_length; b.d_model = d_model; b.heads = heads; b.n_kv = n_kv;
+    b.head_dim = head_dim; b.fa = fa; b.layers.resize((size_t)n_layers);
+    size_t slot = g_banks.size();
+    for (size_t i = 0; i < g_banks.size(); i++) if (!g_banks[i].live) { slot = i; break; }
+    if (slot == g_banks.size()) g_banks.push_back(Bank());
+    g_banks[slot] = std::move(b);
+    return (long long)slot;
+}
+
+extern "C" int qk_attention_bank_reset(long long h) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!valid_bank(h)) return 1;
+    for (auto &l : g_banks[(size_t)h].layers) { l.length = 0; l.poisoned = false; l.wide = false; }
+    return 0;
+}
+
+extern "C" void qk_attention_bank_destroy(long long h) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (valid_bank(h)) destroy_bank(g_banks[(size_t)h]);
+}
+
+extern "C" int qk_attention_bank_import(long long h, int layer, const int64_t *k, const int64_t *v, long long length) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!valid_bank(h)) return 1;
+    Bank &b = g_banks[(size_t)h];
+    if (!k || !v || layer < 0 || layer >= b.n_layers || length < 0 || length > b.max_length || b.layers[(size_t)layer].poisoned ||
+        !ensure_bank_layer(b, b.layers[(size_t)layer])) return 1;
+    BankLayer &l = b.layers[(size_t)layer];
+    const size_t per_head = (size_t)length * (size_t)b.head_dim;
+    if (per_head) {
+        // narrow on the host: a value outside int32 cannot be held, so the next apply on this layer reports the guard
+        std::vector<int32_t> kn((size_t)b.n_kv * per_head), vn((size_t)b.n_kv * per_head);
+        for (size_t i = 0; i < kn.size(); i++) {
+            if (k[i] < INT32_MIN || k[i] > INT32_MAX || v[i] < INT32_MIN || v[i] > INT32_MAX) l.wide = true;
+            kn[i] = (int32_t)k[i]; vn[i] = (int32_t)v[i];
+        }
+        for (int head = 0; head < b.n_kv; head++) {
+            const size_t src = (size_t)head * per_head, dst = (size_t)head * (size_t)b.max_length * (size_t)b.head_dim;
+            if (cudaMemcpy(l.k + dst, kn.data() + src, per_head * 4, cudaMemcpyHostToDevice) != cudaSuccess ||
+                cudaMemcpy(l.v + dst, vn.data() + src, per_head * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+                cudaGetLastError(); l.poisoned = true; return 1;
+            }
+        }
+    }
+    l.length = length;
+    return 0;
+}
+
+extern "C" int qk_attention_bank_apply(long long h, int layer, long long qh, long long kh, long long vh, long long oh,
+                                       const int64_t *x, int fw, int window, int rope, long long inv_sqrt,
+                                       long long output_capacity, int64_t *out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!valid_bank(h) || !x || !out || output_capacity <= 0) return 1;
+    Bank &b = g_banks[(size_t)h];
+    const long long d = b.d_model, qd = (long long)b.heads * b.head_dim, kd = (long long)b.n_kv * b.head_dim;
+    if (output_capacity < d || layer < 0 || layer >= b.n_layers || !valid_q(qh) || !valid_q(kh) || !valid_q(vh) || !valid_q(oh) ||
+        window == 0 || window < -1 || fw < 0 || fw > 62) return 1;
+    BankLayer &l = b.layers[(size_t)layer];
+    if (l.poisoned || l.length >= b.max_length || !ensure_bank_layer(b, l)) return 1;
+    const Weight &wq = g_w[qh], &wk = g_w[kh], &wv = g_w[vh], &wo = g_w[oh];
+    if (wq.nb != d / 256 || wk.nb != d / 256 || wv.nb != d / 256 || wq.out_f != qd || wk.out_f != kd || wv.out_f != kd ||
+        wo.nb != qd / 256 || wo.out_f != d) return 1;
+    if (l.wide) { l.poisoned = true; return 3; }            // imported rows did not fit the bank's int32 storage
+    int64_t *xd = (int64_t *)ensure(R_X, (size_t)d * 8);
+    int64_t *qkv = (int64_t *)ensure(R_TMP0, (size_t)(qd + 2 * kd) * 8);
+    int64_t *att = (int64_t *)ensure(R_TMP2, (size_t)qd * 8);
+    int64_t *od = (int64_t *)ensure(R_OUT, (size_t)d * 8);
+    int8_t *xl = (int8_t *)ensure(R_XL, (size_t)8 * (d > qd ? d : qd));      // also holds the planes of the O product's input
+    if (!xd || !qkv || !att || !od || !xl) return 1;
+    if (read_flags_clear() < 0 || !h2d(xd, x, (size_t)d * 8) || launch_limbs(xd, 1, d, xl, g_flags, g_stream) != cudaSuccess)
+        { cudaGetLastError(); return 1; }
+    bool ok = linear_dev(wq, xd, 1, fw, qkv, false, g_stream, xl) && linear_dev(wk, xd, 1, fw, qkv + qd, false, g_stream, xl) &&
+              linear_dev(wv, xd, 1, fw, qkv + qd + kd, false, g_stream, xl);
+    AttnArgs a = {};
+    a.q = qkv; a.k = qkv + qd; a.v = qkv + qd + kd; a.kcache = l.k; a.vcache = l.v; a.pos = l.length; a.pos_dev = nullptr;
+    a.window = window < 0 ? 0 : window; a.lo = 0; a.Lmax = b.max_length; a.cos = b.cos; a.sin = b.sin; a.rope = rope ? 1 : 0;
+    a.H = b.heads; a.Hkv = b.n_kv; a.hd = b.head_dim;
+    attn_consts(a, b.fa, inv_sqrt);
+    ok = ok && attn_scratch(a, g_stream);
+    a.out = att; a.flags = g_flags;
+    ok = ok && launch_attn_decode(a, g_stream) == cudaSuccess;
+    ok = ok && linear_dev(wo, att, 1, fw, od, false, g_stream);
+    if (!ok) { cudaGetLastError(); cudaStreamSynchronize(g_stream); l.poisoned = true; return 1; }
+    const int f = read_flags_clear();                       // synchronises
+    if (f < 0) { l.poisoned = true; return 1; }
+    if (f != 0) { l.poisoned = true; return 3; }            // a value left an exact envelope: the append is not committed
+    if (!d2h(out, od, (size_t)d * 8) || !sync()) { l.poisoned = true; return 1; }
+    l.length++;
+    return 0;
+}
+
+extern "C" unsigned long long qk_attention_bank_workspace_bytes(long long h) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!valid_bank(h)) return ~0ULL;
+    const Bank &b = g_banks[(size_t)h];
+    unsigned long long total = 2ULL * (unsigned long long)b.max_length * (unsigned long long)(b.head_dim / 2) * 8ULL;
+    for (const auto &l : b.layers)
+        if (l.k) total += 2ULL * (unsigned long long)b.n_kv * (unsigned long long)b.max_length * (unsigned long long)b.head_dim * 4ULL;
+    return total;
 }
 
 extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t *kcache_dev, int32_t *vcache_dev,

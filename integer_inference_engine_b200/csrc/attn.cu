@@ -796,9 +796,15 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const int64_t *x, long lon
 
 }  // namespace
 
+bool attn_shape_ok(int H, int Hkv, int hd) {
+    const int rep = Hkv > 0 ? H / Hkv : 0;
+    return !(H <= 0 || Hkv <= 0 || H % Hkv || rep > AT_MAXREP || hd < 32 || hd > 256 || hd % 32 || 256 % hd ||
+             rep > (256 / hd) * (AT_MAXREP / 2));
+}
+
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
     const int rep = a.Hkv > 0 ? a.H / a.Hkv : 0;
-    if (a.H <= 0 || a.Hkv <= 0 || a.H % a.Hkv || rep > AT_MAXREP || (a.hd > 0 && a.hd <= 256 && rep > (256 / a.hd) * (AT_MAXREP / 2)) || a.hd < 32 || a.hd > 256 || a.hd % 32 || 256 % a.hd ||
+    if (!attn_shape_ok(a.H, a.Hkv, a.hd) ||
         a.pos < 0 || a.pos >= a.Lmax || a.fa < 1 || a.fa > 29 || (a.rope && (!a.cos || !a.sin)))
         return cudaErrorInvalidValue;
     // a.pos is the position itself, or with pos_dev an upper bound of it: the grids cover the largest key span

@@ -99,6 +99,11 @@ def load_library():
         "qk_moe_workspace_release": ([], None), "qk_profile_reset": ([], None),
         "qk_profile_set_enabled": ([c_int], None),
         "qk_profile_snapshot": ([ctypes.POINTER(ctypes.c_uint64), c_int], c_int),
+        "qk_attention_bank_create": ([c_int, i64, i64, c_int, c_int, c_int, c_int, vp, vp], i64),
+        "qk_attention_bank_reset": ([i64], c_int), "qk_attention_bank_destroy": ([i64], None),
+        "qk_attention_bank_import": ([i64, c_int, vp, vp, i64], c_int),
+        "qk_attention_bank_apply": ([i64, c_int, i64, i64, i64, i64, vp, c_int, c_int, c_int, i64, i64, vp], c_int),
+        "qk_attention_bank_workspace_bytes": ([i64], u64),
         "iie_register_weight_dev": ([vp, i64, i64, c_int], i64), "iie_weight_export": ([i64, vp], c_int),
         "iie_moe_layer_create": ([i64, P64, P64, P64, c_int, c_int, i64, i64], i64),
         "iie_moe_layer_destroy": ([i64], None),
@@ -498,6 +503,110 @@ def profile_snapshot() -> dict:
     if n != len(_PROFILE_METRICS):
         raise CudaContextError("profile snapshot size mismatch")
     return {name: int(buf[i]) for i, name in enumerate(_PROFILE_METRICS)}
+
+
+def resident_attention_available() -> bool:
+    """True when the request-scoped attention bank can be used (qk_cuda.py:471-473 of the reference bridge)."""
+    return available()
+
+
+class ResidentAttentionCache:
+    """Request-scoped device K/V bank and exact single-token attention sublayer; names, arguments and error behaviour of
+    north-mini-code/src/nmc/qk_cuda.py:476-569.  A prefill's K/V is imported once per layer; every ``apply`` then takes
+    one normalised hidden row and returns the projected attention row, appending the new K/V row on the device.  A failed
+    call poisons that layer and raises; the caller closes the context instead of retrying."""
+
+    def __init__(self, n_layers: int, max_length: int, d_model: int, n_heads: int, n_kv: int, head_dim: int, fa: int, cos, sin):
+        lib = _lib()
+        n_layers, max_length, d_model, n_heads, n_kv, head_dim, fa = (int(v) for v in (n_layers, max_length, d_model, n_heads,
+                                                                                        n_kv, head_dim, fa))
+        q_width = n_heads * head_dim
+        if n_layers <= 0 or max_length <= 0 or d_model <= 0 or n_heads <= 0 or n_kv <= 0 or n_heads % n_kv or head_dim <= 0 or \
+                head_dim % 2 or not 1 <= fa <= 29 or d_model % 256 or q_width % 256:
+            raise ValueError("invalid resident attention dimensions")
+        c = np.ascontiguousarray(np.asarray(cos, dtype=np.int64))
+        s = np.ascontiguousarray(np.asarray(sin, dtype=np.int64))
+        expected = (max_length, head_dim // 2)
+        if c.shape != expected or s.shape != expected:
+            raise ValueError(f"resident attention RoPE tables must both have shape {expected}")
+        with _CUDA_LOCK:
+            handle = int(lib.qk_attention_bank_create(n_layers, max_length, d_model, n_heads, n_kv, head_dim, fa,
+                                                      c.ctypes.data, s.ctypes.data))
+        if handle < 0:
+            raise CudaContextError("resident attention context creation failed; check dimensions and VRAM")
+        self.handle = handle
+        self.n_layers, self.max_length = n_layers, max_length
+        self.n_heads, self.n_kv, self.head_dim, self.fa = n_heads, n_kv, head_dim, fa
+        self.d_model, self.q_width = d_model, q_width
+        self._lengths = [0] * n_layers
+        self._closed = False
+
+    def length(self, layer=0):
+        return self._lengths[layer]
+
+    def import_layer(self, layer: int, k, v) -> None:
+        if self._closed:
+            raise CudaContextError("resident attention context is closed")
+        layer = int(layer)
+        kk = np.ascontiguousarray(np.asarray(k, dtype=np.int64))
+        vv = np.ascontiguousarray(np.asarray(v, dtype=np.int64))
+        if kk.shape != vv.shape or kk.ndim != 3 or kk.shape[0] != self.n_kv or kk.shape[2] != self.head_dim:
+            raise ValueError("resident attention import expects matching [n_kv, length, head_dim] K/V")
+        length = int(kk.shape[1])
+        if not 0 <= layer < self.n_layers or length > self.max_length:
+            raise ValueError("resident attention import exceeds layer or context bounds")
+        with _CUDA_LOCK:
+            rc = _lib().qk_attention_bank_import(self.handle, layer, kk.ctypes.data, vv.ctypes.data, length)
+        if rc != 0:
+            raise CudaContextError(f"resident attention K/V import failed for layer {layer}")
+        self._lengths[layer] = length
+
+    def apply(self, layer: int, q_handle: int, k_handle: int, v_handle: int, o_handle: int, hidden, fw: int,
+              window: "int | None", rope: bool):
+        if self._closed:
+            raise CudaContextError("resident attention context is closed")
+        layer = int(layer)
+        if not 0 <= layer < self.n_layers or self._lengths[layer] >= self.max_length:
+            raise ValueError("resident attention decode exceeds layer or context bounds")
+        x = np.ascontiguousarray(np.asarray(hidden, dtype=np.int64))
+        if x.shape != (1, self.d_model):
+            raise ValueError(f"resident attention apply expects hidden shape (1, {self.d_model})")
+        out = np.empty((1, self.d_model), dtype=np.int64)
+        inv_sqrt = int(round((1.0 / self.head_dim ** 0.5) * (1 << self.fa)))
+        with _CUDA_LOCK:
+            rc = int(_lib().qk_attention_bank_apply(self.handle, layer, int(q_handle), int(k_handle), int(v_handle), int(o_handle),
+                                                    x.ctypes.data, int(fw), -1 if window is None else int(window),
+                                                    int(bool(rope)), inv_sqrt, out.size, out.ctypes.data))
+        if rc != 0:
+            detail = "exact overflow guard fired" if rc == 3 else f"native status {rc}"
+            raise CudaContextError(f"resident attention apply failed for layer {layer}: {detail}")
+        self._lengths[layer] += 1
+        return out
+
+    def reset(self) -> None:
+        if self._closed:
+            raise CudaContextError("resident attention context is closed")
+        with _CUDA_LOCK:
+            rc = _lib().qk_attention_bank_reset(self.handle)
+        if rc != 0:
+            raise CudaContextError("resident attention reset failed")
+        self._lengths = [0] * self.n_layers
+
+    def workspace_bytes(self) -> int:
+        with _CUDA_LOCK:
+            return int(_lib().qk_attention_bank_workspace_bytes(self.handle))
+
+    def close(self) -> None:
+        if not self._closed:
+            with _CUDA_LOCK:
+                _lib().qk_attention_bank_destroy(self.handle)
+            self._closed = True
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
 
 
 def moe_block(layer_handle: int, x_int, n_used: int, fa: int, fw: int, gain_handle: int = -1, eps: int = 1):
