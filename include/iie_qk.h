@@ -177,6 +177,17 @@ int iie_attn_decode_dev(const int64_t *q_dev, const int64_t *k_dev, const int64_
                         int32_t *vcache_dev, long long pos, const int *pos_dev, long long window, const int64_t *cos_dev,
                         const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim, long long cache_rows,
                         int fa, long long inv_sqrt, int64_t *out_dev, void *stream);
+/* Attention of `tokens` consecutive new tokens at positions start .. start + tokens - 1 (a prefill, or a chunk of one):
+ * q_dev [tokens][n_heads*head_dim], k_dev / v_dev [tokens][n_kv*head_dim] before rotation; all K/V rows are appended
+ * to the int32 caches first, then every token attends to the rows up to its own position (causal; window > 0 keeps the
+ * last `window` rows), with the exact integer softmax of the single-token entry.  out_dev [tokens][n_heads*head_dim].
+ * The computation of north-mini-code/src/nmc/cohere2.py:324-354 (attention_cached with m > 1) and of
+ * bonsai/src/trinote/infer_int/reference_bonsai.py:656-720 (rope 2, no window).  0 ok, 1 bad argument or CUDA failure;
+ * a K/V value outside int32 raises bit 2 of the flag word. */
+int iie_attn_prefill_dev(const int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
+                         int32_t *vcache_dev, long long start, long long tokens, long long window, const int64_t *cos_dev,
+                         const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim, long long cache_rows, int fa,
+                         long long inv_sqrt, int64_t *out_dev, void *stream);
 /* The attention half of a decoder block for ONE token, accumulated into the residual row:
  *   x_dev [d_model] += (attention(q, cache) Wo^T), with [q | k | v] = h Wqkv^T,
  * where h is the normalised row whose digit planes the LAST single-token iie_moe_block_dev / iie_moe_forward_dev

@@ -73,7 +73,7 @@ inline bool stage_on(int st) { return g_stage_mask == 0 || (g_stage_mask & st); 
 
 // Persistent device scratch by role, grown on demand (never shrunk until released).
 enum Role { R_X, R_XL, R_OUT, R_RAW, R_GU, R_GUL, R_TMP0, R_TMP1, R_TMP2, R_TABS, R_META, R_LOGITS, R_IDS, R_GATES,
-            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_ASCORES, R_AEXP, R_ASTAT, R_APART, R_COUNT };
+            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_ASCORES, R_AEXP, R_ASTAT, R_APART, R_PSCORES, R_PEXP, R_PSTAT, R_COUNT };
 struct Buf { void *p = nullptr; size_t cap = 0; };
 Buf g_buf[R_COUNT];
 long long g_ws_allocs = 0;
@@ -992,6 +992,37 @@ extern "C" int iie_attn_decode_dev(const int64_t *q_dev, const int64_t *k_dev, c
     a.out = out_dev; a.flags = g_flags;
     const cudaError_t e = launch_attn_decode(a, (cudaStream_t)stream);
     if (e != cudaSuccess) { cudaGetLastError(); return 1; }
+    return 0;
+}
+
+extern "C" int iie_attn_prefill_dev(const int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
+                                    int32_t *vcache_dev, long long start, long long tokens, long long window,
+                                    const int64_t *cos_dev, const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim,
+                                    long long cache_rows, int fa, long long inv_sqrt, int64_t *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !q_dev || !k_dev || !v_dev || !kcache_dev || !vcache_dev || !out_dev || n_heads <= 0 || n_kv <= 0 || head_dim <= 0 ||
+        cache_rows <= 0 || fa < 1 || fa > 29 || start < 0 || tokens <= 0 || start + tokens > cache_rows) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long Ls = (start + tokens + 63) / 64 * 64;
+    // tokens in slabs so that the per-token score rows stay within a few GB
+    long long slab = (4LL << 30) / ((long long)n_heads * Ls * 12);
+    slab = slab < 1 ? 1 : (slab > tokens ? tokens : (slab > 65535 ? 65535 : slab));
+    // own scratch roles: a captured decode graph keeps the single-token buffers' addresses
+    int64_t *scores = (int64_t *)ensure(R_PSCORES, (size_t)slab * n_heads * Ls * 8);
+    int32_t *e = (int32_t *)ensure(R_PEXP, (size_t)slab * n_heads * Ls * 4);
+    uint8_t *st = (uint8_t *)ensure(R_PSTAT, (size_t)slab * n_heads * 16);
+    if (!scores || !e || !st) return 1;
+    for (long long t0 = 0; t0 < tokens; t0 += slab) {
+        AttnArgs a = {};
+        a.batch = (int)(tokens - t0 < slab ? tokens - t0 : slab);
+        a.q = q_dev + t0 * n_heads * head_dim; a.k = k_dev + t0 * n_kv * head_dim; a.v = v_dev + t0 * n_kv * head_dim;
+        a.kcache = kcache_dev; a.vcache = vcache_dev; a.pos = start + t0; a.window = window; a.Lmax = cache_rows; a.Ls = Ls;
+        a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim;
+        attn_consts(a, fa, inv_sqrt);
+        a.scores = scores; a.e = e; a.hmax = (long long *)st; a.Z = (unsigned long long *)(st + (size_t)slab * n_heads * 8);
+        a.out = out_dev + t0 * n_heads * head_dim; a.flags = g_flags;
+        if (launch_attn_prefill(a, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    }
     return 0;
 }
 

@@ -43,6 +43,17 @@ __device__ __forceinline__ void at_span(const AttnArgs &a, long long &pos, long 
     lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
 }
 
+// prefill: blockIdx.z is the token; shift the position and every per-token pointer to it
+__device__ __forceinline__ void at_batch(AttnArgs &a) {
+    if (a.batch <= 0) return;
+    const long long i = blockIdx.z, Ls = a.Ls ? a.Ls : a.Lmax;
+    a.pos += i;
+    a.lo = (a.window > 0 && a.pos - a.window + 1 > 0) ? a.pos - a.window + 1 : 0;
+    a.q += i * a.H * a.hd;
+    a.scores += i * a.H * Ls; a.e += i * a.H * Ls; a.hmax += i * a.H; a.Z += i * a.H;
+    if (a.out) a.out += i * a.H * a.hd;
+}
+
 // rotation of one (x0, x1) pair with the table row of `pos`
 __device__ __forceinline__ void at_rotate(const AttnArgs &a, long long pos, int i, int64_t &x0, int64_t &x1) {
     if (!a.rope) return;
@@ -94,12 +105,15 @@ __global__ void attn_reset_kernel(long long *hmax, unsigned long long *Z, long l
 __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
     at_span(a_in, a.pos, a.lo);
+    at_batch(a);
+    const long long Ls = a.Ls ? a.Ls : a.Lmax;
     extern __shared__ __align__(16) long long at_q[];     // [rep][hd] int64, then [rep][hd] int32, then the key chunk
     __shared__ long long s_max[AT_MAXREP];
     __shared__ int s_wide;
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31;
     const int half = a.hd / 2;
     const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
+    if (a.batch && l0 > a.pos) return;                     // prefill: a chunk past this token's position
     int32_t *q32 = reinterpret_cast<int32_t *>(at_q + rep * a.hd);
     int32_t *sk = q32 + rep * a.hd;
     if (tid == 0) s_wide = 0;
@@ -117,7 +131,7 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
         wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
     }
     if (wide) s_wide = 1;
-    if (l0 <= a.pos && a.pos < l0 + AT_CH) {              // this CTA owns the new token's cache row
+    if (!a.batch && l0 <= a.pos && a.pos < l0 + AT_CH) {  // this CTA owns the new token's cache row
         bool bad = false;
         for (int i = tid; i < half; i += blockDim.x) {
             const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
@@ -169,7 +183,7 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
             long long sc = INT64_MIN;
             if (key < nk) {
                 sc = (((u ? d1 : d0) >> a.fa) * a.inv_sqrt) >> a.fa;
-                a.scores[(long long)(kv * rep + r) * a.Lmax + l0 + key] = sc;
+                a.scores[(long long)(kv * rep + r) * Ls + l0 + key] = sc;
             }
             long long m = sc;
 #pragma unroll
@@ -185,16 +199,18 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
 __global__ void __launch_bounds__(256) attn_exp_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
     at_span(a_in, a.pos, a.lo);
+    at_batch(a);
+    const long long Ls = a.Ls ? a.Ls : a.Lmax;
     __shared__ unsigned long long s_sum[8];
     const int h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long l = a.lo + (long long)blockIdx.x * 256 + tid;
     unsigned long long e = 0;
     if (l <= a.pos) {
-        const long long m = a.hmax[h], s = a.scores[(long long)h * a.Lmax + l];
+        const long long m = a.hmax[h], s = a.scores[(long long)h * Ls + l];
         long long dlt = m - s;
         dlt = dlt < a.clip ? dlt : a.clip;
         e = (unsigned long long)exp2_neg_fixed((dlt * a.log2e) >> a.fa, a.fa);
-        a.e[(long long)h * a.Lmax + l] = (int32_t)e;
+        a.e[(long long)h * Ls + l] = (int32_t)e;
     }
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) e += __shfl_xor_sync(0xffffffffu, e, s);
@@ -212,6 +228,7 @@ __global__ void __launch_bounds__(256) attn_exp_kernel(const AttnArgs a_in) {
 __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
     at_span(a_in, a.pos, a.lo);
+    const long long Ls = a.Ls ? a.Ls : a.Lmax;
     extern __shared__ __align__(16) int32_t at_v[];        // [AT_CH][hd] values, then [AT_CH][AT_MAXREP] probabilities
     __shared__ int s_last, s_nl;
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x;
@@ -224,7 +241,7 @@ __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
         if (j < nk && r < rep) {
             const int h = kv * rep + r;
             const unsigned long long z = a.Z[h];
-            const unsigned long long e = (unsigned long long)(unsigned)a.e[(long long)h * a.Lmax + l0 + j];
+            const unsigned long long e = (unsigned long long)(unsigned)a.e[(long long)h * Ls + l0 + j];
             p = z ? (int32_t)((e << a.fa) / z) : 0;
         }
         s_p[i] = p;
@@ -290,6 +307,77 @@ __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
     if (tid == 0) { *a.ticket = 0u; if (a.out_nl) *a.out_nl = s_nl; }
 }
 
+// prefill, before the passes: rotate the new keys and append keys and values of all `batch` tokens; grid (batch, Hkv)
+__global__ void __launch_bounds__(128) attn_append_kernel(const AttnArgs a) {
+    const long long i = blockIdx.x, pos = a.pos + i;
+    const int kv = blockIdx.y, tid = threadIdx.x, half = a.hd / 2;
+    const int64_t *ks = a.k + (i * a.Hkv + kv) * a.hd, *vs = a.v + (i * a.Hkv + kv) * a.hd;
+    int32_t *kd = a.kcache + ((long long)kv * a.Lmax + pos) * a.hd, *vd = a.vcache + ((long long)kv * a.Lmax + pos) * a.hd;
+    bool bad = false;
+    for (int j = tid; j < half; j += blockDim.x) {
+        const int i0 = a.rope == 2 ? j : 2 * j, i1 = a.rope == 2 ? j + half : 2 * j + 1;
+        int64_t x0 = ks[i0], x1 = ks[i1];
+        at_rotate(a, pos, j, x0, x1);
+        bad |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+        kd[i0] = (int32_t)x0; kd[i1] = (int32_t)x1;
+    }
+    for (int j = tid; j < a.hd; j += blockDim.x) {
+        const int64_t v = vs[j];
+        bad |= v != (int32_t)v;
+        vd[j] = (int32_t)v;
+    }
+    if (bad) atomicOr(a.flags, 4);
+    const int rep = a.H / a.Hkv;                           // statistics of this token's query heads on this KV head
+    for (int r = tid; r < rep; r += blockDim.x) { a.hmax[i * a.H + kv * rep + r] = INT64_MIN; a.Z[i * a.H + kv * rep + r] = 0ULL; }
+}
+
+// prefill pass 3: one CTA per (token, KV head) walks the token's key chunks, keeps the probability-value sums in
+// registers and writes the shifted result; grid (1, Hkv, batch)
+__global__ void __launch_bounds__(256) attn_pv_rows_kernel(const AttnArgs a_in) {
+    AttnArgs a = a_in;
+    at_batch(a);
+    const long long Ls = a.Ls ? a.Ls : a.Lmax;
+    extern __shared__ __align__(16) int32_t at_v[];        // [AT_CH][hd] values, then [AT_CH][AT_MAXREP] probabilities
+    const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x;
+    int32_t *s_p = at_v + AT_CH * a.hd;
+    const int G = blockDim.x / a.hd, grp = tid / a.hd, d = tid - grp * a.hd;
+    for (int rbase = 0; rbase < rep; rbase += G * 4) {                     // one pass per G*4 query heads
+        const int r0 = rbase + grp * 4;
+        long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+        for (long long l0 = a.lo; l0 <= a.pos; l0 += AT_CH) {
+            const int nk = (int)min((long long)AT_CH, a.pos + 1 - l0);
+            __syncthreads();                                                // the previous chunk has been consumed
+            for (int i = tid; i < AT_MAXREP * AT_CH; i += blockDim.x) {
+                const int j = i / AT_MAXREP, r = i - j * AT_MAXREP;
+                int32_t p = 0;
+                if (j < nk && r < rep) {
+                    const int h = kv * rep + r;
+                    const unsigned long long z = a.Z[h];
+                    const unsigned long long e = (unsigned long long)(unsigned)a.e[(long long)h * Ls + l0 + j];
+                    p = z ? (int32_t)((e << a.fa) / z) : 0;
+                }
+                s_p[i] = p;
+            }
+            at_stage(reinterpret_cast<const int4 *>(a.vcache + ((long long)kv * a.Lmax + l0) * a.hd), nk * (a.hd / 4), tid, blockDim.x,
+                     at_v, [](int i) { return i * 4; });
+            __syncthreads();
+            if (grp < G && r0 < rep) {
+                for (int j = 0; j < nk; j++) {
+                    const int32_t v = at_v[j * a.hd + d];
+                    const int4 p4 = *reinterpret_cast<const int4 *>(s_p + j * AT_MAXREP + r0);
+                    c0 += (long long)p4.x * v; c1 += (long long)p4.y * v; c2 += (long long)p4.z * v; c3 += (long long)p4.w * v;
+                }
+            }
+        }
+        if (grp < G) {
+            const long long cs[4] = {c0, c1, c2, c3};
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (r0 + u < rep) a.out[(long long)(kv * rep + r0 + u) * a.hd + d] = cs[u] >> a.fa;
+        }
+    }
+}
+
 // The three passes in ONE cooperative launch (all CTAs co-resident, two grid-wide barriers): scores and
 // exponentials stay in registers, the value chunk is requested into shared memory together with the key chunk so
 // its latency is hidden behind the first two passes, and nothing but the statistics goes through global memory.
@@ -327,7 +415,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const AttnArgs a_in) {
         wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
     }
     if (wide) s_wide = 1;
-    if (l0 <= a.pos && a.pos < l0 + AT_CH) {              // this CTA owns the new token's cache row
+    if (!a.batch && l0 <= a.pos && a.pos < l0 + AT_CH) {  // this CTA owns the new token's cache row
         bool bad = false;
         for (int i = tid; i < half; i += blockDim.x) {
             const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
@@ -878,6 +966,30 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
     attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H), 256, 0, s>>>(a);
     attn_pv_kernel<<<dim3(chunks, a.Hkv), 256, (size_t)AT_CH * a.hd * 4 + (size_t)AT_CH * AT_MAXREP * 4, s>>>(a);
     note_launch(3);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s) {
+    if (!attn_shape_ok(a.H, a.Hkv, a.hd) || a.batch <= 0 || a.batch > 65535 || a.pos < 0 || a.pos + a.batch > a.Lmax || a.fa < 1 ||
+        a.fa > 29 || (a.rope && (!a.cos || !a.sin)) || a.pos_dev || !a.out || !a.scores || !a.e || !a.hmax || !a.Z)
+        return cudaErrorInvalidValue;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_pv_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess)
+            return cudaGetLastError();
+        configured = true;
+    }
+    const int rep = a.H / a.Hkv;
+    const long long last = a.pos + a.batch - 1;                     // the longest key span is the last token's
+    long long n_keys = last + 1;
+    if (a.window > 0 && n_keys > a.window) n_keys = a.window;
+    const unsigned chunks = (unsigned)((n_keys + AT_CH - 1) / AT_CH);
+    attn_append_kernel<<<dim3((unsigned)a.batch, a.Hkv), 128, 0, s>>>(a);
+    attn_scores_kernel<<<dim3(chunks, a.Hkv, (unsigned)a.batch), 256, (size_t)rep * a.hd * 12 + (size_t)AT_CH * (a.hd + 4) * 4, s>>>(a);
+    attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H, (unsigned)a.batch), 256, 0, s>>>(a);
+    attn_pv_rows_kernel<<<dim3(1, a.Hkv, (unsigned)a.batch), 256, (size_t)AT_CH * a.hd * 4 + (size_t)AT_CH * AT_MAXREP * 4, s>>>(a);
+    note_launch(4);
     return cudaGetLastError();
 }
 

@@ -247,8 +247,14 @@ struct AttnArgs {
     int *out_nl_next;              // nullable: zeroed by the cluster form (the cell the next call accumulates into)
     int pdl;                       // 1: the one-launch form is launched with programmatic stream serialization
     int *flags;                    // bit 0 digit envelope, bit 2 a key / value does not fit the int32 cache
+    int batch;                     // > 0: that many consecutive new tokens (prefill); q, k, v, out then hold one row per token,
+                                   // pos is the position of the first, the scratch holds one set of statistics per token
+    long long Ls;                  // row stride of scores / e (0: Lmax)
 };
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s);
+// `batch` new tokens at positions pos .. pos + batch - 1 against the cache rows before them and each other (causal):
+// all K/V rows are appended first, then scores, exponentials and the probability-value sums run per token
+cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s);
 extern int g_attn_fused;           // 2: cluster per KV head, 1: one cooperative launch, 0: three launches (each falls back to the next)
 // hmax = INT64_MIN, Z = acc = ticket = 0: once after the statistics buffer is (re)allocated; every call leaves them so
 cudaError_t launch_attn_reset(long long *hmax, unsigned long long *Z, long long *acc, unsigned *ticket, int H, int hd, cudaStream_t s);

@@ -140,3 +140,54 @@ def test_every_launch_form_gives_the_same_bytes(form):
             assert np.array_equal(got.reshape(1, -1), want)
     finally:
         lib.iie_set_attn_fused(1)
+
+
+@pytest.mark.parametrize(("H", "Hkv", "hd", "start", "m", "window", "rope"),
+                         [(4, 2, 64, 0, 12, None, 0), (4, 2, 64, 15, 5, 7, 1), (8, 1, 128, 3, 70, None, 2), (8, 2, 32, 60, 9, 64, 1),
+                          (16, 1, 64, 0, 130, 50, 2)])
+def test_prefill_attention_matches_the_checker(H, Hkv, hd, start, m, window, rope):
+    """m new tokens at once (causal, optional window, both rotations) against the CPU checker's cached attention."""
+    import torch
+
+    from integer_inference_engine_b200 import device
+    rng = np.random.default_rng(900 + H + m)
+    rows = start + m + 3
+    cos, sin = o.build_rope_tables(rows, hd, 50000.0, FA)
+    ck = rng.integers(-(1 << 18), 1 << 18, size=(Hkv, rows, hd), dtype=np.int64)
+    cv = rng.integers(-(1 << 18), 1 << 18, size=(Hkv, rows, hd), dtype=np.int64)
+    q = rng.integers(-(1 << 19), 1 << 19, size=(m, H, hd), dtype=np.int64)
+    k = rng.integers(-(1 << 18), 1 << 18, size=(m, Hkv, hd), dtype=np.int64)
+    v = rng.integers(-(1 << 18), 1 << 18, size=(m, Hkv, hd), dtype=np.int64)
+    qr, kr = q, k
+    if rope:
+        rot = lambda t: o.rope_fixed(np.transpose(t, (1, 0, 2)), cos[start:start + m], sin[start:start + m], FA,
+                                     neox=(rope == 2)).transpose(1, 0, 2)
+        qr, kr = rot(q), rot(k)
+    want_k, want_v = ck.copy(), cv.copy()
+    want_k[:, start:start + m] = np.transpose(kr, (1, 0, 2))
+    want_v[:, start:start + m] = np.transpose(v, (1, 0, 2))
+    want = o.attention_cached(qr, want_k[:, :start + m], want_v[:, :start + m], start, H, Hkv, FA, window)
+    cuda = lambda a, dt=torch.int64: torch.from_numpy(np.ascontiguousarray(a)).to(dt).cuda()
+    kc, vc = cuda(ck, torch.int32), cuda(cv, torch.int32)
+    device.read_flags()
+    got = device.attention_prefill(cuda(q.reshape(m, -1)), cuda(k.reshape(m, -1)), cuda(v.reshape(m, -1)), kc, vc, start, H, Hkv, hd,
+                                   FA, window or 0, cuda(cos), cuda(sin), rope)
+    torch.cuda.synchronize()
+    assert device.read_flags() == 0
+    assert np.array_equal(got.cpu().numpy(), want)
+    assert np.array_equal(kc.cpu().numpy(), want_k) and np.array_equal(vc.cpu().numpy(), want_v)
+    # a decode step after the prefill continues from the same cache
+    q1 = rng.integers(-(1 << 19), 1 << 19, size=(1, H, hd), dtype=np.int64)
+    k1 = rng.integers(-(1 << 18), 1 << 18, size=(1, Hkv, hd), dtype=np.int64)
+    v1 = rng.integers(-(1 << 18), 1 << 18, size=(1, Hkv, hd), dtype=np.int64)
+    pos = start + m
+    got1 = device.attention_decode(cuda(q1.reshape(-1)), cuda(k1.reshape(-1)), cuda(v1.reshape(-1)), kc, vc, pos, H, Hkv, hd, FA,
+                                   window or 0, cuda(cos), cuda(sin), rope)
+    q1r, k1r = q1, k1
+    if rope:
+        rot1 = lambda t: o.rope_fixed(np.transpose(t, (1, 0, 2)), cos[pos:pos + 1], sin[pos:pos + 1], FA,
+                                      neox=(rope == 2)).transpose(1, 0, 2)
+        q1r, k1r = rot1(q1), rot1(k1)
+    want_k[:, pos] = k1r[0]; want_v[:, pos] = v1[0]
+    want1 = o.attention_cached(q1r, want_k[:, :pos + 1], want_v[:, :pos + 1], pos, H, Hkv, FA, window)
+    assert np.array_equal(got1.cpu().numpy().reshape(1, -1), want1)
