@@ -598,6 +598,24 @@ def run_prefill(args):
         stack.decode_step(x, FW)
     ms, clocks = _timed(step, args.steps, args.warmup, world, local)
     assert device.read_flags() == 0
+    # the attention sublayer of the same prefill (scores, exact softmax, probability-value sums of T tokens): checked on a
+    # small case against the oracle, then timed alone at the model's shape
+    rng = np.random.default_rng(3)
+    sq, sk, sv = (rng.integers(-(1 << 18), 1 << 18, size=(9, w), dtype=np.int64) for w in (4 * 64, 2 * 64, 2 * 64))
+    skc = torch.zeros((2, 12, 64), dtype=torch.int32, device="cuda"); svc = torch.zeros_like(skc)
+    got = device.attention_prefill(torch.from_numpy(sq).cuda(), torch.from_numpy(sk).cuda(), torch.from_numpy(sv).cuda(), skc, svc,
+                                   0, 4, 2, 64, FA, 5)
+    want = o.attention_cached(sq.reshape(9, 4, 64), sk.reshape(9, 2, 64).transpose(1, 0, 2), sv.reshape(9, 2, 64).transpose(1, 0, 2),
+                              0, 4, 2, FA, 5)
+    assert np.array_equal(got.cpu().numpy(), want), "prefill attention differs from the oracle"
+    g = torch.Generator(device="cuda").manual_seed(5)
+    rnd = lambda *sh: torch.randint(-(1 << 18), 1 << 18, sh, generator=g, device="cuda", dtype=torch.int64)
+    aq, ak, av = rnd(T, N_HEADS * HEAD_DIM), rnd(T, N_KV * HEAD_DIM), rnd(T, N_KV * HEAD_DIM)
+    akc = torch.zeros((N_KV, T, HEAD_DIM), dtype=torch.int32, device="cuda"); avc = torch.zeros_like(akc)
+    aout = torch.empty((T, N_HEADS * HEAD_DIM), dtype=torch.int64, device="cuda")
+    att_ms, _ = _timed(lambda i: device.attention_prefill(aq, ak, av, akc, avc, 0, N_HEADS, N_KV, HEAD_DIM, FA, WINDOW, out=aout),
+                       3, 1, world, local)
+    assert device.read_flags() == 0
     if rank == 0:
         ms_step = ms / args.steps
         print(json.dumps({
@@ -605,7 +623,8 @@ def run_prefill(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int64 via int8 digit planes (tcgen05 kind::i8)", "data": "synthetic",
             "config": {"workload": f"config3_moe_prefill: {T} tokens x {args.layers} MoE blocks, grouped expert GEMMs",
-                       "ms_per_block": ms_step / args.layers, "parallelism": f"replicas x{world}",
+                       "ms_per_block": ms_step / args.layers, "attention_prefill_ms_per_block": att_ms / 3,
+                       "parallelism": f"replicas x{world}",
                        "l2": "inputs larger than L2 (1.2 GB of expert weights per block)", "oracle_checked_rows": len(rows)},
             "clocks": clocks, "gpu_launches": int(launches * args.steps)}))
     if world > 1:

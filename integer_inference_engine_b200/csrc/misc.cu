@@ -260,13 +260,15 @@ __device__ u128 isqrt_fast(u128 v) {
 
 // one element of the normalised row: floor((x << fa) / rms), then (y * gain) >> fa; `bad` is set (and 0 returned)
 // where the oracle's envelope checks would refuse the value
-__device__ __forceinline__ int64_t norm_value(int64_t xv, unsigned long long rms, unsigned long long gm, int64_t g, bool has_gain,
-                                              int fa, bool &bad) {
+__device__ __forceinline__ int64_t norm_value(int64_t xv, unsigned long long rms, unsigned long long inv, unsigned long long gm,
+                                              int64_t g, bool has_gain, int fa, bool &bad) {
     int64_t y;
-    if (uabs64(xv) < (1ULL << (62 - fa)) && rms <= (unsigned long long)INT64_MAX) {     // x << fa fits a signed 64-bit dividend
-        const int64_t num = xv * ((int64_t)1 << fa), den = (int64_t)rms;
-        y = num / den;
-        if (num < 0 && y * den != num) y -= 1;                  // floor toward -inf
+    if (inv != 0 && uabs64(xv) < (1ULL << (62 - fa))) {
+        // |x << fa| < 2^62 and rms < 2^62: quotient from the reciprocal inv = floor((2^64 - 1) / rms), at most 2 low
+        const unsigned long long n = uabs64(xv) << fa;
+        unsigned long long q = __umul64hi(n, inv), r = n - q * rms;
+        while (r >= rms) { q++; r -= rms; }
+        y = xv >= 0 ? (int64_t)q : -(int64_t)q - (r != 0);      // floor toward -inf
     } else {
         const i128 num = (i128)xv << fa;
         i128 q = num / (i128)rms;
@@ -285,21 +287,35 @@ __device__ __forceinline__ int64_t norm_value(int64_t xv, unsigned long long rms
 // rows from `rows_a` on use gain_b (per-head norms of queries and keys in one launch)
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const int64_t *x, long long rows, long long width, const int64_t *gain_a,
                                                        int fa, unsigned long long eps, int64_t *out, int *flags,
-                                                       int8_t *planes, int64_t *totals, const int64_t *gain_b, long long rows_a) {
+                                                       int8_t *planes, int64_t *totals, const int64_t *gain_b, long long rows_a,
+                                                       int split) {
+    // `split` CTAs share a row: each sums the squares of the whole row (cheap, the row sits in L2) and normalises its own
+    // slice, so that the divisions of a long row are spread over several SMs
     __shared__ unsigned long long s_lo[32], s_hi[32], s_max[32], s_gmax[32];
-    __shared__ unsigned long long s_rms, s_gm;
+    __shared__ unsigned long long s_rms, s_gm, s_inv;
     __shared__ int s_bad;
-    const long long row = blockIdx.x;
+    const long long row = blockIdx.x / split;
+    const int part = blockIdx.x - (int)row * split;
     const int64_t *gain = row < rows_a ? gain_a : gain_b;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int64_t *xr = x + row * width;
     int64_t *yr = out + row * width;
     u128 ssq = 0; unsigned long long mx = 0, gmx = 0;
-    for (long long i = tid; i < width; i += blockDim.x) {
-        const unsigned long long a = uabs64(xr[i]);
-        ssq += (u128)a * a;
-        mx = a > mx ? a : mx;
-        if (gain) { const unsigned long long ga = uabs64(gain[i]); gmx = ga > gmx ? ga : gmx; }
+    for (long long i0 = tid; i0 < width; i0 += (long long)blockDim.x * 8) {      // eight loads in flight per thread
+        int64_t xv[8], gv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const long long i = i0 + (long long)u * blockDim.x;
+            xv[u] = i < width ? xr[i] : 0;
+            gv[u] = (gain && i < width) ? gain[i] : 0;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const unsigned long long a = uabs64(xv[u]), ga = uabs64(gv[u]);
+            ssq += (u128)a * a;
+            mx = a > mx ? a : mx;
+            gmx = ga > gmx ? ga : gmx;
+        }
     }
     auto fold = [&]() {
 #pragma unroll
@@ -325,23 +341,25 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const int64_t *x, long lo
             const u128 rms = isqrt_fast(mean);
             if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) bad = 1;
             s_rms = (unsigned long long)rms; s_gm = gmx; s_bad = bad;
+            s_inv = (rms != 0 && rms < ((u128)1 << 62)) ? 0xFFFFFFFFFFFFFFFFULL / (unsigned long long)rms : 0ULL;
         }
     }
     __syncthreads();
-    if (s_bad) { if (tid == 0) atomicOr(flags, 2); return; }
-    const unsigned long long rms = s_rms;
+    if (s_bad) { if (tid == 0 && part == 0) atomicOr(flags, 2); return; }
+    const unsigned long long rms = s_rms, inv = s_inv;
     const unsigned long long gm = s_gm;
     bool bad = false;
     if (planes) {
         // digit planes [row][8][width] and 128-element block sums of the normalised row, for the Q1_0 product
-        const long long nb = width >> 7;
-        for (long long b = warp; b < nb; b += nwarps) {
+        const long long nb = width >> 7, per = (nb + split - 1) / split;
+        const long long b_end = min(nb, (part + 1) * per);
+        for (long long b = part * per + warp; b < b_end; b += nwarps) {
             const long long i0 = b * 128 + lane * 4;
             uint32_t pl[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             unsigned long long sum = 0;
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const int64_t y = norm_value(xr[i0 + j], rms, gm, gain ? gain[i0 + j] : 0, gain != nullptr, fa, bad);
+                const int64_t y = norm_value(xr[i0 + j], rms, inv, gm, gain ? gain[i0 + j] : 0, gain != nullptr, fa, bad);
                 if (out) yr[i0 + j] = y;
                 bool ok;
                 const uint64_t d = balanced_digits8(y, ok);
@@ -356,8 +374,9 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const int64_t *x, long lo
             if (lane == 0) totals[row * nb + b] = (int64_t)sum;
         }
     } else {
-        for (long long i = tid; i < width; i += blockDim.x)
-            yr[i] = norm_value(xr[i], rms, gm, gain ? gain[i] : 0, gain != nullptr, fa, bad);
+        const long long per = (width + split - 1) / split, i_end = min(width, (part + 1) * per);
+        for (long long i = part * per + tid; i < i_end; i += blockDim.x)
+            yr[i] = norm_value(xr[i], rms, inv, gm, gain ? gain[i] : 0, gain != nullptr, fa, bad);
     }
     if (bad) atomicOr(flags, 2);
 }
@@ -433,8 +452,10 @@ cudaError_t launch_topk(const int64_t *logits, long long rows, int n_experts, in
 
 cudaError_t launch_rmsnorm(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
                            unsigned long long eps, int64_t *out, int *flags, cudaStream_t s) {
-    const int threads = width >= 2048 ? 1024 : width > 128 ? 256 : 128;
-    rmsnorm_kernel<<<(unsigned)rows, threads, 0, s>>>(x, rows, width, gain, fa, eps, out, flags, nullptr, nullptr, nullptr, rows);
+    const int split = (rows <= 16 && width >= 1024) ? (int)((width + 511) / 512) : 1;      // few long rows: 512 values per CTA
+    const int threads = split > 1 ? 128 : (width >= 2048 ? 1024 : width > 128 ? 256 : 128);
+    rmsnorm_kernel<<<(unsigned)(rows * split), threads, 0, s>>>(x, rows, width, gain, fa, eps, out, flags, nullptr, nullptr, nullptr, rows,
+                                                                 split);
     note_launch();
     return cudaGetLastError();
 }
@@ -443,7 +464,7 @@ cudaError_t launch_rmsnorm_pair(const int64_t *x, long long rows_a, long long ro
                                 const int64_t *gain_b, int fa, unsigned long long eps, int64_t *out, int *flags, cudaStream_t s) {
     const int threads = width >= 2048 ? 1024 : width > 128 ? 256 : 128;
     rmsnorm_kernel<<<(unsigned)(rows_a + rows_b), threads, 0, s>>>(x, rows_a + rows_b, width, gain_a, fa, eps, out, flags, nullptr, nullptr,
-                                                                  gain_b, rows_a);
+                                                                  gain_b, rows_a, 1);
     note_launch();
     return cudaGetLastError();
 }
@@ -451,8 +472,12 @@ cudaError_t launch_rmsnorm_pair(const int64_t *x, long long rows_a, long long ro
 cudaError_t launch_rmsnorm_planes(const int64_t *x, long long rows, long long width, const int64_t *gain, int fa,
                                   unsigned long long eps, int64_t *out, int8_t *planes, int64_t *totals, int *flags, cudaStream_t s) {
     if (width <= 0 || (width & 127) || !planes || !totals) return cudaErrorInvalidValue;
-    const int threads = width >= 4096 ? 1024 : width >= 1024 ? (int)(width >> 2) : 256;      // one warp per 128-element block
-    rmsnorm_kernel<<<(unsigned)rows, threads, 0, s>>>(x, rows, width, gain, fa, eps, out, flags, planes, totals, nullptr, rows);
+    // one warp per 128-element block; few rows of a long row: four blocks per CTA, several CTAs per row
+    const long long nb = width >> 7;
+    const int split = (rows <= 16 && nb >= 8) ? (int)((nb + 3) / 4) : 1;
+    const int threads = split > 1 ? 128 : (width >= 4096 ? 1024 : width >= 1024 ? (int)(width >> 2) : 256);
+    rmsnorm_kernel<<<(unsigned)(rows * split), threads, 0, s>>>(x, rows, width, gain, fa, eps, out, flags, planes, totals, nullptr, rows,
+                                                                 split);
     note_launch();
     return cudaGetLastError();
 }

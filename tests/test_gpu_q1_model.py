@@ -110,15 +110,15 @@ def test_decode_steps_match_the_checker_eager_and_replayed():
         token, pos = want, pos + 1
 
 
-@pytest.mark.parametrize("T", [1, 3])
-def test_fused_product_forms(T):
+@pytest.mark.parametrize(("T", "nb"), [(1, 4), (3, 4), (1, 9), (2, 32)])
+def test_fused_product_forms(T, nb):
     """Norm, SwiGLU and residual steps folded into the product's launches against their separate restatements."""
     import torch
 
     from integer_inference_engine_b200 import device, q1_gpu
     from oracle import native as onat
-    rng = np.random.default_rng(40 + T)
-    nb, out_f = 4, 200
+    rng = np.random.default_rng(40 + T + nb)
+    out_f = 200
     K = nb * 128
     bits, scale = o.synth_q1(rng, out_f, nb)
     h = q1_gpu.q1_register_weight(bits, scale.astype(np.int32))
@@ -166,3 +166,21 @@ def test_head_norms_in_one_launch():
     q1_gpu.head_norm_dev(torch.from_numpy(x).cuda(), H, Hkv, hd, torch.from_numpy(ga).cuda(), torch.from_numpy(gb).cuda(), FRAC, out)
     want = np.concatenate([o.rmsnorm_fixed(x[:H], FRAC, 1, ga), o.rmsnorm_fixed(x[H:], FRAC, 1, gb)])
     assert np.array_equal(out.cpu().numpy(), want) and device.read_flags() == 0
+
+
+@pytest.mark.parametrize(("rows", "width"), [(1, 4096), (3, 1536), (1, 1000), (20, 2048)])
+def test_rmsnorm_long_rows(rows, width):
+    """Long rows are normalised by several CTAs each; values beyond the narrow-division range take the wide path."""
+    import torch
+
+    from integer_inference_engine_b200 import device, qk_cuda
+    rng = np.random.default_rng(60 + rows + width)
+    x = o.to_fixed(rng.standard_normal((rows, width)) * 4, FRAC)
+    x[0, 1] = 1 << 50; x[-1, width - 1] = -(1 << 49) - 12345
+    gain = np.rint((np.abs(rng.standard_normal(width)) + 0.5) * (1 << FRAC)).astype(np.int64)
+    gh = qk_cuda.register_i64(gain)
+    device.read_flags()
+    for g, h in ((gain, gh), (None, -1)):
+        got = device.rmsnorm(torch.from_numpy(x).cuda(), h, FRAC, 1).cpu().numpy()
+        assert np.array_equal(got, o.rmsnorm_fixed(x, FRAC, 1, g))
+    assert device.read_flags() == 0
