@@ -58,6 +58,7 @@ def parse():
     ap.add_argument("--cpu-sample-layers", type=int, default=2)
     ap.add_argument("--context", type=int, default=4096, help="KV-cache rows already filled when decoding starts")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--overlap", type=int, default=0, help="1: the attention half of a block runs beside its expert kernels")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep_decode", "q1", "q1_token"],
                     help="decode = the headline line (batch-1 MoE decode); the others print a line of the same "
                          "shape for the prefill, expert-parallel and Q1_0 configurations")
@@ -362,7 +363,9 @@ def run_ours(args):
         eager_ids.append(int(model.token.item()))
     model.token.fill_(first_token); model.pos.fill_(pos0)
     l0 = device.launch_count()
+    device.set_block_overlap(bool(args.overlap))                  # the eager chain above ran the halves in sequence
     model.capture(pos_bound)
+    device.set_block_overlap(False)                               # the captured graph keeps its two branches
     launches_per_step = (device.launch_count() - l0) // 2         # capture() runs the step twice
     replay_ids = []
     for i in range(3):
@@ -483,7 +486,7 @@ def run_ours(args):
         "metric": "decode_tok_per_s", "value": world * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers": args.layers, "context": args.context, "parallelism": f"replicas x{world}",
+        "config": {"workload": WORKLOAD, "layers": args.layers, "block_halves": "side by side" if args.overlap else "in sequence", "context": args.context, "parallelism": f"replicas x{world}",
                    "l2": "inputs larger than L2: each step streams %d MB of distinct weights and %d MB of KV cache"
                          % (w_bytes // 2**20, kv_bytes // 2**20),
                    "weight_bytes_per_token": w_bytes, "kv_bytes_per_token": kv_bytes,

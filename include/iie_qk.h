@@ -199,6 +199,14 @@ int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t
                        const int *pos_dev, long long window, const int64_t *cos_dev, const int64_t *sin_dev, int rope,
                        int n_heads, int n_kv, int head_dim, long long cache_rows, int fa, int fw, long long inv_sqrt,
                        void *stream);
+/* Overlap of the two halves of a decoder block.  Both halves read the row the block's routing kernel normalised and
+ * add into the same residual row with integer atomics, so they may run side by side: with the switch on,
+ * iie_attn_block_dev runs on a stream of the library after the routing kernel of the last single-token
+ * iie_moe_block_dev call (its `stream` argument is then ignored), and the next iie_moe_block_dev waits for it.
+ * iie_join_block_overlap makes `stream` wait for an attention half still in flight: call it after the last block,
+ * before anything else reads the residual row (and before a stream capture ends).  0 ok, 1 failure. */
+int iie_set_block_overlap(int on);
+int iie_join_block_overlap(void *stream);
 /* 1 (default): batches of 2 .. tc_min_tokens-1 rows stream every touched expert tile once for all of its rows;
  * 0: the older kernel that re-reads a tile for every four rows.  Results are identical; for measurements. */
 void iie_set_batch_stream(int enabled);

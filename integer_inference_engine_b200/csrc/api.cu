@@ -55,6 +55,13 @@ std::vector<Weight> g_w;
 std::vector<MoeLayer> g_layers;
 cudaStream_t g_stream = nullptr;
 int *g_flags = nullptr;               // device flag word
+// Overlap of the two halves of a decoder block (both read the same normalised row and add into the same residual
+// row with integer atomics): the attention half runs on g_side after the routing kernel, the next block's routing
+// kernel waits for it.
+int g_overlap = 0;
+bool g_attn_pending = false;
+cudaStream_t g_side = nullptr;
+cudaEvent_t g_ev_route = nullptr, g_ev_attn = nullptr;
 int *g_cells = nullptr;               // device ints: [0] limbs of h, [1] limbs of gate*up, [2] routing ticket
 const uint8_t **g_selptr = nullptr;   // device: [3][64] pointers of the experts the last routing selected
 int g_pdl = 1;                        // programmatic dependent launch between the decode kernels
@@ -432,7 +439,13 @@ bool moe_decode_token(const MoeLayer &L, const int64_t *x, const int64_t *gain, 
     ra.flags = g_flags;
     const bool ptrs = k <= 64;
     ra.tabs = ptrs ? L.tabs : nullptr; ra.sel_ptrs = ptrs ? g_selptr : nullptr; ra.pdl = g_pdl;
+    if (g_overlap && g_attn_pending) {                    // the previous block's attention half still adds into x
+        if (cudaStreamWaitEvent(s, g_ev_attn, 0) != cudaSuccess) return false;
+        g_attn_pending = false;
+        ra.pdl = 0;
+    }
     if (stage_on(ST_ROUTER) && launch_route(ra, s) != cudaSuccess) return false;
+    if (g_overlap && cudaEventRecord(g_ev_route, s) != cudaSuccess) return false;
     if (g_fused_expert && ptrs && (g_stage_mask == 0 || (g_stage_mask & 24) == 24) && small_scales(L.maxd_gate, L.maxdmin_gate, fw) &&
         small_scales(L.maxd_down, L.maxdmin_down, fw)) {
         ExpertArgs ea = {};
@@ -1193,6 +1206,11 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     if (wqkv.out_f != qd + 2 * kd || wo.nb * 256 != qd || wo.out_f != d || g_hl_d != d) return 1;   // g_hl_d: the digit planes on hand
     if (!fast_envelope(wqkv.qtype, wqkv.nb, wqkv.maxd, wqkv.maxdmin, fw) || !fast_envelope(wo.qtype, wo.nb, wo.maxd, wo.maxdmin, fw)) return 3;
     cudaStream_t s = (cudaStream_t)stream;
+    const bool side = g_overlap != 0;
+    if (side) {                                            // after the routing kernel of this block, beside its expert kernels
+        s = g_side;
+        if (cudaStreamWaitEvent(s, g_ev_route, 0) != cudaSuccess) { cudaGetLastError(); return 1; }
+    }
     const int8_t *hl = (const int8_t *)g_buf[R_XL].p;
     int64_t *qkv = (int64_t *)ensure(R_TMP0, (size_t)(qd + 2 * kd) * 8);
     int8_t *al = (int8_t *)ensure(R_TMP1, (size_t)8 * qd);
@@ -1200,7 +1218,7 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     StreamArgs sa = {};
     sa.wa = wqkv.cell; sa.wb = wqkv.cell; sa.n_sel = 1; sa.out_f = wqkv.out_f; sa.n_blocks = wqkv.nb; sa.fw = fw; sa.fa = fa;
     sa.xl = hl; sa.x_per_sel = 0; sa.x_nl = g_cells; sa.out = qkv; sa.flags = g_flags;
-    sa.fast = small_scales(wqkv.maxd, wqkv.maxdmin, fw); sa.pdl = g_pdl; sa.early_weights = g_pdl;   // fixed weight pointer: request before the wait
+    sa.fast = small_scales(wqkv.maxd, wqkv.maxdmin, fw); sa.pdl = side ? 0 : g_pdl; sa.early_weights = sa.pdl;   // fixed weight pointer: request before the wait
     if (launch_stream(wqkv.qtype, MODE_LINEAR, sa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     AttnArgs a = {};
     a.q = qkv; a.k = qkv + qd; a.v = qkv + qd + kd; a.kcache = kcache_dev; a.vcache = vcache_dev; a.pos = pos;
@@ -1218,7 +1236,30 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     oa.xl = al; oa.x_per_sel = 1; oa.x_nl = nl_cell; oa.out = x_dev; oa.gates = g_pow2 + fa; oa.flags = g_flags;
     oa.fast = small_scales(wo.maxd, wo.maxdmin, fw); oa.pdl = g_pdl; oa.early_weights = g_pdl;
     if (launch_stream(wo.qtype, MODE_DOWN, oa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    if (side) {
+        if (cudaEventRecord(g_ev_attn, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+        g_attn_pending = true;
+    }
     return 0;
+}
+
+extern "C" int iie_set_block_overlap(int on) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init()) return 1;
+    if (on && !g_side) {
+        if (cudaStreamCreateWithFlags(&g_side, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&g_ev_route, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&g_ev_attn, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); return 1; }
+    }
+    g_overlap = on ? 1 : 0;
+    return 0;
+}
+
+extern "C" int iie_join_block_overlap(void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!g_attn_pending) return 0;
+    g_attn_pending = false;
+    return cudaStreamWaitEvent((cudaStream_t)stream, g_ev_attn, 0) == cudaSuccess ? 0 : 1;
 }
 
 extern "C" int iie_embed_dev(long long h, const int *token_dev, long long token, int frac, int64_t *out_dev, void *stream) {

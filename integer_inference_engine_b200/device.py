@@ -106,6 +106,20 @@ def attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kcache: 
     return out
 
 
+def set_block_overlap(on: bool) -> None:
+    """Run the attention half of a decoder block beside the expert kernels of the same block (see
+    ``iie_set_block_overlap``); :func:`join_block_overlap` must follow the last block of a step."""
+    with _CUDA_LOCK:
+        if qk_cuda._lib().iie_set_block_overlap(1 if on else 0) != 0:
+            raise CudaContextError("block overlap could not be switched")
+
+
+def join_block_overlap() -> None:
+    with _CUDA_LOCK:
+        if qk_cuda._lib().iie_join_block_overlap(_stream_ptr()) != 0:
+            raise CudaContextError("joining the attention stream failed")
+
+
 def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, start: int,
                       n_heads: int, n_kv: int, head_dim: int, fa: int = 16, window: int = 0, cos: torch.Tensor | None = None,
                       sin: torch.Tensor | None = None, rope: int = 0, inv_sqrt: int | None = None,

@@ -97,6 +97,7 @@ class SyntheticDecoder:
             self.moe.layers[li].block(self.x, self.moe.gains[li], fa, fw, 1, out=self.x, want_routes=False)
             device.attention_block(a["wqkv"], a["wo"], self.x, a["k"], a["v"], pos_bound, self.H, self.Hkv, self.hd, fa, fw,
                                    0 if full else self.window, self.cos, self.sin, 0 if full else 1, pos_dev=self.pos)
+        device.join_block_overlap()                         # no-op unless the halves of a block run side by side
         device.rmsnorm(self.x, self.out_gain_h, fa, 1, out=self.hn)
         device.apply(self.embd, self.hn, self.vocab, fw, out=self.logits)
         device.argmax(self.logits.view(-1), out=self.token)

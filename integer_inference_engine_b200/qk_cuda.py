@@ -40,7 +40,7 @@ EXPORTED_SYMBOLS = (
     "qk_profile_snapshot", "qk_attention_bank_create", "qk_attention_bank_reset", "qk_attention_bank_destroy",
     "qk_attention_bank_moe_configure", "qk_attention_bank_moe_bind", "qk_attention_bank_import",
     "qk_attention_bank_apply", "qk_attention_bank_moe_begin", "qk_attention_bank_moe_continue",
-    "qk_attention_bank_moe_export", "qk_attention_bank_workspace_bytes", "iie_attn_prefill_dev",
+    "qk_attention_bank_moe_export", "qk_attention_bank_workspace_bytes", "iie_attn_prefill_dev", "iie_set_block_overlap", "iie_join_block_overlap",
     "iie_register_weight_dev", "iie_weight_export", "iie_moe_layer_create", "iie_moe_layer_destroy",
     "iie_moe_forward_dev", "iie_apply_dev", "iie_flags_read_clear", "iie_rmsnorm_dev", "iie_profile_stage_mask",
     "iie_launch_count", "iie_moe_block_host", "iie_moe_block_dev", "iie_set_pdl",
@@ -115,6 +115,7 @@ def load_library():
         "iie_set_tc_min_tokens": ([i64], None), "iie_set_fused_expert": ([c_int], None), "iie_expert_clusters": ([], c_int), "iie_set_fused_route": ([c_int], None),
         "iie_attn_decode_dev": ([vp, vp, vp, vp, vp, i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, i64, vp, vp], c_int),
         "iie_attn_prefill_dev": ([vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, i64, vp, vp], c_int),
+        "iie_set_block_overlap": ([c_int], c_int), "iie_join_block_overlap": ([vp], c_int),
         "iie_attn_block_dev": ([i64, i64, vp, vp, vp, i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, c_int, i64, vp], c_int),
         "iie_embed_dev": ([i64, vp, i64, c_int, vp, vp], c_int), "iie_set_attn_fused": ([c_int], None), "iie_set_batch_stream": ([c_int], None), "iie_argmax_dev": ([vp, i64, vp, vp], c_int),
         "iie_route_dev": ([i64, c_int, vp, i64, c_int, c_int, vp, vp, vp], c_int),

@@ -33,12 +33,14 @@ def _host_view(model):
     return layers, embd, model.out_gain.cpu().numpy(), cfg
 
 
-def test_decode_steps_match_the_checker_eager_and_replayed():
+@pytest.mark.parametrize("overlap", [False, True], ids=["halves-in-sequence", "halves-side-by-side"])
+def test_decode_steps_match_the_checker_eager_and_replayed(overlap):
     import torch
 
     from integer_inference_engine_b200 import device, qk_cuda as qk
     from integer_inference_engine_b200.model import SyntheticDecoder
     qk.free_all()
+    device.set_block_overlap(overlap)
     model = SyntheticDecoder(n_layers=5, d_model=512, n_heads=8, n_kv=2, head_dim=64, e_ffn=256, n_experts=8, top_k=2,
                              vocab=1000, context=40, max_new=12, window=16, seed=3)
     layers, embd, out_gain, cfg = _host_view(model)
@@ -65,6 +67,7 @@ def test_decode_steps_match_the_checker_eager_and_replayed():
     for i in range(4):                                      # replayed: position and token advance on the device
         g.replay()
         got.append(int(model.token.item()))
+    device.set_block_overlap(False)
     assert device.read_flags() == 0
     assert got == want
     for li in (0, 1, 4):                                    # the caches hold what the checker appended
