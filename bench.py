@@ -132,6 +132,19 @@ def host_cores() -> int:
         return os.cpu_count() or 1
 
 
+def use_all_host_threads() -> int:
+    """The CPU checkers are OpenMP code; a launcher may have exported OMP_NUM_THREADS=1 for its workers (torchrun does).
+    Give the OpenMP runtime they bind every core this process may use and return that count."""
+    import ctypes
+    n = host_cores()
+    os.environ["OMP_NUM_THREADS"] = str(n)
+    try:
+        ctypes.CDLL("libgomp.so.1", mode=ctypes.RTLD_GLOBAL).omp_set_num_threads(n)
+    except (OSError, AttributeError):
+        pass
+    return n
+
+
 def cpu_moe_block_time(kind: str, n_layers: int, repeats: int, seed: int = 1):
     """Time the CPU MoE block (one token) on `n_layers` synthetic layers with all host threads.
     kind "reference": linears by the reference project's compiled kernel (oracle/_ref), element-wise
@@ -213,6 +226,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    use_all_host_threads()
     from oracle import native as onat
     kind = "reference" if onat.ref_available() else "port"
     n_layers = 2
@@ -476,6 +490,7 @@ def run_ours(args):
     cpu = None
     if args.cpu_sample_layers > 0:
         n_cpu = min(args.cpu_sample_layers, args.layers)
+        use_all_host_threads()
         per_layer, head_s = cpu_token_time("port", n_cpu, 3, args.context)
         cpu = {"value": 1.0 / (per_layer * args.layers + head_s), "unit": "tok/s", "cores": host_cores(), "kind": "port",
                "sample": f"{n_cpu} blocks (attention over {args.context} keys + MoE) and the head, 1 token, median of 3, "
