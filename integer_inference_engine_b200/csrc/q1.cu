@@ -115,6 +115,7 @@ struct Q1Args {
     const int64_t *totals;          // [T][nb]
     int64_t *out;                   // [T][out_f]
     const int64_t *add;             // optional [T][out_f] added to the product (may be `out` itself)
+    int *flags;                     // optional: bit 3 is raised when a bulk copy never arrived
 };
 
 // A fragments of MMA m from the two bit words of a lane
@@ -220,6 +221,108 @@ __global__ void __launch_bounds__(512) q1_gemv_kernel(const Q1Args a) {
     }
 }
 
+// ---- single token, streamed: the CTA asks the copy engine for its whole run of tiles up front (one bulk copy per
+// tile, each with its own single-use barrier), then multiplies the tiles as they land.  Same arithmetic as the
+// kernel above; the weights come from shared memory instead of per-lane loads, so every byte of the run is in
+// flight from the first instruction.
+constexpr unsigned Q1_WAIT_LIMIT = 1u << 22;     // polls before a wait gives up and raises flag bit 3
+
+__device__ __forceinline__ uint32_t q1_s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool q1_wait(uint64_t *bar) {                       // bounded: false if the bytes never arrived
+    for (unsigned it = 0; it < Q1_WAIT_LIMIT; it++) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(q1_s32(bar)) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+template <int BPW, typename DT>
+__global__ void __launch_bounds__(512) q1_stream_kernel(const Q1Args a) {
+    constexpr int US = 256 + 16 * (int)sizeof(DT);
+    extern __shared__ __align__(128) uint8_t q1_sm[];
+    __shared__ int s_timeout;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const long long K = a.nb * 128;
+    const long long tile0 = (long long)blockIdx.x * a.tiles_per_cta;
+    const int ntile = (int)min((long long)a.tiles_per_cta, a.n_tiles - tile0);
+    const uint32_t tile_bytes = (uint32_t)(a.nb * US);
+    uint8_t *wbuf = q1_sm;                                                                        // [tiles_per_cta][tile_bytes]
+    unsigned long long *red = reinterpret_cast<unsigned long long *>(q1_sm + (size_t)a.tiles_per_cta * tile_bytes);   // [tiles][16]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(red + a.tiles_per_cta * 16);
+    for (int i = threadIdx.x; i < ntile; i += blockDim.x)
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(q1_s32(&bars[i])));
+    for (int i = threadIdx.x; i < a.tiles_per_cta * 16; i += blockDim.x) red[i] = 0ULL;
+    if (threadIdx.x == 0) s_timeout = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+    for (int i = threadIdx.x; i < ntile; i += blockDim.x) {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(q1_s32(&bars[i])), "r"(tile_bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(q1_s32(wbuf + (size_t)i * tile_bytes)), "l"(a.units + (size_t)(tile0 + i) * tile_bytes), "r"(tile_bytes),
+                       "r"(q1_s32(&bars[i])) : "memory");
+    }
+
+    uint32_t bf[BPW][8];
+    unsigned long long tot[BPW];
+    const int8_t *xcol = a.xl + (long long)col_limb(g) * K + 8 * t;
+#pragma unroll
+    for (int i = 0; i < BPW; i++) {
+        const long long b = warp + (long long)i * W;
+        tot[i] = 0;
+#pragma unroll
+        for (int m = 0; m < 4; m++) { bf[i][2 * m] = 0; bf[i][2 * m + 1] = 0; }
+        if (b < a.nb) {
+            tot[i] = (unsigned long long)__ldg(a.totals + b);
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                const uint2 v = ldg64(xcol + b * 128 + 32 * m);
+                bf[i][2 * m] = v.x; bf[i][2 * m + 1] = v.y;
+            }
+        }
+    }
+    const int myrow = g + 8 * (t & 1);
+    for (int tl = 0; tl < ntile; tl++) {
+        if (!q1_wait(&bars[tl])) { s_timeout = 1; break; }
+        const uint8_t *tile = wbuf + (size_t)tl * tile_bytes;
+        unsigned long long acc = 0;
+#pragma unroll
+        for (int i = 0; i < BPW; i++) {
+            const long long b = warp + (long long)i * W;
+            if (b >= a.nb) continue;
+            const uint8_t *unit = tile + b * US;
+            const uint2 w = *reinterpret_cast<const uint2 *>(unit + lane * 8);
+            const int64_t sc = (int64_t)*(reinterpret_cast<const DT *>(unit + 256) + myrow);
+            int c[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                uint32_t af[4];
+                q1_afrag(w, m, af);
+                mma_u8s8_k32(c, af[0], af[1], af[2], af[3], bf[i][2 * m], bf[i][2 * m + 1]);
+            }
+            unsigned long long lo, hi;
+            q1_partials(c, t, lo, hi);
+            const unsigned long long send = (t & 1) ? lo : hi;
+            unsigned long long mine = ((t & 1) ? hi : lo) + __shfl_xor_sync(0xffffffffu, send, 1);
+            mine += __shfl_xor_sync(0xffffffffu, mine, 2);
+            const unsigned long long s = 2ULL * mine - tot[i];
+            acc += (unsigned long long)q1_shift((int64_t)(s * (unsigned long long)sc), a.sh);
+        }
+        if (t < 2) atomicAdd(&red[tl * 16 + myrow], acc);
+    }
+    __syncthreads();
+    if (s_timeout) {                                       // a copy never arrived: report, store nothing
+        if (threadIdx.x == 0 && a.flags) atomicOr(a.flags, 8);
+        return;
+    }
+    for (int i = threadIdx.x; i < ntile * 16; i += blockDim.x) {
+        const long long row = tile0 * 16 + i;
+        if (row < a.out_f) a.out[row] = (int64_t)(red[i] + (a.add ? (unsigned long long)a.add[row] : 0ULL));
+    }
+}
+
 // ---- many tokens: one warp per 16-row tile, the expanded bits stay in registers, tokens in groups of four ----
 constexpr int Q1_TC = 16;                                             // tokens per CTA
 
@@ -304,8 +407,40 @@ cudaError_t launch_gemv(const Q1Args &a_in, int W, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+int g_q1_stream = 0;               // 1: single-token products through the bulk-copy kernel (same speed: the arithmetic per unit bounds both)
+
+template <int BPW, typename DT>
+cudaError_t launch_q1_stream(const Q1Args &a_in, int W, cudaStream_t s) {
+    Q1Args a = a_in;
+    constexpr int US = 256 + 16 * (int)sizeof(DT);
+    const size_t tile_bytes = (size_t)a.nb * US, per_tile = tile_bytes + 16 * 8 + 8;
+    const int max_tpc = (int)((200 * 1024) / per_tile);
+    if (max_tpc < 1) return cudaErrorInvalidConfiguration;
+    int tpc = (int)((a.n_tiles + 147) / 148);                    // one wave when the run fits in shared memory
+    if (tpc > max_tpc) tpc = max_tpc;
+    a.tiles_per_cta = tpc;
+    const unsigned grid = (unsigned)((a.n_tiles + tpc - 1) / tpc);
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(q1_stream_kernel<BPW, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    q1_stream_kernel<BPW, DT><<<grid, 32 * W, (size_t)tpc * per_tile + 16, s>>>(a);
+    note_launch();
+    return cudaGetLastError();
+}
+
 template <typename DT>
 cudaError_t launch_apply_t(const Q1Args &a, cudaStream_t s) {
+    if (a.T == 1 && a.nb <= 128 && g_q1_stream) {
+        const int W = a.nb > 64 ? 16 : 8;
+        const int bpw = (int)((a.nb + W - 1) / W);
+        if (bpw <= 2) return launch_q1_stream<2, DT>(a, W, s);
+        if (bpw <= 4) return launch_q1_stream<4, DT>(a, W, s);
+        if (bpw <= 6) return launch_q1_stream<6, DT>(a, W, s);
+        return launch_q1_stream<8, DT>(a, W, s);
+    }
     if (a.T == 1 && a.nb <= 128) {
         const int W = a.nb > 64 ? 16 : 8;
         const int bpw = (int)((a.nb + W - 1) / W);
@@ -350,6 +485,8 @@ __global__ void q1_embed_row_kernel(const uint8_t *units, long long nb, const in
 
 }  // namespace
 
+void set_q1_stream(int on) { g_q1_stream = on ? 1 : 0; }
+
 size_t q1_unit_bytes(bool sc32) { return 256 + 16 * (sc32 ? 4 : 8); }
 
 cudaError_t launch_q1_repack(const uint8_t *bits, const void *scale, int src_bits, bool sc32, long long out_f, long long nb,
@@ -387,7 +524,7 @@ cudaError_t launch_q1_apply(const uint8_t *units, bool sc32, long long out_f, lo
     Q1Args a;
     a.units = units; a.out_f = out_f; a.nb = nb; a.n_tiles = (out_f + 15) / 16; a.T = T;
     a.sh = frac <= 0 ? 0 : (frac >= 63 ? 63 : (int)frac);
-    a.tiles_per_cta = 1; a.xl = planes; a.totals = totals; a.out = out; a.add = add;
+    a.tiles_per_cta = 1; a.xl = planes; a.totals = totals; a.out = out; a.add = add; a.flags = shared_flag_word();
     return sc32 ? launch_apply_t<int>(a, s) : launch_apply_t<long long>(a, s);
 }
 

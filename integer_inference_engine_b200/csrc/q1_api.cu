@@ -299,6 +299,8 @@ extern "C" int iie_q1_head_norm_dev(const int64_t *x_dev, long long rows_a, long
                                     (cudaStream_t)stream) == cudaSuccess ? 0 : 2;
 }
 
+extern "C" void iie_q1_set_stream(int on) { iie::set_q1_stream(on); }
+
 extern "C" int iie_q1_silu_mul_dev(const int64_t *gate_dev, const int64_t *up_dev, long long n, long long frac, int64_t *out_dev,
                                    void *stream) {
     if (!gate_dev || !up_dev || !out_dev || n <= 0 || frac < 1 || frac > 29) return 1;

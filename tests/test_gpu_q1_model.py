@@ -184,3 +184,27 @@ def test_rmsnorm_long_rows(rows, width):
         got = device.rmsnorm(torch.from_numpy(x).cuda(), h, FRAC, 1).cpu().numpy()
         assert np.array_equal(got, o.rmsnorm_fixed(x, FRAC, 1, g))
     assert device.read_flags() == 0
+
+
+@pytest.mark.parametrize(("out_f", "nb"), [(48, 1), (200, 4), (4096, 32), (1000, 96), (33, 128)])
+def test_single_token_launch_forms_agree(out_f, nb):
+    """The bulk-copy kernel and the per-lane-load kernel against the checker, int32 and int64 scales."""
+    import torch
+
+    from integer_inference_engine_b200 import device, q1_gpu
+    from oracle import native as onat
+    rng = np.random.default_rng(70 + out_f + nb)
+    bits, scale = o.synth_q1(rng, out_f, nb)
+    x = rng.integers(-(1 << 40), 1 << 40, size=(1, nb * 128), dtype=np.int64)
+    xd = torch.from_numpy(x).cuda()
+    device.read_flags()
+    try:
+        for sc in (scale.astype(np.int32), rng.integers(-(1 << 40), 1 << 40, size=scale.shape, dtype=np.int64)):
+            h = q1_gpu.q1_register_weight(bits, sc)
+            want = onat.q1_linear(x, bits, sc.astype(np.int64), FRAC)
+            for form in (True, False):
+                q1_gpu.set_stream_form(form)
+                assert np.array_equal(q1_gpu.apply_dev(h, xd, FRAC).cpu().numpy(), want), (form, sc.dtype)
+    finally:
+        q1_gpu.set_stream_form(False)
+    assert device.read_flags() == 0
