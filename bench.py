@@ -58,7 +58,6 @@ def parse():
     ap.add_argument("--cpu-sample-layers", type=int, default=2)
     ap.add_argument("--context", type=int, default=4096, help="KV-cache rows already filled when decoding starts")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--overlap", type=int, default=0, help="1: the attention half of a block runs beside its expert kernels")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep_decode", "q1", "q1_token"],
                     help="decode = the headline line (batch-1 MoE decode); the others print a line of the same "
                          "shape for the prefill, expert-parallel and Q1_0 configurations")
@@ -375,11 +374,9 @@ def run_ours(args):
     for i in range(3):
         model.step(pos0 + i)
         eager_ids.append(int(model.token.item()))
-    model.token.fill_(first_token); model.pos.fill_(pos0)
+    model.token.fill_(first_token); model.set_position(pos0)
     l0 = device.launch_count()
-    device.set_block_overlap(bool(args.overlap))                  # the eager chain above ran the halves in sequence
     model.capture(pos_bound)
-    device.set_block_overlap(False)                               # the captured graph keeps its two branches
     launches_per_step = (device.launch_count() - l0) // 2         # capture() runs the step twice
     replay_ids = []
     for i in range(3):
@@ -501,7 +498,7 @@ def run_ours(args):
         "metric": "decode_tok_per_s", "value": world * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers": args.layers, "block_halves": "side by side" if args.overlap else "in sequence", "context": args.context, "parallelism": f"replicas x{world}",
+        "config": {"workload": WORKLOAD, "layers": args.layers, "context": args.context, "parallelism": f"replicas x{world}",
                    "l2": "inputs larger than L2: each step streams %d MB of distinct weights and %d MB of KV cache"
                          % (w_bytes // 2**20, kv_bytes // 2**20),
                    "weight_bytes_per_token": w_bytes, "kv_bytes_per_token": kv_bytes,
@@ -828,7 +825,7 @@ def run_q1_token(args):
     assert device.read_flags() == 0
     tin = torch.zeros(1, dtype=torch.int32).pin_memory(); tout = torch.zeros(1, dtype=torch.int32).pin_memory()
     tin[0] = 11
-    m.pos.fill_(ctx)
+    m.set_position(ctx)
     e2e_ms, _ = _timed(lambda i: m.decode_token(tin, tout), args.steps, 1, 1, local)
     wbytes = m.weight_bytes_per_token()
     kv = 2 * m.Hkv * m.hd * 4 * (ctx + args.warmup + args.steps // 2) * L

@@ -96,6 +96,9 @@ int iie_q1_embed_dev(long long handle, const int *row_dev, long long row, int64_
 /* Launch form of the single-token product: 1 = the run of tiles of a CTA is requested with bulk copies into shared
  * memory up front, 0 (default) = per-lane loads with one tile of look-ahead.  Same results, same speed within 3 %. */
 void iie_q1_set_stream(int on);
+/* Changes whenever a scratch buffer of the Q1_0 entries is freed (to grow, or by bonsai_q1_free_weights): a CUDA graph
+ * captured over iie_q1_*_dev calls holds the old addresses and must be captured again. */
+unsigned long long iie_q1_workspace_generation(void);
 /* Shape of a registered weight; 0 ok, 1 unknown handle. */
 int iie_q1_weight_shape(long long handle, long long *out_f, long long *n_blocks, int *scale_bits);
 

@@ -199,21 +199,9 @@ int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t
                        const int *pos_dev, long long window, const int64_t *cos_dev, const int64_t *sin_dev, int rope,
                        int n_heads, int n_kv, int head_dim, long long cache_rows, int fa, int fw, long long inv_sqrt,
                        void *stream);
-/* Overlap of the two halves of a decoder block.  Both halves read the row the block's routing kernel normalised and
- * add into the same residual row with integer atomics, so they may run side by side: with the switch on,
- * iie_attn_block_dev runs on a stream of the library after the routing kernel of the last single-token
- * iie_moe_block_dev call (its `stream` argument is then ignored), and the next iie_moe_block_dev waits for it.
- * iie_join_block_overlap makes `stream` wait for an attention half still in flight: call it after the last block,
- * before anything else reads the residual row (and before a stream capture ends).  0 ok, 1 failure. */
-int iie_set_block_overlap(int on);
-int iie_join_block_overlap(void *stream);
-/* 1 (default): batches of 2 .. tc_min_tokens-1 rows stream every touched expert tile once for all of its rows;
- * 0: the older kernel that re-reads a tile for every four rows.  Results are identical; for measurements. */
-void iie_set_batch_stream(int enabled);
 /* Form of the single-token attention: 1 (default) one cooperative launch when all of its CTAs fit on the device at
- * once (about 4700 visible keys per KV head on B200), else three launches; 0: always three launches; 2: one
- * thread-block cluster per KV head (up to 5120 visible keys, at most eight query heads per KV head, head_dim <= 128;
- * measured slower: 64 CTAs cannot pull the cache fast enough).  Same bytes in every form. */
+ * once (about 4700 visible keys per KV head on B200), else three launches; 0: always three launches.  Same bytes in
+ * either form; the switch exists so that tests reach both. */
 void iie_set_attn_fused(int enabled);
 /* Row `token` (or *token_dev when token_dev != NULL) of a registered Q4_K / Q6_K matrix as int64 at 2^frac:
  * the embedding look-up (north-mini-code/src/nmc/engine.py:239-243). */
@@ -234,23 +222,20 @@ int iie_rmsnorm_dev(long long gain_h, const int64_t *x_dev, long long rows, long
  * 1 router product, 2 top-k, 3 gate/up, 4 down; 0 = all) so that one kernel can be timed alone on
  * data left by a previous full call; and the number of kernels launched since load. */
 void iie_profile_stage_mask(int mask);
-/* Two alternative launch structures of the single-token block, both off by default because they measured
- * slower on B200 than the three-launch form (routing, gate/up, down); results are identical either way.
- * 1: a single token's routing is recomputed inside the gate/up launch (two launches per block). */
-void iie_set_fused_route(int enabled);
-/* 1: a single token's expert stage runs as one launch, one thread-block cluster per selected expert;
- * 0 (default): as two streamed launches (gate/up, down).  Results are identical; for measurements. */
-void iie_set_fused_expert(int enabled);
-/* Cluster shape that launch settled on: 1000 * CTAs per cluster + clusters the device holds at once
- * (-1 before its first use). */
-int iie_expert_clusters(void);
-
 /* Switch programmatic dependent launch between the three single-token kernels on (default) or off. */
 void iie_set_pdl(int enabled);
 /* Token count from which iie_moe_forward_dev uses the tcgen05 grouped GEMMs instead of the streamed
  * kernels (default 32; a very large value disables the tensor-core path). */
 void iie_set_tc_min_tokens(long long tokens);
 unsigned long long iie_launch_count(void);
+/* Launches of each tensor-core (tcgen05) tile shape since load, so a test can tell which shape served a call:
+ * out[0..6] = Q4_K gate/up with 3 / 4 activation digits, Q6_K down with 5 / 6, Q4_K down with 5, Q4_K linear with
+ * 3 / 5.  Returns 7, or -1 when capacity < 7. */
+int iie_prefill_launch_counts(unsigned long long *out, int capacity);
+/* Workspace generation: changes whenever a scratch buffer of the library is freed (to grow, by
+ * qk_moe_workspace_release or qk_free_all).  A CUDA graph captured over iie_*_dev calls holds the scratch addresses of
+ * its capture; record this value at capture and refuse to replay once it has changed. */
+unsigned long long iie_workspace_generation(void);
 
 /* iie_apply_dev without any allocation (no counterpart in the reference).  For callers that cannot let
  * a library allocate device memory at call time: a process whose own pool already holds the whole

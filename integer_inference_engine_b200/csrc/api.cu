@@ -55,23 +55,12 @@ std::vector<Weight> g_w;
 std::vector<MoeLayer> g_layers;
 cudaStream_t g_stream = nullptr;
 int *g_flags = nullptr;               // device flag word
-// Overlap of the two halves of a decoder block (both read the same normalised row and add into the same residual
-// row with integer atomics): the attention half runs on g_side after the routing kernel, the next block's routing
-// kernel waits for it.
-int g_overlap = 0;
-bool g_attn_pending = false;
-cudaStream_t g_side = nullptr;
-cudaEvent_t g_ev_route = nullptr, g_ev_attn = nullptr;
 int *g_cells = nullptr;               // device ints: [0] limbs of h, [1] limbs of gate*up, [2] routing ticket
 const uint8_t **g_selptr = nullptr;   // device: [3][64] pointers of the experts the last routing selected
 int g_pdl = 1;                        // programmatic dependent launch between the decode kernels
-int g_batch_stream = 1;               // small batches: stream each touched expert tile once (batch.cu) instead of per 4 rows
-int g_fused_expert = 0;               // single-token expert stage as one cluster launch (expert.cu): slower on this part
-int g_fused_route = 0;                // routing recomputed inside the gate/up launch (rgu.cu): slower than its own launch
 long long g_hl_d = 0;                 // width of the digit planes the last single-token routing left in the R_XL scratch
 int64_t *g_pow2 = nullptr;            // device: 2^i for i = 0..31 (unit gates at any activation scale)
 int g_attn_parity = 0;                // which of the two attention digit-count cells the next block call uses
-int g_gu_parity = 0;                  // which of the two gu digit-count cells the next fused launch uses
 long long g_tc_min_tokens = 192;      // from this many tokens on, the MoE block runs on the tcgen05 grouped GEMMs
 int g_ready = -1;                     // -1 unknown, 0 usable, 1 unusable
 int g_stage_mask = 0;                 // profiling: when non-zero, iie_moe_forward_dev runs only these stages
@@ -84,6 +73,9 @@ enum Role { R_X, R_XL, R_OUT, R_RAW, R_GU, R_GUL, R_TMP0, R_TMP1, R_TMP2, R_TABS
 struct Buf { void *p = nullptr; size_t cap = 0; };
 Buf g_buf[R_COUNT];
 long long g_ws_allocs = 0;
+// Incremented whenever a workspace address a caller may have baked into a captured graph stops being valid (a buffer
+// is freed to grow, or the workspaces are released): holders of captured graphs compare it before replaying.
+unsigned long long g_ws_generation = 0;
 
 bool init() {
     if (g_ready >= 0) return g_ready == 0;
@@ -105,7 +97,7 @@ bool init() {
 void *ensure(int role, size_t bytes) {
     Buf &b = g_buf[role];
     if (b.cap >= bytes && b.p) return b.p;
-    if (b.p) { cudaStreamSynchronize(g_stream); cudaFree(b.p); prof(PM_FREE_CALLS); b.p = nullptr; b.cap = 0; }
+    if (b.p) { cudaStreamSynchronize(g_stream); cudaFree(b.p); prof(PM_FREE_CALLS); b.p = nullptr; b.cap = 0; g_ws_generation++; }
     size_t cap = std::max<size_t>(bytes, 256);
     if (cudaMalloc(&b.p, cap) != cudaSuccess) { cudaGetLastError(); b.p = nullptr; return nullptr; }
     b.cap = cap; g_ws_allocs++;
@@ -115,7 +107,7 @@ void *ensure(int role, size_t bytes) {
 
 void release_workspace() {
     if (g_stream) cudaStreamSynchronize(g_stream);
-    for (auto &b : g_buf) if (b.p) { cudaFree(b.p); prof(PM_FREE_CALLS); b.p = nullptr; b.cap = 0; }
+    for (auto &b : g_buf) if (b.p) { cudaFree(b.p); prof(PM_FREE_CALLS); b.p = nullptr; b.cap = 0; g_ws_generation++; }
 }
 
 bool h2d(void *dst, const void *src, size_t n) {
@@ -215,11 +207,10 @@ bool linear_dev(const Weight &w, const int64_t *x, long long T, int fw, int64_t 
         sa.xl = xl; sa.x_per_sel = 0; sa.x_nl = nullptr; sa.out = out; sa.flags = g_flags;
         sa.fast = small_scales(w.maxd, w.maxdmin, fw); sa.pdl = 0;
         if (launch_stream(w.qtype, MODE_LINEAR, sa, s) != cudaSuccess) return false;
-    } else if (T >= 2 && T < (1 << 20) && g_batch_stream && g_stage_mask == 0) {
+    } else if (T >= 2 && T < (1 << 20) && g_stage_mask == 0) {
         // a few rows: one group that owns all of them, every tile streamed once
         int *off = (int *)ensure(R_META, 64);
-        const int host_off[2] = {0, (int)T};
-        if (!off || cudaMemcpyAsync(off, host_off, sizeof(host_off), cudaMemcpyHostToDevice, s) != cudaSuccess) return false;
+        if (!off || launch_set2(off, 0, (int)T, s) != cudaSuccess) return false;
         BatchArgs ba = {};
         ba.wa = w.cell; ba.wb = w.cell; ba.grp_off = off; ba.n_groups = 1; ba.out_f = w.out_f; ba.n_blocks = w.nb; ba.fw = fw; ba.fa = 16;
         ba.fast = small_scales(w.maxd, w.maxdmin, fw); ba.xl = xl; ba.out = out; ba.flags = g_flags;
@@ -254,7 +245,7 @@ bool moe_fused(const MoePlan &p, const int8_t *hl, bool x_bcast_zero, const int 
     int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)n_pairs * 8 * p.e_ffn);
     if (!gul) return false;
     (void)x_bcast_zero;
-    if (!grp_expert && grp_off && g_batch_stream && g_stage_mask == 0) {
+    if (!grp_expert && grp_off && g_stage_mask == 0) {
         // groups are the experts themselves: stream every touched expert tile once for all of its rows
         if (cudaMemsetAsync(g_cells + 1, 0, sizeof(int), s) != cudaSuccess) return false;
         BatchArgs ga = {};
@@ -319,47 +310,63 @@ int read_cell(int idx, cudaStream_t s) {
     return v;
 }
 
-// Tensor-core (tcgen05) path for many tokens: router GEMM, top-k, dispatch, grouped gate/up and down GEMMs.
-// Returns 0 done, 1 error, -1 not applicable (caller uses the streamed kernels).
-// Expert stage of the MoE block on the tensor-core tiles: dispatch -> gate/up (+SiLU*up) -> down (+combine).
-// hl = digit planes of the T hidden rows (nl_h digits in use), ids/gates = routing of every row; experts
-// of this layer are ids expert_base .. expert_base + n_experts - 1, other slots are skipped.
-// Returns -1 when the layer is outside what the tiles carry (the caller then streams), 0 ok, 1 failure.
-int moe_experts_tc(const MoeLayer &L, const int8_t *hl, int nl_h, long long T, const int *ids, const int64_t *gates,
-                   int expert_base, int fa, int fw, int accumulate, int64_t *out_dev, cudaStream_t s) {
-    const int E = L.n_experts, k = L.top_k;
-    const long long P = T * k;
-    if (L.gate_q != QT_Q4K || L.d_model > 8192 || L.e_ffn > 8192 || nl_h < 1 || nl_h > 4) return -1;
-    if (!small_scales(L.maxd_gate, L.maxdmin_gate, fw) || !small_scales(L.maxd_down, L.maxdmin_down, fw)) return -1;
-    if (max_weight(QT_Q4K, L.maxd_gate, L.maxdmin_gate, fw) > CAP4) return -1;
-    if (max_weight(L.down_q, L.maxd_down, L.maxdmin_down, fw) > (L.down_q == QT_Q4K ? CAP4 : (unsigned __int128)0x7FFFFFFFULL * 32)) return -1;   // Q6_K: d_q * 128 stays in int32
-    int *off = (int *)ensure(R_GRPOFF, (size_t)(E + 2) * sizeof(int));
-    int *ptok = (int *)ensure(R_PAIRTOK, (size_t)P * sizeof(int));
-    int64_t *pg = (int64_t *)ensure(R_PAIRGATE, (size_t)P * 8);
-    int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)P * 8 * L.e_ffn);
-    if (!off || !ptok || !pg || !gul) return 1;
+// Expert stage on the tensor-core (tcgen05) tiles for pairs already sorted by group: group x uses the weights
+// gate[x] / up[x] / down[x] and owns pairs [off[x], off[x+1]); xidx maps a pair to its row of digit planes, ptok to its
+// output row, pg holds its gate weight.  gate/up (+SiLU*up, digit planes of the product) -> down (+gate-weighted combine).
+// Returns -1 when the weights or the activation are outside what the tiles carry (the caller then streams), 0 ok, 1 failure.
+struct GroupedWeights {
+    const uint8_t *const *gate, *const *up, *const *down;
+    int gate_q, down_q;
+    long long d_model, e_ffn;
+    unsigned maxd_gate, maxdmin_gate, maxd_down, maxdmin_down;
+};
+
+int grouped_tc(const GroupedWeights &w, int n_groups, const int *off, const int *xidx, const int *ptok, const int64_t *pg,
+               const int8_t *hl, int nl_h, long long T, long long P, int fa, int fw, int accumulate, int64_t *out_dev,
+               cudaStream_t s) {
+    if (w.gate_q != QT_Q4K || w.d_model > 8192 || w.e_ffn > 8192 || nl_h < 1 || nl_h > 4) return -1;
+    if (!small_scales(w.maxd_gate, w.maxdmin_gate, fw) || !small_scales(w.maxd_down, w.maxdmin_down, fw)) return -1;
+    if (max_weight(QT_Q4K, w.maxd_gate, w.maxdmin_gate, fw) > CAP4) return -1;
+    if (max_weight(w.down_q, w.maxd_down, w.maxdmin_down, fw) > (w.down_q == QT_Q4K ? CAP4 : (unsigned __int128)0x7FFFFFFFULL * 32)) return -1;   // Q6_K: d_q * 128 stays in int32
+    int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)P * 8 * w.e_ffn);
+    if (!gul) return 1;
     if (cudaMemsetAsync(g_cells + 1, 0, sizeof(int), s) != cudaSuccess) return 1;
-    if (launch_dispatch(ids, gates, T, k, E, off, ptok, pg, s, expert_base) != cudaSuccess) return 1;
     PrefillArgs ga = {};
-    ga.wa = L.tabs; ga.wb = L.tabs + E; ga.grp_off = off; ga.n_experts = E; ga.n_pairs = P; ga.out_f = L.e_ffn;
-    ga.n_blocks = L.d_model / 256; ga.fw = fw; ga.fa = fa; ga.xl = hl; ga.xidx = ptok; ga.out = nullptr; ga.out_limbs = gul;
+    ga.wa = w.gate; ga.wb = w.up; ga.grp_off = off; ga.n_experts = n_groups; ga.n_pairs = P; ga.out_f = w.e_ffn;
+    ga.n_blocks = w.d_model / 256; ga.fw = fw; ga.fa = fa; ga.xl = hl; ga.xidx = xidx; ga.out = nullptr; ga.out_limbs = gul;
     ga.out_nl = g_cells + 1; ga.flags = g_flags;
     if (launch_prefill(QT_Q4K, MODE_GATEUP, nl_h, ga, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     const int nl_gu = read_cell(1, s);
     if (nl_gu < 0) return 1;
-    if (!accumulate && cudaMemsetAsync(out_dev, 0, (size_t)T * L.d_model * 8, s) != cudaSuccess) return 1;
+    if (!accumulate && cudaMemsetAsync(out_dev, 0, (size_t)T * w.d_model * 8, s) != cudaSuccess) return 1;
     PrefillArgs da = {};
-    da.wa = L.tabs + 2 * E; da.wb = da.wa; da.grp_off = off; da.n_experts = E; da.n_pairs = P; da.out_f = L.d_model;
-    da.n_blocks = L.e_ffn / 256; da.fw = fw; da.fa = fa; da.xl = gul; da.xidx = nullptr; da.out = out_dev; da.gates = pg;
+    da.wa = w.down; da.wb = w.down; da.grp_off = off; da.n_experts = n_groups; da.n_pairs = P; da.out_f = w.d_model;
+    da.n_blocks = w.e_ffn / 256; da.fw = fw; da.fa = fa; da.xl = gul; da.xidx = nullptr; da.out = out_dev; da.gates = pg;
     da.pair_tok = ptok; da.flags = g_flags;
-    const cudaError_t de = launch_prefill(L.down_q, MODE_DOWN, nl_gu < 1 ? 1 : nl_gu, da, s);
+    const cudaError_t de = launch_prefill(w.down_q, MODE_DOWN, nl_gu < 1 ? 1 : nl_gu, da, s);
     if (de == cudaSuccess) return 0;
     cudaGetLastError();
     // the activation needs more digits than the tensor-core tiles carry: streamed kernels for the down stage
     SkinnyArgs d = {};
-    d.wa = L.tabs + 2 * E; d.wb = d.wa; d.grp_off = off; d.pairs_per_group = 1; d.out_f = L.d_model; d.n_blocks = L.e_ffn / 256;
+    d.wa = w.down; d.wb = w.down; d.grp_off = off; d.pairs_per_group = 1; d.out_f = w.d_model; d.n_blocks = w.e_ffn / 256;
     d.fw = fw; d.fa = fa; d.xl = gul; d.out = out_dev; d.gates = pg; d.pair_tok = ptok; d.flags = g_flags;
-    return launch_skinny(L.down_q, MODE_DOWN, d, E, 4, s) == cudaSuccess ? 0 : 1;
+    return launch_skinny(w.down_q, MODE_DOWN, d, n_groups, 4, s) == cudaSuccess ? 0 : 1;
+}
+
+// The same for a registered layer: hl = digit planes of the T hidden rows (nl_h digits in use), ids/gates = routing of
+// every row; experts of this layer are ids expert_base .. expert_base + n_experts - 1, other slots are skipped.
+int moe_experts_tc(const MoeLayer &L, const int8_t *hl, int nl_h, long long T, const int *ids, const int64_t *gates,
+                   int expert_base, int fa, int fw, int accumulate, int64_t *out_dev, cudaStream_t s) {
+    const int E = L.n_experts, k = L.top_k;
+    const long long P = T * k;
+    int *off = (int *)ensure(R_GRPOFF, (size_t)(E + 2) * sizeof(int));
+    int *ptok = (int *)ensure(R_PAIRTOK, (size_t)P * sizeof(int));
+    int64_t *pg = (int64_t *)ensure(R_PAIRGATE, (size_t)P * 8);
+    if (!off || !ptok || !pg) return 1;
+    if (launch_dispatch(ids, gates, T, k, E, off, ptok, pg, s, expert_base) != cudaSuccess) return 1;
+    const GroupedWeights w = {L.tabs, L.tabs + E, L.tabs + 2 * E, L.gate_q, L.down_q, L.d_model, L.e_ffn,
+                              L.maxd_gate, L.maxdmin_gate, L.maxd_down, L.maxdmin_down};
+    return grouped_tc(w, E, off, ptok, ptok, pg, hl, nl_h, T, P, fa, fw, accumulate, out_dev, s);
 }
 
 // Whole block (router GEMM, top-k, expert stage) on the tensor-core tiles.  Same return codes.
@@ -378,8 +385,7 @@ int moe_prefill_tc(const MoeLayer &L, const int64_t *h_dev, long long T, int fa,
     const int nl_h = read_cell(0, s);
     if (nl_h < 1 || nl_h > 4) return nl_h < 1 ? 1 : -1;
     // router: one "expert" that owns all T rows
-    const int host_off[2] = {0, (int)T};
-    if (cudaMemcpyAsync(one_off, host_off, sizeof(host_off), cudaMemcpyHostToDevice, s) != cudaSuccess) return 1;
+    if (launch_set2(one_off, 0, (int)T, s) != cudaSuccess) return 1;
     PrefillArgs ra = {};
     ra.wa = r.cell; ra.wb = r.cell; ra.grp_off = one_off; ra.n_experts = 1; ra.n_pairs = T; ra.out_f = E;
     ra.n_blocks = L.d_model / 256; ra.fw = fw; ra.fa = fa; ra.xl = hl; ra.out = lg; ra.flags = g_flags;
@@ -409,28 +415,6 @@ bool moe_decode_token(const MoeLayer &L, const int64_t *x, const int64_t *gain, 
     int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)k * 8 * L.e_ffn);
     if (!hl || !lg || !gul) return false;
     g_hl_d = L.d_model;
-    if (g_fused_route && g_stage_mask == 0 && r.qtype == QT_Q4K && L.gate_q == QT_Q4K && k <= 64 &&
-        !(init_mode == 1 && out == x)) {
-        int *cell = g_cells + 4 + g_gu_parity, *cell_next = g_cells + 4 + (g_gu_parity ^ 1);
-        RoutedGateUpArgs fa_ = {};
-        fa_.x = x; fa_.gain = gain; fa_.d = (int)L.d_model; fa_.fa = fa; fa_.fw = fw; fa_.eps = eps;
-        fa_.router = (const uint8_t *)r.d; fa_.n_experts = E; fa_.k = k; fa_.e_ffn = L.e_ffn; fa_.tabs = L.tabs;
-        fa_.ids = ids; fa_.gates = gates; fa_.sel_down = g_selptr + 2 * k; fa_.init_out = out; fa_.init_mode = init_mode;
-        fa_.out_limbs = gul; fa_.gu_nl = cell; fa_.gu_nl_next = cell_next; fa_.flags = g_flags; fa_.pdl = g_pdl;
-        fa_.fast = small_scales(L.maxd_gate, L.maxdmin_gate, fw);
-        const cudaError_t fe = launch_routed_gateup(L.gate_q, fa_, s);
-        if (fe == cudaSuccess) {
-            g_gu_parity ^= 1; g_hl_d = 0;                   // this path keeps the digit planes in shared memory only
-            StreamArgs da = {};
-            da.wa = L.tabs + 2 * E; da.wb = da.wa; da.sel = ids; da.n_sel = k; da.out_f = L.d_model; da.n_blocks = L.e_ffn / 256;
-            da.fw = fw; da.fa = fa; da.xl = gul; da.x_per_sel = 1; da.x_nl = cell; da.out = out; da.gates = gates;
-            da.flags = g_flags; da.fast = small_scales(L.maxd_down, L.maxdmin_down, fw);
-            da.sel_wa = g_selptr + 2 * k; da.pdl = g_pdl; da.early_weights = 0;
-            return launch_stream(L.down_q, MODE_DOWN, da, s) == cudaSuccess;
-        }
-        cudaGetLastError();
-        if (fe != cudaErrorNotSupported) return false;
-    }
     RouteArgs ra = {};
     ra.x = x; ra.gain = gain; ra.d = (int)L.d_model; ra.fa = fa; ra.fw = fw; ra.eps = eps;
     ra.router = (const uint8_t *)r.d; ra.router_q = r.qtype; ra.n_experts = E; ra.k = k;
@@ -439,23 +423,7 @@ bool moe_decode_token(const MoeLayer &L, const int64_t *x, const int64_t *gain, 
     ra.flags = g_flags;
     const bool ptrs = k <= 64;
     ra.tabs = ptrs ? L.tabs : nullptr; ra.sel_ptrs = ptrs ? g_selptr : nullptr; ra.pdl = g_pdl;
-    if (g_overlap && g_attn_pending) {                    // the previous block's attention half still adds into x
-        if (cudaStreamWaitEvent(s, g_ev_attn, 0) != cudaSuccess) return false;
-        g_attn_pending = false;
-        ra.pdl = 0;
-    }
     if (stage_on(ST_ROUTER) && launch_route(ra, s) != cudaSuccess) return false;
-    if (g_overlap && cudaEventRecord(g_ev_route, s) != cudaSuccess) return false;
-    if (g_fused_expert && ptrs && (g_stage_mask == 0 || (g_stage_mask & 24) == 24) && small_scales(L.maxd_gate, L.maxdmin_gate, fw) &&
-        small_scales(L.maxd_down, L.maxdmin_down, fw)) {
-        ExpertArgs ea = {};
-        ea.sel_ptrs = g_selptr; ea.k = k; ea.d_model = L.d_model; ea.e_ffn = L.e_ffn; ea.fw = fw; ea.fa = fa;
-        ea.hl = hl; ea.h_nl = g_cells; ea.gates = gates; ea.out = out; ea.flags = g_flags; ea.pdl = g_pdl;
-        const cudaError_t ee = launch_expert(L.gate_q, L.down_q, ea, s);
-        if (ee == cudaSuccess) return true;
-        cudaGetLastError();
-        if (ee != cudaErrorNotSupported) return false;
-    }
     StreamArgs ga = {};
     ga.wa = L.tabs; ga.wb = L.tabs + E; ga.sel = ids; ga.n_sel = k; ga.out_f = L.e_ffn; ga.n_blocks = L.d_model / 256;
     ga.fw = fw; ga.fa = fa; ga.xl = hl; ga.x_per_sel = 0; ga.x_nl = g_cells; ga.out = nullptr; ga.out_limbs = gul;
@@ -508,14 +476,28 @@ int moe_host_entry(const long long *gate_h, const long long *up_h, const long lo
 
     bool done = false;
     if (fast) {
-        // group pairs by identical (gate, up, down) triple, in order of first appearance
-        std::map<std::tuple<long long, long long, long long>, int> index;
+        // group pairs by identical (gate, up, down) triple, in order of first appearance: a table indexed by the gate
+        // handle serves the usual case (an expert's three matrices always appear together), an ordered map the rest
         std::vector<std::vector<int>> members;
-        for (size_t i = 0; i < P; i++) {
-            auto key = std::make_tuple(gate_h[i], up_h[i], down_h[i]);
-            auto it = index.find(key);
-            if (it == index.end()) { it = index.emplace(key, (int)members.size()).first; members.emplace_back(); }
-            members[it->second].push_back((int)i);
+        {
+            std::vector<int> by_gate(g_w.size(), -1);
+            bool simple = true;
+            for (size_t i = 0; i < P && simple; i++) {
+                int &slot = by_gate[(size_t)gate_h[i]];
+                if (slot < 0) { slot = (int)members.size(); members.emplace_back(); }
+                else { const int f = members[slot][0]; simple = up_h[f] == up_h[i] && down_h[f] == down_h[i]; }
+                if (simple) members[slot].push_back((int)i);
+            }
+            if (!simple) {
+                members.clear();
+                std::map<std::tuple<long long, long long, long long>, int> index;
+                for (size_t i = 0; i < P; i++) {
+                    auto key = std::make_tuple(gate_h[i], up_h[i], down_h[i]);
+                    auto it = index.find(key);
+                    if (it == index.end()) { it = index.emplace(key, (int)members.size()).first; members.emplace_back(); }
+                    members[it->second].push_back((int)i);
+                }
+            }
         }
         const int G = (int)members.size();
         std::vector<const uint8_t *> tabs(3 * (size_t)G);
@@ -541,9 +523,19 @@ int moe_host_entry(const long long *gate_h, const long long *up_h, const long lo
         bool ok = h2d(tabs_dev, tabs.data(), tabs.size() * sizeof(void *)) && h2d(off_dev, grp_off.data(), (G + 1) * sizeof(int)) &&
                   h2d(tok_dev, pair_tok.data(), P * sizeof(int)) && h2d(pg_dev, pair_gate.data(), P * 8) &&
                   cudaMemsetAsync(out_dev, 0, (size_t)m * d_model * 8, g_stream) == cudaSuccess &&
-                  launch_limbs(h_dev, m, d_model, hl, g_flags, g_stream) == cudaSuccess &&
-                  moe_fused(plan, hl, false, tok_dev, nullptr, off_dev, G, (long long)P, maxp, pg_dev, tok_dev, fa, fw,
-                            out_dev, g_stream);
+                  cudaMemsetAsync(g_cells, 0, sizeof(int), g_stream) == cudaSuccess &&
+                  launch_limbs(h_dev, m, d_model, hl, g_flags, g_stream, g_cells) == cudaSuccess;
+        int tc = -1;
+        if (ok && m >= g_tc_min_tokens && g_stage_mask == 0) {
+            // prefill-sized call (Engine._moe's batched entry, engine.py:389-411): the grouped tensor-core tiles
+            const int nl_h = read_cell(0, g_stream);
+            const GroupedWeights w = {tabs_dev, tabs_dev + G, tabs_dev + 2 * G, gw[0]->qtype, dw[0]->qtype, d_model, e_ffn, mg, mgm, md, mdm};
+            tc = nl_h < 1 ? 1 : grouped_tc(w, G, off_dev, tok_dev, tok_dev, pg_dev, hl, nl_h, m, (long long)P, fa, fw, 1, out_dev, g_stream);
+            ok = tc != 1;
+        }
+        if (ok && tc < 0)
+            ok = moe_fused(plan, hl, false, tok_dev, nullptr, off_dev, G, (long long)P, maxp, pg_dev, tok_dev, fa, fw, out_dev, g_stream,
+                           g_cells, mg, mgm, md, mdm);
         if (!ok) { cudaGetLastError(); return 1; }
         const int f = read_flags_clear();
         if (f < 0) return 1;
@@ -1121,6 +1113,7 @@ extern "C" int qk_attention_bank_import(long long h, int layer, const int64_t *k
     if (!k || !v || layer < 0 || layer >= b.n_layers || length < 0 || length > b.max_length || b.layers[(size_t)layer].poisoned ||
         !ensure_bank_layer(b, b.layers[(size_t)layer])) return 1;
     BankLayer &l = b.layers[(size_t)layer];
+    l.wide = false;                                          // describes the rows imported by THIS call only
     const size_t per_head = (size_t)length * (size_t)b.head_dim;
     if (per_head) {
         // narrow on the host: a value outside int32 cannot be held, so the next apply on this layer reports the guard
@@ -1162,7 +1155,10 @@ extern "C" int qk_attention_bank_apply(long long h, int layer, long long qh, lon
     int64_t *od = (int64_t *)ensure(R_OUT, (size_t)d * 8);
     int8_t *xl = (int8_t *)ensure(R_XL, (size_t)8 * (d > qd ? d : qd));      // also holds the planes of the O product's input
     if (!xd || !qkv || !att || !od || !xl) return 1;
-    if (read_flags_clear() < 0 || !h2d(xd, x, (size_t)d * 8) || launch_limbs(xd, 1, d, xl, g_flags, g_stream) != cudaSuccess)
+    // flags raised by earlier device-pointer calls belong to their caller: set aside here, put back before returning
+    const int earlier = read_flags_clear();
+    struct Restore { int f; ~Restore() { if (f > 0) { cudaMemcpy(g_flags, &f, sizeof(int), cudaMemcpyHostToDevice); cudaGetLastError(); } } } restore{earlier};
+    if (earlier < 0 || !h2d(xd, x, (size_t)d * 8) || launch_limbs(xd, 1, d, xl, g_flags, g_stream) != cudaSuccess)
         { cudaGetLastError(); return 1; }
     bool ok = linear_dev(wq, xd, 1, fw, qkv, false, g_stream, xl) && linear_dev(wk, xd, 1, fw, qkv + qd, false, g_stream, xl) &&
               linear_dev(wv, xd, 1, fw, qkv + qd + kd, false, g_stream, xl);
@@ -1206,11 +1202,6 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     if (wqkv.out_f != qd + 2 * kd || wo.nb * 256 != qd || wo.out_f != d || g_hl_d != d) return 1;   // g_hl_d: the digit planes on hand
     if (!fast_envelope(wqkv.qtype, wqkv.nb, wqkv.maxd, wqkv.maxdmin, fw) || !fast_envelope(wo.qtype, wo.nb, wo.maxd, wo.maxdmin, fw)) return 3;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool side = g_overlap != 0;
-    if (side) {                                            // after the routing kernel of this block, beside its expert kernels
-        s = g_side;
-        if (cudaStreamWaitEvent(s, g_ev_route, 0) != cudaSuccess) { cudaGetLastError(); return 1; }
-    }
     const int8_t *hl = (const int8_t *)g_buf[R_XL].p;
     int64_t *qkv = (int64_t *)ensure(R_TMP0, (size_t)(qd + 2 * kd) * 8);
     int8_t *al = (int8_t *)ensure(R_TMP1, (size_t)8 * qd);
@@ -1218,7 +1209,7 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     StreamArgs sa = {};
     sa.wa = wqkv.cell; sa.wb = wqkv.cell; sa.n_sel = 1; sa.out_f = wqkv.out_f; sa.n_blocks = wqkv.nb; sa.fw = fw; sa.fa = fa;
     sa.xl = hl; sa.x_per_sel = 0; sa.x_nl = g_cells; sa.out = qkv; sa.flags = g_flags;
-    sa.fast = small_scales(wqkv.maxd, wqkv.maxdmin, fw); sa.pdl = side ? 0 : g_pdl; sa.early_weights = sa.pdl;   // fixed weight pointer: request before the wait
+    sa.fast = small_scales(wqkv.maxd, wqkv.maxdmin, fw); sa.pdl = g_pdl; sa.early_weights = sa.pdl;   // fixed weight pointer: request before the wait
     if (launch_stream(wqkv.qtype, MODE_LINEAR, sa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     AttnArgs a = {};
     a.q = qkv; a.k = qkv + qd; a.v = qkv + qd + kd; a.kcache = kcache_dev; a.vcache = vcache_dev; a.pos = pos;
@@ -1226,9 +1217,9 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim;
     attn_consts(a, fa, inv_sqrt);
     if (!attn_scratch(a, s)) return 1;
-    int *nl_cell = g_cells + 8 + g_attn_parity, *nl_next = g_cells + 8 + (g_attn_parity ^ 1);   // alternate between calls
+    int *nl_cell = g_cells + 8 + g_attn_parity;              // alternate between calls
     g_attn_parity ^= 1;
-    a.out = nullptr; a.out_limbs = al; a.out_nl = nl_cell; a.out_nl_next = nl_next; a.flags = g_flags; a.pdl = g_pdl;
+    a.out = nullptr; a.out_limbs = al; a.out_nl = nl_cell; a.flags = g_flags; a.pdl = g_pdl;
     if (launch_attn_decode(a, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     // O product accumulated into the residual row: the "down" form of the streaming kernel with a unit gate
     StreamArgs oa = {};
@@ -1236,30 +1227,7 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     oa.xl = al; oa.x_per_sel = 1; oa.x_nl = nl_cell; oa.out = x_dev; oa.gates = g_pow2 + fa; oa.flags = g_flags;
     oa.fast = small_scales(wo.maxd, wo.maxdmin, fw); oa.pdl = g_pdl; oa.early_weights = g_pdl;
     if (launch_stream(wo.qtype, MODE_DOWN, oa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
-    if (side) {
-        if (cudaEventRecord(g_ev_attn, s) != cudaSuccess) { cudaGetLastError(); return 1; }
-        g_attn_pending = true;
-    }
     return 0;
-}
-
-extern "C" int iie_set_block_overlap(int on) {
-    std::lock_guard<std::recursive_mutex> lk(g_mu);
-    if (!init()) return 1;
-    if (on && !g_side) {
-        if (cudaStreamCreateWithFlags(&g_side, cudaStreamNonBlocking) != cudaSuccess ||
-            cudaEventCreateWithFlags(&g_ev_route, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventCreateWithFlags(&g_ev_attn, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); return 1; }
-    }
-    g_overlap = on ? 1 : 0;
-    return 0;
-}
-
-extern "C" int iie_join_block_overlap(void *stream) {
-    std::lock_guard<std::recursive_mutex> lk(g_mu);
-    if (!g_attn_pending) return 0;
-    g_attn_pending = false;
-    return cudaStreamWaitEvent((cudaStream_t)stream, g_ev_attn, 0) == cudaSuccess ? 0 : 1;
 }
 
 extern "C" int iie_embed_dev(long long h, const int *token_dev, long long token, int frac, int64_t *out_dev, void *stream) {
@@ -1308,26 +1276,9 @@ extern "C" void iie_set_tc_min_tokens(long long tokens) {
     g_tc_min_tokens = tokens < 2 ? 2 : tokens;
 }
 
-extern "C" void iie_set_batch_stream(int enabled) {
-    std::lock_guard<std::recursive_mutex> lk(g_mu);
-    g_batch_stream = enabled ? 1 : 0;
-}
-
 extern "C" void iie_set_attn_fused(int enabled) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
-    iie::g_attn_fused = enabled < 0 ? 0 : (enabled > 2 ? 2 : enabled);
-}
-
-extern "C" void iie_set_fused_route(int enabled) {
-    std::lock_guard<std::recursive_mutex> lk(g_mu);
-    g_fused_route = enabled ? 1 : 0;
-}
-
-extern "C" int iie_expert_clusters(void) { return iie::g_expert_clusters < 0 ? -1 : iie::g_expert_cluster_size * 1000 + iie::g_expert_clusters; }
-
-extern "C" void iie_set_fused_expert(int enabled) {
-    std::lock_guard<std::recursive_mutex> lk(g_mu);
-    g_fused_expert = enabled ? 1 : 0;
+    iie::g_attn_fused = enabled ? 1 : 0;
 }
 
 extern "C" void iie_set_pdl(int enabled) {
@@ -1338,6 +1289,17 @@ extern "C" void iie_set_pdl(int enabled) {
 extern "C" void iie_profile_stage_mask(int mask) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     g_stage_mask = mask;
+}
+
+extern "C" unsigned long long iie_workspace_generation(void) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    return g_ws_generation;
+}
+
+extern "C" int iie_prefill_launch_counts(unsigned long long *out, int capacity) {
+    if (!out || capacity < iie::PF_SHAPES) return -1;
+    for (int i = 0; i < iie::PF_SHAPES; i++) out[i] = __atomic_load_n(&iie::g_prefill_launches[i], __ATOMIC_RELAXED);
+    return iie::PF_SHAPES;
 }
 
 extern "C" unsigned long long iie_launch_count(void) { return __atomic_load_n(&iie::g_launches, __ATOMIC_RELAXED); }

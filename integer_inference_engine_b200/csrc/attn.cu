@@ -29,8 +29,7 @@ namespace cg = cooperative_groups;
 
 namespace iie {
 
-int g_attn_fused = 1;                      // 1: one cooperative launch when every CTA fits on the device (fastest measured),
-                                           // 2: one cluster per KV head when the shape allows, 0: always three launches
+int g_attn_fused = 1;                      // 1: one cooperative launch when every CTA fits on the device, 0: always three launches
 
 namespace {
 
@@ -38,9 +37,15 @@ constexpr int AT_CH = 64;                   // keys per CTA
 constexpr int AT_MAXREP = 16;               // query heads per KV head
 
 // position of the new token and first visible key: from the device cell when the caller replays a captured graph
-__device__ __forceinline__ void at_span(const AttnArgs &a, long long &pos, long long &lo) {
+// Returns false (uniformly over the grid) when the device cell holds a position beyond the host bound the grids were
+// sized for, or beyond the cache rows: the kernel then raises flag bit 4 and returns without touching the cache.
+__device__ __forceinline__ bool at_span(const AttnArgs &a, long long &pos, long long &lo) {
     pos = a.pos_dev ? (long long)*a.pos_dev : a.pos;
     lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    return !(a.pos_dev && (pos < 0 || pos > a.pos || pos >= a.Lmax));
+}
+__device__ __forceinline__ void at_refuse(const AttnArgs &a) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) atomicOr(a.flags, 16);
 }
 
 // prefill: blockIdx.z is the token; shift the position and every per-token pointer to it
@@ -76,22 +81,6 @@ __device__ __forceinline__ void at_stage(const int4 *src, int n, int tid, int nt
     }
 }
 
-__device__ __forceinline__ void at_bulk(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes), "r"(b) : "memory");
-}
-__device__ __forceinline__ bool at_wait(uint64_t *bar) {                    // bounded: false if the bytes never arrived
-    for (unsigned it = 0; it < (1u << 22); it++) {
-        uint32_t ok;
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n selp.u32 %0, 1, 0, p;\n}"
-                     : "=r"(ok) : "r"((uint32_t)__cvta_generic_to_shared(bar)) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-
 __global__ void attn_reset_kernel(long long *hmax, unsigned long long *Z, long long *acc, unsigned *ticket, int H, int hd) {
     for (int i = threadIdx.x; i < H; i += blockDim.x) { hmax[i] = INT64_MIN; Z[i] = 0ULL; }
     for (int i = threadIdx.x; i < H * hd; i += blockDim.x) acc[i] = 0;
@@ -104,7 +93,7 @@ __global__ void attn_reset_kernel(long long *hmax, unsigned long long *Z, long l
 // value to the cache first.
 __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
-    at_span(a_in, a.pos, a.lo);
+    if (!at_span(a_in, a.pos, a.lo)) { at_refuse(a_in); return; }
     at_batch(a);
     const long long Ls = a.Ls ? a.Ls : a.Lmax;
     extern __shared__ __align__(16) long long at_q[];     // [rep][hd] int64, then [rep][hd] int32, then the key chunk
@@ -198,7 +187,7 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnArgs a_in) {
 // pass 2: exponentials and their sum
 __global__ void __launch_bounds__(256) attn_exp_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
-    at_span(a_in, a.pos, a.lo);
+    if (!at_span(a_in, a.pos, a.lo)) { at_refuse(a_in); return; }
     at_batch(a);
     const long long Ls = a.Ls ? a.Ls : a.Lmax;
     __shared__ unsigned long long s_sum[8];
@@ -227,7 +216,7 @@ __global__ void __launch_bounds__(256) attn_exp_kernel(const AttnArgs a_in) {
 // result (and, on request, its digit planes) and returns the shared statistics to their initial state.
 __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
-    at_span(a_in, a.pos, a.lo);
+    if (!at_span(a_in, a.pos, a.lo)) { at_refuse(a_in); return; }
     const long long Ls = a.Ls ? a.Ls : a.Lmax;
     extern __shared__ __align__(16) int32_t at_v[];        // [AT_CH][hd] values, then [AT_CH][AT_MAXREP] probabilities
     __shared__ int s_last, s_nl;
@@ -383,7 +372,7 @@ __global__ void __launch_bounds__(256) attn_pv_rows_kernel(const AttnArgs a_in) 
 // its latency is hidden behind the first two passes, and nothing but the statistics goes through global memory.
 __global__ void __launch_bounds__(256) attn_fused_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
-    at_span(a_in, a.pos, a.lo);
+    if (!at_span(a_in, a.pos, a.lo)) { at_refuse(a_in); return; }
     cg::grid_group grid = cg::this_grid();
     extern __shared__ __align__(16) long long at_q[];     // q int64 [rep][hd], q int32 [rep][hd], keys [CH][hd+4], values [CH][hd], p [CH][MAXREP]
     __shared__ long long s_max[AT_MAXREP];
@@ -537,7 +526,9 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const AttnArgs a_in) {
     const int sub = (int)(gid & 15);
     int nl = 1;
     bool over = false;
-    for (long long o = gid >> 4; o < n + 15; o += n_groups) {                // +15: whole 16-lane groups stay together for the shuffles
+    // n and n_groups are even and a warp holds the two outputs 2w, 2w + 1: the bound on the even one keeps the trip count
+    // uniform over the warp, as the full-mask shuffles below require
+    for (long long o = gid >> 4; (o & ~1LL) < n; o += n_groups) {
         long long sum = 0;
         if (o < n) {
             const int h = (int)(o / a.hd), dd = (int)(o - (long long)h * a.hd), kvh = h / rep, r = h - kvh * rep;
@@ -561,247 +552,6 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const AttnArgs a_in) {
     }
     if (over) atomicOr(a.flags, 1);
     if (a.out_limbs && a.out_nl && nl > 1) atomicMax(a.out_nl, nl);
-}
-
-// One thread-block CLUSTER per KV head (16 CTAs): the row maximum, the normaliser and the partial sums of a KV
-// head only concern that head's keys, so the three dependencies are resolved with hardware cluster barriers and
-// distributed shared memory instead of grid-wide barriers.  CTA r of a cluster owns the 64-key chunks r, r+16, ...
-// (at most AT_NC of them): all of its key chunks are requested at once, the value chunks follow into the same
-// buffers with cp.async while the maximum and the normaliser are exchanged, and the partial sums [rep][hd] of the
-// 16 CTAs are reduce-scattered through remote shared-memory loads.  For rep <= 8 query heads per KV head.
-constexpr int AT_CS = 16, AT_NC = 5;
-
-__global__ void __launch_bounds__(256, 1) attn_cluster_kernel(const AttnArgs a_in) {
-    AttnArgs a = a_in;
-    at_span(a_in, a.pos, a.lo);
-    cg::cluster_group cluster = cg::this_cluster();
-    extern __shared__ __align__(16) long long at_q[];     // q int64 [rep][hd], q int32, part [rep][hd], xmax/xz [16][8], keys/values [NC][CH][hd+4], p [NC][CH][8]
-    __shared__ long long s_max[8];
-    __shared__ unsigned long long s_z[8];
-    __shared__ int s_wide, s_timeout;
-    __shared__ __align__(8) uint64_t kbar[AT_NC], vbar[AT_NC];
-    const int rank = (int)cluster.block_rank(), kv = blockIdx.x / AT_CS, rep = a.H / a.Hkv;
-    const int tid = threadIdx.x, lane = tid & 31, half = a.hd / 2, ld = a.hd;     // unpadded rows: one bulk copy per chunk
-    const int used = (int)((a.pos - a.lo) / AT_CH) + 1;                       // chunks that hold keys
-    int32_t *q32 = reinterpret_cast<int32_t *>(at_q + rep * a.hd);
-    long long *part = reinterpret_cast<long long *>(q32 + rep * a.hd);
-    long long *xmax = part + rep * a.hd;
-    unsigned long long *xz = reinterpret_cast<unsigned long long *>(xmax + AT_CS * 8);
-    int32_t *buf = reinterpret_cast<int32_t *>(xz + AT_CS * 8);
-    int32_t *s_p = buf + AT_NC * AT_CH * ld;
-    if (tid == 0) {
-        s_wide = 0; s_timeout = 0;
-        for (int i = 0; i < AT_NC; i++) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&kbar[i])));
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&vbar[i])));
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (tid < 8) { s_max[tid] = INT64_MIN; s_z[tid] = 0ULL; }
-    __syncthreads();
-    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");     // "this CTA runs": waited for before the first push
-    if (a.pdl) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
-    bool wide = false;
-    for (int idx = tid; idx < rep * half; idx += blockDim.x) {
-        const int r = idx / half, i = idx - r * half;
-        const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
-        const int64_t *src = a.q + (long long)(kv * rep + r) * a.hd;
-        int64_t x0 = src[i0], x1 = src[i1];
-        at_rotate(a, a.pos, i, x0, x1);
-        at_q[r * a.hd + i0] = x0; at_q[r * a.hd + i1] = x1;
-        q32[r * a.hd + i0] = (int32_t)x0; q32[r * a.hd + i1] = (int32_t)x1;
-        wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
-    }
-    if (wide) s_wide = 1;
-    const int pos_chunk = (int)((a.pos - a.lo) / AT_CH);
-    if (pos_chunk % AT_CS == rank) {                        // this CTA owns the chunk of the new token: append its cache row
-        bool bad = false;
-        for (int i = tid; i < half; i += blockDim.x) {
-            const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
-            int64_t x0 = a.k[kv * a.hd + i0], x1 = a.k[kv * a.hd + i1];
-            at_rotate(a, a.pos, i, x0, x1);
-            bad |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
-            int32_t *dst = a.kcache + ((long long)kv * a.Lmax + a.pos) * a.hd;
-            dst[i0] = (int32_t)x0; dst[i1] = (int32_t)x1;
-        }
-        for (int i = tid; i < a.hd; i += blockDim.x) {
-            const int64_t v = a.v[kv * a.hd + i];
-            bad |= v != (int32_t)v;
-            a.vcache[((long long)kv * a.Lmax + a.pos) * a.hd + i] = (int32_t)v;
-        }
-        if (bad) atomicOr(a.flags, 4);
-    }
-    if (blockIdx.x == 0 && tid == 0 && a.out_nl_next) *a.out_nl_next = 0;      // the cell the NEXT call will use
-    __syncthreads();
-    // ---- all key chunks of this CTA: one bulk copy each -----------------------------------------------------------------------
-    int nk[AT_NC];
-#pragma unroll
-    for (int i = 0; i < AT_NC; i++) {
-        const int c = rank + i * AT_CS;
-        const long long l0 = a.lo + (long long)c * AT_CH;
-        nk[i] = c < used ? (int)min((long long)AT_CH, a.pos + 1 - l0) : 0;
-        if (tid == 0 && nk[i] > 0) at_bulk(buf + i * AT_CH * ld, a.kcache + ((long long)kv * a.Lmax + l0) * a.hd, (uint32_t)(nk[i] * a.hd * 4), &kbar[i]);
-    }
-    // ---- pass 1: thread -> (key, head group of two heads) -----------------------------------------------------------------
-    const int key = tid & (AT_CH - 1), hg = tid / AT_CH, r0 = 2 * hg;      // 4 groups x 2 heads = up to 8 heads
-    const bool two = r0 + 1 < rep, any = r0 < rep, use_wide = s_wide != 0;
-    long long sc0[AT_NC], sc1[AT_NC];
-#pragma unroll
-    for (int i = 0; i < AT_NC; i++) {
-        sc0[i] = INT64_MIN; sc1[i] = INT64_MIN;
-        if (nk[i] > 0 && !at_wait(&kbar[i])) { s_timeout = 1; continue; }
-        if (any && key < nk[i]) {
-            const int32_t *kk = buf + (i * AT_CH + key) * ld;
-            long long d0 = 0, d1 = 0;
-            if (!use_wide) {
-                const int32_t *qa = q32 + r0 * a.hd, *qb = q32 + (two ? r0 + 1 : r0) * a.hd;
-                for (int j0 = 0; j0 < a.hd; j0 += 4) {
-                    const int j = (j0 + 4 * key) & (a.hd - 1);    // each key starts at its own column: unpadded rows, no bank conflicts
-                    const int4 k4 = *reinterpret_cast<const int4 *>(kk + j);
-                    const int4 a4 = *reinterpret_cast<const int4 *>(qa + j), b4 = *reinterpret_cast<const int4 *>(qb + j);
-                    d0 += (long long)a4.x * k4.x; d0 += (long long)a4.y * k4.y; d0 += (long long)a4.z * k4.z; d0 += (long long)a4.w * k4.w;
-                    d1 += (long long)b4.x * k4.x; d1 += (long long)b4.y * k4.y; d1 += (long long)b4.z * k4.z; d1 += (long long)b4.w * k4.w;
-                }
-            } else {
-                const long long *qa = at_q + r0 * a.hd, *qb = at_q + (two ? r0 + 1 : r0) * a.hd;
-                for (int j0 = 0; j0 < a.hd; j0++) { const int j = (j0 + key) & (a.hd - 1); const long long kj = kk[j]; d0 += qa[j] * kj; d1 += qb[j] * kj; }
-            }
-            sc0[i] = ((d0 >> a.fa) * a.inv_sqrt) >> a.fa;
-            if (two) sc1[i] = ((d1 >> a.fa) * a.inv_sqrt) >> a.fa;
-        }
-    }
-    {
-        long long m0 = INT64_MIN, m1 = INT64_MIN;
-#pragma unroll
-        for (int i = 0; i < AT_NC; i++) { m0 = max(m0, sc0[i]); m1 = max(m1, sc1[i]); }
-#pragma unroll
-        for (int s2 = 16; s2 > 0; s2 >>= 1) { m0 = max(m0, __shfl_xor_sync(0xffffffffu, m0, s2)); m1 = max(m1, __shfl_xor_sync(0xffffffffu, m1, s2)); }
-        if (lane == 0 && any) { if (m0 != INT64_MIN) atomicMax(&s_max[r0], m0); if (two && m1 != INT64_MIN) atomicMax(&s_max[r0 + 1], m1); }
-    }
-    __syncthreads();                                         // every score is in registers: the buffers are free
-    // value chunks into the same buffers (bulk copies, waited for before pass 3)
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < AT_NC; i++) {
-        if (tid == 0 && nk[i] > 0) {
-            const long long l0 = a.lo + (long long)(rank + i * AT_CS) * AT_CH;
-            at_bulk(buf + i * AT_CH * ld, a.vcache + ((long long)kv * a.Lmax + l0) * a.hd, (uint32_t)(nk[i] * a.hd * 4), &vbar[i]);
-        }
-    }
-    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");               // every CTA of the cluster is running
-    if (tid < AT_CS * 8) { const int peer = tid >> 3, r = tid & 7; cluster.map_shared_rank(xmax, peer)[rank * 8 + r] = s_max[r]; }
-    cluster.sync();
-    if (tid < 8) {
-        long long m = INT64_MIN;
-#pragma unroll
-        for (int rk = 0; rk < AT_CS; rk++) m = max(m, xmax[rk * 8 + tid]);
-        s_max[tid] = m;
-    }
-    __syncthreads();
-    // ---- pass 2: exponentials in registers, normaliser --------------------------------------------------------------------
-    unsigned e0[AT_NC], e1[AT_NC];
-    {
-        unsigned long long z0 = 0, z1 = 0;
-        const long long m0 = any ? s_max[r0] : 0, m1 = two ? s_max[r0 + 1] : 0;
-#pragma unroll
-        for (int i = 0; i < AT_NC; i++) {
-            e0[i] = 0; e1[i] = 0;
-            if (any && key < nk[i]) {
-                long long dlt = m0 - sc0[i];
-                dlt = dlt < a.clip ? dlt : a.clip;
-                e0[i] = (unsigned)exp2_neg_fixed((dlt * a.log2e) >> a.fa, a.fa);
-                if (two) {
-                    dlt = m1 - sc1[i];
-                    dlt = dlt < a.clip ? dlt : a.clip;
-                    e1[i] = (unsigned)exp2_neg_fixed((dlt * a.log2e) >> a.fa, a.fa);
-                }
-            }
-            z0 += e0[i]; z1 += e1[i];
-        }
-#pragma unroll
-        for (int s2 = 16; s2 > 0; s2 >>= 1) { z0 += __shfl_xor_sync(0xffffffffu, z0, s2); z1 += __shfl_xor_sync(0xffffffffu, z1, s2); }
-        if (lane == 0 && any) { if (z0) atomicAdd(&s_z[r0], z0); if (two && z1) atomicAdd(&s_z[r0 + 1], z1); }
-    }
-    __syncthreads();
-    if (tid < AT_CS * 8) { const int peer = tid >> 3, r = tid & 7; cluster.map_shared_rank(xz, peer)[rank * 8 + r] = s_z[r]; }
-    cluster.sync();
-    if (tid < 8) {
-        unsigned long long z = 0;
-#pragma unroll
-        for (int rk = 0; rk < AT_CS; rk++) z += xz[rk * 8 + tid];
-        s_z[tid] = z;
-    }
-    __syncthreads();
-    // ---- pass 3: probabilities, then probabilities x values for this CTA's keys -------------------------------------------
-    {
-        const unsigned long long z0 = any ? s_z[r0] : 0, z1 = two ? s_z[r0 + 1] : 0;
-#pragma unroll
-        for (int i = 0; i < AT_NC; i++) {
-            int32_t *pp = s_p + (i * AT_CH + key) * 8;
-            pp[r0] = (any && z0) ? (int32_t)(((unsigned long long)e0[i] << a.fa) / z0) : 0;
-            pp[r0 + 1] = (two && z1) ? (int32_t)(((unsigned long long)e1[i] << a.fa) / z1) : 0;
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < AT_NC; i++) if (nk[i] > 0 && !at_wait(&vbar[i])) s_timeout = 1;
-    __syncthreads();
-    {
-        const int G = blockDim.x / a.hd, grp = tid / a.hd, d = tid - grp * a.hd;      // hd 128: two groups of four heads
-        if (grp < G) {
-            for (int rr = grp * 4; rr < 8; rr += G * 4) {
-                long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
-#pragma unroll
-                for (int i = 0; i < AT_NC; i++) {
-                    for (int j = 0; j < nk[i]; j++) {
-                        const int32_t v = buf[(i * AT_CH + j) * ld + d];
-                        const int4 p4 = *reinterpret_cast<const int4 *>(s_p + (i * AT_CH + j) * 8 + rr);
-                        c0 += (long long)p4.x * v; c1 += (long long)p4.y * v; c2 += (long long)p4.z * v; c3 += (long long)p4.w * v;
-                    }
-                }
-                const long long cs[4] = {c0, c1, c2, c3};
-#pragma unroll
-                for (int u = 0; u < 4; u++) if (rr + u < rep) part[(rr + u) * a.hd + d] = cs[u];
-            }
-        }
-    }
-    cluster.sync();
-    // ---- reduce-scatter of the 16 partials: this CTA finishes rep*hd/16 outputs ---------------------------------------------
-    {
-        const int n_out = rep * a.hd, per = (n_out + AT_CS - 1) / AT_CS;               // 64 for 8 heads x 128
-        const int o_local = tid % per, q4 = tid / per, n_q = blockDim.x / per;        // q4: which peers this thread sums
-        long long sum = 0;
-        const int o = rank * per + o_local;
-        if (q4 < n_q && o < n_out)
-            for (int pr = q4; pr < AT_CS; pr += n_q) sum += cluster.map_shared_rank(part, pr)[o];
-        long long *red = reinterpret_cast<long long *>(s_p);                           // probabilities are no longer needed
-        __syncthreads();
-        if (q4 < n_q) red[q4 * per + o_local] = sum;
-        __syncthreads();
-        int nl = 1;
-        if (tid < per && o < n_out) {
-            long long tot = 0;
-            for (int qq = 0; qq < n_q; qq++) tot += red[qq * per + tid];
-            const long long y = tot >> a.fa;
-            const long long gi = (long long)kv * n_out + o, n = (long long)a.H * a.hd;
-            if (a.out) a.out[gi] = y;
-            if (a.out_limbs) {
-                bool ok;
-                const uint64_t dg = balanced_digits8(y, ok);
-                if (!ok) atomicOr(a.flags, 1);
-                nl = digits_used(dg);
-#pragma unroll
-                for (int l = 0; l < 8; l++) a.out_limbs[l * n + gi] = (int8_t)(dg >> (8 * l));
-            }
-        }
-        if (a.out_limbs && a.out_nl) {
-#pragma unroll
-            for (int s2 = 16; s2 > 0; s2 >>= 1) nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, s2));
-            if (lane == 0 && nl > 1) atomicMax(a.out_nl, nl);
-        }
-    }
-    cluster.sync();                                          // nobody may leave while a peer still reads its partial sums
-    if (s_timeout && tid == 0) atomicOr(a.flags, 8);
 }
 
 // one row of a registered Q4_K / Q6_K matrix as int64 at 2^frac (the embedding look-up)
@@ -914,36 +664,6 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
         if (!coop) n_sms = 0;
         configured = true;
-    }
-    // one cluster per KV head: up to AT_NC chunks per CTA, at most eight query heads per KV head, head_dim <= 128
-    const size_t cl_smem = (size_t)rep * a.hd * 12 + (size_t)rep * a.hd * 8 + (size_t)AT_CS * 8 * 16 +
-                           (size_t)AT_NC * AT_CH * a.hd * 4 + (size_t)AT_NC * AT_CH * 8 * 4;
-    static int cluster_ok = -1;                           // -1 not asked, 0 unavailable, else co-resident clusters
-    if (g_attn_fused >= 2 && rep <= 8 && a.hd <= 128 && 256 % a.hd == 0 && chunks <= AT_CS * AT_NC && cl_smem <= 225 * 1024 &&
-        (size_t)rep * a.hd / AT_CS * 8 * (256 / ((rep * a.hd + AT_CS - 1) / AT_CS)) <= (size_t)AT_NC * AT_CH * 8 * 4) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(a.Hkv * AT_CS)); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = cl_smem; cfg.stream = s;
-        cudaLaunchAttribute attr[2];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = AT_CS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[1].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        if (cluster_ok < 0) {
-            cluster_ok = 0;
-            if (cudaFuncSetAttribute(attn_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024) == cudaSuccess &&
-                cudaFuncSetAttribute(attn_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
-                int n = 0;
-                cfg.numAttrs = 1;
-                if (cudaOccupancyMaxActiveClusters(&n, attn_cluster_kernel, &cfg) == cudaSuccess && n >= 1) cluster_ok = n;
-            }
-            cudaGetLastError();
-        }
-        if (cluster_ok >= 1) {
-            cfg.numAttrs = a.pdl ? 2 : 1;
-            const cudaError_t e = cudaLaunchKernelEx(&cfg, attn_cluster_kernel, a);
-            note_launch(1);
-            return e != cudaSuccess ? e : cudaGetLastError();
-        }
     }
     bool fused = g_attn_fused && a.partial && n_sms > 0 && rep4 <= 256 / AT_CH && fused_smem <= 200 * 1024;
     if (fused) {

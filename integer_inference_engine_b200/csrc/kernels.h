@@ -110,52 +110,6 @@ struct BatchArgs {
 };
 cudaError_t launch_batch(int qtype, int mode, const BatchArgs &a, cudaStream_t s);
 
-// Single-token routing + gate/up in one launch (rgu.cu): every CTA recomputes the routing, then multiplies its
-// run of gate/up tiles of the selected experts.
-struct RoutedGateUpArgs {
-    const int64_t *x;              // [d] input row
-    const int64_t *gain;           // [d] RMSNorm gain, or nullptr (h = x)
-    int d, fa, fw;
-    unsigned long long eps;
-    const uint8_t *router;         // repacked Q4_K router [n_experts, d]
-    int n_experts, k;
-    long long e_ffn;
-    const uint8_t *const *tabs;    // device [3][n_experts]: gate, up, down pointers of the layer
-    int *ids;                      // out [k]
-    int64_t *gates;                // out [k]
-    const uint8_t **sel_down;      // out [k]: down-projection pointers of the selected experts
-    int64_t *init_out;             // nullable: the block's output row, initialised here
-    int init_mode;                 // 0 leave, 1 zero, 2 copy x (residual)
-    int8_t *out_limbs;             // out: digit planes of gu [k][8][e_ffn]
-    int *gu_nl;                    // atomicMax of the digits gu needs (zero on entry)
-    int *gu_nl_next;               // zeroed here: the cell the next block's launch uses
-    int *flags;                    // bit 0 digit envelope, bit 1 RMSNorm envelope, bit 3 a copy never arrived
-    int pdl, fast;
-    int tiles_per_expert, tiles_per_cta;   // filled in by the launcher
-    long long sig_log2e, sig_clip;
-};
-cudaError_t launch_routed_gateup(int qtype, const RoutedGateUpArgs &a, cudaStream_t s);
-
-// Single-token expert stage in one launch (expert.cu): one 16-CTA cluster per selected expert runs gate/up,
-// SiLU * up, down and the gate-weighted combine.
-struct ExpertArgs {
-    const uint8_t *const *sel_ptrs;   // device [3][k]: gate, up, down pointers of the selected experts
-    int k;
-    long long d_model, e_ffn;
-    int fw, fa;
-    long long sig_log2e, sig_clip;    // filled in by the launcher
-    const int8_t *hl;                 // digit planes of the hidden row [8][d_model]
-    const int *h_nl;                  // digits in use by it
-    const int64_t *gates;             // [k]
-    int64_t *out;                     // [d_model], accumulated into
-    int *flags;                       // bit 0 digit envelope, bit 3 a copy never arrived
-    int pdl;                          // 1: launched with programmatic stream serialization
-    int gt, dt, down_early;           // tiles per CTA; down tiles requested up front (filled in by the launcher)
-};
-cudaError_t launch_expert(int gate_q, int down_q, const ExpertArgs &a, cudaStream_t s);
-extern int g_expert_clusters;      // co-resident clusters reported for the expert kernel, -1 before its first launch
-extern int g_expert_cluster_size;  // CTAs per cluster the launcher chose
-
 // Prefill-regime grouped products on tcgen05 (prefill.cu).  Pairs are sorted by expert: expert x owns
 // pairs [grp_off[x], grp_off[x+1]).
 struct PrefillArgs {
@@ -178,6 +132,10 @@ struct PrefillArgs {
     int *flags;
 };
 cudaError_t launch_prefill(int qtype, int mode, int nl, const PrefillArgs &a, cudaStream_t s);
+// launches of each tensor-core tile shape since the library was loaded, in the order: Q4_K gate/up with 3 / 4 activation
+// digits, Q6_K down with 5 / 6, Q4_K down with 5, Q4_K linear with 3 / 5
+constexpr int PF_SHAPES = 7;
+extern unsigned long long g_prefill_launches[PF_SHAPES];
 
 // Re-order raw GGUF blocks into the half-tile layout; also reduces max |d| and max |dmin| half bit
 // patterns (sign stripped) into maxbits[0..1] (device memory, caller zeroes).
@@ -190,6 +148,10 @@ cudaError_t launch_unpack(const uint8_t *src, uint8_t *raw, long long out_f, lon
 // int64 rows -> balanced base-256 limb planes [row][8][K]; sets flags bit 0 on overflow.
 cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, cudaStream_t s,
                          int *nl_out = nullptr);   // nl_out: atomicMax of the limbs in use (caller zeroes)
+
+// p[0] = a, p[1] = b on the stream (kernel arguments travel by value, so a captured launch replays correctly where a
+// copy from a host stack variable would not)
+cudaError_t launch_set2(int *p, int a, int b, cudaStream_t s);
 
 // Exact 128-bit reference-order product for inputs outside the fast envelope: out[pair][o].
 cudaError_t launch_exact_linear(const uint8_t *w, int qtype, long long out_f, long long n_blocks, const int64_t *x,
@@ -244,7 +206,6 @@ struct AttnArgs {
     int64_t *out;                  // [H*hd], nullable
     int8_t *out_limbs;             // nullable: digit planes [8][H*hd] of the result
     int *out_nl;                   // nullable: digits in use by the result
-    int *out_nl_next;              // nullable: zeroed by the cluster form (the cell the next call accumulates into)
     int pdl;                       // 1: the one-launch form is launched with programmatic stream serialization
     int *flags;                    // bit 0 digit envelope, bit 2 a key / value does not fit the int32 cache
     int batch;                     // > 0: that many consecutive new tokens (prefill); q, k, v, out then hold one row per token,
@@ -255,7 +216,7 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s);
 // `batch` new tokens at positions pos .. pos + batch - 1 against the cache rows before them and each other (causal):
 // all K/V rows are appended first, then scores, exponentials and the probability-value sums run per token
 cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s);
-extern int g_attn_fused;           // 2: cluster per KV head, 1: one cooperative launch, 0: three launches (each falls back to the next)
+extern int g_attn_fused;           // 1: one cooperative launch when it fits, 0: three launches
 // hmax = INT64_MIN, Z = acc = ticket = 0: once after the statistics buffer is (re)allocated; every call leaves them so
 cudaError_t launch_attn_reset(long long *hmax, unsigned long long *Z, long long *acc, unsigned *ticket, int H, int hd, cudaStream_t s);
 cudaError_t launch_embed_row(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,

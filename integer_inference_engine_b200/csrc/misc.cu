@@ -404,6 +404,14 @@ cudaError_t launch_unpack(const uint8_t *src, uint8_t *raw, long long out_f, lon
     return cudaGetLastError();
 }
 
+__global__ void set2_kernel(int *p, int a, int b) { p[0] = a; p[1] = b; }
+
+cudaError_t launch_set2(int *p, int a, int b, cudaStream_t s) {
+    set2_kernel<<<1, 1, 0, s>>>(p, a, b);
+    note_launch();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, cudaStream_t s,
                          int *nl_out) {
     limbs_kernel<<<grid_for(n_rows * K, 256), 256, 0, s>>>(x, n_rows, K, planes, flags, nl_out);

@@ -27,6 +27,8 @@
 
 namespace iie {
 
+unsigned long long g_prefill_launches[PF_SHAPES];
+
 namespace {
 
 constexpr int PF_BM = 128, PF_KC = 64, PF_STAGES = 3;
@@ -406,7 +408,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
 }
 
 template <int QT, int MODE, int NL, int NWL, int BN>
-cudaError_t launch_pf(const PrefillArgs &a_in, cudaStream_t s) {
+cudaError_t launch_pf(const PrefillArgs &a_in, cudaStream_t s, int shape) {
+    __atomic_fetch_add(&g_prefill_launches[shape], 1ULL, __ATOMIC_RELAXED);
     PrefillArgs a = a_in;
     constexpr int A_PLANE = 2 * 2 * (PF_BM / 8) * 128, B_PLANE = 2 * 2 * (BN / 8) * 128;
     constexpr size_t smem = (size_t)PF_STAGES * (NL * A_PLANE + NWL * B_PLANE) + 1024;
@@ -432,19 +435,19 @@ cudaError_t launch_pf(const PrefillArgs &a_in, cudaStream_t s) {
 cudaError_t launch_prefill(int qtype, int mode, int nl, const PrefillArgs &a, cudaStream_t s) {
     if (a.n_blocks <= 0 || a.n_blocks * 256 > 8192 || a.out_f <= 0 || a.n_pairs <= 0) return cudaErrorInvalidValue;
     if (qtype == QT_Q4K && mode == MODE_GATEUP) {
-        if (nl <= 3) return launch_pf<QT_Q4K, MODE_GATEUP, 3, 4, 64>(a, s);
-        if (nl == 4) return launch_pf<QT_Q4K, MODE_GATEUP, 4, 4, 64>(a, s);
+        if (nl <= 3) return launch_pf<QT_Q4K, MODE_GATEUP, 3, 4, 64>(a, s, 0);
+        if (nl == 4) return launch_pf<QT_Q4K, MODE_GATEUP, 4, 4, 64>(a, s, 1);
     }
     if (qtype == QT_Q6K && mode == MODE_DOWN) {
-        if (nl <= 5) return launch_pf<QT_Q6K, MODE_DOWN, 5, 5, 32>(a, s);
-        if (nl == 6) return launch_pf<QT_Q6K, MODE_DOWN, 6, 5, 32>(a, s);
+        if (nl <= 5) return launch_pf<QT_Q6K, MODE_DOWN, 5, 5, 32>(a, s, 2);
+        if (nl == 6) return launch_pf<QT_Q6K, MODE_DOWN, 6, 5, 32>(a, s, 3);
     }
     if (qtype == QT_Q4K && mode == MODE_DOWN) {
-        if (nl <= 5) return launch_pf<QT_Q4K, MODE_DOWN, 5, 4, 64>(a, s);
+        if (nl <= 5) return launch_pf<QT_Q4K, MODE_DOWN, 5, 4, 64>(a, s, 4);
     }
     if (qtype == QT_Q4K && mode == MODE_LINEAR) {
-        if (nl <= 3) return launch_pf<QT_Q4K, MODE_LINEAR, 3, 4, 64>(a, s);
-        if (nl <= 5) return launch_pf<QT_Q4K, MODE_LINEAR, 5, 4, 64>(a, s);
+        if (nl <= 3) return launch_pf<QT_Q4K, MODE_LINEAR, 3, 4, 64>(a, s, 5);
+        if (nl <= 5) return launch_pf<QT_Q4K, MODE_LINEAR, 5, 4, 64>(a, s, 6);
     }
     return cudaErrorNotSupported;
 }

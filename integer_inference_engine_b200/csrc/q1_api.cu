@@ -33,6 +33,7 @@ int q_ready = -1;
 
 enum QRole { QR_X, QR_PLANES, QR_TOTALS, QR_OUT, QR_GAIN, QR_COUNT };
 struct QBuf { void *p = nullptr; size_t cap = 0; };
+unsigned long long q_generation = 0;   // changes whenever a scratch buffer is freed: captured graphs hold the old addresses
 QBuf q_buf[QR_COUNT];
 
 thread_local int q_err_code = 0;
@@ -64,7 +65,7 @@ bool q_init() {
 void *q_ensure(int role, size_t bytes) {
     QBuf &b = q_buf[role];
     if (b.p && b.cap >= bytes) return b.p;
-    if (b.p) { cudaDeviceSynchronize(); cudaFree(b.p); b.p = nullptr; b.cap = 0; }
+    if (b.p) { cudaDeviceSynchronize(); cudaFree(b.p); b.p = nullptr; b.cap = 0; q_generation++; }
     const size_t cap = std::max<size_t>(bytes, 256);
     if (cudaMalloc(&b.p, cap) != cudaSuccess) { cudaGetLastError(); b.p = nullptr; return nullptr; }
     b.cap = cap;
@@ -229,7 +230,7 @@ extern "C" void bonsai_q1_free_weights(void) {
     for (auto &w : q_w) if (w.live && w.units) cudaFree(w.units);
     q_w.clear();
     q_weight_bytes = 0;
-    for (auto &b : q_buf) if (b.p) { cudaFree(b.p); b.p = nullptr; b.cap = 0; }
+    for (auto &b : q_buf) if (b.p) { cudaFree(b.p); b.p = nullptr; b.cap = 0; q_generation++; }
 }
 
 extern "C" int bonsai_rmsnorm_gpu(const long long *x, long long rows, long long cols, long long frac, long long eps,
@@ -299,6 +300,7 @@ extern "C" int iie_q1_head_norm_dev(const int64_t *x_dev, long long rows_a, long
                                     (cudaStream_t)stream) == cudaSuccess ? 0 : 2;
 }
 
+extern "C" unsigned long long iie_q1_workspace_generation(void) { return q_generation; }
 extern "C" void iie_q1_set_stream(int on) { iie::set_q1_stream(on); }
 
 extern "C" int iie_q1_silu_mul_dev(const int64_t *gate_dev, const int64_t *up_dev, long long n, long long frac, int64_t *out_dev,

@@ -17,14 +17,6 @@ namespace cg = cooperative_groups;
 
 namespace iie {
 
-#ifdef IIE_TRACE
-__device__ unsigned long long g_rtrace[16 * 16];
-__device__ __forceinline__ unsigned long long rt_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define RTRACE(slot) do { if (threadIdx.x == 0 && blockIdx.x < 16) g_rtrace[blockIdx.x * 16 + (slot)] = rt_gtime(); } while (0)
-#else
-#define RTRACE(slot) do {} while (0)
-#endif
-
 namespace {
 
 constexpr int RT_THREADS = 256;
@@ -87,7 +79,6 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
     __shared__ int64_t s_logits[1024];
     __shared__ __align__(8) uint64_t s_bar;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    RTRACE(0);
 
     // ---- before the dependency wait: everything that reads only immutable data ---------------------------
     const long long n_ht = ((long long)a.n_experts + 7) >> 3;
@@ -115,7 +106,6 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
         }
     if (a.pdl) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
 
-    RTRACE(1);
     // ---- stage x, sum of squares and magnitudes -------------------------------------------------------
     {
         u128 ssq = 0; unsigned long long mx = 0;
@@ -158,7 +148,6 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
     __syncthreads();
     if (s_bad) { if (tid == 0 && blockIdx.x == 0) atomicOr(a.flags, 2); return; }   // uniform over the grid
 
-    RTRACE(2);
     // ---- normalise, apply the gain, split into limb planes (four consecutive elements per step) ------------
     const unsigned long long rms = s_rms, inv = s_inv, gm = s_gm;
     bool bad = false, over = false;
@@ -210,7 +199,6 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
     if (blockIdx.x == 0 && tid == 0) { *a.h_nl = s_nl; if (a.gu_nl) *a.gu_nl = 0; }
     const bool half = s_nl <= 4;
 
-    RTRACE(3);
     // ---- router rows of this CTA: one 16-row tile, K split over the warps ------------------------------
     const int g = lane >> 2, t = lane & 3;
     int64_t acc[4] = {0, 0, 0, 0};
@@ -238,7 +226,6 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
     __syncthreads();
     if (s_timeout && tid == 0) atomicOr(a.flags, 8);
 
-    RTRACE(4);
     const int64_t log2e = sigmoid_log2e(a.fa), clip = sigmoid_clip(a.fa);
     const int n = a.n_experts;
     if (CLUSTER) {
@@ -254,7 +241,6 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
             }
         }
         cluster.sync();
-        RTRACE(5);
         const int el = tid >> 4, part = tid & 15;
         const long long row = (el < 8 ? htA : htB) * 8 + (el & 7);
         const bool live = row < n && (el < 8 || htB != htA);
@@ -285,7 +271,6 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
         __threadfence();
         for (int i = tid; i < n; i += RT_THREADS) s_logits[i] = *((volatile int64_t *)&a.logits[i]);
         __syncthreads();
-        RTRACE(5);
         for (int e = tid; e < n; e += RT_THREADS) {
             const int64_t v = s_logits[e];
             const int rank = rank_part(s_logits, e, v, 0, n);
@@ -296,7 +281,6 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
             }
         }
     }
-    RTRACE(6);
 }
 
 }  // namespace
@@ -339,11 +323,4 @@ cudaError_t launch_route(const RouteArgs &a, cudaStream_t s) {
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-#ifdef IIE_TRACE
-}  // namespace iie
-extern "C" int iie_rtrace_read(unsigned long long *out) {
-    return cudaMemcpyFromSymbol(out, iie::g_rtrace, sizeof(unsigned long long) * 256) == cudaSuccess ? 0 : 1;
-}
-namespace iie {
-#endif
 }  // namespace iie

@@ -26,22 +26,6 @@ namespace {
 
 constexpr int NWARPS = 16;
 
-// Optional phase timestamps (compile with -DIIE_TRACE): per CTA, %globaltimer at kernel entry, after the
-// copies were issued, when the first / last tile had arrived, after the last item and at exit.
-#ifdef IIE_TRACE
-__device__ unsigned long long g_trace[256 * 8];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-__device__ unsigned long long g_trace2[16 * 8 * 8];
-#define TRACE_ITEM(k, pt) do { if (lane == 0 && blockIdx.x == 3 && (k) < 8) g_trace2[(warp * 8 + (k)) * 8 + (pt)] = gtime(); } while (0)
-#define TRACE(slot) do { if (threadIdx.x == 0 && blockIdx.x < 256) g_trace[blockIdx.x * 8 + (slot)] = gtime(); } while (0)
-#define TRACE_ANY(slot) do { if (lane == 0 && blockIdx.x < 256) atomicMax(&g_trace[blockIdx.x * 8 + (slot)], gtime()); } while (0)
-#define TRACE_MIN(slot) do { if (lane == 0 && blockIdx.x < 256) atomicMin(&g_trace[blockIdx.x * 8 + (slot)], gtime()); } while (0)
-#else
-#define TRACE_ITEM(k, pt) do {} while (0)
-#define TRACE(slot) do {} while (0)
-#define TRACE_ANY(slot) do {} while (0)
-#define TRACE_MIN(slot) do {} while (0)
-#endif
 constexpr unsigned WAIT_LIMIT = 1u << 22;   // mbarrier polls before a wait gives up and raises flag bit 3
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -84,10 +68,6 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
     int *t_sel = done + tpc, *t_pos = t_sel + tpc;               // tile -> (selected matrix slot, tile inside it)
     __shared__ int s_timeout;
 
-    TRACE(0);
-#ifdef IIE_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 256) { g_trace[blockIdx.x * 8 + 2] = ~0ULL; g_trace[blockIdx.x * 8 + 3] = 0; g_trace[blockIdx.x * 8 + 4] = 0; g_trace[blockIdx.x * 8 + 6] = 0; }
-#endif
     const int n_tiles = a.n_sel * a.tiles_per_expert;
     const int tile0 = (int)blockIdx.x * tpc;
     const int my_tiles = min(tpc, n_tiles - tile0);
@@ -126,7 +106,6 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
         }
     }
     if (a.pdl && a.early_weights) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
-    TRACE(1);
     const bool half = a.x_nl ? (*a.x_nl <= 4) : false;
 
     // items (tile, block) are dealt round-robin to the warps; indices advance without divisions
@@ -138,9 +117,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
     uint32_t bf[16];
     const int8_t *xcur = nullptr;
     int bcur = -1;
-    int item_no = 0;
-    for (int it = warp; it < n_items; it += NWARPS, item_no++) {
-        TRACE_ITEM(item_no, 0);
+    for (int it = warp; it < n_items; it += NWARPS) {
         const int s = t_sel[ti], p = t_pos[ti];
         const int8_t *xp = a.xl + (a.x_per_sel ? (long long)s * 8 * K : 0);
         if (xp != xcur || b != bcur) {                        // activation fragments: reused while (vector, block) repeat
@@ -154,13 +131,9 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
         const int ti_now = ti;
         b += step_b; ti += step_t;
         if (b >= nb) { b -= nb; ti++; }
-        TRACE_ITEM(item_no, 1);
         if (!mbar_wait(&bars[ti_now], 0)) { s_timeout = 1; continue; }
-        TRACE_ITEM(item_no, 2);
-        TRACE_MIN(2); TRACE_ANY(3);
         int64_t acc[4] = {0, 0, 0, 0};
         run_item<QT, FAST>(ua, ub, lane, a.fw, bf, half, acc);
-        TRACE_ITEM(item_no, 3);
         unsigned long long *r = red + (size_t)ti_now * 128;
         atomicAdd(&r[g * 8 + 2 * t], (unsigned long long)acc[0]);
         atomicAdd(&r[(g + 8) * 8 + 2 * t], (unsigned long long)acc[2]);
@@ -168,8 +141,6 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
             atomicAdd(&r[g * 8 + 2 * t + 1], (unsigned long long)acc[1]);
             atomicAdd(&r[(g + 8) * 8 + 2 * t + 1], (unsigned long long)acc[3]);
         }
-        TRACE_ANY(4);
-        TRACE_ITEM(item_no, 4);
         if (MODE == MODE_GATEUP) continue;                    // its epilogue is long: all rows run it in parallel below
         // the warp that completes a tile (all nb blocks added) runs its epilogue; nobody waits
         __threadfence_block();
@@ -218,24 +189,9 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
         nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 1));
         if (lane == 0 && nl > 0 && a.out_nl) atomicMax(a.out_nl, nl);
     }
-    TRACE_ANY(6);
     __syncthreads();
-    TRACE(5);
     if (s_timeout && threadIdx.x == 0) atomicOr(a.flags, 8);
 }
-
-#ifdef IIE_TRACE
-}  // namespace
-}  // namespace iie
-extern "C" int iie_trace2_read(unsigned long long *out) {
-    return cudaMemcpyFromSymbol(out, iie::g_trace2, sizeof(unsigned long long) * 16 * 8 * 8) == cudaSuccess ? 0 : 1;
-}
-extern "C" int iie_trace_read(unsigned long long *out, int n) {
-    return cudaMemcpyFromSymbol(out, iie::g_trace, sizeof(unsigned long long) * (n < 2048 ? n : 2048)) == cudaSuccess ? 0 : 1;
-}
-namespace iie {
-namespace {
-#endif
 
 template <int QT, int MODE, bool FAST>
 cudaError_t launch_stream_t(const StreamArgs &a_in, cudaStream_t s) {

@@ -106,20 +106,6 @@ def attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kcache: 
     return out
 
 
-def set_block_overlap(on: bool) -> None:
-    """Run the attention half of a decoder block beside the expert kernels of the same block (see
-    ``iie_set_block_overlap``); :func:`join_block_overlap` must follow the last block of a step."""
-    with _CUDA_LOCK:
-        if qk_cuda._lib().iie_set_block_overlap(1 if on else 0) != 0:
-            raise CudaContextError("block overlap could not be switched")
-
-
-def join_block_overlap() -> None:
-    with _CUDA_LOCK:
-        if qk_cuda._lib().iie_join_block_overlap(_stream_ptr()) != 0:
-            raise CudaContextError("joining the attention stream failed")
-
-
 def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, start: int,
                       n_heads: int, n_kv: int, head_dim: int, fa: int = 16, window: int = 0, cos: torch.Tensor | None = None,
                       sin: torch.Tensor | None = None, rope: int = 0, inv_sqrt: int | None = None,
@@ -192,6 +178,20 @@ def argmax(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     if rc != 0:
         raise CudaContextError(f"argmax failed with status {rc}")
     return out
+
+
+def workspace_generation() -> int:
+    """Changes whenever a scratch buffer of the library is freed (regrown or released).  A CUDA graph captured over the
+    device entries holds the addresses of its capture: compare before replaying."""
+    return int(qk_cuda.load_library().iie_workspace_generation())
+
+
+def prefill_launch_counts() -> list:
+    """Launches of each tensor-core tile shape since load: [gate/up 3 digits, gate/up 4, Q6_K down 5, Q6_K down 6,
+    Q4_K down 5, linear 3, linear 5]."""
+    buf = (ctypes.c_uint64 * 8)()
+    n = qk_cuda.load_library().iie_prefill_launch_counts(buf, 8)
+    return [int(buf[i]) for i in range(n)]
 
 
 def launch_count() -> int:

@@ -1,4 +1,4 @@
-"""A whole synthetic decoder of the 30B-A3B shape on one GPU: the decode step the benchmark times.
+"""A whole decoder of the north-mini-code (30B-A3B) shape on one GPU: the decode step the benchmark times.
 
 Per layer the reference's parallel block (north-mini-code/src/nmc/cohere2.py:357-376 block_cached):
 
@@ -8,10 +8,11 @@ Per layer the reference's parallel block (north-mini-code/src/nmc/cohere2.py:357
 then the tied head (cohere2.py:201-204): logits = rmsnorm(x, output_norm) E^T, greedy pick = arg-max with the
 lowest index on ties (engine.py:585), next input = row `token` of E at 2**fa (engine.py:239-243).
 
-Weights are seeded synthetic blocks generated on the device (distributions of ``synth.py``); the KV caches are
-filled with seeded int32 values up to the requested context length, standing in for a prefill.  Everything a
-step needs stays on the device: the sampled token and the position live in device cells, so one captured
-launch sequence serves every step.
+:class:`Decoder` holds registered weights and int32 KV caches and runs steps; :meth:`Decoder.from_raw` builds one from
+raw Q4_K / Q6_K bytes (a checkpoint reader or a test fixture), :class:`SyntheticDecoder` from seeded synthetic blocks
+generated on the device (distributions of ``synth.py``) with the caches filled with seeded int32 values up to the
+requested context, standing in for a prefill.  Everything a step needs stays on the device: the sampled token and the
+position live in device cells, so one captured launch sequence serves every step.
 """
 from __future__ import annotations
 
@@ -34,48 +35,64 @@ def rope_tables(rows: int, head_dim: int, base: float, fa: int):
     return np.rint(np.cos(ang) * (1 << fa)).astype(np.int64), np.rint(np.sin(ang) * (1 << fa)).astype(np.int64)
 
 
-class SyntheticDecoder:
-    def __init__(self, n_layers: int = 48, d_model: int = 2048, n_heads: int = 32, n_kv: int = 4, head_dim: int = 128,
-                 e_ffn: int = 768, n_experts: int = 128, top_k: int = 8, vocab: int = 151936, context: int = 4096,
-                 max_new: int = 160, window: int = 4096, rope_base: float = 50000.0, seed: int = 1, fa: int = 16, fw: int = 24):
-        self.n_layers, self.d, self.H, self.Hkv, self.hd = n_layers, d_model, n_heads, n_kv, head_dim
+class Decoder:
+    """Decode steps over registered weights.  ``attn[i]`` = dict(wqkv, wo handles; k, v int32 CUDA caches
+    [n_kv, rows, head_dim]); ``moe_layers[i]`` / ``gain_handles[i]`` the MoE layer and the block's norm gain."""
+
+    def __init__(self, *, d_model, n_heads, n_kv, head_dim, top_k, vocab, window, fa, fw, attn, moe_layers, gain_handles,
+                 embd, out_gain_h, cos, sin, position):
+        self.d, self.H, self.Hkv, self.hd = d_model, n_heads, n_kv, head_dim
         self.vocab, self.fa, self.fw, self.window, self.top_k = vocab, fa, fw, window, top_k
-        self.rows = context + max_new
-        self.moe = SyntheticMoEStack(n_layers, d_model, e_ffn, n_experts, top_k, seed=seed, fa=fa)
-        nb = d_model // 256
-        self.attn = []
-        for li in range(n_layers):
-            gen = torch.Generator(device="cuda").manual_seed(seed * 7919 + 1000 + li)
-            # Wq, Wk, Wv stacked row-wise into one matrix (rows are independent in the block layout)
-            qkv_rows = (n_heads + 2 * n_kv) * head_dim
-            wqkv = device.register_weight(synth_q4k(qkv_rows * nb, gen).view(-1), qkv_rows, nb, Q4_K)
-            wo = device.register_weight(synth_q4k(d_model * (n_heads * head_dim // 256), gen).view(-1), d_model,
-                                        n_heads * head_dim // 256, Q4_K)
-            kc = torch.randint(-(1 << 18), 1 << 18, (n_kv, self.rows, head_dim), generator=gen, device="cuda", dtype=torch.int32)
-            vc = torch.randint(-(1 << 18), 1 << 18, (n_kv, self.rows, head_dim), generator=gen, device="cuda", dtype=torch.int32)
-            self.attn.append({"wqkv": wqkv, "wo": wo, "k": kc, "v": vc})
-        gen = torch.Generator(device="cuda").manual_seed(seed * 7919 + 999)
-        self.embd = device.register_weight(synth_q6k(vocab * nb, gen).view(-1), vocab, nb, Q6_K)
-        gain = torch.round((torch.randn(d_model, generator=gen, device="cuda", dtype=torch.float64).abs() + 0.5)
-                           * (1 << fa)).to(torch.int64)
-        self.out_gain = gain
-        self.out_gain_h = qk_cuda.register_i64(gain.cpu().numpy())
-        cos, sin = rope_tables(self.rows, head_dim, rope_base, fa)
-        self.cos, self.sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
-        self.pos = torch.tensor([context], dtype=torch.int32, device="cuda")        # position of the next token
+        self.attn, self.moe_layers, self.gain_handles = attn, moe_layers, gain_handles
+        self.n_layers = len(attn)
+        self.embd, self.out_gain_h = embd, out_gain_h
+        self.cos, self.sin = cos, sin
+        self.rows = int(attn[0]["k"].shape[1])
+        self.pos = torch.tensor([position], dtype=torch.int32, device="cuda")       # position of the next token
         self.token = torch.zeros(1, dtype=torch.int32, device="cuda")               # its id
-        self.context = context
-        # scratch rows of a step
+        self._pos_host = int(position)                                              # host mirror of the position cell
         z = lambda n: torch.empty((1, n), dtype=torch.int64, device="cuda")
         self.x, self.hn, self.logits = z(d_model), z(d_model), z(vocab)
+        self._graph = None
+
+    @classmethod
+    def from_raw(cls, layers, embd_raw, out_gain, *, d_model, n_heads, n_kv, head_dim, e_ffn, top_k, vocab, window, rows,
+                 rope_base=50000.0, fa=16, fw=24, caches=None, position=0):
+        """``layers[i]`` = dict(gain int64 [d]; wq, wk, wv, wo raw Q4_K bytes; moe=(router, gates, ups, downs) raw Q4_K /
+        Q4_K / Q4_K / Q6_K bytes), as a GGUF reader hands them over; ``embd_raw`` the tied Q6_K matrix [vocab, d].
+        ``caches[i]`` = (k, v) int64 arrays [n_kv, filled, head_dim] already in the cache (after rotation)."""
+        nb = d_model // 256
+        attn, moe_layers, gains = [], [], []
+        for li, L in enumerate(layers):
+            qkv = bytes(L["wq"]) + bytes(L["wk"]) + bytes(L["wv"])                  # rows are independent in the block layout
+            wqkv = qk_cuda.register_weight(qkv, (n_heads + 2 * n_kv) * head_dim, nb, Q4_K)
+            wo = qk_cuda.register_weight(L["wo"], d_model, n_heads * head_dim // 256, Q4_K)
+            kc = torch.zeros((n_kv, rows, head_dim), dtype=torch.int32, device="cuda"); vc = torch.zeros_like(kc)
+            if caches is not None:
+                k0, v0 = caches[li]
+                kc[:, :k0.shape[1]] = torch.from_numpy(np.ascontiguousarray(k0).astype(np.int32)).cuda()
+                vc[:, :v0.shape[1]] = torch.from_numpy(np.ascontiguousarray(v0).astype(np.int32)).cuda()
+            attn.append({"wqkv": wqkv, "wo": wo, "k": kc, "v": vc})
+            router, gate, up, down = L["moe"]
+            rh = qk_cuda.register_weight(router, len(gate), nb, Q4_K)
+            gh = [qk_cuda.register_weight(w, e_ffn, nb, Q4_K) for w in gate]
+            uh = [qk_cuda.register_weight(w, e_ffn, nb, Q4_K) for w in up]
+            dh = [qk_cuda.register_weight(w, d_model, e_ffn // 256, Q6_K) for w in down]
+            moe_layers.append(device.MoELayer(rh, gh, uh, dh, top_k, d_model, e_ffn))
+            gains.append(qk_cuda.register_i64(np.asarray(L["gain"], np.int64)))
+        embd = qk_cuda.register_weight(embd_raw, vocab, nb, Q6_K)
+        out_gain_h = qk_cuda.register_i64(np.asarray(out_gain, np.int64))
+        cos, sin = rope_tables(rows, head_dim, rope_base, fa)
+        return cls(d_model=d_model, n_heads=n_heads, n_kv=n_kv, head_dim=head_dim, top_k=top_k, vocab=vocab, window=window,
+                   fa=fa, fw=fw, attn=attn, moe_layers=moe_layers, gain_handles=gains, embd=embd, out_gain_h=out_gain_h,
+                   cos=torch.from_numpy(cos).cuda(), sin=torch.from_numpy(sin).cuda(), position=position)
 
     def layer_is_full(self, li: int) -> bool:
         return li % SWA_PERIOD == 0
 
-    def weight_bytes_per_token(self) -> int:
-        nb = self.d // 256
-        per_layer_attn = (2 * self.H * self.hd + 2 * self.Hkv * self.hd) * nb * 144
-        return self.moe.weight_bytes_per_token() + self.n_layers * per_layer_attn + self.vocab * nb * 210
+    def set_position(self, position: int) -> None:
+        self.pos.fill_(int(position))
+        self._pos_host = int(position)
 
     def kv_bytes_per_token(self, pos: int) -> int:
         total = 0
@@ -84,9 +101,7 @@ class SyntheticDecoder:
             total += 2 * self.Hkv * keys * self.hd * 4
         return total
 
-    def step(self, pos_bound: int) -> None:
-        """One token: reads ``self.token`` / ``self.pos`` on the device, leaves the next token id in ``self.token``
-        and advances ``self.pos``.  ``pos_bound`` is a host upper bound of the position (sizes the grids)."""
+    def _launch_step(self, pos_bound: int) -> None:
         fa, fw = self.fa, self.fw
         device.embed(self.embd, self.token, self.d, fa, out=self.x)
         for li in range(self.n_layers):
@@ -94,37 +109,97 @@ class SyntheticDecoder:
             full = self.layer_is_full(li)
             # MoE half first: it normalises x, leaves the digit planes of h in the library and adds moe(h) to x;
             # the attention half then reads those planes and adds its own term
-            self.moe.layers[li].block(self.x, self.moe.gains[li], fa, fw, 1, out=self.x, want_routes=False)
+            self.moe_layers[li].block(self.x, self.gain_handles[li], fa, fw, 1, out=self.x, want_routes=False)
             device.attention_block(a["wqkv"], a["wo"], self.x, a["k"], a["v"], pos_bound, self.H, self.Hkv, self.hd, fa, fw,
                                    0 if full else self.window, self.cos, self.sin, 0 if full else 1, pos_dev=self.pos)
-        device.join_block_overlap()                         # no-op unless the halves of a block run side by side
         device.rmsnorm(self.x, self.out_gain_h, fa, 1, out=self.hn)
         device.apply(self.embd, self.hn, self.vocab, fw, out=self.logits)
         device.argmax(self.logits.view(-1), out=self.token)
         self.pos += 1
 
+    def _admit(self, bound: int) -> None:
+        """Host-side refusal of a step the launches were not sized for: the position cell must not pass the bound the
+        grids cover nor the rows of the cache (the kernels refuse too, but then the step is lost)."""
+        if self._pos_host > bound or self._pos_host >= self.rows:
+            raise qk_cuda.CudaContextError(
+                f"decode step at position {self._pos_host} is beyond the bound {bound} / the {self.rows} cache rows")
+
+    def step(self, pos_bound: int) -> None:
+        """One token: reads ``self.token`` / ``self.pos`` on the device, leaves the next token id in ``self.token``
+        and advances ``self.pos``.  ``pos_bound`` is a host upper bound of the position (sizes the grids)."""
+        self._admit(pos_bound)
+        self._launch_step(pos_bound)
+        self._pos_host += 1
+
     def capture(self, pos_bound: int) -> None:
         """Record one step as a CUDA graph valid for every position up to ``pos_bound``; token and position are
         restored afterwards, the KV row written during the warm-up / capture pass is overwritten by the next real step."""
+        self._admit(pos_bound)
         keep = (self.token.clone(), self.pos.clone())
-        self.step(pos_bound)                                   # sizes every workspace
+        self._launch_step(pos_bound)                           # sizes every workspace
         torch.cuda.synchronize()
         self._stream = torch.cuda.Stream()
         self._graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(self._stream):
             with torch.cuda.graph(self._graph, stream=self._stream):
-                self.step(pos_bound)
+                self._launch_step(pos_bound)
         torch.cuda.synchronize()
         self.token.copy_(keep[0]); self.pos.copy_(keep[1])
         self._bound = pos_bound
+        self._generation = device.workspace_generation()
 
     def replay(self) -> None:
+        """Replay the captured step.  Refused on the host when the position has reached the captured bound or the end of
+        the cache, and when the library's workspaces were freed or regrown since the capture (the graph holds their
+        old addresses): capture again in either case."""
+        if self._graph is None:
+            raise qk_cuda.CudaContextError("capture() has not been called")
+        self._admit(self._bound)
+        if device.workspace_generation() != self._generation:
+            raise qk_cuda.CudaContextError("library workspaces changed since capture(): the graph must be captured again")
         self._graph.replay()
+        self._pos_host += 1
 
     def decode_token(self, token_host: torch.Tensor, out_host: torch.Tensor) -> None:
         """Public per-token call with host buffers: pinned int32 ``token_host`` [1] in, next id in pinned ``out_host``
         [1]; returns when the id has arrived.  Needs :meth:`capture` first."""
         self.token.copy_(token_host, non_blocking=True)
-        self._graph.replay()
+        self.replay()
         out_host.copy_(self.token, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+
+
+class SyntheticDecoder(Decoder):
+    def __init__(self, n_layers: int = 48, d_model: int = 2048, n_heads: int = 32, n_kv: int = 4, head_dim: int = 128,
+                 e_ffn: int = 768, n_experts: int = 128, top_k: int = 8, vocab: int = 151936, context: int = 4096,
+                 max_new: int = 160, window: int = 4096, rope_base: float = 50000.0, seed: int = 1, fa: int = 16, fw: int = 24):
+        rows = context + max_new
+        self.moe = SyntheticMoEStack(n_layers, d_model, e_ffn, n_experts, top_k, seed=seed, fa=fa)
+        nb = d_model // 256
+        attn = []
+        for li in range(n_layers):
+            gen = torch.Generator(device="cuda").manual_seed(seed * 7919 + 1000 + li)
+            # Wq, Wk, Wv stacked row-wise into one matrix (rows are independent in the block layout)
+            qkv_rows = (n_heads + 2 * n_kv) * head_dim
+            wqkv = device.register_weight(synth_q4k(qkv_rows * nb, gen).view(-1), qkv_rows, nb, Q4_K)
+            wo = device.register_weight(synth_q4k(d_model * (n_heads * head_dim // 256), gen).view(-1), d_model,
+                                        n_heads * head_dim // 256, Q4_K)
+            kc = torch.randint(-(1 << 18), 1 << 18, (n_kv, rows, head_dim), generator=gen, device="cuda", dtype=torch.int32)
+            vc = torch.randint(-(1 << 18), 1 << 18, (n_kv, rows, head_dim), generator=gen, device="cuda", dtype=torch.int32)
+            attn.append({"wqkv": wqkv, "wo": wo, "k": kc, "v": vc})
+        gen = torch.Generator(device="cuda").manual_seed(seed * 7919 + 999)
+        embd = device.register_weight(synth_q6k(vocab * nb, gen).view(-1), vocab, nb, Q6_K)
+        gain = torch.round((torch.randn(d_model, generator=gen, device="cuda", dtype=torch.float64).abs() + 0.5)
+                           * (1 << fa)).to(torch.int64)
+        self.out_gain = gain
+        cos, sin = rope_tables(rows, head_dim, rope_base, fa)
+        super().__init__(d_model=d_model, n_heads=n_heads, n_kv=n_kv, head_dim=head_dim, top_k=top_k, vocab=vocab, window=window,
+                         fa=fa, fw=fw, attn=attn, moe_layers=self.moe.layers, gain_handles=self.moe.gains, embd=embd,
+                         out_gain_h=qk_cuda.register_i64(gain.cpu().numpy()), cos=torch.from_numpy(cos).cuda(),
+                         sin=torch.from_numpy(sin).cuda(), position=context)
+        self.context = context
+
+    def weight_bytes_per_token(self) -> int:
+        nb = self.d // 256
+        per_layer_attn = (2 * self.H * self.hd + 2 * self.Hkv * self.hd) * nb * 144
+        return self.moe.weight_bytes_per_token() + self.n_layers * per_layer_attn + self.vocab * nb * 210

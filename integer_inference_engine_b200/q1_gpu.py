@@ -24,8 +24,10 @@ EXPORTED_SYMBOLS = (
     "bonsai_gpu_mem_info", "bonsai_q1_resident_weight_bytes", "bonsai_q1_linear_gpu", "bonsai_q1_linear_dp4a_gpu",
     "bonsai_q1_register_weight", "bonsai_q1_register_weight_i32", "bonsai_q1_register_weight_i32_gpu_layout",
     "bonsai_q1_register_weight_i32_bmma", "bonsai_q1_apply_resident", "bonsai_q1_free_weights", "bonsai_rmsnorm_gpu",
-    "iie_q1_apply_dev", "iie_q1_apply_fused_dev", "iie_q1_head_norm_dev", "iie_q1_silu_mul_dev", "iie_q1_embed_dev", "iie_q1_set_stream", "iie_q1_weight_shape",
+    "iie_q1_apply_dev", "iie_q1_apply_fused_dev", "iie_q1_head_norm_dev", "iie_q1_silu_mul_dev", "iie_q1_embed_dev", "iie_q1_set_stream", "iie_q1_weight_shape", "iie_q1_workspace_generation",
 )
+from .qk_cuda import CudaContextError      # noqa: E402  (same error type as the MoE bridge)
+
 _L4_LO, _L4_HI = -2155905152, 2139062143      # balanced base-256 range of four digits (gpu_native.py:223)
 
 
@@ -69,7 +71,7 @@ def load_library():
         "iie_q1_head_norm_dev": ([vp, i64, i64, i64, vp, vp, i64, vp, vp], c_int),
         "iie_q1_silu_mul_dev": ([vp, vp, i64, i64, vp, vp], c_int),
         "iie_q1_embed_dev": ([i64, vp, i64, vp, vp], c_int),
-        "iie_q1_set_stream": ([c_int], None),
+        "iie_q1_set_stream": ([c_int], None), "iie_q1_workspace_generation": ([], ctypes.c_uint64),
         "iie_q1_weight_shape": ([i64, ctypes.POINTER(i64), ctypes.POINTER(i64), ctypes.POINTER(c_int)], c_int),
     }
     for name, (args, res) in sig.items():
@@ -292,6 +294,11 @@ def head_norm_dev(x, rows_a: int, rows_b: int, width: int, gain_a, gain_b, frac:
     if rc != 0:
         raise RuntimeError(f"iie_q1_head_norm_dev failed with status {rc}")
     return out
+
+
+def workspace_generation() -> int:
+    """Changes whenever a scratch buffer of the Q1_0 entries is freed; holders of captured graphs compare it."""
+    return int(_lib().iie_q1_workspace_generation())
 
 
 def set_stream_form(on: bool) -> None:

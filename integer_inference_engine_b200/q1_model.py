@@ -56,6 +56,19 @@ class Q1Decoder:
         z = lambda n: torch.empty((1, n), dtype=torch.int64, device="cuda")
         self.x, self.qkv, self.qkvn, self.att = z(d_model), z(qd + 2 * kd), z(qd + kd), z(qd)
         self.gu, self.logits = z(2 * d_ffn), z(vocab)
+        self.rows = int(self.layers[0]["k"].shape[1])
+        self._pos_host = int(context)                                               # host mirror of the position cell
+        self._graph = None
+
+    def set_position(self, position: int) -> None:
+        self.pos.fill_(int(position))
+        self._pos_host = int(position)
+
+    def _admit(self, bound: int) -> None:
+        """Host-side refusal of a step beyond the bound the launches were sized for or the rows of the cache."""
+        if self._pos_host > bound or self._pos_host >= self.rows:
+            raise q1_gpu.CudaContextError(
+                f"decode step at position {self._pos_host} is beyond the bound {bound} / the {self.rows} cache rows")
 
     def weight_bytes_per_token(self) -> int:
         """Sign bits + int32 scales every matrix streams for one token (one embedding row excluded)."""
@@ -65,6 +78,11 @@ class Q1Decoder:
         return (self.n_layers * rows_in + self.vocab * self.d) // 128 * per_block
 
     def step(self, pos_bound: int) -> None:
+        self._admit(pos_bound)
+        self._launch_step(pos_bound)
+        self._pos_host += 1
+
+    def _launch_step(self, pos_bound: int) -> None:
         """One token: reads ``self.token`` / ``self.pos`` on the device, leaves the next id in ``self.token`` and advances
         ``self.pos``.  Per layer ten launches: norm + digit planes, QKV product, both head norms, attention, planes,
         O product with the residual, norm + planes, gate/up product, SwiGLU + planes, down product with the residual."""
@@ -83,24 +101,35 @@ class Q1Decoder:
         self.pos += 1
 
     def capture(self, pos_bound: int) -> None:
+        self._admit(pos_bound)
         keep = (self.token.clone(), self.pos.clone())
-        self.step(pos_bound)
+        self._launch_step(pos_bound)
         torch.cuda.synchronize()
         self._stream = torch.cuda.Stream()
         self._graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(self._stream):
             with torch.cuda.graph(self._graph, stream=self._stream):
-                self.step(pos_bound)
+                self._launch_step(pos_bound)
         torch.cuda.synchronize()
         self.token.copy_(keep[0]); self.pos.copy_(keep[1])
+        self._bound = pos_bound
+        self._generation = device.workspace_generation() + q1_gpu.workspace_generation()
 
     def replay(self) -> None:
+        """Replay the captured step; refused on the host past the captured bound or the cache rows, and after the
+        library's workspaces were freed or regrown (the graph holds their old addresses)."""
+        if self._graph is None:
+            raise q1_gpu.CudaContextError("capture() has not been called")
+        self._admit(self._bound)
+        if device.workspace_generation() + q1_gpu.workspace_generation() != self._generation:
+            raise q1_gpu.CudaContextError("library workspaces changed since capture(): the graph must be captured again")
         self._graph.replay()
+        self._pos_host += 1
 
     def decode_token(self, token_host: torch.Tensor, out_host: torch.Tensor) -> None:
         """Per-token call with pinned host buffers (int32 [1] in, next id out); needs :meth:`capture` first."""
         self.token.copy_(token_host, non_blocking=True)
-        self._graph.replay()
+        self.replay()
         out_host.copy_(self.token, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 

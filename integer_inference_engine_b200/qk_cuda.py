@@ -40,12 +40,12 @@ EXPORTED_SYMBOLS = (
     "qk_profile_snapshot", "qk_attention_bank_create", "qk_attention_bank_reset", "qk_attention_bank_destroy",
     "qk_attention_bank_moe_configure", "qk_attention_bank_moe_bind", "qk_attention_bank_import",
     "qk_attention_bank_apply", "qk_attention_bank_moe_begin", "qk_attention_bank_moe_continue",
-    "qk_attention_bank_moe_export", "qk_attention_bank_workspace_bytes", "iie_attn_prefill_dev", "iie_set_block_overlap", "iie_join_block_overlap",
+    "qk_attention_bank_moe_export", "qk_attention_bank_workspace_bytes", "iie_attn_prefill_dev", 
     "iie_register_weight_dev", "iie_weight_export", "iie_moe_layer_create", "iie_moe_layer_destroy",
     "iie_moe_forward_dev", "iie_apply_dev", "iie_flags_read_clear", "iie_rmsnorm_dev", "iie_profile_stage_mask",
-    "iie_launch_count", "iie_moe_block_host", "iie_moe_block_dev", "iie_set_pdl",
+    "iie_launch_count", "iie_prefill_launch_counts", "iie_workspace_generation", "iie_moe_block_host", "iie_moe_block_dev", "iie_set_pdl",
     "iie_apply_dev_static", "iie_set_tc_min_tokens", "iie_route_dev", "iie_moe_experts_dev",
-    "iie_set_fused_expert", "iie_expert_clusters", "iie_set_fused_route", "iie_attn_decode_dev", "iie_embed_dev", "iie_argmax_dev", "iie_attn_block_dev", "iie_set_attn_fused", "iie_set_batch_stream",
+    "iie_attn_decode_dev", "iie_embed_dev", "iie_argmax_dev", "iie_attn_block_dev", "iie_set_attn_fused",
 )
 # The library keeps one registry and one set of workspaces per process and ctypes releases the GIL:
 # serialise callers here as the reference bridge does (qk_cuda.py:35-38).
@@ -112,12 +112,12 @@ def load_library():
         "iie_apply_dev_static": ([i64, vp, i64, c_int, vp, vp], c_int),
         "iie_rmsnorm_dev": ([i64, vp, i64, i64, c_int, u64, vp, vp], c_int),
         "iie_profile_stage_mask": ([c_int], None), "iie_launch_count": ([], u64), "iie_set_pdl": ([c_int], None),
-        "iie_set_tc_min_tokens": ([i64], None), "iie_set_fused_expert": ([c_int], None), "iie_expert_clusters": ([], c_int), "iie_set_fused_route": ([c_int], None),
+        "iie_set_tc_min_tokens": ([i64], None), 
         "iie_attn_decode_dev": ([vp, vp, vp, vp, vp, i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, i64, vp, vp], c_int),
         "iie_attn_prefill_dev": ([vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, i64, vp, vp], c_int),
-        "iie_set_block_overlap": ([c_int], c_int), "iie_join_block_overlap": ([vp], c_int),
+        "iie_prefill_launch_counts": ([ctypes.POINTER(ctypes.c_uint64), c_int], c_int), "iie_workspace_generation": ([], u64),
         "iie_attn_block_dev": ([i64, i64, vp, vp, vp, i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, c_int, i64, vp], c_int),
-        "iie_embed_dev": ([i64, vp, i64, c_int, vp, vp], c_int), "iie_set_attn_fused": ([c_int], None), "iie_set_batch_stream": ([c_int], None), "iie_argmax_dev": ([vp, i64, vp, vp], c_int),
+        "iie_embed_dev": ([i64, vp, i64, c_int, vp, vp], c_int), "iie_set_attn_fused": ([c_int], None), "iie_argmax_dev": ([vp, i64, vp, vp], c_int),
         "iie_route_dev": ([i64, c_int, vp, i64, c_int, c_int, vp, vp, vp], c_int),
         "iie_moe_experts_dev": ([i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, c_int, vp, vp], c_int),
         "iie_moe_block_host": ([i64, i64, vp, i64, c_int, c_int, u64, vp, vp, vp], c_int),

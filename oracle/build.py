@@ -6,6 +6,10 @@ in a mounted reference tree, into ``oracle/_ref/`` (nothing is copied into this 
 no-op returning False when the reference tree is not mounted.  Both outputs are git-ignored and
 travel to a GPU machine as prebuilt files.
 
+``install_reference()`` lays the reference's own Python bridge, its CUDA test files and its own CUDA producer (built for
+sm_100a with the flags of its build script) out under the git-ignored ``baseline/_ref/``: the reference arm and the
+drop-in test run that unmodified code; nothing of it enters this repository's history.
+
 Commands (the same ones the reference's build scripts use for these two files):
   gcc -O3 -fopenmp -fPIC -shared <ref>/north-mini-code/tools/nmc_qk_kernel.c -o oracle/_ref/libnmc_qk.so -lm
   gcc -O3 -march=x86-64-v2 -mtune=generic -fwrapv -fno-strict-overflow -fPIC -shared -fopenmp \
@@ -18,7 +22,12 @@ import subprocess
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REFERENCE_ROOT = Path(os.environ.get("IIE_REFERENCE_ROOT", "/root/reference"))
+# where the reference checkout is mounted: IIE_REFERENCE_ROOT, else a checkout named "reference" beside this
+# repository; with neither, nothing is built from it
+_beside = HERE.parent.parent / "reference"
+REFERENCE_ROOT = Path(os.environ["IIE_REFERENCE_ROOT"]) if os.environ.get("IIE_REFERENCE_ROOT") else \
+    (_beside if (_beside / "north-mini-code").is_dir() else None)
+BASELINE_REF = HERE.parent / "baseline" / "_ref"
 
 
 def _stale(target: Path, *sources: Path) -> bool:
@@ -35,6 +44,8 @@ def build_oracle(force: bool = False) -> Path:
 
 
 def build_ref(force: bool = False) -> bool:
+    if REFERENCE_ROOT is None:
+        return False
     nmc = REFERENCE_ROOT / "north-mini-code" / "tools" / "nmc_qk_kernel.c"
     q1 = REFERENCE_ROOT / "bonsai" / "tools" / "bonsai_q1_kernel.c"
     if not nmc.exists():
@@ -51,6 +62,38 @@ def build_ref(force: bool = False) -> bool:
     return True
 
 
+def install_reference(force: bool = False) -> bool:
+    """``baseline/_ref/north-mini-code/{src/nmc, tests/test_qk_*.py}`` = the reference's bridge package and its CUDA
+    differential tests, unmodified; ``baseline/_ref/bin/libnmc_qk_cuda.so`` = the reference's own CUDA producer compiled
+    for sm_100a (north-mini-code/tools/build_nmc_cuda.sh: nvcc -O3 -arch=<sm> --cudart static -Xcompiler -fPIC -shared),
+    with its CPU kernel ``libnmc_qk.so`` beside it.  Returns False when no reference checkout is mounted."""
+    import shutil
+    if REFERENCE_ROOT is None or not (REFERENCE_ROOT / "north-mini-code" / "src" / "nmc").exists():
+        return False
+    root = REFERENCE_ROOT / "north-mini-code"
+    dst = BASELINE_REF / "north-mini-code"
+    if force and dst.exists():
+        shutil.rmtree(dst)
+    if not (dst / "src" / "nmc").exists():
+        shutil.copytree(root / "src" / "nmc", dst / "src" / "nmc", ignore=shutil.ignore_patterns("__pycache__"))
+    (dst / "tests").mkdir(parents=True, exist_ok=True)
+    for name in ("test_qk_cuda.py", "test_qk_cuda_api.py", "test_qk_codec.py"):
+        if (root / "tests" / name).exists():
+            shutil.copyfile(root / "tests" / name, dst / "tests" / name)
+    bin_dir = BASELINE_REF / "bin"
+    bin_dir.mkdir(parents=True, exist_ok=True)
+    cu, out = root / "tools" / "nmc_qk_cuda.cu", bin_dir / "libnmc_qk_cuda.so"
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if cu.exists() and Path(nvcc).exists() and (force or _stale(out, cu)):
+        subprocess.run([nvcc, "-O3", "-arch=sm_100a", "--cudart", "static", "-Xcompiler", "-fPIC", "-shared", str(cu), "-o", str(out)],
+                       check=True)
+    cpu = root / "tools" / "nmc_qk_kernel.c"
+    if cpu.exists() and (force or _stale(bin_dir / "libnmc_qk.so", cpu)):
+        subprocess.run(["gcc", "-O3", "-fopenmp", "-fPIC", "-shared", str(cpu), "-o", str(bin_dir / "libnmc_qk.so"), "-lm"], check=True)
+    return True
+
+
 if __name__ == "__main__":
     print(build_oracle(force=True))
     print("reference CPU kernels built:", build_ref(force=True))
+    print("reference bridge, tests and CUDA producer installed:", install_reference(force=True))

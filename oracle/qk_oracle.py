@@ -435,3 +435,33 @@ GOLDEN_LINEAR_CASES = [(0, 8, 1, 1, 18), (0, 16, 2, 3, 18), (1, 5, 3, 4, 18), (1
                        (1, 9, 1, 1, 50)]
 # name -> (seed, d_model, expert_ffn, n_experts, top_k, tokens); "config1" is the single-block benchmark shape
 GOLDEN_MOE_CASES = {"small": (400, 256, 256, 8, 3, 4), "config1": (0, 2048, 768, 128, 8, 16)}
+
+
+# The small decoder the committed decode-step fixture (tests/golden/nmc_decode.npz) was recorded on: two blocks, the first
+# attends to every key without rotation, the second through a sliding window with interleaved RoPE (cohere2.py:72-84).
+NMC_DECODE_CASE = {"seed": 900, "d": 256, "H": 4, "Hkv": 2, "hd": 64, "eff": 256, "E": 8, "k": 2, "vocab": 96, "window": 4,
+                   "rope_base": 50000.0, "rows": 16, "prompt": (3, 90, 41, 7, 66, 12), "steps": 3, "layers": 2}
+
+
+def synth_decoder(seed: int, case: dict, fa: int = 16) -> dict:
+    """Raw tensors of a small decoder of the north-mini-code shape.  Draw order per block: norm gain
+    (to_fixed(|N(0,1)| + 0.5), cohere2.py:511), Wq, Wk, Wv, Wo (Q4_K), router, then per expert gate, up (Q4_K), down
+    (Q6_K); after the blocks the output-norm gain and the tied embedding / head matrix (Q6_K).  Returns
+    {"layers": [{gain, wq, wk, wv, wo, moe: (router, gates, ups, downs)}], "out_gain", "embd"}."""
+    rng = np.random.default_rng(seed)
+    d, H, Hkv, hd, eff, E = (case[n] for n in ("d", "H", "Hkv", "hd", "eff", "E"))
+    nb = d // 256
+    layers = []
+    for _ in range(case["layers"]):
+        L = {"gain": to_fixed(np.abs(rng.standard_normal(d)) + 0.5, fa)}
+        L["wq"] = synth_q4k(rng, H * hd, nb); L["wk"] = synth_q4k(rng, Hkv * hd, nb); L["wv"] = synth_q4k(rng, Hkv * hd, nb)
+        L["wo"] = synth_q4k(rng, d, H * hd // 256)
+        router = synth_q4k(rng, E, nb)
+        gate, up, down = [], [], []
+        for _e in range(E):
+            gate.append(synth_q4k(rng, eff, nb)); up.append(synth_q4k(rng, eff, nb)); down.append(synth_q6k(rng, d, eff // 256))
+        L["moe"] = (router, gate, up, down)
+        layers.append(L)
+    out_gain = to_fixed(np.abs(rng.standard_normal(d)) + 0.5, fa)
+    embd = synth_q6k(rng, case["vocab"], nb)
+    return {"layers": layers, "out_gain": out_gain, "embd": embd}

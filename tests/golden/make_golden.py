@@ -1,9 +1,11 @@
 """Regenerate the golden vectors in this directory from the reference project's own Python code.
 
-Run where the reference tree is mounted (its location comes from IIE_REFERENCE_ROOT, with the
-mount point used during development as the default):
+Run where the reference tree is mounted; its location must be given in IIE_REFERENCE_ROOT:
 
-    python tests/golden/make_golden.py
+    IIE_REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py [fixture ...]
+
+Without arguments every fixture is regenerated; with names (half_fixed, codec, linear, scalar, q1, moe,
+attention, q1_decode, nmc_decode) only those.
 
 Inputs come from the seeded generators in ``oracle/qk_oracle.py`` (so the fixtures only need to
 store seeds and outputs); outputs come from the reference's modules ``nmc.qk_codec``,
@@ -22,7 +24,9 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parents[1]
-REF = Path(os.environ.get("IIE_REFERENCE_ROOT", "/root/reference"))
+if "IIE_REFERENCE_ROOT" not in os.environ:
+    raise SystemExit("set IIE_REFERENCE_ROOT to the reference checkout")
+REF = Path(os.environ["IIE_REFERENCE_ROOT"])
 sys.path.insert(0, str(REF / "north-mini-code" / "src"))
 sys.path.insert(0, str(REF / "bonsai" / "src"))
 sys.path.insert(0, str(ROOT))
@@ -204,15 +208,67 @@ def q1_decode_fixture():
     return out
 
 
+def nmc_decode_fixture():
+    """KV-cached decode steps of the reference's own parallel MoE block and tied head (cohere2.py block_cached,
+    tied_head_int, generate) on the small synthetic decoder ``oracle.qk_oracle.synth_decoder`` describes: layer 0
+    attends to everything without rotation, layer 1 through a sliding window with interleaved RoPE.  A prompt of
+    ``NMC_DECODE_CASE['prompt']`` tokens fills the cache through the reference; the recorded values are the cache
+    before and after, the row after every block, the logits and the greedy picks of the next decode steps."""
+    case = o.NMC_DECODE_CASE
+    m = o.synth_decoder(case["seed"], case)
+    d, H, Hkv, hd, eff, E, k, vocab = (case[n] for n in ("d", "H", "Hkv", "hd", "eff", "E", "k", "vocab"))
+    nb = d // 256
+    cfg = c2.Cfg(d_model=d, n_heads=H, n_kv=Hkv, head_dim=hd, ffn=eff, vocab=vocab, n_experts=E, n_used=k,
+                 expert_ffn=eff, sliding_window=case["window"], rope_base=case["rope_base"], fa=FA, fw=FW)
+    from nmc._bonsai import rope as rrope
+    cos, sin = rrope.build_rope_tables(case["rows"], hd, case["rope_base"], FA)
+    layers = []
+    for L in m["layers"]:
+        W = {"attn_norm": L["gain"], "wq": ref_dequant(L["wq"], H * hd, nb, 0, FW), "wk": ref_dequant(L["wk"], Hkv * hd, nb, 0, FW),
+             "wv": ref_dequant(L["wv"], Hkv * hd, nb, 0, FW), "wo": ref_dequant(L["wo"], d, H * hd // 256, 0, FW)}
+        router, gate, up, down = L["moe"]
+        We = {"router": ref_dequant(router, E, nb, 0, FW), "gate": _LazyExperts(gate, eff, nb, 0),
+              "up": _LazyExperts(up, eff, nb, 0), "down": _LazyExperts(down, d, eff // 256, 1)}
+        layers.append((W, We))
+    table = ref_dequant(m["embd"], vocab, nb, 1, FA)
+    head_W = {"output_norm": m["out_gain"], "token_embd": ref_dequant(m["embd"], vocab, nb, 1, FW)}
+    embed = lambda t: table[t]
+    cache = c2.KVCache(len(layers), max_length=case["rows"])
+    prompt = list(case["prompt"])
+    last = c2._run_layers_cached(np.stack([embed(t) for t in prompt]), layers, cfg, cos, sin, cache)[-1:]
+    out = {"cos": cos, "sin": sin}
+    for li in range(len(layers)):
+        out[f"k{li}"], out[f"v{li}"] = cache.k[li].copy(), cache.v[li].copy()
+    tok = int(np.argmax(c2.tied_head_int(last, head_W, cfg)[0]))          # first pick: after the prompt
+    picks, xs, logit_rows = [tok], [], []
+    for step in range(case["steps"]):
+        x = embed(tok)[None, :]
+        rows = [x.copy()]
+        for li, (W, We) in enumerate(layers):
+            x = c2.block_cached(x, W, We, cfg, cos, sin, cache, li, c2.window_for_layer(cfg, li))
+            rows.append(x.copy())
+        logits = c2.tied_head_int(x, head_W, cfg)[0]
+        tok = int(np.flatnonzero(logits == logits.max())[0])
+        picks.append(tok); xs.append(np.concatenate(rows)); logit_rows.append(logits)
+    out["picks"], out["x"], out["logits"] = np.array(picks, np.int64), np.stack(xs), np.stack(logit_rows)
+    for li in range(len(layers)):
+        out[f"k{li}_after"], out[f"v{li}_after"] = cache.k[li].copy(), cache.v[li].copy()
+    # the library's own generate() on the same inputs yields the same picks (its pick receives the logits row)
+    gen = c2.generate(prompt, embed, layers, head_W, cfg, cos, sin, case["steps"] + 1,
+                      lambda lg, pos, hist: int(np.flatnonzero(lg == lg.max())[0]))
+    assert gen == picks, (gen, picks)
+    return out
+
+
+FIXTURES = {"half_fixed": half_fixture, "codec": codec_fixture, "linear": linear_fixture, "scalar": scalar_fixture,
+            "q1": q1_fixture, "moe": moe_fixture, "attention": attention_fixture, "q1_decode": q1_decode_fixture,
+            "nmc_decode": nmc_decode_fixture}
+
+
 def main():
-    np.savez_compressed(HERE / "half_fixed.npz", **half_fixture())
-    np.savez_compressed(HERE / "codec.npz", **codec_fixture())
-    np.savez_compressed(HERE / "linear.npz", **linear_fixture())
-    np.savez_compressed(HERE / "scalar.npz", **scalar_fixture())
-    np.savez_compressed(HERE / "q1.npz", **q1_fixture())
-    np.savez_compressed(HERE / "moe.npz", **moe_fixture())
-    np.savez_compressed(HERE / "attention.npz", **attention_fixture())
-    np.savez_compressed(HERE / "q1_decode.npz", **q1_decode_fixture())
+    for name in (sys.argv[1:] or list(FIXTURES)):
+        np.savez_compressed(HERE / f"{name}.npz", **FIXTURES[name]())
+        print("wrote", name, flush=True)
 
 
 if __name__ == "__main__":

@@ -11,6 +11,29 @@ import pytest
 HERE = Path(__file__).resolve().parent
 
 
+def _wait_all(procs, timeout):
+    """Wait for every rank; as soon as one fails or the time runs out, the others are killed, so that no rank is
+    left inside a collective holding a device."""
+    import time
+    deadline = time.monotonic() + timeout
+    try:
+        pending = list(procs)
+        while pending:
+            for p in list(pending):
+                rc = p.poll()
+                if rc is None:
+                    continue
+                pending.remove(p)
+                assert rc == 0, f"rank process exited with {rc}"
+            assert time.monotonic() < deadline, "rank processes timed out"
+            time.sleep(0.05)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+            p.wait()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -22,8 +45,7 @@ def test_exchange_matches_the_single_device_block(world, tmp_path, golden_dir):
     port = _free_port()
     procs = [subprocess.Popen([sys.executable, str(HERE / "ep_worker.py"), str(r), str(world), str(port),
                                str(tmp_path / f"r{r}.npz")]) for r in range(world)]
-    for p in procs:
-        assert p.wait(timeout=300) == 0
+    _wait_all(procs, 180)
     parts = [np.load(tmp_path / f"r{r}.npz") for r in range(world)]
     g = np.load(golden_dir / "moe.npz")
     assert np.array_equal(np.concatenate([p["ids"] for p in parts]), g["small_ids"])

@@ -118,9 +118,9 @@ def test_embedding_row_and_argmax():
     assert int(device.argmax(torch.from_numpy(x).cuda()).item()) == 0
 
 
-@pytest.mark.parametrize("form", [0, 1, 2])
+@pytest.mark.parametrize("form", [0, 1])
 def test_every_launch_form_gives_the_same_bytes(form):
-    """Three launches, one cooperative launch, one cluster per KV head."""
+    """Three launches and one cooperative launch."""
     from integer_inference_engine_b200 import qk_cuda as qk
     lib = qk.load_library()
     H, Hkv, hd, pos, window = 32, 4, 128, 700, 512

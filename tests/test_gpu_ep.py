@@ -44,6 +44,29 @@ def test_route_and_sharded_expert_stage_equal_the_block(d, eff, E, k, T, shards)
     assert np.array_equal(total.cpu().numpy(), out_ref)
 
 
+def _wait_all(procs, timeout):
+    """Wait for every rank; as soon as one fails or the time runs out, the others are killed, so that no rank is
+    left inside a collective holding a device."""
+    import time
+    deadline = time.monotonic() + timeout
+    try:
+        pending = list(procs)
+        while pending:
+            for p in list(pending):
+                rc = p.poll()
+                if rc is None:
+                    continue
+                pending.remove(p)
+                assert rc == 0, f"rank process exited with {rc}"
+            assert time.monotonic() < deadline, "rank processes timed out"
+            time.sleep(0.05)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+            p.wait()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -59,7 +82,6 @@ def test_nccl_exchange_on_two_gpus(T_per_rank, tmp_path):
     port = _free_port()
     procs = [subprocess.Popen([sys.executable, str(HERE / "ep_gpu_worker.py"), str(r), "2", str(port), str(T_per_rank),
                                str(tmp_path / f"r{r}.npz")]) for r in range(2)]
-    for p in procs:
-        assert p.wait(timeout=600) == 0
+    _wait_all(procs, 240)
     parts = [np.load(tmp_path / f"r{r}.npz") for r in range(2)]
     assert all(bool(p["ok"]) for p in parts)

@@ -391,24 +391,3 @@ def test_device_moe_prefill_tensor_core_path(qk, d, eff, E, k, T):
     qk.load_library().iie_set_tc_min_tokens(192)
     assert torch.equal(out, out2)
     qk.free_all()
-
-
-@pytest.mark.parametrize("which", ["route_in_gateup", "cluster_expert"])
-def test_alternative_single_token_launch_structures_give_the_same_bytes(qk, which):
-    """Routing recomputed inside the gate/up launch, and the expert stage as one cluster launch per expert."""
-    import torch
-
-    from integer_inference_engine_b200 import device
-    qk.free_all()
-    lib = qk.load_library()
-    layer, h, (ids_ref, gates_ref, out_ref) = _device_layer(qk, 321, 2048, 768, 16, 8, 1)
-    try:
-        (lib.iie_set_fused_route if which == "route_in_gateup" else lib.iie_set_fused_expert)(1)
-        for _ in range(3):                                     # consecutive calls alternate the digit-count cells
-            out, ids, gates = layer.forward(h, FA, FW)
-            torch.cuda.synchronize()
-            assert device.read_flags() == 0
-            assert np.array_equal(ids.cpu().numpy(), ids_ref) and np.array_equal(gates.cpu().numpy(), gates_ref)
-            assert np.array_equal(out.cpu().numpy(), out_ref)
-    finally:
-        lib.iie_set_fused_route(0); lib.iie_set_fused_expert(0)

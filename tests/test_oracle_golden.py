@@ -183,3 +183,40 @@ def test_q1_decode_token(golden_dir):
     for li in range(2):
         assert np.array_equal(layers[li]["k"][:, :pos + 1], g[f"k{li}_after"])
         assert np.array_equal(layers[li]["v"][:, :pos + 1], g[f"v{li}_after"])
+
+
+def nmc_golden_layers(g):
+    """The decode-step fixture of the MoE decoder (tests/golden/make_golden.py::nmc_decode_fixture) in the checker's
+    layer format: weights from the seeded generator, caches as the reference left them after the prompt."""
+    case = o.NMC_DECODE_CASE
+    m = o.synth_decoder(case["seed"], case)
+    layers = []
+    for li, L in enumerate(m["layers"]):
+        k0, v0 = g[f"k{li}"], g[f"v{li}"]
+        k = np.zeros((k0.shape[0], case["rows"], k0.shape[2]), np.int64); k[:, :k0.shape[1]] = k0
+        v = np.zeros_like(k); v[:, :v0.shape[1]] = v0
+        layers.append({"gain": L["gain"], "wq": L["wq"], "wk": L["wk"], "wv": L["wv"], "wo": L["wo"], "k": k, "v": v,
+                       "full": li % 4 == 0, "moe": L["moe"]})
+    cfg = dict(d=case["d"], H=case["H"], Hkv=case["Hkv"], hd=case["hd"], eff=case["eff"], E=case["E"], k=case["k"],
+               vocab=case["vocab"], window=case["window"], fa=FA, fw=FW)
+    return layers, m, cfg
+
+
+def test_nmc_decode_steps(golden_dir):
+    """Three KV-cached decode steps of the reference's parallel MoE block and tied head (cohere2.block_cached,
+    tied_head_int): the row after every block, the logits, the greedy picks and the appended cache rows are the
+    reference's own, for a full-attention block without rotation and a sliding-window block with RoPE."""
+    from oracle import model_oracle
+    g = np.load(golden_dir / "nmc_decode.npz")
+    case = o.NMC_DECODE_CASE
+    layers, m, cfg = nmc_golden_layers(g)
+    cos, sin = o.build_rope_tables(case["rows"], case["hd"], case["rope_base"], FA)
+    assert np.array_equal(cos, g["cos"]) and np.array_equal(sin, g["sin"])
+    tok, pos = int(g["picks"][0]), len(case["prompt"])
+    for step in range(case["steps"]):
+        tok, trace, logits = model_oracle.decode_token(tok, pos + step, layers, m["embd"], m["out_gain"], cfg, cos, sin)
+        assert np.array_equal(trace, g["x"][step]), step
+        assert np.array_equal(logits, g["logits"][step]) and tok == int(g["picks"][step + 1])
+    for li in range(case["layers"]):
+        n = pos + case["steps"]
+        assert np.array_equal(layers[li]["k"][:, :n], g[f"k{li}_after"]) and np.array_equal(layers[li]["v"][:, :n], g[f"v{li}_after"])
