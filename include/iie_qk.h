@@ -203,6 +203,34 @@ int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t
  * once (about 4700 visible keys per KV head on B200), else three launches; 0: always three launches.  Same bytes in
  * either form; the switch exists so that tests reach both. */
 void iie_set_attn_fused(int enabled);
+/* Whole decode step of the MoE decoder in ONE launch: every block of the model (RMSNorm, fused Q/K/V product, rotation,
+ * cache append, exact softmax attention, O product, router, top-k, sigmoid gates, gate/up with integer SiLU, down with
+ * gate-weighted combine; x += attention + moe) inside a persistent cooperative kernel, one CTA per SM, weights and cache
+ * rows streamed through shared-memory rings that run ahead of the arithmetic across the blocks.  Same bytes as the
+ * per-block entries (iie_moe_block_dev + iie_attn_block_dev), i.e. as north-mini-code/src/nmc/cohere2.py:357-376
+ * (block_cached, one new token) applied layer after layer (cohere2.py:379-383).
+ *   iie_decoder_create: model-wide shape; cos_dev / sin_dev [cache_rows][head_dim/2] int64 at 2^fa stay owned by the caller.
+ *   iie_decoder_set_layer: block li = norm gain (dense int64 handle), MoE layer (iie_moe_layer_create, with its router),
+ *     stacked Wq|Wk|Wv and Wo handles, int32 caches [n_kv][cache_rows][head_dim], full != 0: the block sees every key and
+ *     does not rotate (sliding window + interleaved RoPE otherwise).  rc 5: outside what the one-launch kernel carries
+ *     (quantisation types other than Q4_K for router / attention / gate / up, large block scales, d_model > 2048, more than
+ *     eight query heads per KV head ...): the caller keeps the per-block entries.
+ *   iie_decoder_step_dev: x_dev [d_model] is the residual row, updated in place through all blocks; the position is read from
+ *     *pos_dev when the kernel runs (pos_bound is its host upper bound and sizes nothing but the checks), or is pos_bound
+ *     when pos_dev is NULL.  ids_out_dev / gates_out_dev (optional, [n_layers][top_k]) receive every block's routing.
+ *     rc 5: the visible cache rows at pos_bound exceed what one launch holds (about 4300 per KV head on 148 SMs, head_dim 128).
+ *     Flag bits raised on the device: 0 digit envelope, 1 RMSNorm envelope, 2 K/V beyond int32, 3 a bounded wait gave up,
+ *     4 position cell beyond pos_bound or the cache, 5 a rotated query value beyond int32.
+ * The scratch of a decoder is its own (allocated at the first step, fixed size), so a captured step stays valid whatever the
+ * library's shared workspaces do. */
+long long iie_decoder_create(int n_layers, int n_heads, int n_kv, int head_dim, long long window, long long cache_rows, int fa,
+                             int fw, unsigned long long eps, long long inv_sqrt, const int64_t *cos_dev, const int64_t *sin_dev);
+int iie_decoder_set_layer(long long dec, int li, long long gain_h, long long moe_layer, long long wqkv_h, long long wo_h,
+                          int32_t *kcache_dev, int32_t *vcache_dev, int full);
+int iie_decoder_step_dev(long long dec, int64_t *x_dev, long long pos_bound, const int *pos_dev, int *ids_out_dev,
+                         int64_t *gates_out_dev, void *stream);
+void iie_decoder_destroy(long long dec);
+
 /* Row `token` (or *token_dev when token_dev != NULL) of a registered Q4_K / Q6_K matrix as int64 at 2^frac:
  * the embedding look-up (north-mini-code/src/nmc/engine.py:239-243). */
 int iie_embed_dev(long long h, const int *token_dev, long long token, int frac, int64_t *out_dev, void *stream);

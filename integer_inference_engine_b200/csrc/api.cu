@@ -644,11 +644,13 @@ extern "C" long long qk_resident_capacity(void) {
 }
 
 extern "C" void iie_moe_layer_destroy(long long layer);
+static void iie_decoders_drop();
 
 extern "C" void qk_free_all(void) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (g_ready != 0) { std::vector<Weight>().swap(g_w); return; }
     cudaStreamSynchronize(g_stream);
+    iie_decoders_drop();
     for (size_t i = 0; i < g_layers.size(); i++) iie_moe_layer_destroy((long long)i);
     g_layers.clear();
     for (auto &w : g_w) if (w.live && w.d) { cudaFree(w.d); prof(PM_FREE_CALLS); }
@@ -1357,6 +1359,148 @@ extern "C" int iie_moe_block_host(long long layer, long long gain_h, const int64
     if (!d2h(out, od, n * 8) || (ids_out && !d2h(ids_out, idd, P * sizeof(int))) ||
         (gates_out && !d2h(gates_out, gd, P * 8)) || !sync()) { cudaGetLastError(); return 1; }
     return 0;
+}
+
+// ====================================================================================================
+// Whole decode step in one launch (decode.cu)
+// ====================================================================================================
+namespace {
+struct DecoderObj {
+    bool live = false, dirty = true;
+    int n_layers = 0, n_set = 0, n_ctas = 0;
+    DecodeArgs a = {};                               // model-wide arguments; per-call fields are filled in by the step
+    std::vector<DecodeLayer> layers;
+    std::vector<bool> set;
+    DecodeLayer *layers_dev = nullptr;
+    uint8_t *scratch = nullptr;
+    int down_q = -1;
+};
+std::vector<DecoderObj> g_decoders;
+bool valid_decoder(long long h) { return h >= 0 && (size_t)h < g_decoders.size() && g_decoders[(size_t)h].live; }
+
+void free_decoder(DecoderObj &d) {
+    if (g_stream) cudaDeviceSynchronize();
+    if (d.layers_dev) cudaFree(d.layers_dev);
+    if (d.scratch) cudaFree(d.scratch);
+    d = DecoderObj();
+}
+}  // namespace
+
+extern "C" long long iie_decoder_create(int n_layers, int n_heads, int n_kv, int head_dim, long long window, long long cache_rows,
+                                        int fa, int fw, unsigned long long eps, long long inv_sqrt, const int64_t *cos_dev,
+                                        const int64_t *sin_dev) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || n_layers <= 0 || n_layers > 4096 || n_heads <= 0 || n_kv <= 0 || head_dim <= 0 || cache_rows <= 0 || fa < 1 ||
+        fa > 29 || fw < 24 || fw > 36 || !cos_dev || !sin_dev || window < 0) return -1;
+    DecoderObj d;
+    d.live = true; d.n_layers = n_layers; d.layers.resize((size_t)n_layers); d.set.assign((size_t)n_layers, false);
+    d.a.n_layers = n_layers; d.a.H = n_heads; d.a.Hkv = n_kv; d.a.hd = head_dim; d.a.window = window; d.a.Lmax = cache_rows;
+    d.a.fa = fa; d.a.fw = fw; d.a.eps = eps; d.a.cos = cos_dev; d.a.sin = sin_dev; d.a.flags = g_flags;
+    AttnArgs tmp = {};
+    attn_consts(tmp, fa, inv_sqrt);
+    d.a.inv_sqrt = tmp.inv_sqrt; d.a.log2e = tmp.log2e; d.a.clip = tmp.clip;
+    d.a.sig_log2e = sigmoid_log2e(fa); d.a.sig_clip = sigmoid_clip(fa);
+    size_t slot = g_decoders.size();
+    for (size_t i = 0; i < g_decoders.size(); i++) if (!g_decoders[i].live) { slot = i; break; }
+    if (slot == g_decoders.size()) g_decoders.push_back(DecoderObj());
+    g_decoders[slot] = std::move(d);
+    return (long long)slot;
+}
+
+extern "C" int iie_decoder_set_layer(long long dec, int li, long long gain_h, long long moe_layer, long long wqkv_h, long long wo_h,
+                                     int32_t *kcache_dev, int32_t *vcache_dev, int full) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!valid_decoder(dec)) return 1;
+    DecoderObj &d = g_decoders[(size_t)dec];
+    if (li < 0 || li >= d.n_layers || moe_layer < 0 || (size_t)moe_layer >= g_layers.size() || !g_layers[moe_layer].live ||
+        !valid_i64(gain_h) || !valid_q(wqkv_h) || !valid_q(wo_h) || !kcache_dev || !vcache_dev) return 1;
+    const MoeLayer &L = g_layers[moe_layer];
+    if (L.router < 0) return 1;
+    const Weight &r = g_w[L.router], &wq = g_w[wqkv_h], &wo = g_w[wo_h], &gain = g_w[gain_h];
+    const DecodeArgs &a = d.a;
+    const long long qd = (long long)a.H * a.hd, kd = (long long)a.Hkv * a.hd;
+    if (gain.out_f != 1 || gain.nb != L.d_model || wq.nb * 256 != L.d_model || wq.out_f != qd + 2 * kd || wo.nb * 256 != qd ||
+        wo.out_f != L.d_model) return 1;
+    // what the one-launch kernel carries: Q4_K router / attention / gate / up matrices with small block scales
+    if (r.qtype != QT_Q4K || wq.qtype != QT_Q4K || wo.qtype != QT_Q4K || L.gate_q != QT_Q4K) return 5;
+    if (!small_scales(r.maxd, r.maxdmin, a.fw) || !small_scales(wq.maxd, wq.maxdmin, a.fw) || !small_scales(wo.maxd, wo.maxdmin, a.fw) ||
+        !small_scales(L.maxd_gate, L.maxdmin_gate, a.fw) || !small_scales(L.maxd_down, L.maxdmin_down, a.fw)) return 5;
+    if (!fast_envelope(QT_Q4K, r.nb, r.maxd, r.maxdmin, a.fw) || !fast_envelope(QT_Q4K, wq.nb, wq.maxd, wq.maxdmin, a.fw) ||
+        !fast_envelope(QT_Q4K, wo.nb, wo.maxd, wo.maxdmin, a.fw) ||
+        !fast_envelope(QT_Q4K, L.d_model / 256, L.maxd_gate, L.maxdmin_gate, a.fw) ||
+        !fast_envelope(L.down_q, L.e_ffn / 256, L.maxd_down, L.maxdmin_down, a.fw)) return 5;
+    if (d.n_set == 0) {
+        d.a.d = (int)L.d_model; d.a.E = L.n_experts; d.a.k = L.top_k; d.a.eff = (int)L.e_ffn; d.down_q = L.down_q;
+        if (!decode_shape_ok(d.a.d, a.H, a.Hkv, a.hd, d.a.E, d.a.k, d.a.eff, L.down_q)) return 5;
+    } else if (d.a.d != L.d_model || d.a.E != L.n_experts || d.a.k != L.top_k || d.a.eff != L.e_ffn) return 1;
+    if (!decode_shape_ok(d.a.d, a.H, a.Hkv, a.hd, d.a.E, d.a.k, d.a.eff, L.down_q)) return 5;
+    DecodeLayer &y = d.layers[(size_t)li];
+    y.gain = (const int64_t *)gain.d; y.router = (const uint8_t *)r.d; y.wqkv = (const uint8_t *)wq.d; y.wo = (const uint8_t *)wo.d;
+    y.tabs = L.tabs; y.kcache = kcache_dev; y.vcache = vcache_dev; y.full = full ? 1 : 0; y.down_q = L.down_q;
+    if (!d.set[(size_t)li]) { d.set[(size_t)li] = true; d.n_set++; }
+    d.dirty = true;
+    return 0;
+}
+
+extern "C" int iie_decoder_step_dev(long long dec, int64_t *x_dev, long long pos_bound, const int *pos_dev, int *ids_out_dev,
+                                    int64_t *gates_out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!valid_decoder(dec) || !x_dev) return 1;
+    DecoderObj &d = g_decoders[(size_t)dec];
+    if (d.n_set != d.n_layers || pos_bound < 0 || pos_bound >= d.a.Lmax) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (d.n_ctas == 0) {
+        d.n_ctas = decode_max_ctas(d.a.d, d.a.H, d.a.Hkv, d.a.hd, d.a.E, d.a.eff);
+        if (d.n_ctas < d.a.Hkv) { d.n_ctas = -1; }
+    }
+    if (d.n_ctas < 0) return 5;
+    // history keys the longest-sighted block sees at the bound: every one must fit this launch's key chunks
+    bool any_full = false;
+    for (const auto &y : d.layers) any_full = any_full || y.full || d.a.window <= 0;
+    const long long hist = any_full ? pos_bound : std::min(pos_bound, d.a.window - 1);
+    if (hist > decode_key_capacity(d.n_ctas, d.a.Hkv, d.a.hd)) return 5;
+    if (!d.scratch) {
+        const DecodeArgs &a = d.a;
+        const size_t qkv = (size_t)(a.H + 2 * a.Hkv) * a.hd * 8, lg = (size_t)a.E * 8, gul = (size_t)a.k * 8 * a.eff;
+        const size_t st = (size_t)2 * a.H * 16, acc = (size_t)2 * a.H * a.hd * 8;
+        auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+        const size_t total = up(qkv) + up(lg) + up(gul) + up(st) + up(acc) + 256;
+        if (cudaMalloc(&d.scratch, total) != cudaSuccess || cudaMalloc(&d.layers_dev, sizeof(DecodeLayer) * (size_t)d.n_layers) != cudaSuccess) {
+            cudaGetLastError();
+            if (d.scratch) { cudaFree(d.scratch); d.scratch = nullptr; }
+            return 1;
+        }
+        uint8_t *p = d.scratch;
+        d.a.qkv = (int64_t *)p; p += up(qkv);
+        d.a.logits = (int64_t *)p; p += up(lg);
+        d.a.gul = (int8_t *)p; p += up(gul);
+        d.a.hmax = (long long *)p; d.a.Z = (unsigned long long *)(p + (size_t)2 * a.H * 8); p += up(st);
+        d.a.acc = (long long *)p; p += up(acc);
+        d.a.bars = (unsigned *)p;
+    }
+    if (d.dirty) {
+        // a synchronous copy: the table must not change under a launch that is still running
+        if (cudaDeviceSynchronize() != cudaSuccess ||
+            cudaMemcpy(d.layers_dev, d.layers.data(), sizeof(DecodeLayer) * (size_t)d.n_layers, cudaMemcpyHostToDevice) != cudaSuccess) {
+            cudaGetLastError(); return 1;
+        }
+        d.dirty = false;
+    }
+    DecodeArgs a = d.a;
+    a.layers = d.layers_dev; a.x = x_dev; a.pos_bound = pos_bound; a.pos_dev = pos_dev; a.ids_out = ids_out_dev; a.gates_out = gates_out_dev;
+    if (launch_decode(a, d.n_ctas, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    g_hl_d = 0;                                           // no digit planes of a single-token block are on hand any more
+    return 0;
+}
+
+static void iie_decoders_drop() {
+    for (auto &d : g_decoders) if (d.live) free_decoder(d);
+    g_decoders.clear();
+}
+
+extern "C" void iie_decoder_destroy(long long dec) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (valid_decoder(dec)) free_decoder(g_decoders[(size_t)dec]);
 }
 
 // ====================================================================================================

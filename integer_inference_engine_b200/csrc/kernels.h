@@ -223,6 +223,45 @@ cudaError_t launch_embed_row(const uint8_t *w, int qtype, long long nb, const in
                              int64_t *out, cudaStream_t s);
 cudaError_t launch_argmax(const int64_t *x, long long n, int *out, cudaStream_t s);
 
+// Whole decode step as one persistent cooperative kernel (decode.cu).
+struct DecodeLayer {
+    const int64_t *gain;           // [d] RMSNorm gain of the block
+    const uint8_t *router;         // repacked Q4_K [E, d]
+    const uint8_t *wqkv;           // repacked Q4_K [(H + 2 Hkv) * hd, d]: rows of Wq, Wk, Wv stacked
+    const uint8_t *wo;             // repacked Q4_K [d, H * hd]
+    const uint8_t *const *tabs;    // device [3][E]: gate, up, down pointers of the block's experts
+    int32_t *kcache, *vcache;      // [Hkv][Lmax][hd]
+    int full;                      // 1: attends to every key, no rotation; 0: sliding window + interleaved RoPE
+    int down_q;                    // quantisation type of the down matrices
+};
+struct DecodeArgs {
+    const DecodeLayer *layers;     // device [n_layers]
+    int n_layers;
+    int d, H, Hkv, hd, E, k, eff, fa, fw;
+    unsigned long long eps;
+    long long window, Lmax;
+    const int64_t *cos, *sin;      // [Lmax][hd/2] at 2^fa
+    const int *pos_dev;            // position of the token (device cell), or nullptr: pos_bound is the position
+    long long pos_bound;
+    int64_t *x;                    // residual row [d]: input of the first block, output of the last
+    int64_t *qkv;                  // scratch [(H + 2 Hkv) * hd]
+    int64_t *logits;               // scratch [E]
+    int8_t *gul;                   // scratch [k][8][eff]: digit planes of silu(gate) * up of the routed experts
+    long long *hmax;               // scratch [2][H] row maxima, by block parity
+    unsigned long long *Z;         // scratch [2][H] normalisers
+    long long *acc;                // scratch [2][H * hd] probability-value sums
+    unsigned *bars;                // scratch [6] arrival counters (zeroed by the launcher)
+    int *ids_out;                  // optional [n_layers][k]: routed experts of every block
+    int64_t *gates_out;            // optional [n_layers][k]
+    int *flags;                    // bit 0 digit envelope, 1 RMSNorm envelope, 2 K/V beyond int32, 3 a wait gave up,
+                                   // 4 position beyond the bound, 5 a query value beyond int32
+    long long inv_sqrt, log2e, clip, sig_log2e, sig_clip;
+};
+bool decode_shape_ok(int d, int H, int Hkv, int hd, int E, int k, int eff, int down_q);
+int decode_max_ctas(int d, int H, int Hkv, int hd, int E, int eff);      // CTAs of one cooperative launch (0: unavailable)
+long long decode_key_capacity(int n_ctas, int Hkv, int hd);             // cached keys per KV head one launch can hold
+cudaError_t launch_decode(const DecodeArgs &a, int n_ctas, cudaStream_t s);
+
 // Q1_0 linear (q1.cu).  Units: 16-row tiles x 128-weight blocks, 256 B of sign bits in MMA order + 16 scales.
 size_t q1_unit_bytes(bool sc32);
 cudaError_t launch_q1_repack(const uint8_t *bits, const void *scale, int src_bits, bool sc32, long long out_f, long long nb,

@@ -153,6 +153,63 @@ def attention_block(wqkv: int, wo: int, x: torch.Tensor, kcache: torch.Tensor, v
         raise CudaContextError(f"attention block failed with status {rc}")
 
 
+class DecoderKernel:
+    """All blocks of a decoder as one launch per token (``iie_decoder_*``).  ``layers`` = sequence of dicts with ``gain``
+    (dense int64 handle), ``moe`` (:class:`MoELayer` with its router), ``wqkv``, ``wo`` (handles), ``k``, ``v`` (int32 CUDA
+    caches [n_kv, rows, head_dim]) and ``full`` (bool).  Raises :class:`UnsupportedShape` when the model is outside what the
+    one-launch kernel carries; the caller then keeps the per-block entries."""
+
+    class UnsupportedShape(RuntimeError):
+        pass
+
+    def __init__(self, layers, n_heads: int, n_kv: int, head_dim: int, window: int, cos: torch.Tensor, sin: torch.Tensor,
+                 fa: int = 16, fw: int = 24, eps: int = 1, inv_sqrt: int | None = None):
+        lib = qk_cuda._lib()
+        rows = int(layers[0]["k"].shape[1])
+        if inv_sqrt is None:
+            inv_sqrt = int(round((1.0 / head_dim ** 0.5) * (1 << fa)))
+        assert cos.is_cuda and sin.is_cuda and cos.dtype == torch.int64 and cos.is_contiguous() and sin.is_contiguous()
+        assert cos.shape[0] >= rows and cos.shape[1] == head_dim // 2
+        with _CUDA_LOCK:
+            self.handle = int(lib.iie_decoder_create(len(layers), n_heads, n_kv, head_dim, int(window or 0), rows, int(fa), int(fw),
+                                                     int(eps), int(inv_sqrt), cos.data_ptr(), sin.data_ptr()))
+        if self.handle < 0:
+            raise self.UnsupportedShape("decoder shape rejected")
+        self._keep = (cos, sin, [(L["k"], L["v"]) for L in layers])          # the kernel reads these: keep them alive
+        for li, L in enumerate(layers):
+            k, v = L["k"], L["v"]
+            assert k.dtype == torch.int32 and v.dtype == torch.int32 and k.is_contiguous() and v.is_contiguous()
+            assert k.shape == v.shape == (n_kv, rows, head_dim)
+            with _CUDA_LOCK:
+                rc = lib.iie_decoder_set_layer(self.handle, li, int(L["gain"]), int(L["moe"].handle), int(L["wqkv"]), int(L["wo"]),
+                                               k.data_ptr(), v.data_ptr(), 1 if L["full"] else 0)
+            if rc != 0:
+                self.close()
+                if rc == 5:
+                    raise self.UnsupportedShape(f"block {li} is outside what the one-launch kernel carries")
+                raise CudaContextError(f"decoder block {li} rejected with status {rc}")
+
+    def step(self, x: torch.Tensor, pos_bound: int, pos_dev: torch.Tensor | None = None, ids_out: torch.Tensor | None = None,
+             gates_out: torch.Tensor | None = None) -> None:
+        """x [1, d_model] int64 updated in place through every block, on the current stream."""
+        assert x.is_cuda and x.dtype == torch.int64 and x.is_contiguous()
+        with _CUDA_LOCK:
+            rc = qk_cuda._lib().iie_decoder_step_dev(self.handle, x.data_ptr(), int(pos_bound),
+                                                     pos_dev.data_ptr() if pos_dev is not None else None,
+                                                     ids_out.data_ptr() if ids_out is not None else None,
+                                                     gates_out.data_ptr() if gates_out is not None else None, _stream_ptr())
+        if rc == 5:
+            raise self.UnsupportedShape("the visible cache rows exceed what one launch holds")
+        if rc != 0:
+            raise CudaContextError(f"decoder step failed with status {rc}")
+
+    def close(self) -> None:
+        if self.handle >= 0:
+            with _CUDA_LOCK:
+                qk_cuda._lib().iie_decoder_destroy(self.handle)
+            self.handle = -1
+
+
 def embed(handle: int, token, d_model: int, fa: int = 16, out: torch.Tensor | None = None) -> torch.Tensor:
     """Row ``token`` (an int, or a CUDA int32 tensor holding it) of a registered matrix at 2**fa -> [1, d_model]."""
     lib = qk_cuda._lib()

@@ -40,7 +40,7 @@ class Decoder:
     [n_kv, rows, head_dim]); ``moe_layers[i]`` / ``gain_handles[i]`` the MoE layer and the block's norm gain."""
 
     def __init__(self, *, d_model, n_heads, n_kv, head_dim, top_k, vocab, window, fa, fw, attn, moe_layers, gain_handles,
-                 embd, out_gain_h, cos, sin, position):
+                 embd, out_gain_h, cos, sin, position, one_launch=True):
         self.d, self.H, self.Hkv, self.hd = d_model, n_heads, n_kv, head_dim
         self.vocab, self.fa, self.fw, self.window, self.top_k = vocab, fa, fw, window, top_k
         self.attn, self.moe_layers, self.gain_handles = attn, moe_layers, gain_handles
@@ -54,10 +54,20 @@ class Decoder:
         z = lambda n: torch.empty((1, n), dtype=torch.int64, device="cuda")
         self.x, self.hn, self.logits = z(d_model), z(d_model), z(vocab)
         self._graph = None
+        # every block in one launch where the shape allows it; otherwise two entries per block
+        self.kernel = None
+        if one_launch:
+            try:
+                self.kernel = device.DecoderKernel(
+                    [{"gain": gain_handles[i], "moe": moe_layers[i], "wqkv": attn[i]["wqkv"], "wo": attn[i]["wo"], "k": attn[i]["k"],
+                      "v": attn[i]["v"], "full": self.layer_is_full(i)} for i in range(self.n_layers)],
+                    n_heads, n_kv, head_dim, window, cos, sin, fa, fw)
+            except device.DecoderKernel.UnsupportedShape:
+                self.kernel = None
 
     @classmethod
     def from_raw(cls, layers, embd_raw, out_gain, *, d_model, n_heads, n_kv, head_dim, e_ffn, top_k, vocab, window, rows,
-                 rope_base=50000.0, fa=16, fw=24, caches=None, position=0):
+                 rope_base=50000.0, fa=16, fw=24, caches=None, position=0, one_launch=True):
         """``layers[i]`` = dict(gain int64 [d]; wq, wk, wv, wo raw Q4_K bytes; moe=(router, gates, ups, downs) raw Q4_K /
         Q4_K / Q4_K / Q6_K bytes), as a GGUF reader hands them over; ``embd_raw`` the tied Q6_K matrix [vocab, d].
         ``caches[i]`` = (k, v) int64 arrays [n_kv, filled, head_dim] already in the cache (after rotation)."""
@@ -85,7 +95,7 @@ class Decoder:
         cos, sin = rope_tables(rows, head_dim, rope_base, fa)
         return cls(d_model=d_model, n_heads=n_heads, n_kv=n_kv, head_dim=head_dim, top_k=top_k, vocab=vocab, window=window,
                    fa=fa, fw=fw, attn=attn, moe_layers=moe_layers, gain_handles=gains, embd=embd, out_gain_h=out_gain_h,
-                   cos=torch.from_numpy(cos).cuda(), sin=torch.from_numpy(sin).cuda(), position=position)
+                   cos=torch.from_numpy(cos).cuda(), sin=torch.from_numpy(sin).cuda(), position=position, one_launch=one_launch)
 
     def layer_is_full(self, li: int) -> bool:
         return li % SWA_PERIOD == 0
@@ -104,7 +114,14 @@ class Decoder:
     def _launch_step(self, pos_bound: int) -> None:
         fa, fw = self.fa, self.fw
         device.embed(self.embd, self.token, self.d, fa, out=self.x)
-        for li in range(self.n_layers):
+        done = False
+        if self.kernel is not None:
+            try:
+                self.kernel.step(self.x, pos_bound, self.pos)
+                done = True
+            except device.DecoderKernel.UnsupportedShape:      # more visible cache rows than one launch holds
+                done = False
+        for li in range(0 if not done else self.n_layers, self.n_layers):
             a = self.attn[li]
             full = self.layer_is_full(li)
             # MoE half first: it normalises x, leaves the digit planes of h in the library and adds moe(h) to x;
@@ -172,7 +189,8 @@ class Decoder:
 class SyntheticDecoder(Decoder):
     def __init__(self, n_layers: int = 48, d_model: int = 2048, n_heads: int = 32, n_kv: int = 4, head_dim: int = 128,
                  e_ffn: int = 768, n_experts: int = 128, top_k: int = 8, vocab: int = 151936, context: int = 4096,
-                 max_new: int = 160, window: int = 4096, rope_base: float = 50000.0, seed: int = 1, fa: int = 16, fw: int = 24):
+                 max_new: int = 160, window: int = 4096, rope_base: float = 50000.0, seed: int = 1, fa: int = 16, fw: int = 24,
+                 one_launch: bool = True):
         rows = context + max_new
         self.moe = SyntheticMoEStack(n_layers, d_model, e_ffn, n_experts, top_k, seed=seed, fa=fa)
         nb = d_model // 256
@@ -196,7 +214,7 @@ class SyntheticDecoder(Decoder):
         super().__init__(d_model=d_model, n_heads=n_heads, n_kv=n_kv, head_dim=head_dim, top_k=top_k, vocab=vocab, window=window,
                          fa=fa, fw=fw, attn=attn, moe_layers=self.moe.layers, gain_handles=self.moe.gains, embd=embd,
                          out_gain_h=qk_cuda.register_i64(gain.cpu().numpy()), cos=torch.from_numpy(cos).cuda(),
-                         sin=torch.from_numpy(sin).cuda(), position=context)
+                         sin=torch.from_numpy(sin).cuda(), position=context, one_launch=one_launch)
         self.context = context
 
     def weight_bytes_per_token(self) -> int:

@@ -46,6 +46,7 @@ EXPORTED_SYMBOLS = (
     "iie_launch_count", "iie_prefill_launch_counts", "iie_workspace_generation", "iie_moe_block_host", "iie_moe_block_dev", "iie_set_pdl",
     "iie_apply_dev_static", "iie_set_tc_min_tokens", "iie_route_dev", "iie_moe_experts_dev",
     "iie_attn_decode_dev", "iie_embed_dev", "iie_argmax_dev", "iie_attn_block_dev", "iie_set_attn_fused",
+    "iie_decoder_create", "iie_decoder_set_layer", "iie_decoder_step_dev", "iie_decoder_destroy",
 )
 # The library keeps one registry and one set of workspaces per process and ctypes releases the GIL:
 # serialise callers here as the reference bridge does (qk_cuda.py:35-38).
@@ -115,6 +116,9 @@ def load_library():
         "iie_set_tc_min_tokens": ([i64], None), 
         "iie_attn_decode_dev": ([vp, vp, vp, vp, vp, i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, i64, vp, vp], c_int),
         "iie_attn_prefill_dev": ([vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, i64, vp, vp], c_int),
+        "iie_decoder_create": ([c_int, c_int, c_int, c_int, i64, i64, c_int, c_int, u64, i64, vp, vp], i64),
+        "iie_decoder_set_layer": ([i64, c_int, i64, i64, i64, i64, vp, vp, c_int], c_int),
+        "iie_decoder_step_dev": ([i64, vp, i64, vp, vp, vp, vp], c_int), "iie_decoder_destroy": ([i64], None),
         "iie_prefill_launch_counts": ([ctypes.POINTER(ctypes.c_uint64), c_int], c_int), "iie_workspace_generation": ([], u64),
         "iie_attn_block_dev": ([i64, i64, vp, vp, vp, i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, c_int, i64, vp], c_int),
         "iie_embed_dev": ([i64, vp, i64, c_int, vp, vp], c_int), "iie_set_attn_fused": ([c_int], None), "iie_argmax_dev": ([vp, i64, vp, vp], c_int),

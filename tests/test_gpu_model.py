@@ -33,14 +33,16 @@ def _host_view(model):
     return layers, embd, model.out_gain.cpu().numpy(), cfg
 
 
-def test_decode_steps_match_the_checker_eager_and_replayed():
+@pytest.mark.parametrize("one_launch", [True, False], ids=["all-blocks-in-one-launch", "two-entries-per-block"])
+def test_decode_steps_match_the_checker_eager_and_replayed(one_launch):
     import torch
 
     from integer_inference_engine_b200 import device, qk_cuda as qk
     from integer_inference_engine_b200.model import SyntheticDecoder
     qk.free_all()
     model = SyntheticDecoder(n_layers=5, d_model=512, n_heads=8, n_kv=2, head_dim=64, e_ffn=256, n_experts=8, top_k=2,
-                             vocab=1000, context=40, max_new=12, window=16, seed=3)
+                             vocab=1000, context=40, max_new=12, window=16, seed=3, one_launch=one_launch)
+    assert (model.kernel is not None) == one_launch
     layers, embd, out_gain, cfg = _host_view(model)
     cos, sin = model.cos.cpu().numpy(), model.sin.cpu().numpy()
     tok, pos = 123, model.context
@@ -95,7 +97,8 @@ def test_replay_is_refused_after_the_workspaces_changed():
     qk.free_all()
 
 
-def test_reference_recorded_decode_steps(golden_dir):
+@pytest.mark.parametrize("one_launch", [True, False], ids=["all-blocks-in-one-launch", "two-entries-per-block"])
+def test_reference_recorded_decode_steps(golden_dir, one_launch):
     """Three decode steps recorded from the reference's own block_cached / tied_head_int (tests/golden/nmc_decode.npz): the
     device decoder built from the same raw tensors and prompt caches yields the same picks, residual rows and cache rows."""
     import torch
@@ -110,7 +113,8 @@ def test_reference_recorded_decode_steps(golden_dir):
     dec = Decoder.from_raw(m["layers"], m["embd"], m["out_gain"], d_model=case["d"], n_heads=case["H"], n_kv=case["Hkv"],
                            head_dim=case["hd"], e_ffn=case["eff"], top_k=case["k"], vocab=case["vocab"], window=case["window"],
                            rows=case["rows"], rope_base=case["rope_base"], caches=[(g[f"k{li}"], g[f"v{li}"]) for li in range(2)],
-                           position=n_prompt)
+                           position=n_prompt, one_launch=one_launch)
+    assert (dec.kernel is not None) == one_launch
     assert np.array_equal(dec.cos.cpu().numpy(), g["cos"]) and np.array_equal(dec.sin.cpu().numpy(), g["sin"])
     dec.token.fill_(int(g["picks"][0]))
     for step in range(case["steps"]):
