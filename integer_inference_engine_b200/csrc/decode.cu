@@ -59,10 +59,33 @@ enum { KIND_P0 = 0, KIND_G, KIND_D, KIND_O };
 __device__ __forceinline__ uint32_t dk_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cbar() { asm volatile("bar.sync 1, %0;" ::"n"(DK_CT) : "memory"); }   // consumer warps only
 
-struct Ring {
-    uint64_t *full, *empty;                      // [DK_NS] each
+// Everything the warps of a CTA share lives in shared memory (one copy per CTA, broadcast reads), never in per-thread
+// structures: a per-thread copy would sit in local memory, and with 200+ KB of shared memory in use the L1 left for
+// local memory is a few tens of KB.
+struct Geo {
+    int nb, nbo, nbd;                 // 256-column blocks of d_model, of n_heads*head_dim, of e_ffn
+    int t_qkv, t_r, n_p0;             // 16-row tiles of Wqkv and of the router; together
+    int nht_g, n_g;                   // 8-row units of one expert's gate (= up) matrix; gate/up tiles of all routed experts
+    int td, TD, ipe, n_d;             // down: tiles per expert, tiles per ring item, items per expert, items of all routed experts
+    int to, okn;                      // O: row tiles; ring slots per tile (K chunks of <= 8 blocks)
+    int htb_d;                        // bytes of a down unit block
+    int cpk, kps;                     // CTAs per KV head, keys per ring slot
+};
+
+struct Shared {
+    uint64_t full[DK_NS], empty[DK_NS], idsbar;           // mbarriers
+    Geo g;
     uint8_t *slots;
-    volatile int *abort_flag;
+    unsigned long long *red;                              // [DK_NS][2][128]
+    int done[DK_NS * 2], slot_done[DK_NS];                // blocks of each tile already added; tiles of each item finished
+    int ids[DK_MAXK];
+    int64_t gates[DK_MAXK];
+    const uint8_t *sel[3 * DK_MAXK];
+    unsigned long long lo[DK_CW], hi[DK_CW], mx[DK_CW], gmx[DK_CW];
+    unsigned long long rms, inv, gm;
+    long long hmax[DK_MAXREP];
+    unsigned long long z[DK_MAXREP];
+    int bad, nl, abort;
 };
 
 __device__ __forceinline__ bool mb_try(uint64_t *bar, uint32_t parity) {
@@ -72,7 +95,8 @@ __device__ __forceinline__ bool mb_try(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded, abort-aware wait: false when the phase never completed (the caller skips the work that needed it).
-__device__ __forceinline__ bool mb_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mb_wait(uint64_t *bar, uint32_t parity, int *abort_ptr) {
+    volatile int *abort_flag = abort_ptr;
     for (unsigned it = 0; it < DK_POLLS; it++) {
         if (mb_try(bar, parity)) return true;
         if ((it & 255) == 255 && *abort_flag) return false;
@@ -94,7 +118,8 @@ __device__ __forceinline__ void grid_arrive(unsigned *bars, int id) {          /
     __threadfence();
     atomicAdd(bars + id, 1u);
 }
-__device__ __forceinline__ void grid_wait(unsigned *bars, int id, unsigned target, volatile int *abort_flag) {   // one thread
+__device__ __forceinline__ void grid_wait(unsigned *bars, int id, unsigned target, int *abort_ptr) {   // one thread
+    volatile int *abort_flag = abort_ptr;
     for (unsigned it = 0; it < DK_POLLS; it++) {
         unsigned v;
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(bars + id) : "memory");
@@ -106,16 +131,6 @@ __device__ __forceinline__ void grid_wait(unsigned *bars, int id, unsigned targe
 }
 
 // ---- geometry shared by the producer and the consumers ------------------------------------------------------------------
-struct Geo {
-    int nb, nbo, nbd;                 // 256-column blocks of d_model, of n_heads*head_dim, of e_ffn
-    int t_qkv, t_r, n_p0;             // 16-row tiles of Wqkv and of the router; together
-    int nht_g, n_g;                   // 8-row units of one expert's gate (= up) matrix; gate/up tiles of all routed experts
-    int td, TD, ipe, n_d;             // down: tiles per expert, tiles per ring item, items per expert, items of all routed experts
-    int to, okn;                      // O: row tiles; ring slots per tile (K chunks of <= 8 blocks)
-    int htb_d;                        // bytes of a down unit block
-    int cpk, kps;                     // CTAs per KV head, keys per ring slot
-};
-
 __device__ __forceinline__ Geo make_geo(const DecodeArgs &a, int down_q) {
     Geo g;
     g.nb = a.d / 256; g.nbo = a.H * a.hd / 256; g.nbd = a.eff / 256;
@@ -154,47 +169,48 @@ __device__ __forceinline__ Chunk make_chunk(const DecodeArgs &a, const Geo &g, l
 
 // ---- the producer: one lane streams every item of this CTA through the ring, in consumption order ----------------------
 struct Producer {
-    Ring ring;
-    unsigned seq;
-    uint32_t last_parity[DK_NS];
-    bool used[DK_NS];
+    Shared *sh;
+    unsigned seq, used_mask, parity_mask;                  // per slot: ever used; parity of its last request
 
-    __device__ bool acquire(int &slot) {
+    __device__ __forceinline__ bool acquire(int &slot) {
         slot = (int)(seq % DK_NS);
-        if (*ring.abort_flag) return false;
-        if (seq >= DK_NS && !mb_wait(&ring.empty[slot], ((seq / DK_NS) - 1) & 1, ring.abort_flag)) return false;
+        if (*(volatile int *)&sh->abort) return false;
+        if (seq >= DK_NS && !mb_wait(&sh->empty[slot], ((seq / DK_NS) - 1) & 1, &sh->abort)) return false;
         return true;
     }
-    __device__ void commit(int slot) { last_parity[slot] = (seq / DK_NS) & 1; used[slot] = true; seq++; }
-    __device__ bool one(const void *src, uint32_t bytes) {
+    __device__ __forceinline__ void commit(int slot) {
+        used_mask |= 1u << slot;
+        parity_mask = (parity_mask & ~(1u << slot)) | (((seq / DK_NS) & 1u) << slot);
+        seq++;
+    }
+    __device__ __forceinline__ bool one(const void *src, uint32_t bytes) {
         int slot;
         if (!acquire(slot)) return false;
-        mb_expect(&ring.full[slot], bytes);
-        dk_bulk(ring.slots + (size_t)slot * DK_SLOT, src, bytes, &ring.full[slot]);
+        mb_expect(&sh->full[slot], bytes);
+        dk_bulk(sh->slots + (size_t)slot * DK_SLOT, src, bytes, &sh->full[slot]);
         commit(slot);
         return true;
     }
-    __device__ bool two(const void *s0, const void *s1, uint32_t bytes_each) {
+    __device__ __forceinline__ bool two(const void *s0, const void *s1, uint32_t bytes_each) {
         int slot;
         if (!acquire(slot)) return false;
-        mb_expect(&ring.full[slot], 2 * bytes_each);
-        uint8_t *dst = ring.slots + (size_t)slot * DK_SLOT;
-        dk_bulk(dst, s0, bytes_each, &ring.full[slot]);
-        dk_bulk(dst + bytes_each, s1, bytes_each, &ring.full[slot]);
+        mb_expect(&sh->full[slot], 2 * bytes_each);
+        uint8_t *dst = sh->slots + (size_t)slot * DK_SLOT;
+        dk_bulk(dst, s0, bytes_each, &sh->full[slot]);
+        dk_bulk(dst + bytes_each, s1, bytes_each, &sh->full[slot]);
         commit(slot);
         return true;
     }
 };
 
-__device__ void producer_run(const DecodeArgs &a, Ring ring, uint64_t *ids_bar, const uint8_t *const *s_sel, long long pos) {
+__device__ __noinline__ void producer_run(const DecodeArgs &a, Shared *sh, long long pos) {
     Producer p;
-    p.ring = ring; p.seq = 0;
-    for (int s = 0; s < DK_NS; s++) { p.used[s] = false; p.last_parity[s] = 0; }
+    p.sh = sh; p.seq = 0; p.used_mask = 0; p.parity_mask = 0;
     const int c = (int)blockIdx.x, nc = (int)gridDim.x;
+    const Geo g = sh->g;
     bool ok = true;
     for (int L = 0; L < a.n_layers && ok; L++) {
         const DecodeLayer &ly = a.layers[L];
-        const Geo g = make_geo(a, ly.down_q);
         const long long lo = (!ly.full && a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
         const Chunk ch = make_chunk(a, g, pos, lo);
         int i0, i1;
@@ -216,15 +232,15 @@ __device__ void producer_run(const DecodeArgs &a, Ring ring, uint64_t *ids_bar, 
         share(g.n_g, c, nc, i0, i1);
         int d0, d1;
         share(g.n_d, c, nc, d0, d1);
-        if (ok && (i1 > i0 || d1 > d0)) ok = mb_wait(ids_bar, (uint32_t)(L & 1), ring.abort_flag);
+        if (ok && (i1 > i0 || d1 > d0)) ok = mb_wait(&sh->idsbar, (uint32_t)(L & 1), &sh->abort);
         for (int i = i0; i < i1 && ok; i++) {
             const int s = i / g.nht_g, u = i - s * g.nht_g;
-            ok = p.two(s_sel[s] + (size_t)u * g.nb * HTB_Q4K, s_sel[a.k + s] + (size_t)u * g.nb * HTB_Q4K, (uint32_t)(g.nb * HTB_Q4K));
+            ok = p.two(sh->sel[s] + (size_t)u * g.nb * HTB_Q4K, sh->sel[a.k + s] + (size_t)u * g.nb * HTB_Q4K, (uint32_t)(g.nb * HTB_Q4K));
         }
         for (int i = d0; i < d1 && ok; i++) {
             const int s = i / g.ipe, q = i - s * g.ipe;
             const int n_ht = a.d / 8, units = min(2 * g.TD, n_ht - 2 * q * g.TD);
-            ok = p.one(s_sel[2 * a.k + s] + (size_t)(2 * q * g.TD) * g.nbd * g.htb_d, (uint32_t)(units * g.nbd * g.htb_d));
+            ok = p.one(sh->sel[2 * a.k + s] + (size_t)(2 * q * g.TD) * g.nbd * g.htb_d, (uint32_t)(units * g.nbd * g.htb_d));
         }
         // values of the chunk
         for (int j = 0; j < ch.slots && ok; j++) {
@@ -242,32 +258,17 @@ __device__ void producer_run(const DecodeArgs &a, Ring ring, uint64_t *ids_bar, 
     }
     // copies of this lane still in flight must land before the CTA's shared memory goes away
     for (int s = 0; s < DK_NS; s++)
-        if (p.used[s]) {
+        if ((p.used_mask >> s) & 1u) {
             for (unsigned it = 0; it < DK_POLLS; it++)
-                if (mb_try(&ring.full[s], p.last_parity[s])) break;
+                if (mb_try(&sh->full[s], (p.parity_mask >> s) & 1u)) break;
         }
 }
 
 // ---- consumers: 16-row tiles of a ring item on the warp MMA, K split over the warps -------------------------------------
-struct Ctx {
-    const DecodeArgs *a;
-    const DecodeLayer *ly;
-    Geo g;
-    Ring ring;
-    unsigned long long *red;          // [DK_NS][2][128]
-    int *done;                        // [DK_NS][2] blocks of each tile already added; [DK_NS] tiles of each slot finished
-    int *slot_done;
-    int8_t *planes; int pstride;      // activation digit planes in shared memory [8][pstride]
-    const int *s_ids; const int64_t *s_gates;
-    int par;                          // parity of this block's statistics buffers
-    int tid, lane, warp;
-};
-
 // Epilogue of one finished tile: lanes 0..15 own its 16 rows (gate/up: lanes 0..7 own the 8 (gate, up) row pairs).
-template <int QT>
-__device__ __forceinline__ void tile_epilogue(const Ctx &cx, int kind, int gi, int tile_in_item, const volatile unsigned long long *rv, int lane) {
-    const DecodeArgs &a = *cx.a;
-    const Geo &g = cx.g;
+__device__ __forceinline__ void tile_epilogue(const DecodeArgs &a, const Shared *sh, int kind, int gi, int tile_in_item,
+                                              const volatile unsigned long long *rv, int lane) {
+    const Geo &g = sh->g;
     if (kind == KIND_P0) {
         const bool r = gi >= g.t_qkv;
         const int tile = r ? gi - g.t_qkv : gi;
@@ -302,7 +303,7 @@ __device__ __forceinline__ void tile_epilogue(const Ctx &cx, int kind, int gi, i
 #pragma unroll
             for (int c = 0; c < 8; c++) cc[c] = rv[lane * 8 + c];
             const int64_t y = recombine_cols(cc, a.fw);
-            atomicAdd(reinterpret_cast<unsigned long long *>(a.x + row), (unsigned long long)mul_shift(y, cx.s_gates[s], a.fa));
+            atomicAdd(reinterpret_cast<unsigned long long *>(a.x + row), (unsigned long long)mul_shift(y, sh->gates[s], a.fa));
         }
     } else {
         const long long row = (long long)gi * 16 + lane;
@@ -320,29 +321,28 @@ __device__ __forceinline__ void tile_epilogue(const Ctx &cx, int kind, int gi, i
 // last tile, hands the item's slots back to the producer.  An item is one slot holding one tile (P0, gate/up), one slot
 // holding up to two tiles (down), or one tile whose K blocks span several slots (O).
 template <int QT>
-__device__ __noinline__ void lin_items(const Ctx &cx, int kind, int i0, int i1, unsigned seq0, bool half, const int8_t *planes, int pstride) {
+__device__ __noinline__ void lin_items(const DecodeArgs &a, Shared *sh, int kind, int i0, int i1, unsigned seq0, bool half,
+                                       const int8_t *planes, int pstride) {
     constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
-    const DecodeArgs &a = *cx.a;
-    const Geo &g = cx.g;
-    const int lane = cx.lane, warp = cx.warp;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int gq = lane >> 2, t = lane & 3;
     uint32_t bf[16];
     int bcur = -1;
     int widx = 0;                                           // (tile, block) pairs of the earlier items: keeps the deal round-robin
-    const int sp = kind == KIND_O ? g.okn : 1;              // ring slots per item
+    const int sp = kind == KIND_O ? sh->g.okn : 1;          // ring slots per item
     for (int i = i0; i < i1; i++) {
-        int tiles = 1, nbk = g.nb, n_units = 2;
+        int tiles = 1, nbk = sh->g.nb, n_units = 2;
         if (kind == KIND_P0) {
-            const bool r = i >= g.t_qkv;
-            const int tile = r ? i - g.t_qkv : i, n_ht = r ? (a.E + 7) / 8 : (a.H + 2 * a.Hkv) * a.hd / 8;
+            const bool r = i >= sh->g.t_qkv;
+            const int tile = r ? i - sh->g.t_qkv : i, n_ht = r ? (a.E + 7) / 8 : (a.H + 2 * a.Hkv) * a.hd / 8;
             n_units = (2 * tile + 1 < n_ht) ? 2 : 1;
         } else if (kind == KIND_D) {
-            const int q = i % g.ipe;
-            nbk = g.nbd;
-            tiles = min(g.TD, g.td - q * g.TD);
-            n_units = min(2 * g.TD, a.d / 8 - 2 * q * g.TD);
+            const int q = i % sh->g.ipe;
+            nbk = sh->g.nbd;
+            tiles = min(sh->g.TD, sh->g.td - q * sh->g.TD);
+            n_units = min(2 * sh->g.TD, a.d / 8 - 2 * q * sh->g.TD);
         } else if (kind == KIND_O) {
-            nbk = g.nbo;
+            nbk = sh->g.nbo;
         }
         const unsigned first = seq0 + (unsigned)(i - i0) * (unsigned)sp;
         const int slot0 = (int)(first % DK_NS);
@@ -354,14 +354,14 @@ __device__ __noinline__ void lin_items(const Ctx &cx, int kind, int i0, int i1, 
             const unsigned sq = first + (unsigned)sj;
             const int slot = (int)(sq % DK_NS);
             // warp-uniform outcome: the MMA below needs every lane
-            if (!__all_sync(0xffffffffu, mb_wait(&cx.ring.full[slot], (sq / DK_NS) & 1, cx.ring.abort_flag))) break;
+            if (!__all_sync(0xffffffffu, mb_wait(&sh->full[slot], (sq / DK_NS) & 1, &sh->abort))) break;
             if (b != bcur) { load_bfrag<QT, false>(planes + col_limb(gq) * pstride + b * 256, t, bf); bcur = b; }
-            const uint8_t *sb = cx.ring.slots + (size_t)slot * DK_SLOT;
+            const uint8_t *sb = sh->slots + (size_t)slot * DK_SLOT;
             const uint8_t *ua = sb + (size_t)(2 * tj) * bps * HTB + (size_t)bl * HTB;
             const uint8_t *ub = (2 * tj + 1 < n_units) ? ua + (size_t)bps * HTB : ua;
             int64_t acc[4] = {0, 0, 0, 0};
             run_item<QT, true>(ua, ub, lane, a.fw, bf, half, acc);
-            unsigned long long *r = cx.red + ((size_t)slot0 * 2 + tj) * 128;
+            unsigned long long *r = sh->red + ((size_t)slot0 * 2 + tj) * 128;
             atomicAdd(&r[gq * 8 + 2 * t], (unsigned long long)acc[0]);
             atomicAdd(&r[(gq + 8) * 8 + 2 * t], (unsigned long long)acc[2]);
             if (!half) {
@@ -370,42 +370,115 @@ __device__ __noinline__ void lin_items(const Ctx &cx, int kind, int i0, int i1, 
             }
             __threadfence_block();
             int prior = 0;
-            if (lane == 0) prior = atomicAdd(&cx.done[slot0 * 2 + tj], 1);
+            if (lane == 0) prior = atomicAdd(&sh->done[slot0 * 2 + tj], 1);
             prior = __shfl_sync(0xffffffffu, prior, 0);
             if (prior != nbk - 1) continue;
             // last block of the tile: epilogue, then leave the accumulators clean for the slot's next use
             __threadfence_block();
-            tile_epilogue<QT>(cx, kind, i, tj, r, lane);
+            tile_epilogue(a, sh, kind, i, tj, r, lane);
             __syncwarp();
             for (int z = lane; z < 128; z += 32) r[z] = 0ULL;
-            if (lane == 0) cx.done[slot0 * 2 + tj] = 0;
+            if (lane == 0) sh->done[slot0 * 2 + tj] = 0;
             __threadfence_block();
             int fin = 0;
-            if (lane == 0) fin = atomicAdd(&cx.slot_done[slot0], 1);
+            if (lane == 0) fin = atomicAdd(&sh->slot_done[slot0], 1);
             fin = __shfl_sync(0xffffffffu, fin, 0);
             if (fin == tiles - 1 && lane == 0) {
-                cx.slot_done[slot0] = 0;
-                for (int q = 0; q < sp; q++) mb_arrive(&cx.ring.empty[(first + (unsigned)q) % DK_NS]);
+                sh->slot_done[slot0] = 0;
+                for (int q = 0; q < sp; q++) mb_arrive(&sh->empty[(first + (unsigned)q) % DK_NS]);
             }
         }
         widx += n_work;
     }
 }
 
+// h = rmsnorm(x) * gain as balanced digit planes in shared memory; returns through sh->nl the digits in use.
+__device__ __noinline__ void norm_planes(const DecodeArgs &a, Shared *sh, const int64_t *gain, int8_t *planes, int pstride) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, c = (int)blockIdx.x;
+    int64_t xv[DK_EPT], gv[DK_EPT];
+    u128 ssq = 0; unsigned long long mx = 0, gmx = 0;
+    const int i0 = tid * DK_EPT;
+#pragma unroll
+    for (int e = 0; e < DK_EPT; e++) {
+        const bool in = i0 + e < a.d;
+        xv[e] = in ? __ldcg(a.x + i0 + e) : 0;
+        gv[e] = in ? __ldg(gain + i0 + e) : 0;
+        const unsigned long long v = uabs64(xv[e]), gg = uabs64(gv[e]);
+        ssq += (u128)v * v; mx = v > mx ? v : mx; gmx = gg > gmx ? gg : gmx;
+    }
+    unsigned long long slo = (unsigned long long)ssq, shi = (unsigned long long)(ssq >> 64);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        const unsigned long long lo2 = __shfl_xor_sync(0xffffffffu, slo, s), hi2 = __shfl_xor_sync(0xffffffffu, shi, s);
+        const u128 sum = (((u128)shi << 64) | slo) + (((u128)hi2 << 64) | lo2);
+        slo = (unsigned long long)sum; shi = (unsigned long long)(sum >> 64);
+        const unsigned long long m2 = __shfl_xor_sync(0xffffffffu, mx, s), g2 = __shfl_xor_sync(0xffffffffu, gmx, s);
+        mx = m2 > mx ? m2 : mx; gmx = g2 > gmx ? g2 : gmx;
+    }
+    if (lane == 0) { sh->lo[warp] = slo; sh->hi[warp] = shi; sh->mx[warp] = mx; sh->gmx[warp] = gmx; }
+    if (tid == 0) { sh->bad = 0; sh->nl = 1; }
+    cbar();
+    if (tid == 0) {
+        u128 total = 0; unsigned long long m = 0, gm = 0;
+        for (int i = 0; i < DK_CW; i++) {
+            total += ((u128)sh->hi[i] << 64) | sh->lo[i];
+            m = sh->mx[i] > m ? sh->mx[i] : m; gm = sh->gmx[i] > gm ? sh->gmx[i] : gm;
+        }
+        if (m > (1ULL << 57)) sh->bad = 1;                 // keeps the 128-bit sum of squares exact
+        u128 mean;
+        if ((total >> 64) == 0) mean = (u128)((unsigned long long)total / (unsigned long long)a.d);
+        else mean = total / (u128)(unsigned long long)a.d;
+        const u128 rms = isqrt128(mean + a.eps);
+        if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) sh->bad = 1;
+        sh->rms = (unsigned long long)rms; sh->gm = gm;
+        sh->inv = rms != 0 ? 0xFFFFFFFFFFFFFFFFULL / (unsigned long long)rms : 0;
+    }
+    cbar();
+    const unsigned long long rms = sh->rms, inv = sh->inv, gm = sh->gm;
+    const bool dead = sh->bad != 0;                        // the row cannot be normalised exactly: zeros, flag raised
+    bool bad = false, over = false;
+    int nl = 1;
+    uint32_t pw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int e = 0; e < DK_EPT; e++) {
+        int64_t y = 0;
+        if (!dead && i0 + e < a.d) {
+            if (uabs64(xv[e]) < (1ULL << (62 - a.fa)) && rms < (1ULL << 62)) y = floor_div_recip(xv[e] * ((long long)1 << a.fa), rms, inv);
+            else {
+                const i128 num = (i128)xv[e] * ((i128)1 << a.fa);
+                i128 q = num / (i128)rms;
+                if (num < 0 && q * (i128)rms != num) q -= 1;
+                if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; q = 0; }
+                y = (int64_t)q;
+            }
+            if ((u128)uabs64(y) * gm > (u128)INT64_MAX) bad = true;      // the oracle refuses such a gain product
+            y = mul_shift(y, gv[e], a.fa);
+        }
+        bool ok;
+        const uint64_t dg = balanced_digits8(y, ok);
+        over |= !ok;
+        nl = max(nl, digits_used(dg));
+#pragma unroll
+        for (int l = 0; l < 8; l++) pw[l] |= (uint32_t)((dg >> (8 * l)) & 0xFF) << (8 * e);
+    }
+    if (i0 < a.d) {
+#pragma unroll
+        for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(planes + l * pstride + i0) = pw[l];
+    }
+    if ((bad || dead) && c == 0) atomicOr(a.flags, 2);
+    if (over && c == 0) atomicOr(a.flags, 1);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, s));
+    if (lane == 0) atomicMax(&sh->nl, nl);
+    cbar();
+}
+
 }  // namespace
 
-__global__ void __launch_bounds__(DK_THREADS, 1) decode_kernel(const DecodeArgs a) {
+__global__ void __launch_bounds__(DK_THREADS, 1) decode_kernel(const __grid_constant__ DecodeArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t s_full[DK_NS], s_empty[DK_NS], s_idsbar;
-    __shared__ int s_done[DK_NS * 2], s_slot_done[DK_NS];
-    __shared__ int s_ids[DK_MAXK];
-    __shared__ int64_t s_gates[DK_MAXK];
-    __shared__ const uint8_t *s_sel[3 * DK_MAXK];
-    __shared__ unsigned long long s_lo[DK_CW], s_hi[DK_CW], s_mx[DK_CW], s_gmx[DK_CW];
-    __shared__ unsigned long long s_rms, s_inv, s_gm;
-    __shared__ long long s_hmax[DK_MAXREP];
-    __shared__ unsigned long long s_z[DK_MAXREP];
-    __shared__ int s_bad, s_nl, s_abort;
+    __shared__ __align__(16) Shared sh_;
+    Shared *sh = &sh_;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int c = (int)blockIdx.x, nc = (int)gridDim.x;
@@ -431,47 +504,50 @@ __global__ void __launch_bounds__(DK_THREADS, 1) decode_kernel(const DecodeArgs 
 
     if (tid == 0) {
         for (int s = 0; s < DK_NS; s++) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dk_u32(&s_full[s])));
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dk_u32(&s_empty[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dk_u32(&sh->full[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dk_u32(&sh->empty[s])));
         }
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dk_u32(&s_idsbar)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dk_u32(&sh->idsbar)));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        s_abort = 0;
+        sh->abort = 0; sh->slots = slots; sh->red = red;
+        sh->g = make_geo(a, a.layers[0].down_q);
     }
     for (int i = tid; i < DK_NS * 2 * 128; i += DK_THREADS) red[i] = 0ULL;
-    for (int i = tid; i < DK_NS * 2; i += DK_THREADS) s_done[i] = 0;
-    for (int i = tid; i < DK_NS; i += DK_THREADS) s_slot_done[i] = 0;
+    for (int i = tid; i < DK_NS * 2; i += DK_THREADS) sh->done[i] = 0;
+    for (int i = tid; i < DK_NS; i += DK_THREADS) sh->slot_done[i] = 0;
     __syncthreads();
-    Ring ring = {s_full, s_empty, slots, &s_abort};
 
     if (warp == DK_CW) {                                     // ================= producer warp =================
-        if (lane == 0) producer_run(a, ring, &s_idsbar, s_sel, pos);
+        if (lane == 0) producer_run(a, sh, pos);
         __syncwarp();
-        if (lane == 0 && s_abort) atomicOr(a.flags, 8);
+        if (lane == 0 && sh->abort) atomicOr(a.flags, 8);
         return;
     }
 
     // ===================================== consumer warps =====================================
-    Ctx cx;
-    cx.a = &a; cx.ring = ring; cx.red = red; cx.done = s_done; cx.slot_done = s_slot_done; cx.planes = planes; cx.pstride = pstride;
-    cx.s_ids = s_ids; cx.s_gates = s_gates; cx.tid = tid; cx.lane = lane; cx.warp = warp;
     unsigned seq = 0;                                        // ring sequence number of this CTA's next item
     const int half_hd = a.hd / 2;
+    const int cpk = sh->g.cpk, kps = sh->g.kps;
 
     for (int L = 0; L < a.n_layers; L++) {
         const DecodeLayer &ly = a.layers[L];
-        const Geo g = make_geo(a, ly.down_q);
-        cx.ly = &ly; cx.g = g; cx.par = L & 1;
         const int par = L & 1;
-        const long long lo = (!ly.full && a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
-        const Chunk ch = make_chunk(a, g, pos, lo);
+        const bool full = ly.full != 0;
+        const long long lo = (!full && a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+        // this CTA's key chunk (make_chunk, kept in scalars)
+        const bool active = c < cpk * a.Hkv;
+        const int kv = active ? c / cpk : 0, ci = active ? c % cpk : 0;
+        const long long n_hist = pos - lo, per = (n_hist + cpk - 1) / cpk;
+        const long long ck0 = lo + (long long)ci * per, ck1 = min(ck0 + per, pos);
+        const int nk = active ? (int)max(0LL, ck1 - ck0) : 0, kslots = (nk + kps - 1) / kps;
+        const bool owner = active && ci == 0;
         const unsigned target = (unsigned)(L + 1) * (unsigned)nc;
         long long *hmax = a.hmax + par * a.H;
         unsigned long long *Z = a.Z + par * a.H;
         long long *acc = a.acc + (long long)par * a.H * a.hd;
 
         // ================================ P0: RMSNorm, Q/K/V and router rows ================================
-        if (L > 0) { if (tid == 0) grid_wait(a.bars, GB_X, (unsigned)L * (unsigned)nc, &s_abort); cbar(); }
+        if (L > 0) { if (tid == 0) grid_wait(a.bars, GB_X, (unsigned)L * (unsigned)nc, &sh->abort); cbar(); }
         if (c == 0) {                                        // statistics of the NEXT block (and, first of all, of this one)
             for (int pp = (L == 0 ? 0 : 1); pp < 2; pp++) {
                 const int q = (par + pp) & 1;
@@ -479,91 +555,14 @@ __global__ void __launch_bounds__(DK_THREADS, 1) decode_kernel(const DecodeArgs 
                 for (int i = tid; i < a.H * a.hd; i += DK_CT) a.acc[(long long)q * a.H * a.hd + i] = 0;
             }
         }
-        {
-            int64_t xv[DK_EPT], gv[DK_EPT];
-            u128 ssq = 0; unsigned long long mx = 0, gmx = 0;
-            const int i0 = tid * DK_EPT;
-#pragma unroll
-            for (int e = 0; e < DK_EPT; e++) {
-                const bool in = i0 + e < a.d;
-                xv[e] = in ? __ldcg(a.x + i0 + e) : 0;
-                gv[e] = in ? __ldg(ly.gain + i0 + e) : 0;
-                const unsigned long long v = uabs64(xv[e]), gg = uabs64(gv[e]);
-                ssq += (u128)v * v; mx = v > mx ? v : mx; gmx = gg > gmx ? gg : gmx;
-            }
-            unsigned long long slo = (unsigned long long)ssq, shi = (unsigned long long)(ssq >> 64);
-#pragma unroll
-            for (int s = 16; s > 0; s >>= 1) {
-                const unsigned long long lo2 = __shfl_xor_sync(0xffffffffu, slo, s), hi2 = __shfl_xor_sync(0xffffffffu, shi, s);
-                const u128 sum = (((u128)shi << 64) | slo) + (((u128)hi2 << 64) | lo2);
-                slo = (unsigned long long)sum; shi = (unsigned long long)(sum >> 64);
-                const unsigned long long m2 = __shfl_xor_sync(0xffffffffu, mx, s), g2 = __shfl_xor_sync(0xffffffffu, gmx, s);
-                mx = m2 > mx ? m2 : mx; gmx = g2 > gmx ? g2 : gmx;
-            }
-            if (lane == 0) { s_lo[warp] = slo; s_hi[warp] = shi; s_mx[warp] = mx; s_gmx[warp] = gmx; }
-            if (tid == 0) { s_bad = 0; s_nl = 1; }
-            cbar();
-            if (tid == 0) {
-                u128 total = 0; unsigned long long m = 0, gm = 0;
-                for (int i = 0; i < DK_CW; i++) {
-                    total += ((u128)s_hi[i] << 64) | s_lo[i];
-                    m = s_mx[i] > m ? s_mx[i] : m; gm = s_gmx[i] > gm ? s_gmx[i] : gm;
-                }
-                if (m > (1ULL << 57)) s_bad = 1;                 // keeps the 128-bit sum of squares exact
-                u128 mean;
-                if ((total >> 64) == 0) mean = (u128)((unsigned long long)total / (unsigned long long)a.d);
-                else mean = total / (u128)(unsigned long long)a.d;
-                const u128 rms = isqrt128(mean + a.eps);
-                if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) s_bad = 1;
-                s_rms = (unsigned long long)rms; s_gm = gm;
-                s_inv = rms != 0 ? 0xFFFFFFFFFFFFFFFFULL / (unsigned long long)rms : 0;
-            }
-            cbar();
-            const unsigned long long rms = s_rms, inv = s_inv, gm = s_gm;
-            const bool dead = s_bad != 0;                      // the row cannot be normalised exactly: zeros, flag raised
-            bool bad = false, over = false;
-            int nl = 1;
-            uint32_t pw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-            for (int e = 0; e < DK_EPT; e++) {
-                int64_t y = 0;
-                if (!dead && i0 + e < a.d) {
-                    if (uabs64(xv[e]) < (1ULL << (62 - a.fa)) && rms < (1ULL << 62)) y = floor_div_recip(xv[e] * ((long long)1 << a.fa), rms, inv);
-                    else {
-                        const i128 num = (i128)xv[e] * ((i128)1 << a.fa);
-                        i128 q = num / (i128)rms;
-                        if (num < 0 && q * (i128)rms != num) q -= 1;
-                        if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; q = 0; }
-                        y = (int64_t)q;
-                    }
-                    if ((u128)uabs64(y) * gm > (u128)INT64_MAX) bad = true;      // the oracle refuses such a gain product
-                    y = mul_shift(y, gv[e], a.fa);
-                }
-                bool ok;
-                const uint64_t dg = balanced_digits8(y, ok);
-                over |= !ok;
-                nl = max(nl, digits_used(dg));
-#pragma unroll
-                for (int l = 0; l < 8; l++) pw[l] |= (uint32_t)((dg >> (8 * l)) & 0xFF) << (8 * e);
-            }
-            if (i0 < a.d) {
-#pragma unroll
-                for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(planes + l * pstride + i0) = pw[l];
-            }
-            if ((bad || dead) && c == 0) atomicOr(a.flags, 2);
-            if (over && c == 0) atomicOr(a.flags, 1);
-#pragma unroll
-            for (int s = 16; s > 0; s >>= 1) nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, s));
-            if (lane == 0) atomicMax(&s_nl, nl);
-            cbar();
-        }
-        const bool half_h = s_nl <= 4;
+        norm_planes(a, sh, ly.gain, planes, pstride);
+        const bool half_h = sh->nl <= 4;
         int i0, i1;
-        share(g.n_p0, c, nc, i0, i1);
-        lin_items<QT_Q4K>(cx, KIND_P0, i0, i1, seq, half_h, planes, pstride);
+        share(sh->g.n_p0, c, nc, i0, i1);
+        lin_items<QT_Q4K>(a, sh, KIND_P0, i0, i1, seq, half_h, planes, pstride);
         seq += (unsigned)(i1 - i0);
         cbar();
-        if (tid == 0) { grid_arrive(a.bars, GB_QKV); grid_wait(a.bars, GB_QKV, target, &s_abort); }
+        if (tid == 0) { grid_arrive(a.bars, GB_QKV); grid_wait(a.bars, GB_QKV, target, &sh->abort); }
         cbar();
 
         // ================================ P1: routing, scores, gate/up ================================
@@ -576,23 +575,23 @@ __global__ void __launch_bounds__(DK_THREADS, 1) decode_kernel(const DecodeArgs 
                 int rank = 0;
                 for (int j = 0; j < a.E; j++) { const long long w = lg[j]; rank += (w > v) || (w == v && j < e); }
                 if (rank < a.k) {
-                    s_ids[rank] = e; s_gates[rank] = sigmoid_fixed_c(v, a.fa, a.sig_log2e, a.sig_clip);
-                    for (int m = 0; m < 3; m++) s_sel[m * a.k + rank] = ly.tabs[(size_t)m * a.E + e];
-                    if (c == 0 && a.ids_out) { a.ids_out[(long long)L * a.k + rank] = e; a.gates_out[(long long)L * a.k + rank] = s_gates[rank]; }
+                    sh->ids[rank] = e; sh->gates[rank] = sigmoid_fixed_c(v, a.fa, a.sig_log2e, a.sig_clip);
+                    for (int m = 0; m < 3; m++) sh->sel[m * a.k + rank] = ly.tabs[(size_t)m * a.E + e];
+                    if (c == 0 && a.ids_out) { a.ids_out[(long long)L * a.k + rank] = e; a.gates_out[(long long)L * a.k + rank] = sh->gates[rank]; }
                 }
             }
             cbar();
-            if (tid == 0) mb_arrive(&s_idsbar);                 // the producer may now request this block's expert tiles
+            if (tid == 0) mb_arrive(&sh->idsbar);               // the producer may now request this block's expert tiles
         }
         // rotated query heads of this CTA's KV head; the chunk-0 CTA also rotates and appends the new key / value
-        if (ch.active) {
-            const long long qoff = (long long)ch.kv * rep * a.hd;
+        if (active) {
+            const long long qoff = (long long)kv * rep * a.hd;
             bool wide = false;
             for (int idx = tid; idx < rep * half_hd; idx += DK_CT) {
                 const int r = idx / half_hd, i = idx - r * half_hd;
                 const int e0 = 2 * i, e1 = e0 + 1;                  // interleaved pairs (cohere2.py:114-120)
                 int64_t x0 = __ldcg(a.qkv + qoff + r * a.hd + e0), x1 = __ldcg(a.qkv + qoff + r * a.hd + e1);
-                if (!ly.full) {
+                if (!full) {
                     const int64_t cs = a.cos[pos * half_hd + i], sn = a.sin[pos * half_hd + i];
                     const int64_t y0 = (x0 * cs - x1 * sn) >> a.fa, y1 = (x0 * sn + x1 * cs) >> a.fa;
                     x0 = y0; x1 = y1;
@@ -601,44 +600,44 @@ __global__ void __launch_bounds__(DK_THREADS, 1) decode_kernel(const DecodeArgs 
                 wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
             }
             if (wide) atomicOr(a.flags, 32);                     // a query value beyond int32: this kernel cannot hold it
-            if (ch.owner) {
-                const long long koff = (long long)a.H * a.hd + (long long)ch.kv * a.hd, voff = koff + (long long)a.Hkv * a.hd;
+            if (owner) {
+                const long long koff = (long long)a.H * a.hd + (long long)kv * a.hd, voff = koff + (long long)a.Hkv * a.hd;
                 bool badkv = false;
                 for (int i = tid; i < half_hd; i += DK_CT) {
                     int64_t x0 = __ldcg(a.qkv + koff + 2 * i), x1 = __ldcg(a.qkv + koff + 2 * i + 1);
-                    if (!ly.full) {
+                    if (!full) {
                         const int64_t cs = a.cos[pos * half_hd + i], sn = a.sin[pos * half_hd + i];
                         const int64_t y0 = (x0 * cs - x1 * sn) >> a.fa, y1 = (x0 * sn + x1 * cs) >> a.fa;
                         x0 = y0; x1 = y1;
                     }
                     badkv |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
                     s_knew[2 * i] = (int32_t)x0; s_knew[2 * i + 1] = (int32_t)x1;
-                    int32_t *dst = ly.kcache + ((long long)ch.kv * a.Lmax + pos) * a.hd;
+                    int32_t *dst = ly.kcache + ((long long)kv * a.Lmax + pos) * a.hd;
                     dst[2 * i] = (int32_t)x0; dst[2 * i + 1] = (int32_t)x1;
                 }
                 for (int i = tid; i < a.hd; i += DK_CT) {
                     const int64_t v = __ldcg(a.qkv + voff + i);
                     badkv |= v != (int32_t)v;
                     s_vnew[i] = (int32_t)v;
-                    ly.vcache[((long long)ch.kv * a.Lmax + pos) * a.hd + i] = (int32_t)v;
+                    ly.vcache[((long long)kv * a.Lmax + pos) * a.hd + i] = (int32_t)v;
                 }
                 if (badkv) atomicOr(a.flags, 4);
             }
-            if (tid < DK_MAXREP) { s_hmax[tid] = INT64_MIN; s_z[tid] = 0ULL; }
+            if (tid < DK_MAXREP) { sh->hmax[tid] = INT64_MIN; sh->z[tid] = 0ULL; }
         }
         cbar();
-        const int nk_all = ch.nk + (ch.owner ? 1 : 0);           // keys this CTA scores: its history chunk, plus the new one
+        const int nk_all = nk + (owner ? 1 : 0);                 // keys this CTA scores: its history chunk, plus the new one
         const unsigned kseq = seq;                               // ring items of the key chunk
-        if (ch.active) {
+        if (active) {
             bool ready = true;
-            for (int j = 0; j < ch.slots; j++)
-                ready = mb_wait(&s_full[(kseq + j) % DK_NS], ((kseq + j) / DK_NS) & 1, &s_abort) && ready;
+            for (int j = 0; j < kslots; j++)
+                ready = mb_wait(&sh->full[(kseq + j) % DK_NS], ((kseq + j) / DK_NS) & 1, &sh->abort) && ready;
             const int npair = (rep + 1) / 2;
             for (int it = tid; it < nk_all * npair && ready; it += DK_CT) {
                 const int key = it % nk_all, r0 = (it / nk_all) * 2;
                 const bool two = r0 + 1 < rep;
                 const int32_t *kk;
-                if (key < ch.nk) { const unsigned sq = kseq + key / g.kps; kk = reinterpret_cast<const int32_t *>(slots + (size_t)(sq % DK_NS) * DK_SLOT) + (key % g.kps) * a.hd; }
+                if (key < nk) { const unsigned sq = kseq + key / kps; kk = reinterpret_cast<const int32_t *>(slots + (size_t)(sq % DK_NS) * DK_SLOT) + (key % kps) * a.hd; }
                 else kk = s_knew;
                 const int32_t *qa = s_q + r0 * a.hd, *qb = s_q + (two ? r0 + 1 : r0) * a.hd;
                 long long d0 = 0, d1 = 0;
@@ -651,47 +650,48 @@ __global__ void __launch_bounds__(DK_THREADS, 1) decode_kernel(const DecodeArgs 
                 }
                 const long long sc0 = ((d0 >> a.fa) * a.inv_sqrt) >> a.fa, sc1 = ((d1 >> a.fa) * a.inv_sqrt) >> a.fa;
                 s_sc[key * rep + r0] = sc0;
-                atomicMax(&s_hmax[r0], sc0);
-                if (two) { s_sc[key * rep + r0 + 1] = sc1; atomicMax(&s_hmax[r0 + 1], sc1); }
+                atomicMax(&sh->hmax[r0], sc0);
+                if (two) { s_sc[key * rep + r0 + 1] = sc1; atomicMax(&sh->hmax[r0 + 1], sc1); }
             }
         }
         cbar();
-        if (ch.active && tid < rep && s_hmax[tid] != INT64_MIN) atomicMax(hmax + ch.kv * rep + tid, s_hmax[tid]);
-        if (tid == 0) for (int j = 0; j < ch.slots; j++) mb_arrive(&s_empty[(kseq + j) % DK_NS]);     // key slots back to the producer
-        seq += (unsigned)ch.slots;
+        if (active && tid < rep && sh->hmax[tid] != INT64_MIN) atomicMax(hmax + kv * rep + tid, sh->hmax[tid]);
+        if (tid == 0) for (int j = 0; j < kslots; j++) mb_arrive(&sh->empty[(kseq + j) % DK_NS]);     // key slots back to the producer
+        seq += (unsigned)kslots;
         cbar();
         if (tid == 0) grid_arrive(a.bars, GB_MAX);
 
-        share(g.n_g, c, nc, i0, i1);
-        lin_items<QT_Q4K>(cx, KIND_G, i0, i1, seq, half_h, planes, pstride);
+        share(sh->g.n_g, c, nc, i0, i1);
+        lin_items<QT_Q4K>(a, sh, KIND_G, i0, i1, seq, half_h, planes, pstride);
         seq += (unsigned)(i1 - i0);
         cbar();
-        if (tid == 0) { grid_arrive(a.bars, GB_GU); grid_wait(a.bars, GB_MAX, target, &s_abort); }
+        if (tid == 0) { grid_arrive(a.bars, GB_GU); grid_wait(a.bars, GB_MAX, target, &sh->abort); }
         cbar();
 
         // ================================ P2: exponentials; down ================================
-        if (ch.active) {
+        if (active) {
             for (int it = tid; it < nk_all * rep; it += DK_CT) {
                 const int r = it % rep;
-                long long dlt = __ldcg(hmax + ch.kv * rep + r) - s_sc[it];
+                long long dlt = __ldcg(hmax + kv * rep + r) - s_sc[it];
                 dlt = dlt < a.clip ? dlt : a.clip;
                 const unsigned e = (unsigned)exp2_neg_fixed((dlt * a.log2e) >> a.fa, a.fa);
                 s_e[it] = e;
-                if (e) atomicAdd(&s_z[r], (unsigned long long)e);
+                if (e) atomicAdd(&sh->z[r], (unsigned long long)e);
             }
         }
         cbar();
-        if (ch.active && tid < rep && s_z[tid]) atomicAdd(Z + ch.kv * rep + tid, s_z[tid]);
+        if (active && tid < rep && sh->z[tid]) atomicAdd(Z + kv * rep + tid, sh->z[tid]);
         cbar();
-        if (tid == 0) { grid_arrive(a.bars, GB_Z); grid_wait(a.bars, GB_GU, target, &s_abort); }
+        if (tid == 0) { grid_arrive(a.bars, GB_Z); grid_wait(a.bars, GB_GU, target, &sh->abort); }
         cbar();
         {
             int d0, d1;
-            share(g.n_d, c, nc, d0, d1);
+            share(sh->g.n_d, c, nc, d0, d1);
+            const int ipe = sh->g.ipe;
             unsigned dseq = seq;
             for (int i = d0; i < d1;) {                          // one routed expert at a time: its digit planes staged once
-                const int s = i / g.ipe;
-                const int iend = min(d1, (s + 1) * g.ipe);
+                const int s = i / ipe;
+                const int iend = min(d1, (s + 1) * ipe);
                 int nl = 1;
                 for (int v = tid; v < 8 * (a.eff / 16); v += DK_CT) {
                     const int l = v / (a.eff / 16), o16 = v - l * (a.eff / 16);
@@ -701,13 +701,13 @@ __global__ void __launch_bounds__(DK_THREADS, 1) decode_kernel(const DecodeArgs 
                 }
 #pragma unroll
                 for (int sft = 16; sft > 0; sft >>= 1) nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, sft));
-                if (tid == 0) s_nl = 1;
+                if (tid == 0) sh->nl = 1;
                 cbar();
-                if (lane == 0) atomicMax(&s_nl, nl);
+                if (lane == 0) atomicMax(&sh->nl, nl);
                 cbar();
-                const bool half_g = s_nl <= 4;
-                if (ly.down_q == QT_Q6K) lin_items<QT_Q6K>(cx, KIND_D, i, iend, dseq, half_g, gup, gstride);
-                else lin_items<QT_Q4K>(cx, KIND_D, i, iend, dseq, half_g, gup, gstride);
+                const bool half_g = sh->nl <= 4;
+                if (ly.down_q == QT_Q6K) lin_items<QT_Q6K>(a, sh, KIND_D, i, iend, dseq, half_g, gup, gstride);
+                else lin_items<QT_Q4K>(a, sh, KIND_D, i, iend, dseq, half_g, gup, gstride);
                 dseq += (unsigned)(iend - i);
                 i = iend;
                 cbar();
@@ -716,53 +716,53 @@ __global__ void __launch_bounds__(DK_THREADS, 1) decode_kernel(const DecodeArgs 
         }
 
         // ================================ P3: probabilities x values ================================
-        if (tid == 0) grid_wait(a.bars, GB_Z, target, &s_abort);
+        if (tid == 0) grid_wait(a.bars, GB_Z, target, &sh->abort);
         cbar();
         const unsigned vseq = seq;
-        if (ch.active) {
+        if (active) {
             for (int it = tid; it < nk_all * rep; it += DK_CT) {
-                const unsigned long long z = __ldcg(Z + ch.kv * rep + it % rep);
+                const unsigned long long z = __ldcg(Z + kv * rep + it % rep);
                 s_e[it] = z ? (unsigned)(((unsigned long long)s_e[it] << a.fa) / z) : 0u;
             }
         }
         cbar();
-        if (ch.active) {
+        if (active) {
             bool ready = true;
-            for (int j = 0; j < ch.slots; j++)
-                ready = mb_wait(&s_full[(vseq + j) % DK_NS], ((vseq + j) / DK_NS) & 1, &s_abort) && ready;
+            for (int j = 0; j < kslots; j++)
+                ready = mb_wait(&sh->full[(vseq + j) % DK_NS], ((vseq + j) / DK_NS) & 1, &sh->abort) && ready;
             const int G = DK_CT / a.hd, grp = tid / a.hd, dcol = tid - grp * a.hd;
             if (grp < G && ready) {
                 for (int r0 = grp * 2; r0 < rep; r0 += G * 2) {
                     const bool two = r0 + 1 < rep;
                     long long c0 = 0, c1 = 0;
-                    for (int j = 0; j < ch.slots; j++) {
+                    for (int j = 0; j < kslots; j++) {
                         const int32_t *vs = reinterpret_cast<const int32_t *>(slots + (size_t)((vseq + j) % DK_NS) * DK_SLOT) + dcol;
-                        const int n = min(g.kps, ch.nk - j * g.kps);
-                        const unsigned *pe = s_e + (size_t)j * g.kps * rep + r0;
+                        const int n = min(kps, nk - j * kps);
+                        const unsigned *pe = s_e + (size_t)j * kps * rep + r0;
                         for (int kk = 0; kk < n; kk++) {
                             const long long v = vs[kk * a.hd];
                             c0 += (long long)(int)pe[kk * rep] * v;
                             if (two) c1 += (long long)(int)pe[kk * rep + 1] * v;
                         }
                     }
-                    if (ch.owner) {
+                    if (owner) {
                         const long long v = s_vnew[dcol];
-                        c0 += (long long)(int)s_e[ch.nk * rep + r0] * v;
-                        if (two) c1 += (long long)(int)s_e[ch.nk * rep + r0 + 1] * v;
+                        c0 += (long long)(int)s_e[nk * rep + r0] * v;
+                        if (two) c1 += (long long)(int)s_e[nk * rep + r0 + 1] * v;
                     }
-                    if (c0) atomicAdd(reinterpret_cast<unsigned long long *>(acc + (long long)(ch.kv * rep + r0) * a.hd + dcol), (unsigned long long)c0);
-                    if (two && c1) atomicAdd(reinterpret_cast<unsigned long long *>(acc + (long long)(ch.kv * rep + r0 + 1) * a.hd + dcol), (unsigned long long)c1);
+                    if (c0) atomicAdd(reinterpret_cast<unsigned long long *>(acc + (long long)(kv * rep + r0) * a.hd + dcol), (unsigned long long)c0);
+                    if (two && c1) atomicAdd(reinterpret_cast<unsigned long long *>(acc + (long long)(kv * rep + r0 + 1) * a.hd + dcol), (unsigned long long)c1);
                 }
             }
         }
         cbar();
-        if (tid == 0) for (int j = 0; j < ch.slots; j++) mb_arrive(&s_empty[(vseq + j) % DK_NS]);     // value slots back to the producer
-        seq += (unsigned)ch.slots;
-        if (tid == 0) { grid_arrive(a.bars, GB_ACC); grid_wait(a.bars, GB_ACC, target, &s_abort); }
+        if (tid == 0) for (int j = 0; j < kslots; j++) mb_arrive(&sh->empty[(vseq + j) % DK_NS]);     // value slots back to the producer
+        seq += (unsigned)kslots;
+        if (tid == 0) { grid_arrive(a.bars, GB_ACC); grid_wait(a.bars, GB_ACC, target, &sh->abort); }
         cbar();
 
         // ================================ P4: O product ================================
-        share(g.to, c, nc, i0, i1);
+        share(sh->g.to, c, nc, i0, i1);
         if (i1 > i0) {
             int nl = 1;
             bool over = false;
@@ -785,17 +785,17 @@ __global__ void __launch_bounds__(DK_THREADS, 1) decode_kernel(const DecodeArgs 
             if (over) atomicOr(a.flags, 1);
 #pragma unroll
             for (int sft = 16; sft > 0; sft >>= 1) nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, sft));
-            if (tid == 0) s_nl = 1;
+            if (tid == 0) sh->nl = 1;
             cbar();
-            if (lane == 0) atomicMax(&s_nl, nl);
+            if (lane == 0) atomicMax(&sh->nl, nl);
             cbar();
-            lin_items<QT_Q4K>(cx, KIND_O, i0, i1, seq, s_nl <= 4, planes, pstride);
-            seq += (unsigned)(i1 - i0) * (unsigned)g.okn;
+            lin_items<QT_Q4K>(a, sh, KIND_O, i0, i1, seq, sh->nl <= 4, planes, pstride);
+            seq += (unsigned)(i1 - i0) * (unsigned)sh->g.okn;
         }
         cbar();
         if (tid == 0) grid_arrive(a.bars, GB_X);
     }
-    if (tid == 0 && s_abort) atomicOr(a.flags, 8);
+    if (tid == 0 && sh->abort) atomicOr(a.flags, 8);
 }
 
 size_t decode_smem_bytes(int d, int H, int Hkv, int hd, int E, int eff) {

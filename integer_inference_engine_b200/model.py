@@ -40,7 +40,7 @@ class Decoder:
     [n_kv, rows, head_dim]); ``moe_layers[i]`` / ``gain_handles[i]`` the MoE layer and the block's norm gain."""
 
     def __init__(self, *, d_model, n_heads, n_kv, head_dim, top_k, vocab, window, fa, fw, attn, moe_layers, gain_handles,
-                 embd, out_gain_h, cos, sin, position, one_launch=True):
+                 embd, out_gain_h, cos, sin, position, one_launch=False):
         self.d, self.H, self.Hkv, self.hd = d_model, n_heads, n_kv, head_dim
         self.vocab, self.fa, self.fw, self.window, self.top_k = vocab, fa, fw, window, top_k
         self.attn, self.moe_layers, self.gain_handles = attn, moe_layers, gain_handles
@@ -54,7 +54,8 @@ class Decoder:
         z = lambda n: torch.empty((1, n), dtype=torch.int64, device="cuda")
         self.x, self.hn, self.logits = z(d_model), z(d_model), z(vocab)
         self._graph = None
-        # every block in one launch where the shape allows it; otherwise two entries per block
+        # one_launch: every block inside one persistent kernel where the shape allows it (byte-identical; on B200 it does not
+        # yet beat the two entries per block, so it is opt-in)
         self.kernel = None
         if one_launch:
             try:
@@ -67,7 +68,7 @@ class Decoder:
 
     @classmethod
     def from_raw(cls, layers, embd_raw, out_gain, *, d_model, n_heads, n_kv, head_dim, e_ffn, top_k, vocab, window, rows,
-                 rope_base=50000.0, fa=16, fw=24, caches=None, position=0, one_launch=True):
+                 rope_base=50000.0, fa=16, fw=24, caches=None, position=0, one_launch=False):
         """``layers[i]`` = dict(gain int64 [d]; wq, wk, wv, wo raw Q4_K bytes; moe=(router, gates, ups, downs) raw Q4_K /
         Q4_K / Q4_K / Q6_K bytes), as a GGUF reader hands them over; ``embd_raw`` the tied Q6_K matrix [vocab, d].
         ``caches[i]`` = (k, v) int64 arrays [n_kv, filled, head_dim] already in the cache (after rotation)."""
@@ -190,7 +191,7 @@ class SyntheticDecoder(Decoder):
     def __init__(self, n_layers: int = 48, d_model: int = 2048, n_heads: int = 32, n_kv: int = 4, head_dim: int = 128,
                  e_ffn: int = 768, n_experts: int = 128, top_k: int = 8, vocab: int = 151936, context: int = 4096,
                  max_new: int = 160, window: int = 4096, rope_base: float = 50000.0, seed: int = 1, fa: int = 16, fw: int = 24,
-                 one_launch: bool = True):
+                 one_launch: bool = False):
         rows = context + max_new
         self.moe = SyntheticMoEStack(n_layers, d_model, e_ffn, n_experts, top_k, seed=seed, fa=fa)
         nb = d_model // 256
