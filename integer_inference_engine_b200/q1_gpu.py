@@ -1,10 +1,11 @@
-"""Host-side bridge to the Q1_0 entry points, with the reference bridge's function names.
+"""Host-side bridge to the Q1_0 entry points of include/iie_q1.h.
 
-Mirrors bonsai/src/trinote/infer_int/gpu_native.py:188-415 (``q1_apply_gpu``, ``q1_apply_dp4a_gpu``,
-``q1_register_weight``, ``q1_apply_resident``, ``q1_free_weights``, ``rmsnorm_gpu``, ``gpu_memory_info``):
-same arguments, same exceptions for malformed input, ``None`` when the library declines a call (rc != 0).
-One deliberate difference: a missing library or GPU raises ``CudaUnavailableError`` instead of turning every
-function into a silent no-op, because nothing behind this module can take over.
+The host-array functions carry the names and arguments of the reference's bridge (bonsai/src/trinote/infer_int/
+gpu_native.py:188-415: ``q1_apply_gpu``, ``q1_apply_dp4a_gpu``, ``q1_register_weight``, ``q1_apply_resident``,
+``q1_free_weights``, ``rmsnorm_gpu``, ``gpu_memory_info``) so its callers can switch modules: malformed input raises,
+``None`` means the library declined the call.  Their bodies are this repository's own (two coercion helpers and one
+locked call helper).  One deliberate difference: a missing library or GPU raises ``CudaUnavailableError`` instead of
+turning every function into a silent no-op, because nothing behind this module can take over.
 
 Arrays are host NumPy arrays.  Device-resident callers use :func:`apply_dev` with CUDA tensors.
 """
@@ -95,52 +96,59 @@ def _lib():
     return lib
 
 
-def _weight_arrays(bits, scale_fp, dtype=np.int64):
-    b = np.ascontiguousarray(np.asarray(bits, dtype=np.uint8))
-    src = np.asarray(scale_fp)
-    if not np.issubdtype(src.dtype, np.integer):
-        raise TypeError(f"Q1_0 scale must be an integer dtype, got {src.dtype}")
-    s = np.ascontiguousarray(src, dtype=dtype)
-    return b, s
+def _activation(x_fp, n_blocks: int) -> np.ndarray:
+    """Host activations as a C-contiguous int64 matrix whose width is the weight's contraction length."""
+    x = np.asarray(x_fp, dtype=np.int64)
+    x = np.ascontiguousarray(x.reshape(1, -1) if x.ndim < 2 else x)
+    if x.shape[1] != int(n_blocks) * 128:
+        raise ValueError(f"the activation is {x.shape[1]} wide, the weight contracts over {int(n_blocks) * 128}")
+    return x
+
+
+def _packed_weight(bits, scale_fp, scale_dtype=np.int64):
+    """(sign bytes [out_f, n_blocks, 16] uint8, scales [out_f, n_blocks] of ``scale_dtype``), both C-contiguous.
+    Scales are committed fixed-point integers: a floating array here is a caller bug, not something to round."""
+    scales = np.asarray(scale_fp)
+    if scales.dtype.kind not in "iu":
+        raise TypeError(f"Q1_0 scales are integers at 2**frac; got dtype {scales.dtype}")
+    return np.ascontiguousarray(bits, dtype=np.uint8), np.ascontiguousarray(scales, dtype=scale_dtype)
+
+
+def _fits_four_digits(x: np.ndarray) -> bool:
+    return x.size == 0 or (_L4_LO <= int(x.min()) and int(x.max()) <= _L4_HI)
+
+
+def _call(name: str, *args) -> int:
+    fn = getattr(_lib(), name)
+    with _CUDA_LOCK:
+        return int(fn(*args))
 
 
 def q1_apply_gpu(x_fp, bits, scale_fp, frac: int):
-    """Packed Q1_0 linear ``x @ W.T`` with a per-call weight upload (gpu_native.py:193-220)."""
-    lib = _lib()
-    x = np.ascontiguousarray(np.atleast_2d(np.asarray(x_fp, dtype=np.int64)))
-    b, s = _weight_arrays(bits, scale_fp)
-    out_f, n_blocks = s.shape
-    if x.shape[1] != n_blocks * 128:
-        raise ValueError(f"Q1_0 contraction mismatch: x has {x.shape[1]}, weight expects {n_blocks * 128}")
-    out = np.empty((x.shape[0], out_f), dtype=np.int64)
-    with _CUDA_LOCK:
-        rc = lib.bonsai_q1_linear_gpu(x.ctypes.data, b.ctypes.data, s.ctypes.data, x.shape[0], int(out_f), int(n_blocks),
-                                      int(frac), out.ctypes.data)
-    return None if rc != 0 else out
+    """``x @ W.T`` for a packed Q1_0 weight that travels with the call (reference name: gpu_native.py q1_apply_gpu).
+    ``None`` when the library declines."""
+    b, s = _packed_weight(bits, scale_fp)
+    x = _activation(x_fp, s.shape[1])
+    y = np.empty((x.shape[0], s.shape[0]), np.int64)
+    rc = _call("bonsai_q1_linear_gpu", x.ctypes.data, b.ctypes.data, s.ctypes.data, x.shape[0], s.shape[0], s.shape[1], int(frac),
+               y.ctypes.data)
+    return y if rc == 0 else None
 
 
 def q1_apply_dp4a_gpu(x_fp, bits, scale_fp, frac: int, L: "int | None" = None):
-    """The digit-path entry (gpu_native.py:226-261): ``L`` is the digit count the caller vouches for; an
-    explicit ``L=4`` with activations outside the four-digit range raises, as in the reference."""
-    lib = _lib()
-    x = np.ascontiguousarray(np.atleast_2d(np.asarray(x_fp, dtype=np.int64)))
-    b, s = _weight_arrays(bits, scale_fp)
-    out_f, n_blocks = s.shape
-    if x.shape[1] != n_blocks * 128:
-        raise ValueError(f"Q1_0 contraction mismatch: x has {x.shape[1]}, weight expects {n_blocks * 128}")
+    """The entry that takes a digit count ``L`` (reference name: q1_apply_dp4a_gpu).  Without ``L`` the count follows the
+    activations (four digits when they fit, else eight); ``L=4`` for activations that need more is refused here, before
+    the call, because the native side would have to trust it."""
+    b, s = _packed_weight(bits, scale_fp)
+    x = _activation(x_fp, s.shape[1])
     if L is None:
-        mn, mx = (int(x.min()), int(x.max())) if x.size else (0, 0)
-        L = 4 if (_L4_LO <= mn and mx <= _L4_HI) else 8
-    elif int(L) == 4 and x.size:
-        mn, mx = int(x.min()), int(x.max())
-        if not (_L4_LO <= mn and mx <= _L4_HI):
-            raise ValueError(f"q1_apply_dp4a_gpu: explicit L=4 requires activations in [{_L4_LO}, {_L4_HI}], "
-                             f"got [{mn}, {mx}]")
-    out = np.empty((x.shape[0], out_f), dtype=np.int64)
-    with _CUDA_LOCK:
-        rc = lib.bonsai_q1_linear_dp4a_gpu(x.ctypes.data, b.ctypes.data, s.ctypes.data, x.shape[0], int(out_f),
-                                           int(n_blocks), int(frac), int(L), out.ctypes.data)
-    return None if rc != 0 else out
+        L = 4 if _fits_four_digits(x) else 8
+    elif int(L) == 4 and not _fits_four_digits(x):
+        raise ValueError(f"L=4 promises activations inside [{_L4_LO}, {_L4_HI}]; these span [{int(x.min())}, {int(x.max())}]")
+    y = np.empty((x.shape[0], s.shape[0]), np.int64)
+    rc = _call("bonsai_q1_linear_dp4a_gpu", x.ctypes.data, b.ctypes.data, s.ctypes.data, x.shape[0], s.shape[0], s.shape[1],
+               int(frac), int(L), y.ctypes.data)
+    return y if rc == 0 else None
 
 
 def residency_available() -> bool:
@@ -148,72 +156,56 @@ def residency_available() -> bool:
 
 
 def q1_register_weight(bits, scale_fp, *, gpu_coalesced: bool = False, gpu_bmma: bool = False):
-    """Upload a projection once; returns a handle or ``None`` (gpu_native.py:270-306).  The two layout
-    switches are accepted for compatibility and select the same tensor-core layout."""
-    lib = _lib()
-    src = np.asarray(scale_fp)
-    if not np.issubdtype(src.dtype, np.integer):
-        raise TypeError(f"Q1_0 scale must be an integer dtype, got {src.dtype}")
-    use_i32 = src.dtype.itemsize <= 4
+    """Commit a projection to the device once; its handle, or ``None`` when the library declines.  Scales of at most 32
+    bits are kept as int32.  ``gpu_coalesced`` / ``gpu_bmma`` are the reference's layout switches: they exist so that its
+    callers need no change and both select the one tensor-core layout this library has."""
+    narrow = np.asarray(scale_fp).dtype.itemsize <= 4
     if gpu_coalesced and gpu_bmma:
-        raise ValueError("choose one GPU Q1 runtime layout")
-    if (gpu_coalesced or gpu_bmma) and not use_i32:
-        raise ValueError("GPU-coalesced Q1 registration currently requires committed int32 scales")
-    b, s = _weight_arrays(bits, src, np.int32 if use_i32 else np.int64)
-    out_f, n_blocks = s.shape
-    if gpu_bmma:
-        fn = lib.bonsai_q1_register_weight_i32_bmma
-    elif gpu_coalesced:
-        fn = lib.bonsai_q1_register_weight_i32_gpu_layout
-    else:
-        fn = lib.bonsai_q1_register_weight_i32 if use_i32 else lib.bonsai_q1_register_weight
-    with _CUDA_LOCK:
-        h = fn(b.ctypes.data, s.ctypes.data, int(out_f), int(n_blocks))
-    return None if int(h) < 0 else int(h)
+        raise ValueError("gpu_coalesced and gpu_bmma exclude each other")
+    if (gpu_coalesced or gpu_bmma) and not narrow:
+        raise ValueError("the layout switches are defined for int32 scales only")
+    b, s = _packed_weight(bits, scale_fp, np.int32 if narrow else np.int64)
+    entry = ("bonsai_q1_register_weight_i32_bmma" if gpu_bmma else "bonsai_q1_register_weight_i32_gpu_layout" if gpu_coalesced
+             else "bonsai_q1_register_weight_i32" if narrow else "bonsai_q1_register_weight")
+    handle = _call(entry, b.ctypes.data, s.ctypes.data, s.shape[0], s.shape[1])
+    return handle if handle >= 0 else None
 
 
 def q1_apply_resident(handle: int, x_fp, out_features: int, n_blocks: int, frac: int):
-    """Apply a registered weight to fresh host activations (gpu_native.py:364-380)."""
-    lib = _lib()
-    x = np.ascontiguousarray(np.atleast_2d(np.asarray(x_fp, dtype=np.int64)))
-    if x.shape[1] != int(n_blocks) * 128:
-        raise ValueError(f"Q1_0 contraction mismatch: x has {x.shape[1]}, weight expects {int(n_blocks) * 128}")
-    out = np.empty((x.shape[0], int(out_features)), dtype=np.int64)
-    with _CUDA_LOCK:
-        rc = lib.bonsai_q1_apply_resident(int(handle), x.ctypes.data, x.shape[0], int(frac), out.ctypes.data)
-    return None if rc != 0 else out
+    """Fresh host activations through a registered weight; ``None`` when the library declines."""
+    x = _activation(x_fp, n_blocks)
+    y = np.empty((x.shape[0], int(out_features)), np.int64)
+    rc = _call("bonsai_q1_apply_resident", int(handle), x.ctypes.data, x.shape[0], int(frac), y.ctypes.data)
+    return y if rc == 0 else None
 
 
 def q1_free_weights() -> None:
-    with _CUDA_LOCK:
-        _lib().bonsai_q1_free_weights()
+    _call("bonsai_q1_free_weights")
 
 
 def gpu_memory_info():
+    """Free / total / used device bytes and the bytes registered weights hold, or ``None`` when the query fails."""
     lib = _lib()
     free, total = ctypes.c_uint64(), ctypes.c_uint64()
     if lib.bonsai_gpu_mem_info(ctypes.byref(free), ctypes.byref(total)) != 0:
         return None
-    return {"free_bytes": int(free.value), "total_bytes": int(total.value),
-            "used_bytes": int(total.value - free.value),
+    return {"free_bytes": free.value, "total_bytes": total.value, "used_bytes": total.value - free.value,
             "resident_weight_bytes": int(lib.bonsai_q1_resident_weight_bytes())}
 
 
 def rmsnorm_gpu(x_fp, frac: int, eps: int = 1, gain_q=None):
-    """Fixed-point RMSNorm of host rows (gpu_native.py:390-415); ``None`` when a row leaves the exact envelope."""
-    lib = _lib()
-    x = np.ascontiguousarray(np.atleast_2d(np.asarray(x_fp, dtype=np.int64)))
-    rows, cols = x.shape
-    out = np.empty((rows, cols), dtype=np.int64)
-    g_ptr, g = 0, None
+    """Fixed-point RMSNorm of host rows with an optional gain row; ``None`` when a row leaves the exact envelope."""
+    x = np.asarray(x_fp, dtype=np.int64)
+    x = np.ascontiguousarray(x.reshape(1, -1) if x.ndim < 2 else x)
+    gain = None
     if gain_q is not None:
-        g = np.ascontiguousarray(np.asarray(gain_q, dtype=np.int64))
-        if g.shape[0] != cols:
-            raise ValueError(f"RMSNorm gain has {g.shape[0]} elems, expected cols={cols}")
-        g_ptr = g.ctypes.data
-    with _CUDA_LOCK:
-        rc = lib.bonsai_rmsnorm_gpu(x.ctypes.data, rows, cols, int(frac), int(eps), ctypes.c_void_p(g_ptr), out.ctypes.data)
-    return None if rc != 0 else out
+        gain = np.ascontiguousarray(gain_q, dtype=np.int64).reshape(-1)
+        if gain.size != x.shape[1]:
+            raise ValueError(f"a gain of {gain.size} values cannot scale rows of {x.shape[1]}")
+    y = np.empty_like(x)
+    rc = _call("bonsai_rmsnorm_gpu", x.ctypes.data, x.shape[0], x.shape[1], int(frac), int(eps),
+               ctypes.c_void_p(gain.ctypes.data if gain is not None else 0), y.ctypes.data)
+    return y if rc == 0 else None
 
 
 def apply_dev(handle: int, x, frac: int, out=None):

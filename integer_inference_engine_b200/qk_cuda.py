@@ -1,13 +1,18 @@
-"""Host-side bridge to ``libnmc_qk_cuda.so`` with the reference bridge's function names.
+"""Host-side bridge to ``libnmc_qk_cuda.so``: NumPy arrays in, NumPy arrays out, through the C-ABI of include/iie_qk.h.
 
-Mirrors north-mini-code/src/nmc/qk_cuda.py (names, argument meaning, ``None`` / exception behaviour)
-for the MoE hot path, so a caller of ``nmc.qk_cuda`` can switch modules, and tests written against
-the reference bridge read the same here.  One deliberate difference: there is no CPU fallback behind
-this module.  If the shared library or a GPU is missing, every compute entry raises
-``CudaUnavailableError`` instead of returning ``None`` for a caller to fall back on.
+The public names and their meaning are those of the reference's bridge module (north-mini-code/src/nmc/qk_cuda.py), so
+that a caller of ``nmc.qk_cuda`` finds the same calls here: ``register_weight`` / ``apply_resident*`` (qk_cuda.py:230-442),
+``rmsnorm_router`` (:331-372), ``moe_ffn`` / ``moe_ffn_batched`` (:1073-1124), the limb policy (:973-1026), the profile
+counters (:870-900) and the request-scoped attention bank (:476-569).  How they are written is this repository's own: one
+table of C signatures drives both the symbol check and the ctypes set-up, array arguments go through two small coercion
+helpers, and every native call goes through :func:`_native`, which takes the process-wide lock.
 
-All arrays are host NumPy arrays; the library copies them to the device and back.  Device-resident
-(PyTorch) callers use :mod:`integer_inference_engine_b200.device` instead.
+One deliberate difference from the reference: nothing here falls back to a CPU path.  Without the built library or a
+usable GPU every compute entry raises :class:`CudaUnavailableError`; a native status that the reference maps to "use the
+host path" is handed to the caller as ``None`` exactly as there, and it is the caller who owns that decision.
+
+Device-resident (PyTorch) callers use :mod:`integer_inference_engine_b200.device` instead; it shares this module's
+library instance, lock and error types.
 """
 from __future__ import annotations
 
@@ -20,9 +25,8 @@ import numpy as np
 
 Q4_K, Q6_K = 0, 1
 _BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
-_CUDA_ABI_VERSION = 5
-_DP4A_SAFE_LIMBS = 4
-PROFILE_Q, PROFILE_K, PROFILE_V, PROFILE_O, PROFILE_OTHER = 1, 2, 3, 4, 0
+PROFILE_OTHER, PROFILE_Q, PROFILE_K, PROFILE_V, PROFILE_O = 0, 1, 2, 3, 4
+# counter order of qk_profile_snapshot (the ABI fixes it)
 _PROFILE_METRICS = (
     "registration_calls", "registration_ns", "h2d_calls", "h2d_bytes", "h2d_ns", "d2h_calls", "d2h_bytes", "d2h_ns",
     "allocation_calls", "allocation_bytes", "allocation_ns", "free_calls", "native_calls", "resident_apply_calls",
@@ -30,26 +34,9 @@ _PROFILE_METRICS = (
     "q_projection_ns", "k_projection_calls", "k_projection_ns", "v_projection_calls", "v_projection_ns",
     "o_projection_calls", "o_projection_ns", "other_projection_calls", "other_projection_ns",
 )
-# Every symbol include/iie_qk.h declares; the CPU test-suite checks that the library exports all of them.
-EXPORTED_SYMBOLS = (
-    "qk_cuda_abi_version", "qk_cuda_available", "qk_linear_cuda", "qk_resident_reserve", "qk_register_weight",
-    "qk_register_i64", "qk_resident_count", "qk_resident_capacity", "qk_free_all", "qk_apply_resident",
-    "qk_apply_resident_grouped", "qk_apply_resident_q6k_dp4a", "qk_apply_resident_q4k_dp4a", "qk_rmsnorm_router",
-    "qk_moe_ffn", "qk_moe_ffn_dp4a", "qk_moe_ffn_batched", "qk_moe_ffn_batched_dp4a", "qk_moe_workspace_allocations",
-    "qk_moe_workspace_bytes", "qk_moe_workspace_release", "qk_profile_reset", "qk_profile_set_enabled",
-    "qk_profile_snapshot", "qk_attention_bank_create", "qk_attention_bank_reset", "qk_attention_bank_destroy",
-    "qk_attention_bank_moe_configure", "qk_attention_bank_moe_bind", "qk_attention_bank_import",
-    "qk_attention_bank_apply", "qk_attention_bank_moe_begin", "qk_attention_bank_moe_continue",
-    "qk_attention_bank_moe_export", "qk_attention_bank_workspace_bytes", "iie_attn_prefill_dev", 
-    "iie_register_weight_dev", "iie_weight_export", "iie_moe_layer_create", "iie_moe_layer_destroy",
-    "iie_moe_forward_dev", "iie_apply_dev", "iie_flags_read_clear", "iie_rmsnorm_dev", "iie_profile_stage_mask",
-    "iie_launch_count", "iie_prefill_launch_counts", "iie_workspace_generation", "iie_moe_block_host", "iie_moe_block_dev", "iie_set_pdl",
-    "iie_apply_dev_static", "iie_set_tc_min_tokens", "iie_route_dev", "iie_moe_experts_dev",
-    "iie_attn_decode_dev", "iie_embed_dev", "iie_argmax_dev", "iie_attn_block_dev", "iie_set_attn_fused",
-    "iie_decoder_create", "iie_decoder_set_layer", "iie_decoder_step_dev", "iie_decoder_destroy",
-)
-# The library keeps one registry and one set of workspaces per process and ctypes releases the GIL:
-# serialise callers here as the reference bridge does (qk_cuda.py:35-38).
+_MAX_GROUP = 16          # handles one grouped apply may carry (the ABI's limit)
+_DIGITS = 8              # balanced base-256 digits the kernels carry per activation
+# One registry and one set of workspaces per process, and ctypes releases the GIL during a call: callers are serialised.
 _CUDA_LOCK = threading.RLock()
 
 
@@ -65,24 +52,12 @@ class CudaContextError(RuntimeError):
     """A resident call failed validation, allocation, or an exact-envelope guard."""
 
 
-def lib_path() -> Path:
-    return Path(__file__).resolve().parent / "lib" / "libnmc_qk_cuda.so"
-
-
-@lru_cache(maxsize=1)
-def load_library():
-    """``ctypes.CDLL`` of the in-tree library with argument types set; raises if it is not built.
-    Loading needs no GPU (the CPU test-suite checks the exported symbols this way)."""
-    p = lib_path()
-    if not p.exists():
-        raise CudaUnavailableError(f"{p} is not built (python -m integer_inference_engine_b200.build)")
-    lib = ctypes.CDLL(str(p))
-    missing = [s for s in EXPORTED_SYMBOLS if not hasattr(lib, s)]
-    if missing:
-        raise CudaUnavailableError(f"{p} lacks symbols {missing}")
+def _signatures():
+    """name -> (argument types, result type) of every symbol include/iie_qk.h declares."""
     c_int, i64, u64, vp = ctypes.c_int, ctypes.c_int64, ctypes.c_uint64, ctypes.c_void_p
     P64, P32 = ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int)
-    sig = {
+    moe_stub = ([], c_int)          # retained-layer executor entries: present in the ABI, never called from here
+    return {
         "qk_cuda_abi_version": ([], c_int), "qk_cuda_available": ([], c_int),
         "qk_linear_cuda": ([vp, vp, i64, i64, i64, c_int, c_int, vp], c_int),
         "qk_resident_reserve": ([i64], c_int), "qk_register_weight": ([vp, i64, i64, c_int], i64),
@@ -126,510 +101,472 @@ def load_library():
         "iie_moe_experts_dev": ([i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, c_int, vp, vp], c_int),
         "iie_moe_block_host": ([i64, i64, vp, i64, c_int, c_int, u64, vp, vp, vp], c_int),
         "iie_moe_block_dev": ([i64, i64, vp, i64, c_int, c_int, u64, vp, vp, vp, vp], c_int),
+        "qk_attention_bank_moe_configure": moe_stub, "qk_attention_bank_moe_bind": moe_stub,
+        "qk_attention_bank_moe_begin": moe_stub, "qk_attention_bank_moe_continue": moe_stub,
+        "qk_attention_bank_moe_export": moe_stub,
     }
-    for name, (args, res) in sig.items():
-        fn = getattr(lib, name)
-        fn.argtypes, fn.restype = args, res
-    if int(lib.qk_cuda_abi_version()) != _CUDA_ABI_VERSION:
-        raise CudaUnavailableError("library reports a different ABI version")
-    return lib
+
+
+# Every symbol the header declares; the CPU test-suite checks that the built library exports all of them.
+EXPORTED_SYMBOLS = tuple(_signatures())
+
+
+def lib_path() -> Path:
+    return Path(__file__).resolve().parent / "lib" / "libnmc_qk_cuda.so"
 
 
 @lru_cache(maxsize=1)
-def _gpu_ok() -> bool:
-    with _CUDA_LOCK:
-        return load_library().qk_cuda_available() == 0
+def load_library():
+    """``ctypes.CDLL`` of the in-tree library with argument types set; raises if it is not built.
+    Loading needs no GPU (the CPU test-suite checks the exported symbols this way)."""
+    path = lib_path()
+    if not path.exists():
+        raise CudaUnavailableError(f"{path} is not built (python -m integer_inference_engine_b200.build)")
+    lib = ctypes.CDLL(str(path))
+    table = _signatures()
+    absent = [name for name in table if not hasattr(lib, name)]
+    if absent:
+        raise CudaUnavailableError(f"{path} lacks symbols {absent}")
+    for name, (args, res) in table.items():
+        if args or res is not ctypes.c_int or not name.startswith("qk_attention_bank_moe_"):
+            fn = getattr(lib, name)
+            fn.argtypes, fn.restype = args, res
+    return lib
 
 
 def available() -> bool:
     """True when the library is built and a GPU is usable."""
     try:
-        return _gpu_ok()
+        with _CUDA_LOCK:
+            return load_library().qk_cuda_available() == 0
     except CudaUnavailableError:
         return False
 
 
 def _lib():
     lib = load_library()
-    if not _gpu_ok():
+    with _CUDA_LOCK:
+        usable = lib.qk_cuda_available() == 0
+    if not usable:
         raise CudaUnavailableError("no usable CUDA device; this package has no CPU path")
     return lib
 
 
-def _require_weight_bytes(weight_raw, out_f: int, n_blocks: int, qtype: int) -> int:
-    """The kernel reads out_f*n_blocks*block_bytes bytes: refuse a shorter buffer
-    (north-mini-code/src/nmc/qk_native.py:19-31)."""
-    bs = _BLOCK_BYTES.get(int(qtype))
-    if bs is None:
-        raise ValueError(f"unknown qtype {qtype} (expected Q4_K={Q4_K} or Q6_K={Q6_K})")
-    out_f, n_blocks = int(out_f), int(n_blocks)
-    if out_f <= 0 or n_blocks <= 0:
-        raise ValueError(f"out_f and n_blocks must be positive, got out_f={out_f}, n_blocks={n_blocks}")
-    need = out_f * n_blocks * bs
-    if len(weight_raw) < need:
-        raise ValueError(f"weight buffer too short: {len(weight_raw)} bytes < required {need}")
-    return need
-
-
-def _bytes_ptr(raw):
-    buf = np.frombuffer(raw, np.uint8) if not isinstance(raw, np.ndarray) else np.ascontiguousarray(raw).view(np.uint8)
-    return buf, buf.ctypes.data
-
-
-def _x2d(x_int) -> np.ndarray:
-    return np.ascontiguousarray(np.atleast_2d(np.asarray(x_int, dtype=np.int64)))
-
-
-# ------------------------------------------------------------------------------------- linear / residency ---
-def qk_linear(weight_raw, x_int, out_f: int, n_blocks: int, fw: int, qtype: int):
-    """y[t,o] = (sum_i W[o,i]*x[t,i]) >> fw from raw Q4_K/Q6_K bytes; x [T,in_f] int64 -> [T,out_f] int64.
-    ``None`` on a native failure (qk_cuda.py:230-244)."""
-    lib = _lib()
-    x = _x2d(x_int)
-    assert x.shape[1] == n_blocks * 256, (x.shape, n_blocks)
-    _require_weight_bytes(weight_raw, out_f, n_blocks, qtype)
-    keep, wp = _bytes_ptr(weight_raw)
-    out = np.empty((x.shape[0], out_f), np.int64)
+def _native(name: str, *args):
+    """One native call under the lock."""
+    fn = getattr(_lib(), name)
     with _CUDA_LOCK:
-        rc = lib.qk_linear_cuda(wp, x.ctypes.data, x.shape[0], out_f, n_blocks, int(fw), int(qtype), out.ctypes.data)
-    return None if rc != 0 else out
+        return fn(*args)
 
 
-def resident_available() -> bool:
-    return available()
+# every optional capability of the reference bridge is always present in this library
+resident_available = grouped_available = dp4a_available = resident_preprocess_available = available
+moe_ffn_available = moe_ffn_dp4a_available = moe_ffn_batched_available = moe_ffn_batched_dp4a_available = available
+resident_attention_available = available
+
+
+# ------------------------------------------------------------------------------------------ argument helpers ---
+def _rows(x) -> np.ndarray:
+    """Activation as a C-contiguous int64 matrix; a vector is one row."""
+    a = np.asarray(x, dtype=np.int64)
+    if a.ndim < 2:
+        a = a.reshape(1, -1)
+    return np.ascontiguousarray(a)
+
+
+def _blob(raw) -> np.ndarray:
+    """Raw weight bytes as a uint8 array that stays alive for the duration of the call."""
+    if isinstance(raw, np.ndarray):
+        return np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+    return np.frombuffer(raw, dtype=np.uint8)
+
+
+def _require_weight_bytes(weight_raw, out_f: int, n_blocks: int, qtype: int) -> int:
+    """Bytes the kernels will read for an [out_f, n_blocks*256] tensor of this type; a shorter buffer is refused here,
+    before any pointer reaches native code."""
+    if int(qtype) not in _BLOCK_BYTES:
+        raise ValueError(f"qtype {qtype} is neither Q4_K ({Q4_K}) nor Q6_K ({Q6_K})")
+    rows, blocks = int(out_f), int(n_blocks)
+    if min(rows, blocks) <= 0:
+        raise ValueError(f"a weight needs positive out_f and n_blocks, not {rows} and {blocks}")
+    span = rows * blocks * _BLOCK_BYTES[int(qtype)]
+    have = len(weight_raw)
+    if have < span:
+        raise ValueError(f"weight buffer holds {have} bytes, the tensor needs {span}")
+    return span
+
+
+def _handle_array(handles, n: int):
+    return (ctypes.c_int64 * n)(*(int(h) for h in handles))
+
+
+# --------------------------------------------------------------------------------------- products, residency ---
+def qk_linear(weight_raw, x_int, out_f: int, n_blocks: int, fw: int, qtype: int):
+    """y[t,o] = (sum_i W[o,i] x[t,i]) >> fw straight from raw Q4_K / Q6_K bytes: x [T, n_blocks*256] int64 -> [T, out_f].
+    ``None`` when native code reports a failure."""
+    x = _rows(x_int)
+    if x.shape[1] != int(n_blocks) * 256:
+        raise ValueError(f"activation width {x.shape[1]} does not match {n_blocks} blocks of 256")
+    _require_weight_bytes(weight_raw, out_f, n_blocks, qtype)
+    w = _blob(weight_raw)
+    y = np.empty((x.shape[0], int(out_f)), np.int64)
+    rc = _native("qk_linear_cuda", w.ctypes.data, x.ctypes.data, x.shape[0], int(out_f), int(n_blocks), int(fw), int(qtype),
+                 y.ctypes.data)
+    return y if rc == 0 else None
 
 
 def register_weight(weight_raw, out_f: int, n_blocks: int, qtype: int) -> int:
-    """Upload a weight tensor once; returns its handle, raises on failure (qk_cuda.py:252-271)."""
-    lib = _lib()
+    """Commit a Q4_K / Q6_K tensor to device memory once and return its handle."""
     _require_weight_bytes(weight_raw, out_f, n_blocks, qtype)
-    keep, wp = _bytes_ptr(weight_raw)
-    with _CUDA_LOCK:
-        h = lib.qk_register_weight(wp, out_f, n_blocks, qtype)
-    if h < 0:
-        raise CudaRegistrationError(f"registration failed for shape [{out_f}, {n_blocks * 256}] (qtype={qtype})")
-    return int(h)
+    w = _blob(weight_raw)
+    handle = int(_native("qk_register_weight", w.ctypes.data, int(out_f), int(n_blocks), int(qtype)))
+    if handle < 0:
+        raise CudaRegistrationError(f"could not register a [{out_f}, {int(n_blocks) * 256}] tensor of qtype {qtype}")
+    return handle
 
 
 def register_i64(matrix) -> int:
-    """Upload a dense int64 matrix (a vector becomes one row) for RMSNorm gains and dense routers
-    (qk_cuda.py:280-304)."""
-    lib = _lib()
-    value = np.asarray(matrix, dtype=np.int64)
-    if value.ndim == 1:
-        value = value.reshape(1, -1)
-    if value.ndim != 2 or value.shape[0] <= 0 or value.shape[1] <= 0:
-        raise ValueError("resident int64 registration requires a non-empty vector or 2-D matrix")
-    value = np.ascontiguousarray(value)
-    with _CUDA_LOCK:
-        h = int(lib.qk_register_i64(value.ctypes.data, value.shape[0], value.shape[1]))
-    if h < 0:
-        raise CudaRegistrationError(f"int64 registration failed for shape {value.shape}")
-    return h
+    """Commit a dense int64 matrix (RMSNorm gain row, dense router); a vector counts as one row."""
+    m = _rows(matrix)
+    if m.ndim != 2 or 0 in m.shape:
+        raise ValueError("a dense registration needs a non-empty vector or matrix")
+    handle = int(_native("qk_register_i64", m.ctypes.data, m.shape[0], m.shape[1]))
+    if handle < 0:
+        raise CudaRegistrationError(f"could not register a dense int64 matrix of shape {m.shape}")
+    return handle
 
 
 def reserve_resident_capacity(count: int) -> bool:
-    with _CUDA_LOCK:
-        return _lib().qk_resident_reserve(int(count)) == 0
+    return _native("qk_resident_reserve", int(count)) == 0
 
 
 def resident_count() -> int:
-    with _CUDA_LOCK:
-        return int(_lib().qk_resident_count())
+    return int(_native("qk_resident_count"))
 
 
 def resident_capacity() -> int:
-    with _CUDA_LOCK:
-        return int(_lib().qk_resident_capacity())
+    return int(_native("qk_resident_capacity"))
 
 
 def free_all() -> None:
-    with _CUDA_LOCK:
-        _lib().qk_free_all()
+    _native("qk_free_all")
 
 
 def apply_resident(handle: int, x_int, out_f: int, fw: int):
-    """Apply a resident weight; ``None`` for a bad handle or native failure (qk_cuda.py:387-397)."""
-    lib = _lib()
-    x = _x2d(x_int)
-    out = np.empty((x.shape[0], out_f), np.int64)
-    with _CUDA_LOCK:
-        rc = lib.qk_apply_resident(int(handle), x.ctypes.data, x.shape[0], int(fw), out.ctypes.data)
-    return None if rc != 0 else out
-
-
-def grouped_available() -> bool:
-    return available()
+    """x through a registered weight; ``None`` for an unknown handle or a native failure."""
+    x = _rows(x_int)
+    y = np.empty((x.shape[0], int(out_f)), np.int64)
+    rc = _native("qk_apply_resident", int(handle), x.ctypes.data, x.shape[0], int(fw), y.ctypes.data)
+    return y if rc == 0 else None
 
 
 def apply_resident_grouped(handles, x_int, out_features, fw: int, phase_ids=None):
-    """Same input through several resident weights with one upload and one download; results in
-    handle order (qk_cuda.py:405-442)."""
-    lib = _lib()
-    hs = tuple(int(h) for h in handles)
-    ofs = tuple(int(n) for n in out_features)
-    if not hs or len(hs) != len(ofs) or len(hs) > 16 or any(n <= 0 for n in ofs):
-        raise ValueError("grouped resident apply requires 1..16 handles and matching positive output sizes")
-    phases = tuple(PROFILE_OTHER for _ in hs) if phase_ids is None else tuple(int(p) for p in phase_ids)
-    if len(phases) != len(hs) or any(p not in (0, 1, 2, 3, 4) for p in phases):
-        raise ValueError("grouped resident phase_ids must match handles and use known identifiers")
-    x = _x2d(x_int)
-    rows = int(x.shape[0])
-    total = rows * sum(ofs)
-    flat = np.empty(total, np.int64)
-    harr = (ctypes.c_int64 * len(hs))(*hs)
-    parr = (ctypes.c_int * len(hs))(*phases)
-    with _CUDA_LOCK:
-        rc = lib.qk_apply_resident_grouped(harr, parr, len(hs), x.ctypes.data, rows, int(fw), total, flat.ctypes.data)
+    """One activation through up to sixteen registered weights with a single upload and download; a tuple of results in
+    the order of ``handles``.  ``phase_ids`` label the products for the profile counters."""
+    hs, widths = [int(h) for h in handles], [int(n) for n in out_features]
+    n = len(hs)
+    if not 1 <= n <= _MAX_GROUP or len(widths) != n or min(widths) <= 0:
+        raise ValueError(f"a grouped apply takes 1..{_MAX_GROUP} handles with one positive output width each")
+    labels = [PROFILE_OTHER] * n if phase_ids is None else [int(p) for p in phase_ids]
+    if len(labels) != n or not set(labels) <= {PROFILE_OTHER, PROFILE_Q, PROFILE_K, PROFILE_V, PROFILE_O}:
+        raise ValueError("phase_ids must give one known phase label per handle")
+    x = _rows(x_int)
+    t = x.shape[0]
+    packed = np.empty(t * sum(widths), np.int64)
+    rc = _native("qk_apply_resident_grouped", _handle_array(hs, n), (ctypes.c_int * n)(*labels), n, x.ctypes.data, t, int(fw),
+                 packed.size, packed.ctypes.data)
     if rc != 0:
         return None
-    result, off = [], 0
-    for n in ofs:
-        result.append(flat[off:off + rows * n].reshape(rows, n))
-        off += rows * n
-    return tuple(result)
+    edges = np.cumsum([t * w for w in widths])[:-1]
+    return tuple(part.reshape(t, w) for part, w in zip(np.split(packed, edges), widths))
 
 
-# ------------------------------------------------------------------------------------------- limb policy ---
+# ------------------------------------------------------------------------------------------------ limb policy ---
 def _balanced_capacity(L: int) -> int:
-    """Largest |x| that L balanced base-256 digits represent: 127*(256^L-1)/255 (qk_cuda.py:973-976)."""
-    return 127 * ((256 ** L - 1) // 255)
+    """Largest magnitude L balanced base-256 digits (each in [-128, 127]) can represent."""
+    return 127 * sum(256 ** i for i in range(int(L)))
+
+
+_CAPACITY = [_balanced_capacity(L) for L in range(_DIGITS + 1)]
 
 
 def limbs_needed(maxabs: int) -> int:
-    """Smallest digit count 1..8 covering +-maxabs; OverflowError beyond eight (qk_cuda.py:979-992)."""
+    """Fewest digits (1..8) that cover +-maxabs; OverflowError when even eight do not."""
     m = int(maxabs)
-    L = 1
-    while L < 8 and m > _balanced_capacity(L):
-        L += 1
-    if m > _balanced_capacity(8):
-        raise OverflowError(f"|x| max {m} exceeds 8 balanced base-256 digits ({_balanced_capacity(8)})")
-    return L
+    for L in range(1, _DIGITS + 1):
+        if m <= _CAPACITY[L]:
+            return L
+    raise OverflowError(f"magnitude {m} is beyond {_DIGITS} balanced base-256 digits ({_CAPACITY[_DIGITS]})")
 
 
 def _activation_absmax(x: np.ndarray) -> int:
-    return max(abs(int(x.min())), abs(int(x.max()))) if x.size else 0
+    return 0 if x.size == 0 else max(-int(x.min()), int(x.max()))
 
 
 def _dp4a_limb_count(x: np.ndarray, requested=None):
-    """Digit count for the type-specific applies.  The kernels here always carry eight digits and
-    recombine them in 128 bits, so any count up to eight is exact; ``None`` means the activation
-    needs a ninth digit and the caller must use :func:`apply_resident` (which then takes the
-    128-bit kernel).  An explicit count that is too small or out of range is a caller error."""
+    """Digit count handed to the type-specific applies.  The kernels always carry eight digits and recombine in 128 bits,
+    so any sufficient count is exact.  ``None``: the activation needs a ninth digit and no count was asked for (the caller
+    then uses :func:`apply_resident`, which takes the 128-bit kernel); an explicit count that cannot hold the activation is
+    the caller's error."""
     try:
-        needed = limbs_needed(_activation_absmax(x))
+        need = limbs_needed(_activation_absmax(x))
     except OverflowError:
         if requested is None:
             return None
-        raise ValueError("activation is not representable by eight balanced base-256 digits") from None
+        raise ValueError(f"the activation does not fit {_DIGITS} balanced base-256 digits") from None
     if requested is None:
-        return needed
-    requested = int(requested)
-    if not 1 <= requested <= 8:
-        raise ValueError(f"limb count must be in [1, 8], got {requested}")
-    if requested < needed:
-        raise ValueError(f"limb count {requested} is too small; activation requires {needed}")
-    return requested
-
-
-def dp4a_available() -> bool:
-    return available()
+        return need
+    want = int(requested)
+    if want < 1 or want > _DIGITS:
+        raise ValueError(f"a digit count lies in 1..{_DIGITS}, not {want}")
+    if want < need:
+        raise ValueError(f"{want} digits cannot hold this activation, which needs {need}")
+    return want
 
 
 def apply_resident_dp4a(handle: int, x_int, out_f: int, fw: int, qtype: int, ln=None):
-    """Type-checked apply of a resident Q4_K / Q6_K weight, byte-identical to :func:`apply_resident`
-    (qk_cuda.py:1029-1050).  ``None`` when the handle has the other type or the activation needs a
-    ninth digit."""
-    if qtype not in (Q4_K, Q6_K):
-        raise ValueError(f"unknown qtype {qtype} (expected Q4_K={Q4_K} or Q6_K={Q6_K})")
-    lib = _lib()
-    fn = lib.qk_apply_resident_q4k_dp4a if qtype == Q4_K else lib.qk_apply_resident_q6k_dp4a
-    x = _x2d(x_int)
-    ln = _dp4a_limb_count(x, ln)
-    if ln is None:
+    """Type-checked apply (same bytes as :func:`apply_resident`): ``None`` when the handle is of the other type or the
+    activation needs a ninth digit."""
+    entry = {Q4_K: "qk_apply_resident_q4k_dp4a", Q6_K: "qk_apply_resident_q6k_dp4a"}.get(qtype)
+    if entry is None:
+        raise ValueError(f"qtype {qtype} is neither Q4_K ({Q4_K}) nor Q6_K ({Q6_K})")
+    x = _rows(x_int)
+    digits = _dp4a_limb_count(x, ln)
+    if digits is None:
         return None
-    out = np.empty((x.shape[0], out_f), np.int64)
-    with _CUDA_LOCK:
-        rc = fn(int(handle), x.ctypes.data, x.shape[0], int(fw), int(ln), out.ctypes.data)
-    return None if rc != 0 else out
+    y = np.empty((x.shape[0], int(out_f)), np.int64)
+    rc = _native(entry, int(handle), x.ctypes.data, x.shape[0], int(fw), digits, y.ctypes.data)
+    return y if rc == 0 else None
 
 
 def apply_resident_q6k_dp4a(handle: int, x_int, out_f: int, fw: int, ln=None):
     return apply_resident_dp4a(handle, x_int, out_f, fw, Q6_K, ln)
 
 
-# ------------------------------------------------------------------------------------- router / MoE block ---
-_I128_MAX = (1 << 127) - 1
-
-
+# ----------------------------------------------------------------------------------------- router, MoE block ---
 def _rmsnorm_i128_safe(x: np.ndarray) -> bool:
-    """Each row's sum of squares must fit a signed 128-bit integer (qk_cuda.py:310-328)."""
-    if x.ndim != 2 or x.shape[1] <= 0:
+    """Whether every row's sum of squares stays below 2**127, the width the native accumulator has."""
+    if x.ndim != 2 or x.shape[1] == 0:
         return False
-    width = int(x.shape[1])
-    for row in x:
-        maxabs = max(abs(int(row.min())), abs(int(row.max())))
-        if maxabs * maxabs * width <= _I128_MAX:
+    limit = 1 << 127
+    peak = np.abs(x.astype(object)).max(axis=1)                 # Python integers: abs(INT64_MIN) must not wrap
+    for row, m in zip(x, peak):
+        if int(m) ** 2 * x.shape[1] < limit:                    # the cheap bound settles almost every row
             continue
-        total = 0
-        for v in row:
-            total += int(v) * int(v)
-            if total > _I128_MAX:
-                return False
+        if sum(int(v) * int(v) for v in row) >= limit:
+            return False
     return True
 
 
-def resident_preprocess_available() -> bool:
-    return available()
-
-
 def rmsnorm_router(gain_handle: int, router_handle: int, x_int, n_used: int, fa: int, fw: int, eps: int = 1):
-    """Exact RMSNorm, dense int64 router product, top-k (lowest index on ties) and sigmoid gates.
-    Returns (h [T,D], ids [T,K] int32, gates [T,K]) or ``None`` when the activation leaves the exact
-    envelope; shape/runtime failures raise (qk_cuda.py:331-372)."""
-    lib = _lib()
-    x = np.asarray(x_int, dtype=np.int64)
-    if x.ndim == 1:
-        x = x.reshape(1, -1)
-    if x.ndim != 2 or x.shape[0] <= 0 or x.shape[1] <= 0:
-        raise ValueError("resident RMSNorm/router requires a non-empty vector or 2-D activation")
-    x = np.ascontiguousarray(x)
-    n_used, fa, fw, eps = int(n_used), int(fa), int(fw), int(eps)
-    if not 0 < n_used <= np.iinfo(np.int32).max:
-        raise ValueError("n_used out of range")
-    if not 1 <= fa <= 29 or not 0 <= fw <= 62 or not 0 <= eps <= (1 << 64) - 1:
-        raise ValueError("fixed-point parameters are outside the native envelope")
+    """Exact RMSNorm, dense int64 router product, top-k (lowest index wins ties), sigmoid gates.
+    (h [T,D], ids [T,K] int32, gates [T,K]) or ``None`` when a row leaves the exact envelope; a bad shape or a runtime
+    failure raises."""
+    x = _rows(x_int)
+    if 0 in x.shape:
+        raise ValueError("the router needs a non-empty activation")
+    k, fa, fw, eps = int(n_used), int(fa), int(fw), int(eps)
+    if k <= 0:
+        raise ValueError("n_used must be positive")
+    if not (1 <= fa <= 29 and 0 <= fw <= 62 and 0 <= eps < 1 << 64):
+        raise ValueError("fa, fw or eps lies outside what the native entry accepts")
     if not _rmsnorm_i128_safe(x):
         return None
-    rows = int(x.shape[0])
-    h = np.empty_like(x)
-    ids = np.empty((rows, n_used), np.int32)
-    gates = np.empty((rows, n_used), np.int64)
-    with _CUDA_LOCK:
-        rc = int(lib.qk_rmsnorm_router(int(gain_handle), int(router_handle), x.ctypes.data, rows, fa, fw, eps, n_used,
-                                       h.size, ids.size, h.ctypes.data, ids.ctypes.data, gates.ctypes.data))
+    t = x.shape[0]
+    h, ids, gates = np.empty_like(x), np.empty((t, k), np.int32), np.empty((t, k), np.int64)
+    rc = int(_native("qk_rmsnorm_router", int(gain_handle), int(router_handle), x.ctypes.data, t, fa, fw, eps, k, h.size, ids.size,
+                     h.ctypes.data, ids.ctypes.data, gates.ctypes.data))
     if rc == 3:
         return None
-    if rc != 0:
-        raise CudaContextError(f"resident RMSNorm/router failed with native status {rc}")
+    if rc:
+        raise CudaContextError(f"RMSNorm + router returned native status {rc}")
     return h, ids, gates
 
 
-def moe_ffn_available() -> bool:
-    return available()
-
-
-moe_ffn_dp4a_available = moe_ffn_batched_available = moe_ffn_batched_dp4a_available = moe_ffn_available
+def _expert_triples(gate_h, up_h, down_h, count: int, what: str):
+    if count <= 0 or not (len(gate_h) == len(up_h) == len(down_h) == count):
+        raise ValueError(f"{what} needs {max(count, 1)} gate, up and down handles each")
+    return tuple(_handle_array(hs, count) for hs in (gate_h, up_h, down_h))
 
 
 def moe_ffn(gate_h, up_h, down_h, h, gates, d_model: int, e_ffn: int, fa: int, fw: int, dp4a: bool = False):
-    """Decode MoE expert FFN on one token: out[d_model] = sum_e ((down_e(silu(gate_e h) * up_e h) * g_e) >> fa).
-    ``dp4a`` selects the type-specific entry name; both produce identical bytes (qk_cuda.py:1104-1124)."""
-    lib = _lib()
-    fn = lib.qk_moe_ffn_dp4a if dp4a else lib.qk_moe_ffn
+    """One token through its routed experts: out[d_model] = sum_e ((down_e(silu(gate_e h) * up_e h) * g_e) >> fa).
+    ``dp4a`` selects the second entry name of the ABI; both give the same bytes.  ``None`` on a native failure."""
     n_e = len(gate_h)
-    if n_e <= 0 or len(up_h) != n_e or len(down_h) != n_e:
-        raise ValueError("MoE requires the same positive number of gate, up, and down handles")
-    arr = lambda hs: (ctypes.c_int64 * n_e)(*[int(v) for v in hs])
-    hh = np.ascontiguousarray(np.asarray(h, np.int64).reshape(-1))
-    gg = np.ascontiguousarray(np.asarray(gates, np.int64).reshape(-1))
-    if hh.size != d_model or gg.size != n_e:
-        raise ValueError(f"MoE expected h.size={d_model} and gates.size={n_e}, got {hh.size} and {gg.size}")
+    triples = _expert_triples(gate_h, up_h, down_h, n_e, "the expert stage")
+    row, g = _rows(h).reshape(-1), _rows(gates).reshape(-1)
+    if row.size != int(d_model) or g.size != n_e:
+        raise ValueError(f"expected {d_model} hidden values and {n_e} gates, got {row.size} and {g.size}")
     out = np.empty(int(d_model), np.int64)
-    with _CUDA_LOCK:
-        rc = fn(arr(gate_h), arr(up_h), arr(down_h), n_e, hh.ctypes.data, gg.ctypes.data, int(d_model), int(e_ffn),
-                int(fa), int(fw), out.ctypes.data)
-    return None if rc != 0 else out
+    rc = _native("qk_moe_ffn_dp4a" if dp4a else "qk_moe_ffn", *triples, n_e, row.ctypes.data, g.ctypes.data, int(d_model), int(e_ffn),
+                 int(fa), int(fw), out.ctypes.data)
+    return out if rc == 0 else None
 
 
 def moe_ffn_batched(gate_h, up_h, down_h, m: int, k: int, h, gates, d_model: int, e_ffn: int, fa: int, fw: int, *,
                     dp4a: bool = False):
-    """Batched MoE over all m*k (token, selected expert) pairs, handles flattened token-major
-    (pair = t*k + j); h [m,d_model], gates [m*k] -> [m,d_model] (qk_cuda.py:1073-1101)."""
-    lib = _lib()
-    P = m * k
+    """All m*k (token, routed expert) pairs in one call, handles flattened token-major (pair = t*k + j):
+    h [m, d_model], gates [m*k] -> [m, d_model].  Prefill-sized calls run on the grouped tensor-core tiles."""
+    m, k = int(m), int(k)
     if m <= 0 or k <= 0:
-        raise ValueError(f"batched MoE requires positive m and k, got m={m}, k={k}")
-    if len(gate_h) != P or len(up_h) != P or len(down_h) != P:
-        raise ValueError(f"batched MoE requires exactly m*k={P} handles for each projection")
-    arr = lambda hs: (ctypes.c_int64 * P)(*[int(v) for v in hs])
-    hh = np.ascontiguousarray(np.asarray(h, np.int64).reshape(-1))
-    gg = np.ascontiguousarray(np.asarray(gates, np.int64).reshape(-1))
-    if hh.size != m * d_model or gg.size != P:
-        raise ValueError(f"batched MoE expected h.size={m * d_model} and gates.size={P}")
-    out = np.empty((m, d_model), np.int64)
-    with _CUDA_LOCK:
-        args = (arr(gate_h), arr(up_h), arr(down_h), int(m), int(k), hh.ctypes.data, gg.ctypes.data, int(d_model),
-                int(e_ffn), int(fa), int(fw), out.ctypes.data)
-        use_dp4a = bool(dp4a and _dp4a_limb_count(hh) is not None and
-                        limbs_needed(_activation_absmax(hh)) <= _DP4A_SAFE_LIMBS)
-        rc = lib.qk_moe_ffn_batched_dp4a(*args) if use_dp4a else lib.qk_moe_ffn_batched(*args)
-        if use_dp4a and rc == 2:
-            rc = lib.qk_moe_ffn_batched(*args)
-    return None if rc != 0 else out
+        raise ValueError(f"m and k must be positive, got {m} and {k}")
+    pairs = m * k
+    triples = _expert_triples(gate_h, up_h, down_h, pairs, "the batched expert stage")
+    rows, g = _rows(h).reshape(-1), _rows(gates).reshape(-1)
+    if rows.size != m * int(d_model) or g.size != pairs:
+        raise ValueError(f"expected {m * int(d_model)} hidden values and {pairs} gates, got {rows.size} and {g.size}")
+    out = np.empty((m, int(d_model)), np.int64)
+    args = (*triples, m, k, rows.ctypes.data, g.ctypes.data, int(d_model), int(e_ffn), int(fa), int(fw), out.ctypes.data)
+    rc = 2
+    if dp4a and _dp4a_limb_count(rows) is not None and limbs_needed(_activation_absmax(rows)) <= 4:
+        rc = _native("qk_moe_ffn_batched_dp4a", *args)              # status 2 = envelope miss: the exact entry follows
+    if rc == 2:
+        rc = _native("qk_moe_ffn_batched", *args)
+    return out if rc == 0 else None
 
 
-def moe_workspace_allocations():
-    with _CUDA_LOCK:
-        return int(_lib().qk_moe_workspace_allocations())
+def moe_workspace_allocations() -> int:
+    return int(_native("qk_moe_workspace_allocations"))
 
 
-def moe_workspace_bytes():
-    with _CUDA_LOCK:
-        return int(_lib().qk_moe_workspace_bytes())
+def moe_workspace_bytes() -> int:
+    return int(_native("qk_moe_workspace_bytes"))
 
 
 def release_moe_workspace() -> bool:
-    with _CUDA_LOCK:
-        _lib().qk_moe_workspace_release()
+    _native("qk_moe_workspace_release")
     return True
 
 
-# ------------------------------------------------------------------------------------------------ profile ---
+def moe_block(layer_handle: int, x_int, n_used: int, fa: int, fw: int, gain_handle: int = -1, eps: int = 1):
+    """Whole MoE block on host arrays in one native call: ``moe(x)`` or, with a gain handle, ``x + moe(rmsnorm(x, gain))``.
+    (out [T,d], ids [T,k] int32, gates [T,k]) or ``None`` when an input leaves the exact envelope.  An additive entry
+    without a counterpart in the reference bridge: one upload and one download instead of the per-layer sequence
+    rmsnorm_router + moe_ffn."""
+    x = _rows(x_int)
+    t, k = x.shape[0], int(n_used)
+    out, ids, gates = np.empty_like(x), np.empty((t, k), np.int32), np.empty((t, k), np.int64)
+    rc = _native("iie_moe_block_host", int(layer_handle), int(gain_handle), x.ctypes.data, t, int(fa), int(fw), int(eps),
+                 out.ctypes.data, ids.ctypes.data, gates.ctypes.data)
+    if rc == 3:
+        return None
+    if rc:
+        raise CudaContextError(f"the MoE block returned native status {rc}")
+    return out, ids, gates
+
+
+# ------------------------------------------------------------------------------------------- profile counters ---
 def profile_reset(*, enabled: bool = True) -> bool:
-    """Zero the native counters and switch collection on or off (qk_cuda.py:870-879)."""
+    """Zero the native counters; collection is on afterwards unless ``enabled`` is false."""
     lib = _lib()
-    with _CUDA_LOCK:
+    with _CUDA_LOCK:                                 # one critical section: no call may count between the three steps
         lib.qk_profile_set_enabled(0)
         lib.qk_profile_reset()
-        lib.qk_profile_set_enabled(int(bool(enabled)))
+        lib.qk_profile_set_enabled(1 if enabled else 0)
     return True
 
 
 def profile_set_enabled(enabled: bool) -> bool:
-    with _CUDA_LOCK:
-        _lib().qk_profile_set_enabled(1 if enabled else 0)
+    _native("qk_profile_set_enabled", 1 if enabled else 0)
     return True
 
 
 def profile_snapshot() -> dict:
-    buf = (ctypes.c_uint64 * len(_PROFILE_METRICS))()
-    with _CUDA_LOCK:
-        n = _lib().qk_profile_snapshot(buf, len(_PROFILE_METRICS))
-    if n != len(_PROFILE_METRICS):
-        raise CudaContextError("profile snapshot size mismatch")
-    return {name: int(buf[i]) for i, name in enumerate(_PROFILE_METRICS)}
+    n = len(_PROFILE_METRICS)
+    raw = (ctypes.c_uint64 * n)()
+    if _native("qk_profile_snapshot", raw, n) != n:
+        raise CudaContextError("the native profile snapshot has an unexpected number of counters")
+    return dict(zip(_PROFILE_METRICS, (int(v) for v in raw)))
 
 
-def resident_attention_available() -> bool:
-    """True when the request-scoped attention bank can be used (qk_cuda.py:471-473 of the reference bridge)."""
-    return available()
-
-
+# --------------------------------------------------------------------------------------------- attention bank ---
 class ResidentAttentionCache:
-    """Request-scoped device K/V bank and exact single-token attention sublayer; names, arguments and error behaviour of
-    north-mini-code/src/nmc/qk_cuda.py:476-569.  A prefill's K/V is imported once per layer; every ``apply`` then takes
-    one normalised hidden row and returns the projected attention row, appending the new K/V row on the device.  A failed
-    call poisons that layer and raises; the caller closes the context instead of retrying."""
+    """K/V rows of one request kept on the device, and the single-token attention sublayer over them
+    (``qk_attention_bank_*``).  After a prefill each layer's K/V is imported once; every :meth:`apply` takes one
+    normalised hidden row, appends that token's K/V row on the device and returns the projected attention row.
+    A call that fails leaves its layer unusable: the caller drops the context rather than retrying."""
 
     def __init__(self, n_layers: int, max_length: int, d_model: int, n_heads: int, n_kv: int, head_dim: int, fa: int, cos, sin):
-        lib = _lib()
-        n_layers, max_length, d_model, n_heads, n_kv, head_dim, fa = (int(v) for v in (n_layers, max_length, d_model, n_heads,
-                                                                                        n_kv, head_dim, fa))
-        q_width = n_heads * head_dim
-        if n_layers <= 0 or max_length <= 0 or d_model <= 0 or n_heads <= 0 or n_kv <= 0 or n_heads % n_kv or head_dim <= 0 or \
-                head_dim % 2 or not 1 <= fa <= 29 or d_model % 256 or q_width % 256:
-            raise ValueError("invalid resident attention dimensions")
-        c = np.ascontiguousarray(np.asarray(cos, dtype=np.int64))
-        s = np.ascontiguousarray(np.asarray(sin, dtype=np.int64))
-        expected = (max_length, head_dim // 2)
-        if c.shape != expected or s.shape != expected:
-            raise ValueError(f"resident attention RoPE tables must both have shape {expected}")
-        with _CUDA_LOCK:
-            handle = int(lib.qk_attention_bank_create(n_layers, max_length, d_model, n_heads, n_kv, head_dim, fa,
-                                                      c.ctypes.data, s.ctypes.data))
+        dims = dict(n_layers=int(n_layers), max_length=int(max_length), d_model=int(d_model), n_heads=int(n_heads),
+                    n_kv=int(n_kv), head_dim=int(head_dim), fa=int(fa))
+        q_width = dims["n_heads"] * dims["head_dim"]
+        positive = all(dims[name] > 0 for name in ("n_layers", "max_length", "d_model", "n_heads", "n_kv", "head_dim"))
+        if not positive or dims["n_heads"] % dims["n_kv"] or dims["head_dim"] % 2 or dims["d_model"] % 256 or q_width % 256 \
+                or not 1 <= dims["fa"] <= 29:
+            raise ValueError(f"the attention bank cannot take these dimensions: {dims}")
+        tables = [np.ascontiguousarray(np.asarray(t, dtype=np.int64)) for t in (cos, sin)]
+        want = (dims["max_length"], dims["head_dim"] // 2)
+        if any(t.shape != want for t in tables):
+            raise ValueError(f"cos and sin must each be {want}, got {tables[0].shape} and {tables[1].shape}")
+        handle = int(_native("qk_attention_bank_create", dims["n_layers"], dims["max_length"], dims["d_model"], dims["n_heads"],
+                             dims["n_kv"], dims["head_dim"], dims["fa"], tables[0].ctypes.data, tables[1].ctypes.data))
         if handle < 0:
-            raise CudaContextError("resident attention context creation failed; check dimensions and VRAM")
-        self.handle = handle
-        self.n_layers, self.max_length = n_layers, max_length
-        self.n_heads, self.n_kv, self.head_dim, self.fa = n_heads, n_kv, head_dim, fa
-        self.d_model, self.q_width = d_model, q_width
-        self._lengths = [0] * n_layers
-        self._closed = False
+            raise CudaContextError("the attention bank could not be created (dimensions or device memory)")
+        self.handle, self.q_width = handle, q_width
+        for name, value in dims.items():
+            setattr(self, name, value)
+        self._filled = [0] * dims["n_layers"]
+        self._open = True
+
+    def _check(self, layer: int) -> int:
+        if not self._open:
+            raise CudaContextError("this attention bank has been closed")
+        layer = int(layer)
+        if not 0 <= layer < self.n_layers:
+            raise ValueError(f"layer {layer} is outside 0..{self.n_layers - 1}")
+        return layer
 
     def length(self, layer=0):
-        return self._lengths[layer]
+        return self._filled[layer]
 
     def import_layer(self, layer: int, k, v) -> None:
-        if self._closed:
-            raise CudaContextError("resident attention context is closed")
-        layer = int(layer)
-        kk = np.ascontiguousarray(np.asarray(k, dtype=np.int64))
-        vv = np.ascontiguousarray(np.asarray(v, dtype=np.int64))
-        if kk.shape != vv.shape or kk.ndim != 3 or kk.shape[0] != self.n_kv or kk.shape[2] != self.head_dim:
-            raise ValueError("resident attention import expects matching [n_kv, length, head_dim] K/V")
-        length = int(kk.shape[1])
-        if not 0 <= layer < self.n_layers or length > self.max_length:
-            raise ValueError("resident attention import exceeds layer or context bounds")
-        with _CUDA_LOCK:
-            rc = _lib().qk_attention_bank_import(self.handle, layer, kk.ctypes.data, vv.ctypes.data, length)
-        if rc != 0:
-            raise CudaContextError(f"resident attention K/V import failed for layer {layer}")
-        self._lengths[layer] = length
+        layer = self._check(layer)
+        rows = [np.ascontiguousarray(np.asarray(t, dtype=np.int64)) for t in (k, v)]
+        if rows[0].ndim != 3 or rows[0].shape != rows[1].shape or rows[0].shape[0] != self.n_kv or rows[0].shape[2] != self.head_dim:
+            raise ValueError(f"K and V must both be [{self.n_kv}, length, {self.head_dim}]")
+        filled = rows[0].shape[1]
+        if filled > self.max_length:
+            raise ValueError(f"{filled} rows do not fit a bank of {self.max_length}")
+        if _native("qk_attention_bank_import", self.handle, layer, rows[0].ctypes.data, rows[1].ctypes.data, filled) != 0:
+            raise CudaContextError(f"importing K/V into layer {layer} failed")
+        self._filled[layer] = filled
 
     def apply(self, layer: int, q_handle: int, k_handle: int, v_handle: int, o_handle: int, hidden, fw: int,
               window: "int | None", rope: bool):
-        if self._closed:
-            raise CudaContextError("resident attention context is closed")
-        layer = int(layer)
-        if not 0 <= layer < self.n_layers or self._lengths[layer] >= self.max_length:
-            raise ValueError("resident attention decode exceeds layer or context bounds")
+        layer = self._check(layer)
+        if self._filled[layer] >= self.max_length:
+            raise ValueError(f"layer {layer} already holds its {self.max_length} rows")
         x = np.ascontiguousarray(np.asarray(hidden, dtype=np.int64))
         if x.shape != (1, self.d_model):
-            raise ValueError(f"resident attention apply expects hidden shape (1, {self.d_model})")
-        out = np.empty((1, self.d_model), dtype=np.int64)
-        inv_sqrt = int(round((1.0 / self.head_dim ** 0.5) * (1 << self.fa)))
-        with _CUDA_LOCK:
-            rc = int(_lib().qk_attention_bank_apply(self.handle, layer, int(q_handle), int(k_handle), int(v_handle), int(o_handle),
-                                                    x.ctypes.data, int(fw), -1 if window is None else int(window),
-                                                    int(bool(rope)), inv_sqrt, out.size, out.ctypes.data))
-        if rc != 0:
-            detail = "exact overflow guard fired" if rc == 3 else f"native status {rc}"
-            raise CudaContextError(f"resident attention apply failed for layer {layer}: {detail}")
-        self._lengths[layer] += 1
+            raise ValueError(f"the hidden row must be (1, {self.d_model}), not {x.shape}")
+        out = np.empty_like(x)
+        scale = int(round(2 ** self.fa / self.head_dim ** 0.5))
+        rc = int(_native("qk_attention_bank_apply", self.handle, layer, int(q_handle), int(k_handle), int(v_handle), int(o_handle),
+                         x.ctypes.data, int(fw), -1 if window is None else int(window), 1 if rope else 0, scale, out.size,
+                         out.ctypes.data))
+        if rc:
+            why = "a value left the exact envelope" if rc == 3 else f"native status {rc}"
+            raise CudaContextError(f"attention on layer {layer} failed: {why}")
+        self._filled[layer] += 1
         return out
 
     def reset(self) -> None:
-        if self._closed:
-            raise CudaContextError("resident attention context is closed")
-        with _CUDA_LOCK:
-            rc = _lib().qk_attention_bank_reset(self.handle)
-        if rc != 0:
-            raise CudaContextError("resident attention reset failed")
-        self._lengths = [0] * self.n_layers
+        if not self._open:
+            raise CudaContextError("this attention bank has been closed")
+        if _native("qk_attention_bank_reset", self.handle) != 0:
+            raise CudaContextError("the attention bank could not be reset")
+        self._filled = [0] * self.n_layers
 
     def workspace_bytes(self) -> int:
-        with _CUDA_LOCK:
-            return int(_lib().qk_attention_bank_workspace_bytes(self.handle))
+        return int(_native("qk_attention_bank_workspace_bytes", self.handle))
 
     def close(self) -> None:
-        if not self._closed:
-            with _CUDA_LOCK:
-                _lib().qk_attention_bank_destroy(self.handle)
-            self._closed = True
+        if self._open:
+            _native("qk_attention_bank_destroy", self.handle)
+            self._open = False
 
     def __enter__(self):
         return self
 
     def __exit__(self, *exc):
         self.close()
-
-
-def moe_block(layer_handle: int, x_int, n_used: int, fa: int, fw: int, gain_handle: int = -1, eps: int = 1):
-    """Whole MoE block on host arrays in one native call: ``moe(x)`` or, with a gain handle,
-    ``x + moe(rmsnorm(x, gain))``.  Returns (out [T,d], ids [T,k] int32, gates [T,k]) or ``None`` when an
-    input leaves the exact envelope.  Additive entry (no counterpart in the reference bridge): it
-    replaces the per-layer sequence rmsnorm_router + moe_ffn with one upload and one download."""
-    lib = _lib()
-    x = _x2d(x_int)
-    out = np.empty_like(x)
-    ids = np.empty((x.shape[0], int(n_used)), np.int32)
-    gates = np.empty((x.shape[0], int(n_used)), np.int64)
-    with _CUDA_LOCK:
-        rc = lib.iie_moe_block_host(int(layer_handle), int(gain_handle), x.ctypes.data, x.shape[0], int(fa), int(fw),
-                                    int(eps), out.ctypes.data, ids.ctypes.data, gates.ctypes.data)
-    if rc == 3:
-        return None
-    if rc != 0:
-        raise CudaContextError(f"MoE block failed with native status {rc}")
-    return out, ids, gates
