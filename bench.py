@@ -12,15 +12,20 @@ values in place of a prefill.  A step streams 1.9 GB of distinct weights and 0.8
 
 Printed JSON line (rank 0): `value` = tokens/s of the device-resident greedy chain (token id and position stay in
 device cells; one CUDA-graph replay per token); `e2e` = the same through the public per-token call with the
-token id going in and coming out through pinned host buffers; `roofline` = the MoE gate/up kernel (largest single
-consumer of the step) timed alone with CUDA events against the measured HBM copy bandwidth; `cpu_baseline` = the
-CPU oracle on this box's host cores for a bounded sample; `config.moe_blocks_only` = the 48 MoE blocks alone.
-Before timing, every stage of one token (embedding, norms, projections, cache row, attention, MoE routing and
-output of every block, head logits, pick) is compared byte for byte with the CPU oracle, and the graph replay is
-compared with the eager chain.
+token id going in and coming out through pinned host buffers; `e2e_abi` = the reference-facing host-buffer entries
+(`qk_moe_ffn_batched`, `iie_moe_block_host`) on the config-1 block with NumPy buffers, host<->device copies inside the
+timed call, next to the reference project's own CUDA producer called through the reference's own bridge;
+`roofline` = the MoE gate/up kernel (largest single consumer of the step) timed alone with CUDA events against the
+measured HBM copy bandwidth; `int8_peak` = an int8 GEMM (torch._int_mm, 8192^3) measured in the same run, the
+denominator of the prefill line; `cpu_baseline` = the CPU oracle on this box's host cores for a bounded sample;
+`config.moe_blocks_only` = the 48 MoE blocks alone.  Before timing, every stage of a token (embedding, norms,
+projections, cache row, attention, MoE routing and output of every block, head logits, pick) is compared byte for
+byte with the CPU oracle for four consecutive greedy tokens (all blocks of the first, a sample of the others), and
+the replayed graph is compared with that oracle-checked chain.
 
 `--impl reference` times the reference project's compiled CPU kernel (oracle/_ref) composed the way its engine
-composes a decode step on the CPU, on a bounded sample per step.
+composes a decode step on the CPU: every step runs all the blocks and the head (two synthetic blocks' weights are
+cycled through, so the kernel calls and their sizes are those of the whole model).
 """
 from __future__ import annotations
 
@@ -39,9 +44,21 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 FA, FW = 16, 24
+SUSTAIN_STEPS = 60         # replays before and after the timed steps, inside the clock sampler's window
 D_MODEL, E_FFN, N_EXPERTS, TOP_K = 2048, 768, 128, 8
 N_HEADS, N_KV, HEAD_DIM, VOCAB, WINDOW = 32, 4, 128, 151936, 4096
-GATEUP_DRAM_BYTES_NCU = 14200000          # dram read+write of one gate/up launch (ncu capture of this workload's kernel)
+
+
+def ncu_figure(name: str):
+    """A figure read off an ncu capture, kept as `key=value` lines in profiles/ncu_figures.txt; None when absent."""
+    f = ROOT / "profiles" / "ncu_figures.txt"
+    if f.exists():
+        for line in f.read_text().splitlines():
+            key, _, val = line.partition("=")
+            if key.strip() == name:
+                return float(val.split("#")[0])
+    return None
+
 WORKLOAD = ("config2_decode: batch-1 KV-cached greedy decode of the 30B-A3B-shaped model, 48 blocks (RMSNorm, Q/K/V, RoPE on "
             "sliding-window blocks, int32 KV cache at context 4096, exact integer softmax attention, O, MoE with 128 experts "
             "top-8 eff 768), tied Q6_K head over 151936 tokens, arg-max; Q4_K weights, Q6_K down and head")
@@ -144,81 +161,68 @@ def use_all_host_threads() -> int:
     return n
 
 
-def cpu_moe_block_time(kind: str, n_layers: int, repeats: int, seed: int = 1):
-    """Time the CPU MoE block (one token) on `n_layers` synthetic layers with all host threads.
-    kind "reference": linears by the reference project's compiled kernel (oracle/_ref), element-wise
-    steps in NumPy, composed as north-mini-code/src/nmc/engine.py:429-443; kind "port": this
-    repository's C oracle.  Returns seconds per layer-token (median over repeats)."""
-    from oracle import native as onat
-    from oracle import qk_oracle as o
-    layers = []
-    for li in range(n_layers):
-        router, gate, up, down, h = o.synth_moe(seed * 1000 + li, D_MODEL, E_FFN, N_EXPERTS, 1, FA)
-        layers.append((router, gate, up, down, h))
-    nb_in, nb_dn = D_MODEL // 256, E_FFN // 256
+class CpuDecodeStep:
+    """One decode step on the CPU, composed as the reference's engine composes it on its CPU path
+    (north-mini-code/src/nmc/engine.py:429-443 for the experts, cohere2.py:357-376 for the block, :201-204 for the head):
+    per block the four attention projections, NumPy integer attention over `context` cached keys, router, top-k, the
+    routed experts' gate / up / down products with integer SiLU and the gate-weighted sum; then the tied head.
+    `n_sets` synthetic blocks are built and cycled through, so a step of `layers` blocks makes the kernel calls of the
+    whole model without holding 19 GB of host weights.  kind "reference": products by the reference project's compiled
+    kernel (oracle/_ref); "port": this repository's C oracle."""
 
-    def ref_block(router, gate, up, down, h):
-        lin = onat.ref_qk_linear
-        logits = lin(router, h, N_EXPERTS, nb_in, FW, o.Q4_K)[0]
+    def __init__(self, kind: str, n_sets: int, context: int, seed: int = 1):
+        from oracle import native as onat
+        from oracle import qk_oracle as o
+        self.o, self.onat, self.kind, self.context = o, onat, kind, context
+        self.lin = onat.ref_qk_linear if kind == "reference" else onat.qk_linear
+        rng = np.random.default_rng(seed)
+        nb = D_MODEL // 256
+        self.sets = []
+        for li in range(n_sets):
+            router, gate, up, down, _ = o.synth_moe(seed * 1000 + li, D_MODEL, E_FFN, N_EXPERTS, 1, FA)
+            self.sets.append({
+                "wq": o.synth_q4k(rng, N_HEADS * HEAD_DIM, nb), "wk": o.synth_q4k(rng, N_KV * HEAD_DIM, nb),
+                "wv": o.synth_q4k(rng, N_KV * HEAD_DIM, nb), "wo": o.synth_q4k(rng, D_MODEL, N_HEADS * HEAD_DIM // 256),
+                "router": router, "gate": gate, "up": up, "down": down,
+                "gain": o.to_fixed(np.abs(rng.standard_normal(D_MODEL)) + 0.5, FA),
+                "k": rng.integers(-(1 << 18), 1 << 18, size=(N_KV, context + 1, HEAD_DIM), dtype=np.int64),
+                "v": rng.integers(-(1 << 18), 1 << 18, size=(N_KV, context + 1, HEAD_DIM), dtype=np.int64)})
+        self.embd = o.synth_q6k(rng, VOCAB, nb)
+        self.out_gain = o.to_fixed(np.abs(rng.standard_normal(D_MODEL)) + 0.5, FA)
+        self.cos, self.sin = o.build_rope_tables(1, HEAD_DIM, 50000.0, FA)
+        self.x0 = o.to_fixed(rng.standard_normal((1, D_MODEL)), FA)
+
+    def block(self, x, W, full: bool):
+        o, lin, nb, ctx = self.o, self.lin, D_MODEL // 256, self.context
+        h = o.rmsnorm_fixed(x, FA, 1, W["gain"])
+        q = lin(W["wq"], h, N_HEADS * HEAD_DIM, nb, FW, o.Q4_K).reshape(1, N_HEADS, HEAD_DIM)
+        k = lin(W["wk"], h, N_KV * HEAD_DIM, nb, FW, o.Q4_K).reshape(1, N_KV, HEAD_DIM)
+        v = lin(W["wv"], h, N_KV * HEAD_DIM, nb, FW, o.Q4_K).reshape(1, N_KV, HEAD_DIM)
+        if not full:
+            rot = lambda t: o.rope_fixed(np.transpose(t, (1, 0, 2)), self.cos, self.sin, FA).transpose(1, 0, 2)
+            q, k = rot(q), rot(k)
+        W["k"][:, ctx] = k[0]; W["v"][:, ctx] = v[0]
+        att = o.attention_cached(q, W["k"], W["v"], ctx, N_HEADS, N_KV, FA, None if full else WINDOW)
+        ao = lin(W["wo"], att, D_MODEL, N_HEADS * HEAD_DIM // 256, FW, o.Q4_K)
+        logits = lin(W["router"], h, N_EXPERTS, nb, FW, o.Q4_K)[0]
         sel = o.topk_lowidx(logits, TOP_K)
         gates = o.sigmoid_fixed(logits[sel], FA)
-        out = np.zeros(D_MODEL, dtype=object)
+        moe = np.zeros(D_MODEL, dtype=object)
         for j, e in enumerate(sel):
-            g = o.silu_int(lin(gate[e], h, E_FFN, nb_in, FW, o.Q4_K), FA)
-            u = lin(up[e], h, E_FFN, nb_in, FW, o.Q4_K)
-            gu = o.mul_shift(g, u, FA)
-            dn = lin(down[e], gu, D_MODEL, nb_dn, FW, o.Q6_K)[0].astype(object)
-            out += (dn * int(gates[j])) >> FA
-        return out.astype(np.int64)
+            g = o.silu_int(lin(W["gate"][e], h, E_FFN, nb, FW, o.Q4_K), FA)
+            u = lin(W["up"][e], h, E_FFN, nb, FW, o.Q4_K)
+            dn = lin(W["down"][e], o.mul_shift(g, u, FA), D_MODEL, E_FFN // 256, FW, o.Q6_K)[0].astype(object)
+            moe += (dn * int(gates[j])) >> FA
+        return x + ao + moe.astype(np.int64)
 
-    def port_block(router, gate, up, down, h):
-        return onat.moe_block(router, o.Q4_K, gate, up, down, o.Q4_K, o.Q6_K, TOP_K, h, D_MODEL, E_FFN, FA, FW)[2][0]
-
-    fn = ref_block if kind == "reference" else port_block
-    a = ref_block(*layers[0]) if onat.ref_available() else None
-    b = port_block(*layers[0])
-    if a is not None:
-        assert np.array_equal(a, b), "reference-built kernel and the C oracle disagree"
-    times = []
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        for lay in layers:
-            fn(*lay)
-        times.append((time.perf_counter() - t0) / n_layers)
-    return float(np.median(times))
-
-
-def cpu_token_time(kind: str, n_layers: int, repeats: int, context: int, seed: int = 1):
-    """CPU time of a decode step, split as (seconds per block, seconds for the head): per sampled block the four
-    attention projections and the MoE block (reference-built kernel or the C oracle), NumPy integer attention over
-    `context` cached keys as north-mini-code/src/nmc/cohere2.py:324-354, and once the tied head product."""
-    from oracle import native as onat
-    from oracle import qk_oracle as o
-    rng = np.random.default_rng(seed)
-    nb = D_MODEL // 256
-    lin = onat.ref_qk_linear if kind == "reference" else onat.qk_linear
-    wq = o.synth_q4k(rng, N_HEADS * HEAD_DIM, nb); wk = o.synth_q4k(rng, N_KV * HEAD_DIM, nb); wv = o.synth_q4k(rng, N_KV * HEAD_DIM, nb)
-    wo = o.synth_q4k(rng, D_MODEL, N_HEADS * HEAD_DIM // 256)
-    ck = rng.integers(-(1 << 18), 1 << 18, size=(N_KV, context + 1, HEAD_DIM), dtype=np.int64)
-    cv = rng.integers(-(1 << 18), 1 << 18, size=(N_KV, context + 1, HEAD_DIM), dtype=np.int64)
-    h = o.to_fixed(rng.standard_normal((1, D_MODEL)), FA)
-    cos, sin = o.build_rope_tables(1, HEAD_DIM, 50000.0, FA)
-
-    def attn_part():
-        q = lin(wq, h, N_HEADS * HEAD_DIM, nb, FW, o.Q4_K).reshape(1, N_HEADS, HEAD_DIM)
-        k = lin(wk, h, N_KV * HEAD_DIM, nb, FW, o.Q4_K).reshape(1, N_KV, HEAD_DIM)
-        v = lin(wv, h, N_KV * HEAD_DIM, nb, FW, o.Q4_K).reshape(1, N_KV, HEAD_DIM)
-        q = o.rope_fixed(np.transpose(q, (1, 0, 2)), cos, sin, FA).transpose(1, 0, 2)
-        ck[:, context] = o.rope_fixed(np.transpose(k, (1, 0, 2)), cos, sin, FA)[:, 0]; cv[:, context] = v[0]
-        att = o.attention_cached(q, ck, cv, context, N_HEADS, N_KV, FA, WINDOW)
-        return lin(wo, att, D_MODEL, N_HEADS * HEAD_DIM // 256, FW, o.Q4_K)
-    moe_s = cpu_moe_block_time(kind, n_layers, repeats, seed)
-    ts = []
-    for _ in range(repeats):
-        t0 = time.perf_counter(); attn_part(); ts.append(time.perf_counter() - t0)
-    embd = o.synth_q6k(rng, VOCAB, nb)
-    t0 = time.perf_counter(); lin(embd, h, VOCAB, nb, FW, o.Q6_K); head_s = time.perf_counter() - t0
-    return moe_s + float(np.median(ts)), head_s
+    def step(self, layers: int) -> int:
+        o = self.o
+        x = self.x0
+        for li in range(layers):
+            x = self.block(x, self.sets[li % len(self.sets)], li % 4 == 0)
+        hn = o.rmsnorm_fixed(x, FA, 1, self.out_gain)
+        logits = self.lin(self.embd, hn, VOCAB, D_MODEL // 256, FW, o.Q6_K)[0]
+        return int(np.flatnonzero(logits == logits.max())[0])
 
 
 def run_reference(args):
@@ -228,25 +232,145 @@ def run_reference(args):
     use_all_host_threads()
     from oracle import native as onat
     kind = "reference" if onat.ref_available() else "port"
-    n_layers = 2
-    for _ in range(max(args.warmup, 1) - 1):
-        cpu_moe_block_time(kind, n_layers, 1)
-    t0 = time.perf_counter()
-    per_layer, head_s = cpu_token_time(kind, n_layers, max(args.steps, 1), args.context)
-    wall = time.perf_counter() - t0
-    step_s = per_layer * args.layers + head_s
+    cpu = CpuDecodeStep(kind, 2, args.context)
+    for _ in range(args.warmup):
+        cpu.step(args.layers)
+    times = []
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        cpu.step(args.layers)
+        times.append(time.perf_counter() - t0)
+    wall = time.perf_counter() - t_all
+    step_s = wall / max(args.steps, 1)
     value = 1.0 / step_s
-    sample = (f"{n_layers} blocks (4 projections, attention over {args.context} keys, MoE block) and the head per step, "
-              f"scaled to {args.layers} blocks")
+    sample = (f"every step: {args.layers} blocks (4 projections, attention over {args.context} keys, router, top-{TOP_K}, "
+              f"{TOP_K} experts) and the head over {VOCAB} tokens; weights of 2 synthetic blocks cycled")
     print(json.dumps({
         "impl": "reference", "metric": "decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "n/a (CPU)"},
+        "config": {"workload": WORKLOAD, "layers": args.layers, "context": args.context, "l2": "n/a (CPU)"},
         "cpu_baseline": {"value": value, "unit": "tok/s", "cores": host_cores(), "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "wall_s": wall,
+        "wall_s": wall, "ms_per_step_median": float(np.median(times)) * 1e3,
     }))
+
+
+def int8_peak():
+    """int8 x int8 -> int32 GEMM throughput of this GPU, measured in this run (torch._int_mm, 8192^3, 2*N^3 integer
+    operations): best of 10 launches (burst) and back to back for ~2 s (sustained).  The denominator of the prefill line."""
+    import torch
+    n = 8192
+    a = torch.randint(-128, 127, (n, n), dtype=torch.int8, device="cuda")
+    b = torch.randint(-128, 127, (n, n), dtype=torch.int8, device="cuda")
+    ops = 2.0 * n ** 3
+    for _ in range(3):
+        torch._int_mm(a, b)
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); torch._int_mm(a, b); e1.record(); torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(20, int(2000.0 / best))
+    e0.record()
+    for _ in range(reps):
+        torch._int_mm(a, b)
+    e1.record(); torch.cuda.synchronize()
+    sustained_ms = e0.elapsed_time(e1) / reps
+    del a, b
+    return {"burst_tops": ops / (best * 1e-3) / 1e12, "sustained_tops": ops / (sustained_ms * 1e-3) / 1e12,
+            "how": "torch._int_mm 8192^3 int8, 2*N^3 ops; best of 10 and mean of a ~2 s loop, CUDA events"}
+
+
+_BRIDGE_PROBE = r'''
+import json, sys, time
+import numpy as np
+sys.path.insert(0, sys.argv[1])                       # the repository root: oracle generators only
+from oracle import qk_oracle as o
+from nmc import qk_cuda as q                          # the reference's own bridge (baseline/_ref), library from BONSAI_BIN_DIR
+assert q.available(), "bridge reports the library unusable"
+FA, FW, d, eff, E, k, T = 16, 24, 2048, 768, 128, 8, 16
+router, gate, up, down, h = o.synth_moe(0, d, eff, E, T)
+sel = np.load(sys.argv[2])["config1_ids"]; want = np.load(sys.argv[2])["config1_out"]
+logits = o.qk_linear(router, h, E, d // 256, FW, o.Q4_K)
+gates = np.stack([o.sigmoid_fixed(logits[t][sel[t]], FA) for t in range(T)])
+need = sorted(set(int(e) for e in sel.reshape(-1)))
+gh = {e: q.register_weight(gate[e], eff, d // 256, q.Q4_K) for e in need}
+uh = {e: q.register_weight(up[e], eff, d // 256, q.Q4_K) for e in need}
+dh = {e: q.register_weight(down[e], d, eff // 256, q.Q6_K) for e in need}
+flat = lambda hs: [hs[int(e)] for t in range(T) for e in sel[t]]
+G, U, D = flat(gh), flat(uh), flat(dh)
+out = q.moe_ffn_batched(G, U, D, T, k, h, gates.reshape(-1), d, eff, FA, FW)
+assert out is not None and np.array_equal(out, want), "bytes differ from the golden block output"
+reps = int(sys.argv[3])
+ts = []
+for _ in range(reps):
+    t0 = time.perf_counter(); q.moe_ffn_batched(G, U, D, T, k, h, gates.reshape(-1), d, eff, FA, FW); ts.append(time.perf_counter() - t0)
+print(json.dumps({"ms_per_call": float(np.median(ts)) * 1e3, "calls": reps, "library": str(q._so_path())}))
+'''
+
+
+def reference_bridge_timing(lib_dir: Path, reps: int = 20):
+    """`qk_moe_ffn_batched` on the config-1 block (16 tokens, 128 experts, top-8) called through the REFERENCE's own bridge
+    module, with `lib_dir/libnmc_qk_cuda.so` as the library it loads: once for the reference's CUDA producer built for
+    sm_100a (baseline/_ref/bin), once for this repository's library.  A child process each, because the bridge binds one
+    library per process.  Returns a dict, or {"unavailable": why}."""
+    ref = ROOT / "baseline" / "_ref" / "north-mini-code"
+    if not (ref / "src" / "nmc" / "qk_cuda.py").exists() or not (lib_dir / "libnmc_qk_cuda.so").exists():
+        return {"unavailable": "reference bridge or library not installed under baseline/_ref"}
+    env = dict(os.environ)
+    env["BONSAI_BIN_DIR"] = str(lib_dir)
+    env["PYTHONPATH"] = str(ref / "src")
+    env.pop("BONSAI_NOTARY_HOME", None)
+    try:
+        run = subprocess.run([sys.executable, "-c", _BRIDGE_PROBE, str(ROOT), str(ROOT / "tests" / "golden" / "moe.npz"), str(reps)],
+                             env=env, capture_output=True, text=True, timeout=600)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "timed out"}
+    if run.returncode != 0:
+        return {"unavailable": (run.stderr.strip().splitlines() or ["failed"])[-1][:200]}
+    return json.loads(run.stdout.strip().splitlines()[-1])
+
+
+def e2e_abi(reps: int = 20):
+    """The reference-facing entries with HOST buffers on the config-1 block (seed 0, 16 tokens, 128 experts, top-8):
+    `qk_moe_ffn_batched` (what Engine._moe calls) and `iie_moe_block_host` (routing included), wall clock around the
+    call, uploads and downloads inside it; results compared with the golden bytes first."""
+    from integer_inference_engine_b200 import device, qk_cuda
+    from oracle import qk_oracle as o
+    d, eff, E, k, T = D_MODEL, E_FFN, N_EXPERTS, TOP_K, 16
+    g = np.load(ROOT / "tests" / "golden" / "moe.npz")
+    router, gate, up, down, h = o.synth_moe(0, d, eff, E, T)
+    sel = g["config1_ids"]
+    logits = o.qk_linear(router, h, E, d // 256, FW, o.Q4_K)
+    gates = np.stack([o.sigmoid_fixed(logits[t][sel[t]], FA) for t in range(T)])
+    rh = qk_cuda.register_weight(router, E, d // 256, o.Q4_K)
+    gh = [qk_cuda.register_weight(w, eff, d // 256, o.Q4_K) for w in gate]
+    uh = [qk_cuda.register_weight(w, eff, d // 256, o.Q4_K) for w in up]
+    dh = [qk_cuda.register_weight(w, d, eff // 256, o.Q6_K) for w in down]
+    layer = device.MoELayer(rh, gh, uh, dh, k, d, eff)
+    flat = lambda hs: [hs[int(e)] for t in range(T) for e in sel[t]]
+    G, U, Dn, gflat = flat(gh), flat(uh), flat(dh), gates.reshape(-1)
+    out = {}
+    a = qk_cuda.moe_ffn_batched(G, U, Dn, T, k, h, gflat, d, eff, FA, FW)
+    b = qk_cuda.moe_block(layer.handle, h, k, FA, FW)
+    assert a is not None and np.array_equal(a, g["config1_out"]), "qk_moe_ffn_batched differs from the golden block output"
+    assert b is not None and np.array_equal(b[0], g["config1_out"]) and np.array_equal(b[1], sel), "iie_moe_block_host differs"
+    for name, fn in (("qk_moe_ffn_batched", lambda: qk_cuda.moe_ffn_batched(G, U, Dn, T, k, h, gflat, d, eff, FA, FW)),
+                     ("iie_moe_block_host", lambda: qk_cuda.moe_block(layer.handle, h, k, FA, FW))):
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter(); fn(); ts.append(time.perf_counter() - t0)
+        ms = float(np.median(ts)) * 1e3
+        routed = name == "iie_moe_block_host"
+        out[name] = {"ms_per_call": ms, "tok_per_s": T / (ms * 1e-3), "tokens": T,
+                     "h2d_bytes_per_call": h.nbytes + (0 if routed else gflat.nbytes + 3 * len(G) * 8),
+                     "d2h_bytes_per_call": h.nbytes + (T * k * 12 if routed else 0)}
+    layer.close()
+    return out
 
 
 # ---------------------------------------------------------------------------------------------- our arm ---
@@ -276,9 +400,10 @@ def check_moe_block(stack, li, hn, ids, gates, out):
     assert np.array_equal(out, ref.astype(np.int64)), f"block {li}: block output"
 
 
-def verify_token(model, token: int, n_check: int):
-    """Eager walk of one decode step; every stage of the first `n_check` blocks, the head and the pick are compared
-    with the CPU oracle fed with the SAME stage inputs (exported weights, host copies of the caches)."""
+def verify_token(model, token: int, n_check: int, check_blocks=None):
+    """Eager walk of one decode step at the model's current position; every stage of the first `n_check` blocks (or of the
+    blocks listed in `check_blocks`), the head and the pick are compared with the CPU oracle fed with the SAME stage inputs
+    (exported weights, host copies of the caches).  Leaves the appended cache rows in place and returns the pick."""
     import torch
 
     from integer_inference_engine_b200 import device
@@ -287,9 +412,10 @@ def verify_token(model, token: int, n_check: int):
     d, H, Hkv, hd, nb = model.d, model.H, model.Hkv, model.hd, model.d // 256
     pos = int(model.pos.item())
     cos, sin = model.cos[pos:pos + 1].cpu().numpy(), model.sin[pos:pos + 1].cpu().numpy()
-    embd_raw = device.export_weight(model.embd, model.vocab, nb, o.Q6_K) if n_check > 0 else None
+    do_head = n_check > 0 or bool(check_blocks)
+    embd_raw = device.export_weight(model.embd, model.vocab, nb, o.Q6_K) if do_head else None
     x = device.embed(model.embd, token, d, FA)
-    if n_check > 0:
+    if do_head:
         row = embd_raw[token * nb * 210:(token + 1) * nb * 210]
         assert np.array_equal(x.cpu().numpy()[0], o.dequant(row, 1, nb, o.Q6_K, FA)[0]), "embedding row"
     checked = 0
@@ -312,7 +438,7 @@ def verify_token(model, token: int, n_check: int):
         torch.cuda.synchronize()
         assert device.read_flags() == 0, f"block {li}: envelope flag raised"
         assert torch.equal(xb, x + ao + out), f"block {li}: block entries differ from the stage-by-stage composition"
-        if li < n_check:
+        if li < n_check or (check_blocks is not None and li in check_blocks):
             xn, hn = x.cpu().numpy(), h.cpu().numpy()
             assert np.array_equal(hn, o.rmsnorm_fixed(xn, FA, 1, model.moe.handles[li]["gain"].cpu().numpy())), f"block {li}: RMSNorm"
             w = device.export_weight(a["wqkv"], qr + 2 * kr, nb, o.Q4_K)
@@ -334,7 +460,7 @@ def verify_token(model, token: int, n_check: int):
     hn = device.rmsnorm(x, model.out_gain_h, FA, 1)
     logits = device.apply(model.embd, hn, model.vocab, FW)
     tok = int(device.argmax(logits.view(-1)).item())
-    if n_check > 0:
+    if do_head:
         assert np.array_equal(hn.cpu().numpy(), o.rmsnorm_fixed(x.cpu().numpy(), FA, 1, model.out_gain.cpu().numpy())), "output norm"
         want = onat.qk_linear(embd_raw, hn.cpu().numpy(), model.vocab, nb, FW, o.Q6_K)[0]
         assert np.array_equal(logits.cpu().numpy()[0], want), "head logits"
@@ -358,7 +484,8 @@ def run_ours(args):
         raise SystemExit("CUDA library or GPU missing: there is no fallback path")
 
     n_e2e = 0 if args.no_e2e else max(2, min(args.steps, 16))
-    total_steps = args.warmup + args.steps + n_e2e + 24
+    n_pad = 0 if args.no_e2e else 2 * SUSTAIN_STEPS               # identical replays around the timed region (clock sampling)
+    total_steps = args.warmup + args.steps + n_e2e + n_pad + 24
     model = SyntheticDecoder(n_layers=args.layers, d_model=D_MODEL, n_heads=N_HEADS, n_kv=N_KV, head_dim=HEAD_DIM, e_ffn=E_FFN,
                              n_experts=N_EXPERTS, top_k=TOP_K, vocab=VOCAB, context=args.context, max_new=total_steps + 8,
                              window=WINDOW, seed=1 + rank, fa=FA, fw=FW)
@@ -367,22 +494,35 @@ def run_ours(args):
     pos0 = model.context
     pos_bound = pos0 + total_steps
 
-    # ---- parity before timing: every stage of one token, then graph replay == eager chain --------------------------
-    checked, _ = verify_token(model, first_token, args.verify_layers if rank == 0 else 0)
-    model.token.fill_(first_token)
+    # ---- parity before timing: four consecutive greedy tokens walked stage by stage against the CPU oracle (every block
+    # of the first token, a spread of blocks of the others, head and pick of each), then the step entries and the replayed
+    # graph must reproduce that oracle-checked chain --------------------------------------------------------------------
+    n_chain = 4
+    oracle_ids, checked, tok = [], 0, first_token
+    for i in range(n_chain):
+        model.set_position(pos0 + i)
+        if rank == 0:
+            blocks = None if i == 0 else set(range(i, args.layers, max(1, args.layers // 4)))
+            n_chk, tok = verify_token(model, tok, args.verify_layers if i == 0 else 0, blocks if args.verify_layers else None)
+        else:
+            n_chk, tok = verify_token(model, tok, 0)
+        checked += n_chk
+        oracle_ids.append(tok)
+    model.token.fill_(first_token); model.set_position(pos0)
     eager_ids = []
-    for i in range(3):
+    for i in range(n_chain):
         model.step(pos0 + i)
         eager_ids.append(int(model.token.item()))
+    assert eager_ids == oracle_ids, f"step entries {eager_ids} differ from the oracle-checked chain {oracle_ids}"
     model.token.fill_(first_token); model.set_position(pos0)
     l0 = device.launch_count()
     model.capture(pos_bound)
     launches_per_step = (device.launch_count() - l0) // 2         # capture() runs the step twice
     replay_ids = []
-    for i in range(3):
+    for i in range(n_chain):
         model.replay()
         replay_ids.append(int(model.token.item()))
-    assert replay_ids == eager_ids, f"graph replay {replay_ids} differs from the eager chain {eager_ids}"
+    assert replay_ids == oracle_ids, f"graph replay {replay_ids} differs from the oracle-checked chain {oracle_ids}"
 
     # ---- device-resident timing: the greedy chain continues, one graph replay per token ----------------------------
     for i in range(args.warmup):
@@ -393,10 +533,15 @@ def run_ours(args):
     torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
+        # the timed K steps sit inside a longer run of identical replays, so that the 100 ms clock sampler sees the load
+        for i in range(n_pad // 2):
+            model.replay()
         ev0.record()
         for i in range(args.steps):
             model.replay()
         ev1.record()
+        for i in range(n_pad // 2):
+            model.replay()
         torch.cuda.synchronize()
     ms = ev0.elapsed_time(ev1)
     if world > 1:
@@ -484,13 +629,26 @@ def run_ours(args):
         if world > 1:
             dist.destroy_process_group()
         return
+    abi, i8 = None, None
+    if not args.no_e2e:
+        i8 = int8_peak()
+        # the reference's own CUDA producer first, in its own process, through the reference's own bridge; then this library
+        # through the same bridge call, and through this repository's bridge
+        abi = {"workload": "config1 block: 16 tokens, 128 experts, top-8, host NumPy buffers, copies inside the call",
+               "reference_bridge_with_reference_cuda_producer": reference_bridge_timing(ROOT / "baseline" / "_ref" / "bin"),
+               "reference_bridge_with_this_library": reference_bridge_timing(ROOT / "integer_inference_engine_b200" / "lib")}
+        abi.update(e2e_abi())
     cpu = None
     if args.cpu_sample_layers > 0:
         n_cpu = min(args.cpu_sample_layers, args.layers)
         use_all_host_threads()
-        per_layer, head_s = cpu_token_time("port", n_cpu, 3, args.context)
-        cpu = {"value": 1.0 / (per_layer * args.layers + head_s), "unit": "tok/s", "cores": host_cores(), "kind": "port",
-               "sample": f"{n_cpu} blocks (attention over {args.context} keys + MoE) and the head, 1 token, median of 3, "
+        step = CpuDecodeStep("port", n_cpu, args.context)
+        step.step(n_cpu)                                       # warm-up
+        t0 = time.perf_counter(); step.step(n_cpu); t_blocks_head = time.perf_counter() - t0
+        t0 = time.perf_counter(); step.step(0); t_head = time.perf_counter() - t0
+        per_block = (t_blocks_head - t_head) / n_cpu
+        cpu = {"value": 1.0 / (per_block * args.layers + t_head), "unit": "tok/s", "cores": host_cores(), "kind": "port",
+               "sample": f"{n_cpu} blocks (attention over {args.context} keys + MoE) and the head, 1 token, "
                          f"scaled to {args.layers} blocks"}
     ms_step = ms / args.steps
     w_bytes, kv_bytes = model.weight_bytes_per_token(), model.kv_bytes_per_token(pos_timed)
@@ -505,12 +663,12 @@ def run_ours(args):
                    "step_hbm_frac_of_%s_peak" % peak_kind: (w_bytes + kv_bytes) / (ms_step * 1e-3) / 1e9 / peak,
                    "moe_blocks_only": {"ms_per_token": moe_only_ms, "tok_per_s": 1e3 / moe_only_ms,
                                        "weight_bytes": stack.weight_bytes_per_token()},
-                   "oracle_checked_blocks": checked, "kv_cache": "seeded int32 values stand in for the prefill"},
-        "clocks": clk.summary(),
-        "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps),
+                   "oracle_checked_blocks": checked, "oracle_checked_tokens": n_chain, "one_launch_decode": model.kernel is not None, "kv_cache": "seeded int32 values stand in for the prefill"},
+        "clocks": dict(clk.summary(), window="the timed steps plus %d identical replays before and after them" % (n_pad // 2)),
+        "e2e": e2e, "e2e_abi": abi, "int8_peak": i8, "gpu_launches": int(launches_per_step * args.steps),
         "roofline": {"bound": "hbm", "kernel": "stream_kernel<Q4_K, GATEUP>", "achieved": achieved, "peak": peak,
-                     "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": GATEUP_DRAM_BYTES_NCU,
-                     "traffic_source": "ncu dram__bytes_read+write of one launch, profiles/stream_kernel_gateup_decode.md",
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": ncu_figure("stream_kernel_gateup.dram_bytes_per_launch"),
+                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch in an ncu capture of this kernel",
                      "bytes_per_launch": gateup_bytes, "ms_per_launch": gateup_ms,
                      "other_kernels_us": {"route": route_ms * 1e3, "down": down_ms * 1e3,
                                           "down_frac": down_bytes / (down_ms * 1e-3) / 1e9 / peak}},
