@@ -188,6 +188,17 @@ int iie_attn_prefill_dev(const int64_t *q_dev, const int64_t *k_dev, const int64
                          int32_t *vcache_dev, long long start, long long tokens, long long window, const int64_t *cos_dev,
                          const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim, long long cache_rows, int fa,
                          long long inv_sqrt, int64_t *out_dev, void *stream);
+/* Batched decode attention: the new tokens of n_seqs independent sequences in one call, every sequence with its own int32
+ * caches (sequence i at kcache_dev / vcache_dev + i * seq_stride elements, each [n_kv][cache_rows][head_dim]) and all at the
+ * same position pos (sequences decoded in lockstep).  q_dev [n_seqs][n_heads*head_dim], k_dev / v_dev [n_seqs][n_kv*head_dim]
+ * before rotation; row pos of every sequence's caches is written; out_dev [n_seqs][n_heads*head_dim].  Arithmetic of the
+ * single-token entry per sequence (north-mini-code/src/nmc/cohere2.py:324-354, m = 1); the reference's batched analogue for
+ * its 1-bit decoder is attention_decode_batched_kernel (bonsai/tools/bonsai_q1_gpu.cu:1409).  0 ok, 1 bad argument or CUDA
+ * failure; a K/V value outside int32 raises bit 2 of the flag word. */
+int iie_attn_decode_batch_dev(const int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
+                              int32_t *vcache_dev, long long pos, long long n_seqs, long long seq_stride, long long window,
+                              const int64_t *cos_dev, const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim,
+                              long long cache_rows, int fa, long long inv_sqrt, int64_t *out_dev, void *stream);
 /* The attention half of a decoder block for ONE token, accumulated into the residual row:
  *   x_dev [d_model] += (attention(q, cache) Wo^T), with [q | k | v] = h Wqkv^T,
  * where h is the normalised row whose digit planes the LAST single-token iie_moe_block_dev / iie_moe_forward_dev

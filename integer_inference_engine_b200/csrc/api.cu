@@ -69,7 +69,7 @@ inline bool stage_on(int st) { return g_stage_mask == 0 || (g_stage_mask & st); 
 
 // Persistent device scratch by role, grown on demand (never shrunk until released).
 enum Role { R_X, R_XL, R_OUT, R_RAW, R_GU, R_GUL, R_TMP0, R_TMP1, R_TMP2, R_TABS, R_META, R_LOGITS, R_IDS, R_GATES,
-            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_ASCORES, R_AEXP, R_ASTAT, R_APART, R_PSCORES, R_PEXP, R_PSTAT, R_COUNT };
+            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_ASCORES, R_AEXP, R_ASTAT, R_APART, R_PSCORES, R_PEXP, R_PSTAT, R_BSCORES, R_BEXP, R_BSTAT, R_COUNT };
 struct Buf { void *p = nullptr; size_t cap = 0; };
 Buf g_buf[R_COUNT];
 long long g_ws_allocs = 0;
@@ -1030,6 +1030,32 @@ extern "C" int iie_attn_prefill_dev(const int64_t *q_dev, const int64_t *k_dev, 
         a.out = out_dev + t0 * n_heads * head_dim; a.flags = g_flags;
         if (launch_attn_prefill(a, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     }
+    return 0;
+}
+
+extern "C" int iie_attn_decode_batch_dev(const int64_t *q_dev, const int64_t *k_dev, const int64_t *v_dev, int32_t *kcache_dev,
+                                         int32_t *vcache_dev, long long pos, long long n_seqs, long long seq_stride, long long window,
+                                         const int64_t *cos_dev, const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim,
+                                         long long cache_rows, int fa, long long inv_sqrt, int64_t *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !q_dev || !k_dev || !v_dev || !kcache_dev || !vcache_dev || !out_dev || n_heads <= 0 || n_kv <= 0 || head_dim <= 0 ||
+        cache_rows <= 0 || fa < 1 || fa > 29 || pos < 0 || pos >= cache_rows || n_seqs <= 0 || n_seqs > 65535 ||
+        seq_stride < (long long)n_kv * cache_rows * head_dim) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long Ls = (pos + 1 + 63) / 64 * 64;
+    // scratch roles of their own (a captured single-token step keeps the addresses of the single-token buffers)
+    int64_t *scores = (int64_t *)ensure(R_BSCORES, (size_t)n_seqs * n_heads * Ls * 8);
+    int32_t *e = (int32_t *)ensure(R_BEXP, (size_t)n_seqs * n_heads * Ls * 4);
+    uint8_t *st = (uint8_t *)ensure(R_BSTAT, (size_t)n_seqs * n_heads * 16);
+    if (!scores || !e || !st) return 1;
+    AttnArgs a = {};
+    a.batch = (int)n_seqs; a.seq_stride = seq_stride;
+    a.q = q_dev; a.k = k_dev; a.v = v_dev; a.kcache = kcache_dev; a.vcache = vcache_dev; a.pos = pos; a.window = window;
+    a.Lmax = cache_rows; a.Ls = Ls; a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim;
+    attn_consts(a, fa, inv_sqrt);
+    a.scores = scores; a.e = e; a.hmax = (long long *)st; a.Z = (unsigned long long *)(st + (size_t)n_seqs * n_heads * 8);
+    a.out = out_dev; a.flags = g_flags;
+    if (launch_attn_prefill(a, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     return 0;
 }
 

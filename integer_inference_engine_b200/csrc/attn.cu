@@ -48,11 +48,14 @@ __device__ __forceinline__ void at_refuse(const AttnArgs &a) {
     if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) atomicOr(a.flags, 16);
 }
 
-// prefill: blockIdx.z is the token; shift the position and every per-token pointer to it
+// several new tokens in one launch: blockIdx.z is the token; shift every per-token pointer to it.  Prefill (seq_stride == 0):
+// the tokens are consecutive positions of ONE sequence and share its cache.  Batched decode (seq_stride > 0): token i is
+// the new token of sequence i, all at position pos, each sequence with its own cache seq_stride elements further on.
 __device__ __forceinline__ void at_batch(AttnArgs &a) {
     if (a.batch <= 0) return;
     const long long i = blockIdx.z, Ls = a.Ls ? a.Ls : a.Lmax;
-    a.pos += i;
+    if (a.seq_stride > 0) { a.kcache += i * a.seq_stride; a.vcache += i * a.seq_stride; }
+    else a.pos += i;
     a.lo = (a.window > 0 && a.pos - a.window + 1 > 0) ? a.pos - a.window + 1 : 0;
     a.q += i * a.H * a.hd;
     a.scores += i * a.H * Ls; a.e += i * a.H * Ls; a.hmax += i * a.H; a.Z += i * a.H;
@@ -296,12 +299,13 @@ __global__ void __launch_bounds__(256) attn_pv_kernel(const AttnArgs a_in) {
     if (tid == 0) { *a.ticket = 0u; if (a.out_nl) *a.out_nl = s_nl; }
 }
 
-// prefill, before the passes: rotate the new keys and append keys and values of all `batch` tokens; grid (batch, Hkv)
+// several tokens, before the passes: rotate the new keys and append keys and values of all `batch` tokens (to one cache at
+// consecutive positions, or each to its own sequence's cache at position pos); grid (batch, Hkv)
 __global__ void __launch_bounds__(128) attn_append_kernel(const AttnArgs a) {
-    const long long i = blockIdx.x, pos = a.pos + i;
+    const long long i = blockIdx.x, pos = a.seq_stride > 0 ? a.pos : a.pos + i, seq = a.seq_stride > 0 ? i * a.seq_stride : 0;
     const int kv = blockIdx.y, tid = threadIdx.x, half = a.hd / 2;
     const int64_t *ks = a.k + (i * a.Hkv + kv) * a.hd, *vs = a.v + (i * a.Hkv + kv) * a.hd;
-    int32_t *kd = a.kcache + ((long long)kv * a.Lmax + pos) * a.hd, *vd = a.vcache + ((long long)kv * a.Lmax + pos) * a.hd;
+    int32_t *kd = a.kcache + seq + ((long long)kv * a.Lmax + pos) * a.hd, *vd = a.vcache + seq + ((long long)kv * a.Lmax + pos) * a.hd;
     bool bad = false;
     for (int j = tid; j < half; j += blockDim.x) {
         const int i0 = a.rope == 2 ? j : 2 * j, i1 = a.rope == 2 ? j + half : 2 * j + 1;
@@ -690,7 +694,8 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
 }
 
 cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s) {
-    if (!attn_shape_ok(a.H, a.Hkv, a.hd) || a.batch <= 0 || a.batch > 65535 || a.pos < 0 || a.pos + a.batch > a.Lmax || a.fa < 1 ||
+    const long long last_pos = a.seq_stride > 0 ? a.pos : a.pos + a.batch - 1;
+    if (!attn_shape_ok(a.H, a.Hkv, a.hd) || a.batch <= 0 || a.batch > 65535 || a.pos < 0 || last_pos >= a.Lmax || a.seq_stride < 0 || a.fa < 1 ||
         a.fa > 29 || (a.rope && (!a.cos || !a.sin)) || a.pos_dev || !a.out || !a.scores || !a.e || !a.hmax || !a.Z)
         return cudaErrorInvalidValue;
     static bool configured = false;
@@ -701,7 +706,7 @@ cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s) {
         configured = true;
     }
     const int rep = a.H / a.Hkv;
-    const long long last = a.pos + a.batch - 1;                     // the longest key span is the last token's
+    const long long last = last_pos;                                // the longest key span is the last token's
     long long n_keys = last + 1;
     if (a.window > 0 && n_keys > a.window) n_keys = a.window;
     const unsigned chunks = (unsigned)((n_keys + AT_CH - 1) / AT_CH);

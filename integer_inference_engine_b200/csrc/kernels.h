@@ -211,6 +211,8 @@ struct AttnArgs {
     int batch;                     // > 0: that many consecutive new tokens (prefill); q, k, v, out then hold one row per token,
                                    // pos is the position of the first, the scratch holds one set of statistics per token
     long long Ls;                  // row stride of scores / e (0: Lmax)
+    long long seq_stride;          // with batch > 0: elements between the caches of consecutive sequences (batched decode: token i is
+                                   // sequence i's new token, all at position pos); 0: the tokens are consecutive positions of one sequence
 };
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s);
 // `batch` new tokens at positions pos .. pos + batch - 1 against the cache rows before them and each other (causal):

@@ -133,6 +133,34 @@ def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kcache:
     return out
 
 
+def attention_decode_batch(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: int,
+                           n_heads: int, n_kv: int, head_dim: int, fa: int = 16, window: int = 0, cos: torch.Tensor | None = None,
+                           sin: torch.Tensor | None = None, rope: int = 0, inv_sqrt: int | None = None,
+                           out: torch.Tensor | None = None) -> torch.Tensor:
+    """The new tokens of ``B`` independent sequences, all at position ``pos``: ``q`` [B, n_heads*head_dim], ``k`` / ``v``
+    [B, n_kv*head_dim] before rotation, caches [B, n_kv, rows, head_dim] int32 (row ``pos`` of each is written).
+    Returns [B, n_heads*head_dim] int64."""
+    lib = qk_cuda._lib()
+    B = q.shape[0]
+    assert q.is_cuda and q.dtype == torch.int64 and q.is_contiguous() and q.shape == (B, n_heads * head_dim)
+    assert k.dtype == torch.int64 and v.dtype == torch.int64 and k.is_contiguous() and v.is_contiguous()
+    assert k.shape == (B, n_kv * head_dim) == v.shape
+    assert kcache.dtype == torch.int32 and vcache.dtype == torch.int32 and kcache.is_contiguous() and vcache.is_contiguous()
+    assert kcache.shape == vcache.shape and kcache.shape[0] == B and kcache.shape[1] == n_kv and kcache.shape[3] == head_dim
+    if inv_sqrt is None:
+        inv_sqrt = int(round((1.0 / head_dim ** 0.5) * (1 << fa)))
+    if out is None:
+        out = torch.empty((B, n_heads * head_dim), dtype=torch.int64, device=q.device)
+    with _CUDA_LOCK:
+        rc = lib.iie_attn_decode_batch_dev(q.data_ptr(), k.data_ptr(), v.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), int(pos), B,
+                                           int(kcache.stride(0)), int(window or 0), cos.data_ptr() if rope else None,
+                                           sin.data_ptr() if rope else None, int(rope), n_heads, n_kv, head_dim,
+                                           int(kcache.shape[2]), int(fa), int(inv_sqrt), out.data_ptr(), _stream_ptr())
+    if rc != 0:
+        raise CudaContextError(f"batched decode attention failed with status {rc}")
+    return out
+
+
 def attention_block(wqkv: int, wo: int, x: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: int, n_heads: int,
                     n_kv: int, head_dim: int, fa: int = 16, fw: int = 24, window: int = 0, cos: torch.Tensor | None = None,
                     sin: torch.Tensor | None = None, rope: int = 0, inv_sqrt: int | None = None,

@@ -43,7 +43,7 @@ def test_resident_attention_decode_matches_host_cache(d_model, heads, n_kv, head
     _, wrong_oh = make_weight(d_model, o.Q6_K, 25000, q_nb + 1)
     _, wrong_kh = make_weight(n_kv * head_dim, o.Q6_K, 26000, nb + 1)
     probe = np.zeros((1, d_model), dtype=np.int64)
-    with pytest.raises(ValueError, match="hidden shape"):
+    with pytest.raises(ValueError, match="hidden row must be"):
         bank.apply(0, qh, kh, vh, oh, np.zeros((1, d_model + 1), dtype=np.int64), FW, None, False)
     for handles in ((wrong_qh, kh, vh, oh), (qh, wrong_kh, vh, oh), (qh, kh, wrong_kh, oh), (qh, kh, vh, wrong_oh)):
         with pytest.raises(qk_cuda.CudaContextError, match="native status"):
@@ -70,7 +70,7 @@ def test_resident_attention_decode_matches_host_cache(d_model, heads, n_kv, head
     # the bank is full after max_length rows
     bank.apply(0, qh, kh, vh, oh, probe, FW, None, False)
     assert bank.length(0) == max_length
-    with pytest.raises(ValueError, match="context bounds"):
+    with pytest.raises(ValueError, match="already holds its"):
         bank.apply(0, qh, kh, vh, oh, probe, FW, None, False)
     bank.reset()
     assert bank.length(0) == 0
@@ -81,7 +81,7 @@ def test_resident_attention_decode_matches_host_cache(d_model, heads, n_kv, head
     bad = qk_cuda.ResidentAttentionCache(1, max_length, d_model, heads, n_kv, head_dim, FA, cos, sin)
     bad.import_layer(0, np.zeros((n_kv, 1, head_dim), dtype=np.int64),
                      np.full((n_kv, 1, head_dim), np.iinfo(np.int64).max, dtype=np.int64))
-    with pytest.raises(qk_cuda.CudaContextError, match="overflow guard"):
+    with pytest.raises(qk_cuda.CudaContextError, match="left the exact envelope"):
         bad.apply(0, qh, kh, vh, oh, probe, FW, None, False)
     with pytest.raises(qk_cuda.CudaContextError, match="native status"):
         bad.apply(0, qh, kh, vh, oh, probe, FW, None, False)
