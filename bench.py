@@ -625,6 +625,17 @@ def run_ours(args):
         e2e = {"value": world / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4, "steps": n_e2e}
     assert device.read_flags() == 0
 
+    # with more than one rank the path shards (experts over ranks, sequences over ranks): measure that step too
+    ep_res = None
+    w_bytes, kv_bytes, one_launch = model.weight_bytes_per_token(), model.kv_bytes_per_token(pos_timed), model.kernel is not None
+    moe_weight_bytes = stack.weight_bytes_per_token()
+    if world > 1 and not args.no_e2e:
+        del model, stack
+        qk_cuda.free_all()
+        torch.cuda.empty_cache()
+        ep_args = argparse.Namespace(**vars(args))
+        ep_args.tokens = 64
+        ep_res = ep_decode_measure(ep_args, rank, world, local, 10, 3)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -651,7 +662,6 @@ def run_ours(args):
                "sample": f"{n_cpu} blocks (attention over {args.context} keys + MoE) and the head, 1 token, "
                          f"scaled to {args.layers} blocks"}
     ms_step = ms / args.steps
-    w_bytes, kv_bytes = model.weight_bytes_per_token(), model.kv_bytes_per_token(pos_timed)
     print(json.dumps({
         "metric": "decode_tok_per_s", "value": world * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -662,8 +672,8 @@ def run_ours(args):
                    "weight_bytes_per_token": w_bytes, "kv_bytes_per_token": kv_bytes,
                    "step_hbm_frac_of_%s_peak" % peak_kind: (w_bytes + kv_bytes) / (ms_step * 1e-3) / 1e9 / peak,
                    "moe_blocks_only": {"ms_per_token": moe_only_ms, "tok_per_s": 1e3 / moe_only_ms,
-                                       "weight_bytes": stack.weight_bytes_per_token()},
-                   "oracle_checked_blocks": checked, "oracle_checked_tokens": n_chain, "one_launch_decode": model.kernel is not None, "kv_cache": "seeded int32 values stand in for the prefill"},
+                                       "weight_bytes": moe_weight_bytes},
+                   "ep_decode": ep_res, "oracle_checked_blocks": checked, "oracle_checked_tokens": n_chain, "one_launch_decode": one_launch, "kv_cache": "seeded int32 values stand in for the prefill"},
         "clocks": dict(clk.summary(), window="the timed steps plus %d identical replays before and after them" % (n_pad // 2)),
         "e2e": e2e, "e2e_abi": abi, "int8_peak": i8, "gpu_launches": int(launches_per_step * args.steps),
         "roofline": {"bound": "hbm", "kernel": "stream_kernel<Q4_K, GATEUP>", "achieved": achieved, "peak": peak,
@@ -804,67 +814,98 @@ def run_prefill(args):
         dist.destroy_process_group()
 
 
-def run_ep_decode(args):
-    """Expert-parallel batched decode: `tokens` (64) sequences split over the ranks, experts sharded 128/P per
-    rank, one all-to-all dispatch and one combine per block.  One rank runs the same code with both elided."""
+def ep_decode_measure(args, rank, world, local, steps, warmup):
+    """Config 4: `tokens` (64) concurrent sequences at context `args.context`, whole decode step (every block with attention
+    over each sequence's own cache and the expert-parallel MoE, head, greedy picks), sequences data-parallel and experts
+    sharded over the ranks; the step is one replayed CUDA graph.  Block 0 is checked against the CPU oracle for one sequence
+    per rank before timing.  Returns the figures of the line (max over ranks)."""
     import torch
     import torch.distributed as dist
 
-    from integer_inference_engine_b200 import device, ep
-    from integer_inference_engine_b200.synth import SyntheticMoEStack
+    from integer_inference_engine_b200 import device
+    from integer_inference_engine_b200.ep_model import ExpertParallelDecoder
+    from oracle import native as onat
     from oracle import qk_oracle as o
-    rank, world, local = _dist_setup()
     S = args.tokens or 64
-    assert S % world == 0 and N_EXPERTS % world == 0
-    per = S // world
-    epr = N_EXPERTS // world
-    stack = SyntheticMoEStack(args.layers, D_MODEL, E_FFN, N_EXPERTS, TOP_K, seed=1, fa=FA,
-                              expert_range=(rank * epr, (rank + 1) * epr))
-    blocks = [ep.from_device_layer(stack.handles[li]["router"], stack.layers[li], N_EXPERTS, FA, FW) for li in range(args.layers)]
-    xs = o.to_fixed(np.random.default_rng(11).standard_normal((S, D_MODEL)), FA)          # same on every rank
-    x0 = torch.from_numpy(xs[rank * per:(rank + 1) * per].copy()).cuda()
-
-    def forward(x):
-        for li, blk in enumerate(blocks):
-            h = device.rmsnorm(x, stack.gains[li], FA, 1)
-            out, _, _ = blk.forward(h)
-            x += out
-        return x
-    # parity of block 0: this rank's rows against the checker run over ALL experts (needs the other shards'
-    # weights, so the check uses a full-model stack of one block on rank 0 only)
-    h0 = device.rmsnorm(x0, stack.gains[0], FA, 1)
-    out0, ids0, _ = blocks[0].forward(h0)
+    m = ExpertParallelDecoder(S, n_layers=args.layers, d_model=D_MODEL, n_heads=N_HEADS, n_kv=N_KV, head_dim=HEAD_DIM, e_ffn=E_FFN,
+                              n_experts=N_EXPERTS, top_k=TOP_K, vocab=VOCAB, context=args.context, max_new=4, window=WINDOW, seed=1,
+                              fa=FA, fw=FW)
+    # ---- parity of block 0 for this rank's first sequence: attention against the NumPy checker, MoE rows against the C oracle
+    x0 = torch.from_numpy(o.to_fixed(np.random.default_rng(50 + rank).standard_normal((m.B, D_MODEL)), FA)).cuda()
+    pos, nb, a0_, hs = m.position, D_MODEL // 256, m.attn[0], m.stack.handles[0]
+    qd, kd = N_HEADS * HEAD_DIM, N_KV * HEAD_DIM
+    h = device.rmsnorm(x0, m.stack.gains[0], FA, 1)
+    qkv = device.apply(a0_["wqkv"], h, qd + 2 * kd, FW)
+    att = device.attention_decode_batch(qkv[:, :qd].contiguous(), qkv[:, qd:qd + kd].contiguous(), qkv[:, qd + kd:].contiguous(),
+                                        a0_["k"], a0_["v"], pos, N_HEADS, N_KV, HEAD_DIM, FA, 0, m.cos, m.sin, 0)
+    moe = (m.blocks[0].forward(h) if m.blocks[0] is not None else m.stack.layers[0].forward(h, FA, FW))[0]
     torch.cuda.synchronize()
     assert device.read_flags() == 0
-    if rank == 0:
+    hn = h[:1].cpu().numpy()
+    w = device.export_weight(a0_["wqkv"], qd + 2 * kd, nb, o.Q4_K)
+    assert np.array_equal(qkv[:1].cpu().numpy(), onat.qk_linear(w, hn, qd + 2 * kd, nb, FW, o.Q4_K)), "EP decode: fused QKV"
+    ck = a0_["k"][0, :, :pos + 1].cpu().numpy().astype(np.int64); cv = a0_["v"][0, :, :pos + 1].cpu().numpy().astype(np.int64)
+    want = o.attention_cached(qkv[:1, :qd].cpu().numpy().reshape(1, N_HEADS, HEAD_DIM), ck, cv, pos, N_HEADS, N_KV, FA, None)
+    assert np.array_equal(att[:1].cpu().numpy(), want), "EP decode: batched attention of sequence 0"
+    if rank == 0:                                              # the other shards' weights exist on rank 0 only as a 1-block full stack
+        from integer_inference_engine_b200.synth import SyntheticMoEStack
         full = SyntheticMoEStack(1, D_MODEL, E_FFN, N_EXPERTS, TOP_K, seed=1, fa=FA)
-        rows = [0, per - 1]
-        sel, ref = _oracle_rows(full, 0, h0[rows].cpu().numpy())
-        assert np.array_equal(ids0[rows].cpu().numpy(), sel) and np.array_equal(out0[rows].cpu().numpy(), ref), \
-            "expert-parallel block 0 differs from the oracle"
+        _, ref = _oracle_rows(full, 0, hn)
+        assert np.array_equal(moe[:1].cpu().numpy(), ref), "EP decode: MoE rows of block 0 differ from the oracle"
         for lay in full.layers:
             lay.close()
-    x = x0.clone()
+    m.tokens.copy_(torch.arange(rank * m.B, (rank + 1) * m.B, dtype=torch.int32, device="cuda") * 13 + 5)
     l0 = device.launch_count()
-    forward(x)
-    launches = device.launch_count() - l0
-
-    def step(i):
-        x.copy_(x0)
-        forward(x)
-    ms, clocks = _timed(step, args.steps, args.warmup, world, local)
+    m.capture()
+    launches = (device.launch_count() - l0) // 2
+    ms, clocks = _timed(lambda i: m.replay(), steps, warmup, world, local)
     assert device.read_flags() == 0
+    ms_step = ms / steps
+    peak, kind = measured_peak_gbs()
+    # bytes one rank streams per step: its expert shard (every expert is touched at 64 x 8 routed pairs), the replicated
+    # attention matrices and router, its sequences' visible cache rows, the head
+    expert_b = (2 * E_FFN * nb * 144 + D_MODEL * (E_FFN // 256) * 210) * (N_EXPERTS // world)
+    attn_b = (2 * qd + 2 * kd) * nb * 144 + N_EXPERTS * nb * 144
+    kv_b = m.B * 2 * N_KV * (pos + 1) * HEAD_DIM * 4
+    bytes_rank = args.layers * (expert_b + attn_b + kv_b) + VOCAB * nb * 210
+    out = {"sequences": S, "ms_per_step": ms_step, "tok_per_s": S * 1e3 / ms_step, "parallelism": f"ep{world} x dp{world}",
+           "layers": args.layers, "context": args.context, "step": "whole decode step (attention over per-sequence caches, "
+           "expert-parallel MoE, head, picks) as one replayed CUDA graph at a fixed position",
+           "exchange": ("all-gather dispatch + reduce-scatter combine per block (NCCL)" if world > 1 else "none (one rank)"),
+           "a2a_bytes_per_rank_per_block": m.a2a_bytes_per_block, "gpu_launches_per_step": int(launches),
+           "bytes_per_rank_per_step": bytes_rank, "hbm_frac_of_%s_peak" % kind: bytes_rank / (ms_step * 1e-3) / 1e9 / peak,
+           "oracle_checked": "block 0: fused QKV, batched attention (sequence 0 of every rank), MoE rows (rank 0)", "clocks": clocks}
+    del m
+    return out
+
+
+def run_ep_decode(args):
+    rank, world, local = _dist_setup()
+    res = ep_decode_measure(args, rank, world, local, args.steps, args.warmup)
     if rank == 0:
-        ms_step = ms / args.steps
+        cpu = None
+        if args.cpu_sample_layers > 0:
+            use_all_host_threads()
+            step = CpuDecodeStep("port", 1, args.context)
+            step.step(1)
+            t0 = time.perf_counter(); step.step(1); t1 = time.perf_counter() - t0
+            t0 = time.perf_counter(); step.step(0); th = time.perf_counter() - t0
+            cpu = {"value": 1.0 / ((t1 - th) * args.layers + th), "unit": "tok/s", "cores": host_cores(), "kind": "port",
+                   "sample": f"1 block and the head for ONE sequence, scaled to {args.layers} blocks (sequences are independent on the CPU)"}
+        peak, kind = measured_peak_gbs()
         print(json.dumps({
-            "metric": "decode_tok_per_s", "value": S * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "metric": "decode_tok_per_s", "value": res["tok_per_s"], "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int64", "data": "synthetic",
-            "config": {"workload": f"config4_ep_decode: {S} sequences, {args.layers} MoE blocks, experts {epr}/rank, "
-                                   f"all-to-all dispatch + combine per block", "parallelism": f"ep{world}",
-                       "a2a_bytes_per_rank_per_block": blocks[0].bytes_sent_last,
-                       "l2": "inputs larger than L2 (expert weights streamed per block)", "oracle_checked_rows": 2},
-            "clocks": clocks, "gpu_launches": int(launches * args.steps)}))
+            "config": dict({"workload": f"config4_ep_decode: {res['sequences']} sequences x context {args.context}, {args.layers} blocks, "
+                                        f"experts {N_EXPERTS // world}/rank, sequences {res['sequences'] // world}/rank",
+                            "l2": "inputs larger than L2 (expert shard, caches and head streamed every step)"}, **res),
+            "clocks": res["clocks"], "gpu_launches": res["gpu_launches_per_step"] * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "all kernels of one step on one rank (aggregate)", "unit": "GB/s", "peak": peak,
+                         "peak_kind": kind, "achieved": res["bytes_per_rank_per_step"] / (res["ms_per_step"] * 1e-3) / 1e9,
+                         "frac": res["bytes_per_rank_per_step"] / (res["ms_per_step"] * 1e-3) / 1e9 / peak, "traffic": None},
+            "cpu_baseline": cpu}))
+    import torch.distributed as dist
     if world > 1:
         dist.destroy_process_group()
 
