@@ -129,7 +129,8 @@ class ExpertParallelDecoder:
         self._stream = torch.cuda.Stream()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(self._stream):
-            with torch.cuda.graph(graph, stream=self._stream):
+            # thread-local capture mode: the collective library's watchdog thread may query events while this thread captures
+            with torch.cuda.graph(graph, stream=self._stream, capture_error_mode="thread_local"):
                 self.step()
         torch.cuda.synchronize()
         self.tokens.copy_(keep)

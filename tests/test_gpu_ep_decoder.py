@@ -54,18 +54,37 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run_ranks(world, n_seqs, tmp_path, tag):
+def _run_ranks(world, n_seqs, tmp_path, tag, timeout=150):
+    """Start one process per rank; poll them all, and as soon as one fails or the time runs out kill the others, so that no
+    rank is left waiting inside a collective.  The ranks' output goes to files whose tails are shown on failure."""
+    import time
     port = _free_port()
+    logs = [open(tmp_path / f"{tag}{r}.log", "w") for r in range(world)]
     procs = [subprocess.Popen([sys.executable, str(HERE / "ep_decoder_worker.py"), str(r), str(world), str(port), str(n_seqs),
-                               str(tmp_path / f"{tag}{r}.npz")]) for r in range(world)]
+                               str(tmp_path / f"{tag}{r}.npz")], stdout=logs[r], stderr=subprocess.STDOUT) for r in range(world)]
+    deadline, failed = time.monotonic() + timeout, None
     try:
-        for p in procs:
-            assert p.wait(timeout=300) == 0
+        pending = list(range(world))
+        while pending and failed is None:
+            for r in list(pending):
+                rc = procs[r].poll()
+                if rc is not None:
+                    pending.remove(r)
+                    if rc != 0:
+                        failed = f"rank {r} exited with {rc}"
+            if failed is None and pending and time.monotonic() > deadline:
+                failed = f"ranks {pending} still running after {timeout} s"
+            time.sleep(0.05)
     finally:
         for p in procs:
             if p.poll() is None:
                 p.kill()
             p.wait()
+        for f in logs:
+            f.close()
+    if failed:
+        tails = "\n".join(f"--- rank {r} ---\n" + (tmp_path / f"{tag}{r}.log").read_text()[-1500:] for r in range(world))
+        raise AssertionError(f"{failed}\n{tails}")
     return [np.load(tmp_path / f"{tag}{r}.npz") for r in range(world)]
 
 
