@@ -40,7 +40,7 @@ class Decoder:
     [n_kv, rows, head_dim]); ``moe_layers[i]`` / ``gain_handles[i]`` the MoE layer and the block's norm gain."""
 
     def __init__(self, *, d_model, n_heads, n_kv, head_dim, top_k, vocab, window, fa, fw, attn, moe_layers, gain_handles,
-                 embd, out_gain_h, cos, sin, position, one_launch=False):
+                 embd, out_gain_h, cos, sin, position, one_launch=False, dense_router=False):
         self.d, self.H, self.Hkv, self.hd = d_model, n_heads, n_kv, head_dim
         self.vocab, self.fa, self.fw, self.window, self.top_k = vocab, fa, fw, window, top_k
         self.attn, self.moe_layers, self.gain_handles = attn, moe_layers, gain_handles
@@ -54,10 +54,11 @@ class Decoder:
         z = lambda n: torch.empty((1, n), dtype=torch.int64, device="cuda")
         self.x, self.hn, self.logits = z(d_model), z(d_model), z(vocab)
         self._graph = None
+        self.dense_router = dense_router                 # routers are dense int64 matrices: the blocks run stage by stage
         # one_launch: every block inside one persistent kernel where the shape allows it (byte-identical; on B200 it does not
         # yet beat the two entries per block, so it is opt-in)
         self.kernel = None
-        if one_launch:
+        if one_launch and not dense_router:
             try:
                 self.kernel = device.DecoderKernel(
                     [{"gain": gain_handles[i], "moe": moe_layers[i], "wqkv": attn[i]["wqkv"], "wo": attn[i]["wo"], "k": attn[i]["k"],
@@ -98,6 +99,62 @@ class Decoder:
                    fa=fa, fw=fw, attn=attn, moe_layers=moe_layers, gain_handles=gains, embd=embd, out_gain_h=out_gain_h,
                    cos=torch.from_numpy(cos).cuda(), sin=torch.from_numpy(sin).cuda(), position=position, one_launch=one_launch)
 
+    @classmethod
+    def from_gguf(cls, path, rows: "int | None" = None, fa: int = 16, fw: int = 24, one_launch: bool = False):
+        """Load a checkpoint of the north-mini-code layout (see :mod:`gguf`; tensor names of
+        north-mini-code/src/nmc/engine.py:449-498): Q4_K attention matrices, the dense F32 router as int64 at 2**fw
+        (engine.py:245-254), expert tensors split per expert, F32 norm gains at 2**fa, the tied Q6_K embedding / head."""
+        from .gguf import ARCH, GGUFFile
+        g = GGUFFile(path)
+        kv = lambda key: g.kv[f"{ARCH}.{key}"]
+        if kv("leading_dense_block_count") != 0:
+            raise ValueError("dense leading blocks are not supported by this decoder")
+        d, H, Hkv, hd = kv("embedding_length"), kv("attention.head_count"), kv("attention.head_count_kv"), kv("attention.key_length")
+        E, k, eff, vocab = kv("expert_count"), kv("expert_used_count"), kv("expert_feed_forward_length"), kv("vocab_size")
+        rows = int(rows or kv("context_length"))
+        nb = d // 256
+        to_fixed = lambda a, frac: np.round(np.asarray(a, np.float64) * (1 << frac)).astype(np.int64)
+        attn, moe_layers, gains = [], [], []
+        for li in range(kv("block_count")):
+            p = f"blk.{li}."
+            qkv = g.raw(p + "attn_q.weight") + g.raw(p + "attn_k.weight") + g.raw(p + "attn_v.weight")
+            wqkv = qk_cuda.register_weight(qkv, (H + 2 * Hkv) * hd, nb, Q4_K)
+            wo = qk_cuda.register_weight(g.raw(p + "attn_output.weight"), d, H * hd // 256, Q4_K)
+            kc = torch.zeros((Hkv, rows, hd), dtype=torch.int32, device="cuda")
+            attn.append({"wqkv": wqkv, "wo": wo, "k": kc, "v": torch.zeros_like(kc)})
+            router = qk_cuda.register_i64(to_fixed(g.f32(p + "ffn_gate_inp.weight"), fw))
+            gh = [qk_cuda.register_weight(g.expert(p + "ffn_gate_exps.weight", e), eff, nb, Q4_K) for e in range(E)]
+            uh = [qk_cuda.register_weight(g.expert(p + "ffn_up_exps.weight", e), eff, nb, Q4_K) for e in range(E)]
+            dh = [qk_cuda.register_weight(g.expert(p + "ffn_down_exps.weight", e), d, eff // 256, Q6_K) for e in range(E)]
+            moe_layers.append(device.MoELayer(router, gh, uh, dh, k, d, eff))
+            gains.append(qk_cuda.register_i64(to_fixed(g.f32(p + "attn_norm.weight"), fa)))
+        embd = qk_cuda.register_weight(g.raw("token_embd.weight"), vocab, nb, Q6_K)
+        out_gain_h = qk_cuda.register_i64(to_fixed(g.f32("output_norm.weight"), fa))
+        cos, sin = rope_tables(rows, hd, float(kv("rope.freq_base")), fa)
+        dec = cls(d_model=d, n_heads=H, n_kv=Hkv, head_dim=hd, top_k=k, vocab=vocab, window=kv("attention.sliding_window"), fa=fa, fw=fw,
+                  attn=attn, moe_layers=moe_layers, gain_handles=gains, embd=embd, out_gain_h=out_gain_h,
+                  cos=torch.from_numpy(cos).cuda(), sin=torch.from_numpy(sin).cuda(), position=0, one_launch=one_launch,
+                  dense_router=True)
+        return dec
+
+    def generate(self, prompt, n_new: int):
+        """Greedy generation as the reference's ``Engine.generate`` (engine.py:535-597) defines it: the prompt fills the cache
+        (here one token at a time, which yields the same cache rows and the same last hidden row as a batched prefill), then
+        ``n_new`` tokens are picked, each fed back.  Starts at position 0."""
+        self.set_position(0)
+        out, picked = [], None
+        for i, tok in enumerate(list(prompt)):
+            self.token.fill_(int(tok))
+            self.step(i)
+        picked = int(self.token.item())                        # the pick after the last prompt token is the first new token
+        for i in range(int(n_new)):
+            out.append(picked)
+            if i + 1 == int(n_new):
+                break
+            self.step(len(prompt) + i)
+            picked = int(self.token.item())
+        return out
+
     def layer_is_full(self, li: int) -> bool:
         return li % SWA_PERIOD == 0
 
@@ -125,6 +182,19 @@ class Decoder:
         for li in range(0 if not done else self.n_layers, self.n_layers):
             a = self.attn[li]
             full = self.layer_is_full(li)
+            if self.dense_router:
+                # a dense router has no fused routing kernel: norm, products, attention and the MoE stage as separate entries
+                qd, kd = self.H * self.hd, self.Hkv * self.hd
+                h = device.rmsnorm(self.x, self.gain_handles[li], fa, 1)
+                qkv = device.apply(a["wqkv"], h, qd + 2 * kd, fw).view(-1)
+                att = device.attention_decode(qkv[:qd], qkv[qd:qd + kd], qkv[qd + kd:], a["k"], a["v"], pos_bound, self.H, self.Hkv,
+                                              self.hd, fa, 0 if full else self.window, self.cos, self.sin, 0 if full else 1,
+                                              pos_dev=self.pos)
+                ao = device.apply(a["wo"], att.view(1, -1), self.d, fw)
+                moe, _, _ = self.moe_layers[li].forward(h, fa, fw, want_routes=False)
+                self.x += ao
+                self.x += moe
+                continue
             # MoE half first: it normalises x, leaves the digit planes of h in the library and adds moe(h) to x;
             # the attention half then reads those planes and adds its own term
             self.moe_layers[li].block(self.x, self.gain_handles[li], fa, fw, 1, out=self.x, want_routes=False)

@@ -465,3 +465,11 @@ def synth_decoder(seed: int, case: dict, fa: int = 16) -> dict:
     out_gain = to_fixed(np.abs(rng.standard_normal(d)) + 0.5, fa)
     embd = synth_q6k(rng, case["vocab"], nb)
     return {"layers": layers, "out_gain": out_gain, "embd": embd}
+
+
+# The synthetic checkpoint and request the committed generation fixture (tests/golden/engine_generate.npz) was recorded on:
+# two MoE blocks (the first full attention without rotation, the second a sliding window of 8 with RoPE), a prompt longer
+# than the window, eight greedy tokens.
+ENGINE_CASE = {"model": dict(n_layers=2, d_model=256, n_heads=4, n_kv=2, head_dim=64, e_ffn=256, n_experts=8, top_k=2, vocab=96,
+                             window=8, context=64, rope_base=50000.0, seed=5),
+               "prompt": (3, 50, 7, 11, 90, 2, 33, 8, 41, 5), "n_new": 8}

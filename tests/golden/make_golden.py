@@ -5,7 +5,7 @@ Run where the reference tree is mounted; its location must be given in IIE_REFER
     IIE_REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py [fixture ...]
 
 Without arguments every fixture is regenerated; with names (half_fixed, codec, linear, scalar, q1, moe,
-attention, q1_decode, nmc_decode) only those.
+attention, q1_decode, nmc_decode, engine_generate) only those.
 
 Inputs come from the seeded generators in ``oracle/qk_oracle.py`` (so the fixtures only need to
 store seeds and outputs); outputs come from the reference's modules ``nmc.qk_codec``,
@@ -260,7 +260,24 @@ def nmc_decode_fixture():
     return out
 
 
-FIXTURES = {"half_fixed": half_fixture, "codec": codec_fixture, "linear": linear_fixture, "scalar": scalar_fixture,
+def engine_generate_fixture():
+    """Greedy generation by the reference's own ``Engine`` (engine.py:535-597) on its CPU backend, for the synthetic GGUF
+    checkpoint ``integer_inference_engine_b200.gguf.write_synthetic_model`` writes with ``oracle.qk_oracle.ENGINE_CASE``;
+    the CPU kernel it binds is the one ``oracle/build.py`` compiles from the reference (BONSAI_BIN_DIR)."""
+    import tempfile
+    from integer_inference_engine_b200 import gguf as ours
+    case = o.ENGINE_CASE
+    os.environ["BONSAI_BIN_DIR"] = str(ROOT / "oracle" / "_ref")
+    from nmc.engine import Engine
+    with tempfile.TemporaryDirectory() as tmp:
+        shape = ours.write_synthetic_model(Path(tmp) / "m.gguf", **case["model"])
+        ours.write_stub_tokenizer(Path(tmp) / "tok", shape["vocab"])
+        eng = Engine(str(Path(tmp) / "m.gguf"), str(Path(tmp) / "tok"), backend="cpu")
+        ids = eng.generate(list(case["prompt"]), case["n_new"], stop_eos=False)
+    return {"ids": np.array(ids, np.int64)}
+
+
+FIXTURES = {"engine_generate": engine_generate_fixture, "half_fixed": half_fixture, "codec": codec_fixture, "linear": linear_fixture, "scalar": scalar_fixture,
             "q1": q1_fixture, "moe": moe_fixture, "attention": attention_fixture, "q1_decode": q1_decode_fixture,
             "nmc_decode": nmc_decode_fixture}
 
