@@ -769,17 +769,6 @@ extern "C" unsigned long long qk_moe_workspace_bytes(void) {
 }
 extern "C" void qk_moe_workspace_release(void) { std::lock_guard<std::recursive_mutex> lk(g_mu); release_workspace(); }
 
-// ---- attention bank, retained-layer executor part: only meaningful when the experts do not all fit on the device;
-// these entries report failure so the reference bridge keeps its host path for that protocol.  The bank itself
-// (create / import / apply) follows the attention entries further down.
-extern "C" int qk_attention_bank_moe_configure(long long, int, int, int, long long, long long) { return 1; }
-extern "C" int qk_attention_bank_moe_bind(long long, int, int, long long, long long, long long) { return 1; }
-extern "C" int qk_attention_bank_moe_begin(long long, int, long long, long long, long long, long long, long long,
-                                           long long, const int64_t *, int, int, unsigned long long, int, int,
-                                           long long, int, int *, int *) { return 1; }
-extern "C" int qk_attention_bank_moe_continue(long long, int, int, int, long long, int64_t *) { return 1; }
-extern "C" int qk_attention_bank_moe_export(long long, long long, int64_t *) { return 1; }
-
 // ====================================================================================================
 // Part 2: device-pointer extension
 // ====================================================================================================
@@ -1064,13 +1053,38 @@ extern "C" int iie_attn_decode_batch_dev(const int64_t *q_dev, const int64_t *k_
 // exact softmax attention, O product.  K/V rows are kept as int32; a value that does not fit raises the guard
 // (status 3, layer poisoned) where the reference's own guards are wider.
 namespace {
-struct BankLayer { int32_t *k = nullptr, *v = nullptr; long long length = 0; bool poisoned = false, wide = false; };
+// Expert bindings of one layer of a request (retained-layer executor): which registered triplets the request may use.
+struct BankExperts {
+    int experts = 0, used = 0;
+    long long e_ffn = 0;
+    int gate_q = -1, down_q = -1;                  // one block format per layer for gate/up and one for down
+    unsigned maxd_gate = 0, maxdmin_gate = 0, maxd_down = 0, maxdmin_down = 0;
+    std::vector<long long> gate_h, up_h, down_h;   // -1 = unbound
+    const uint8_t **tabs = nullptr;                // device [3][experts]: gate, up, down pointers
+    unsigned char *bound = nullptr;                // device [experts]
+    std::vector<int> cold;                         // selected by the pending begin and still unbound
+};
+struct BankLayer {
+    int32_t *k = nullptr, *v = nullptr; long long length = 0; bool poisoned = false, wide = false;
+    BankExperts moe;
+};
+// Rows a request keeps on the device between begin and continue and from one layer to the next.
+struct BankScratch {
+    void *base = nullptr; size_t bytes = 0;
+    int experts = 0, used = 0;                     // sized for
+    int64_t *residual[2] = {nullptr, nullptr}, *hn = nullptr, *attn = nullptr, *logits = nullptr, *gates = nullptr;
+    int *ids = nullptr, *cold = nullptr, *cells = nullptr;
+    int8_t *hl = nullptr;
+};
 struct Bank {
     bool live = false;
     int n_layers = 0, heads = 0, n_kv = 0, head_dim = 0, fa = 0;
     long long max_length = 0, d_model = 0;
     int64_t *cos = nullptr, *sin = nullptr;
     std::vector<BankLayer> layers;
+    BankScratch sc;
+    bool pending = false, has_residual = false;
+    int pending_layer = -1, retained_layer = -1, slot = 0;
 };
 std::vector<Bank> g_banks;
 
@@ -1078,7 +1092,13 @@ bool valid_bank(long long h) { return h >= 0 && (size_t)h < g_banks.size() && g_
 
 void destroy_bank(Bank &b) {
     cudaDeviceSynchronize();
-    for (auto &l : b.layers) { if (l.k) cudaFree(l.k); if (l.v) cudaFree(l.v); }
+    for (auto &l : b.layers) {
+        if (l.k) cudaFree(l.k);
+        if (l.v) cudaFree(l.v);
+        if (l.moe.tabs) cudaFree(l.moe.tabs);
+        if (l.moe.bound) cudaFree(l.moe.bound);
+    }
+    if (b.sc.base) cudaFree(b.sc.base);
     if (b.cos) cudaFree(b.cos);
     if (b.sin) cudaFree(b.sin);
     b = Bank();
@@ -1125,7 +1145,9 @@ extern "C" long long qk_attention_bank_create(int n_layers, long long max_length
 extern "C" int qk_attention_bank_reset(long long h) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (!valid_bank(h)) return 1;
-    for (auto &l : g_banks[(size_t)h].layers) { l.length = 0; l.poisoned = false; l.wide = false; }
+    Bank &b = g_banks[(size_t)h];
+    for (auto &l : b.layers) { l.length = 0; l.poisoned = false; l.wide = false; l.moe.cold.clear(); }
+    b.pending = false; b.has_residual = false; b.pending_layer = -1; b.retained_layer = -1; b.slot = 0;
     return 0;
 }
 
@@ -1138,7 +1160,7 @@ extern "C" int qk_attention_bank_import(long long h, int layer, const int64_t *k
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (!valid_bank(h)) return 1;
     Bank &b = g_banks[(size_t)h];
-    if (!k || !v || layer < 0 || layer >= b.n_layers || length < 0 || length > b.max_length || b.layers[(size_t)layer].poisoned ||
+    if (!k || !v || b.pending || layer < 0 || layer >= b.n_layers || length < 0 || length > b.max_length || b.layers[(size_t)layer].poisoned ||
         !ensure_bank_layer(b, b.layers[(size_t)layer])) return 1;
     BankLayer &l = b.layers[(size_t)layer];
     l.wide = false;                                          // describes the rows imported by THIS call only
@@ -1169,7 +1191,7 @@ extern "C" int qk_attention_bank_apply(long long h, int layer, long long qh, lon
     if (!valid_bank(h) || !x || !out || output_capacity <= 0) return 1;
     Bank &b = g_banks[(size_t)h];
     const long long d = b.d_model, qd = (long long)b.heads * b.head_dim, kd = (long long)b.n_kv * b.head_dim;
-    if (output_capacity < d || layer < 0 || layer >= b.n_layers || !valid_q(qh) || !valid_q(kh) || !valid_q(vh) || !valid_q(oh) ||
+    if (output_capacity < d || b.pending || layer < 0 || layer >= b.n_layers || !valid_q(qh) || !valid_q(kh) || !valid_q(vh) || !valid_q(oh) ||
         window == 0 || window < -1 || fw < 0 || fw > 62) return 1;
     BankLayer &l = b.layers[(size_t)layer];
     if (l.poisoned || l.length >= b.max_length || !ensure_bank_layer(b, l)) return 1;
@@ -1213,9 +1235,251 @@ extern "C" unsigned long long qk_attention_bank_workspace_bytes(long long h) {
     if (!valid_bank(h)) return ~0ULL;
     const Bank &b = g_banks[(size_t)h];
     unsigned long long total = 2ULL * (unsigned long long)b.max_length * (unsigned long long)(b.head_dim / 2) * 8ULL;
-    for (const auto &l : b.layers)
+    for (const auto &l : b.layers) {
         if (l.k) total += 2ULL * (unsigned long long)b.n_kv * (unsigned long long)b.max_length * (unsigned long long)b.head_dim * 4ULL;
-    return total;
+        if (l.moe.experts > 0) total += (unsigned long long)l.moe.experts * (3ULL * sizeof(void *) + 1ULL);
+    }
+    return total + b.sc.bytes;
+}
+
+// ---- retained-layer executor over the bank (north-mini-code/tools/nmc_qk_cuda.cu:932-1028 configure / bind, 1553-1766
+// begin / continue / export; bridge north-mini-code/src/nmc/qk_cuda.py:571-700).  A decode token walks consecutive MoE
+// layers with the residual row, the normalised row, the routing and the attention row kept on the device:
+//   begin    = norm + dense router + top-k + sigmoid gates + attention sublayer (K/V appended); returns only the
+//              selected experts that have no binding yet ("cold"), so the caller can upload exactly those;
+//   continue = expert stage of the selected (now bound) experts + residual + attention row -> next residual,
+//              kept on the device (publish = 0) or copied out (publish = 1).
+// Copies back to the host per layer: the flag word and [count | cold ids] in begin, the flag word in continue.
+// Narrower than the reference, on the refusing side: one block format per layer for gate/up and one for down (a binding
+// with another format returns 1); int32 K/V rows and eight-digit activations as in qk_attention_bank_apply (status 3).
+namespace {
+bool bank_scratch(Bank &b, int experts, int used) {
+    BankScratch &sc = b.sc;
+    if (sc.base && sc.experts >= experts && sc.used >= used) return true;
+    experts = std::max(experts, sc.experts); used = std::max(used, sc.used);
+    const size_t d = (size_t)b.d_model;
+    auto up = [](size_t n) { return (n + 255) & ~(size_t)255; };
+    const size_t row = up(d * 8);
+    const size_t bytes = 4 * row + up((size_t)experts * 8) + up((size_t)used * 8) + up((size_t)used * 4) + up((size_t)(used + 1) * 4) + 256 + up(8 * d);
+    char *p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); return false; }
+    prof(PM_ALLOC_CALLS); prof(PM_ALLOC_BYTES, bytes);
+    BankScratch n;
+    n.base = p; n.bytes = bytes; n.experts = experts; n.used = used;
+    n.residual[0] = (int64_t *)p; p += row; n.residual[1] = (int64_t *)p; p += row; n.hn = (int64_t *)p; p += row; n.attn = (int64_t *)p; p += row;
+    n.logits = (int64_t *)p; p += up((size_t)experts * 8); n.gates = (int64_t *)p; p += up((size_t)used * 8);
+    n.ids = (int *)p; p += up((size_t)used * 4); n.cold = (int *)p; p += up((size_t)(used + 1) * 4); n.cells = (int *)p; p += 256;
+    n.hl = (int8_t *)p;
+    if (sc.base) {                                   // a wider layer was configured later: the residual rows move along
+        cudaStreamSynchronize(g_stream);
+        if (cudaMemcpy(n.residual[0], sc.residual[0], d * 8, cudaMemcpyDeviceToDevice) != cudaSuccess ||
+            cudaMemcpy(n.residual[1], sc.residual[1], d * 8, cudaMemcpyDeviceToDevice) != cudaSuccess) {
+            cudaGetLastError(); cudaFree(n.base); return false;
+        }
+        cudaFree(sc.base); prof(PM_FREE_CALLS);
+    }
+    sc = n;
+    return true;
+}
+
+// flag word -> host, counted like every other copy back to the host
+int bank_read_flags() {
+    prof(PM_D2H_CALLS); prof(PM_D2H_BYTES, sizeof(int));
+    return read_flags_clear();
+}
+}  // namespace
+
+extern "C" int qk_attention_bank_moe_configure(long long h, int layer, int experts, int used, long long d_model, long long expert_ffn) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS);
+    if (!valid_bank(h) || layer < 0 || experts <= 0 || experts > 1024 || used <= 0 || used > experts || used > 64 || d_model <= 0 ||
+        expert_ffn <= 0 || d_model % 256 != 0 || expert_ffn % 256 != 0) return 1;
+    Bank &b = g_banks[(size_t)h];
+    if (layer >= b.n_layers || d_model != b.d_model || b.pending || b.layers[(size_t)layer].poisoned) return 1;
+    BankExperts &m = b.layers[(size_t)layer].moe;
+    if (m.experts) return (m.experts == experts && m.used == used && m.e_ffn == expert_ffn) ? 0 : 1;
+    const uint8_t **tabs = nullptr; unsigned char *bound = nullptr;
+    if (cudaMalloc(&tabs, (size_t)3 * experts * sizeof(void *)) != cudaSuccess || cudaMalloc(&bound, (size_t)experts) != cudaSuccess ||
+        cudaMemset(tabs, 0, (size_t)3 * experts * sizeof(void *)) != cudaSuccess || cudaMemset(bound, 0, (size_t)experts) != cudaSuccess) {
+        cudaGetLastError();
+        if (tabs) cudaFree(tabs);
+        if (bound) cudaFree(bound);
+        return 1;
+    }
+    prof(PM_ALLOC_CALLS, 2); prof(PM_ALLOC_BYTES, (size_t)experts * (3 * sizeof(void *) + 1));
+    m.tabs = tabs; m.bound = bound; m.experts = experts; m.used = used; m.e_ffn = expert_ffn;
+    m.gate_h.assign((size_t)experts, -1); m.up_h.assign((size_t)experts, -1); m.down_h.assign((size_t)experts, -1);
+    return 0;
+}
+
+extern "C" int qk_attention_bank_moe_bind(long long h, int layer, int expert, long long gate_h, long long up_h, long long down_h) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS);
+    if (!valid_bank(h) || layer < 0) return 1;
+    Bank &b = g_banks[(size_t)h];
+    if (layer >= b.n_layers || b.layers[(size_t)layer].poisoned) return 1;
+    BankLayer &l = b.layers[(size_t)layer];
+    BankExperts &m = l.moe;
+    if (expert < 0 || expert >= m.experts || !valid_q(gate_h) || !valid_q(up_h) || !valid_q(down_h)) return 1;
+    const Weight &g = g_w[gate_h], &u = g_w[up_h], &dn = g_w[down_h];
+    if (g.out_f != m.e_ffn || g.nb != b.d_model / 256 || u.out_f != m.e_ffn || u.nb != b.d_model / 256 || dn.out_f != b.d_model ||
+        dn.nb != m.e_ffn / 256 || g.qtype != u.qtype) return 1;
+    auto retire = [&]() {
+        if (b.pending && b.pending_layer == layer) m.cold.erase(std::remove(m.cold.begin(), m.cold.end(), expert), m.cold.end());
+    };
+    if (m.gate_h[(size_t)expert] >= 0) {
+        if (m.gate_h[(size_t)expert] != gate_h || m.up_h[(size_t)expert] != up_h || m.down_h[(size_t)expert] != down_h) return 1;
+        retire();
+        return 0;
+    }
+    if ((m.gate_q >= 0 && (m.gate_q != g.qtype || m.down_q != dn.qtype))) return 1;
+    const void *pg = g.d, *pu = u.d, *pd = dn.d;
+    const unsigned char one = 1;
+    // the bound byte goes last: a failed copy cannot leave a half-written triplet selectable
+    if (cudaMemcpyAsync(m.tabs + expert, &pg, sizeof(void *), cudaMemcpyHostToDevice, g_stream) != cudaSuccess ||
+        cudaMemcpyAsync(m.tabs + m.experts + expert, &pu, sizeof(void *), cudaMemcpyHostToDevice, g_stream) != cudaSuccess ||
+        cudaMemcpyAsync(m.tabs + 2 * m.experts + expert, &pd, sizeof(void *), cudaMemcpyHostToDevice, g_stream) != cudaSuccess ||
+        cudaMemcpyAsync(m.bound + expert, &one, 1, cudaMemcpyHostToDevice, g_stream) != cudaSuccess || !sync()) {
+        cudaGetLastError(); l.poisoned = true; return 1;
+    }
+    m.gate_q = g.qtype; m.down_q = dn.qtype;
+    m.maxd_gate = std::max({m.maxd_gate, g.maxd, u.maxd}); m.maxdmin_gate = std::max({m.maxdmin_gate, g.maxdmin, u.maxdmin});
+    m.maxd_down = std::max(m.maxd_down, dn.maxd); m.maxdmin_down = std::max(m.maxdmin_down, dn.maxdmin);
+    m.gate_h[(size_t)expert] = gate_h; m.up_h[(size_t)expert] = up_h; m.down_h[(size_t)expert] = down_h;
+    retire();
+    return 0;
+}
+
+extern "C" int qk_attention_bank_moe_begin(long long h, int layer, long long gain_h, long long router_h, long long qh, long long kh,
+                                           long long vh, long long oh, const int64_t *x, int use_retained, int fw,
+                                           unsigned long long eps, int window, int rope, long long inv_sqrt, int cold_capacity,
+                                           int *cold_count_out, int *cold_ids_out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS);
+    if (!valid_bank(h) || layer < 0 || !cold_count_out || !cold_ids_out || use_retained < 0 || use_retained > 1 || fw < 0 || fw > 62 ||
+        window == 0 || window < -1) return 1;
+    Bank &b = g_banks[(size_t)h];
+    if (layer >= b.n_layers || b.pending || !valid_i64(gain_h) || !valid_i64(router_h)) return 1;
+    BankLayer &l = b.layers[(size_t)layer];
+    BankExperts &m = l.moe;
+    const Weight &gain = g_w[gain_h], &router = g_w[router_h];
+    const long long d = b.d_model, qd = (long long)b.heads * b.head_dim, kd = (long long)b.n_kv * b.head_dim;
+    if (l.poisoned || m.experts <= 0 || !m.cold.empty() || cold_capacity < m.used || gain.out_f != 1 || gain.nb != d ||
+        router.out_f != m.experts || router.nb != d) return 1;
+    if ((!use_retained && !x) || (use_retained && (!b.has_residual || b.retained_layer + 1 != layer))) return 1;
+    // the projections are checked before anything is queued: a refused begin leaves the request as it was
+    if (!valid_q(qh) || !valid_q(kh) || !valid_q(vh) || !valid_q(oh) || l.length >= b.max_length) return 1;
+    const Weight &wq = g_w[qh], &wk = g_w[kh], &wv = g_w[vh], &wo = g_w[oh];
+    if (wq.nb != d / 256 || wk.nb != d / 256 || wv.nb != d / 256 || wq.out_f != qd || wk.out_f != kd || wv.out_f != kd ||
+        wo.nb != qd / 256 || wo.out_f != d) return 1;
+    if (!ensure_bank_layer(b, l) || !bank_scratch(b, m.experts, m.used)) return 1;
+    if (l.wide) { l.poisoned = true; return 3; }
+    BankScratch &sc = b.sc;
+    int64_t *qkv = (int64_t *)ensure(R_TMP0, (size_t)(qd + 2 * kd) * 8);
+    int64_t *att = (int64_t *)ensure(R_TMP2, (size_t)qd * 8);
+    if (!qkv || !att) return 1;
+    const int earlier = read_flags_clear();
+    struct Restore { int f; ~Restore() { if (f > 0) { cudaMemcpy(g_flags, &f, sizeof(int), cudaMemcpyHostToDevice); cudaGetLastError(); } } } restore{earlier};
+    if (earlier < 0) return 1;
+    int64_t *residual = sc.residual[use_retained ? b.slot : 0];
+    if (!use_retained) {
+        if (!h2d(residual, x, (size_t)d * 8)) { cudaGetLastError(); return 1; }
+        b.slot = 0;
+    }
+    bool ok = cudaMemsetAsync(sc.cells, 0, 4 * sizeof(int), g_stream) == cudaSuccess &&
+              launch_rmsnorm(residual, 1, d, (const int64_t *)gain.d, b.fa, eps, sc.hn, g_flags, g_stream) == cudaSuccess &&
+              launch_limbs(sc.hn, 1, d, sc.hl, g_flags, g_stream, sc.cells) == cudaSuccess &&
+              launch_exact_dense((const int64_t *)router.d, m.experts, d, sc.hn, 1, fw, sc.logits, g_flags, g_stream) == cudaSuccess &&
+              launch_topk(sc.logits, 1, m.experts, m.used, b.fa, sc.ids, sc.gates, g_stream) == cudaSuccess &&
+              launch_cold_routes(sc.ids, m.used, m.bound, m.experts, sc.cold, g_flags, g_stream) == cudaSuccess;
+    ok = ok && linear_dev(wq, sc.hn, 1, fw, qkv, false, g_stream, sc.hl) && linear_dev(wk, sc.hn, 1, fw, qkv + qd, false, g_stream, sc.hl) &&
+         linear_dev(wv, sc.hn, 1, fw, qkv + qd + kd, false, g_stream, sc.hl);
+    AttnArgs a = {};
+    a.q = qkv; a.k = qkv + qd; a.v = qkv + qd + kd; a.kcache = l.k; a.vcache = l.v; a.pos = l.length; a.pos_dev = nullptr;
+    a.window = window < 0 ? 0 : window; a.lo = 0; a.Lmax = b.max_length; a.cos = b.cos; a.sin = b.sin; a.rope = rope ? 1 : 0;
+    a.H = b.heads; a.Hkv = b.n_kv; a.hd = b.head_dim;
+    attn_consts(a, b.fa, inv_sqrt);
+    ok = ok && attn_scratch(a, g_stream);
+    a.out = att; a.flags = g_flags;
+    ok = ok && launch_attn_decode(a, g_stream) == cudaSuccess;
+    ok = ok && linear_dev(wo, att, 1, fw, sc.attn, false, g_stream);
+    if (!ok) { cudaGetLastError(); cudaStreamSynchronize(g_stream); l.poisoned = true; return 1; }
+    const int f = bank_read_flags();                       // synchronises: routing, attention and the append are judged together
+    if (f < 0) { l.poisoned = true; return 1; }
+    if (f != 0) { l.poisoned = true; return 3; }
+    std::vector<int> cold((size_t)m.used + 1, 0);
+    if (!d2h(cold.data(), sc.cold, cold.size() * sizeof(int)) || !sync() || cold[0] < 0 || cold[0] > m.used) {
+        cudaGetLastError(); l.poisoned = true; return 1;
+    }
+    m.cold.assign(cold.begin() + 1, cold.begin() + 1 + cold[0]);
+    for (int i = 0; i < cold[0]; i++) cold_ids_out[i] = cold[(size_t)i + 1];
+    *cold_count_out = cold[0];
+    l.length++;
+    b.has_residual = true; b.pending = true; b.pending_layer = layer;
+    return 0;
+}
+
+extern "C" int qk_attention_bank_moe_continue(long long h, int layer, int fw, int publish, long long output_capacity, int64_t *out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS); prof(PM_MOE);
+    if (!valid_bank(h) || layer < 0 || fw < 0 || fw > 62 || publish < 0 || publish > 1 || (publish && (!out || output_capacity <= 0))) return 1;
+    Bank &b = g_banks[(size_t)h];
+    if (layer >= b.n_layers || !b.pending || b.pending_layer != layer) return 1;
+    BankLayer &l = b.layers[(size_t)layer];
+    BankExperts &m = l.moe;
+    const long long d = b.d_model;
+    if (l.poisoned || m.experts <= 0 || !b.sc.base || (publish && output_capacity < d)) return 1;
+    if (!m.cold.empty()) return 4;                            // begin's cold set has not been bound completely
+    BankScratch &sc = b.sc;
+    const int k = m.used, E = m.experts;
+    int64_t *residual = sc.residual[b.slot], *next = sc.residual[b.slot ^ 1];
+    const int earlier = read_flags_clear();
+    struct Restore { int f; ~Restore() { if (f > 0) { cudaMemcpy(g_flags, &f, sizeof(int), cudaMemcpyHostToDevice); cudaGetLastError(); } } } restore{earlier};
+    if (earlier < 0) return 1;
+    bool ok = launch_add_rows(residual, sc.attn, next, d, g_stream) == cudaSuccess;
+    if (fast_envelope(m.gate_q, d / 256, m.maxd_gate, m.maxdmin_gate, fw) && fast_envelope(m.down_q, m.e_ffn / 256, m.maxd_down, m.maxdmin_down, fw)) {
+        int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)k * 8 * m.e_ffn);
+        ok = ok && gul;
+        StreamArgs ga = {};
+        ga.wa = m.tabs; ga.wb = m.tabs + E; ga.sel = sc.ids; ga.n_sel = k; ga.out_f = m.e_ffn; ga.n_blocks = d / 256; ga.fw = fw; ga.fa = b.fa;
+        ga.xl = sc.hl; ga.x_per_sel = 0; ga.x_nl = sc.cells; ga.out = nullptr; ga.out_limbs = gul; ga.out_nl = sc.cells + 1; ga.flags = g_flags;
+        ga.fast = small_scales(m.maxd_gate, m.maxdmin_gate, fw);
+        StreamArgs da = {};
+        da.wa = m.tabs + 2 * E; da.wb = da.wa; da.sel = sc.ids; da.n_sel = k; da.out_f = d; da.n_blocks = m.e_ffn / 256; da.fw = fw; da.fa = b.fa;
+        da.xl = gul; da.x_per_sel = 1; da.x_nl = sc.cells + 1; da.out = next; da.gates = sc.gates; da.flags = g_flags;
+        da.fast = small_scales(m.maxd_down, m.maxdmin_down, fw);
+        ok = ok && launch_stream(m.gate_q, MODE_GATEUP, ga, g_stream) == cudaSuccess && launch_stream(m.down_q, MODE_DOWN, da, g_stream) == cudaSuccess;
+    } else {
+        // block scales beyond the streamed kernels' envelope: the per-weight 128-bit products, selected on the host
+        std::vector<int> ids((size_t)k);
+        ok = ok && d2h(ids.data(), sc.ids, (size_t)k * sizeof(int)) && sync();
+        std::vector<const Weight *> gw, uw, dw;
+        for (int i = 0; ok && i < k; i++) {
+            const int e = ids[(size_t)i];
+            if (e < 0 || e >= E || m.gate_h[(size_t)e] < 0) { ok = false; break; }
+            gw.push_back(&g_w[m.gate_h[(size_t)e]]); uw.push_back(&g_w[m.up_h[(size_t)e]]); dw.push_back(&g_w[m.down_h[(size_t)e]]);
+        }
+        int64_t *moe = ok ? (int64_t *)ensure(R_OUT, (size_t)d * 8) : nullptr;
+        ok = ok && moe && moe_exact_pairs(gw, uw, dw, sc.hn, std::vector<int>((size_t)k, 0), sc.gates, 1, k, d, m.e_ffn, b.fa, fw, moe) &&
+             launch_add_rows(next, moe, next, d, g_stream) == cudaSuccess;
+    }
+    if (!ok) { cudaGetLastError(); cudaStreamSynchronize(g_stream); l.poisoned = true; return 1; }
+    const int f = bank_read_flags();
+    if (f < 0) { l.poisoned = true; return 1; }
+    if (f != 0) { l.poisoned = true; return 3; }
+    if (publish && (!d2h(out, next, (size_t)d * 8) || !sync())) { cudaGetLastError(); l.poisoned = true; return 1; }
+    b.slot ^= 1; b.has_residual = true; b.retained_layer = layer; b.pending = false; b.pending_layer = -1;
+    return 0;
+}
+
+extern "C" int qk_attention_bank_moe_export(long long h, long long output_capacity, int64_t *out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    prof(PM_NATIVE_CALLS);
+    if (!valid_bank(h) || !out || output_capacity <= 0) return 1;
+    Bank &b = g_banks[(size_t)h];
+    if (b.pending || !b.has_residual || b.retained_layer < 0 || !b.sc.base || output_capacity < b.d_model) return 1;
+    if (!d2h(out, b.sc.residual[b.slot], (size_t)b.d_model * 8) || !sync()) { cudaGetLastError(); return 1; }
+    return 0;
 }
 
 extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t *kcache_dev, int32_t *vcache_dev,

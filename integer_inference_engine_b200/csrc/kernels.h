@@ -153,6 +153,11 @@ cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t
 // copy from a host stack variable would not)
 cudaError_t launch_set2(int *p, int a, int b, cudaStream_t s);
 
+// cold[0] = number of ids whose `bound` byte is 0, cold[1..] = those ids in order; an id outside [0, n_experts) raises flag bit 1
+cudaError_t launch_cold_routes(const int *ids, int k, const unsigned char *bound, int n_experts, int *cold, int *flags, cudaStream_t s);
+// out = a + b (wrapping), out may alias either input
+cudaError_t launch_add_rows(const int64_t *a, const int64_t *b, int64_t *out, long long n, cudaStream_t s);
+
 // Exact 128-bit reference-order product for inputs outside the fast envelope: out[pair][o].
 cudaError_t launch_exact_linear(const uint8_t *w, int qtype, long long out_f, long long n_blocks, const int64_t *x,
                                 long long T, int fw, int64_t *out, cudaStream_t s);

@@ -412,6 +412,35 @@ cudaError_t launch_set2(int *p, int a, int b, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+// Selected experts without a binding, compacted in routing order: cold[0] = how many, cold[1..] = their ids
+// (north-mini-code/tools/nmc_qk_cuda.cu cold_routes_k).  An id outside the table raises flag bit 1.
+__global__ void cold_routes_kernel(const int *ids, int k, const unsigned char *bound, int n_experts, int *cold, int *flags) {
+    int n = 0;
+    for (int i = 0; i < k; i++) {
+        const int e = ids[i];
+        if (e < 0 || e >= n_experts) { atomicOr(flags, 2); continue; }
+        if (!bound[e]) cold[1 + n++] = e;
+    }
+    cold[0] = n;
+}
+
+cudaError_t launch_cold_routes(const int *ids, int k, const unsigned char *bound, int n_experts, int *cold, int *flags, cudaStream_t s) {
+    cold_routes_kernel<<<1, 1, 0, s>>>(ids, k, bound, n_experts, cold, flags);
+    note_launch();
+    return cudaGetLastError();
+}
+
+__global__ void add_rows_kernel(const int64_t *a, const int64_t *b, int64_t *out, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = (int64_t)((uint64_t)a[i] + (uint64_t)b[i]);
+}
+
+cudaError_t launch_add_rows(const int64_t *a, const int64_t *b, int64_t *out, long long n, cudaStream_t s) {
+    add_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, out, n);
+    note_launch();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, cudaStream_t s,
                          int *nl_out) {
     limbs_kernel<<<grid_for(n_rows * K, 256), 256, 0, s>>>(x, n_rows, K, planes, flags, nl_out);

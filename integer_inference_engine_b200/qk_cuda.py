@@ -56,7 +56,6 @@ def _signatures():
     """name -> (argument types, result type) of every symbol include/iie_qk.h declares."""
     c_int, i64, u64, vp = ctypes.c_int, ctypes.c_int64, ctypes.c_uint64, ctypes.c_void_p
     P64, P32 = ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int)
-    moe_stub = ([], c_int)          # retained-layer executor entries: present in the ABI, never called from here
     return {
         "qk_cuda_abi_version": ([], c_int), "qk_cuda_available": ([], c_int),
         "qk_linear_cuda": ([vp, vp, i64, i64, i64, c_int, c_int, vp], c_int),
@@ -102,9 +101,12 @@ def _signatures():
         "iie_moe_experts_dev": ([i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, c_int, vp, vp], c_int),
         "iie_moe_block_host": ([i64, i64, vp, i64, c_int, c_int, u64, vp, vp, vp], c_int),
         "iie_moe_block_dev": ([i64, i64, vp, i64, c_int, c_int, u64, vp, vp, vp, vp], c_int),
-        "qk_attention_bank_moe_configure": moe_stub, "qk_attention_bank_moe_bind": moe_stub,
-        "qk_attention_bank_moe_begin": moe_stub, "qk_attention_bank_moe_continue": moe_stub,
-        "qk_attention_bank_moe_export": moe_stub,
+        "qk_attention_bank_moe_configure": ([i64, c_int, c_int, c_int, i64, i64], c_int),
+        "qk_attention_bank_moe_bind": ([i64, c_int, c_int, i64, i64, i64], c_int),
+        "qk_attention_bank_moe_begin": ([i64, c_int, i64, i64, i64, i64, i64, i64, vp, c_int, c_int, u64, c_int, c_int, i64, c_int,
+                                         P32, P32], c_int),
+        "qk_attention_bank_moe_continue": ([i64, c_int, c_int, c_int, i64, vp], c_int),
+        "qk_attention_bank_moe_export": ([i64, i64, vp], c_int),
     }
 
 
@@ -129,9 +131,8 @@ def load_library():
     if absent:
         raise CudaUnavailableError(f"{path} lacks symbols {absent}")
     for name, (args, res) in table.items():
-        if args or res is not ctypes.c_int or not name.startswith("qk_attention_bank_moe_"):
-            fn = getattr(lib, name)
-            fn.argtypes, fn.restype = args, res
+        fn = getattr(lib, name)
+        fn.argtypes, fn.restype = args, res
     return lib
 
 
@@ -163,7 +164,7 @@ def _native(name: str, *args):
 # every optional capability of the reference bridge is always present in this library
 resident_available = grouped_available = dp4a_available = resident_preprocess_available = available
 moe_ffn_available = moe_ffn_dp4a_available = moe_ffn_batched_available = moe_ffn_batched_dp4a_available = available
-resident_attention_available = available
+resident_attention_available = resident_layer_available = available
 
 
 # ------------------------------------------------------------------------------------------ argument helpers ---
@@ -508,6 +509,9 @@ class ResidentAttentionCache:
             setattr(self, name, value)
         self._filled = [0] * dims["n_layers"]
         self._open = True
+        self._moe_shape = {}              # layer -> (experts, used, e_ffn) as configured
+        self._begun = None                # layer whose begin_moe_layer awaits its continue_moe_layer
+        self._epoch = 0                   # advances whenever the retained row changes; markers of older epochs are stale
 
     def _check(self, layer: int) -> int:
         if not self._open:
@@ -551,23 +555,218 @@ class ResidentAttentionCache:
         self._filled[layer] += 1
         return out
 
+    # -- retained-layer executor: a token walks consecutive MoE layers with its residual row kept on the device --------
+    def configure_moe_layer(self, layer: int, n_experts: int, n_used: int, d_model: int, expert_ffn: int) -> None:
+        """Declare the expert table of one layer (no expert weight is touched; see :meth:`bind_moe_expert`)."""
+        layer = self._check(layer)
+        shape = (int(n_experts), int(n_used), int(expert_ffn))
+        if int(d_model) != self.d_model or shape[0] <= 0 or not 0 < shape[1] <= shape[0] or shape[2] <= 0 or shape[2] % 256:
+            raise ValueError(f"layer {layer}: not a usable MoE shape {shape} at width {d_model}")
+        if self._moe_shape.get(layer, shape) != shape:
+            raise ValueError(f"layer {layer} is already configured as {self._moe_shape[layer]}")
+        if _native("qk_attention_bank_moe_configure", self.handle, layer, shape[0], shape[1], self.d_model, shape[2]) != 0:
+            raise CudaContextError(f"the MoE table of layer {layer} could not be configured")
+        self._moe_shape[layer] = shape
+
+    def bind_moe_expert(self, layer: int, expert: int, gate_handle: int, up_handle: int, down_handle: int) -> None:
+        """Let this request use the registered (gate, up, down) matrices as expert ``expert`` of ``layer``."""
+        layer, expert = self._check(layer), int(expert)
+        if layer not in self._moe_shape or not 0 <= expert < self._moe_shape[layer][0]:
+            raise ValueError(f"expert {expert} of layer {layer} is outside the configured table")
+        if _native("qk_attention_bank_moe_bind", self.handle, layer, expert, int(gate_handle), int(up_handle), int(down_handle)) != 0:
+            raise CudaContextError(f"binding expert {expert} of layer {layer} failed")
+
+    def begin_moe_layer(self, layer: int, gain_handle: int, router_handle: int, q_handle: int, k_handle: int, v_handle: int,
+                        o_handle: int, hidden, fw: int, eps: int, window: "int | None", rope: bool) -> "tuple[int, ...]":
+        """Norm, routing and the attention sublayer of one token on ``layer``; everything stays on the device.  ``hidden`` is a
+        host row [1, d_model] or the marker a previous :meth:`continue_moe_layer` returned.  Returns the selected experts
+        that are not bound yet: bind them, then call :meth:`continue_moe_layer`."""
+        layer = self._check(layer)
+        if layer not in self._moe_shape or self._begun is not None or self._filled[layer] >= self.max_length:
+            raise ValueError(f"layer {layer} cannot begin: not configured, another layer is pending, or the bank is full")
+        if isinstance(hidden, ResidentLayerHidden):
+            if hidden.bank is not self or hidden.epoch != self._epoch:
+                raise ValueError("this retained-row marker is stale or belongs to another bank")
+            keep, pointer, retained = None, None, 1
+        else:
+            keep = np.ascontiguousarray(np.asarray(hidden, dtype=np.int64))
+            if keep.shape != (1, self.d_model):
+                raise ValueError(f"the hidden row must be (1, {self.d_model}), not {keep.shape}")
+            pointer, retained = keep.ctypes.data, 0
+        used = self._moe_shape[layer][1]
+        count, cold = ctypes.c_int(0), (ctypes.c_int * used)()
+        scale = int(round(2 ** self.fa / self.head_dim ** 0.5))
+        rc = int(_native("qk_attention_bank_moe_begin", self.handle, layer, int(gain_handle), int(router_handle), int(q_handle),
+                         int(k_handle), int(v_handle), int(o_handle), pointer, retained, int(fw), int(eps),
+                         -1 if window is None else int(window), 1 if rope else 0, scale, used, ctypes.byref(count), cold))
+        if rc:
+            why = "a value left the exact envelope" if rc == 3 else f"native status {rc}"
+            raise CudaContextError(f"begin on layer {layer} failed: {why}")
+        if not 0 <= count.value <= used:
+            raise CudaContextError(f"layer {layer} reported {count.value} cold experts of {used} selected")
+        self._filled[layer] += 1
+        self._begun = layer
+        return tuple(int(cold[i]) for i in range(count.value))
+
+    def continue_moe_layer(self, layer: int, fw: int, *, publish: bool = False):
+        """Expert stage and residual of the layer begun last.  Returns the new residual row (``publish``) or a marker that
+        only the next layer's :meth:`begin_moe_layer` of this bank accepts."""
+        layer = self._check(layer)
+        if self._begun != layer:
+            raise ValueError(f"layer {layer} has no begin_moe_layer pending")
+        out = np.empty((1, self.d_model), dtype=np.int64) if publish else None
+        rc = int(_native("qk_attention_bank_moe_continue", self.handle, layer, int(fw), 1 if publish else 0,
+                         0 if out is None else out.size, None if out is None else out.ctypes.data))
+        if rc:
+            why = {3: "a value left the exact envelope", 4: "selected cold experts remain unbound"}.get(rc, f"native status {rc}")
+            raise CudaContextError(f"continue on layer {layer} failed: {why}")
+        self._begun = None
+        self._epoch += 1
+        return out if publish else ResidentLayerHidden(self, self._epoch)
+
+    def export_moe_hidden(self) -> np.ndarray:
+        """Copy of the retained residual row (debugging, or leaving the retained chain early)."""
+        if not self._open or self._begun is not None:
+            raise CudaContextError("no retained row can be exported while the bank is closed or a layer is pending")
+        out = np.empty((1, self.d_model), dtype=np.int64)
+        if _native("qk_attention_bank_moe_export", self.handle, out.size, out.ctypes.data) != 0:
+            raise CudaContextError("the bank holds no retained row")
+        return out
+
     def reset(self) -> None:
         if not self._open:
             raise CudaContextError("this attention bank has been closed")
         if _native("qk_attention_bank_reset", self.handle) != 0:
             raise CudaContextError("the attention bank could not be reset")
         self._filled = [0] * self.n_layers
+        self._begun = None
+        self._epoch += 1
 
     def workspace_bytes(self) -> int:
-        return int(_native("qk_attention_bank_workspace_bytes", self.handle))
+        if not self._open:
+            raise CudaContextError("this attention bank has been closed")
+        value = int(_native("qk_attention_bank_workspace_bytes", self.handle))
+        if value == 2 ** 64 - 1:
+            raise CudaContextError("the bank could not account for its device memory")
+        return value
 
     def close(self) -> None:
         if self._open:
             _native("qk_attention_bank_destroy", self.handle)
             self._open = False
+            self._begun = None
+            self._epoch += 1
 
     def __enter__(self):
         return self
 
     def __exit__(self, *exc):
         self.close()
+
+
+class ResidentLayerHidden:
+    """Stands for the residual row a bank keeps on the device after ``continue_moe_layer(publish=False)``."""
+    __slots__ = ("bank", "epoch")
+
+    def __init__(self, bank: ResidentAttentionCache, epoch: int):
+        self.bank, self.epoch = bank, epoch
+
+
+class ResidentMoeLayerSpec:
+    """Handles and attention settings of one MoE layer of a retained chain."""
+    __slots__ = ("layer", "gain_handle", "router_handle", "q_handle", "k_handle", "v_handle", "o_handle", "window", "rope")
+
+    def __init__(self, layer, gain_handle, router_handle, q_handle, k_handle, v_handle, o_handle, window, rope):
+        self.layer, self.gain_handle, self.router_handle = int(layer), int(gain_handle), int(router_handle)
+        self.q_handle, self.k_handle, self.v_handle, self.o_handle = int(q_handle), int(k_handle), int(v_handle), int(o_handle)
+        self.window, self.rope = (None if window is None else int(window)), bool(rope)
+
+
+class ResidentMoeTokenExecutor:
+    """One decode token through ``layer_count`` consecutive MoE layers of a bank, uploading only the experts a token selects
+    (north-mini-code/src/nmc/qk_cuda.py:741-867).  ``lookup_expert(layer, expert)`` returns the (gate, up, down) handles of an
+    expert that is already registered, or ``None``; ``load_expert(layer, expert)`` registers one and returns its handles, and
+    is called only for the experts a layer reports as cold.  After any failure the executor refuses further work: the K/V
+    rows of the layers already visited have advanced, so the request has to be reset or dropped."""
+
+    def __init__(self, cache: ResidentAttentionCache, *, first_layer: int, layer_count: int, n_experts: int, n_used: int,
+                 d_model: int, expert_ffn: int, fw: int, eps: int, lookup_expert, load_expert):
+        if not isinstance(cache, ResidentAttentionCache) or not cache._open:
+            raise ValueError("the executor needs an open attention bank")
+        if not callable(lookup_expert) or not callable(load_expert):
+            raise TypeError("lookup_expert and load_expert must be callables")
+        self.first_layer, self.layer_count = int(first_layer), int(layer_count)
+        self.shape = (int(n_experts), int(n_used), int(d_model), int(expert_ffn))
+        self.fw, self.eps = int(fw), int(eps)
+        last = self.first_layer + self.layer_count
+        if self.first_layer < 0 or self.layer_count <= 0 or last > cache.n_layers or self.shape[0] <= 0 or \
+                not 0 < self.shape[1] <= self.shape[0] or self.shape[2] != cache.d_model or self.shape[3] <= 0 or \
+                self.shape[3] % 256 or not 0 <= self.fw <= 62 or not 0 <= self.eps < 2 ** 64:
+            raise ValueError("the executor cannot take these dimensions")
+        self.cache, self.lookup_expert, self.load_expert = cache, lookup_expert, load_expert
+        self._tables_done = set()           # layers whose table is configured and whose known experts are bound
+        self.poisoned = False
+
+    @staticmethod
+    def _triplet(value, where: str):
+        try:
+            handles = tuple(int(h) for h in value)
+        except (TypeError, ValueError):
+            handles = ()
+        if len(handles) != 3 or min(handles, default=-1) < 0:
+            raise CudaContextError(f"{where} did not give a (gate, up, down) handle triplet")
+        return handles
+
+    def _table(self, layer: int) -> None:
+        if layer in self._tables_done:
+            return
+        experts, used, d_model, e_ffn = self.shape
+        self.cache.configure_moe_layer(layer, experts, used, d_model, e_ffn)
+        for expert in range(experts):
+            known = self.lookup_expert(layer, expert)
+            if known is not None:
+                self.cache.bind_moe_expert(layer, expert, *self._triplet(known, f"lookup of expert {expert}, layer {layer}"))
+        self._tables_done.add(layer)
+
+    def _specs(self, layers):
+        specs = tuple(layers)
+        want = list(range(self.first_layer, self.first_layer + self.layer_count))
+        if [getattr(spec, "layer", None) for spec in specs] != want or not all(isinstance(s, ResidentMoeLayerSpec) for s in specs):
+            raise ValueError(f"the executor runs layers {want[0]}..{want[-1]} in order")
+        return specs
+
+    def prepare(self, layers):
+        """Configure the tables and bind what is already resident, before any K/V row moves."""
+        if self.poisoned:
+            raise CudaContextError("this executor failed earlier: reset or drop the request")
+        specs = self._specs(layers)
+        try:
+            for spec in specs:
+                self._table(spec.layer)
+        except Exception:
+            self.poisoned = True
+            raise
+        return specs
+
+    def run(self, hidden, layers) -> np.ndarray:
+        specs = self.prepare(layers)
+        row = np.ascontiguousarray(np.asarray(hidden, dtype=np.int64))
+        if row.shape != (1, self.shape[2]):
+            raise ValueError(f"the hidden row must be (1, {self.shape[2]}), not {row.shape}")
+        try:
+            state = row
+            for spec in specs:
+                cold = self.cache.begin_moe_layer(spec.layer, spec.gain_handle, spec.router_handle, spec.q_handle, spec.k_handle,
+                                                  spec.v_handle, spec.o_handle, state, self.fw, self.eps, spec.window, spec.rope)
+                if len(set(cold)) != len(cold) or any(not 0 <= e < self.shape[0] for e in cold):
+                    raise CudaContextError(f"layer {spec.layer} reported cold experts {cold}")
+                for expert in cold:
+                    loaded = self._triplet(self.load_expert(spec.layer, expert), f"load of expert {expert}, layer {spec.layer}")
+                    self.cache.bind_moe_expert(spec.layer, expert, *loaded)
+                state = self.cache.continue_moe_layer(spec.layer, self.fw, publish=spec is specs[-1])
+            if not isinstance(state, np.ndarray):
+                raise CudaContextError("the last layer did not publish its row")
+            return state
+        except Exception:
+            self.poisoned = True
+            raise
