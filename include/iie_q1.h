@@ -66,6 +66,50 @@ void bonsai_q1_free_weights(void);
 int bonsai_rmsnorm_gpu(const long long *x, long long rows, long long cols, long long frac, long long eps,
                        const long long *gain, long long *out);
 
+/* ---- part 1b: whole-model entries (the bridge treats each as optional, gpu_native.py:53-170) ------------------
+ * Layouts are the reference's: q [H][M][hd], K/V [Hkv][L][hd], caches of the decode context [n_layers][Hkv][Lb][hd]
+ * per sequence, all int64 host arrays.  On the device K/V rows are int32: a value that does not fit gives the
+ * overflow status on which the bridge redoes the call on the host (2 for the two attention entries, 4 for the model
+ * entries), like any RMSNorm envelope miss. */
+
+/* bonsai_q1_gpu.cu:2020 - upload an int64 array once (gains, rope tables); handle >= 0 or -1.  Released by
+ * bonsai_q1_free_weights. */
+long long bonsai_buf_upload_i64(const long long *host, long long n);
+/* bonsai_q1_gpu.cu:2475 - causal attention of M new tokens at positions start .. start+M-1 over L = start+M keys;
+ * q after per-head norm and rotation, k/v the full rows.  out [H][M][hd].  0 ok, 1 bad arguments / CUDA, 2 overflow. */
+int bonsai_attention_prefill_gpu(const long long *q, const long long *k, const long long *v, long long H, long long Hkv,
+                                 long long hd, long long M, long long L, long long start, long long frac,
+                                 long long inv_sqrt_fp, long long *out);
+/* bonsai_q1_gpu.cu:2550 - one new token of each of B sequences: q [B][H][hd], caches [B][Hkv][cap][hd] padded,
+ * lengths [B] = valid rows of each sequence (the new token's row included).  out [B][H][hd].  0 / 1 / 2 as above. */
+int bonsai_attention_decode_batched_gpu(const long long *q, const long long *Kc, const long long *Vc, const long long *lengths,
+                                        long long B, long long H, long long Hkv, long long hd, long long cap, long long frac,
+                                        long long inv_sqrt_fp, long long *out);
+/* bonsai_q1_gpu.cu:3694 - the whole prefill on the device: x_embed [T][d] -> every layer -> final norm and output matrix
+ * on the last row -> out_logits [vocab].  wq .. w2: per-layer weight handles; n1g .. kng: per-layer buffer handles of the
+ * gains; finalg, cos_h, sin_h buffer handles; out_head a weight handle.  out_k / out_v (nullable): the K (after head
+ * norm and rotation) and V rows of every layer, [n_layers][Hkv][T][hd].  0 ok, 1 bad arguments / CUDA, 4 overflow. */
+int bonsai_prefill_forward_gpu(const long long *x_embed, long long T, long long d, long long n_layers, long long H, long long Hkv,
+                               long long hd, long long dff, long long frac, long long eps, long long inv_sqrt_fp,
+                               const long long *wq, const long long *wk, const long long *wv, const long long *wo,
+                               const long long *w1, const long long *wu, const long long *w2, const long long *n1g,
+                               const long long *n2g, const long long *qng, const long long *kng, long long finalg,
+                               long long out_head, long long cos_h, long long sin_h, long long *out_logits, long long *out_k,
+                               long long *out_v);
+/* bonsai_q1_gpu.cu:3517,3565,3588,3649 - decode context of B sequences with device K/V of `cap` rows each: create
+ * (handle >= 0 or -1), seed sequence b with the K/V rows of its prefill, one decode step for all sequences
+ * (x_in [B][d] the new tokens' embedded rows, pos [B] each sequence's position = rows cached before the step,
+ * out_logits [B][vocab]; 0 ok, 1 bad arguments / CUDA, 4 overflow), free. */
+long long bonsai_decode_ctx_create(long long B, long long n_layers, long long H, long long Hkv, long long hd, long long d,
+                                   long long dff, long long cap, long long vocab, long long frac, long long eps,
+                                   long long inv_sqrt, const long long *wq, const long long *wk, const long long *wv,
+                                   const long long *wo, const long long *w1, const long long *wu, const long long *w2,
+                                   const long long *n1g, const long long *n2g, const long long *qng, const long long *kng,
+                                   long long finalg, long long out_head, long long cos_h, long long sin_h);
+int bonsai_decode_ctx_seed_seq(long long ctx_h, long long b, const long long *k_src, const long long *v_src, long long Lb);
+int bonsai_decode_step(long long ctx_h, const long long *x_in, const long long *pos, long long *out_logits);
+void bonsai_decode_ctx_free(long long ctx_h);
+
 /* ---- part 2: additive, device pointers (no counterpart in the reference) --------------------------- */
 
 /* Product with a registered weight on device buffers, asynchronous on `stream` (NULL = the CUDA default

@@ -573,6 +573,14 @@ int *shared_flag_word() {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     return init() ? g_flags : nullptr;
 }
+void restore_flag_bits(int bits) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (bits <= 0 || !init()) return;
+    int now = 0;
+    if (cudaMemcpy(&now, g_flags, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return; }
+    now |= bits;
+    if (cudaMemcpy(g_flags, &now, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) cudaGetLastError();
+}
 }  // namespace iie
 
 extern "C" int qk_cuda_abi_version(void) { return 5; }

@@ -285,6 +285,7 @@ cudaError_t launch_rmsnorm_pair(const int64_t *x, long long rows_a, long long ro
 bool attn_shape_ok(int n_heads, int n_kv, int head_dim);      // shapes launch_attn_decode accepts
 void set_q1_stream(int on);        // 1: single-token Q1_0 products through the bulk-copy kernel, 0 (default): per-lane loads
 int *shared_flag_word();           // the library's device flag word (bit 1: RMSNorm envelope), NULL without a device
+void restore_flag_bits(int bits);  // OR bits back into the flag word (flags an entry set aside while it ran)
 cudaError_t launch_q1_silu_mul(const int64_t *gate, const int64_t *up, long long n, int frac, int64_t *out, cudaStream_t s);
 cudaError_t launch_q1_embed_row(const uint8_t *units, bool sc32, long long nb, const int *row_dev, long long row_host, int64_t *out,
                                 cudaStream_t s);

@@ -25,6 +25,8 @@ EXPORTED_SYMBOLS = (
     "bonsai_gpu_mem_info", "bonsai_q1_resident_weight_bytes", "bonsai_q1_linear_gpu", "bonsai_q1_linear_dp4a_gpu",
     "bonsai_q1_register_weight", "bonsai_q1_register_weight_i32", "bonsai_q1_register_weight_i32_gpu_layout",
     "bonsai_q1_register_weight_i32_bmma", "bonsai_q1_apply_resident", "bonsai_q1_free_weights", "bonsai_rmsnorm_gpu",
+    "bonsai_buf_upload_i64", "bonsai_attention_prefill_gpu", "bonsai_attention_decode_batched_gpu", "bonsai_prefill_forward_gpu",
+    "bonsai_decode_ctx_create", "bonsai_decode_ctx_seed_seq", "bonsai_decode_step", "bonsai_decode_ctx_free",
     "iie_q1_apply_dev", "iie_q1_apply_fused_dev", "iie_q1_head_norm_dev", "iie_q1_silu_mul_dev", "iie_q1_embed_dev", "iie_q1_set_stream", "iie_q1_weight_shape", "iie_q1_workspace_generation",
 )
 from .qk_cuda import CudaContextError      # noqa: E402  (same error type as the MoE bridge)
@@ -67,6 +69,13 @@ def load_library():
         "bonsai_q1_register_weight_i32_bmma": ([vp, vp, i64, i64], i64),
         "bonsai_q1_apply_resident": ([i64, vp, i64, i64, vp], c_int), "bonsai_q1_free_weights": ([], None),
         "bonsai_rmsnorm_gpu": ([vp, i64, i64, i64, i64, vp, vp], c_int),
+        "bonsai_buf_upload_i64": ([vp, i64], i64),
+        "bonsai_attention_prefill_gpu": ([vp, vp, vp] + [i64] * 8 + [vp], c_int),
+        "bonsai_attention_decode_batched_gpu": ([vp] * 4 + [i64] * 7 + [vp], c_int),
+        "bonsai_prefill_forward_gpu": ([vp] + [i64] * 10 + [vp] * 11 + [i64] * 4 + [vp] * 3, c_int),
+        "bonsai_decode_ctx_create": ([i64] * 12 + [vp] * 11 + [i64] * 4, i64),
+        "bonsai_decode_ctx_seed_seq": ([i64, i64, vp, vp, i64], c_int),
+        "bonsai_decode_step": ([i64, vp, vp, vp], c_int), "bonsai_decode_ctx_free": ([i64], None),
         "iie_q1_apply_dev": ([i64, vp, i64, i64, vp, vp], c_int),
         "iie_q1_apply_fused_dev": ([i64, c_int, vp, vp, i64, vp, i64, i64, vp, vp, vp], c_int),
         "iie_q1_head_norm_dev": ([vp, i64, i64, i64, vp, vp, i64, vp, vp], c_int),
@@ -121,7 +130,8 @@ def _fits_four_digits(x: np.ndarray) -> bool:
 def _call(name: str, *args) -> int:
     fn = getattr(_lib(), name)
     with _CUDA_LOCK:
-        return int(fn(*args))
+        result = fn(*args)
+    return 0 if result is None else int(result)
 
 
 def q1_apply_gpu(x_fp, bits, scale_fp, frac: int):
@@ -206,6 +216,107 @@ def rmsnorm_gpu(x_fp, frac: int, eps: int = 1, gain_q=None):
     rc = _call("bonsai_rmsnorm_gpu", x.ctypes.data, x.shape[0], x.shape[1], int(frac), int(eps),
                ctypes.c_void_p(gain.ctypes.data if gain is not None else 0), y.ctypes.data)
     return y if rc == 0 else None
+
+
+# ---- whole-model entries (names and results of bonsai/src/trinote/infer_int/gpu_native.py:418-595) -------------------
+def monolith_available() -> bool:
+    return gpu_available()
+
+
+def _i64(a) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(a, dtype=np.int64))
+
+
+def buf_upload_i64(arr) -> "int | None":
+    """Upload an int64 array once (gains, rope tables); a buffer handle, or ``None`` when the upload failed."""
+    flat = _i64(arr).ravel()
+    h = int(_call("bonsai_buf_upload_i64", flat.ctypes.data, flat.size))
+    return None if h < 0 else h
+
+
+def attention_prefill_gpu(q_fp, k_fp, v_fp, start: int, frac: int, inv_sqrt_fp: int):
+    """Causal attention of M new tokens: q (H, M, hd) after head norm and rotation, k / v (Hkv, L, hd) with L = start + M.
+    (H, M, hd) int64, or ``None`` when a value left the exact envelope (the caller's host path decides then)."""
+    q, k, v = _i64(q_fp), _i64(k_fp), _i64(v_fp)
+    if q.ndim != 3 or k.ndim != 3 or k.shape != v.shape or k.shape[2] != q.shape[2] or k.shape[1] != int(start) + q.shape[1]:
+        raise ValueError(f"q {q.shape}, k {k.shape}, v {v.shape} do not describe {q.shape[1] if q.ndim == 3 else '?'} tokens after {start}")
+    out = np.empty_like(q)
+    rc = _call("bonsai_attention_prefill_gpu", q.ctypes.data, k.ctypes.data, v.ctypes.data, q.shape[0], k.shape[0], q.shape[2],
+               q.shape[1], k.shape[1], int(start), int(frac), int(inv_sqrt_fp), out.ctypes.data)
+    return out if rc == 0 else None
+
+
+def attention_decode_batched_gpu(q_fp, Kc, Vc, lengths, frac: int, inv_sqrt_fp: int):
+    """One new token of each of B sequences: q (B, H, hd), padded caches (B, Hkv, cap, hd), valid lengths (B,).
+    (B, H, hd) int64 or ``None``."""
+    q, K, V, n = _i64(q_fp), _i64(Kc), _i64(Vc), _i64(lengths)
+    if q.ndim != 3 or K.ndim != 4 or K.shape != V.shape or K.shape[0] != q.shape[0] or K.shape[3] != q.shape[2] or n.shape != (q.shape[0],):
+        raise ValueError(f"q {q.shape}, caches {K.shape} / {V.shape}, lengths {n.shape} do not belong together")
+    out = np.empty_like(q)
+    rc = _call("bonsai_attention_decode_batched_gpu", q.ctypes.data, K.ctypes.data, V.ctypes.data, n.ctypes.data, q.shape[0], q.shape[1],
+               K.shape[1], q.shape[2], K.shape[2], int(frac), int(inv_sqrt_fp), out.ctypes.data)
+    return out if rc == 0 else None
+
+
+_WEIGHT_LISTS, _GAIN_LISTS = ("wq", "wk", "wv", "wo", "w1", "wu", "w2"), ("n1g", "n2g", "qng", "kng")
+
+
+def _handle_lists(w: dict, g: dict, n_layers: int):
+    lists = [_i64(w[name]) for name in _WEIGHT_LISTS] + [_i64(g[name]) for name in _GAIN_LISTS]
+    if any(a.shape != (n_layers,) for a in lists):
+        raise ValueError(f"every per-layer handle list must hold {n_layers} handles")
+    return lists
+
+
+def prefill_forward_gpu(x_embed, dims, w: dict, g: dict, frac: int, eps: int, inv_sqrt_fp: int, *, export_kv: bool = False):
+    """The whole prefill on the device.  ``x_embed`` (T, d) embedded rows; ``dims`` = (T, d, n_layers, H, Hkv, hd, dff);
+    ``w``: per-layer weight-handle lists wq wk wv wo w1 wu w2, the output matrix ``out_head`` and its row count
+    ``out_head_vocab``; ``g``: per-layer buffer-handle lists n1g n2g qng kng and the handles ``finalg``, ``cos_h``,
+    ``sin_h``.  Returns the last position's logits (vocab,), with ``export_kv`` also K and V (n_layers, Hkv, T, hd);
+    ``None`` (or three of them) when a value left the exact envelope."""
+    T, d, n_layers, H, Hkv, hd, dff = (int(v) for v in dims)
+    x = _i64(x_embed)
+    if x.shape != (T, d):
+        raise ValueError(f"x_embed is {x.shape}, dims say ({T}, {d})")
+    lists = _handle_lists(w, g, n_layers)
+    logits = np.empty(int(w["out_head_vocab"]), dtype=np.int64)
+    k = np.empty((n_layers, Hkv, T, hd), dtype=np.int64) if export_kv else None
+    v = np.empty_like(k) if export_kv else None
+    rc = _call("bonsai_prefill_forward_gpu", x.ctypes.data, T, d, n_layers, H, Hkv, hd, dff, int(frac), int(eps), int(inv_sqrt_fp),
+               *[a.ctypes.data for a in lists], int(g["finalg"]), int(w["out_head"]), int(g["cos_h"]), int(g["sin_h"]),
+               logits.ctypes.data, k.ctypes.data if export_kv else None, v.ctypes.data if export_kv else None)
+    if rc != 0:
+        return (None, None, None) if export_kv else None
+    return (logits, k, v) if export_kv else logits
+
+
+def decode_ctx_create(dims, w: dict, g: dict, frac: int, eps: int, inv_sqrt_fp: int, cap: int) -> "int | None":
+    """Device decode context of B sequences with ``cap`` cache rows each; ``dims`` = (B, n_layers, H, Hkv, hd, d, dff, vocab)."""
+    B, n_layers, H, Hkv, hd, d, dff, vocab = (int(v) for v in dims)
+    lists = _handle_lists(w, g, n_layers)
+    h = int(_call("bonsai_decode_ctx_create", B, n_layers, H, Hkv, hd, d, dff, int(cap), vocab, int(frac), int(eps), int(inv_sqrt_fp),
+                  *[a.ctypes.data for a in lists], int(g["finalg"]), int(w["out_head"]), int(g["cos_h"]), int(g["sin_h"])))
+    return None if h < 0 else h
+
+
+def decode_ctx_seed_seq(ctx: int, b: int, k_arr, v_arr) -> bool:
+    """Copy the prefilled K/V rows (n_layers, Hkv, Lb, hd) of sequence ``b`` into the context."""
+    k, v = _i64(k_arr), _i64(v_arr)
+    if k.ndim != 4 or k.shape != v.shape:
+        raise ValueError(f"K {k.shape} and V {v.shape} must both be (n_layers, Hkv, Lb, hd)")
+    return _call("bonsai_decode_ctx_seed_seq", int(ctx), int(b), k.ctypes.data, v.ctypes.data, k.shape[2]) == 0
+
+
+def decode_step(ctx: int, x_in, pos, vocab: int):
+    """One token for every sequence of the context: ``x_in`` (B, d) embedded rows, ``pos`` (B,) positions.  (B, vocab)
+    logits, or ``None`` on overflow or failure."""
+    x, p = _i64(x_in), _i64(pos)
+    out = np.empty((x.shape[0], int(vocab)), dtype=np.int64)
+    return out if _call("bonsai_decode_step", int(ctx), x.ctypes.data, p.ctypes.data, out.ctypes.data) == 0 else None
+
+
+def decode_ctx_free(ctx: int) -> None:
+    _call("bonsai_decode_ctx_free", int(ctx))
 
 
 def apply_dev(handle: int, x, frac: int, out=None):

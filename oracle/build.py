@@ -66,7 +66,8 @@ def install_reference(force: bool = False) -> bool:
     """``baseline/_ref/north-mini-code/{src/nmc, tests/test_qk_*.py}`` = the reference's bridge package and its CUDA
     differential tests, unmodified; ``baseline/_ref/bin/libnmc_qk_cuda.so`` = the reference's own CUDA producer compiled
     for sm_100a (north-mini-code/tools/build_nmc_cuda.sh: nvcc -O3 -arch=<sm> --cudart static -Xcompiler -fPIC -shared),
-    with its CPU kernel ``libnmc_qk.so`` beside it.  Returns False when no reference checkout is mounted."""
+    with its CPU kernel ``libnmc_qk.so`` beside it; and the same for the 1-bit decoder (``baseline/_ref/bonsai``, see below).
+    Returns False when no reference checkout is mounted."""
     import shutil
     if REFERENCE_ROOT is None or not (REFERENCE_ROOT / "north-mini-code" / "src" / "nmc").exists():
         return False
@@ -90,6 +91,26 @@ def install_reference(force: bool = False) -> bool:
     cpu = root / "tools" / "nmc_qk_kernel.c"
     if cpu.exists() and (force or _stale(bin_dir / "libnmc_qk.so", cpu)):
         subprocess.run(["gcc", "-O3", "-fopenmp", "-fPIC", "-shared", str(cpu), "-o", str(bin_dir / "libnmc_qk.so"), "-lm"], check=True)
+    # the 1-bit decoder: the reference's package ``trinote`` and its GPU parity tests, its CPU kernel, and its own CUDA
+    # library compiled for sm_100a under another name (bonsai/tools/build_bonsai_q1_gpu.sh: nvcc -O3 -arch=<sm>
+    # -Xcompiler -fPIC -shared; bonsai/tools/build_bonsai_q1_kernel.sh for the C kernel)
+    broot, bdst = REFERENCE_ROOT / "bonsai", BASELINE_REF / "bonsai"
+    if (broot / "src" / "trinote").exists():
+        if force and bdst.exists():
+            shutil.rmtree(bdst)
+        if not (bdst / "src" / "trinote").exists():
+            shutil.copytree(broot / "src" / "trinote", bdst / "src" / "trinote", ignore=shutil.ignore_patterns("__pycache__"))
+        (bdst / "tests").mkdir(parents=True, exist_ok=True)
+        for name in ("test_bonsai_gpu.py", "test_q1_oracle_subset.py"):
+            if (broot / "tests" / name).exists():
+                shutil.copyfile(broot / "tests" / name, bdst / "tests" / name)
+        q1c, q1cu = broot / "tools" / "bonsai_q1_kernel.c", broot / "tools" / "bonsai_q1_gpu.cu"
+        if q1c.exists() and (force or _stale(bin_dir / "libbonsai_q1_kernel.so", q1c)):
+            subprocess.run(["gcc", "-O3", "-march=x86-64-v2", "-mtune=generic", "-fwrapv", "-fno-strict-overflow", "-fPIC", "-shared",
+                            "-fopenmp", str(q1c), "-o", str(bin_dir / "libbonsai_q1_kernel.so")], check=True)
+        ref_gpu = bin_dir / "reference_libbonsai_q1_gpu.so"
+        if q1cu.exists() and Path(nvcc).exists() and (force or _stale(ref_gpu, q1cu)):
+            subprocess.run([nvcc, "-O3", "-arch=sm_100a", "-Xcompiler", "-fPIC", "-shared", str(q1cu), "-o", str(ref_gpu)], check=True)
     return True
 
 

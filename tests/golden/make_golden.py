@@ -190,8 +190,14 @@ def q1_decode_fixture():
                 layer[key] = np.rint(sc.astype(np.float64) * 65536).astype(np.int64)
     model = rb.BonsaiReferenceModel(artifact=art)
     cache = rb._BonsaiKVCache(2)
-    model._run_layers([3, 90, 41, 7, 66], cache)
+    prompt = [3, 90, 41, 7, 66]
+    x_prompt = model._run_layers(prompt, cache)
     out = {"cos": art["cos_fp"], "sin": art["sin_fp"], "token": np.int64(12), "pos": np.int64(5)}
+    # the prefill itself: embedded prompt rows, the last position's logits (what forward(..., last_only=True) returns;
+    # the K/V rows it leaves are k0/v0, k1/v1 below)
+    out["prompt"] = np.asarray(prompt, dtype=np.int64)
+    out["prompt_embed"] = rb.q1_rows_fp(art["embed_bits"], art["embed_scale_fp"], out["prompt"], 16)
+    out["prefill_logits"] = model._output_linear(rb._rmsnorm(x_prompt[-1:], 16, art["final_norm_gain_fp"]), 16, fast=False)
     for li in range(2):
         out[f"k{li}"], out[f"v{li}"] = cache.k[li].copy(), cache.v[li].copy()
     x = model._run_layers([12], cache)
