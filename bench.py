@@ -75,7 +75,7 @@ def parse():
     ap.add_argument("--cpu-sample-layers", type=int, default=2)
     ap.add_argument("--context", type=int, default=4096, help="KV-cache rows already filled when decoding starts")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep_decode", "q1", "q1_token"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep_decode", "q1", "q1_token", "q1_prefill"],
                     help="decode = the headline line (batch-1 MoE decode); the others print a line of the same "
                          "shape for the prefill, expert-parallel and Q1_0 configurations")
     ap.add_argument("--tokens", type=int, default=0, help="prefill: tokens per step (2048); ep_decode: sequences (64)")
@@ -1043,6 +1043,145 @@ def run_q1_token(args):
                      "frac": (wbytes + kv) / (ms_step * 1e-3) / 1e9 / peak, "traffic": None, "bytes_per_launch": wbytes + kv}}))
 
 
+_Q1_BRIDGE_PROBE = r'''
+import json, sys, time
+import numpy as np
+from trinote.infer_int import gpu_native as g          # the reference's own bridge (baseline/_ref), library from BONSAI_BIN_DIR
+assert g.gpu_available() and g.monolith_available(), "bridge reports the library unusable"
+L, T, reps = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3])
+d, H, Hkv, hd, ffn, vocab, frac = 4096, 32, 8, 128, 12288, int(sys.argv[4]), 16
+rng = np.random.default_rng(2)
+def make(out_f, in_f):
+    bits = rng.integers(0, 256, size=(out_f, in_f // 128, 16), dtype=np.uint8)
+    sc = np.rint(np.abs(rng.standard_normal((out_f, in_f // 128)) * 0.02).astype(np.float16).astype(np.float64) * (1 << frac))
+    return g.q1_register_weight(bits, sc.astype(np.int64))
+gain = lambda n: g.buf_upload_i64(np.rint((np.abs(rng.standard_normal(n)) + 0.5) * (1 << frac)).astype(np.int64))
+shapes = {"wq": (H * hd, d), "wk": (Hkv * hd, d), "wv": (Hkv * hd, d), "wo": (d, H * hd), "w1": (ffn, d), "wu": (ffn, d), "w2": (d, ffn)}
+w = {k: [] for k in shapes}; gg = {k: [] for k in ("n1g", "n2g", "qng", "kng")}
+for li in range(L):
+    for k, (of, inf) in shapes.items():
+        w[k].append(make(of, inf))
+    gg["n1g"].append(gain(d)); gg["n2g"].append(gain(d)); gg["qng"].append(gain(hd)); gg["kng"].append(gain(hd))
+w["out_head"], w["out_head_vocab"] = make(vocab, d), vocab
+inv = 1.0 / (1e6 ** (np.arange(0, hd, 2) / hd)); ang = np.arange(T)[:, None] * inv[None, :]
+gg["finalg"], gg["cos_h"], gg["sin_h"] = gain(d), g.buf_upload_i64(np.rint(np.cos(ang) * (1 << frac)).astype(np.int64)), \
+    g.buf_upload_i64(np.rint(np.sin(ang) * (1 << frac)).astype(np.int64))
+x = np.rint(rng.standard_normal((T, d)) * 0.05 * (1 << frac)).astype(np.int64)
+inv_sqrt = round((1.0 / np.sqrt(hd)) * (1 << frac))
+run = lambda: g.prefill_forward_gpu(x, (T, d, L, H, Hkv, hd, ffn), w, gg, frac, 1, inv_sqrt)
+first = run()
+assert first is not None, "the prefill reported overflow"
+ts = []
+for _ in range(reps):
+    t0 = time.perf_counter(); run(); ts.append(time.perf_counter() - t0)
+import hashlib
+print(json.dumps({"ms_per_call": float(np.median(ts)) * 1e3, "calls": reps, "layers": L, "tokens": T,
+                  "logits_sha256": hashlib.sha256(first.tobytes()).hexdigest(), "library": str(g._load_lib()._name)}))
+'''
+
+
+def q1_bridge_timing(lib_file: Path, layers: int, tokens: int, reps: int, vocab: int):
+    """`bonsai_prefill_forward_gpu` called through the REFERENCE's own bridge module on a seeded model of the 8B layer
+    shape, with `lib_file` as the `libbonsai_q1_gpu.so` it loads.  A child process per library."""
+    import tempfile
+    ref = ROOT / "baseline" / "_ref" / "bonsai"
+    if not (ref / "src" / "trinote").exists() or not lib_file.exists():
+        return {"unavailable": "reference 1-bit bridge or library not installed under baseline/_ref"}
+    with tempfile.TemporaryDirectory() as tmp:
+        os.symlink(lib_file, Path(tmp) / "libbonsai_q1_gpu.so")
+        env = dict(os.environ)
+        env["BONSAI_BIN_DIR"] = tmp
+        env["BONSAI_NOTARY_HOME"] = tmp
+        env["PYTHONPATH"] = str(ref / "src")
+        try:
+            run = subprocess.run([sys.executable, "-c", _Q1_BRIDGE_PROBE, str(layers), str(tokens), str(reps), str(vocab)],
+                                 env=env, capture_output=True, text=True, timeout=900)
+        except subprocess.TimeoutExpired:
+            return {"unavailable": "timed out"}
+    if run.returncode != 0:
+        return {"unavailable": (run.stderr.strip().splitlines() or ["failed"])[-1][:200]}
+    return json.loads(run.stdout.strip().splitlines()[-1])
+
+
+def run_q1_prefill(args):
+    """The 1-bit decoder's prefill through the reference's entry name `bonsai_prefill_forward_gpu` with HOST buffers (what
+    `BonsaiReferenceModel.prefill_logits_gpu_resident` calls): 512 tokens through the layers of the 8B shape, last-row
+    logits out.  Time is wall clock around the call (the entry synchronises; uploads and downloads are inside it).
+    The same call is made through the reference's own bridge, once over the reference's CUDA library compiled for
+    sm_100a and once over this one, on a bounded number of layers; the logits of the two must be the same bytes."""
+    import torch
+
+    from integer_inference_engine_b200 import device, q1_gpu
+    from oracle import model_oracle
+    rank, world, local = _dist_setup()
+    assert world == 1, "the 1-bit prefill line is a single-GPU measurement"
+    L = 36 if args.layers == 48 else args.layers
+    T = args.tokens or 512
+    d, H, Hkv, hd, ffn, vocab, frac = 4096, 32, 8, 128, 12288, 151936, 16
+    rng = np.random.default_rng(2)
+
+    def make(out_f, in_f):
+        bits = rng.integers(0, 256, size=(out_f, in_f // 128, 16), dtype=np.uint8)
+        sc = np.rint(np.abs(rng.standard_normal((out_f, in_f // 128)) * 0.02).astype(np.float16).astype(np.float64) * (1 << frac))
+        return q1_gpu.q1_register_weight(bits, sc.astype(np.int32))
+    gain = lambda n: q1_gpu.buf_upload_i64(np.rint((np.abs(rng.standard_normal(n)) + 0.5) * (1 << frac)).astype(np.int64))
+    shapes = {"wq": (H * hd, d), "wk": (Hkv * hd, d), "wv": (Hkv * hd, d), "wo": (d, H * hd), "w1": (ffn, d), "wu": (ffn, d), "w2": (d, ffn)}
+    w = {k: [] for k in shapes}
+    g = {k: [] for k in ("n1g", "n2g", "qng", "kng")}
+    wbytes = 0
+    for li in range(L):
+        for k, (of, inf) in shapes.items():
+            w[k].append(make(of, inf))
+            wbytes += of * (inf // 128) * 20
+        g["n1g"].append(gain(d)); g["n2g"].append(gain(d)); g["qng"].append(gain(hd)); g["kng"].append(gain(hd))
+    w["out_head"], w["out_head_vocab"] = make(vocab, d), vocab
+    from integer_inference_engine_b200.model import rope_tables
+    cos, sin = rope_tables(T, hd, 1e6, frac)
+    g["finalg"], g["cos_h"], g["sin_h"] = gain(d), q1_gpu.buf_upload_i64(cos), q1_gpu.buf_upload_i64(sin)
+    x = np.rint(rng.standard_normal((T, d)) * 0.05 * (1 << frac)).astype(np.int64)
+    inv_sqrt = round((1.0 / np.sqrt(hd)) * (1 << frac))
+    dims = (T, d, L, H, Hkv, hd, ffn)
+    call = lambda: q1_gpu.prefill_forward_gpu(x, dims, w, g, frac, 1, inv_sqrt)
+    l0 = device.launch_count()
+    first = call()
+    launches = device.launch_count() - l0
+    assert first is not None, "the prefill reported overflow"
+    for _ in range(args.warmup):
+        call()
+    ts = []
+    with ClockSampler(local) as clk:
+        for _ in range(args.steps):
+            t0 = time.perf_counter(); out = call(); ts.append(time.perf_counter() - t0)
+    clocks = clk.summary()
+    assert np.array_equal(out, first)
+    ms = float(np.mean(ts)) * 1e3
+    q1_gpu.q1_free_weights()
+    torch.cuda.empty_cache()
+    # kernel for kernel, through the reference's own bridge, on a bounded model (4 layers, small head)
+    cmpL, cmpV = min(L, 4), 4096
+    ref_lib = ROOT / "baseline" / "_ref" / "bin" / "reference_libbonsai_q1_gpu.so"
+    theirs = q1_bridge_timing(ref_lib, cmpL, T, 3, cmpV)
+    ours = q1_bridge_timing(ROOT / "integer_inference_engine_b200" / "lib" / "libbonsai_q1_gpu.so", cmpL, T, 3, cmpV)
+    same = ("logits_sha256" in theirs and theirs.get("logits_sha256") == ours.get("logits_sha256"))
+    peak, kind = measured_peak_gbs()
+    macs = T * (wbytes // 20) * 128                          # one multiply-add per weight per token
+    print(json.dumps({
+        "metric": "prefill_tok_per_s", "value": T * 1e3 / ms, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int64 modulo 2^64 via int8 digit planes", "data": "synthetic",
+        "config": {"workload": f"config5_q1_prefill: {T} tokens through {L} layers of the 8B 1-bit shape (norms, Q/K/V, per-head norms, "
+                               f"RoPE, causal attention, O, SwiGLU, down) and the head on the last row, through "
+                               f"bonsai_prefill_forward_gpu with host buffers",
+                   "l2": "inputs larger than L2: %d MB of weights per pass" % (wbytes // 2**20),
+                   "same_call_through_the_reference_bridge": {"layers": cmpL, "vocab": cmpV, "reference_cuda_library": theirs,
+                                                              "this_library": ours, "logits_identical": bool(same)}},
+        "clocks": clocks, "gpu_launches": int(launches * args.steps),
+        "e2e": {"value": T * 1e3 / ms, "unit": "tok/s", "h2d_bytes_per_step": int(x.nbytes), "d2h_bytes_per_step": vocab * 8},
+        "roofline": {"bound": "tensor", "kernel": "all kernels of one prefill pass (aggregate)", "unit": "TFLOP/s",
+                     "achieved": 2 * macs * 8 / (ms * 1e-3) / 1e12, "peak": None, "frac": None, "traffic": None,
+                     "note": "int8 digit-plane operations (8 planes per activation); the int8 peak is measured by the default workload"}}))
+
+
 if __name__ == "__main__":
     a = parse()
     if a.impl == "reference":
@@ -1055,5 +1194,7 @@ if __name__ == "__main__":
         run_q1(a)
     elif a.workload == "q1_token":
         run_q1_token(a)
+    elif a.workload == "q1_prefill":
+        run_q1_prefill(a)
     else:
         run_ours(a)
