@@ -426,7 +426,8 @@ __device__ __noinline__ void norm_planes(const DecodeArgs &a, Shared *sh, const 
         }
         if (m > (1ULL << 57)) sh->bad = 1;                 // keeps the 128-bit sum of squares exact
         u128 mean;
-        if ((total >> 64) == 0) mean = (u128)((unsigned long long)total / (unsigned long long)a.d);
+        if ((a.d & (a.d - 1)) == 0) mean = total >> (31 - __clz(a.d));
+        else if ((total >> 64) == 0) mean = (u128)((unsigned long long)total / (unsigned long long)a.d);
         else mean = total / (u128)(unsigned long long)a.d;
         const u128 rms = isqrt128(mean + a.eps);
         if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) sh->bad = 1;

@@ -7,13 +7,15 @@ namespace iie {
 
 __device__ __forceinline__ unsigned long long uabs64(int64_t v) { return v < 0 ? (0ULL - (unsigned long long)v) : (unsigned long long)v; }
 
+// floor(sqrt(v)).  Below 2^104 a double estimate is off by at most a few units and is fixed up with exact 128-bit
+// products (the usual case: the mean square of a residual row is far below that); beyond it the bitwise root.
 __device__ inline u128 isqrt128(u128 v) {
-    if (v < ((u128)1 << 62)) {             // common case: exact from a double estimate plus a fix-up
-        const unsigned long long x = (unsigned long long)v;
-        unsigned long long r = (unsigned long long)sqrt((double)x);
-        while (r * r > x) r--;
-        while ((r + 1) * (r + 1) <= x) r++;
-        return r;
+    if (v < ((u128)1 << 104)) {
+        const double dv = (double)(unsigned long long)(v >> 64) * 18446744073709551616.0 + (double)(unsigned long long)v;
+        unsigned long long r = (unsigned long long)sqrt(dv);
+        for (int it = 0; it < 8 && (u128)r * r > v; it++) r--;
+        for (int it = 0; it < 8 && (u128)(r + 1) * (r + 1) <= v; it++) r++;
+        if ((u128)r * r <= v && (u128)(r + 1) * (r + 1) > v) return r;
     }
     u128 res = 0, bit = (u128)1 << 126;
     while (bit > v) bit >>= 2;

@@ -109,7 +109,8 @@ __global__ void __launch_bounds__(RT_THREADS) route_kernel(const RouteArgs a) {
                 }
                 if (m > (1ULL << 57)) s_bad = 1;                 // keeps the 128-bit sum of squares exact
                 u128 mean;
-                if ((total >> 64) == 0) mean = (u128)((unsigned long long)total / (unsigned long long)d);
+                if ((d & (d - 1)) == 0) mean = total >> (31 - __clz(d));        // widths are powers of two in practice
+                else if ((total >> 64) == 0) mean = (u128)((unsigned long long)total / (unsigned long long)d);
                 else mean = total / (u128)(unsigned long long)d;
                 const u128 rms = isqrt128(mean + a.eps);
                 if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) s_bad = 1;
