@@ -1530,6 +1530,84 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     return 0;
 }
 
+// One whole parallel decoder block for one token, x += attention(h) Wo^T + moe(h) with h = rmsnorm(x, gain), as five
+// launches chained by programmatic dependent launch:
+//   front     every CTA normalises x and takes its share of the rows of [Wq|Wk|Wv] and of the router (one kernel
+//             instead of the routing kernel followed by the fused QKV product);
+//   attention cooperative single-token attention (K/V append, scores, softmax, p.V);
+//   O         product accumulated into x;
+//   gate/up   every CTA ranks the router logits itself (top-k, sigmoid gates), so its expert weights are requested before
+//             the O product has finished;
+//   down      the same ranking, weights requested early, gate-weighted rows accumulated into x.
+// Same bytes as iie_moe_block_dev followed by iie_attn_block_dev.  Status 5: this shape has no fused form (dense router,
+// router and Wqkv of different block formats, more than 64 selected experts) and the two entries must be used.
+extern "C" int iie_block_dev(long long layer, long long gain_h, long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t *kcache_dev,
+                             int32_t *vcache_dev, long long pos, const int *pos_dev, long long window, const int64_t *cos_dev,
+                             const int64_t *sin_dev, int rope, int n_heads, int n_kv, int head_dim, long long cache_rows, int fa, int fw,
+                             unsigned long long eps, long long inv_sqrt, int *ids_dev, int64_t *gates_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || layer < 0 || (size_t)layer >= g_layers.size() || !g_layers[layer].live || !valid_q(wqkv_h) || !valid_q(wo_h) || !x_dev ||
+        !kcache_dev || !vcache_dev || n_heads <= 0 || n_kv <= 0 || head_dim <= 0 || cache_rows <= 0 || fa < 1 || fa > 29 ||
+        fw < 0 || fw > 62) return 1;
+    const MoeLayer &L = g_layers[layer];
+    if (L.router < 0) return 1;
+    const Weight &r = g_w[L.router], &wqkv = g_w[wqkv_h], &wo = g_w[wo_h];
+    const long long d = L.d_model, qd = (long long)n_heads * head_dim, kd = (long long)n_kv * head_dim;
+    const int E = L.n_experts, k = L.top_k;
+    if (wqkv.nb * 256 != d || wqkv.out_f != qd + 2 * kd || wo.nb * 256 != qd || wo.out_f != d) return 1;
+    if (r.qtype == QT_I64 || r.qtype != wqkv.qtype || k > 64 || E > 1024 || d > 4096 || g_stage_mask != 0) return 5;
+    const int64_t *gain = nullptr;
+    if (gain_h >= 0) {
+        if (!valid_i64(gain_h) || g_w[gain_h].out_f != 1 || g_w[gain_h].nb != d) return 1;
+        gain = (const int64_t *)g_w[gain_h].d;
+    }
+    if (!fast_envelope(L.gate_q, d / 256, L.maxd_gate, L.maxdmin_gate, fw) || !fast_envelope(L.down_q, L.e_ffn / 256, L.maxd_down, L.maxdmin_down, fw) ||
+        !fast_envelope(wqkv.qtype, wqkv.nb, wqkv.maxd, wqkv.maxdmin, fw) || !fast_envelope(wo.qtype, wo.nb, wo.maxd, wo.maxdmin, fw) ||
+        !fast_envelope(r.qtype, r.nb, r.maxd, r.maxdmin, fw)) return 3;
+    cudaStream_t s = (cudaStream_t)stream;
+    int8_t *hl = (int8_t *)ensure(R_XL, (size_t)8 * d);
+    int64_t *lg = (int64_t *)ensure(R_LOGITS, (size_t)E * 8);
+    int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)k * 8 * L.e_ffn);
+    int64_t *qkv = (int64_t *)ensure(R_TMP0, (size_t)(qd + 2 * kd) * 8);
+    int8_t *al = (int8_t *)ensure(R_TMP1, (size_t)8 * qd);
+    if (!hl || !lg || !gul || !qkv || !al) return 1;
+    g_hl_d = d;
+    StreamArgs f = {};
+    f.wa = wqkv.cell; f.wb = r.cell; f.n_sel = 1; f.out_f = wqkv.out_f; f.out_f_b = E; f.n_blocks = d / 256; f.fw = fw; f.fa = fa;
+    f.x = x_dev; f.gain = gain; f.eps = eps; f.out = qkv; f.out_b = lg; f.hl_out = hl; f.h_nl_out = g_cells; f.gu_nl_zero = g_cells + 1;
+    f.flags = g_flags; f.pdl = g_pdl; f.early_weights = g_pdl;
+    f.fast = small_scales(std::max(wqkv.maxd, r.maxd), std::max(wqkv.maxdmin, r.maxdmin), fw);
+    if (launch_stream(wqkv.qtype, MODE_FRONT, f, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    AttnArgs a = {};
+    a.q = qkv; a.k = qkv + qd; a.v = qkv + qd + kd; a.kcache = kcache_dev; a.vcache = vcache_dev; a.pos = pos;
+    a.pos_dev = pos_dev; a.window = window; a.lo = 0; a.Lmax = cache_rows;
+    a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim;
+    attn_consts(a, fa, inv_sqrt);
+    if (!attn_scratch(a, s)) return 1;
+    int *nl_cell = g_cells + 8 + g_attn_parity;
+    g_attn_parity ^= 1;
+    a.out = nullptr; a.out_limbs = al; a.out_nl = nl_cell; a.flags = g_flags; a.pdl = g_pdl;
+    if (launch_attn_decode(a, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    StreamArgs oa = {};
+    oa.wa = wo.cell; oa.wb = wo.cell; oa.n_sel = 1; oa.out_f = wo.out_f; oa.n_blocks = wo.nb; oa.fw = fw; oa.fa = fa;
+    oa.xl = al; oa.x_per_sel = 1; oa.x_nl = nl_cell; oa.out = x_dev; oa.gates = g_pow2 + fa; oa.flags = g_flags;
+    oa.fast = small_scales(wo.maxd, wo.maxdmin, fw); oa.pdl = g_pdl; oa.early_weights = g_pdl;
+    if (launch_stream(wo.qtype, MODE_DOWN, oa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    StreamArgs ga = {};
+    ga.wa = L.tabs; ga.wb = L.tabs + E; ga.n_sel = k; ga.out_f = L.e_ffn; ga.n_blocks = d / 256; ga.fw = fw; ga.fa = fa;
+    ga.logits = lg; ga.n_experts = E; ga.ids_out = ids_dev; ga.gates_out = gates_dev;
+    ga.xl = hl; ga.x_per_sel = 0; ga.x_nl = g_cells; ga.out = nullptr; ga.out_limbs = gul; ga.out_nl = g_cells + 1; ga.flags = g_flags;
+    ga.fast = small_scales(L.maxd_gate, L.maxdmin_gate, fw); ga.pdl = g_pdl; ga.early_weights = g_pdl;   // logits final two launches ago
+    if (launch_stream(L.gate_q, MODE_GATEUP, ga, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    StreamArgs da = {};
+    da.wa = L.tabs + 2 * E; da.wb = da.wa; da.n_sel = k; da.out_f = d; da.n_blocks = L.e_ffn / 256; da.fw = fw; da.fa = fa;
+    da.logits = lg; da.n_experts = E;
+    da.xl = gul; da.x_per_sel = 1; da.x_nl = g_cells + 1; da.out = x_dev; da.flags = g_flags;
+    da.fast = small_scales(L.maxd_down, L.maxdmin_down, fw); da.pdl = g_pdl; da.early_weights = g_pdl;
+    if (launch_stream(L.down_q, MODE_DOWN, da, s) != cudaSuccess) { cudaGetLastError(); return 1; }
+    return 0;
+}
+
 extern "C" int iie_embed_dev(long long h, const int *token_dev, long long token, int frac, int64_t *out_dev, void *stream) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (!init() || !valid_q(h) || !out_dev || frac < 0 || frac > 40) return 1;

@@ -9,7 +9,7 @@ namespace iie {
 extern unsigned long long g_launches;
 inline void note_launch(unsigned long long n = 1) { __atomic_fetch_add(&g_launches, n, __ATOMIC_RELAXED); }
 
-enum SkinnyMode { MODE_LINEAR = 0, MODE_GATEUP = 1, MODE_DOWN = 2 };
+enum SkinnyMode { MODE_LINEAR = 0, MODE_GATEUP = 1, MODE_DOWN = 2, MODE_FRONT = 3 };
 
 // Arguments of the streamed ("skinny") fused-dequant product.  Work is organised in groups: group g
 // uses weight matrix `expert = grp_expert ? grp_expert[g] : g` and owns the activation rows
@@ -59,6 +59,24 @@ struct StreamArgs {
     int *out_nl;                   // GATEUP: atomicMax of the limbs gu needs
     const int64_t *gates;          // DOWN: [n_sel]
     int *flags;                    // bit 0 limb envelope, bit 3 a copy never arrived
+    // Top-k prologue (GATEUP / DOWN, logits != nullptr): every CTA ranks the n_experts router logits itself (lowest index
+    // first among equals) and the k best select the matrices of wa / wb; their sigmoid gates weight the DOWN epilogue.
+    // `sel`, `sel_wa` and `gates` are then not read.  CTA 0 also stores ids / gates where the pointers are given.
+    const int64_t *logits;
+    int n_experts;
+    int *ids_out;
+    int64_t *gates_out;
+    // MODE_FRONT: the front of a decoder block in one launch.  Every CTA normalises the row x (RMSNorm with `gain`,
+    // digit planes in shared memory), then the CTAs share the rows of two matrices with that one activation:
+    // wa[0] (out_f rows -> out) and wb[0] (out_f_b rows -> out_b), e.g. the stacked Q/K/V matrix and the router.
+    // CTA 0 also leaves the planes and their digit count for the kernels that follow, and zeroes *gu_nl_zero.
+    const int64_t *x, *gain;
+    unsigned long long eps;
+    long long out_f_b;
+    int64_t *out_b;
+    int8_t *hl_out;
+    int *h_nl_out, *gu_nl_zero;
+    int tiles_b;                   // filled in by the launcher
 };
 cudaError_t launch_stream(int qtype, int mode, const StreamArgs &a, cudaStream_t s);
 

@@ -19,12 +19,15 @@
 #include "kernels.h"
 #include "layout.cuh"
 #include "mma_items.cuh"
+#include "norm.cuh"
 
 namespace iie {
 
 namespace {
 
 constexpr int NWARPS = 16;
+constexpr int FR_PAD = 32;          // padding of a digit plane in shared memory (bytes): the eight planes start on different banks
+constexpr int SK_MAXK = 64, SK_MAXE = 1024;   // top-k prologue: largest k and number of logits
 
 constexpr unsigned WAIT_LIMIT = 1u << 22;   // mbarrier polls before a wait gives up and raises flag bit 3
 
@@ -66,33 +69,70 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
     uint64_t *bars = reinterpret_cast<uint64_t *>(red + (size_t)tpc * 128);
     int *done = reinterpret_cast<int *>(bars + tpc);             // blocks of each tile already accumulated
     int *t_sel = done + tpc, *t_pos = t_sel + tpc;               // tile -> (selected matrix slot, tile inside it)
+    // MODE_FRONT only: digit planes of the normalised row [8][K + pad], the staged row and gain
+    const int pstride = (int)K + FR_PAD;
+    int8_t *planes = reinterpret_cast<int8_t *>((reinterpret_cast<uintptr_t>(t_pos + tpc) + 15) & ~(uintptr_t)15);
+    int64_t *xs = reinterpret_cast<int64_t *>(planes + (size_t)8 * pstride);
+    int64_t *gs = xs + K;
     __shared__ int s_timeout;
+    __shared__ int s_ids[SK_MAXK];                               // top-k prologue: selected experts and their gates
+    __shared__ long long s_gates[SK_MAXK];
+    __shared__ int64_t s_lg[SK_MAXE];
+    __shared__ unsigned long long s_lo[NWARPS], s_hi[NWARPS], s_mx[NWARPS], s_gmx[NWARPS];
+    __shared__ unsigned long long s_rms, s_inv, s_gm;
+    __shared__ int s_bad, s_nl;
 
-    const int n_tiles = a.n_sel * a.tiles_per_expert;
+    const int n_tiles = MODE == MODE_FRONT ? a.tiles_per_expert + a.tiles_b : a.n_sel * a.tiles_per_expert;
     const int tile0 = (int)blockIdx.x * tpc;
     const int my_tiles = min(tpc, n_tiles - tile0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n_ht = (int)((a.out_f + 7) >> 3);
+    const int n_ht = (int)((a.out_f + 7) >> 3), n_ht_b = (int)((a.out_f_b + 7) >> 3);
+    const bool topk = MODE != MODE_FRONT && MODE != MODE_LINEAR && a.logits != nullptr;
 
     for (int i = threadIdx.x; i < my_tiles * 128; i += blockDim.x) red[i] = 0ULL;
     for (int i = threadIdx.x; i < my_tiles; i += blockDim.x) {
         done[i] = 0;
-        const int tau = tile0 + i, sl = tau / a.tiles_per_expert;
-        t_sel[i] = sl; t_pos[i] = tau - sl * a.tiles_per_expert;
+        const int tau = tile0 + i;
+        int sl, ps;
+        if (MODE == MODE_FRONT) { sl = tau < a.tiles_per_expert ? 0 : 1; ps = tau - sl * a.tiles_per_expert; }
+        else { sl = tau / a.tiles_per_expert; ps = tau - sl * a.tiles_per_expert; }
+        t_sel[i] = sl; t_pos[i] = ps;
         mbar_init(&bars[i], 1);
     }
-    if (threadIdx.x == 0) s_timeout = 0;
+    if (threadIdx.x == 0) { s_timeout = 0; s_bad = 0; s_nl = 1; }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
+    // Top-k prologue.  With early_weights the logits were final before the previous kernel started (the caller's promise,
+    // as for the pointer arrays), so the ranking and the weight requests both happen before the dependency wait.
+    auto rank_topk = [&]() {
+        const int n = a.n_experts;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) s_lg[i] = a.logits[i];
+        __syncthreads();
+        for (int e = threadIdx.x; e < n; e += blockDim.x) {
+            const int64_t v = s_lg[e];
+            int rank = 0;
+            for (int j = 0; j < n; j++) { const int64_t w = s_lg[j]; rank += (w > v) || (w == v && j < e); }
+            if (rank < a.n_sel) {
+                const long long gt = sigmoid_fixed_c(v, a.fa, a.sig_log2e, a.sig_clip);
+                s_ids[rank] = e; s_gates[rank] = gt;
+                if (blockIdx.x == 0) { if (a.ids_out) a.ids_out[rank] = e; if (a.gates_out) a.gates_out[rank] = gt; }
+            }
+        }
+        __syncthreads();
+    };
+    if (topk && a.pdl && a.early_weights) rank_topk();
     // Programmatic dependent launch: everything above touched only this CTA's shared memory.  When the
     // selected-expert pointers were final before the previous kernel started (early_weights), the weight
     // copies are requested before waiting for that kernel, so they overlap its execution.
     if (a.pdl && !a.early_weights) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
+    if (topk && !(a.pdl && a.early_weights)) rank_topk();
     // one lane per tile resolves its matrix pointer and asks the copy engine for the whole tile
     for (int i = threadIdx.x; i < my_tiles; i += blockDim.x) {
         const int s = t_sel[i], p = t_pos[i];
         const uint8_t *pa, *pb = nullptr;
-        if (a.sel_wa) { pa = a.sel_wa[s]; if (MODE == MODE_GATEUP) pb = a.sel_wb[s]; }
+        if (MODE == MODE_FRONT) pa = s == 0 ? a.wa[0] : a.wb[0];
+        else if (topk) { const int e = s_ids[s]; pa = a.wa[e]; if (MODE == MODE_GATEUP) pb = a.wb[e]; }
+        else if (a.sel_wa) { pa = a.sel_wa[s]; if (MODE == MODE_GATEUP) pb = a.sel_wb[s]; }
         else { const int e = a.sel ? a.sel[s] : s; pa = a.wa[e]; if (MODE == MODE_GATEUP) pb = a.wb[e]; }
         uint8_t *dst = wbuf + (size_t)i * tile_bytes;
         if (MODE == MODE_GATEUP) {
@@ -100,13 +140,106 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
             bulk_g2s(dst, pa + (size_t)p * nb * HTB, (uint32_t)(nb * HTB), &bars[i]);
             bulk_g2s(dst + nb * HTB, pb + (size_t)p * nb * HTB, (uint32_t)(nb * HTB), &bars[i]);
         } else {
-            const int units = (2 * p + 1 < n_ht) ? 2 : 1;                // an odd last half-tile stands alone
+            const int units = (2 * p + 1 < ((MODE == MODE_FRONT && s == 1) ? n_ht_b : n_ht)) ? 2 : 1;   // an odd last half-tile stands alone
             mbar_expect_tx(&bars[i], (uint32_t)(units * nb * HTB));
             bulk_g2s(dst, pa + (size_t)(2 * p) * nb * HTB, (uint32_t)(units * nb * HTB), &bars[i]);
         }
     }
+    unsigned long long gmx = 0;
+    if (MODE == MODE_FRONT && a.gain)                              // the gain is immutable: staged before the dependency wait
+        for (int i = threadIdx.x * 2; i < (int)K; i += blockDim.x * 2) {
+            const longlong2 gv = *reinterpret_cast<const longlong2 *>(a.gain + i);
+            *reinterpret_cast<longlong2 *>(gs + i) = gv;
+            const unsigned long long g0 = uabs64(gv.x), g1 = uabs64(gv.y);
+            gmx = g0 > gmx ? g0 : gmx; gmx = g1 > gmx ? g1 : gmx;
+        }
     if (a.pdl && a.early_weights) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
-    const bool half = a.x_nl ? (*a.x_nl <= 4) : false;
+    if (MODE == MODE_FRONT) {
+        // ---- RMSNorm of the row and its digit planes, in every CTA (arithmetic of route.cu) ----------------------------
+        u128 ssq = 0; unsigned long long mx = 0;
+        for (int i = threadIdx.x * 2; i < (int)K; i += blockDim.x * 2) {
+            const longlong2 xv = *reinterpret_cast<const longlong2 *>(a.x + i);
+            *reinterpret_cast<longlong2 *>(xs + i) = xv;
+            const unsigned long long v0 = uabs64(xv.x), v1 = uabs64(xv.y);
+            ssq += (u128)v0 * v0; ssq += (u128)v1 * v1;
+            mx = v0 > mx ? v0 : mx; mx = v1 > mx ? v1 : mx;
+        }
+        unsigned long long lo = (unsigned long long)ssq, hi = (unsigned long long)(ssq >> 64);
+#pragma unroll
+        for (int sft = 16; sft > 0; sft >>= 1) {
+            const unsigned long long lo2 = __shfl_xor_sync(0xffffffffu, lo, sft), hi2 = __shfl_xor_sync(0xffffffffu, hi, sft);
+            const u128 sum = (((u128)hi << 64) | lo) + (((u128)hi2 << 64) | lo2);
+            lo = (unsigned long long)sum; hi = (unsigned long long)(sum >> 64);
+            const unsigned long long m2 = __shfl_xor_sync(0xffffffffu, mx, sft), g2 = __shfl_xor_sync(0xffffffffu, gmx, sft);
+            mx = m2 > mx ? m2 : mx; gmx = g2 > gmx ? g2 : gmx;
+        }
+        if (lane == 0) { s_lo[warp] = lo; s_hi[warp] = hi; s_mx[warp] = mx; s_gmx[warp] = gmx; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            u128 total = 0; unsigned long long m = 0, gm = 0;
+            for (int i = 0; i < NWARPS; i++) {
+                total += ((u128)s_hi[i] << 64) | s_lo[i];
+                m = s_mx[i] > m ? s_mx[i] : m; gm = s_gmx[i] > gm ? s_gmx[i] : gm;
+            }
+            int bad = m > (1ULL << 57) ? 1 : 0;                  // keeps the 128-bit sum of squares exact
+            const int d = (int)K;
+            u128 mean;
+            if ((d & (d - 1)) == 0) mean = total >> (31 - __clz(d));
+            else if ((total >> 64) == 0) mean = (u128)((unsigned long long)total / (unsigned long long)d);
+            else mean = total / (u128)(unsigned long long)d;
+            const u128 rms = isqrt128(mean + a.eps);
+            if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) bad = 1;
+            s_rms = (unsigned long long)rms; s_gm = gm; s_bad = bad;
+            s_inv = rms != 0 ? 0xFFFFFFFFFFFFFFFFULL / (unsigned long long)rms : 0;
+        }
+        __syncthreads();
+        const unsigned long long rms = s_rms, inv = s_inv, gm = s_gm;
+        const bool dead = s_bad != 0;                             // not normalisable exactly: flag raised, zero planes, the launch still drains its copies
+        bool bad = false, over = false;
+        int nl = 1;
+        for (int i = threadIdx.x * 4; i < (int)K; i += blockDim.x * 4) {
+            uint32_t pw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int64_t xv = xs[i + e];
+                int64_t y = xv;
+                if (dead) y = 0;
+                else if (a.gain) {
+                    if (uabs64(xv) < (1ULL << (62 - a.fa)) && rms < (1ULL << 62)) y = floor_div_recip(xv * ((long long)1 << a.fa), rms, inv);
+                    else {
+                        const i128 num = (i128)xv * ((i128)1 << a.fa);
+                        i128 q = num / (i128)rms;
+                        if (num < 0 && q * (i128)rms != num) q -= 1;
+                        if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; q = 0; }
+                        y = (int64_t)q;
+                    }
+                    if ((u128)uabs64(y) * gm > (u128)INT64_MAX) bad = true;      // the oracle refuses such a gain product
+                    y = mul_shift(y, gs[i + e], a.fa);
+                }
+                bool ok;
+                const uint64_t dg = balanced_digits8(y, ok);
+                over |= !ok;
+                nl = max(nl, digits_used(dg));
+#pragma unroll
+                for (int l = 0; l < 8; l++) pw[l] |= (uint32_t)((dg >> (8 * l)) & 0xFF) << (8 * e);
+            }
+#pragma unroll
+            for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(planes + l * pstride + i) = pw[l];
+            if (blockIdx.x == 0 && a.hl_out) {
+#pragma unroll
+                for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(a.hl_out + (long long)l * K + i) = pw[l];
+            }
+        }
+        if ((bad || dead) && lane == 0) atomicOr(a.flags, 2);
+        if (over) atomicOr(a.flags, 1);
+        nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 16)); nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 8));
+        nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 4));  nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 2));
+        nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 1));
+        if (lane == 0) atomicMax(&s_nl, nl);
+        __syncthreads();
+        if (blockIdx.x == 0 && threadIdx.x == 0) { if (a.h_nl_out) *a.h_nl_out = s_nl; if (a.gu_nl_zero) *a.gu_nl_zero = 0; }
+    }
+    const bool half = MODE == MODE_FRONT ? (s_nl <= 4) : (a.x_nl ? (*a.x_nl <= 4) : false);
 
     // items (tile, block) are dealt round-robin to the warps; indices advance without divisions
     const int n_items = my_tiles * nb;
@@ -119,15 +252,16 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
     int bcur = -1;
     for (int it = warp; it < n_items; it += NWARPS) {
         const int s = t_sel[ti], p = t_pos[ti];
-        const int8_t *xp = a.xl + (a.x_per_sel ? (long long)s * 8 * K : 0);
+        const int8_t *xp = MODE == MODE_FRONT ? planes : a.xl + (a.x_per_sel ? (long long)s * 8 * K : 0);
         if (xp != xcur || b != bcur) {                        // activation fragments: reused while (vector, block) repeat
-            load_bfrag<QT, true>(xp + xoff + (long long)b * 256, t, bf);
+            if (MODE == MODE_FRONT) load_bfrag<QT, false>(planes + col_limb(g) * pstride + b * 256, t, bf);
+            else load_bfrag<QT, true>(xp + xoff + (long long)b * 256, t, bf);
             xcur = xp; bcur = b;
         }
         const uint8_t *ua = wbuf + (size_t)ti * tile_bytes + (size_t)b * HTB;
         const uint8_t *ub;
         if (MODE == MODE_GATEUP) ub = ua + (size_t)nb * HTB;
-        else ub = (2 * p + 1 < n_ht) ? ua + (size_t)nb * HTB : ua;
+        else ub = (2 * p + 1 < ((MODE == MODE_FRONT && s == 1) ? n_ht_b : n_ht)) ? ua + (size_t)nb * HTB : ua;
         const int ti_now = ti;
         b += step_b; ti += step_t;
         if (b >= nb) { b -= nb; ti++; }
@@ -152,14 +286,15 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
         const volatile unsigned long long *rv = r;
         if (lane < 16) {
             const long long row = (long long)p * 16 + lane;
-            if (row < a.out_f) {
+            if (row < ((MODE == MODE_FRONT && s == 1) ? a.out_f_b : a.out_f)) {
                 unsigned long long cc[8];
 #pragma unroll
                 for (int c = 0; c < 8; c++) cc[c] = rv[lane * 8 + c];
                 const int64_t y = recombine_cols(cc, a.fw);
-                if (MODE == MODE_LINEAR) a.out[(long long)s * a.out_f + row] = y;
+                if (MODE == MODE_FRONT) (s == 0 ? a.out : a.out_b)[row] = y;
+                else if (MODE == MODE_LINEAR) a.out[(long long)s * a.out_f + row] = y;
                 else atomicAdd(reinterpret_cast<unsigned long long *>(a.out + row),
-                               (unsigned long long)mul_shift(y, a.gates[s], a.fa));
+                               (unsigned long long)mul_shift(y, topk ? s_gates[s] : a.gates[s], a.fa));
             }
         }
     }
@@ -199,19 +334,23 @@ cudaError_t launch_stream_t(const StreamArgs &a_in, cudaStream_t s) {
     constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
     const long long n_ht = (a.out_f + 7) >> 3;
     a.tiles_per_expert = (int)(MODE == MODE_GATEUP ? n_ht : (n_ht + 1) / 2);
-    const long long n_tiles = (long long)a.n_sel * a.tiles_per_expert;
+    a.tiles_b = MODE == MODE_FRONT ? (int)((((a.out_f_b + 7) >> 3) + 1) / 2) : 0;
+    const long long n_tiles = MODE == MODE_FRONT ? (long long)a.tiles_per_expert + a.tiles_b : (long long)a.n_sel * a.tiles_per_expert;
     const size_t tile_bytes = (size_t)2 * a.n_blocks * HTB, per_tile = tile_bytes + 128 * 8 + 8 + 12;
-    const int max_tpc = (int)((200 * 1024) / per_tile);
+    const size_t front_bytes = MODE == MODE_FRONT ? (size_t)8 * (a.n_blocks * 256 + FR_PAD) + (size_t)16 * a.n_blocks * 256 + 16 : 0;
+    if (MODE == MODE_FRONT && (!a.x || !a.out || !a.out_b || a.out_f_b <= 0 || a.n_blocks * 256 > 8192)) return cudaErrorInvalidValue;
+    if (MODE != MODE_FRONT && a.logits && (a.n_experts <= 0 || a.n_experts > SK_MAXE || a.n_sel > SK_MAXK || a.n_sel > a.n_experts)) return cudaErrorInvalidValue;
+    const int max_tpc = (int)((200 * 1024 - front_bytes) / per_tile);
     if (max_tpc < 1) return cudaErrorInvalidConfiguration;
     int tpc = (int)((n_tiles + 147) / 148);                      // one wave when everything fits
     if (tpc > max_tpc) tpc = max_tpc;                            // several waves: one CTA per SM (registers), so the longest run that fits
     a.tiles_per_cta = tpc;
     a.sig_log2e = sigmoid_log2e(a.fa); a.sig_clip = sigmoid_clip(a.fa);
     const unsigned grid = (unsigned)((n_tiles + tpc - 1) / tpc);
-    const size_t smem = (size_t)tpc * per_tile + 64;
+    const size_t smem = (size_t)tpc * per_tile + 64 + front_bytes;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(stream_kernel<QT, MODE, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(stream_kernel<QT, MODE, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 214 * 1024);
         if (e != cudaSuccess) return e;
         configured = true;
     }
@@ -238,11 +377,13 @@ cudaError_t launch_stream(int qtype, int mode, const StreamArgs &a, cudaStream_t
     if (qtype == QT_Q4K) {
         if (mode == MODE_LINEAR) return launch_stream_f<QT_Q4K, MODE_LINEAR>(a, s);
         if (mode == MODE_GATEUP) return launch_stream_f<QT_Q4K, MODE_GATEUP>(a, s);
+        if (mode == MODE_FRONT) return launch_stream_f<QT_Q4K, MODE_FRONT>(a, s);
         return launch_stream_f<QT_Q4K, MODE_DOWN>(a, s);
     }
     if (qtype == QT_Q6K) {
         if (mode == MODE_LINEAR) return launch_stream_f<QT_Q6K, MODE_LINEAR>(a, s);
         if (mode == MODE_GATEUP) return launch_stream_f<QT_Q6K, MODE_GATEUP>(a, s);
+        if (mode == MODE_FRONT) return launch_stream_f<QT_Q6K, MODE_FRONT>(a, s);
         return launch_stream_f<QT_Q6K, MODE_DOWN>(a, s);
     }
     return cudaErrorInvalidValue;

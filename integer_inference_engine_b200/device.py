@@ -181,6 +181,34 @@ def attention_block(wqkv: int, wo: int, x: torch.Tensor, kcache: torch.Tensor, v
         raise CudaContextError(f"attention block failed with status {rc}")
 
 
+class NoFusedBlock(RuntimeError):
+    """The shape has no five-launch block form; use ``MoELayer.block`` followed by :func:`attention_block`."""
+
+
+def decoder_block(layer: "MoELayer", gain_handle: int, wqkv: int, wo: int, x: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                  pos: int, n_heads: int, n_kv: int, head_dim: int, fa: int = 16, fw: int = 24, eps: int = 1, window: int = 0,
+                  cos: torch.Tensor | None = None, sin: torch.Tensor | None = None, rope: int = 0, inv_sqrt: int | None = None,
+                  pos_dev: torch.Tensor | None = None, ids: torch.Tensor | None = None, gates: torch.Tensor | None = None) -> None:
+    """One whole parallel decoder block on the row ``x`` [1, d_model], in place: ``x += attention(h) Wo^T + moe(h)`` with
+    ``h = rmsnorm(x, gain)`` (``iie_block_dev``: five launches).  ``ids`` (int32 [k]) / ``gates`` (int64 [k]) receive the routing
+    when given.  Raises :class:`NoFusedBlock` for shapes without this form."""
+    lib = qk_cuda._lib()
+    assert x.is_cuda and x.dtype == torch.int64 and x.is_contiguous()
+    assert kcache.dtype == torch.int32 and vcache.dtype == torch.int32 and kcache.is_contiguous() and vcache.is_contiguous()
+    if inv_sqrt is None:
+        inv_sqrt = int(round((1.0 / head_dim ** 0.5) * (1 << fa)))
+    with _CUDA_LOCK:
+        rc = lib.iie_block_dev(int(layer.handle), int(gain_handle), int(wqkv), int(wo), x.data_ptr(), kcache.data_ptr(), vcache.data_ptr(),
+                               int(pos), pos_dev.data_ptr() if pos_dev is not None else None, int(window or 0),
+                               cos.data_ptr() if rope else None, sin.data_ptr() if rope else None, int(rope), n_heads, n_kv, head_dim,
+                               int(kcache.shape[1]), int(fa), int(fw), int(eps), int(inv_sqrt),
+                               ids.data_ptr() if ids is not None else None, gates.data_ptr() if gates is not None else None, _stream_ptr())
+    if rc == 5:
+        raise NoFusedBlock("this block shape has no fused form")
+    if rc != 0:
+        raise CudaContextError(f"decoder block failed with status {rc}")
+
+
 class DecoderKernel:
     """All blocks of a decoder as one launch per token (``iie_decoder_*``).  ``layers`` = sequence of dicts with ``gain``
     (dense int64 handle), ``moe`` (:class:`MoELayer` with its router), ``wqkv``, ``wo`` (handles), ``k``, ``v`` (int32 CUDA

@@ -55,6 +55,9 @@ class Decoder:
         self.x, self.hn, self.logits = z(d_model), z(d_model), z(vocab)
         self._graph = None
         self.dense_router = dense_router                 # routers are dense int64 matrices: the blocks run stage by stage
+        # a block as five launches (iie_block_dev) where the shape has that form, else as the MoE half followed by the
+        # attention half (six launches); settable for comparisons, both give the same bytes
+        self.fused_block = not dense_router
         # one_launch: every block inside one persistent kernel where the shape allows it (byte-identical; on B200 it does not
         # yet beat the two entries per block, so it is opt-in)
         self.kernel = None
@@ -195,6 +198,15 @@ class Decoder:
                 self.x += ao
                 self.x += moe
                 continue
+            if self.fused_block:
+                # the whole block in five launches (norm + QKV + router rows, attention, O, gate/up, down)
+                try:
+                    device.decoder_block(self.moe_layers[li], self.gain_handles[li], a["wqkv"], a["wo"], self.x, a["k"], a["v"], pos_bound,
+                                         self.H, self.Hkv, self.hd, fa, fw, 1, 0 if full else self.window, self.cos, self.sin,
+                                         0 if full else 1, pos_dev=self.pos)
+                    continue
+                except device.NoFusedBlock:
+                    self.fused_block = False
             # MoE half first: it normalises x, leaves the digit planes of h in the library and adds moe(h) to x;
             # the attention half then reads those planes and adds its own term
             self.moe_layers[li].block(self.x, self.gain_handles[li], fa, fw, 1, out=self.x, want_routes=False)

@@ -33,8 +33,12 @@ def _host_view(model):
     return layers, embd, model.out_gain.cpu().numpy(), cfg
 
 
-@pytest.mark.parametrize("one_launch", [True, False], ids=["all-blocks-in-one-launch", "two-entries-per-block"])
-def test_decode_steps_match_the_checker_eager_and_replayed(one_launch):
+FORMS = pytest.mark.parametrize(("one_launch", "fused_block"), [(True, True), (False, True), (False, False)],
+                                ids=["all-blocks-in-one-launch", "five-launches-per-block", "two-entries-per-block"])
+
+
+@FORMS
+def test_decode_steps_match_the_checker_eager_and_replayed(one_launch, fused_block):
     import torch
 
     from integer_inference_engine_b200 import device, qk_cuda as qk
@@ -43,6 +47,7 @@ def test_decode_steps_match_the_checker_eager_and_replayed(one_launch):
     model = SyntheticDecoder(n_layers=5, d_model=512, n_heads=8, n_kv=2, head_dim=64, e_ffn=256, n_experts=8, top_k=2,
                              vocab=1000, context=40, max_new=12, window=16, seed=3, one_launch=one_launch)
     assert (model.kernel is not None) == one_launch
+    model.fused_block = fused_block
     layers, embd, out_gain, cfg = _host_view(model)
     cos, sin = model.cos.cpu().numpy(), model.sin.cpu().numpy()
     tok, pos = 123, model.context
@@ -65,6 +70,7 @@ def test_decode_steps_match_the_checker_eager_and_replayed(one_launch):
     assert int(model.pos.item()) == pos + 6
     assert device.read_flags() == 0
     assert got == want
+    assert model.fused_block == fused_block                 # the five-launch form was not silently dropped
     for li in (0, 1, 4):                                    # the caches hold what the checker appended
         assert np.array_equal(model.attn[li]["k"][:, pos:pos + 6].cpu().numpy(), layers[li]["k"][:, pos:pos + 6].astype(np.int32))
 
@@ -97,8 +103,8 @@ def test_replay_is_refused_after_the_workspaces_changed():
     qk.free_all()
 
 
-@pytest.mark.parametrize("one_launch", [True, False], ids=["all-blocks-in-one-launch", "two-entries-per-block"])
-def test_reference_recorded_decode_steps(golden_dir, one_launch):
+@FORMS
+def test_reference_recorded_decode_steps(golden_dir, one_launch, fused_block):
     """Three decode steps recorded from the reference's own block_cached / tied_head_int (tests/golden/nmc_decode.npz): the
     device decoder built from the same raw tensors and prompt caches yields the same picks, residual rows and cache rows."""
     import torch
@@ -115,6 +121,7 @@ def test_reference_recorded_decode_steps(golden_dir, one_launch):
                            rows=case["rows"], rope_base=case["rope_base"], caches=[(g[f"k{li}"], g[f"v{li}"]) for li in range(2)],
                            position=n_prompt, one_launch=one_launch)
     assert (dec.kernel is not None) == one_launch
+    dec.fused_block = fused_block
     assert np.array_equal(dec.cos.cpu().numpy(), g["cos"]) and np.array_equal(dec.sin.cpu().numpy(), g["sin"])
     dec.token.fill_(int(g["picks"][0]))
     for step in range(case["steps"]):
@@ -123,7 +130,7 @@ def test_reference_recorded_decode_steps(golden_dir, one_launch):
         assert np.array_equal(dec.x.cpu().numpy()[0], g["x"][step][-1]), step
         assert np.array_equal(dec.logits.cpu().numpy()[0], g["logits"][step]), step
         assert int(dec.token.item()) == int(g["picks"][step + 1])
-    assert device.read_flags() == 0
+    assert device.read_flags() == 0 and dec.fused_block == fused_block
     n = n_prompt + case["steps"]
     for li in range(2):
         assert np.array_equal(dec.attn[li]["k"][:, :n].cpu().numpy(), g[f"k{li}_after"].astype(np.int32))
