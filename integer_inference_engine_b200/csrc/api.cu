@@ -1656,7 +1656,7 @@ extern "C" void iie_set_tc_min_tokens(long long tokens) {
 
 extern "C" void iie_set_attn_fused(int enabled) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
-    iie::g_attn_fused = enabled ? 1 : 0;
+    iie::g_attn_fused = enabled < 0 ? 0 : enabled > 2 ? 2 : enabled;
 }
 
 extern "C" void iie_set_pdl(int enabled) {

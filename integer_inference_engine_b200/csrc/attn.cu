@@ -21,6 +21,8 @@
 // stores them the same way and refuses such values).
 #include <cooperative_groups.h>
 
+#include <algorithm>
+
 #include "kernels.h"
 #include "layout.cuh"
 #include "mma_items.cuh"
@@ -29,7 +31,8 @@ namespace cg = cooperative_groups;
 
 namespace iie {
 
-int g_attn_fused = 1;                      // 1: one cooperative launch when every CTA fits on the device, 0: always three launches
+int g_attn_fused = 1;                      // 1: one cooperative launch where every CTA fits on the device (one CTA per SM where the chunks fit
+                                           // shared memory), 2: the same without the one-CTA-per-SM form, 0: always three launches
 
 namespace {
 
@@ -558,6 +561,271 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const AttnArgs a_in) {
     if (a.out_limbs && a.out_nl && nl > 1) atomicMax(a.out_nl, nl);
 }
 
+// ---- the same four passes with one CTA per SM (up to 148 CTAs of 512 threads instead of 256 of 256) ------------------
+// Every KV head's visible keys are cut into as many chunks as there are SMs per head, so each SM holds exactly one
+// CTA, the grid barriers have fewer participants and the per-chunk partial sums are fewer.  The K and V rows of a
+// chunk arrive through bulk copies requested at kernel entry (V lands while the scores and the exponentials are
+// computed); scores are register-tiled (a lane owns one key and a quarter of the head dimension for all query heads of
+// the KV head, so a key value is read from shared memory once for eight heads) and so is probability x value (a
+// thread owns two output dimensions of four heads for a quarter of the keys).
+constexpr int AF_THREADS = 512;
+constexpr int AF_HEADS = 8;                  // query heads per KV head this form carries
+constexpr unsigned AF_POLLS = 1u << 22;
+
+__device__ __forceinline__ uint32_t af_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool af_wait(uint64_t *bar) {
+    for (unsigned it = 0; it < AF_POLLS; it++) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(af_u32(bar)) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void af_copy(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(af_u32(dst)), "l"(src), "r"(bytes), "r"(af_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs a_in) {
+    AttnArgs a = a_in;
+    if (!at_span(a_in, a.pos, a.lo)) { at_refuse(a_in); return; }          // uniform over the grid
+    cg::grid_group grid = cg::this_grid();
+    extern __shared__ __align__(16) unsigned char af_smem[];
+    __shared__ long long s_max[AF_HEADS];
+    __shared__ unsigned long long s_z[AF_HEADS];
+    __shared__ int s_wide, s_timeout;
+    __shared__ __align__(8) uint64_t bars[2];
+    const int C = a.chunk, hd = a.hd, ld = hd + 4, rep = a.H / a.Hkv, kv = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, half = hd / 2;
+    const int KQ = AF_THREADS / hd;                                         // key groups of the probability x value pass
+    int32_t *sk = reinterpret_cast<int32_t *>(af_smem);                     // keys [C][hd + 4]
+    int32_t *sv = sk + (size_t)C * ld;                                      // values [C][hd]
+    int32_t *q32 = sv + (size_t)C * hd;                                     // rotated queries [8][hd] (rows beyond rep are zero)
+    long long *q64 = reinterpret_cast<long long *>(q32 + AF_HEADS * hd);    // the same as int64
+    unsigned *s_e = reinterpret_cast<unsigned *>(q64 + AF_HEADS * hd);      // exponentials, then probabilities [C][8]
+    long long *red = reinterpret_cast<long long *>(s_e + (size_t)C * AF_HEADS);   // [KQ][8][hd] partial sums of pass 3
+    const long long l0 = a.lo + (long long)blockIdx.x * C, l1 = min(l0 + C, a.pos + 1);
+    const int nk = (int)max(0LL, l1 - l0);
+    const bool own = l0 <= a.pos && a.pos < l0 + C;                         // this chunk ends with the new token's row
+    const int nk_old = own ? nk - 1 : nk;                                   // rows that are already in the cache
+    if (tid == 0) {
+        s_wide = 0; s_timeout = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(af_u32(&bars[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(af_u32(&bars[1])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const uint32_t bytes = (uint32_t)((size_t)nk_old * hd * 4);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(af_u32(&bars[0])), "r"(bytes) : "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(af_u32(&bars[1])), "r"(bytes) : "memory");
+    }
+    if (tid < AF_HEADS) { s_max[tid] = INT64_MIN; s_z[tid] = 0ULL; }
+    __syncthreads();
+    // rows below the new position were written by earlier steps: requested before the dependency wait
+    for (int r = tid; r < nk_old; r += AF_THREADS)
+        af_copy(sk + (size_t)r * ld, a.kcache + ((long long)kv * a.Lmax + l0 + r) * hd, (uint32_t)(hd * 4), &bars[0]);
+    if (tid == 0 && nk_old > 0)
+        af_copy(sv, a.vcache + ((long long)kv * a.Lmax + l0) * hd, (uint32_t)((size_t)nk_old * hd * 4), &bars[1]);
+    if (a.pdl) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
+    // ---- rotated queries ------------------------------------------------------------------------------------------------
+    bool wide = false;
+    for (int idx = tid; idx < AF_HEADS * half; idx += AF_THREADS) {
+        const int r = idx / half, i = idx - r * half;
+        const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
+        int64_t x0 = 0, x1 = 0;
+        if (r < rep) {
+            const int64_t *src = a.q + (long long)(kv * rep + r) * hd;
+            x0 = src[i0]; x1 = src[i1];
+            at_rotate(a, a.pos, i, x0, x1);
+        }
+        q64[r * hd + i0] = x0; q64[r * hd + i1] = x1;
+        q32[r * hd + i0] = (int32_t)x0; q32[r * hd + i1] = (int32_t)x1;
+        wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+    }
+    if (wide) s_wide = 1;
+    if (own) {                                                              // the new token's row: cache and shared memory
+        bool bad = false;
+        for (int i = tid; i < half; i += AF_THREADS) {
+            const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
+            int64_t x0 = a.k[kv * hd + i0], x1 = a.k[kv * hd + i1];
+            at_rotate(a, a.pos, i, x0, x1);
+            bad |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+            int32_t *dst = a.kcache + ((long long)kv * a.Lmax + a.pos) * hd;
+            dst[i0] = (int32_t)x0; dst[i1] = (int32_t)x1;
+            sk[(size_t)(nk - 1) * ld + i0] = (int32_t)x0; sk[(size_t)(nk - 1) * ld + i1] = (int32_t)x1;
+        }
+        for (int i = tid; i < hd; i += AF_THREADS) {
+            const int64_t v = a.v[kv * hd + i];
+            bad |= v != (int32_t)v;
+            a.vcache[((long long)kv * a.Lmax + a.pos) * hd + i] = (int32_t)v;
+            sv[(size_t)(nk - 1) * hd + i] = (int32_t)v;
+        }
+        if (bad) atomicOr(a.flags, 4);
+    }
+    if (!af_wait(&bars[0])) s_timeout = 1;
+    __syncthreads();
+    // ---- pass 1: a warp takes eight keys at a time; lane = (key, quarter of the head dimension), all heads ------------------
+    const int ks = lane >> 2, dq = lane & 3;
+    const bool use_wide = s_wide != 0;
+    long long sc[2][2] = {{INT64_MIN, INT64_MIN}, {INT64_MIN, INT64_MIN}};  // scores of heads 2dq, 2dq + 1 for up to two keys
+    long long mloc[2] = {INT64_MIN, INT64_MIN};
+#pragma unroll
+    for (int it = 0; it < 2; it++) {
+        const int key = (warp + it * (AF_THREADS / 32)) * 8 + ks;
+        if ((warp + it * (AF_THREADS / 32)) * 8 >= nk) break;              // warp-uniform
+        long long acc[AF_HEADS];
+#pragma unroll
+        for (int h = 0; h < AF_HEADS; h++) acc[h] = 0;
+        if (key < nk) {
+            const int32_t *kk = sk + (size_t)key * ld;
+            if (!use_wide) {
+                for (int j = 0; j < hd / 16; j++) {
+                    const int off = (j * 4 + dq) * 4;
+                    const int4 k4 = *reinterpret_cast<const int4 *>(kk + off);
+#pragma unroll
+                    for (int h = 0; h < AF_HEADS; h++) {
+                        const int4 q4 = *reinterpret_cast<const int4 *>(q32 + h * hd + off);
+                        acc[h] += (long long)q4.x * k4.x; acc[h] += (long long)q4.y * k4.y;
+                        acc[h] += (long long)q4.z * k4.z; acc[h] += (long long)q4.w * k4.w;
+                    }
+                }
+            } else {
+                for (int j = 0; j < hd / 16; j++) {
+                    const int off = (j * 4 + dq) * 4;
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const long long kj = kk[off + u];
+#pragma unroll
+                        for (int h = 0; h < AF_HEADS; h++) acc[h] += q64[h * hd + off + u] * kj;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < AF_HEADS; h++) {
+            acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 1);
+            acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 2);
+        }
+        const long long d0 = dq == 0 ? acc[0] : dq == 1 ? acc[2] : dq == 2 ? acc[4] : acc[6];
+        const long long d1 = dq == 0 ? acc[1] : dq == 1 ? acc[3] : dq == 2 ? acc[5] : acc[7];
+        if (key < nk) {
+            if (2 * dq < rep) { sc[it][0] = ((d0 >> a.fa) * a.inv_sqrt) >> a.fa; mloc[0] = max(mloc[0], sc[it][0]); }
+            if (2 * dq + 1 < rep) { sc[it][1] = ((d1 >> a.fa) * a.inv_sqrt) >> a.fa; mloc[1] = max(mloc[1], sc[it][1]); }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+        long long m = mloc[u];
+#pragma unroll
+        for (int s2 = 4; s2 < 32; s2 <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s2));
+        if (ks == 0 && m != INT64_MIN) atomicMax(&s_max[2 * dq + u], m);
+    }
+    __syncthreads();
+    if (tid < rep && s_max[tid] != INT64_MIN) atomicMax(a.hmax + kv * rep + tid, s_max[tid]);
+    grid.sync();
+    // ---- pass 2: exponentials into shared memory and their sums ------------------------------------------------------------
+    unsigned long long zloc[2] = {0ULL, 0ULL};
+#pragma unroll
+    for (int it = 0; it < 2; it++) {
+        const int key = (warp + it * (AF_THREADS / 32)) * 8 + ks;
+        if (key >= nk) continue;
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int h = 2 * dq + u;
+            unsigned e = 0;
+            if (h < rep) {
+                long long dlt = __ldcg(a.hmax + kv * rep + h) - sc[it][u];
+                dlt = dlt < a.clip ? dlt : a.clip;
+                e = (unsigned)exp2_neg_fixed((dlt * a.log2e) >> a.fa, a.fa);
+                zloc[u] += e;
+            }
+            s_e[key * AF_HEADS + h] = e;
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+        unsigned long long z = zloc[u];
+#pragma unroll
+        for (int s2 = 4; s2 < 32; s2 <<= 1) z += __shfl_xor_sync(0xffffffffu, z, s2);
+        if (ks == 0 && z) atomicAdd(&s_z[2 * dq + u], z);
+    }
+    __syncthreads();
+    if (tid < rep && s_z[tid]) atomicAdd(a.Z + kv * rep + tid, s_z[tid]);
+    grid.sync();
+    // ---- pass 3: probabilities in place of the exponentials, then probabilities x values --------------------------------------
+    for (int idx = tid; idx < nk * AF_HEADS; idx += AF_THREADS) {
+        const int h = idx & (AF_HEADS - 1);
+        unsigned p = 0;
+        if (h < rep) {
+            const unsigned long long z = __ldcg(a.Z + kv * rep + h);
+            p = z ? (unsigned)(((unsigned long long)s_e[idx] << a.fa) / z) : 0u;
+        }
+        s_e[idx] = p;
+    }
+    if (!af_wait(&bars[1])) s_timeout = 1;
+    __syncthreads();
+    {
+        const int dp = tid % half, hh = (tid / half) & 1, kq = tid / hd;
+        const int per = (nk + KQ - 1) / KQ, j0 = min(nk, kq * per), j1 = min(nk, j0 + per);
+        long long c[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};
+        const int32_t *sp = reinterpret_cast<const int32_t *>(s_e);
+        for (int j = j0; j < j1; j++) {
+            const int2 v2 = *reinterpret_cast<const int2 *>(sv + (size_t)j * hd + 2 * dp);
+            const int4 p4 = *reinterpret_cast<const int4 *>(sp + j * AF_HEADS + 4 * hh);
+            c[0][0] += (long long)p4.x * v2.x; c[0][1] += (long long)p4.x * v2.y;
+            c[1][0] += (long long)p4.y * v2.x; c[1][1] += (long long)p4.y * v2.y;
+            c[2][0] += (long long)p4.z * v2.x; c[2][1] += (long long)p4.z * v2.y;
+            c[3][0] += (long long)p4.w * v2.x; c[3][1] += (long long)p4.w * v2.y;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            *reinterpret_cast<longlong2 *>(red + ((size_t)kq * AF_HEADS + 4 * hh + u) * hd + 2 * dp) = make_longlong2(c[u][0], c[u][1]);
+    }
+    __syncthreads();
+    long long *part = a.partial + ((long long)blockIdx.x * a.Hkv + kv) * rep * hd;        // this CTA's [rep][hd] partial sums
+    for (int o = tid; o < rep * hd; o += AF_THREADS) {
+        long long sum = 0;
+        for (int g = 0; g < KQ; g++) sum += red[(size_t)g * AF_HEADS * hd + o];
+        part[o] = sum;
+    }
+    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && a.out_nl) *a.out_nl = 1;
+    grid.sync();
+    // ---- pass 4: every output is the sum of the chunk partials; sixteen lanes share one output ---------------------------
+    if (blockIdx.x == 0 && blockIdx.y == 0)
+        for (int i = tid; i < a.H; i += blockDim.x) { a.hmax[i] = INT64_MIN; a.Z[i] = 0ULL; }     // nobody reads them any more
+    const long long n = (long long)a.H * hd;
+    const int used = (int)((a.pos - a.lo) / C) + 1;                          // chunks that held keys
+    const long long gid = ((long long)(blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + tid);
+    const long long n_groups = (long long)gridDim.x * gridDim.y * blockDim.x / 16;
+    const int sub = (int)(gid & 15);
+    int nl = 1;
+    bool over = false;
+    for (long long o = gid >> 4; (o & ~1LL) < n; o += n_groups) {           // a warp holds outputs 2w, 2w + 1: uniform trip count
+        long long sum = 0;
+        if (o < n) {
+            const int h = (int)(o / hd), dd = (int)(o - (long long)h * hd), kvh = h / rep, r = h - kvh * rep;
+            for (int cc = sub; cc < used; cc += 16)
+                sum += __ldcg(a.partial + (((long long)cc * a.Hkv + kvh) * rep + r) * hd + dd);
+        }
+#pragma unroll
+        for (int s2 = 8; s2 > 0; s2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s2);
+        if (o < n && sub == 0) {
+            const long long y = sum >> a.fa;
+            if (a.out) a.out[o] = y;
+            if (a.out_limbs) {
+                bool ok;
+                const uint64_t dg = balanced_digits8(y, ok);
+                over |= !ok;
+                nl = max(nl, digits_used(dg));
+#pragma unroll
+                for (int l = 0; l < 8; l++) a.out_limbs[l * n + o] = (int8_t)(dg >> (8 * l));
+            }
+        }
+    }
+    if (over) atomicOr(a.flags, 1);
+    if (a.out_limbs && a.out_nl && nl > 1) atomicMax(a.out_nl, nl);
+    if (s_timeout && tid == 0) atomicOr(a.flags, 8);
+}
+
 // one row of a registered Q4_K / Q6_K matrix as int64 at 2^frac (the embedding look-up)
 __global__ void embed_row_kernel(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,
                                  int64_t *out) {
@@ -668,6 +936,37 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
         if (!coop) n_sms = 0;
         configured = true;
+    }
+    // one CTA per SM where a KV head's keys, cut into n_sms / Hkv chunks, fit the shared memory of a CTA
+    if (g_attn_fused == 1 && a.partial && n_sms > 0 && !a.batch && rep <= AF_HEADS && AF_THREADS % a.hd == 0 && a.hd % 16 == 0) {
+        static bool fat_configured = false;
+        if (!fat_configured) {
+            if (cudaFuncSetAttribute(attn_fat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024) != cudaSuccess) return cudaGetLastError();
+            fat_configured = true;
+        }
+        const int per_head = std::max(1, n_sms / a.Hkv);
+        int C = (int)((n_keys + per_head - 1) / per_head);
+        C = std::max(16, (C + 15) / 16 * 16);
+        const unsigned fat_chunks = (unsigned)((n_keys + C - 1) / C);
+        const size_t fat_smem = (size_t)C * (a.hd + 4) * 4 + (size_t)C * a.hd * 4 + (size_t)AF_HEADS * a.hd * 12 + (size_t)C * AF_HEADS * 4 +
+                                (size_t)AF_THREADS / a.hd * AF_HEADS * a.hd * 8;
+        int per_sm = 0;
+        if (C <= 2 * 8 * (AF_THREADS / 32) && fat_smem <= 208 * 1024 &&
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_fat_kernel, AF_THREADS, fat_smem) == cudaSuccess &&
+            (long long)fat_chunks * a.Hkv <= (long long)per_sm * n_sms) {
+            AttnArgs f = a;
+            f.chunk = C;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(fat_chunks, a.Hkv); cfg.blockDim = dim3(AF_THREADS); cfg.dynamicSmemBytes = fat_smem; cfg.stream = s;
+            cudaLaunchAttribute attr[2];
+            attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = 1;
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr; cfg.numAttrs = a.pdl ? 2 : 1;
+            const cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fat_kernel, f);
+            note_launch(1);
+            return e != cudaSuccess ? e : cudaGetLastError();
+        }
+        cudaGetLastError();
     }
     bool fused = g_attn_fused && a.partial && n_sms > 0 && rep4 <= 256 / AT_CH && fused_smem <= 200 * 1024;
     if (fused) {

@@ -236,6 +236,7 @@ struct AttnArgs {
     long long Ls;                  // row stride of scores / e (0: Lmax)
     long long seq_stride;          // with batch > 0: elements between the caches of consecutive sequences (batched decode: token i is
                                    // sequence i's new token, all at position pos); 0: the tokens are consecutive positions of one sequence
+    int chunk;                     // keys per CTA of the one-CTA-per-SM form (filled in by the launcher)
 };
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s);
 // `batch` new tokens at positions pos .. pos + batch - 1 against the cache rows before them and each other (causal):
