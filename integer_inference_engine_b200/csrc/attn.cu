@@ -587,6 +587,30 @@ __device__ __forceinline__ void af_copy(void *dst, const void *src, uint32_t byt
                  ::"r"(af_u32(dst)), "l"(src), "r"(bytes), "r"(af_u32(bar)) : "memory");
 }
 
+// the four bytes of four consecutive int32 values, transposed: d_b = byte b of (x, y, z, w)
+__device__ __forceinline__ void af_bytes(const int4 v, uint32_t &d0, uint32_t &d1, uint32_t &d2, uint32_t &d3) {
+    const uint32_t t0 = __byte_perm((uint32_t)v.x, (uint32_t)v.y, 0x5140), t1 = __byte_perm((uint32_t)v.x, (uint32_t)v.y, 0x7362);
+    const uint32_t t2 = __byte_perm((uint32_t)v.z, (uint32_t)v.w, 0x5140), t3 = __byte_perm((uint32_t)v.z, (uint32_t)v.w, 0x7362);
+    d0 = __byte_perm(t0, t2, 0x5410); d1 = __byte_perm(t0, t2, 0x7632);
+    d2 = __byte_perm(t1, t3, 0x5410); d3 = __byte_perm(t1, t3, 0x7632);
+}
+// D(16x8,s32) += A(16x32, 8-bit, row) * B(32x8, 8-bit, col) with the signedness of each operand chosen per byte plane
+template <bool A_SIGNED, bool B_SIGNED>
+__device__ __forceinline__ void af_mma(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if (A_SIGNED && B_SIGNED)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else if (A_SIGNED)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else if (B_SIGNED)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
 __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
     if (!at_span(a_in, a.pos, a.lo)) { at_refuse(a_in); return; }          // uniform over the grid
@@ -604,7 +628,10 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     int32_t *q32 = sv + (size_t)C * hd;                                     // rotated queries [8][hd] (rows beyond rep are zero)
     long long *q64 = reinterpret_cast<long long *>(q32 + AF_HEADS * hd);    // the same as int64
     unsigned *s_e = reinterpret_cast<unsigned *>(q64 + AF_HEADS * hd);      // exponentials, then probabilities [C][8]
-    long long *red = reinterpret_cast<long long *>(s_e + (size_t)C * AF_HEADS);   // [KQ][8][hd] partial sums of pass 3
+    long long *red = reinterpret_cast<long long *>(s_e + (size_t)C * AF_HEADS);   // [KQ][8][hd] partial sums of pass 3; before that the
+                                                                                  // dot products [2][C][8] of pass 1
+    const int qld = hd + 16;                                                // row stride of a byte plane (bytes): heads on different banks
+    int8_t *qd = reinterpret_cast<int8_t *>(red + (size_t)KQ * AF_HEADS * hd);    // bytes of the rotated queries [4][8][hd + 16]
     const long long l0 = a.lo + (long long)blockIdx.x * C, l1 = min(l0 + C, a.pos + 1);
     const int nk = (int)max(0LL, l1 - l0);
     const bool own = l0 <= a.pos && a.pos < l0 + C;                         // this chunk ends with the new token's row
@@ -639,6 +666,11 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
         }
         q64[r * hd + i0] = x0; q64[r * hd + i1] = x1;
         q32[r * hd + i0] = (int32_t)x0; q32[r * hd + i1] = (int32_t)x1;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            qd[(b * AF_HEADS + r) * qld + i0] = (int8_t)((uint32_t)(int32_t)x0 >> (8 * b));
+            qd[(b * AF_HEADS + r) * qld + i1] = (int8_t)((uint32_t)(int32_t)x1 >> (8 * b));
+        }
         wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
     }
     if (wide) s_wide = 1;
@@ -663,91 +695,103 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     }
     if (!af_wait(&bars[0])) s_timeout = 1;
     __syncthreads();
-    // ---- pass 1: a warp takes eight keys at a time; lane = (key, quarter of the head dimension), all heads ------------------
-    const int ks = lane >> 2, dq = lane & 3;
+    // ---- pass 1 on the tensor cores: an int32 is its four bytes, x = b0 + 2^8 b1 + 2^16 b2 + 2^24 b3 with b0..b2 unsigned and b3
+    //      signed, so q . k = sum over byte pairs of 2^(8(a+b)) (k_a . q_b), every pair an exact int8 MMA (16 keys x 8 heads x 32
+    //      dimensions), pairs of equal a + b sharing an int32 accumulator (at most 4 x 255^2 x hd < 2^31).  Two warps share a
+    //      16-key tile, half of the head dimension each, where there are at most eight tiles.
     const bool use_wide = s_wide != 0;
-    long long sc[2][2] = {{INT64_MIN, INT64_MIN}, {INT64_MIN, INT64_MIN}};  // scores of heads 2dq, 2dq + 1 for up to two keys
-    long long mloc[2] = {INT64_MIN, INT64_MIN};
+    long long *dots = red;
+    const int tiles_c = C >> 4, ksteps = hd / 32;
+    const bool split = tiles_c <= 8 && (ksteps & 1) == 0;
+    if (!use_wide) {
+        const int kt = split ? (warp >> 1) : warp, kh = split ? (warp & 1) : 0;
+        const int s_lo = split ? kh * (ksteps / 2) : 0, s_hi = split ? s_lo + ksteps / 2 : ksteps;
+        if (kt < tiles_c && kt * 16 < nk) {                                 // warp-uniform
+            int acc[7][4];
 #pragma unroll
-    for (int it = 0; it < 2; it++) {
-        const int key = (warp + it * (AF_THREADS / 32)) * 8 + ks;
-        if ((warp + it * (AF_THREADS / 32)) * 8 >= nk) break;              // warp-uniform
-        long long acc[AF_HEADS];
+            for (int i = 0; i < 7; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0; }
+            const int g = lane >> 2, t = lane & 3;
+            const int32_t *rowA = sk + (size_t)(kt * 16 + g) * ld, *rowB = rowA + 8 * ld;
+            for (int st = s_lo; st < s_hi; st++) {
+                uint32_t A[4][4];
+                af_bytes(*reinterpret_cast<const int4 *>(rowA + 32 * st + 4 * t), A[0][0], A[1][0], A[2][0], A[3][0]);
+                af_bytes(*reinterpret_cast<const int4 *>(rowB + 32 * st + 4 * t), A[0][1], A[1][1], A[2][1], A[3][1]);
+                af_bytes(*reinterpret_cast<const int4 *>(rowA + 32 * st + 16 + 4 * t), A[0][2], A[1][2], A[2][2], A[3][2]);
+                af_bytes(*reinterpret_cast<const int4 *>(rowB + 32 * st + 16 + 4 * t), A[0][3], A[1][3], A[2][3], A[3][3]);
 #pragma unroll
-        for (int h = 0; h < AF_HEADS; h++) acc[h] = 0;
-        if (key < nk) {
-            const int32_t *kk = sk + (size_t)key * ld;
-            if (!use_wide) {
-                for (int j = 0; j < hd / 16; j++) {
-                    const int off = (j * 4 + dq) * 4;
-                    const int4 k4 = *reinterpret_cast<const int4 *>(kk + off);
+                for (int b = 0; b < 4; b++) {
+                    const int8_t *qb = qd + (b * AF_HEADS + g) * qld + 32 * st + 4 * t;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(qb), b1 = *reinterpret_cast<const uint32_t *>(qb + 16);
 #pragma unroll
-                    for (int h = 0; h < AF_HEADS; h++) {
-                        const int4 q4 = *reinterpret_cast<const int4 *>(q32 + h * hd + off);
-                        acc[h] += (long long)q4.x * k4.x; acc[h] += (long long)q4.y * k4.y;
-                        acc[h] += (long long)q4.z * k4.z; acc[h] += (long long)q4.w * k4.w;
-                    }
-                }
-            } else {
-                for (int j = 0; j < hd / 16; j++) {
-                    const int off = (j * 4 + dq) * 4;
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        const long long kj = kk[off + u];
-#pragma unroll
-                        for (int h = 0; h < AF_HEADS; h++) acc[h] += q64[h * hd + off + u] * kj;
+                    for (int aa = 0; aa < 4; aa++) {
+                        if (aa < 3 && b < 3) af_mma<false, false>(acc[aa + b], A[aa], b0, b1);
+                        else if (aa < 3) af_mma<false, true>(acc[aa + b], A[aa], b0, b1);
+                        else if (b < 3) af_mma<true, false>(acc[aa + b], A[aa], b0, b1);
+                        else af_mma<true, true>(acc[aa + b], A[aa], b0, b1);
                     }
                 }
             }
-        }
 #pragma unroll
-        for (int h = 0; h < AF_HEADS; h++) {
-            acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 1);
-            acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 2);
+            for (int i = 0; i < 4; i++) {
+                long long dot = 0;
+#pragma unroll
+                for (int w = 6; w >= 0; w--) dot = dot * 256 + (long long)acc[w][i];
+                const int row = kt * 16 + g + (i >= 2 ? 8 : 0), col = 2 * t + (i & 1);
+                dots[((size_t)kh * C + row) * AF_HEADS + col] = dot;
+            }
         }
-        const long long d0 = dq == 0 ? acc[0] : dq == 1 ? acc[2] : dq == 2 ? acc[4] : acc[6];
-        const long long d1 = dq == 0 ? acc[1] : dq == 1 ? acc[3] : dq == 2 ? acc[5] : acc[7];
-        if (key < nk) {
-            if (2 * dq < rep) { sc[it][0] = ((d0 >> a.fa) * a.inv_sqrt) >> a.fa; mloc[0] = max(mloc[0], sc[it][0]); }
-            if (2 * dq + 1 < rep) { sc[it][1] = ((d1 >> a.fa) * a.inv_sqrt) >> a.fa; mloc[1] = max(mloc[1], sc[it][1]); }
+    } else {
+        // a query value beyond int32: wrapping 64-bit products, one (key, head) pair per thread and turn
+        for (int i = tid; i < nk * AF_HEADS; i += AF_THREADS) {
+            const int key = i >> 3, h = i & 7;
+            long long dot = 0;
+            if (h < rep) {
+                const int32_t *kk = sk + (size_t)key * ld;
+                for (int j = 0; j < hd; j++) dot += q64[h * hd + j] * (long long)kk[j];
+            }
+            dots[i] = dot;
         }
     }
+    __syncthreads();
+    // scores of the (key, head) pairs i = tid, tid + 512, ...: key = i / 8, head = i % 8 = lane % 8
+    const int head = lane & 7;
+    long long sc[4] = {INT64_MIN, INT64_MIN, INT64_MIN, INT64_MIN};
+    long long mloc = INT64_MIN;
 #pragma unroll
-    for (int u = 0; u < 2; u++) {
-        long long m = mloc[u];
-#pragma unroll
-        for (int s2 = 4; s2 < 32; s2 <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s2));
-        if (ks == 0 && m != INT64_MIN) atomicMax(&s_max[2 * dq + u], m);
+    for (int u = 0; u < 4; u++) {
+        const int i = tid + u * AF_THREADS;
+        if (i < nk * AF_HEADS && head < rep) {
+            long long d = dots[i];
+            if (split && !use_wide) d += dots[(size_t)C * AF_HEADS + i];
+            sc[u] = ((d >> a.fa) * a.inv_sqrt) >> a.fa;
+            mloc = max(mloc, sc[u]);
+        }
     }
+    mloc = max(mloc, __shfl_xor_sync(0xffffffffu, mloc, 8));
+    mloc = max(mloc, __shfl_xor_sync(0xffffffffu, mloc, 16));
+    if (lane < 8 && mloc != INT64_MIN) atomicMax(&s_max[head], mloc);
     __syncthreads();
     if (tid < rep && s_max[tid] != INT64_MIN) atomicMax(a.hmax + kv * rep + tid, s_max[tid]);
     grid.sync();
     // ---- pass 2: exponentials into shared memory and their sums ------------------------------------------------------------
-    unsigned long long zloc[2] = {0ULL, 0ULL};
+    unsigned long long zloc = 0ULL;
+    const long long hm = head < rep ? __ldcg(a.hmax + kv * rep + head) : 0;
 #pragma unroll
-    for (int it = 0; it < 2; it++) {
-        const int key = (warp + it * (AF_THREADS / 32)) * 8 + ks;
-        if (key >= nk) continue;
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-            const int h = 2 * dq + u;
-            unsigned e = 0;
-            if (h < rep) {
-                long long dlt = __ldcg(a.hmax + kv * rep + h) - sc[it][u];
-                dlt = dlt < a.clip ? dlt : a.clip;
-                e = (unsigned)exp2_neg_fixed((dlt * a.log2e) >> a.fa, a.fa);
-                zloc[u] += e;
-            }
-            s_e[key * AF_HEADS + h] = e;
+    for (int u = 0; u < 4; u++) {
+        const int i = tid + u * AF_THREADS;
+        if (i >= nk * AF_HEADS) continue;
+        unsigned e = 0;
+        if (head < rep) {
+            long long dlt = hm - sc[u];
+            dlt = dlt < a.clip ? dlt : a.clip;
+            e = (unsigned)exp2_neg_fixed((dlt * a.log2e) >> a.fa, a.fa);
+            zloc += e;
         }
+        s_e[i] = e;
     }
-#pragma unroll
-    for (int u = 0; u < 2; u++) {
-        unsigned long long z = zloc[u];
-#pragma unroll
-        for (int s2 = 4; s2 < 32; s2 <<= 1) z += __shfl_xor_sync(0xffffffffu, z, s2);
-        if (ks == 0 && z) atomicAdd(&s_z[2 * dq + u], z);
-    }
+    zloc += __shfl_xor_sync(0xffffffffu, zloc, 8);
+    zloc += __shfl_xor_sync(0xffffffffu, zloc, 16);
+    if (lane < 8 && zloc) atomicAdd(&s_z[head], zloc);
     __syncthreads();
     if (tid < rep && s_z[tid]) atomicAdd(a.Z + kv * rep + tid, s_z[tid]);
     grid.sync();
@@ -944,12 +988,12 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
             if (cudaFuncSetAttribute(attn_fat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024) != cudaSuccess) return cudaGetLastError();
             fat_configured = true;
         }
-        const int per_head = std::max(1, n_sms / a.Hkv);
+        const int per_head = std::max(1, std::min(n_sms, 192) / a.Hkv);      // the partial-sum scratch holds 192 chunks
         int C = (int)((n_keys + per_head - 1) / per_head);
         C = std::max(16, (C + 15) / 16 * 16);
         const unsigned fat_chunks = (unsigned)((n_keys + C - 1) / C);
         const size_t fat_smem = (size_t)C * (a.hd + 4) * 4 + (size_t)C * a.hd * 4 + (size_t)AF_HEADS * a.hd * 12 + (size_t)C * AF_HEADS * 4 +
-                                (size_t)AF_THREADS / a.hd * AF_HEADS * a.hd * 8;
+                                (size_t)AF_THREADS / a.hd * AF_HEADS * a.hd * 8 + (size_t)4 * AF_HEADS * (a.hd + 16);
         int per_sm = 0;
         if (C <= 2 * 8 * (AF_THREADS / 32) && fat_smem <= 208 * 1024 &&
             cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_fat_kernel, AF_THREADS, fat_smem) == cudaSuccess &&
