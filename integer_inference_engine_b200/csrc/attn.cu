@@ -624,14 +624,16 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, half = hd / 2;
     const int KQ = AF_THREADS / hd;                                         // key groups of the probability x value pass
     int32_t *sk = reinterpret_cast<int32_t *>(af_smem);                     // keys [C][hd + 4]
-    int32_t *sv = sk + (size_t)C * ld;                                      // values [C][hd]
-    int32_t *q32 = sv + (size_t)C * hd;                                     // rotated queries [8][hd] (rows beyond rep are zero)
+    int32_t *sv = sk + (size_t)C * ld;                                      // values [C][hd + 4]
+    int32_t *q32 = sv + (size_t)C * ld;                                     // rotated queries [8][hd] (rows beyond rep are zero)
     long long *q64 = reinterpret_cast<long long *>(q32 + AF_HEADS * hd);    // the same as int64
     unsigned *s_e = reinterpret_cast<unsigned *>(q64 + AF_HEADS * hd);      // exponentials, then probabilities [C][8]
     long long *red = reinterpret_cast<long long *>(s_e + (size_t)C * AF_HEADS);   // [KQ][8][hd] partial sums of pass 3; before that the
                                                                                   // dot products [2][C][8] of pass 1
     const int qld = hd + 16;                                                // row stride of a byte plane (bytes): heads on different banks
     int8_t *qd = reinterpret_cast<int8_t *>(red + (size_t)KQ * AF_HEADS * hd);    // bytes of the rotated queries [4][8][hd + 16]
+    const int pld = C + 16;                                                 // row stride of a probability byte plane
+    uint8_t *pT = reinterpret_cast<uint8_t *>(qd + 4 * AF_HEADS * qld);     // bytes of the probabilities [3][8][C + 16]
     const long long l0 = a.lo + (long long)blockIdx.x * C, l1 = min(l0 + C, a.pos + 1);
     const int nk = (int)max(0LL, l1 - l0);
     const bool own = l0 <= a.pos && a.pos < l0 + C;                         // this chunk ends with the new token's row
@@ -650,8 +652,8 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     // rows below the new position were written by earlier steps: requested before the dependency wait
     for (int r = tid; r < nk_old; r += AF_THREADS)
         af_copy(sk + (size_t)r * ld, a.kcache + ((long long)kv * a.Lmax + l0 + r) * hd, (uint32_t)(hd * 4), &bars[0]);
-    if (tid == 0 && nk_old > 0)
-        af_copy(sv, a.vcache + ((long long)kv * a.Lmax + l0) * hd, (uint32_t)((size_t)nk_old * hd * 4), &bars[1]);
+    for (int r = tid - AF_THREADS / 2; r >= 0 && r < nk_old; r += AF_THREADS)     // the upper half of the CTA asks for the value rows
+        af_copy(sv + (size_t)r * ld, a.vcache + ((long long)kv * a.Lmax + l0 + r) * hd, (uint32_t)(hd * 4), &bars[1]);
     if (a.pdl) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
     // ---- rotated queries ------------------------------------------------------------------------------------------------
     bool wide = false;
@@ -689,7 +691,7 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
             const int64_t v = a.v[kv * hd + i];
             bad |= v != (int32_t)v;
             a.vcache[((long long)kv * a.Lmax + a.pos) * hd + i] = (int32_t)v;
-            sv[(size_t)(nk - 1) * hd + i] = (int32_t)v;
+            sv[(size_t)(nk - 1) * ld + i] = (int32_t)v;
         }
         if (bad) atomicOr(a.flags, 4);
     }
@@ -795,41 +797,56 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     __syncthreads();
     if (tid < rep && s_z[tid]) atomicAdd(a.Z + kv * rep + tid, s_z[tid]);
     grid.sync();
-    // ---- pass 3: probabilities in place of the exponentials, then probabilities x values --------------------------------------
-    for (int idx = tid; idx < nk * AF_HEADS; idx += AF_THREADS) {
-        const int h = idx & (AF_HEADS - 1);
+    // ---- pass 3: probabilities as byte planes, then probabilities x values on the tensor cores ---------------------------
+    //      out[head][dim] = sum over keys p[key][head] v[key][dim]: A = bytes of p (heads x keys; p <= 2^fa has three unsigned
+    //      bytes), B = bytes of v gathered from four key rows (keys x dims), a warp owns eight dimensions for all keys
+    const int nk32 = (nk + 31) & ~31;
+    for (int idx = tid; idx < nk32 * AF_HEADS; idx += AF_THREADS) {
+        const int key = idx >> 3, h = idx & (AF_HEADS - 1);
         unsigned p = 0;
-        if (h < rep) {
+        if (key < nk && h < rep) {
             const unsigned long long z = __ldcg(a.Z + kv * rep + h);
             p = z ? (unsigned)(((unsigned long long)s_e[idx] << a.fa) / z) : 0u;
         }
-        s_e[idx] = p;
+#pragma unroll
+        for (int b = 0; b < 3; b++) pT[(b * AF_HEADS + h) * pld + key] = (uint8_t)(p >> (8 * b));
     }
+    // value rows beyond the chunk's keys multiply zero probabilities but must hold numbers: clear them
+    for (int i = tid; i < (nk32 - nk) * hd; i += AF_THREADS) sv[(size_t)(nk + i / hd) * ld + (i % hd)] = 0;
     if (!af_wait(&bars[1])) s_timeout = 1;
     __syncthreads();
-    {
-        const int dp = tid % half, hh = (tid / half) & 1, kq = tid / hd;
-        const int per = (nk + KQ - 1) / KQ, j0 = min(nk, kq * per), j1 = min(nk, j0 + per);
-        long long c[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};
-        const int32_t *sp = reinterpret_cast<const int32_t *>(s_e);
-        for (int j = j0; j < j1; j++) {
-            const int2 v2 = *reinterpret_cast<const int2 *>(sv + (size_t)j * hd + 2 * dp);
-            const int4 p4 = *reinterpret_cast<const int4 *>(sp + j * AF_HEADS + 4 * hh);
-            c[0][0] += (long long)p4.x * v2.x; c[0][1] += (long long)p4.x * v2.y;
-            c[1][0] += (long long)p4.y * v2.x; c[1][1] += (long long)p4.y * v2.y;
-            c[2][0] += (long long)p4.z * v2.x; c[2][1] += (long long)p4.z * v2.y;
-            c[3][0] += (long long)p4.w * v2.x; c[3][1] += (long long)p4.w * v2.y;
-        }
-#pragma unroll
-        for (int u = 0; u < 4; u++)
-            *reinterpret_cast<longlong2 *>(red + ((size_t)kq * AF_HEADS + 4 * hh + u) * hd + 2 * dp) = make_longlong2(c[u][0], c[u][1]);
-    }
-    __syncthreads();
     long long *part = a.partial + ((long long)blockIdx.x * a.Hkv + kv) * rep * hd;        // this CTA's [rep][hd] partial sums
-    for (int o = tid; o < rep * hd; o += AF_THREADS) {
-        long long sum = 0;
-        for (int g = 0; g < KQ; g++) sum += red[(size_t)g * AF_HEADS * hd + o];
-        part[o] = sum;
+    {
+        const int g = lane >> 2, t = lane & 3;
+        for (int nt = warp; nt < hd / 8; nt += AF_THREADS / 32) {           // eight dimensions per warp and turn
+            int acc[6][4];
+#pragma unroll
+            for (int i = 0; i < 6; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0; }
+            for (int st = 0; st < nk32 / 32; st++) {
+                uint32_t B0[4], B1[4];
+                const int32_t *vb = sv + (size_t)(32 * st + 4 * t) * ld + nt * 8 + g;
+                af_bytes(make_int4(vb[0], vb[ld], vb[2 * ld], vb[3 * ld]), B0[0], B0[1], B0[2], B0[3]);
+                af_bytes(make_int4(vb[16 * ld], vb[17 * ld], vb[18 * ld], vb[19 * ld]), B1[0], B1[1], B1[2], B1[3]);
+#pragma unroll
+                for (int pa = 0; pa < 3; pa++) {
+                    const uint8_t *pp = pT + (pa * AF_HEADS + g) * pld + 32 * st + 4 * t;
+                    const uint32_t A[4] = {*reinterpret_cast<const uint32_t *>(pp), 0u, *reinterpret_cast<const uint32_t *>(pp + 16), 0u};
+#pragma unroll
+                    for (int vb8 = 0; vb8 < 4; vb8++) {
+                        if (vb8 < 3) af_mma<false, false>(acc[pa + vb8], A, B0[vb8], B1[vb8]);
+                        else af_mma<false, true>(acc[pa + vb8], A, B0[vb8], B1[vb8]);
+                    }
+                }
+            }
+            // rows 0..7 of the tile are the heads: c0, c1 = (head g, dims 2t, 2t + 1)
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                long long sum = 0;
+#pragma unroll
+                for (int w = 5; w >= 0; w--) sum = sum * 256 + (long long)acc[w][i];
+                if (g < rep) part[g * hd + nt * 8 + 2 * t + i] = sum;
+            }
+        }
     }
     if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && a.out_nl) *a.out_nl = 1;
     grid.sync();
@@ -982,7 +999,8 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
         configured = true;
     }
     // one CTA per SM where a KV head's keys, cut into n_sms / Hkv chunks, fit the shared memory of a CTA
-    if (g_attn_fused == 1 && a.partial && n_sms > 0 && !a.batch && rep <= AF_HEADS && AF_THREADS % a.hd == 0 && a.hd % 16 == 0) {
+    if (g_attn_fused == 1 && a.partial && n_sms > 0 && !a.batch && rep <= AF_HEADS && AF_THREADS % a.hd == 0 && a.hd % 32 == 0 &&
+        a.fa <= 23) {                                       // probabilities (at most 2^fa) as three bytes
         static bool fat_configured = false;
         if (!fat_configured) {
             if (cudaFuncSetAttribute(attn_fat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024) != cudaSuccess) return cudaGetLastError();
@@ -990,10 +1008,10 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
         }
         const int per_head = std::max(1, std::min(n_sms, 192) / a.Hkv);      // the partial-sum scratch holds 192 chunks
         int C = (int)((n_keys + per_head - 1) / per_head);
-        C = std::max(16, (C + 15) / 16 * 16);
+        C = std::max(32, (C + 31) / 32 * 32);                      // whole 32-key steps of the tensor-core passes
         const unsigned fat_chunks = (unsigned)((n_keys + C - 1) / C);
-        const size_t fat_smem = (size_t)C * (a.hd + 4) * 4 + (size_t)C * a.hd * 4 + (size_t)AF_HEADS * a.hd * 12 + (size_t)C * AF_HEADS * 4 +
-                                (size_t)AF_THREADS / a.hd * AF_HEADS * a.hd * 8 + (size_t)4 * AF_HEADS * (a.hd + 16);
+        const size_t fat_smem = (size_t)2 * C * (a.hd + 4) * 4 + (size_t)AF_HEADS * a.hd * 12 + (size_t)C * AF_HEADS * 4 +
+                                (size_t)AF_THREADS / a.hd * AF_HEADS * a.hd * 8 + (size_t)4 * AF_HEADS * (a.hd + 16) + (size_t)3 * AF_HEADS * (C + 16);
         int per_sm = 0;
         if (C <= 2 * 8 * (AF_THREADS / 32) && fat_smem <= 208 * 1024 &&
             cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_fat_kernel, AF_THREADS, fat_smem) == cudaSuccess &&
