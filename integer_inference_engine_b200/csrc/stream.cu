@@ -56,6 +56,15 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+// floor((x << fa) / rms) in 128 bits, for rows whose values are too wide for the reciprocal path (kept out of line: rare)
+__device__ __noinline__ int64_t norm_quotient_wide(int64_t xv, unsigned long long rms, int fa, bool &bad) {
+    const i128 num = (i128)xv * ((i128)1 << fa);
+    i128 q = num / (i128)rms;
+    if (num < 0 && q * (i128)rms != num) q -= 1;
+    if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; q = 0; }
+    return (int64_t)q;
+}
+
 template <int QT, int MODE, bool FAST>
 __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -203,25 +212,36 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
             for (int e = 0; e < 4; e++) {
                 const int64_t xv = xs[i + e];
                 int64_t y = xv;
+                bool small = false;
                 if (dead) y = 0;
                 else if (a.gain) {
-                    if (uabs64(xv) < (1ULL << (62 - a.fa)) && rms < (1ULL << 62)) y = floor_div_recip(xv * ((long long)1 << a.fa), rms, inv);
+                    if (uabs64(xv) < (1ULL << (62 - a.fa)) && rms < (1ULL << 62)) {
+                        y = floor_div_recip(xv * ((long long)1 << a.fa), rms, inv);
+                        small = uabs64(y) < (1ULL << 31) && gm < (1ULL << 31);
+                    } else y = norm_quotient_wide(xv, rms, a.fa, bad);
+                    if (small) y = (y * gs[i + e]) >> a.fa;                       // |y * gain| < 2^62: the 64-bit product is exact
                     else {
-                        const i128 num = (i128)xv * ((i128)1 << a.fa);
-                        i128 q = num / (i128)rms;
-                        if (num < 0 && q * (i128)rms != num) q -= 1;
-                        if (q > (i128)INT64_MAX || q < (i128)INT64_MIN) { bad = true; q = 0; }
-                        y = (int64_t)q;
+                        if ((u128)uabs64(y) * gm > (u128)INT64_MAX) bad = true;  // the oracle refuses such a gain product
+                        y = mul_shift(y, gs[i + e], a.fa);
                     }
-                    if ((u128)uabs64(y) * gm > (u128)INT64_MAX) bad = true;      // the oracle refuses such a gain product
-                    y = mul_shift(y, gs[i + e], a.fa);
                 }
-                bool ok;
-                const uint64_t dg = balanced_digits8(y, ok);
-                over |= !ok;
-                nl = max(nl, digits_used(dg));
+                if (y >= -2147483648LL && y <= 2139062143LL) {
+                    // four balanced digits hold it: 32-bit arithmetic, the upper planes stay zero
+                    int v = (int)y;
+                    uint32_t pk = 0;
 #pragma unroll
-                for (int l = 0; l < 8; l++) pw[l] |= (uint32_t)((dg >> (8 * l)) & 0xFF) << (8 * e);
+                    for (int l = 0; l < 4; l++) { pk |= (uint32_t)(v & 0xFF) << (8 * l); v = (v >> 8) + ((v >> 7) & 1); }
+                    nl = max(nl, pk == 0 ? 1 : 4 - (__clz((int)pk) >> 3));
+#pragma unroll
+                    for (int l = 0; l < 4; l++) pw[l] |= ((pk >> (8 * l)) & 0xFF) << (8 * e);
+                } else {
+                    bool ok;
+                    const uint64_t dg = balanced_digits8(y, ok);
+                    over |= !ok;
+                    nl = max(nl, digits_used(dg));
+#pragma unroll
+                    for (int l = 0; l < 8; l++) pw[l] |= (uint32_t)((dg >> (8 * l)) & 0xFF) << (8 * e);
+                }
             }
 #pragma unroll
             for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(planes + l * pstride + i) = pw[l];
