@@ -184,12 +184,21 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
         }
         if (lane == 0) { s_lo[warp] = lo; s_hi[warp] = hi; s_mx[warp] = mx; s_gmx[warp] = gmx; }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            u128 total = 0; unsigned long long m = 0, gm = 0;
-            for (int i = 0; i < NWARPS; i++) {
-                total += ((u128)s_hi[i] << 64) | s_lo[i];
-                m = s_mx[i] > m ? s_mx[i] : m; gm = s_gmx[i] > gm ? s_gmx[i] : gm;
+        if (warp == 0) {
+            lo = lane < NWARPS ? s_lo[lane] : 0ULL; hi = lane < NWARPS ? s_hi[lane] : 0ULL;
+            mx = lane < NWARPS ? s_mx[lane] : 0ULL; gmx = lane < NWARPS ? s_gmx[lane] : 0ULL;
+#pragma unroll
+            for (int sft = NWARPS / 2; sft > 0; sft >>= 1) {
+                const unsigned long long lo2 = __shfl_xor_sync(0xffffffffu, lo, sft), hi2 = __shfl_xor_sync(0xffffffffu, hi, sft);
+                const u128 sum = (((u128)hi << 64) | lo) + (((u128)hi2 << 64) | lo2);
+                lo = (unsigned long long)sum; hi = (unsigned long long)(sum >> 64);
+                const unsigned long long m2 = __shfl_xor_sync(0xffffffffu, mx, sft), g2 = __shfl_xor_sync(0xffffffffu, gmx, sft);
+                mx = m2 > mx ? m2 : mx; gmx = g2 > gmx ? g2 : gmx;
             }
+        }
+        if (threadIdx.x == 0) {
+            const u128 total = ((u128)hi << 64) | lo;
+            const unsigned long long m = mx, gm = gmx;
             int bad = m > (1ULL << 57) ? 1 : 0;                  // keeps the 128-bit sum of squares exact
             const int d = (int)K;
             u128 mean;
