@@ -864,8 +864,14 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
         long long sum = 0;
         if (o < n) {
             const int h = (int)(o / hd), dd = (int)(o - (long long)h * hd), kvh = h / rep, r = h - kvh * rep;
-            for (int cc = sub; cc < used; cc += 16)
-                sum += __ldcg(a.partial + (((long long)cc * a.Hkv + kvh) * rep + r) * hd + dd);
+            const long long *base = a.partial + ((long long)kvh * rep + r) * hd + dd;
+            const long long step = (long long)a.Hkv * rep * hd;
+            // three loads in flight per lane (48 chunks), then whatever is left
+            const long long v0 = sub < used ? __ldcg(base + (long long)sub * step) : 0;
+            const long long v1 = sub + 16 < used ? __ldcg(base + (long long)(sub + 16) * step) : 0;
+            const long long v2 = sub + 32 < used ? __ldcg(base + (long long)(sub + 32) * step) : 0;
+            sum = v0 + v1 + v2;
+            for (int cc = sub + 48; cc < used; cc += 16) sum += __ldcg(base + (long long)cc * step);
         }
 #pragma unroll
         for (int s2 = 8; s2 > 0; s2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s2);
