@@ -69,7 +69,7 @@ inline bool stage_on(int st) { return g_stage_mask == 0 || (g_stage_mask & st); 
 
 // Persistent device scratch by role, grown on demand (never shrunk until released).
 enum Role { R_X, R_XL, R_OUT, R_RAW, R_GU, R_GUL, R_TMP0, R_TMP1, R_TMP2, R_TABS, R_META, R_LOGITS, R_IDS, R_GATES,
-            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_ASCORES, R_AEXP, R_ASTAT, R_APART, R_PSCORES, R_PEXP, R_PSTAT, R_BSCORES, R_BEXP, R_BSTAT, R_COUNT };
+            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_ASCORES, R_AEXP, R_ASTAT, R_APART, R_PSCORES, R_PEXP, R_PSTAT, R_BSCORES, R_BEXP, R_BSTAT, R_BPART, R_COUNT };
 struct Buf { void *p = nullptr; size_t cap = 0; };
 Buf g_buf[R_COUNT];
 long long g_ws_allocs = 0;
@@ -1053,6 +1053,14 @@ extern "C" int iie_attn_decode_batch_dev(const int64_t *q_dev, const int64_t *k_
     attn_consts(a, fa, inv_sqrt);
     a.scores = scores; a.e = e; a.hmax = (long long *)st; a.Z = (unsigned long long *)(st + (size_t)n_seqs * n_heads * 8);
     a.out = out_dev; a.flags = g_flags;
+    // few sequences leave most SMs idle in the probability x value pass: share each pair's chunks over up to eight CTAs
+    const long long pairs = n_seqs * n_kv;
+    int splits = (int)std::min<long long>(8, std::min<long long>(Ls / 64, (1184 + pairs - 1) / pairs));
+    if (splits > 1) {
+        a.pv_part = (long long *)ensure(R_BPART, (size_t)n_seqs * splits * n_heads * head_dim * 8);
+        if (!a.pv_part) return 1;
+        a.pv_splits = splits;
+    }
     if (launch_attn_prefill(a, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     return 0;
 }

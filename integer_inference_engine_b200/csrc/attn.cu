@@ -337,10 +337,14 @@ __global__ void __launch_bounds__(256) attn_pv_rows_kernel(const AttnArgs a_in) 
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x;
     int32_t *s_p = at_v + AT_CH * a.hd;
     const int G = blockDim.x / a.hd, grp = tid / a.hd, d = tid - grp * a.hd;
+    // with pv_splits > 1 this CTA takes a contiguous share of the key chunks and leaves raw sums for attn_pv_finish_kernel
+    const int splits = a.pv_splits > 1 ? a.pv_splits : 1;
+    const long long n_chunks = (a.pos - a.lo) / AT_CH + 1, per = (n_chunks + splits - 1) / splits;
+    const long long c_lo = (long long)blockIdx.x * per, c_hi = min(n_chunks, c_lo + per);
     for (int rbase = 0; rbase < rep; rbase += G * 4) {                     // one pass per G*4 query heads
         const int r0 = rbase + grp * 4;
         long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
-        for (long long l0 = a.lo; l0 <= a.pos; l0 += AT_CH) {
+        for (long long l0 = a.lo + c_lo * AT_CH; l0 < a.lo + c_hi * AT_CH; l0 += AT_CH) {
             const int nk = (int)min((long long)AT_CH, a.pos + 1 - l0);
             __syncthreads();                                                // the previous chunk has been consumed
             for (int i = tid; i < AT_MAXREP * AT_CH; i += blockDim.x) {
@@ -368,10 +372,24 @@ __global__ void __launch_bounds__(256) attn_pv_rows_kernel(const AttnArgs a_in) 
         if (grp < G) {
             const long long cs[4] = {c0, c1, c2, c3};
 #pragma unroll
-            for (int u = 0; u < 4; u++)
-                if (r0 + u < rep) a.out[(long long)(kv * rep + r0 + u) * a.hd + d] = cs[u] >> a.fa;
+            for (int u = 0; u < 4; u++) {
+                if (r0 + u >= rep) continue;
+                const long long o = (long long)(kv * rep + r0 + u) * a.hd + d;
+                if (splits == 1) a.out[o] = cs[u] >> a.fa;
+                else a.pv_part[(((long long)blockIdx.z * splits + blockIdx.x) * a.H) * a.hd + o] = cs[u];
+            }
         }
     }
+}
+
+// out = (sum of the pv_splits partial sums) >> fa, one thread per output of every token
+__global__ void attn_pv_finish_kernel(const AttnArgs a) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x, per_tok = (long long)a.H * a.hd;
+    if (i >= (long long)a.batch * per_tok) return;
+    const long long tok = i / per_tok, o = i - tok * per_tok;
+    long long sum = 0;
+    for (int sidx = 0; sidx < a.pv_splits; sidx++) sum += a.pv_part[((tok * a.pv_splits + sidx) * a.H) * a.hd + o];
+    a.out[i] = sum >> a.fa;
 }
 
 // The three passes in ONE cooperative launch (all CTAs co-resident, two grid-wide barriers): scores and
@@ -893,6 +911,125 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     if (s_timeout && tid == 0) atomicOr(a.flags, 8);
 }
 
+// ---- several tokens at once (a prefill chunk, or the new tokens of independent sequences): the scores on the tensor cores,
+//      byte decomposition as in attn_fat_kernel.  Same grid as attn_scores_kernel, which remains for shapes this does not
+//      carry (more than eight query heads per KV head, head_dim other than 64 / 128).
+__global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in) {
+    AttnArgs a = a_in;
+    if (!at_span(a_in, a.pos, a.lo)) { at_refuse(a_in); return; }
+    at_batch(a);
+    const long long Ls = a.Ls ? a.Ls : a.Lmax;
+    extern __shared__ __align__(16) unsigned char ts_smem[];
+    __shared__ long long s_max[AF_HEADS];
+    __shared__ int s_wide;
+    const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, hd = a.hd, half = hd / 2;
+    const int ld = hd + 4, qld = hd + 16;
+    const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
+    if (l0 > a.pos) return;                                // a chunk past this token's position
+    const int nk = (int)max(0LL, l1 - l0);
+    long long *q64 = reinterpret_cast<long long *>(ts_smem);                 // [8][hd]
+    long long *dots = q64 + AF_HEADS * hd;                                  // [2][64][8]
+    int32_t *sk = reinterpret_cast<int32_t *>(dots + 2 * AT_CH * AF_HEADS); // [64][hd + 4]
+    int8_t *qd = reinterpret_cast<int8_t *>(sk + AT_CH * ld);               // [4][8][hd + 16]
+    if (tid == 0) s_wide = 0;
+    if (tid < AF_HEADS) s_max[tid] = INT64_MIN;
+    __syncthreads();
+    bool wide = false;
+    for (int idx = tid; idx < AF_HEADS * half; idx += blockDim.x) {
+        const int r = idx / half, i = idx - r * half;
+        const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
+        int64_t x0 = 0, x1 = 0;
+        if (r < rep) {
+            const int64_t *src = a.q + (long long)(kv * rep + r) * hd;
+            x0 = src[i0]; x1 = src[i1];
+            at_rotate(a, a.pos, i, x0, x1);
+        }
+        q64[r * hd + i0] = x0; q64[r * hd + i1] = x1;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            qd[(b * AF_HEADS + r) * qld + i0] = (int8_t)((uint32_t)(int32_t)x0 >> (8 * b));
+            qd[(b * AF_HEADS + r) * qld + i1] = (int8_t)((uint32_t)(int32_t)x1 >> (8 * b));
+        }
+        wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+    }
+    if (wide) s_wide = 1;
+    const int vec_per_row = hd / 4;
+    at_stage(reinterpret_cast<const int4 *>(a.kcache + ((long long)kv * a.Lmax + l0) * hd), nk * vec_per_row, tid, blockDim.x, sk,
+             [&](int i) { const int row = i / vec_per_row; return row * ld + (i - row * vec_per_row) * 4; });
+    __syncthreads();
+    const bool use_wide = s_wide != 0;
+    const int ksteps = hd / 32;
+    const bool split = (ksteps & 1) == 0;                  // four 16-key tiles: two warps per tile, half of the head dimension each
+    if (!use_wide) {
+        const int kt = split ? (warp >> 1) : warp, kh = split ? (warp & 1) : 0;
+        const int s_lo = split ? kh * (ksteps / 2) : 0, s_hi = split ? s_lo + ksteps / 2 : ksteps;
+        if (kt < AT_CH / 16 && kt * 16 < nk) {
+            int acc[7][4];
+#pragma unroll
+            for (int i = 0; i < 7; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0; }
+            const int g = lane >> 2, t = lane & 3;
+            const int32_t *rowA = sk + (size_t)(kt * 16 + g) * ld, *rowB = rowA + 8 * ld;
+            for (int st = s_lo; st < s_hi; st++) {
+                uint32_t A[4][4];
+                af_bytes(*reinterpret_cast<const int4 *>(rowA + 32 * st + 4 * t), A[0][0], A[1][0], A[2][0], A[3][0]);
+                af_bytes(*reinterpret_cast<const int4 *>(rowB + 32 * st + 4 * t), A[0][1], A[1][1], A[2][1], A[3][1]);
+                af_bytes(*reinterpret_cast<const int4 *>(rowA + 32 * st + 16 + 4 * t), A[0][2], A[1][2], A[2][2], A[3][2]);
+                af_bytes(*reinterpret_cast<const int4 *>(rowB + 32 * st + 16 + 4 * t), A[0][3], A[1][3], A[2][3], A[3][3]);
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    const int8_t *qb = qd + (b * AF_HEADS + g) * qld + 32 * st + 4 * t;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(qb), b1 = *reinterpret_cast<const uint32_t *>(qb + 16);
+#pragma unroll
+                    for (int aa = 0; aa < 4; aa++) {
+                        if (aa < 3 && b < 3) af_mma<false, false>(acc[aa + b], A[aa], b0, b1);
+                        else if (aa < 3) af_mma<false, true>(acc[aa + b], A[aa], b0, b1);
+                        else if (b < 3) af_mma<true, false>(acc[aa + b], A[aa], b0, b1);
+                        else af_mma<true, true>(acc[aa + b], A[aa], b0, b1);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                long long dot = 0;
+#pragma unroll
+                for (int w = 6; w >= 0; w--) dot = dot * 256 + (long long)acc[w][i];
+                const int row = kt * 16 + g + (i >= 2 ? 8 : 0), col = 2 * t + (i & 1);
+                dots[((size_t)kh * AT_CH + row) * AF_HEADS + col] = dot;
+            }
+        }
+    } else {
+        for (int i = tid; i < nk * AF_HEADS; i += blockDim.x) {             // a query value beyond int32: wrapping 64-bit products
+            const int key = i >> 3, h = i & 7;
+            long long dot = 0;
+            if (h < rep) {
+                const int32_t *kk = sk + (size_t)key * ld;
+                for (int j = 0; j < hd; j++) dot += q64[h * hd + j] * (long long)kk[j];
+            }
+            dots[i] = dot;
+        }
+    }
+    __syncthreads();
+    // thread -> (key = tid % 64, heads tid / 64 and tid / 64 + 4): a warp stores 32 consecutive keys of one head
+    const int key = tid & (AT_CH - 1);
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+        const int h = (tid >> 6) + 4 * u;
+        long long sc = INT64_MIN;
+        if (key < nk && h < rep) {
+            long long d = dots[key * AF_HEADS + h];
+            if (split && !use_wide) d += dots[(size_t)(AT_CH + key) * AF_HEADS + h];
+            sc = ((d >> a.fa) * a.inv_sqrt) >> a.fa;
+            a.scores[(long long)(kv * rep + h) * Ls + l0 + key] = sc;
+        }
+        long long m = sc;
+#pragma unroll
+        for (int s2 = 16; s2 > 0; s2 >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s2));
+        if (lane == 0 && m != INT64_MIN && h < rep) atomicMax(&s_max[h], m);
+    }
+    __syncthreads();
+    if (tid < rep && s_max[tid] != INT64_MIN) atomicMax(a.hmax + kv * rep + tid, s_max[tid]);
+}
+
 // one row of a registered Q4_K / Q6_K matrix as int64 at 2^frac (the embedding look-up)
 __global__ void embed_row_kernel(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,
                                  int64_t *out) {
@@ -1078,9 +1215,29 @@ cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s) {
     if (a.window > 0 && n_keys > a.window) n_keys = a.window;
     const unsigned chunks = (unsigned)((n_keys + AT_CH - 1) / AT_CH);
     attn_append_kernel<<<dim3((unsigned)a.batch, a.Hkv), 128, 0, s>>>(a);
-    attn_scores_kernel<<<dim3(chunks, a.Hkv, (unsigned)a.batch), 256, (size_t)rep * a.hd * 12 + (size_t)AT_CH * (a.hd + 4) * 4, s>>>(a);
+    const bool tc = g_attn_fused != 0 && rep <= AF_HEADS && (a.hd == 64 || a.hd == 128);      // shapes the tensor-core kernel carries
+    if (tc) {
+        static bool tc_configured = false;
+        if (!tc_configured) {
+            if (cudaFuncSetAttribute(attn_scores_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess)
+                return cudaGetLastError();
+            tc_configured = true;
+        }
+        const size_t sc_smem = (size_t)AF_HEADS * a.hd * 8 + (size_t)2 * AT_CH * AF_HEADS * 8 + (size_t)AT_CH * (a.hd + 4) * 4 +
+                               (size_t)4 * AF_HEADS * (a.hd + 16);
+        attn_scores_tc_kernel<<<dim3(chunks, a.Hkv, (unsigned)a.batch), 256, sc_smem, s>>>(a);
+    } else
+        attn_scores_kernel<<<dim3(chunks, a.Hkv, (unsigned)a.batch), 256, (size_t)rep * a.hd * 12 + (size_t)AT_CH * (a.hd + 4) * 4, s>>>(a);
     attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H, (unsigned)a.batch), 256, 0, s>>>(a);
-    attn_pv_rows_kernel<<<dim3(1, a.Hkv, (unsigned)a.batch), 256, (size_t)AT_CH * a.hd * 4 + (size_t)AT_CH * AT_MAXREP * 4, s>>>(a);
+    const size_t pv_smem = (size_t)AT_CH * a.hd * 4 + (size_t)AT_CH * AT_MAXREP * 4;
+    if (a.pv_splits > 1 && a.pv_part) {
+        // few (token, KV head) pairs: the key chunks of a pair are shared out over pv_splits CTAs, a small launch adds their sums
+        attn_pv_rows_kernel<<<dim3((unsigned)a.pv_splits, a.Hkv, (unsigned)a.batch), 256, pv_smem, s>>>(a);
+        const long long n_out = (long long)a.batch * a.H * a.hd;
+        attn_pv_finish_kernel<<<(unsigned)((n_out + 255) / 256), 256, 0, s>>>(a);
+        note_launch(1);
+    } else
+        attn_pv_rows_kernel<<<dim3(1, a.Hkv, (unsigned)a.batch), 256, pv_smem, s>>>(a);
     note_launch(4);
     return cudaGetLastError();
 }

@@ -237,6 +237,8 @@ struct AttnArgs {
     long long seq_stride;          // with batch > 0: elements between the caches of consecutive sequences (batched decode: token i is
                                    // sequence i's new token, all at position pos); 0: the tokens are consecutive positions of one sequence
     int chunk;                     // keys per CTA of the one-CTA-per-SM form (filled in by the launcher)
+    int pv_splits;                 // batch > 0: CTAs that share the key chunks of one (token, KV head) pair (0 / 1: one)
+    long long *pv_part;            // scratch [batch][pv_splits][H][hd] for their raw sums
 };
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s);
 // `batch` new tokens at positions pos .. pos + batch - 1 against the cache rows before them and each other (causal):

@@ -18,7 +18,9 @@ HERE = Path(__file__).resolve().parent
 
 
 @pytest.mark.parametrize(("B", "H", "Hkv", "hd", "pos", "window", "rope"), [(3, 4, 2, 64, 20, None, 0), (5, 8, 2, 64, 37, 9, 1),
-                                                                         (2, 8, 1, 128, 130, 64, 1)])
+                                                                         (2, 8, 1, 128, 130, 64, 1),
+                                                                         # long enough for several CTAs to share one pair's key chunks
+                                                                         (2, 8, 2, 64, 700, None, 1), (3, 16, 2, 128, 450, 300, 0)])
 def test_batched_decode_attention_matches_the_checker_per_sequence(B, H, Hkv, hd, pos, window, rope):
     import torch
 
