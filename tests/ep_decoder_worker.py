@@ -14,6 +14,8 @@ SHAPE = dict(n_layers=3, d_model=512, n_heads=8, n_kv=2, head_dim=64, e_ffn=256,
 
 
 def main():
+    import faulthandler
+    faulthandler.dump_traceback_later(100, exit=False)      # a rank that hangs leaves its stack in the log the test shows
     rank, world, port, n_seqs, out_path = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     import torch
@@ -39,8 +41,13 @@ def main():
     np.savez(out_path, ok=ok, t1=t1, x1=x1, t2=m.tokens.cpu().numpy(), x2=m.x.cpu().numpy(),
              k0=m.attn[0]["k"][:, :, SHAPE["context"]:SHAPE["context"] + 2].cpu().numpy())
     if world > 1:
+        # every rank has saved its results; tearing the process group down while a captured graph still holds collective
+        # launches can block, so the graph is released first and the process leaves without the teardown
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        m._graph = None
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
