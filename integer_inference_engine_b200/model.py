@@ -304,3 +304,30 @@ class SyntheticDecoder(Decoder):
         nb = self.d // 256
         per_layer_attn = (2 * self.H * self.hd + 2 * self.Hkv * self.hd) * nb * 144
         return self.moe.weight_bytes_per_token() + self.n_layers * per_layer_attn + self.vocab * nb * 210
+
+
+def host_view(model: "SyntheticDecoder"):
+    """Host copies of everything a CPU checker of a decode step needs, read back from the device: per block the raw
+    GGUF-order blocks of Wq / Wk / Wv / Wo, router and experts, the norm gain and the caches (int64), then the tied
+    embedding, the output gain and the shape.  For small decoders (it copies every tensor)."""
+    from .qk_cuda import Q4_K, Q6_K
+    nb = model.d // 256
+    layers = []
+    for li in range(model.n_layers):
+        a, hs = model.attn[li], model.moe.handles[li]
+        E = model.moe.n_experts
+        qr, kr = model.H * model.hd, model.Hkv * model.hd
+        fused = device.export_weight(a["wqkv"], qr + 2 * kr, nb, Q4_K)           # rows of Wq, Wk, Wv stacked
+        cut = lambda r0, r1: bytes(fused[r0 * nb * 144:r1 * nb * 144])
+        layers.append({
+            "gain": hs["gain"].cpu().numpy(), "wq": cut(0, qr), "wk": cut(qr, qr + kr), "wv": cut(qr + kr, qr + 2 * kr),
+            "wo": device.export_weight(a["wo"], model.d, qr // 256, Q4_K),
+            "k": a["k"].cpu().numpy().astype(np.int64), "v": a["v"].cpu().numpy().astype(np.int64), "full": model.layer_is_full(li),
+            "moe": (device.export_weight(hs["router"], E, nb, Q4_K),
+                    [device.export_weight(h, model.moe.e_ffn, nb, Q4_K) for h in hs["gate"]],
+                    [device.export_weight(h, model.moe.e_ffn, nb, Q4_K) for h in hs["up"]],
+                    [device.export_weight(h, model.d, model.moe.e_ffn // 256, Q6_K) for h in hs["down"]])})
+    cfg = dict(d=model.d, H=model.H, Hkv=model.Hkv, hd=model.hd, eff=model.moe.e_ffn, E=model.moe.n_experts, k=model.top_k,
+               vocab=model.vocab, window=model.window, fa=model.fa, fw=model.fw)
+    embd = device.export_weight(model.embd, model.vocab, nb, Q6_K)
+    return layers, embd, model.out_gain.cpu().numpy(), cfg

@@ -10,27 +10,8 @@ pytestmark = pytest.mark.gpu
 
 
 def _host_view(model):
-    from integer_inference_engine_b200 import device
-    nb = model.d // 256
-    layers = []
-    for li in range(model.n_layers):
-        a, hs = model.attn[li], model.moe.handles[li]
-        E = model.moe.n_experts
-        qr, kr = model.H * model.hd, model.Hkv * model.hd
-        fused = device.export_weight(a["wqkv"], qr + 2 * kr, nb, o.Q4_K)          # rows of Wq, Wk, Wv stacked
-        cut = lambda r0, r1: bytes(fused[r0 * nb * 144:r1 * nb * 144])
-        layers.append({
-            "gain": hs["gain"].cpu().numpy(), "wq": cut(0, qr), "wk": cut(qr, qr + kr), "wv": cut(qr + kr, qr + 2 * kr),
-            "wo": device.export_weight(a["wo"], model.d, model.H * model.hd // 256, o.Q4_K),
-            "k": a["k"].cpu().numpy().astype(np.int64), "v": a["v"].cpu().numpy().astype(np.int64), "full": model.layer_is_full(li),
-            "moe": (device.export_weight(hs["router"], E, nb, o.Q4_K),
-                    [device.export_weight(h, model.moe.e_ffn, nb, o.Q4_K) for h in hs["gate"]],
-                    [device.export_weight(h, model.moe.e_ffn, nb, o.Q4_K) for h in hs["up"]],
-                    [device.export_weight(h, model.d, model.moe.e_ffn // 256, o.Q6_K) for h in hs["down"]])})
-    cfg = dict(d=model.d, H=model.H, Hkv=model.Hkv, hd=model.hd, eff=model.moe.e_ffn, E=model.moe.n_experts, k=model.top_k,
-               vocab=model.vocab, window=model.window, fa=model.fa, fw=model.fw)
-    embd = device.export_weight(model.embd, model.vocab, nb, o.Q6_K)
-    return layers, embd, model.out_gain.cpu().numpy(), cfg
+    from integer_inference_engine_b200.model import host_view
+    return host_view(model)
 
 
 FORMS = pytest.mark.parametrize(("one_launch", "fused_block"), [(True, True), (False, True), (False, False)],
