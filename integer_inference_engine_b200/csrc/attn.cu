@@ -588,6 +588,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const AttnArgs a_in) {
 // thread owns two output dimensions of four heads for a quarter of the keys).
 constexpr int AF_THREADS = 512;
 constexpr int AF_HEADS = 8;                  // query heads per KV head this form carries
+constexpr int TS_CHUNKS = 4;                 // 64-key chunks one CTA of attn_scores_tc_kernel walks
 constexpr unsigned AF_POLLS = 1u << 22;
 
 __device__ __forceinline__ uint32_t af_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -924,15 +925,30 @@ __global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in
     __shared__ int s_wide;
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, hd = a.hd, half = hd / 2;
     const int ld = hd + 4, qld = hd + 16;
-    const long long l0 = a.lo + (long long)blockIdx.x * AT_CH, l1 = min(l0 + AT_CH, a.pos + 1);
-    if (l0 > a.pos) return;                                // a chunk past this token's position
-    const int nk = (int)max(0LL, l1 - l0);
+    // a CTA walks TS_CHUNKS consecutive 64-key chunks: the queries are rotated once and the next chunk's keys stream in
+    // (cp.async into the other buffer) while the current chunk is multiplied
+    const long long first = a.lo + (long long)blockIdx.x * TS_CHUNKS * AT_CH;
+    if (first > a.pos) return;                             // all of this CTA's chunks lie past the token's position
     long long *q64 = reinterpret_cast<long long *>(ts_smem);                 // [8][hd]
     long long *dots = q64 + AF_HEADS * hd;                                  // [2][64][8]
-    int32_t *sk = reinterpret_cast<int32_t *>(dots + 2 * AT_CH * AF_HEADS); // [64][hd + 4]
-    int8_t *qd = reinterpret_cast<int8_t *>(sk + AT_CH * ld);               // [4][8][hd + 16]
+    int32_t *skb = reinterpret_cast<int32_t *>(dots + 2 * AT_CH * AF_HEADS); // two key buffers [64][hd + 4]
+    int8_t *qd = reinterpret_cast<int8_t *>(skb + 2 * AT_CH * ld);          // [4][8][hd + 16]
     if (tid == 0) s_wide = 0;
     if (tid < AF_HEADS) s_max[tid] = INT64_MIN;
+    const int vec_per_row = hd / 4;
+    auto request = [&](int c) {                            // keys of chunk c of this CTA into buffer c & 1
+        const long long l0 = first + (long long)c * AT_CH;
+        const int nk = (int)max(0LL, min(l0 + AT_CH, a.pos + 1) - l0);
+        const int4 *src = reinterpret_cast<const int4 *>(a.kcache + ((long long)kv * a.Lmax + l0) * hd);
+        int32_t *dst = skb + (size_t)(c & 1) * AT_CH * ld;
+        for (int i = tid; i < nk * vec_per_row; i += blockDim.x) {
+            const int row = i / vec_per_row;
+            const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst + row * ld + (i - row * vec_per_row) * 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + i) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    request(0);
     __syncthreads();
     bool wide = false;
     for (int idx = tid; idx < AF_HEADS * half; idx += blockDim.x) {
@@ -953,75 +969,87 @@ __global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in
         wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
     }
     if (wide) s_wide = 1;
-    const int vec_per_row = hd / 4;
-    at_stage(reinterpret_cast<const int4 *>(a.kcache + ((long long)kv * a.Lmax + l0) * hd), nk * vec_per_row, tid, blockDim.x, sk,
-             [&](int i) { const int row = i / vec_per_row; return row * ld + (i - row * vec_per_row) * 4; });
     __syncthreads();
     const bool use_wide = s_wide != 0;
     const int ksteps = hd / 32;
     const bool split = (ksteps & 1) == 0;                  // four 16-key tiles: two warps per tile, half of the head dimension each
-    if (!use_wide) {
-        const int kt = split ? (warp >> 1) : warp, kh = split ? (warp & 1) : 0;
-        const int s_lo = split ? kh * (ksteps / 2) : 0, s_hi = split ? s_lo + ksteps / 2 : ksteps;
-        if (kt < AT_CH / 16 && kt * 16 < nk) {
-            int acc[7][4];
+    const int key = tid & (AT_CH - 1);                     // thread -> (key, heads tid / 64 and tid / 64 + 4) for the score stores
+    long long mloc[2] = {INT64_MIN, INT64_MIN};
+    for (int c = 0; c < TS_CHUNKS; c++) {
+        const long long l0 = first + (long long)c * AT_CH;
+        if (l0 > a.pos) break;                             // uniform over the CTA
+        const int nk = (int)(min(l0 + AT_CH, a.pos + 1) - l0);
+        const bool more = c + 1 < TS_CHUNKS && l0 + AT_CH <= a.pos;
+        if (more) { request(c + 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                   // chunk c has landed for every thread
+        const int32_t *sk = skb + (size_t)(c & 1) * AT_CH * ld;
+        if (!use_wide) {
+            const int kt = split ? (warp >> 1) : warp, kh = split ? (warp & 1) : 0;
+            const int s_lo = split ? kh * (ksteps / 2) : 0, s_hi = split ? s_lo + ksteps / 2 : ksteps;
+            if (kt < AT_CH / 16 && kt * 16 < nk) {
+                int acc[7][4];
 #pragma unroll
-            for (int i = 0; i < 7; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0; }
-            const int g = lane >> 2, t = lane & 3;
-            const int32_t *rowA = sk + (size_t)(kt * 16 + g) * ld, *rowB = rowA + 8 * ld;
-            for (int st = s_lo; st < s_hi; st++) {
-                uint32_t A[4][4];
-                af_bytes(*reinterpret_cast<const int4 *>(rowA + 32 * st + 4 * t), A[0][0], A[1][0], A[2][0], A[3][0]);
-                af_bytes(*reinterpret_cast<const int4 *>(rowB + 32 * st + 4 * t), A[0][1], A[1][1], A[2][1], A[3][1]);
-                af_bytes(*reinterpret_cast<const int4 *>(rowA + 32 * st + 16 + 4 * t), A[0][2], A[1][2], A[2][2], A[3][2]);
-                af_bytes(*reinterpret_cast<const int4 *>(rowB + 32 * st + 16 + 4 * t), A[0][3], A[1][3], A[2][3], A[3][3]);
+                for (int i = 0; i < 7; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0; }
+                const int g = lane >> 2, t = lane & 3;
+                const int32_t *rowA = sk + (size_t)(kt * 16 + g) * ld, *rowB = rowA + 8 * ld;
+                for (int st = s_lo; st < s_hi; st++) {
+                    uint32_t A[4][4];
+                    af_bytes(*reinterpret_cast<const int4 *>(rowA + 32 * st + 4 * t), A[0][0], A[1][0], A[2][0], A[3][0]);
+                    af_bytes(*reinterpret_cast<const int4 *>(rowB + 32 * st + 4 * t), A[0][1], A[1][1], A[2][1], A[3][1]);
+                    af_bytes(*reinterpret_cast<const int4 *>(rowA + 32 * st + 16 + 4 * t), A[0][2], A[1][2], A[2][2], A[3][2]);
+                    af_bytes(*reinterpret_cast<const int4 *>(rowB + 32 * st + 16 + 4 * t), A[0][3], A[1][3], A[2][3], A[3][3]);
 #pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    const int8_t *qb = qd + (b * AF_HEADS + g) * qld + 32 * st + 4 * t;
-                    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(qb), b1 = *reinterpret_cast<const uint32_t *>(qb + 16);
+                    for (int b = 0; b < 4; b++) {
+                        const int8_t *qb = qd + (b * AF_HEADS + g) * qld + 32 * st + 4 * t;
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(qb), b1 = *reinterpret_cast<const uint32_t *>(qb + 16);
 #pragma unroll
-                    for (int aa = 0; aa < 4; aa++) {
-                        if (aa < 3 && b < 3) af_mma<false, false>(acc[aa + b], A[aa], b0, b1);
-                        else if (aa < 3) af_mma<false, true>(acc[aa + b], A[aa], b0, b1);
-                        else if (b < 3) af_mma<true, false>(acc[aa + b], A[aa], b0, b1);
-                        else af_mma<true, true>(acc[aa + b], A[aa], b0, b1);
+                        for (int aa = 0; aa < 4; aa++) {
+                            if (aa < 3 && b < 3) af_mma<false, false>(acc[aa + b], A[aa], b0, b1);
+                            else if (aa < 3) af_mma<false, true>(acc[aa + b], A[aa], b0, b1);
+                            else if (b < 3) af_mma<true, false>(acc[aa + b], A[aa], b0, b1);
+                            else af_mma<true, true>(acc[aa + b], A[aa], b0, b1);
+                        }
                     }
                 }
-            }
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
+                for (int i = 0; i < 4; i++) {
+                    long long dot = 0;
+#pragma unroll
+                    for (int w = 6; w >= 0; w--) dot = dot * 256 + (long long)acc[w][i];
+                    const int row = kt * 16 + g + (i >= 2 ? 8 : 0), col = 2 * t + (i & 1);
+                    dots[((size_t)kh * AT_CH + row) * AF_HEADS + col] = dot;
+                }
+            }
+        } else {
+            for (int i = tid; i < nk * AF_HEADS; i += blockDim.x) {         // a query value beyond int32: wrapping 64-bit products
+                const int kk2 = i >> 3, h = i & 7;
                 long long dot = 0;
+                if (h < rep) {
+                    const int32_t *kk = sk + (size_t)kk2 * ld;
+                    for (int j = 0; j < hd; j++) dot += q64[h * hd + j] * (long long)kk[j];
+                }
+                dots[i] = dot;
+            }
+        }
+        __syncthreads();
 #pragma unroll
-                for (int w = 6; w >= 0; w--) dot = dot * 256 + (long long)acc[w][i];
-                const int row = kt * 16 + g + (i >= 2 ? 8 : 0), col = 2 * t + (i & 1);
-                dots[((size_t)kh * AT_CH + row) * AF_HEADS + col] = dot;
+        for (int u = 0; u < 2; u++) {
+            const int h = (tid >> 6) + 4 * u;
+            if (key < nk && h < rep) {
+                long long d = dots[key * AF_HEADS + h];
+                if (split && !use_wide) d += dots[(size_t)(AT_CH + key) * AF_HEADS + h];
+                const long long sc = ((d >> a.fa) * a.inv_sqrt) >> a.fa;
+                a.scores[(long long)(kv * rep + h) * Ls + l0 + key] = sc;
+                mloc[u] = max(mloc[u], sc);
             }
         }
-    } else {
-        for (int i = tid; i < nk * AF_HEADS; i += blockDim.x) {             // a query value beyond int32: wrapping 64-bit products
-            const int key = i >> 3, h = i & 7;
-            long long dot = 0;
-            if (h < rep) {
-                const int32_t *kk = sk + (size_t)key * ld;
-                for (int j = 0; j < hd; j++) dot += q64[h * hd + j] * (long long)kk[j];
-            }
-            dots[i] = dot;
-        }
+        __syncthreads();                                   // dots and the buffer of chunk c may be overwritten
     }
-    __syncthreads();
-    // thread -> (key = tid % 64, heads tid / 64 and tid / 64 + 4): a warp stores 32 consecutive keys of one head
-    const int key = tid & (AT_CH - 1);
 #pragma unroll
     for (int u = 0; u < 2; u++) {
         const int h = (tid >> 6) + 4 * u;
-        long long sc = INT64_MIN;
-        if (key < nk && h < rep) {
-            long long d = dots[key * AF_HEADS + h];
-            if (split && !use_wide) d += dots[(size_t)(AT_CH + key) * AF_HEADS + h];
-            sc = ((d >> a.fa) * a.inv_sqrt) >> a.fa;
-            a.scores[(long long)(kv * rep + h) * Ls + l0 + key] = sc;
-        }
-        long long m = sc;
+        long long m = mloc[u];
 #pragma unroll
         for (int s2 = 16; s2 > 0; s2 >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s2));
         if (lane == 0 && m != INT64_MIN && h < rep) atomicMax(&s_max[h], m);
@@ -1223,9 +1251,9 @@ cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s) {
                 return cudaGetLastError();
             tc_configured = true;
         }
-        const size_t sc_smem = (size_t)AF_HEADS * a.hd * 8 + (size_t)2 * AT_CH * AF_HEADS * 8 + (size_t)AT_CH * (a.hd + 4) * 4 +
+        const size_t sc_smem = (size_t)AF_HEADS * a.hd * 8 + (size_t)2 * AT_CH * AF_HEADS * 8 + (size_t)2 * AT_CH * (a.hd + 4) * 4 +
                                (size_t)4 * AF_HEADS * (a.hd + 16);
-        attn_scores_tc_kernel<<<dim3(chunks, a.Hkv, (unsigned)a.batch), 256, sc_smem, s>>>(a);
+        attn_scores_tc_kernel<<<dim3((chunks + TS_CHUNKS - 1) / TS_CHUNKS, a.Hkv, (unsigned)a.batch), 256, sc_smem, s>>>(a);
     } else
         attn_scores_kernel<<<dim3(chunks, a.Hkv, (unsigned)a.batch), 256, (size_t)rep * a.hd * 12 + (size_t)AT_CH * (a.hd + 4) * 4, s>>>(a);
     attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H, (unsigned)a.batch), 256, 0, s>>>(a);
