@@ -34,6 +34,9 @@ __device__ __forceinline__ bool bt_wait(uint64_t *bar) {
     return false;
 }
 
+// dense items pay when ceil(rows / 8) * digits walks (each a little dearer than a digit-column walk) undercut one walk per row
+__device__ __forceinline__ bool bt_dense(int rows, int digits) { return ((rows + 7) / 8) * digits * 23 < rows * 20; }
+
 template <int QT, int MODE, bool FAST>
 __global__ void __launch_bounds__(BT_WARPS * 32, 2) batch_kernel(const BatchArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -52,13 +55,18 @@ __global__ void __launch_bounds__(BT_WARPS * 32, 2) batch_kernel(const BatchArgs
     const int my_tiles = (int)max(0LL, min((long long)tpc, (long long)a.n_groups * tpe - tile0));
 
     for (int i = tid; i < tpc; i += blockDim.x) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bt_u32(&bars[i])));
+    // Digits in use by the activations (8 when unknown).  An expert with enough rows takes "dense" items: eight rows are the
+    // eight MMA columns and the item walks K once per digit, so the weight codes are unpacked ceil(rows / 8) * digits times
+    // instead of once per row.  bt_dense() decides per expert (the same in every thread).
+    const int nl_x = a.x_nl ? max(1, min(8, *a.x_nl)) : 8;
     if (tid == 0) {
         s_timeout = 0;
         int run = 0;
         for (int i = 0; i < my_tiles; i++) {
             const int e = (int)((tile0 + i) / tpe);
             t_off[i] = run;
-            run += a.grp_off[e + 1] - a.grp_off[e];
+            const int rows = a.grp_off[e + 1] - a.grp_off[e];
+            run += bt_dense(rows, nl_x) ? (rows + 7) / 8 : rows;
         }
         for (int i = my_tiles; i <= tpc; i++) t_off[i] = run;
     }
@@ -90,6 +98,66 @@ __global__ void __launch_bounds__(BT_WARPS * 32, 2) batch_kernel(const BatchArgs
         while (it >= t_off[ti + 1]) ti++;                              // items are ordered by tile
         const long long tau = tile0 + ti;
         const int e = (int)(tau / tpe), p = (int)(tau - (long long)e * tpe);
+        const int rows_e = a.grp_off[e + 1] - a.grp_off[e];
+        if (bt_dense(rows_e, nl_x)) {
+            // ---- dense item: rows pair0 .. pair0 + 7 of this expert are the MMA columns; one walk of K per digit ----------------
+            const int pair0 = a.grp_off[e] + 8 * (it - t_off[ti]), last = a.grp_off[e] + rows_e;
+            const int pcol = min(pair0 + g, last - 1);                  // a column past the expert's rows repeats the last row (result unused)
+            const long long xr = a.xidx ? a.xidx[pcol] : pcol;
+            if (!bt_wait(&bars[ti])) { s_timeout = 1; continue; }
+            const uint8_t *ua0 = wbuf + (size_t)ti * tile_bytes;
+            i128 tot[4] = {0, 0, 0, 0};
+            for (int l = 0; l < nl_x; l++) {
+                const int8_t *xc = a.xl + (xr * 8 + l) * K;
+                int64_t acc[4] = {0, 0, 0, 0};
+                for (int b = 0; b < nb; b++) {
+                    uint32_t bf[16];
+                    load_bfrag<QT, true>(xc + (long long)b * 256, t, bf);
+                    const uint8_t *ua = ua0 + (size_t)b * HTB;
+                    const uint8_t *ub = (MODE == MODE_GATEUP || 2 * p + 1 < n_ht) ? ua + (size_t)nb * HTB : ua;
+                    run_item<QT, FAST>(ua, ub, lane, a.fw, bf, false, acc);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) tot[i] += (i128)acc[i] << (8 * l);
+            }
+            int64_t y[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) y[i] = (int64_t)(tot[i] >> a.fw);
+#pragma unroll
+            for (int c = 0; c < 2; c++) {                               // this lane's two columns: rows pair0 + 2t, pair0 + 2t + 1
+                const int pair = pair0 + 2 * t + c;
+                if (pair >= last) continue;
+                if (MODE == MODE_GATEUP) {
+                    const long long row = (long long)p * 8 + g;         // MMA rows 0..7 gate, 8..15 up of the same output index
+                    if (row < a.out_f) {
+                        const int64_t yg = y[c], yu = y[2 + c];
+                        const int64_t sg = mul_shift(yg, sigmoid_fixed_c(yg, a.fa, a.sig_log2e, a.sig_clip), a.fa);
+                        const int64_t gu = mul_shift(sg, yu, a.fa);
+                        if (a.out) a.out[(long long)pair * a.out_f + row] = gu;
+                        bool ok;
+                        const uint64_t dg = balanced_digits8(gu, ok);
+                        if (!ok) atomicOr(a.flags, 1);
+                        nl = max(nl, digits_used(dg));
+#pragma unroll
+                        for (int l = 0; l < 8; l++) a.out_limbs[((long long)pair * 8 + l) * a.out_f + row] = (int8_t)(dg >> (8 * l));
+                    }
+                } else {
+#pragma unroll
+                    for (int hrow = 0; hrow < 2; hrow++) {
+                        const long long row = (long long)p * 16 + g + 8 * hrow;
+                        if (row >= a.out_f || (hrow && 2 * p + 1 >= n_ht)) continue;
+                        const int64_t yv = y[2 * hrow + c];
+                        if (MODE == MODE_LINEAR) a.out[(long long)pair * a.out_f + row] = yv;
+                        else {
+                            const long long tok = a.pair_tok ? a.pair_tok[pair] : pair;
+                            atomicAdd(reinterpret_cast<unsigned long long *>(a.out + tok * a.out_f + row),
+                                      (unsigned long long)mul_shift(yv, a.gates[pair], a.fa));
+                        }
+                    }
+                }
+            }
+            continue;
+        }
         const int pair = a.grp_off[e] + (it - t_off[ti]);
         const long long xrow = a.xidx ? a.xidx[pair] : pair;
         const int8_t *xcol = a.xl + (xrow * 8 + col_limb(g)) * K;
@@ -137,6 +205,7 @@ __global__ void __launch_bounds__(BT_WARPS * 32, 2) batch_kernel(const BatchArgs
         }
     }
     if (MODE == MODE_GATEUP && a.out_nl) {
+        nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 16)); nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 8));
         nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 4)); nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 2));
         nl = max(nl, __shfl_xor_sync(0xffffffffu, nl, 1));
         if (lane == 0 && nl > 0) atomicMax(a.out_nl, nl);
