@@ -195,9 +195,15 @@ bool linear_dev(const Weight &w, const int64_t *x, long long T, int fw, int64_t 
     if (!fast_envelope(w.qtype, w.nb, w.maxd, w.maxdmin, fw))
         return launch_exact_linear((const uint8_t *)w.d, w.qtype, w.out_f, w.nb, x, T, fw, out, s) == cudaSuccess;
     const int8_t *xl = xl_ready;
+    const int *x_nl = nullptr;                             // digits in use by the rows, where the planes are made here
     if (!xl) {
         int8_t *buf = (int8_t *)ensure(R_XL, (size_t)T * 8 * K);
-        if (!buf || launch_limbs(x, T, K, buf, g_flags, s) != cudaSuccess) return false;
+        if (!buf) return false;
+        if (T >= 2) {
+            if (cudaMemsetAsync(g_cells + 4, 0, sizeof(int), s) != cudaSuccess) return false;
+            x_nl = g_cells + 4;
+        }
+        if (launch_limbs(x, T, K, buf, g_flags, s, const_cast<int *>(x_nl)) != cudaSuccess) return false;
         xl = buf;
     }
     if (T == 1 && w.out_f >= 256 && g_stage_mask == 0) {
@@ -213,7 +219,7 @@ bool linear_dev(const Weight &w, const int64_t *x, long long T, int fw, int64_t 
         if (!off || launch_set2(off, 0, (int)T, s) != cudaSuccess) return false;
         BatchArgs ba = {};
         ba.wa = w.cell; ba.wb = w.cell; ba.grp_off = off; ba.n_groups = 1; ba.out_f = w.out_f; ba.n_blocks = w.nb; ba.fw = fw; ba.fa = 16;
-        ba.fast = small_scales(w.maxd, w.maxdmin, fw); ba.xl = xl; ba.out = out; ba.flags = g_flags;
+        ba.fast = small_scales(w.maxd, w.maxdmin, fw); ba.xl = xl; ba.x_nl = x_nl; ba.out = out; ba.flags = g_flags;
         if (launch_batch(w.qtype, MODE_LINEAR, ba, s) != cudaSuccess) return false;
     } else {
         SkinnyArgs a = {};
