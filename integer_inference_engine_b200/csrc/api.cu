@@ -1061,7 +1061,7 @@ extern "C" int iie_attn_decode_batch_dev(const int64_t *q_dev, const int64_t *k_
     a.out = out_dev; a.flags = g_flags;
     // few sequences leave most SMs idle in the probability x value pass: share each pair's chunks over up to eight CTAs
     const long long pairs = n_seqs * n_kv;
-    int splits = (int)std::min<long long>(8, std::min<long long>(Ls / 64, (1184 + pairs - 1) / pairs));
+    int splits = (int)std::min<long long>(8, std::min<long long>(Ls / 64, (2368 + pairs - 1) / pairs));   // about two CTAs per SM, four waves
     if (splits > 1) {
         a.pv_part = (long long *)ensure(R_BPART, (size_t)n_seqs * splits * n_heads * head_dim * 8);
         if (!a.pv_part) return 1;

@@ -327,28 +327,46 @@ __global__ void __launch_bounds__(128) attn_append_kernel(const AttnArgs a) {
     for (int r = tid; r < rep; r += blockDim.x) { a.hmax[i * a.H + kv * rep + r] = INT64_MIN; a.Z[i * a.H + kv * rep + r] = 0ULL; }
 }
 
-// prefill pass 3: one CTA per (token, KV head) walks the token's key chunks, keeps the probability-value sums in
-// registers and writes the shifted result; grid (1, Hkv, batch)
+// prefill / batched pass 3: one CTA per (token, KV head[, share of the chunks]) walks key chunks; the next chunk's values
+// stream in (cp.async, second buffer) while the current one is multiplied.  A thread owns two output dimensions of four
+// query heads for one part of a chunk's keys (one value load and one probability load per eight multiply-adds); the
+// parts are added through shared memory at the end.  grid (pv_splits or 1, Hkv, batch)
 __global__ void __launch_bounds__(256) attn_pv_rows_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
     at_batch(a);
     const long long Ls = a.Ls ? a.Ls : a.Lmax;
-    extern __shared__ __align__(16) int32_t at_v[];        // [AT_CH][hd] values, then [AT_CH][AT_MAXREP] probabilities
-    const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x;
-    int32_t *s_p = at_v + AT_CH * a.hd;
-    const int G = blockDim.x / a.hd, grp = tid / a.hd, d = tid - grp * a.hd;
+    extern __shared__ __align__(16) int32_t at_v[];        // two value buffers [AT_CH][hd], probabilities [AT_CH][AT_MAXREP], sums
+    const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, hd = a.hd, half = hd / 2;
+    int32_t *s_p = at_v + 2 * AT_CH * hd;
+    long long *red = reinterpret_cast<long long *>(s_p + AT_CH * AT_MAXREP);            // [KQ][AT_MAXREP][hd]
+    const int KQ = blockDim.x / hd;                        // parts of a chunk's keys
+    const int dp = tid % half, hh = (tid / half) & 1, kq = tid / hd;
     // with pv_splits > 1 this CTA takes a contiguous share of the key chunks and leaves raw sums for attn_pv_finish_kernel
     const int splits = a.pv_splits > 1 ? a.pv_splits : 1;
     const long long n_chunks = (a.pos - a.lo) / AT_CH + 1, per = (n_chunks + splits - 1) / splits;
     const long long c_lo = (long long)blockIdx.x * per, c_hi = min(n_chunks, c_lo + per);
-    for (int rbase = 0; rbase < rep; rbase += G * 4) {                     // one pass per G*4 query heads
-        const int r0 = rbase + grp * 4;
-        long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
-        for (long long l0 = a.lo + c_lo * AT_CH; l0 < a.lo + c_hi * AT_CH; l0 += AT_CH) {
+    const int vec_per_chunk = AT_CH * hd / 4;
+    auto request = [&](long long c) {                      // values of chunk c into buffer c & 1
+        const long long l0 = a.lo + c * AT_CH;
+        const int nk = (int)min((long long)AT_CH, a.pos + 1 - l0);
+        const int4 *src = reinterpret_cast<const int4 *>(a.vcache + ((long long)kv * a.Lmax + l0) * hd);
+        int32_t *dst = at_v + (size_t)(c & 1) * AT_CH * hd;
+        for (int i = tid; i < nk * (hd / 4) && i < vec_per_chunk; i += blockDim.x) {
+            const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst + i * 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + i) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int rbase = 0; rbase < rep; rbase += 8) {                          // eight query heads per pass
+        long long c[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};
+        if (c_lo < c_hi) request(c_lo);
+        for (long long ch = c_lo; ch < c_hi; ch++) {
+            const long long l0 = a.lo + ch * AT_CH;
             const int nk = (int)min((long long)AT_CH, a.pos + 1 - l0);
-            __syncthreads();                                                // the previous chunk has been consumed
-            for (int i = tid; i < AT_MAXREP * AT_CH; i += blockDim.x) {
-                const int j = i / AT_MAXREP, r = i - j * AT_MAXREP;
+            __syncthreads();                                                // the previous chunk's probabilities and its buffer are free
+            if (ch + 1 < c_hi) request(ch + 1);
+            for (int i = tid; i < 8 * AT_CH; i += blockDim.x) {
+                const int j = i >> 3, r = rbase + (i & 7);
                 int32_t p = 0;
                 if (j < nk && r < rep) {
                     const int h = kv * rep + r;
@@ -358,26 +376,33 @@ __global__ void __launch_bounds__(256) attn_pv_rows_kernel(const AttnArgs a_in) 
                 }
                 s_p[i] = p;
             }
-            at_stage(reinterpret_cast<const int4 *>(a.vcache + ((long long)kv * a.Lmax + l0) * a.hd), nk * (a.hd / 4), tid, blockDim.x,
-                     at_v, [](int i) { return i * 4; });
+            if (ch + 1 < c_hi) asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();
-            if (grp < G && r0 < rep) {
-                for (int j = 0; j < nk; j++) {
-                    const int32_t v = at_v[j * a.hd + d];
-                    const int4 p4 = *reinterpret_cast<const int4 *>(s_p + j * AT_MAXREP + r0);
-                    c0 += (long long)p4.x * v; c1 += (long long)p4.y * v; c2 += (long long)p4.z * v; c3 += (long long)p4.w * v;
-                }
+            const int32_t *sv = at_v + (size_t)(ch & 1) * AT_CH * hd;
+            const int perk = (nk + KQ - 1) / KQ, j0 = min(nk, kq * perk), j1 = min(nk, j0 + perk);
+            for (int j = j0; j < j1; j++) {
+                const int2 v2 = *reinterpret_cast<const int2 *>(sv + (size_t)j * hd + 2 * dp);
+                const int4 p4 = *reinterpret_cast<const int4 *>(s_p + j * 8 + 4 * hh);
+                c[0][0] += (long long)p4.x * v2.x; c[0][1] += (long long)p4.x * v2.y;
+                c[1][0] += (long long)p4.y * v2.x; c[1][1] += (long long)p4.y * v2.y;
+                c[2][0] += (long long)p4.z * v2.x; c[2][1] += (long long)p4.z * v2.y;
+                c[3][0] += (long long)p4.w * v2.x; c[3][1] += (long long)p4.w * v2.y;
             }
         }
-        if (grp < G) {
-            const long long cs[4] = {c0, c1, c2, c3};
+        __syncthreads();
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                if (r0 + u >= rep) continue;
-                const long long o = (long long)(kv * rep + r0 + u) * a.hd + d;
-                if (splits == 1) a.out[o] = cs[u] >> a.fa;
-                else a.pv_part[(((long long)blockIdx.z * splits + blockIdx.x) * a.H) * a.hd + o] = cs[u];
-            }
+        for (int u = 0; u < 4; u++)
+            *reinterpret_cast<longlong2 *>(red + ((size_t)kq * 8 + 4 * hh + u) * hd + 2 * dp) = make_longlong2(c[u][0], c[u][1]);
+        __syncthreads();
+        for (int o = tid; o < 8 * hd; o += blockDim.x) {
+            const int r = rbase + o / hd, d = o % hd;
+            if (r >= rep) continue;
+            long long sum = 0;
+            for (int g = 0; g < KQ; g++) sum += red[(size_t)g * 8 * hd + o];
+            const long long oo = (long long)(kv * rep + r) * hd + d;
+            if (splits == 1) a.out[oo] = sum >> a.fa;
+            else a.pv_part[(((long long)blockIdx.z * splits + blockIdx.x) * a.H) * hd + oo] = sum;
         }
     }
 }
@@ -1233,7 +1258,7 @@ cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attn_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
-            cudaFuncSetAttribute(attn_pv_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess)
+            cudaFuncSetAttribute(attn_pv_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
             return cudaGetLastError();
         configured = true;
     }
@@ -1257,7 +1282,8 @@ cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s) {
     } else
         attn_scores_kernel<<<dim3(chunks, a.Hkv, (unsigned)a.batch), 256, (size_t)rep * a.hd * 12 + (size_t)AT_CH * (a.hd + 4) * 4, s>>>(a);
     attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H, (unsigned)a.batch), 256, 0, s>>>(a);
-    const size_t pv_smem = (size_t)AT_CH * a.hd * 4 + (size_t)AT_CH * AT_MAXREP * 4;
+    const size_t pv_smem = (size_t)2 * AT_CH * a.hd * 4 + (size_t)AT_CH * AT_MAXREP * 4 + (size_t)(256 / a.hd) * 8 * a.hd * 8;
+    if (256 % a.hd) return cudaErrorInvalidValue;                    // the probability x value pass splits 256 threads over the head dimension
     if (a.pv_splits > 1 && a.pv_part) {
         // few (token, KV head) pairs: the key chunks of a pair are shared out over pv_splits CTAs, a small launch adds their sums
         attn_pv_rows_kernel<<<dim3((unsigned)a.pv_splits, a.Hkv, (unsigned)a.batch), 256, pv_smem, s>>>(a);
