@@ -69,7 +69,7 @@ inline bool stage_on(int st) { return g_stage_mask == 0 || (g_stage_mask & st); 
 
 // Persistent device scratch by role, grown on demand (never shrunk until released).
 enum Role { R_X, R_XL, R_OUT, R_RAW, R_GU, R_GUL, R_TMP0, R_TMP1, R_TMP2, R_TABS, R_META, R_LOGITS, R_IDS, R_GATES,
-            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_ASCORES, R_AEXP, R_ASTAT, R_APART, R_PSCORES, R_PEXP, R_PSTAT, R_BSCORES, R_BEXP, R_BSTAT, R_BPART, R_COUNT };
+            R_GRPOFF, R_PAIRTOK, R_PAIRGATE, R_HNORM, R_ZERO, R_ASCORES, R_AEXP, R_ASTAT, R_APART, R_PSCORES, R_PEXP, R_PSTAT, R_BSCORES, R_BEXP, R_BSTAT, R_BPART, R_XG, R_COUNT };
 struct Buf { void *p = nullptr; size_t cap = 0; };
 Buf g_buf[R_COUNT];
 long long g_ws_allocs = 0;
@@ -335,11 +335,12 @@ int grouped_tc(const GroupedWeights &w, int n_groups, const int *off, const int 
     if (max_weight(QT_Q4K, w.maxd_gate, w.maxdmin_gate, fw) > CAP4) return -1;
     if (max_weight(w.down_q, w.maxd_down, w.maxdmin_down, fw) > (w.down_q == QT_Q4K ? CAP4 : (unsigned __int128)0x7FFFFFFFULL * 32)) return -1;   // Q6_K: d_q * 128 stays in int32
     int8_t *gul = (int8_t *)ensure(R_GUL, (size_t)P * 8 * w.e_ffn);
-    if (!gul) return 1;
+    int8_t *xg = xidx ? (int8_t *)ensure(R_XG, (size_t)P * 4 * w.d_model) : nullptr;
+    if (!gul || (xidx && !xg)) return 1;
     if (cudaMemsetAsync(g_cells + 1, 0, sizeof(int), s) != cudaSuccess) return 1;
     PrefillArgs ga = {};
     ga.wa = w.gate; ga.wb = w.up; ga.grp_off = off; ga.n_experts = n_groups; ga.n_pairs = P; ga.out_f = w.e_ffn;
-    ga.n_blocks = w.d_model / 256; ga.fw = fw; ga.fa = fa; ga.xl = hl; ga.xidx = xidx; ga.out = nullptr; ga.out_limbs = gul;
+    ga.n_blocks = w.d_model / 256; ga.fw = fw; ga.fa = fa; ga.xl = hl; ga.xidx = xidx; ga.xg = xg; ga.out = nullptr; ga.out_limbs = gul;
     ga.out_nl = g_cells + 1; ga.flags = g_flags;
     if (launch_prefill(QT_Q4K, MODE_GATEUP, nl_h, ga, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     const int nl_gu = read_cell(1, s);

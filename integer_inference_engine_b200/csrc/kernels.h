@@ -142,6 +142,7 @@ struct PrefillArgs {
     long long sig_log2e, sig_clip;
     const int8_t *xl;              // activation limb planes [x_row][8][K]
     const int *xidx;               // pair -> x_row, or nullptr (identity)
+    int8_t *xg;                    // with xidx: scratch for the planes gathered into pair order, n_pairs * 4 * K bytes
     int64_t *out;                  // GATEUP: gu [pair][out_f] (nullable); DOWN: [token][out_f] accumulated; LINEAR [pair][out_f]
     int8_t *out_limbs;             // GATEUP: limb planes of gu [pair][8][out_f]
     int *out_nl;                   // GATEUP: atomicMax of the limbs gu needs

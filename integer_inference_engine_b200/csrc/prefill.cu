@@ -11,13 +11,20 @@
 // min(NWL,NL) pairs x K x 128 x 128 < 2^31 for K <= 8192), the accumulation runs over the FULL K, and the
 // epilogue forms sum_s 256^s acc_s in 128 bits and performs the reference's single floor shift.
 //
-// Tile: 128 (token, expert) pairs (MMA M, TMEM lanes) x BN weight rows (MMA N) x K in chunks of 64.
-// Three groups of four warps produce, one shared-memory stage each: they copy the activation digit planes of
-// their pair into the canonical K-major layout with cp.async (A operand, no register staging) and dequantise +
-// digit-split the weight chunk (B operand); then they run the epilogue, one TMEM lane = one pair each.  The last
-// warp allocates TMEM and one elected thread issues the MMAs; tcgen05.commit hands a stage back to its group.  Gate and up rows share a tile
-// (columns 0..BN/2-1 gate, BN/2..BN-1 up) so the integer SiLU * up product is formed in the epilogue.
+// Tile: 128 weight rows (MMA M, TMEM lanes) x BN (token, expert) pairs (MMA N, TMEM columns) x K in chunks of 64.  The
+// weights sit on the wide side because a dequantised weight costs 0.56 bytes of traffic per element and an activation NL
+// bytes: the pair side is the one TMEM limits (accumulators x BN <= 512 columns), so it carries the expensive operand.
+// Three groups of four warps produce, one shared-memory stage each: one thread asks the copy engine (TMA, 64-byte
+// swizzle) for the activation digit planes of the tile's pairs (B operand), and every thread dequantises + digit-splits
+// the 64 chunk columns of its weight row into the canonical K-major layout (A operand); then the groups run the epilogue,
+// one TMEM lane = one weight row each.  The last warps allocate TMEM and issue the MMAs; tcgen05.commit hands a stage back
+// to its group.  Gate and up rows share a tile (lanes 0..63 gate, 64..127 up) and trade halves of their columns through
+// shared memory, so the integer SiLU * up product is formed in the epilogue by all 128 threads.
+// Activation rows reached through an index (pair -> token) are first gathered into pair order, NL planes per pair, so
+// that a tile's rows are consecutive for the copy engine.
 // Every wait is bounded; on a time-out the CTA raises flag bit 3, leaves its loops, frees TMEM and exits.
+#include <cuda.h>
+
 #include <algorithm>
 #include <type_traits>
 
@@ -36,7 +43,6 @@ constexpr int PF_GROUPS = PF_STAGES;                     // producer groups of 1
 constexpr int PF_ISSUERS = 3;                              // MMA-issuing warps: accumulator s belongs to issuer s % 3
 constexpr int PF_THREADS = PF_GROUPS * 128 + PF_ISSUERS * 32;
 constexpr unsigned PF_WAIT_LIMIT = 1u << 24;
-
 __device__ __forceinline__ uint32_t pf_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void pf_bar_init(uint64_t *b, int n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pf_u32(b)), "r"(n)); }
 __device__ __forceinline__ void pf_bar_arrive(uint64_t *b) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pf_u32(b)) : "memory"); }
@@ -166,22 +172,49 @@ __device__ __forceinline__ void dequant32_q6k(const uint8_t *unit, int rr, int c
     }
 }
 
+// Descriptor of an activation digit plane as the copy engine wrote it: rows of 64 bytes (the whole chunk), 64-byte swizzle,
+// eight-row groups 512 bytes apart.  The second K step of a chunk starts 32 bytes into the rows.
+__device__ __forceinline__ uint64_t pf_desc_sw64(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ULL << 16) | ((uint64_t)(512 >> 4) << 32) | (1ULL << 46) | (4ULL << 61);
+}
+__device__ __forceinline__ void pf_expect_tx(uint64_t *b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pf_u32(b)), "r"(bytes) : "memory");
+}
+// rows [row, row + BN) of plane `plane`, columns [col, col + 64) of a [rows][planes][K] byte tensor -> shared memory
+__device__ __forceinline__ void pf_tma_plane(void *dst, const CUtensorMap *map, int col, int plane, int row, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(pf_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(col), "r"(plane), "r"(row), "r"(pf_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void pf_group_sync(int group) { asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory"); }
+
+// pair -> digit planes in pair order: dst[pair][NL][K] = src[xidx[pair]][0..NL-1][K] (the planes of a row are contiguous)
+__global__ void __launch_bounds__(128) gather_planes_kernel(const int8_t *__restrict__ src, const int *__restrict__ xidx, int8_t *__restrict__ dst,
+                                                            long long row_bytes, long long src_stride) {
+    const long long pair = blockIdx.x;
+    const uint4 *s = reinterpret_cast<const uint4 *>(src + (long long)xidx[pair] * src_stride);
+    uint4 *d = reinterpret_cast<uint4 *>(dst + pair * row_bytes);
+    for (long long i = threadIdx.x; i < row_bytes / 16; i += 128) d[i] = __ldg(s + i);
+}
+
 template <int QT, int MODE, int NL, int NWL, int BN>
-__global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArgs a) {
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap xmap) {
     constexpr int NACC = NL + NWL - 1;
-    static_assert(NACC * BN <= 512, "accumulators exceed TMEM");
+    static_assert(NACC * BN <= 512 && BN % 16 == 0, "accumulators exceed TMEM");
     constexpr int HTB = QT == QT_Q4K ? HTB_Q4K : HTB_Q6K;
-    constexpr int A_PLANE = 2 * 2 * (PF_BM / 8) * 128;        // [kstep][khalf][row group][128 B] = 8192
-    constexpr int B_PLANE = 2 * 2 * (BN / 8) * 128;
-    constexpr int STAGE_BYTES = NL * A_PLANE + NWL * B_PLANE;
-    extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr int W_PLANE = 2 * 2 * (PF_BM / 8) * 128;        // weights: [kstep][khalf][row group][8 rows x 16 B] = 8192
+    constexpr int X_PLANE = BN * PF_KC;                        // activations: BN rows of 64 bytes (swizzled by the copy engine)
+    constexpr int STAGE_BYTES = NWL * W_PLANE + NL * X_PLANE;
+    static_assert(X_PLANE % 512 == 0 && STAGE_BYTES % 1024 == 0, "operand tiles must keep the swizzle alignment");
+    constexpr int NROW = MODE == MODE_GATEUP ? PF_BM / 2 : PF_BM;   // output rows of one tile
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t full_bar[PF_STAGES], empty_bar[PF_STAGES], accum_bar;
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nb = (int)a.n_blocks, K = nb * 256, n_chunks = K / PF_KC;
 
-    // ---- which tile: (expert, 128-pair slab, BN-row slab) ---------------------------------------------
+    // ---- which tile: (expert, BN-pair slab, row slab) -------------------------------------------------
     const int n_ntiles = a.n_ntiles;
     const int mt = blockIdx.x / n_ntiles, ni = blockIdx.x - mt * n_ntiles;
     int e = -1, m0 = 0, m_end = 0;
@@ -189,8 +222,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
         int acc_tiles = 0;
         for (int x = 0; x < a.n_experts; x++) {
             const int lo = a.grp_off[x], hi = a.grp_off[x + 1];
-            const int nt = (hi - lo + PF_BM - 1) / PF_BM;
-            if (mt < acc_tiles + nt) { e = x; m0 = lo + (mt - acc_tiles) * PF_BM; m_end = hi; break; }
+            const int nt = (hi - lo + BN - 1) / BN;
+            if (mt < acc_tiles + nt) { e = x; m0 = lo + (mt - acc_tiles) * BN; m_end = hi; break; }
             acc_tiles += nt;
         }
     }
@@ -198,7 +231,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < PF_STAGES; s++) { pf_bar_init(&full_bar[s], 256); pf_bar_init(&empty_bar[s], PF_ISSUERS); }   // 128 async-copy + 128 store arrivals; one commit per issuer
+        for (int s = 0; s < PF_STAGES; s++) { pf_bar_init(&full_bar[s], 5); pf_bar_init(&empty_bar[s], PF_ISSUERS); }   // the copy's expect_tx arrival + four warps; one commit per issuer
         pf_bar_init(&accum_bar, PF_ISSUERS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -213,135 +246,114 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
 
     if (warp < PF_GROUPS * 4) {
         // ================= producers: group g fills stage g for chunks g, g + 3, ... ======================
-        const int group = warp >> 2, gtid = tid & 127;
-        const int prow = gtid;                                 // pair row of this thread (A) ...
-        const int pair = m0 + prow;
-        const bool live = pair < m_end;
-        const long long xrow = live ? (a.xidx ? a.xidx[pair] : pair) : 0;
-        const int8_t *xsrc = a.xl + xrow * 8 * (long long)K;
-        const int brow = gtid & 63, hsel = gtid >> 6;          // ... and weight row / 32-column half (B): consecutive lanes, consecutive rows
-        // Q4_K tiles of 64 rows (one row and column half per thread): the 48 weight-block bytes of the NEXT chunk of this
-        // group are requested before waiting for the stage, so their latency hides behind the wait and the A copies
-        constexpr bool PREFETCH = QT == QT_Q4K && BN == 64;
-        long long pf_wrow = 0; const uint8_t *pf_wbase = nullptr;
-        if (PREFETCH) {
-            if (MODE == MODE_GATEUP) { pf_wrow = (long long)ni * (BN / 2) + (brow % (BN / 2)); pf_wbase = brow < BN / 2 ? a.wa[e] : a.wb[e]; }
-            else { pf_wrow = (long long)ni * BN + brow; pf_wbase = a.wa[e]; }
-        }
-        const bool pf_row_ok = PREFETCH && pf_wrow < a.out_f;
+        const int group = warp >> 2, gtid = tid & 127;          // gtid = weight row of the tile = TMEM lane
+        long long wrow; const uint8_t *wbase;
+        if (MODE == MODE_GATEUP) { wrow = (long long)ni * NROW + (gtid & 63); wbase = gtid < 64 ? a.wa[e] : a.wb[e]; }
+        else { wrow = (long long)ni * NROW + gtid; wbase = a.wa[e]; }
+        const bool row_ok = wrow < a.out_f;
+        const uint8_t *wunit = wbase + (row_ok ? (wrow >> 3) * nb * (long long)HTB : 0);
+        const int rr = (int)(wrow & 7);
+        // Q4_K: the 48 weight-block bytes of the NEXT chunk of this group are requested before waiting for the stage
         Q4Raw raw_next = {};
-        if (pf_row_ok && group < n_chunks) load_q4k(pf_wbase + ((pf_wrow >> 3) * nb + (group >> 2)) * HTB, (int)(pf_wrow & 7), group & 3, raw_next);
+        if (QT == QT_Q4K && row_ok && group < n_chunks) load_q4k(wunit + (long long)(group >> 2) * HTB, rr, group & 3, raw_next);
         for (int c = group; c < n_chunks; c += PF_GROUPS) {
             const int s = group;
             const Q4Raw raw = raw_next;
-            if (pf_row_ok && c + PF_GROUPS < n_chunks) {
+            if (QT == QT_Q4K && row_ok && c + PF_GROUPS < n_chunks) {
                 const int cn = c + PF_GROUPS;
-                load_q4k(pf_wbase + ((pf_wrow >> 3) * nb + (cn >> 2)) * HTB, (int)(pf_wrow & 7), cn & 3, raw_next);
+                load_q4k(wunit + (long long)(cn >> 2) * HTB, rr, cn & 3, raw_next);
             }
             if (c >= PF_STAGES && !pf_bar_wait(&empty_bar[s], ((c / PF_STAGES) - 1) & 1, &s_abort)) break;
             uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
-            // A: NL digit planes x 64 columns of this thread's pair, copied global -> shared without passing through
-            // registers (cp.async, zero-filled for rows past the slab); the copies complete on the stage's barrier
+            if (gtid == 0) {                                   // activations: NL planes x BN pairs x 64 columns, by the copy engine
+                pf_expect_tx(&full_bar[s], NL * X_PLANE);
 #pragma unroll
-            for (int b = 0; b < NL; b++) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const uint32_t dst = pf_u32(stage + b * A_PLANE + (j >> 1) * (A_PLANE / 2) + (j & 1) * (A_PLANE / 4) +
-                                                (prow >> 3) * 128 + (prow & 7) * 16);
-                    const int8_t *src = xsrc + (long long)b * K + c * PF_KC + j * 16;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(live ? 16 : 0) : "memory");
-                }
+                for (int b = 0; b < NL; b++) pf_tma_plane(stage + NWL * W_PLANE + b * X_PLANE, &xmap, c * PF_KC, b, m0, &full_bar[s]);
             }
-            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(pf_u32(&full_bar[s])) : "memory");
-            // B: BN weight rows x 64 columns, each thread one (row, 32-column half) per pass
-            for (int r0 = 0; r0 < BN; r0 += 64) {
-                const int r = r0 + brow;
-                if (r < BN) {
-                    long long wrow; const uint8_t *wbase;
-                    if (MODE == MODE_GATEUP) { wrow = (long long)ni * (BN / 2) + (r % (BN / 2)); wbase = r < BN / 2 ? a.wa[e] : a.wb[e]; }
-                    else { wrow = (long long)ni * BN + r; wbase = a.wa[e]; }
-                    uint32_t pl[NWL][8];
-                    if (wrow < a.out_f) {
-                        const uint8_t *unit = wbase + ((wrow >> 3) * nb + (c >> 2)) * HTB;
-                        if constexpr (PREFETCH) expand_q4k<NWL>(raw, c & 3, hsel, a.fw, pl);
-                        else if constexpr (QT == QT_Q4K) dequant32_q4k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
-                        else dequant32_q6k<NWL>(unit, (int)(wrow & 7), c & 3, hsel, a.fw, pl);
-                    } else {
+            // weights: this thread's row, 64 columns as two halves of 32 (= the two K steps of the chunk)
 #pragma unroll
-                        for (int l = 0; l < NWL; l++)
+            for (int hsel = 0; hsel < 2; hsel++) {
+                uint32_t pl[NWL][8];
+                if (row_ok) {
+                    if constexpr (QT == QT_Q4K) expand_q4k<NWL>(raw, c & 3, hsel, a.fw, pl);
+                    else dequant32_q6k<NWL>(wunit + (long long)(c >> 2) * HTB, rr, c & 3, hsel, a.fw, pl);
+                } else {
 #pragma unroll
-                            for (int w = 0; w < 8; w++) pl[l][w] = 0;
-                    }
-                    uint8_t *bdst = stage + NL * A_PLANE + hsel * (B_PLANE / 2) + (r >> 3) * 128 + (r & 7) * 16;
+                    for (int l = 0; l < NWL; l++)
 #pragma unroll
-                    for (int l = 0; l < NWL; l++) {
-                        *reinterpret_cast<uint4 *>(bdst + l * B_PLANE) = make_uint4(pl[l][0], pl[l][1], pl[l][2], pl[l][3]);
-                        *reinterpret_cast<uint4 *>(bdst + l * B_PLANE + B_PLANE / 4) = make_uint4(pl[l][4], pl[l][5], pl[l][6], pl[l][7]);
-                    }
+                        for (int w = 0; w < 8; w++) pl[l][w] = 0;
+                }
+                uint8_t *wdst = stage + hsel * (W_PLANE / 2) + (gtid >> 3) * 128 + (gtid & 7) * 16;
+#pragma unroll
+                for (int l = 0; l < NWL; l++) {
+                    *reinterpret_cast<uint4 *>(wdst + l * W_PLANE) = make_uint4(pl[l][0], pl[l][1], pl[l][2], pl[l][3]);
+                    *reinterpret_cast<uint4 *>(wdst + l * W_PLANE + W_PLANE / 4) = make_uint4(pl[l][4], pl[l][5], pl[l][6], pl[l][7]);
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> visible to the MMA
-            pf_bar_arrive(&full_bar[s]);
+            __syncwarp();
+            if (lane == 0) pf_bar_arrive(&full_bar[s]);
         }
 
-        // ================= epilogue: TMEM lane = pair ========================================================
+        // ================= epilogue: TMEM lane = weight row, columns = pairs ================================
         if (pf_bar_wait(&accum_bar, 0, &s_abort)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-            constexpr int NOUT = MODE == MODE_GATEUP ? BN / 2 : BN;
-            int nl_max = 0;
-            for (int c0 = group * 8; c0 < NOUT; c0 += 8 * PF_GROUPS) {     // the groups share the columns
-                int64_t y0[8], y1[8];
-#pragma unroll
-                for (int part = 0; part < (MODE == MODE_GATEUP ? 2 : 1); part++) {
+            int64_t *exch = reinterpret_cast<int64_t *>(smem) + group * 1024;     // gate/up: two buffers of [128 rows][4] per group (the stages are free now)
+            int nl_max = 0, round = 0;
+            for (int c0 = group * 8; c0 < BN; c0 += 8 * PF_GROUPS, round++) {     // the groups share the columns
+                int64_t y[8];
+                {
                     int r[NACC][8];
 #pragma unroll
-                    for (int s = 0; s < NACC; s++) pf_tmem_ld8(tlane + s * BN + part * (BN / 2) + c0, r[s]);
+                    for (int s = 0; s < NACC; s++) pf_tmem_ld8(tlane + s * BN + c0, r[s]);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
                         i128 v = 0;
 #pragma unroll
                         for (int s = NACC - 1; s >= 0; s--) v = (v << 8) + (i128)r[s][j];
-                        const int64_t y = (int64_t)(v >> a.fw);
-                        if (part == 0) y0[j] = y; else y1[j] = y;
+                        y[j] = (int64_t)(v >> a.fw);
                     }
                 }
-                if (!live) continue;
-                const long long row0 = (long long)ni * NOUT + c0;
                 if (MODE == MODE_GATEUP) {
-                    uint64_t packed[8];
+                    // gate rows keep columns 0..3 and hand 4..7 to their up row; up rows hand 0..3 to their gate row
+                    const bool is_up = gtid >= 64;
+                    int64_t *mine = exch + (round & 1) * 512 + gtid * 4, *theirs = exch + (round & 1) * 512 + (gtid ^ 64) * 4;
 #pragma unroll
-                    for (int l = 0; l < 8; l++) packed[l] = 0;
+                    for (int j = 0; j < 4; j++) mine[j] = y[is_up ? j : 4 + j];
+                    pf_group_sync(group);
+                    const int jb = is_up ? 4 : 0;
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const int64_t sg = mul_shift(y0[j], sigmoid_fixed_c(y0[j], a.fa, a.sig_log2e, a.sig_clip), a.fa);
-                        const int64_t gu = mul_shift(sg, y1[j], a.fa);
-                        if (a.out && row0 + j < a.out_f) a.out[(long long)pair * a.out_f + row0 + j] = gu;
+                    for (int j = 0; j < 4; j++) {
+                        const long long pair = (long long)m0 + c0 + jb + j;
+                        if (pair >= m_end) break;
+                        const int64_t yg = is_up ? theirs[j] : y[j], yu = is_up ? y[4 + j] : theirs[j];
+                        const int64_t sg = mul_shift(yg, sigmoid_fixed_c(yg, a.fa, a.sig_log2e, a.sig_clip), a.fa);
+                        const int64_t gu = mul_shift(sg, yu, a.fa);
                         bool ok;
                         const uint64_t d = balanced_digits8(gu, ok);
                         if (!ok) atomicOr(a.flags, 1);
                         nl_max = max(nl_max, digits_used(d));
+                        if (row_ok) {
+                            if (a.out) a.out[pair * a.out_f + wrow] = gu;
+                            int8_t *ol = a.out_limbs + pair * 8 * a.out_f + wrow;
 #pragma unroll
-                        for (int l = 0; l < 8; l++) packed[l] |= ((d >> (8 * l)) & 0xFF) << (8 * j);
-                    }
-                    if (row0 + 8 <= a.out_f) {
-#pragma unroll
-                        for (int l = 0; l < 8; l++)
-                            *reinterpret_cast<uint64_t *>(a.out_limbs + ((long long)pair * 8 + l) * a.out_f + row0) = packed[l];
-                    } else {
-                        for (int j = 0; j < 8 && row0 + j < a.out_f; j++)
-                            for (int l = 0; l < 8; l++)
-                                a.out_limbs[((long long)pair * 8 + l) * a.out_f + row0 + j] = (int8_t)(packed[l] >> (8 * j));
+                            for (int l = 0; l < 8; l++) ol[l * a.out_f] = (int8_t)(d >> (8 * l));
+                        }
                     }
                 } else {
-                    const long long tok = a.pair_tok ? a.pair_tok[pair] : pair;
-                    const int64_t gate = a.gates ? a.gates[pair] : 0;
+#pragma unroll
                     for (int j = 0; j < 8; j++) {
-                        if (row0 + j >= a.out_f) break;
-                        if (MODE == MODE_LINEAR) a.out[(long long)pair * a.out_f + row0 + j] = y0[j];
-                        else atomicAdd(reinterpret_cast<unsigned long long *>(a.out + tok * a.out_f + row0 + j),
-                                       (unsigned long long)mul_shift(y0[j], gate, a.fa));
+                        const long long pair = (long long)m0 + c0 + j;
+                        if (pair >= m_end) break;
+                        if (!row_ok) continue;
+                        if (MODE == MODE_LINEAR) a.out[pair * a.out_f + wrow] = y[j];
+                        else {
+                            const long long tok = a.pair_tok ? a.pair_tok[pair] : pair;
+                            atomicAdd(reinterpret_cast<unsigned long long *>(a.out + tok * a.out_f + wrow),
+                                      (unsigned long long)mul_shift(y[j], a.gates ? a.gates[pair] : 0, a.fa));
+                        }
                     }
                 }
             }
@@ -366,10 +378,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                 const int s = c % PF_STAGES;
                 ok = pf_bar_wait(&full_bar[s], (c / PF_STAGES) & 1, &s_abort);
                 if (!ok) break;
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the cp.async writes, observed through the barrier
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t stage = pf_u32(smem + (size_t)s * STAGE_BYTES);
-                const uint64_t da0 = pf_desc(stage, A_PLANE / 4, 128), db0 = pf_desc(stage + NL * A_PLANE, B_PLANE / 4, 128);
+                const uint64_t dw0 = pf_desc(stage, W_PLANE / 4, 128), dx0 = pf_desc_sw64(stage + NWL * W_PLANE);
                 const uint32_t later = c > 0 ? 1u : 0u;
                 auto issue = [&](auto iss_c) {                 // ISS is a compile-time constant: the skipped pairs fold away
                     constexpr int ISS = decltype(iss_c)::value;
@@ -384,9 +395,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                                 const bool first = !((seen >> acc) & 1u);
                                 seen |= 1u << acc;
                                 if (acc % PF_ISSUERS != ISS) continue;
-                                const uint64_t da = da0 + (uint64_t)((b * A_PLANE + ks * (A_PLANE / 2)) >> 4);
-                                const uint64_t db = db0 + (uint64_t)((w * B_PLANE + ks * (B_PLANE / 2)) >> 4);
-                                pf_mma(tmem + acc * BN, da, db, IDESC, first ? later : 1u);
+                                const uint64_t dw = dw0 + (uint64_t)((w * W_PLANE + ks * (W_PLANE / 2)) >> 4);
+                                const uint64_t dx = dx0 + (uint64_t)((b * X_PLANE + ks * 32) >> 4);
+                                pf_mma(tmem + acc * BN, dw, dx, IDESC, first ? later : 1u);
                             }
                 };
                 if (issuer == 0) issue(std::integral_constant<int, 0>{});
@@ -407,23 +418,55 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
     if (tid == 0 && s_abort) atomicOr(a.flags, 8);
 }
 
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiled>(p);
+    }();
+    return fn;
+}
+
 template <int QT, int MODE, int NL, int NWL, int BN>
 cudaError_t launch_pf(const PrefillArgs &a_in, cudaStream_t s, int shape) {
     __atomic_fetch_add(&g_prefill_launches[shape], 1ULL, __ATOMIC_RELAXED);
     PrefillArgs a = a_in;
-    constexpr int A_PLANE = 2 * 2 * (PF_BM / 8) * 128, B_PLANE = 2 * 2 * (BN / 8) * 128;
-    constexpr size_t smem = (size_t)PF_STAGES * (NL * A_PLANE + NWL * B_PLANE) + 1024;
-    constexpr int NOUT = MODE == MODE_GATEUP ? BN / 2 : BN;
-    a.n_ntiles = (int)((a.out_f + NOUT - 1) / NOUT);
+    constexpr int W_PLANE = 2 * 2 * (PF_BM / 8) * 128, X_PLANE = BN * PF_KC;
+    constexpr size_t smem = (size_t)PF_STAGES * (NWL * W_PLANE + NL * X_PLANE) + 1024;
+    constexpr int NROW = MODE == MODE_GATEUP ? PF_BM / 2 : PF_BM;
+    a.n_ntiles = (int)((a.out_f + NROW - 1) / NROW);
     a.sig_log2e = sigmoid_log2e(a.fa); a.sig_clip = sigmoid_clip(a.fa);
+    const long long K = a.n_blocks * 256;
+    // activation planes as a [rows][planes][K] byte tensor; rows reached through an index are gathered into pair order first
+    const int8_t *planes = a.xl;
+    long long n_planes = 8;
+    if (a.xidx) {
+        if (!a.xg) return cudaErrorInvalidValue;
+        gather_planes_kernel<<<(unsigned)a.n_pairs, 128, 0, s>>>(a.xl, a.xidx, a.xg, (long long)NL * K, 8 * K);
+        note_launch();
+        planes = a.xg; n_planes = NL;
+    }
+    EncodeTiled enc = encode_tiled();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap map;
+    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)n_planes, (cuuint64_t)a.n_pairs};
+    const cuuint64_t strides[2] = {(cuuint64_t)K, (cuuint64_t)(n_planes * K)};
+    const cuuint32_t box[3] = {PF_KC, 1, BN}, estr[3] = {1, 1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t *>(planes), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(prefill_kernel<QT, MODE, NL, NWL, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const long long max_mtiles = (a.n_pairs + PF_BM - 1) / PF_BM + a.n_experts;
-    prefill_kernel<QT, MODE, NL, NWL, BN><<<(unsigned)(max_mtiles * a.n_ntiles), PF_THREADS, smem, s>>>(a);
+    const long long max_mtiles = (a.n_pairs + BN - 1) / BN + a.n_experts;
+    prefill_kernel<QT, MODE, NL, NWL, BN><<<(unsigned)(max_mtiles * a.n_ntiles), PF_THREADS, smem, s>>>(a, map);
     note_launch();
     return cudaGetLastError();
 }
@@ -439,8 +482,8 @@ cudaError_t launch_prefill(int qtype, int mode, int nl, const PrefillArgs &a, cu
         if (nl == 4) return launch_pf<QT_Q4K, MODE_GATEUP, 4, 4, 64>(a, s, 1);
     }
     if (qtype == QT_Q6K && mode == MODE_DOWN) {
-        if (nl <= 5) return launch_pf<QT_Q6K, MODE_DOWN, 5, 5, 32>(a, s, 2);
-        if (nl == 6) return launch_pf<QT_Q6K, MODE_DOWN, 6, 5, 32>(a, s, 3);
+        if (nl <= 5) return launch_pf<QT_Q6K, MODE_DOWN, 5, 5, 48>(a, s, 2);
+        if (nl == 6) return launch_pf<QT_Q6K, MODE_DOWN, 6, 5, 48>(a, s, 3);
     }
     if (qtype == QT_Q4K && mode == MODE_DOWN) {
         if (nl <= 5) return launch_pf<QT_Q4K, MODE_DOWN, 5, 4, 64>(a, s, 4);
