@@ -38,8 +38,13 @@ unsigned long long g_prefill_launches[PF_SHAPES];
 
 namespace {
 
-constexpr int PF_BM = 128, PF_KC = 64, PF_STAGES = 3;
-constexpr int PF_GROUPS = PF_STAGES;                     // producer groups of 128 threads; group g owns stage g
+constexpr int PF_BM = 128, PF_KC = 64;
+constexpr int PF_GROUPS = 3;                              // producer groups of 128 threads; group g fills chunks g, g + 3, ...
+constexpr int PF_MAX_STAGES = 6;
+constexpr int PF_SMEM_BUDGET = 230 * 1024;                // dynamic shared memory a CTA may ask for, less the alignment slack and the static part
+// stages of a tile shape: as many as fit (more stages than groups, so that a group dequantises its next chunk while the
+// MMAs of its previous one are still queued)
+__host__ __device__ constexpr int pf_stages(int stage_bytes) { return PF_SMEM_BUDGET / stage_bytes < PF_MAX_STAGES ? PF_SMEM_BUDGET / stage_bytes : PF_MAX_STAGES; }
 constexpr int PF_ISSUERS = 3;                              // MMA-issuing warps: accumulator s belongs to issuer s % 3
 constexpr int PF_THREADS = PF_GROUPS * 128 + PF_ISSUERS * 32;
 constexpr unsigned PF_WAIT_LIMIT = 1u << 24;
@@ -204,34 +209,46 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
     constexpr int W_PLANE = 2 * 2 * (PF_BM / 8) * 128;        // weights: [kstep][khalf][row group][8 rows x 16 B] = 8192
     constexpr int X_PLANE = BN * PF_KC;                        // activations: BN rows of 64 bytes (swizzled by the copy engine)
     constexpr int STAGE_BYTES = NWL * W_PLANE + NL * X_PLANE;
+    constexpr int STAGES = pf_stages(STAGE_BYTES);
+    static_assert(STAGES >= 3, "a tile shape needs three stages");
     static_assert(X_PLANE % 512 == 0 && STAGE_BYTES % 1024 == 0, "operand tiles must keep the swizzle alignment");
     constexpr int NROW = MODE == MODE_GATEUP ? PF_BM / 2 : PF_BM;   // output rows of one tile
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t full_bar[PF_STAGES], empty_bar[PF_STAGES], accum_bar;
+    __shared__ __align__(8) uint64_t full_bar[PF_MAX_STAGES], empty_bar[PF_MAX_STAGES], accum_bar;
     __shared__ uint32_t s_tmem;
-    __shared__ int s_abort;
+    __shared__ int s_abort, s_tile[3];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nb = (int)a.n_blocks, K = nb * 256, n_chunks = K / PF_KC;
 
     // ---- which tile: (expert, BN-pair slab, row slab) -------------------------------------------------
     const int n_ntiles = a.n_ntiles;
     const int mt = blockIdx.x / n_ntiles, ni = blockIdx.x - mt * n_ntiles;
-    int e = -1, m0 = 0, m_end = 0;
-    {
-        int acc_tiles = 0;
-        for (int x = 0; x < a.n_experts; x++) {
-            const int lo = a.grp_off[x], hi = a.grp_off[x + 1];
+    // warp 0 looks the tile up, 32 experts per step: an expert with n pairs owns ceil(n / BN) consecutive tiles
+    if (warp == 0) {
+        int base = 0;
+        bool found = false;
+        for (int x0 = 0; x0 < a.n_experts && !found; x0 += 32) {
+            const int x = x0 + lane;
+            const int lo = x < a.n_experts ? a.grp_off[x] : 0, hi = x < a.n_experts ? a.grp_off[x + 1] : 0;
             const int nt = (hi - lo + BN - 1) / BN;
-            if (mt < acc_tiles + nt) { e = x; m0 = lo + (mt - acc_tiles) * BN; m_end = hi; break; }
-            acc_tiles += nt;
+            int incl = nt;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) { const int t = __shfl_up_sync(0xffffffffu, incl, d); if (lane >= d) incl += t; }
+            const bool hit = mt >= base + incl - nt && mt < base + incl;
+            if (hit) { s_tile[0] = x; s_tile[1] = lo + (mt - (base + incl - nt)) * BN; s_tile[2] = hi; }
+            found = __any_sync(0xffffffffu, hit);
+            base += __shfl_sync(0xffffffffu, incl, 31);
         }
+        if (!found && lane == 0) s_tile[0] = -1;
     }
+    __syncthreads();
+    const int e = s_tile[0], m0 = s_tile[1], m_end = s_tile[2];
     if (e < 0) return;                                        // grid is an upper bound on the tile count
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < PF_STAGES; s++) { pf_bar_init(&full_bar[s], 5); pf_bar_init(&empty_bar[s], PF_ISSUERS); }   // the copy's expect_tx arrival + four warps; one commit per issuer
+        for (int s = 0; s < STAGES; s++) { pf_bar_init(&full_bar[s], 5); pf_bar_init(&empty_bar[s], PF_ISSUERS); }   // the copy's expect_tx arrival + four warps; one commit per issuer
         pf_bar_init(&accum_bar, PF_ISSUERS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -257,13 +274,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
         Q4Raw raw_next = {};
         if (QT == QT_Q4K && row_ok && group < n_chunks) load_q4k(wunit + (long long)(group >> 2) * HTB, rr, group & 3, raw_next);
         for (int c = group; c < n_chunks; c += PF_GROUPS) {
-            const int s = group;
+            const int s = c % STAGES;
             const Q4Raw raw = raw_next;
             if (QT == QT_Q4K && row_ok && c + PF_GROUPS < n_chunks) {
                 const int cn = c + PF_GROUPS;
                 load_q4k(wunit + (long long)(cn >> 2) * HTB, rr, cn & 3, raw_next);
             }
-            if (c >= PF_STAGES && !pf_bar_wait(&empty_bar[s], ((c / PF_STAGES) - 1) & 1, &s_abort)) break;
+            if (c >= STAGES && !pf_bar_wait(&empty_bar[s], ((c / STAGES) - 1) & 1, &s_abort)) break;
             uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
             if (gtid == 0) {                                   // activations: NL planes x BN pairs x 64 columns, by the copy engine
                 pf_expect_tx(&full_bar[s], NL * X_PLANE);
@@ -303,6 +320,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
             int nl_max = 0, round = 0;
             for (int c0 = group * 8; c0 < BN; c0 += 8 * PF_GROUPS, round++) {     // the groups share the columns
                 int64_t y[8];
+                long long tok[8];
+                int64_t gate[8];
+                if (MODE == MODE_DOWN) {                       // requested before the accumulators are read, so the latencies overlap
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const long long pair = (long long)m0 + c0 + j;
+                        const bool live = pair < m_end;
+                        tok[j] = !live ? -1 : a.pair_tok ? a.pair_tok[pair] : pair;
+                        gate[j] = live && a.gates ? a.gates[pair] : 0;
+                    }
+                }
                 {
                     int r[NACC][8];
 #pragma unroll
@@ -349,11 +377,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                         if (pair >= m_end) break;
                         if (!row_ok) continue;
                         if (MODE == MODE_LINEAR) a.out[pair * a.out_f + wrow] = y[j];
-                        else {
-                            const long long tok = a.pair_tok ? a.pair_tok[pair] : pair;
-                            atomicAdd(reinterpret_cast<unsigned long long *>(a.out + tok * a.out_f + wrow),
-                                      (unsigned long long)mul_shift(y[j], a.gates ? a.gates[pair] : 0, a.fa));
-                        }
+                        else atomicAdd(reinterpret_cast<unsigned long long *>(a.out + tok[j] * a.out_f + wrow),
+                                       (unsigned long long)mul_shift(y[j], gate[j], a.fa));
                     }
                 }
             }
@@ -375,8 +400,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
             const int issuer = warp - PF_GROUPS * 4;
             bool ok = true;
             for (int c = 0; c < n_chunks && ok; c++) {
-                const int s = c % PF_STAGES;
-                ok = pf_bar_wait(&full_bar[s], (c / PF_STAGES) & 1, &s_abort);
+                const int s = c % STAGES;
+                ok = pf_bar_wait(&full_bar[s], (c / STAGES) & 1, &s_abort);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t stage = pf_u32(smem + (size_t)s * STAGE_BYTES);
@@ -436,7 +461,7 @@ cudaError_t launch_pf(const PrefillArgs &a_in, cudaStream_t s, int shape) {
     __atomic_fetch_add(&g_prefill_launches[shape], 1ULL, __ATOMIC_RELAXED);
     PrefillArgs a = a_in;
     constexpr int W_PLANE = 2 * 2 * (PF_BM / 8) * 128, X_PLANE = BN * PF_KC;
-    constexpr size_t smem = (size_t)PF_STAGES * (NWL * W_PLANE + NL * X_PLANE) + 1024;
+    constexpr size_t smem = (size_t)pf_stages(NWL * W_PLANE + NL * X_PLANE) * (NWL * W_PLANE + NL * X_PLANE) + 1024;
     constexpr int NROW = MODE == MODE_GATEUP ? PF_BM / 2 : PF_BM;
     a.n_ntiles = (int)((a.out_f + NROW - 1) / NROW);
     a.sig_log2e = sigmoid_log2e(a.fa); a.sig_clip = sigmoid_clip(a.fa);
