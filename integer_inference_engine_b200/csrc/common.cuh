@@ -75,16 +75,29 @@ __device__ __forceinline__ uint64_t udiv_small(uint64_t num, uint64_t z) {
 __host__ __device__ inline int64_t sigmoid_log2e(int fa) { const int s = 16 - fa; return s >= 0 ? ((int64_t)94548 >> s) : ((int64_t)94548 << -s); }
 __host__ __device__ inline int64_t sigmoid_clip(int fa) { return (((int64_t)(fa + 2)) << (2 * fa)) / sigmoid_log2e(fa); }
 
+// floor(num / z) for 0 <= num < 2^60, 0 < z < 2^31 with a quotient below 2^31: two single-precision estimates (the
+// second one of the remainder) and an exact fix-up; no double-precision division.
+__device__ __forceinline__ uint64_t udiv_small_q31(uint64_t num, uint32_t z) {
+    const float rz = __frcp_rn((float)z);
+    uint32_t q = __float2uint_rz((float)(uint32_t)(num >> 29) * rz * 536870912.0f);            // within 2^-21 relative
+    int64_t r = (int64_t)(num - (uint64_t)q * z);                                               // |r| < 2^41
+    const int q2 = __float2int_rn((float)(int)(r >> 10) * rz * 1024.0f);
+    q += q2; r -= (int64_t)q2 * z;
+    while (r < 0) { q--; r += z; }
+    while (r >= (int64_t)z) { q++; r -= z; }
+    return q;
+}
+
+// sigmoid(x) = e1 / (e0 + e1) with e0 = 2^-(max(x,0) log2 e), e1 = 2^-((max(x,0) - x) log2 e), both clipped in the
+// exponent (fixedpoint.py:136-163).  One of the two exponents is always zero and its power exactly 2^fa, so only the
+// other power is evaluated; x = INT64_MIN wraps exactly as the NumPy oracle's int64 arithmetic does.
 __device__ __forceinline__ int64_t sigmoid_fixed_c(int64_t x, int fa, int64_t log2e, int64_t clip) {
-    const int64_t m = x > 0 ? x : 0;
-    const int64_t d0 = m < clip ? m : clip;
-    // the NumPy oracle evaluates m - x and d * log2e in wrapping int64 (only x = INT64_MIN wraps)
-    int64_t d1 = (int64_t)((uint64_t)m - (uint64_t)x);
-    if (d1 > clip) d1 = clip;
-    const int64_t e0 = exp2_neg_fixed((d0 * log2e) >> fa, fa);
-    const int64_t e1 = exp2_neg_fixed((int64_t)((uint64_t)d1 * (uint64_t)log2e) >> fa, fa);
-    const int64_t z = e0 + e1;          // e0, e1 <= 2^fa, fa <= 29: the quotient below fits 64 bits
-    return z == 0 ? 0 : (int64_t)udiv_small((uint64_t)e1 << fa, (uint64_t)z);
+    const bool neg = x < 0;
+    int64_t d = neg ? (int64_t)(0ULL - (uint64_t)x) : x;
+    if (d > clip) d = clip;
+    const int64_t es = exp2_neg_fixed((int64_t)((uint64_t)d * (uint64_t)log2e) >> fa, fa);
+    const int64_t one = (int64_t)1 << fa;
+    return (int64_t)udiv_small_q31((uint64_t)(neg ? es : one) << fa, (uint32_t)(es + one));   // fa <= 29: es + one <= 2^30
 }
 
 __device__ __forceinline__ int64_t sigmoid_fixed(int64_t x, int fa) {

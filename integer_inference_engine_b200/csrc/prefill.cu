@@ -192,10 +192,12 @@ __device__ __forceinline__ void pf_tma_plane(void *dst, const CUtensorMap *map, 
 }
 __device__ __forceinline__ void pf_group_sync(int group) { asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory"); }
 
-// pair -> digit planes in pair order: dst[pair][NL][K] = src[xidx[pair]][0..NL-1][K] (the planes of a row are contiguous)
+// pair -> digit planes in pair order: dst[pair][NL][K] = src[xidx[pair]][0..NL-1][K] (the planes of a row are contiguous).
+// Only the pairs the groups own exist (the grid covers the caller's upper bound); `n_live` points at their count.
 __global__ void __launch_bounds__(128) gather_planes_kernel(const int8_t *__restrict__ src, const int *__restrict__ xidx, int8_t *__restrict__ dst,
-                                                            long long row_bytes, long long src_stride) {
+                                                            long long row_bytes, long long src_stride, const int *__restrict__ n_live) {
     const long long pair = blockIdx.x;
+    if (pair >= *n_live) return;
     const uint4 *s = reinterpret_cast<const uint4 *>(src + (long long)xidx[pair] * src_stride);
     uint4 *d = reinterpret_cast<uint4 *>(dst + pair * row_bytes);
     for (long long i = threadIdx.x; i < row_bytes / 16; i += 128) d[i] = __ldg(s + i);
@@ -355,12 +357,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         const long long pair = (long long)m0 + c0 + jb + j;
-                        if (pair >= m_end) break;
+                        const bool live = pair < m_end;               // predicated, not a break: the four chains interleave
                         const int64_t yg = is_up ? theirs[j] : y[j], yu = is_up ? y[4 + j] : theirs[j];
                         const int64_t sg = mul_shift(yg, sigmoid_fixed_c(yg, a.fa, a.sig_log2e, a.sig_clip), a.fa);
                         const int64_t gu = mul_shift(sg, yu, a.fa);
                         bool ok;
                         const uint64_t d = balanced_digits8(gu, ok);
+                        if (!live) continue;
                         if (!ok) atomicOr(a.flags, 1);
                         nl_max = max(nl_max, digits_used(d));
                         if (row_ok) {
@@ -374,8 +377,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
                         const long long pair = (long long)m0 + c0 + j;
-                        if (pair >= m_end) break;
-                        if (!row_ok) continue;
+                        if (pair >= m_end || !row_ok) continue;
                         if (MODE == MODE_LINEAR) a.out[pair * a.out_f + wrow] = y[j];
                         else atomicAdd(reinterpret_cast<unsigned long long *>(a.out + tok[j] * a.out_f + wrow),
                                        (unsigned long long)mul_shift(y[j], gate[j], a.fa));
@@ -471,7 +473,7 @@ cudaError_t launch_pf(const PrefillArgs &a_in, cudaStream_t s, int shape) {
     long long n_planes = 8;
     if (a.xidx) {
         if (!a.xg) return cudaErrorInvalidValue;
-        gather_planes_kernel<<<(unsigned)a.n_pairs, 128, 0, s>>>(a.xl, a.xidx, a.xg, (long long)NL * K, 8 * K);
+        gather_planes_kernel<<<(unsigned)a.n_pairs, 128, 0, s>>>(a.xl, a.xidx, a.xg, (long long)NL * K, 8 * K, a.grp_off + a.n_experts);
         note_launch();
         planes = a.xg; n_planes = NL;
     }
