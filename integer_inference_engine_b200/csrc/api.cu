@@ -330,7 +330,7 @@ struct GroupedWeights {
 int grouped_tc(const GroupedWeights &w, int n_groups, const int *off, const int *xidx, const int *ptok, const int64_t *pg,
                const int8_t *hl, int nl_h, long long T, long long P, int fa, int fw, int accumulate, int64_t *out_dev,
                cudaStream_t s) {
-    if (w.gate_q != QT_Q4K || w.d_model > 8192 || w.e_ffn > 8192 || nl_h < 1 || nl_h > 4) return -1;
+    if (w.gate_q != QT_Q4K || w.d_model > 8192 || w.e_ffn > 8192 || nl_h < 1 || nl_h > 4 || fw > 32) return -1;
     if (!small_scales(w.maxd_gate, w.maxdmin_gate, fw) || !small_scales(w.maxd_down, w.maxdmin_down, fw)) return -1;
     if (max_weight(QT_Q4K, w.maxd_gate, w.maxdmin_gate, fw) > CAP4) return -1;
     if (max_weight(w.down_q, w.maxd_down, w.maxdmin_down, fw) > (w.down_q == QT_Q4K ? CAP4 : (unsigned __int128)0x7FFFFFFFULL * 32)) return -1;   // Q6_K: d_q * 128 stays in int32

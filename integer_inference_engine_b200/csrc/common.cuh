@@ -114,14 +114,12 @@ __device__ __forceinline__ int64_t silu_fixed(int64_t x, int fa) { return mul_sh
 // Eight digits cover |x| <= 127*(2^64-1)/255; `ok` is cleared when a ninth digit would be needed
 // (capacity rule of north-mini-code/src/nmc/qk_cuda.py:973-992).
 __device__ __forceinline__ uint64_t balanced_digits8(int64_t x, bool &ok) {
-    uint64_t packed = 0;
-#pragma unroll
-    for (int l = 0; l < 8; l++) {
-        packed |= (uint64_t)(x & 0xFF) << (8 * l);
-        x = (x >> 8) + ((x >> 7) & 1);          // (x - digit) / 256 without leaving int64
-    }
-    ok = (x == 0);
-    return packed;
+    // with u_l = d_l + 128 in [0, 255]: x + 0x80..80 = sum_l u_l 256^l, so the digits are the bytes of that sum with the
+    // top bit flipped.  Every negative int64 has eight digits (the smallest eight-digit number is below INT64_MIN); a
+    // positive one does while the sum stays below 2^64.
+    constexpr uint64_t C = 0x8080808080808080ULL;
+    ok = x <= (int64_t)0x7F7F7F7F7F7F7F7FLL;
+    return ((uint64_t)x + C) ^ C;
 }
 
 // ---- warp-level integer MMA (legacy tensor path; the decode kernels are HBM-bound) ---------------------

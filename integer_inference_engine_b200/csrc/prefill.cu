@@ -86,14 +86,12 @@ __device__ __forceinline__ void pf_tmem_ld8(uint32_t taddr, int (&r)[8]) {
 }
 
 // four int32 weights -> one word per digit plane (byte i of plane l = digit l of weight i)
-__device__ __forceinline__ void digits4(const int (&w)[4], uint32_t (&plane)[4]) {
-    uint32_t v[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) v[i] = ((uint32_t)w[i] + 0x80808080u) ^ 0x80808080u;   // byte l = balanced digit l
+// (the weights arrive with 0x80808080 already added: byte l of (w + 0x80808080) ^ 0x80808080 is the balanced digit l)
+__device__ __forceinline__ void digits4(const uint32_t (&v)[4], uint32_t (&plane)[4]) {
     const uint32_t t0 = __byte_perm(v[0], v[1], 0x5140), t1 = __byte_perm(v[2], v[3], 0x5140);
     const uint32_t t2 = __byte_perm(v[0], v[1], 0x7362), t3 = __byte_perm(v[2], v[3], 0x7362);
-    plane[0] = __byte_perm(t0, t1, 0x5410); plane[1] = __byte_perm(t0, t1, 0x7632);
-    plane[2] = __byte_perm(t2, t3, 0x5410); plane[3] = __byte_perm(t2, t3, 0x7632);
+    plane[0] = __byte_perm(t0, t1, 0x5410) ^ 0x80808080u; plane[1] = __byte_perm(t0, t1, 0x7632) ^ 0x80808080u;
+    plane[2] = __byte_perm(t2, t3, 0x5410) ^ 0x80808080u; plane[3] = __byte_perm(t2, t3, 0x7632) ^ 0x80808080u;
 }
 
 // Dequantise 32 consecutive-k weights of one row into NWL digit planes (eight words each).
@@ -114,14 +112,15 @@ __device__ __forceinline__ void expand_q4k(const Q4Raw &raw, int G, int hsel, in
     const int j = 2 * G + hsel;
     const int ws = scale_small(raw.meta.x & 0xFFFF, fw) * (int)(((j < 4 ? sc0 : sc1) >> (8 * (j & 3))) & 0xFF);
     const int wm = scale_small(raw.meta.x >> 16, fw) * (int)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xFF);
+    const uint32_t bias = 0x80808080u - (uint32_t)wm;
 #pragma unroll
     for (int t = 0; t < 4; t++) {
         const uint32_t words[2] = {(raw.q[t].x >> (4 * hsel)) & 0x0f0f0f0fu, (raw.q[t].y >> (4 * hsel)) & 0x0f0f0f0fu};
 #pragma unroll
         for (int h2 = 0; h2 < 2; h2++) {
-            int w[4];
+            uint32_t w[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) w[i] = ws * (int)((words[h2] >> (8 * i)) & 0xFF) - wm;
+            for (int i = 0; i < 4; i++) w[i] = (uint32_t)ws * ((words[h2] >> (8 * i)) & 0xFF) + bias;
             uint32_t p4[4];
             digits4(w, p4);
 #pragma unroll
@@ -131,48 +130,52 @@ __device__ __forceinline__ void expand_q4k(const Q4Raw &raw, int G, int hsel, in
     }
 }
 
-// Dequantise 32 consecutive-k weights of one row into NWL digit planes (eight words each).
-// Q4_K: chunk = group G of a block; hsel 0 = low nibbles (first 32 columns), 1 = high nibbles.
-template <int NWL>
-__device__ __forceinline__ void dequant32_q4k(const uint8_t *unit, int rr, int G, int hsel, int fw, uint32_t (&pl)[NWL][8]) {
-    Q4Raw raw;
-    load_q4k(unit, rr, G, raw);
-    expand_q4k<NWL>(raw, G, hsel, fw, pl);
-}
-
-// Q6_K: chunk cc (0..3) of a block covers half h = cc >> 1 and kq = 2*(cc & 1) + hsel.  |W| = |d_q sc (q-32)|
-// can need a fifth digit, so the split adds 0x80...80 over 40 bits: byte l of (w + 0x8080808080) ^ 0x80..80
-// is the balanced digit l for |w| <= 127*(256^5-1)/255.
-template <int NWL>
-__device__ __forceinline__ void dequant32_q6k(const uint8_t *unit, int rr, int cc, int hsel, int fw, uint32_t (&pl)[NWL][8]) {
-    static_assert(NWL == 5, "Q6_K tiles carry five weight digits");
-    const int h = cc >> 1, kq = 2 * (cc & 1) + hsel;
+// Q6_K: chunk cc (0..3) of a block covers half h = cc >> 1 and kq = 2*(cc & 1) + hsel for the two 32-column halves hsel.
+// |W| = |d_q sc (q-32)| can need a fifth digit, so the split adds 0x80...80 over 40 bits: byte l of
+// (w + 0x8080808080) ^ 0x80..80 is the balanced digit l for |w| <= 127*(256^5-1)/255.  The bias and the -32 ride in the
+// addend of the one 32x32->64 multiply-add per weight.  The row's 64 columns are written straight to the five planes of
+// the stage (plane stride PLANE): vector (hsel, u) = 16 columns, four words per plane.
+template <int PLANE>
+__device__ __forceinline__ void dequant64_q6k_store(const uint8_t *unit, int rr, int cc, int fw, uint8_t *wdst) {
+    const int h = cc >> 1, hi_nib = cc & 1;
     const int dq = scale_small(__ldg(reinterpret_cast<const unsigned short *>(unit + 1664 + rr * 2)), fw);
-    const int8_t *scp = reinterpret_cast<const int8_t *>(unit + 1536 + rr * 16 + 8 * h + 2 * kq);
+    const uint32_t sc4 = __ldg(reinterpret_cast<const uint32_t *>(unit + 1536 + rr * 16 + 8 * h + 4 * hi_nib));   // scales of (hsel, u)
+    uint4 lw[4];
+    uint2 hb2[4];
 #pragma unroll
-    for (int u = 0; u < 2; u++) {
-        const int ws = dq * (int)__ldg(scp + u);                                          // |ws| < 2^31 inside the envelope
+    for (int t = 0; t < 4; t++) {
+        lw[t] = ldg128(unit + h * 512 + (rr * 4 + t) * 16);                             // u0:{first 32, second 32} u1:{..}
+        const uint4 hw = ldg128(unit + 1024 + (rr * 4 + t) * 16);                       // [h*2+u]
+        hb2[t] = h ? make_uint2(hw.z, hw.w) : make_uint2(hw.x, hw.y);
+    }
 #pragma unroll
-        for (int t = 0; t < 4; t++) {
-            const uint4 lw = ldg128(unit + h * 512 + (rr * 4 + t) * 16);                // u0:{first 32, second 32} u1:{..}
-            const uint4 hw = ldg128(unit + 1024 + (rr * 4 + t) * 16);                   // [h*2+u]
-            const uint32_t n = (kq & 1) ? (u ? lw.w : lw.y) : (u ? lw.z : lw.x);
-            const uint32_t hb = h ? (u ? hw.w : hw.z) : (u ? hw.y : hw.x);
-            const uint32_t lo = (kq < 2 ? n : (n >> 4)) & 0x0f0f0f0fu, hi = ((hb >> (2 * kq)) << 4) & 0x30303030u;
-            const uint32_t q = lo | hi;
-            uint32_t vlo[4], d4 = 0;
+    for (int hsel = 0; hsel < 2; hsel++) {
+        const int kq = 2 * hi_nib + hsel;
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int64_t w = (int64_t)ws * ((int)((q >> (8 * i)) & 0xFF) - 32);
-                const uint64_t uu = (uint64_t)w + 0x8080808080ULL;
-                vlo[i] = (uint32_t)uu ^ 0x80808080u;
-                d4 |= ((((uint32_t)(uu >> 32)) & 0xFF) ^ 0x80u) << (8 * i);
+        for (int u = 0; u < 2; u++) {
+            const int ws = dq * (int)(int8_t)(sc4 >> (8 * (2 * hsel + u)));             // |ws| < 2^31 inside the envelope
+            const int64_t bias = 0x8080808080LL - 32 * (int64_t)ws;
+            uint32_t pl[5][4];
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                const uint32_t n = hsel ? (u ? lw[t].w : lw[t].y) : (u ? lw[t].z : lw[t].x);
+                const uint32_t hb = u ? hb2[t].y : hb2[t].x;
+                const uint32_t q = ((hi_nib ? n >> 4 : n) & 0x0f0f0f0fu) | (((hb >> (2 * kq)) << 4) & 0x30303030u);
+                uint32_t vlo[4], vhi[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int64_t uu = (int64_t)ws * (int64_t)(int)((q >> (8 * i)) & 0xFF) + bias;
+                    vlo[i] = (uint32_t)uu; vhi[i] = (uint32_t)((uint64_t)uu >> 32);
+                }
+                const uint32_t t0 = __byte_perm(vlo[0], vlo[1], 0x5140), t1 = __byte_perm(vlo[2], vlo[3], 0x5140);
+                const uint32_t t2 = __byte_perm(vlo[0], vlo[1], 0x7362), t3 = __byte_perm(vlo[2], vlo[3], 0x7362);
+                pl[0][t] = __byte_perm(t0, t1, 0x5410) ^ 0x80808080u; pl[1][t] = __byte_perm(t0, t1, 0x7632) ^ 0x80808080u;
+                pl[2][t] = __byte_perm(t2, t3, 0x5410) ^ 0x80808080u; pl[3][t] = __byte_perm(t2, t3, 0x7632) ^ 0x80808080u;
+                pl[4][t] = __byte_perm(__byte_perm(vhi[0], vhi[1], 0x0040), __byte_perm(vhi[2], vhi[3], 0x0040), 0x5410) ^ 0x80808080u;
             }
-            const uint32_t t0 = __byte_perm(vlo[0], vlo[1], 0x5140), t1 = __byte_perm(vlo[2], vlo[3], 0x5140);
-            const uint32_t t2 = __byte_perm(vlo[0], vlo[1], 0x7362), t3 = __byte_perm(vlo[2], vlo[3], 0x7362);
-            pl[0][u * 4 + t] = __byte_perm(t0, t1, 0x5410); pl[1][u * 4 + t] = __byte_perm(t0, t1, 0x7632);
-            pl[2][u * 4 + t] = __byte_perm(t2, t3, 0x5410); pl[3][u * 4 + t] = __byte_perm(t2, t3, 0x7632);
-            pl[4][u * 4 + t] = d4;
+#pragma unroll
+            for (int l = 0; l < 5; l++)
+                *reinterpret_cast<uint4 *>(wdst + hsel * (PLANE / 2) + l * PLANE + u * (PLANE / 4)) = make_uint4(pl[l][0], pl[l][1], pl[l][2], pl[l][3]);
         }
     }
 }
@@ -191,6 +194,23 @@ __device__ __forceinline__ void pf_tma_plane(void *dst, const CUtensorMap *map, 
                  ::"r"(pf_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(col), "r"(plane), "r"(row), "r"(pf_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void pf_group_sync(int group) { asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory"); }
+
+// floor(sum_s r_s 256^s / 2^fw), low 64 bits, for fw <= 32: four accumulators at a time fit int64 (|.| < 2^56), and a
+// group's factor 2^(32 g) is a whole multiple of 2^fw from the second group on, so only the first group is floored.
+template <int NACC>
+__device__ __forceinline__ int64_t pf_recombine(const int (&r)[NACC][8], int j, int fw) {
+    uint64_t y = 0;
+#pragma unroll
+    for (int g = 0; g * 4 < NACC; g++) {
+        int64_t v = r[4 * g][j];
+#pragma unroll
+        for (int t = 1; t < 4; t++)
+            if (4 * g + t < NACC) v += (int64_t)r[4 * g + t][j] * (int64_t)(1 << (8 * t));
+        if (g == 0) y = (uint64_t)(v >> fw);
+        else { const int sh = 32 * g - fw; if (sh < 64) y += (uint64_t)v << sh; }
+    }
+    return (int64_t)y;
+}
 
 // pair -> digit planes in pair order: dst[pair][NL][K] = src[xidx[pair]][0..NL-1][K] (the planes of a row are contiguous).
 // Only the pairs the groups own exist (the grid covers the caller's upper bound); `n_live` points at their count.
@@ -290,23 +310,26 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                 for (int b = 0; b < NL; b++) pf_tma_plane(stage + NWL * W_PLANE + b * X_PLANE, &xmap, c * PF_KC, b, m0, &full_bar[s]);
             }
             // weights: this thread's row, 64 columns as two halves of 32 (= the two K steps of the chunk)
+            uint8_t *wdst = stage + (gtid >> 3) * 128 + (gtid & 7) * 16;
+            if (QT == QT_Q6K && row_ok) {
+                static_assert(QT != QT_Q6K || NWL == 5, "Q6_K tiles carry five weight digits");
+                dequant64_q6k_store<W_PLANE>(wunit + (long long)(c >> 2) * HTB, rr, c & 3, a.fw, wdst);
+            } else {
 #pragma unroll
-            for (int hsel = 0; hsel < 2; hsel++) {
-                uint32_t pl[NWL][8];
-                if (row_ok) {
-                    if constexpr (QT == QT_Q4K) expand_q4k<NWL>(raw, c & 3, hsel, a.fw, pl);
-                    else dequant32_q6k<NWL>(wunit + (long long)(c >> 2) * HTB, rr, c & 3, hsel, a.fw, pl);
-                } else {
+                for (int hsel = 0; hsel < 2; hsel++) {
+                    uint32_t pl[NWL][8];
+                    if (QT == QT_Q4K && row_ok) expand_q4k<NWL>(raw, c & 3, hsel, a.fw, pl);
+                    else {
 #pragma unroll
-                    for (int l = 0; l < NWL; l++)
+                        for (int l = 0; l < NWL; l++)
 #pragma unroll
-                        for (int w = 0; w < 8; w++) pl[l][w] = 0;
-                }
-                uint8_t *wdst = stage + hsel * (W_PLANE / 2) + (gtid >> 3) * 128 + (gtid & 7) * 16;
+                            for (int w = 0; w < 8; w++) pl[l][w] = 0;
+                    }
 #pragma unroll
-                for (int l = 0; l < NWL; l++) {
-                    *reinterpret_cast<uint4 *>(wdst + l * W_PLANE) = make_uint4(pl[l][0], pl[l][1], pl[l][2], pl[l][3]);
-                    *reinterpret_cast<uint4 *>(wdst + l * W_PLANE + W_PLANE / 4) = make_uint4(pl[l][4], pl[l][5], pl[l][6], pl[l][7]);
+                    for (int l = 0; l < NWL; l++) {
+                        *reinterpret_cast<uint4 *>(wdst + hsel * (W_PLANE / 2) + l * W_PLANE) = make_uint4(pl[l][0], pl[l][1], pl[l][2], pl[l][3]);
+                        *reinterpret_cast<uint4 *>(wdst + hsel * (W_PLANE / 2) + l * W_PLANE + W_PLANE / 4) = make_uint4(pl[l][4], pl[l][5], pl[l][6], pl[l][7]);
+                    }
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> visible to the MMA
@@ -339,12 +362,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                     for (int s = 0; s < NACC; s++) pf_tmem_ld8(tlane + s * BN + c0, r[s]);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        i128 v = 0;
-#pragma unroll
-                        for (int s = NACC - 1; s >= 0; s--) v = (v << 8) + (i128)r[s][j];
-                        y[j] = (int64_t)(v >> a.fw);
-                    }
+                    for (int j = 0; j < 8; j++) y[j] = pf_recombine<NACC>(r, j, a.fw);
                 }
                 if (MODE == MODE_GATEUP) {
                     // gate rows keep columns 0..3 and hand 4..7 to their up row; up rows hand 0..3 to their gate row
@@ -504,6 +522,7 @@ cudaError_t launch_pf(const PrefillArgs &a_in, cudaStream_t s, int shape) {
 // combination has no tensor-core instantiation (the caller then uses the streamed kernels).
 cudaError_t launch_prefill(int qtype, int mode, int nl, const PrefillArgs &a, cudaStream_t s) {
     if (a.n_blocks <= 0 || a.n_blocks * 256 > 8192 || a.out_f <= 0 || a.n_pairs <= 0) return cudaErrorInvalidValue;
+    if (a.fw < 1 || a.fw > 32) return cudaErrorNotSupported;              // the epilogue's recombination floors the low group only
     if (qtype == QT_Q4K && mode == MODE_GATEUP) {
         if (nl <= 3) return launch_pf<QT_Q4K, MODE_GATEUP, 3, 4, 64>(a, s, 0);
         if (nl == 4) return launch_pf<QT_Q4K, MODE_GATEUP, 4, 4, 64>(a, s, 1);
