@@ -63,6 +63,56 @@ __global__ void limbs_kernel(const int64_t *x, long long n_rows, long long K, in
     if (nl_out && nl > 0) atomicMax(nl_out, nl);
 }
 
+// The same for K a multiple of 8: a thread takes eight consecutive columns (64 bytes in), transposes the 8 x 8 digit
+// bytes in registers and writes eight bytes to each plane.
+__global__ void __launch_bounds__(256) limbs8_kernel(const int64_t *__restrict__ x, long long n_rows, long long K, int8_t *__restrict__ planes,
+                                                     int *flags, int *nl_out) {
+    const long long per_row = K >> 3, total = n_rows * per_row;
+    bool bad = false;
+    uint64_t seen = 0;
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (long long)gridDim.x * blockDim.x) {
+        const long long row = g / per_row, col = (g - row * per_row) << 3;
+        const ulonglong2 *src = reinterpret_cast<const ulonglong2 *>(x + row * K + col);
+        uint32_t lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const ulonglong2 v = __ldg(src + i);
+            bool ok0, ok1;
+            const uint64_t d0 = balanced_digits8((int64_t)v.x, ok0), d1 = balanced_digits8((int64_t)v.y, ok1);
+            bad |= !ok0 | !ok1;
+            seen |= d0 | d1;                               // a digit position is in use if any element has a non-zero digit there or above
+            lo[2 * i] = (uint32_t)d0; hi[2 * i] = (uint32_t)(d0 >> 32);
+            lo[2 * i + 1] = (uint32_t)d1; hi[2 * i + 1] = (uint32_t)(d1 >> 32);
+        }
+        int8_t *dst = planes + row * 8 * K + col;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {             // digits 0..3 from the low words, 4..7 from the high words
+            const uint32_t *v = half ? hi : lo;
+            uint32_t a[4], b[4];                           // a: elements 0..3, b: elements 4..7, one word per digit
+            {
+                const uint32_t t0 = __byte_perm(v[0], v[1], 0x5140), t1 = __byte_perm(v[2], v[3], 0x5140);
+                const uint32_t t2 = __byte_perm(v[0], v[1], 0x7362), t3 = __byte_perm(v[2], v[3], 0x7362);
+                a[0] = __byte_perm(t0, t1, 0x5410); a[1] = __byte_perm(t0, t1, 0x7632);
+                a[2] = __byte_perm(t2, t3, 0x5410); a[3] = __byte_perm(t2, t3, 0x7632);
+            }
+            {
+                const uint32_t t0 = __byte_perm(v[4], v[5], 0x5140), t1 = __byte_perm(v[6], v[7], 0x5140);
+                const uint32_t t2 = __byte_perm(v[4], v[5], 0x7362), t3 = __byte_perm(v[6], v[7], 0x7362);
+                b[0] = __byte_perm(t0, t1, 0x5410); b[1] = __byte_perm(t0, t1, 0x7632);
+                b[2] = __byte_perm(t2, t3, 0x5410); b[3] = __byte_perm(t2, t3, 0x7632);
+            }
+#pragma unroll
+            for (int l = 0; l < 4; l++) *reinterpret_cast<uint2 *>(dst + (half * 4 + l) * K) = make_uint2(a[l], b[l]);
+        }
+    }
+    if (bad) atomicOr(flags, 1);
+    if (nl_out) {
+        // digits in use = position of the highest non-zero digit byte over all elements seen (at least one)
+        const int nl = seen == 0 ? 1 : 8 - (__clzll((long long)seen) >> 3);
+        atomicMax(nl_out, nl);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------
 // exact fallback: one thread per output, 128-bit accumulation in the reference's per-weight form
 // (north-mini-code/tools/nmc_qk_kernel.c:85-120).  Valid for every int64 input.
@@ -443,7 +493,10 @@ cudaError_t launch_add_rows(const int64_t *a, const int64_t *b, int64_t *out, lo
 
 cudaError_t launch_limbs(const int64_t *x, long long n_rows, long long K, int8_t *planes, int *flags, cudaStream_t s,
                          int *nl_out) {
-    limbs_kernel<<<grid_for(n_rows * K, 256), 256, 0, s>>>(x, n_rows, K, planes, flags, nl_out);
+    if (K % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(planes) & 7) == 0)
+        limbs8_kernel<<<grid_for(n_rows * (K >> 3), 256), 256, 0, s>>>(x, n_rows, K, planes, flags, nl_out);
+    else
+        limbs_kernel<<<grid_for(n_rows * K, 256), 256, 0, s>>>(x, n_rows, K, planes, flags, nl_out);
     note_launch();
     return cudaGetLastError();
 }

@@ -524,7 +524,7 @@ cudaError_t launch_prefill(int qtype, int mode, int nl, const PrefillArgs &a, cu
     if (a.n_blocks <= 0 || a.n_blocks * 256 > 8192 || a.out_f <= 0 || a.n_pairs <= 0) return cudaErrorInvalidValue;
     if (a.fw < 1 || a.fw > 32) return cudaErrorNotSupported;              // the epilogue's recombination floors the low group only
     if (qtype == QT_Q4K && mode == MODE_GATEUP) {
-        if (nl <= 3) return launch_pf<QT_Q4K, MODE_GATEUP, 3, 4, 64>(a, s, 0);
+        if (nl <= 3) return launch_pf<QT_Q4K, MODE_GATEUP, 3, 4, 80>(a, s, 0);
         if (nl == 4) return launch_pf<QT_Q4K, MODE_GATEUP, 4, 4, 64>(a, s, 1);
     }
     if (qtype == QT_Q6K && mode == MODE_DOWN) {
