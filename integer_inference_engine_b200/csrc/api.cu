@@ -189,6 +189,10 @@ long long register_quant(const void *raw, bool raw_on_device, long long out_f, l
 
 // y[T,out_f] on device from x[T,K] on device.  check_flags: synchronise and re-run the exact kernel
 // if an activation left the limb envelope (host-pointer entries); otherwise flags stay raised.
+// Dense product of a prefill-sized batch on the tensor-core tiles; returns false when the shape, the weights or the stream
+// (a capture cannot read the digit count back) rule them out, and the caller then takes the batched kernels.
+bool linear_tc(const Weight &w, const int8_t *xl, const int *x_nl, long long T, int fw, int64_t *out, cudaStream_t s);
+
 bool linear_dev(const Weight &w, const int64_t *x, long long T, int fw, int64_t *out, bool check_flags, cudaStream_t s,
                 const int8_t *xl_ready = nullptr) {
     const long long K = w.nb * 256;
@@ -206,7 +210,9 @@ bool linear_dev(const Weight &w, const int64_t *x, long long T, int fw, int64_t 
         if (launch_limbs(x, T, K, buf, g_flags, s, const_cast<int *>(x_nl)) != cudaSuccess) return false;
         xl = buf;
     }
-    if (T == 1 && w.out_f >= 256 && g_stage_mask == 0) {
+    if (T >= g_tc_min_tokens && x_nl && g_stage_mask == 0 && linear_tc(w, xl, x_nl, T, fw, out, s)) {
+        // done on the tcgen05 tiles
+    } else if (T == 1 && w.out_f >= 256 && g_stage_mask == 0) {
         // one row: the bulk-copy streaming kernel (every CTA requests its run of 16-row tiles up front)
         StreamArgs sa = {};
         sa.wa = w.cell; sa.wb = w.cell; sa.n_sel = 1; sa.out_f = w.out_f; sa.n_blocks = w.nb; sa.fw = fw; sa.fa = 16;
@@ -314,6 +320,23 @@ int read_cell(int idx, cudaStream_t s) {
     if (cudaMemcpyAsync(&v, g_cells + idx, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
     if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
     return v;
+}
+
+bool linear_tc(const Weight &w, const int8_t *xl, const int *x_nl, long long T, int fw, int64_t *out, cudaStream_t s) {
+    if (w.qtype != QT_Q4K || w.nb * 256 > 8192 || fw > 32 || !small_scales(w.maxd, w.maxdmin, fw) ||
+        max_weight(QT_Q4K, w.maxd, w.maxdmin, fw) > CAP4) return false;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) { cudaGetLastError(); return false; }
+    int nl = -1;
+    if (cudaMemcpyAsync(&nl, x_nl, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) return false;
+    if (nl < 1 || nl > 5) return false;
+    int *one_off = (int *)ensure(R_META, 64);
+    if (!one_off || launch_set2(one_off, 0, (int)T, s) != cudaSuccess) return false;
+    PrefillArgs ra = {};
+    ra.wa = w.cell; ra.wb = w.cell; ra.grp_off = one_off; ra.n_experts = 1; ra.n_pairs = T; ra.out_f = w.out_f;
+    ra.n_blocks = w.nb; ra.fw = fw; ra.fa = 16; ra.xl = xl; ra.out = out; ra.flags = g_flags;
+    if (launch_prefill(QT_Q4K, MODE_LINEAR, nl, ra, s) != cudaSuccess) { cudaGetLastError(); return false; }
+    return true;
 }
 
 // Expert stage on the tensor-core (tcgen05) tiles for pairs already sorted by group: group x uses the weights

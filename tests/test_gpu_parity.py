@@ -44,6 +44,20 @@ def test_linear_matches_oracle(qk, qtype, out_f, n_blocks, T):
         assert np.array_equal(got, o.qk_linear(raw, x, out_f, n_blocks, FW, qtype))
 
 
+@pytest.mark.parametrize("out_f,n_blocks,T,xbits", [(150, 2, 200, 20), (128, 1, 260, 34), (300, 3, 192, 12)])
+def test_prefill_sized_linear_runs_on_the_tensor_core_tiles(qk, out_f, n_blocks, T, xbits):
+    """From 192 rows on a dense Q4_K product takes the tcgen05 tiles (three or five activation digits); same answer."""
+    from integer_inference_engine_b200 import device
+    rng = np.random.default_rng(out_f + T)
+    raw = _synth(rng, o.Q4_K, out_f, n_blocks)
+    x = rng.integers(-(1 << xbits), 1 << xbits, size=(T, n_blocks * 256), dtype=np.int64)
+    before = device.prefill_launch_counts()
+    got = qk.qk_linear(raw, x, out_f, n_blocks, FW, o.Q4_K)
+    delta = [b - a for a, b in zip(before, device.prefill_launch_counts())]
+    assert got is not None and np.array_equal(got, onat.qk_linear(raw, x, out_f, n_blocks, FW, o.Q4_K))
+    assert delta[5] + delta[6] == 1, f"the product did not reach the tensor-core tiles: {delta}"
+
+
 def test_linear_golden_vectors(qk, golden_dir):
     g = np.load(golden_dir / "linear.npz")
     for i, (qt, out_f, nb, T, magbits) in enumerate(o.GOLDEN_LINEAR_CASES):
