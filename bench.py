@@ -769,12 +769,19 @@ def run_prefill(args):
     torch.cuda.synchronize()
     assert device.read_flags() == 0
     rows = [0, T // 3, T - 1]
-    sel, ref = _oracle_rows(stack, 0, h[rows].cpu().numpy())
+    h_rows = h[rows].cpu().numpy()
+    if rank == 0:
+        use_all_host_threads()
+    t0 = time.perf_counter()
+    sel, ref = _oracle_rows(stack, 0, h_rows)
+    cpu_s = time.perf_counter() - t0
     assert np.array_equal(ids[rows].cpu().numpy(), sel) and np.array_equal(out[rows].cpu().numpy(), ref), "block 0 differs from the oracle"
     x = x0.clone()
     l0 = device.launch_count()
+    shapes0 = device.prefill_launch_counts()
     stack.decode_step(x, FW)
     launches = device.launch_count() - l0
+    shapes = [b - a for a, b in zip(shapes0, device.prefill_launch_counts())]
 
     def step(i):
         x.copy_(x0)
@@ -801,6 +808,23 @@ def run_prefill(args):
     assert device.read_flags() == 0
     if rank == 0:
         ms_step = ms / args.steps
+        i8 = int8_peak()
+        # integer operations of one MoE block: algorithmic = 2 per multiply-add of the three expert products of every
+        # (token, expert) pair; issued = the same times the digit pairs the tiles multiply (activation digits x weight digits)
+        pair_macs = TOP_K * T * D_MODEL * E_FFN
+        nl_gu = 3 if shapes[0] else 4
+        nl_dn = 5 if shapes[2] else 6
+        algorithmic = 2.0 * 3 * pair_macs
+        issued = 2.0 * pair_macs * (2 * nl_gu * 4 + nl_dn * 5)
+        blk_s = ms_step / args.layers * 1e-3
+        roofline = {"bound": "tensor", "kernel": "prefill_kernel gate/up + down of one MoE block (router, sort and digit planes included in the time)",
+                    "unit": "TOP/s", "peak": i8["sustained_tops"], "peak_kind": "int8 GEMM measured in this run (torch._int_mm, sustained)",
+                    "achieved": algorithmic / blk_s / 1e12, "frac": algorithmic / blk_s / 1e12 / i8["sustained_tops"],
+                    "issued_achieved": issued / blk_s / 1e12, "issued_frac": issued / blk_s / 1e12 / i8["sustained_tops"],
+                    "digits": {"gate_up": {"activation": nl_gu, "weight": 4}, "down": {"activation": nl_dn, "weight": 5}},
+                    "tile_launches": shapes, "traffic": None}
+        cpu = {"value": len(rows) / cpu_s / args.layers, "unit": "tok/s", "cores": host_cores(), "kind": "port",
+               "sample": f"{len(rows)} rows through router, top-{TOP_K} and their {TOP_K} experts of one block on the CPU oracle, scaled to {args.layers} blocks (rows are independent)"}
         print(json.dumps({
             "metric": "prefill_tok_per_s", "value": world * T * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -809,7 +833,7 @@ def run_prefill(args):
                        "ms_per_block": ms_step / args.layers, "attention_prefill_ms_per_block": att_ms / 3,
                        "parallelism": f"replicas x{world}",
                        "l2": "inputs larger than L2 (1.2 GB of expert weights per block)", "oracle_checked_rows": len(rows)},
-            "clocks": clocks, "gpu_launches": int(launches * args.steps)}))
+            "clocks": clocks, "gpu_launches": int(launches * args.steps), "int8_peak": i8, "roofline": roofline, "cpu_baseline": cpu}))
     if world > 1:
         dist.destroy_process_group()
 

@@ -258,6 +258,11 @@ void iie_decoder_destroy(long long dec);
 int iie_embed_dev(long long h, const int *token_dev, long long token, int frac, int64_t *out_dev, void *stream);
 /* Index of the largest of n int64 values, lowest index on ties (greedy pick of engine.py:585). */
 int iie_argmax_dev(const int64_t *x_dev, long long n, int *out_dev, void *stream);
+/* The same for a batch of sequences in one launch each: rows tokens_dev[i] of the matrix -> out_dev[i][width], and the
+ * arg-max of each of `rows` rows of n values -> out_dev[i] (a token id of the embedding outside the matrix is the
+ * caller's error: ids come from iie_argmax_rows_dev over the same vocabulary). */
+int iie_embed_rows_dev(long long h, const int *tokens_dev, int rows, int frac, int64_t *out_dev, void *stream);
+int iie_argmax_rows_dev(const int64_t *x_dev, long long rows, long long n, int *out_dev, void *stream);
 
 /* Plain resident product on device tensors: out_dev [T,out_f] = floor(x_dev W^T / 2^fw). */
 int iie_apply_dev(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev, void *stream);

@@ -1661,6 +1661,19 @@ extern "C" int iie_argmax_dev(const int64_t *x_dev, long long n, int *out_dev, v
     return launch_argmax(x_dev, n, out_dev, (cudaStream_t)stream) == cudaSuccess ? 0 : 1;
 }
 
+extern "C" int iie_embed_rows_dev(long long h, const int *tokens_dev, int rows, int frac, int64_t *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !valid_q(h) || !tokens_dev || !out_dev || rows <= 0 || frac < 0 || frac > 40) return 1;
+    const Weight &w = g_w[h];
+    return launch_embed_rows((const uint8_t *)w.d, w.qtype, w.nb, tokens_dev, rows, frac, out_dev, (cudaStream_t)stream) == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int iie_argmax_rows_dev(const int64_t *x_dev, long long rows, long long n, int *out_dev, void *stream) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!init() || !x_dev || !out_dev || n <= 0 || rows <= 0) return 1;
+    return launch_argmax_rows(x_dev, rows, n, out_dev, (cudaStream_t)stream) == cudaSuccess ? 0 : 1;
+}
+
 extern "C" int iie_apply_dev(long long h, const int64_t *x_dev, long long T, int fw, int64_t *out_dev, void *stream) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (!init() || !valid_q(h) || !x_dev || !out_dev || T <= 0) return 1;

@@ -1084,11 +1084,13 @@ __global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in
 }
 
 // one row of a registered Q4_K / Q6_K matrix as int64 at 2^frac (the embedding look-up)
+// (grid.y rows at once: row_dev[y] -> out[y][nb * 256])
 __global__ void embed_row_kernel(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,
                                  int64_t *out) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nb * 256) return;
-    const long long o = row_dev ? (long long)*row_dev : row_host, b = i >> 8;
+    out += (long long)blockIdx.y * nb * 256;
+    const long long o = row_dev ? (long long)row_dev[blockIdx.y] : row_host, b = i >> 8;
     const int e = (int)(i & 255);
     auto byte = [&](int k) { return (int)repacked_byte(w, qtype, nb, o, b, k); };
     int64_t val;
@@ -1108,6 +1110,45 @@ __global__ void embed_row_kernel(const uint8_t *w, int qtype, long long nb, cons
         val = dq * (int64_t)(int8_t)byte(192 + 8 * half + 2 * k + (sb & 1)) * q;
     }
     out[i] = val;
+}
+
+// arg-max of each of grid.x rows of n values, lowest index on ties: one CTA per row
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const int64_t *x, long long n, int *out) {
+    __shared__ long long s_v[32];
+    __shared__ long long s_i[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t *row = x + (long long)blockIdx.x * n;
+    long long bv = INT64_MIN, bi = n;
+    auto better = [](long long ov, long long oi, long long v, long long i) { return ov > v || (ov == v && oi < i); };
+    long long i = tid * 2LL;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0)
+        for (; i + 1 < n; i += 2048) {                              // two values per load
+            const longlong2 v = *reinterpret_cast<const longlong2 *>(row + i);
+            if (better(v.x, i, bv, bi)) { bv = v.x; bi = i; }
+            if (better(v.y, i + 1, bv, bi)) { bv = v.y; bi = i + 1; }
+        }
+    else
+        for (; i + 1 < n; i += 2048) {
+            if (better(row[i], i, bv, bi)) { bv = row[i]; bi = i; }
+            if (better(row[i + 1], i + 1, bv, bi)) { bv = row[i + 1]; bi = i + 1; }
+        }
+    if (i < n && better(row[i], i, bv, bi)) { bv = row[i]; bi = i; }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        const long long ov = __shfl_xor_sync(0xffffffffu, bv, s), oi = __shfl_xor_sync(0xffffffffu, bi, s);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { s_v[warp] = bv; s_i[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        bv = s_v[lane]; bi = s_i[lane];
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) {
+            const long long ov = __shfl_xor_sync(0xffffffffu, bv, s), oi = __shfl_xor_sync(0xffffffffu, bi, s);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = (int)bi;
+    }
 }
 
 // arg-max with the lowest index on ties: every CTA leaves its candidate in a static table, the CTA that arrives last
@@ -1305,6 +1346,20 @@ cudaError_t launch_attn_reset(long long *hmax, unsigned long long *Z, long long 
 cudaError_t launch_embed_row(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,
                              int64_t *out, cudaStream_t s) {
     embed_row_kernel<<<(unsigned)((nb * 256 + 255) / 256), 256, 0, s>>>(w, qtype, nb, row_dev, row_host, frac, out);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_embed_rows(const uint8_t *w, int qtype, long long nb, const int *rows_dev, int n_rows, int frac, int64_t *out, cudaStream_t s) {
+    if (n_rows <= 0 || n_rows > 65535 || !rows_dev) return cudaErrorInvalidValue;
+    embed_row_kernel<<<dim3((unsigned)((nb * 256 + 255) / 256), (unsigned)n_rows), 256, 0, s>>>(w, qtype, nb, rows_dev, 0, frac, out);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_rows(const int64_t *x, long long rows, long long n, int *out, cudaStream_t s) {
+    if (n <= 0 || rows <= 0 || rows > 0x7fffffffLL) return cudaErrorInvalidValue;
+    argmax_rows_kernel<<<(unsigned)rows, 1024, 0, s>>>(x, n, out);
     note_launch();
     return cudaGetLastError();
 }

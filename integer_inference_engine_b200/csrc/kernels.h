@@ -251,6 +251,9 @@ cudaError_t launch_attn_reset(long long *hmax, unsigned long long *Z, long long 
 cudaError_t launch_embed_row(const uint8_t *w, int qtype, long long nb, const int *row_dev, long long row_host, int frac,
                              int64_t *out, cudaStream_t s);
 cudaError_t launch_argmax(const int64_t *x, long long n, int *out, cudaStream_t s);
+// the same for many rows in one launch: rows_dev[i] -> out[i][nb * 256]; arg-max of each of `rows` rows of n values
+cudaError_t launch_embed_rows(const uint8_t *w, int qtype, long long nb, const int *rows_dev, int n_rows, int frac, int64_t *out, cudaStream_t s);
+cudaError_t launch_argmax_rows(const int64_t *x, long long rows, long long n, int *out, cudaStream_t s);
 
 // Whole decode step as one persistent cooperative kernel (decode.cu).
 struct DecodeLayer {

@@ -293,6 +293,34 @@ def argmax(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     return out
 
 
+def embed_rows(handle: int, tokens: torch.Tensor, d_model: int, fa: int = 16, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Rows ``tokens`` (CUDA int32 [B]) of a registered matrix at 2**fa -> [B, d_model], one launch."""
+    lib = qk_cuda._lib()
+    assert tokens.is_cuda and tokens.dtype == torch.int32 and tokens.is_contiguous()
+    B = tokens.numel()
+    if out is None:
+        out = torch.empty((B, d_model), dtype=torch.int64, device="cuda")
+    assert out.is_contiguous() and out.shape == (B, d_model)
+    with _CUDA_LOCK:
+        rc = lib.iie_embed_rows_dev(int(handle), tokens.data_ptr(), B, int(fa), out.data_ptr(), _stream_ptr())
+    if rc != 0:
+        raise CudaContextError(f"embedding look-up failed with status {rc}")
+    return out
+
+
+def argmax_rows(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Per row of ``x`` [B, n]: index of the largest value, lowest index on ties -> CUDA int32 [B], one launch."""
+    lib = qk_cuda._lib()
+    assert x.is_cuda and x.dtype == torch.int64 and x.dim() == 2 and x.is_contiguous()
+    if out is None:
+        out = torch.empty(x.shape[0], dtype=torch.int32, device=x.device)
+    with _CUDA_LOCK:
+        rc = lib.iie_argmax_rows_dev(x.data_ptr(), x.shape[0], x.shape[1], out.data_ptr(), _stream_ptr())
+    if rc != 0:
+        raise CudaContextError(f"argmax failed with status {rc}")
+    return out
+
+
 def workspace_generation() -> int:
     """Changes whenever a scratch buffer of the library is freed (regrown or released).  A CUDA graph captured over the
     device entries holds the addresses of its capture: compare before replaying."""

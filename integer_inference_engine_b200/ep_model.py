@@ -107,13 +107,11 @@ class ExpertParallelDecoder:
     def step(self) -> None:
         """One token for every sequence of this rank: embedding rows of ``self.tokens`` -> blocks -> head -> greedy picks,
         left in ``self.tokens``.  The position does not advance here (see :meth:`advance`)."""
-        for b in range(self.B):
-            device.embed(self.embd, self.tokens[b:b + 1], self.d, self.fa, out=self.x[b:b + 1])
+        device.embed_rows(self.embd, self.tokens, self.d, self.fa, out=self.x)
         self.blocks_step(self.x)
         device.rmsnorm(self.x, self.out_gain_h, self.fa, 1, out=self.hn)
         device.apply(self.embd, self.hn, self.vocab, self.fw, out=self.logits)
-        for b in range(self.B):
-            device.argmax(self.logits[b], out=self.tokens[b:b + 1])
+        device.argmax_rows(self.logits, out=self.tokens)
 
     def advance(self) -> None:
         if self.position + 1 >= self.rows:

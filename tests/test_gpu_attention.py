@@ -116,6 +116,14 @@ def test_embedding_row_and_argmax():
     assert int(device.argmax(torch.from_numpy(x).cuda()).item()) == 7
     x[:] = -5
     assert int(device.argmax(torch.from_numpy(x).cuda()).item()) == 0
+    # the batched forms: several rows / several sequences in one launch each
+    toks = torch.tensor([49, 0, 17, 17, 33], dtype=torch.int32, device="cuda")
+    assert np.array_equal(device.embed_rows(h, toks, 768, FA).cpu().numpy(), table[[49, 0, 17, 17, 33]])
+    for n in (151936, 1001, 7):
+        xs = rng.integers(-1000, 1000, size=(5, n), dtype=np.int64)
+        xs[1, [3, n - 1]] = 7000; xs[2, :] = -9; xs[3, n - 1] = 9000; xs[4, n // 2] = 8000
+        want = [int(np.flatnonzero(r == r.max())[0]) for r in xs]
+        assert device.argmax_rows(torch.from_numpy(xs).cuda()).cpu().tolist() == want
 
 
 @pytest.mark.parametrize("form", [0, 1])
