@@ -1309,6 +1309,14 @@ cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s) {
     if (a.window > 0 && n_keys > a.window) n_keys = a.window;
     const unsigned chunks = (unsigned)((n_keys + AT_CH - 1) / AT_CH);
     attn_append_kernel<<<dim3((unsigned)a.batch, a.Hkv), 128, 0, s>>>(a);
+    if (g_attn_fused != 0 && attn_tiles_ok(a)) {
+        // consecutive tokens of one sequence: sixteen tokens per CTA share every staged chunk of keys and values
+        note_launch(2);
+        cudaError_t e = launch_attn_tile_scores(a, s);
+        if (e != cudaSuccess) return e;
+        attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H, (unsigned)a.batch), 256, 0, s>>>(a);
+        return launch_attn_tile_pv(a, s);
+    }
     const bool tc = g_attn_fused != 0 && rep <= AF_HEADS && (a.hd == 64 || a.hd == 128);      // shapes the tensor-core kernel carries
     if (tc) {
         static bool tc_configured = false;

@@ -1,0 +1,447 @@
+// Prefill attention by query tiles: passes 1 and 3 of the exact softmax (north-mini-code/src/nmc/cohere2.py:324-354 with
+// _bonsai/fixedpoint.py:99-133; the arithmetic is stated at the top of attn.cu) for `batch` consecutive tokens of one
+// sequence, sixteen tokens x the query heads of one KV head per CTA.
+//
+// The per-token kernels of attn.cu stage a 64-key chunk of K (or V) for the eight score columns of ONE token; here the chunk
+// is staged once for 128 columns, as byte planes, and both products run on the tensor cores with the byte decomposition of
+// attn_fat_kernel: an int32 is b0 + 2^8 b1 + 2^16 b2 + 2^24 b3 with b0..b2 unsigned and b3 signed, every byte pair is an
+// exact int8 MMA (m16n8k32), pairs of equal a + b share an int32 accumulator, and the 64-bit value is re-assembled as
+// sum_s 256^s acc_s in wrapping arithmetic (which is what the reference's int64 products do).
+//   scores:  D[key][column] = K bytes (A, 16 keys x 32 dims) x rotated query bytes (B, 32 dims x 8 heads of one token)
+//   p x v:   D[token of one head][dim] = probability bytes (A, 16 tokens x 32 keys) x value bytes (B, 32 keys x 8 dims)
+// The exponentials in between are attn_exp_kernel's.  Causality and the window are masks per (token, key); a masked
+// probability is zero.  A query beyond int32 (the reference multiplies it as int64) takes a scalar path inside the
+// scores kernel.
+#include <algorithm>
+
+#include "kernels.h"
+
+namespace iie {
+
+namespace {
+
+constexpr int PT_Q = 16;                    // tokens of a tile
+constexpr int PT_HEADS = 8;                 // query heads of a KV head (rows beyond the real count are zero)
+constexpr int PT_COLS = PT_Q * PT_HEADS;    // 128 (token, head) columns / rows
+constexpr int PT_THREADS = 512;
+constexpr int PT_CH = 64;                   // keys per chunk
+constexpr int PT_WALK = 4;                  // chunks a scores CTA walks
+constexpr int PT_PLD = PT_CH + 16;          // bytes per row of a key-major byte plane (probabilities, transposed values)
+
+// D(16x8,s32) += A(16x32, 8-bit, row) * B(32x8, 8-bit, col), signedness per operand
+template <bool A_SIGNED, bool B_SIGNED>
+__device__ __forceinline__ void pt_mma(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if (A_SIGNED && B_SIGNED)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else if (A_SIGNED)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else if (B_SIGNED)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// four int32 -> one word per byte plane (byte i of plane b = byte b of value i)
+__device__ __forceinline__ void pt_planes(uint32_t x, uint32_t y, uint32_t z, uint32_t w, uint32_t &d0, uint32_t &d1, uint32_t &d2, uint32_t &d3) {
+    const uint32_t t0 = __byte_perm(x, y, 0x5140), t1 = __byte_perm(x, y, 0x7362);
+    const uint32_t t2 = __byte_perm(z, w, 0x5140), t3 = __byte_perm(z, w, 0x7362);
+    d0 = __byte_perm(t0, t2, 0x5410); d1 = __byte_perm(t0, t2, 0x7632);
+    d2 = __byte_perm(t1, t3, 0x5410); d3 = __byte_perm(t1, t3, 0x7632);
+}
+
+__device__ __forceinline__ void pt_rotate(const AttnArgs &a, long long pos, int i, int64_t &x0, int64_t &x1) {
+    if (!a.rope) return;
+    const int half = a.hd / 2;
+    const int64_t c = a.cos[pos * half + i], s = a.sin[pos * half + i];
+    const int64_t y0 = (x0 * c - x1 * s) >> a.fa, y1 = (x0 * s + x1 * c) >> a.fa;
+    x0 = y0; x1 = y1;
+}
+
+struct Tile {                               // the sixteen tokens of a CTA
+    long long t0, pos0, pos_last, lo_t;
+    int nq;
+};
+__device__ __forceinline__ Tile pt_tile(const AttnArgs &a, long long tile) {
+    Tile t;
+    t.t0 = tile * PT_Q;
+    t.nq = (int)min((long long)PT_Q, (long long)a.batch - t.t0);
+    t.pos0 = a.pos + t.t0;
+    t.pos_last = t.pos0 + t.nq - 1;
+    t.lo_t = (a.window > 0 && t.pos0 - a.window + 1 > 0) ? t.pos0 - a.window + 1 : 0;      // first key the first token sees
+    return t;
+}
+__device__ __forceinline__ long long pt_lo(const AttnArgs &a, long long pos) { return (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0; }
+
+// ---- pass 1: scores[token][head][key] and the row maxima ----------------------------------------------------------------
+// grid (walks, Hkv, tiles): CTA x walks PT_WALK chunks of the tile's key span.  16 warps = 4 key tiles x 4 groups of four
+// tokens; a warp multiplies one key tile with two tokens at a time (56 accumulator registers).
+template <int HD>
+__global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_scores_kernel(const AttnArgs a) {
+    constexpr int QLD = HD + 16, HALF = HD / 2, VPT = HD / 32;     // bytes per plane row; 16-byte vectors of a chunk per thread
+    extern __shared__ __align__(16) unsigned char pt_smem[];
+    __shared__ long long s_max[PT_COLS];
+    __shared__ int s_wide;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int rep = a.H / a.Hkv, kv = blockIdx.y;
+    const Tile T = pt_tile(a, (long long)gridDim.z - 1 - blockIdx.z);           // long tiles first
+    const long long c_first = T.lo_t / PT_CH + (long long)blockIdx.x * PT_WALK;
+    if (c_first * PT_CH > T.pos_last) return;
+    const long long Ls = a.Ls ? a.Ls : a.Lmax;
+    int8_t *qd = reinterpret_cast<int8_t *>(pt_smem);             // query byte planes [4][128 columns][QLD], column = token * 8 + head
+    int8_t *kd = qd + 4 * PT_COLS * QLD;                          // key byte planes [2 buffers][4][64 keys][QLD]
+    if (tid < PT_COLS) s_max[tid] = INT64_MIN;
+    if (tid == 0) s_wide = 0;
+    __syncthreads();
+    bool wide = false;
+    for (int idx = tid; idx < PT_COLS * HALF; idx += PT_THREADS) {
+        const int col = idx / HALF, i = idx - col * HALF, qi = col >> 3, h = col & 7;
+        const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + HALF : 2 * i + 1;
+        int64_t x0 = 0, x1 = 0;
+        if (qi < T.nq && h < rep) {
+            const int64_t *src = a.q + ((T.t0 + qi) * a.H + kv * rep + h) * HD;
+            x0 = src[i0]; x1 = src[i1];
+            pt_rotate(a, T.pos0 + qi, i, x0, x1);
+        }
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            qd[(b * PT_COLS + col) * QLD + i0] = (int8_t)((uint32_t)(int32_t)x0 >> (8 * b));
+            qd[(b * PT_COLS + col) * QLD + i1] = (int8_t)((uint32_t)(int32_t)x1 >> (8 * b));
+        }
+        wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+    }
+    if (wide) s_wide = 1;
+    __syncthreads();
+    auto publish_max = [&]() {
+        __syncthreads();
+        if (tid < PT_COLS && s_max[tid] != INT64_MIN) {
+            const int qi = tid >> 3, h = tid & 7;
+            atomicMax(a.hmax + (T.t0 + qi) * a.H + kv * rep + h, s_max[tid]);
+        }
+    };
+    if (s_wide) {
+        // a query value beyond int32: 64-bit wrapping products, one thread per (key, column); the rotated queries as int64
+        // take the place of every byte plane
+        long long *q64 = reinterpret_cast<long long *>(pt_smem);   // [128][HD]
+        for (int idx = tid; idx < PT_COLS * HALF; idx += PT_THREADS) {
+            const int col = idx / HALF, i = idx - col * HALF, qi = col >> 3, h = col & 7;
+            const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + HALF : 2 * i + 1;
+            int64_t x0 = 0, x1 = 0;
+            if (qi < T.nq && h < rep) {
+                const int64_t *src = a.q + ((T.t0 + qi) * a.H + kv * rep + h) * HD;
+                x0 = src[i0]; x1 = src[i1];
+                pt_rotate(a, T.pos0 + qi, i, x0, x1);
+            }
+            q64[col * HD + i0] = x0; q64[col * HD + i1] = x1;
+        }
+        __syncthreads();
+        for (int w = 0; w < PT_WALK; w++) {
+            const long long l0 = (c_first + w) * PT_CH;
+            if (l0 > T.pos_last) break;
+            for (int idx = tid; idx < PT_CH * PT_COLS; idx += PT_THREADS) {
+                const int key = idx >> 7, col = idx & 127, qi = col >> 3, h = col & 7;
+                const long long l = l0 + key, pos_q = T.pos0 + qi;
+                if (qi >= T.nq || h >= rep || l > pos_q || l < pt_lo(a, pos_q)) continue;
+                const int32_t *kk = a.kcache + ((long long)kv * a.Lmax + l) * HD;
+                long long dot = 0;
+                for (int j = 0; j < HD; j++) dot += q64[col * HD + j] * (long long)kk[j];
+                const long long sc = ((dot >> a.fa) * a.inv_sqrt) >> a.fa;
+                a.scores[((T.t0 + qi) * a.H + kv * rep + h) * Ls + l] = sc;
+                atomicMax(&s_max[col], sc);
+            }
+        }
+        publish_max();
+        return;
+    }
+    int4 kreg[VPT];
+    auto load = [&](long long c) {                                 // keys of chunk c into registers (rows past the last token: zero)
+#pragma unroll
+        for (int u = 0; u < VPT; u++) {
+            const int v = tid + u * PT_THREADS, key = v / (HD / 4), part = v - key * (HD / 4);
+            const long long l = c * PT_CH + key;
+            kreg[u] = l <= T.pos_last ? __ldg(reinterpret_cast<const int4 *>(a.kcache + ((long long)kv * a.Lmax + l) * HD) + part) : make_int4(0, 0, 0, 0);
+        }
+    };
+    auto store = [&](int buf) {                                    // registers -> byte planes of buffer buf
+#pragma unroll
+        for (int u = 0; u < VPT; u++) {
+            const int v = tid + u * PT_THREADS, key = v / (HD / 4), part = v - key * (HD / 4);
+            uint32_t d[4];
+            pt_planes((uint32_t)kreg[u].x, (uint32_t)kreg[u].y, (uint32_t)kreg[u].z, (uint32_t)kreg[u].w, d[0], d[1], d[2], d[3]);
+#pragma unroll
+            for (int b = 0; b < 4; b++) *reinterpret_cast<uint32_t *>(kd + ((buf * 4 + b) * PT_CH + key) * QLD + part * 4) = d[b];
+        }
+    };
+    const int mt = warp & 3, ng = warp >> 2;
+    load(c_first);
+    for (int w = 0; w < PT_WALK; w++) {
+        const long long c = c_first + w, l0 = c * PT_CH;
+        if (l0 > T.pos_last) break;                                // uniform over the CTA
+        const int buf = w & 1;
+        store(buf);
+        __syncthreads();                                           // planes of chunk c visible; the other buffer's readers are done
+        if (w + 1 < PT_WALK && l0 + PT_CH <= T.pos_last) load(c + 1);
+        const long long key_lo = l0 + mt * 16, key_hi = key_lo + 15;
+#pragma unroll 1
+        for (int np = 0; np < 2; np++) {
+            const int n0 = ng * 4 + np * 2;                        // tokens n0 and n0 + 1
+            // nothing of this key tile is visible to either token: warp-uniform skip
+            if (n0 >= T.nq || key_lo > T.pos0 + n0 + 1 || key_hi < pt_lo(a, T.pos0 + n0)) continue;
+            int acc[2][7][4];
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int s = 0; s < 7; s++) { acc[j][s][0] = acc[j][s][1] = acc[j][s][2] = acc[j][s][3] = 0; }
+#pragma unroll
+            for (int st = 0; st < HD / 32; st++) {
+                uint32_t A[4][4];
+#pragma unroll
+                for (int aa = 0; aa < 4; aa++) {
+                    const int8_t *base = kd + ((buf * 4 + aa) * PT_CH + mt * 16 + g) * QLD + 32 * st + 4 * t;
+                    A[aa][0] = *reinterpret_cast<const uint32_t *>(base); A[aa][1] = *reinterpret_cast<const uint32_t *>(base + 8 * QLD);
+                    A[aa][2] = *reinterpret_cast<const uint32_t *>(base + 16); A[aa][3] = *reinterpret_cast<const uint32_t *>(base + 8 * QLD + 16);
+                }
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int b = 0; b < 4; b++) {
+                        const int8_t *qb = qd + (b * PT_COLS + (n0 + j) * 8 + g) * QLD + 32 * st + 4 * t;
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(qb), b1 = *reinterpret_cast<const uint32_t *>(qb + 16);
+#pragma unroll
+                        for (int aa = 0; aa < 4; aa++) {
+                            if (aa < 3 && b < 3) pt_mma<false, false>(acc[j][aa + b], A[aa], b0, b1);
+                            else if (aa < 3) pt_mma<false, true>(acc[j][aa + b], A[aa], b0, b1);
+                            else if (b < 3) pt_mma<true, false>(acc[j][aa + b], A[aa], b0, b1);
+                            else pt_mma<true, true>(acc[j][aa + b], A[aa], b0, b1);
+                        }
+                    }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int qi = n0 + j;
+                const long long pos_q = T.pos0 + qi, lo_q = pt_lo(a, pos_q);
+                long long m2[2] = {INT64_MIN, INT64_MIN};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    long long dot = 0;
+#pragma unroll
+                    for (int s = 6; s >= 0; s--) dot = dot * 256 + (long long)acc[j][s][i];
+                    const long long l = key_lo + g + (i >= 2 ? 8 : 0);
+                    const int h = 2 * t + (i & 1);
+                    if (qi < T.nq && h < rep && l <= pos_q && l >= lo_q) {
+                        const long long sc = ((dot >> a.fa) * a.inv_sqrt) >> a.fa;
+                        a.scores[((T.t0 + qi) * a.H + kv * rep + h) * Ls + l] = sc;
+                        m2[i & 1] = max(m2[i & 1], sc);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    long long m = m2[u];
+                    m = max(m, __shfl_xor_sync(0xffffffffu, m, 4)); m = max(m, __shfl_xor_sync(0xffffffffu, m, 8));
+                    m = max(m, __shfl_xor_sync(0xffffffffu, m, 16));
+                    if (g == 0 && m != INT64_MIN) atomicMax(&s_max[qi * 8 + 2 * t + u], m);
+                }
+            }
+        }
+    }
+    publish_max();
+}
+
+// ---- pass 3: out[token][head][dim] = (sum over keys of p x v) >> fa --------------------------------------------------------
+// grid (1, Hkv, tiles): the CTA walks every chunk of the tile's key span.  Rows are head * 16 + token; 16 warps = 8 heads x
+// the two halves of the head dimension; the 64-bit sums of a thread's outputs stay in registers over the whole walk.
+template <int HD>
+__global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_pv_kernel(const AttnArgs a) {
+    constexpr int NT = HD / 16;                                    // 8-wide dimension tiles of a warp
+    constexpr int VU = HD / 32;                                    // (dimension, four keys) units of a thread per chunk
+    extern __shared__ __align__(16) unsigned char pt_smem[];
+    __shared__ unsigned long long s_z[PT_COLS], s_inv[PT_COLS];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int rep = a.H / a.Hkv, kv = blockIdx.y;
+    const Tile T = pt_tile(a, (long long)gridDim.z - 1 - blockIdx.z);
+    const long long Ls = a.Ls ? a.Ls : a.Lmax;
+    uint8_t *vT = pt_smem;                                         // value byte planes [2 buffers][4][HD dims][PT_PLD], keys along a row
+    uint8_t *pT = vT + 2 * 4 * HD * PT_PLD;                        // probability byte planes [3][128 rows][PT_PLD]
+    if (tid < PT_COLS) {
+        const int h = tid >> 4, qi = tid & 15;
+        unsigned long long z = 0;
+        if (qi < T.nq && h < rep) z = a.Z[(T.t0 + qi) * a.H + kv * rep + h];
+        s_z[tid] = z; s_inv[tid] = z ? 0xFFFFFFFFFFFFFFFFULL / z : 0ULL;
+    }
+    const int vd = tid % HD, vq0 = tid / HD;                       // this thread's dimension and first key group of the value staging
+    int vreg[VU][4];
+    auto load_v = [&](long long c) {
+#pragma unroll
+        for (int u = 0; u < VU; u++) {
+            const int kq = vq0 + u * (PT_THREADS / HD);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const long long l = c * PT_CH + 4 * kq + i;
+                vreg[u][i] = l <= T.pos_last ? __ldg(a.vcache + ((long long)kv * a.Lmax + l) * HD + vd) : 0;
+            }
+        }
+    };
+    auto store_v = [&](int buf) {
+#pragma unroll
+        for (int u = 0; u < VU; u++) {
+            const int kq = vq0 + u * (PT_THREADS / HD);
+            uint32_t d[4];
+            pt_planes((uint32_t)vreg[u][0], (uint32_t)vreg[u][1], (uint32_t)vreg[u][2], (uint32_t)vreg[u][3], d[0], d[1], d[2], d[3]);
+#pragma unroll
+            for (int b = 0; b < 4; b++) *reinterpret_cast<uint32_t *>(vT + ((buf * 4 + b) * HD + vd) * PT_PLD + 4 * kq) = d[b];
+        }
+    };
+    long long acc64[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) { acc64[nt][0] = acc64[nt][1] = acc64[nt][2] = acc64[nt][3] = 0; }
+    const int mt = warp & 7, nh = warp >> 3;
+    const long long c_lo = T.lo_t / PT_CH, c_hi = T.pos_last / PT_CH;
+    load_v(c_lo);
+    __syncthreads();                                               // s_z / s_inv
+    for (long long c = c_lo; c <= c_hi; c++) {
+        const int buf = (int)((c - c_lo) & 1);
+        const long long l0 = c * PT_CH;
+        // exponentials of this chunk: requested first, the value planes are written while they arrive
+        int4 e4[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int row = (tid >> 4) + 32 * u, kg = tid & 15, h = row >> 4, qi = row & 15;
+            e4[u] = make_int4(0, 0, 0, 0);
+            if (qi < T.nq && h < rep && l0 + 4 * kg <= T.pos0 + qi)
+                e4[u] = __ldg(reinterpret_cast<const int4 *>(a.e + ((T.t0 + qi) * a.H + kv * rep + h) * Ls + l0 + 4 * kg));
+        }
+        store_v(buf);
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int row = (tid >> 4) + 32 * u, kg = tid & 15, qi = row & 15;
+            const long long pos_q = T.pos0 + qi, lo_q = pt_lo(a, pos_q);
+            const unsigned long long z = s_z[row], inv = s_inv[row];
+            const int ev[4] = {e4[u].x, e4[u].y, e4[u].z, e4[u].w};
+            uint32_t p[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const long long l = l0 + 4 * kg + i;
+                uint32_t pv = 0;
+                if (z && l <= pos_q && l >= lo_q) {                // (e << fa) / z through the row's reciprocal: the estimate is at most 2 low
+                    const unsigned long long n = (unsigned long long)(uint32_t)ev[i] << a.fa;
+                    unsigned long long q = __umul64hi(n, inv), r = n - q * z;
+                    while (r >= z) { q++; r -= z; }
+                    pv = (uint32_t)q;
+                }
+                p[i] = pv;
+            }
+            uint32_t d0, d1, d2, d3;
+            pt_planes(p[0], p[1], p[2], p[3], d0, d1, d2, d3);
+            uint8_t *dst = pT + row * PT_PLD + 4 * kg;
+            *reinterpret_cast<uint32_t *>(dst) = d0;
+            *reinterpret_cast<uint32_t *>(dst + PT_COLS * PT_PLD) = d1;
+            *reinterpret_cast<uint32_t *>(dst + 2 * PT_COLS * PT_PLD) = d2;
+        }
+        __syncthreads();                                           // planes of chunk c visible
+        if (c < c_hi) load_v(c + 1);
+        // the head's sixteen tokens x this warp's dimensions; tokens that see nothing of the chunk have zero probabilities
+        uint32_t A[2][3][4];
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+            for (int b = 0; b < 3; b++) {
+                const uint8_t *base = pT + (b * PT_COLS + mt * 16 + g) * PT_PLD + 32 * ks + 4 * t;
+                A[ks][b][0] = *reinterpret_cast<const uint32_t *>(base); A[ks][b][1] = *reinterpret_cast<const uint32_t *>(base + 8 * PT_PLD);
+                A[ks][b][2] = *reinterpret_cast<const uint32_t *>(base + 16); A[ks][b][3] = *reinterpret_cast<const uint32_t *>(base + 8 * PT_PLD + 16);
+            }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            int acc[6][4];
+#pragma unroll
+            for (int s = 0; s < 6; s++) { acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0; }
+            const int dim0 = (nh * NT + nt) * 8;
+#pragma unroll
+            for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    const uint8_t *bp = vT + ((buf * 4 + b) * HD + dim0 + g) * PT_PLD + 32 * ks + 4 * t;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp), b1 = *reinterpret_cast<const uint32_t *>(bp + 16);
+#pragma unroll
+                    for (int aa = 0; aa < 3; aa++) {
+                        if (b < 3) pt_mma<false, false>(acc[aa + b], A[ks][aa], b0, b1);
+                        else pt_mma<false, true>(acc[aa + b], A[ks][aa], b0, b1);
+                    }
+                }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                long long s64 = 0;
+#pragma unroll
+                for (int s = 5; s >= 0; s--) s64 = s64 * 256 + (long long)acc[s][i];
+                acc64[nt][i] += s64;
+            }
+        }
+        __syncthreads();                                           // the probability planes and the other value buffer may be overwritten
+    }
+    if (mt < rep) {
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int qi = g + (i >= 2 ? 8 : 0), dim = (nh * NT + nt) * 8 + 2 * t + (i & 1);
+                if (qi < T.nq) a.out[((T.t0 + qi) * a.H + kv * rep + mt) * HD + dim] = acc64[nt][i] >> a.fa;
+            }
+    }
+}
+
+template <int HD>
+cudaError_t scores_launch(const AttnArgs &a, unsigned walks, unsigned tiles, cudaStream_t s) {
+    constexpr size_t smem = (size_t)4 * PT_COLS * (HD + 16) + (size_t)2 * 4 * PT_CH * (HD + 16);
+    static_assert(smem >= (size_t)PT_COLS * HD * 8, "the int64 queries of the scalar path overlay the byte planes");
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_tile_scores_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    attn_tile_scores_kernel<HD><<<dim3(walks, a.Hkv, tiles), PT_THREADS, smem, s>>>(a);
+    return cudaGetLastError();
+}
+
+template <int HD>
+cudaError_t pv_launch(const AttnArgs &a, unsigned tiles, cudaStream_t s) {
+    constexpr size_t smem = (size_t)2 * 4 * HD * PT_PLD + (size_t)3 * PT_COLS * PT_PLD;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_tile_pv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    attn_tile_pv_kernel<HD><<<dim3(1, a.Hkv, tiles), PT_THREADS, smem, s>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool attn_tiles_ok(const AttnArgs &a) {
+    const int rep = a.Hkv > 0 ? a.H / a.Hkv : 0;
+    return a.batch >= 4 && a.seq_stride == 0 && rep >= 1 && rep <= PT_HEADS && (a.hd == 64 || a.hd == 128) && a.fa <= 23 && !a.pos_dev;
+}
+
+cudaError_t launch_attn_tile_scores(const AttnArgs &a, cudaStream_t s) {
+    if (!attn_tiles_ok(a)) return cudaErrorInvalidValue;
+    const unsigned tiles = (unsigned)((a.batch + PT_Q - 1) / PT_Q);
+    long long span = a.pos + a.batch;                              // keys the last token sees, plus the tile's own tokens under a window
+    if (a.window > 0 && span > a.window + PT_Q) span = a.window + PT_Q;
+    const unsigned walks = (unsigned)((span / PT_CH + 2 + PT_WALK - 1) / PT_WALK);
+    const cudaError_t e = a.hd == 128 ? scores_launch<128>(a, walks, tiles, s) : scores_launch<64>(a, walks, tiles, s);
+    note_launch();
+    return e;
+}
+
+cudaError_t launch_attn_tile_pv(const AttnArgs &a, cudaStream_t s) {
+    if (!attn_tiles_ok(a) || !a.out) return cudaErrorInvalidValue;
+    const unsigned tiles = (unsigned)((a.batch + PT_Q - 1) / PT_Q);
+    const cudaError_t e = a.hd == 128 ? pv_launch<128>(a, tiles, s) : pv_launch<64>(a, tiles, s);
+    note_launch();
+    return e;
+}
+
+}  // namespace iie

@@ -152,7 +152,8 @@ def test_every_launch_form_gives_the_same_bytes(form):
 
 @pytest.mark.parametrize(("H", "Hkv", "hd", "start", "m", "window", "rope"),
                          [(4, 2, 64, 0, 12, None, 0), (4, 2, 64, 15, 5, 7, 1), (8, 1, 128, 3, 70, None, 2), (8, 2, 32, 60, 9, 64, 1),
-                          (16, 1, 64, 0, 130, 50, 2)])
+                          (16, 1, 64, 0, 130, 50, 2), (8, 2, 128, 37, 150, 64, 2), (8, 1, 64, 130, 97, None, 1), (32, 4, 128, 100, 90, None, 1),
+                          (6, 2, 128, 0, 33, 16, 0)])
 def test_prefill_attention_matches_the_checker(H, Hkv, hd, start, m, window, rope):
     """m new tokens at once (causal, optional window, both rotations) against the CPU checker's cached attention."""
     import torch
@@ -199,3 +200,36 @@ def test_prefill_attention_matches_the_checker(H, Hkv, hd, start, m, window, rop
     want_k[:, pos] = k1r[0]; want_v[:, pos] = v1[0]
     want1 = o.attention_cached(q1r, want_k[:, :pos + 1], want_v[:, :pos + 1], pos, H, Hkv, FA, window)
     assert np.array_equal(got1.cpu().numpy().reshape(1, -1), want1)
+
+
+@pytest.mark.parametrize("qbits", [19, 40])
+def test_prefill_tiles_equal_the_per_token_kernels(qbits):
+    """A longer prefill (several key chunks, a window that cuts through them, a ragged last tile) through the sixteen-token
+    tiles and through the per-token kernels: the same bytes.  qbits = 40 puts query values beyond int32 (the scalar path)."""
+    import torch
+
+    from integer_inference_engine_b200 import device, qk_cuda as qk
+    H, Hkv, hd, start, m, window = 16, 2, 128, 45, 311, 200
+    rng = np.random.default_rng(77 + qbits)
+    rows = start + m + 1
+    cos, sin = o.build_rope_tables(rows, hd, 50000.0, FA)
+    cuda = lambda a, dt=torch.int64: torch.from_numpy(np.ascontiguousarray(a)).to(dt).cuda()
+    ck = rng.integers(-(1 << 20), 1 << 20, size=(Hkv, rows, hd), dtype=np.int64)
+    cv = rng.integers(-(1 << 30), 1 << 30, size=(Hkv, rows, hd), dtype=np.int64)
+    q = rng.integers(-(1 << qbits), 1 << qbits, size=(m, H * hd), dtype=np.int64)
+    k = rng.integers(-(1 << 20), 1 << 20, size=(m, Hkv * hd), dtype=np.int64)
+    v = rng.integers(-(1 << 30), 1 << 30, size=(m, Hkv * hd), dtype=np.int64)
+    lib = qk._lib()
+    outs = []
+    try:
+        for form in (1, 0):
+            lib.iie_set_attn_fused(form)
+            kc, vc = cuda(ck, torch.int32), cuda(cv, torch.int32)
+            got = device.attention_prefill(cuda(q), cuda(k), cuda(v), kc, vc, start, H, Hkv, hd, FA, window, cuda(cos), cuda(sin), 1)
+            torch.cuda.synchronize()
+            outs.append((got.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy()))
+    finally:
+        lib.iie_set_attn_fused(1)
+    assert device.read_flags() == 0
+    for a, b in zip(outs[0], outs[1]):
+        assert np.array_equal(a, b)
