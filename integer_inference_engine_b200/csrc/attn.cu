@@ -1311,11 +1311,10 @@ cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s) {
     attn_append_kernel<<<dim3((unsigned)a.batch, a.Hkv), 128, 0, s>>>(a);
     if (g_attn_fused != 0 && attn_tiles_ok(a)) {
         // consecutive tokens of one sequence: sixteen tokens per CTA share every staged chunk of keys and values
-        note_launch(2);
+        note_launch(1);
         cudaError_t e = launch_attn_tile_scores(a, s);
-        if (e != cudaSuccess) return e;
-        attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H, (unsigned)a.batch), 256, 0, s>>>(a);
-        return launch_attn_tile_pv(a, s);
+        if (e == cudaSuccess) e = launch_attn_tile_exp(a, s);
+        return e == cudaSuccess ? launch_attn_tile_pv(a, s) : e;
     }
     const bool tc = g_attn_fused != 0 && rep <= AF_HEADS && (a.hd == 64 || a.hd == 128);      // shapes the tensor-core kernel carries
     if (tc) {

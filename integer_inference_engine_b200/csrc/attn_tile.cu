@@ -9,11 +9,15 @@
 // sum_s 256^s acc_s in wrapping arithmetic (which is what the reference's int64 products do).
 //   scores:  D[key][column] = K bytes (A, 16 keys x 32 dims) x rotated query bytes (B, 32 dims x 8 heads of one token)
 //   p x v:   D[token of one head][dim] = probability bytes (A, 16 tokens x 32 keys) x value bytes (B, 32 keys x 8 dims)
-// The exponentials in between are attn_exp_kernel's.  Causality and the window are masks per (token, key); a masked
-// probability is zero.  A query beyond int32 (the reference multiplies it as int64) takes a scalar path inside the
+// Where every value of an operand lies in [-2^23, 2^23) its top byte plane is left out (three planes, the third signed):
+// nine byte pairs instead of sixteen for the scores, nine instead of twelve for p x v; decided per chunk of keys / values.
+// The exponentials in between run one warp per (token, head) row.  Causality and the window are masks per (token, key); a
+// masked probability is zero.  A query beyond int32 (the reference multiplies it as int64) takes a scalar path inside the
 // scores kernel.
 #include <algorithm>
+#include <type_traits>
 
+#include "common.cuh"
 #include "kernels.h"
 
 namespace iie {
@@ -84,7 +88,7 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_scores_kernel(const A
     constexpr int QLD = HD + 16, HALF = HD / 2, VPT = HD / 32;     // bytes per plane row; 16-byte vectors of a chunk per thread
     extern __shared__ __align__(16) unsigned char pt_smem[];
     __shared__ long long s_max[PT_COLS];
-    __shared__ int s_wide;
+    __shared__ int s_wide, s_qwide24;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int rep = a.H / a.Hkv, kv = blockIdx.y;
     const Tile T = pt_tile(a, (long long)gridDim.z - 1 - blockIdx.z);           // long tiles first
@@ -94,9 +98,9 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_scores_kernel(const A
     int8_t *qd = reinterpret_cast<int8_t *>(pt_smem);             // query byte planes [4][128 columns][QLD], column = token * 8 + head
     int8_t *kd = qd + 4 * PT_COLS * QLD;                          // key byte planes [2 buffers][4][64 keys][QLD]
     if (tid < PT_COLS) s_max[tid] = INT64_MIN;
-    if (tid == 0) s_wide = 0;
+    if (tid == 0) { s_wide = 0; s_qwide24 = 0; }
     __syncthreads();
-    bool wide = false;
+    bool wide = false, wide24 = false;
     for (int idx = tid; idx < PT_COLS * HALF; idx += PT_THREADS) {
         const int col = idx / HALF, i = idx - col * HALF, qi = col >> 3, h = col & 7;
         const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + HALF : 2 * i + 1;
@@ -112,8 +116,10 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_scores_kernel(const A
             qd[(b * PT_COLS + col) * QLD + i1] = (int8_t)((uint32_t)(int32_t)x1 >> (8 * b));
         }
         wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+        wide24 |= x0 < -(1 << 23) || x0 >= (1 << 23) || x1 < -(1 << 23) || x1 >= (1 << 23);
     }
     if (wide) s_wide = 1;
+    if (wide24) s_qwide24 = 1;
     __syncthreads();
     auto publish_max = [&]() {
         __syncthreads();
@@ -165,41 +171,49 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_scores_kernel(const A
             kreg[u] = l <= T.pos_last ? __ldg(reinterpret_cast<const int4 *>(a.kcache + ((long long)kv * a.Lmax + l) * HD) + part) : make_int4(0, 0, 0, 0);
         }
     };
-    auto store = [&](int buf) {                                    // registers -> byte planes of buffer buf
+    auto store = [&](int buf) {                                    // registers -> byte planes of buffer buf; true if every key value fits 24 bits
+        bool fits = true;
 #pragma unroll
         for (int u = 0; u < VPT; u++) {
             const int v = tid + u * PT_THREADS, key = v / (HD / 4), part = v - key * (HD / 4);
+            const int vals[4] = {kreg[u].x, kreg[u].y, kreg[u].z, kreg[u].w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) fits &= vals[i] >= -(1 << 23) && vals[i] < (1 << 23);
             uint32_t d[4];
             pt_planes((uint32_t)kreg[u].x, (uint32_t)kreg[u].y, (uint32_t)kreg[u].z, (uint32_t)kreg[u].w, d[0], d[1], d[2], d[3]);
 #pragma unroll
             for (int b = 0; b < 4; b++) *reinterpret_cast<uint32_t *>(kd + ((buf * 4 + b) * PT_CH + key) * QLD + part * 4) = d[b];
         }
+        return fits;
     };
     const int mt = warp & 3, ng = warp >> 2;
+    const bool q_narrow = s_qwide24 == 0;
     load(c_first);
     for (int w = 0; w < PT_WALK; w++) {
         const long long c = c_first + w, l0 = c * PT_CH;
         if (l0 > T.pos_last) break;                                // uniform over the CTA
         const int buf = w & 1;
-        store(buf);
-        __syncthreads();                                           // planes of chunk c visible; the other buffer's readers are done
+        const bool k_fits = store(buf);
+        const bool narrow = __syncthreads_and(k_fits) && q_narrow;   // planes of chunk c visible; the other buffer's readers are done
         if (w + 1 < PT_WALK && l0 + PT_CH <= T.pos_last) load(c + 1);
         const long long key_lo = l0 + mt * 16, key_hi = key_lo + 15;
+        auto tile_pairs = [&](auto nb_c) {                        // NB byte planes per operand, the last one signed
+        constexpr int NB = decltype(nb_c)::value;
 #pragma unroll 1
         for (int np = 0; np < 2; np++) {
             const int n0 = ng * 4 + np * 2;                        // tokens n0 and n0 + 1
             // nothing of this key tile is visible to either token: warp-uniform skip
             if (n0 >= T.nq || key_lo > T.pos0 + n0 + 1 || key_hi < pt_lo(a, T.pos0 + n0)) continue;
-            int acc[2][7][4];
+            int acc[2][2 * NB - 1][4];
 #pragma unroll
             for (int j = 0; j < 2; j++)
 #pragma unroll
-                for (int s = 0; s < 7; s++) { acc[j][s][0] = acc[j][s][1] = acc[j][s][2] = acc[j][s][3] = 0; }
+                for (int s = 0; s < 2 * NB - 1; s++) { acc[j][s][0] = acc[j][s][1] = acc[j][s][2] = acc[j][s][3] = 0; }
 #pragma unroll
             for (int st = 0; st < HD / 32; st++) {
-                uint32_t A[4][4];
+                uint32_t A[NB][4];
 #pragma unroll
-                for (int aa = 0; aa < 4; aa++) {
+                for (int aa = 0; aa < NB; aa++) {
                     const int8_t *base = kd + ((buf * 4 + aa) * PT_CH + mt * 16 + g) * QLD + 32 * st + 4 * t;
                     A[aa][0] = *reinterpret_cast<const uint32_t *>(base); A[aa][1] = *reinterpret_cast<const uint32_t *>(base + 8 * QLD);
                     A[aa][2] = *reinterpret_cast<const uint32_t *>(base + 16); A[aa][3] = *reinterpret_cast<const uint32_t *>(base + 8 * QLD + 16);
@@ -207,14 +221,14 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_scores_kernel(const A
 #pragma unroll
                 for (int j = 0; j < 2; j++)
 #pragma unroll
-                    for (int b = 0; b < 4; b++) {
+                    for (int b = 0; b < NB; b++) {
                         const int8_t *qb = qd + (b * PT_COLS + (n0 + j) * 8 + g) * QLD + 32 * st + 4 * t;
                         const uint32_t b0 = *reinterpret_cast<const uint32_t *>(qb), b1 = *reinterpret_cast<const uint32_t *>(qb + 16);
 #pragma unroll
-                        for (int aa = 0; aa < 4; aa++) {
-                            if (aa < 3 && b < 3) pt_mma<false, false>(acc[j][aa + b], A[aa], b0, b1);
-                            else if (aa < 3) pt_mma<false, true>(acc[j][aa + b], A[aa], b0, b1);
-                            else if (b < 3) pt_mma<true, false>(acc[j][aa + b], A[aa], b0, b1);
+                        for (int aa = 0; aa < NB; aa++) {
+                            if (aa < NB - 1 && b < NB - 1) pt_mma<false, false>(acc[j][aa + b], A[aa], b0, b1);
+                            else if (aa < NB - 1) pt_mma<false, true>(acc[j][aa + b], A[aa], b0, b1);
+                            else if (b < NB - 1) pt_mma<true, false>(acc[j][aa + b], A[aa], b0, b1);
                             else pt_mma<true, true>(acc[j][aa + b], A[aa], b0, b1);
                         }
                     }
@@ -228,7 +242,7 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_scores_kernel(const A
                 for (int i = 0; i < 4; i++) {
                     long long dot = 0;
 #pragma unroll
-                    for (int s = 6; s >= 0; s--) dot = dot * 256 + (long long)acc[j][s][i];
+                    for (int s = 2 * NB - 2; s >= 0; s--) dot = dot * 256 + (long long)acc[j][s][i];
                     const long long l = key_lo + g + (i >= 2 ? 8 : 0);
                     const int h = 2 * t + (i & 1);
                     if (qi < T.nq && h < rep && l <= pos_q && l >= lo_q) {
@@ -246,8 +260,43 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_scores_kernel(const A
                 }
             }
         }
+        };
+        if (narrow) tile_pairs(std::integral_constant<int, 3>{}); else tile_pairs(std::integral_constant<int, 4>{});
     }
     publish_max();
+}
+
+// ---- pass 2: exponentials and their sum, one warp per (token, head) row -----------------------------------------------------
+// e_l = 2^-((min(max - score_l, clip) * log2e) >> fa) for the visible keys of the row, two keys per lane and step; the row's
+// normaliser is written once (no atomics: the row belongs to this warp).
+__global__ void __launch_bounds__(256) attn_tile_exp_kernel(const AttnArgs a) {
+    const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5), n_rows = (long long)a.batch * a.H;
+    if (row >= n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const long long tok = row / a.H, pos = a.pos + tok, lo = pt_lo(a, pos), Ls = a.Ls ? a.Ls : a.Lmax;
+    const int64_t *sc = a.scores + row * Ls;
+    int32_t *e = a.e + row * Ls;
+    const long long m = a.hmax[row];
+    unsigned long long sum = 0;
+    for (long long l = (lo & ~1LL) + 2 * lane; l <= pos; l += 64) {
+        const longlong2 s2 = *reinterpret_cast<const longlong2 *>(sc + l);
+        int2 e2 = make_int2(0, 0);
+        if (l >= lo) {
+            long long d = m - s2.x;
+            d = d < a.clip ? d : a.clip;
+            e2.x = (int)exp2_neg_fixed((d * a.log2e) >> a.fa, a.fa);
+        }
+        if (l + 1 <= pos) {
+            long long d = m - s2.y;
+            d = d < a.clip ? d : a.clip;
+            e2.y = (int)exp2_neg_fixed((d * a.log2e) >> a.fa, a.fa);
+        }
+        sum += (unsigned long long)(unsigned)e2.x + (unsigned long long)(unsigned)e2.y;
+        *reinterpret_cast<int2 *>(e + l) = e2;
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+    if (lane == 0) a.Z[row] = sum;
 }
 
 // ---- pass 3: out[token][head][dim] = (sum over keys of p x v) >> fa --------------------------------------------------------
@@ -263,48 +312,55 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_pv_kernel(const AttnA
     const int rep = a.H / a.Hkv, kv = blockIdx.y;
     const Tile T = pt_tile(a, (long long)gridDim.z - 1 - blockIdx.z);
     const long long Ls = a.Ls ? a.Ls : a.Lmax;
-    uint8_t *vT = pt_smem;                                         // value byte planes [2 buffers][4][HD dims][PT_PLD], keys along a row
-    uint8_t *pT = vT + 2 * 4 * HD * PT_PLD;                        // probability byte planes [3][128 rows][PT_PLD]
+    uint8_t *vT = pt_smem;                                         // value byte planes [4][HD dims][PT_PLD], keys along a row
+    uint8_t *pT = vT + 4 * HD * PT_PLD;                            // probability byte planes [3][128 rows][PT_PLD]
+    int32_t *vraw = reinterpret_cast<int32_t *>(pT + 3 * PT_COLS * PT_PLD);      // the next chunk's values as they lie in the cache [64][HD]
     if (tid < PT_COLS) {
         const int h = tid >> 4, qi = tid & 15;
         unsigned long long z = 0;
         if (qi < T.nq && h < rep) z = a.Z[(T.t0 + qi) * a.H + kv * rep + h];
         s_z[tid] = z; s_inv[tid] = z ? 0xFFFFFFFFFFFFFFFFULL / z : 0ULL;
     }
-    const int vd = tid % HD, vq0 = tid / HD;                       // this thread's dimension and first key group of the value staging
-    int vreg[VU][4];
-    auto load_v = [&](long long c) {
+    auto fetch_v = [&](long long c) {                              // asynchronous copies, no registers held (rows past the last token: zero)
 #pragma unroll
         for (int u = 0; u < VU; u++) {
-            const int kq = vq0 + u * (PT_THREADS / HD);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const long long l = c * PT_CH + 4 * kq + i;
-                vreg[u][i] = l <= T.pos_last ? __ldg(a.vcache + ((long long)kv * a.Lmax + l) * HD + vd) : 0;
-            }
+            const int v = tid + u * PT_THREADS, key = v / (HD / 4), part = v - key * (HD / 4);
+            const long long l = c * PT_CH + key;
+            int32_t *dst = vraw + key * HD + part * 4;
+            if (l <= T.pos_last) {
+                const int32_t *src = a.vcache + ((long long)kv * a.Lmax + l) * HD + part * 4;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+            } else *reinterpret_cast<int4 *>(dst) = make_int4(0, 0, 0, 0);
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    auto store_v = [&](int buf) {
+    const int vd = tid % HD, vq0 = tid / HD;                       // this thread's dimension and first key group of the transposition
+    auto convert_v = [&]() {                                       // raw chunk -> transposed byte planes; true if every value fits 24 bits
+        bool fits = true;
 #pragma unroll
         for (int u = 0; u < VU; u++) {
             const int kq = vq0 + u * (PT_THREADS / HD);
-            uint32_t d[4];
-            pt_planes((uint32_t)vreg[u][0], (uint32_t)vreg[u][1], (uint32_t)vreg[u][2], (uint32_t)vreg[u][3], d[0], d[1], d[2], d[3]);
+            int x[4];
 #pragma unroll
-            for (int b = 0; b < 4; b++) *reinterpret_cast<uint32_t *>(vT + ((buf * 4 + b) * HD + vd) * PT_PLD + 4 * kq) = d[b];
+            for (int i = 0; i < 4; i++) { x[i] = vraw[(4 * kq + i) * HD + vd]; fits &= x[i] >= -(1 << 23) && x[i] < (1 << 23); }
+            uint32_t d[4];
+            pt_planes((uint32_t)x[0], (uint32_t)x[1], (uint32_t)x[2], (uint32_t)x[3], d[0], d[1], d[2], d[3]);
+#pragma unroll
+            for (int b = 0; b < 4; b++) *reinterpret_cast<uint32_t *>(vT + (b * HD + vd) * PT_PLD + 4 * kq) = d[b];
         }
+        return fits;
     };
     long long acc64[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) { acc64[nt][0] = acc64[nt][1] = acc64[nt][2] = acc64[nt][3] = 0; }
     const int mt = warp & 7, nh = warp >> 3;
     const long long c_lo = T.lo_t / PT_CH, c_hi = T.pos_last / PT_CH;
-    load_v(c_lo);
-    __syncthreads();                                               // s_z / s_inv
+    fetch_v(c_lo);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                                               // s_z / s_inv, the first chunk's values
     for (long long c = c_lo; c <= c_hi; c++) {
-        const int buf = (int)((c - c_lo) & 1);
         const long long l0 = c * PT_CH;
-        // exponentials of this chunk: requested first, the value planes are written while they arrive
+        // exponentials of this chunk: requested first, the value planes are transposed while they arrive
         int4 e4[4];
 #pragma unroll
         for (int u = 0; u < 4; u++) {
@@ -313,7 +369,7 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_pv_kernel(const AttnA
             if (qi < T.nq && h < rep && l0 + 4 * kg <= T.pos0 + qi)
                 e4[u] = __ldg(reinterpret_cast<const int4 *>(a.e + ((T.t0 + qi) * a.H + kv * rep + h) * Ls + l0 + 4 * kg));
         }
-        store_v(buf);
+        const bool v_fits = convert_v();
 #pragma unroll
         for (int u = 0; u < 4; u++) {
             const int row = (tid >> 4) + 32 * u, kg = tid & 15, qi = row & 15;
@@ -340,8 +396,8 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_pv_kernel(const AttnA
             *reinterpret_cast<uint32_t *>(dst + PT_COLS * PT_PLD) = d1;
             *reinterpret_cast<uint32_t *>(dst + 2 * PT_COLS * PT_PLD) = d2;
         }
-        __syncthreads();                                           // planes of chunk c visible
-        if (c < c_hi) load_v(c + 1);
+        const bool narrow = __syncthreads_and(v_fits);             // planes of chunk c visible, the raw buffer is free
+        if (c < c_hi) fetch_v(c + 1);
         // the head's sixteen tokens x this warp's dimensions; tokens that see nothing of the chunk have zero probabilities
         uint32_t A[2][3][4];
 #pragma unroll
@@ -352,21 +408,23 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_pv_kernel(const AttnA
                 A[ks][b][0] = *reinterpret_cast<const uint32_t *>(base); A[ks][b][1] = *reinterpret_cast<const uint32_t *>(base + 8 * PT_PLD);
                 A[ks][b][2] = *reinterpret_cast<const uint32_t *>(base + 16); A[ks][b][3] = *reinterpret_cast<const uint32_t *>(base + 8 * PT_PLD + 16);
             }
+        auto dims = [&](auto nb_c) {                               // NBV value planes, the last one signed
+        constexpr int NBV = decltype(nb_c)::value;
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-            int acc[6][4];
+            int acc[NBV + 2][4];
 #pragma unroll
-            for (int s = 0; s < 6; s++) { acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0; }
+            for (int s = 0; s < NBV + 2; s++) { acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0; }
             const int dim0 = (nh * NT + nt) * 8;
 #pragma unroll
             for (int ks = 0; ks < 2; ks++)
 #pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    const uint8_t *bp = vT + ((buf * 4 + b) * HD + dim0 + g) * PT_PLD + 32 * ks + 4 * t;
+                for (int b = 0; b < NBV; b++) {
+                    const uint8_t *bp = vT + (b * HD + dim0 + g) * PT_PLD + 32 * ks + 4 * t;
                     const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp), b1 = *reinterpret_cast<const uint32_t *>(bp + 16);
 #pragma unroll
                     for (int aa = 0; aa < 3; aa++) {
-                        if (b < 3) pt_mma<false, false>(acc[aa + b], A[ks][aa], b0, b1);
+                        if (b < NBV - 1) pt_mma<false, false>(acc[aa + b], A[ks][aa], b0, b1);
                         else pt_mma<false, true>(acc[aa + b], A[ks][aa], b0, b1);
                     }
                 }
@@ -374,11 +432,14 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_pv_kernel(const AttnA
             for (int i = 0; i < 4; i++) {
                 long long s64 = 0;
 #pragma unroll
-                for (int s = 5; s >= 0; s--) s64 = s64 * 256 + (long long)acc[s][i];
+                for (int s = NBV + 1; s >= 0; s--) s64 = s64 * 256 + (long long)acc[s][i];
                 acc64[nt][i] += s64;
             }
         }
-        __syncthreads();                                           // the probability planes and the other value buffer may be overwritten
+        };
+        if (narrow) dims(std::integral_constant<int, 3>{}); else dims(std::integral_constant<int, 4>{});
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                           // the planes may be overwritten; the next chunk's values have landed
     }
     if (mt < rep) {
 #pragma unroll
@@ -407,7 +468,7 @@ cudaError_t scores_launch(const AttnArgs &a, unsigned walks, unsigned tiles, cud
 
 template <int HD>
 cudaError_t pv_launch(const AttnArgs &a, unsigned tiles, cudaStream_t s) {
-    constexpr size_t smem = (size_t)2 * 4 * HD * PT_PLD + (size_t)3 * PT_COLS * PT_PLD;
+    constexpr size_t smem = (size_t)4 * HD * PT_PLD + (size_t)3 * PT_COLS * PT_PLD + (size_t)PT_CH * HD * 4;
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(attn_tile_pv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -434,6 +495,14 @@ cudaError_t launch_attn_tile_scores(const AttnArgs &a, cudaStream_t s) {
     const cudaError_t e = a.hd == 128 ? scores_launch<128>(a, walks, tiles, s) : scores_launch<64>(a, walks, tiles, s);
     note_launch();
     return e;
+}
+
+cudaError_t launch_attn_tile_exp(const AttnArgs &a, cudaStream_t s) {
+    if (!attn_tiles_ok(a)) return cudaErrorInvalidValue;
+    const long long rows = (long long)a.batch * a.H;
+    attn_tile_exp_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(a);
+    note_launch();
+    return cudaGetLastError();
 }
 
 cudaError_t launch_attn_tile_pv(const AttnArgs &a, cudaStream_t s) {

@@ -249,6 +249,7 @@ extern int g_attn_fused;           // 1: one cooperative launch when it fits, 0:
 // passes 1 and 3 of a prefill by tiles of sixteen tokens on the tensor cores (attn_tile.cu), for the shapes attn_tiles_ok accepts
 bool attn_tiles_ok(const AttnArgs &a);
 cudaError_t launch_attn_tile_scores(const AttnArgs &a, cudaStream_t s);
+cudaError_t launch_attn_tile_exp(const AttnArgs &a, cudaStream_t s);
 cudaError_t launch_attn_tile_pv(const AttnArgs &a, cudaStream_t s);
 // hmax = INT64_MIN, Z = acc = ticket = 0: once after the statistics buffer is (re)allocated; every call leaves them so
 cudaError_t launch_attn_reset(long long *hmax, unsigned long long *Z, long long *acc, unsigned *ticket, int H, int hd, cudaStream_t s);
