@@ -266,9 +266,10 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_scores_kernel(const A
     publish_max();
 }
 
-// ---- pass 2: exponentials and their sum, one warp per (token, head) row -----------------------------------------------------
-// e_l = 2^-((min(max - score_l, clip) * log2e) >> fa) for the visible keys of the row, two keys per lane and step; the row's
-// normaliser is written once (no atomics: the row belongs to this warp).
+// ---- pass 2: exponentials, their sum and the probabilities, one warp per (token, head) row ----------------------------------
+// e_l = 2^-((min(max - score_l, clip) * log2e) >> fa) for the visible keys of the row, two keys per lane and step; the row
+// belongs to this warp, so its normaliser Z needs no atomics and the same lanes turn their e_l into p_l = (e_l << fa) / Z in
+// place (through the reciprocal of Z with an exact fix-up: the estimate is at most 2 low).
 __global__ void __launch_bounds__(256) attn_tile_exp_kernel(const AttnArgs a) {
     const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5), n_rows = (long long)a.batch * a.H;
     if (row >= n_rows) return;
@@ -297,6 +298,19 @@ __global__ void __launch_bounds__(256) attn_tile_exp_kernel(const AttnArgs a) {
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
     if (lane == 0) a.Z[row] = sum;
+    if (sum == 0) return;                                          // (cannot happen: the row maximum has e = 2^fa)
+    const unsigned long long inv = 0xFFFFFFFFFFFFFFFFULL / sum;
+    auto prob = [&](int ev) {
+        const unsigned long long n = (unsigned long long)(unsigned)ev << a.fa;
+        unsigned long long q = __umul64hi(n, inv), r = n - q * sum;
+        while (r >= sum) { q++; r -= sum; }
+        return (int)q;
+    };
+    for (long long l = (lo & ~1LL) + 2 * lane; l <= pos; l += 64) {
+        int2 e2 = *reinterpret_cast<int2 *>(e + l);               // this lane's own stores
+        e2.x = prob(e2.x); e2.y = prob(e2.y);
+        *reinterpret_cast<int2 *>(e + l) = e2;
+    }
 }
 
 // ---- pass 3: out[token][head][dim] = (sum over keys of p x v) >> fa --------------------------------------------------------
@@ -307,7 +321,6 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_pv_kernel(const AttnA
     constexpr int NT = HD / 16;                                    // 8-wide dimension tiles of a warp
     constexpr int VU = HD / 32;                                    // (dimension, four keys) units of a thread per chunk
     extern __shared__ __align__(16) unsigned char pt_smem[];
-    __shared__ unsigned long long s_z[PT_COLS], s_inv[PT_COLS];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int rep = a.H / a.Hkv, kv = blockIdx.y;
     const Tile T = pt_tile(a, (long long)gridDim.z - 1 - blockIdx.z);
@@ -315,12 +328,6 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_pv_kernel(const AttnA
     uint8_t *vT = pt_smem;                                         // value byte planes [4][HD dims][PT_PLD], keys along a row
     uint8_t *pT = vT + 4 * HD * PT_PLD;                            // probability byte planes [3][128 rows][PT_PLD]
     int32_t *vraw = reinterpret_cast<int32_t *>(pT + 3 * PT_COLS * PT_PLD);      // the next chunk's values as they lie in the cache [64][HD]
-    if (tid < PT_COLS) {
-        const int h = tid >> 4, qi = tid & 15;
-        unsigned long long z = 0;
-        if (qi < T.nq && h < rep) z = a.Z[(T.t0 + qi) * a.H + kv * rep + h];
-        s_z[tid] = z; s_inv[tid] = z ? 0xFFFFFFFFFFFFFFFFULL / z : 0ULL;
-    }
     auto fetch_v = [&](long long c) {                              // asynchronous copies, no registers held (rows past the last token: zero)
 #pragma unroll
         for (int u = 0; u < VU; u++) {
@@ -357,10 +364,10 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_pv_kernel(const AttnA
     const long long c_lo = T.lo_t / PT_CH, c_hi = T.pos_last / PT_CH;
     fetch_v(c_lo);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();                                               // s_z / s_inv, the first chunk's values
+    __syncthreads();                                               // the first chunk's values
     for (long long c = c_lo; c <= c_hi; c++) {
         const long long l0 = c * PT_CH;
-        // exponentials of this chunk: requested first, the value planes are transposed while they arrive
+        // probabilities of this chunk: requested first, the value planes are transposed while they arrive
         int4 e4[4];
 #pragma unroll
         for (int u = 0; u < 4; u++) {
@@ -374,19 +381,13 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_pv_kernel(const AttnA
         for (int u = 0; u < 4; u++) {
             const int row = (tid >> 4) + 32 * u, kg = tid & 15, qi = row & 15;
             const long long pos_q = T.pos0 + qi, lo_q = pt_lo(a, pos_q);
-            const unsigned long long z = s_z[row], inv = s_inv[row];
             const int ev[4] = {e4[u].x, e4[u].y, e4[u].z, e4[u].w};
             uint32_t p[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const long long l = l0 + 4 * kg + i;
                 uint32_t pv = 0;
-                if (z && l <= pos_q && l >= lo_q) {                // (e << fa) / z through the row's reciprocal: the estimate is at most 2 low
-                    const unsigned long long n = (unsigned long long)(uint32_t)ev[i] << a.fa;
-                    unsigned long long q = __umul64hi(n, inv), r = n - q * z;
-                    while (r >= z) { q++; r -= z; }
-                    pv = (uint32_t)q;
-                }
+                if (l <= pos_q && l >= lo_q) pv = (uint32_t)ev[i];
                 p[i] = pv;
             }
             uint32_t d0, d1, d2, d3;
@@ -452,6 +453,194 @@ __global__ void __launch_bounds__(PT_THREADS, 1) attn_tile_pv_kernel(const AttnA
     }
 }
 
+
+// ---- pass 3 on the 5th-generation tensor cores ---------------------------------------------------------------------------
+// D[row = head * 16 + token][dim] over a 64-dimension half of the head: grid (HD / 64, Hkv, tiles).  The probability byte
+// planes (A, 128 rows x 64 keys) and the transposed value byte planes (B, 64 dims x 64 keys) of a chunk are written by sixteen
+// producer warps into the canonical K-major shared-memory layout (8 x 16-byte core matrices, no swizzle), three stages deep;
+// one thread issues tcgen05.mma kind::i8 (M 128, N 64, K 32), one per byte pair and K step, pairs of equal a + b into the
+// same TMEM accumulator.  The int32 accumulators run over the WHOLE key span (at most 3 pairs x 255^2 x 64 keys per chunk
+// and accumulator, so up to 170 chunks stay below 2^31: the launcher bounds the span), and are read out once at the end:
+// sum_s 256^s acc_s in wrapping 64-bit arithmetic, shifted, stored.  Every wait is bounded; on a time-out the CTA raises flag
+// bit 3, leaves its loops, frees its TMEM and exits.
+constexpr int PC_PRODUCERS = 512, PC_THREADS = PC_PRODUCERS + 32, PC_STAGES = 3, PC_N = 64;
+constexpr int PC_P_PLANE = PT_COLS * PT_CH, PC_V_PLANE = PC_N * PT_CH;             // 8192 / 4096 bytes
+constexpr int PC_STAGE = 3 * PC_P_PLANE + 4 * PC_V_PLANE;                          // 40960 bytes
+constexpr unsigned PC_WAIT_LIMIT = 1u << 24;
+constexpr long long PC_MAX_CHUNKS = 160;
+
+__device__ __forceinline__ uint32_t pc_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool pc_wait(uint64_t *b, uint32_t parity, volatile int *abort_flag) {
+    for (unsigned it = 0; it < PC_WAIT_LIMIT; it++) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(pc_u32(b)), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 1023) == 1023 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+// K-major, no swizzle: LBO = distance of the two 16-byte K halves of one MMA, SBO = distance of consecutive 8-row groups
+__device__ __forceinline__ uint64_t pc_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ULL << 46);
+}
+__device__ __forceinline__ void pc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void pc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pc_u32(bar)) : "memory");
+}
+
+template <int HD>
+__global__ void __launch_bounds__(PC_THREADS, 1) attn_tile_pv_tc_kernel(const AttnArgs a) {
+    extern __shared__ __align__(1024) unsigned char pc_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(pc_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_bar[PC_STAGES], empty_bar[PC_STAGES], accum_bar;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rep = a.H / a.Hkv, kv = blockIdx.y, dim_base = blockIdx.x * PC_N;
+    const Tile T = pt_tile(a, (long long)gridDim.z - 1 - blockIdx.z);
+    const long long Ls = a.Ls ? a.Ls : a.Lmax;
+    const long long c_lo = T.lo_t / PT_CH, c_hi = T.pos_last / PT_CH;
+    const int n_chunks = (int)(c_hi - c_lo + 1);
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < PC_STAGES; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pc_u32(&full_bar[s])), "r"(PC_PRODUCERS / 32));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pc_u32(&empty_bar[s])), "r"(1));
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pc_u32(&accum_bar)), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == PC_PRODUCERS / 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pc_u32(&s_tmem)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp < PC_PRODUCERS / 32) {
+        // ================= producers: every warp writes whole core matrices (8 rows x 16 bytes), lane = (row, 4-key word) ====
+        const int r8 = lane >> 2, w4 = lane & 3;
+        for (int ci = 0; ci < n_chunks; ci++) {
+            const int s = ci % PC_STAGES;
+            if (ci >= PC_STAGES && !pc_wait(&empty_bar[s], ((ci / PC_STAGES) - 1) & 1, &s_abort)) break;
+            unsigned char *stage = smem + (size_t)s * PC_STAGE;
+            const long long l0 = (c_lo + ci) * PT_CH;
+            // probabilities: 16 row groups x 4 key quarters = 64 core matrices per plane, four per warp
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int cm = warp + 16 * u, rg = cm & 15, kq = cm >> 4;
+                const int row = rg * 8 + r8, h = row >> 4, qi = row & 15;
+                const long long pos_q = T.pos0 + qi, lo_q = pt_lo(a, pos_q), l = l0 + 16 * kq + 4 * w4;
+                int4 p4 = make_int4(0, 0, 0, 0);
+                if (qi < T.nq && h < rep && l <= pos_q && l + 3 >= lo_q) {
+                    p4 = *reinterpret_cast<const int4 *>(a.e + ((T.t0 + qi) * a.H + kv * rep + h) * Ls + l);
+                    if (l < lo_q) p4.x = 0;
+                    if (l + 1 > pos_q || l + 1 < lo_q) p4.y = 0;
+                    if (l + 2 > pos_q || l + 2 < lo_q) p4.z = 0;
+                    if (l + 3 > pos_q || l + 3 < lo_q) p4.w = 0;
+                }
+                uint32_t d0, d1, d2, d3;
+                pt_planes((uint32_t)p4.x, (uint32_t)p4.y, (uint32_t)p4.z, (uint32_t)p4.w, d0, d1, d2, d3);
+                unsigned char *dst = stage + kq * (PT_COLS * 16) + rg * 128 + r8 * 16 + w4 * 4;
+                *reinterpret_cast<uint32_t *>(dst) = d0;
+                *reinterpret_cast<uint32_t *>(dst + PC_P_PLANE) = d1;
+                *reinterpret_cast<uint32_t *>(dst + 2 * PC_P_PLANE) = d2;
+            }
+            // values, transposed: 8 dim groups x 4 key quarters = 32 core matrices per plane, two per warp
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int cm = warp + 16 * u, dg = cm & 7, kq = cm >> 3;
+                const int dim = dim_base + dg * 8 + r8;
+                uint32_t x[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const long long l = l0 + 16 * kq + 4 * w4 + i;
+                    x[i] = l <= T.pos_last ? (uint32_t)__ldg(a.vcache + ((long long)kv * a.Lmax + l) * HD + dim) : 0u;
+                }
+                uint32_t d[4];
+                pt_planes(x[0], x[1], x[2], x[3], d[0], d[1], d[2], d[3]);
+                unsigned char *dst = stage + 3 * PC_P_PLANE + kq * (PC_N * 16) + dg * 128 + r8 * 16 + w4 * 4;
+#pragma unroll
+                for (int b = 0; b < 4; b++) *reinterpret_cast<uint32_t *>(dst + b * PC_V_PLANE) = d[b];
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> visible to the MMA
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pc_u32(&full_bar[s])) : "memory");
+        }
+        // ================= read-out: warps 0..3, TMEM lane = row ==============================================================
+        if (warp < 4 && pc_wait(&accum_bar, 0, &s_abort)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = warp * 32 + lane, h = row >> 4, qi = row & 15;
+            const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
+            int64_t *dst = a.out + ((T.t0 + qi) * a.H + kv * rep + h) * HD + dim_base;
+            for (int c0 = 0; c0 < PC_N; c0 += 8) {
+                int r[6][8];
+#pragma unroll
+                for (int s = 0; s < 6; s++)
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                 : "=r"(r[s][0]), "=r"(r[s][1]), "=r"(r[s][2]), "=r"(r[s][3]), "=r"(r[s][4]), "=r"(r[s][5]), "=r"(r[s][6]), "=r"(r[s][7])
+                                 : "r"(tlane + s * PC_N + c0));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (qi < T.nq && h < rep) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        long long s64 = 0;
+#pragma unroll
+                        for (int s = 5; s >= 0; s--) s64 = s64 * 256 + (long long)r[s][j];
+                        dst[c0 + j] = s64 >> a.fa;
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    } else {
+        // ================= MMA issuer ===========================================================================================
+        if (lane == 0) {
+            constexpr uint32_t IDESC_U = (2u << 4) | ((uint32_t)(PC_N >> 3) << 17) | ((uint32_t)(PT_COLS >> 4) << 24);      // u8 x u8 -> s32
+            constexpr uint32_t IDESC_S = IDESC_U | (1u << 10);                                                                 // u8 x s8 (top value byte)
+            bool ok = true;
+            for (int ci = 0; ci < n_chunks && ok; ci++) {
+                const int s = ci % PC_STAGES;
+                ok = pc_wait(&full_bar[s], (ci / PC_STAGES) & 1, &s_abort);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t stage = pc_u32(smem + (size_t)s * PC_STAGE);
+                const uint64_t dp0 = pc_desc(stage, PT_COLS * 16, 128), dv0 = pc_desc(stage + 3 * PC_P_PLANE, PC_N * 16, 128);
+                const uint32_t later = ci > 0 ? 1u : 0u;
+#pragma unroll
+                for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+                    for (int b = 0; b < 4; b++)
+#pragma unroll
+                        for (int aa = 0; aa < 3; aa++) {
+                            const bool first = ks == 0 && (b == 0 || aa == 2);            // first product into accumulator aa + b
+                            const uint64_t dp = dp0 + (uint64_t)((aa * PC_P_PLANE + ks * 2 * PT_COLS * 16) >> 4);
+                            const uint64_t dv = dv0 + (uint64_t)((b * PC_V_PLANE + ks * 2 * PC_N * 16) >> 4);
+                            pc_mma(tmem + (aa + b) * PC_N, dp, dv, b == 3 ? IDESC_S : IDESC_U, first ? later : 1u);
+                        }
+                pc_commit(&empty_bar[s]);
+            }
+            if (ok) pc_commit(&accum_bar);
+        }
+        __syncwarp();
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == PC_PRODUCERS / 32) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+    if (tid == 0 && s_abort) atomicOr(a.flags, 8);
+}
+
 template <int HD>
 cudaError_t scores_launch(const AttnArgs &a, unsigned walks, unsigned tiles, cudaStream_t s) {
     constexpr size_t smem = (size_t)4 * PT_COLS * (HD + 16) + (size_t)2 * 4 * PT_CH * (HD + 16);
@@ -479,7 +668,22 @@ cudaError_t pv_launch(const AttnArgs &a, unsigned tiles, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+template <int HD>
+cudaError_t pv_tc_launch(const AttnArgs &a, unsigned tiles, cudaStream_t s) {
+    constexpr size_t smem = (size_t)PC_STAGES * PC_STAGE + 1024;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_tile_pv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    attn_tile_pv_tc_kernel<HD><<<dim3(HD / PC_N, a.Hkv, tiles), PC_THREADS, smem, s>>>(a);
+    return cudaGetLastError();
+}
+
 }  // namespace
+
+int g_attn_tile_tc = 1;                    // 1: probability x value of a prefill on tcgen05 where the key span allows, 0: mma.sync tiles
 
 bool attn_tiles_ok(const AttnArgs &a) {
     const int rep = a.Hkv > 0 ? a.H / a.Hkv : 0;
@@ -508,7 +712,11 @@ cudaError_t launch_attn_tile_exp(const AttnArgs &a, cudaStream_t s) {
 cudaError_t launch_attn_tile_pv(const AttnArgs &a, cudaStream_t s) {
     if (!attn_tiles_ok(a) || !a.out) return cudaErrorInvalidValue;
     const unsigned tiles = (unsigned)((a.batch + PT_Q - 1) / PT_Q);
-    const cudaError_t e = a.hd == 128 ? pv_launch<128>(a, tiles, s) : pv_launch<64>(a, tiles, s);
+    long long span = a.pos + a.batch;                              // keys a tile can walk
+    if (a.window > 0 && span > a.window + PT_Q) span = a.window + PT_Q;
+    const bool tc = g_attn_tile_tc != 0 && span / PT_CH + 2 <= PC_MAX_CHUNKS;      // the int32 accumulators run over the whole span
+    const cudaError_t e = tc ? (a.hd == 128 ? pv_tc_launch<128>(a, tiles, s) : pv_tc_launch<64>(a, tiles, s))
+                             : (a.hd == 128 ? pv_launch<128>(a, tiles, s) : pv_launch<64>(a, tiles, s));
     note_launch();
     return e;
 }
