@@ -641,6 +641,252 @@ __global__ void __launch_bounds__(PC_THREADS, 1) attn_tile_pv_tc_kernel(const At
     if (tid == 0 && s_abort) atomicOr(a.flags, 8);
 }
 
+// ---- pass 1 on the 5th-generation tensor cores ---------------------------------------------------------------------------
+// D[row = token * 8 + head][key] per 64-key chunk: A = the rotated-query byte planes (128 rows x HD, written once), B = the
+// key byte planes of the chunk (64 keys x HD, two stages), both K-major along the head dimension in the canonical layout.
+// Sixteen warps produce the key planes and read the accumulators out (scores to the scratch, row maxima); one thread issues
+// the MMAs, HD / 32 K steps x the byte pairs (16, or 9 where the queries and the chunk's keys fit 24 bits), first product of
+// every accumulator of a chunk without accumulation.  The accumulators are single-buffered: the issuer waits until the
+// previous chunk has been read out, the producers are already a chunk ahead.  grid (walks, Hkv, tiles).
+constexpr int SC_WALK = 8, SC_STAGES = 2;
+constexpr int SC_SLD = PT_CH + 2;           // row stride (int64) of the staged scores: 16-byte rows, lanes spread over the banks
+
+// every producer thread learns whether all of them got through their waits (a named barrier with an AND reduction): the
+// warps leave the chunk loop together, so none is left waiting at the plain barriers of the write-out
+__device__ __forceinline__ bool pc_all_ok(bool ok) {
+    uint32_t r;
+    asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 q, %1, 0;\n barrier.cta.red.and.pred p, 1, %2, q;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(r) : "r"((uint32_t)ok), "r"(PC_PRODUCERS) : "memory");
+    return r != 0;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(PC_THREADS, 1) attn_tile_scores_tc_kernel(const AttnArgs a) {
+    constexpr int HALF = HD / 2, Q_PLANE = PT_COLS * HD, K_PLANE = PT_CH * HD, K_STAGE = 4 * K_PLANE;
+    extern __shared__ __align__(1024) unsigned char pc_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(pc_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_bar[SC_STAGES], empty_bar[SC_STAGES], acc_bar, free_bar;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort, s_wide, s_qwide24, s_kwide24[SC_STAGES], s_mode[2];
+    __shared__ long long s_max[PT_COLS];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rep = a.H / a.Hkv, kv = blockIdx.y;
+    const Tile T = pt_tile(a, (long long)gridDim.z - 1 - blockIdx.z);
+    const long long c_first = T.lo_t / PT_CH + (long long)blockIdx.x * SC_WALK;
+    if (c_first * PT_CH > T.pos_last) return;
+    const long long Ls = a.Ls ? a.Ls : a.Lmax;
+    const int n_chunks = (int)min((long long)SC_WALK, T.pos_last / PT_CH - c_first + 1);
+    unsigned char *qd = smem;                                      // query byte planes [4][HD / 16][16 row groups][8 x 16 B]
+    unsigned char *kd = qd + 4 * Q_PLANE;                          // key byte planes [2 stages][4][HD / 16][8 key groups][8 x 16 B]
+    long long *sbuf = reinterpret_cast<long long *>(kd + SC_STAGES * K_STAGE);      // a chunk's scores [128 rows][SC_SLD] on their way out
+    if (tid == 0) {
+        s_abort = 0; s_wide = 0; s_qwide24 = 0;
+        for (int s = 0; s < SC_STAGES; s++) {
+            s_kwide24[s] = 0;
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pc_u32(&full_bar[s])), "r"(PC_PRODUCERS / 32));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pc_u32(&empty_bar[s])), "r"(1));
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pc_u32(&acc_bar)), "r"(1));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pc_u32(&free_bar)), "r"(PC_PRODUCERS / 32));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid < PT_COLS) s_max[tid] = INT64_MIN;
+    if (warp == PC_PRODUCERS / 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pc_u32(&s_tmem)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    // rotated queries as byte planes in the canonical layout (row = token * 8 + head)
+    {
+        bool wide = false, wide24 = false;
+        for (int idx = tid; idx < PT_COLS * HALF; idx += PC_THREADS) {
+            const int row = idx / HALF, i = idx - row * HALF, qi = row >> 3, h = row & 7;
+            const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + HALF : 2 * i + 1;
+            int64_t x0 = 0, x1 = 0;
+            if (qi < T.nq && h < rep) {
+                const int64_t *src = a.q + ((T.t0 + qi) * a.H + kv * rep + h) * HD;
+                x0 = src[i0]; x1 = src[i1];
+                pt_rotate(a, T.pos0 + qi, i, x0, x1);
+            }
+            unsigned char *d0 = qd + (i0 >> 4) * (PT_COLS * 16) + (row >> 3) * 128 + (row & 7) * 16 + (i0 & 15);
+            unsigned char *d1 = qd + (i1 >> 4) * (PT_COLS * 16) + (row >> 3) * 128 + (row & 7) * 16 + (i1 & 15);
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                d0[b * Q_PLANE] = (unsigned char)((uint32_t)(int32_t)x0 >> (8 * b));
+                d1[b * Q_PLANE] = (unsigned char)((uint32_t)(int32_t)x1 >> (8 * b));
+            }
+            wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+            wide24 |= x0 < -(1 << 23) || x0 >= (1 << 23) || x1 < -(1 << 23) || x1 >= (1 << 23);
+        }
+        if (wide) s_wide = 1;
+        if (wide24) s_qwide24 = 1;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");         // the planes are read by the MMAs
+    }
+    __syncthreads();
+    if (s_wide) {
+        // a query value beyond int32: 64-bit wrapping products, one thread per (key, row); the rotated queries as int64 take
+        // the place of every byte plane
+        long long *q64 = reinterpret_cast<long long *>(smem);      // [128][HD]
+        for (int idx = tid; idx < PT_COLS * HALF; idx += PC_THREADS) {
+            const int row = idx / HALF, i = idx - row * HALF, qi = row >> 3, h = row & 7;
+            const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + HALF : 2 * i + 1;
+            int64_t x0 = 0, x1 = 0;
+            if (qi < T.nq && h < rep) {
+                const int64_t *src = a.q + ((T.t0 + qi) * a.H + kv * rep + h) * HD;
+                x0 = src[i0]; x1 = src[i1];
+                pt_rotate(a, T.pos0 + qi, i, x0, x1);
+            }
+            q64[row * HD + i0] = x0; q64[row * HD + i1] = x1;
+        }
+        __syncthreads();
+        for (int w = 0; w < n_chunks; w++) {
+            const long long l0 = (c_first + w) * PT_CH;
+            for (int idx = tid; idx < PT_CH * PT_COLS; idx += PC_THREADS) {
+                const int key = idx >> 7, row = idx & 127, qi = row >> 3, h = row & 7;
+                const long long l = l0 + key, pos_q = T.pos0 + qi;
+                if (qi >= T.nq || h >= rep || l > pos_q || l < pt_lo(a, pos_q)) continue;
+                const int32_t *kk = a.kcache + ((long long)kv * a.Lmax + l) * HD;
+                long long dot = 0;
+                for (int j = 0; j < HD; j++) dot += q64[row * HD + j] * (long long)kk[j];
+                const long long sc = ((dot >> a.fa) * a.inv_sqrt) >> a.fa;
+                a.scores[((T.t0 + qi) * a.H + kv * rep + h) * Ls + l] = sc;
+                atomicMax(&s_max[row], sc);
+            }
+        }
+    } else if (warp < PC_PRODUCERS / 32) {
+        const int r8 = lane >> 2, w4 = lane & 3;
+        const int row = (warp & 3) * 32 + lane, qi = row >> 3, h = row & 7, cg = warp >> 2;      // read-out: TMEM lane and 16-key column group
+        const long long pos_q = T.pos0 + qi, lo_q = pt_lo(a, pos_q);
+        const bool row_ok = qi < T.nq && h < rep;
+        const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        long long mloc = INT64_MIN;
+        auto produce = [&](int ci) {                               // key planes of chunk ci into its stage
+            const int s = ci % SC_STAGES;
+            if (ci >= SC_STAGES && !pc_wait(&empty_bar[s], ((ci / SC_STAGES) - 1) & 1, &s_abort)) return false;
+            unsigned char *stage = kd + (size_t)s * K_STAGE;
+            const long long l0 = (c_first + ci) * PT_CH;
+            bool fits = true;
+#pragma unroll
+            for (int u = 0; u < HD / 32; u++) {                    // (HD / 16) x 8 core matrices per plane, HD / 32 per warp
+                const int cm = warp + 16 * u, kg = cm & 7, k16 = cm >> 3;
+                const long long l = l0 + kg * 8 + r8;
+                int4 v = make_int4(0, 0, 0, 0);
+                if (l <= T.pos_last) v = __ldg(reinterpret_cast<const int4 *>(a.kcache + ((long long)kv * a.Lmax + l) * HD + k16 * 16) + w4);
+                fits &= v.x >= -(1 << 23) && v.x < (1 << 23) && v.y >= -(1 << 23) && v.y < (1 << 23) &&
+                        v.z >= -(1 << 23) && v.z < (1 << 23) && v.w >= -(1 << 23) && v.w < (1 << 23);
+                uint32_t d[4];
+                pt_planes((uint32_t)v.x, (uint32_t)v.y, (uint32_t)v.z, (uint32_t)v.w, d[0], d[1], d[2], d[3]);
+                unsigned char *dst = stage + k16 * (PT_CH * 16) + kg * 128 + r8 * 16 + w4 * 4;
+#pragma unroll
+                for (int b = 0; b < 4; b++) *reinterpret_cast<uint32_t *>(dst + b * K_PLANE) = d[b];
+            }
+            if (!__all_sync(0xffffffffu, fits) && lane == 0) atomicOr(&s_kwide24[s], 1);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pc_u32(&full_bar[s])) : "memory");
+            return true;
+        };
+        bool ok = produce(0);
+        for (int ci = 0; ci < n_chunks; ci++) {
+            if (ok && ci + 1 < n_chunks) ok = produce(ci + 1);
+            ok = ok && pc_wait(&acc_bar, ci & 1, &s_abort);
+            if (!pc_all_ok(ok)) break;                             // uniform over the sixteen warps
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int ns = s_mode[ci & 1];                         // accumulators in use: 5 or 7
+            const long long lc = (c_first + ci) * PT_CH, l0 = lc + cg * 16;
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                int r[7][8];
+#pragma unroll
+                for (int s = 0; s < 7; s++)
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                 : "=r"(r[s][0]), "=r"(r[s][1]), "=r"(r[s][2]), "=r"(r[s][3]), "=r"(r[s][4]), "=r"(r[s][5]), "=r"(r[s][6]), "=r"(r[s][7])
+                                 : "r"(tlane + s * PT_CH + cg * 16 + half * 8));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                long long sv[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    long long dot = 0;
+                    if (ns == 7) dot = ((long long)r[6][j] * 256 + (long long)r[5][j]) * 256;
+#pragma unroll
+                    for (int s = 4; s >= 0; s--) dot = (s == 4 ? dot + (long long)r[4][j] : dot * 256 + (long long)r[s][j]);
+                    const long long l = l0 + half * 8 + j;
+                    sv[j] = ((dot >> a.fa) * a.inv_sqrt) >> a.fa;
+                    if (row_ok && l <= pos_q && l >= lo_q) mloc = max(mloc, sv[j]);
+                }
+                longlong2 *dst = reinterpret_cast<longlong2 *>(sbuf + row * SC_SLD + cg * 16 + half * 8);
+#pragma unroll
+                for (int j = 0; j < 4; j++) dst[j] = make_longlong2(sv[2 * j], sv[2 * j + 1]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pc_u32(&free_bar)) : "memory");
+            // the chunk's scores leave through shared memory so that a warp writes whole 512-byte rows (entries of keys a token
+            // does not see are written too: they lie inside its row of the scratch and are never read)
+            asm volatile("bar.sync 1, %0;" ::"r"(PC_PRODUCERS) : "memory");
+            for (int rr = warp; rr < PT_COLS; rr += PC_PRODUCERS / 32) {
+                const int q2 = rr >> 3, h2 = rr & 7;
+                if (q2 < T.nq && h2 < rep)
+                    *reinterpret_cast<longlong2 *>(a.scores + ((T.t0 + q2) * a.H + kv * rep + h2) * Ls + lc + 2 * lane) =
+                        *reinterpret_cast<const longlong2 *>(sbuf + rr * SC_SLD + 2 * lane);
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(PC_PRODUCERS) : "memory");
+        }
+        if (mloc != INT64_MIN) atomicMax(&s_max[row], mloc);
+    } else {
+        // ================= MMA issuer ===========================================================================================
+        if (lane == 0) {
+            constexpr uint32_t IDESC = (2u << 4) | ((uint32_t)(PT_CH >> 3) << 17) | ((uint32_t)(PT_COLS >> 4) << 24);      // + (1 << 7) A signed, (1 << 10) B signed
+            const bool q_narrow = s_qwide24 == 0;
+            bool ok = true;
+            for (int ci = 0; ci < n_chunks && ok; ci++) {
+                const int s = ci % SC_STAGES;
+                ok = pc_wait(&full_bar[s], (ci / SC_STAGES) & 1, &s_abort);
+                if (ok && ci > 0) ok = pc_wait(&free_bar, (ci - 1) & 1, &s_abort);      // the previous chunk's scores have left TMEM
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const bool narrow = q_narrow && s_kwide24[s] == 0;
+                s_kwide24[s] = 0;                                  // for the next chunk of this stage (ordered by the commit below)
+                s_mode[ci & 1] = narrow ? 5 : 7;
+                const uint32_t stage = pc_u32(kd + (size_t)s * K_STAGE);
+                const uint64_t dq0 = pc_desc(pc_u32(qd), PT_COLS * 16, 128), dk0 = pc_desc(stage, PT_CH * 16, 128);
+                auto issue = [&](auto nb_c) {
+                    constexpr int NB = decltype(nb_c)::value;
+#pragma unroll
+                    for (int ks = 0; ks < HD / 32; ks++)
+#pragma unroll
+                        for (int b = 0; b < NB; b++)
+#pragma unroll
+                            for (int aa = 0; aa < NB; aa++) {
+                                const bool first = ks == 0 && (b == 0 || aa == NB - 1);       // first product into accumulator aa + b
+                                const uint64_t dq = dq0 + (uint64_t)((aa * Q_PLANE + ks * 2 * PT_COLS * 16) >> 4);
+                                const uint64_t dk = dk0 + (uint64_t)((b * K_PLANE + ks * 2 * PT_CH * 16) >> 4);
+                                pc_mma(tmem + (aa + b) * PT_CH, dq, dk, IDESC | (aa == NB - 1 ? 1u << 7 : 0u) | (b == NB - 1 ? 1u << 10 : 0u), first ? 0u : 1u);
+                            }
+                };
+                if (narrow) issue(std::integral_constant<int, 3>{}); else issue(std::integral_constant<int, 4>{});
+                pc_commit(&empty_bar[s]);
+                pc_commit(&acc_bar);
+            }
+        }
+        __syncwarp();
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == PC_PRODUCERS / 32) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+    if (tid < PT_COLS && s_max[tid] != INT64_MIN) {
+        const int qi = tid >> 3, h = tid & 7;
+        atomicMax(a.hmax + (T.t0 + qi) * a.H + kv * rep + h, s_max[tid]);
+    }
+    if (tid == 0 && s_abort) atomicOr(a.flags, 8);
+}
+
 template <int HD>
 cudaError_t scores_launch(const AttnArgs &a, unsigned walks, unsigned tiles, cudaStream_t s) {
     constexpr size_t smem = (size_t)4 * PT_COLS * (HD + 16) + (size_t)2 * 4 * PT_CH * (HD + 16);
@@ -665,6 +911,20 @@ cudaError_t pv_launch(const AttnArgs &a, unsigned tiles, cudaStream_t s) {
         configured = true;
     }
     attn_tile_pv_kernel<HD><<<dim3(1, a.Hkv, tiles), PT_THREADS, smem, s>>>(a);
+    return cudaGetLastError();
+}
+
+template <int HD>
+cudaError_t scores_tc_launch(const AttnArgs &a, unsigned walks, unsigned tiles, cudaStream_t s) {
+    constexpr size_t smem = (size_t)4 * PT_COLS * HD + (size_t)SC_STAGES * 4 * PT_CH * HD + (size_t)PT_COLS * SC_SLD * 8 + 1024;
+    static_assert(smem - 1024 >= (size_t)PT_COLS * HD * 8, "the int64 queries of the scalar path overlay the byte planes");
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_tile_scores_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    attn_tile_scores_tc_kernel<HD><<<dim3(walks, a.Hkv, tiles), PC_THREADS, smem, s>>>(a);
     return cudaGetLastError();
 }
 
@@ -695,8 +955,10 @@ cudaError_t launch_attn_tile_scores(const AttnArgs &a, cudaStream_t s) {
     const unsigned tiles = (unsigned)((a.batch + PT_Q - 1) / PT_Q);
     long long span = a.pos + a.batch;                              // keys the last token sees, plus the tile's own tokens under a window
     if (a.window > 0 && span > a.window + PT_Q) span = a.window + PT_Q;
-    const unsigned walks = (unsigned)((span / PT_CH + 2 + PT_WALK - 1) / PT_WALK);
-    const cudaError_t e = a.hd == 128 ? scores_launch<128>(a, walks, tiles, s) : scores_launch<64>(a, walks, tiles, s);
+    const int walk = g_attn_tile_tc != 0 ? SC_WALK : PT_WALK;
+    const unsigned walks = (unsigned)((span / PT_CH + 2 + walk - 1) / walk);
+    const cudaError_t e = g_attn_tile_tc != 0 ? (a.hd == 128 ? scores_tc_launch<128>(a, walks, tiles, s) : scores_tc_launch<64>(a, walks, tiles, s))
+                                              : (a.hd == 128 ? scores_launch<128>(a, walks, tiles, s) : scores_launch<64>(a, walks, tiles, s));
     note_launch();
     return e;
 }
