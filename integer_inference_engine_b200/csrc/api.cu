@@ -1711,6 +1711,11 @@ extern "C" void iie_set_attn_fused(int enabled) {
     iie::g_attn_fused = enabled < 0 ? 0 : enabled > 2 ? 2 : enabled;
 }
 
+extern "C" void iie_set_attn_tile_tc(int enabled) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    iie::g_attn_tile_tc = enabled ? 1 : 0;
+}
+
 extern "C" void iie_set_pdl(int enabled) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     g_pdl = enabled ? 1 : 0;

@@ -1,19 +1,18 @@
-// Prefill attention by query tiles: passes 1 and 3 of the exact softmax (north-mini-code/src/nmc/cohere2.py:324-354 with
+// Prefill attention by query tiles: the three passes of the exact softmax (north-mini-code/src/nmc/cohere2.py:324-354 with
 // _bonsai/fixedpoint.py:99-133; the arithmetic is stated at the top of attn.cu) for `batch` consecutive tokens of one
 // sequence, sixteen tokens x the query heads of one KV head per CTA.
 //
 // The per-token kernels of attn.cu stage a 64-key chunk of K (or V) for the eight score columns of ONE token; here the chunk
-// is staged once for 128 columns, as byte planes, and both products run on the tensor cores with the byte decomposition of
-// attn_fat_kernel: an int32 is b0 + 2^8 b1 + 2^16 b2 + 2^24 b3 with b0..b2 unsigned and b3 signed, every byte pair is an
-// exact int8 MMA (m16n8k32), pairs of equal a + b share an int32 accumulator, and the 64-bit value is re-assembled as
-// sum_s 256^s acc_s in wrapping arithmetic (which is what the reference's int64 products do).
-//   scores:  D[key][column] = K bytes (A, 16 keys x 32 dims) x rotated query bytes (B, 32 dims x 8 heads of one token)
-//   p x v:   D[token of one head][dim] = probability bytes (A, 16 tokens x 32 keys) x value bytes (B, 32 keys x 8 dims)
-// Where every value of an operand lies in [-2^23, 2^23) its top byte plane is left out (three planes, the third signed):
-// nine byte pairs instead of sixteen for the scores, nine instead of twelve for p x v; decided per chunk of keys / values.
-// The exponentials in between run one warp per (token, head) row.  Causality and the window are masks per (token, key); a
-// masked probability is zero.  A query beyond int32 (the reference multiplies it as int64) takes a scalar path inside the
-// scores kernel.
+// is staged once for 128 (token, head) rows, as byte planes, and both products run on the tensor cores with the byte
+// decomposition of attn_fat_kernel: an int32 is b0 + 2^8 b1 + 2^16 b2 + 2^24 b3 with b0..b2 unsigned and b3 signed, every
+// byte pair is an exact int8 MMA, pairs of equal a + b share an int32 accumulator, and the 64-bit value is re-assembled as
+// sum_s 256^s acc_s in wrapping arithmetic (which is what the reference's int64 products do).  Where every value of an
+// operand lies in [-2^23, 2^23) its top byte plane is left out (three planes, the third signed), decided per chunk.
+// Two forms of each product: tcgen05 (kind::i8, M 128, accumulators in TMEM; the default) and mma.sync m16n8k32 (64-bit sums
+// in registers; for key spans the int32 TMEM accumulators of the probability x value pass do not carry, and as the partner
+// the tests compare against).  The exponentials in between run one warp per (token, head) row and leave probabilities.
+// Causality and the window are masks per (token, key); a masked probability is zero.  A query beyond int32 (the reference
+// multiplies it as int64) takes a scalar path inside the scores kernels.
 #include <algorithm>
 #include <type_traits>
 

@@ -98,7 +98,7 @@ def _signatures():
         "iie_attn_block_dev": ([i64, i64, vp, vp, vp, i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, c_int, i64, vp], c_int),
         "iie_block_dev": ([i64, i64, i64, i64, vp, vp, vp, i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, i64, c_int, c_int, u64, i64,
                            vp, vp, vp], c_int),
-        "iie_embed_dev": ([i64, vp, i64, c_int, vp, vp], c_int), "iie_set_attn_fused": ([c_int], None), "iie_argmax_dev": ([vp, i64, vp, vp], c_int),
+        "iie_embed_dev": ([i64, vp, i64, c_int, vp, vp], c_int), "iie_set_attn_fused": ([c_int], None), "iie_set_attn_tile_tc": ([c_int], None), "iie_argmax_dev": ([vp, i64, vp, vp], c_int),
         "iie_embed_rows_dev": ([i64, vp, c_int, c_int, vp, vp], c_int), "iie_argmax_rows_dev": ([vp, i64, i64, vp, vp], c_int),
         "iie_route_dev": ([i64, c_int, vp, i64, c_int, c_int, vp, vp, vp], c_int),
         "iie_moe_experts_dev": ([i64, vp, i64, vp, vp, c_int, c_int, c_int, c_int, c_int, vp, vp], c_int),

@@ -222,14 +222,15 @@ def test_prefill_tiles_equal_the_per_token_kernels(qbits):
     lib = qk._lib()
     outs = []
     try:
-        for form in (1, 0):
-            lib.iie_set_attn_fused(form)
+        for form, tile_tc in ((1, 1), (1, 0), (0, 1)):           # tcgen05 tiles, mma.sync tiles, per-token kernels
+            lib.iie_set_attn_fused(form); lib.iie_set_attn_tile_tc(tile_tc)
             kc, vc = cuda(ck, torch.int32), cuda(cv, torch.int32)
             got = device.attention_prefill(cuda(q), cuda(k), cuda(v), kc, vc, start, H, Hkv, hd, FA, window, cuda(cos), cuda(sin), 1)
             torch.cuda.synchronize()
             outs.append((got.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy()))
     finally:
-        lib.iie_set_attn_fused(1)
+        lib.iie_set_attn_fused(1); lib.iie_set_attn_tile_tc(1)
     assert device.read_flags() == 0
-    for a, b in zip(outs[0], outs[1]):
-        assert np.array_equal(a, b)
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert np.array_equal(a, b)
