@@ -226,7 +226,7 @@ int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t
  * either form; the switch exists so that tests reach both. */
 void iie_set_attn_fused(int enabled);
 /* Prefill attention by sixteen-token tiles: 1 (default) both products on tcgen05, 0 on mma.sync (the form that also takes
- * key spans beyond what the int32 TMEM accumulators of the tcgen05 form carry). */
+ * key spans beyond what the int32 TMEM accumulators of the tcgen05 form carry), -1 no tiles (the per-token kernels). */
 void iie_set_attn_tile_tc(int enabled);
 /* Whole decode step of the MoE decoder in ONE launch: every block of the model (RMSNorm, fused Q/K/V product, rotation,
  * cache append, exact softmax attention, O product, router, top-k, sigmoid gates, gate/up with integer SiLU, down with

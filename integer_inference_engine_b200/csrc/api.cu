@@ -1713,7 +1713,7 @@ extern "C" void iie_set_attn_fused(int enabled) {
 
 extern "C" void iie_set_attn_tile_tc(int enabled) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
-    iie::g_attn_tile_tc = enabled ? 1 : 0;
+    iie::g_attn_tile_tc = enabled > 0 ? 1 : enabled < 0 ? -1 : 0;
 }
 
 extern "C" void iie_set_pdl(int enabled) {

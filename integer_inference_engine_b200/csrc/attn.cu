@@ -1309,7 +1309,7 @@ cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s) {
     if (a.window > 0 && n_keys > a.window) n_keys = a.window;
     const unsigned chunks = (unsigned)((n_keys + AT_CH - 1) / AT_CH);
     attn_append_kernel<<<dim3((unsigned)a.batch, a.Hkv), 128, 0, s>>>(a);
-    if (g_attn_fused != 0 && attn_tiles_ok(a)) {
+    if (g_attn_fused != 0 && g_attn_tile_tc >= 0 && attn_tiles_ok(a)) {
         // consecutive tokens of one sequence: sixteen tokens per CTA share every staged chunk of keys and values
         note_launch(1);
         cudaError_t e = launch_attn_tile_scores(a, s);

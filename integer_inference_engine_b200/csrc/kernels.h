@@ -248,7 +248,7 @@ cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s);
 extern int g_attn_fused;           // 1: one cooperative launch when it fits, 0: three launches
 // passes 1 and 3 of a prefill by tiles of sixteen tokens on the tensor cores (attn_tile.cu), for the shapes attn_tiles_ok accepts
 bool attn_tiles_ok(const AttnArgs &a);
-extern int g_attn_tile_tc;         // 1: the tile products on tcgen05 (the default), 0: on mma.sync
+extern int g_attn_tile_tc;         // 1: the tile products on tcgen05 (the default), 0: on mma.sync, -1: no tiles
 cudaError_t launch_attn_tile_scores(const AttnArgs &a, cudaStream_t s);
 cudaError_t launch_attn_tile_exp(const AttnArgs &a, cudaStream_t s);
 cudaError_t launch_attn_tile_pv(const AttnArgs &a, cudaStream_t s);

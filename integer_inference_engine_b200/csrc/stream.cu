@@ -236,10 +236,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
                 }
                 if (y >= -2147483648LL && y <= 2139062143LL) {
                     // four balanced digits hold it: 32-bit arithmetic, the upper planes stay zero
-                    int v = (int)y;
-                    uint32_t pk = 0;
-#pragma unroll
-                    for (int l = 0; l < 4; l++) { pk |= (uint32_t)(v & 0xFF) << (8 * l); v = (v >> 8) + ((v >> 7) & 1); }
+                    const uint32_t pk = ((uint32_t)(int)y + 0x80808080u) ^ 0x80808080u;      // byte l = balanced digit l (the sum cannot wrap in this range)
                     nl = max(nl, pk == 0 ? 1 : 4 - (__clz((int)pk) >> 3));
 #pragma unroll
                     for (int l = 0; l < 4; l++) pw[l] |= ((pk >> (8 * l)) & 0xFF) << (8 * e);
