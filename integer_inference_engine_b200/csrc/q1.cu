@@ -21,6 +21,8 @@
 // fits, else int64).  Lane (g,t) owns two 32-bit words; bit r + 8 i of word mp is the sign bit of row
 // g + 8 (r & 1), column 32 (2 mp + (r >> 2)) + 8 t + 4 ((r >> 1) & 1) + i, so A register j of MMA m is
 // (word[m >> 1] >> (4 (m & 1) + j)) & 0x01010101: two instructions per register.
+#include <cuda.h>
+
 #include "kernels.h"
 #include "mma_items.cuh"
 
@@ -395,6 +397,227 @@ __global__ void __launch_bounds__(256, 2) q1_tile_kernel(const Q1Args a) {
     }
 }
 
+
+// ---- many tokens on the 5th-generation tensor cores ------------------------------------------------------------------------
+// Tile: 128 weight rows (MMA M, TMEM lanes) x 64 tokens (MMA N) x one 128-weight block at a time.  A = the block's sign bits
+// expanded to bytes 0/1 (u8) in the canonical K-major layout, written by eight warps straight from the repacked units (a
+// shift and a mask give four consecutive columns of a row); B = the eight digit planes of the 64 tokens (s8), fetched by
+// the copy engine (TMA, 64-byte swizzle) from the [token][8][K] planes; one TMEM accumulator per digit plane (8 x 64 = all 512
+// columns).  After the 32 MMAs of a block the eight warps read the accumulators out: P = sum_l 256^l acc_l (mod 2^64),
+// (2 P - S) * scale, the per-block floor shift, added into 64-bit registers (a thread owns one row and 32 tokens);
+// the issuer waits for that before it starts the next block, the producers are a block ahead.  Every wait is bounded; the
+// eight warps leave the block loop by a vote.
+constexpr int QT_PRODUCERS = 256, QT_THREADS = QT_PRODUCERS + 32, QT_STAGES = 4, QT_N = 64;
+constexpr int QT_A_BYTES = 128 * 64, QT_B_PLANE = QT_N * 64, QT_STAGE = QT_A_BYTES + 8 * QT_B_PLANE;      // 8192 + 32768
+constexpr unsigned QT_WAIT_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t qt_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool qt_wait(uint64_t *b, uint32_t parity, volatile int *abort_flag) {
+    for (unsigned it = 0; it < QT_WAIT_LIMIT; it++) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(qt_u32(b)), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 1023) == 1023 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ bool qt_all_ok(bool ok) {                // AND over the producer warps (named barrier 1)
+    uint32_t r;
+    asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 q, %1, 0;\n barrier.cta.red.and.pred p, 1, %2, q;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(r) : "r"((uint32_t)ok), "r"(QT_PRODUCERS) : "memory");
+    return r != 0;
+}
+
+template <typename DT>
+__global__ void __launch_bounds__(QT_THREADS, 1) q1_tc_kernel(const Q1Args a, const __grid_constant__ CUtensorMap xmap) {
+    constexpr int US = 256 + 16 * (int)sizeof(DT);
+    extern __shared__ __align__(1024) unsigned char qt_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(qt_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_bar[QT_STAGES], empty_bar[QT_STAGES], acc_bar, free_bar;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long tile = blockIdx.x, tok0 = (long long)blockIdx.y * QT_N;          // 128-row tile, first token
+    const int nb = (int)a.nb, n_chunks = 2 * nb;
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < QT_STAGES; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(qt_u32(&full_bar[s])), "r"(QT_PRODUCERS / 32 + 1));   // the producer warps + the copy's expect_tx arrival
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(qt_u32(&empty_bar[s])), "r"(1));
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(qt_u32(&acc_bar)), "r"(1));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(qt_u32(&free_bar)), "r"(QT_PRODUCERS / 32));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == QT_PRODUCERS / 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(qt_u32(&s_tmem)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp < QT_PRODUCERS / 32) {
+        // ---- producer part: thread -> (16-row sub-tile, lane (g, t) of the unit's bit words): one word, eight bit groups -------
+        const int sub = tid >> 5, ul = tid & 31, g = ul >> 2, t = ul & 3;
+        const long long tile16 = tile * 8 + sub;
+        const bool sub_ok = tile16 < a.n_tiles;
+        auto produce = [&](int c) {                                // chunk c = half (c & 1) of block c >> 1
+            const int s = c % QT_STAGES;
+            if (c >= QT_STAGES && !qt_wait(&empty_bar[s], ((c / QT_STAGES) - 1) & 1, &s_abort)) return false;
+            unsigned char *stage = smem + (size_t)s * QT_STAGE;
+            if (tid == 0) {
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(qt_u32(&full_bar[s])), "r"(8 * QT_B_PLANE) : "memory");
+#pragma unroll
+                for (int l = 0; l < 8; l++)
+                    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                                 ::"r"(qt_u32(stage + QT_A_BYTES + l * QT_B_PLANE)), "l"(reinterpret_cast<uint64_t>(&xmap)), "r"(c * 64), "r"(l),
+                                   "r"((int)tok0), "r"(qt_u32(&full_bar[s])) : "memory");
+            }
+            uint32_t w = 0;
+            if (sub_ok) w = __ldg(reinterpret_cast<const uint32_t *>(a.units + (tile16 * nb + (c >> 1)) * US) + ul * 2 + (c & 1));
+#pragma unroll
+            for (int r = 0; r < 8; r++) {                          // bit group r: MMA m & 1 = rhalf, column half jj, row half hi
+                const int rhalf = r >> 2, jj = (r >> 1) & 1, hi = r & 1;
+                const int row = sub * 16 + g + 8 * hi;
+                const int k16 = 2 * rhalf + (t >> 1), kin = 8 * (t & 1) + 4 * jj;              // columns 32 rhalf + 8 t + 4 jj + (0..3) of the chunk
+                *reinterpret_cast<uint32_t *>(stage + k16 * (128 * 16) + (row >> 3) * 128 + (row & 7) * 16 + kin) = (w >> r) & 0x01010101u;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qt_u32(&full_bar[s])) : "memory");
+            return true;
+        };
+        // ---- read-out part: TMEM lane = row of the tile, 32 tokens per thread ------------------------------------------
+        const int rowt = (warp & 3) * 32 + lane, cg = warp >> 2;
+        const long long row = tile * 128 + rowt;
+        const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const bool row_ok = row < a.out_f && (tile * 8 + (rowt >> 4)) < a.n_tiles;
+        const uint8_t *scale_unit = a.units + ((tile * 8 + (rowt >> 4)) * (long long)nb) * US;
+        unsigned long long acc64[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) acc64[j] = 0;
+        bool ok = produce(0) && produce(1);
+        for (int b = 0; b < nb; b++) {
+            if (ok && b + 1 < nb) ok = produce(2 * b + 2) && produce(2 * b + 3);
+            ok = ok && qt_wait(&acc_bar, b & 1, &s_abort);
+            if (!qt_all_ok(ok)) break;                             // uniform over the producer warps
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const unsigned long long sc = row_ok ? (unsigned long long)q1_scale_at<DT>(scale_unit + (long long)b * US, rowt & 15) : 0ULL;
+#pragma unroll
+            for (int qu = 0; qu < 8; qu++) {                       // four tokens at a time: 32 registers of accumulators in flight
+                int r[8][4];
+#pragma unroll
+                for (int l = 0; l < 8; l++)
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(r[l][0]), "=r"(r[l][1]), "=r"(r[l][2]), "=r"(r[l][3]) : "r"(tlane + l * QT_N + cg * 32 + qu * 4));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const long long tok = min(tok0 + cg * 32 + qu * 4 + j, a.T - 1);
+                    const unsigned long long tt = (unsigned long long)__ldg(a.totals + tok * nb + b);
+                    // P = sum_l 256^l acc_l (mod 2^64): the low four planes as 32 x 32 -> 64 multiply-adds, the high four shifted in
+                    const long long lo = (long long)r[0][j] + (long long)r[1][j] * 256LL + (long long)r[2][j] * 65536LL + (long long)r[3][j] * 16777216LL;
+                    const long long hi4 = (long long)r[4][j] + (long long)r[5][j] * 256LL + (long long)r[6][j] * 65536LL + (long long)r[7][j] * 16777216LL;
+                    const unsigned long long P = (unsigned long long)lo + ((unsigned long long)hi4 << 32);
+                    acc64[qu * 4 + j] += (unsigned long long)q1_shift((int64_t)((2ULL * P - tt) * sc), a.sh);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qt_u32(&free_bar)) : "memory");
+        }
+        if (ok && row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const long long tok = tok0 + cg * 32 + j;
+                if (tok < a.T) a.out[tok * a.out_f + row] = (int64_t)(acc64[j] + (a.add ? (unsigned long long)a.add[tok * a.out_f + row] : 0ULL));
+            }
+        }
+    } else {
+        // ---- MMA issuer ---------------------------------------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t IDESC = (2u << 4) | (1u << 10) | ((uint32_t)(QT_N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);     // u8 x s8 -> s32
+            bool ok = true;
+            for (int c = 0; c < n_chunks && ok; c++) {
+                const int s = c % QT_STAGES;
+                ok = qt_wait(&full_bar[s], (c / QT_STAGES) & 1, &s_abort);
+                if (ok && (c & 1) == 0 && c > 0) ok = qt_wait(&free_bar, ((c >> 1) - 1) & 1, &s_abort);      // the previous block has left TMEM
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t stage = qt_u32(smem + (size_t)s * QT_STAGE);
+                // A: K-major, no swizzle (LBO = distance of the two 16-byte K halves of an MMA, SBO = 8-row groups); B: 64-byte swizzle
+                const uint64_t da0 = (uint64_t)((stage >> 4) & 0x3FFF) | ((uint64_t)((128 * 16) >> 4) << 16) | ((uint64_t)(128 >> 4) << 32) | (1ULL << 46);
+                const uint64_t db0 = (uint64_t)(((stage + QT_A_BYTES) >> 4) & 0x3FFF) | (1ULL << 16) | ((uint64_t)(512 >> 4) << 32) | (1ULL << 46) | (4ULL << 61);
+#pragma unroll
+                for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+                    for (int l = 0; l < 8; l++) {
+                        const uint64_t da = da0 + (uint64_t)((ks * 2 * 128 * 16) >> 4);
+                        const uint64_t db = db0 + (uint64_t)((l * QT_B_PLANE + ks * 32) >> 4);
+                        const uint32_t accumulate = ((c & 1) == 0 && ks == 0) ? 0u : 1u;      // a block starts from zero
+                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                                     " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
+                                     ::"r"(tmem + l * QT_N), "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u) : "memory");
+                    }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(qt_u32(&empty_bar[s])) : "memory");
+                if (c & 1) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(qt_u32(&acc_bar)) : "memory");
+            }
+        }
+        __syncwarp();
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == QT_PRODUCERS / 32) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+    if (tid == 0 && s_abort && a.flags) atomicOr(a.flags, 8);
+}
+
+using QtEncode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+QtEncode qt_encode() {
+    static QtEncode fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return reinterpret_cast<QtEncode>(p);
+    }();
+    return fn;
+}
+
+int g_q1_tc = 1;                   // 1: products of 32 tokens or more on the tcgen05 tiles, 0: always the warp-MMA tiles
+
+template <typename DT>
+cudaError_t launch_q1_tc(const Q1Args &a, cudaStream_t s) {
+    QtEncode enc = qt_encode();
+    if (!enc) return cudaErrorNotSupported;
+    const long long K = a.nb * 128;
+    CUtensorMap map;
+    const cuuint64_t dims[3] = {(cuuint64_t)K, 8, (cuuint64_t)a.T};
+    const cuuint64_t strides[2] = {(cuuint64_t)K, (cuuint64_t)(8 * K)};
+    const cuuint32_t box[3] = {64, 1, QT_N}, estr[3] = {1, 1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t *>(a.xl), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    constexpr size_t smem = (size_t)QT_STAGES * QT_STAGE + 1024;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(q1_tc_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    dim3 grid((unsigned)((a.out_f + 127) / 128), (unsigned)((a.T + QT_N - 1) / QT_N));
+    q1_tc_kernel<DT><<<grid, QT_THREADS, smem, s>>>(a, map);
+    note_launch();
+    return cudaGetLastError();
+}
+
 template <int BPW, typename DT>
 cudaError_t launch_gemv(const Q1Args &a_in, int W, cudaStream_t s) {
     Q1Args a = a_in;
@@ -449,6 +672,11 @@ cudaError_t launch_apply_t(const Q1Args &a, cudaStream_t s) {
         if (bpw <= 6) return launch_gemv<6, DT>(a, W, s);
         return launch_gemv<8, DT>(a, W, s);
     }
+    if (g_q1_tc && a.T >= 32 && (a.nb * 128) % 16 == 0 && (reinterpret_cast<uintptr_t>(a.xl) & 15) == 0) {
+        const cudaError_t e = launch_q1_tc<DT>(a, s);
+        if (e == cudaSuccess) return e;
+        cudaGetLastError();                                    // no tensor map on this driver: the warp-MMA tiles
+    }
     dim3 grid((unsigned)((a.n_tiles + 7) / 8), (unsigned)((a.T + Q1_TC - 1) / Q1_TC));
     q1_tile_kernel<DT><<<grid, 256, 0, s>>>(a);
     note_launch();
@@ -486,6 +714,7 @@ __global__ void q1_embed_row_kernel(const uint8_t *units, long long nb, const in
 }  // namespace
 
 void set_q1_stream(int on) { g_q1_stream = on ? 1 : 0; }
+void set_q1_tc(int on) { g_q1_tc = on ? 1 : 0; }
 
 size_t q1_unit_bytes(bool sc32) { return 256 + 16 * (sc32 ? 4 : 8); }
 

@@ -37,7 +37,7 @@ def test_golden_vectors_from_the_reference(golden_dir):
 
 
 @pytest.mark.parametrize("out_f,nb,T", [(16, 1, 1), (33, 5, 1), (256, 32, 1), (4096, 32, 1), (512, 96, 1), (48, 130, 1),
-                                        (16, 1, 2), (100, 7, 5), (256, 32, 33), (64, 96, 70), (1024, 32, 4)])
+                                        (16, 1, 2), (100, 7, 5), (256, 32, 33), (64, 96, 70), (1024, 32, 4), (200, 3, 129), (130, 1, 64), (9, 2, 32)])
 def test_linear_matches_the_oracle(out_f, nb, T):
     bits, scale, x = _case(out_f * 131 + nb * 7 + T, out_f, nb, T, 26)
     want = onat.q1_linear(x, bits, scale, FRAC)
@@ -45,7 +45,7 @@ def test_linear_matches_the_oracle(out_f, nb, T):
 
 
 @pytest.mark.parametrize("magbits", [8, 31, 40, 55, 63])
-@pytest.mark.parametrize("T", [1, 6])
+@pytest.mark.parametrize("T", [1, 6, 40])
 def test_every_int64_activation_is_exact(magbits, T):
     """Sums wrap modulo 2^64 exactly as in the reference, including the int64 extremes."""
     bits, scale, x = _case(900 + magbits + T, 40, 4, T, magbits, wide_scale=True)
