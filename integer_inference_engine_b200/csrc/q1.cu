@@ -118,6 +118,7 @@ struct Q1Args {
     int64_t *out;                   // [T][out_f]
     const int64_t *add;             // optional [T][out_f] added to the product (may be `out` itself)
     int *flags;                     // optional: bit 3 is raised when a bulk copy never arrived
+    const int *nl_dev;              // tcgen05 tiles: digit planes in use by xl (planes at and above it are zero), on the device
 };
 
 // A fragments of MMA m from the two bit words of a lane
@@ -430,6 +431,21 @@ __device__ __forceinline__ bool qt_all_ok(bool ok) {                // AND over 
     return r != 0;
 }
 
+// digit planes in use: one warp per (token, plane) row of the [T][8][K] planes ORs the row; a non-zero row of plane l
+// raises the cell to l + 1 (the cell is cleared before the launch)
+__device__ int d_q1_nl;
+__global__ void __launch_bounds__(256) q1_planes_in_use_kernel(const int8_t *__restrict__ planes, long long rows, long long K, int *cell) {
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (wid >= rows) return;
+    const int lane = threadIdx.x & 31, l = (int)(wid & 7);
+    if (l == 0) return;                                            // one plane is always in use
+    const uint4 *src = reinterpret_cast<const uint4 *>(planes + wid * K);
+    uint32_t any = 0;
+    for (long long i = lane; i < K / 16; i += 32) { const uint4 v = __ldg(src + i); any |= v.x | v.y | v.z | v.w; }
+    any = __reduce_or_sync(0xffffffffu, any);
+    if (lane == 0 && any) atomicMax(cell, l + 1);
+}
+
 template <typename DT>
 __global__ void __launch_bounds__(QT_THREADS, 1) q1_tc_kernel(const Q1Args a, const __grid_constant__ CUtensorMap xmap) {
     constexpr int US = 256 + 16 * (int)sizeof(DT);
@@ -438,9 +454,11 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q1_tc_kernel(const Q1Args a, co
     __shared__ __align__(8) uint64_t full_bar[QT_STAGES], empty_bar[QT_STAGES], acc_bar, free_bar;
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
+    long long *s_tot = reinterpret_cast<long long *>(smem + (size_t)QT_STAGES * QT_STAGE);      // block sums of the tile's tokens [nb][64]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long tile = blockIdx.x, tok0 = (long long)blockIdx.y * QT_N;          // 128-row tile, first token
     const int nb = (int)a.nb, n_chunks = 2 * nb;
+    const int nl = max(1, min(8, *a.nl_dev));                       // digit planes that are not all zero (uniform over the grid)
     if (tid == 0) {
         s_abort = 0;
         for (int s = 0; s < QT_STAGES; s++) {
@@ -455,6 +473,10 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q1_tc_kernel(const Q1Args a, co
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(qt_u32(&s_tmem)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
+    for (int i = tid; i < nb * QT_N; i += QT_THREADS) {            // s_tot[b][token]
+        const int b = i / QT_N, tk = i - b * QT_N;
+        s_tot[i] = a.totals[min(tok0 + tk, a.T - 1) * nb + b];
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -465,15 +487,16 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q1_tc_kernel(const Q1Args a, co
         const int sub = tid >> 5, ul = tid & 31, g = ul >> 2, t = ul & 3;
         const long long tile16 = tile * 8 + sub;
         const bool sub_ok = tile16 < a.n_tiles;
+        const int np_t = nl <= 3 ? 3 : nl == 4 ? 4 : nl <= 6 ? 6 : 8;        // planes fetched, multiplied and read out
         auto produce = [&](int c) {                                // chunk c = half (c & 1) of block c >> 1
             const int s = c % QT_STAGES;
             if (c >= QT_STAGES && !qt_wait(&empty_bar[s], ((c / QT_STAGES) - 1) & 1, &s_abort)) return false;
             unsigned char *stage = smem + (size_t)s * QT_STAGE;
             if (tid == 0) {
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(qt_u32(&full_bar[s])), "r"(8 * QT_B_PLANE) : "memory");
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(qt_u32(&full_bar[s])), "r"(np_t * QT_B_PLANE) : "memory");
 #pragma unroll
                 for (int l = 0; l < 8; l++)
-                    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                    if (l < np_t) asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                                  ::"r"(qt_u32(stage + QT_A_BYTES + l * QT_B_PLANE)), "l"(reinterpret_cast<uint64_t>(&xmap)), "r"(c * 64), "r"(l),
                                    "r"((int)tok0), "r"(qt_u32(&full_bar[s])) : "memory");
             }
@@ -500,35 +523,53 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q1_tc_kernel(const Q1Args a, co
         unsigned long long acc64[32];
 #pragma unroll
         for (int j = 0; j < 32; j++) acc64[j] = 0;
+        // read-out of one block with NP planes known at compile time (NP >= nl: the planes between are zero and multiplied):
+        // eight tokens per round; TMEM is handed back as soon as the last round's loads have landed, before its arithmetic
+        auto drain = [&](auto np_c, int b, unsigned long long sc) {
+            constexpr int NP = decltype(np_c)::value;
+            const long long *tot = s_tot + b * QT_N + cg * 32;
+#pragma unroll
+            for (int ro = 0; ro < 4; ro++) {
+                int r[NP][8];
+#pragma unroll
+                for (int l = 0; l < NP; l++)
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                 : "=r"(r[l][0]), "=r"(r[l][1]), "=r"(r[l][2]), "=r"(r[l][3]), "=r"(r[l][4]), "=r"(r[l][5]), "=r"(r[l][6]), "=r"(r[l][7])
+                                 : "r"(tlane + l * QT_N + cg * 32 + ro * 8));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (ro == 3) {
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qt_u32(&free_bar)) : "memory");
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    // P = sum_l 256^l acc_l (mod 2^64): four planes at a time as 32 x 32 -> 64 multiply-adds
+                    long long lo = (long long)r[0][j];
+#pragma unroll
+                    for (int l = 1; l < 4 && l < NP; l++) lo += (long long)r[l][j] * (long long)(1 << (8 * l));
+                    unsigned long long P = (unsigned long long)lo;
+                    if (NP > 4) {
+                        long long hi4 = (long long)r[4][j];
+#pragma unroll
+                        for (int l = 5; l < NP; l++) hi4 += (long long)r[l][j] * (long long)(1 << (8 * (l - 4)));
+                        P += (unsigned long long)hi4 << 32;
+                    }
+                    acc64[ro * 8 + j] += (unsigned long long)q1_shift((int64_t)((2ULL * P - (unsigned long long)tot[ro * 8 + j]) * sc), a.sh);
+                }
+            }
+        };
         bool ok = produce(0) && produce(1);
         for (int b = 0; b < nb; b++) {
             if (ok && b + 1 < nb) ok = produce(2 * b + 2) && produce(2 * b + 3);
+            const unsigned long long sc = row_ok ? (unsigned long long)q1_scale_at<DT>(scale_unit + (long long)b * US, rowt & 15) : 0ULL;   // in flight during the wait
             ok = ok && qt_wait(&acc_bar, b & 1, &s_abort);
             if (!qt_all_ok(ok)) break;                             // uniform over the producer warps
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned long long sc = row_ok ? (unsigned long long)q1_scale_at<DT>(scale_unit + (long long)b * US, rowt & 15) : 0ULL;
-#pragma unroll
-            for (int qu = 0; qu < 8; qu++) {                       // four tokens at a time: 32 registers of accumulators in flight
-                int r[8][4];
-#pragma unroll
-                for (int l = 0; l < 8; l++)
-                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(r[l][0]), "=r"(r[l][1]), "=r"(r[l][2]), "=r"(r[l][3]) : "r"(tlane + l * QT_N + cg * 32 + qu * 4));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const long long tok = min(tok0 + cg * 32 + qu * 4 + j, a.T - 1);
-                    const unsigned long long tt = (unsigned long long)__ldg(a.totals + tok * nb + b);
-                    // P = sum_l 256^l acc_l (mod 2^64): the low four planes as 32 x 32 -> 64 multiply-adds, the high four shifted in
-                    const long long lo = (long long)r[0][j] + (long long)r[1][j] * 256LL + (long long)r[2][j] * 65536LL + (long long)r[3][j] * 16777216LL;
-                    const long long hi4 = (long long)r[4][j] + (long long)r[5][j] * 256LL + (long long)r[6][j] * 65536LL + (long long)r[7][j] * 16777216LL;
-                    const unsigned long long P = (unsigned long long)lo + ((unsigned long long)hi4 << 32);
-                    acc64[qu * 4 + j] += (unsigned long long)q1_shift((int64_t)((2ULL * P - tt) * sc), a.sh);
-                }
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qt_u32(&free_bar)) : "memory");
+            if (nl <= 3) drain(std::integral_constant<int, 3>{}, b, sc);
+            else if (nl == 4) drain(std::integral_constant<int, 4>{}, b, sc);
+            else if (nl <= 6) drain(std::integral_constant<int, 6>{}, b, sc);
+            else drain(std::integral_constant<int, 8>{}, b, sc);
         }
         if (ok && row_ok) {
 #pragma unroll
@@ -541,6 +582,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q1_tc_kernel(const Q1Args a, co
         // ---- MMA issuer ---------------------------------------------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t IDESC = (2u << 4) | (1u << 10) | ((uint32_t)(QT_N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);     // u8 x s8 -> s32
+            const int np = nl <= 3 ? 3 : nl == 4 ? 4 : nl <= 6 ? 6 : 8;      // the planes the read-out combines
             bool ok = true;
             for (int c = 0; c < n_chunks && ok; c++) {
                 const int s = c % QT_STAGES;
@@ -556,6 +598,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q1_tc_kernel(const Q1Args a, co
                 for (int ks = 0; ks < 2; ks++)
 #pragma unroll
                     for (int l = 0; l < 8; l++) {
+                        if (l >= np) continue;
                         const uint64_t da = da0 + (uint64_t)((ks * 2 * 128 * 16) >> 4);
                         const uint64_t db = db0 + (uint64_t)((l * QT_B_PLANE + ks * 32) >> 4);
                         const uint32_t accumulate = ((c & 1) == 0 && ks == 0) ? 0u : 1u;      // a block starts from zero
@@ -594,10 +637,17 @@ QtEncode qt_encode() {
 int g_q1_tc = 1;                   // 1: products of 32 tokens or more on the tcgen05 tiles, 0: always the warp-MMA tiles
 
 template <typename DT>
-cudaError_t launch_q1_tc(const Q1Args &a, cudaStream_t s) {
+cudaError_t launch_q1_tc(const Q1Args &a_in, cudaStream_t s) {
     QtEncode enc = qt_encode();
     if (!enc) return cudaErrorNotSupported;
+    Q1Args a = a_in;
     const long long K = a.nb * 128;
+    static int *cell = nullptr;
+    if (!cell && cudaGetSymbolAddress((void **)&cell, d_q1_nl) != cudaSuccess) return cudaErrorNotSupported;
+    if (cudaMemsetAsync(cell, 0, sizeof(int), s) != cudaSuccess) return cudaGetLastError();
+    q1_planes_in_use_kernel<<<(unsigned)((a.T * 8 * 32 + 255) / 256), 256, 0, s>>>(a.xl, a.T * 8, K, cell);
+    note_launch();
+    a.nl_dev = cell;
     CUtensorMap map;
     const cuuint64_t dims[3] = {(cuuint64_t)K, 8, (cuuint64_t)a.T};
     const cuuint64_t strides[2] = {(cuuint64_t)K, (cuuint64_t)(8 * K)};
@@ -605,10 +655,11 @@ cudaError_t launch_q1_tc(const Q1Args &a, cudaStream_t s) {
     if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t *>(a.xl), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    constexpr size_t smem = (size_t)QT_STAGES * QT_STAGE + 1024;
+    if (a.nb > 128) return cudaErrorNotSupported;                  // the block sums of a tile's tokens sit in shared memory
+    const size_t smem = (size_t)QT_STAGES * QT_STAGE + (size_t)a.nb * QT_N * 8 + 1024;
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(q1_tc_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const cudaError_t e = cudaFuncSetAttribute(q1_tc_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)QT_STAGES * QT_STAGE + (size_t)128 * QT_N * 8 + 1024));
         if (e != cudaSuccess) return e;
         configured = true;
     }
@@ -753,7 +804,7 @@ cudaError_t launch_q1_apply(const uint8_t *units, bool sc32, long long out_f, lo
     Q1Args a;
     a.units = units; a.out_f = out_f; a.nb = nb; a.n_tiles = (out_f + 15) / 16; a.T = T;
     a.sh = frac <= 0 ? 0 : (frac >= 63 ? 63 : (int)frac);
-    a.tiles_per_cta = 1; a.xl = planes; a.totals = totals; a.out = out; a.add = add; a.flags = shared_flag_word();
+    a.tiles_per_cta = 1; a.xl = planes; a.totals = totals; a.out = out; a.add = add; a.flags = shared_flag_word(); a.nl_dev = nullptr;
     return sc32 ? launch_apply_t<int>(a, s) : launch_apply_t<long long>(a, s);
 }
 
