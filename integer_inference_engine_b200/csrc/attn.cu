@@ -662,7 +662,7 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     extern __shared__ __align__(16) unsigned char af_smem[];
     __shared__ long long s_max[AF_HEADS];
     __shared__ unsigned long long s_z[AF_HEADS];
-    __shared__ int s_wide, s_timeout;
+    __shared__ int s_wide, s_timeout, s_last, s_nl_out;
     __shared__ __align__(8) uint64_t bars[2];
     const int C = a.chunk, hd = a.hd, ld = hd + 4, rep = a.H / a.Hkv, kv = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, half = hd / 2;
@@ -859,7 +859,7 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     for (int i = tid; i < (nk32 - nk) * hd; i += AF_THREADS) sv[(size_t)(nk + i / hd) * ld + (i % hd)] = 0;
     if (!af_wait(&bars[1])) s_timeout = 1;
     __syncthreads();
-    long long *part = a.partial + ((long long)blockIdx.x * a.Hkv + kv) * rep * hd;        // this CTA's [rep][hd] partial sums
+    long long *accum = a.acc + (long long)kv * rep * hd;                                  // the [rep][hd] sums of this KV head, shared by its chunks
     {
         const int g = lane >> 2, t = lane & 3;
         for (int nt = warp; nt < hd / 8; nt += AF_THREADS / 32) {           // eight dimensions per warp and turn
@@ -888,53 +888,52 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
                 long long sum = 0;
 #pragma unroll
                 for (int w = 5; w >= 0; w--) sum = sum * 256 + (long long)acc[w][i];
-                if (g < rep) part[g * hd + nt * 8 + 2 * t + i] = sum;
+                if (g < rep) atomicAdd(reinterpret_cast<unsigned long long *>(accum + g * hd + nt * 8 + 2 * t + i), (unsigned long long)sum);
             }
         }
     }
-    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && a.out_nl) *a.out_nl = 1;
-    grid.sync();
-    // ---- pass 4: every output is the sum of the chunk partials; sixteen lanes share one output ---------------------------
-    if (blockIdx.x == 0 && blockIdx.y == 0)
-        for (int i = tid; i < a.H; i += blockDim.x) { a.hmax[i] = INT64_MIN; a.Z[i] = 0ULL; }     // nobody reads them any more
+    // ---- the chunk sums were added into one accumulator per output (integer adds are order-free); the CTA that arrives last
+    //      (a counter, no waiting) shifts, writes the result and its digit planes and returns the statistics to their
+    //      initial state, which spares a third grid-wide barrier and a reduction over the chunks
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) { s_last = atomicAdd(a.ticket, 1u) == gridDim.x * gridDim.y - 1 ? 1 : 0; s_nl_out = 1; }
+    __syncthreads();
+    if (s_timeout && tid == 0) atomicOr(a.flags, 8);
+    if (!s_last) return;
+    __threadfence();
     const long long n = (long long)a.H * hd;
-    const int used = (int)((a.pos - a.lo) / C) + 1;                          // chunks that held keys
-    const long long gid = ((long long)(blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + tid);
-    const long long n_groups = (long long)gridDim.x * gridDim.y * blockDim.x / 16;
-    const int sub = (int)(gid & 15);
     int nl = 1;
     bool over = false;
-    for (long long o = gid >> 4; (o & ~1LL) < n; o += n_groups) {           // a warp holds outputs 2w, 2w + 1: uniform trip count
-        long long sum = 0;
-        if (o < n) {
-            const int h = (int)(o / hd), dd = (int)(o - (long long)h * hd), kvh = h / rep, r = h - kvh * rep;
-            const long long *base = a.partial + ((long long)kvh * rep + r) * hd + dd;
-            const long long step = (long long)a.Hkv * rep * hd;
-            // three loads in flight per lane (48 chunks), then whatever is left
-            const long long v0 = sub < used ? __ldcg(base + (long long)sub * step) : 0;
-            const long long v1 = sub + 16 < used ? __ldcg(base + (long long)(sub + 16) * step) : 0;
-            const long long v2 = sub + 32 < used ? __ldcg(base + (long long)(sub + 32) * step) : 0;
-            sum = v0 + v1 + v2;
-            for (int cc = sub + 48; cc < used; cc += 16) sum += __ldcg(base + (long long)cc * step);
+    for (long long i0 = 0; i0 < n; i0 += (long long)AF_THREADS * 8) {
+        long long yv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {                                       // all eight loads in flight before any is used
+            const long long i = i0 + (long long)u * AF_THREADS + tid;
+            yv[u] = i < n ? __ldcg(a.acc + i) : 0;
         }
 #pragma unroll
-        for (int s2 = 8; s2 > 0; s2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s2);
-        if (o < n && sub == 0) {
-            const long long y = sum >> a.fa;
-            if (a.out) a.out[o] = y;
+        for (int u = 0; u < 8; u++) {
+            const long long i = i0 + (long long)u * AF_THREADS + tid;
+            if (i >= n) continue;
+            const long long y = yv[u] >> a.fa;
+            if (a.out) a.out[i] = y;
             if (a.out_limbs) {
                 bool ok;
                 const uint64_t dg = balanced_digits8(y, ok);
                 over |= !ok;
                 nl = max(nl, digits_used(dg));
 #pragma unroll
-                for (int l = 0; l < 8; l++) a.out_limbs[l * n + o] = (int8_t)(dg >> (8 * l));
+                for (int l = 0; l < 8; l++) a.out_limbs[l * n + i] = (int8_t)(dg >> (8 * l));
             }
+            a.acc[i] = 0;
         }
     }
     if (over) atomicOr(a.flags, 1);
-    if (a.out_limbs && a.out_nl && nl > 1) atomicMax(a.out_nl, nl);
-    if (s_timeout && tid == 0) atomicOr(a.flags, 8);
+    if (a.out_limbs) atomicMax(&s_nl_out, nl);
+    for (int i = tid; i < a.H; i += AF_THREADS) { a.hmax[i] = INT64_MIN; a.Z[i] = 0ULL; }
+    __syncthreads();
+    if (tid == 0) { *a.ticket = 0u; if (a.out_nl) *a.out_nl = s_nl_out; }
 }
 
 // ---- several tokens at once (a prefill chunk, or the new tokens of independent sequences): the scores on the tensor cores,
