@@ -946,7 +946,7 @@ __global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in
     const long long Ls = a.Ls ? a.Ls : a.Lmax;
     extern __shared__ __align__(16) unsigned char ts_smem[];
     __shared__ long long s_max[AF_HEADS];
-    __shared__ int s_wide;
+    __shared__ int s_wide, s_q24;
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, hd = a.hd, half = hd / 2;
     const int ld = hd + 4, qld = hd + 16;
     // a CTA walks TS_CHUNKS consecutive 64-key chunks: the queries are rotated once and the next chunk's keys stream in
@@ -957,7 +957,7 @@ __global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in
     long long *dots = q64 + AF_HEADS * hd;                                  // [2][64][8]
     int32_t *skb = reinterpret_cast<int32_t *>(dots + 2 * AT_CH * AF_HEADS); // two key buffers [64][hd + 4]
     int8_t *qd = reinterpret_cast<int8_t *>(skb + 2 * AT_CH * ld);          // [4][8][hd + 16]
-    if (tid == 0) s_wide = 0;
+    if (tid == 0) { s_wide = 0; s_q24 = 0; }
     if (tid < AF_HEADS) s_max[tid] = INT64_MIN;
     const int vec_per_row = hd / 4;
     auto request = [&](int c) {                            // keys of chunk c of this CTA into buffer c & 1
@@ -974,7 +974,7 @@ __global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in
     };
     request(0);
     __syncthreads();
-    bool wide = false;
+    bool wide = false, wide24 = false;
     for (int idx = tid; idx < AF_HEADS * half; idx += blockDim.x) {
         const int r = idx / half, i = idx - r * half;
         const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + half : 2 * i + 1;
@@ -991,10 +991,12 @@ __global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in
             qd[(b * AF_HEADS + r) * qld + i1] = (int8_t)((uint32_t)(int32_t)x1 >> (8 * b));
         }
         wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
+        wide24 |= x0 < -(1 << 23) || x0 >= (1 << 23) || x1 < -(1 << 23) || x1 >= (1 << 23);
     }
     if (wide) s_wide = 1;
+    if (wide24) s_q24 = 1;
     __syncthreads();
-    const bool use_wide = s_wide != 0;
+    const bool use_wide = s_wide != 0, q_narrow = s_q24 == 0;
     const int ksteps = hd / 32;
     const bool split = (ksteps & 1) == 0;                  // four 16-key tiles: two warps per tile, half of the head dimension each
     const int key = tid & (AT_CH - 1);                     // thread -> (key, heads tid / 64 and tid / 64 + 4) for the score stores
@@ -1019,10 +1021,32 @@ __global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in
                 const int32_t *rowA = sk + (size_t)(kt * 16 + g) * ld, *rowB = rowA + 8 * ld;
                 for (int st = s_lo; st < s_hi; st++) {
                     uint32_t A[4][4];
-                    af_bytes(*reinterpret_cast<const int4 *>(rowA + 32 * st + 4 * t), A[0][0], A[1][0], A[2][0], A[3][0]);
-                    af_bytes(*reinterpret_cast<const int4 *>(rowB + 32 * st + 4 * t), A[0][1], A[1][1], A[2][1], A[3][1]);
-                    af_bytes(*reinterpret_cast<const int4 *>(rowA + 32 * st + 16 + 4 * t), A[0][2], A[1][2], A[2][2], A[3][2]);
-                    af_bytes(*reinterpret_cast<const int4 *>(rowB + 32 * st + 16 + 4 * t), A[0][3], A[1][3], A[2][3], A[3][3]);
+                    const int4 k0 = *reinterpret_cast<const int4 *>(rowA + 32 * st + 4 * t), k1 = *reinterpret_cast<const int4 *>(rowB + 32 * st + 4 * t);
+                    const int4 k2 = *reinterpret_cast<const int4 *>(rowA + 32 * st + 16 + 4 * t), k3 = *reinterpret_cast<const int4 *>(rowB + 32 * st + 16 + 4 * t);
+                    af_bytes(k0, A[0][0], A[1][0], A[2][0], A[3][0]);
+                    af_bytes(k1, A[0][1], A[1][1], A[2][1], A[3][1]);
+                    af_bytes(k2, A[0][2], A[1][2], A[2][2], A[3][2]);
+                    af_bytes(k3, A[0][3], A[1][3], A[2][3], A[3][3]);
+                    // keys and queries within [-2^23, 2^23): three byte planes each, the third signed (9 byte pairs instead of
+                    // 16); decided per warp and K step, the accumulators take either form
+                    auto fits = [](const int4 v) {
+                        return ((unsigned)(v.x + (1 << 23)) | (unsigned)(v.y + (1 << 23)) | (unsigned)(v.z + (1 << 23)) | (unsigned)(v.w + (1 << 23))) < (1u << 24);
+                    };
+                    const bool narrow = q_narrow && __all_sync(0xffffffffu, fits(k0) && fits(k1) && fits(k2) && fits(k3));
+                    if (narrow) {
+#pragma unroll
+                        for (int b = 0; b < 3; b++) {
+                            const int8_t *qb = qd + (b * AF_HEADS + g) * qld + 32 * st + 4 * t;
+                            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(qb), b1 = *reinterpret_cast<const uint32_t *>(qb + 16);
+#pragma unroll
+                            for (int aa = 0; aa < 3; aa++) {
+                                if (aa < 2 && b < 2) af_mma<false, false>(acc[aa + b], A[aa], b0, b1);
+                                else if (aa < 2) af_mma<false, true>(acc[aa + b], A[aa], b0, b1);
+                                else if (b < 2) af_mma<true, false>(acc[aa + b], A[aa], b0, b1);
+                                else af_mma<true, true>(acc[aa + b], A[aa], b0, b1);
+                            }
+                        }
+                    } else {
 #pragma unroll
                     for (int b = 0; b < 4; b++) {
                         const int8_t *qb = qd + (b * AF_HEADS + g) * qld + 32 * st + 4 * t;
@@ -1034,6 +1058,7 @@ __global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in
                             else if (b < 3) af_mma<true, false>(acc[aa + b], A[aa], b0, b1);
                             else af_mma<true, true>(acc[aa + b], A[aa], b0, b1);
                         }
+                    }
                     }
                 }
 #pragma unroll

@@ -17,11 +17,13 @@ FA, FW = 16, 24
 HERE = Path(__file__).resolve().parent
 
 
-@pytest.mark.parametrize(("B", "H", "Hkv", "hd", "pos", "window", "rope"), [(3, 4, 2, 64, 20, None, 0), (5, 8, 2, 64, 37, 9, 1),
-                                                                         (2, 8, 1, 128, 130, 64, 1),
-                                                                         # long enough for several CTAs to share one pair's key chunks
-                                                                         (2, 8, 2, 64, 700, None, 1), (3, 16, 2, 128, 450, 300, 0)])
-def test_batched_decode_attention_matches_the_checker_per_sequence(B, H, Hkv, hd, pos, window, rope):
+@pytest.mark.parametrize(("B", "H", "Hkv", "hd", "pos", "window", "rope", "kbits"),
+                         [(3, 4, 2, 64, 20, None, 0, 19), (5, 8, 2, 64, 37, 9, 1, 19), (2, 8, 1, 128, 130, 64, 1, 19),
+                          # long enough for several CTAs to share one pair's key chunks
+                          (2, 8, 2, 64, 700, None, 1, 19), (3, 16, 2, 128, 450, 300, 0, 19),
+                          # cached keys beyond 24 bits in some chunks only: the four-plane and the three-plane products side by side
+                          (2, 8, 2, 64, 300, None, 1, 29), (2, 8, 1, 128, 200, None, 0, 30)])
+def test_batched_decode_attention_matches_the_checker_per_sequence(B, H, Hkv, hd, pos, window, rope, kbits):
     import torch
 
     from integer_inference_engine_b200 import device
@@ -31,6 +33,8 @@ def test_batched_decode_attention_matches_the_checker_per_sequence(B, H, Hkv, hd
     k = rng.integers(-(1 << 19), 1 << 19, size=(B, Hkv * hd), dtype=np.int64)
     v = rng.integers(-(1 << 19), 1 << 19, size=(B, Hkv * hd), dtype=np.int64)
     kc = rng.integers(-(1 << 19), 1 << 19, size=(B, Hkv, rows, hd)).astype(np.int32)
+    if kbits > 19:
+        kc[:, :, 70:190] = rng.integers(-(1 << kbits), 1 << kbits, size=(B, Hkv, 120, hd)).astype(np.int32)
     vc = rng.integers(-(1 << 19), 1 << 19, size=(B, Hkv, rows, hd)).astype(np.int32)
     cos, sin = o.build_rope_tables(rows, hd, 50000.0, FA)
     kcd, vcd = torch.from_numpy(kc).cuda(), torch.from_numpy(vc).cuda()
