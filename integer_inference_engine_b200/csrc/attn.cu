@@ -613,7 +613,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const AttnArgs a_in) {
 // thread owns two output dimensions of four heads for a quarter of the keys).
 constexpr int AF_THREADS = 512;
 constexpr int AF_HEADS = 8;                  // query heads per KV head this form carries
-constexpr int TS_CHUNKS = 4;                 // 64-key chunks one CTA of attn_scores_tc_kernel walks
+constexpr int TS_CHUNKS_MIN = 4, TS_CHUNKS_MAX = 16;      // 64-key chunks one CTA of attn_scores_tc_kernel walks (a.chunk, chosen at launch)
 constexpr unsigned AF_POLLS = 1u << 22;
 
 __device__ __forceinline__ uint32_t af_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -949,9 +949,10 @@ __global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in
     __shared__ int s_wide, s_q24;
     const int kv = blockIdx.y, rep = a.H / a.Hkv, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, hd = a.hd, half = hd / 2;
     const int ld = hd + 4, qld = hd + 16;
-    // a CTA walks TS_CHUNKS consecutive 64-key chunks: the queries are rotated once and the next chunk's keys stream in
+    // a CTA walks a.chunk consecutive 64-key chunks: the queries are rotated once and the next chunk's keys stream in
     // (cp.async into the other buffer) while the current chunk is multiplied
-    const long long first = a.lo + (long long)blockIdx.x * TS_CHUNKS * AT_CH;
+    const int walk = a.chunk;
+    const long long first = a.lo + (long long)blockIdx.x * walk * AT_CH;
     if (first > a.pos) return;                             // all of this CTA's chunks lie past the token's position
     long long *q64 = reinterpret_cast<long long *>(ts_smem);                 // [8][hd]
     long long *dots = q64 + AF_HEADS * hd;                                  // [2][64][8]
@@ -1001,11 +1002,11 @@ __global__ void __launch_bounds__(256) attn_scores_tc_kernel(const AttnArgs a_in
     const bool split = (ksteps & 1) == 0;                  // four 16-key tiles: two warps per tile, half of the head dimension each
     const int key = tid & (AT_CH - 1);                     // thread -> (key, heads tid / 64 and tid / 64 + 4) for the score stores
     long long mloc[2] = {INT64_MIN, INT64_MIN};
-    for (int c = 0; c < TS_CHUNKS; c++) {
+    for (int c = 0; c < walk; c++) {
         const long long l0 = first + (long long)c * AT_CH;
         if (l0 > a.pos) break;                             // uniform over the CTA
         const int nk = (int)(min(l0 + AT_CH, a.pos + 1) - l0);
-        const bool more = c + 1 < TS_CHUNKS && l0 + AT_CH <= a.pos;
+        const bool more = c + 1 < walk && l0 + AT_CH <= a.pos;
         if (more) { request(c + 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
         else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                                   // chunk c has landed for every thread
@@ -1350,7 +1351,13 @@ cudaError_t launch_attn_prefill(const AttnArgs &a, cudaStream_t s) {
         }
         const size_t sc_smem = (size_t)AF_HEADS * a.hd * 8 + (size_t)2 * AT_CH * AF_HEADS * 8 + (size_t)2 * AT_CH * (a.hd + 4) * 4 +
                                (size_t)4 * AF_HEADS * (a.hd + 16);
-        attn_scores_tc_kernel<<<dim3((chunks + TS_CHUNKS - 1) / TS_CHUNKS, a.Hkv, (unsigned)a.batch), 256, sc_smem, s>>>(a);
+        // longer walks amortise the query rotation and the pipeline start, as long as a few CTAs per SM remain
+        AttnArgs t = a;
+        const long long pairs = (long long)a.Hkv * a.batch;
+        int walk = (int)((long long)chunks * pairs / (4 * 148));
+        walk = walk < TS_CHUNKS_MIN ? TS_CHUNKS_MIN : walk > TS_CHUNKS_MAX ? TS_CHUNKS_MAX : walk;
+        t.chunk = walk;
+        attn_scores_tc_kernel<<<dim3((chunks + walk - 1) / walk, a.Hkv, (unsigned)a.batch), 256, sc_smem, s>>>(t);
     } else
         attn_scores_kernel<<<dim3(chunks, a.Hkv, (unsigned)a.batch), 256, (size_t)rep * a.hd * 12 + (size_t)AT_CH * (a.hd + 4) * 4, s>>>(a);
     attn_exp_kernel<<<dim3((unsigned)((n_keys + 255) / 256), a.H, (unsigned)a.batch), 256, 0, s>>>(a);
