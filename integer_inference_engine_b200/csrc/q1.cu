@@ -488,7 +488,10 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q1_tc_kernel(const Q1Args a, co
         const long long tile16 = tile * 8 + sub;
         const bool sub_ok = tile16 < a.n_tiles;
         const int np_t = nl <= 3 ? 3 : nl == 4 ? 4 : nl <= 6 ? 6 : 8;        // planes fetched, multiplied and read out
-        auto produce = [&](int c) {                                // chunk c = half (c & 1) of block c >> 1
+        auto words = [&](int b) {                                  // this thread's two bit words of block b (one per chunk)
+            return sub_ok ? ldg64(a.units + (tile16 * nb + b) * US + ul * 8) : make_uint2(0u, 0u);
+        };
+        auto produce = [&](int c, uint32_t w) {                    // chunk c = half (c & 1) of block c >> 1, w = its bit word
             const int s = c % QT_STAGES;
             if (c >= QT_STAGES && !qt_wait(&empty_bar[s], ((c / QT_STAGES) - 1) & 1, &s_abort)) return false;
             unsigned char *stage = smem + (size_t)s * QT_STAGE;
@@ -500,8 +503,6 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q1_tc_kernel(const Q1Args a, co
                                  ::"r"(qt_u32(stage + QT_A_BYTES + l * QT_B_PLANE)), "l"(reinterpret_cast<uint64_t>(&xmap)), "r"(c * 64), "r"(l),
                                    "r"((int)tok0), "r"(qt_u32(&full_bar[s])) : "memory");
             }
-            uint32_t w = 0;
-            if (sub_ok) w = __ldg(reinterpret_cast<const uint32_t *>(a.units + (tile16 * nb + (c >> 1)) * US) + ul * 2 + (c & 1));
 #pragma unroll
             for (int r = 0; r < 8; r++) {                          // bit group r: MMA m & 1 = rhalf, column half jj, row half hi
                 const int rhalf = r >> 2, jj = (r >> 1) & 1, hi = r & 1;
@@ -559,9 +560,12 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q1_tc_kernel(const Q1Args a, co
                 }
             }
         };
-        bool ok = produce(0) && produce(1);
+        uint2 wn = words(0);
+        bool ok = produce(0, wn.x) && produce(1, wn.y);
+        if (nb > 1) wn = words(1);
         for (int b = 0; b < nb; b++) {
-            if (ok && b + 1 < nb) ok = produce(2 * b + 2) && produce(2 * b + 3);
+            if (ok && b + 1 < nb) ok = produce(2 * b + 2, wn.x) && produce(2 * b + 3, wn.y);
+            if (b + 2 < nb) wn = words(b + 2);                     // in flight during the wait and the read-out
             const unsigned long long sc = row_ok ? (unsigned long long)q1_scale_at<DT>(scale_unit + (long long)b * US, rowt & 15) : 0ULL;   // in flight during the wait
             ok = ok && qt_wait(&acc_bar, b & 1, &s_abort);
             if (!qt_all_ok(ok)) break;                             // uniform over the producer warps
