@@ -701,24 +701,36 @@ __global__ void __launch_bounds__(PC_THREADS, 1) attn_tile_scores_tc_kernel(cons
     // rotated queries as byte planes in the canonical layout (row = token * 8 + head)
     {
         bool wide = false, wide24 = false;
-        for (int idx = tid; idx < PT_COLS * HALF; idx += PC_THREADS) {
-            const int row = idx / HALF, i = idx - row * HALF, qi = row >> 3, h = row & 7;
-            const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + HALF : 2 * i + 1;
-            int64_t x0 = 0, x1 = 0;
-            if (qi < T.nq && h < rep) {
-                const int64_t *src = a.q + ((T.t0 + qi) * a.H + kv * rep + h) * HD;
-                x0 = src[i0]; x1 = src[i1];
-                pt_rotate(a, T.pos0 + qi, i, x0, x1);
-            }
-            unsigned char *d0 = qd + (i0 >> 4) * (PT_COLS * 16) + (row >> 3) * 128 + (row & 7) * 16 + (i0 & 15);
-            unsigned char *d1 = qd + (i1 >> 4) * (PT_COLS * 16) + (row >> 3) * 128 + (row & 7) * 16 + (i1 & 15);
+        for (int idx0 = tid; idx0 < PT_COLS * HALF; idx0 += 4 * PC_THREADS) {      // four pairs per step: their loads are in flight together
+            int64_t x0[4], x1[4], cs[4], sn[4];
 #pragma unroll
-            for (int b = 0; b < 4; b++) {
-                d0[b * Q_PLANE] = (unsigned char)((uint32_t)(int32_t)x0 >> (8 * b));
-                d1[b * Q_PLANE] = (unsigned char)((uint32_t)(int32_t)x1 >> (8 * b));
+            for (int u = 0; u < 4; u++) {
+                const int idx = idx0 + u * PC_THREADS, row = idx / HALF, i = idx - row * HALF, qi = row >> 3, h = row & 7;
+                const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + HALF : 2 * i + 1;
+                x0[u] = x1[u] = 0; cs[u] = sn[u] = 0;
+                if (idx < PT_COLS * HALF && qi < T.nq && h < rep) {
+                    const int64_t *src = a.q + ((T.t0 + qi) * a.H + kv * rep + h) * HD;
+                    x0[u] = src[i0]; x1[u] = src[i1];
+                    if (a.rope) { cs[u] = a.cos[(T.pos0 + qi) * HALF + i]; sn[u] = a.sin[(T.pos0 + qi) * HALF + i]; }
+                }
             }
-            wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
-            wide24 |= x0 < -(1 << 23) || x0 >= (1 << 23) || x1 < -(1 << 23) || x1 >= (1 << 23);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int idx = idx0 + u * PC_THREADS, row = idx / HALF, i = idx - row * HALF;
+                if (idx >= PT_COLS * HALF) continue;
+                const int i0 = a.rope == 2 ? i : 2 * i, i1 = a.rope == 2 ? i + HALF : 2 * i + 1;
+                int64_t y0 = x0[u], y1 = x1[u];
+                if (a.rope) { y0 = (x0[u] * cs[u] - x1[u] * sn[u]) >> a.fa; y1 = (x0[u] * sn[u] + x1[u] * cs[u]) >> a.fa; }
+                unsigned char *d0 = qd + (i0 >> 4) * (PT_COLS * 16) + (row >> 3) * 128 + (row & 7) * 16 + (i0 & 15);
+                unsigned char *d1 = qd + (i1 >> 4) * (PT_COLS * 16) + (row >> 3) * 128 + (row & 7) * 16 + (i1 & 15);
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    d0[b * Q_PLANE] = (unsigned char)((uint32_t)(int32_t)y0 >> (8 * b));
+                    d1[b * Q_PLANE] = (unsigned char)((uint32_t)(int32_t)y1 >> (8 * b));
+                }
+                wide |= y0 != (int32_t)y0 || y1 != (int32_t)y1;
+                wide24 |= y0 < -(1 << 23) || y0 >= (1 << 23) || y1 < -(1 << 23) || y1 >= (1 << 23);
+            }
         }
         if (wide) s_wide = 1;
         if (wide24) s_qwide24 = 1;
