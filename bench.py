@@ -806,6 +806,21 @@ def run_prefill(args):
     att_ms, _ = _timed(lambda i: device.attention_prefill(aq, ak, av, akc, avc, 0, N_HEADS, N_KV, HEAD_DIM, FA, WINDOW, out=aout),
                        3, 1, world, local)
     assert device.read_flags() == 0
+    # the two dense products of the same block (fused Q/K/V and O) at T rows: Q4_K matrices on the tcgen05 LINEAR tiles
+    from integer_inference_engine_b200.qk_cuda import Q4_K
+    from integer_inference_engine_b200.synth import synth_q4k
+    nbd, qkv_rows, qd = D_MODEL // 256, (N_HEADS + 2 * N_KV) * HEAD_DIM, N_HEADS * HEAD_DIM
+    wqkv = device.register_weight(synth_q4k(qkv_rows * nbd, g).view(-1), qkv_rows, nbd, Q4_K)
+    wo = device.register_weight(synth_q4k(D_MODEL * (qd // 256), g).view(-1), D_MODEL, qd // 256, Q4_K)
+    lin_qkv = torch.empty((T, qkv_rows), dtype=torch.int64, device="cuda")
+    lin_o = torch.empty((T, D_MODEL), dtype=torch.int64, device="cuda")
+    att_in = rnd(T, qd)
+
+    def linears(i):
+        device.apply(wqkv, h, qkv_rows, FW, out=lin_qkv)
+        device.apply(wo, att_in, D_MODEL, FW, out=lin_o)
+    lin_ms, _ = _timed(linears, 3, 1, world, local)
+    assert device.read_flags() == 0
     if rank == 0:
         ms_step = ms / args.steps
         i8 = int8_peak()
@@ -830,7 +845,8 @@ def run_prefill(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int64 via int8 digit planes (tcgen05 kind::i8)", "data": "synthetic",
             "config": {"workload": f"config3_moe_prefill: {T} tokens x {args.layers} MoE blocks, grouped expert GEMMs",
-                       "ms_per_block": ms_step / args.layers, "attention_prefill_ms_per_block": att_ms / 3,
+                       "ms_per_block": ms_step / args.layers, "attention_prefill_ms_per_block": att_ms / 3, "qkv_o_linears_ms_per_block": lin_ms / 3,
+                       "whole_block_ms": ms_step / args.layers + att_ms / 3 + lin_ms / 3,
                        "parallelism": f"replicas x{world}",
                        "l2": "inputs larger than L2 (1.2 GB of expert weights per block)", "oracle_checked_rows": len(rows)},
             "clocks": clocks, "gpu_launches": int(launches * args.steps), "int8_peak": i8, "roofline": roofline, "cpu_baseline": cpu}))
