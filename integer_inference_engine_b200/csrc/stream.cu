@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
     __shared__ int64_t s_lg[SK_MAXE];
     __shared__ unsigned long long s_lo[NWARPS], s_hi[NWARPS], s_mx[NWARPS], s_gmx[NWARPS];
     __shared__ unsigned long long s_rms, s_inv, s_gm;
-    __shared__ int s_bad, s_nl;
+    __shared__ int s_bad, s_nl, s_fast;
 
     const int n_tiles = MODE == MODE_FRONT ? a.tiles_per_expert + a.tiles_b : a.n_sel * a.tiles_per_expert;
     const int tile0 = (int)blockIdx.x * tpc;
@@ -166,12 +166,16 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
     if (MODE == MODE_FRONT) {
         // ---- RMSNorm of the row and its digit planes, in every CTA (arithmetic of route.cu) ----------------------------
         u128 ssq = 0; unsigned long long mx = 0;
-        for (int i = threadIdx.x * 2; i < (int)K; i += blockDim.x * 2) {
+        for (int i = threadIdx.x * 2; i < (int)K; i += blockDim.x * 4) {          // two loads in flight per thread
+            const int i2 = i + blockDim.x * 2;
             const longlong2 xv = *reinterpret_cast<const longlong2 *>(a.x + i);
+            longlong2 xw = make_longlong2(0, 0);
+            if (i2 < (int)K) xw = *reinterpret_cast<const longlong2 *>(a.x + i2);
             *reinterpret_cast<longlong2 *>(xs + i) = xv;
-            const unsigned long long v0 = uabs64(xv.x), v1 = uabs64(xv.y);
-            ssq += (u128)v0 * v0; ssq += (u128)v1 * v1;
-            mx = v0 > mx ? v0 : mx; mx = v1 > mx ? v1 : mx;
+            if (i2 < (int)K) *reinterpret_cast<longlong2 *>(xs + i2) = xw;
+            const unsigned long long v0 = uabs64(xv.x), v1 = uabs64(xv.y), v2 = uabs64(xw.x), v3 = uabs64(xw.y);
+            ssq += (u128)v0 * v0; ssq += (u128)v1 * v1; ssq += (u128)v2 * v2; ssq += (u128)v3 * v3;
+            mx = v0 > mx ? v0 : mx; mx = v1 > mx ? v1 : mx; mx = v2 > mx ? v2 : mx; mx = v3 > mx ? v3 : mx;
         }
         unsigned long long lo = (unsigned long long)ssq, hi = (unsigned long long)(ssq >> 64);
 #pragma unroll
@@ -208,13 +212,51 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
             const u128 rms = isqrt128(mean + a.eps);
             if (rms == 0 || rms > (u128)0xFFFFFFFFFFFFFFFFULL) bad = 1;
             s_rms = (unsigned long long)rms; s_gm = gm; s_bad = bad;
-            s_inv = rms != 0 ? 0xFFFFFFFFFFFFFFFFULL / (unsigned long long)rms : 0;
+            const unsigned long long inv = recip_below((unsigned long long)rms);
+            s_inv = inv;
+            // block-wide bound: with q <= n / rms + 1 for every quotient and |gain| <= gm, n < rms * (2^31 - 2) keeps the
+            // quotients in 32 bits and n * gm <= rms * ((L - 2) * 2^fa - gm) keeps every gain product within the four-digit
+            // range L = 0x7F7F7F7F; the per-element range tests then drop out of the loop below
+            bool fast = false;
+            if (!bad && a.gain && a.fa <= 30 && m < (1ULL << (62 - a.fa)) && rms < ((u128)1 << 62) && gm < (1ULL << 31)) {
+                const unsigned long long n = m << a.fa, r64 = (unsigned long long)rms, lim = 2139062141ULL << a.fa;
+                fast = (u128)n < (u128)r64 * 2147483646ULL && lim > gm && (u128)n * gm <= (u128)r64 * (lim - gm);
+            }
+            s_fast = fast ? 1 : 0;
         }
         __syncthreads();
         const unsigned long long rms = s_rms, inv = s_inv, gm = s_gm;
         const bool dead = s_bad != 0;                             // not normalisable exactly: flag raised, zero planes, the launch still drains its copies
         bool bad = false, over = false;
         int nl = 1;
+        if (s_fast) {
+            const int fa = a.fa;
+            for (int i = threadIdx.x * 4; i < (int)K; i += blockDim.x * 4) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int64_t xv = xs[i + e];
+                    const unsigned long long n = uabs64(xv) << fa;
+                    unsigned long long q = __umul64hi(n, inv), r = n - q * rms;
+                    while (r >= rms) { q++; r -= rms; }
+                    const int yq = xv >= 0 ? (int)q : -(int)q - (r != 0);                      // floor of the signed quotient
+                    const int64_t y = ((int64_t)yq * (int)gs[i + e]) >> fa;                    // both factors fit 32 bits here
+                    pk[e] = ((uint32_t)(int)y + 0x80808080u) ^ 0x80808080u;                    // byte l = balanced digit l
+                }
+                const uint32_t any = pk[0] | pk[1] | pk[2] | pk[3];
+                nl = max(nl, any == 0 ? 1 : 4 - (__clz((int)any) >> 3));
+                const uint32_t lo01 = __byte_perm(pk[0], pk[1], 0x5140), hi01 = __byte_perm(pk[0], pk[1], 0x7362);
+                const uint32_t lo23 = __byte_perm(pk[2], pk[3], 0x5140), hi23 = __byte_perm(pk[2], pk[3], 0x7362);
+                uint32_t pw[8] = {__byte_perm(lo01, lo23, 0x5410), __byte_perm(lo01, lo23, 0x7632),
+                                  __byte_perm(hi01, hi23, 0x5410), __byte_perm(hi01, hi23, 0x7632), 0, 0, 0, 0};
+#pragma unroll
+                for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(planes + l * pstride + i) = pw[l];
+                if (blockIdx.x == 0 && a.hl_out) {
+#pragma unroll
+                    for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(a.hl_out + (long long)l * K + i) = pw[l];
+                }
+            }
+        } else
         for (int i = threadIdx.x * 4; i < (int)K; i += blockDim.x * 4) {
             uint32_t pw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll

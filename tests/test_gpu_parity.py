@@ -382,6 +382,36 @@ def test_device_moe_block_with_norm_and_residual(qk, T):
     qk.free_all()
 
 
+@pytest.mark.parametrize("shift", [0, 20, 31])
+def test_decode_block_norm_over_the_residual_magnitudes(qk, shift):
+    """The one-token block normalises its row inside the first streaming kernel.  Small residuals take the loop whose range
+    tests were settled once for the whole row; at 2^20 the mean square needs the 128-bit root; at 2^31 the row leaves the
+    64-bit quotient and the element-wise path with the wide quotient and the bitwise root runs.  All equal the checker."""
+    import torch
+
+    from integer_inference_engine_b200 import device
+    qk.free_all()
+    d, eff, E, k = 2048, 768, 16, 4
+    router, gate, up, down, h0 = o.synth_moe(93, d, eff, E, 1)
+    rh = qk.register_weight(router, E, d // 256, o.Q4_K)
+    gh = [qk.register_weight(w, eff, d // 256, o.Q4_K) for w in gate]
+    uh = [qk.register_weight(w, eff, d // 256, o.Q4_K) for w in up]
+    dh = [qk.register_weight(w, d, eff // 256, o.Q6_K) for w in down]
+    layer = device.MoELayer(rh, gh, uh, dh, k, d, eff)
+    gain = o.to_fixed(np.abs(np.random.default_rng(5).standard_normal(d)) + 0.5, FA)
+    gain_h = qk.register_i64(gain)
+    xn = (h0 * 37).astype(np.int64) << shift
+    assert int(np.abs(xn).max()) < 1 << 57
+    hn = o.rmsnorm_fixed(xn, FA, 1, gain)
+    ids_ref, gates_ref, moe_ref = onat.moe_block(router, o.Q4_K, gate, up, down, o.Q4_K, o.Q6_K, k, hn, d, eff, FA, FW)
+    out, ids, gates = layer.block(torch.from_numpy(xn).cuda(), gain_h, FA, FW, 1)
+    torch.cuda.synchronize()
+    assert device.read_flags() == 0
+    assert np.array_equal(ids.cpu().numpy(), ids_ref) and np.array_equal(gates.cpu().numpy(), gates_ref)
+    assert np.array_equal(out.cpu().numpy(), xn + moe_ref)
+    qk.free_all()
+
+
 @pytest.mark.parametrize("d,eff,E,k,T", [(512, 256, 8, 2, 40), (2048, 768, 16, 4, 150), (256, 256, 4, 2, 300)])
 def test_device_moe_prefill_tensor_core_path(qk, d, eff, E, k, T):
     """From a set token count on (lowered to 32 here) the block runs on the tcgen05 grouped GEMMs (router GEMM, dispatch, gate/up with
