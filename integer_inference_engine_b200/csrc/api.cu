@@ -990,7 +990,7 @@ bool attn_scratch(AttnArgs &a, cudaStream_t s) {
     static int last_h = 0, last_hd = 0;
     a.scores = (int64_t *)ensure(R_ASCORES, (size_t)a.H * a.Lmax * 8);
     a.e = (int32_t *)ensure(R_AEXP, (size_t)a.H * a.Lmax * 4);
-    uint8_t *st = (uint8_t *)ensure(R_ASTAT, (size_t)a.H * 16 + (size_t)a.H * a.hd * 8 + 64);
+    uint8_t *st = (uint8_t *)ensure(R_ASTAT, (size_t)a.H * 16 + (size_t)a.H * a.hd * 8 + 2048);     // + the ticket and 256 barrier counters
     // per-chunk partial sums: 64-key chunks, or one chunk per SM of a KV head (at most 192 chunks on any device this targets)
     a.partial = (long long *)ensure(R_APART, (size_t)std::max<long long>((a.Lmax + 63) / 64, 192) * a.H * a.hd * 8);
     if (!a.scores || !a.e || !st || !a.partial) return false;

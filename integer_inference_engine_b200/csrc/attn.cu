@@ -26,6 +26,7 @@
 #include "kernels.h"
 #include "layout.cuh"
 #include "mma_items.cuh"
+#include "norm.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -90,7 +91,7 @@ __device__ __forceinline__ void at_stage(const int4 *src, int n, int tid, int nt
 __global__ void attn_reset_kernel(long long *hmax, unsigned long long *Z, long long *acc, unsigned *ticket, int H, int hd) {
     for (int i = threadIdx.x; i < H; i += blockDim.x) { hmax[i] = INT64_MIN; Z[i] = 0ULL; }
     for (int i = threadIdx.x; i < H * hd; i += blockDim.x) acc[i] = 0;
-    if (threadIdx.x == 0) *ticket = 0u;
+    for (int i = threadIdx.x; i < 257; i += blockDim.x) ticket[i] = 0u;        // the ticket and the per-KV-head barrier counters
 }
 
 // pass 1: scores of AT_CH keys for the `rep` query heads of one KV head; the keys are staged in shared memory and
@@ -655,21 +656,45 @@ __device__ __forceinline__ void af_mma(int (&c)[4], const uint32_t (&a)[4], uint
                      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Barrier among the CTAs of one KV head (the row maximum and the normaliser are per head, so nothing wider is needed): a
+// counter that only grows within a launch, `target` arrivals open it.  The launch is cooperative, so every CTA is resident;
+// the wait is bounded all the same and reports a give-up instead of spinning on.  The last CTA of the launch zeroes the counter.
+__device__ __forceinline__ bool af_group_barrier(unsigned *counter, unsigned target) {
+    __shared__ int s_open;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(counter, 1u);
+        unsigned seen = 0;
+        for (int spin = 0; spin < (1 << 22); spin++) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+            if (seen >= target) break;
+        }
+        s_open = seen >= target ? 1 : 0;
+    }
+    __syncthreads();
+    return s_open != 0;
+}
+
 __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs a_in) {
     AttnArgs a = a_in;
     if (!at_span(a_in, a.pos, a.lo)) { at_refuse(a_in); return; }          // uniform over the grid
-    cg::grid_group grid = cg::this_grid();
     extern __shared__ __align__(16) unsigned char af_smem[];
     __shared__ long long s_max[AF_HEADS];
     __shared__ unsigned long long s_z[AF_HEADS];
     __shared__ int s_wide, s_timeout, s_last, s_nl_out;
     __shared__ __align__(8) uint64_t bars[2];
-    const int C = a.chunk, hd = a.hd, ld = hd + 4, rep = a.H / a.Hkv, kv = blockIdx.y;
+    const int C = a.chunk, hd = a.hd, rep = a.H / a.Hkv, kv = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, half = hd / 2;
     const int KQ = AF_THREADS / hd;                                         // key groups of the probability x value pass
-    int32_t *sk = reinterpret_cast<int32_t *>(af_smem);                     // keys [C][hd + 4]
-    int32_t *sv = sk + (size_t)C * ld;                                      // values [C][hd + 4]
-    int32_t *q32 = sv + (size_t)C * ld;                                     // rotated queries [8][hd] (rows beyond rep are zero)
+    // Key and value rows lie in groups of eight consecutive rows, as in the cache, so one bulk copy brings a group; a gap
+    // after every group (16 words for keys, 8 for values) spreads the rows that one shared-memory read touches over the banks:
+    // a key read takes rows of two neighbouring groups per quarter warp, a value read rows of four groups per warp.
+    auto koff = [hd](int r) { return (size_t)r * hd + (size_t)(r >> 3) * 16; };
+    auto voff = [hd](int r) { return (size_t)r * hd + (size_t)(r >> 3) * 8; };
+    int32_t *sk = reinterpret_cast<int32_t *>(af_smem);                     // keys, C rows
+    int32_t *sv = sk + koff(C);                                             // values, C rows
+    int32_t *q32 = sv + voff(C);                                            // rotated queries [8][hd] (rows beyond rep are zero)
     long long *q64 = reinterpret_cast<long long *>(q32 + AF_HEADS * hd);    // the same as int64
     unsigned *s_e = reinterpret_cast<unsigned *>(q64 + AF_HEADS * hd);      // exponentials, then probabilities [C][8]
     long long *red = reinterpret_cast<long long *>(s_e + (size_t)C * AF_HEADS);   // [KQ][8][hd] partial sums of pass 3; before that the
@@ -694,10 +719,11 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     if (tid < AF_HEADS) { s_max[tid] = INT64_MIN; s_z[tid] = 0ULL; }
     __syncthreads();
     // rows below the new position were written by earlier steps: requested before the dependency wait
-    for (int r = tid; r < nk_old; r += AF_THREADS)
-        af_copy(sk + (size_t)r * ld, a.kcache + ((long long)kv * a.Lmax + l0 + r) * hd, (uint32_t)(hd * 4), &bars[0]);
-    for (int r = tid - AF_THREADS / 2; r >= 0 && r < nk_old; r += AF_THREADS)     // the upper half of the CTA asks for the value rows
-        af_copy(sv + (size_t)r * ld, a.vcache + ((long long)kv * a.Lmax + l0 + r) * hd, (uint32_t)(hd * 4), &bars[1]);
+    // (one copy per group of eight rows: the copy unit takes a dozen clocks per request, whatever its size)
+    for (int r = 8 * tid; r < nk_old; r += 8 * AF_THREADS)
+        af_copy(sk + koff(r), a.kcache + ((long long)kv * a.Lmax + l0 + r) * hd, (uint32_t)(min(8, nk_old - r) * hd * 4), &bars[0]);
+    for (int r = 8 * (tid - AF_THREADS / 2); r >= 0 && r < nk_old; r += 8 * AF_THREADS)   // the upper half of the CTA asks for the value rows
+        af_copy(sv + voff(r), a.vcache + ((long long)kv * a.Lmax + l0 + r) * hd, (uint32_t)(min(8, nk_old - r) * hd * 4), &bars[1]);
     if (a.pdl) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
     // ---- rotated queries ------------------------------------------------------------------------------------------------
     bool wide = false;
@@ -729,13 +755,13 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
             bad |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
             int32_t *dst = a.kcache + ((long long)kv * a.Lmax + a.pos) * hd;
             dst[i0] = (int32_t)x0; dst[i1] = (int32_t)x1;
-            sk[(size_t)(nk - 1) * ld + i0] = (int32_t)x0; sk[(size_t)(nk - 1) * ld + i1] = (int32_t)x1;
+            sk[koff(nk - 1) + i0] = (int32_t)x0; sk[koff(nk - 1) + i1] = (int32_t)x1;
         }
         for (int i = tid; i < hd; i += AF_THREADS) {
             const int64_t v = a.v[kv * hd + i];
             bad |= v != (int32_t)v;
             a.vcache[((long long)kv * a.Lmax + a.pos) * hd + i] = (int32_t)v;
-            sv[(size_t)(nk - 1) * ld + i] = (int32_t)v;
+            sv[voff(nk - 1) + i] = (int32_t)v;
         }
         if (bad) atomicOr(a.flags, 4);
     }
@@ -757,7 +783,10 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
 #pragma unroll
             for (int i = 0; i < 7; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0; }
             const int g = lane >> 2, t = lane & 3;
-            const int32_t *rowA = sk + (size_t)(kt * 16 + g) * ld, *rowB = rowA + 8 * ld;
+            // fragment row g is key (g & 1) * 8 + (g >> 1) of the tile and row g + 8 the key four further on: the two rows
+            // of a quarter warp then lie in neighbouring groups, half the banks apart
+            const int keyA = kt * 16 + (g & 1) * 8 + (g >> 1);
+            const int32_t *rowA = sk + koff(keyA), *rowB = rowA + 4 * hd;
             for (int st = s_lo; st < s_hi; st++) {
                 uint32_t A[4][4];
                 af_bytes(*reinterpret_cast<const int4 *>(rowA + 32 * st + 4 * t), A[0][0], A[1][0], A[2][0], A[3][0]);
@@ -782,7 +811,7 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
                 long long dot = 0;
 #pragma unroll
                 for (int w = 6; w >= 0; w--) dot = dot * 256 + (long long)acc[w][i];
-                const int row = kt * 16 + g + (i >= 2 ? 8 : 0), col = 2 * t + (i & 1);
+                const int row = keyA + (i >= 2 ? 4 : 0), col = 2 * t + (i & 1);
                 dots[((size_t)kh * C + row) * AF_HEADS + col] = dot;
             }
         }
@@ -792,7 +821,7 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
             const int key = i >> 3, h = i & 7;
             long long dot = 0;
             if (h < rep) {
-                const int32_t *kk = sk + (size_t)key * ld;
+                const int32_t *kk = sk + koff(key);
                 for (int j = 0; j < hd; j++) dot += q64[h * hd + j] * (long long)kk[j];
             }
             dots[i] = dot;
@@ -818,7 +847,7 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     if (lane < 8 && mloc != INT64_MIN) atomicMax(&s_max[head], mloc);
     __syncthreads();
     if (tid < rep && s_max[tid] != INT64_MIN) atomicMax(a.hmax + kv * rep + tid, s_max[tid]);
-    grid.sync();
+    if (!af_group_barrier(a.ticket + 1 + kv, gridDim.x)) s_timeout = 1;
     // ---- pass 2: exponentials into shared memory and their sums ------------------------------------------------------------
     unsigned long long zloc = 0ULL;
     const long long hm = head < rep ? __ldcg(a.hmax + kv * rep + head) : 0;
@@ -840,23 +869,32 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     if (lane < 8 && zloc) atomicAdd(&s_z[head], zloc);
     __syncthreads();
     if (tid < rep && s_z[tid]) atomicAdd(a.Z + kv * rep + tid, s_z[tid]);
-    grid.sync();
+    if (!af_group_barrier(a.ticket + 1 + kv, 2u * gridDim.x)) s_timeout = 1;
     // ---- pass 3: probabilities as byte planes, then probabilities x values on the tensor cores ---------------------------
     //      out[head][dim] = sum over keys p[key][head] v[key][dim]: A = bytes of p (heads x keys; p <= 2^fa has three unsigned
     //      bytes), B = bytes of v gathered from four key rows (keys x dims), a warp owns eight dimensions for all keys
     const int nk32 = (nk + 31) & ~31;
+    // a thread's pairs all belong to head tid % 8: one reciprocal of that head's normaliser, then floor(e 2^fa / z) per pair
+    // as a high product with an exact fix-up instead of a 64-bit division each
+    const unsigned long long z_own = head < rep ? __ldcg(a.Z + kv * rep + head) : 0ULL;
+    const unsigned long long z_inv = recip_below(z_own);
     for (int idx = tid; idx < nk32 * AF_HEADS; idx += AF_THREADS) {
         const int key = idx >> 3, h = idx & (AF_HEADS - 1);
         unsigned p = 0;
-        if (key < nk && h < rep) {
-            const unsigned long long z = __ldcg(a.Z + kv * rep + h);
-            p = z ? (unsigned)(((unsigned long long)s_e[idx] << a.fa) / z) : 0u;
+        if (key < nk && z_own) {
+            const unsigned long long n = (unsigned long long)s_e[idx] << a.fa;
+            unsigned long long q = __umul64hi(n, z_inv), r = n - q * z_own;
+            while (r >= z_own) { q++; r -= z_own; }
+            p = (unsigned)q;
         }
+        // position of the key inside its 32-key step: keys 8t + 4u + j sit at 16u + 4t + j, so that the four rows a lane
+        // gathers for one step come from four different groups of the value rows
+        const int kpos = (key & ~31) | ((key & 4) << 2) | ((key & 24) >> 1) | (key & 3);
 #pragma unroll
-        for (int b = 0; b < 3; b++) pT[(b * AF_HEADS + h) * pld + key] = (uint8_t)(p >> (8 * b));
+        for (int b = 0; b < 3; b++) pT[(b * AF_HEADS + h) * pld + kpos] = (uint8_t)(p >> (8 * b));
     }
     // value rows beyond the chunk's keys multiply zero probabilities but must hold numbers: clear them
-    for (int i = tid; i < (nk32 - nk) * hd; i += AF_THREADS) sv[(size_t)(nk + i / hd) * ld + (i % hd)] = 0;
+    for (int i = tid; i < (nk32 - nk) * hd; i += AF_THREADS) sv[voff(nk + i / hd) + (i % hd)] = 0;
     if (!af_wait(&bars[1])) s_timeout = 1;
     __syncthreads();
     long long *accum = a.acc + (long long)kv * rep * hd;                                  // the [rep][hd] sums of this KV head, shared by its chunks
@@ -868,9 +906,9 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
             for (int i = 0; i < 6; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0; }
             for (int st = 0; st < nk32 / 32; st++) {
                 uint32_t B0[4], B1[4];
-                const int32_t *vb = sv + (size_t)(32 * st + 4 * t) * ld + nt * 8 + g;
-                af_bytes(make_int4(vb[0], vb[ld], vb[2 * ld], vb[3 * ld]), B0[0], B0[1], B0[2], B0[3]);
-                af_bytes(make_int4(vb[16 * ld], vb[17 * ld], vb[18 * ld], vb[19 * ld]), B1[0], B1[1], B1[2], B1[3]);
+                const int32_t *vb = sv + voff(32 * st + 8 * t) + nt * 8 + g;          // positions 4t + j and 16 + 4t + j: keys 8t + j, 8t + 4 + j
+                af_bytes(make_int4(vb[0], vb[hd], vb[2 * hd], vb[3 * hd]), B0[0], B0[1], B0[2], B0[3]);
+                af_bytes(make_int4(vb[4 * hd], vb[5 * hd], vb[6 * hd], vb[7 * hd]), B1[0], B1[1], B1[2], B1[3]);
 #pragma unroll
                 for (int pa = 0; pa < 3; pa++) {
                     const uint8_t *pp = pT + (pa * AF_HEADS + g) * pld + 32 * st + 4 * t;
@@ -902,38 +940,65 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     if (s_timeout && tid == 0) atomicOr(a.flags, 8);
     if (!s_last) return;
     __threadfence();
-    const long long n = (long long)a.H * hd;
+    const long long n = (long long)a.H * hd;                                // a multiple of 32
     int nl = 1;
     bool over = false;
-    for (long long i0 = 0; i0 < n; i0 += (long long)AF_THREADS * 8) {
-        long long yv[8];
+    const bool word_planes = (reinterpret_cast<uintptr_t>(a.out_limbs) & 3) == 0;
+    for (long long i0 = 0; i0 < n; i0 += (long long)AF_THREADS * 8) {       // four consecutive outputs per thread and turn, two turns in flight
+        longlong2 yv[2][2];
 #pragma unroll
-        for (int u = 0; u < 8; u++) {                                       // all eight loads in flight before any is used
-            const long long i = i0 + (long long)u * AF_THREADS + tid;
-            yv[u] = i < n ? __ldcg(a.acc + i) : 0;
+        for (int u = 0; u < 2; u++) {
+            const long long i = i0 + ((long long)u * AF_THREADS + tid) * 4;
+            yv[u][0] = yv[u][1] = make_longlong2(0, 0);
+            if (i < n) {
+                yv[u][0] = __ldcg(reinterpret_cast<const longlong2 *>(a.acc + i));
+                yv[u][1] = __ldcg(reinterpret_cast<const longlong2 *>(a.acc + i + 2));
+            }
         }
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-            const long long i = i0 + (long long)u * AF_THREADS + tid;
+        for (int u = 0; u < 2; u++) {
+            const long long i = i0 + ((long long)u * AF_THREADS + tid) * 4;
             if (i >= n) continue;
-            const long long y = yv[u] >> a.fa;
-            if (a.out) a.out[i] = y;
+            const long long y[4] = {yv[u][0].x >> a.fa, yv[u][0].y >> a.fa, yv[u][1].x >> a.fa, yv[u][1].y >> a.fa};
+            if (a.out) { a.out[i] = y[0]; a.out[i + 1] = y[1]; a.out[i + 2] = y[2]; a.out[i + 3] = y[3]; }
             if (a.out_limbs) {
-                bool ok;
-                const uint64_t dg = balanced_digits8(y, ok);
-                over |= !ok;
-                nl = max(nl, digits_used(dg));
+                uint64_t dg[4];
 #pragma unroll
-                for (int l = 0; l < 8; l++) a.out_limbs[l * n + i] = (int8_t)(dg >> (8 * l));
+                for (int e = 0; e < 4; e++) {
+                    bool ok;
+                    dg[e] = balanced_digits8(y[e], ok);
+                    over |= !ok;
+                    nl = max(nl, digits_used(dg[e]));
+                }
+                uint32_t pw[8];                                              // word l = digit l of the four outputs (a byte transpose)
+#pragma unroll
+                for (int hw = 0; hw < 2; hw++) {
+                    const uint32_t w0 = (uint32_t)(dg[0] >> (32 * hw)), w1 = (uint32_t)(dg[1] >> (32 * hw));
+                    const uint32_t w2 = (uint32_t)(dg[2] >> (32 * hw)), w3 = (uint32_t)(dg[3] >> (32 * hw));
+                    const uint32_t lo01 = __byte_perm(w0, w1, 0x5140), hi01 = __byte_perm(w0, w1, 0x7362);
+                    const uint32_t lo23 = __byte_perm(w2, w3, 0x5140), hi23 = __byte_perm(w2, w3, 0x7362);
+                    pw[4 * hw + 0] = __byte_perm(lo01, lo23, 0x5410); pw[4 * hw + 1] = __byte_perm(lo01, lo23, 0x7632);
+                    pw[4 * hw + 2] = __byte_perm(hi01, hi23, 0x5410); pw[4 * hw + 3] = __byte_perm(hi01, hi23, 0x7632);
+                }
+                if (word_planes) {
+#pragma unroll
+                    for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(a.out_limbs + l * n + i) = pw[l];
+                } else {
+#pragma unroll
+                    for (int l = 0; l < 8; l++)
+                        for (int e = 0; e < 4; e++) a.out_limbs[l * n + i + e] = (int8_t)(pw[l] >> (8 * e));
+                }
             }
-            a.acc[i] = 0;
+            *reinterpret_cast<longlong2 *>(a.acc + i) = make_longlong2(0, 0);
+            *reinterpret_cast<longlong2 *>(a.acc + i + 2) = make_longlong2(0, 0);
         }
     }
     if (over) atomicOr(a.flags, 1);
     if (a.out_limbs) atomicMax(&s_nl_out, nl);
     for (int i = tid; i < a.H; i += AF_THREADS) { a.hmax[i] = INT64_MIN; a.Z[i] = 0ULL; }
     __syncthreads();
-    if (tid == 0) { *a.ticket = 0u; if (a.out_nl) *a.out_nl = s_nl_out; }
+    if (tid <= (int)gridDim.y) a.ticket[tid] = 0u;                          // the ticket and the barrier counter of every KV head
+    if (tid == 0 && a.out_nl) *a.out_nl = s_nl_out;
 }
 
 // ---- several tokens at once (a prefill chunk, or the new tokens of independent sequences): the scores on the tensor cores,
@@ -1272,7 +1337,7 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
         int C = (int)((n_keys + per_head - 1) / per_head);
         C = std::max(32, (C + 31) / 32 * 32);                      // whole 32-key steps of the tensor-core passes
         const unsigned fat_chunks = (unsigned)((n_keys + C - 1) / C);
-        const size_t fat_smem = (size_t)2 * C * (a.hd + 4) * 4 + (size_t)AF_HEADS * a.hd * 12 + (size_t)C * AF_HEADS * 4 +
+        const size_t fat_smem = ((size_t)2 * C * a.hd + (size_t)C / 8 * 24) * 4 + (size_t)AF_HEADS * a.hd * 12 + (size_t)C * AF_HEADS * 4 +
                                 (size_t)AF_THREADS / a.hd * AF_HEADS * a.hd * 8 + (size_t)4 * AF_HEADS * (a.hd + 16) + (size_t)3 * AF_HEADS * (C + 16);
         int per_sm = 0;
         if (C <= 2 * 8 * (AF_THREADS / 32) && fat_smem <= 208 * 1024 &&
