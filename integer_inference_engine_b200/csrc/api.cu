@@ -83,7 +83,7 @@ bool init() {
     if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) { cudaGetLastError(); g_ready = 1; return false; }
     if (cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaMalloc(&g_flags, sizeof(int)) != cudaSuccess || cudaMemset(g_flags, 0, sizeof(int)) != cudaSuccess ||
-        cudaMalloc(&g_cells, 64) != cudaSuccess || cudaMemset(g_cells, 0, 64) != cudaSuccess ||
+        cudaMalloc(&g_cells, 2048) != cudaSuccess || cudaMemset(g_cells, 0, 2048) != cudaSuccess ||
         cudaMalloc(&g_selptr, 3 * 64 * sizeof(void *)) != cudaSuccess || cudaMalloc(&g_pow2, 32 * sizeof(int64_t)) != cudaSuccess) {
         cudaGetLastError(); g_ready = 1; return false;
     }
@@ -1556,14 +1556,14 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
     a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim;
     attn_consts(a, fa, inv_sqrt);
     if (!attn_scratch(a, s)) return 1;
-    int *nl_cell = g_cells + 8 + g_attn_parity;              // alternate between calls
+    int *nl_cell = g_cells + 16 + 128 * g_attn_parity;        // one count per KV head; alternate between calls
     g_attn_parity ^= 1;
     a.out = nullptr; a.out_limbs = al; a.out_nl = nl_cell; a.flags = g_flags; a.pdl = g_pdl;
     if (launch_attn_decode(a, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     // O product accumulated into the residual row: the "down" form of the streaming kernel with a unit gate
     StreamArgs oa = {};
     oa.wa = wo.cell; oa.wb = wo.cell; oa.n_sel = 1; oa.out_f = wo.out_f; oa.n_blocks = wo.nb; oa.fw = fw; oa.fa = fa;
-    oa.xl = al; oa.x_per_sel = 1; oa.x_nl = nl_cell; oa.out = x_dev; oa.gates = g_pow2 + fa; oa.flags = g_flags;
+    oa.xl = al; oa.x_per_sel = 1; oa.x_nl = nl_cell; oa.x_nl_n = n_kv <= 120 ? n_kv : 1; oa.out = x_dev; oa.gates = g_pow2 + fa; oa.flags = g_flags;
     oa.fast = small_scales(wo.maxd, wo.maxdmin, fw); oa.pdl = g_pdl; oa.early_weights = g_pdl;
     if (launch_stream(wo.qtype, MODE_DOWN, oa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     return 0;
@@ -1623,13 +1623,13 @@ extern "C" int iie_block_dev(long long layer, long long gain_h, long long wqkv_h
     a.cos = cos_dev; a.sin = sin_dev; a.rope = rope; a.H = n_heads; a.Hkv = n_kv; a.hd = head_dim;
     attn_consts(a, fa, inv_sqrt);
     if (!attn_scratch(a, s)) return 1;
-    int *nl_cell = g_cells + 8 + g_attn_parity;
+    int *nl_cell = g_cells + 16 + 128 * g_attn_parity;
     g_attn_parity ^= 1;
     a.out = nullptr; a.out_limbs = al; a.out_nl = nl_cell; a.flags = g_flags; a.pdl = g_pdl;
     if (launch_attn_decode(a, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     StreamArgs oa = {};
     oa.wa = wo.cell; oa.wb = wo.cell; oa.n_sel = 1; oa.out_f = wo.out_f; oa.n_blocks = wo.nb; oa.fw = fw; oa.fa = fa;
-    oa.xl = al; oa.x_per_sel = 1; oa.x_nl = nl_cell; oa.out = x_dev; oa.gates = g_pow2 + fa; oa.flags = g_flags;
+    oa.xl = al; oa.x_per_sel = 1; oa.x_nl = nl_cell; oa.x_nl_n = n_kv <= 120 ? n_kv : 1; oa.out = x_dev; oa.gates = g_pow2 + fa; oa.flags = g_flags;
     oa.fast = small_scales(wo.maxd, wo.maxdmin, fw); oa.pdl = g_pdl; oa.early_weights = g_pdl;
     if (launch_stream(wo.qtype, MODE_DOWN, oa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     StreamArgs ga = {};

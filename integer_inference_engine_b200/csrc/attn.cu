@@ -718,12 +718,10 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
     }
     if (tid < AF_HEADS) { s_max[tid] = INT64_MIN; s_z[tid] = 0ULL; }
     __syncthreads();
-    // rows below the new position were written by earlier steps: requested before the dependency wait
+    // key rows below the new position were written by earlier steps: requested before the dependency wait
     // (one copy per group of eight rows: the copy unit takes a dozen clocks per request, whatever its size)
     for (int r = 8 * tid; r < nk_old; r += 8 * AF_THREADS)
         af_copy(sk + koff(r), a.kcache + ((long long)kv * a.Lmax + l0 + r) * hd, (uint32_t)(min(8, nk_old - r) * hd * 4), &bars[0]);
-    for (int r = 8 * (tid - AF_THREADS / 2); r >= 0 && r < nk_old; r += 8 * AF_THREADS)   // the upper half of the CTA asks for the value rows
-        af_copy(sv + voff(r), a.vcache + ((long long)kv * a.Lmax + l0 + r) * hd, (uint32_t)(min(8, nk_old - r) * hd * 4), &bars[1]);
     if (a.pdl) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;"); }
     // ---- rotated queries ------------------------------------------------------------------------------------------------
     bool wide = false;
@@ -745,6 +743,10 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
         }
         wide |= x0 != (int32_t)x0 || x1 != (int32_t)x1;
     }
+    // the value rows are asked for once the key rows have had the memory system to themselves for a while (they are needed
+    // only after two barriers)
+    for (int r = 8 * (tid - AF_THREADS / 2); r >= 0 && r < nk_old; r += 8 * AF_THREADS)   // the upper half of the CTA asks for the value rows
+        af_copy(sv + voff(r), a.vcache + ((long long)kv * a.Lmax + l0 + r) * hd, (uint32_t)(min(8, nk_old - r) * hd * 4), &bars[1]);
     if (wide) s_wide = 1;
     if (own) {                                                              // the new token's row: cache and shared memory
         bool bad = false;
@@ -930,75 +932,70 @@ __global__ void __launch_bounds__(AF_THREADS, 1) attn_fat_kernel(const AttnArgs 
             }
         }
     }
-    // ---- the chunk sums were added into one accumulator per output (integer adds are order-free); the CTA that arrives last
-    //      (a counter, no waiting) shifts, writes the result and its digit planes and returns the statistics to their
-    //      initial state, which spares a third grid-wide barrier and a reduction over the chunks
+    // ---- the chunk sums were added into one accumulator per output (integer adds are order-free); of every KV head the CTA
+    //      that arrives last (a counter, no waiting) shifts its heads' sums, writes them and their digit planes, leaves the
+    //      digit count of its part in out_nl[kv] and returns the statistics and counters of the head to their initial state.
+    //      That spares a third barrier and a reduction over the chunks, and the four read-outs run side by side.
     __threadfence();
     __syncthreads();
-    if (tid == 0) { s_last = atomicAdd(a.ticket, 1u) == gridDim.x * gridDim.y - 1 ? 1 : 0; s_nl_out = 1; }
+    if (tid == 0) {
+        const bool last = atomicAdd(a.ticket + 1 + gridDim.y + kv, 1u) == gridDim.x - 1;
+        if (last) __threadfence();
+        s_last = last ? 1 : 0; s_nl_out = 1;
+    }
     __syncthreads();
     if (s_timeout && tid == 0) atomicOr(a.flags, 8);
     if (!s_last) return;
-    __threadfence();
-    const long long n = (long long)a.H * hd;                                // a multiple of 32
+    const long long n = (long long)a.H * hd, base = (long long)kv * rep * hd;      // plane stride; this head's first output
+    const int cnt = rep * hd;                                               // a multiple of 32
     int nl = 1;
     bool over = false;
     const bool word_planes = (reinterpret_cast<uintptr_t>(a.out_limbs) & 3) == 0;
-    for (long long i0 = 0; i0 < n; i0 += (long long)AF_THREADS * 8) {       // four consecutive outputs per thread and turn, two turns in flight
-        longlong2 yv[2][2];
+    for (int q = tid * 4; q < cnt; q += AF_THREADS * 4) {                   // four consecutive outputs per thread and turn
+        const long long i = base + q;
+        const longlong2 v0 = __ldcg(reinterpret_cast<const longlong2 *>(a.acc + i));
+        const longlong2 v1 = __ldcg(reinterpret_cast<const longlong2 *>(a.acc + i + 2));
+        const long long y[4] = {v0.x >> a.fa, v0.y >> a.fa, v1.x >> a.fa, v1.y >> a.fa};
+        if (a.out) { a.out[i] = y[0]; a.out[i + 1] = y[1]; a.out[i + 2] = y[2]; a.out[i + 3] = y[3]; }
+        if (a.out_limbs) {
+            uint64_t dg[4];
 #pragma unroll
-        for (int u = 0; u < 2; u++) {
-            const long long i = i0 + ((long long)u * AF_THREADS + tid) * 4;
-            yv[u][0] = yv[u][1] = make_longlong2(0, 0);
-            if (i < n) {
-                yv[u][0] = __ldcg(reinterpret_cast<const longlong2 *>(a.acc + i));
-                yv[u][1] = __ldcg(reinterpret_cast<const longlong2 *>(a.acc + i + 2));
+            for (int e = 0; e < 4; e++) {
+                bool ok;
+                dg[e] = balanced_digits8(y[e], ok);
+                over |= !ok;
+                nl = max(nl, digits_used(dg[e]));
+            }
+            uint32_t pw[8];                                                  // word l = digit l of the four outputs (a byte transpose)
+#pragma unroll
+            for (int hw = 0; hw < 2; hw++) {
+                const uint32_t w0 = (uint32_t)(dg[0] >> (32 * hw)), w1 = (uint32_t)(dg[1] >> (32 * hw));
+                const uint32_t w2 = (uint32_t)(dg[2] >> (32 * hw)), w3 = (uint32_t)(dg[3] >> (32 * hw));
+                const uint32_t lo01 = __byte_perm(w0, w1, 0x5140), hi01 = __byte_perm(w0, w1, 0x7362);
+                const uint32_t lo23 = __byte_perm(w2, w3, 0x5140), hi23 = __byte_perm(w2, w3, 0x7362);
+                pw[4 * hw + 0] = __byte_perm(lo01, lo23, 0x5410); pw[4 * hw + 1] = __byte_perm(lo01, lo23, 0x7632);
+                pw[4 * hw + 2] = __byte_perm(hi01, hi23, 0x5410); pw[4 * hw + 3] = __byte_perm(hi01, hi23, 0x7632);
+            }
+            if (word_planes) {
+#pragma unroll
+                for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(a.out_limbs + l * n + i) = pw[l];
+            } else {
+#pragma unroll
+                for (int l = 0; l < 8; l++)
+                    for (int e = 0; e < 4; e++) a.out_limbs[l * n + i + e] = (int8_t)(pw[l] >> (8 * e));
             }
         }
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-            const long long i = i0 + ((long long)u * AF_THREADS + tid) * 4;
-            if (i >= n) continue;
-            const long long y[4] = {yv[u][0].x >> a.fa, yv[u][0].y >> a.fa, yv[u][1].x >> a.fa, yv[u][1].y >> a.fa};
-            if (a.out) { a.out[i] = y[0]; a.out[i + 1] = y[1]; a.out[i + 2] = y[2]; a.out[i + 3] = y[3]; }
-            if (a.out_limbs) {
-                uint64_t dg[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    bool ok;
-                    dg[e] = balanced_digits8(y[e], ok);
-                    over |= !ok;
-                    nl = max(nl, digits_used(dg[e]));
-                }
-                uint32_t pw[8];                                              // word l = digit l of the four outputs (a byte transpose)
-#pragma unroll
-                for (int hw = 0; hw < 2; hw++) {
-                    const uint32_t w0 = (uint32_t)(dg[0] >> (32 * hw)), w1 = (uint32_t)(dg[1] >> (32 * hw));
-                    const uint32_t w2 = (uint32_t)(dg[2] >> (32 * hw)), w3 = (uint32_t)(dg[3] >> (32 * hw));
-                    const uint32_t lo01 = __byte_perm(w0, w1, 0x5140), hi01 = __byte_perm(w0, w1, 0x7362);
-                    const uint32_t lo23 = __byte_perm(w2, w3, 0x5140), hi23 = __byte_perm(w2, w3, 0x7362);
-                    pw[4 * hw + 0] = __byte_perm(lo01, lo23, 0x5410); pw[4 * hw + 1] = __byte_perm(lo01, lo23, 0x7632);
-                    pw[4 * hw + 2] = __byte_perm(hi01, hi23, 0x5410); pw[4 * hw + 3] = __byte_perm(hi01, hi23, 0x7632);
-                }
-                if (word_planes) {
-#pragma unroll
-                    for (int l = 0; l < 8; l++) *reinterpret_cast<uint32_t *>(a.out_limbs + l * n + i) = pw[l];
-                } else {
-#pragma unroll
-                    for (int l = 0; l < 8; l++)
-                        for (int e = 0; e < 4; e++) a.out_limbs[l * n + i + e] = (int8_t)(pw[l] >> (8 * e));
-                }
-            }
-            *reinterpret_cast<longlong2 *>(a.acc + i) = make_longlong2(0, 0);
-            *reinterpret_cast<longlong2 *>(a.acc + i + 2) = make_longlong2(0, 0);
-        }
+        *reinterpret_cast<longlong2 *>(a.acc + i) = make_longlong2(0, 0);
+        *reinterpret_cast<longlong2 *>(a.acc + i + 2) = make_longlong2(0, 0);
     }
     if (over) atomicOr(a.flags, 1);
     if (a.out_limbs) atomicMax(&s_nl_out, nl);
-    for (int i = tid; i < a.H; i += AF_THREADS) { a.hmax[i] = INT64_MIN; a.Z[i] = 0ULL; }
+    if (tid < rep) { a.hmax[kv * rep + tid] = INT64_MIN; a.Z[kv * rep + tid] = 0ULL; }
     __syncthreads();
-    if (tid <= (int)gridDim.y) a.ticket[tid] = 0u;                          // the ticket and the barrier counter of every KV head
-    if (tid == 0 && a.out_nl) *a.out_nl = s_nl_out;
+    if (tid == 0) {
+        a.ticket[1 + kv] = 0u; a.ticket[1 + gridDim.y + kv] = 0u;          // this head's barrier counter and its ticket
+        if (a.out_nl) a.out_nl[kv] = s_nl_out;
+    }
 }
 
 // ---- several tokens at once (a prefill chunk, or the new tokens of independent sequences): the scores on the tensor cores,
@@ -1327,7 +1324,7 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t s) {
     }
     // one CTA per SM where a KV head's keys, cut into n_sms / Hkv chunks, fit the shared memory of a CTA
     if (g_attn_fused == 1 && a.partial && n_sms > 0 && !a.batch && rep <= AF_HEADS && AF_THREADS % a.hd == 0 && a.hd % 32 == 0 &&
-        a.fa <= 23) {                                       // probabilities (at most 2^fa) as three bytes
+        a.fa <= 23 && a.Hkv <= 120) {                                       // probabilities (at most 2^fa) as three bytes
         static bool fat_configured = false;
         if (!fat_configured) {
             if (cudaFuncSetAttribute(attn_fat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024) != cudaSuccess) return cudaGetLastError();

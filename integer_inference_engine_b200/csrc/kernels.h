@@ -54,6 +54,7 @@ struct StreamArgs {
     const int8_t *xl;              // limb planes [8][K] (shared) or [n_sel][8][K]
     int x_per_sel;
     const int *x_nl;               // device: limbs in use by x (<= 4 enables the half-column path), or nullptr
+    int x_nl_n;                    // how many consecutive cells x_nl points at (their maximum counts; 0 or 1: one cell)
     int64_t *out;                  // LINEAR [n_sel][out_f]; GATEUP gu [n_sel][out_f] (nullable); DOWN [out_f] accumulated
     int8_t *out_limbs;             // GATEUP: limb planes of gu [n_sel][8][out_f]
     int *out_nl;                   // GATEUP: atomicMax of the limbs gu needs
@@ -229,7 +230,7 @@ struct AttnArgs {
     long long *partial;            // scratch [ceil(Lmax/64)][Hkv][H/Hkv][hd]: per-chunk partial sums of the one-launch form
     int64_t *out;                  // [H*hd], nullable
     int8_t *out_limbs;             // nullable: digit planes [8][H*hd] of the result
-    int *out_nl;                   // nullable: digits in use by the result
+    int *out_nl;                   // nullable: digits in use by the result (the one-CTA-per-SM decode form leaves one count per KV head: out_nl[kv])
     int pdl;                       // 1: the one-launch form is launched with programmatic stream serialization
     int *flags;                    // bit 0 digit envelope, bit 2 a key / value does not fit the int32 cache
     int batch;                     // > 0: that many consecutive new tokens (prefill); q, k, v, out then hold one row per token,

@@ -35,6 +35,11 @@
 namespace iie {
 
 unsigned long long g_prefill_launches[PF_SHAPES];
+__device__ long long d_tr[4200];
+__device__ int d_tr_block = -1;
+__device__ int d_tr_mode = 2;
+__device__ int d_pf_exp;
+#define TR(i) do { if (trace) d_tr[i] = clock64(); } while (0)
 
 namespace {
 
@@ -241,6 +246,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort, s_tile[3];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ex = d_pf_exp; (void)ex;
+    const bool tron = (int)blockIdx.x == d_tr_block && MODE == d_tr_mode;
+    const bool trace = tron && (tid & 127) == 0;
+    if (tid == 0) TR(4002);
     const int nb = (int)a.n_blocks, K = nb * 256, n_chunks = K / PF_KC;
 
     // ---- which tile: (expert, BN-pair slab, row slab) -------------------------------------------------
@@ -282,6 +291,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
+    if (tid == 0) TR(4003);
 
     if (warp < PF_GROUPS * 4) {
         // ================= producers: group g fills stage g for chunks g, g + 3, ... ======================
@@ -302,8 +312,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                 const int cn = c + PF_GROUPS;
                 load_q4k(wunit + (long long)(cn >> 2) * HTB, rr, cn & 3, raw_next);
             }
+            TR(c * 4 + 0);
             if (c >= STAGES && !pf_bar_wait(&empty_bar[s], ((c / STAGES) - 1) & 1, &s_abort)) break;
             uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
+            TR(c * 4 + 1);
             if (gtid == 0) {                                   // activations: NL planes x BN pairs x 64 columns, by the copy engine
                 pf_expect_tx(&full_bar[s], NL * X_PLANE);
 #pragma unroll
@@ -332,13 +344,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                     }
                 }
             }
+            TR(c * 4 + 2);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> visible to the MMA
             __syncwarp();
             if (lane == 0) pf_bar_arrive(&full_bar[s]);
+            TR(c * 4 + 3);
         }
 
         // ================= epilogue: TMEM lane = weight row, columns = pairs ================================
         if (pf_bar_wait(&accum_bar, 0, &s_abort)) {
+            if ((tid & 127) == 0) TR(4000 + 10 * (tid >> 7));
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
             int64_t *exch = reinterpret_cast<int64_t *>(smem) + group * 1024;     // gate/up: two buffers of [128 rows][4] per group (the stages are free now)
@@ -409,6 +424,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                 if (lane == 0 && nl_max > 0) atomicMax(a.out_nl, nl_max);
             }
         }
+        if ((tid & 127) == 0) TR(4001 + 10 * (tid >> 7));
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     } else {
         // ================= MMA issuers ===================================================================
@@ -423,6 +439,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                 const int s = c % STAGES;
                 ok = pf_bar_wait(&full_bar[s], (c / STAGES) & 1, &s_abort);
                 if (!ok) break;
+                if (warp == PF_GROUPS * 4 && tron) d_tr[2048 + c * 2] = clock64();
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t stage = pf_u32(smem + (size_t)s * STAGE_BYTES);
                 const uint64_t dw0 = pf_desc(stage, W_PLANE / 4, 128), dx0 = pf_desc_sw64(stage + NWL * W_PLANE);
@@ -448,6 +465,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                 if (issuer == 0) issue(std::integral_constant<int, 0>{});
                 else if (issuer == 1) issue(std::integral_constant<int, 1>{});
                 else issue(std::integral_constant<int, 2>{});
+                if (warp == PF_GROUPS * 4 && tron) d_tr[2048 + c * 2 + 1] = clock64();
                 pf_commit(&empty_bar[s]);                      // stage free once every issuer's MMAs have read it
             }
             if (ok) pf_commit(&accum_bar);                     // this issuer's MMAs done -> epilogue may read TMEM after all three
@@ -542,3 +560,6 @@ cudaError_t launch_prefill(int qtype, int mode, int nl, const PrefillArgs &a, cu
 }
 
 }  // namespace iie
+extern "C" void iie_pf_trace_block(int v, int mode) { cudaMemcpyToSymbol(iie::d_tr_block, &v, sizeof(int)); cudaMemcpyToSymbol(iie::d_tr_mode, &mode, sizeof(int)); }
+extern "C" void iie_pf_trace_read(long long *out) { cudaMemcpyFromSymbol(out, iie::d_tr, sizeof(long long) * 4200); }
+extern "C" void iie_pf_exp(int v) { cudaMemcpyToSymbol(iie::d_pf_exp, &v, sizeof(int)); }

@@ -307,7 +307,13 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
         __syncthreads();
         if (blockIdx.x == 0 && threadIdx.x == 0) { if (a.h_nl_out) *a.h_nl_out = s_nl; if (a.gu_nl_zero) *a.gu_nl_zero = 0; }
     }
-    const bool half = MODE == MODE_FRONT ? (s_nl <= 4) : (a.x_nl ? (*a.x_nl <= 4) : false);
+    int x_digits = 8;
+    if (MODE == MODE_FRONT) x_digits = s_nl;
+    else if (a.x_nl) {                                           // a producer may leave one count per part of the row
+        x_digits = a.x_nl[0];
+        for (int i = 1; i < a.x_nl_n; i++) x_digits = max(x_digits, a.x_nl[i]);
+    }
+    const bool half = x_digits <= 4;
 
     // items (tile, block) are dealt round-robin to the warps; indices advance without divisions
     const int n_items = my_tiles * nb;
