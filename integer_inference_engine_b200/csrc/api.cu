@@ -1614,6 +1614,8 @@ extern "C" int iie_block_dev(long long layer, long long gain_h, long long wqkv_h
     StreamArgs f = {};
     f.wa = wqkv.cell; f.wb = r.cell; f.n_sel = 1; f.out_f = wqkv.out_f; f.out_f_b = E; f.n_blocks = d / 256; f.fw = fw; f.fa = fa;
     f.x = x_dev; f.gain = gain; f.eps = eps; f.out = qkv; f.out_b = lg; f.hl_out = hl; f.h_nl_out = g_cells; f.gu_nl_zero = g_cells + 1;
+    f.pf_base = kcache_dev; f.pf_rows = cache_rows; f.pf_pos = pos; f.pf_window = window; f.pf_heads = n_kv;
+    f.pf_row_bytes = head_dim * 4; f.pf_pos_dev = pos_dev;      // the key rows attention asks for first: into L2 meanwhile
     f.flags = g_flags; f.pdl = g_pdl; f.early_weights = g_pdl;
     f.fast = small_scales(std::max(wqkv.maxd, r.maxd), std::max(wqkv.maxdmin, r.maxdmin), fw);
     if (launch_stream(wqkv.qtype, MODE_FRONT, f, s) != cudaSuccess) { cudaGetLastError(); return 1; }

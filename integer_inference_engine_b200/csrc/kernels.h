@@ -77,6 +77,12 @@ struct StreamArgs {
     int64_t *out_b;
     int8_t *hl_out;
     int *h_nl_out, *gu_nl_zero;
+    // optional: rows [lo, pos) of `pf_heads` row-major tables (the key cache of the attention kernel that follows) are
+    // prefetched into L2 while this kernel runs; lo from the window, pos = *pf_pos_dev (or pf_pos), refused beyond pf_pos
+    const void *pf_base;
+    long long pf_rows, pf_pos, pf_window;
+    int pf_heads, pf_row_bytes;
+    const int *pf_pos_dev;
     int tiles_b;                   // filled in by the launcher
 };
 cudaError_t launch_stream(int qtype, int mode, const StreamArgs &a, cudaStream_t s);

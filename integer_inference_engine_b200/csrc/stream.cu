@@ -154,6 +154,20 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
             bulk_g2s(dst, pa + (size_t)(2 * p) * nb * HTB, (uint32_t)(units * nb * HTB), &bars[i]);
         }
     }
+    if (MODE == MODE_FRONT && a.pf_base) {
+        // rows the next kernel will ask for first: written by earlier steps, so they can be on their way into L2 now
+        const long long pos = a.pf_pos_dev ? (long long)*a.pf_pos_dev : a.pf_pos;
+        if (pos > 0 && pos <= a.pf_pos && pos < a.pf_rows && (a.pf_row_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(a.pf_base) & 15) == 0) {
+            const long long lo = (a.pf_window > 0 && pos - a.pf_window + 1 > 0) ? pos - a.pf_window + 1 : 0;
+            const long long span = pos - lo, per_head = (span + 31) >> 5, total = per_head * a.pf_heads;
+            for (long long p = blockIdx.x + (long long)gridDim.x * threadIdx.x; p < total; p += (long long)gridDim.x * blockDim.x) {
+                const long long head = p / per_head, r0 = (p - head * per_head) << 5;
+                const uint32_t bytes = (uint32_t)(min(32LL, span - r0) * a.pf_row_bytes);
+                const char *src = reinterpret_cast<const char *>(a.pf_base) + ((head * a.pf_rows + lo + r0) * a.pf_row_bytes);
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+            }
+        }
+    }
     unsigned long long gmx = 0;
     if (MODE == MODE_FRONT && a.gain)                              // the gain is immutable: staged before the dependency wait
         for (int i = threadIdx.x * 2; i < (int)K; i += blockDim.x * 2) {
