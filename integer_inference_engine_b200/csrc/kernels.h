@@ -83,6 +83,13 @@ struct StreamArgs {
     long long pf_rows, pf_pos, pf_window;
     int pf_heads, pf_row_bytes;
     const int *pf_pos_dev;
+    // optional, MODE_DOWN: one CTA beyond those that own tiles ranks rank_n router logits (largest first, lowest index among
+    // equals), and leaves the rank_k selected indices and their sigmoid gates in rank_ids / rank_gates (and ids_out / gates_out)
+    // for the kernels behind this one.  The logits must be final before the kernel in front of this one started.
+    const int64_t *rank_logits;
+    int rank_n, rank_k;
+    int *rank_ids;
+    int64_t *rank_gates;
     int tiles_b;                   // filled in by the launcher
 };
 cudaError_t launch_stream(int qtype, int mode, const StreamArgs &a, cudaStream_t s);

@@ -129,6 +129,25 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
         }
         __syncthreads();
     };
+    if (MODE == MODE_DOWN && a.rank_logits && my_tiles <= 0) {
+        // the spare CTA: the ranking runs beside the product, on an SM the product leaves idle, instead of in the prologue of
+        // every CTA of the two kernels behind this one
+        const int n = a.rank_n;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) s_lg[i] = a.rank_logits[i];
+        __syncthreads();
+        for (int e = threadIdx.x; e < n; e += blockDim.x) {
+            const int64_t v = s_lg[e];
+            int rank = 0;
+            for (int j = 0; j < n; j++) { const int64_t w = s_lg[j]; rank += (w > v) || (w == v && j < e); }
+            if (rank < a.rank_k) {
+                const long long gt = sigmoid_fixed_c(v, a.fa, a.sig_log2e, a.sig_clip);
+                a.rank_ids[rank] = e; a.rank_gates[rank] = gt;
+                if (a.ids_out) a.ids_out[rank] = e;
+                if (a.gates_out) a.gates_out[rank] = gt;
+            }
+        }
+        return;
+    }
     if (topk && a.pdl && a.early_weights) rank_topk();
     // Programmatic dependent launch: everything above touched only this CTA's shared memory.  When the
     // selected-expert pointers were final before the previous kernel started (early_weights), the weight
@@ -434,7 +453,9 @@ cudaError_t launch_stream_t(const StreamArgs &a_in, cudaStream_t s) {
     if (tpc > max_tpc) tpc = max_tpc;                            // several waves: one CTA per SM (registers), so the longest run that fits
     a.tiles_per_cta = tpc;
     a.sig_log2e = sigmoid_log2e(a.fa); a.sig_clip = sigmoid_clip(a.fa);
-    const unsigned grid = (unsigned)((n_tiles + tpc - 1) / tpc);
+    if (a.rank_logits && (MODE != MODE_DOWN || a.rank_n <= 0 || a.rank_n > SK_MAXE || a.rank_k <= 0 || a.rank_k > a.rank_n || !a.rank_ids || !a.rank_gates))
+        return cudaErrorInvalidValue;
+    const unsigned grid = (unsigned)((n_tiles + tpc - 1) / tpc) + (a.rank_logits ? 1u : 0u);   // + the CTA that only ranks
     const size_t smem = (size_t)tpc * per_tile + 64 + front_bytes;
     static bool configured = false;
     if (!configured) {
