@@ -1638,16 +1638,17 @@ extern "C" int iie_block_dev(long long layer, long long gain_h, long long wqkv_h
     int64_t *gates = gates_dev ? gates_dev : (int64_t *)ensure(R_GATES, (size_t)k * 8);
     if (!ids || !gates) return 1;
     oa.rank_logits = lg; oa.rank_n = E; oa.rank_k = k; oa.rank_ids = ids; oa.rank_gates = gates;
+    oa.rank_tabs = L.tabs; oa.rank_ptrs = g_selptr;          // k <= 64 here: the table holds 3 x 64 pointers
     if (launch_stream(wo.qtype, MODE_DOWN, oa, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     StreamArgs ga = {};
     ga.wa = L.tabs; ga.wb = L.tabs + E; ga.n_sel = k; ga.out_f = L.e_ffn; ga.n_blocks = d / 256; ga.fw = fw; ga.fa = fa;
-    ga.sel = ids;
+    ga.sel = ids; ga.sel_wa = g_selptr; ga.sel_wb = g_selptr + k;
     ga.xl = hl; ga.x_per_sel = 0; ga.x_nl = g_cells; ga.out = nullptr; ga.out_limbs = gul; ga.out_nl = g_cells + 1; ga.flags = g_flags;
     ga.fast = small_scales(L.maxd_gate, L.maxdmin_gate, fw); ga.pdl = g_pdl; ga.early_weights = 0;       // the selection comes from the kernel in front
     if (launch_stream(L.gate_q, MODE_GATEUP, ga, s) != cudaSuccess) { cudaGetLastError(); return 1; }
     StreamArgs da = {};
     da.wa = L.tabs + 2 * E; da.wb = da.wa; da.n_sel = k; da.out_f = d; da.n_blocks = L.e_ffn / 256; da.fw = fw; da.fa = fa;
-    da.sel = ids; da.gates = gates;
+    da.sel = ids; da.gates = gates; da.sel_wa = g_selptr + 2 * k;
     da.xl = gul; da.x_per_sel = 1; da.x_nl = g_cells + 1; da.out = x_dev; da.flags = g_flags;
     da.fast = small_scales(L.maxd_down, L.maxdmin_down, fw); da.pdl = g_pdl; da.early_weights = g_pdl;
     if (launch_stream(L.down_q, MODE_DOWN, da, s) != cudaSuccess) { cudaGetLastError(); return 1; }

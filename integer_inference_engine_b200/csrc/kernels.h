@@ -90,6 +90,10 @@ struct StreamArgs {
     int rank_n, rank_k;
     int *rank_ids;
     int64_t *rank_gates;
+    // optional: rank_tabs = [3][rank_n] matrix pointers (gate, up, down); the selected ones are left in rank_ptrs [3][rank_k], so
+    // that the kernels behind find their weights with one load (their sel_wa / sel_wb)
+    const uint8_t *const *rank_tabs;
+    const uint8_t **rank_ptrs;
     int tiles_b;                   // filled in by the launcher
 };
 cudaError_t launch_stream(int qtype, int mode, const StreamArgs &a, cudaStream_t s);

@@ -142,6 +142,10 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) stream_kernel(const StreamArgs
             if (rank < a.rank_k) {
                 const long long gt = sigmoid_fixed_c(v, a.fa, a.sig_log2e, a.sig_clip);
                 a.rank_ids[rank] = e; a.rank_gates[rank] = gt;
+                if (a.rank_tabs && a.rank_ptrs) {
+#pragma unroll
+                    for (int m = 0; m < 3; m++) a.rank_ptrs[m * a.rank_k + rank] = a.rank_tabs[m * n + e];
+                }
                 if (a.ids_out) a.ids_out[rank] = e;
                 if (a.gates_out) a.gates_out[rank] = gt;
             }
