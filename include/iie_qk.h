@@ -191,8 +191,8 @@ int iie_attn_prefill_dev(const int64_t *q_dev, const int64_t *k_dev, const int64
 /* One whole parallel decoder block for one token: x_dev += attention(h) Wo^T + moe(h), h = rmsnorm(x_dev, gain) (gain_h < 0:
  * h = x_dev), i.e. north-mini-code/src/nmc/cohere2.py:357-383 (block_cached) with Engine._moe (engine.py:375-443) for the
  * expert half.  `layer` is an iie_moe_layer_create handle with a quantised router, wqkv_h the stacked [Wq|Wk|Wv] matrix, the
- * remaining arguments as for iie_attn_block_dev.  Five launches (norm + QKV + router rows, attention, O, gate/up, down; the
- * last two rank the router logits themselves) against the six of iie_moe_block_dev + iie_attn_block_dev, same bytes.
+ * remaining arguments as for iie_attn_block_dev.  Five launches (norm + QKV + router rows, attention, O, gate/up, down; a
+ * spare CTA of the O launch ranks the router logits for the last two) against the six of iie_moe_block_dev + iie_attn_block_dev, same bytes.
  * ids_dev / gates_dev (nullable): the selected experts and their gates.  0 ok, 1 bad argument or CUDA failure, 3 a block
  * scale outside the exact envelope, 5 no fused form for this shape (use the two entries). */
 int iie_block_dev(long long layer, long long gain_h, long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t *kcache_dev,

@@ -1574,10 +1574,12 @@ extern "C" int iie_attn_block_dev(long long wqkv_h, long long wo_h, int64_t *x_d
 //   front     every CTA normalises x and takes its share of the rows of [Wq|Wk|Wv] and of the router (one kernel
 //             instead of the routing kernel followed by the fused QKV product);
 //   attention cooperative single-token attention (K/V append, scores, softmax, p.V);
-//   O         product accumulated into x;
-//   gate/up   every CTA ranks the router logits itself (top-k, sigmoid gates), so its expert weights are requested before
-//             the O product has finished;
-//   down      the same ranking, weights requested early, gate-weighted rows accumulated into x.
+//   O         product accumulated into x; one more CTA of the same launch ranks the router logits (top-k, lowest index
+//             among equals, sigmoid gates) on an SM the product leaves idle and leaves indices, gates and the selected
+//             matrices' pointers for the two kernels behind it;
+//   gate/up   expert gate and up products of the selected experts, SiLU, digit planes of the result;
+//   down      weights requested before its dependency wait (the selection is final a launch earlier), gate-weighted rows
+//             accumulated into x.
 // Same bytes as iie_moe_block_dev followed by iie_attn_block_dev.  Status 5: this shape has no fused form (dense router,
 // router and Wqkv of different block formats, more than 64 selected experts) and the two entries must be used.
 extern "C" int iie_block_dev(long long layer, long long gain_h, long long wqkv_h, long long wo_h, int64_t *x_dev, int32_t *kcache_dev,
