@@ -5,12 +5,12 @@
 
 namespace iie {
 
-__device__ __forceinline__ unsigned long long uabs64(int64_t v) { return v < 0 ? (0ULL - (unsigned long long)v) : (unsigned long long)v; }
+__host__ __device__ __forceinline__ unsigned long long uabs64(int64_t v) { return v < 0 ? (0ULL - (unsigned long long)v) : (unsigned long long)v; }
 
 // floor(sqrt(v)).  Below 2^104 the root is under 2^52, so the double estimate is within a unit or two of it and the
 // residual v - r^2 (under 2^55 in size) is exact in the low 64 bits: the fix-up walks r by the residual in 64-bit words
 // (the usual case: the mean square of a residual row is far below that bound); beyond it the bitwise root.
-__device__ inline u128 isqrt128(u128 v) {
+__host__ __device__ inline u128 isqrt128(u128 v) {
     if (v < ((u128)1 << 104)) {
         const double dv = (double)(unsigned long long)(v >> 64) * 18446744073709551616.0 + (double)(unsigned long long)v;
         unsigned long long r = (unsigned long long)sqrt(dv);
@@ -31,18 +31,27 @@ __device__ inline u128 isqrt128(u128 v) {
 // A reciprocal for floor_div_recip: any value from a few units below floor((2^64 - 1) / den) up to it serves (the
 // quotient estimate only starts lower and the correction loop takes an extra step).  In the middle range a double
 // quotient minus its error bound replaces the 64-bit division.
-__device__ __forceinline__ unsigned long long recip_below(unsigned long long den) {
+__host__ __device__ __forceinline__ unsigned long long recip_below(unsigned long long den) {
     if (den == 0) return 0;
     if (den >= (1ULL << 13) && den < (1ULL << 60))             // 2^64/den <= 2^51: the double quotient is within 1 of it
         return (unsigned long long)(18446744073709551616.0 / (double)den) - 4;
     return 0xFFFFFFFFFFFFFFFFULL / den;
 }
 
+// high half of a 64 x 64-bit product (the host form lets tests/host_norm_check.cu run these helpers on the CPU)
+__host__ __device__ __forceinline__ unsigned long long mulhi64(unsigned long long a, unsigned long long b) {
+#ifdef __CUDA_ARCH__
+    return __umul64hi(a, b);
+#else
+    return (unsigned long long)(((u128)a * b) >> 64);
+#endif
+}
+
 // floor(num / den) for |num| < 2^62 and 0 < den < 2^62 through a precomputed reciprocal
 // inv <= floor((2^64 - 1) / den) and within a few units of it: the estimate is a few units below the quotient at most.
-__device__ __forceinline__ int64_t floor_div_recip(int64_t num, unsigned long long den, unsigned long long inv) {
+__host__ __device__ __forceinline__ int64_t floor_div_recip(int64_t num, unsigned long long den, unsigned long long inv) {
     const unsigned long long n = uabs64(num);
-    unsigned long long q = __umul64hi(n, inv), r = n - q * den;
+    unsigned long long q = mulhi64(n, inv), r = n - q * den;
     while (r >= den) { q++; r -= den; }
     return num >= 0 ? (int64_t)q : -(int64_t)q - (r != 0);
 }
