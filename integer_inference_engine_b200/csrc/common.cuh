@@ -49,7 +49,7 @@ __device__ __forceinline__ int half_to_fixed_small(uint32_t h, int frac) {
 }
 
 // ---- integer sigmoid / SiLU (north-mini-code/src/nmc/_bonsai/fixedpoint.py:74-96,136-163) ----------
-__device__ __forceinline__ int64_t exp2_neg_fixed(int64_t u, int fa) {
+__host__ __device__ __forceinline__ int64_t exp2_neg_fixed(int64_t u, int fa) {
     const int s = 16 - fa;
     uint32_t c0 = 65536, c1 = 45426, c2 = 15743, c3 = 3638;          // all operands below stay under 2^32 for fa <= 29
     if (s >= 0) { c0 >>= s; c1 >>= s; c2 >>= s; c3 >>= s; } else { c0 <<= -s; c1 <<= -s; c2 <<= -s; c3 <<= -s; }
@@ -77,11 +77,22 @@ __host__ __device__ inline int64_t sigmoid_clip(int fa) { return (((int64_t)(fa 
 
 // floor(num / z) for 0 <= num < 2^60, 0 < z < 2^31 with a quotient below 2^31: two single-precision estimates (the
 // second one of the remainder) and an exact fix-up; no double-precision division.
-__device__ __forceinline__ uint64_t udiv_small_q31(uint64_t num, uint32_t z) {
+// (The host forms of the three conversions let tests/host_fixed_check.cu run the same function on the CPU; the fix-up makes
+// the result independent of how the estimates round.)
+__host__ __device__ __forceinline__ uint64_t udiv_small_q31(uint64_t num, uint32_t z) {
+#ifdef __CUDA_ARCH__
     const float rz = __frcp_rn((float)z);
     uint32_t q = __float2uint_rz((float)(uint32_t)(num >> 29) * rz * 536870912.0f);            // within 2^-21 relative
+#else
+    const float rz = 1.0f / (float)z;
+    uint32_t q = (uint32_t)((float)(uint32_t)(num >> 29) * rz * 536870912.0f);
+#endif
     int64_t r = (int64_t)(num - (uint64_t)q * z);                                               // |r| < 2^41
+#ifdef __CUDA_ARCH__
     const int q2 = __float2int_rn((float)(int)(r >> 10) * rz * 1024.0f);
+#else
+    const int q2 = (int)((float)(int)(r >> 10) * rz * 1024.0f + ((r >> 10) >= 0 ? 0.5f : -0.5f));
+#endif
     q += q2; r -= (int64_t)q2 * z;
     while (r < 0) { q--; r += z; }
     while (r >= (int64_t)z) { q++; r -= z; }
@@ -91,7 +102,7 @@ __device__ __forceinline__ uint64_t udiv_small_q31(uint64_t num, uint32_t z) {
 // sigmoid(x) = e1 / (e0 + e1) with e0 = 2^-(max(x,0) log2 e), e1 = 2^-((max(x,0) - x) log2 e), both clipped in the
 // exponent (fixedpoint.py:136-163).  One of the two exponents is always zero and its power exactly 2^fa, so only the
 // other power is evaluated; x = INT64_MIN wraps exactly as the NumPy oracle's int64 arithmetic does.
-__device__ __forceinline__ int64_t sigmoid_fixed_c(int64_t x, int fa, int64_t log2e, int64_t clip) {
+__host__ __device__ __forceinline__ int64_t sigmoid_fixed_c(int64_t x, int fa, int64_t log2e, int64_t clip) {
     const bool neg = x < 0;
     int64_t d = neg ? (int64_t)(0ULL - (uint64_t)x) : x;
     if (d > clip) d = clip;
@@ -100,20 +111,20 @@ __device__ __forceinline__ int64_t sigmoid_fixed_c(int64_t x, int fa, int64_t lo
     return (int64_t)udiv_small_q31((uint64_t)(neg ? es : one) << fa, (uint32_t)(es + one));   // fa <= 29: es + one <= 2^30
 }
 
-__device__ __forceinline__ int64_t sigmoid_fixed(int64_t x, int fa) {
+__host__ __device__ __forceinline__ int64_t sigmoid_fixed(int64_t x, int fa) {
     return sigmoid_fixed_c(x, fa, sigmoid_log2e(fa), sigmoid_clip(fa));
 }
 
-__device__ __forceinline__ int64_t mul_shift(int64_t a, int64_t b, int sh) {
+__host__ __device__ __forceinline__ int64_t mul_shift(int64_t a, int64_t b, int sh) {
     return (int64_t)(((i128)a * (i128)b) >> sh);
 }
 
-__device__ __forceinline__ int64_t silu_fixed(int64_t x, int fa) { return mul_shift(x, sigmoid_fixed(x, fa), fa); }
+__host__ __device__ __forceinline__ int64_t silu_fixed(int64_t x, int fa) { return mul_shift(x, sigmoid_fixed(x, fa), fa); }
 
 // ---- balanced base-256 digits: x = sum_l d_l * 256^l, d_l in [-128,127] --------------------------------
 // Eight digits cover |x| <= 127*(2^64-1)/255; `ok` is cleared when a ninth digit would be needed
 // (capacity rule of north-mini-code/src/nmc/qk_cuda.py:973-992).
-__device__ __forceinline__ uint64_t balanced_digits8(int64_t x, bool &ok) {
+__host__ __device__ __forceinline__ uint64_t balanced_digits8(int64_t x, bool &ok) {
     // with u_l = d_l + 128 in [0, 255]: x + 0x80..80 = sum_l u_l 256^l, so the digits are the bytes of that sum with the
     // top bit flipped.  Every negative int64 has eight digits (the smallest eight-digit number is below INT64_MIN); a
     // positive one does while the sum stays below 2^64.
